@@ -1,0 +1,198 @@
+"""CUDA kernels against the pure-PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+import transformerengine_b200 as te
+from transformerengine_b200 import ops
+from transformerengine_b200.ops import quantize as qz
+from transformerengine_b200.ops.ref import quant as Q
+from transformerengine_b200.tensor import MXFP8Quantizer, Float8Quantizer, Float8CurrentScalingQuantizer
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 520, 264), (1024, 1024, 4096), (64, 96, 32)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gemm_16bit(M, N, K, dtype):
+    a = torch.randn(M, K, device=DEV, dtype=dtype)
+    b = torch.randn(N, K, device=DEV, dtype=dtype)
+    ref = a.float() @ b.float().t()
+    out = ops.gemm_nt(a, b, out_dtype=dtype)
+    te.check_status()
+    assert _rel(out, ref) < 1e-2
+    out32 = ops.gemm_nt(a, b, out_dtype=torch.float32)
+    assert _rel(out32, ref) < 1e-5 * K ** 0.5 + 1e-4
+
+
+def test_gemm_16bit_bias_accumulate():
+    M, N, K = 384, 640, 512
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t() + bias.float()
+    out = ops.gemm_nt(a, b, out_dtype=torch.float32, bias=bias)
+    assert _rel(out, ref) < 1e-3
+    acc = torch.randn(M, N, device=DEV, dtype=torch.float32)
+    ref2 = acc + a.float() @ b.float().t()
+    ops.gemm_nt(a, b, out=acc, accumulate=True)
+    te.check_status()
+    assert _rel(acc, ref2) < 1e-3
+
+
+def test_gemm_16bit_gelu_epilogues():
+    M, N, K = 256, 256, 128
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16) * 0.2
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.2
+    pre = a.float() @ b.float().t()
+    aux = torch.empty(M, N, device=DEV, dtype=torch.float32)
+    out = ops.gemm_nt(a, b, out_dtype=torch.float32, epilogue=ops.gemm.EPI_GELU, aux=aux)
+    assert _rel(aux, pre) < 1e-3
+    assert _rel(out, torch.nn.functional.gelu(pre, approximate="tanh")) < 1e-3
+
+
+def test_gemm_mn_major_operands():
+    M, N, K = 256, 384, 320
+    at = torch.randn(K, M, device=DEV, dtype=torch.bfloat16)  # A stored transposed
+    bt = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    ref = at.float().t() @ bt.float()
+    ops.set_mn_major_operands(True)
+    try:
+        out = ops.gemm_nt(ops.as_operand(at, "columnwise"), ops.as_operand(bt, "columnwise"), out_dtype=torch.float32)
+        te.check_status()
+    finally:
+        ops.set_mn_major_operands(False)
+    assert _rel(out, ref) < 1e-3
+
+
+@pytest.mark.parametrize("R,C", [(128, 128), (256, 384), (160, 96), (1024, 4096)])
+@pytest.mark.parametrize("fp8", [torch.float8_e4m3fn, torch.float8_e5m2])
+def test_quantize_mxfp8_bit_exact(R, C, fp8):
+    x = (torch.randn(R, C, device=DEV) * torch.exp(torch.randn(R, 1, device=DEV) * 2)).to(torch.bfloat16)
+    rd, rs, cd, cs = qz.quantize_mxfp8(x, fp8)
+    rd_r, rs_r, cd_r, cs_r = qz.quantize_mxfp8(x.cpu(), fp8)
+    assert torch.equal(rd.cpu(), rd_r)
+    assert torch.equal(cd.cpu(), cd_r)
+    assert torch.equal(qz.unswizzle_scales(rs, R, C // 32).cpu(), Q.unswizzle_scales(rs_r, R, C // 32))
+    assert torch.equal(qz.unswizzle_scales(cs, C, R // 32).cpu(), Q.unswizzle_scales(cs_r, C, R // 32))
+    deq = qz.dequantize_mxfp8(rd, rs, fp8, torch.float32)
+    deq_r = qz.dequantize_mxfp8(rd_r, rs_r, fp8, torch.float32)
+    assert torch.equal(deq.cpu(), deq_r)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (384, 128, 256), (1024, 2048, 4096), (160, 96, 64)])
+def test_gemm_mxfp8(M, N, K):
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    qa = MXFP8Quantizer(torch.float8_e4m3fn, columnwise=False)(a)
+    qb = MXFP8Quantizer(torch.float8_e4m3fn, columnwise=False)(b)
+    ref = qa.dequantize(dtype=torch.float32) @ qb.dequantize(dtype=torch.float32).t()
+    out = ops.gemm_nt(ops.as_operand(qa), ops.as_operand(qb), out_dtype=torch.float32)
+    te.check_status()
+    assert _rel(out, ref) < 1e-4
+    # columnwise (transposed) copies give the transposed-operand product
+    qa2 = MXFP8Quantizer(torch.float8_e5m2)(a)
+    ref2 = qa2.dequantize(dtype=torch.float32)
+    got2 = qz.dequantize_mxfp8(qa2._columnwise_data, qa2._columnwise_scale_inv, torch.float8_e5m2, torch.float32)
+    assert _rel(got2.t(), a.float()) < 0.1 and ref2.shape == a.shape
+
+
+def test_quantize_fp8_tensor():
+    x = torch.randn(256, 512, device=DEV, dtype=torch.bfloat16)
+    scale = torch.full((1,), 3.0, device=DEV)
+    amax = torch.zeros(1, device=DEV)
+    q = Float8Quantizer(scale, amax, torch.float8_e4m3fn)(x)
+    ref = Q.quantize_fp8_tensor(x.cpu(), torch.tensor([3.0]), torch.float8_e4m3fn)
+    assert torch.equal(q._data.cpu(), ref.view(torch.uint8))
+    assert torch.equal(q._transpose.cpu(), ref.t().contiguous().view(torch.uint8))
+    assert abs(amax.item() - x.abs().max().item()) < 1e-6
+    qc = Float8CurrentScalingQuantizer(torch.float8_e4m3fn, device=DEV)(x)
+    assert _rel(qc.dequantize(dtype=torch.float32), x) < 0.05
+
+
+@pytest.mark.parametrize("layernorm", [False, True])
+@pytest.mark.parametrize("zc", [False, True])
+def test_norm_fwd_bwd(layernorm, zc):
+    R, C = 512, 1024
+    x = torch.randn(R, C, device=DEV, dtype=torch.bfloat16)
+    g = (torch.randn(C, device=DEV) * 0.1 + (0 if zc else 1)).to(torch.bfloat16)
+    b = torch.randn(C, device=DEV).to(torch.bfloat16) if layernorm else None
+    y, _, mu, rs = ops.norm_fwd(x, g, b, 1e-5, zc, layernorm)
+    yr, mur, rsr = ops.norm.norm_fwd_ref(x, g, b, 1e-5, zc, layernorm)
+    assert _rel(y, yr) < 5e-3 and _rel(rs, rsr) < 1e-5
+    dy = torch.randn(R, C, device=DEV, dtype=torch.bfloat16)
+    dx, dg, db = ops.norm_bwd(dy, x, mu, rs, g, zc, layernorm)
+    dxr, dgr, dbr = ops.norm.norm_bwd_ref(dy, x, mur, rsr, g, zc, layernorm)
+    assert _rel(dx, dxr) < 5e-3 and _rel(dg, dgr) < 1e-2
+    if layernorm:
+        assert _rel(db, dbr) < 1e-2
+    # fused MXFP8 output equals quantizing the 16-bit output
+    quant = MXFP8Quantizer()
+    _, yq, _, _ = ops.norm_fwd(x, g, b, 1e-5, zc, layernorm, quantizer=quant, want_hp=False)
+    y2 = quant(y)
+    assert torch.equal(yq._rowwise_data, y2._rowwise_data) or _rel(yq.dequantize(), y2.dequantize()) < 2e-2
+
+
+@pytest.mark.parametrize("name", ["gelu", "silu", "relu", "swiglu", "geglu", "qgelu", "srelu"])
+def test_activation(name):
+    R, C = 256, 512
+    x = torch.randn(R, C, device=DEV, dtype=torch.bfloat16)
+    y, _ = ops.activation_fwd(x, name)
+    yr = ops.activation.activation_fwd_ref(x, name)
+    assert _rel(y, yr) < 5e-3
+    dy = torch.randn_like(y)
+    dx, _, _ = ops.activation_bwd(dy, x, name)
+    dxr = ops.activation.activation_bwd_ref(dy, x, name)
+    assert _rel(dx, dxr) < 5e-3
+    quant = MXFP8Quantizer()
+    _, yq = ops.activation_fwd(x, name, quantizer=quant, want_hp=False)
+    assert _rel(yq.dequantize(dtype=torch.float32), yr) < 0.05
+
+
+def test_multi_tensor_adam_matches_torch():
+    ps = [torch.randn(n, device=DEV) for n in (1000, 70000, 3, 1 << 20)]
+    gs = [torch.randn_like(p) for p in ps]
+    ref_p = [p.clone().requires_grad_(True) for p in ps]
+    opt = torch.optim.AdamW(ref_p, lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    master = [p.clone() for p in ps]
+    model = [p.to(torch.bfloat16) for p in ps]
+    m = [torch.zeros_like(p) for p in ps]
+    v = [torch.zeros_like(p) for p in ps]
+    for step in (1, 2, 3):
+        for rp, g in zip(ref_p, gs):
+            rp.grad = g.clone()
+        opt.step()
+        ops.multi_tensor_adam([[g.to(torch.bfloat16).float() for g in gs] if False else gs, model, m, v, master], 1e-2, 0.9, 0.95,
+                              1e-8, step, True, True, 0.1)
+    for rp, mp, bp in zip(ref_p, master, model):
+        assert _rel(mp, rp) < 1e-5
+        assert _rel(bp, rp) < 1e-2
+
+
+def test_cross_entropy():
+    R, V = 64, 32000
+    logits = torch.randn(R, V, device=DEV, dtype=torch.bfloat16)
+    tgt = torch.randint(0, V, (R,), device=DEV)
+    tgt[3] = -100
+    ref = logits.float().clone().requires_grad_(True)
+    lref = torch.nn.functional.cross_entropy(ref, tgt, reduction="none", ignore_index=-100)
+    lref.sum().backward()
+    loss, grad = ops.cross_entropy_fwd_bwd(logits.clone(), tgt, 1.0, inplace_grad=False)
+    assert _rel(loss, lref) < 1e-4
+    assert _rel(grad, ref.grad) < 2e-2
+
+
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope(interleaved):
+    s, b, h, d = 128, 2, 4, 64
+    x = torch.randn(s, b, h, d, device=DEV, dtype=torch.bfloat16)
+    f = ops.rope_freqs(torch.arange(s, device=DEV), d, 10000.0, interleaved)
+    y = ops.rope_apply(x, f, interleaved=interleaved)
+    yr = ops.misc.rope_ref(x, f, d, interleaved)
+    assert _rel(y, yr) < 1e-2
+    g = ops.rope_apply(y, f, interleaved=interleaved, backward=True)
+    assert _rel(g, x) < 2e-2  # the rotation is orthogonal: backward undoes forward

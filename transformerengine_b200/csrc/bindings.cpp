@@ -1,0 +1,405 @@
+// Python bindings: thin glue from at::Tensor to the raw-pointer launchers.
+// Output tensors are allocated by the Python callers; nothing here allocates
+// except the per-device status word.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <teb200/api.h>
+#include <teb200/misc.h>
+#include <teb200/norm.h>
+#include <teb200/quant.h>
+#include <torch/extension.h>
+
+#include <optional>
+#include <vector>
+
+namespace py = pybind11;
+using teb200::DType;
+using OptT = std::optional<at::Tensor>;
+
+namespace {
+
+int to_dtype(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return teb200::kFloat32;
+    case at::kHalf: return teb200::kFloat16;
+    case at::kBFloat16: return teb200::kBFloat16;
+    case at::kByte: return teb200::kByte;
+    case at::kFloat8_e4m3fn: return teb200::kFloat8E4M3;
+    case at::kFloat8_e5m2: return teb200::kFloat8E5M2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+  }
+}
+template <typename T = void>
+T* ptr(const OptT& t) {
+  return t.has_value() && t->defined() ? static_cast<T*>(t->data_ptr()) : nullptr;
+}
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+void check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, " failed: ", cudaGetErrorString(e));
+}
+
+// One int per device; kernels write a Status code there when a bounded wait expires.
+at::Tensor& status_tensor(int device) {
+  static std::vector<at::Tensor> st(64);
+  if (!st[device].defined())
+    st[device] = at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+  return st[device];
+}
+
+at::Tensor status(int device) { return status_tensor(device); }
+
+// kind: 0 = 16-bit, 1 = mxfp8, 2 = nvfp4.  a [M,K] (or [K,M] when a_mn), b [N,K] (or [K,N]); d [M,N].
+void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const OptT& sfa, const OptT& sfb,
+          const OptT& bias, const OptT& aux, int epilogue, bool accumulate, bool a_e5m2, bool b_e5m2, bool a_mn,
+          bool b_mn, double alpha, const OptT& alpha_dev, const OptT& group_offsets, int num_groups, int sm_count,
+          int64_t K_override) {
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "gemm operands must be 2-D");
+  TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm operands must be row-major");
+  teb200::GemmArgs g;
+  g.a = a.data_ptr();
+  g.b = b.data_ptr();
+  g.d = d.data_ptr();
+  g.M = static_cast<int>(d.size(0));
+  g.N = static_cast<int>(d.size(1));
+  if (kind == 0) {
+    g.K = static_cast<int>(a_mn ? a.size(0) : a.size(1));
+    g.a_dtype = to_dtype(a);
+    g.b_dtype = to_dtype(b);
+    TORCH_CHECK(g.a_dtype == g.b_dtype && (g.a_dtype == teb200::kBFloat16 || g.a_dtype == teb200::kFloat16),
+                "16-bit gemm needs matching bf16/fp16 operands");
+    g.lda = a.stride(0);
+    g.ldb = b.stride(0);
+  } else if (kind == 1) {
+    g.K = static_cast<int>(a.size(1));
+    g.a_dtype = a_e5m2 ? teb200::kFloat8E5M2 : teb200::kFloat8E4M3;
+    g.b_dtype = b_e5m2 ? teb200::kFloat8E5M2 : teb200::kFloat8E4M3;
+    g.lda = a.stride(0);
+    g.ldb = b.stride(0);
+  } else {
+    g.K = static_cast<int>(a.size(1)) * 2;
+    g.lda = a.stride(0) * 2;
+    g.ldb = b.stride(0) * 2;
+  }
+  if (K_override > 0) g.K = static_cast<int>(K_override);
+  if (num_groups > 0) g.N = static_cast<int>(b.size(a_mn || b_mn ? 1 : 0)) / num_groups;
+  g.ldd = d.stride(0);
+  g.d_dtype = to_dtype(d);
+  g.sfa = ptr<uint8_t>(sfa);
+  g.sfb = ptr<uint8_t>(sfb);
+  if (bias.has_value() && bias->defined()) {
+    g.bias = bias->data_ptr();
+    g.bias_dtype = to_dtype(*bias);
+  }
+  g.aux = ptr<void>(aux);
+  g.epilogue = epilogue;
+  g.accumulate = accumulate;
+  g.a_mn_major = a_mn;
+  g.b_mn_major = b_mn;
+  g.alpha = static_cast<float>(alpha);
+  g.alpha_dev = ptr<float>(alpha_dev);
+  g.num_groups = num_groups;
+  g.group_offsets = ptr<int32_t>(group_offsets);
+  g.sm_count = sm_count;
+  g.status = status_tensor(a.get_device()).data_ptr<int>();
+  cudaError_t e = kind == 0 ? teb200::gemm_bf16(g, stream())
+                            : (kind == 1 ? teb200::gemm_mxfp8(g, stream()) : teb200::gemm_nvfp4(g, stream()));
+  check(e, "gemm");
+}
+
+// mode: 0 = mxfp8, 1 = per-tensor fp8, 2 = no quantization (produce y only)
+void quantize(int mode, int prologue, int act, const at::Tensor& x, const OptT& dy, int64_t R, int64_t C,
+              const OptT& y, const OptT& row_data, const OptT& row_scale, const OptT& col_data, const OptT& col_scale,
+              bool e5m2, const OptT& mu, const OptT& rs, const OptT& gamma, const OptT& beta, bool zero_centered,
+              const OptT& row_mul, const OptT& scale, const OptT& amax, const OptT& scale_inv, const OptT& dbias) {
+  c10::cuda::CUDAGuard guard(x.device());
+  teb200::QuantArgs q;
+  q.x = x.data_ptr();
+  q.x_dtype = to_dtype(x);
+  q.ldx = x.dim() >= 2 ? x.stride(-2) : x.size(-1);
+  q.dy = ptr<void>(dy);
+  q.mu = ptr<float>(mu);
+  q.rs = ptr<float>(rs);
+  if (gamma.has_value() && gamma->defined()) {
+    q.gamma = gamma->data_ptr();
+    q.gamma_dtype = to_dtype(*gamma);
+  }
+  q.beta = ptr<void>(beta);
+  q.zero_centered = zero_centered;
+  q.row_scale = ptr<float>(row_mul);
+  q.prologue = prologue;
+  q.act = act;
+  q.R = static_cast<int>(R);
+  q.C = static_cast<int>(C);
+  if (y.has_value() && y->defined()) {
+    q.y = y->data_ptr();
+    q.y_dtype = to_dtype(*y);
+  }
+  q.row_data = ptr<uint8_t>(row_data);
+  q.row_scale_out = ptr<uint8_t>(row_scale);
+  q.col_data = ptr<uint8_t>(col_data);
+  q.col_scale_out = ptr<uint8_t>(col_scale);
+  q.fp8_e5m2 = e5m2;
+  q.scale = ptr<float>(scale);
+  q.amax = ptr<float>(amax);
+  q.scale_inv = ptr<float>(scale_inv);
+  q.dbias = ptr<float>(dbias);
+  cudaError_t e = mode == 0 ? teb200::quantize_mxfp8(q, stream())
+                            : (mode == 1 ? teb200::quantize_fp8_tensor(q, stream()) : teb200::apply_prologue(q, stream()));
+  check(e, "quantize");
+}
+
+void dequantize_mxfp8(const at::Tensor& q, const at::Tensor& sf, int64_t R, int64_t C, bool e5m2, at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check(teb200::dequantize_mxfp8(static_cast<const uint8_t*>(q.data_ptr()), static_cast<const uint8_t*>(sf.data_ptr()),
+                                 static_cast<int>(R), static_cast<int>(C), e5m2, out.data_ptr(), to_dtype(out), stream()),
+        "dequantize_mxfp8");
+}
+void dequantize_fp8(const at::Tensor& q, const at::Tensor& scale_inv, bool e5m2, at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  check(teb200::dequantize_fp8_tensor(static_cast<const uint8_t*>(q.data_ptr()), scale_inv.data_ptr<float>(), q.numel(),
+                                      e5m2, out.data_ptr(), to_dtype(out), stream()),
+        "dequantize_fp8");
+}
+void amax(const at::Tensor& x, at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check(teb200::amax_abs(x.data_ptr(), to_dtype(x), x.numel(), out.data_ptr<float>(), stream()), "amax");
+}
+void swizzle(const at::Tensor& in, int64_t rows, int64_t cols, at::Tensor& out, bool to_swizzled) {
+  c10::cuda::CUDAGuard guard(in.device());
+  auto* i = static_cast<const uint8_t*>(in.data_ptr());
+  auto* o = static_cast<uint8_t*>(out.data_ptr());
+  check(to_swizzled ? teb200::swizzle_scales(i, rows, cols, o, stream()) : teb200::unswizzle_scales(i, rows, cols, o, stream()),
+        "swizzle");
+}
+
+void norm_fwd(bool layernorm, const at::Tensor& x, const at::Tensor& gamma, const OptT& beta, const OptT& y,
+              const OptT& mu, at::Tensor& rs, double eps, bool zero_centered) {
+  c10::cuda::CUDAGuard guard(x.device());
+  teb200::NormArgs n;
+  n.layernorm = layernorm;
+  n.C = static_cast<int>(x.size(-1));
+  n.R = static_cast<int>(x.numel() / x.size(-1));
+  n.x_dtype = to_dtype(x);
+  n.w_dtype = to_dtype(gamma);
+  n.eps = static_cast<float>(eps);
+  n.zero_centered = zero_centered;
+  n.x = x.data_ptr();
+  n.gamma = gamma.data_ptr();
+  n.beta = ptr<void>(beta);
+  n.y = ptr<void>(y);
+  n.mu = ptr<float>(mu);
+  n.rs = rs.data_ptr<float>();
+  check(teb200::norm_fwd(n, stream()), "norm_fwd");
+}
+int64_t norm_bwd_workspace(int64_t R, int64_t C) { return static_cast<int64_t>(teb200::norm_bwd_parts(R)) * 2 * C; }
+void norm_bwd(bool layernorm, const at::Tensor& dy, const at::Tensor& x, const OptT& mu, const at::Tensor& rs,
+              const at::Tensor& gamma, const OptT& add, at::Tensor& dx, at::Tensor& dgamma, const OptT& dbeta,
+              at::Tensor& workspace, bool zero_centered) {
+  c10::cuda::CUDAGuard guard(x.device());
+  teb200::NormArgs n;
+  n.layernorm = layernorm;
+  n.C = static_cast<int>(x.size(-1));
+  n.R = static_cast<int>(x.numel() / x.size(-1));
+  n.x_dtype = to_dtype(x);
+  n.w_dtype = to_dtype(gamma);
+  n.zero_centered = zero_centered;
+  n.x = x.data_ptr();
+  n.dy = dy.data_ptr();
+  n.gamma = gamma.data_ptr();
+  n.mu = ptr<float>(mu);
+  n.rs = rs.data_ptr<float>();
+  n.add = ptr<void>(add);
+  n.dx = dx.data_ptr();
+  n.dgamma = dgamma.data_ptr();
+  n.dbeta = ptr<void>(dbeta);
+  n.workspace = workspace.data_ptr<float>();
+  TORCH_CHECK(workspace.numel() >= norm_bwd_workspace(n.R, n.C), "norm_bwd workspace too small");
+  check(teb200::norm_bwd(n, stream()), "norm_bwd");
+}
+
+// lists[k][i]: tensor i of list k.  Splits into launches of <= kMtMaxTensors tensors / kMtMaxBlocks blocks.
+template <typename Launch>
+void multi_tensor_apply(const std::vector<std::vector<at::Tensor>>& lists, int64_t chunk, Launch&& launch) {
+  const size_t nt = lists[0].size();
+  teb200::MultiTensorTable tab;
+  int nten = 0, nblk = 0, base = 0;
+  for (size_t i = 0; i < nt; ++i) {
+    const int64_t n = lists[0][i].numel();
+    if (n == 0) continue;
+    for (size_t k = 0; k < lists.size(); ++k) tab.ptr[k][nten] = lists[k][i].data_ptr();
+    tab.numel[nten] = n;
+    const int64_t nchunks = (n + chunk - 1) / chunk;
+    ++nten;
+    for (int64_t c = 0; c < nchunks; ++c) {
+      tab.block_tensor[nblk] = static_cast<uint8_t>(nten - 1);
+      tab.block_chunk[nblk] = static_cast<int32_t>(c);
+      ++nblk;
+      const bool last_chunk = c == nchunks - 1;
+      const bool tensors_full = nten == teb200::kMtMaxTensors && last_chunk;
+      const bool blocks_full = nblk == teb200::kMtMaxBlocks;
+      const bool final_item = i == nt - 1 && last_chunk;
+      if (tensors_full || blocks_full || final_item) {
+        launch(tab, nblk, base);
+        nblk = 0;
+        if (last_chunk) {
+          base += nten;
+          nten = 0;
+        } else {
+          // carry the unfinished tensor over as slot 0 of the next table
+          for (size_t k = 0; k < lists.size(); ++k) tab.ptr[k][0] = tab.ptr[k][nten - 1];
+          tab.numel[0] = tab.numel[nten - 1];
+          base += nten - 1;
+          nten = 1;
+        }
+      }
+    }
+  }
+  if (nblk > 0) launch(tab, nblk, base);
+}
+
+void multi_tensor_adam(std::vector<std::vector<at::Tensor>> lists, double lr, double beta1, double beta2, double eps,
+                       int64_t step, bool adamw, bool bias_correction, double weight_decay, double grad_scale,
+                       const OptT& inv_scale, const OptT& noop, int64_t chunk) {
+  TORCH_CHECK(lists.size() == 4 || lists.size() == 5, "adam expects [g, p, m, v] or [g, p, m, v, master]");
+  if (lists[0].empty()) return;
+  c10::cuda::CUDAGuard guard(lists[0][0].device());
+  teb200::AdamArgs a;
+  a.lr = static_cast<float>(lr);
+  a.beta1 = static_cast<float>(beta1);
+  a.beta2 = static_cast<float>(beta2);
+  a.eps = static_cast<float>(eps);
+  a.weight_decay = static_cast<float>(weight_decay);
+  a.bias_correction1 = bias_correction ? static_cast<float>(1.0 - std::pow(beta1, static_cast<double>(step))) : 1.f;
+  a.bias_correction2 = bias_correction ? static_cast<float>(1.0 - std::pow(beta2, static_cast<double>(step))) : 1.f;
+  a.adamw = adamw;
+  a.grad_dtype = to_dtype(lists[0][0]);
+  a.param_dtype = to_dtype(lists[1][0]);
+  a.state_dtype = to_dtype(lists[2][0]);
+  a.has_master = lists.size() == 5;
+  a.grad_scale = static_cast<float>(grad_scale);
+  a.inv_scale_dev = ptr<float>(inv_scale);
+  a.noop = ptr<int>(noop);
+  a.chunk = chunk;
+  auto s = stream();
+  multi_tensor_apply(lists, chunk, [&](const teb200::MultiTensorTable& t, int nblk, int) {
+    check(teb200::multi_tensor_adam(t, nblk, a, s), "multi_tensor_adam");
+  });
+}
+
+void multi_tensor_sgd(std::vector<std::vector<at::Tensor>> lists, double lr, double momentum, double dampening,
+                      double weight_decay, bool nesterov, bool first_run, bool wd_after_momentum, double grad_scale,
+                      const OptT& noop, int64_t chunk) {
+  if (lists[0].empty()) return;
+  c10::cuda::CUDAGuard guard(lists[0][0].device());
+  teb200::SgdArgs a;
+  a.lr = lr; a.momentum = momentum; a.dampening = dampening; a.weight_decay = weight_decay;
+  a.nesterov = nesterov; a.first_run = first_run; a.wd_after_momentum = wd_after_momentum;
+  a.grad_scale = grad_scale;
+  a.grad_dtype = to_dtype(lists[0][0]);
+  a.param_dtype = to_dtype(lists[1][0]);
+  a.has_master = lists.size() == 4;
+  a.noop = ptr<int>(noop);
+  a.chunk = chunk;
+  auto s = stream();
+  multi_tensor_apply(lists, chunk, [&](const teb200::MultiTensorTable& t, int nblk, int) {
+    check(teb200::multi_tensor_sgd(t, nblk, a, s), "multi_tensor_sgd");
+  });
+}
+
+void multi_tensor_scale(std::vector<std::vector<at::Tensor>> lists, double scale, const OptT& noop, int64_t chunk) {
+  if (lists[0].empty()) return;
+  c10::cuda::CUDAGuard guard(lists[0][0].device());
+  const int in_dt = to_dtype(lists[0][0]), out_dt = to_dtype(lists[1][0]);
+  auto s = stream();
+  multi_tensor_apply(lists, chunk, [&](const teb200::MultiTensorTable& t, int nblk, int) {
+    check(teb200::multi_tensor_scale(t, nblk, in_dt, out_dt, static_cast<float>(scale), ptr<int>(noop), chunk, s),
+          "multi_tensor_scale");
+  });
+}
+
+void multi_tensor_l2norm_sq(std::vector<std::vector<at::Tensor>> lists, at::Tensor& out, const OptT& per_tensor,
+                            int64_t chunk) {
+  if (lists[0].empty()) return;
+  c10::cuda::CUDAGuard guard(lists[0][0].device());
+  const int dt = to_dtype(lists[0][0]);
+  auto s = stream();
+  multi_tensor_apply(lists, chunk, [&](const teb200::MultiTensorTable& t, int nblk, int base) {
+    check(teb200::multi_tensor_l2norm_sq(t, nblk, dt, out.data_ptr<float>(), ptr<float>(per_tensor), base, chunk, s),
+          "multi_tensor_l2norm");
+  });
+}
+
+void cross_entropy(const at::Tensor& logits, const at::Tensor& targets, const OptT& loss, const OptT& grad,
+                   const OptT& row_max, const OptT& row_sum, const OptT& row_tgt, int64_t vocab_start,
+                   double grad_scale, double label_smoothing, int64_t ignore_index, const OptT& gmax,
+                   const OptT& gsum) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  teb200::CrossEntropyArgs a;
+  a.logits = logits.data_ptr();
+  a.dtype = to_dtype(logits);
+  a.targets = targets.data_ptr<int64_t>();
+  a.loss = ptr<float>(loss);
+  a.grad = ptr<void>(grad);
+  a.row_max = ptr<float>(row_max);
+  a.row_sum = ptr<float>(row_sum);
+  a.row_tgt = ptr<float>(row_tgt);
+  a.V = static_cast<int>(logits.size(-1));
+  a.R = static_cast<int>(logits.numel() / logits.size(-1));
+  a.ld = logits.stride(-2);
+  a.vocab_start = static_cast<int>(vocab_start);
+  a.grad_scale = static_cast<float>(grad_scale);
+  a.label_smoothing = static_cast<float>(label_smoothing);
+  a.ignore_index = ignore_index;
+  if (gmax.has_value() && gmax->defined())
+    check(teb200::cross_entropy_parallel_bwd(a, gmax->data_ptr<float>(), gsum->data_ptr<float>(), stream()),
+          "cross_entropy_parallel_bwd");
+  else
+    check(teb200::cross_entropy_fwd_bwd(a, stream()), "cross_entropy");
+}
+
+// x, out: 4-D views [s, b, h, d] (any strides with unit stride on d)
+void rope(const at::Tensor& x, at::Tensor& out, const at::Tensor& freqs, int64_t d_rot, bool interleaved,
+          bool backward, int64_t pos_offset, int64_t cp_size, int64_t cp_rank, const OptT& start_positions) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 4 && x.stride(3) == 1 && out.strides() == x.strides(), "rope expects [s,b,h,d] views");
+  teb200::RopeArgs a;
+  a.x = x.data_ptr();
+  a.out = out.data_ptr();
+  a.freqs = freqs.data_ptr<float>();
+  a.dtype = to_dtype(x);
+  a.s = x.size(0); a.b = x.size(1); a.h = x.size(2); a.d = x.size(3);
+  a.d_rot = static_cast<int>(d_rot);
+  a.stride_s = x.stride(0); a.stride_b = x.stride(1); a.stride_h = x.stride(2);
+  a.interleaved = interleaved;
+  a.backward = backward;
+  a.pos_offset = static_cast<int>(pos_offset);
+  a.cp_size = static_cast<int>(cp_size);
+  a.cp_rank = static_cast<int>(cp_rank);
+  a.start_positions = ptr<int32_t>(start_positions);
+  check(teb200::rope_apply(a, stream()), "rope");
+}
+
+}  // namespace
+
+void register_extra(py::module_& m);  // bindings of kernels added in other translation units
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("status", &status);
+  m.def("gemm", &gemm);
+  m.def("quantize", &quantize);
+  m.def("dequantize_mxfp8", &dequantize_mxfp8);
+  m.def("dequantize_fp8", &dequantize_fp8);
+  m.def("amax", &amax);
+  m.def("swizzle", &swizzle);
+  m.def("norm_fwd", &norm_fwd);
+  m.def("norm_bwd", &norm_bwd);
+  m.def("norm_bwd_workspace", &norm_bwd_workspace);
+  m.def("multi_tensor_adam", &multi_tensor_adam);
+  m.def("multi_tensor_sgd", &multi_tensor_sgd);
+  m.def("multi_tensor_scale", &multi_tensor_scale);
+  m.def("multi_tensor_l2norm_sq", &multi_tensor_l2norm_sq);
+  m.def("cross_entropy", &cross_entropy);
+  m.def("rope", &rope);
+  register_extra(m);
+}

@@ -1,0 +1,58 @@
+// Host-side launcher declarations of the teb200 kernels.  All launchers take
+// raw device pointers and a stream; none allocates device memory.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace teb200 {
+
+enum DType : int { kFloat32 = 0, kFloat16 = 1, kBFloat16 = 2, kByte = 3, kFloat8E4M3 = 4, kFloat8E5M2 = 5 };
+
+inline size_t dtype_size(int t) { return t == kFloat32 ? 4 : (t == kFloat16 || t == kBFloat16) ? 2 : 1; }
+
+// Epilogue selector of the GEMM kernels.
+enum Epilogue : int {
+  kEpiNone = 0,
+  kEpiBias = 1,        // D = acc + bias[n]
+  kEpiGelu = 2,        // aux = acc (+bias); D = gelu(aux)
+  kEpiDGelu = 3,       // D = acc * gelu'(aux)
+  kEpiSwiGluPair = 4,  // reserved
+};
+
+struct GemmArgs {
+  // D[M,N] (row-major, leading dim ldd) = alpha * A[M,K] * B[N,K]^T (+ D if accumulate) (+ bias)
+  const void* a = nullptr;
+  const void* b = nullptr;
+  void* d = nullptr;
+  const void* bias = nullptr;   // [N], dtype bias_dtype
+  void* aux = nullptr;          // pre-activation output/input for gelu epilogues, same layout as D
+  const uint8_t* sfa = nullptr; // block scales of A (128x4-tile swizzled), block-scaled kinds only
+  const uint8_t* sfb = nullptr;
+  const float* alpha_dev = nullptr;  // optional device scalar multiplied into the accumulator
+  float alpha = 1.0f;
+  int M = 0, N = 0, K = 0;
+  int64_t lda = 0, ldb = 0, ldd = 0;  // in elements
+  int a_dtype = kBFloat16, b_dtype = kBFloat16, d_dtype = kBFloat16, bias_dtype = kBFloat16;
+  int epilogue = kEpiNone;
+  bool accumulate = false;
+  bool a_mn_major = false;  // A stored [K, M] (contraction dim slow); 16-bit kinds only
+  bool b_mn_major = false;
+  int* status = nullptr;    // device int, receives a Status code on failure
+  int sm_count = 0;         // 0 = all SMs
+  // grouped mode (MoE): rows of A/D are split in `num_groups` contiguous slabs; slab g uses
+  // B rows [g*N, (g+1)*N).  `group_offsets` is a device array [num_groups+1] of row offsets.
+  int num_groups = 0;
+  const int32_t* group_offsets = nullptr;
+};
+
+// dense / grouped tcgen05 GEMMs
+cudaError_t gemm_bf16(const GemmArgs& args, cudaStream_t stream);    // fp16 or bf16 operands
+cudaError_t gemm_mxfp8(const GemmArgs& args, cudaStream_t stream);   // e4m3/e5m2 + ue8m0 per 32
+cudaError_t gemm_nvfp4(const GemmArgs& args, cudaStream_t stream);   // e2m1 + e4m3 per 16
+
+// build a 2-D row-major tensor map (TMA descriptor)
+bool make_tensor_map_2d(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols,
+                        uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols, bool swizzle128);
+
+}  // namespace teb200

@@ -1,0 +1,145 @@
+// Launchers: multi-tensor optimizer kernels, cross entropy, RoPE, softmax, dropout,
+// MoE router / permutation, padding helpers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace teb200 {
+
+// ---------------------------------------------------------------- multi-tensor apply
+constexpr int kMtMaxTensors = 24;
+constexpr int kMtMaxBlocks = 320;
+constexpr int kMtLists = 5;
+
+struct MultiTensorTable {
+  void* ptr[kMtLists][kMtMaxTensors];
+  int64_t numel[kMtMaxTensors];
+  uint8_t block_tensor[kMtMaxBlocks];
+  int32_t block_chunk[kMtMaxBlocks];
+};
+
+struct AdamArgs {
+  float lr = 0, beta1 = 0.9f, beta2 = 0.999f, eps = 1e-8f, weight_decay = 0;
+  float bias_correction1 = 1, bias_correction2 = 1;
+  int adamw = 1;           // 1: decoupled weight decay, 0: L2 added to the gradient
+  int grad_dtype = 2;      // lists: 0 = grad, 1 = param (model dtype), 2 = exp_avg, 3 = exp_avg_sq, 4 = master
+  int param_dtype = 2;
+  int state_dtype = 0;     // fp32 or bf16 moments
+  int has_master = 1;
+  float grad_scale = 1.f;  // gradients are multiplied by this (1/loss_scale, 1/accumulation steps)
+  const float* inv_scale_dev = nullptr;  // optional device scalar multiplied into the gradient
+  const int* noop = nullptr;             // skip the update when *noop != 0
+  int64_t chunk = 0;
+};
+cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nblocks, const AdamArgs& a, cudaStream_t s);
+
+struct SgdArgs {
+  float lr = 0, momentum = 0, dampening = 0, weight_decay = 0, grad_scale = 1.f;
+  int nesterov = 0, first_run = 0, wd_after_momentum = 0;
+  int grad_dtype = 2, param_dtype = 2, has_master = 0;  // lists: 0 grad, 1 param, 2 momentum buf (fp32), 3 master
+  const int* noop = nullptr;
+  int64_t chunk = 0;
+};
+cudaError_t multi_tensor_sgd(const MultiTensorTable& t, int nblocks, const SgdArgs& a, cudaStream_t s);
+// out (list 1) = in (list 0) * scale, dtype conversions allowed; sets *noop on non-finite input
+cudaError_t multi_tensor_scale(const MultiTensorTable& t, int nblocks, int in_dtype, int out_dtype, float scale,
+                               int* noop, int64_t chunk, cudaStream_t s);
+// sum of squares of list 0 accumulated into out[0] (and per tensor into per_tensor[i] when not null)
+cudaError_t multi_tensor_l2norm_sq(const MultiTensorTable& t, int nblocks, int dtype, float* out,
+                                   float* per_tensor, int tensor_base, int64_t chunk, cudaStream_t s);
+
+// ---------------------------------------------------------------- cross entropy
+// logits [R, V] (bf16/fp16/fp32), targets int64 [R].  Writes loss[R] (fp32) and, when
+// grad is not null, d(loss)/d(logits) * grad_scale into grad (may alias logits).
+struct CrossEntropyArgs {
+  const void* logits = nullptr;
+  int dtype = 2;
+  const int64_t* targets = nullptr;
+  float* loss = nullptr;
+  void* grad = nullptr;
+  float* row_max = nullptr;  // optional [R]: statistics for vocab-parallel reduction
+  float* row_sum = nullptr;
+  float* row_tgt = nullptr;
+  int R = 0, V = 0;
+  int64_t ld = 0;
+  int vocab_start = 0;  // first vocabulary id held by this rank
+  float grad_scale = 1.f;
+  float label_smoothing = 0.f;
+  int64_t ignore_index = -100;
+};
+cudaError_t cross_entropy_fwd_bwd(const CrossEntropyArgs& a, cudaStream_t s);
+// vocab-parallel second stage: given the all-reduced max / sum / target logit, write the gradient
+cudaError_t cross_entropy_parallel_bwd(const CrossEntropyArgs& a, const float* gmax, const float* gsum,
+                                       cudaStream_t s);
+
+// ---------------------------------------------------------------- RoPE
+// x [s, b, h, d] (sbhd=1) or [b, s, h, d]; freqs [s_total, d_rot] fp32 angles.  In-place allowed.
+struct RopeArgs {
+  const void* x = nullptr;
+  void* out = nullptr;
+  const float* freqs = nullptr;
+  int dtype = 2;
+  int s = 0, b = 0, h = 0, d = 0, d_rot = 0;
+  int64_t stride_s = 0, stride_b = 0, stride_h = 0;  // element strides of x / out
+  int interleaved = 0;
+  int backward = 0;
+  int pos_offset = 0;  // added to the sequence index (context parallel / KV cache)
+  int cp_size = 1, cp_rank = 0;  // dual-chunk position remap when cp_size > 1
+  const int32_t* start_positions = nullptr;  // optional [b]
+};
+cudaError_t rope_apply(const RopeArgs& a, cudaStream_t s);
+
+// ---------------------------------------------------------------- softmax (unfused attention path)
+struct SoftmaxArgs {
+  const void* x = nullptr;  // [rows, cols] scores, rows = b*h*sq
+  void* y = nullptr;
+  const uint8_t* mask = nullptr;  // optional [b, 1, sq, sk] bytes, non-zero = masked out
+  int dtype = 2;
+  int64_t rows = 0;
+  int cols = 0, sq = 0, heads = 0;
+  float scale = 1.f;
+  int causal = 0;          // 1: upper-triangular mask aligned bottom-right
+  const void* dy = nullptr;  // backward when not null: y holds probs, out = dx
+};
+cudaError_t softmax_fwd(const SoftmaxArgs& a, cudaStream_t s);
+cudaError_t softmax_bwd(const SoftmaxArgs& a, cudaStream_t s);
+
+// ---------------------------------------------------------------- dropout
+cudaError_t dropout_fwd(const void* x, void* y, uint8_t* mask_bits, int64_t n, int dtype, float p, uint64_t seed,
+                        uint64_t offset, cudaStream_t s);
+cudaError_t dropout_bwd(const void* dy, const uint8_t* mask_bits, void* dx, int64_t n, int dtype, float p,
+                        cudaStream_t s);
+
+// ---------------------------------------------------------------- MoE router / permutation
+struct RouterArgs {
+  const void* logits = nullptr;  // [T, E]
+  int dtype = 2;
+  int T = 0, E = 0, topk = 0;
+  int score_fn = 1;              // 0 sigmoid, 1 softmax, 2 sqrt-softplus
+  int use_pre_softmax = 0;
+  float scaling_factor = 1.f;
+  const float* expert_bias = nullptr;
+  int num_groups = 0, group_topk = 0;
+  float* probs = nullptr;        // [T, E] dense, zero outside the top-k
+  uint8_t* routing_map = nullptr;  // [T, E] bytes
+  int32_t* topk_idx = nullptr;   // [T, topk]
+  float* topk_w = nullptr;       // [T, topk]
+  float* scores = nullptr;       // [T, E] optional: full score-function output (aux loss)
+  int32_t* tokens_per_expert = nullptr;  // [E] optional, accumulated atomically (zeroed by callee)
+};
+cudaError_t router_topk_fwd(const RouterArgs& a, cudaStream_t s);
+cudaError_t router_topk_bwd(const RouterArgs& a, const float* grad_probs, void* grad_logits, cudaStream_t s);
+
+// rows of `in` [T, H] scattered to expert-major order.  `dest_row` [T, topk] gives the
+// destination row of every (token, slot) or -1.
+cudaError_t permute_rows(const void* in, void* out, const int32_t* dest_row, const float* probs, float* probs_out,
+                         int T, int topk, int H, int dtype, cudaStream_t s);
+// out[t] = sum_k w[t,k] * in[dest_row[t,k]]  (w may be null = plain sum)
+cudaError_t unpermute_rows(const void* in, void* out, const int32_t* dest_row, const float* w, int T, int topk, int H,
+                           int dtype, cudaStream_t s);
+// dest_row from a routing of T tokens to E experts: stable expert-major order, per-expert
+// row counts padded to `align`.  counts [E], offsets [E+1] written on device.
+cudaError_t build_dest_rows(const int32_t* topk_idx, int T, int topk, int E, int align, int32_t* counts,
+                            int32_t* offsets, int32_t* dest_row, cudaStream_t s);
+
+}  // namespace teb200

@@ -1,0 +1,292 @@
+"""RoPE, cross entropy, softmax, dropout and multi-tensor optimizer ops."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _ext
+
+MT_CHUNK = 512 * 1024
+
+
+# ----------------------------------------------------------------------------- RoPE
+def rope_freqs(positions: torch.Tensor, dim: int, base: float = 10000.0, interleaved: bool = False) -> torch.Tensor:
+    """Angles ``[len, dim]`` = cat(freqs, freqs) (or interleaved repeat), fp32."""
+    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float32, device=positions.device) / dim))
+    f = torch.outer(positions.float(), inv)
+    if interleaved:
+        return torch.stack([f, f], dim=-1).reshape(f.shape[0], -1)
+    return torch.cat([f, f], dim=-1)
+
+
+def _rotate(x, interleaved):
+    if interleaved:
+        x1, x2 = x[..., 0::2], x[..., 1::2]
+        return torch.stack([-x2, x1], dim=-1).reshape(x.shape)
+    h = x.shape[-1] // 2
+    return torch.cat([-x[..., h:], x[..., :h]], dim=-1)
+
+
+def _cp_positions(s, cp_size, cp_rank, device):
+    idx = torch.arange(s, device=device)
+    if cp_size <= 1:
+        return idx
+    half = s // 2
+    return torch.where(idx < half, idx + cp_rank * half, idx + s * cp_size - (cp_rank + 1) * half - half)
+
+
+def rope_ref(x_sbhd, freqs, d_rot, interleaved=False, backward=False, pos_offset=0, cp_size=1, cp_rank=0,
+             start_positions=None):
+    s, b = x_sbhd.shape[0], x_sbhd.shape[1]
+    pos = _cp_positions(s, cp_size, cp_rank, x_sbhd.device) + pos_offset
+    if start_positions is not None:
+        pos = pos[:, None] + start_positions[None, :].to(pos.device)  # [s, b]
+        f = freqs[pos][:, :, None, :]
+    else:
+        f = freqs[pos][:, None, None, :]
+    xf = x_sbhd.float()
+    xr, xp = xf[..., :d_rot], xf[..., d_rot:]
+    cos, sin = torch.cos(f), torch.sin(f)
+    if not backward:
+        yr = xr * cos + _rotate(xr, interleaved) * sin
+    else:
+        # transpose of the rotation: rot^T(v) = -rot(v)
+        yr = xr * cos - _rotate(xr * sin, interleaved)
+    return torch.cat([yr, xp], dim=-1).to(x_sbhd.dtype)
+
+
+def rope_apply(x_sbhd: torch.Tensor, freqs: torch.Tensor, *, interleaved=False, backward=False, pos_offset=0,
+               cp_size=1, cp_rank=0, start_positions=None, inplace=False) -> torch.Tensor:
+    """Rotary embedding on a ``[s, b, h, d]`` view (strided views are fine on CUDA)."""
+    d_rot = freqs.shape[-1]
+    if _ext.use_cuda(x_sbhd) and x_sbhd.stride(-1) == 1 and x_sbhd.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        out = x_sbhd if inplace else torch.empty_strided(x_sbhd.shape, x_sbhd.stride(), dtype=x_sbhd.dtype,
+                                                         device=x_sbhd.device)
+        sp = start_positions.to(torch.int32) if start_positions is not None else None
+        _ext.get().rope(x_sbhd, out, freqs.float().contiguous(), d_rot, interleaved, backward, pos_offset, cp_size,
+                        cp_rank, sp)
+        return out
+    y = rope_ref(x_sbhd, freqs.float(), d_rot, interleaved, backward, pos_offset, cp_size, cp_rank, start_positions)
+    if inplace:
+        x_sbhd.copy_(y)
+        return x_sbhd
+    return y
+
+
+# ----------------------------------------------------------------------------- cross entropy
+def cross_entropy_ref(logits, targets, label_smoothing=0.0, ignore_index=-100):
+    lf = logits.float().reshape(-1, logits.shape[-1])
+    t = targets.reshape(-1)
+    lse = torch.logsumexp(lf, dim=-1)
+    safe_t = t.clamp(min=0)
+    nll = lse - lf.gather(1, safe_t[:, None]).squeeze(1)
+    if label_smoothing > 0:
+        smooth = lse - lf.mean(-1)
+        nll = (1 - label_smoothing) * nll + label_smoothing * smooth
+    return torch.where(t == ignore_index, torch.zeros_like(nll), nll)
+
+
+def cross_entropy_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, grad_scale: float = 1.0,
+                          label_smoothing: float = 0.0, ignore_index: int = -100, inplace_grad: bool = True):
+    """Per-row loss (fp32 ``[R]``) and d(loss)/d(logits)*grad_scale (written over the logits when
+    ``inplace_grad``)."""
+    V = logits.shape[-1]
+    l2 = logits.reshape(-1, V)
+    t = targets.reshape(-1).to(torch.int64)
+    if _ext.use_cuda(logits) and label_smoothing == 0.0 and l2.stride(-1) == 1 \
+            and logits.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        loss = torch.empty(l2.shape[0], dtype=torch.float32, device=logits.device)
+        grad = l2 if inplace_grad else torch.empty_like(l2)
+        _ext.get().cross_entropy(l2, t.contiguous(), loss, grad, None, None, None, 0, grad_scale, label_smoothing,
+                                 ignore_index, None, None)
+        return loss, grad.reshape(logits.shape)
+    lf = l2.float()
+    loss = cross_entropy_ref(lf, t, label_smoothing, ignore_index)
+    p = torch.softmax(lf, dim=-1)
+    p = p - label_smoothing / V
+    p[torch.arange(p.shape[0], device=p.device), t.clamp(min=0)] -= 1 - label_smoothing
+    p = torch.where((t == ignore_index)[:, None], torch.zeros_like(p), p) * grad_scale
+    return loss, p.to(logits.dtype).reshape(logits.shape)
+
+
+def cross_entropy_stats(logits, targets, vocab_start, ignore_index=-100):
+    """Vocab-parallel stage 1: per-row (max, sum-exp, target logit or 0) of the local shard."""
+    V = logits.shape[-1]
+    l2 = logits.reshape(-1, V)
+    t = targets.reshape(-1).to(torch.int64)
+    R = l2.shape[0]
+    if _ext.use_cuda(logits) and l2.stride(-1) == 1:
+        st = torch.empty(3, R, dtype=torch.float32, device=logits.device)
+        _ext.get().cross_entropy(l2, t.contiguous(), None, None, st[0], st[1], st[2], vocab_start, 1.0, 0.0,
+                                 ignore_index, None, None)
+        return st[0], st[1], st[2]
+    lf = l2.float()
+    m = lf.max(-1).values
+    s = torch.exp(lf - m[:, None]).sum(-1)
+    local = t - vocab_start
+    mine = (local >= 0) & (local < V) & (t != ignore_index)
+    tl = torch.where(mine, lf.gather(1, local.clamp(0, V - 1)[:, None]).squeeze(1), torch.zeros_like(m))
+    return m, s, tl
+
+
+def cross_entropy_parallel_grad(logits, targets, gmax, gsum, vocab_start, grad_scale=1.0, ignore_index=-100,
+                                inplace_grad=True):
+    """Vocab-parallel stage 2: gradient from the all-reduced statistics."""
+    V = logits.shape[-1]
+    l2 = logits.reshape(-1, V)
+    t = targets.reshape(-1).to(torch.int64)
+    if _ext.use_cuda(logits) and l2.stride(-1) == 1:
+        grad = l2 if inplace_grad else torch.empty_like(l2)
+        _ext.get().cross_entropy(l2, t.contiguous(), None, grad, None, None, None, vocab_start, grad_scale, 0.0,
+                                 ignore_index, gmax.contiguous(), gsum.contiguous())
+        return grad.reshape(logits.shape)
+    p = torch.exp(l2.float() - gmax[:, None]) / gsum[:, None]
+    local = t - vocab_start
+    mine = (local >= 0) & (local < V)
+    rows = torch.arange(p.shape[0], device=p.device)[mine]
+    p[rows, local[mine]] -= 1.0
+    p = torch.where((t == ignore_index)[:, None], torch.zeros_like(p), p) * grad_scale
+    return p.to(logits.dtype).reshape(logits.shape)
+
+
+# ----------------------------------------------------------------------------- multi-tensor
+def _filter_empty(lists):
+    keep = [i for i, t in enumerate(lists[0]) if t.numel() > 0]
+    return [[l[i] for i in keep] for l in lists]
+
+
+def multi_tensor_adam(lists: Sequence[List[torch.Tensor]], lr, beta1, beta2, eps, step, adamw=True,
+                      bias_correction=True, weight_decay=0.0, grad_scale=1.0, inv_scale=None, noop=None):
+    """lists = [grads, params, exp_avg, exp_avg_sq (, master fp32)]; updates in place."""
+    lists = _filter_empty(lists)
+    if not lists[0]:
+        return
+    if _ext.use_cuda(lists[0][0]):
+        _ext.get().multi_tensor_adam([list(l) for l in lists], lr, beta1, beta2, eps, int(step), adamw,
+                                     bias_correction, weight_decay, grad_scale, inv_scale, noop, MT_CHUNK)
+        return
+    if noop is not None and int(noop.item()) != 0:
+        return
+    bc1 = 1 - beta1 ** step if bias_correction else 1.0
+    bc2 = 1 - beta2 ** step if bias_correction else 1.0
+    gs = grad_scale * (float(inv_scale.item()) if inv_scale is not None else 1.0)
+    has_master = len(lists) == 5
+    for i in range(len(lists[0])):
+        g = lists[0][i].float() * gs
+        p = lists[4][i] if has_master else lists[1][i].float()
+        m, v = lists[2][i].float(), lists[3][i].float()
+        if not adamw:
+            g = g + weight_decay * p
+        m = beta1 * m + (1 - beta1) * g
+        v = beta2 * v + (1 - beta2) * g * g
+        upd = (m / bc1) / (torch.sqrt(v / bc2) + eps)
+        if adamw:
+            upd = upd + weight_decay * p
+        pn = p - lr * upd
+        lists[2][i].copy_(m)
+        lists[3][i].copy_(v)
+        if has_master:
+            lists[4][i].copy_(pn)
+        lists[1][i].copy_(pn)
+
+
+def multi_tensor_sgd(lists, lr, momentum=0.0, dampening=0.0, weight_decay=0.0, nesterov=False, first_run=False,
+                     wd_after_momentum=False, grad_scale=1.0, noop=None):
+    """lists = [grads, params, momentum_buf fp32 (, master fp32)]."""
+    lists = _filter_empty(lists)
+    if not lists[0]:
+        return
+    if _ext.use_cuda(lists[0][0]):
+        _ext.get().multi_tensor_sgd([list(l) for l in lists], lr, momentum, dampening, weight_decay, nesterov,
+                                    first_run, wd_after_momentum, grad_scale, noop, MT_CHUNK)
+        return
+    has_master = len(lists) == 4
+    for i in range(len(lists[0])):
+        g = lists[0][i].float() * grad_scale
+        w = lists[3][i] if has_master else lists[1][i].float()
+        if weight_decay and not wd_after_momentum:
+            g = g + weight_decay * w
+        if momentum:
+            b = g if first_run else lists[2][i] * momentum + (1 - dampening) * g
+            lists[2][i].copy_(b)
+            g = g + momentum * b if nesterov else b
+        if weight_decay and wd_after_momentum:
+            g = g + weight_decay * w
+        wn = w - lr * g
+        if has_master:
+            lists[3][i].copy_(wn)
+        lists[1][i].copy_(wn)
+
+
+def multi_tensor_scale(lists, scale, noop=None):
+    """lists = [src, dst]: dst = src * scale; sets ``noop`` to 1 on inf/nan input."""
+    lists = _filter_empty(lists)
+    if not lists[0]:
+        return
+    if _ext.use_cuda(lists[0][0]):
+        _ext.get().multi_tensor_scale([list(l) for l in lists], scale, noop, MT_CHUNK)
+        return
+    for s, d in zip(*lists):
+        if noop is not None and not torch.isfinite(s).all():
+            noop.fill_(1)
+        d.copy_(s.float() * scale)
+
+
+def multi_tensor_l2norm(tensors: List[torch.Tensor], per_tensor: bool = False):
+    """Returns (global L2 norm [1], per-tensor norms or None)."""
+    tensors = [t for t in tensors if t.numel() > 0]
+    if not tensors:
+        z = torch.zeros(1)
+        return z, (torch.zeros(0) if per_tensor else None)
+    dev = tensors[0].device
+    if _ext.use_cuda(tensors[0]):
+        out = torch.zeros(1, dtype=torch.float32, device=dev)
+        pt = torch.zeros(len(tensors), dtype=torch.float32, device=dev) if per_tensor else None
+        by_dtype = {}
+        for i, t in enumerate(tensors):
+            by_dtype.setdefault(t.dtype, []).append((i, t))
+        for dt, items in by_dtype.items():
+            sub_pt = torch.zeros(len(items), dtype=torch.float32, device=dev) if per_tensor else None
+            _ext.get().multi_tensor_l2norm_sq([[t.contiguous() for _, t in items]], out, sub_pt, MT_CHUNK)
+            if per_tensor:
+                pt[torch.tensor([i for i, _ in items], device=dev)] = sub_pt
+        return out.sqrt(), (pt.sqrt() if per_tensor else None)
+    sq = [t.float().pow(2).sum() for t in tensors]
+    tot = torch.stack(sq).sum().sqrt().reshape(1)
+    return tot, (torch.stack(sq).sqrt() if per_tensor else None)
+
+
+# ----------------------------------------------------------------------------- softmax / dropout (unfused attention)
+def scaled_masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor], scale: float, causal: bool = False):
+    """softmax(scale * scores + mask) over the last dim, fp32 accumulation; ``mask`` True = masked out.
+    ``causal`` applies a bottom-right aligned upper-triangular mask."""
+    s = scores.float() * scale
+    if causal:
+        sq, sk = s.shape[-2], s.shape[-1]
+        tri = torch.ones(sq, sk, dtype=torch.bool, device=s.device).triu(diagonal=sk - sq + 1)
+        s = s.masked_fill(tri, float("-inf"))
+    if mask is not None:
+        s = s.masked_fill(mask, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    p = torch.nan_to_num(p, nan=0.0)  # fully masked rows
+    return p.to(scores.dtype)
+
+
+def softmax_bwd(probs: torch.Tensor, dprobs: torch.Tensor, scale: float) -> torch.Tensor:
+    p, d = probs.float(), dprobs.float()
+    return ((d - (d * p).sum(-1, keepdim=True)) * p * scale).to(probs.dtype)
+
+
+def dropout_fwd(x: torch.Tensor, p: float, generator=None):
+    """Returns (y, keep mask as bool)."""
+    if p <= 0.0:
+        return x, None
+    keep = torch.rand(x.shape, device=x.device, generator=generator) >= p
+    return (x.float() * keep / (1 - p)).to(x.dtype), keep
+
+
+def dropout_bwd(dy: torch.Tensor, keep: Optional[torch.Tensor], p: float):
+    if keep is None:
+        return dy
+    return (dy.float() * keep / (1 - p)).to(dy.dtype)

@@ -1,0 +1,298 @@
+"""Quantizer / quantized-tensor base classes.
+
+A :class:`Quantizer` is a builder that turns a high-precision tensor into a
+quantized one.  A quantized tensor carries up to two physical copies of the
+logical matrix: a *rowwise* copy (scales along the last dim, used when the
+tensor is contracted over its last dim) and a *columnwise* copy (scales along
+the flattened leading dims, used when the tensor is contracted over those).
+In this library every columnwise copy is stored transposed ``[C, R]`` so that
+all GEMM operands are contraction-dim contiguous for the tcgen05 kernels.
+
+``*Storage`` classes are plain containers without autograd; the ``*Tensor``
+classes wrap them as ``torch.Tensor`` subclasses so that quantized parameters
+behave like tensors (reference: ``pytorch/quantized_tensor.py:53-1083``).
+"""
+from __future__ import annotations
+
+import abc
+import copy
+from typing import Any, Dict, Iterable, Optional, Tuple
+
+import torch
+from torch.utils._pytree import tree_map
+
+
+class QuantizedTensorStorage:
+    """Container of quantized data.  Sub-classes define the fields."""
+
+    _quantizer: Optional["Quantizer"] = None
+    _dtype: torch.dtype = torch.float32
+    _shape: Tuple[int, ...] = ()
+
+    # -- interface ----------------------------------------------------------
+    def dequantize(self, *, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def update_usage(self, rowwise_usage: Optional[bool] = None, columnwise_usage: Optional[bool] = None) -> None:
+        """Drop the copy that is no longer needed (frees memory)."""
+        raise NotImplementedError
+
+    def get_usages(self) -> Dict[str, bool]:
+        raise NotImplementedError
+
+    def get_data_tensors(self) -> Tuple[Optional[torch.Tensor], ...]:
+        raise NotImplementedError
+
+    def prepare_for_saving(self):
+        """Return (tensors, self) with the tensor fields detached from ``self``,
+        for ``ctx.save_for_backward``."""
+        raise NotImplementedError
+
+    def restore_from_saved(self, tensors: list) -> list:
+        raise NotImplementedError
+
+    @property
+    def logical_shape(self) -> Tuple[int, ...]:
+        return tuple(self._shape)
+
+    @property
+    def device(self):  # type: ignore[override]
+        for t in self.get_data_tensors():
+            if t is not None:
+                return t.device
+        raise RuntimeError("quantized tensor holds no data")
+
+    def size(self, dim: Optional[int] = None):
+        return torch.Size(self._shape) if dim is None else self._shape[dim]
+
+    def numel(self) -> int:
+        n = 1
+        for s in self._shape:
+            n *= s
+        return n
+
+    def _rows_cols(self) -> Tuple[int, int]:
+        c = self._shape[-1]
+        return self.numel() // max(c, 1), c
+
+
+class Quantizer(abc.ABC):
+    """Builder of quantized tensors.
+
+    ``rowwise_usage`` / ``columnwise_usage`` select which copies are produced;
+    ``internal=True`` produces a bare Storage object (cheaper, no autograd).
+    """
+
+    def __init__(self, *, rowwise: bool = True, columnwise: bool = True) -> None:
+        self.rowwise_usage = rowwise
+        self.columnwise_usage = columnwise
+        self.internal = False
+        self.optimize_for_gemm = True
+
+    def set_usage(self, *, rowwise: Optional[bool] = None, columnwise: Optional[bool] = None) -> None:
+        if rowwise is not None:
+            self.rowwise_usage = rowwise
+        if columnwise is not None:
+            self.columnwise_usage = columnwise
+
+    def copy(self) -> "Quantizer":
+        return copy.copy(self)
+
+    def __call__(self, tensor: torch.Tensor) -> Any:
+        return self.quantize(tensor)
+
+    def quantize(self, tensor: torch.Tensor, *, out: Optional[QuantizedTensorStorage] = None, dtype=None):
+        if out is not None:
+            return self.update_quantized(tensor, out)
+        if isinstance(tensor, QuantizedTensorStorage):
+            tensor = tensor.dequantize()
+        return self.quantize_impl(tensor.detach() if self.internal else tensor, dtype=dtype)
+
+    @abc.abstractmethod
+    def quantize_impl(self, tensor: torch.Tensor, dtype=None):
+        ...
+
+    @abc.abstractmethod
+    def update_quantized(self, src: torch.Tensor, dst: QuantizedTensorStorage, *, noop_flag=None):
+        ...
+
+    @abc.abstractmethod
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+        ...
+
+    def calibrate(self, tensor: torch.Tensor) -> None:
+        """Record statistics without quantizing (``autocast(calibrating=True)``)."""
+
+    def is_quantizable(self, tensor: torch.Tensor) -> bool:
+        return True
+
+    def supports_only_rowwise_all_gather(self) -> bool:
+        return False
+
+    def get_usages(self) -> Dict[str, bool]:
+        return {"rowwise": self.rowwise_usage, "columnwise": self.columnwise_usage}
+
+
+def _stride_for(shape) -> Tuple[int, ...]:
+    st, acc = [], 1
+    for s in reversed(tuple(shape)):
+        st.append(acc)
+        acc *= max(int(s), 1)
+    return tuple(reversed(st))
+
+
+class _QuantizeFunc(torch.autograd.Function):
+    """Differentiable quantize: straight-through gradient."""
+
+    @staticmethod
+    def forward(ctx, tensor, quantizer):  # type: ignore[override]
+        return quantizer.quantize_impl(tensor.detach())
+
+    @staticmethod
+    def backward(ctx, grad):  # type: ignore[override]
+        return grad, None
+
+
+class _DequantizeFunc(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tensor, dtype):  # type: ignore[override]
+        return tensor._dequantize_impl(dtype)
+
+    @staticmethod
+    def backward(ctx, grad):  # type: ignore[override]
+        return grad, None
+
+
+class QuantizedTensor(torch.Tensor):
+    """``torch.Tensor`` wrapper over a quantized payload.
+
+    Generic torch ops see the dequantized values (``__torch_dispatch__``);
+    in-place ops re-quantize into the payload.  Library kernels read the
+    payload fields directly.
+    """
+
+    @staticmethod
+    def __new__(cls, *args, shape, dtype, requires_grad=False, device=None, **kwargs):
+        shape = tuple(int(s) for s in shape)
+        return torch.Tensor._make_wrapper_subclass(
+            cls,
+            shape,
+            strides=_stride_for(shape),
+            storage_offset=0,
+            dtype=dtype,
+            layout=torch.strided,
+            requires_grad=requires_grad,
+            device=torch.device("cpu") if device is None else device,
+        )
+
+    # sub-classes implement
+    def _dequantize_impl(self, dtype: Optional[torch.dtype]) -> torch.Tensor:
+        raise NotImplementedError
+
+    def _new_like(self, **overrides):
+        raise NotImplementedError
+
+    def quantize_(self, tensor: torch.Tensor, *, noop_flag=None) -> "QuantizedTensor":
+        """Overwrite the payload with a quantization of ``tensor``."""
+        q = self._quantizer
+        assert q is not None, "in-place update needs the quantizer that built this tensor"
+        if isinstance(tensor, QuantizedTensor):
+            tensor = tensor.dequantize()
+        q.update_quantized(tensor, self, noop_flag=noop_flag)
+        return self
+
+    def dequantize(self, *, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        if torch.is_grad_enabled() and self.requires_grad:
+            return _DequantizeFunc.apply(self, dtype)
+        return self._dequantize_impl(dtype)
+
+    def detach(self):  # type: ignore[override]
+        return self._new_like(requires_grad=False)
+
+    def clone(self, *a, **k):  # type: ignore[override]
+        return self._new_like(clone=True)
+
+    def float(self):  # type: ignore[override]
+        return self.dequantize(dtype=torch.float32)
+
+    def bfloat16(self):  # type: ignore[override]
+        return self.dequantize(dtype=torch.bfloat16)
+
+    def half(self):  # type: ignore[override]
+        return self.dequantize(dtype=torch.float16)
+
+    def cpu(self, *a, **k):  # type: ignore[override]
+        return self.dequantize().cpu()
+
+    def __repr__(self, *, tensor_contents=None):  # type: ignore[override]
+        return f"{self.__class__.__name__}(shape={tuple(self.shape)}, dtype={self.dtype}, data={self.dequantize()})"
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        if func in (torch.ops.aten.detach.default, torch.ops.aten.alias.default):
+            return args[0]._new_like(requires_grad=False)
+        if func == torch.ops.aten.clone.default:
+            return args[0]._new_like(clone=True)
+        if func == torch.ops.aten.copy_.default:
+            dst, src = args[0], args[1]
+            if isinstance(dst, QuantizedTensor):
+                dst.quantize_(src.dequantize() if isinstance(src, QuantizedTensor) else src)
+                return dst
+            dst.copy_(src.dequantize(dtype=dst.dtype))
+            return dst
+        if func == torch.ops.aten.view.default and tuple(args[1]) == tuple(args[0].shape):
+            return args[0]._new_like(requires_grad=False)
+
+        def unwrap(t):
+            return t._dequantize_impl(None) if isinstance(t, QuantizedTensor) else t
+
+        # in-place ops on a quantized destination: compute in high precision, requantize
+        schema = getattr(func, "_schema", None)
+        if schema is not None and schema.is_mutable and len(args) and isinstance(args[0], QuantizedTensor):
+            dst = args[0]
+            hp = dst._dequantize_impl(None)
+            rest = tree_map(unwrap, args[1:])
+            func(hp, *rest, **tree_map(unwrap, kwargs))
+            dst.quantize_(hp)
+            return dst
+        return func(*tree_map(unwrap, args), **tree_map(unwrap, kwargs))
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*args, **kwargs)
+
+    # parameters of quantized type must survive .data assignment and state_dict
+    def contiguous(self, memory_format=torch.contiguous_format):  # type: ignore[override]
+        return self
+
+    def to_dtype(self, dtype: torch.dtype):
+        return self._new_like(dtype=dtype)
+
+
+def prepare_for_saving(*tensors):
+    """Split a mix of plain and quantized tensors into (saveable tensors, objects)."""
+    flat, objs = [], []
+    for t in tensors:
+        if t is None or isinstance(t, torch.Tensor) and not isinstance(t, QuantizedTensorStorage):
+            flat.append(t)
+            objs.append(None)
+        else:
+            ts, obj = t.prepare_for_saving()
+            flat.extend(ts)
+            objs.append(obj)
+    return flat, objs
+
+
+def restore_from_saved(objs, saved):
+    saved = list(saved)
+    out = []
+    for o in objs:
+        if o is None:
+            out.append(saved.pop(0))
+        else:
+            saved = o.restore_from_saved(saved)
+            out.append(o)
+    return out

@@ -1,0 +1,212 @@
+"""Per-tensor scaled FP8 tensors (delayed and current scaling).
+
+Payload: ``_data`` uint8 ``[..., C]``, ``_scale_inv`` fp32 ``[1]`` and an
+optional ``_transpose`` uint8 ``[C, R]`` (the columnwise copy).
+Reference behaviour: ``pytorch/tensor/float8_tensor.py:53-1099``.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+
+from .. import ops
+from ..ops.ref import quant as Q
+from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+
+
+class Float8TensorStorage(QuantizedTensorStorage):
+    def __init__(self, *, data, fp8_scale_inv, fp8_dtype, data_transpose=None, quantizer=None,
+                 shape=None, dtype=torch.float32):
+        self._data = data
+        self._scale_inv = fp8_scale_inv
+        self._fp8_dtype = fp8_dtype
+        self._transpose = data_transpose
+        self._quantizer = quantizer
+        self._dtype = dtype
+        if shape is None:
+            shape = tuple(data.shape) if data is not None else tuple(reversed(data_transpose.shape))
+        self._shape = tuple(shape)
+
+    def get_data_tensors(self):
+        return self._data, self._transpose
+
+    def get_usages(self):
+        return {"rowwise": self._data is not None, "columnwise": self._transpose is not None}
+
+    def update_usage(self, rowwise_usage=None, columnwise_usage=None):
+        if columnwise_usage and self._transpose is None and self._data is not None:
+            R, C = self._rows_cols()
+            self._transpose = self._data.reshape(R, C).t().contiguous()
+        if rowwise_usage and self._data is None and self._transpose is not None:
+            self._data = self._transpose.t().contiguous().reshape(self._shape)
+        if rowwise_usage is False:
+            self._data = None
+        if columnwise_usage is False:
+            self._transpose = None
+
+    def _dequantize_impl(self, dtype=None):
+        dtype = dtype or self._dtype
+        if self._data is not None:
+            return ops.dequantize_fp8(self._data, self._scale_inv, self._fp8_dtype, dtype).reshape(self._shape)
+        R, C = self._rows_cols()
+        t = ops.dequantize_fp8(self._transpose, self._scale_inv, self._fp8_dtype, dtype)
+        return t.t().contiguous().reshape(self._shape)
+
+    def dequantize(self, *, dtype=None):
+        return self._dequantize_impl(dtype)
+
+    def prepare_for_saving(self):
+        ts = [self._data, self._transpose, self._scale_inv]
+        self._data = self._transpose = self._scale_inv = None
+        return ts, self
+
+    def restore_from_saved(self, tensors):
+        self._data, self._transpose, self._scale_inv = tensors[:3]
+        return tensors[3:]
+
+
+class Float8Tensor(Float8TensorStorage, QuantizedTensor):
+    def __new__(cls, *, shape, dtype, data, fp8_scale_inv, fp8_dtype, data_transpose=None,
+                quantizer=None, requires_grad=False, device=None):
+        dev = device if device is not None else (data if data is not None else data_transpose).device
+        self = QuantizedTensor.__new__(cls, shape=shape, dtype=dtype, requires_grad=requires_grad, device=dev)
+        Float8TensorStorage.__init__(self, data=data, fp8_scale_inv=fp8_scale_inv, fp8_dtype=fp8_dtype,
+                                     data_transpose=data_transpose, quantizer=quantizer, shape=shape, dtype=dtype)
+        return self
+
+    def __init__(self, *a, **k):
+        pass
+
+    def dequantize(self, *, dtype=None):
+        return QuantizedTensor.dequantize(self, dtype=dtype)
+
+    def _new_like(self, requires_grad=None, clone=False, dtype=None):
+        c = (lambda t: t.clone() if (clone and t is not None) else t)
+        return Float8Tensor(shape=self._shape, dtype=dtype or self._dtype, data=c(self._data),
+                            fp8_scale_inv=c(self._scale_inv), fp8_dtype=self._fp8_dtype,
+                            data_transpose=c(self._transpose), quantizer=self._quantizer,
+                            requires_grad=self.requires_grad if requires_grad is None else requires_grad)
+
+    def __reduce_ex__(self, protocol):
+        return (_make_float8_tensor_in_reduce_ex,
+                (self._data, self._fp8_dtype, self._scale_inv, self._dtype, self._shape, self._transpose))
+
+
+def _make_float8_tensor_in_reduce_ex(data, fp8_dtype, scale_inv, dtype, shape, data_transpose=None):
+    return Float8Tensor(shape=shape, dtype=dtype, data=data, fp8_scale_inv=scale_inv, fp8_dtype=fp8_dtype,
+                        data_transpose=data_transpose)
+
+
+class _Float8QuantizerBase(Quantizer):
+    dtype: torch.dtype
+
+    def _wrap(self, data, tr, scale_inv, shape, hp_dtype, requires_grad=False):
+        if self.internal:
+            return Float8TensorStorage(data=data, fp8_scale_inv=scale_inv, fp8_dtype=self.dtype,
+                                       data_transpose=tr, quantizer=self, shape=shape, dtype=hp_dtype)
+        return Float8Tensor(shape=shape, dtype=hp_dtype, data=data, fp8_scale_inv=scale_inv,
+                            fp8_dtype=self.dtype, data_transpose=tr, quantizer=self, requires_grad=requires_grad)
+
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+        shape = tuple(shape)
+        C = shape[-1]
+        R = 1
+        for s in shape[:-1]:
+            R *= s
+        data = torch.empty(shape, dtype=torch.uint8, device=device) if self.rowwise_usage else None
+        tr = torch.empty(C, R, dtype=torch.uint8, device=device) if self.columnwise_usage else None
+        si = torch.ones(1, dtype=torch.float32, device=device)
+        was, self.internal = self.internal, False
+        try:
+            return self._wrap(data, tr, si, shape, dtype, requires_grad)
+        finally:
+            self.internal = was
+
+
+class Float8Quantizer(_Float8QuantizerBase):
+    """Delayed scaling: the scale is given, the observed amax is recorded.
+
+    ``scale`` and ``amax`` are views into the module's recipe state so that the
+    amax-history update sees what was recorded here.
+    """
+
+    def __init__(self, scale: torch.Tensor, amax: torch.Tensor, fp8_dtype: torch.dtype, *,
+                 rowwise: bool = True, columnwise: bool = True):
+        super().__init__(rowwise=rowwise, columnwise=columnwise)
+        self.scale, self.amax, self.dtype = scale, amax, fp8_dtype
+
+    def quantize_impl(self, tensor, dtype=None):
+        shape = tuple(tensor.shape)
+        x2d = tensor.reshape(-1, shape[-1])
+        data, tr, scale_inv = ops.quantize_fp8(x2d, self.scale, self.dtype, amax_out=self.amax,
+                                               rowwise=self.rowwise_usage, columnwise=self.columnwise_usage)
+        if data is not None:
+            data = data.reshape(shape)
+        return self._wrap(data, tr, scale_inv, shape, dtype or tensor.dtype)
+
+    def update_quantized(self, src, dst, *, noop_flag=None):
+        shape = tuple(dst._shape)
+        x2d = src.reshape(-1, shape[-1])
+        want_row = dst._data is not None or dst._transpose is None
+        data, tr, scale_inv = ops.quantize_fp8(x2d, self.scale, self.dtype, amax_out=self.amax,
+                                               rowwise=want_row, columnwise=dst._transpose is not None)
+        if noop_flag is not None and bool(noop_flag.item()):
+            return dst
+        if data is not None:
+            dst._data = data.reshape(shape) if dst._data is None else dst._data.copy_(data.reshape(shape))
+        if tr is not None:
+            dst._transpose.copy_(tr)
+        if dst._scale_inv is None:
+            dst._scale_inv = scale_inv
+        else:
+            dst._scale_inv.copy_(scale_inv)
+        return dst
+
+    def calibrate(self, tensor):
+        self.amax.copy_(torch.maximum(self.amax.reshape(1), Q.amax_abs(tensor).to(self.amax.device)).reshape(self.amax.shape))
+
+
+class Float8CurrentScalingQuantizer(_Float8QuantizerBase):
+    """Current scaling: amax of the tensor being cast decides its scale."""
+
+    def __init__(self, fp8_dtype: torch.dtype, device=None, *, rowwise=True, columnwise=True,
+                 with_amax_reduction=False, amax_reduction_group=None, force_pow_2_scales=False,
+                 amax_epsilon=0.0):
+        super().__init__(rowwise=rowwise, columnwise=columnwise)
+        self.dtype = fp8_dtype
+        self.with_amax_reduction = with_amax_reduction
+        self.amax_reduction_group = amax_reduction_group
+        self.force_pow_2_scales = force_pow_2_scales
+        self.amax_epsilon = amax_epsilon
+
+    def _scale_for(self, tensor):
+        amax = ops.amax(tensor)
+        if self.with_amax_reduction and self.amax_reduction_group is not None:
+            torch.distributed.all_reduce(amax, op=torch.distributed.ReduceOp.MAX, group=self.amax_reduction_group)
+        return Q.compute_scale_from_amax(amax, Q.fp8_max(self.dtype), 0, self.force_pow_2_scales, self.amax_epsilon)
+
+    def quantize_impl(self, tensor, dtype=None):
+        shape = tuple(tensor.shape)
+        scale = self._scale_for(tensor)
+        data, tr, scale_inv = ops.quantize_fp8(tensor.reshape(-1, shape[-1]), scale, self.dtype,
+                                               rowwise=self.rowwise_usage, columnwise=self.columnwise_usage)
+        if data is not None:
+            data = data.reshape(shape)
+        return self._wrap(data, tr, scale_inv, shape, dtype or tensor.dtype)
+
+    def update_quantized(self, src, dst, *, noop_flag=None):
+        shape = tuple(dst._shape)
+        scale = self._scale_for(src)
+        data, tr, scale_inv = ops.quantize_fp8(src.reshape(-1, shape[-1]), scale, self.dtype,
+                                               rowwise=dst._data is not None or dst._transpose is None,
+                                               columnwise=dst._transpose is not None)
+        if data is not None:
+            dst._data = data.reshape(shape) if dst._data is None else dst._data.copy_(data.reshape(shape))
+        if tr is not None:
+            dst._transpose.copy_(tr)
+        if dst._scale_inv is None:
+            dst._scale_inv = scale_inv
+        else:
+            dst._scale_inv.copy_(scale_inv)
+        return dst

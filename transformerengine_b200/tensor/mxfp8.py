@@ -1,0 +1,191 @@
+"""MXFP8 tensors: FP8 data with one UE8M0 scale per 32 values.
+
+Payload:
+  ``_rowwise_data``      uint8 ``[..., C]``   blocks of 32 along the last dim
+  ``_rowwise_scale_inv`` uint8, 128x4-tile swizzled, padded ``[ru(R,128) * ru(C/32,4)]``
+  ``_columnwise_data``   uint8 ``[C, R]``     TRANSPOSED; blocks of 32 along R
+  ``_columnwise_scale_inv`` uint8 swizzled, padded ``[ru(C,128) * ru(R/32,4)]``
+
+The reference keeps the columnwise copy untransposed
+(``pytorch/tensor/mxfp8_tensor.py:139-180``) and lets cuBLASLt read it
+MN-major; here the quantize kernel writes it transposed at no extra memory
+traffic so that all tcgen05 operands are K-major.  ``to_reference_layout``
+converts for checkpoint exchange.
+"""
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+
+from .. import ops
+from ..ops.ref import quant as Q
+from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+
+
+class MXFP8TensorStorage(QuantizedTensorStorage):
+    def __init__(self, *, rowwise_data, rowwise_scale_inv, columnwise_data, columnwise_scale_inv,
+                 fp8_dtype, quantizer=None, shape=None, dtype=torch.float32):
+        self._rowwise_data = rowwise_data
+        self._rowwise_scale_inv = rowwise_scale_inv
+        self._columnwise_data = columnwise_data
+        self._columnwise_scale_inv = columnwise_scale_inv
+        self._fp8_dtype = fp8_dtype
+        self._quantizer = quantizer
+        self._dtype = dtype
+        self._with_gemm_swizzled_scales = True
+        if shape is None:
+            shape = tuple(rowwise_data.shape) if rowwise_data is not None else tuple(reversed(columnwise_data.shape))
+        self._shape = tuple(shape)
+
+    def get_data_tensors(self):
+        return self._rowwise_data, self._columnwise_data
+
+    def get_usages(self):
+        return {"rowwise": self._rowwise_data is not None, "columnwise": self._columnwise_data is not None}
+
+    def update_usage(self, rowwise_usage=None, columnwise_usage=None):
+        # the two copies are different quantizations: a missing one cannot be rebuilt
+        if rowwise_usage and self._rowwise_data is None:
+            raise RuntimeError("MXFP8 tensor has no rowwise copy")
+        if columnwise_usage and self._columnwise_data is None:
+            raise RuntimeError("MXFP8 tensor has no columnwise copy")
+        if rowwise_usage is False:
+            self._rowwise_data = self._rowwise_scale_inv = None
+        if columnwise_usage is False:
+            self._columnwise_data = self._columnwise_scale_inv = None
+
+    def _dequantize_impl(self, dtype=None):
+        dtype = dtype or self._dtype
+        R, C = self._rows_cols()
+        if self._rowwise_data is not None:
+            out = ops.dequantize_mxfp8(self._rowwise_data.reshape(R, C), self._rowwise_scale_inv,
+                                       self._fp8_dtype, dtype)
+            return out.reshape(self._shape)
+        out = ops.dequantize_mxfp8(self._columnwise_data, self._columnwise_scale_inv, self._fp8_dtype, dtype)
+        return out.t().contiguous().reshape(self._shape)
+
+    def dequantize(self, *, dtype=None):
+        return self._dequantize_impl(dtype)
+
+    def prepare_for_saving(self):
+        ts = [self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv]
+        self._rowwise_data = self._rowwise_scale_inv = None
+        self._columnwise_data = self._columnwise_scale_inv = None
+        return ts, self
+
+    def restore_from_saved(self, tensors):
+        (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data,
+         self._columnwise_scale_inv) = tensors[:4]
+        return tensors[4:]
+
+    def to_reference_layout(self):
+        """(rowwise_data, rowwise_scale [Rp,Kp] compact, columnwise_data [R,C],
+        columnwise_scale [ru(R/32,4), ru(C,128)] compact) as the reference stores them."""
+        R, C = self._rows_cols()
+        rs = cs = cd = None
+        if self._rowwise_scale_inv is not None:
+            rs = Q.pad_scales(Q.unswizzle_scales(self._rowwise_scale_inv, R, C // 32))
+        if self._columnwise_data is not None:
+            cd = self._columnwise_data.t().contiguous().reshape(self._shape)
+            cs_t = Q.unswizzle_scales(self._columnwise_scale_inv, C, R // 32)  # [C, R/32]
+            cs = Q.pad_scales(cs_t.t().contiguous(), 4, 128)
+        return self._rowwise_data, rs, cd, cs
+
+
+class MXFP8Tensor(MXFP8TensorStorage, QuantizedTensor):
+    def __new__(cls, *, shape, dtype, rowwise_data, rowwise_scale_inv, columnwise_data, columnwise_scale_inv,
+                fp8_dtype, quantizer=None, requires_grad=False, device=None):
+        dev = device if device is not None else (rowwise_data if rowwise_data is not None else columnwise_data).device
+        self = QuantizedTensor.__new__(cls, shape=shape, dtype=dtype, requires_grad=requires_grad, device=dev)
+        MXFP8TensorStorage.__init__(self, rowwise_data=rowwise_data, rowwise_scale_inv=rowwise_scale_inv,
+                                    columnwise_data=columnwise_data, columnwise_scale_inv=columnwise_scale_inv,
+                                    fp8_dtype=fp8_dtype, quantizer=quantizer, shape=shape, dtype=dtype)
+        return self
+
+    def __init__(self, *a, **k):
+        pass
+
+    def dequantize(self, *, dtype=None):
+        return QuantizedTensor.dequantize(self, dtype=dtype)
+
+    def _new_like(self, requires_grad=None, clone=False, dtype=None):
+        c = (lambda t: t.clone() if (clone and t is not None) else t)
+        return MXFP8Tensor(shape=self._shape, dtype=dtype or self._dtype, rowwise_data=c(self._rowwise_data),
+                           rowwise_scale_inv=c(self._rowwise_scale_inv), columnwise_data=c(self._columnwise_data),
+                           columnwise_scale_inv=c(self._columnwise_scale_inv), fp8_dtype=self._fp8_dtype,
+                           quantizer=self._quantizer,
+                           requires_grad=self.requires_grad if requires_grad is None else requires_grad)
+
+    def __reduce_ex__(self, protocol):
+        return (_make_mxfp8_tensor_in_reduce_ex,
+                (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
+                 self._fp8_dtype, self._dtype, self._shape, None, True))
+
+
+def _make_mxfp8_tensor_in_reduce_ex(rowwise_data, rowwise_scale_inv, columnwise_data, columnwise_scale_inv,
+                                    fp8_dtype, dtype, shape, quantizer=None, with_gemm_swizzled_scales=True):
+    return MXFP8Tensor(shape=shape, dtype=dtype, rowwise_data=rowwise_data, rowwise_scale_inv=rowwise_scale_inv,
+                       columnwise_data=columnwise_data, columnwise_scale_inv=columnwise_scale_inv,
+                       fp8_dtype=fp8_dtype, quantizer=quantizer)
+
+
+class MXFP8Quantizer(Quantizer):
+    def __init__(self, fp8_dtype: torch.dtype = torch.float8_e4m3fn, *, rowwise=True, columnwise=True):
+        super().__init__(rowwise=rowwise, columnwise=columnwise)
+        self.dtype = fp8_dtype
+
+    def is_quantizable(self, tensor):
+        if tensor.dim() < 2:
+            return False
+        C = tensor.shape[-1]
+        R = tensor.numel() // max(C, 1)
+        return C % 32 == 0 and R % 32 == 0
+
+    def _wrap(self, rd, rs, cd, cs, shape, hp_dtype, requires_grad=False):
+        kw = dict(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd, columnwise_scale_inv=cs,
+                  fp8_dtype=self.dtype, quantizer=self, shape=shape, dtype=hp_dtype)
+        if self.internal:
+            return MXFP8TensorStorage(**kw)
+        return MXFP8Tensor(requires_grad=requires_grad, **kw)
+
+    def quantize_impl(self, tensor, dtype=None):
+        shape = tuple(tensor.shape)
+        x2d = tensor.reshape(-1, shape[-1])
+        rd, rs, cd, cs = ops.quantize_mxfp8(x2d, self.dtype, rowwise=self.rowwise_usage,
+                                            columnwise=self.columnwise_usage)
+        if rd is not None:
+            rd = rd.reshape(shape)
+        return self._wrap(rd, rs, cd, cs, shape, dtype or tensor.dtype)
+
+    def update_quantized(self, src, dst, *, noop_flag=None):
+        shape = tuple(dst._shape)
+        rd, rs, cd, cs = ops.quantize_mxfp8(src.reshape(-1, shape[-1]), self.dtype,
+                                            rowwise=dst._rowwise_data is not None,
+                                            columnwise=dst._columnwise_data is not None)
+        if rd is not None:
+            dst._rowwise_data.copy_(rd.reshape(shape))
+            dst._rowwise_scale_inv.copy_(rs)
+        if cd is not None:
+            dst._columnwise_data.copy_(cd)
+            dst._columnwise_scale_inv.copy_(cs)
+        return dst
+
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+        shape = tuple(shape)
+        C = shape[-1]
+        R = 1
+        for s in shape[:-1]:
+            R *= s
+        rd = rs = cd = cs = None
+        if self.rowwise_usage:
+            rd = torch.empty(shape, dtype=torch.uint8, device=device)
+            rs = torch.zeros(Q.round_up(R, 128) * Q.round_up(C // 32, 4), dtype=torch.uint8, device=device)
+        if self.columnwise_usage:
+            cd = torch.empty(C, R, dtype=torch.uint8, device=device)
+            cs = torch.zeros(Q.round_up(C, 128) * Q.round_up(R // 32, 4), dtype=torch.uint8, device=device)
+        was, self.internal = self.internal, False
+        try:
+            return self._wrap(rd, rs, cd, cs, shape, dtype, requires_grad)
+        finally:
+            self.internal = was

@@ -1,0 +1,220 @@
+"""NVFP4 tensors: E2M1 data, E4M3 scale per 16 values, fp32 amax per tensor.
+
+Payload (reference layout, ``pytorch/tensor/nvfp4_tensor.py:272-327``):
+  ``_rowwise_data``   uint8 ``[R, C/2]``;  ``_rowwise_scale_inv`` E4M3 bytes, swizzled,
+  padded ``[ru(R,128) * ru(C/16,4)]``;  ``_amax_rowwise`` fp32 ``[1]``
+  ``_columnwise_data`` uint8 ``[C, R/2]`` (transposed); ``_columnwise_scale_inv``
+  padded ``[ru(C,128) * ru(R/16,4)]``; ``_amax_columnwise`` fp32 ``[1]``.
+With the random Hadamard transform the columnwise copy holds ``RHT(x^T)``:
+blocks of 16 tokens are rotated by a fixed signed 16x16 Hadamard matrix, which
+cancels in the wgrad GEMM because both operands carry the same rotation.
+"""
+from __future__ import annotations
+
+from typing import Iterable, Optional
+
+import torch
+
+from .. import ops
+from ..ops.ref import quant as Q
+from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+
+
+class NVFP4TensorStorage(QuantizedTensorStorage):
+    def __init__(self, *, rowwise_data, rowwise_scale_inv, columnwise_data, columnwise_scale_inv,
+                 amax_rowwise, amax_columnwise, fp4_dtype=None, quantizer=None, shape=None,
+                 dtype=torch.float32, columnwise_rht=False):
+        self._rowwise_data = rowwise_data
+        self._rowwise_scale_inv = rowwise_scale_inv
+        self._columnwise_data = columnwise_data
+        self._columnwise_scale_inv = columnwise_scale_inv
+        self._amax_rowwise = amax_rowwise
+        self._amax_columnwise = amax_columnwise
+        self._fp4_dtype = fp4_dtype
+        self._quantizer = quantizer
+        self._dtype = dtype
+        self._columnwise_rht = columnwise_rht
+        if shape is None:
+            if rowwise_data is not None:
+                shape = tuple(rowwise_data.shape[:-1]) + (rowwise_data.shape[-1] * 2,)
+            else:
+                shape = (columnwise_data.shape[1] * 2, columnwise_data.shape[0])
+        self._shape = tuple(shape)
+
+    def get_data_tensors(self):
+        return self._rowwise_data, self._columnwise_data
+
+    def get_usages(self):
+        return {"rowwise": self._rowwise_data is not None, "columnwise": self._columnwise_data is not None}
+
+    def update_usage(self, rowwise_usage=None, columnwise_usage=None):
+        if rowwise_usage and self._rowwise_data is None:
+            raise RuntimeError("NVFP4 tensor has no rowwise copy")
+        if columnwise_usage and self._columnwise_data is None:
+            raise RuntimeError("NVFP4 tensor has no columnwise copy")
+        if rowwise_usage is False:
+            self._rowwise_data = self._rowwise_scale_inv = self._amax_rowwise = None
+        if columnwise_usage is False:
+            self._columnwise_data = self._columnwise_scale_inv = self._amax_columnwise = None
+
+    def _dequantize_impl(self, dtype=None):
+        dtype = dtype or self._dtype
+        R, C = self._rows_cols()
+        if self._rowwise_data is not None:
+            out = ops.dequantize_nvfp4(self._rowwise_data.reshape(R, C // 2), self._rowwise_scale_inv,
+                                       self._amax_rowwise, R, C, dtype)
+            return out.reshape(self._shape)
+        out_t = ops.dequantize_nvfp4(self._columnwise_data, self._columnwise_scale_inv,
+                                     self._amax_columnwise, C, R, torch.float32)
+        if self._columnwise_rht:
+            # the Hadamard matrix with signs is orthogonal: undo with its transpose
+            h = Q.hadamard_matrix_16(out_t.device)
+            out_t = (out_t.reshape(C, R // 16, 16) @ h.t()).reshape(C, R)
+        return out_t.t().contiguous().reshape(self._shape).to(dtype)
+
+    def dequantize(self, *, dtype=None):
+        return self._dequantize_impl(dtype)
+
+    def prepare_for_saving(self):
+        ts = [self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
+              self._amax_rowwise, self._amax_columnwise]
+        self._rowwise_data = self._rowwise_scale_inv = self._columnwise_data = None
+        self._columnwise_scale_inv = self._amax_rowwise = self._amax_columnwise = None
+        return ts, self
+
+    def restore_from_saved(self, tensors):
+        (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
+         self._amax_rowwise, self._amax_columnwise) = tensors[:6]
+        return tensors[6:]
+
+
+class NVFP4Tensor(NVFP4TensorStorage, QuantizedTensor):
+    def __new__(cls, *, shape, dtype, rowwise_data, rowwise_scale_inv, columnwise_data, columnwise_scale_inv,
+                amax_rowwise, amax_columnwise, fp4_dtype=None, quantizer=None, requires_grad=False,
+                device=None, columnwise_rht=False):
+        dev = device if device is not None else (rowwise_data if rowwise_data is not None else columnwise_data).device
+        self = QuantizedTensor.__new__(cls, shape=shape, dtype=dtype, requires_grad=requires_grad, device=dev)
+        NVFP4TensorStorage.__init__(self, rowwise_data=rowwise_data, rowwise_scale_inv=rowwise_scale_inv,
+                                    columnwise_data=columnwise_data, columnwise_scale_inv=columnwise_scale_inv,
+                                    amax_rowwise=amax_rowwise, amax_columnwise=amax_columnwise,
+                                    fp4_dtype=fp4_dtype, quantizer=quantizer, shape=shape, dtype=dtype,
+                                    columnwise_rht=columnwise_rht)
+        return self
+
+    def __init__(self, *a, **k):
+        pass
+
+    def dequantize(self, *, dtype=None):
+        return QuantizedTensor.dequantize(self, dtype=dtype)
+
+    def _new_like(self, requires_grad=None, clone=False, dtype=None):
+        c = (lambda t: t.clone() if (clone and t is not None) else t)
+        return NVFP4Tensor(shape=self._shape, dtype=dtype or self._dtype, rowwise_data=c(self._rowwise_data),
+                           rowwise_scale_inv=c(self._rowwise_scale_inv), columnwise_data=c(self._columnwise_data),
+                           columnwise_scale_inv=c(self._columnwise_scale_inv), amax_rowwise=c(self._amax_rowwise),
+                           amax_columnwise=c(self._amax_columnwise), fp4_dtype=self._fp4_dtype,
+                           quantizer=self._quantizer, columnwise_rht=self._columnwise_rht,
+                           requires_grad=self.requires_grad if requires_grad is None else requires_grad)
+
+    def __reduce_ex__(self, protocol):
+        return (_make_nvfp4_tensor_in_reduce_ex,
+                (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
+                 self._amax_rowwise, self._amax_columnwise, self._fp4_dtype, self._dtype, self._shape,
+                 self._columnwise_rht))
+
+
+def _make_nvfp4_tensor_in_reduce_ex(rd, rs, cd, cs, ar, ac, fp4_dtype, dtype, shape, columnwise_rht=False):
+    return NVFP4Tensor(shape=shape, dtype=dtype, rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd,
+                       columnwise_scale_inv=cs, amax_rowwise=ar, amax_columnwise=ac, fp4_dtype=fp4_dtype,
+                       columnwise_rht=columnwise_rht)
+
+
+class NVFP4Quantizer(Quantizer):
+    """NVFP4 builder.
+
+    ``with_rht`` rotates the columnwise (transposed) copy; ``with_2d_quantization``
+    uses 16x16 blocks (weights) so that the rowwise and columnwise copies
+    dequantize to the same values; ``stochastic_rounding`` for gradients.
+    """
+
+    def __init__(self, fp4_dtype=None, *, rowwise=True, columnwise=True, with_amax_reduction=False,
+                 amax_reduction_group=None, with_rht=False, with_post_rht_amax=True,
+                 with_2d_quantization=False, stochastic_rounding=False, with_random_sign_mask=True):
+        super().__init__(rowwise=rowwise, columnwise=columnwise)
+        self.dtype = fp4_dtype
+        self.with_amax_reduction = with_amax_reduction
+        self.amax_reduction_group = amax_reduction_group
+        self.with_rht = with_rht
+        self.with_post_rht_amax = with_post_rht_amax
+        self.with_2d_quantization = with_2d_quantization
+        self.stochastic_rounding = stochastic_rounding
+        self.generator: Optional[torch.Generator] = None
+
+    def is_quantizable(self, tensor):
+        if tensor.dim() < 2:
+            return False
+        C = tensor.shape[-1]
+        R = tensor.numel() // max(C, 1)
+        return C % 16 == 0 and R % 16 == 0
+
+    def _reduce(self, amax):
+        if self.with_amax_reduction and self.amax_reduction_group is not None:
+            torch.distributed.all_reduce(amax, op=torch.distributed.ReduceOp.MAX, group=self.amax_reduction_group)
+        return amax
+
+    def _wrap(self, parts, shape, hp_dtype, requires_grad=False):
+        rd, rs, ar, cd, cs, ac = parts
+        kw = dict(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd, columnwise_scale_inv=cs,
+                  amax_rowwise=ar, amax_columnwise=ac, fp4_dtype=self.dtype, quantizer=self, shape=shape,
+                  dtype=hp_dtype, columnwise_rht=self.with_rht)
+        if self.internal:
+            return NVFP4TensorStorage(**kw)
+        return NVFP4Tensor(requires_grad=requires_grad, **kw)
+
+    def _quantize_parts(self, x2d, rowwise, columnwise):
+        return ops.quantize_nvfp4(x2d, rowwise=rowwise, columnwise=columnwise, with_rht=self.with_rht,
+                                  with_2d=self.with_2d_quantization, stochastic_rounding=self.stochastic_rounding,
+                                  amax_reduce=self._reduce, generator=self.generator)
+
+    def quantize_impl(self, tensor, dtype=None):
+        shape = tuple(tensor.shape)
+        parts = self._quantize_parts(tensor.reshape(-1, shape[-1]), self.rowwise_usage, self.columnwise_usage)
+        rd = parts[0]
+        if rd is not None:
+            parts = (rd.reshape(shape[:-1] + (shape[-1] // 2,)),) + tuple(parts[1:])
+        return self._wrap(parts, shape, dtype or tensor.dtype)
+
+    def update_quantized(self, src, dst, *, noop_flag=None):
+        shape = tuple(dst._shape)
+        rd, rs, ar, cd, cs, ac = self._quantize_parts(src.reshape(-1, shape[-1]), dst._rowwise_data is not None,
+                                                     dst._columnwise_data is not None)
+        if rd is not None:
+            dst._rowwise_data.copy_(rd.reshape(dst._rowwise_data.shape))
+            dst._rowwise_scale_inv.copy_(rs)
+            dst._amax_rowwise.copy_(ar)
+        if cd is not None:
+            dst._columnwise_data.copy_(cd)
+            dst._columnwise_scale_inv.copy_(cs)
+            dst._amax_columnwise.copy_(ac)
+        return dst
+
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+        shape = tuple(shape)
+        C = shape[-1]
+        R = 1
+        for s in shape[:-1]:
+            R *= s
+        rd = rs = ar = cd = cs = ac = None
+        if self.rowwise_usage:
+            rd = torch.empty(shape[:-1] + (C // 2,), dtype=torch.uint8, device=device)
+            rs = torch.zeros(Q.round_up(R, 128) * Q.round_up(C // 16, 4), dtype=torch.uint8, device=device)
+            ar = torch.zeros(1, dtype=torch.float32, device=device)
+        if self.columnwise_usage:
+            cd = torch.empty(C, R // 2, dtype=torch.uint8, device=device)
+            cs = torch.zeros(Q.round_up(C, 128) * Q.round_up(R // 16, 4), dtype=torch.uint8, device=device)
+            ac = torch.zeros(1, dtype=torch.float32, device=device)
+        was, self.internal = self.internal, False
+        try:
+            return self._wrap((rd, rs, ar, cd, cs, ac), shape, dtype, requires_grad)
+        finally:
+            self.internal = was

@@ -1,5 +1,29 @@
-"""B200-native low-precision transformer library (PyTorch front end)."""
+"""B200-native low-precision transformer library (PyTorch front end).
+
+Public surface mirrors ``transformer_engine.pytorch``: the modules ``Linear``,
+``LayerNormLinear``, ``LayerNormMLP``, ``GroupedLinear``, ``LayerNorm``,
+``RMSNorm``, ``DotProductAttention``, ``MultiheadAttention``,
+``TransformerLayer``; ``autocast`` / ``fp8_autocast`` with the recipes in
+``transformerengine_b200.recipe``; ``quantized_model_init``; ``checkpoint``;
+fused optimizers.  CUDA tensors run hand-written sm_100a kernels; CPU tensors run
+a pure-PyTorch reference path with the same numerics.
+"""
 from .common import recipe  # noqa: F401
 from . import ops  # noqa: F401
 from .ops import check_status  # noqa: F401
 from . import tensor  # noqa: F401
+from .quantization import (autocast, fp8_autocast, quantized_model_init, fp8_model_init, FP8GlobalStateManager,
+                           is_fp8_available, is_mxfp8_available, is_nvfp4_available,
+                           is_fp8_block_scaling_available, get_default_fp8_recipe, get_default_recipe)
+from .modules.linear import Linear
+from .modules.layernorm_linear import LayerNormLinear, LayerNorm, RMSNorm
+from .modules.layernorm_mlp import LayerNormMLP
+from .attention.dot_product_attention import DotProductAttention
+from .attention.multi_head_attention import MultiheadAttention
+from .attention.rope import RotaryPositionEmbedding, apply_rotary_pos_emb
+from .transformer import TransformerLayer
+from .parallel.distributed import checkpoint, CudaRNGStatesTracker
+from .optim import FusedAdam, FusedSGD
+from . import optim as optimizers  # noqa: F401
+
+__version__ = "0.1.0"

@@ -1,0 +1,197 @@
+"""``DotProductAttention``: softmax(Q K^T / sqrt(d) + mask) V with GQA, the mask
+types, sliding windows, bias, softmax variants, packed (thd) sequences, KV cache
+and context parallelism (reference: ``pytorch/attention/dot_product_attention/
+dot_product_attention.py:415-1380``, backend selection ``utils.py:393``).
+"""
+from __future__ import annotations
+
+import math
+import os
+from typing import Any, Callable, Dict, List, Optional, Tuple, Union
+
+import torch
+
+from .. import ops
+from ..parallel import distributed as D
+
+_MASK_TYPES = ("no_mask", "padding", "causal", "padding_causal", "causal_bottom_right",
+               "padding_causal_bottom_right", "arbitrary")
+
+
+def _padding_mask_from_cu(cu_q, cu_kv, sq, sk, device):
+    """[b,1,sq,sk] bool, True = masked, from cumulative sequence lengths."""
+    lq = (cu_q[1:] - cu_q[:-1]).to(device)
+    lk = (cu_kv[1:] - cu_kv[:-1]).to(device)
+    qi = torch.arange(sq, device=device)[None, :, None]
+    ki = torch.arange(sk, device=device)[None, None, :]
+    m = (qi >= lq[:, None, None]) | (ki >= lk[:, None, None])
+    return m[:, None]
+
+
+class DotProductAttention(torch.nn.Module):
+    def __init__(self, num_attention_heads: int, kv_channels: Union[int, Tuple[int, int]],
+                 num_gqa_groups: Optional[int] = None, attention_dropout: float = 0.0, qkv_format: str = "sbhd",
+                 attn_mask_type: str = "causal", window_size: Optional[Tuple[int, int]] = None,
+                 sequence_parallel: bool = False, tp_size: int = 1, get_rng_state_tracker: Optional[Callable] = None,
+                 tp_group=None, layer_number: Optional[int] = None, attention_type: str = "self", cp_group=None,
+                 cp_global_ranks: Optional[List[int]] = None, cp_stream=None, cp_comm_type: str = "p2p",
+                 softmax_scale: Optional[float] = None, softmax_type: str = "vanilla",
+                 return_max_logit: bool = False) -> None:
+        super().__init__()
+        assert attn_mask_type in _MASK_TYPES, f"unknown attn_mask_type {attn_mask_type}"
+        assert qkv_format in ("sbhd", "bshd", "thd")
+        self.qkv_format = qkv_format
+        self.attn_mask_type = attn_mask_type
+        self.window_size = window_size
+        self.tp_size = tp_size if tp_group is None else D.get_world_size(tp_group)
+        self.tp_group = tp_group
+        self.get_rng_state_tracker = get_rng_state_tracker
+        self.layer_number = layer_number
+        self.attention_type = attention_type
+        self.cp_group, self.cp_global_ranks, self.cp_stream, self.cp_comm_type = cp_group, cp_global_ranks, cp_stream, cp_comm_type
+        kv = kv_channels if isinstance(kv_channels, int) else kv_channels[0]
+        self.hidden_size_per_attention_head = kv
+        self.num_gqa_groups = num_attention_heads if num_gqa_groups is None else num_gqa_groups
+        self.num_attention_heads = num_attention_heads
+        self.num_heads_per_partition = num_attention_heads // self.tp_size
+        self.num_gqa_groups_per_partition = max(self.num_gqa_groups // self.tp_size, 1)
+        self.softmax_scale = softmax_scale if softmax_scale is not None else 1.0 / math.sqrt(kv)
+        self.attention_dropout = attention_dropout
+        self.softmax_type = softmax_type
+        self.softmax_offset = None
+        if softmax_type == "learnable":
+            self.softmax_offset = torch.nn.Parameter(torch.zeros(self.num_heads_per_partition,
+                                                                 device="cuda" if torch.cuda.is_available() else "cpu"))
+        # reference checkpoints carry an (empty) extra state for the core attention
+        self.register_load_state_dict_post_hook(self._ignore_missing_extra_state)
+
+    @staticmethod
+    def _ignore_missing_extra_state(module, incompatible):
+        for k in list(incompatible.missing_keys):
+            if k.endswith("_extra_state"):
+                incompatible.missing_keys.remove(k)
+
+    def get_extra_state(self):
+        return torch.empty(0, dtype=torch.uint8)
+
+    def set_extra_state(self, state):
+        return
+
+    def set_context_parallel_group(self, cp_group, cp_global_ranks, cp_stream, cp_comm_type="p2p") -> None:
+        self.cp_group, self.cp_global_ranks, self.cp_stream, self.cp_comm_type = cp_group, cp_global_ranks, cp_stream, cp_comm_type
+
+    # ------------------------------------------------------------------
+    def forward(self, query_layer: torch.Tensor, key_layer: torch.Tensor, value_layer: torch.Tensor,
+                attention_mask=None, qkv_format: Optional[str] = None, cu_seqlens_q: Optional[torch.Tensor] = None,
+                cu_seqlens_kv: Optional[torch.Tensor] = None, cu_seqlens_q_padded=None, cu_seqlens_kv_padded=None,
+                max_seqlen_q: Optional[int] = None, max_seqlen_kv: Optional[int] = None,
+                attn_mask_type: Optional[str] = None, window_size: Optional[Tuple[int, int]] = None,
+                checkpoint_core_attention: bool = False, core_attention_bias_type: str = "no_bias",
+                core_attention_bias: Optional[torch.Tensor] = None, alibi_slopes: Optional[torch.Tensor] = None,
+                fast_zero_fill: bool = True, inference_params=None, pad_between_seqs: Optional[bool] = None):
+        fmt = qkv_format or self.qkv_format
+        mask_type = attn_mask_type or self.attn_mask_type
+        window = window_size if window_size is not None else self.window_size
+        if inference_params is not None:
+            query_layer, key_layer, value_layer, fmt, mask_type, cu_seqlens_q, cu_seqlens_kv = \
+                inference_params.step(self.layer_number, query_layer, key_layer, value_layer, fmt, mask_type)
+        if checkpoint_core_attention:
+            def run(q, k, v):
+                return self._core(q, k, v, fmt, mask_type, window, attention_mask, cu_seqlens_q, cu_seqlens_kv,
+                                  core_attention_bias_type, core_attention_bias, alibi_slopes)
+            return D.checkpoint(run, query_layer, key_layer, value_layer,
+                                get_rng_state_tracker=self.get_rng_state_tracker)
+        return self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
+                          cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes)
+
+    def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes):
+        if fmt == "thd":
+            return self._thd(q, k, v, mask_type, window, cu_q, cu_kv)
+        # -> [b, h, s, d] views
+        if fmt == "sbhd":
+            qb, kb, vb = (t.permute(1, 2, 0, 3) for t in (q, k, v))
+        else:
+            qb, kb, vb = (t.permute(0, 2, 1, 3) for t in (q, k, v))
+        b, hq, sq, d = qb.shape
+        sk = kb.shape[2]
+        causal = "causal" in mask_type
+        bottom_right = "bottom_right" in mask_type or (causal and self.attention_type == "cross")
+        mask = None
+        if "padding" in mask_type:
+            if attention_mask is not None:
+                if isinstance(attention_mask, (tuple, list)):
+                    mq, mk = attention_mask
+                    mask = mq.reshape(b, 1, sq, 1) | mk.reshape(b, 1, 1, sk)
+                else:
+                    mask = attention_mask
+                    if mask.dim() == 4 and mask.shape[-2] == 1 and sq > 1:
+                        mask = mask.reshape(b, 1, 1, sk) | mask.reshape(b, 1, sk, 1)[:, :, :sq]
+            elif cu_q is not None:
+                mask = _padding_mask_from_cu(cu_q, cu_kv if cu_kv is not None else cu_q, sq, sk, qb.device)
+        elif mask_type == "arbitrary":
+            mask = attention_mask
+        the_bias = None
+        if bias_type == "alibi":
+            the_bias = _alibi_bias(hq, sq, sk, alibi_slopes, qb.device, bottom_right)
+        elif bias_type != "no_bias":
+            the_bias = bias
+        dropout = self.attention_dropout if self.training else 0.0
+        if self.cp_group is not None and D.get_world_size(self.cp_group) > 1:
+            from ..parallel.context_parallel import attn_forward_func_with_cp
+
+            o = attn_forward_func_with_cp(qb, kb, vb, cp_group=self.cp_group, cp_comm_type=self.cp_comm_type,
+                                          scale=self.softmax_scale, causal=causal, window=window,
+                                          cp_global_ranks=self.cp_global_ranks, cp_stream=self.cp_stream)
+        else:
+            ctx = self.get_rng_state_tracker().fork() if (self.get_rng_state_tracker is not None and dropout > 0) \
+                else _null()
+            with ctx:
+                o = ops.attention(qb, kb, vb, scale=self.softmax_scale, causal=causal, window=window, attn_mask=mask,
+                                  bias=the_bias, dropout_p=dropout, softmax_type=self.softmax_type,
+                                  sink=self.softmax_offset, bottom_right=bottom_right or sq == sk)
+        if fmt == "sbhd":
+            return o.permute(2, 0, 1, 3).reshape(sq, b, hq * o.shape[-1])
+        return o.permute(0, 2, 1, 3).reshape(b, sq, hq * o.shape[-1])
+
+    def _thd(self, q, k, v, mask_type, window, cu_q, cu_kv):
+        assert cu_q is not None, "thd format needs cu_seqlens_q"
+        cu_kv = cu_kv if cu_kv is not None else cu_q
+        cq, ck = cu_q.tolist(), cu_kv.tolist()
+        causal = "causal" in mask_type
+        outs = []
+        for i in range(len(cq) - 1):
+            qi = q[cq[i]:cq[i + 1]].permute(1, 0, 2).unsqueeze(0)
+            ki = k[ck[i]:ck[i + 1]].permute(1, 0, 2).unsqueeze(0)
+            vi = v[ck[i]:ck[i + 1]].permute(1, 0, 2).unsqueeze(0)
+            if qi.shape[2] == 0:
+                continue
+            o = ops.attention(qi, ki, vi, scale=self.softmax_scale, causal=causal, window=window,
+                              softmax_type=self.softmax_type, sink=self.softmax_offset,
+                              bottom_right="bottom_right" in mask_type or qi.shape[2] == ki.shape[2])
+            outs.append(o.squeeze(0).permute(1, 0, 2))
+        o = torch.cat(outs, dim=0)
+        if o.shape[0] < q.shape[0]:  # padding tokens after the last sequence
+            o = torch.cat([o, o.new_zeros(q.shape[0] - o.shape[0], *o.shape[1:])], dim=0)
+        return o.reshape(o.shape[0], -1)
+
+
+class _null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        return False
+
+
+def _alibi_bias(h, sq, sk, slopes, device, bottom_right=True):
+    if slopes is None:
+        n = 2 ** math.floor(math.log2(h))
+        m0 = 2.0 ** (-8.0 / n)
+        slopes = torch.pow(m0, torch.arange(1, 1 + n))
+        if n < h:
+            m1 = 2.0 ** (-4.0 / n)
+            slopes = torch.cat([slopes, torch.pow(m1, torch.arange(1, 1 + 2 * (h - n), 2))])
+    slopes = slopes.to(device).float().reshape(1, h, 1, 1)
+    qi = torch.arange(sq, device=device)[:, None] + ((sk - sq) if bottom_right else 0)
+    ki = torch.arange(sk, device=device)[None, :]
+    return -slopes * (qi - ki).abs().float()[None, None]

@@ -1,0 +1,75 @@
+"""Rotary position embeddings (reference: ``pytorch/attention/rope.py:18-345``)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+
+
+class RotaryPositionEmbedding(torch.nn.Module):
+    """Produces the angle table ``[seq, 1, 1, dim]`` (fp32) consumed by :func:`apply_rotary_pos_emb`."""
+
+    def __init__(self, dim: int, rotary_percent: float = 1.0, seq_len_interpolation_factor: Optional[int] = None,
+                 pretrained_max_position_embeddings: Optional[int] = None, rotary_base: float = 10000.0,
+                 interleaved: bool = False):
+        super().__init__()
+        if rotary_percent < 1.0:
+            dim = int(dim * rotary_percent)
+        self.dim = dim
+        self.seq_len_interpolation_factor = seq_len_interpolation_factor
+        self.rotary_base = rotary_base
+        self.pretrained_max_position_embeddings = pretrained_max_position_embeddings
+        self.interleaved = interleaved
+
+    def forward(self, max_seq_len: int, offset: int = 0) -> torch.Tensor:
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        seq = torch.arange(max_seq_len, device=dev, dtype=torch.float32) + offset
+        if self.pretrained_max_position_embeddings is not None and self.seq_len_interpolation_factor is not None:
+            if max_seq_len > self.pretrained_max_position_embeddings * self.seq_len_interpolation_factor:
+                seq = seq * (self.pretrained_max_position_embeddings / max_seq_len)
+            else:
+                seq = seq / self.seq_len_interpolation_factor
+        emb = ops.rope_freqs(seq, self.dim, self.rotary_base, self.interleaved)
+        return emb.reshape(emb.shape[0], 1, 1, emb.shape[1])
+
+
+class _RopeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, t, freqs, fmt, interleaved, cp_size, cp_rank, start_positions):  # type: ignore[override]
+        x = t if fmt == "sbhd" else t.transpose(0, 1)
+        f = freqs.reshape(freqs.shape[0], freqs.shape[-1])
+        y = ops.rope_apply(x, f, interleaved=interleaved, cp_size=cp_size, cp_rank=cp_rank,
+                           start_positions=start_positions)
+        ctx.save_for_backward(f, start_positions if start_positions is not None else torch.empty(0))
+        ctx.cfg = (fmt, interleaved, cp_size, cp_rank, start_positions is not None)
+        return y if fmt == "sbhd" else y.transpose(0, 1)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        f, sp = ctx.saved_tensors
+        fmt, interleaved, cp_size, cp_rank, has_sp = ctx.cfg
+        x = g if fmt == "sbhd" else g.transpose(0, 1)
+        if x.stride(-1) != 1:
+            x = x.contiguous()
+        y = ops.rope_apply(x, f, interleaved=interleaved, backward=True, cp_size=cp_size, cp_rank=cp_rank,
+                           start_positions=sp if has_sp else None)
+        return (y if fmt == "sbhd" else y.transpose(0, 1)), None, None, None, None, None, None
+
+
+def apply_rotary_pos_emb(t: torch.Tensor, freqs: torch.Tensor, tensor_format: str = "sbhd",
+                         start_positions: Optional[torch.Tensor] = None, interleaved: bool = False,
+                         fused: bool = True, cu_seqlens: Optional[torch.Tensor] = None, cp_size: int = 1,
+                         cp_rank: int = 0) -> torch.Tensor:
+    """Rotate the first ``freqs.shape[-1]`` channels of ``t`` (``sbhd``, ``bshd`` or ``thd``)."""
+    if tensor_format == "thd":
+        assert cu_seqlens is not None, "thd format needs cu_seqlens"
+        outs = []
+        cs = cu_seqlens.tolist()
+        for i in range(len(cs) - 1):
+            seg = t[cs[i] // cp_size:cs[i + 1] // cp_size].unsqueeze(1)  # [s,1,h,d]
+            outs.append(_RopeFn.apply(seg, freqs, "sbhd", interleaved, cp_size, cp_rank, None).squeeze(1))
+        return torch.cat(outs, dim=0)
+    assert tensor_format in ("sbhd", "bshd")
+    return _RopeFn.apply(t, freqs, tensor_format, interleaved, cp_size, cp_rank, start_positions)

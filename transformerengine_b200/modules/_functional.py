@@ -1,0 +1,136 @@
+"""Shared forward/backward building blocks of the linear-family modules.
+
+``fprop``:  ``y = x @ W^T (+ b)``            operands: x rowwise, W rowwise
+``dgrad``:  ``dx = dy @ W``                  operands: dy rowwise, W columnwise
+``wgrad``:  ``dW = dy^T @ x``                operands: dy columnwise, x columnwise
+(reference data flow: ``pytorch/module/linear.py:268-1352``).  Tensor parallel:
+column-parallel layers all-gather a sequence-sharded input before fprop and
+reduce-scatter (or all-reduce) dgrad; row-parallel layers reduce-scatter (or
+all-reduce) the fprop output and all-gather grad_output.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..ops.gemm import as_operand, gemm_nt
+from ..parallel import distributed as D
+from ..tensor.base import QuantizedTensorStorage, Quantizer
+from ..tensor.mxfp8 import MXFP8Quantizer, MXFP8TensorStorage
+
+
+@dataclass
+class LinearConfig:
+    """Static settings of one GEMM of a module."""
+
+    parallel_mode: Optional[str] = None  # None | "column" | "row"
+    sequence_parallel: bool = False
+    tp_group: Any = None
+    tp_size: int = 1
+    fuse_wgrad_accumulation: bool = False
+    activation_dtype: torch.dtype = torch.float32
+    wgrad_store: Any = None
+    comm_overlap: Any = None  # parallel.comm_gemm.CommGemm when fused collectives are enabled
+    name: str = ""
+
+
+def _is_q(t) -> bool:
+    return isinstance(t, QuantizedTensorStorage)
+
+
+def quantize_for_gemm(x2d: torch.Tensor, quantizer: Optional[Quantizer], rowwise: bool, columnwise: bool):
+    """Quantize an activation / gradient for the GEMMs that will consume it."""
+    if quantizer is None or _is_q(x2d):
+        return x2d
+    if not quantizer.is_quantizable(x2d):
+        return x2d
+    quantizer.set_usage(rowwise=rowwise, columnwise=columnwise)
+    quantizer.internal = True
+    return quantizer(x2d)
+
+
+def gather_input(x, cfg: LinearConfig, quantizer, rowwise: bool, columnwise: bool):
+    """Sequence-parallel all-gather (+ quantize) of a column-parallel layer's input."""
+    local_rows = x.shape[0] if not _is_q(x) else x._rows_cols()[0]
+    if quantizer is not None and isinstance(quantizer, MXFP8Quantizer) and local_rows % 128 == 0:
+        q = quantize_for_gemm(x, quantizer, rowwise, columnwise)
+        if isinstance(q, MXFP8TensorStorage):
+            return D.gather_mxfp8_along_first_dim(q, cfg.tp_group)
+    if _is_q(x):
+        x = x.dequantize()
+    total, _ = D.gather_along_first_dim(x, cfg.tp_group)
+    return quantize_for_gemm(total, quantizer, rowwise, columnwise)
+
+
+def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False):
+    """``x`` [T, in] (plain or quantized, already gathered), ``w`` [out, in].
+    Returns (out2d after the row-parallel collective, pre-gelu aux or None)."""
+    aux = None
+    fuse_bias = bias is not None and not (cfg.parallel_mode == "row" and cfg.tp_size > 1)
+    a, b = as_operand(x, "rowwise"), as_operand(w, "rowwise")
+    if gelu:
+        aux = torch.empty(a.rows, b.rows, dtype=out_dtype, device=a.data.device)
+        out = gemm_nt(a, b, out_dtype=out_dtype, bias=bias if fuse_bias else None, epilogue=ops.gemm.EPI_GELU, aux=aux)
+    else:
+        out = gemm_nt(a, b, out_dtype=out_dtype, bias=bias if fuse_bias else None)
+    if cfg.parallel_mode == "row" and cfg.tp_size > 1:
+        if cfg.sequence_parallel:
+            out, _ = D.reduce_scatter_along_first_dim(out, cfg.tp_group)
+        else:
+            out, _ = D.allreduce(out, cfg.tp_group)
+        if bias is not None:
+            out = out + bias.to(out.dtype)
+    return out, aux
+
+
+def linear_dgrad(dy, w, cfg: LinearConfig, out_dtype, *, async_comm: bool = False):
+    """``dx = dy @ W``; column-parallel layers then reduce-scatter / all-reduce.
+    Returns (dx2d, comm handle or None)."""
+    a, b = as_operand(dy, "rowwise"), as_operand(w, "columnwise")
+    dx = gemm_nt(a, b, out_dtype=out_dtype)
+    h = None
+    if cfg.parallel_mode == "column" and cfg.tp_size > 1:
+        if cfg.sequence_parallel:
+            dx, h = D.reduce_scatter_along_first_dim(dx, cfg.tp_group, async_op=async_comm)
+        else:
+            dx, h = D.allreduce(dx, cfg.tp_group, async_op=async_comm)
+    return dx, h
+
+
+def linear_wgrad(dy, x, weight: torch.Tensor, cfg: LinearConfig):
+    """``dW = dy^T @ x``.  With ``fuse_wgrad_accumulation`` the product is accumulated into
+    ``weight.main_grad`` (fp32) inside the GEMM epilogue and a dummy is returned."""
+    a, b = as_operand(dy, "columnwise"), as_operand(x, "columnwise")
+
+    def run():
+        if cfg.fuse_wgrad_accumulation and hasattr(weight, "main_grad"):
+            first = getattr(weight, "overwrite_main_grad", False) or not getattr(weight, "grad_added_to_main_grad_once", True)
+            gemm_nt(a, b, out=weight.main_grad.reshape(a.rows, b.rows), accumulate=not first)
+            return None
+        return gemm_nt(a, b, out_dtype=weight.dtype if weight.dtype in (torch.bfloat16, torch.float16, torch.float32)
+                       else cfg.activation_dtype)
+
+    if cfg.wgrad_store is not None and cfg.wgrad_store.delay_wgrad_compute():
+        def deferred():
+            g = run()
+            if g is not None:
+                weight.grad = g if weight.grad is None else weight.grad + g
+        cfg.wgrad_store.put(deferred)
+        return None
+    g = run()
+    if g is None:
+        if hasattr(weight, "grad_added_to_main_grad"):
+            weight.grad_added_to_main_grad = True
+            weight.grad_added_to_main_grad_once = True
+            return torch.zeros(1, dtype=weight.dtype, device=weight.device).expand(weight.shape) \
+                if getattr(weight, "zero_out_wgrad", False) else \
+                torch.empty(1, dtype=weight.dtype, device=weight.device).expand(weight.shape)
+        return None
+    return g.reshape(weight.shape)
+
+
+def bias_grad(dy2d: torch.Tensor, dtype) -> torch.Tensor:
+    return dy2d.float().sum(dim=0).to(dtype)

@@ -1,0 +1,281 @@
+"""Base class of all modules that run quantized GEMMs.
+
+Holds the per-module recipe state (quantizers for input / weight / output of
+each GEMM in the forward and grad_output / grad_input in the backward), the
+quantized-weight cache, tensor-parallel settings and the ``_extra_state``
+checkpoint entry (reference: ``pytorch/module/base.py:575-1480``).
+"""
+from __future__ import annotations
+
+import io
+import pickle
+import warnings
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..common.recipe import DelayedScaling, Recipe
+from ..quantization import FP8GlobalStateManager, RecipeState, DelayedScalingRecipeState
+from ..tensor.base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+
+# bumped by the optimizers of this library after they update parameters in place
+# through raw pointers (which does not touch torch's version counters)
+_WEIGHTS_EPOCH = [0]
+
+
+def bump_weights_epoch() -> None:
+    _WEIGHTS_EPOCH[0] += 1
+
+
+def weights_epoch() -> int:
+    return _WEIGHTS_EPOCH[0]
+
+
+def get_distributed_world_size(group=None) -> int:
+    if not torch.distributed.is_available() or not torch.distributed.is_initialized():
+        return 1
+    return torch.distributed.get_world_size(group=group)
+
+
+def get_distributed_rank(group=None) -> int:
+    if not torch.distributed.is_available() or not torch.distributed.is_initialized():
+        return 0
+    return torch.distributed.get_rank(group=group)
+
+
+def _default_init(std: float = 0.023):
+    def init_(t):
+        return torch.nn.init.normal_(t, mean=0.0, std=std)
+    return init_
+
+
+def get_default_init_method():
+    return _default_init(0.023)
+
+
+_UNSAFE_PICKLE_ENV = "NVTE_ALLOW_UNSAFE_PICKLE_EXTRA_STATE"
+
+
+class _SafeUnpickler(pickle.Unpickler):
+    """Only recipe classes, torch tensors rebuilt by torch, and builtins may be loaded."""
+
+    _ALLOWED_PREFIXES = ("transformer_engine.common.recipe", "transformerengine_b200.common.recipe", "torch",
+                         "collections", "builtins", "numpy", "_codecs")
+
+    def find_class(self, module, name):
+        if module.startswith(self._ALLOWED_PREFIXES):
+            if module.startswith("transformer_engine.common.recipe"):
+                from ..common import recipe as r
+                return getattr(r, name)
+            return super().find_class(module, name)
+        raise pickle.UnpicklingError(f"refusing to load {module}.{name} from _extra_state")
+
+
+class TransformerEngineBaseModule(torch.nn.Module):
+    def __init__(self) -> None:
+        super().__init__()
+        self.fp8 = False
+        self.fp8_calibration = False
+        self.fp8_initialized = False
+        self.fp8_meta: Dict[str, Any] = {"recipe": None, "num_gemms": 1, "fp8_checkpoint": False}
+        self.quantizers: Dict[str, List[Optional[Quantizer]]] = {"scaling_fwd": [], "scaling_bwd": []}
+        self._states: Dict[str, Optional[RecipeState]] = {"scaling_fwd": None, "scaling_bwd": None}
+        self._weight_cache: Dict[str, Any] = {}
+        self.tp_group = None
+        self.tp_size = 1
+        self.sequence_parallel = False
+        self.primary_weights_in_fp8 = FP8GlobalStateManager.with_fp8_parameters()
+        self.preserve_high_precision_init_val = FP8GlobalStateManager.with_high_precision_init_val()
+        self.name = None
+        self.wgrad_store = None
+        self.fuse_wgrad_accumulation = False
+
+    # ------------------------------------------------------------------ TP
+    def set_tensor_parallel_group(self, tp_group) -> None:
+        self.tp_group = tp_group
+        self.tp_size = get_distributed_world_size(tp_group)
+
+    # ------------------------------------------------------------------ recipe state
+    def init_fp8_metadata(self, num_gemms: int = 1) -> None:
+        """(Re)build quantizers when entering a quantized region or when the recipe changed."""
+        self.fp8 = FP8GlobalStateManager.is_fp8_enabled()
+        self.fp8_calibration = FP8GlobalStateManager.is_fp8_calibration()
+        self.fp8_meta["fp8_checkpoint"] = self.fp8 or self.fp8_calibration or self.fp8_meta["fp8_checkpoint"]
+        if not (self.fp8 or self.fp8_calibration):
+            return
+        recipe = FP8GlobalStateManager.get_fp8_recipe()
+        cur = self.fp8_meta.get("recipe")
+        same = self.fp8_initialized and cur is not None and type(cur) is type(recipe) and \
+            self.fp8_meta.get("num_gemms") == num_gemms
+        if same and recipe.delayed():
+            same = cur.amax_history_len == recipe.amax_history_len
+        self.fp8_meta["recipe"] = recipe
+        self.fp8_meta["num_gemms"] = num_gemms
+        if same:
+            # keep states, but follow changes of margin/format made on a new recipe object
+            for st in self._states.values():
+                if st is not None:
+                    st.recipe = recipe
+            return
+        dev = self._param_device()
+        self._states["scaling_fwd"] = RecipeState.create(recipe, mode="forward", num_quantizers=3 * num_gemms, device=dev)
+        self._states["scaling_bwd"] = RecipeState.create(recipe, mode="backward", num_quantizers=2 * num_gemms, device=dev)
+        self.quantizers["scaling_fwd"] = self._states["scaling_fwd"].make_quantizers()
+        self.quantizers["scaling_bwd"] = self._states["scaling_bwd"].make_quantizers()
+        self._weight_cache.clear()
+        self.fp8_initialized = True
+        pending = self.fp8_meta.pop("_loaded_state", None)
+        if pending is not None:
+            self._apply_loaded_state(pending)
+
+    def _param_device(self):
+        for p in self.parameters(recurse=False):
+            return p.device
+        for p in self.parameters():
+            return p.device
+        return torch.device("cuda" if torch.cuda.is_available() else "cpu")
+
+    def prepare_forward(self, num_gemms: int = 1) -> None:
+        self.init_fp8_metadata(num_gemms)
+        if self.fp8 and isinstance(self._states["scaling_fwd"], DelayedScalingRecipeState):
+            FP8GlobalStateManager.add_pending(self._states["scaling_fwd"], forward=True)
+            if torch.is_grad_enabled():
+                FP8GlobalStateManager.add_pending(self._states["scaling_bwd"], forward=False)
+
+    def get_quantizer(self, fwd: bool, idx: int) -> Optional[Quantizer]:
+        if not self.fp8:
+            return None
+        return self.quantizers["scaling_fwd" if fwd else "scaling_bwd"][idx]
+
+    # ------------------------------------------------------------------ weights
+    def get_quantized_weight(self, weight: torch.Tensor, quantizer: Optional[Quantizer], *, cache_name: str,
+                             is_first_microbatch: Optional[bool] = None, need_columnwise: bool = True):
+        """Quantize ``weight`` (both copies) or return the cached result.
+
+        The cache is valid while the parameter has not changed: same torch version
+        counter and same optimizer epoch; ``is_first_microbatch=False`` forces reuse
+        and ``True`` forces an update, as in the reference.
+        """
+        if quantizer is None:
+            return weight
+        if isinstance(weight, QuantizedTensorStorage):
+            return weight
+        quantizer.set_usage(rowwise=True, columnwise=need_columnwise)
+        quantizer.internal = True
+        key = (weight._version, weights_epoch(), need_columnwise, id(quantizer))
+        ent = self._weight_cache.get(cache_name)
+        if ent is not None and is_first_microbatch is not True:
+            if is_first_microbatch is False or ent[0] == key:
+                if not need_columnwise or ent[1].get_usages()["columnwise"]:
+                    return ent[1]
+        q = quantizer(weight.detach())
+        self._weight_cache[cache_name] = (key, q)
+        return q
+
+    def reset_weight_cache(self) -> None:
+        self._weight_cache.clear()
+
+    # ------------------------------------------------------------------ checkpoint
+    def get_extra_state(self) -> torch.Tensor:
+        """uint8 tensor with a pickle of the recipe and (delayed scaling) its scale/amax tensors."""
+        if not self.fp8_meta.get("fp8_checkpoint") or self.fp8_meta.get("recipe") is None:
+            return torch.empty(0, dtype=torch.uint8)
+        recipe: Recipe = self.fp8_meta["recipe"]
+        state: Dict[str, Any] = {"recipe": recipe}
+        if recipe.delayed():
+            f, b = self._states["scaling_fwd"], self._states["scaling_bwd"]
+            if f is None:
+                return torch.empty(0, dtype=torch.uint8)
+            state["scale_fwd"] = f.scale.detach().cpu().clone()
+            state["amax_history_fwd"] = f.amax_history.detach().cpu().clone()
+            state["scale_bwd"] = b.scale.detach().cpu().clone()
+            state["amax_history_bwd"] = b.amax_history.detach().cpu().clone()
+        elif recipe.stateless():
+            return torch.empty(0, dtype=torch.uint8)
+        state["extra_fp8_variables"] = {
+            k: v for k, v in self.fp8_meta.items()
+            if isinstance(v, (bool, int, float, str)) and not k.startswith("_")
+        }
+        buf = io.BytesIO()
+        pickle.dump(state, buf)
+        return torch.frombuffer(bytearray(buf.getvalue()), dtype=torch.uint8).clone()
+
+    def set_extra_state(self, state) -> None:
+        if state is None:
+            return
+        import os
+
+        if isinstance(state, torch.Tensor):
+            if state.numel() == 0:
+                return
+            raw = bytes(state.detach().cpu().numpy().tobytes())
+        elif isinstance(state, io.BytesIO):
+            state.seek(0)
+            raw = state.read()
+        else:
+            raise RuntimeError("Unsupported checkpoint format.")
+        if os.getenv(_UNSAFE_PICKLE_ENV, "0") == "1":
+            obj = pickle.loads(raw)
+        else:
+            obj = _SafeUnpickler(io.BytesIO(raw)).load()
+        if obj is None:
+            return
+        if "recipe" not in obj:  # files written before recipes were stored
+            obj["recipe"] = DelayedScaling()
+        self.fp8_meta["fp8_checkpoint"] = True
+        self.fp8_meta.update(obj.get("extra_fp8_variables", {}))
+        if self.fp8_initialized and type(self.fp8_meta.get("recipe")) is type(obj["recipe"]):
+            self._apply_loaded_state(obj)
+        else:
+            self.fp8_meta["_loaded_state"] = obj
+            self.fp8_meta["recipe"] = obj["recipe"]
+
+    def _apply_loaded_state(self, obj) -> None:
+        recipe = obj["recipe"]
+        if not recipe.delayed() or "scale_fwd" not in obj:
+            return
+        f, b = self._states["scaling_fwd"], self._states["scaling_bwd"]
+        if not isinstance(f, DelayedScalingRecipeState):
+            return
+
+        def load(dst, src):
+            if dst.shape != src.shape:
+                warnings.warn(f"_extra_state shape mismatch {tuple(src.shape)} vs {tuple(dst.shape)}; "
+                              "copying the overlapping part")
+                sl = tuple(slice(0, min(a, c)) for a, c in zip(dst.shape, src.shape))
+                dst[sl].copy_(src[sl])
+            else:
+                dst.copy_(src)
+
+        load(f.scale, obj["scale_fwd"])
+        load(f.amax_history, obj["amax_history_fwd"])
+        load(b.scale, obj["scale_bwd"])
+        load(b.amax_history, obj["amax_history_bwd"])
+
+    # ------------------------------------------------------------------ delayed wgrad
+    def backward_dw(self) -> None:
+        """Run the weight-gradient GEMMs that were postponed with ``delay_wgrad_compute``."""
+        if self.wgrad_store is not None:
+            self.wgrad_store.pop()
+
+    def need_backward_dw(self) -> bool:
+        return self.wgrad_store is not None and self.wgrad_store.delay
+
+
+class WeightGradStore:
+    """Queue of postponed weight-gradient computations (zero-bubble pipeline schedules)."""
+
+    def __init__(self, delay: bool = False) -> None:
+        self.delay = delay
+        self._queue: List = []
+
+    def delay_wgrad_compute(self) -> bool:
+        return self.delay
+
+    def put(self, fn) -> None:
+        self._queue.append(fn)
+
+    def pop(self) -> None:
+        q, self._queue = self._queue, []
+        for fn in q:
+            fn()

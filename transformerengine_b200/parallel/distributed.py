@@ -1,0 +1,246 @@
+"""Collective helpers for tensor / sequence parallel modules, RNG-state tracking and
+activation recompute (reference: ``pytorch/distributed.py:241-2257``).
+
+Everything here is plain ``torch.distributed`` (NCCL on GPUs, gloo on CPU) and is
+the baseline transport; the fused compute+collective kernels live in
+``parallel/comm_gemm.py``.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Any, Callable, Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def get_world_size(group=None) -> int:
+    if not dist.is_available() or not dist.is_initialized():
+        return 1
+    return dist.get_world_size(group=group)
+
+
+def get_rank(group=None) -> int:
+    if not dist.is_available() or not dist.is_initialized():
+        return 0
+    return dist.get_rank(group=group)
+
+
+def gather_along_first_dim(x: torch.Tensor, group, async_op: bool = False):
+    """All-gather shards along dim 0.  Returns (tensor, handle or None)."""
+    ws = get_world_size(group)
+    if ws == 1:
+        return x, None
+    x = x.contiguous()
+    out = torch.empty((x.shape[0] * ws,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    h = dist.all_gather_into_tensor(out, x, group=group, async_op=async_op)
+    return out, h
+
+
+def reduce_scatter_along_first_dim(x: torch.Tensor, group, async_op: bool = False):
+    """Sum over ranks, keep this rank's slice of dim 0.  Returns (tensor, handle or None)."""
+    ws = get_world_size(group)
+    if ws == 1:
+        return x, None
+    x = x.contiguous()
+    assert x.shape[0] % ws == 0, "first dim must divide by the group size"
+    out = torch.empty((x.shape[0] // ws,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    h = dist.reduce_scatter_tensor(out, x, group=group, async_op=async_op)
+    return out, h
+
+
+def allreduce(x: torch.Tensor, group, async_op: bool = False):
+    if get_world_size(group) == 1:
+        return x, None
+    h = dist.all_reduce(x, group=group, async_op=async_op)
+    return x, h
+
+
+def gather_mxfp8_along_first_dim(q, group):
+    """All-gather an MXFP8 tensor sharded on its row dim without dequantizing.
+
+    Rowwise data/scales concatenate along rows; the transposed columnwise copy
+    ``[C, R/ws]`` concatenates along its second dim.  Needs the local row count to
+    be a multiple of 128 so that whole scale tiles move.
+    """
+    from ..tensor.mxfp8 import MXFP8TensorStorage
+    from ..ops.ref.quant import round_up
+
+    ws = get_world_size(group)
+    if ws == 1:
+        return q
+    R, C = q._rows_cols()
+    assert R % 128 == 0, "quantized all-gather needs a multiple of 128 local rows"
+    rd = rs = cd = cs = None
+    if q._rowwise_data is not None:
+        rd, _ = gather_along_first_dim(q._rowwise_data.reshape(R, C), group)
+        rs, _ = gather_along_first_dim(q._rowwise_scale_inv, group)
+    if q._columnwise_data is not None:
+        g, _ = gather_along_first_dim(q._columnwise_data.reshape(1, C, R), group)  # [ws, C, R]
+        cd = g.permute(1, 0, 2).reshape(C, ws * R).contiguous()
+        kt = round_up(R // 32, 4) // 4
+        ct = round_up(C, 128) // 128
+        s, _ = gather_along_first_dim(q._columnwise_scale_inv.reshape(1, ct, kt, 512), group)  # [ws, ct, kt, 512]
+        cs = s.permute(1, 0, 2, 3).reshape(-1).contiguous()
+    shape = (R * ws, C)
+    return MXFP8TensorStorage(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd, columnwise_scale_inv=cs,
+                              fp8_dtype=q._fp8_dtype, quantizer=q._quantizer, shape=shape, dtype=q._dtype)
+
+
+# --------------------------------------------------------------------------- RNG tracker
+class CudaRNGStatesTracker:
+    """Named RNG states so that tensor-parallel ranks can draw the same or different
+    random numbers on demand (dropout inside vs outside TP regions)."""
+
+    def __init__(self) -> None:
+        self.states_: Dict[str, torch.Tensor] = {}
+        self.seeds_ = set()
+
+    def reset(self) -> None:
+        self.states_, self.seeds_ = {}, set()
+
+    def get_states(self) -> Dict[str, torch.Tensor]:
+        return dict(self.states_)
+
+    def set_states(self, states: Dict[str, torch.Tensor]) -> None:
+        self.states_ = states
+
+    @staticmethod
+    def _get_state():
+        return torch.cuda.get_rng_state() if torch.cuda.is_available() else torch.get_rng_state()
+
+    @staticmethod
+    def _set_state(s):
+        if torch.cuda.is_available():
+            torch.cuda.set_rng_state(s)
+        else:
+            torch.set_rng_state(s)
+
+    def add(self, name: str, seed: int) -> None:
+        if seed in self.seeds_:
+            raise RuntimeError(f"seed {seed} already exists")
+        if name in self.states_:
+            raise RuntimeError(f"cuda rng state {name} already exists")
+        self.seeds_.add(seed)
+        orig = self._get_state()
+        if torch.cuda.is_available():
+            torch.cuda.manual_seed(seed)
+        else:
+            torch.manual_seed(seed)
+        self.states_[name] = self._get_state()
+        self._set_state(orig)
+
+    @contextlib.contextmanager
+    def fork(self, name: str = "model-parallel-rng"):
+        if name not in self.states_:
+            raise KeyError(f"cuda rng state {name} is not added")
+        orig = self._get_state()
+        self._set_state(self.states_[name])
+        try:
+            yield
+        finally:
+            self.states_[name] = self._get_state()
+            self._set_state(orig)
+
+
+# --------------------------------------------------------------------------- activation recompute
+_IN_RECOMPUTE = [False]
+
+
+def is_in_recompute() -> bool:
+    return _IN_RECOMPUTE[0]
+
+
+class _CheckpointFunction(torch.autograd.Function):
+    """Re-entrant activation recompute: keep only the inputs, re-run the forward in backward
+    under the same RNG state and the same quantization region."""
+
+    @staticmethod
+    def forward(ctx, run_function, rng_tracker_fn, kwargs, *args):  # type: ignore[override]
+        from ..quantization import FP8GlobalStateManager
+
+        ctx.run_function = run_function
+        ctx.kwargs = kwargs
+        ctx.rng_tracker_fn = rng_tracker_fn
+        ctx.cpu_rng = torch.get_rng_state()
+        ctx.cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
+        ctx.tracker_states = rng_tracker_fn().get_states() if rng_tracker_fn is not None else None
+        ctx.autocast_state = FP8GlobalStateManager.get_autocast_state()
+        ctx.torch_autocast = torch.is_autocast_enabled()
+        with torch.no_grad():
+            out = run_function(*args, **kwargs)
+        ctx.tensor_idx = [i for i, a in enumerate(args) if torch.is_tensor(a)]
+        ctx.others = [None if torch.is_tensor(a) else a for a in args]
+        ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
+        return out
+
+    @staticmethod
+    def backward(ctx, *grads):  # type: ignore[override]
+        from ..quantization import FP8GlobalStateManager
+
+        saved = list(ctx.saved_tensors)
+        args = list(ctx.others)
+        for i, t in zip(ctx.tensor_idx, saved):
+            args[i] = t.detach().requires_grad_(t.requires_grad)
+        cpu_rng = torch.get_rng_state()
+        cuda_rng = torch.cuda.get_rng_state() if torch.cuda.is_available() else None
+        tracker_now = ctx.rng_tracker_fn().get_states() if ctx.rng_tracker_fn is not None else None
+        torch.set_rng_state(ctx.cpu_rng)
+        if ctx.cuda_rng is not None:
+            torch.cuda.set_rng_state(ctx.cuda_rng)
+        if ctx.tracker_states is not None:
+            ctx.rng_tracker_fn().set_states(ctx.tracker_states)
+        cur_state = FP8GlobalStateManager.get_autocast_state()
+        FP8GlobalStateManager.set_autocast_state(ctx.autocast_state)
+        _IN_RECOMPUTE[0] = True
+        try:
+            with torch.enable_grad():
+                out = ctx.run_function(*args, **ctx.kwargs)
+        finally:
+            _IN_RECOMPUTE[0] = False
+            FP8GlobalStateManager.set_autocast_state(cur_state)
+            torch.set_rng_state(cpu_rng)
+            if cuda_rng is not None:
+                torch.cuda.set_rng_state(cuda_rng)
+            if tracker_now is not None:
+                ctx.rng_tracker_fn().set_states(tracker_now)
+        outs = out if isinstance(out, (tuple, list)) else (out,)
+        pairs = [(o, g) for o, g in zip(outs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        res = [None, None, None]
+        for a in args:
+            res.append(a.grad if torch.is_tensor(a) else None)
+        return tuple(res)
+
+
+def checkpoint(function: Callable, *args, distribute_saved_activations: bool = False,
+               get_rng_state_tracker: Optional[Callable] = None, tp_group=None, use_reentrant: bool = True,
+               **kwargs):
+    """Recompute ``function`` in the backward pass instead of storing its activations."""
+    if not use_reentrant:
+        from torch.utils.checkpoint import checkpoint as torch_ckpt
+        from ..quantization import FP8GlobalStateManager
+
+        st = FP8GlobalStateManager.get_autocast_state()
+
+        def ctx_fn():
+            @contextlib.contextmanager
+            def recompute_ctx():
+                cur = FP8GlobalStateManager.get_autocast_state()
+                FP8GlobalStateManager.set_autocast_state(st)
+                _IN_RECOMPUTE[0] = True
+                try:
+                    yield
+                finally:
+                    _IN_RECOMPUTE[0] = False
+                    FP8GlobalStateManager.set_autocast_state(cur)
+            return contextlib.nullcontext(), recompute_ctx()
+
+        return torch_ckpt(function, *args, use_reentrant=False, context_fn=ctx_fn, **kwargs)
+    return _CheckpointFunction.apply(function, get_rng_state_tracker, kwargs, *args)
+
+
+def set_tensor_model_parallel_attributes(tensor: torch.Tensor, is_parallel: bool, dim: int, stride: int) -> None:
+    setattr(tensor, "tensor_model_parallel", is_parallel)
+    setattr(tensor, "partition_dim", dim)
+    setattr(tensor, "partition_stride", stride)

@@ -1,0 +1,351 @@
+"""Flagship benchmark: one Llama-3-8B-architecture pre-training step (forward, backward,
+fused Adam with fp32 master weights) at seq 8192, micro-batch 1, MXFP8 block scaling.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+
+N = 1: single GPU.  N = 2, 4: data parallel (one sequence per GPU, gradient
+all-reduce).  N = 8: tensor parallel with sequence parallelism.  Launched with
+``torch.distributed.run`` for N > 1.  Prints one JSON line from rank 0.
+Weights are random N(0, 0.02), token ids uniform over the vocabulary.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+sys.path.insert(0, ROOT)
+
+SEQ = 8192
+METRIC = "tokens_per_second"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    # development knobs; the defaults are the benchmarked configuration
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--seq", type=int, default=SEQ)
+    ap.add_argument("--recompute", type=int, default=-1, help="-1 auto, 0 off, 1 per-layer recompute")
+    ap.add_argument("--recipe", default="mxfp8")
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU every 200 ms through NVML (read only)."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.sm_max = index, [], set(), None
+        self._stop_evt = threading.Event()
+
+    def run(self):
+        try:
+            import pynvml as N
+            N.nvmlInit()
+            h = N.nvmlDeviceGetHandleByIndex(self.index)
+            self.sm_max = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+            names = {N.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     N.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     N.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                     N.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap"}
+            while not self._stop_evt.is_set():
+                self.samples.append(N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM))
+                r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, nm in names.items():
+                    if r & bit:
+                        self.reasons.add(nm)
+                time.sleep(0.2)
+        except Exception as e:  # noqa: BLE001
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def stop(self):
+        self._stop_evt.set()
+        self.join(timeout=2)
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.sm_max, "reasons": sorted(self.reasons)}
+
+
+def physical_gpu_index(local_rank: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            return local_rank
+    return local_rank
+
+
+def init_dist(n):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def timed_loop(step_fn, steps, world, sampler_index=None):
+    """Barrier + synchronize on both sides, CUDA events around exactly `steps` steps, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    sampler = ClockSampler(sampler_index) if sampler_index is not None else None
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.start()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(steps):
+        step_fn(i)
+    e.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, clocks
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import transformerengine_b200 as te
+    from transformerengine_b200.models import llama
+    from transformerengine_b200.ops import _ext
+
+    rank, local, world = init_dist(args.gpus)
+    torch.manual_seed(0)
+    tp = world if world == 8 else 1
+    dp = world // tp
+    cfg = llama.LlamaConfig.llama3_8b(num_layers=args.layers)
+    # single-GPU / DP ranks hold the whole model and optimizer (~128 GB); activations of one 8192-token
+    # sequence add ~30 GB, which fits in 180 GB without recompute
+    cfg.recompute = bool(args.recompute) if args.recompute >= 0 else False
+    tp_group = dist.group.WORLD if tp > 1 else None
+    model = llama.LlamaModel(cfg, tp_group=tp_group, sequence_parallel=True)
+    if dp > 1:
+        for p in model.parameters():
+            dist.broadcast(p.data, 0)
+    opt = te.FusedAdam(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                       master_weights=True)
+    recipe = {"mxfp8": te.recipe.MXFP8BlockScaling(), "nvfp4": te.recipe.NVFP4BlockScaling(),
+              "delayed": te.recipe.DelayedScaling(), "current": te.recipe.Float8CurrentScaling(),
+              "bf16": None}[args.recipe]
+    gen = torch.Generator().manual_seed(1234 + rank * (1 if dp > 1 else 0))
+    n_batches = 4
+    host = [torch.randint(0, cfg.vocab_size, (1, args.seq), generator=gen).pin_memory() for _ in range(n_batches)]
+    dev = [h.cuda() for h in host]
+    grads = [p for p in model.parameters()]
+
+    def allreduce_grads():
+        if dp == 1:
+            return
+        bucket, size = [], 0
+        for p in grads:
+            if p.grad is None:
+                continue
+            bucket.append(p.grad)
+            size += p.grad.numel()
+            if size >= 64 << 20:
+                _flat_allreduce(bucket, dp)
+                bucket, size = [], 0
+        if bucket:
+            _flat_allreduce(bucket, dp)
+
+    def _flat_allreduce(bucket, n):
+        flat = torch._utils._flatten_dense_tensors(bucket)
+        dist.all_reduce(flat)
+        flat.div_(n)
+        for g, f in zip(bucket, torch._utils._unflatten_dense_tensors(flat, bucket)):
+            g.copy_(f)
+
+    def train_step(tokens):
+        opt.zero_grad(set_to_none=True)
+        with te.autocast(enabled=recipe is not None, recipe=recipe):
+            loss = model(tokens, labels=tokens)
+        loss.backward()
+        allreduce_grads()
+        opt.step()
+        return loss
+
+    def step_device(i):
+        train_step(dev[i % n_batches])
+
+    losses = []
+
+    def step_e2e(i):
+        tok = host[i % n_batches].cuda(non_blocking=True)   # H2D of this step's inputs from pinned memory
+        loss = train_step(tok)
+        losses.append(float(loss.item()))                    # D2H read of the step's result
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    te.check_status()
+    C_ = _ext.get()
+    l0 = C_.launch_count()
+    ms, clocks = timed_loop(step_device, args.steps, world, physical_gpu_index(local))
+    launches = C_.launch_count() - l0
+    te.check_status()
+    tokens_per_step = args.seq * dp
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    e2e = None
+    if not args.skip_e2e:
+        step_e2e(0)
+        ms2, _ = timed_loop(step_e2e, args.steps, world)
+        e2e = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
+               "h2d_bytes_per_step": host[0].numel() * host[0].element_size(), "d2h_bytes_per_step": 4,
+               "ms_per_step": ms2 / args.steps, "last_loss": losses[-1] if losses else None}
+    if rank == 0:
+        tflops = value * cfg.flops_per_token(args.seq) / 1e12 / world
+        out = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+               "scaling": "weak" if tp == 1 else "strong", "vs_baseline": None, "dtype": "bf16+" + args.recipe,
+               "data": "synthetic", "impl": "ours",
+               "config": {"model": "llama3-8b-arch" if args.layers == 32 else f"llama3-8b-arch-{args.layers}L",
+                          "global_batch": dp, "seq_len": args.seq,
+                          "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
+                          "recipe": args.recipe, "optimizer": "fused-adam fp32 master", "recompute": cfg.recompute,
+                          "l2": "inputs and weights (16 GB) far exceed the 126 MB L2"},
+               "tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
+               "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30}
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """Same step through the unmodified reference installed under baseline/_ref."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    try:
+        if not os.path.isdir(os.path.join(ref_dir, "transformer_engine")):
+            raise ImportError("baseline/_ref holds no transformer_engine install (offline build did not finish)")
+        sys.path.insert(0, ref_dir)
+        import torch
+        import transformer_engine.pytorch as rte
+        from transformer_engine.common import recipe as rrecipe
+    except Exception as e:  # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}), flush=True)
+        return
+    import torch.distributed as dist
+
+    rank, local, world = init_dist(args.gpus)
+    torch.manual_seed(0)
+    tp = world if world == 8 else 1
+    dp = world // tp
+    V, H, L, NH, NKV, FFN = 128256, 4096, args.layers, 32, 8, 14336
+    tp_group = dist.group.WORLD if tp > 1 else None
+    init = lambda t: torch.nn.init.normal_(t, 0.0, 0.02)  # noqa: E731
+
+    class RefLlama(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(V, H, dtype=torch.bfloat16, device="cuda")
+            self.layers = torch.nn.ModuleList([
+                rte.TransformerLayer(H, FFN, NH, num_gqa_groups=NKV, layernorm_epsilon=1e-5, hidden_dropout=0.0,
+                                     attention_dropout=0.0, init_method=init, output_layer_init_method=init,
+                                     layer_number=i + 1, self_attn_mask_type="causal", tp_group=tp_group,
+                                     tp_size=tp, params_dtype=torch.bfloat16, sequence_parallel=tp > 1,
+                                     set_parallel_mode=tp > 1, fuse_qkv_params=True, bias=False,
+                                     activation="swiglu", normalization="RMSNorm", attn_input_format="sbhd")
+                for i in range(L)])
+            self.norm = rte.RMSNorm(H, eps=1e-5, params_dtype=torch.bfloat16)
+            self.head = rte.Linear(H, V, bias=False, init_method=init, params_dtype=torch.bfloat16)
+            self.rope = rte.RotaryPositionEmbedding(H // NH, rotary_base=500000.0)
+
+        def forward(self, tokens, recompute):
+            x = self.emb(tokens.t().contiguous())
+            if tp > 1:
+                x = x.chunk(tp, dim=0)[rank].contiguous()
+            f = self.rope(tokens.shape[1]).cuda()
+            for layer in self.layers:
+                if recompute:
+                    x = rte.checkpoint(layer, x, rotary_pos_emb=f)
+                else:
+                    x = layer(x, rotary_pos_emb=f)
+            x = self.norm(x)
+            if tp > 1:
+                xs = [torch.empty_like(x) for _ in range(tp)]
+                dist.all_gather(xs, x)
+                xs[rank] = x
+                x = torch.cat(xs, dim=0)
+            logits = self.head(x)
+            tgt = torch.full_like(tokens.t(), -100)
+            tgt[:-1] = tokens.t()[1:]
+            return torch.nn.functional.cross_entropy(logits.reshape(-1, V).float(), tgt.reshape(-1), ignore_index=-100)
+
+    model = RefLlama()
+    opt = rte.optimizers.FusedAdam(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                                   master_weights=True)
+    rec = rrecipe.MXFP8BlockScaling()
+    recompute = bool(args.recompute) if args.recompute >= 0 else False
+    gen = torch.Generator().manual_seed(1234 + rank * (1 if dp > 1 else 0))
+    host = [torch.randint(0, V, (1, args.seq), generator=gen).pin_memory() for _ in range(4)]
+    dev = [h.cuda() for h in host]
+
+    def train_step(tok):
+        opt.zero_grad(set_to_none=True)
+        with rte.autocast(enabled=True, recipe=rec):
+            loss = model(tok, recompute)
+        loss.backward()
+        if dp > 1:
+            for p in model.parameters():
+                if p.grad is not None:
+                    dist.all_reduce(p.grad)
+                    p.grad.div_(dp)
+        opt.step()
+        return loss
+
+    for i in range(args.warmup):
+        train_step(dev[i % 4])
+    ms, clocks = timed_loop(lambda i: train_step(dev[i % 4]), args.steps, world, physical_gpu_index(local))
+    value = args.seq * dp * args.steps / (ms / 1e3)
+    losses = []
+
+    def e2e_step(i):
+        losses.append(float(train_step(host[i % 4].cuda(non_blocking=True)).item()))
+
+    e2e_step(0)
+    ms2, _ = timed_loop(e2e_step, args.steps, world)
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+                          "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+                          "scaling": "weak" if tp == 1 else "strong", "vs_baseline": None, "dtype": "bf16+mxfp8",
+                          "data": "synthetic", "impl": "reference",
+                          "config": {"model": "llama3-8b-arch", "global_batch": dp, "seq_len": args.seq,
+                                     "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
+                                     "recompute": recompute},
+                          "clocks": clocks,
+                          "e2e": {"value": args.seq * dp * args.steps / (ms2 / 1e3), "unit": "tokens/s",
+                                  "h2d_bytes_per_step": host[0].numel() * 8, "d2h_bytes_per_step": 4}}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -34,9 +34,13 @@ T* ptr(const OptT& t) {
   return t.has_value() && t->defined() ? static_cast<T*>(t->data_ptr()) : nullptr;
 }
 cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+// number of kernel launches issued through this module (one per launcher call)
+long long g_launches = 0;
 void check(cudaError_t e, const char* what) {
+  ++g_launches;
   TORCH_CHECK(e == cudaSuccess, what, " failed: ", cudaGetErrorString(e));
 }
+long long launch_count() { return g_launches; }
 
 // One int per device; kernels write a Status code there when a bounded wait expires.
 at::Tensor& status_tensor(int device) {
@@ -215,6 +219,7 @@ void norm_bwd(bool layernorm, const at::Tensor& dy, const at::Tensor& x, const O
   n.dbeta = ptr<void>(dbeta);
   n.workspace = workspace.data_ptr<float>();
   TORCH_CHECK(workspace.numel() >= norm_bwd_workspace(n.R, n.C), "norm_bwd workspace too small");
+  ++g_launches;  // statistics kernel + finalize kernel
   check(teb200::norm_bwd(n, stream()), "norm_bwd");
 }
 
@@ -386,6 +391,7 @@ void register_extra(py::module_& m);  // bindings of kernels added in other tran
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("status", &status);
+  m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("quantize", &quantize);
   m.def("dequantize_mxfp8", &dequantize_mxfp8);

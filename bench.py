@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--recompute", type=int, default=-1, help="-1 auto, 0 off, 1 per-layer recompute")
     ap.add_argument("--recipe", default="mxfp8")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
     return ap.parse_args()
 
 
@@ -136,8 +137,9 @@ def run_ours(args):
 
     rank, local, world = init_dist(args.gpus)
     torch.manual_seed(0)
-    tp = world if world == 8 else 1
+    tp = args.tp if args.tp > 0 else (world if world == 8 else 1)
     dp = world // tp
+    assert dp == 1 or tp == 1, "this benchmark runs pure DP or pure TP"
     cfg = llama.LlamaConfig.llama3_8b(num_layers=args.layers)
     # single-GPU / DP ranks hold the whole model and optimizer (~128 GB); activations of one 8192-token
     # sequence add ~30 GB, which fits in 180 GB without recompute
@@ -252,7 +254,7 @@ def run_reference(args):
 
     rank, local, world = init_dist(args.gpus)
     torch.manual_seed(0)
-    tp = world if world == 8 else 1
+    tp = args.tp if args.tp > 0 else (world if world == 8 else 1)
     dp = world // tp
     V, H, L, NH, NKV, FFN = 128256, 4096, args.layers, 32, 8, 14336
     tp_group = dist.group.WORLD if tp > 1 else None

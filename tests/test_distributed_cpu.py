@@ -1,0 +1,101 @@
+"""Tensor parallel + sequence parallel over gloo (2 CPU ranks) against the unsharded layer."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import transformerengine_b200 as te
+from transformerengine_b200.common import recipe as R
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _make_layer(tp_group=None, tp=1):
+    torch.manual_seed(0)
+    init = lambda t: torch.nn.init.normal_(t, 0.0, 0.02)  # noqa: E731
+    return te.TransformerLayer(256, 1024, 4, layernorm_epsilon=1e-5, hidden_dropout=0.0, attention_dropout=0.0,
+                               init_method=init, output_layer_init_method=init, self_attn_mask_type="causal",
+                               params_dtype=torch.float32, device="cpu", activation="gelu", tp_group=tp_group,
+                               tp_size=tp, set_parallel_mode=tp > 1, sequence_parallel=tp > 1)
+
+
+def _shard(full, name, rank, tp):
+    """Slice of the unsharded parameter that rank `rank` owns."""
+    col = ("query_weight", "key_weight", "value_weight", "query_bias", "key_bias", "value_bias", "fc1_weight",
+           "fc1_bias")
+    row = ("proj.weight", "fc2_weight")
+    if name.endswith(col):
+        return full.chunk(tp, dim=0)[rank]
+    if name.endswith(row):
+        return full.chunk(tp, dim=1)[rank]
+    return full
+
+
+def _worker(rank, tp, port, use_fp8, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=tp)
+    try:
+        full = _make_layer()
+        layer = _make_layer(dist.group.WORLD, tp)
+        fp = dict(full.named_parameters())
+        with torch.no_grad():
+            for n, p in layer.named_parameters():
+                p.copy_(_shard(fp[n], n, rank, tp))
+        torch.manual_seed(1)
+        x = torch.randn(64, 2, 256)
+        gy = torch.randn(64, 2, 256)
+        rec = R.DelayedScaling(amax_history_len=16)
+        xs = x.chunk(tp, dim=0)[rank].clone().requires_grad_(True)
+        xf = x.clone().requires_grad_(True)
+        with te.autocast(enabled=use_fp8, recipe=rec, amax_reduction_group=dist.group.WORLD):
+            y = layer(xs)
+        y.backward(gy.chunk(tp, dim=0)[rank])
+        with te.autocast(enabled=use_fp8, recipe=rec):
+            yf = full(xf)
+        yf.backward(gy)
+        tol = 0.06 if use_fp8 else 1e-5
+
+        def rel(a, b):
+            return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+        errs = {"out": rel(y, yf.chunk(tp, dim=0)[rank]), "dx": rel(xs.grad, xf.grad.chunk(tp, dim=0)[rank])}
+        lp = dict(layer.named_parameters())
+        for n in ("layernorm_mlp.fc1_weight", "layernorm_mlp.fc2_weight", "self_attention.proj.weight",
+                  "self_attention.layernorm_qkv.key_weight"):
+            errs[n] = rel(lp[n].grad, _shard(fp[n].grad, n, rank, tp))
+        # parameters replicated over TP but fed sequence shards: their gradient is summed by the trainer
+        g = lp["layernorm_mlp.layer_norm_weight"].grad.clone()
+        dist.all_reduce(g)
+        errs["ln_w"] = rel(g, fp["layernorm_mlp.layer_norm_weight"].grad)
+        assert getattr(lp["layernorm_mlp.layer_norm_weight"], "sequence_parallel", False)
+        bad = {k: v for k, v in errs.items() if not v < tol}
+        q.put((rank, bad))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, {"exception": traceback.format_exc()[-1500:]}))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("use_fp8", [False, True])
+def test_tp2_sequence_parallel_matches_unsharded(use_fp8):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, use_fp8, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, bad in res:
+        assert not bad, f"rank {rank}: {bad}"

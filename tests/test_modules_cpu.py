@@ -1,0 +1,278 @@
+"""Modules on the CPU reference path against plain torch.nn implementations."""
+import copy
+import io
+import pickle
+
+import pytest
+import torch
+import torch.nn.functional as TF
+
+import transformerengine_b200 as te
+from transformerengine_b200.common import recipe as R
+
+RECIPES = {
+    "delayed": lambda: R.DelayedScaling(amax_history_len=16),
+    "current": lambda: R.Float8CurrentScaling(),
+    "mxfp8": lambda: R.MXFP8BlockScaling(),
+    "nvfp4": lambda: R.NVFP4BlockScaling(),
+    "block": lambda: R.Float8BlockScaling(),
+}
+TOL = {"delayed": 0.08, "current": 0.08, "mxfp8": 0.08, "nvfp4": 0.3, "block": 0.08}
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
+def test_linear_matches_torch():
+    m = te.Linear(64, 96, device="cpu", params_dtype=torch.float32)
+    x = torch.randn(4, 8, 64, requires_grad=True)
+    y = m(x)
+    ref = TF.linear(x, m.weight, m.bias)
+    assert rel(y, ref) < 1e-6
+    y.sum().backward()
+    assert rel(m.weight.grad, torch.ones(32, 96).t() @ x.detach().reshape(32, 64)) < 1e-5
+
+
+@pytest.mark.parametrize("name", list(RECIPES))
+def test_linear_quantized(name):
+    m = te.Linear(128, 256, device="cpu", params_dtype=torch.float32)
+    x = torch.randn(64, 128, requires_grad=True)
+    with te.autocast(enabled=True, recipe=RECIPES[name]()):
+        y = m(x)
+    ref = TF.linear(x, m.weight, m.bias)
+    assert rel(y, ref) < TOL[name]
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().clone().requires_grad_(True)
+    w = m.weight.detach().clone().requires_grad_(True)
+    TF.linear(xr, w, m.bias.detach()).backward(g)
+    assert rel(x.grad, xr.grad) < TOL[name] * 1.5
+    assert rel(m.weight.grad, w.grad) < TOL[name] * 1.5
+    assert rel(m.bias.grad, g.sum(0)) < 1e-5
+
+
+@pytest.mark.parametrize("norm", ["LayerNorm", "RMSNorm"])
+@pytest.mark.parametrize("zc", [False, True])
+def test_layernorm_linear(norm, zc):
+    m = te.LayerNormLinear(64, 128, normalization=norm, zero_centered_gamma=zc, device="cpu",
+                           params_dtype=torch.float32)
+    with torch.no_grad():
+        m.layer_norm_weight.add_(torch.randn(64) * 0.1)
+    x = torch.randn(16, 64, requires_grad=True)
+    y = m(x)
+    g = m.layer_norm_weight + (1 if zc else 0)
+    if norm == "LayerNorm":
+        ln = TF.layer_norm(x, (64,), g, m.layer_norm_bias, 1e-5)
+    else:
+        ln = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * g
+    ref = TF.linear(ln, m.weight, m.bias)
+    assert rel(y, ref) < 1e-5
+    gy = torch.randn_like(y)
+    gx_ref, gw_ref = torch.autograd.grad(ref, [x, m.layer_norm_weight], gy, retain_graph=True)
+    y.backward(gy)
+    assert rel(x.grad, gx_ref) < 1e-4 and rel(m.layer_norm_weight.grad, gw_ref) < 1e-4
+
+
+@pytest.mark.parametrize("act", ["gelu", "swiglu", "relu", "geglu", "silu", "qgelu", "srelu", "reglu"])
+def test_layernorm_mlp(act):
+    m = te.LayerNormMLP(64, 128, activation=act, normalization="RMSNorm", device="cpu", params_dtype=torch.float32)
+    x = torch.randn(32, 64, requires_grad=True)
+    y = m(x)
+    ln = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * m.layer_norm_weight
+    h = TF.linear(ln, m.fc1_weight, m.fc1_bias)
+    base = {"gelu": lambda t: TF.gelu(t, approximate="tanh"), "relu": torch.relu, "silu": TF.silu,
+            "qgelu": lambda t: t * torch.sigmoid(1.702 * t), "srelu": lambda t: torch.relu(t) ** 2}
+    gated = {"swiglu": "silu", "geglu": "gelu", "reglu": "relu"}
+    if act in gated:
+        a, b = h.chunk(2, dim=-1)
+        h = base[gated[act]](a) * b
+    else:
+        h = base[act](h)
+    ref = TF.linear(h, m.fc2_weight, m.fc2_bias)
+    assert rel(y, ref) < 1e-5
+    gy = torch.randn_like(y)
+    refs = torch.autograd.grad(ref, [x, m.fc1_weight, m.fc2_weight, m.fc1_bias], gy, retain_graph=True)
+    y.backward(gy)
+    for got, want in zip([x.grad, m.fc1_weight.grad, m.fc2_weight.grad, m.fc1_bias.grad], refs):
+        assert rel(got, want) < 1e-4
+
+
+def _torch_layer_reference(layer, x):
+    """Pre-LN GPT block with the same parameters, written with torch only ([s, b, h] input)."""
+    sa, mlp = layer.self_attention, layer.layernorm_mlp
+    lq = sa.layernorm_qkv
+    s, b, h = x.shape
+    nh = sa.num_attention_heads
+    d = h // nh
+    ln1 = TF.layer_norm(x, (h,), lq.layer_norm_weight, lq.layer_norm_bias, 1e-5)
+    w = torch.cat([lq.query_weight, lq.key_weight, lq.value_weight], 0)
+    bb = torch.cat([lq.query_bias, lq.key_bias, lq.value_bias], 0)
+    qkv = TF.linear(ln1, w, bb)
+    q, k, v = (t.reshape(s, b, nh, d).permute(1, 2, 0, 3) for t in qkv.chunk(3, dim=-1))
+    o = TF.scaled_dot_product_attention(q, k, v, is_causal=True)
+    o = o.permute(2, 0, 1, 3).reshape(s, b, h)
+    x1 = x + TF.linear(o, sa.proj.weight, sa.proj.bias)
+    ln2 = TF.layer_norm(x1, (h,), mlp.layer_norm_weight, mlp.layer_norm_bias, 1e-5)
+    f = TF.gelu(TF.linear(ln2, mlp.fc1_weight, mlp.fc1_bias), approximate="tanh")
+    return x1 + TF.linear(f, mlp.fc2_weight, mlp.fc2_bias)
+
+
+def make_cfg1_layer(**kw):
+    """One layer of the CPU plumbing configuration: hidden 256, 4 heads, FFN 1024 GeLU, LayerNorm."""
+    torch.manual_seed(0)
+    init = lambda t: torch.nn.init.normal_(t, 0.0, 0.02)  # noqa: E731
+    return te.TransformerLayer(256, 1024, 4, layernorm_epsilon=1e-5, hidden_dropout=0.0, attention_dropout=0.0,
+                               init_method=init, output_layer_init_method=init, self_attn_mask_type="causal",
+                               params_dtype=torch.float32, device="cpu", activation="gelu", **kw)
+
+
+def test_transformer_layer_matches_torch_reference():
+    layer = make_cfg1_layer()
+    x = torch.randn(64, 2, 256, requires_grad=True)
+    y = layer(x)
+    ref = _torch_layer_reference(layer, x)
+    assert rel(y, ref) < 1e-5
+    gy = torch.randn_like(y)
+    gref = torch.autograd.grad(ref, [x, layer.layernorm_mlp.fc1_weight, layer.self_attention.proj.weight], gy,
+                               retain_graph=True)
+    y.backward(gy)
+    assert rel(x.grad, gref[0]) < 1e-4
+    assert rel(layer.layernorm_mlp.fc1_weight.grad, gref[1]) < 1e-4
+    assert rel(layer.self_attention.proj.weight.grad, gref[2]) < 1e-4
+
+
+def test_transformer_layer_fp8_delayed_scaling_emulation():
+    layer = make_cfg1_layer()
+    x = torch.randn(64, 2, 256, requires_grad=True)
+    ref = _torch_layer_reference(layer, x)
+    rec = R.DelayedScaling(amax_history_len=16, margin=0, fp8_format=R.Format.HYBRID)
+    for _ in range(3):  # the first step runs with scale 1; later steps use the recorded amax
+        layer.zero_grad()
+        with te.fp8_autocast(enabled=True, fp8_recipe=rec):
+            y = layer(x)
+        y.sum().backward()
+    assert rel(y, ref) < 0.05
+    st = layer.layernorm_mlp._states["scaling_fwd"]
+    assert st.amax_history.shape == (16, 6) and (st.scale != 1).any()
+
+
+def test_delayed_scaling_history_roll_and_scale():
+    m = te.Linear(32, 32, device="cpu", params_dtype=torch.float32)
+    rec = R.DelayedScaling(amax_history_len=4, amax_compute_algo="max")
+    x = torch.ones(32, 32) * 2.0
+    with te.autocast(enabled=True, recipe=rec):
+        m(x)
+    st = m._states["scaling_fwd"]
+    # after exit: amax of the step moved to slot 3 (roll by -1), slot 0 cleared, scale = 448/2
+    assert st.amax_history[0, 0] == 0 and st.amax_history[3, 0] == 2.0
+    assert abs(st.scale[0].item() - 224.0) < 1e-3
+    with te.autocast(enabled=True, recipe=rec):
+        m(x * 0.5)
+    assert st.amax_history[3, 0] == 1.0 and st.amax_history[2, 0] == 2.0
+    assert abs(st.scale[0].item() - 224.0) < 1e-3  # max over history still 2
+
+
+def test_extra_state_roundtrip_and_recipe_module_path():
+    m = te.Linear(32, 64, device="cpu", params_dtype=torch.float32)
+    rec = R.DelayedScaling(amax_history_len=8)
+    with te.autocast(enabled=True, recipe=rec):
+        m(torch.randn(32, 32)).sum().backward()
+    sd = m.state_dict()
+    assert "_extra_state" in sd and sd["_extra_state"].dtype == torch.uint8 and sd["_extra_state"].numel() > 0
+    raw = bytes(sd["_extra_state"].numpy().tobytes())
+    assert b"transformer_engine.common.recipe" in raw  # loadable by the reference library
+    obj = pickle.loads(raw)
+    assert set(obj) >= {"recipe", "scale_fwd", "amax_history_fwd", "scale_bwd", "amax_history_bwd",
+                        "extra_fp8_variables"}
+    m2 = te.Linear(32, 64, device="cpu", params_dtype=torch.float32)
+    buf = io.BytesIO()
+    torch.save(sd, buf)
+    buf.seek(0)
+    m2.load_state_dict(torch.load(buf, weights_only=False))
+    with te.autocast(enabled=True, recipe=rec):
+        m2(torch.randn(32, 32))
+    # loaded scales were applied when the state was built (then updated once at exit)
+    assert torch.equal(m2.weight, m.weight)
+    # modules that never ran quantized store an empty state
+    m3 = te.Linear(8, 8, device="cpu")
+    assert m3.state_dict()["_extra_state"].numel() == 0
+    # stateless recipes store an empty state too
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
+        te.Linear(32, 32, device="cpu", params_dtype=torch.float32)(torch.randn(32, 32))
+
+
+def test_unsafe_pickle_is_refused():
+    m = te.Linear(8, 8, device="cpu")
+
+    class Evil:
+        def __reduce__(self):
+            return (print, ("pwned",))
+
+    blob = torch.frombuffer(bytearray(pickle.dumps({"recipe": Evil()})), dtype=torch.uint8)
+    with pytest.raises(Exception):
+        m.set_extra_state(blob)
+
+
+def test_parameters_split_names_and_weight_cache():
+    m = te.Linear(32, 96, parameters_split=("query", "key", "value"), device="cpu", params_dtype=torch.float32)
+    names = dict(m.named_parameters()).keys()
+    assert {"query_weight", "key_weight", "value_weight", "query_bias"} <= set(names)
+    x = torch.randn(32, 32)
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
+        m(x)
+        first = m._weight_cache["weight"][1]
+        m(x)
+        assert m._weight_cache["weight"][1] is first  # unchanged weights are not re-quantized
+    y = m(x)
+    y.sum().backward()
+    assert m.key_weight.grad is not None and m.key_weight.grad.shape == (32, 32)
+
+
+def test_quantized_model_init_and_fused_adam():
+    with te.quantized_model_init(enabled=True, recipe=R.MXFP8BlockScaling(), preserve_high_precision_init_val=True):
+        m = te.Linear(64, 64, device="cpu", params_dtype=torch.float32)
+    assert isinstance(m.weight, te.tensor.MXFP8Tensor)
+    opt = te.FusedAdam(m.parameters(), lr=1e-2, master_weights=True)
+    x = torch.randn(32, 64)
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
+        y = m(x)
+    y.pow(2).mean().backward()
+    before = m.weight.dequantize().clone()
+    opt.step()
+    assert not torch.equal(before, m.weight.dequantize())
+
+
+def test_activation_recompute_matches():
+    layer = make_cfg1_layer()
+    x = torch.randn(16, 2, 256, requires_grad=True)
+    y = layer(x)
+    y.sum().backward()
+    g0, w0 = x.grad.clone(), layer.layernorm_mlp.fc2_weight.grad.clone()
+    layer.zero_grad()
+    x.grad = None
+    for reentrant in (True, False):
+        y2 = te.checkpoint(layer, x, use_reentrant=reentrant)
+        y2.sum().backward()
+        assert rel(x.grad, g0) < 1e-6 and rel(layer.layernorm_mlp.fc2_weight.grad, w0) < 1e-6
+        layer.zero_grad()
+        x.grad = None
+
+
+def test_fused_adam_matches_torch_adamw():
+    ps = [torch.randn(33, 7), torch.randn(128)]
+    a = [p.clone().requires_grad_(True) for p in ps]
+    b = [p.clone().requires_grad_(True) for p in ps]
+    o1 = te.FusedAdam(a, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    o2 = torch.optim.AdamW(b, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1)
+    for _ in range(4):
+        for p, q in zip(a, b):
+            g = torch.randn_like(p)
+            p.grad, q.grad = g.clone(), g.clone()
+        o1.step()
+        o2.step()
+    for p, q in zip(a, b):
+        assert rel(p, q) < 1e-5
+    sd = o1.state_dict()
+    o3 = te.FusedAdam(a, lr=1e-2)
+    o3.load_state_dict(sd)

@@ -1,0 +1,123 @@
+"""Numerics of the pure-PyTorch quantization path (the oracle of the CUDA kernels)."""
+import pickle
+
+import pytest
+import torch
+
+import transformerengine_b200 as te
+from transformerengine_b200.ops.ref import quant as Q
+from transformerengine_b200.tensor import (Float8BlockQuantizer, Float8CurrentScalingQuantizer, Float8Quantizer,
+                                           MXFP8Quantizer, NVFP4Quantizer)
+
+
+def test_float_to_e8m0_rounds_up_and_saturates():
+    v = torch.tensor([0.0, 1.0, 1.0001, 0.5, 3.0, float("inf"), float("nan"), 2.0 ** -127, 2.0 ** -126 * 0.75])
+    e = Q.float_to_e8m0(v)
+    assert e.tolist()[:5] == [0, 127, 128, 126, 129]
+    assert e[5].item() == 0xFE and e[6].item() == 0xFF
+    assert e[7].item() == 0  # 2^-127 is representable as exponent 0
+    assert e[8].item() == 1  # above 2^-127: rounds up to 2^-126
+    back = Q.e8m0_to_float(e[:5])
+    assert torch.all(back >= v[:5])
+
+
+def test_mxfp8_quantize_roundtrip_and_scale_rule():
+    x = torch.randn(64, 128) * torch.exp(torch.randn(64, 1) * 3)
+    q, e = Q.quantize_mxfp8_rowwise(x, torch.float8_e4m3fn)
+    amax = x.reshape(64, 4, 32).abs().amax(-1)
+    scale = Q.e8m0_to_float(e)
+    # scaled block maximum fits the format, and the scale is the smallest power of two that does
+    assert torch.all(amax / scale <= 448.0)
+    assert torch.all((amax / (scale / 2) > 448.0) | (amax == 0))
+    deq = Q.dequantize_mxfp8_rowwise(q, e, torch.float32)
+    assert ((deq - x).abs() <= x.reshape(64, 4, 32).abs().amax(-1).repeat_interleave(32, 1) * 0.07).all()
+
+
+def test_swizzle_roundtrip_and_index_formula():
+    R, K = 200, 10
+    e = torch.randint(0, 255, (R, K), dtype=torch.uint8)
+    s = Q.swizzle_scales(e)
+    assert torch.equal(Q.unswizzle_scales(s, R, K), e)
+    kt = (K + 3) // 4
+    for i, j in [(0, 0), (33, 1), (130, 5), (199, 9)]:
+        off = ((i // 128) * kt + j // 4) * 512 + (i % 32) * 16 + ((i % 128) // 32) * 4 + j % 4
+        assert s[off] == e[i, j]
+
+
+def test_fp8_scale_rule():
+    amax = torch.tensor([0.0, 1.0, float("inf"), 448.0])
+    prev = torch.tensor([3.0, 3.0, 3.0, 3.0])
+    s = Q.compute_scale_from_amax(amax, 448.0, margin=1, prev_scale=prev)
+    assert s.tolist() == [3.0, 224.0, 3.0, 0.5]
+    p2 = Q.compute_scale_from_amax(torch.tensor([3.0]), 448.0, force_pow_2=True)
+    assert p2.item() == 128.0  # 448/3 = 149.3 floors to 2^7
+
+
+def test_nvfp4_codes_round_to_nearest_even():
+    x = torch.tensor([[0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 7.0, -0.25, -0.3, -6.0, 0.0, 0.26, 5.01, -2.5, 1.0]])
+    c = Q.cast_to_e2m1_codes(x)[0].tolist()
+    assert c == [0, 2, 2, 4, 4, 6, 6, 7, 8, 9, 15, 0, 1, 7, 12, 2]
+
+
+def test_nvfp4_quantize_dequantize_error():
+    x = torch.randn(128, 256)
+    amax = Q.amax_abs(x)
+    d, s = Q.quantize_nvfp4_1d(x, amax)
+    deq = Q.dequantize_nvfp4(d, s, amax, torch.float32)
+    rel = (deq - x).norm() / x.norm()
+    assert rel < 0.15
+    d2, s2 = Q.quantize_nvfp4_2d(x, amax)
+    # 2-D scales: the transposed quantization sees the same block scales
+    d2t, s2t = Q.quantize_nvfp4_2d(x.t().contiguous(), amax)
+    a = Q.dequantize_nvfp4(d2, s2, amax, torch.float32)
+    b = Q.dequantize_nvfp4(d2t, s2t, amax, torch.float32).t()
+    assert torch.equal(a, b)
+
+
+def test_rht_is_orthogonal_and_sr_is_unbiased():
+    h = Q.hadamard_matrix_16()
+    assert torch.allclose(h @ h.t(), torch.eye(16), atol=1e-6)
+    x = torch.full((64, 64), 0.7)
+    g = torch.Generator().manual_seed(0)
+    acc = torch.zeros_like(x)
+    for _ in range(64):
+        codes = Q.stochastic_round_e2m1_codes(x, torch.rand(x.shape, generator=g))
+        acc += Q.e2m1_codes_to_float(codes)
+    assert abs((acc / 64).mean().item() - 0.7) < 0.01  # round-to-nearest would give 0.5 or 1.0
+
+
+@pytest.mark.parametrize("make", [
+    lambda: Float8Quantizer(torch.ones(1), torch.zeros(1), torch.float8_e4m3fn),
+    lambda: Float8CurrentScalingQuantizer(torch.float8_e4m3fn),
+    lambda: MXFP8Quantizer(),
+    lambda: NVFP4Quantizer(),
+    lambda: NVFP4Quantizer(with_rht=True),
+    lambda: Float8BlockQuantizer(block_scaling_dim=1),
+    lambda: Float8BlockQuantizer(block_scaling_dim=2),
+])
+def test_quantized_tensor_behaviour(make):
+    q = make()
+    x = torch.randn(128, 256)
+    t = q(x)
+    assert isinstance(t, te.tensor.QuantizedTensor) and t.shape == x.shape
+    tol = 0.2 if isinstance(q, NVFP4Quantizer) else 0.08
+    assert (t.dequantize() - x).norm() / x.norm() < tol
+    # columnwise copy alone dequantizes to the same logical tensor
+    t2 = t.detach()
+    t2.update_usage(rowwise_usage=False)
+    assert (t2.dequantize() - x).norm() / x.norm() < tol
+    # generic torch ops see dequantized values; pickling keeps the payload
+    assert torch.allclose((t + 1).float(), t.dequantize().float() + 1)
+    r = pickle.loads(pickle.dumps(t))
+    assert torch.equal(r.dequantize(), t.dequantize())
+    # in-place update re-quantizes
+    t.copy_(torch.zeros_like(x))
+    assert t.dequantize().abs().max() == 0
+
+
+def test_make_empty_and_update_quantized():
+    q = MXFP8Quantizer()
+    t = q.make_empty((64, 64), dtype=torch.bfloat16)
+    x = torch.randn(64, 64)
+    q.update_quantized(x, t)
+    assert torch.equal(t.dequantize(dtype=torch.float32), q(x).dequantize(dtype=torch.float32))

@@ -338,7 +338,7 @@ void multi_tensor_l2norm_sq(std::vector<std::vector<at::Tensor>> lists, at::Tens
 void cross_entropy(const at::Tensor& logits, const at::Tensor& targets, const OptT& loss, const OptT& grad,
                    const OptT& row_max, const OptT& row_sum, const OptT& row_tgt, int64_t vocab_start,
                    double grad_scale, double label_smoothing, int64_t ignore_index, const OptT& gmax,
-                   const OptT& gsum) {
+                   const OptT& gsum, const OptT& grad_scale_dev) {
   c10::cuda::CUDAGuard guard(logits.device());
   teb200::CrossEntropyArgs a;
   a.logits = logits.data_ptr();
@@ -354,6 +354,7 @@ void cross_entropy(const at::Tensor& logits, const at::Tensor& targets, const Op
   a.ld = logits.stride(-2);
   a.vocab_start = static_cast<int>(vocab_start);
   a.grad_scale = static_cast<float>(grad_scale);
+  a.grad_scale_dev = ptr<float>(grad_scale_dev);
   a.label_smoothing = static_cast<float>(label_smoothing);
   a.ignore_index = ignore_index;
   if (gmax.has_value() && gmax->defined())

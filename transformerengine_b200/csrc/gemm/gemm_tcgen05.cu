@@ -19,6 +19,8 @@
 #include <teb200/api.h>
 #include <teb200/ptx.cuh>
 
+#include <cstdlib>
+
 namespace teb200 {
 
 namespace {
@@ -569,6 +571,8 @@ bool make_tensor_map_2d(CUtensorMap* map, const void* base, int dtype, uint64_t 
 }
 
 static int pick_bn(int N, int M, bool block_scaled) {
+  static const char* env = getenv("TEB200_GEMM_BN");  // experiment knob: force the tile width
+  if (env != nullptr && atoi(env) == 128) return 128;
   // wide tiles need fewer shared-memory bytes per flop; narrow ones waste less on small N
   if (N <= 128) return 128;
   if (block_scaled) return 256;

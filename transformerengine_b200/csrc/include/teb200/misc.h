@@ -64,6 +64,7 @@ struct CrossEntropyArgs {
   int64_t ld = 0;
   int vocab_start = 0;  // first vocabulary id held by this rank
   float grad_scale = 1.f;
+  const float* grad_scale_dev = nullptr;  // optional device scalar multiplied into grad_scale
   float label_smoothing = 0.f;
   int64_t ignore_index = -100;
 };

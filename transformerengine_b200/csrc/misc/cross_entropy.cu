@@ -131,7 +131,8 @@ __global__ void __launch_bounds__(NT) ce_kernel(const CrossEntropyArgs a) {
     if (ignored) {
       for (int c = threadIdx.x; c < a.V; c += NT) grow[c] = static_cast<T>(0.f);
     } else {
-      write_grad(row, grow, a.V, st.m, st.s, local, a.grad_scale, a.label_smoothing, a.V);
+      write_grad(row, grow, a.V, st.m, st.s, local, a.grad_scale * (a.grad_scale_dev ? *a.grad_scale_dev : 1.f),
+                 a.label_smoothing, a.V);
     }
   }
 }
@@ -147,7 +148,8 @@ __global__ void __launch_bounds__(NT) ce_parallel_bwd_kernel(const CrossEntropyA
     for (int c = threadIdx.x; c < a.V; c += NT) grow[c] = static_cast<T>(0.f);
     return;
   }
-  write_grad(row, grow, a.V, gmax[r], gsum[r], tgt - a.vocab_start, a.grad_scale, 0.f, a.V);
+  write_grad(row, grow, a.V, gmax[r], gsum[r], tgt - a.vocab_start,
+             a.grad_scale * (a.grad_scale_dev ? *a.grad_scale_dev : 1.f), 0.f, a.V);
 }
 
 }  // namespace

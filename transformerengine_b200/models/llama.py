@@ -129,31 +129,35 @@ class _GatherFromSP(torch.autograd.Function):
 
 
 class _FusedCrossEntropy(torch.autograd.Function):
-    """Mean token loss; the logits buffer is overwritten with the gradient in forward."""
+    """Mean token loss over a (possibly vocab-sharded) logits tensor.
+
+    Forward reads the logits once for the per-row max / sum-exp / target logit;
+    backward overwrites the logits buffer with the gradient, scaled on the device
+    by the incoming gradient, so no separate scaling pass runs.
+    """
 
     @staticmethod
     def forward(ctx, logits, labels, tp_group, vocab_start):  # type: ignore[override]
-        n = labels.numel()
         valid = (labels != -100).sum().clamp(min=1).float()
-        if tp_group is None or D.get_world_size(tp_group) == 1:
-            loss_rows, grad = ops.cross_entropy_fwd_bwd(logits, labels, 1.0, inplace_grad=True)
-        else:
-            m, s, t = ops.cross_entropy_stats(logits, labels, vocab_start)
+        m, s, t = ops.cross_entropy_stats(logits, labels, vocab_start)
+        if tp_group is not None and D.get_world_size(tp_group) > 1:
             gm = m.clone()
             dist.all_reduce(gm, op=dist.ReduceOp.MAX, group=tp_group)
-            s = s * torch.exp(m - gm)
-            st = torch.stack([s, t])
+            st = torch.stack([s * torch.exp(m - gm), t])
             dist.all_reduce(st, group=tp_group)
             gs, gt = st[0], st[1]
-            loss_rows = torch.where(labels.reshape(-1) == -100, torch.zeros_like(gs), gm + torch.log(gs) - gt)
-            grad = ops.cross_entropy_parallel_grad(logits, labels, gm, gs, vocab_start, 1.0, inplace_grad=True)
-        ctx.save_for_backward(grad, valid)
+        else:
+            gm, gs, gt = m, s, t
+        loss_rows = torch.where(labels.reshape(-1) == -100, torch.zeros_like(gs), gm + torch.log(gs) - gt)
+        ctx.save_for_backward(logits, labels, gm, gs, valid)
+        ctx.vocab_start = vocab_start
         return loss_rows.sum() / valid
 
     @staticmethod
     def backward(ctx, go):  # type: ignore[override]
-        grad, valid = ctx.saved_tensors
-        grad.mul_((go / valid).to(grad.dtype))
+        logits, labels, gm, gs, valid = ctx.saved_tensors
+        grad = ops.cross_entropy_parallel_grad(logits, labels, gm, gs, ctx.vocab_start, 1.0, inplace_grad=True,
+                                               grad_scale_dev=(go.float() / valid))
         return grad, None, None, None
 
 

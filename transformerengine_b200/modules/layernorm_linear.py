@@ -114,7 +114,8 @@ class _LayerNormLinear(torch.autograd.Function):
             keep = (ln_hp if sp_gather else ln_total) if need_wgrad else None
             if F._is_q(keep) and keep.get_usages()["columnwise"]:
                 keep.update_usage(rowwise_usage=False)
-            flat, objs = prepare_for_saving(keep, wq if F._is_q(wq) else None)
+            ctx.wq = wq if F._is_q(wq) else None  # cached object shared across calls: not stripped
+            flat, objs = prepare_for_saving(keep)
             ctx.save_for_backward(*flat, x2d, ln_w, ln_b, mu, rs, weight, bias)
             ctx.objs = objs
             ctx.module, ctx.cfg, ctx.fp8 = module, cfg, fp8
@@ -136,7 +137,8 @@ class _LayerNormLinear(torch.autograd.Function):
         saved = list(ctx.saved_tensors)
         bias = saved.pop(); weight = saved.pop(); rs = saved.pop(); mu = saved.pop()
         ln_b = saved.pop(); ln_w = saved.pop(); x2d = saved.pop()
-        keep, wq = restore_from_saved(ctx.objs, saved)
+        (keep,) = restore_from_saved(ctx.objs, saved)
+        wq = ctx.wq
         module, cfg = ctx.module, ctx.cfg
         w_use = wq if wq is not None else weight
         dy2d = grad_output.reshape(-1, grad_output.shape[-1]).to(cfg.activation_dtype).contiguous()

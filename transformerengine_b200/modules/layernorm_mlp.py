@@ -59,8 +59,9 @@ class _LayerNormMLP(torch.autograd.Function):
                 keep_ln.update_usage(rowwise_usage=False)
             if F._is_q(act_in) and act_in.get_usages()["columnwise"]:
                 act_in.update_usage(rowwise_usage=False)
-            flat, objs = prepare_for_saving(keep_ln, act_in, w1q if F._is_q(w1q) else None,
-                                            w2q if F._is_q(w2q) else None)
+            ctx.w1q = w1q if F._is_q(w1q) else None  # cached objects shared across calls: not stripped
+            ctx.w2q = w2q if F._is_q(w2q) else None
+            flat, objs = prepare_for_saving(keep_ln, act_in)
             ctx.save_for_backward(*flat, x2d, ln_w, ln_b, mu, rs, fc1_out, fc1_w, fc1_b, fc2_w, fc2_b)
             ctx.objs = objs
             ctx.module, ctx.fp8 = module, fp8
@@ -79,7 +80,8 @@ class _LayerNormMLP(torch.autograd.Function):
         fc2_b = saved.pop(); fc2_w = saved.pop(); fc1_b = saved.pop(); fc1_w = saved.pop()
         fc1_out = saved.pop(); rs = saved.pop(); mu = saved.pop(); ln_b = saved.pop(); ln_w = saved.pop()
         x2d = saved.pop()
-        keep_ln, act_in, w1q, w2q = restore_from_saved(ctx.objs, saved)
+        keep_ln, act_in = restore_from_saved(ctx.objs, saved)
+        w1q, w2q = ctx.w1q, ctx.w2q
         module = ctx.module
         cfg1, cfg2 = module.cfg1, module.cfg2
         adt = cfg1.activation_dtype

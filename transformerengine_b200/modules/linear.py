@@ -38,7 +38,9 @@ class _Linear(torch.autograd.Function):
             if F._is_q(save_x) and need_wgrad:
                 save_x.update_usage(rowwise_usage=False) if save_x.get_usages()["columnwise"] else None
             keep_x = save_x if need_wgrad else None
-            flat, objs = prepare_for_saving(keep_x, weight_q if F._is_q(weight_q) else None)
+            # the quantized weight is a cached object shared across calls: keep a reference, do not strip it
+            ctx.wq = weight_q if F._is_q(weight_q) else None
+            flat, objs = prepare_for_saving(keep_x)
             ctx.save_for_backward(*flat, weight, bias)
             ctx.objs = objs
             ctx.module, ctx.cfg = module, cfg
@@ -63,7 +65,8 @@ class _Linear(torch.autograd.Function):
         saved = list(ctx.saved_tensors)
         bias = saved.pop()
         weight = saved.pop()
-        keep_x, wq = restore_from_saved(ctx.objs, saved)
+        (keep_x,) = restore_from_saved(ctx.objs, saved)
+        wq = ctx.wq
         module, cfg = ctx.module, ctx.cfg
         w_use = wq if wq is not None else weight
         dy2d = grad_output.reshape(-1, grad_output.shape[-1])

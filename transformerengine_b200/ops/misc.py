@@ -99,7 +99,7 @@ def cross_entropy_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, grad_scal
         loss = torch.empty(l2.shape[0], dtype=torch.float32, device=logits.device)
         grad = l2 if inplace_grad else torch.empty_like(l2)
         _ext.get().cross_entropy(l2, t.contiguous(), loss, grad, None, None, None, 0, grad_scale, label_smoothing,
-                                 ignore_index, None, None)
+                                 ignore_index, None, None, None)
         return loss, grad.reshape(logits.shape)
     lf = l2.float()
     loss = cross_entropy_ref(lf, t, label_smoothing, ignore_index)
@@ -119,7 +119,7 @@ def cross_entropy_stats(logits, targets, vocab_start, ignore_index=-100):
     if _ext.use_cuda(logits) and l2.stride(-1) == 1:
         st = torch.empty(3, R, dtype=torch.float32, device=logits.device)
         _ext.get().cross_entropy(l2, t.contiguous(), None, None, st[0], st[1], st[2], vocab_start, 1.0, 0.0,
-                                 ignore_index, None, None)
+                                 ignore_index, None, None, None)
         return st[0], st[1], st[2]
     lf = l2.float()
     m = lf.max(-1).values
@@ -131,7 +131,7 @@ def cross_entropy_stats(logits, targets, vocab_start, ignore_index=-100):
 
 
 def cross_entropy_parallel_grad(logits, targets, gmax, gsum, vocab_start, grad_scale=1.0, ignore_index=-100,
-                                inplace_grad=True):
+                                inplace_grad=True, grad_scale_dev=None):
     """Vocab-parallel stage 2: gradient from the all-reduced statistics."""
     V = logits.shape[-1]
     l2 = logits.reshape(-1, V)
@@ -139,7 +139,8 @@ def cross_entropy_parallel_grad(logits, targets, gmax, gsum, vocab_start, grad_s
     if _ext.use_cuda(logits) and l2.stride(-1) == 1:
         grad = l2 if inplace_grad else torch.empty_like(l2)
         _ext.get().cross_entropy(l2, t.contiguous(), None, grad, None, None, None, vocab_start, grad_scale, 0.0,
-                                 ignore_index, gmax.contiguous(), gsum.contiguous())
+                                 ignore_index, gmax.contiguous(), gsum.contiguous(),
+                                 grad_scale_dev.float().reshape(1) if grad_scale_dev is not None else None)
         return grad.reshape(logits.shape)
     p = torch.exp(l2.float() - gmax[:, None]) / gsum[:, None]
     local = t - vocab_start
@@ -147,6 +148,8 @@ def cross_entropy_parallel_grad(logits, targets, gmax, gsum, vocab_start, grad_s
     rows = torch.arange(p.shape[0], device=p.device)[mine]
     p[rows, local[mine]] -= 1.0
     p = torch.where((t == ignore_index)[:, None], torch.zeros_like(p), p) * grad_scale
+    if grad_scale_dev is not None:
+        p = p * grad_scale_dev.float()
     return p.to(logits.dtype).reshape(logits.shape)
 
 

@@ -5,13 +5,88 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <teb200/api.h>
+#include <teb200/comm.h>
 #include <teb200/misc.h>
 #include <teb200/quant.h>
 #include <torch/extension.h>
 
 #include <optional>
+#include <vector>
 
 namespace py = pybind11;
 using OptT = std::optional<at::Tensor>;
 
-void register_extra(py::module_& m) { (void)m; }
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int dtype_code(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return teb200::kFloat32;
+    case at::kHalf: return teb200::kFloat16;
+    case at::kBFloat16: return teb200::kBFloat16;
+    default: return teb200::kByte;
+  }
+}
+
+// Fused collective GEMM.  `a` is the LOCAL gathered buffer [M, K] (all-gather) or the local
+// operand [M, K_local] (reduce-scatter); peer buffers are passed as raw device addresses taken
+// from the symmetric-memory rendezvous.
+void comm_gemm(int64_t mode, int64_t rank, int64_t world, int64_t epoch, int64_t copy_ctas, const at::Tensor& a,
+               const OptT& sfa, const at::Tensor& b, const OptT& sfb, const OptT& d, const OptT& bias, bool a_e5m2,
+               bool b_e5m2, std::vector<int64_t> a_ptrs, std::vector<int64_t> sfa_ptrs,
+               std::vector<int64_t> ready_ptrs, int64_t chunk_flags_ptr, std::vector<int64_t> stage_ptrs,
+               std::vector<int64_t> tile_flag_ptrs, const OptT& out, int64_t N, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(a.device());
+  teb200::CommGemmArgs c;
+  teb200::GemmArgs& g = c.g;
+  const bool mx = sfa.has_value() && sfa->defined();
+  g.a = a.data_ptr();
+  g.b = b.data_ptr();
+  g.M = static_cast<int>(a.size(0));
+  g.K = static_cast<int>(a.size(1));
+  g.N = static_cast<int>(N);
+  g.lda = a.stride(0);
+  g.ldb = b.stride(0);
+  if (mx) {
+    g.a_dtype = a_e5m2 ? teb200::kFloat8E5M2 : teb200::kFloat8E4M3;
+    g.b_dtype = b_e5m2 ? teb200::kFloat8E5M2 : teb200::kFloat8E4M3;
+    g.sfa = static_cast<const uint8_t*>(sfa->data_ptr());
+    g.sfb = static_cast<const uint8_t*>(sfb->data_ptr());
+  } else {
+    g.a_dtype = g.b_dtype = dtype_code(a);
+  }
+  const at::Tensor& o = (mode == teb200::kCommAllGather) ? *d : *out;
+  g.d_dtype = dtype_code(o);
+  if (mode == teb200::kCommAllGather) {
+    g.d = d->data_ptr();
+    g.ldd = d->stride(0);
+  }
+  if (bias.has_value() && bias->defined()) {
+    g.bias = bias->data_ptr();
+    g.bias_dtype = dtype_code(*bias);
+  }
+  g.status = status.data_ptr<int>();
+  c.mode = static_cast<int>(mode);
+  c.rank = static_cast<int>(rank);
+  c.world = static_cast<int>(world);
+  c.epoch = static_cast<uint32_t>(epoch);
+  c.copy_ctas = static_cast<int>(copy_ctas);
+  for (int r = 0; r < world && r < teb200::kCommMaxRanks; ++r) {
+    if (!a_ptrs.empty()) c.a_full[r] = reinterpret_cast<const uint8_t*>(a_ptrs[r]);
+    if (!sfa_ptrs.empty()) c.sfa_full[r] = reinterpret_cast<const uint8_t*>(sfa_ptrs[r]);
+    if (!ready_ptrs.empty()) c.ready[r] = reinterpret_cast<uint32_t*>(ready_ptrs[r]);
+    if (!stage_ptrs.empty()) c.stage[r] = reinterpret_cast<uint8_t*>(stage_ptrs[r]);
+    if (!tile_flag_ptrs.empty()) c.tile_flags[r] = reinterpret_cast<uint32_t*>(tile_flag_ptrs[r]);
+  }
+  c.a_row_bytes = a.stride(0) * a.element_size();
+  c.sf_bytes_per_mblock = mx ? static_cast<long long>(((g.K + 31) / 32 + 3) / 4) * 512 : 0;
+  c.chunk_flags = reinterpret_cast<uint32_t*>(chunk_flags_ptr);
+  c.out = (out.has_value() && out->defined()) ? out->data_ptr() : nullptr;
+  cudaError_t e = teb200::comm_gemm(c, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "comm_gemm failed: ", cudaGetErrorString(e));
+}
+
+}  // namespace
+
+void register_extra(py::module_& m) { m.def("comm_gemm", &comm_gemm); }

@@ -1,0 +1,509 @@
+// tcgen05 GEMM fused with an all-gather of its A operand or a reduce-scatter of its
+// output over NVLink peer memory (see teb200/comm.h for the protocol).  The GEMM
+// pipeline is the one of gemm/gemm_tcgen05.cu (TMA producer warp, MMA warp, four
+// epilogue warps, TMEM accumulators); this file adds
+//   * copy CTAs that pull peer rows with L1-bypassing loads and publish per-block flags,
+//   * a producer that waits (bounded) for the flag of the block it is about to load,
+//   * an epilogue that stores tiles into the owner rank's staging buffer and a tail that
+//     reduces the blocks this rank owns once every rank has delivered them.
+// Tiles are visited in an order rotated by the rank so that at any time the ranks
+// pull from / push to different peers.
+#include <teb200/comm.h>
+#include <teb200/gemm_common.cuh>
+#include <teb200/ptx.cuh>
+
+namespace teb200 {
+namespace {
+
+using namespace gemm_detail;
+
+constexpr int BN = 256;
+
+struct CommParams {
+  KernelParams k;
+  int mode, rank, world;
+  uint32_t epoch;
+  int copy_ctas;
+  int mb_per_rank;   // 128-row blocks owned by one rank
+  int num_n;         // column tiles
+  const uint8_t* a_full[kCommMaxRanks];
+  const uint8_t* sfa_full[kCommMaxRanks];
+  long long a_row_bytes, sf_bytes_per_mblock;
+  uint32_t* ready[kCommMaxRanks];
+  uint32_t* chunk_flags;
+  uint8_t* stage[kCommMaxRanks];
+  uint32_t* tile_flags[kCommMaxRanks];
+  void* out;
+};
+
+struct Tile {
+  int mb, nb;
+};
+
+// Logical tile index -> (row block, column tile).  Row blocks are visited shard by shard,
+// starting with the local shard (all-gather) or with the next rank's shard (reduce-scatter,
+// own rows last); inside a shard the row block varies fastest.
+__device__ __forceinline__ bool comm_tile(const CommParams& p, int t, Tile& out) {
+  const int per_shard = p.mb_per_rank * p.num_n;
+  if (t >= per_shard * p.world) return false;
+  const int i = t / per_shard, r = t - i * per_shard;
+  const int shard = p.mode == kCommAllGather ? (p.rank + i) % p.world : (p.rank + 1 + i) % p.world;
+  out.mb = shard * p.mb_per_rank + r % p.mb_per_rank;
+  out.nb = r / p.mb_per_rank;
+  return true;
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+__device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want) {
+  if (ld_acquire_gpu(p) >= want) return true;
+  const long long t0 = clock64();
+  while (ld_acquire_gpu(p) < want) {
+    if (clock64() - t0 > kWaitCycles) return false;
+    __nanosleep(32);
+  }
+  return true;
+}
+
+// ---------------------------------------------------------------- copy CTAs (all-gather)
+__device__ void copy_cta_loop(const CommParams& p, int cta, int* s_ok) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  if (cta == 0 && tid < p.world && tid != p.rank) {
+    // this rank's rows were written by earlier kernels of this stream: publish them to every peer
+    st_release_sys(p.ready[tid] + p.rank, p.epoch);
+  }
+  const int items = (p.world - 1) * p.mb_per_rank;
+  for (int it = cta; it < items; it += p.copy_ctas) {
+    const int src = (p.rank + 1 + it / p.mb_per_rank) % p.world;
+    const int mb = src * p.mb_per_rank + it % p.mb_per_rank;
+    if (tid == 0) {
+      const bool ok = wait_flag_ge(p.ready[p.rank] + src, p.epoch);
+      if (!ok && p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
+      *s_ok = ok ? 1 : 0;
+    }
+    __syncthreads();
+    if (*s_ok) {
+      const size_t off = static_cast<size_t>(mb) * kBlockM * p.a_row_bytes;
+      const uint4* s4 = reinterpret_cast<const uint4*>(p.a_full[src] + off);
+      uint4* d4 = reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.a_full[p.rank]) + off);
+      const int n16 = static_cast<int>(kBlockM * p.a_row_bytes / 16);
+      int i = tid;
+      for (; i + 3 * nt < n16; i += 4 * nt) {
+        const uint4 v0 = __ldcg(s4 + i), v1 = __ldcg(s4 + i + nt), v2 = __ldcg(s4 + i + 2 * nt),
+                    v3 = __ldcg(s4 + i + 3 * nt);
+        d4[i] = v0; d4[i + nt] = v1; d4[i + 2 * nt] = v2; d4[i + 3 * nt] = v3;
+      }
+      for (; i < n16; i += nt) d4[i] = __ldcg(s4 + i);
+      if (p.sf_bytes_per_mblock > 0) {
+        const size_t so = static_cast<size_t>(mb) * p.sf_bytes_per_mblock;
+        const uint4* ss = reinterpret_cast<const uint4*>(p.sfa_full[src] + so);
+        uint4* ds = reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.sfa_full[p.rank]) + so);
+        for (int j = tid; j < static_cast<int>(p.sf_bytes_per_mblock / 16); j += nt) ds[j] = __ldcg(ss + j);
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      st_release_gpu(p.chunk_flags + mb, p.epoch);  // published even after a time-out so the GEMM never hangs
+    }
+  }
+}
+
+// ---------------------------------------------------------------- reduce tail (reduce-scatter)
+// Executed by the four epilogue warps (128 threads, named barrier 1) after their tile loop.
+template <typename T>
+__device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, int* s_ok) {
+  const int items = p.mb_per_rank * p.num_n;
+  const int rows_per_rank = p.mb_per_rank * kBlockM;
+  const uint32_t expected = p.epoch * static_cast<uint32_t>(p.num_n);
+  const T* stage = reinterpret_cast<const T*>(p.stage[p.rank]);
+  T* out = reinterpret_cast<T*>(p.out);
+  const int N = p.k.N;
+  for (int it = cta; it < items; it += num_ctas) {
+    const int mbl = it % p.mb_per_rank, nb = it / p.mb_per_rank;
+    if (et < p.world) {
+      // one waiter per source rank
+      const bool ok = wait_flag_ge(p.tile_flags[p.rank] + et * p.mb_per_rank + mbl, expected);
+      if (!ok) {
+        if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
+      }
+    }
+    named_bar_sync(1, 128);
+    const int c_lo = nb * BN;
+    const int vec_per_row = BN / 8;
+    for (int v = et; v < kBlockM * vec_per_row; v += 128) {
+      const int r = v / vec_per_row, c = c_lo + (v % vec_per_row) * 8;
+      if (c >= N) continue;
+      const int lrow = mbl * kBlockM + r;
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+      for (int s = 0; s < p.world; ++s) {
+        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(
+            stage + (static_cast<size_t>(s) * rows_per_rank + lrow) * N + c));
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (sizeof(T) == 2 && p.k.d_dtype == kBFloat16) {
+            acc[2 * j] += __uint_as_float(w[j] << 16);
+            acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+            acc[2 * j] += __low2float(h);
+            acc[2 * j + 1] += __high2float(h);
+          }
+        }
+      }
+      if (p.k.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float b;
+          if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[c + i];
+          else if (p.k.bias_dtype == kBFloat16) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[c + i]);
+          else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[c + i]);
+          acc[i] += b;
+        }
+      }
+      uint4 o;
+      if (p.k.d_dtype == kBFloat16) {
+        o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                       pack_bf16x2(acc[6], acc[7]));
+      } else {
+        o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]),
+                       pack_f16x2(acc[6], acc[7]));
+      }
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(lrow) * N + c) = o;
+    }
+    named_bar_sync(1, 128);
+  }
+  (void)s_ok;
+}
+
+template <int KIND, int MODE>
+__global__ void __launch_bounds__(kNumThreads, 1)
+comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const CommParams p) {
+  using C = Cfg<KIND, BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + C::kStages;
+  uint64_t* tfull_bar = bars + 2 * C::kStages;
+  uint64_t* tempty_bar = tfull_bar + C::kAccStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAccStages);
+  int* s_ok = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  int gemm_ctas = gridDim.x, gemm_cta = blockIdx.x;
+  if (MODE == kCommAllGather) {
+    gemm_ctas = gridDim.x - p.copy_ctas;
+    gemm_cta = blockIdx.x - p.copy_ctas;
+    if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
+      copy_cta_loop(p, blockIdx.x, s_ok);
+      return;  // copy CTAs never touch TMEM or the pipeline barriers
+    }
+  }
+  const int num_k_blocks = (p.k.K + C::kBlockK - 1) / C::kBlockK;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < C::kAccStages; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 4);
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_sfa = tmem_base + C::kAccStages * BN;
+  const uint32_t tmem_sfb = tmem_sfa + C::kSfaCols;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      Tile ti;
+      for (int t = gemm_cta; ok && comm_tile(p, t, ti); t += gemm_ctas) {
+        if (MODE == kCommAllGather && ti.mb / p.mb_per_rank != p.rank) {
+          // rows of a peer: wait until a copy CTA has landed this 128-row block in local memory
+          if (!wait_ge_gpu(p.chunk_flags + ti.mb, p.epoch)) {
+            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
+          }
+          fence_proxy_async_all();  // generic-proxy writes of the copy CTA -> TMA (async proxy) reads
+        }
+        const int m0 = ti.mb * kBlockM, n0 = ti.nb * BN;
+        for (int kb = 0; kb < num_k_blocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutProducer);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          mbar_expect_tx(&full_bar[stage], C::kABytes + C::kBBytes + C::kSfaBytes + C::kSfbBytes);
+          if constexpr (KIND == kKindF16) {
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * C::kBlockK, m0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kb * C::kBlockK, n0);
+          } else {
+            const int kbyte0 = kb * C::kBlockKBytes;
+            tma_load_2d(sa, &tmap_a, &full_bar[stage], kbyte0, m0);
+            tma_load_2d(sb, &tmap_b, &full_bar[stage], kbyte0, n0);
+            uint8_t* ssfa = sb + C::kBBytes;
+            uint8_t* ssfb = ssfa + C::kSfaBytes;
+            bulk_load_1d(ssfa, p.k.sfa + (static_cast<size_t>(ti.mb) * p.k.sf_k_tiles + kb) * 512, 512,
+                         &full_bar[stage]);
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              bulk_load_1d(ssfb + j * 512,
+                           p.k.sfb + (static_cast<size_t>(n0 / 128 + j) * p.k.sf_k_tiles + kb) * 512, 512,
+                           &full_bar[stage]);
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      Tile ti;
+      for (int t = gemm_cta; ok && comm_tile(p, t, ti); t += gemm_ctas) {
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
+          if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k_blocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase)) {
+            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+          const uint64_t adesc = umma_desc_k_sw128(sa);
+          const uint64_t bdesc = umma_desc_k_sw128(sb);
+          if constexpr (KIND == kKindF16) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f16(tmem_d, adesc + k * 2, bdesc + k * 2, p.k.idesc, (kb | k) != 0);
+          } else {
+            const uint32_t ssfa = sb + C::kBBytes;
+            const uint32_t ssfb = ssfa + C::kSfaBytes;
+            utccp_sf(tmem_sfa, umma_desc_sf(ssfa));
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) utccp_sf(tmem_sfb + j * 4, umma_desc_sf(ssfb + j * 512));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t idesc = p.k.idesc | (uint32_t(k) << 29) | (uint32_t(k) << 4);
+              umma_mxf8(tmem_d, adesc + k * 2, bdesc + k * 2, idesc, (kb | k) != 0, tmem_sfa, tmem_sfb);
+            }
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);
+        if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    const int et = quarter * 32 + lane;  // 0..127 inside the epilogue group
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
+    const int rows_per_rank = p.mb_per_rank * kBlockM;
+    Tile ti;
+    for (int t = gemm_cta; comm_tile(p, t, ti); t += gemm_ctas) {
+      if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
+        if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int m0 = ti.mb * kBlockM, n0 = ti.nb * BN;
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
+      // destination row: plain output for all-gather, the owner's staging slot for reduce-scatter
+      uint16_t* drow;
+      if (MODE == kCommReduceScatter) {
+        const int owner = ti.mb / p.mb_per_rank;
+        const int lrow = row - owner * rows_per_rank;
+        drow = reinterpret_cast<uint16_t*>(p.stage[owner]) +
+               (static_cast<size_t>(p.rank) * rows_per_rank + lrow) * p.k.N;
+      } else {
+        drow = reinterpret_cast<uint16_t*>(p.k.d) + static_cast<size_t>(row) * p.k.ldd;
+      }
+      const bool bf = p.k.d_dtype == kBFloat16;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c0, r);
+        tmem_ld_wait();
+        if (c0 + 32 >= BN) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+        }
+        const int col0 = n0 + c0;
+        if (row >= p.k.M || col0 >= p.k.N) continue;
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+        if (MODE != kCommReduceScatter && p.k.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + i < p.k.N) {
+              float b;
+              if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
+              else if (p.k.bias_dtype == kBFloat16)
+                b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
+              else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
+              v[i] += b;
+            }
+          }
+        }
+        uint16_t* dp = drow + col0;
+        if (col0 + 32 <= p.k.N) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            if (bf) {
+              o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                             pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+            } else {
+              o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
+                             pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
+            }
+            *reinterpret_cast<uint4*>(dp + i) = o;
+          }
+        } else {
+          for (int i = 0; col0 + i < p.k.N; ++i) {
+            if (bf) reinterpret_cast<__nv_bfloat16*>(dp)[i] = __float2bfloat16(v[i]);
+            else reinterpret_cast<__half*>(dp)[i] = __float2half(v[i]);
+          }
+        }
+      }
+      if (MODE == kCommReduceScatter) {
+        // make this thread's peer stores visible system-wide, then one thread bumps the owner's counter
+        __threadfence_system();
+        named_bar_sync(1, 128);
+        if (et == 0) {
+          const int owner = ti.mb / p.mb_per_rank;
+          red_release_sys_add(p.tile_flags[owner] + p.rank * p.mb_per_rank + ti.mb % p.mb_per_rank, 1u);
+        }
+      }
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+    }
+    if (MODE == kCommReduceScatter) {
+      if (p.k.d_dtype == kBFloat16) reduce_tail<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et, s_ok);
+      else reduce_tail<__half>(p, gemm_cta, gemm_ctas, et, s_ok);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int KIND, int MODE>
+cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
+  using C = Cfg<KIND, BN>;
+  const GemmArgs& g = a.g;
+  CUtensorMap ta, tb;
+  bool ok;
+  if (KIND == kKindF16) {
+    ok = make_tensor_map_2d(&ta, g.a, g.a_dtype, g.M, g.K, g.lda, kBlockM, 64, true) &&
+         make_tensor_map_2d(&tb, g.b, g.b_dtype, g.N, g.K, g.ldb, BN, 64, true);
+  } else {
+    ok = make_tensor_map_2d(&ta, g.a, kByte, g.M, g.K, g.lda, kBlockM, 128, true) &&
+         make_tensor_map_2d(&tb, g.b, kByte, g.N, g.K, g.ldb, BN, 128, true);
+  }
+  if (!ok) return cudaErrorInvalidValue;
+  CommParams p = {};
+  KernelParams& k = p.k;
+  k.d = g.d; k.bias = g.bias; k.aux = nullptr; k.sfa = g.sfa; k.sfb = g.sfb; k.alpha_dev = g.alpha_dev;
+  k.group_offsets = nullptr; k.status = g.status; k.alpha = g.alpha;
+  k.M = g.M; k.N = g.N; k.K = g.K; k.ldd = g.ldd;
+  k.d_dtype = g.d_dtype; k.bias_dtype = g.bias_dtype; k.epilogue = 0; k.accumulate = 0; k.a_mn = 0; k.b_mn = 0;
+  k.idesc = make_idesc(KIND, g.a_dtype, g.b_dtype, BN, false, false);
+  k.num_groups = 0;
+  k.sf_k_tiles = KIND == kKindF16 ? 0 : ((g.K + 31) / 32 + 3) / 4;
+  p.mode = MODE; p.rank = a.rank; p.world = a.world; p.epoch = a.epoch;
+  p.mb_per_rank = g.M / kBlockM / a.world;
+  p.num_n = (g.N + BN - 1) / BN;
+  const int sms = g.sm_count > 0 ? g.sm_count : device_sm_count();
+  int copy = MODE == kCommAllGather ? a.copy_ctas : 0;
+  if (copy < 1 && MODE == kCommAllGather) copy = 1;
+  if (copy > sms / 2) copy = sms / 2;
+  p.copy_ctas = copy;
+  for (int r = 0; r < kCommMaxRanks; ++r) {
+    p.a_full[r] = a.a_full[r]; p.sfa_full[r] = a.sfa_full[r]; p.ready[r] = a.ready[r];
+    p.stage[r] = a.stage[r]; p.tile_flags[r] = a.tile_flags[r];
+  }
+  p.a_row_bytes = a.a_row_bytes; p.sf_bytes_per_mblock = a.sf_bytes_per_mblock;
+  p.chunk_flags = a.chunk_flags; p.out = a.out;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<KIND, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  // every CTA must be resident at once (copy CTAs and GEMM CTAs wait on one another; the
+  // reduce tail waits on peers): one CTA per SM, never more CTAs than SMs
+  comm_gemm_kernel<KIND, MODE><<<sms, kNumThreads, C::kSmemBytes, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t comm_gemm(const CommGemmArgs& a, cudaStream_t stream) {
+  const GemmArgs& g = a.g;
+  if (a.world < 2 || a.world > kCommMaxRanks) return cudaErrorInvalidValue;
+  if (g.M % (kBlockM * a.world) != 0 || g.N % 8 != 0 || g.K <= 0) return cudaErrorInvalidValue;
+  if (g.d_dtype != kBFloat16 && g.d_dtype != kFloat16) return cudaErrorInvalidValue;
+  const bool mx = g.sfa != nullptr;
+  if (mx && g.K % 128 != 0) return cudaErrorInvalidValue;
+  if (a.mode == kCommAllGather)
+    return mx ? launch_comm<kKindMxf8, kCommAllGather>(a, stream) : launch_comm<kKindF16, kCommAllGather>(a, stream);
+  if (a.mode == kCommReduceScatter)
+    return mx ? launch_comm<kKindMxf8, kCommReduceScatter>(a, stream)
+              : launch_comm<kKindF16, kCommReduceScatter>(a, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace teb200

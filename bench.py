@@ -35,6 +35,7 @@ def parse():
     ap.add_argument("--recompute", type=int, default=-1, help="-1 auto, 0 off, 1 per-layer recompute")
     ap.add_argument("--recipe", default="mxfp8")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--fused-comm", type=int, default=1, help="fuse TP collectives into the GEMM kernels")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
     return ap.parse_args()
 
@@ -145,6 +146,8 @@ def run_ours(args):
     # sequence add ~30 GB, which fits in 180 GB without recompute
     cfg.recompute = bool(args.recompute) if args.recompute >= 0 else False
     tp_group = dist.group.WORLD if tp > 1 else None
+    if tp > 1 and args.fused_comm:
+        te.initialize_ub(tp_group=tp_group)
     model = llama.LlamaModel(cfg, tp_group=tp_group, sequence_parallel=True)
     if dp > 1:
         for p in model.parameters():
@@ -228,7 +231,8 @@ def run_ours(args):
                "config": {"model": "llama3-8b-arch" if args.layers == 32 else f"llama3-8b-arch-{args.layers}L",
                           "global_batch": dp, "seq_len": args.seq,
                           "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
-                          "recipe": args.recipe, "optimizer": "fused-adam fp32 master", "recompute": cfg.recompute,
+                          "recipe": args.recipe, "optimizer": "fused-adam fp32 master",
+                          "fused_comm_gemm": bool(tp > 1 and args.fused_comm), "recompute": cfg.recompute,
                           "l2": "inputs and weights (16 GB) far exceed the 126 MB L2"},
                "tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
                "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30}

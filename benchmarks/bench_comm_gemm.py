@@ -1,0 +1,99 @@
+"""Fused collective GEMMs vs NCCL collective + dense GEMM, per shape.
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/bench_comm_gemm.py
+
+Device time (CUDA events), max over ranks.  Roofline of a fused op = the slower of
+(FLOPs / GEMM rate of the dense kernel measured here) and (bytes over NVLink / 770 GB/s).
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import transformerengine_b200 as te  # noqa: E402
+from transformerengine_b200 import ops  # noqa: E402
+from transformerengine_b200.parallel.comm_gemm import AllGatherGemm, GemmReduceScatter  # noqa: E402
+from transformerengine_b200.tensor import MXFP8Quantizer  # noqa: E402
+
+LINK_GBS = 770.0
+
+
+def timed(fn, iters=10):
+    for _ in range(3):
+        fn()
+    dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shapes", default="llama")
+    ap.add_argument("--copy-ctas", type=int, default=12)
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+    g = dist.group.WORLD
+    # (tokens, hidden, full width of the sharded dim)
+    shapes = {"llama": [(8192, 4096, 6144), (8192, 4096, 28672)],
+              "layer12288": [(4096, 12288, 36864), (4096, 12288, 49152)]}[a.shapes]
+    q = MXFP8Quantizer(columnwise=False)
+    for T, H, F in shapes:
+        Fl = F // world
+        for mx in (True, False):
+            xl = torch.randn(T // world, H, device="cuda", dtype=torch.bfloat16)
+            w1 = torch.randn(Fl, H, device="cuda", dtype=torch.bfloat16)
+            x2 = torch.randn(T, Fl, device="cuda", dtype=torch.bfloat16)
+            w2 = torch.randn(H, Fl, device="cuda", dtype=torch.bfloat16)
+            if mx:
+                xl_o, w1_o, x2_o, w2_o = q(xl), q(w1), q(x2), q(w2)
+            else:
+                xl_o, w1_o, x2_o, w2_o = xl, w1, x2, w2
+            ag = AllGatherGemm(g, T, H, mxfp8=mx, copy_ctas=a.copy_ctas)
+            rs = GemmReduceScatter(g, T, H)
+            xg = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(xg, xl)
+            xg_o = q(xg) if mx else xg
+            xg8 = torch.empty(T, H, device="cuda", dtype=torch.uint8 if mx else torch.bfloat16)
+            xl8 = xl_o._rowwise_data if mx else xl
+            part = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
+            outrs = torch.empty(T // world, H, device="cuda", dtype=torch.bfloat16)
+
+            t_ag_fused = timed(lambda: ag(xl_o, w1_o))
+            t_ag_gemm = timed(lambda: ops.gemm_nt(ops.as_operand(xg_o), ops.as_operand(w1_o), out_dtype=torch.bfloat16))
+            t_ag_nccl = timed(lambda: dist.all_gather_into_tensor(xg8, xl8))
+            t_rs_fused = timed(lambda: rs(x2_o, w2_o))
+            t_rs_gemm = timed(lambda: ops.gemm_nt(ops.as_operand(x2_o), ops.as_operand(w2_o), out=part))
+            t_rs_nccl = timed(lambda: dist.reduce_scatter_tensor(outrs, part))
+            te.check_status()
+            elem = 1 if mx else 2
+            ag_bytes = T * H * elem * (world - 1) / world
+            rs_bytes = T * H * 2 * (world - 1) / world
+            roof_ag = max(t_ag_gemm, ag_bytes / LINK_GBS / 1e6)
+            roof_rs = max(t_rs_gemm, rs_bytes / LINK_GBS / 1e6)
+            if rank == 0:
+                print(json.dumps(dict(T=T, H=H, F_local=Fl, mxfp8=mx, world=world,
+                                      ag_fused_ms=t_ag_fused, ag_gemm_ms=t_ag_gemm, ag_nccl_ms=t_ag_nccl,
+                                      ag_roofline_ms=roof_ag, ag_frac_of_roofline=roof_ag / t_ag_fused,
+                                      rs_fused_ms=t_rs_fused, rs_gemm_ms=t_rs_gemm, rs_nccl_ms=t_rs_nccl,
+                                      rs_roofline_ms=roof_rs, rs_frac_of_roofline=roof_rs / t_rs_fused)), flush=True)
+            del ag, rs
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -24,6 +24,7 @@ from .attention.rope import RotaryPositionEmbedding, apply_rotary_pos_emb
 from .transformer import TransformerLayer
 from .parallel.distributed import checkpoint, CudaRNGStatesTracker
 from .optim import FusedAdam, FusedSGD
+from .parallel.comm_gemm import initialize_ub, destroy_ub
 from . import optim as optimizers  # noqa: F401
 
 __version__ = "0.1.0"

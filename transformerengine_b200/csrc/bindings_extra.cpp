@@ -61,6 +61,8 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, int64_t epoch, int64_t
   if (mode == teb200::kCommAllGather) {
     g.d = d->data_ptr();
     g.ldd = d->stride(0);
+  } else if (d.has_value() && d->defined()) {
+    g.aux = d->data_ptr();  // optional int64 [ctas, 4] timeline buffer (profiling aid)
   }
   if (bias.has_value() && bias->defined()) {
     g.bias = bias->data_ptr();

@@ -61,6 +61,11 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ unsigned long long gtimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
 __device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want) {
@@ -74,91 +79,160 @@ __device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want) {
 }
 
 // ---------------------------------------------------------------- copy CTAs (all-gather)
-__device__ void copy_cta_loop(const CommParams& p, int cta, int* s_ok) {
-  const int tid = threadIdx.x, nt = blockDim.x;
+// One thread per copy CTA streams peer rows through a ring of shared-memory slots with bulk
+// async copies: peer global -> shared (completion on an mbarrier), shared -> local global
+// (bulk group).  About kCopySlots * kCopyPiece bytes stay in flight per CTA, which is what hides
+// the NVLink round trip; plain per-thread loads keep only a few KB in flight.
+constexpr int kCopyPiece = 32 * 1024;
+constexpr int kCopySlots = 6;
+
+__device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars) {
+  const int tid = threadIdx.x;
   if (cta == 0 && tid < p.world && tid != p.rank) {
     // this rank's rows were written by earlier kernels of this stream: publish them to every peer
     st_release_sys(p.ready[tid] + p.rank, p.epoch);
   }
+  if (tid != 0) return;
+  for (int i = 0; i < kCopySlots; ++i) mbar_init(&bars[i], 1);
+  mbar_fence_init();
   const int items = (p.world - 1) * p.mb_per_rank;
-  for (int it = cta; it < items; it += p.copy_ctas) {
-    const int src = (p.rank + 1 + it / p.mb_per_rank) % p.world;
-    const int mb = src * p.mb_per_rank + it % p.mb_per_rank;
-    if (tid == 0) {
-      const bool ok = wait_flag_ge(p.ready[p.rank] + src, p.epoch);
-      if (!ok && p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
-      *s_ok = ok ? 1 : 0;
+  const long long data_bytes = static_cast<long long>(kBlockM) * p.a_row_bytes;
+  const long long item_bytes = data_bytes + p.sf_bytes_per_mblock;
+  const int pieces_per_item = static_cast<int>((data_bytes + kCopyPiece - 1) / kCopyPiece) +
+                              static_cast<int>((p.sf_bytes_per_mblock + kCopyPiece - 1) / kCopyPiece);
+  const int my_items = cta < items ? (items - cta + p.copy_ctas - 1) / p.copy_ctas : 0;
+  const int total = my_items * pieces_per_item;
+  (void)item_bytes;
+
+  // piece index -> (source pointer, destination pointer, bytes, is last piece of its item, block id)
+  auto piece = [&](int q, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, int& mb, int& srank) {
+    const int it = cta + (q / pieces_per_item) * p.copy_ctas;
+    const int j = q % pieces_per_item;
+    srank = (p.rank + 1 + it / p.mb_per_rank) % p.world;
+    mb = srank * p.mb_per_rank + it % p.mb_per_rank;
+    const int data_pieces = static_cast<int>((data_bytes + kCopyPiece - 1) / kCopyPiece);
+    if (j < data_pieces) {
+      const long long off = static_cast<long long>(mb) * data_bytes + static_cast<long long>(j) * kCopyPiece;
+      const long long left = data_bytes - static_cast<long long>(j) * kCopyPiece;
+      bytes = static_cast<uint32_t>(left < kCopyPiece ? left : kCopyPiece);
+      src = p.a_full[srank] + off;
+      dst = const_cast<uint8_t*>(p.a_full[p.rank]) + off;
+    } else {
+      const int js = j - data_pieces;
+      const long long off = static_cast<long long>(mb) * p.sf_bytes_per_mblock + static_cast<long long>(js) * kCopyPiece;
+      const long long left = p.sf_bytes_per_mblock - static_cast<long long>(js) * kCopyPiece;
+      bytes = static_cast<uint32_t>(left < kCopyPiece ? left : kCopyPiece);
+      src = p.sfa_full[srank] + off;
+      dst = const_cast<uint8_t*>(p.sfa_full[p.rank]) + off;
     }
-    __syncthreads();
-    if (*s_ok) {
-      const size_t off = static_cast<size_t>(mb) * kBlockM * p.a_row_bytes;
-      const uint4* s4 = reinterpret_cast<const uint4*>(p.a_full[src] + off);
-      uint4* d4 = reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.a_full[p.rank]) + off);
-      const int n16 = static_cast<int>(kBlockM * p.a_row_bytes / 16);
-      int i = tid;
-      for (; i + 3 * nt < n16; i += 4 * nt) {
-        const uint4 v0 = __ldcg(s4 + i), v1 = __ldcg(s4 + i + nt), v2 = __ldcg(s4 + i + 2 * nt),
-                    v3 = __ldcg(s4 + i + 3 * nt);
-        d4[i] = v0; d4[i + nt] = v1; d4[i + 2 * nt] = v2; d4[i + 3 * nt] = v3;
-      }
-      for (; i < n16; i += nt) d4[i] = __ldcg(s4 + i);
-      if (p.sf_bytes_per_mblock > 0) {
-        const size_t so = static_cast<size_t>(mb) * p.sf_bytes_per_mblock;
-        const uint4* ss = reinterpret_cast<const uint4*>(p.sfa_full[src] + so);
-        uint4* ds = reinterpret_cast<uint4*>(const_cast<uint8_t*>(p.sfa_full[p.rank]) + so);
-        for (int j = tid; j < static_cast<int>(p.sf_bytes_per_mblock / 16); j += nt) ds[j] = __ldcg(ss + j);
+  };
+
+  bool ok = true;
+  int issued = 0;
+  auto issue_load = [&](int q) {
+    const uint8_t* src; uint8_t* dst; uint32_t bytes; int mb, srank;
+    piece(q, src, dst, bytes, mb, srank);
+    if (q % pieces_per_item == 0) {
+      // first piece of an item: the source rank must have published its rows for this call
+      if (!wait_flag_ge(p.ready[p.rank] + srank, p.epoch)) {
+        if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
-    __syncthreads();
-    if (tid == 0) {
+    const int slot = q % kCopySlots;
+    mbar_expect_tx(&bars[slot], bytes);
+    bulk_load_1d(smem + slot * kCopyPiece, src, bytes, &bars[slot]);
+  };
+  for (; issued < total && issued < kCopySlots - 1; ++issued) issue_load(issued);
+  for (int q = 0; q < total && ok; ++q) {
+    const int slot = q % kCopySlots;
+    const uint32_t phase = (q / kCopySlots) & 1;
+    if (!mbar_wait(&bars[slot], phase)) {
+      if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
+      ok = false;
+    }
+    const uint8_t* src; uint8_t* dst; uint32_t bytes; int mb, srank;
+    piece(q, src, dst, bytes, mb, srank);
+    if (ok) {
+      bulk_store_1d(dst, smem + slot * kCopyPiece, bytes);
+      tma_store_commit();
+    }
+    if (issued < total) {
+      // the slot of piece `issued` was last read by the store of piece issued - kCopySlots = q - 1
+      tma_store_wait_read<1>();
+      issue_load(issued);
+      ++issued;
+    }
+    if (q % pieces_per_item == pieces_per_item - 1) {
+      // whole 128-row block landed: wait for the local writes, then publish the block
+      tma_store_wait<0>();
+      fence_proxy_async_all();
       __threadfence();
-      st_release_gpu(p.chunk_flags + mb, p.epoch);  // published even after a time-out so the GEMM never hangs
+      st_release_gpu(p.chunk_flags + mb, p.epoch);
+    }
+  }
+  if (!ok) {
+    // never leave the GEMM waiting: publish every block of this CTA (data is wrong, status is set)
+    tma_store_wait<0>();
+    for (int it = cta; it < items; it += p.copy_ctas) {
+      const int srank = (p.rank + 1 + it / p.mb_per_rank) % p.world;
+      st_release_gpu(p.chunk_flags + srank * p.mb_per_rank + it % p.mb_per_rank, p.epoch);
     }
   }
 }
 
 // ---------------------------------------------------------------- reduce tail (reduce-scatter)
+// Owner-side staging layout (written by the peers' bulk stores): one 64 KB record per
+// (source rank, local row block, column tile); inside, two half tiles of 128 rows x 128
+// columns, rows of 256 bytes whose 16-byte chunks are XOR-swizzled with (row & 7).
+__device__ __forceinline__ size_t stage_tile_offset(const CommParams& p, int src, int mbl, int nb) {
+  return ((static_cast<size_t>(src) * p.mb_per_rank + mbl) * p.num_n + nb) * 65536;
+}
+
 // Executed by the four epilogue warps (128 threads, named barrier 1) after their tile loop.
 template <typename T>
-__device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, int* s_ok) {
+__device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et) {
   const int items = p.mb_per_rank * p.num_n;
-  const int rows_per_rank = p.mb_per_rank * kBlockM;
-  const uint32_t expected = p.epoch * static_cast<uint32_t>(p.num_n);
-  const T* stage = reinterpret_cast<const T*>(p.stage[p.rank]);
+  const uint32_t expected = p.epoch * static_cast<uint32_t>(p.num_n) * 2u;  // two half tiles per tile
+  const uint8_t* stage = p.stage[p.rank];
   T* out = reinterpret_cast<T*>(p.out);
   const int N = p.k.N;
   for (int it = cta; it < items; it += num_ctas) {
     const int mbl = it % p.mb_per_rank, nb = it / p.mb_per_rank;
     if (et < p.world) {
       // one waiter per source rank
-      const bool ok = wait_flag_ge(p.tile_flags[p.rank] + et * p.mb_per_rank + mbl, expected);
-      if (!ok) {
+      if (!wait_flag_ge(p.tile_flags[p.rank] + et * p.mb_per_rank + mbl, expected)) {
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
     named_bar_sync(1, 128);
     const int c_lo = nb * BN;
-    const int vec_per_row = BN / 8;
-    for (int v = et; v < kBlockM * vec_per_row; v += 128) {
-      const int r = v / vec_per_row, c = c_lo + (v % vec_per_row) * 8;
+    for (int v = et; v < kBlockM * 32; v += 128) {
+      const int r = v >> 5, cv = v & 31;  // row, 8-column vector index inside the 256-column tile
+      const int c = c_lo + cv * 8;
       if (c >= N) continue;
-      const int lrow = mbl * kBlockM + r;
+      const int half = cv >> 4, chunk = (cv & 15) ^ (r & 7);
+      const size_t in_tile = static_cast<size_t>(half) * 32768 + static_cast<size_t>(r) * 256 + chunk * 16;
       float acc[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      for (int s = 0; s < p.world; ++s) {
-        const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(
-            stage + (static_cast<size_t>(s) * rows_per_rank + lrow) * N + c));
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint4 raw[kCommMaxRanks];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (sizeof(T) == 2 && p.k.d_dtype == kBFloat16) {
-            acc[2 * j] += __uint_as_float(w[j] << 16);
-            acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
-          } else {
-            const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
-            acc[2 * j] += __low2float(h);
-            acc[2 * j + 1] += __high2float(h);
+      for (int sr = 0; sr < kCommMaxRanks; ++sr)
+        if (sr < p.world) raw[sr] = __ldcg(reinterpret_cast<const uint4*>(stage + stage_tile_offset(p, sr, mbl, nb) + in_tile));
+#pragma unroll
+      for (int sr = 0; sr < kCommMaxRanks; ++sr) {
+        if (sr < p.world) {
+          const uint32_t w[4] = {raw[sr].x, raw[sr].y, raw[sr].z, raw[sr].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (p.k.d_dtype == kBFloat16) {
+              acc[2 * j] += __uint_as_float(w[j] << 16);
+              acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+            } else {
+              const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+              acc[2 * j] += __low2float(h);
+              acc[2 * j + 1] += __high2float(h);
+            }
           }
         }
       }
@@ -180,27 +254,40 @@ __device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, 
         o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]),
                        pack_f16x2(acc[6], acc[7]));
       }
-      *reinterpret_cast<uint4*>(out + static_cast<size_t>(lrow) * N + c) = o;
+      *reinterpret_cast<uint4*>(out + static_cast<size_t>(mbl * kBlockM + r) * N + c) = o;
     }
     named_bar_sync(1, 128);
   }
-  (void)s_ok;
 }
+
+// Shared-memory plan: the reduce-scatter kernel trades one pipeline stage for a 64 KB output
+// staging area from which whole half tiles leave as single bulk stores to the owner rank.
+template <int KIND, int MODE>
+struct CommSmem {
+  using C = Cfg<KIND, BN>;
+  static constexpr int kStagingBytes = MODE == kCommReduceScatter ? 2 * 32768 : 0;
+  static constexpr int kStages = MODE == kCommReduceScatter ? 3 : C::kStages;
+  static constexpr int kBytes = kStages * C::kStageBytes + kStagingBytes + 1024 + 1024;
+  static_assert(kBytes <= 227 * 1024, "shared memory plan exceeds the per-CTA limit");
+  static_assert(kCopySlots * kCopyPiece <= kStages * C::kStageBytes || MODE != kCommAllGather,
+                "copy ring must fit in front of the barriers");
+};
 
 template <int KIND, int MODE>
 __global__ void __launch_bounds__(kNumThreads, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const CommParams p) {
   using C = Cfg<KIND, BN>;
+  constexpr int NS = CommSmem<KIND, MODE>::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* staging = smem + NS * C::kStageBytes;  // reduce-scatter: two 32 KB half-tile buffers
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + CommSmem<KIND, MODE>::kStagingBytes);
   uint64_t* full_bar = bars;
-  uint64_t* empty_bar = bars + C::kStages;
-  uint64_t* tfull_bar = bars + 2 * C::kStages;
+  uint64_t* empty_bar = bars + NS;
+  uint64_t* tfull_bar = bars + 2 * NS;
   uint64_t* tempty_bar = tfull_bar + C::kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAccStages);
-  int* s_ok = reinterpret_cast<int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -210,7 +297,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     gemm_ctas = gridDim.x - p.copy_ctas;
     gemm_cta = blockIdx.x - p.copy_ctas;
     if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
-      copy_cta_loop(p, blockIdx.x, s_ok);
+      copy_cta_loop(p, blockIdx.x, smem, bars);
       return;  // copy CTAs never touch TMEM or the pipeline barriers
     }
   }
@@ -219,7 +306,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
-    for (int i = 0; i < C::kStages; ++i) {
+    for (int i = 0; i < NS; ++i) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
     }
@@ -282,7 +369,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                            p.k.sfb + (static_cast<size_t>(n0 / 128 + j) * p.k.sf_k_tiles + kb) * 512, 512,
                            &full_bar[stage]);
           }
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == NS) { stage = 0; phase ^= 1; }
         }
       }
     }
@@ -329,7 +416,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           tc_commit(&empty_bar[stage]);
-          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+          if (++stage == NS) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
@@ -343,7 +430,11 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
-    const int rows_per_rank = p.mb_per_rank * kBlockM;
+    const bool bf = p.k.d_dtype == kBFloat16;
+    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.k.aux);  // optional timeline, 4 stamps per CTA
+    if (dbg && et == 0) dbg[gemm_cta * 4 + 0] = gtimer();
+    uint32_t halves = 0;                       // half tiles sent so far (reduce-scatter)
+    uint32_t* pending[2] = {nullptr, nullptr}; // owner counters to bump once a half tile has landed
     Tile ti;
     for (int t = gemm_cta; comm_tile(p, t, ti); t += gemm_ctas) {
       if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
@@ -354,80 +445,127 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int m0 = ti.mb * kBlockM, n0 = ti.nb * BN;
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      // destination row: plain output for all-gather, the owner's staging slot for reduce-scatter
-      uint16_t* drow;
       if (MODE == kCommReduceScatter) {
-        const int owner = ti.mb / p.mb_per_rank;
-        const int lrow = row - owner * rows_per_rank;
-        drow = reinterpret_cast<uint16_t*>(p.stage[owner]) +
-               (static_cast<size_t>(p.rank) * rows_per_rank + lrow) * p.k.N;
-      } else {
-        drow = reinterpret_cast<uint16_t*>(p.k.d) + static_cast<size_t>(row) * p.k.ldd;
-      }
-      const bool bf = p.k.d_dtype == kBFloat16;
+        const int owner = ti.mb / p.mb_per_rank, mbl = ti.mb % p.mb_per_rank;
+        uint8_t* dst_tile = p.stage[owner] + stage_tile_offset(p, p.rank, mbl, ti.nb);
+        uint32_t* flag = p.tile_flags[owner] + p.rank * p.mb_per_rank + mbl;
+        const int r_in = quarter * 32 + lane;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c0, r);
-        tmem_ld_wait();
-        if (c0 + 32 >= BN) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-        }
-        const int col0 = n0 + c0;
-        if (row >= p.k.M || col0 >= p.k.N) continue;
-        float v[32];
+        for (int half = 0; half < 2; ++half) {
+          uint8_t* buf = staging + (halves & 1) * 32768;
+          if (et == 0 && halves >= 2) {
+            // the bulk store that last used this buffer (two half tiles ago) has completed:
+            // its data is in the owner's memory, so the owner's counter may move
+            tma_store_wait<1>();
+            fence_proxy_async_all();
+            __threadfence_system();
+            red_release_sys_add(pending[halves & 1], 1u);
+          }
+          named_bar_sync(1, 128);
+#pragma unroll 1
+          for (int c0 = 0; c0 < 128; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + half * 128 + c0, r);
+            tmem_ld_wait();
+            if (half == 1 && c0 == 96) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+            }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-        if (MODE != kCommReduceScatter && p.k.bias != nullptr) {
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              float v[8];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            if (col0 + i < p.k.N) {
-              float b;
-              if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
-              else if (p.k.bias_dtype == kBFloat16)
-                b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
-              else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
-              v[i] += b;
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[i + j]) * alpha;
+              if (bf) {
+                o = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
+                               pack_bf16x2(v[6], v[7]));
+              } else {
+                o = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
+                               pack_f16x2(v[6], v[7]));
+              }
+              const int chunk = ((c0 + i) >> 3) ^ (r_in & 7);
+              *reinterpret_cast<uint4*>(buf + r_in * 256 + chunk * 16) = o;
             }
           }
+          fence_proxy_async_smem();  // generic-proxy writes to shared memory -> bulk (async proxy) read
+          named_bar_sync(1, 128);
+          if (et == 0) {
+            bulk_store_1d(dst_tile + half * 32768, buf, 32768);
+            tma_store_commit();
+            pending[halves & 1] = flag;
+          }
+          ++halves;
         }
-        uint16_t* dp = drow + col0;
-        if (col0 + 32 <= p.k.N) {
+      } else {
+        uint16_t* drow = reinterpret_cast<uint16_t*>(p.k.d) + static_cast<size_t>(row) * p.k.ldd;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          if (c0 + 32 >= BN) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+          }
+          const int col0 = n0 + c0;
+          if (row >= p.k.M || col0 >= p.k.N) continue;
+          float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 o;
-            if (bf) {
-              o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
-                             pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
-            } else {
-              o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
-                             pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+          if (p.k.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col0 + i < p.k.N) {
+                float b;
+                if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
+                else if (p.k.bias_dtype == kBFloat16)
+                  b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
+                else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
+                v[i] += b;
+              }
             }
-            *reinterpret_cast<uint4*>(dp + i) = o;
           }
-        } else {
-          for (int i = 0; col0 + i < p.k.N; ++i) {
-            if (bf) reinterpret_cast<__nv_bfloat16*>(dp)[i] = __float2bfloat16(v[i]);
-            else reinterpret_cast<__half*>(dp)[i] = __float2half(v[i]);
+          uint16_t* dp = drow + col0;
+          if (col0 + 32 <= p.k.N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              uint4 o;
+              if (bf) {
+                o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                               pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+              } else {
+                o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
+                               pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
+              }
+              *reinterpret_cast<uint4*>(dp + i) = o;
+            }
+          } else {
+            for (int i = 0; col0 + i < p.k.N; ++i) {
+              if (bf) reinterpret_cast<__nv_bfloat16*>(dp)[i] = __float2bfloat16(v[i]);
+              else reinterpret_cast<__half*>(dp)[i] = __float2half(v[i]);
+            }
           }
-        }
-      }
-      if (MODE == kCommReduceScatter) {
-        // make this thread's peer stores visible system-wide, then one thread bumps the owner's counter
-        __threadfence_system();
-        named_bar_sync(1, 128);
-        if (et == 0) {
-          const int owner = ti.mb / p.mb_per_rank;
-          red_release_sys_add(p.tile_flags[owner] + p.rank * p.mb_per_rank + ti.mb % p.mb_per_rank, 1u);
         }
       }
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
+    if (dbg && et == 0) dbg[gemm_cta * 4 + 1] = gtimer();
     if (MODE == kCommReduceScatter) {
-      if (p.k.d_dtype == kBFloat16) reduce_tail<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et, s_ok);
-      else reduce_tail<__half>(p, gemm_cta, gemm_ctas, et, s_ok);
+      if (et == 0) {
+        // last one or two half tiles: wait for their stores, then bump the owners' counters
+        tma_store_wait<0>();
+        fence_proxy_async_all();
+        __threadfence_system();
+        if (halves >= 2) red_release_sys_add(pending[halves & 1], 1u);
+        if (halves >= 1) red_release_sys_add(pending[(halves - 1) & 1], 1u);
+        if (dbg) dbg[gemm_cta * 4 + 2] = gtimer();
+      }
+      if (p.k.d_dtype == kBFloat16) reduce_tail<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et);
+      else reduce_tail<__half>(p, gemm_cta, gemm_ctas, et);
+      if (dbg && et == 0) dbg[gemm_cta * 4 + 3] = gtimer();
     }
   }
 
@@ -455,7 +593,7 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   if (!ok) return cudaErrorInvalidValue;
   CommParams p = {};
   KernelParams& k = p.k;
-  k.d = g.d; k.bias = g.bias; k.aux = nullptr; k.sfa = g.sfa; k.sfb = g.sfb; k.alpha_dev = g.alpha_dev;
+  k.d = g.d; k.bias = g.bias; k.aux = g.aux; k.sfa = g.sfa; k.sfb = g.sfb; k.alpha_dev = g.alpha_dev;
   k.group_offsets = nullptr; k.status = g.status; k.alpha = g.alpha;
   k.M = g.M; k.N = g.N; k.K = g.K; k.ldd = g.ldd;
   k.d_dtype = g.d_dtype; k.bias_dtype = g.bias_dtype; k.epilogue = 0; k.accumulate = 0; k.a_mn = 0; k.b_mn = 0;
@@ -479,13 +617,13 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<KIND, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
+                                         CommSmem<KIND, MODE>::kBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
   // every CTA must be resident at once (copy CTAs and GEMM CTAs wait on one another; the
   // reduce tail waits on peers): one CTA per SM, never more CTAs than SMs
-  comm_gemm_kernel<KIND, MODE><<<sms, kNumThreads, C::kSmemBytes, stream>>>(ta, tb, p);
+  comm_gemm_kernel<KIND, MODE><<<sms, kNumThreads, CommSmem<KIND, MODE>::kBytes, stream>>>(ta, tb, p);
   return cudaGetLastError();
 }
 

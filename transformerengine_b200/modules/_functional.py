@@ -65,12 +65,64 @@ def gather_input(x, cfg: LinearConfig, quantizer, rowwise: bool, columnwise: boo
     return quantize_for_gemm(total, quantizer, rowwise, columnwise)
 
 
+def _fused_comm_ok(cfg: LinearConfig, rows_local: int, *tensors) -> bool:
+    """Fused collective GEMMs need the feature switched on for this TP group, CUDA operands and
+    whole 128-row blocks per rank."""
+    from ..parallel import comm_gemm
+
+    if not (cfg.sequence_parallel and cfg.tp_size > 1 and comm_gemm.enabled_for(cfg.tp_group)):
+        return False
+    if rows_local % 128 != 0:
+        return False
+    return all(getattr(as_operand(t).data, "is_cuda", False) for t in tensors)
+
+
+def _comm_kind(a_op, b_op):
+    """'mx', 'hp' or None when the operand pair has no fused collective kernel."""
+    if a_op.kind == "mxfp8" and b_op.kind == "mxfp8" and a_op.k % 128 == 0:
+        return "mx"
+    if a_op.kind == "hp" and b_op.kind == "hp" and a_op.data.dtype == b_op.data.dtype \
+            and a_op.data.dtype in (torch.bfloat16, torch.float16) and a_op.k % 8 == 0 \
+            and a_op.data.is_contiguous() and b_op.data.is_contiguous():
+        return "hp"
+    return None
+
+
+def fused_all_gather_gemm(x_local, w_op, bias, cfg: LinearConfig, quantizer, out_dtype, tag: str):
+    """Sequence-parallel all-gather of ``x_local`` fused into ``gather(x) @ w^T``.
+    Returns None when this operand pair is not covered (caller falls back to NCCL + GEMM)."""
+    from ..parallel import comm_gemm
+
+    xq = quantize_for_gemm(x_local, quantizer, True, False) if not _is_q(x_local) else x_local
+    a_op = as_operand(xq, "rowwise")
+    kind = _comm_kind(a_op, w_op)
+    if kind is None or out_dtype not in (torch.bfloat16, torch.float16):
+        return None
+    T = a_op.rows * cfg.tp_size
+    ctx = comm_gemm.get_all_gather_gemm(f"{cfg.name}.{tag}", cfg.tp_group, T, a_op.k, kind == "mx",
+                                        a_op.data.dtype)
+    return ctx(a_op, w_op, bias=bias, out_dtype=out_dtype)
+
+
+def fused_gemm_reduce_scatter(a_op, b_op, bias, cfg: LinearConfig, out_dtype, tag: str):
+    from ..parallel import comm_gemm
+
+    if _comm_kind(a_op, b_op) is None or out_dtype not in (torch.bfloat16, torch.float16):
+        return None
+    ctx = comm_gemm.get_gemm_reduce_scatter(f"{cfg.name}.{tag}", cfg.tp_group, a_op.rows, b_op.rows, out_dtype)
+    return ctx(a_op, b_op, bias=bias)
+
+
 def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False):
     """``x`` [T, in] (plain or quantized, already gathered), ``w`` [out, in].
     Returns (out2d after the row-parallel collective, pre-gelu aux or None)."""
     aux = None
     fuse_bias = bias is not None and not (cfg.parallel_mode == "row" and cfg.tp_size > 1)
     a, b = as_operand(x, "rowwise"), as_operand(w, "rowwise")
+    if cfg.parallel_mode == "row" and not gelu and _fused_comm_ok(cfg, a.rows // max(cfg.tp_size, 1), x, w):
+        out = fused_gemm_reduce_scatter(a, b, bias, cfg, out_dtype, "fprop")
+        if out is not None:
+            return out, None
     if gelu:
         aux = torch.empty(a.rows, b.rows, dtype=out_dtype, device=a.data.device)
         out = gemm_nt(a, b, out_dtype=out_dtype, bias=bias if fuse_bias else None, epilogue=ops.gemm.EPI_GELU, aux=aux)
@@ -86,10 +138,38 @@ def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False
     return out, aux
 
 
+def row_parallel_grad_output(dy_local, w, cfg: LinearConfig, quantizer, need_dgrad: bool, need_wgrad: bool, out_dtype):
+    """Backward of a row-parallel layer under sequence parallelism: grad_output arrives sharded on
+    rows.  Returns (gathered grad_output for the wgrad / dgrad GEMMs, dx or None).  With fused
+    collectives the all-gather runs inside the dgrad GEMM and only the columnwise copy (wgrad
+    operand) is gathered by NCCL."""
+    import copy as _copy
+
+    if need_dgrad and _fused_comm_ok(cfg, dy_local.shape[0], dy_local):
+        dq = quantize_for_gemm(dy_local, quantizer, True, need_wgrad)
+        w_op = as_operand(w, "columnwise")
+        if _comm_kind(as_operand(dq, "rowwise"), w_op) is not None:
+            dx = fused_all_gather_gemm(dq, w_op, None, cfg, None, out_dtype, "dgrad")
+            total = None
+            if need_wgrad:
+                if _is_q(dq):
+                    col = _copy.copy(dq)
+                    col.update_usage(rowwise_usage=False)
+                    total = D.gather_mxfp8_along_first_dim(col, cfg.tp_group)
+                else:
+                    total, _ = D.gather_along_first_dim(dq, cfg.tp_group)
+            return total, dx
+    return gather_input(dy_local, cfg, quantizer, need_dgrad, need_wgrad), None
+
+
 def linear_dgrad(dy, w, cfg: LinearConfig, out_dtype, *, async_comm: bool = False):
     """``dx = dy @ W``; column-parallel layers then reduce-scatter / all-reduce.
     Returns (dx2d, comm handle or None)."""
     a, b = as_operand(dy, "rowwise"), as_operand(w, "columnwise")
+    if cfg.parallel_mode == "column" and _fused_comm_ok(cfg, a.rows // max(cfg.tp_size, 1), dy):
+        dx = fused_gemm_reduce_scatter(a, b, None, cfg, out_dtype, "dgrad")
+        if dx is not None:
+            return dx, None
     dx = gemm_nt(a, b, out_dtype=out_dtype)
     h = None
     if cfg.parallel_mode == "column" and cfg.tp_size > 1:

@@ -105,11 +105,18 @@ class _LayerNormLinear(torch.autograd.Function):
                                            module.normalization == "LayerNorm",
                                            quantizer=in_q if not sp_gather else None,
                                            want_hp=return_ln_out or in_q is None or sp_gather)
+        out = None
+        ln_total = None
         if sp_gather:
-            ln_total = F.gather_input(ln_hp, cfg, in_q, True, need_wgrad)
+            if F._fused_comm_ok(cfg, ln_hp.shape[0], ln_hp):
+                out = F.fused_all_gather_gemm(ln_hp, F.as_operand(wq, "rowwise"), bias, cfg, in_q,
+                                              cfg.activation_dtype, "fprop")
+            if out is None:
+                ln_total = F.gather_input(ln_hp, cfg, in_q, True, need_wgrad)
         else:
             ln_total = ln_q if ln_q is not None else ln_hp
-        out, _ = F.linear_fprop(ln_total, wq, bias, cfg, cfg.activation_dtype)
+        if out is None:
+            out, _ = F.linear_fprop(ln_total, wq, bias, cfg, cfg.activation_dtype)
         if grad_on:
             keep = (ln_hp if sp_gather else ln_total) if need_wgrad else None
             if F._is_q(keep) and keep.get_usages()["columnwise"]:

@@ -43,10 +43,18 @@ class _LayerNormMLP(torch.autograd.Function):
         ln_hp, ln_q, mu, rs = ops.norm_fwd(x2d, ln_w, ln_b, module.eps, module.zero_centered_gamma, is_ln,
                                            quantizer=q_in1 if not sp else None,
                                            want_hp=return_ln_out or q_in1 is None or sp)
-        ln_total = F.gather_input(ln_hp, cfg1, q_in1, True, grad) if sp else (ln_q if ln_q is not None else ln_hp)
         act = module.activation
-        gelu_fused = False
-        fc1_out, _ = F.linear_fprop(ln_total, w1q, fc1_b, cfg1, adt)
+        fc1_out = None
+        ln_total = None
+        if sp:
+            if F._fused_comm_ok(cfg1, ln_hp.shape[0], ln_hp):
+                fc1_out = F.fused_all_gather_gemm(ln_hp, F.as_operand(w1q, "rowwise"), fc1_b, cfg1, q_in1, adt, "fprop")
+            if fc1_out is None:
+                ln_total = F.gather_input(ln_hp, cfg1, q_in1, True, grad)
+        else:
+            ln_total = ln_q if ln_q is not None else ln_hp
+        if fc1_out is None:
+            fc1_out, _ = F.linear_fprop(ln_total, w1q, fc1_b, cfg1, adt)
         if q_in2 is not None:
             q_in2.set_usage(rowwise=True, columnwise=grad)
             q_in2.internal = True
@@ -91,12 +99,14 @@ class _LayerNormMLP(torch.autograd.Function):
         q_go2 = module.get_quantizer(False, 2) if ctx.fp8 else None
         q_go1 = module.get_quantizer(False, 0) if ctx.fp8 else None
         db2 = F.bias_grad(dy2d, fc2_b.dtype) if fc2_b is not None else None
+        dact = None
         if ctx.sp:
-            dyq = F.gather_input(dy2d, cfg2, q_go2, True, True)
+            dyq, dact = F.row_parallel_grad_output(dy2d, w2, cfg2, q_go2, True, True, adt)
         else:
             dyq = F.quantize_for_gemm(dy2d, q_go2, True, True)
-        # fc2 dgrad (row-parallel: no collective on dgrad) and wgrad
-        dact, _ = F.linear_dgrad(dyq, w2, cfg2, adt)
+        # fc2 dgrad (row-parallel: no collective after dgrad) and wgrad
+        if dact is None:
+            dact, _ = F.linear_dgrad(dyq, w2, cfg2, adt)
         dw2 = F.linear_wgrad(dyq, act_in, fc2_w, cfg2) if fc2_w.requires_grad else None
         # activation backward fused with quantization (+ fc1 bias gradient)
         if q_go1 is not None:

@@ -26,14 +26,20 @@ class _Linear(torch.autograd.Function):
         need_wgrad = weight.requires_grad and grad_on
         if x2d.dtype != cfg.activation_dtype and not F._is_q(x2d):
             x2d = x2d.to(cfg.activation_dtype)
-        if cfg.parallel_mode == "column" and cfg.sequence_parallel and cfg.tp_size > 1:
-            x_local = x2d
-            xq = F.gather_input(x2d, cfg, in_q, True, need_wgrad)
-            save_x = x_local  # re-gathered in backward
+        out = None
+        sp_col = cfg.parallel_mode == "column" and cfg.sequence_parallel and cfg.tp_size > 1
+        if sp_col:
+            save_x = x2d  # local rows; gathered again in backward for wgrad
+            if F._fused_comm_ok(cfg, x2d.shape[0], x2d):
+                out = F.fused_all_gather_gemm(x2d, F.as_operand(weight_q, "rowwise"), bias, cfg, in_q,
+                                              cfg.activation_dtype, "fprop")
+            if out is None:
+                xq = F.gather_input(x2d, cfg, in_q, True, need_wgrad)
         else:
             xq = F.quantize_for_gemm(x2d, in_q, True, need_wgrad)
             save_x = xq
-        out, _ = F.linear_fprop(xq, weight_q, bias, cfg, cfg.activation_dtype)
+        if out is None:
+            out, _ = F.linear_fprop(xq, weight_q, bias, cfg, cfg.activation_dtype)
         if grad_on:
             if F._is_q(save_x) and need_wgrad:
                 save_x.update_usage(rowwise_usage=False) if save_x.get_usages()["columnwise"] else None
@@ -49,7 +55,7 @@ class _Linear(torch.autograd.Function):
             ctx.use_bias = bias is not None
             ctx.requires_dgrad = inp.requires_grad
             ctx.requires_wgrad = need_wgrad
-            ctx.gathered_in_fwd = save_x is not xq
+            ctx.gathered_in_fwd = sp_col
             ctx.reduce_bwd_amax = FP8GlobalStateManager.is_first_fp8_module() if fp8 else False
         out_lead = lead
         if cfg.parallel_mode == "row" and cfg.sequence_parallel and cfg.tp_size > 1:
@@ -76,15 +82,16 @@ class _Linear(torch.autograd.Function):
         go_q = module.get_quantizer(False, 0) if ctx.fp8 else None
         db = F.bias_grad(dy2d if not (cfg.parallel_mode == "row" and cfg.sequence_parallel and cfg.tp_size > 1)
                          else dy2d, bias.dtype) if ctx.use_bias else None
+        dx = dw = None
+        h = None
         if cfg.parallel_mode == "row" and cfg.sequence_parallel and cfg.tp_size > 1:
             if ctx.use_bias:
                 db = F.bias_grad(dy2d, bias.dtype)
-            dyq = F.gather_input(dy2d, cfg, go_q, ctx.requires_dgrad, ctx.requires_wgrad)
+            dyq, dx = F.row_parallel_grad_output(dy2d, w_use, cfg, go_q, ctx.requires_dgrad, ctx.requires_wgrad,
+                                                 cfg.activation_dtype)
         else:
             dyq = F.quantize_for_gemm(dy2d, go_q, ctx.requires_dgrad, ctx.requires_wgrad)
-        dx = dw = None
-        h = None
-        if ctx.requires_dgrad:
+        if ctx.requires_dgrad and dx is None:
             dx, h = F.linear_dgrad(dyq, w_use, cfg, cfg.activation_dtype, async_comm=True)
         if ctx.requires_wgrad:
             xw = keep_x

@@ -88,7 +88,8 @@ class AllGatherGemm:
     def __call__(self, x_local, w, *, bias=None, out_dtype=torch.bfloat16) -> torch.Tensor:
         """``x_local``: this rank's rows (plain 16-bit tensor or MXFP8 with a rowwise copy);
         ``w``: the local weight ``[N, K]`` of the same kind.  Returns ``[T, N]``."""
-        a_op, b_op = as_operand(x_local, "rowwise"), as_operand(w, "rowwise")
+        a_op = x_local if isinstance(x_local, Operand) else as_operand(x_local, "rowwise")
+        b_op = w if isinstance(w, Operand) else as_operand(w, "rowwise")
         rows = self.T // self.world
         assert a_op.rows == rows and a_op.k == self.K
         self.epoch += 1
@@ -123,7 +124,7 @@ class GemmReduceScatter:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert T % (128 * self.world) == 0 and N % 8 == 0
         self.epoch = 0
-        stage_bytes = T * N * 2
+        stage_bytes = T * round_up(N, 256) * 2  # one 64 KB record per 128 x 256 output tile
         mbl = T // 128 // self.world
         self.buf = SymmetricBuffer(2 * stage_bytes + 4 * self.world * mbl * 2 + 4096, group)
         self.stage_ptrs = []
@@ -137,9 +138,10 @@ class GemmReduceScatter:
             self.flag_ptrs.append(p)
         self.calls = [0, 0]
 
-    def __call__(self, x, w, *, bias=None) -> torch.Tensor:
+    def __call__(self, x, w, *, bias=None, timeline: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x`` [T, K/tp], ``w`` [N, K/tp] (16-bit or MXFP8 rowwise).  Returns this rank's ``[T/tp, N]``."""
-        a_op, b_op = as_operand(x, "rowwise"), as_operand(w, "rowwise")
+        a_op = x if isinstance(x, Operand) else as_operand(x, "rowwise")
+        b_op = w if isinstance(w, Operand) else as_operand(w, "rowwise")
         assert a_op.rows == self.T and b_op.rows == self.N
         self.epoch += 1
         slot = self.epoch & 1
@@ -147,7 +149,7 @@ class GemmReduceScatter:
         mx = a_op.kind == "mxfp8"
         out = torch.empty(self.T // self.world, self.N, dtype=self.dtype, device=a_op.data.device)
         _ext.get().comm_gemm(2, self.rank, self.world, self.calls[slot], 0, a_op.data, a_op.scale if mx else None,
-                             b_op.data, b_op.scale if mx else None, None, bias,
+                             b_op.data, b_op.scale if mx else None, timeline, bias,
                              a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,
                              [], [], [], 0, self.stage_ptrs[slot], self.flag_ptrs[slot], out, self.N,
                              _status(out.device))

@@ -1,0 +1,148 @@
+"""MoE router, permutation, GroupedLinear, and expert parallelism (gloo) on CPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import transformerengine_b200 as te
+from transformerengine_b200.common import recipe as R
+from transformerengine_b200.models import mixtral
+from transformerengine_b200.modules.grouped_linear import GroupedLinear
+from transformerengine_b200.moe import (fused_compute_score_for_moe_aux_loss, fused_moe_aux_loss,
+                                        fused_topk_with_score_function, moe_permute, moe_permute_with_probs,
+                                        moe_sort_chunks_by_index, moe_unpermute)
+
+
+@pytest.mark.parametrize("score", ["softmax", "sigmoid", "sqrtsoftplus"])
+@pytest.mark.parametrize("pre", [False, True])
+def test_router_topk(score, pre):
+    T, E, k = 32, 16, 4
+    logits = torch.randn(T, E)
+    bias = torch.randn(E) * 0.1 if score != "softmax" else None
+    probs, rmap = fused_topk_with_score_function(logits, k, pre, None, None, 2.0, score, bias)
+    assert rmap.sum(-1).eq(k).all() and ((probs != 0) == rmap).all()
+    if score == "softmax" and not pre:
+        ref = torch.softmax(logits.topk(k).values, -1) * 2.0
+        assert torch.allclose(probs.gather(1, logits.topk(k).indices), ref, atol=1e-6)
+    if score == "sigmoid":
+        sel = (torch.sigmoid(logits) + bias).topk(k).indices
+        assert torch.equal(rmap, torch.zeros(T, E, dtype=torch.bool).scatter_(1, sel, True))
+        assert torch.allclose(probs.sum(-1), torch.full((T,), 2.0), atol=1e-5)  # renormalised, then scaled
+
+
+def test_router_group_limited_and_bitmap():
+    logits = torch.randn(16, 16)
+    probs, rmap = fused_topk_with_score_function(logits, 4, True, 4, 2, None, "softmax", None)
+    groups_used = rmap.reshape(16, 4, 4).any(-1).sum(-1)
+    assert (groups_used <= 2).all()
+    _, bm = fused_topk_with_score_function(logits, 4, True, None, None, None, "softmax", None, "bitmap_u8")
+    assert bm.dtype == torch.uint8 and bm.shape == (16, 2)
+
+
+def test_aux_loss_formula():
+    T, E, k = 64, 8, 2
+    logits = torch.randn(T, E, requires_grad=True)
+    rmap, scores = fused_compute_score_for_moe_aux_loss(logits, k, "softmax")
+    tpe = rmap.sum(0)
+    loss = fused_moe_aux_loss(scores, tpe, T, E, topk=k, coeff=0.01)
+    ref = (scores.sum(0) * tpe).sum() * E * 0.01 / (k * T * T)
+    assert torch.allclose(loss, ref)
+    loss.backward()
+    assert logits.grad.abs().sum() > 0
+
+
+def test_permute_roundtrip_mask_and_index():
+    T, E, H, k = 48, 8, 16, 2
+    x = torch.randn(T, H, requires_grad=True)
+    logits = torch.randn(T, E)
+    probs, rmap = fused_topk_with_score_function(logits, k, False, None, None, None, "softmax", None)
+    out, rid = moe_permute(x, rmap, T * k)
+    # expert-major and stable
+    counts = rmap.sum(0)
+    off = 0
+    for e in range(E):
+        toks = rmap[:, e].nonzero().squeeze(1)
+        assert torch.equal(out[off:off + counts[e]], x[toks])
+        off += int(counts[e])
+    y = moe_unpermute(out, rid, merging_probs=probs)
+    assert torch.allclose(y, x * probs.sum(-1, keepdim=True), atol=1e-6)
+    y.sum().backward()
+    assert torch.allclose(x.grad, probs.sum(-1, keepdim=True).expand_as(x), atol=1e-6)
+    idx = logits.topk(k).indices.int()
+    out2, rid2 = moe_permute(x, idx, 0, map_type="index")
+    y2 = moe_unpermute(out2, rid2, map_type="index")
+    assert torch.allclose(y2, x * k, atol=1e-5)
+    chunks = moe_sort_chunks_by_index(torch.arange(10.)[:, None], torch.tensor([2, 3, 5]), torch.tensor([2, 0, 1]))
+    assert chunks.squeeze(1).tolist() == [5., 6., 7., 8., 9., 0., 1., 2., 3., 4.]
+
+
+def test_mixtral_tiny_trains():
+    torch.manual_seed(0)
+    cfg = mixtral.MixtralConfig.tiny(params_dtype=torch.float32)
+    m = mixtral.MixtralModel(cfg, device="cpu")
+    tok = torch.randint(0, cfg.vocab_size, (2, 32))
+    loss = m(tok, labels=tok)
+    loss.backward()
+    assert torch.isfinite(loss)
+    assert m.layers[0].moe.router.weight.grad.abs().sum() > 0
+    assert m.layers[0].moe.fc1.weight0.grad is not None
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
+        l2 = m(tok, labels=tok)
+    assert abs(l2.item() - loss.item()) < 0.1
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _ep_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        cfg = mixtral.MixtralConfig.tiny(params_dtype=torch.float32, num_layers=1)
+        torch.manual_seed(0)
+        full = mixtral.MoELayer(cfg, None, "cpu")
+        torch.manual_seed(0)
+        ep = mixtral.MoELayer(cfg, dist.group.WORLD, "cpu")
+        le = cfg.num_experts // world
+        with torch.no_grad():
+            ep.router.weight.copy_(full.router.weight)
+            for i in range(le):
+                getattr(ep.fc1, f"weight{i}").copy_(getattr(full.fc1, f"weight{rank * le + i}"))
+                getattr(ep.fc2, f"weight{i}").copy_(getattr(full.fc2, f"weight{rank * le + i}"))
+        torch.manual_seed(10 + rank)
+        x = torch.randn(24, cfg.hidden_size, requires_grad=True)
+        y, aux = ep(x)
+        (y.sum() + aux).backward()
+        xr = x.detach().clone().requires_grad_(True)
+        yr, _ = full(xr)
+        yr.sum().backward()
+        err = ((y - yr).norm() / yr.norm()).item()
+        gerr = ((x.grad - xr.grad).norm() / xr.grad.norm()).item()
+        q.put((rank, {} if err < 1e-5 and gerr < 2e-2 else {"out": err, "dx": gerr}))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, {"exception": traceback.format_exc()[-1500:]}))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_matches_local():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ep_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, bad in res:
+        assert not bad, f"rank {rank}: {bad}"

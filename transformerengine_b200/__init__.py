@@ -22,6 +22,11 @@ from .attention.dot_product_attention import DotProductAttention
 from .attention.multi_head_attention import MultiheadAttention
 from .attention.rope import RotaryPositionEmbedding, apply_rotary_pos_emb
 from .transformer import TransformerLayer
+from .modules.grouped_linear import GroupedLinear, Fp8Padding, Fp8Unpadding
+from .moe import (fused_topk_with_score_function, fused_compute_score_for_moe_aux_loss, fused_moe_aux_loss,
+                  moe_permute, moe_permute_with_probs, moe_permute_and_pad_with_probs, moe_unpermute,
+                  moe_sort_chunks_by_index, moe_sort_chunks_by_index_with_probs)
+from .parallel.expert_parallel import ep_dispatch, ep_combine
 from .parallel.distributed import checkpoint, CudaRNGStatesTracker
 from .optim import FusedAdam, FusedSGD
 from .parallel.comm_gemm import initialize_ub, destroy_ub

@@ -1,0 +1,250 @@
+"""``GroupedLinear``: ``num_gemms`` independent linear layers applied to consecutive row slabs
+of one input (MoE experts), and ``Fp8Padding`` / ``Fp8Unpadding`` that align the slabs for
+quantized GEMMs (reference: ``pytorch/module/grouped_linear.py:154-2137``,
+``fp8_padding.py``, ``fp8_unpadding.py``).
+
+Forward and dgrad of all groups run as ONE launch of the tcgen05 grouped GEMM (device-side
+slab offsets) when the slabs are 128-row aligned; otherwise, and for wgrad (contraction over
+the rows of a slab), one GEMM per group is issued.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Union
+
+import torch
+
+from .. import ops
+from ..ops.gemm import Operand, as_operand, gemm_nt
+from ..quantization import FP8GlobalStateManager, get_align_size_for_quantization
+from ..tensor.base import QuantizedTensorStorage
+from ..tensor.mxfp8 import MXFP8Quantizer
+from . import _functional as F
+from .base import TransformerEngineBaseModule, get_default_init_method
+
+
+def _offsets(m_splits: List[int], device) -> torch.Tensor:
+    offs = [0]
+    for m in m_splits:
+        offs.append(offs[-1] + int(m))
+    return torch.tensor(offs, dtype=torch.int32, device=device)
+
+
+def _can_group(m_splits, x_ops, quantized: bool) -> bool:
+    if not getattr(x_ops.data, "is_cuda", False):
+        return False
+    if quantized:
+        return all(m % 128 == 0 for m in m_splits)
+    return True
+
+
+class _GroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, inp, m_splits, module, adt, *weights_and_biases):  # type: ignore[override]
+        G = module.num_gemms
+        weights = list(weights_and_biases[:G])
+        biases = list(weights_and_biases[G:]) if module.use_bias else [None] * G
+        x2d = inp.reshape(-1, inp.shape[-1])
+        if x2d.dtype != adt:
+            x2d = x2d.to(adt)
+        fp8 = module.fp8
+        grad_on = any(ctx.needs_input_grad)
+        N, K = module.out_features, module.in_features
+        out = torch.empty(x2d.shape[0], N, dtype=adt, device=x2d.device)
+        offs = [0]
+        for m in m_splits:
+            offs.append(offs[-1] + int(m))
+        in_q = module.get_quantizer(True, 0)
+        quant_ok = fp8 and in_q is not None and all(m % 32 == 0 for m in m_splits) and K % 32 == 0
+        xq = None
+        wqs = []
+        if quant_ok:
+            in_q.set_usage(rowwise=True, columnwise=grad_on)
+            in_q.internal = True
+            aligned = all(m % 128 == 0 for m in m_splits) and isinstance(in_q, MXFP8Quantizer)
+            for g in range(G):
+                wqs.append(module.get_quantized_weight(weights[g], module.get_quantizer(True, 3 * g + 1),
+                                                       cache_name=f"weight{g}"))
+            if aligned and x2d.shape[0] > 0:
+                xq = in_q(x2d)  # one quantization for all slabs
+                a = as_operand(xq, "rowwise")
+                b_data = torch.cat([as_operand(w, "rowwise").data for w in wqs], 0)
+                b_scale = torch.cat([as_operand(w, "rowwise").scale for w in wqs], 0)
+                b = Operand("mxfp8", b_data, b_scale, in_q.dtype, rows=G * N, k=K)
+                if _can_group(m_splits, a, True):
+                    gemm_nt(a, b, out=out, group_offsets=_offsets(m_splits, x2d.device), num_groups=G)
+                else:
+                    xq = None
+            if xq is None:
+                xs = []
+                for g in range(G):
+                    if m_splits[g] == 0:
+                        xs.append(None)
+                        continue
+                    xg = in_q(x2d[offs[g]:offs[g + 1]])
+                    xs.append(xg)
+                    gemm_nt(as_operand(xg, "rowwise"), as_operand(wqs[g], "rowwise"), out=out[offs[g]:offs[g + 1]])
+                xq = xs
+        else:
+            wcat = None
+            if getattr(x2d, "is_cuda", False) and x2d.shape[0] > 0 and adt in (torch.bfloat16, torch.float16):
+                wcat = torch.cat([w.to(adt) for w in weights], 0)
+                gemm_nt(x2d, wcat, out=out, group_offsets=_offsets(m_splits, x2d.device), num_groups=G)
+            else:
+                for g in range(G):
+                    if m_splits[g]:
+                        gemm_nt(x2d[offs[g]:offs[g + 1]], weights[g].to(adt), out=out[offs[g]:offs[g + 1]])
+            xq = x2d
+        for g in range(G):
+            if biases[g] is not None and m_splits[g]:
+                out[offs[g]:offs[g + 1]] += biases[g].to(adt)
+        if grad_on:
+            ctx.module, ctx.m_splits, ctx.offs, ctx.adt, ctx.fp8q = module, list(m_splits), offs, adt, quant_ok
+            ctx.xq, ctx.wqs = xq, wqs
+            ctx.save_for_backward(*weights)
+            ctx.inp_shape = inp.shape
+            ctx.reduce_bwd_amax = FP8GlobalStateManager.is_first_fp8_module() if fp8 else False
+        return out.reshape(*inp.shape[:-1], N)
+
+    @staticmethod
+    def backward(ctx, grad_out):  # type: ignore[override]
+        module, m_splits, offs, adt = ctx.module, ctx.m_splits, ctx.offs, ctx.adt
+        weights = list(ctx.saved_tensors)
+        G, N, K = module.num_gemms, module.out_features, module.in_features
+        dy = grad_out.reshape(-1, N).to(adt).contiguous()
+        dx = torch.empty(dy.shape[0], K, dtype=adt, device=dy.device)
+        dws = [None] * G
+        dbs = [None] * G
+        for g in range(G):
+            sl = slice(offs[g], offs[g + 1])
+            if module.use_bias:
+                dbs[g] = dy[sl].float().sum(0).to(weights[g].dtype)
+            if m_splits[g] == 0:
+                dws[g] = torch.zeros_like(weights[g])
+                continue
+            if ctx.fp8q:
+                gq = module.get_quantizer(False, 2 * g)
+                gq.set_usage(rowwise=True, columnwise=True)
+                gq.internal = True
+                dyq = gq(dy[sl])
+                xg = ctx.xq[g] if isinstance(ctx.xq, list) else None
+                gemm_nt(as_operand(dyq, "rowwise"), as_operand(ctx.wqs[g], "columnwise"), out=dx[sl])
+                if xg is None:
+                    # the input was quantized as one tensor: re-quantize this slab's rows columnwise
+                    in_q = module.get_quantizer(True, 0)
+                    in_q.set_usage(rowwise=False, columnwise=True)
+                    xg = in_q(ctx.xq.dequantize(dtype=adt)[sl]) if isinstance(ctx.xq, QuantizedTensorStorage) \
+                        else in_q(ctx.xq[sl])
+                dws[g] = gemm_nt(as_operand(dyq, "columnwise"), as_operand(xg, "columnwise"),
+                                 out_dtype=weights[g].dtype if weights[g].dtype != torch.float32 else torch.float32)
+            else:
+                w = weights[g].to(adt)
+                gemm_nt(as_operand(dy[sl], "rowwise"), as_operand(w, "columnwise"), out=dx[sl])
+                dws[g] = gemm_nt(as_operand(dy[sl], "columnwise"), as_operand(ctx.xq[sl], "columnwise"),
+                                 out_dtype=weights[g].dtype)
+            if module.fuse_wgrad_accumulation and hasattr(weights[g], "main_grad"):
+                weights[g].main_grad.add_(dws[g].float())
+                dws[g] = None
+        if ctx.fp8q and ctx.reduce_bwd_amax:
+            FP8GlobalStateManager.reduce_and_update_fp8_tensors(forward=False)
+        res = [dx.reshape(ctx.inp_shape), None, None, None] + dws
+        if module.use_bias:
+            res += dbs
+        return tuple(res)
+
+
+class GroupedLinear(TransformerEngineBaseModule):
+    def __init__(self, num_gemms: int, in_features: int, out_features: int, sequence_parallel: bool = False,
+                 fuse_wgrad_accumulation: bool = False, tp_group=None, tp_size: int = 1,
+                 get_rng_state_tracker: Optional[Callable] = None, rng_tracker_name: Optional[str] = None,
+                 init_method: Optional[Callable] = None, bias: bool = True, return_bias: bool = False,
+                 params_dtype: Optional[torch.dtype] = None, parallel_mode: Optional[str] = None,
+                 device: Union[torch.device, str] = None, ub_overlap_rs: bool = False, ub_overlap_ag: bool = False,
+                 ub_name: Optional[str] = None, delay_wgrad_compute: bool = False,
+                 save_original_input: bool = False, single_grouped_weight: bool = False,
+                 single_grouped_bias: bool = False, name: Optional[str] = None) -> None:
+        super().__init__()
+        params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
+        if device is None:
+            device = "cuda" if torch.cuda.is_available() else "cpu"
+        self.num_gemms = num_gemms
+        self.use_bias, self.return_bias = bias, return_bias
+        self.apply_bias = bias and not return_bias
+        self.fuse_wgrad_accumulation = fuse_wgrad_accumulation
+        self.name = name
+        if tp_group is None:
+            self.tp_size = tp_size
+        else:
+            self.set_tensor_parallel_group(tp_group)
+        self.parallel_mode = parallel_mode
+        assert parallel_mode in (None, "column", "row")
+        if parallel_mode == "column":
+            out_features //= self.tp_size
+        elif parallel_mode == "row":
+            in_features //= self.tp_size
+        self.in_features, self.out_features = in_features, out_features
+        init_method = init_method or get_default_init_method()
+        # all expert weights live in one [G * out, in] buffer; weight{i} are views of it
+        self._stacked = torch.empty(num_gemms * out_features, in_features, device=device, dtype=params_dtype)
+        for i in range(num_gemms):
+            w = self._stacked[i * out_features:(i + 1) * out_features]
+            if str(device) != "meta":
+                init_method(w)
+            self.register_parameter(f"weight{i}", torch.nn.Parameter(w))
+            if bias:
+                self.register_parameter(f"bias{i}", torch.nn.Parameter(
+                    torch.zeros(out_features, device=device, dtype=params_dtype)))
+
+    def forward(self, inp: torch.Tensor, m_splits: List[int], is_first_microbatch: Optional[bool] = None):
+        assert len(m_splits) == self.num_gemms, "one row count per GEMM"
+        self.prepare_forward(num_gemms=self.num_gemms)
+        adt = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else inp.dtype
+        ws = [getattr(self, f"weight{i}") for i in range(self.num_gemms)]
+        bs = [getattr(self, f"bias{i}") for i in range(self.num_gemms)] if self.use_bias else []
+        if not self.apply_bias and self.use_bias:
+            out = _GroupedLinear.apply(inp, m_splits, _NoBias(self), adt, *ws)
+            return out, [b.to(adt) for b in bs]
+        return _GroupedLinear.apply(inp, m_splits, self, adt, *ws, *bs)
+
+
+class _NoBias:
+    """View of a GroupedLinear that skips the bias add (``return_bias=True``)."""
+
+    def __init__(self, m):
+        self._m = m
+        self.use_bias = False
+
+    def __getattr__(self, k):
+        return getattr(self._m, k)
+
+
+class Fp8Padding(torch.nn.Module):
+    """Pad every row slab with zero rows up to a multiple of ``align_size``."""
+
+    def __init__(self, num_gemms: int, align_size: Optional[int] = None) -> None:
+        super().__init__()
+        self.num_gemms, self.align_size = num_gemms, align_size
+
+    def forward(self, inp: torch.Tensor, m_splits: List[int]):
+        align = self.align_size or get_align_size_for_quantization(FP8GlobalStateManager.get_fp8_recipe())
+        padded = [(m + align - 1) // align * align for m in m_splits]
+        if padded == list(m_splits):
+            return inp, list(m_splits)
+        chunks = torch.split(inp.reshape(-1, inp.shape[-1]), list(m_splits), dim=0)
+        out = [torch.nn.functional.pad(c, (0, 0, 0, p - m)) for c, m, p in zip(chunks, m_splits, padded)]
+        return torch.cat(out, dim=0), padded
+
+
+class Fp8Unpadding(torch.nn.Module):
+    """Inverse of :class:`Fp8Padding`."""
+
+    def __init__(self, num_gemms: int, align_size: Optional[int] = None) -> None:
+        super().__init__()
+        self.num_gemms, self.align_size = num_gemms, align_size
+
+    def forward(self, inp: torch.Tensor, m_splits: List[int]):
+        align = self.align_size or get_align_size_for_quantization(FP8GlobalStateManager.get_fp8_recipe())
+        padded = [(m + align - 1) // align * align for m in m_splits]
+        if padded == list(m_splits):
+            return inp
+        chunks = torch.split(inp.reshape(-1, inp.shape[-1]), padded, dim=0)
+        return torch.cat([c[:m] for c, m in zip(chunks, m_splits)], dim=0)

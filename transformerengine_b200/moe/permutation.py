@@ -1,0 +1,118 @@
+"""Token permutation for MoE: group the (token, expert) pairs expert-major, and the inverse
+with probability-weighted merging (reference API: ``pytorch/permutation.py:876-1340``).
+
+The map returned by ``moe_permute`` is ``dest_row`` (int32): ``[T, E]`` for a mask routing map,
+``[T, topk]`` for an index map; entry = row of the permuted buffer, or -1.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+
+def _dest_rows_from_mask(routing_map: torch.Tensor, align: int = 1):
+    """Expert-major stable ordering.  Returns (dest_row [T,E] int64 (-1 = not routed),
+    tokens_per_expert [E], padded offsets [E+1])."""
+    m = routing_map.bool()
+    T, E = m.shape
+    counts = m.sum(0)
+    padded = (counts + align - 1) // align * align if align > 1 else counts
+    offs = torch.zeros(E + 1, dtype=torch.int64, device=m.device)
+    offs[1:] = padded.cumsum(0)
+    within = m.long().cumsum(0) - 1  # rank of the token inside its expert
+    dest = torch.where(m, within + offs[:-1][None, :], torch.full_like(within, -1))
+    return dest, counts, offs
+
+
+def moe_permute(inp: torch.Tensor, routing_map: torch.Tensor, num_out_tokens: int = 0, max_token_num: int = -1,
+                map_type: str = "mask") -> Tuple[torch.Tensor, torch.Tensor]:
+    out, _, row_id_map = _permute(inp, routing_map, None, num_out_tokens, map_type, 1)
+    return out, row_id_map
+
+
+def moe_permute_with_probs(inp: torch.Tensor, probs: torch.Tensor, routing_map: torch.Tensor,
+                           num_out_tokens: int = 0) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Also permutes ``probs`` ([T, E]) into a vector aligned with the permuted rows."""
+    out, pp, row_id_map = _permute(inp, routing_map, probs, num_out_tokens, "mask", 1)
+    return out, pp, row_id_map
+
+
+def moe_permute_and_pad_with_probs(inp: torch.Tensor, probs: Optional[torch.Tensor], routing_map: torch.Tensor,
+                                   tokens_per_expert: torch.Tensor, align_size: int):
+    """Permute and pad every expert slab to a multiple of ``align_size`` rows (zero rows).
+    Returns (output, permuted_probs, row_id_map, pad_offsets, padded tokens_per_expert)."""
+    out, pp, row_id_map = _permute(inp, routing_map, probs, 0, "mask", align_size)
+    counts = routing_map.bool().sum(0)
+    padded = (counts + align_size - 1) // align_size * align_size
+    pad_offsets = torch.zeros_like(padded)
+    pad_offsets[1:] = (padded - counts).cumsum(0)[:-1]
+    return out, pp, row_id_map, pad_offsets, padded
+
+
+def _permute(inp, routing_map, probs, num_out_tokens, map_type, align):
+    T, H = inp.shape
+    if map_type == "index":
+        idx = routing_map.long()
+        topk = idx.shape[1]
+        E = int(idx.max().item()) + 1 if idx.numel() else 1
+        flat_e = idx.reshape(-1)
+        order = torch.sort(flat_e, stable=True).indices  # expert-major, token order kept
+        dest_flat = torch.empty_like(order)
+        dest_flat[order] = torch.arange(order.numel(), device=inp.device)
+        dest = dest_flat.reshape(T, topk)
+        n_out = T * topk
+        if num_out_tokens and num_out_tokens < n_out:  # capacity drop: rows beyond the budget vanish
+            dest = torch.where(dest < num_out_tokens, dest, torch.full_like(dest, -1))
+            n_out = num_out_tokens
+    else:
+        dest, counts, offs = _dest_rows_from_mask(routing_map, align)
+        n_out = int(offs[-1].item()) if align > 1 or not num_out_tokens else num_out_tokens
+        if align == 1 and num_out_tokens:
+            dest = torch.where(dest < num_out_tokens, dest, torch.full_like(dest, -1))
+    valid = dest >= 0
+    tok = torch.arange(T, device=inp.device)[:, None].expand_as(dest)[valid]
+    rows = dest[valid]
+    from ..tensor.base import QuantizedTensorStorage
+
+    src = inp.dequantize() if isinstance(inp, QuantizedTensorStorage) else inp
+    out = torch.zeros(n_out, H, dtype=src.dtype, device=src.device).index_put((rows,), src[tok])
+    pp = None
+    if probs is not None:
+        pp = torch.zeros(n_out, dtype=probs.dtype, device=probs.device).index_put((rows,), probs[valid])
+    return out, pp, dest.to(torch.int32)
+
+
+def moe_unpermute(inp: torch.Tensor, row_id_map: torch.Tensor, merging_probs: Optional[torch.Tensor] = None,
+                  restore_shape: Optional[torch.Size] = None, map_type: str = "mask",
+                  probs: Optional[torch.Tensor] = None, pad_offsets: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[t] = sum_slots w[t, slot] * inp[dest_row[t, slot]]`` (plain sum without weights)."""
+    if merging_probs is None:
+        merging_probs = probs
+    dest = row_id_map.long()
+    T = dest.shape[0]
+    H = inp.shape[-1]
+    valid = dest >= 0
+    tok = torch.arange(T, device=inp.device)[:, None].expand_as(dest)[valid]
+    rows = dest[valid]
+    vals = inp[rows]
+    if merging_probs is not None:
+        vals = vals.float() * merging_probs.float()[valid][:, None]
+    out = torch.zeros(T, H, dtype=vals.dtype, device=inp.device).index_add(0, tok, vals)
+    out = out.to(inp.dtype)
+    if restore_shape is not None:
+        out = out.reshape(restore_shape)
+    return out
+
+
+def moe_sort_chunks_by_index(inp: torch.Tensor, split_sizes: torch.Tensor, sorted_index: torch.Tensor) -> torch.Tensor:
+    """Split ``inp`` into consecutive chunks of ``split_sizes`` rows and concatenate them in the
+    order given by ``sorted_index`` (expert-parallel token exchange)."""
+    chunks = torch.split(inp, [int(s) for s in split_sizes.tolist()], dim=0)
+    return torch.cat([chunks[int(i)] for i in sorted_index.tolist()], dim=0)
+
+
+def moe_sort_chunks_by_index_with_probs(inp, probs, split_sizes, sorted_index):
+    out = moe_sort_chunks_by_index(inp, split_sizes, sorted_index)
+    pr = moe_sort_chunks_by_index(probs.reshape(-1, 1), split_sizes, sorted_index).reshape(-1)
+    return out, pr

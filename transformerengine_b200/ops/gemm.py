@@ -280,7 +280,9 @@ def general_gemm(
     epi, aux = EPI_NONE, None
     if grad and bias is not None:
         # bgrad: column sums of the grad-output operand
-        src = B.dequantize() if hasattr(B, "dequantize") else B
+        from ..tensor.base import QuantizedTensorStorage as _QS
+
+        src = B.dequantize() if isinstance(B, _QS) else B
         bias_grad = src.reshape(-1, src.shape[-1]).float().sum(0).to(bias.dtype)
         bias = None
     M, N = a_op.rows, b_op.rows

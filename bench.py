@@ -246,13 +246,15 @@ def run_reference(args):
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     try:
         if not os.path.isdir(os.path.join(ref_dir, "transformer_engine")):
-            raise ImportError("baseline/_ref holds no transformer_engine install (offline build did not finish)")
+            raise ImportError("baseline/_ref holds no transformer_engine install: the offline build of the unmodified "
+                              "reference stops in common/fused_attn/*.cu, which need a newer cudnn-frontend than "
+                              "the 1.18 headers of this image (no member set_ragged_offset_multiplier)")
         sys.path.insert(0, ref_dir)
         import torch
         import transformer_engine.pytorch as rte
         from transformer_engine.common import recipe as rrecipe
     except Exception as e:  # noqa: BLE001
-        print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:200]}"}), flush=True)
+        print(json.dumps({"impl": "reference", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}), flush=True)
         return
     import torch.distributed as dist
 

@@ -1,0 +1,87 @@
+"""Context-parallel attention over gloo ranks versus full-sequence attention on one rank
+(test model: reference ``tests/pytorch/attention/test_attention_with_cp.py``)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, comm, causal, result_q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from transformerengine_b200.ops.attention import attention_ref
+        from transformerengine_b200.parallel.context_parallel import (attn_forward_func_with_cp,
+                                                                      get_batch_on_this_cp_rank)
+
+        torch.manual_seed(0)
+        b, hq, hk, s, d = 2, 4, 2, 32, 16
+        q = torch.randn(b, hq, s, d, dtype=torch.float64)
+        k = torch.randn(b, hk, s, d, dtype=torch.float64)
+        v = torch.randn(b, hk, s, d, dtype=torch.float64)
+        do = torch.randn(b, hq, s, d, dtype=torch.float64)
+        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+        ref = attention_ref(qf, kf, vf, causal=causal)
+        ref.backward(do)
+
+        def shard(t):
+            if causal:
+                return get_batch_on_this_cp_rank(t, world, rank, seq_dim=2).contiguous()
+            return t.chunk(world, dim=2)[rank].contiguous()
+
+        ql, kl, vl = (shard(t).clone().requires_grad_() for t in (q, k, v))
+        out = attn_forward_func_with_cp(ql, kl, vl, cp_group=dist.group.WORLD, cp_comm_type=comm, causal=causal)
+        out.backward(shard(do))
+        errs = [
+            (out - shard(ref.detach())).abs().max().item(),
+            (ql.grad - shard(qf.grad)).abs().max().item(),
+            (kl.grad - shard(kf.grad)).abs().max().item(),
+            (vl.grad - shard(vf.grad)).abs().max().item(),
+        ]
+        result_q.put((rank, max(errs), None))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("comm", ["p2p", "all_gather", "a2a"])
+@pytest.mark.parametrize("causal", [True, False])
+def test_cp_matches_single_rank(comm, causal):
+    world = 2
+    ctx = mp.get_context("spawn")
+    result_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, comm, causal, result_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [result_q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, err, tb in results:
+        assert tb is None, tb
+        assert err < 2e-5, (rank, err)
+
+
+def test_dual_chunk_layout():
+    from transformerengine_b200.parallel.context_parallel import (dual_chunk_positions, get_batch_on_this_cp_rank,
+                                                                  pad_thd_sequences_for_cp)
+
+    x = torch.arange(16)[None, :]
+    got = get_batch_on_this_cp_rank(x, 4, 1, seq_dim=1)
+    assert got.tolist() == [[2, 3, 12, 13]]
+    assert dual_chunk_positions(4, 4, 1).tolist() == [2, 3, 12, 13]
+    cu = torch.tensor([0, 5, 13])
+    assert pad_thd_sequences_for_cp(cu, 2).tolist() == [0, 8, 16]

@@ -1,0 +1,392 @@
+// GEMM on CTA pairs (tcgen05 cta_group::2): D[M,N] = alpha * A[M,K] * B[N,K]^T with a 256x256
+// tile per pair of SMs.  Each CTA of a pair loads its own 128 rows of A and only HALF of the
+// B tile (128 rows); the tensor cores of both SMs read both halves, so bytes fetched from L2
+// per flop drop by a third against one 128x256 tile per CTA, which is what limits the
+// single-CTA kernel (its TMA feed is latency bound with all shared memory in use).
+//
+//   CTA rank 0 (leader): TMA producer, MMA issuer for the pair, epilogue of rows 0..127
+//   CTA rank 1 (partner): TMA producer (signals the leader's barriers), epilogue of rows 128..255
+//
+// "Stage full" barriers live in the leader and count the bytes of both CTAs; "stage empty" and
+// "accumulator full" are committed to the same-offset barrier of both CTAs; "accumulator empty"
+// lives in the leader and is arrived on by the epilogue warps of both CTAs.  All loads fill
+// only the issuing CTA's shared memory.  Every wait is bounded.
+#include <cstdlib>
+#include <teb200/api.h>
+#include <teb200/gemm_common.cuh>
+#include <teb200/ptx.cuh>
+
+namespace teb200 {
+namespace {
+
+using namespace gemm_detail;
+
+constexpr int PM = 256;   // rows per pair tile
+constexpr int PN = 256;   // columns per pair tile
+
+template <int KIND>
+struct PairCfg {
+  static constexpr int kABytes = 128 * 128;
+  static constexpr int kBBytes = (PN / 2) * 128;
+  static constexpr int kSfaBytes = KIND == kKindMxf8 ? 512 : 0;
+  static constexpr int kSfbBytes = KIND == kKindMxf8 ? 512 * (PN / 128) : 0;
+  static constexpr int kStageBytes = ((kABytes + kBBytes + kSfaBytes + kSfbBytes + 1023) / 1024) * 1024;
+  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;
+  static constexpr int kSfaCols = KIND == kKindMxf8 ? 4 : 0;
+  static constexpr int kSfbCols = KIND == kKindMxf8 ? 4 * (PN / 128) : 0;
+  static constexpr int kAccStages = (2 * PN + kSfaCols + kSfbCols <= 512) ? 2 : 1;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+  static constexpr int kBlockK = KIND == kKindF16 ? 64 : 128;
+  // bytes that land per stage over BOTH CTAs (every CTA loads the whole B scale block)
+  static constexpr uint32_t kTxBytes = 2u * (kABytes + kBBytes + kSfaBytes + kSfbBytes);
+};
+
+struct PairParams {
+  KernelParams k;
+  int num_m, num_n;  // pair tiles
+};
+
+__device__ __forceinline__ bool pair_tile(const PairParams& p, int t, int& mb, int& nb) {
+  if (t >= p.num_m * p.num_n) return false;
+  const int per_group = kGroupM * p.num_n;
+  const int g = t / per_group;
+  const int first = g * kGroupM;
+  const int gsize = min(p.num_m - first, kGroupM);
+  const int r = t - g * per_group;
+  mb = first + r % gsize;
+  nb = r / gsize;
+  return true;
+}
+
+template <int KIND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                 const PairParams p) {
+  using C = PairCfg<KIND>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint64_t* full_bar = bars;                       // used in the leader only
+  uint64_t* empty_bar = bars + C::kStages;         // one copy per CTA
+  uint64_t* tfull_bar = bars + 2 * C::kStages;     // one copy per CTA
+  uint64_t* tempty_bar = tfull_bar + C::kAccStages;  // used in the leader only
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAccStages);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_k_blocks = (p.k.K + C::kBlockK - 1) / C::kBlockK;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_a);
+    prefetch_tensormap(&tmap_b);
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(&full_bar[i], 1);
+      mbar_init(&empty_bar[i], 1);
+    }
+    for (int i = 0; i < C::kAccStages; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 8);  // four epilogue warps in each of the two CTAs
+    }
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs exist before any remote signal
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_sfa = tmem_base + C::kAccStages * PN;
+  const uint32_t tmem_sfb = tmem_sfa + C::kSfaCols;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int mb, nb;
+      for (int t = pair; ok && pair_tile(p, t, mb, nb); t += num_pairs) {
+        const int m0 = mb * PM + static_cast<int>(rank) * 128;       // this CTA's rows of A
+        const int nrow0 = nb * PN + static_cast<int>(rank) * (PN / 2);  // this CTA's half of B
+        for (int kb = 0; kb < num_k_blocks; ++kb) {
+          if (!mbar_wait_cluster(&empty_bar[stage], phase ^ 1)) {
+            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutProducer);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::kStageBytes;
+          uint8_t* sb = sa + C::kABytes;
+          const uint32_t fb = map_to_cta(smem_u32(&full_bar[stage]), 0);  // the leader's barrier
+          if (leader) mbar_expect_tx(&full_bar[stage], C::kTxBytes);
+          const int kc = KIND == kKindF16 ? kb * C::kBlockK : kb * 128;
+          tma_load_2d_pair(sa, &tmap_a, fb, kc, m0);
+          tma_load_2d_pair(sb, &tmap_b, fb, kc, nrow0);
+          if constexpr (KIND == kKindMxf8) {
+            uint8_t* ssfa = sb + C::kBBytes;
+            uint8_t* ssfb = ssfa + C::kSfaBytes;
+            // scale buffers are addressed as [tile][128 words]: tile = row_tile * k_tiles + k
+            tma_load_2d_pair(ssfa, &tmap_sfa, fb, 0, (m0 / 128) * p.k.sf_k_tiles + kb);
+#pragma unroll
+            for (int j = 0; j < PN / 128; ++j)
+              tma_load_2d_pair(ssfb + j * 512, &tmap_sfb, fb, 0, (nb * (PN / 128) + j) * p.k.sf_k_tiles + kb);
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader only)
+    if (leader && lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      int mb, nb;
+      for (int t = pair; ok && pair_tile(p, t, mb, nb); t += num_pairs) {
+        if (!mbar_wait_cluster(&tempty_bar[acc], acc_phase ^ 1)) {
+          if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * PN;
+        for (int kb = 0; kb < num_k_blocks; ++kb) {
+          if (!mbar_wait_cluster(&full_bar[stage], phase)) {
+            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
+          const uint32_t sb = sa + C::kABytes;
+          const uint64_t adesc = umma_desc_k_sw128(sa);
+          const uint64_t bdesc = umma_desc_k_sw128(sb);
+          if constexpr (KIND == kKindF16) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              umma_f16_pair(tmem_d, adesc + k * 2, bdesc + k * 2, p.k.idesc, (kb | k) != 0);
+          } else {
+            const uint32_t ssfa = sb + C::kBBytes;
+            const uint32_t ssfb = ssfa + C::kSfaBytes;
+            utccp_sf_pair(tmem_sfa, umma_desc_sf(ssfa));
+#pragma unroll
+            for (int j = 0; j < PN / 128; ++j) utccp_sf_pair(tmem_sfb + j * 4, umma_desc_sf(ssfb + j * 512));
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t idesc = p.k.idesc | (uint32_t(k) << 29) | (uint32_t(k) << 4);
+              umma_mxf8_pair(tmem_d, adesc + k * 2, bdesc + k * 2, idesc, (kb | k) != 0, tmem_sfa, tmem_sfb);
+            }
+          }
+          // the stage may be refilled in both CTAs once these MMAs have read it
+          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
+          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 0));
+        tc_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+        if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
+    const bool bf = p.k.d_dtype == kBFloat16;
+    int mb, nb;
+    for (int t = pair; pair_tile(p, t, mb, nb); t += num_pairs) {
+      if (!mbar_wait_cluster(&tfull_bar[acc], acc_phase)) {
+        if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int row = mb * PM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const int n0 = nb * PN;
+      const bool row_ok = row < p.k.M;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * PN;
+      {
+#pragma unroll 1
+        for (int c0 = 0; c0 < PN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c0, r);
+          tmem_ld_wait();
+          if (c0 + 32 >= PN) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+          }
+          const int col0 = n0 + c0;
+          if (!row_ok || col0 >= p.k.N) continue;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
+          const int ncols = min(32, p.k.N - col0);
+          if (p.k.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (i < ncols) {
+                float b;
+                if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
+                else if (p.k.bias_dtype == kBFloat16)
+                  b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
+                else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
+                v[i] += b;
+              }
+            }
+          }
+          const size_t off = static_cast<size_t>(row) * p.k.ldd + col0;
+          if (p.k.d_dtype == kFloat32) {
+            float* dp = reinterpret_cast<float*>(p.k.d) + off;
+            if (ncols == 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (p.k.accumulate) {
+                  const float4 old = *reinterpret_cast<const float4*>(dp + i);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(dp + i) = o;
+              }
+            } else {
+              for (int i = 0; i < ncols; ++i) dp[i] = v[i] + (p.k.accumulate ? dp[i] : 0.f);
+            }
+          } else {
+            uint16_t* dp = reinterpret_cast<uint16_t*>(p.k.d) + off;
+            if (ncols == 32 && !p.k.accumulate && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+#pragma unroll
+              for (int i = 0; i < 32; i += 8) {
+                uint4 o;
+                if (bf) {
+                  o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                                 pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+                } else {
+                  o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
+                                 pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
+                }
+                *reinterpret_cast<uint4*>(dp + i) = o;
+              }
+            } else {
+              for (int i = 0; i < ncols; ++i) {
+                float x = v[i];
+                if (bf) {
+                  __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(dp) + i;
+                  if (p.k.accumulate) x += __bfloat162float(*q);
+                  *q = __float2bfloat16(x);
+                } else {
+                  __half* q = reinterpret_cast<__half*>(dp) + i;
+                  if (p.k.accumulate) x += __half2float(*q);
+                  *q = __float2half(x);
+                }
+              }
+            }
+          }
+        }
+      }
+      if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees TMEM or exits while its partner may still use it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <int KIND>
+cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
+  using C = PairCfg<KIND>;
+  CUtensorMap ta, tb, tsa, tsb;
+  bool ok;
+  const int k_tiles = KIND == kKindMxf8 ? ((a.K + 31) / 32 + 3) / 4 : 0;
+  if (KIND == kKindF16) {
+    ok = make_tensor_map_2d(&ta, a.a, a.a_dtype, a.M, a.K, a.lda, 128, 64, true) &&
+         make_tensor_map_2d(&tb, a.b, a.b_dtype, a.N, a.K, a.ldb, PN / 2, 64, true);
+    tsa = ta;
+    tsb = tb;
+  } else {
+    ok = make_tensor_map_2d(&ta, a.a, kByte, a.M, a.K, a.lda, 128, 128, true) &&
+         make_tensor_map_2d(&tb, a.b, kByte, a.N, a.K, a.ldb, PN / 2, 128, true);
+    // scale buffers as [number of 512-byte tiles][128 x 4-byte words]
+    const uint64_t ta_tiles = static_cast<uint64_t>((a.M + 127) / 128) * k_tiles;
+    const uint64_t tb_tiles = static_cast<uint64_t>((a.N + 127) / 128) * k_tiles;
+    ok = ok && make_tensor_map_2d(&tsa, a.sfa, kFloat32, ta_tiles, 128, 128, 1, 128, false) &&
+         make_tensor_map_2d(&tsb, a.sfb, kFloat32, tb_tiles, 128, 128, 1, 128, false);
+  }
+  if (!ok) return cudaErrorInvalidValue;
+  PairParams p = {};
+  KernelParams& k = p.k;
+  k.d = a.d; k.bias = a.bias; k.aux = nullptr; k.sfa = a.sfa; k.sfb = a.sfb; k.alpha_dev = a.alpha_dev;
+  k.group_offsets = nullptr; k.status = a.status; k.alpha = a.alpha;
+  k.M = a.M; k.N = a.N; k.K = a.K; k.ldd = a.ldd;
+  k.d_dtype = a.d_dtype; k.bias_dtype = a.bias_dtype; k.epilogue = a.epilogue;
+  k.accumulate = a.accumulate ? 1 : 0; k.a_mn = 0; k.b_mn = 0;
+  // instruction shape of the pair: M = 256, N = 256
+  uint32_t idesc = make_idesc(KIND, a.a_dtype, a.b_dtype, PN, false, false);
+  idesc &= ~(0x1Fu << 24);
+  idesc |= (uint32_t(PM) >> 4) << 24;
+  k.idesc = idesc;
+  k.num_groups = 0;
+  k.sf_k_tiles = k_tiles;
+  p.num_m = (a.M + PM - 1) / PM;
+  p.num_n = (a.N + PN - 1) / PN;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>(p.num_m) * p.num_n;
+  const int sms = a.sm_count > 0 ? a.sm_count : device_sm_count();
+  // pairs that can be resident at once (a pair must sit inside one GPC)
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms - sms % 2);
+    cfg.blockDim = dim3(kNumThreads);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2;
+    at.val.clusterDim.y = 1;
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<KIND>, &cfg) != cudaSuccess || n <= 0) n = sms / 2;
+    max_pairs = n;
+  }
+  long long pairs = max_pairs < sms / 2 ? max_pairs : sms / 2;
+  if (tiles < pairs) pairs = tiles;
+  if (pairs < 1) pairs = 1;
+  gemm_pair_kernel<KIND><<<static_cast<int>(pairs * 2), kNumThreads, C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemm_pair_supported(const GemmArgs& a, bool mxfp8) {
+  if (a.num_groups > 0 || a.a_mn_major || a.b_mn_major) return false;
+  if (a.epilogue != kEpiNone && a.epilogue != kEpiBias) return false;
+  if (a.M < 256 || a.N < 256) return false;
+  if (mxfp8 && a.K % 128 != 0) return false;
+  return true;
+}
+
+cudaError_t gemm_pair_bf16(const GemmArgs& a, cudaStream_t s) { return launch_pair<kKindF16>(a, s); }
+cudaError_t gemm_pair_mxfp8(const GemmArgs& a, cudaStream_t s) { return launch_pair<kKindMxf8>(a, s); }
+
+}  // namespace teb200

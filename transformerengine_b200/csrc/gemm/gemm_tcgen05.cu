@@ -476,15 +476,22 @@ static int pick_bn(int N, int M, bool block_scaled) {
   return 256;
 }
 
+static bool use_pairs() {
+  static const char* env = getenv("TEB200_GEMM_2CTA");  // "0" selects the single-CTA kernels
+  return env == nullptr || atoi(env) != 0;
+}
+
 cudaError_t gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0) return cudaSuccess;
   if (a.K <= 0) return cudaErrorInvalidValue;
+  if (use_pairs() && gemm_pair_supported(a, false)) return gemm_pair_bf16(a, stream);
   return pick_bn(a.N, a.M, false) == 128 ? launch<kKindF16, 128>(a, stream) : launch<kKindF16, 256>(a, stream);
 }
 
 cudaError_t gemm_mxfp8(const GemmArgs& a, cudaStream_t stream) {
   if (a.M <= 0 || a.N <= 0) return cudaSuccess;
   if (a.K <= 0 || a.K % 32 != 0) return cudaErrorInvalidValue;
+  if (use_pairs() && gemm_pair_supported(a, true)) return gemm_pair_mxfp8(a, stream);
   return pick_bn(a.N, a.M, true) == 128 ? launch<kKindMxf8, 128>(a, stream) : launch<kKindMxf8, 256>(a, stream);
 }
 

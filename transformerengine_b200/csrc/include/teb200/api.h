@@ -51,6 +51,11 @@ cudaError_t gemm_bf16(const GemmArgs& args, cudaStream_t stream);    // fp16 or 
 cudaError_t gemm_mxfp8(const GemmArgs& args, cudaStream_t stream);   // e4m3/e5m2 + ue8m0 per 32
 cudaError_t gemm_nvfp4(const GemmArgs& args, cudaStream_t stream);   // e2m1 + e4m3 per 16
 
+// CTA-pair (cta_group::2) variants, 256x256 tile per pair of SMs
+bool gemm_pair_supported(const GemmArgs& args, bool mxfp8);
+cudaError_t gemm_pair_bf16(const GemmArgs& args, cudaStream_t stream);
+cudaError_t gemm_pair_mxfp8(const GemmArgs& args, cudaStream_t stream);
+
 // build a 2-D row-major tensor map (TMA descriptor)
 bool make_tensor_map_2d(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols,
                         uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols, bool swizzle128);

@@ -1,0 +1,264 @@
+"""Context parallelism: attention over a sequence that is sharded across ranks.
+
+Communication types (reference: ``pytorch/attention/dot_product_attention/
+context_parallel.py:1356, 3014, 4170, 4924``):
+
+* ``"p2p"``        ring exchange of K/V blocks with online-softmax (LSE) merging;
+* ``"all_gather"`` gather all K/V, attend locally;
+* ``"a2a"``        Ulysses: all-to-all trades the sequence shard for a head shard.
+
+For causal masks the sequence is expected in the load-balanced "dual chunk" order: the
+sequence is cut in ``2*cp`` chunks and rank ``r`` holds chunks ``r`` and ``2*cp-1-r``
+(:func:`get_batch_on_this_cp_rank`).  Masks are derived from global token positions, so any
+chunk order works.  Tensors are ``[b, h, s_local, d]``.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+# --------------------------------------------------------------------------- layout helpers
+def dual_chunk_positions(s_local: int, cp_size: int, cp_rank: int, device=None) -> torch.Tensor:
+    """Global positions of this rank's tokens in the dual-chunk layout."""
+    half = s_local // 2
+    a = torch.arange(half, device=device)
+    return torch.cat([a + cp_rank * half, a + (2 * cp_size - 1 - cp_rank) * half])
+
+
+def get_batch_on_this_cp_rank(x: torch.Tensor, cp_size: int, cp_rank: int, seq_dim: int = 1) -> torch.Tensor:
+    """Slice a full-sequence tensor to the two chunks owned by ``cp_rank``."""
+    if cp_size == 1:
+        return x
+    chunks = x.chunk(2 * cp_size, dim=seq_dim)
+    return torch.cat([chunks[cp_rank], chunks[2 * cp_size - 1 - cp_rank]], dim=seq_dim)
+
+
+def pad_thd_sequences_for_cp(cu_seqlens: torch.Tensor, cp_size: int) -> torch.Tensor:
+    """Cumulative lengths after padding every sequence to a multiple of ``2*cp``."""
+    lens = cu_seqlens[1:] - cu_seqlens[:-1]
+    m = 2 * cp_size
+    padded = (lens + m - 1) // m * m
+    out = torch.zeros_like(cu_seqlens)
+    out[1:] = padded.cumsum(0)
+    return out
+
+
+# --------------------------------------------------------------------------- block attention with explicit backward
+def _block_fwd(q, k, v, scale, mask):
+    """Returns (out fp32, lse) of one K/V block; ``mask`` True = masked out."""
+    hq, hk = q.shape[1], k.shape[1]
+    kf, vf = k.float(), v.float()
+    if hk != hq:
+        kf = kf.repeat_interleave(hq // hk, dim=1)
+        vf = vf.repeat_interleave(hq // hk, dim=1)
+    s = torch.matmul(q.float(), kf.transpose(-1, -2)) * scale
+    if mask is not None:
+        s = s.masked_fill(mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    p = torch.exp(s - lse[..., None])
+    p = torch.nan_to_num(p, nan=0.0)
+    return torch.matmul(p, vf), lse
+
+
+def _block_bwd(do, q, k, v, o, lse, scale, mask):
+    """Gradients of one block given the GLOBAL output ``o`` and log-sum-exp ``lse``."""
+    hq, hk = q.shape[1], k.shape[1]
+    rep = hq // hk
+    kf, vf = k.float(), v.float()
+    if rep > 1:
+        kf = kf.repeat_interleave(rep, dim=1)
+        vf = vf.repeat_interleave(rep, dim=1)
+    s = torch.matmul(q.float(), kf.transpose(-1, -2)) * scale
+    if mask is not None:
+        s = s.masked_fill(mask, float("-inf"))
+    p = torch.nan_to_num(torch.exp(s - lse[..., None]), nan=0.0)
+    dof = do.float()
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    dp = torch.matmul(dof, vf.transpose(-1, -2))
+    delta = (dof * o.float()).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = torch.matmul(ds, kf)
+    dk = torch.matmul(ds.transpose(-1, -2), q.float())
+    if rep > 1:
+        b, _, sk, d = dk.shape
+        dk = dk.reshape(b, hk, rep, sk, d).sum(2)
+        dv = dv.reshape(b, hk, rep, sk, d).sum(2)
+    return dq, dk, dv
+
+
+def _mask_for(qpos, kpos, causal, window):
+    if not causal and (window is None or (window[0] < 0 and window[1] < 0)):
+        return None
+    rel = kpos[None, :] - qpos[:, None]
+    m = torch.zeros(rel.shape, dtype=torch.bool, device=qpos.device)
+    right = 0 if causal else window[1]
+    left = window[0] if window is not None else -1
+    if right >= 0:
+        m |= rel > right
+    if left >= 0:
+        m |= rel < -left
+    return m
+
+
+def _ring_exchange(t: torch.Tensor, group, ranks: Optional[List[int]]) -> torch.Tensor:
+    """Send ``t`` to the next rank of the ring, receive from the previous one."""
+    cp = dist.get_world_size(group)
+    me = dist.get_rank(group)
+    nxt, prv = (me + 1) % cp, (me - 1) % cp
+    if ranks is not None:
+        nxt, prv = ranks[nxt], ranks[prv]
+    else:
+        nxt, prv = dist.get_global_rank(group, nxt), dist.get_global_rank(group, prv)
+    recv = torch.empty_like(t)
+    ops = [dist.P2POp(dist.isend, t.contiguous(), nxt, group), dist.P2POp(dist.irecv, recv, prv, group)]
+    if me % 2:
+        ops.reverse()
+    for r in dist.batch_isend_irecv(ops):
+        r.wait()
+    return recv
+
+
+class _RingAttention(torch.autograd.Function):
+    """K/V blocks travel around the ring; partial results are merged with their log-sum-exp."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, group, ranks, scale, causal, window):  # type: ignore[override]
+        cp, me = dist.get_world_size(group), dist.get_rank(group)
+        sq, sk = q.shape[2], k.shape[2]
+        qpos = dual_chunk_positions(sq, cp, me, q.device) if causal else torch.arange(sq, device=q.device) + me * sq
+        kv = torch.stack([k, v]).contiguous()
+        out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        lse = torch.full(q.shape[:3], float("-inf"), dtype=torch.float32, device=q.device)
+        for step in range(cp):
+            src = (me - step) % cp
+            kpos = dual_chunk_positions(sk, cp, src, q.device) if causal else torch.arange(sk, device=q.device) + src * sk
+            mask = _mask_for(qpos, kpos, causal, window)
+            if mask is None or not bool(mask.all()):
+                o_b, lse_b = _block_fwd(q, kv[0], kv[1], scale, mask)
+                new = torch.logaddexp(lse, lse_b)
+                w0 = torch.nan_to_num(torch.exp(lse - new), nan=0.0)[..., None]
+                w1 = torch.nan_to_num(torch.exp(lse_b - new), nan=0.0)[..., None]
+                out = out * w0 + o_b * w1
+                lse = new
+            if step != cp - 1:
+                kv = _ring_exchange(kv, group, ranks)
+        o = out.to(q.dtype)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.cfg = (group, ranks, scale, causal, window)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):  # type: ignore[override]
+        q, k, v, o, lse = ctx.saved_tensors
+        group, ranks, scale, causal, window = ctx.cfg
+        cp, me = dist.get_world_size(group), dist.get_rank(group)
+        sq, sk = q.shape[2], k.shape[2]
+        qpos = dual_chunk_positions(sq, cp, me, q.device) if causal else torch.arange(sq, device=q.device) + me * sq
+        kv = torch.stack([k, v]).contiguous()
+        dkv = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)
+        dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+        for step in range(cp):
+            src = (me - step) % cp
+            kpos = dual_chunk_positions(sk, cp, src, q.device) if causal else torch.arange(sk, device=q.device) + src * sk
+            mask = _mask_for(qpos, kpos, causal, window)
+            if mask is None or not bool(mask.all()):
+                dq_b, dk_b, dv_b = _block_bwd(do, q, kv[0], kv[1], o, lse, scale, mask)
+                dq += dq_b
+                dkv[0] += dk_b
+                dkv[1] += dv_b
+            # gradients travel with their K/V block; after cp hops they are back at the owner
+            if cp > 1:
+                dkv = _ring_exchange(dkv, group, ranks)
+                if step != cp - 1:
+                    kv = _ring_exchange(kv, group, ranks)
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None, None
+
+
+class _AllGatherSeq(torch.autograd.Function):
+    """All-gather along the sequence dim (2); backward reduce-scatters."""
+
+    @staticmethod
+    def forward(ctx, x, group):  # type: ignore[override]
+        ctx.group = group
+        cp = dist.get_world_size(group)
+        xs = [torch.empty_like(x) for _ in range(cp)]
+        dist.all_gather(xs, x.contiguous(), group=group)
+        return torch.stack(xs, dim=0)  # [cp, b, h, s, d]
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        cp = dist.get_world_size(ctx.group)
+        out = torch.empty_like(g[0])
+        dist.reduce_scatter(out, [g[i].contiguous() for i in range(cp)], group=ctx.group)
+        return out, None
+
+
+class _SeqToHeads(torch.autograd.Function):
+    """Ulysses all-to-all: [b, h, s/cp, d] -> [b, h/cp, s, d] (and back in backward)."""
+
+    @staticmethod
+    def forward(ctx, x, group, to_heads):  # type: ignore[override]
+        ctx.group, ctx.to_heads = group, to_heads
+        return _a2a(x, group, to_heads)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return _a2a(g.contiguous(), ctx.group, not ctx.to_heads), None, None
+
+
+def _a2a(x, group, to_heads):
+    cp = dist.get_world_size(group)
+    b, h, s, d = x.shape
+    if to_heads:
+        inp = x.reshape(b, cp, h // cp, s, d).permute(1, 0, 2, 3, 4).contiguous()  # [cp, b, h/cp, s, d]
+        out = torch.empty_like(inp)
+        dist.all_to_all_single(out, inp, group=group)
+        return out.permute(1, 2, 0, 3, 4).reshape(b, h // cp, cp * s, d)  # sequence chunks in rank order
+    inp = x.reshape(b, h, cp, s // cp, d).permute(2, 0, 1, 3, 4).contiguous()  # [cp, b, h, s/cp, d]
+    out = torch.empty_like(inp)
+    dist.all_to_all_single(out, inp, group=group)
+    return out.permute(1, 0, 2, 3, 4).reshape(b, cp * h, s // cp, d)
+
+
+def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", scale: Optional[float] = None,
+                              causal: bool = True, window=None, cp_global_ranks=None, cp_stream=None):
+    """Attention over the full sequence from per-rank shards; returns ``[b, h, s_local, d]``."""
+    from ..ops.attention import attention_ref
+
+    cp = dist.get_world_size(cp_group)
+    me = dist.get_rank(cp_group)
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if cp == 1:
+        return attention_ref(q, k, v, scale=scale, causal=causal, window=window)
+    if cp_comm_type == "p2p":
+        return _RingAttention.apply(q, k, v, cp_group, cp_global_ranks, scale, causal, window)
+    if cp_comm_type == "all_gather":
+        sq, sk = q.shape[2], k.shape[2]
+        kg, vg = _AllGatherSeq.apply(k, cp_group), _AllGatherSeq.apply(v, cp_group)
+        kf = torch.cat([kg[i] for i in range(cp)], dim=2)
+        vf = torch.cat([vg[i] for i in range(cp)], dim=2)
+        if causal:
+            qpos = dual_chunk_positions(sq, cp, me, q.device)
+            kpos = torch.cat([dual_chunk_positions(sk, cp, r, q.device) for r in range(cp)])
+        else:
+            qpos = torch.arange(sq, device=q.device) + me * sq
+            kpos = torch.arange(sk * cp, device=q.device)
+        mask = _mask_for(qpos, kpos, causal, window)
+        return attention_ref(q, kf, vf, scale=scale, attn_mask=mask)
+    if cp_comm_type == "a2a":
+        assert q.shape[1] % cp == 0 and k.shape[1] % cp == 0, "Ulysses needs heads divisible by the CP size"
+        qh, kh, vh = (_SeqToHeads.apply(t, cp_group, True) for t in (q, k, v))
+        s_full = qh.shape[2]
+        if causal:  # chunks arrive in rank order: positions follow the dual-chunk layout of every rank
+            pos = torch.cat([dual_chunk_positions(q.shape[2], cp, r, q.device) for r in range(cp)])
+            mask = _mask_for(pos, pos, True, window)
+        else:
+            mask = _mask_for(torch.arange(s_full, device=q.device), torch.arange(s_full, device=q.device), False,
+                             window)
+        oh = attention_ref(qh, kh, vh, scale=scale, attn_mask=mask)
+        return _SeqToHeads.apply(oh, cp_group, False)
+    raise ValueError(f"unknown cp_comm_type {cp_comm_type}")

@@ -148,7 +148,8 @@ class DotProductAttention(torch.nn.Module):
             with ctx:
                 o = ops.attention(qb, kb, vb, scale=self.softmax_scale, causal=causal, window=window, attn_mask=mask,
                                   bias=the_bias, dropout_p=dropout, softmax_type=self.softmax_type,
-                                  sink=self.softmax_offset, bottom_right=bottom_right or sq == sk)
+                                  sink=self.softmax_offset, bottom_right=bottom_right or sq == sk,
+                                  out_format=fmt)
         if fmt == "sbhd":
             return o.permute(2, 0, 1, 3).reshape(sq, b, hq * o.shape[-1])
         return o.permute(0, 2, 1, 3).reshape(b, sq, hq * o.shape[-1])

@@ -1,0 +1,93 @@
+// Shared pieces of the fused attention kernels (head dim 128, 16-bit inputs, fp32 softmax).
+//
+// All three kernels (forward, dQ, dK/dV) are warp-specialised: one TMA producer warp, one
+// tcgen05 issuer warp and two groups of four softmax warps that work on two independent score
+// tiles, so that the tensor pipe computes one tile's products while the other tile's
+// exponentials run.  Score and output accumulators live in TMEM; probabilities go back to the
+// tensor cores through 128-byte-swizzled shared-memory tiles.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "teb200/api.h"
+#include "teb200/ptx.cuh"
+
+namespace teb200 {
+namespace attn {
+
+constexpr int kHeadDim = 128;
+constexpr int kThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 tile 0, warps 6-9 tile 1
+
+enum FlashStatus : int {
+  kFlashOk = 0,
+  kFlashTimeoutProducer = 21,
+  kFlashTimeoutMma = 22,
+  kFlashTimeoutSoftmax = 23,
+};
+
+struct FlashParams {
+  int b, hq, hk, sq, sk;
+  int causal;      // 1: key j visible to query i when j <= i + causal_off
+  int causal_off;  // sk - sq for the bottom-right aligned mask, 0 for top-left
+  float scale;       // softmax scale
+  float scale_log2;  // scale * log2(e)
+  int is_bf16;
+  // outputs, addressed as [b, h, s, d] views with element strides (d contiguous)
+  void* out;       // forward: O; dQ kernel: dQ
+  long long o_sb, o_sh, o_ss;
+  void* out2;      // dK/dV kernel: dV (out = dK), same strides
+  float* lse;      // [b, hq, s_pad] natural-log LSE
+  float* delta;    // [b, hq, s_pad] rowsum(dO * O)
+  int s_pad;
+  int* status;
+};
+
+// 4-D tile load: coordinates (d, s, h, b)
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,
+                                            int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, "
+      "%6}], [%2];" ::"r"(smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// instruction descriptor of a 16-bit MMA with fp32 accumulation, M = 128
+__host__ __device__ inline uint32_t attn_idesc(bool bf16, int n, bool a_mn, bool b_mn) {
+  uint32_t d = 0;
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  d |= 1u << 4;
+  d |= fmt << 7;
+  d |= fmt << 10;
+  d |= (a_mn ? 1u : 0u) << 15;
+  d |= (b_mn ? 1u : 0u) << 16;
+  d |= (uint32_t(n) >> 3) << 17;
+  d |= (128u >> 4) << 24;
+  return d;
+}
+
+// Write one row of a [128 x 64] 16-bit tile in the 128-byte-swizzled K-major layout the
+// tensor core reads: row r starts at r * 128 bytes, its 16-byte chunk c sits at chunk c ^ (r % 8).
+__device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint32_t (&w)[32]) {
+  uint8_t* row = tile + r * 128;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
+  }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// 4-D tensor map over a [b, h, s, d] view; strides in elements, box = [rows x 64 elements]
+bool make_tensor_map_bhsd(CUtensorMap* map, const void* base, bool bf16, int b, int h, int s, long long sb,
+                          long long sh, long long ss, int box_rows);
+
+}  // namespace attn
+}  // namespace teb200

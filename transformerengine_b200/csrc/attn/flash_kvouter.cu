@@ -1,0 +1,365 @@
+// Fused attention backward, key-stationary kernel: dK and dV.
+//
+// One CTA owns 128 key rows of one K/V head and walks every 64-row query block that can see
+// them, for every query head of the GQA group.  Per query block, on transposed tiles:
+//   S^T = K Q^T, dP^T = V dO^T           (tensor cores, accumulators in TMEM)
+//   P^T = exp2(S^T*c - lse), dS^T = P^T * (dP^T - delta)      (softmax warps, thread = key row)
+//   dV += P^T dO,  dK += dS^T Q          (dO and Q blocks reused as MN-major B operands)
+// Two groups of softmax warps alternate over the query blocks so that the tensor pipe and the
+// exponentials overlap.  dK/dV stay in TMEM for the whole walk and are written once.
+#include "flash_common.cuh"
+
+namespace teb200 {
+namespace attn {
+
+struct KvCfg {
+  static constexpr int kRing = 2;
+  static constexpr int kKBytes = 32768, kVBytes = 32768;
+  static constexpr int kQBlk = 16384;                       // [64 x 128] Q or dO block
+  static constexpr int kVecBytes = 256;                     // 64 floats of lse / delta
+  static constexpr int kStageBytes = 2 * kQBlk + 2 * kVecBytes + 512;  // keep 1024-byte alignment
+  static constexpr int kOffV = kKBytes;
+  static constexpr int kOffRing = kOffV + kVBytes;
+  static constexpr int kOffP = kOffRing + kRing * kStageBytes;   // P^T[2], then dS^T[2]
+  static constexpr int kOffBar = kOffP + 4 * 16384;
+  static constexpr int kNumBars = 1 + 2 * kRing + 2 + 2 + 2 + 1;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
+  static constexpr int kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
+};
+static_assert(KvCfg::kStageBytes % 1024 == 0, "ring stages must keep the swizzle alignment");
+
+__global__ void __launch_bounds__(kThreads, 1)
+flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const FlashParams p) {
+  using C = KvCfg;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint64_t* kv_full = bars;
+  uint64_t* r_full = bars + 1;             // [kRing]
+  uint64_t* r_empty = r_full + C::kRing;   // [kRing]
+  uint64_t* s_full = r_empty + C::kRing;   // [2]
+  uint64_t* p_ready = s_full + 2;          // [2]
+  uint64_t* pd_done = p_ready + 2;         // [2]
+  uint64_t* acc_done = pd_done + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kb = blockIdx.x;
+  const int hk = blockIdx.y;
+  const int b = blockIdx.z;
+  const int G = p.hq / p.hk;
+  const int kv0 = kb * 128;
+  const int nq = (p.sq + 63) / 64;
+  int i_start = 0;
+  if (p.causal) {
+    const int first_q = kv0 - p.causal_off;  // first query row that sees key kv0
+    i_start = first_q <= 0 ? 0 : first_q / 64;
+  }
+  const int ni = nq > i_start ? nq - i_start : 0;
+  const int N = G * ni;
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&tmap_q);
+    prefetch_tensormap(&tmap_k);
+    prefetch_tensormap(&tmap_v);
+    prefetch_tensormap(&tmap_do);
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < C::kRing; ++i) {
+      mbar_init(&r_full[i], 1);
+      mbar_init(&r_empty[i], 1);
+    }
+    for (int u = 0; u < 2; ++u) {
+      mbar_init(&s_full[u], 1);
+      mbar_init(&p_ready[u], 4);
+      mbar_init(&pd_done[u], 1);
+    }
+    mbar_init(acc_done, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && N > 0) {
+      mbar_expect_tx(kv_full, C::kKBytes + C::kVBytes);
+      for (int pn = 0; pn < 2; ++pn) {
+        tma_load_4d(smem + pn * 16384, &tmap_k, kv_full, pn * 64, kv0, hk, b);
+        tma_load_4d(smem + C::kOffV + pn * 16384, &tmap_v, kv_full, pn * 64, kv0, hk, b);
+      }
+      for (int it = 0; it < N; ++it) {
+        const int st = it % C::kRing;
+        const int h = hk * G + it / ni;
+        const int qr = (i_start + it % ni) * 64;
+        if (!mbar_wait(&r_empty[st], ((it / C::kRing) & 1) ^ 1)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
+        uint8_t* base = smem + C::kOffRing + st * C::kStageBytes;
+        mbar_expect_tx(&r_full[st], 2 * C::kQBlk + 2 * C::kVecBytes);
+        for (int pn = 0; pn < 2; ++pn) {
+          tma_load_4d(base + pn * 8192, &tmap_q, &r_full[st], pn * 64, qr, h, b);
+          tma_load_4d(base + C::kQBlk + pn * 8192, &tmap_do, &r_full[st], pn * 64, qr, h, b);
+        }
+        const size_t off = (static_cast<size_t>(b) * p.hq + h) * p.s_pad + qr;
+        bulk_load_1d(base + 2 * C::kQBlk, p.lse + off, C::kVecBytes, &r_full[st]);
+        bulk_load_1d(base + 2 * C::kQBlk + C::kVecBytes, p.delta + off, C::kVecBytes, &r_full[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ tcgen05 issuer
+    if (lane == 0 && N > 0) {
+      const bool bf = p.is_bf16 != 0;
+      const uint32_t idesc_s = attn_idesc(bf, 64, false, false);
+      const uint32_t idesc_acc = attn_idesc(bf, 128, false, true);
+      const uint32_t sK = smem_u32(smem), sV = smem_u32(smem + C::kOffV);
+      const uint32_t sRing = smem_u32(smem + C::kOffRing), sP = smem_u32(smem + C::kOffP);
+      bool ok = mbar_wait(kv_full, 0);
+      auto issue_s = [&](int it) -> bool {
+        const int st = it % C::kRing, u = it & 1;
+        if (!mbar_wait(&r_full[st], (it / C::kRing) & 1)) return false;
+        tc_fence_after();
+        const uint32_t sQ = sRing + st * C::kStageBytes, sDo = sQ + C::kQBlk;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t a = umma_desc_k_sw128(sK + (k >> 2) * 16384) + (k & 3) * 2;
+          const uint64_t bd = umma_desc_k_sw128(sQ + (k >> 2) * 8192) + (k & 3) * 2;
+          umma_f16(tmem_base + C::kColS + u * 64, a, bd, idesc_s, k != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t a = umma_desc_k_sw128(sV + (k >> 2) * 16384) + (k & 3) * 2;
+          const uint64_t bd = umma_desc_k_sw128(sDo + (k >> 2) * 8192) + (k & 3) * 2;
+          umma_f16(tmem_base + C::kColDp + u * 64, a, bd, idesc_s, k != 0);
+        }
+        tc_commit(&s_full[u]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int it = 0; ok && it < N; ++it) {
+        const int st = it % C::kRing, u = it & 1;
+        if (it + 1 < N) ok = issue_s(it + 1);
+        if (!ok) break;
+        if (!mbar_wait(&p_ready[u], (it >> 1) & 1)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sQ = sRing + st * C::kStageBytes, sDo = sQ + C::kQBlk;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t a = umma_desc_k_sw128(sP + u * 16384) + k * 2;
+          const uint64_t bd = umma_desc_mn_sw128(sDo, 8192) + k * (2048 >> 4);
+          umma_f16(tmem_base + C::kColDv, a, bd, idesc_acc, (it | k) != 0);
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t a = umma_desc_k_sw128(sP + (2 + u) * 16384) + k * 2;
+          const uint64_t bd = umma_desc_mn_sw128(sQ, 8192) + k * (2048 >> 4);
+          umma_f16(tmem_base + C::kColDk, a, bd, idesc_acc, (it | k) != 0);
+        }
+        tc_commit(&pd_done[u]);
+        tc_commit(&r_empty[st]);
+      }
+      if (ok) tc_commit(acc_done);
+      else atomicCAS(p.status, 0, kFlashTimeoutMma);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / dS warps
+    const int u = (warp - 2) >> 2;       // group u takes iterations it with it % 2 == u
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int kv_row = kv0 + r;
+    const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
+    uint8_t* sPt = smem + C::kOffP + u * 16384;
+    uint8_t* sDst = smem + C::kOffP + (2 + u) * 16384;
+    bool ok = true;
+    for (int it = u; it < N; it += 2) {
+      const int st = it % C::kRing;
+      const int qr = (i_start + it % ni) * 64;
+      if (!mbar_wait(&s_full[u], (it >> 1) & 1)) { ok = false; break; }
+      tc_fence_after();
+      const float* vec = reinterpret_cast<const float*>(smem + C::kOffRing + st * C::kStageBytes + 2 * C::kQBlk);
+      const bool need_mask = (kv0 + 128 > p.sk) || (qr + 64 > p.sq) || (p.causal && kv0 + 127 > qr + p.causal_off);
+      // key kv_row is visible to query q iff q >= q_min (and the key exists)
+      const int q_min = kv_row < p.sk ? (p.causal ? kv_row - p.causal_off : 0) : 0x7fffffff;
+      uint32_t wp[32], wd[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32(lane_base + C::kColS + u * 64 + half * 32, s);
+        tmem_ld_32x32(lane_base + C::kColDp + u * 64 + half * 32, dp);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float4 l4 = *reinterpret_cast<const float4*>(vec + half * 32 + c);
+          const float4 d4 = *reinterpret_cast<const float4*>(vec + 64 + half * 32 + c);
+          const float ls[4] = {l4.x, l4.y, l4.z, l4.w};
+          const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+          float pv[4], dv[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float x = fast_exp2(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -ls[e] * 1.4426950408889634f));
+            float y = x * (__uint_as_float(dp[c + e]) - dl[e]);
+            if (need_mask) {
+              const int q = qr + half * 32 + c + e;
+              const bool vis = q >= q_min && q < p.sq;
+              x = vis ? x : 0.f;
+              y = vis ? y : 0.f;
+            }
+            pv[e] = x;
+            dv[e] = y;
+          }
+          wp[half * 16 + c / 2] = p.is_bf16 ? pack_bf16x2(pv[0], pv[1]) : pack_f16x2(pv[0], pv[1]);
+          wp[half * 16 + c / 2 + 1] = p.is_bf16 ? pack_bf16x2(pv[2], pv[3]) : pack_f16x2(pv[2], pv[3]);
+          wd[half * 16 + c / 2] = p.is_bf16 ? pack_bf16x2(dv[0], dv[1]) : pack_f16x2(dv[0], dv[1]);
+          wd[half * 16 + c / 2 + 1] = p.is_bf16 ? pack_bf16x2(dv[2], dv[3]) : pack_f16x2(dv[2], dv[3]);
+        }
+      }
+      if (it >= 2) {
+        if (!mbar_wait(&pd_done[u], ((it >> 1) - 1) & 1)) { ok = false; break; }
+      }
+      store_row_sw128(sPt, r, wp);
+      store_row_sw128(sDst, r, wd);
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[u]);
+    }
+    if (!ok && lane == 0) atomicCAS(p.status, 0, kFlashTimeoutSoftmax);
+    // ---------------------------------------------------------------- epilogue: group 0 -> dK, group 1 -> dV
+    if (ok && N > 0) {
+      if (!mbar_wait(acc_done, 0)) {
+        ok = false;
+        if (lane == 0) atomicCAS(p.status, 0, kFlashTimeoutSoftmax);
+      }
+      tc_fence_after();
+    }
+    // TMEM loads are warp-wide: every lane takes part, only the stores depend on the row
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      const bool row_ok = kv_row < p.sk;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(u == 0 ? p.out : p.out2) + b * p.o_sb + hk * p.o_sh +
+                       static_cast<long long>(kv_row) * p.o_ss;
+      const float mul = u == 0 ? p.scale : 1.f;
+      const uint32_t col0 = u == 0 ? C::kColDk : C::kColDv;
+#pragma unroll 1
+      for (int c0 = 0; c0 < 128; c0 += 32) {
+        uint32_t o[32];
+        if (N > 0) {
+          tmem_ld_32x32(lane_base + col0 + c0, o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int c = 0; c < 32; c += 8) {
+            uint32_t q4[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float x0 = __uint_as_float(o[c + 2 * i]) * mul, x1 = __uint_as_float(o[c + 2 * i + 1]) * mul;
+              q4[i] = p.is_bf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
+            }
+            *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(q4[0], q4[1], q4[2], q4[3]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// delta[b, h, s] = sum_d dO * O, one warp per row
+__global__ void flash_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout, float* delta,
+                                   int b, int h, int s, int s_pad, long long o_sb, long long o_sh, long long o_ss,
+                                   long long d_sb, long long d_sh, long long d_ss, int is_bf16) {
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long rows = static_cast<long long>(b) * h * s;
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const int si = static_cast<int>(row % s);
+  const int hi = static_cast<int>((row / s) % h);
+  const int bi = static_cast<int>(row / (static_cast<long long>(s) * h));
+  const uint2 a = *reinterpret_cast<const uint2*>(o + bi * o_sb + hi * o_sh + si * o_ss + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(dout + bi * d_sb + hi * d_sh + si * d_ss + lane * 4);
+  float acc = 0.f;
+  const uint32_t aw[2] = {a.x, a.y}, gw[2] = {g.x, g.y};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float a0, a1, g0, g1;
+    if (is_bf16) {
+      a0 = __uint_as_float(aw[i] << 16); a1 = __uint_as_float(aw[i] & 0xffff0000u);
+      g0 = __uint_as_float(gw[i] << 16); g1 = __uint_as_float(gw[i] & 0xffff0000u);
+    } else {
+      const __half2 ah = *reinterpret_cast<const __half2*>(&aw[i]);
+      const __half2 gh = *reinterpret_cast<const __half2*>(&gw[i]);
+      a0 = __low2float(ah); a1 = __high2float(ah); g0 = __low2float(gh); g1 = __high2float(gh);
+    }
+    acc += a0 * g0 + a1 * g1;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[(static_cast<size_t>(bi) * h + hi) * s_pad + si] = acc;
+}
+
+}  // namespace attn
+
+cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
+  using namespace attn;
+  using C = KvCfg;
+  CUtensorMap tq, tk, tv, tdo;
+  const bool bf = a.is_bf16;
+  const bool ok = make_tensor_map_bhsd(&tq, a.q, bf, a.b, a.hq, a.sq, a.q_sb, a.q_sh, a.q_ss, 64) &&
+                  make_tensor_map_bhsd(&tk, a.k, bf, a.b, a.hk, a.sk, a.k_sb, a.k_sh, a.k_ss, 128) &&
+                  make_tensor_map_bhsd(&tv, a.v, bf, a.b, a.hk, a.sk, a.v_sb, a.v_sh, a.v_ss, 128) &&
+                  make_tensor_map_bhsd(&tdo, a.dout, bf, a.b, a.hq, a.sq, a.do_sb, a.do_sh, a.do_ss, 64);
+  if (!ok) return cudaErrorInvalidValue;
+  if (a.s_pad % 64 != 0 || a.s_pad < ((a.sq + 63) / 64) * 64) return cudaErrorInvalidValue;
+  if (a.dk_sb != a.dv_sb || a.dk_sh != a.dv_sh || a.dk_ss != a.dv_ss) return cudaErrorInvalidValue;
+  FlashParams p = {};
+  p.b = a.b; p.hq = a.hq; p.hk = a.hk; p.sq = a.sq; p.sk = a.sk;
+  p.causal = a.causal ? 1 : 0;
+  p.causal_off = a.bottom_right ? a.sk - a.sq : 0;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.is_bf16 = bf ? 1 : 0;
+  p.out = a.dk; p.out2 = a.dv; p.o_sb = a.dk_sb; p.o_sh = a.dk_sh; p.o_ss = a.dk_ss;
+  if ((reinterpret_cast<uintptr_t>(a.dk) & 15) || (reinterpret_cast<uintptr_t>(a.dv) & 15) || p.o_sb % 8 || p.o_sh % 8 ||
+      p.o_ss % 8)
+    return cudaErrorInvalidValue;
+  p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(flash_kvouter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  dim3 grid((a.sk + 127) / 128, a.hk, a.b);
+  flash_kvouter_kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  return cudaGetLastError();
+}
+
+cudaError_t flash_delta(const FlashArgs& a, cudaStream_t stream) {
+  const long long rows = static_cast<long long>(a.b) * a.hq * a.sq;
+  if (rows == 0) return cudaSuccess;
+  if (a.o_ss % 4 || a.o_sh % 4 || a.o_sb % 4 || a.do_ss % 4 || a.do_sh % 4 || a.do_sb % 4) return cudaErrorInvalidValue;
+  const int warps = 8;
+  const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
+  attn::flash_delta_kernel<<<grid, warps * 32, 0, stream>>>(
+      reinterpret_cast<const uint16_t*>(a.out), reinterpret_cast<const uint16_t*>(a.dout), a.delta, a.b, a.hq, a.sq,
+      a.s_pad, a.o_sb, a.o_sh, a.o_ss, a.do_sb, a.do_sh, a.do_ss, a.is_bf16 ? 1 : 0);
+  return cudaGetLastError();
+}
+
+}  // namespace teb200

@@ -89,6 +89,70 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, int64_t epoch, int64_t
   TORCH_CHECK(e == cudaSuccess, "comm_gemm failed: ", cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------------------- fused attention
+// Tensors are [b, h, s, d] views (any strides with d contiguous).
+void fill_strides(const at::Tensor& t, long long& sb, long long& sh, long long& ss) {
+  TORCH_CHECK(t.dim() == 4 && t.stride(3) == 1, "attention tensors must be [b, h, s, d] views with contiguous d");
+  sb = t.stride(0);
+  sh = t.stride(1);
+  ss = t.stride(2);
+}
+
+teb200::FlashArgs flash_args(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
+                             const at::Tensor& lse, double scale, bool causal, bool bottom_right,
+                             const at::Tensor& status) {
+  TORCH_CHECK(q.size(3) == 128 && k.size(3) == 128 && v.size(3) == 128, "fused attention needs head dim 128");
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kHalf, "fused attention needs fp16/bf16");
+  teb200::FlashArgs a;
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr(); a.out = out.data_ptr();
+  a.lse = lse.data_ptr<float>();
+  a.b = static_cast<int>(q.size(0)); a.hq = static_cast<int>(q.size(1)); a.hk = static_cast<int>(k.size(1));
+  a.sq = static_cast<int>(q.size(2)); a.sk = static_cast<int>(k.size(2));
+  a.s_pad = static_cast<int>(lse.size(2));
+  a.causal = causal; a.bottom_right = bottom_right; a.is_bf16 = q.scalar_type() == at::kBFloat16;
+  a.scale = static_cast<float>(scale);
+  fill_strides(q, a.q_sb, a.q_sh, a.q_ss);
+  fill_strides(k, a.k_sb, a.k_sh, a.k_ss);
+  fill_strides(v, a.v_sb, a.v_sh, a.v_ss);
+  fill_strides(out, a.o_sb, a.o_sh, a.o_ss);
+  a.status = status.data_ptr<int>();
+  return a;
+}
+
+void flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
+               const at::Tensor& lse, double scale, bool causal, bool bottom_right, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  cudaError_t e = teb200::flash_fwd(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_fwd failed: ", cudaGetErrorString(e));
+}
+
+void flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+               const at::Tensor& out, const at::Tensor& lse, const at::Tensor& delta, const at::Tensor& dq,
+               const at::Tensor& dk, const at::Tensor& dv, double scale, bool causal, bool bottom_right,
+               const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  a.dout = dout.data_ptr();
+  a.delta = delta.data_ptr<float>();
+  a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  fill_strides(dout, a.do_sb, a.do_sh, a.do_ss);
+  fill_strides(dq, a.dq_sb, a.dq_sh, a.dq_ss);
+  fill_strides(dk, a.dk_sb, a.dk_sh, a.dk_ss);
+  fill_strides(dv, a.dv_sb, a.dv_sh, a.dv_ss);
+  cudaError_t e = teb200::flash_delta(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_delta failed: ", cudaGetErrorString(e));
+  e = teb200::flash_bwd_dkdv(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_bwd_dkdv failed: ", cudaGetErrorString(e));
+  e = teb200::flash_bwd_dq(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_bwd_dq failed: ", cudaGetErrorString(e));
+}
+
 }  // namespace
 
-void register_extra(py::module_& m) { m.def("comm_gemm", &comm_gemm); }
+void register_extra(py::module_& m) {
+  m.def("comm_gemm", &comm_gemm);
+  m.def("flash_fwd", &flash_fwd);
+  m.def("flash_bwd", &flash_bwd);
+}
+

@@ -56,6 +56,32 @@ bool gemm_pair_supported(const GemmArgs& args, bool mxfp8);
 cudaError_t gemm_pair_bf16(const GemmArgs& args, cudaStream_t stream);
 cudaError_t gemm_pair_mxfp8(const GemmArgs& args, cudaStream_t stream);
 
+// Fused attention (head dim 128, fp16/bf16).  Every tensor is a [b, h, s, d] VIEW described by
+// element strides (d contiguous), so sbhd / bshd / packed-QKV layouts need no copy.
+struct FlashArgs {
+  const void* q = nullptr;
+  const void* k = nullptr;
+  const void* v = nullptr;
+  const void* dout = nullptr;
+  void* out = nullptr;   // forward output (read by the delta pass in the backward)
+  void* dq = nullptr;
+  void* dk = nullptr;
+  void* dv = nullptr;
+  float* lse = nullptr;    // [b, hq, s_pad]
+  float* delta = nullptr;  // [b, hq, s_pad]
+  int b = 0, hq = 0, hk = 0, sq = 0, sk = 0, s_pad = 0;
+  bool causal = false, bottom_right = true, is_bf16 = true;
+  float scale = 1.0f;
+  long long q_sb = 0, q_sh = 0, q_ss = 0, k_sb = 0, k_sh = 0, k_ss = 0, v_sb = 0, v_sh = 0, v_ss = 0;
+  long long o_sb = 0, o_sh = 0, o_ss = 0, do_sb = 0, do_sh = 0, do_ss = 0;
+  long long dq_sb = 0, dq_sh = 0, dq_ss = 0, dk_sb = 0, dk_sh = 0, dk_ss = 0, dv_sb = 0, dv_sh = 0, dv_ss = 0;
+  int* status = nullptr;
+};
+cudaError_t flash_fwd(const FlashArgs& args, cudaStream_t stream);
+cudaError_t flash_delta(const FlashArgs& args, cudaStream_t stream);     // delta = rowsum(dO * O)
+cudaError_t flash_bwd_dq(const FlashArgs& args, cudaStream_t stream);
+cudaError_t flash_bwd_dkdv(const FlashArgs& args, cudaStream_t stream);
+
 // build a 2-D row-major tensor map (TMA descriptor)
 bool make_tensor_map_2d(CUtensorMap* map, const void* base, int dtype, uint64_t rows, uint64_t cols,
                         uint64_t ld_elems, uint32_t box_rows, uint32_t box_cols, bool swizzle128);

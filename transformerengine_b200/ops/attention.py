@@ -8,6 +8,8 @@ UnfusedDotProductAttention and the cuDNN graphs of ``common/fused_attn``).
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Optional, Tuple
 
@@ -71,11 +73,14 @@ def attention_ref(q, k, v, *, scale=None, causal=False, window=None, attn_mask=N
 
 
 _USE_LIBRARY_SDPA = True
+# TEB200_ATTN=library routes the plain 16-bit case to torch's SDPA instead of csrc/attn (A/B timing)
+_USE_OWN_FLASH = os.environ.get("TEB200_ATTN", "own") != "library"
 
 
 def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None, bias=None, dropout_p=0.0,
-              softmax_type="vanilla", sink=None, bottom_right=True):
-    """Differentiable attention on ``[b, h, s, d]``.
+              softmax_type="vanilla", sink=None, bottom_right=True, out_format="bhsd"):
+    """Differentiable attention on ``[b, h, s, d]``; ``out_format`` names the memory layout of the
+    returned ``[b, h, s, d]`` view ("bhsd", "sbhd" or "bshd") when the fused kernel runs.
 
     On CUDA the fused flash kernel of this library handles the common case
     (16-bit, no bias / arbitrary mask / dropout, head dim 64 or 128); everything
@@ -86,8 +91,8 @@ def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None,
     if _ext.use_cuda(q) and plain and q.dtype in (torch.bfloat16, torch.float16):
         from . import flash
 
-        if flash.supported(q, k, v, causal):
-            return flash.flash_attention(q, k, v, scale, causal, bottom_right)
+        if _USE_OWN_FLASH and flash.supported(q, k, v, causal):
+            return flash.flash_attention(q, k, v, scale, causal, bottom_right, out_format)
         if _USE_LIBRARY_SDPA and (not causal or q.shape[2] == k.shape[2] or not bottom_right):
             return torch.nn.functional.scaled_dot_product_attention(
                 q, k, v, is_causal=causal, scale=scale, enable_gqa=q.shape[1] != k.shape[1])

@@ -1,6 +1,6 @@
 """Run one kernel of the library a few times on a fixed case (target for ncu captures).
 
-    python benchmarks/kernel_case.py --kernel gemm_mxfp8|gemm_bf16|quantize|swiglu_quantize|adam|rmsnorm_bwd|cross_entropy
+    python benchmarks/kernel_case.py --kernel gemm_mxfp8|gemm_bf16|quantize|swiglu_quantize|adam|rmsnorm_bwd|cross_entropy|attention
 """
 import argparse
 import os
@@ -53,6 +53,15 @@ def main():
         lg = torch.randn(2048, 128256, device="cuda", dtype=bf)
         t = torch.randint(0, 128256, (2048,), device="cuda")
         fn = lambda: ops.cross_entropy_fwd_bwd(lg, t, 1.0, inplace_grad=False)  # noqa: E731
+    elif a.kernel == "attention":
+        # causal GQA, 16 query / 4 key-value heads, seq 4096: forward + both backward kernels
+        from transformerengine_b200.ops import flash
+
+        q = torch.randn(1, 16, 4096, 128, device="cuda", dtype=bf, requires_grad=True)
+        k = torch.randn(1, 4, 4096, 128, device="cuda", dtype=bf, requires_grad=True)
+        v = torch.randn(1, 4, 4096, 128, device="cuda", dtype=bf, requires_grad=True)
+        do = torch.randn(1, 16, 4096, 128, device="cuda", dtype=bf)
+        fn = lambda: flash.flash_attention(q, k, v, None, True).backward(do)  # noqa: E731
     else:
         raise SystemExit(f"unknown kernel {a.kernel}")
     for _ in range(a.reps):

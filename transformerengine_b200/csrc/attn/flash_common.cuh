@@ -19,7 +19,7 @@ namespace teb200 {
 namespace attn {
 
 constexpr int kHeadDim = 128;
-constexpr int kThreads = 320;  // warp 0 TMA, warp 1 MMA, warps 2-5 tile 0, warps 6-9 tile 1
+constexpr int kThreads = 576;  // warp 0 TMA, warp 1 MMA, warps 2-9 tile (group) 0, warps 10-17 tile (group) 1
 
 enum FlashStatus : int {
   kFlashOk = 0,
@@ -43,6 +43,7 @@ struct FlashParams {
   float* delta;    // [b, hq, s_pad] rowsum(dO * O)
   int s_pad;
   int* status;
+  long long* timeline;  // optional [64][16] clock stamps of CTA 0 (profiling aid), else nullptr
 };
 
 // 4-D tile load: coordinates (d, s, h, b)
@@ -56,7 +57,7 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
 }
 
 // instruction descriptor of a 16-bit MMA with fp32 accumulation, M = 128
-__host__ __device__ inline uint32_t attn_idesc(bool bf16, int n, bool a_mn, bool b_mn) {
+__host__ __device__ constexpr uint32_t attn_idesc(bool bf16, int n, bool a_mn, bool b_mn) {
   uint32_t d = 0;
   const uint32_t fmt = bf16 ? 1u : 0u;
   d |= 1u << 4;
@@ -77,6 +78,30 @@ __device__ __forceinline__ void store_row_sw128(uint8_t* tile, int r, const uint
   for (int c = 0; c < 8; ++c) {
     *reinterpret_cast<uint4*>(row + ((c ^ (r & 7)) << 4)) = make_uint4(w[c * 4], w[c * 4 + 1], w[c * 4 + 2], w[c * 4 + 3]);
   }
+}
+
+// tcgen05.mma with the A operand read from TMEM (16-bit elements packed two per 32-bit column,
+// row = lane) and B from shared memory
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 16 columns: registers -> TMEM
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};\n" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+      : "memory");
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

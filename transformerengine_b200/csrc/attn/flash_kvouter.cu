@@ -4,30 +4,31 @@
 // them, for every query head of the GQA group.  Per query block, on transposed tiles:
 //   S^T = K Q^T, dP^T = V dO^T           (tensor cores, accumulators in TMEM)
 //   P^T = exp2(S^T*c - lse), dS^T = P^T * (dP^T - delta)      (softmax warps, thread = key row)
-//   dV += P^T dO,  dK += dS^T Q          (dO and Q blocks reused as MN-major B operands)
+//   dV += P^T dO,  dK += dS^T Q          (A operands from TMEM; dO and Q blocks reused as MN-major B)
 // Two groups of softmax warps alternate over the query blocks so that the tensor pipe and the
 // exponentials overlap.  dK/dV stay in TMEM for the whole walk and are written once.
 #include "flash_common.cuh"
+#include "flash_qouter_softmax.cuh"
 
 namespace teb200 {
 namespace attn {
 
 struct KvCfg {
-  static constexpr int kRing = 2;
+  static constexpr int kRing = 4;
   static constexpr int kKBytes = 32768, kVBytes = 32768;
   static constexpr int kQBlk = 16384;                       // [64 x 128] Q or dO block
   static constexpr int kVecBytes = 256;                     // 64 floats of lse / delta
   static constexpr int kStageBytes = 2 * kQBlk + 2 * kVecBytes + 512;  // keep 1024-byte alignment
   static constexpr int kOffV = kKBytes;
   static constexpr int kOffRing = kOffV + kVBytes;
-  static constexpr int kOffP = kOffRing + kRing * kStageBytes;   // P^T[2], then dS^T[2]
-  static constexpr int kOffBar = kOffP + 4 * 16384;
+  static constexpr int kOffBar = kOffRing + kRing * kStageBytes;
   static constexpr int kNumBars = 1 + 2 * kRing + 2 + 2 + 2 + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
   static constexpr int kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
 };
 static_assert(KvCfg::kStageBytes % 1024 == 0, "ring stages must keep the swizzle alignment");
 
+template <bool BF>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -73,7 +74,7 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(&s_full[u], 1);
-      mbar_init(&p_ready[u], 4);
+      mbar_init(&p_ready[u], 8);
       mbar_init(&pd_done[u], 1);
     }
     mbar_init(acc_done, 1);
@@ -114,31 +115,35 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ tcgen05 issuer
-    if (lane == 0 && N > 0) {
-      const bool bf = p.is_bf16 != 0;
-      const uint32_t idesc_s = attn_idesc(bf, 64, false, false);
-      const uint32_t idesc_acc = attn_idesc(bf, 128, false, true);
-      const uint32_t sK = smem_u32(smem), sV = smem_u32(smem + C::kOffV);
-      const uint32_t sRing = smem_u32(smem + C::kOffRing), sP = smem_u32(smem + C::kOffP);
-      bool ok = mbar_wait(kv_full, 0);
+    // Descriptors are precomputed and the whole warp walks the loop, so that every value stays
+    // warp-uniform; one elected lane issues the tcgen05 instructions.
+    if (N > 0) {
+      constexpr uint32_t idesc_s = attn_idesc(BF, 64, false, false);
+      constexpr uint32_t idesc_acc = attn_idesc(BF, 128, false, true);
+      const uint64_t dK = umma_desc_k_sw128(smem_u32(smem));
+      const uint64_t dV = umma_desc_k_sw128(smem_u32(smem + C::kOffV));
+      const uint64_t dRk = umma_desc_k_sw128(smem_u32(smem + C::kOffRing));        // Q block, K-major view
+      const uint64_t dRmn = umma_desc_mn_sw128(smem_u32(smem + C::kOffRing), 8192);  // Q block, MN-major view
+      constexpr uint32_t kDoOff = C::kQBlk >> 4;                                    // dO block follows Q
+      bool ok = __all_sync(0xffffffffu, mbar_wait(kv_full, 0));
       auto issue_s = [&](int it) -> bool {
         const int st = it % C::kRing, u = it & 1;
-        if (!mbar_wait(&r_full[st], (it / C::kRing) & 1)) return false;
+        if (!__all_sync(0xffffffffu, mbar_wait(&r_full[st], (it / C::kRing) & 1))) return false;
         tc_fence_after();
-        const uint32_t sQ = sRing + st * C::kStageBytes, sDo = sQ + C::kQBlk;
+        const uint64_t q = dRk + static_cast<uint64_t>(st * (C::kStageBytes >> 4));
+        const uint32_t cs = tmem_base + C::kColS + u * 64, cd = tmem_base + C::kColDp + u * 64;
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint64_t a = umma_desc_k_sw128(sK + (k >> 2) * 16384) + (k & 3) * 2;
-          const uint64_t bd = umma_desc_k_sw128(sQ + (k >> 2) * 8192) + (k & 3) * 2;
-          umma_f16(tmem_base + C::kColS + u * 64, a, bd, idesc_s, k != 0);
-        }
+          for (int k = 0; k < 8; ++k)
+            umma_f16(cs, dK + (((k >> 2) * 16384) >> 4) + (k & 3) * 2, q + (((k >> 2) * 8192) >> 4) + (k & 3) * 2,
+                     idesc_s, k != 0);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint64_t a = umma_desc_k_sw128(sV + (k >> 2) * 16384) + (k & 3) * 2;
-          const uint64_t bd = umma_desc_k_sw128(sDo + (k >> 2) * 8192) + (k & 3) * 2;
-          umma_f16(tmem_base + C::kColDp + u * 64, a, bd, idesc_s, k != 0);
+          for (int k = 0; k < 8; ++k)
+            umma_f16(cd, dV + (((k >> 2) * 16384) >> 4) + (k & 3) * 2,
+                     q + kDoOff + (((k >> 2) * 8192) >> 4) + (k & 3) * 2, idesc_s, k != 0);
+          tc_commit(&s_full[u]);
         }
-        tc_commit(&s_full[u]);
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -146,49 +151,53 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         const int st = it % C::kRing, u = it & 1;
         if (it + 1 < N) ok = issue_s(it + 1);
         if (!ok) break;
-        if (!mbar_wait(&p_ready[u], (it >> 1) & 1)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(&p_ready[u], (it >> 1) & 1))) { ok = false; break; }
         tc_fence_after();
-        const uint32_t sQ = sRing + st * C::kStageBytes, sDo = sQ + C::kQBlk;
+        const uint64_t q = dRmn + static_cast<uint64_t>(st * (C::kStageBytes >> 4));
+        // A = P^T / dS^T from TMEM, left by the softmax halves at the start of their own columns
+        const uint32_t cp = tmem_base + C::kColS + u * 64, cd = tmem_base + C::kColDp + u * 64;
+        if (elect_one()) {
+          umma_f16_ts(tmem_base + C::kColDv, cp, q + kDoOff, idesc_acc, it != 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint64_t a = umma_desc_k_sw128(sP + u * 16384) + k * 2;
-          const uint64_t bd = umma_desc_mn_sw128(sDo, 8192) + k * (2048 >> 4);
-          umma_f16(tmem_base + C::kColDv, a, bd, idesc_acc, (it | k) != 0);
-        }
+          for (int k = 1; k < 4; ++k)
+            umma_f16_ts(tmem_base + C::kColDv, cp + (k >> 1) * 32 + (k & 1) * 8, q + kDoOff + k * (2048 >> 4),
+                        idesc_acc, 1);
+          umma_f16_ts(tmem_base + C::kColDk, cd, q, idesc_acc, it != 0);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint64_t a = umma_desc_k_sw128(sP + (2 + u) * 16384) + k * 2;
-          const uint64_t bd = umma_desc_mn_sw128(sQ, 8192) + k * (2048 >> 4);
-          umma_f16(tmem_base + C::kColDk, a, bd, idesc_acc, (it | k) != 0);
+          for (int k = 1; k < 4; ++k)
+            umma_f16_ts(tmem_base + C::kColDk, cd + (k >> 1) * 32 + (k & 1) * 8, q + k * (2048 >> 4), idesc_acc, 1);
+          tc_commit(&pd_done[u]);
+          tc_commit(&r_empty[st]);
         }
-        tc_commit(&pd_done[u]);
-        tc_commit(&r_empty[st]);
+        __syncwarp();
       }
-      if (ok) tc_commit(acc_done);
-      else atomicCAS(p.status, 0, kFlashTimeoutMma);
+      if (ok) {
+        if (elect_one()) tc_commit(acc_done);
+      } else if (lane == 0) {
+        atomicCAS(p.status, 0, kFlashTimeoutMma);
+      }
     }
   } else {
     // ------------------------------------------------------------------ softmax / dS warps
-    const int u = (warp - 2) >> 2;       // group u takes iterations it with it % 2 == u
+    const int u = (warp - 2) >> 3;       // group u takes iterations it with it % 2 == u
+    const int half = ((warp - 2) & 7) >> 2;  // which 32 query columns / which 64 output columns
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;
     const int kv_row = kv0 + r;
     const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
-    uint8_t* sPt = smem + C::kOffP + u * 16384;
-    uint8_t* sDst = smem + C::kOffP + (2 + u) * 16384;
     bool ok = true;
     for (int it = u; it < N; it += 2) {
       const int st = it % C::kRing;
       const int qr = (i_start + it % ni) * 64;
       if (!mbar_wait(&s_full[u], (it >> 1) & 1)) { ok = false; break; }
+      __syncwarp();
       tc_fence_after();
       const float* vec = reinterpret_cast<const float*>(smem + C::kOffRing + st * C::kStageBytes + 2 * C::kQBlk);
       const bool need_mask = (kv0 + 128 > p.sk) || (qr + 64 > p.sq) || (p.causal && kv0 + 127 > qr + p.causal_off);
       // key kv_row is visible to query q iff q >= q_min (and the key exists)
       const int q_min = kv_row < p.sk ? (p.causal ? kv_row - p.causal_off : 0) : 0x7fffffff;
-      uint32_t wp[32], wd[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      uint32_t wp[16], wd[16];
+      {
         uint32_t s[32], dp[32];
         tmem_ld_32x32(lane_base + C::kColS + u * 64 + half * 32, s);
         tmem_ld_32x32(lane_base + C::kColDp + u * 64 + half * 32, dp);
@@ -213,18 +222,19 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             pv[e] = x;
             dv[e] = y;
           }
-          wp[half * 16 + c / 2] = p.is_bf16 ? pack_bf16x2(pv[0], pv[1]) : pack_f16x2(pv[0], pv[1]);
-          wp[half * 16 + c / 2 + 1] = p.is_bf16 ? pack_bf16x2(pv[2], pv[3]) : pack_f16x2(pv[2], pv[3]);
-          wd[half * 16 + c / 2] = p.is_bf16 ? pack_bf16x2(dv[0], dv[1]) : pack_f16x2(dv[0], dv[1]);
-          wd[half * 16 + c / 2 + 1] = p.is_bf16 ? pack_bf16x2(dv[2], dv[3]) : pack_f16x2(dv[2], dv[3]);
+          wp[c / 2] = pack16<BF>(pv[0], pv[1]);
+          wp[c / 2 + 1] = pack16<BF>(pv[2], pv[3]);
+          wd[c / 2] = pack16<BF>(dv[0], dv[1]);
+          wd[c / 2 + 1] = pack16<BF>(dv[2], dv[3]);
         }
       }
       if (it >= 2) {
         if (!mbar_wait(&pd_done[u], ((it >> 1) - 1) & 1)) { ok = false; break; }
       }
-      store_row_sw128(sPt, r, wp);
-      store_row_sw128(sDst, r, wd);
-      fence_proxy_async_smem();
+      // P^T and dS^T return through TMEM over the columns this thread has just read
+      tmem_st_32x16(lane_base + C::kColS + u * 64 + half * 32, wp);
+      tmem_st_32x16(lane_base + C::kColDp + u * 64 + half * 32, wd);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[u]);
@@ -243,11 +253,11 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (ok) {
       const bool row_ok = kv_row < p.sk;
       uint16_t* orow = reinterpret_cast<uint16_t*>(u == 0 ? p.out : p.out2) + b * p.o_sb + hk * p.o_sh +
-                       static_cast<long long>(kv_row) * p.o_ss;
+                       static_cast<long long>(kv_row) * p.o_ss + half * 64;
       const float mul = u == 0 ? p.scale : 1.f;
-      const uint32_t col0 = u == 0 ? C::kColDk : C::kColDv;
+      const uint32_t col0 = (u == 0 ? C::kColDk : C::kColDv) + half * 64;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t o[32];
         if (N > 0) {
           tmem_ld_32x32(lane_base + col0 + c0, o);
@@ -261,10 +271,8 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           for (int c = 0; c < 32; c += 8) {
             uint32_t q4[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float x0 = __uint_as_float(o[c + 2 * i]) * mul, x1 = __uint_as_float(o[c + 2 * i + 1]) * mul;
-              q4[i] = p.is_bf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-            }
+            for (int i = 0; i < 4; ++i)
+              q4[i] = pack16<BF>(__uint_as_float(o[c + 2 * i]) * mul, __uint_as_float(o[c + 2 * i + 1]) * mul);
             *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(q4[0], q4[1], q4[2], q4[3]);
           }
         }
@@ -341,12 +349,15 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
   p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_kvouter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(flash_kvouter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(flash_kvouter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
   dim3 grid((a.sk + 127) / 128, a.hk, a.b);
-  flash_kvouter_kernel<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  if (bf) flash_kvouter_kernel<true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else flash_kvouter_kernel<false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 

@@ -1,58 +1,74 @@
 // Fused attention, query-stationary kernels: the forward pass and the dQ pass of the backward.
 //
 // One CTA owns 256 query rows of one head (two 128-row tiles) and walks the key/value sequence
-// in blocks of 64.  Per block and tile:
+// in blocks.  Per block and tile:
 //   forward : S = Q K^T            -> softmax warps: P = exp2(S*c - m), row sums, lazy rescale
 //             O += P V                of the TMEM accumulator when the row max moved by > 8
 //   dQ pass : S = Q K^T, dP = dO V^T -> dS = P * (dP - delta)   (P rebuilt from the saved LSE)
 //             dQ += dS K
-// K and V blocks arrive through separate TMA rings; a V block doubles as the MN-major B
-// operand of P V, a K block as the MN-major B operand of dS K, so nothing is transposed.
+// Warp roles: warp 0 feeds K/V blocks through TMA rings, warp 1 issues tcgen05.mma, and each
+// tile has eight softmax warps (two per TMEM lane quarter, each taking 32 of the 64 columns).
+// The forward walks keys 128 at a time (one tcgen05.mma costs about 60 cycles whatever its N, so
+// N = 128 doubles the score product's rate), the dQ pass 64 at a time (TMEM holds S, dP and dQ of
+// both tiles).  P (and dS) return to the tensor core through TMEM as the A
+// operand: each softmax thread overwrites the start of the score columns it has just read.  A V
+// block doubles as the MN-major B operand of P V, a K block as the MN-major B operand of dS K,
+// so nothing is transposed and shared memory holds only Q, dO and the K/V rings.
 // (Reference behaviour: common/fused_attn/fused_attn_f16_arbitrary_seqlen.cu, cuDNN graphs.)
 #include "flash_common.cuh"
+#include "flash_qouter_softmax.cuh"
 
 namespace teb200 {
 namespace attn {
 
 enum { kFwd = 0, kDq = 1 };
 
-template <int MODE>
-struct QCfg {
-  static constexpr int kKvStages = MODE == kFwd ? 3 : 2;
-  static constexpr int kQBytes = 2 * 32768;                       // two Q tiles
-  static constexpr int kDoBytes = MODE == kFwd ? 0 : 2 * 32768;   // two dO tiles
-  static constexpr int kPBytes = 2 * 16384;                       // P (or dS) tiles
-  static constexpr int kKvBytes = 16384;                          // one K or V block
-  static constexpr int kOffDo = kQBytes;
-  static constexpr int kOffP = kOffDo + kDoBytes;
-  static constexpr int kOffK = kOffP + kPBytes;
-  static constexpr int kOffV = kOffK + kKvStages * kKvBytes;
-  static constexpr int kOffBar = kOffV + kKvStages * kKvBytes;
-  static constexpr int kNumBars = 1 + 4 * kKvStages + 6;
-  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
-  // TMEM columns
-  static constexpr int kColS = 0;                              // + t * 64
-  static constexpr int kColDp = 128;                           // + t * 64 (dQ pass)
-  static constexpr int kColO = MODE == kFwd ? 128 : 256;       // + t * 128
+template <int V>
+struct IC {
+  static constexpr int value = V;
 };
 
-__device__ __forceinline__ int kv_blocks_of_tile(const FlashParams& p, int row0) {
+template <int MODE>
+struct QCfg {
+  static constexpr int kBlockKv = MODE == kFwd ? 128 : 64;        // keys per step (MMA N of the score product)
+  static constexpr int kKvStages = MODE == kFwd ? 2 : 3;
+  static constexpr int kSBufs = 1;                                // score accumulators per tile
+  static constexpr int kQBytes = 2 * 32768;                       // two Q tiles
+  static constexpr int kDoBytes = MODE == kFwd ? 0 : 2 * 32768;   // two dO tiles
+  static constexpr int kKvBytes = kBlockKv * 256;                 // one K or V block
+  static constexpr int kPanel = kBlockKv * 128;                   // one 64-column panel of it
+  static constexpr int kOffDo = kQBytes;
+  static constexpr int kOffK = kOffDo + kDoBytes;
+  static constexpr int kOffV = kOffK + kKvStages * kKvBytes;
+  static constexpr int kOffBar = kOffV + kKvStages * kKvBytes;
+  static constexpr int kNumBars = 1 + 4 * kKvStages + 8;
+  static constexpr int kOffXchg = kOffBar + kNumBars * 8 + 24;    // row max / row sum exchange
+  static constexpr int kXchgBytes = MODE == kFwd ? 2 * 2 * 2 * 128 * 8 : 0;
+  static constexpr int kSmemBytes = kOffXchg + kXchgBytes + 1024;
+  // TMEM columns
+  static constexpr int kColS = 0;                              // + t * kBlockKv
+  static constexpr int kColDp = 128;                           // + t * 64 (dQ pass)
+  static constexpr int kColO = 256;                            // + t * 128
+};
+
+__device__ __forceinline__ int kv_blocks_of_tile(const FlashParams& p, int row0, int bk) {
   if (row0 >= p.sq) return 0;
   int kv_end = p.sk;
   if (p.causal) {
     const int lim = row0 + 128 + p.causal_off;  // exclusive bound for the tile's last row
     kv_end = lim < kv_end ? lim : kv_end;
   }
-  return kv_end <= 0 ? 0 : (kv_end + 63) / 64;
+  return kv_end <= 0 ? 0 : (kv_end + bk - 1) / bk;
 }
 
-template <int MODE>
+template <int MODE, bool BF>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                     const FlashParams p) {
   using C = QCfg<MODE>;
   constexpr int KS = C::kKvStages;
+  constexpr int SB = C::kSBufs;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
@@ -61,21 +77,25 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint64_t* k_empty = k_full + KS;
   uint64_t* v_full = k_empty + KS;
   uint64_t* v_empty = v_full + KS;
-  uint64_t* s_full = v_empty + KS;   // [2]
-  uint64_t* p_ready = s_full + 2;    // [2]
+  uint64_t* s_full = v_empty + KS;   // [2 tiles][2 buffers]
+  uint64_t* p_ready = s_full + 4;    // [2]
   uint64_t* pv_done = p_ready + 2;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  unsigned long long* xchg = reinterpret_cast<unsigned long long*>(smem + C::kOffXchg);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int qb = gridDim.x - 1 - blockIdx.x;  // longest causal rows first
-  const int h = blockIdx.y;
-  const int b = blockIdx.z;
+  // heaviest query blocks of every head first
+  const int nqb = (p.sq + 255) / 256;
+  const int qb = nqb - 1 - static_cast<int>(blockIdx.x) / p.hq;
+  const int h = static_cast<int>(blockIdx.x) % p.hq;
+  const int b = blockIdx.y;
   const int hk = h / (p.hq / p.hk);
   const int q0 = qb * 256;
   int n[2];
-  n[0] = kv_blocks_of_tile(p, q0);
-  n[1] = kv_blocks_of_tile(p, q0 + 128);
+  constexpr int BK = C::kBlockKv;
+  n[0] = kv_blocks_of_tile(p, q0, BK);
+  n[1] = kv_blocks_of_tile(p, q0 + 128, BK);
   const int nmax = n[0] > n[1] ? n[0] : n[1];
 
   if (threadIdx.x == 0) {
@@ -90,13 +110,15 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
+    for (int i = 0; i < 4; ++i) mbar_init(&s_full[i], 1);
     for (int t = 0; t < 2; ++t) {
-      mbar_init(&s_full[t], 1);
-      mbar_init(&p_ready[t], 4);
+      mbar_init(&p_ready[t], 8);
       mbar_init(&pv_done[t], 1);
     }
     mbar_fence_init();
   }
+  if (MODE == kFwd)
+    for (int i = threadIdx.x; i < C::kXchgBytes / 8; i += kThreads) xchg[i] = 0ull;  // tag 0 = nothing published
   if (warp == 1) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -122,230 +144,107 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!mbar_wait(&k_empty[st], par)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         mbar_expect_tx(&k_full[st], C::kKvBytes);
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(smem + C::kOffK + st * C::kKvBytes + pn * 8192, &tmap_k, &k_full[st], pn * 64, j * 64, hk, b);
+          tma_load_4d(smem + C::kOffK + st * C::kKvBytes + pn * C::kPanel, &tmap_k, &k_full[st], pn * 64, j * BK, hk, b);
         if (!mbar_wait(&v_empty[st], par)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         mbar_expect_tx(&v_full[st], C::kKvBytes);
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(smem + C::kOffV + st * C::kKvBytes + pn * 8192, &tmap_v, &v_full[st], pn * 64, j * 64, hk, b);
+          tma_load_4d(smem + C::kOffV + st * C::kKvBytes + pn * C::kPanel, &tmap_v, &v_full[st], pn * 64, j * BK, hk, b);
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ tcgen05 issuer
-    if (lane == 0 && nmax > 0) {
-      const bool bf = p.is_bf16 != 0;
-      const uint32_t idesc_s = attn_idesc(bf, 64, false, false);
-      const uint32_t idesc_o = attn_idesc(bf, 128, false, true);
-      const uint32_t sQ = smem_u32(smem), sDo = smem_u32(smem + C::kOffDo), sP = smem_u32(smem + C::kOffP);
-      const uint32_t sK = smem_u32(smem + C::kOffK), sV = smem_u32(smem + C::kOffV);
-      bool ok = mbar_wait(q_full, 0);
-      if (!ok) atomicCAS(p.status, 0, kFlashTimeoutMma);
-      // S (and dP) of block j for tile t
-      auto issue_s = [&](int t, int j) -> bool {
+    // One thread issues every MMA, so its instruction stream is the pipeline's clock: all
+    // descriptors are precomputed (low words in registers, tile and step offsets folded at
+    // compile time).  The whole warp walks the loop so that every value stays warp-uniform (the
+    // descriptors live in uniform registers); one elected lane issues the tcgen05 instructions.
+    if (nmax > 0) {
+      constexpr uint32_t idesc_s = attn_idesc(BF, BK, false, false);
+      constexpr uint32_t idesc_o = attn_idesc(BF, 128, false, true);
+      const uint64_t dQ = umma_desc_k_sw128(smem_u32(smem));
+      const uint64_t dDo = umma_desc_k_sw128(smem_u32(smem + C::kOffDo));
+      const uint64_t dK = umma_desc_k_sw128(smem_u32(smem + C::kOffK));
+      const uint64_t dVk = umma_desc_k_sw128(smem_u32(smem + C::kOffV));
+      const uint64_t dBmn = umma_desc_mn_sw128(smem_u32(smem + (MODE == kFwd ? C::kOffV : C::kOffK)), C::kPanel);
+      bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0));
+      // S (and dP) of block j for tile T
+      auto issue_s = [&](auto tc, int j) -> bool {
+        constexpr int T = decltype(tc)::value;
         const int st = j % KS;
         const uint32_t par = (j / KS) & 1;
-        if (!mbar_wait(&k_full[st], par)) return false;
-        if (MODE == kDq && !mbar_wait(&v_full[st], par)) return false;
+        const int buf = j % SB;
+        bool w = mbar_wait(&k_full[st], par);
+        if (MODE == kDq) w = w && mbar_wait(&v_full[st], par);
+        if (!__all_sync(0xffffffffu, w)) return false;
         tc_fence_after();
+        const bool stamp = p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && T == 0 && j >= SB && j - SB < 64 && lane == 0;
+        if (stamp) p.timeline[(j - SB) * 16 + 10] = clock64();
+        const uint32_t col_s = tmem_base + C::kColS + T * BK;
+        const uint64_t kst = dK + static_cast<uint64_t>(st * (C::kKvBytes >> 4));
+        const uint64_t vst = dVk + static_cast<uint64_t>(st * (C::kKvBytes >> 4));
+        const bool last = T == 1 || j >= n[1];
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint64_t a = umma_desc_k_sw128(sQ + t * 32768 + (k >> 2) * 16384) + (k & 3) * 2;
-          const uint64_t bd = umma_desc_k_sw128(sK + st * C::kKvBytes + (k >> 2) * 8192) + (k & 3) * 2;
-          umma_f16(tmem_base + C::kColS + t * 64, a, bd, idesc_s, k != 0);
-        }
-        if (MODE == kDq) {
+          for (int k = 0; k < 8; ++k)
+            umma_f16(col_s, dQ + ((T * 32768 + (k >> 2) * 16384) >> 4) + (k & 3) * 2,
+                     kst + (((k >> 2) * C::kPanel) >> 4) + (k & 3) * 2, idesc_s, k != 0);
+          if (MODE == kDq) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint64_t a = umma_desc_k_sw128(sDo + t * 32768 + (k >> 2) * 16384) + (k & 3) * 2;
-            const uint64_t bd = umma_desc_k_sw128(sV + st * C::kKvBytes + (k >> 2) * 8192) + (k & 3) * 2;
-            umma_f16(tmem_base + C::kColDp + t * 64, a, bd, idesc_s, k != 0);
+            for (int k = 0; k < 8; ++k)
+              umma_f16(tmem_base + C::kColDp + T * 64, dDo + ((T * 32768 + (k >> 2) * 16384) >> 4) + (k & 3) * 2,
+                       vst + (((k >> 2) * C::kPanel) >> 4) + (k & 3) * 2, idesc_s, k != 0);
           }
-        }
-        tc_commit(&s_full[t]);
-        const bool last = (t == 1) || (j >= n[1]);
-        if (last) {
+          tc_commit(&s_full[T * 2 + buf]);
           // forward: the K block is done; dQ pass: the V block is done (K is still needed by dS K)
-          if (MODE == kFwd) tc_commit(&k_empty[st]);
-          else tc_commit(&v_empty[st]);
+          if (last) tc_commit(MODE == kFwd ? &k_empty[st] : &v_empty[st]);
         }
+        __syncwarp();
+        if (stamp) p.timeline[(j - SB) * 16 + 11] = clock64();
         return true;
       };
-      for (int t = 0; ok && t < 2; ++t)
-        if (n[t] > 0) ok = issue_s(t, 0);
-      if (!ok) atomicCAS(p.status, 0, kFlashTimeoutMma);
-      for (int j = 0; ok && j < nmax; ++j) {
+      // O += P V (dQ += dS K) of block j for tile T, then the next score block into the freed buffer
+      auto step = [&](auto tc, int j) -> bool {
+        constexpr int T = decltype(tc)::value;
         const int st = j % KS;
-        const uint32_t par = (j / KS) & 1;
-        for (int t = 0; ok && t < 2; ++t) {
-          if (j >= n[t]) continue;
-          if (!mbar_wait(&p_ready[t], j & 1)) { ok = false; break; }
-          if (MODE == kFwd && !mbar_wait(&v_full[st], par)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sB = (MODE == kFwd ? sV : sK) + st * C::kKvBytes;
+        bool w = mbar_wait(&p_ready[T], j & 1);
+        if (MODE == kFwd) w = w && mbar_wait(&v_full[st], (j / KS) & 1);
+        if (!__all_sync(0xffffffffu, w)) return false;
+        tc_fence_after();
+        const bool stamp = p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && T == 0 && j < 64 && lane == 0;
+        if (stamp) p.timeline[j * 16 + 6] = clock64();
+        const uint64_t bst = dBmn + static_cast<uint64_t>(st * (C::kKvBytes >> 4));
+        // A = P (or dS) from TMEM: each softmax half left its BK/2 keys as BK/4 packed columns at
+        // the start of its own BK/2 score columns; one step takes 16 keys = 8 columns
+        const uint32_t col_p = tmem_base + C::kColS + T * BK;
+        const uint32_t col_o = tmem_base + C::kColO + T * 128;
+        const bool last = T == 1 || j >= n[1];
+        if (elect_one()) {
+          umma_f16_ts(col_o, col_p, bst, idesc_o, j != 0);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t a = umma_desc_k_sw128(sP + t * 16384) + k * 2;
-            const uint64_t bd = umma_desc_mn_sw128(sB, 8192) + k * (2048 >> 4);
-            umma_f16(tmem_base + C::kColO + t * 128, a, bd, idesc_o, (j | k) != 0);
-          }
-          tc_commit(&pv_done[t]);
-          const bool last = (t == 1) || (j >= n[1]);
-          if (last) {
-            if (MODE == kFwd) tc_commit(&v_empty[st]);
-            else tc_commit(&k_empty[st]);
-          }
-          if (j + 1 < n[t]) ok = issue_s(t, j + 1);
+          for (int k = 1; k < BK / 16; ++k)
+            umma_f16_ts(col_o, col_p + (k / (BK / 32)) * (BK / 2) + (k % (BK / 32)) * 8, bst + k * (2048 >> 4), idesc_o, 1);
+          tc_commit(&pv_done[T]);
+          if (last) tc_commit(MODE == kFwd ? &v_empty[st] : &k_empty[st]);
         }
-        if (!ok) atomicCAS(p.status, 0, kFlashTimeoutMma);
+        __syncwarp();
+        if (stamp) p.timeline[j * 16 + 9] = clock64();
+        bool r = true;
+        if (j + SB < n[T]) r = issue_s(tc, j + SB);
+        if (stamp) p.timeline[j * 16 + 7] = clock64();
+        return r;
+      };
+      for (int jj = 0; ok && jj < SB; ++jj) {
+        if (ok && jj < n[0]) ok = issue_s(IC<0>{}, jj);
+        if (ok && jj < n[1]) ok = issue_s(IC<1>{}, jj);
       }
+      for (int j = 0; ok && j < nmax; ++j) {
+        if (j < n[0]) ok = step(IC<0>{}, j);
+        if (ok && j < n[1]) ok = step(IC<1>{}, j);
+      }
+      if (!ok && lane == 0) atomicCAS(p.status, 0, kFlashTimeoutMma);
     }
   } else {
-    // ------------------------------------------------------------------ softmax / dS warps
-    const int t = (warp - 2) >> 2;
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;       // row inside the tile
-    const int q_row = q0 + t * 128 + r;
-    const uint32_t lane_base = tmem_base + (uint32_t(quarter * 32) << 16);
-    uint8_t* sP = smem + C::kOffP + t * 16384;
-    const int nt = n[t];
-    const float NEG_INF = -INFINITY;
-    bool ok = true;
-    float m_run = NEG_INF, l_run = 0.f;
-    float lse2 = INFINITY, delta = 0.f;
-    if (MODE == kDq && q_row < p.sq) {
-      const size_t off = (static_cast<size_t>(b) * p.hq + h) * p.s_pad + q_row;
-      lse2 = p.lse[off] * 1.4426950408889634f;
-      delta = p.delta[off];
-    }
-    for (int j = 0; j < nt; ++j) {
-      if (!mbar_wait(&s_full[t], j & 1)) { ok = false; break; }
-      tc_fence_after();
-      const int kv0 = j * 64;
-      const bool need_mask = (kv0 + 64 > p.sk) || (p.causal && kv0 + 63 > q0 + t * 128 + p.causal_off);
-      const int lim = p.causal ? min(p.sk - 1, q_row + p.causal_off) : p.sk - 1;  // last visible key
-      uint32_t w[32];
-      if (MODE == kFwd) {
-        uint32_t s0[32], s1[32];
-        tmem_ld_32x32(lane_base + C::kColS + t * 64, s0);
-        tmem_ld_32x32(lane_base + C::kColS + t * 64 + 32, s1);
-        tmem_ld_wait();
-        if (need_mask) {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            if (kv0 + c > lim) s0[c] = __float_as_uint(NEG_INF);
-            if (kv0 + 32 + c > lim) s1[c] = __float_as_uint(NEG_INF);
-          }
-        }
-        float mx = NEG_INF;
-#pragma unroll
-        for (int c = 0; c < 32; ++c) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[c]), __uint_as_float(s1[c])));
-        const float m_new = fmaxf(m_run, mx * p.scale_log2);
-        const bool first = m_run == NEG_INF;
-        const float m_use = (!first && m_new - m_run <= 8.f) ? m_run : m_new;
-        const float m_eff = m_use == NEG_INF ? 0.f : m_use;
-        const float alpha = first ? 1.f : fast_exp2(m_run - m_use);
-        float sum = 0.f;
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float a0 = fast_exp2(fmaf(__uint_as_float(s0[c]), p.scale_log2, -m_eff));
-          const float a1 = fast_exp2(fmaf(__uint_as_float(s0[c + 1]), p.scale_log2, -m_eff));
-          const float b0 = fast_exp2(fmaf(__uint_as_float(s1[c]), p.scale_log2, -m_eff));
-          const float b1 = fast_exp2(fmaf(__uint_as_float(s1[c + 1]), p.scale_log2, -m_eff));
-          sum += (a0 + a1) + (b0 + b1);
-          w[c / 2] = p.is_bf16 ? pack_bf16x2(a0, a1) : pack_f16x2(a0, a1);
-          w[16 + c / 2] = p.is_bf16 ? pack_bf16x2(b0, b1) : pack_f16x2(b0, b1);
-        }
-        l_run = l_run * alpha + sum;
-        m_run = m_use;
-        if (j > 0) {
-          if (!mbar_wait(&pv_done[t], (j - 1) & 1)) { ok = false; break; }
-          tc_fence_after();
-          if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < 128; c0 += 32) {
-              uint32_t o[32];
-              tmem_ld_32x32(lane_base + C::kColO + t * 128 + c0, o);
-              tmem_ld_wait();
-#pragma unroll
-              for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-              tmem_st_32x32(lane_base + C::kColO + t * 128 + c0, o);
-            }
-            tmem_st_wait();
-          }
-        }
-      } else {
-        // dS = P * (dP - delta), P rebuilt from the saved log-sum-exp
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t s[32], dp[32];
-          tmem_ld_32x32(lane_base + C::kColS + t * 64 + half * 32, s);
-          tmem_ld_32x32(lane_base + C::kColDp + t * 64 + half * 32, dp);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float p0 = fast_exp2(fmaf(__uint_as_float(s[c]), p.scale_log2, -lse2));
-            float p1 = fast_exp2(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -lse2));
-            if (need_mask) {
-              if (kv0 + half * 32 + c > lim) p0 = 0.f;
-              if (kv0 + half * 32 + c + 1 > lim) p1 = 0.f;
-            }
-            const float d0 = p0 * (__uint_as_float(dp[c]) - delta);
-            const float d1 = p1 * (__uint_as_float(dp[c + 1]) - delta);
-            w[half * 16 + c / 2] = p.is_bf16 ? pack_bf16x2(d0, d1) : pack_f16x2(d0, d1);
-          }
-        }
-        if (j > 0) {
-          if (!mbar_wait(&pv_done[t], (j - 1) & 1)) { ok = false; break; }
-        }
-      }
-      store_row_sw128(sP, r, w);
-      fence_proxy_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_ready[t]);
-    }
-    if (!ok && lane == 0) atomicCAS(p.status, 0, kFlashTimeoutSoftmax);
-    // ---------------------------------------------------------------- epilogue
-    if (ok && nt > 0) {
-      if (!mbar_wait(&pv_done[t], (nt - 1) & 1)) {
-        ok = false;
-        if (lane == 0) atomicCAS(p.status, 0, kFlashTimeoutSoftmax);
-      }
-      tc_fence_after();
-    }
-    // TMEM loads are warp-wide: every lane takes part, only the stores depend on the row
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
-      const bool row_ok = q_row < p.sq;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.out) + b * p.o_sb + h * p.o_sh + static_cast<long long>(q_row) * p.o_ss;
-      const float mul = MODE == kFwd ? (l_run > 0.f ? 1.f / l_run : 0.f) : p.scale;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
-        uint32_t o[32];
-        if (nt > 0) {
-          tmem_ld_32x32(lane_base + C::kColO + t * 128 + c0, o);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int c = 0; c < 32; ++c) o[c] = 0u;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int c = 0; c < 32; c += 8) {
-            uint32_t q4[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float x0 = __uint_as_float(o[c + 2 * i]) * mul, x1 = __uint_as_float(o[c + 2 * i + 1]) * mul;
-              q4[i] = p.is_bf16 ? pack_bf16x2(x0, x1) : pack_f16x2(x0, x1);
-            }
-            *reinterpret_cast<uint4*>(orow + c0 + c) = make_uint4(q4[0], q4[1], q4[2], q4[3]);
-          }
-        }
-      }
-      if (MODE == kFwd && row_ok) {
-        const size_t off = (static_cast<size_t>(b) * p.hq + h) * p.s_pad + q_row;
-        p.lse[off] = l_run > 0.f ? m_run * 0.6931471805599453f + logf(l_run) : NEG_INF;
-      }
-    }
+    const int t = (warp - 2) >> 3;
+    qouter_softmax_role<MODE, BF, C>(p, smem, s_full, p_ready, pv_done, xchg, tmem_base, warp, lane, q0, h, b, n[t], t);
   }
 
   tc_fence_before();
@@ -391,8 +290,8 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
   CUtensorMap tq, tk, tv, tdo;
   const bool bf = a.is_bf16;
   bool ok = make_tensor_map_bhsd(&tq, a.q, bf, a.b, a.hq, a.sq, a.q_sb, a.q_sh, a.q_ss, 128) &&
-            make_tensor_map_bhsd(&tk, a.k, bf, a.b, a.hk, a.sk, a.k_sb, a.k_sh, a.k_ss, 64) &&
-            make_tensor_map_bhsd(&tv, a.v, bf, a.b, a.hk, a.sk, a.v_sb, a.v_sh, a.v_ss, 64);
+            make_tensor_map_bhsd(&tk, a.k, bf, a.b, a.hk, a.sk, a.k_sb, a.k_sh, a.k_ss, C::kBlockKv) &&
+            make_tensor_map_bhsd(&tv, a.v, bf, a.b, a.hk, a.sk, a.v_sb, a.v_sh, a.v_ss, C::kBlockKv);
   if (MODE == kDq) ok = ok && make_tensor_map_bhsd(&tdo, a.dout, bf, a.b, a.hq, a.sq, a.do_sb, a.do_sh, a.do_ss, 128);
   else tdo = tq;
   if (!ok) return cudaErrorInvalidValue;
@@ -406,16 +305,20 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
   if (MODE == kFwd) { p.out = a.out; p.o_sb = a.o_sb; p.o_sh = a.o_sh; p.o_ss = a.o_ss; }
   else { p.out = a.dq; p.o_sb = a.dq_sb; p.o_sh = a.dq_sh; p.o_ss = a.dq_ss; }
   if ((reinterpret_cast<uintptr_t>(p.out) & 15) || p.o_sb % 8 || p.o_sh % 8 || p.o_ss % 8) return cudaErrorInvalidValue;
-  p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status;
+  p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status; p.timeline = a.timeline;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_qouter_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(flash_qouter_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(flash_qouter_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               C::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  dim3 grid((a.sq + 255) / 256, a.hq, a.b);
-  flash_qouter_kernel<MODE><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  dim3 grid(((a.sq + 255) / 256) * a.hq, a.b);
+  if (bf) flash_qouter_kernel<MODE, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else flash_qouter_kernel<MODE, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 

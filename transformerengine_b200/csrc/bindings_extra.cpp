@@ -120,9 +120,14 @@ teb200::FlashArgs flash_args(const at::Tensor& q, const at::Tensor& k, const at:
 }
 
 void flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
-               const at::Tensor& lse, double scale, bool causal, bool bottom_right, const at::Tensor& status) {
+               const at::Tensor& lse, double scale, bool causal, bool bottom_right, const at::Tensor& status,
+               const OptT& timeline) {
   c10::cuda::CUDAGuard guard(q.device());
   teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  if (timeline.has_value() && timeline->defined()) {
+    TORCH_CHECK(timeline->scalar_type() == at::kLong && timeline->numel() >= 1024, "timeline must be int64 [64, 16]");
+    a.timeline = reinterpret_cast<long long*>(timeline->data_ptr());
+  }
   cudaError_t e = teb200::flash_fwd(a, cur_stream());
   TORCH_CHECK(e == cudaSuccess, "flash_fwd failed: ", cudaGetErrorString(e));
 }
@@ -152,7 +157,9 @@ void flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
 
 void register_extra(py::module_& m) {
   m.def("comm_gemm", &comm_gemm);
-  m.def("flash_fwd", &flash_fwd);
+  m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
+        py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
+        py::arg("timeline") = py::none());
   m.def("flash_bwd", &flash_bwd);
 }
 

@@ -76,6 +76,7 @@ struct FlashArgs {
   long long o_sb = 0, o_sh = 0, o_ss = 0, do_sb = 0, do_sh = 0, do_ss = 0;
   long long dq_sb = 0, dq_sh = 0, dq_ss = 0, dk_sb = 0, dk_sh = 0, dk_ss = 0, dv_sb = 0, dv_sh = 0, dv_ss = 0;
   int* status = nullptr;
+  long long* timeline = nullptr;  // optional [64][16] clock stamps written by CTA 0 (profiling aid)
 };
 cudaError_t flash_fwd(const FlashArgs& args, cudaStream_t stream);
 cudaError_t flash_delta(const FlashArgs& args, cudaStream_t stream);     // delta = rowsum(dO * O)

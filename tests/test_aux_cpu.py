@@ -1,0 +1,108 @@
+"""Auxiliary subsystems on CPU: debug features, activation offload, parallel cross entropy,
+export mode, utilities."""
+import os
+
+import torch
+
+import transformerengine_b200 as te
+from transformerengine_b200 import debug
+from transformerengine_b200.cpu_offload import get_cpu_offload_context
+from transformerengine_b200.cross_entropy import parallel_cross_entropy
+from transformerengine_b200.debug import debug_api
+
+
+def test_debug_logging_and_disable(tmp_path):
+    torch.manual_seed(0)
+    lin = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu", name="decoder.fc")
+    other = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu", name="decoder.proj")
+    x = torch.randn(32, 64)
+    debug_api.initialize({
+        "stats": {"enabled": True, "layers": {"layer_name_regex_pattern": r".*\.fc$"},
+                  "features": {"LogTensorStats": {"tensors": ["activation"], "stats": ["max", "l2_norm"]},
+                               "LogFp8TensorStats": {"tensors": ["activation", "weight"], "stats": ["mse"]}}},
+        "off": {"enabled": True, "layers": {"layer_names": ["decoder.proj"]},
+                "features": {"DisableQuantizationLayer": {}}},
+    }, log_dir=str(tmp_path))
+    try:
+        with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+            y = lin(x)
+            z = other(x)
+        recs = debug_api.records()
+        stats = {(r["tensor"], r["stat"]) for r in recs}
+        assert ("activation", "max") in stats and ("weight", "mse") in stats
+        amax = [r["value"] for r in recs if r["stat"] == "max"][0]
+        assert abs(amax - x.max().item()) < 1e-6
+        # the disabled layer ran in full precision
+        assert torch.allclose(z, x @ other.weight.t(), atol=1e-5)
+        assert not torch.allclose(y, x @ lin.weight.t(), atol=1e-5)
+        debug_api.flush()
+        assert os.path.exists(tmp_path / "tensor_stats.jsonl")
+    finally:
+        debug_api.end_debug()
+    assert not debug.is_enabled()
+
+
+def test_cpu_offload_roundtrip():
+    torch.manual_seed(0)
+    layers = [torch.nn.Linear(512, 512) for _ in range(3)]
+    ctx, sync = get_cpu_offload_context(enabled=True, num_layers=2, model_layers=3)
+    x = torch.randn(256, 512, requires_grad=True)
+    h = x
+    for l in layers:
+        with ctx:
+            h = torch.tanh(l(h))
+        h = sync(h)
+    h.sum().backward()
+    assert ctx.handler.bytes_offloaded > 0 and not ctx.handler.store
+    ref = x.detach().clone().requires_grad_()
+    hr = ref
+    for l in layers:
+        hr = torch.tanh(l(hr))
+    hr.sum().backward()
+    assert torch.allclose(x.grad, ref.grad, atol=1e-6)
+
+
+def test_parallel_cross_entropy_single_rank():
+    torch.manual_seed(0)
+    logits = torch.randn(2, 5, 33, requires_grad=True)
+    tgt = torch.randint(0, 33, (2, 5))
+    tgt[0, 1] = -100
+    loss = parallel_cross_entropy(logits, tgt)
+    ref = torch.nn.functional.cross_entropy(logits.reshape(-1, 33), tgt.reshape(-1), reduction="none",
+                                            ignore_index=-100).reshape(2, 5)
+    assert torch.allclose(loss, ref, atol=1e-5)
+    loss.sum().backward()
+    g = torch.autograd.grad(ref.sum(), logits)[0]
+    assert torch.allclose(logits.grad, g, atol=1e-5)
+    red = parallel_cross_entropy(logits.detach(), tgt, reduce_loss=True)
+    assert torch.allclose(red, ref.sum() / 9, atol=1e-5)
+
+
+def test_export_mode_and_utils():
+    from transformerengine_b200.export import is_in_onnx_export_mode, onnx_export
+    from transformerengine_b200.newton_schulz import newton_schulz
+    from transformerengine_b200.utils import DeviceTimers, env_flag, nvtx_range
+
+    assert not is_in_onnx_export_mode()
+    with onnx_export(True):
+        assert is_in_onnx_export_mode()
+    with nvtx_range("x"):
+        pass
+    t = DeviceTimers()
+    with t("a"):
+        pass
+    assert isinstance(t.summary(), dict)
+    assert env_flag("TEB200_SURELY_UNSET", True)
+    g = torch.randn(16, 32)
+    o = newton_schulz(g, steps=8)
+    sv = torch.linalg.svdvals(o.float())
+    assert sv.max() < 1.3 and sv.min() > 0.5
+
+
+def test_quantize_master_weights_single_rank():
+    from transformerengine_b200.tensor.utils import quantize_master_weights
+
+    w = torch.nn.Parameter(torch.zeros(8, 4))
+    master = torch.arange(16, dtype=torch.float32)
+    quantize_master_weights([w], [master], [8])
+    assert torch.equal(w.detach().reshape(-1)[8:24], master) and w.detach().reshape(-1)[:8].abs().sum() == 0

@@ -21,6 +21,7 @@ from .modules.layernorm_mlp import LayerNormMLP
 from .attention.dot_product_attention import DotProductAttention
 from .attention.multi_head_attention import MultiheadAttention
 from .attention.rope import RotaryPositionEmbedding, apply_rotary_pos_emb
+from .attention.inference import InferenceParams, KVCacheManager, NonPagedKVCacheManager, PagedKVCacheManager
 from .transformer import TransformerLayer
 from .modules.grouped_linear import GroupedLinear, Fp8Padding, Fp8Unpadding
 from .moe import (fused_topk_with_score_function, fused_compute_score_for_moe_aux_loss, fused_moe_aux_loss,
@@ -31,5 +32,13 @@ from .parallel.distributed import checkpoint, CudaRNGStatesTracker
 from .optim import FusedAdam, FusedSGD
 from .parallel.comm_gemm import initialize_ub, destroy_ub
 from . import optim as optimizers  # noqa: F401
+from . import fusible  # noqa: F401  (operation fuser: fusible.Sequential and the basic operations)
+from . import debug  # noqa: F401
+from .graph import make_graphed_callables
+from .cpu_offload import get_cpu_offload_context
+from .export import onnx_export, is_in_onnx_export_mode
+from .cross_entropy import parallel_cross_entropy
+from .newton_schulz import newton_schulz
+from .parallel.context_parallel import get_batch_on_this_cp_rank, pad_thd_sequences_for_cp
 
 __version__ = "0.1.0"

@@ -101,8 +101,11 @@ class DotProductAttention(torch.nn.Module):
                                   core_attention_bias_type, core_attention_bias, alibi_slopes)
             return D.checkpoint(run, query_layer, key_layer, value_layer,
                                 get_rng_state_tracker=self.get_rng_state_tracker)
-        return self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
-                          cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes)
+        out = self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
+                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes)
+        if inference_params is not None:
+            out = inference_params.unpack_output(out)
+        return out
 
     def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes):
         if fmt == "thd":

@@ -1,0 +1,253 @@
+"""Numerics debugging: per-layer, per-tensor features that wrap a module's quantizers
+(reference: ``transformer_engine/debug/pytorch/debug_quantization.py:43,607``,
+``debug/features/api.py:21,102,399`` and the feature files next to it).
+
+Configuration is a dict (or a YAML file with the same content)::
+
+    debug_api.initialize({
+        "log_attention": {                      # any section name
+            "enabled": True,
+            "layers": {"layer_name_regex_pattern": ".*self_attention.*"},
+            "features": {
+                "LogTensorStats": {"tensors": ["activation", "weight"], "stats": ["min", "max", "l2_norm"]},
+                "LogFp8TensorStats": {"tensors": ["activation"], "stats": ["underflows%", "mse"]},
+                "FakeQuant": {"tensors": ["gradient"], "gemms": ["wgrad"]},
+                "DisableQuantizationGEMM": {"gemms": ["dgrad"]},
+                "DisableQuantizationLayer": {},
+                "DumpTensors": {"tensors": ["activation"], "dir": "dumps"},
+            },
+        }
+    }, log_dir="debug_logs")
+
+Tensor names: ``activation`` (forward input), ``weight``, ``output``, ``gradient`` (grad output),
+``dgrad`` (grad input).  A module takes part when it was built with ``name=...`` and a section's
+pattern matches the name.  ``debug_api.step()`` advances the iteration counter used in the logs.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from typing import Any, Dict, List, Optional
+
+import torch
+
+from ..tensor.base import QuantizedTensorStorage, Quantizer
+
+_FWD_SLOTS = ("activation", "weight", "output")
+_BWD_SLOTS = ("gradient", "dgrad")
+_GEMM_OF = {"activation": ("fprop", "wgrad"), "weight": ("fprop", "dgrad"), "output": ("fprop",),
+            "gradient": ("dgrad", "wgrad"), "dgrad": ("dgrad",)}
+
+
+def tensor_name_of_slot(fwd: bool, idx: int) -> str:
+    names = _FWD_SLOTS if fwd else _BWD_SLOTS
+    return names[idx % len(names)]
+
+
+def _stat(name: str, x: torch.Tensor) -> float:
+    xf = x.float()
+    if name == "min":
+        return xf.min().item()
+    if name == "max":
+        return xf.max().item()
+    if name == "mean":
+        return xf.mean().item()
+    if name == "std":
+        return xf.std().item()
+    if name == "l1_norm":
+        return xf.abs().sum().item()
+    if name == "l2_norm":
+        return xf.norm().item()
+    if name in ("cur_amax", "amax"):
+        return xf.abs().max().item()
+    if name == "dynamic_range":
+        a = xf.abs()
+        nz = a[a > 0]
+        return (torch.log2(a.max()) - torch.log2(nz.min())).item() if nz.numel() else 0.0
+    raise ValueError(f"unknown statistic {name}")
+
+
+def _quant_stat(name: str, x: torch.Tensor, q: QuantizedTensorStorage) -> float:
+    dq = q.dequantize().float()
+    xf = x.float()
+    if name == "underflows%":
+        return 100.0 * ((dq == 0) & (xf != 0)).float().mean().item()
+    if name == "overflows%":
+        return 100.0 * (dq.abs() < xf.abs() * 0.5).float().mean().item()
+    if name == "mse":
+        return (dq - xf).square().mean().item()
+    if name in ("scale_inv_min", "scale_inv_max"):
+        s = getattr(q, "_rowwise_scale_inv", None)
+        if s is None:
+            s = getattr(q, "_scale_inv", None)
+        if s is None:
+            return float("nan")
+        s = s.float() if s.dtype != torch.uint8 else torch.exp2(s.float() - 127.0)
+        return (s.min() if name.endswith("min") else s.max()).item()
+    raise ValueError(f"unknown quantized statistic {name}")
+
+
+class _DebugState:
+    def __init__(self):
+        self.enabled = False
+        self.sections: List[Dict[str, Any]] = []
+        self.log_dir: Optional[str] = None
+        self.iteration = 0
+        self.records: List[Dict[str, Any]] = []
+        self.reduction_group = None
+
+    def features_for(self, layer_name: Optional[str]) -> Dict[str, Dict[str, Any]]:
+        out: Dict[str, Dict[str, Any]] = {}
+        if not self.enabled or layer_name is None:
+            return out
+        for sec in self.sections:
+            if not sec.get("enabled", True):
+                continue
+            layers = sec.get("layers", {})
+            pat = layers.get("layer_name_regex_pattern")
+            names = layers.get("layer_names")
+            if (pat and re.search(pat, layer_name)) or (names and layer_name in names) or (not pat and not names):
+                out.update(sec.get("features", sec.get("transformer_engine", {})))
+        return out
+
+
+_STATE = _DebugState()
+
+
+class debug_api:  # noqa: N801  (namespace with the reference's spelling)
+    @staticmethod
+    def initialize(config=None, feature_dirs=None, log_dir: Optional[str] = None, default_logging_enabled=True):
+        if isinstance(config, str):
+            import yaml
+
+            with open(config) as f:
+                config = yaml.safe_load(f)
+        _STATE.sections = list((config or {}).values())
+        _STATE.enabled = True
+        _STATE.log_dir = log_dir
+        _STATE.iteration = 0
+        _STATE.records = []
+        if log_dir:
+            os.makedirs(log_dir, exist_ok=True)
+
+    @staticmethod
+    def step():
+        _STATE.iteration += 1
+
+    @staticmethod
+    def end_debug():
+        debug_api.flush()
+        _STATE.enabled = False
+        _STATE.sections = []
+
+    @staticmethod
+    def set_tensor_reduction_group(group):
+        _STATE.reduction_group = group
+
+    @staticmethod
+    def flush():
+        if _STATE.log_dir and _STATE.records:
+            with open(os.path.join(_STATE.log_dir, "tensor_stats.jsonl"), "a") as f:
+                for r in _STATE.records:
+                    f.write(json.dumps(r) + "\n")
+            _STATE.records = []
+
+    @staticmethod
+    def records() -> List[Dict[str, Any]]:
+        return _STATE.records
+
+
+def _wants(cfg: Dict[str, Any], tensor: str) -> bool:
+    t = cfg.get("tensors")
+    if t is not None and tensor not in t:
+        return False
+    g = cfg.get("gemms")
+    return g is None or any(x in g for x in _GEMM_OF[tensor])
+
+
+class DebugQuantizer(Quantizer):
+    """Wraps a module's quantizer and applies the configured debug features on every call."""
+
+    def __init__(self, parent: Optional[Quantizer], layer_name: str, tensor_name: str, features: Dict[str, Dict]):
+        super().__init__(rowwise=True, columnwise=True)
+        self.parent, self.layer_name, self.tensor_name, self.features = parent, layer_name, tensor_name, features
+        if parent is not None:
+            self.rowwise_usage, self.columnwise_usage = parent.rowwise_usage, parent.columnwise_usage
+
+    def set_usage(self, *, rowwise=None, columnwise=None):
+        super().set_usage(rowwise=rowwise, columnwise=columnwise)
+        if self.parent is not None:
+            self.parent.set_usage(rowwise=rowwise, columnwise=columnwise)
+
+    def __getattr__(self, name):  # delegate recipe-specific attributes (dtype, scale, amax ...)
+        parent = self.__dict__.get("parent")
+        if parent is None:
+            raise AttributeError(name)
+        return getattr(parent, name)
+
+    def _log(self, rec: Dict[str, Any]):
+        rec.update(layer=self.layer_name, tensor=self.tensor_name, iteration=_STATE.iteration)
+        _STATE.records.append(rec)
+
+    def quantize_impl(self, tensor, dtype=None):
+        f = self.features
+        if "LogTensorStats" in f and _wants(f["LogTensorStats"], self.tensor_name):
+            for s in f["LogTensorStats"].get("stats", ["min", "max", "mean", "std"]):
+                self._log({"stat": s, "value": _stat(s, tensor)})
+        if "DumpTensors" in f and _wants(f["DumpTensors"], self.tensor_name) and _STATE.log_dir:
+            d = os.path.join(_STATE.log_dir, f["DumpTensors"].get("dir", "dumps"))
+            os.makedirs(d, exist_ok=True)
+            torch.save(tensor.detach().cpu(), os.path.join(
+                d, f"{self.layer_name}.{self.tensor_name}.{_STATE.iteration}.pt".replace("/", "_")))
+        q = self.parent.quantize_impl(tensor, dtype) if self.parent is not None else tensor
+        for feat in ("LogFp8TensorStats", "LogNvfp4TensorStats"):
+            if feat in f and _wants(f[feat], self.tensor_name) and isinstance(q, QuantizedTensorStorage):
+                for s in f[feat].get("stats", ["underflows%", "mse"]):
+                    self._log({"stat": s, "value": _quant_stat(s, tensor, q)})
+        return q
+
+    def make_empty(self, shape, *, dtype=torch.float32, device=None, requires_grad=False):
+        return self.parent.make_empty(shape, dtype=dtype, device=device, requires_grad=requires_grad)
+
+    def update_quantized(self, src, dst, *, noop_flag=None):
+        return self.parent.update_quantized(src, dst, noop_flag=noop_flag)
+
+    def copy(self):
+        return DebugQuantizer(self.parent.copy() if self.parent is not None else None, self.layer_name,
+                              self.tensor_name, self.features)
+
+
+class _FakeQuantizer(Quantizer):
+    """Quantize-dequantize: the GEMM runs in high precision on values rounded to the low-precision grid."""
+
+    def __init__(self, parent: Quantizer):
+        super().__init__(rowwise=True, columnwise=False)
+        self.parent = parent
+
+    def quantize_impl(self, tensor, dtype=None):
+        p = self.parent.copy()
+        p.set_usage(rowwise=True, columnwise=False)
+        return p.quantize_impl(tensor, dtype).dequantize().to(tensor.dtype)
+
+
+def wrap_quantizer(parent: Optional[Quantizer], layer_name: Optional[str], fwd: bool, idx: int):
+    """Called by modules for every quantizer slot; returns the quantizer the module should use."""
+    feats = _STATE.features_for(layer_name)
+    if not feats:
+        return parent
+    tname = tensor_name_of_slot(fwd, idx)
+    if "DisableQuantizationLayer" in feats or "DisableFP8Layer" in feats:
+        return None
+    for key in ("DisableQuantizationGEMM", "DisableFP8GEMM"):
+        if key in feats and _wants(feats[key], tname):
+            return None
+    if parent is None:
+        return None
+    if isinstance(parent, DebugQuantizer):
+        return parent
+    return DebugQuantizer(parent, layer_name, tname, feats)
+
+
+def is_enabled() -> bool:
+    return _STATE.enabled

@@ -1,0 +1,279 @@
+"""Basic fusible operations (reference: ``pytorch/ops/basic/*.py``).
+
+Every operation is an ``nn.Module`` with ``forward(x, *extra_inputs)``.  ``num_extra_inputs`` /
+``num_extra_outputs`` tell ``Sequential`` how many additional tensors an operation consumes
+from / adds to the call.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .. import ops as K
+from ..modules.layernorm_linear import LayerNorm as _TELayerNorm
+from ..modules.layernorm_linear import RMSNorm as _TERMSNorm
+from ..modules.linear import Linear as _TELinear
+from ..parallel import distributed as D
+
+
+class FusibleOperation(torch.nn.Module):
+    """Base class: an operation that ``Sequential`` may replace by a fused implementation."""
+
+    num_extra_inputs = 0
+    num_extra_outputs = 0
+
+    @property
+    def is_fused_op(self) -> bool:
+        return False
+
+
+class BasicLinear(_TELinear, FusibleOperation):
+    """``y = x W^T`` (no bias); parameter ``weight``."""
+
+    def __init__(self, in_features, out_features, *, device=None, dtype=None, tensor_parallel_mode=None,
+                 tensor_parallel_group=None, sequence_parallel=False, accumulate_into_main_grad=False, **kw):
+        super().__init__(in_features, out_features, bias=False, params_dtype=dtype, device=device,
+                         parallel_mode=tensor_parallel_mode, tp_group=tensor_parallel_group,
+                         sequence_parallel=sequence_parallel, fuse_wgrad_accumulation=accumulate_into_main_grad, **kw)
+
+
+class Linear(_TELinear, FusibleOperation):
+    """``y = x W^T + b``; parameters ``weight`` and ``bias``."""
+
+    def __init__(self, in_features, out_features, *, bias=True, device=None, dtype=None, tensor_parallel_mode=None,
+                 tensor_parallel_group=None, sequence_parallel=False, accumulate_into_main_grad=False, **kw):
+        super().__init__(in_features, out_features, bias=bias, params_dtype=dtype, device=device,
+                         parallel_mode=tensor_parallel_mode, tp_group=tensor_parallel_group,
+                         sequence_parallel=sequence_parallel, fuse_wgrad_accumulation=accumulate_into_main_grad, **kw)
+
+
+class Bias(FusibleOperation):
+    def __init__(self, size, *, device=None, dtype=None):
+        super().__init__()
+        self.bias = torch.nn.Parameter(torch.zeros(size, device=device, dtype=dtype))
+
+    def forward(self, x):
+        return x + self.bias.to(x.dtype)
+
+
+class LayerNorm(_TELayerNorm, FusibleOperation):
+    def __init__(self, normalized_shape, *, eps=1e-5, device=None, dtype=None, zero_centered_gamma=False, **kw):
+        n = normalized_shape if isinstance(normalized_shape, int) else normalized_shape[-1]
+        super().__init__(n, eps=eps, params_dtype=dtype, device=device, zero_centered_gamma=zero_centered_gamma, **kw)
+
+
+class RMSNorm(_TERMSNorm, FusibleOperation):
+    def __init__(self, normalized_shape, *, eps=1e-5, device=None, dtype=None, zero_centered_gamma=False, **kw):
+        n = normalized_shape if isinstance(normalized_shape, int) else normalized_shape[-1]
+        super().__init__(n, eps=eps, params_dtype=dtype, device=device, zero_centered_gamma=zero_centered_gamma, **kw)
+
+
+class _ActFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, name):  # type: ignore[override]
+        y, _ = K.activation_fwd(x.contiguous(), name)
+        ctx.save_for_backward(x)
+        ctx.name = name
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        (x,) = ctx.saved_tensors
+        dx, _, _ = K.activation_bwd(dy.contiguous(), x.contiguous(), ctx.name)
+        return dx.to(x.dtype), None
+
+
+class _Activation(FusibleOperation):
+    act_name = "gelu"
+
+    def __init__(self, *, cache_quantized_input: bool = False):
+        super().__init__()
+        self.cache_quantized_input = cache_quantized_input
+
+    def forward(self, x):
+        return _ActFn.apply(x, self.act_name)
+
+
+class GELU(_Activation):
+    act_name = "gelu"
+
+
+class ReLU(_Activation):
+    act_name = "relu"
+
+
+class SiLU(_Activation):
+    act_name = "silu"
+
+
+class QGELU(_Activation):
+    act_name = "qgelu"
+
+
+class SReLU(_Activation):
+    act_name = "srelu"
+
+
+class SwiGLU(_Activation):
+    act_name = "swiglu"
+
+
+class GEGLU(_Activation):
+    act_name = "geglu"
+
+
+class ReGLU(_Activation):
+    act_name = "reglu"
+
+
+class _QuantizeFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, quantizer, keep):  # type: ignore[override]
+        q = quantizer(x)
+        return q if keep else q.dequantize().to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return g, None, None
+
+
+class Quantize(FusibleOperation):
+    """Quantize the activation with the recipe of the surrounding ``autocast`` (identity outside it)."""
+
+    def __init__(self, forward: bool = True, backward: bool = False):
+        super().__init__()
+        self.quantize_forward, self.quantize_backward = forward, backward
+
+    def forward(self, x):
+        from ..quantization import FP8GlobalStateManager, RecipeState
+
+        if not self.quantize_forward or not FP8GlobalStateManager.is_fp8_enabled():
+            return x
+        state = RecipeState.create(FP8GlobalStateManager.get_fp8_recipe(), mode="forward", num_quantizers=1)
+        quantizer = state.make_quantizers()[0]
+        quantizer.set_usage(rowwise=True, columnwise=False)
+        return _QuantizeFn.apply(x, quantizer, False)
+
+
+class Identity(FusibleOperation):
+    def forward(self, x):
+        return x
+
+
+class Reshape(FusibleOperation):
+    def __init__(self, shape: Sequence[int]):
+        super().__init__()
+        self.shape = tuple(shape)
+
+    def forward(self, x):
+        return x.reshape(self.shape)
+
+
+class ConstantScale(FusibleOperation):
+    def __init__(self, scale: float):
+        super().__init__()
+        self.scale = scale
+
+    def forward(self, x):
+        return x * self.scale
+
+
+class Dropout(FusibleOperation):
+    def __init__(self, p: float):
+        super().__init__()
+        self.p = p
+
+    def forward(self, x):
+        return torch.nn.functional.dropout(x, self.p, self.training)
+
+
+class L2Normalization(FusibleOperation):
+    def __init__(self, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+
+    def forward(self, x):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.square().sum(-1, keepdim=True) + self.eps)).to(x.dtype)
+
+
+class AddExtraInput(FusibleOperation):
+    """``y = x + extra`` (residual connection); consumes one extra input of the call."""
+
+    num_extra_inputs = 1
+
+    def __init__(self, *, in_place: bool = False):
+        super().__init__()
+        self.in_place = in_place
+
+    def forward(self, x, extra):
+        return x + extra
+
+
+class MakeExtraOutput(FusibleOperation):
+    """Pass ``x`` on and also return it as an extra output of the call."""
+
+    num_extra_outputs = 1
+
+    def forward(self, x):
+        return x, x
+
+
+class _CollFn(torch.autograd.Function):
+    """Collective on dim 0 whose backward is the adjoint collective."""
+
+    _ADJOINT = {"all_reduce": "identity", "all_gather": "reduce_scatter", "reduce_scatter": "all_gather"}
+
+    @staticmethod
+    def _run(kind, x, group):
+        x = x.contiguous()
+        n = dist.get_world_size(group)
+        if kind == "identity":
+            return x
+        if kind == "all_reduce":
+            y = x.clone()
+            dist.all_reduce(y, group=group)
+            return y
+        if kind == "all_gather":
+            y = torch.empty((n * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(y.view(-1), x.view(-1), group=group)
+            return y
+        y = torch.empty((x.shape[0] // n,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(y.view(-1), x.view(-1), group=group)
+        return y
+
+    @staticmethod
+    def forward(ctx, x, kind, group):  # type: ignore[override]
+        ctx.kind, ctx.group = kind, group
+        return _CollFn._run(kind, x, group)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return _CollFn._run(_CollFn._ADJOINT[ctx.kind], g, ctx.group), None, None
+
+
+class _Collective(FusibleOperation):
+    kind = "all_reduce"
+
+    def __init__(self, process_group=None):
+        super().__init__()
+        self.group = process_group
+
+    def forward(self, x):
+        if D.get_world_size(self.group) <= 1:
+            return x
+        return _CollFn.apply(x, self.kind, self.group)
+
+
+class AllReduce(_Collective):
+    kind = "all_reduce"
+
+
+class AllGather(_Collective):
+    kind = "all_gather"
+
+
+class ReduceScatter(_Collective):
+    kind = "reduce_scatter"

@@ -1,0 +1,148 @@
+"""``Sequential`` container that fuses runs of basic operations (reference:
+``pytorch/ops/sequential.py``, ``pytorch/ops/fuser.py:53,400``)."""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Tuple
+
+import torch
+
+from . import ops as O
+from ..modules.layernorm_linear import LayerNormLinear
+from ..modules.layernorm_mlp import LayerNormMLP
+
+
+class _Fused(torch.nn.Module):
+    """A fused implementation standing in for ``span`` consecutive basic operations."""
+
+    is_fused_op = True
+
+    def __init__(self, impl: Callable, span: int, extra_inputs: int = 0, name: str = ""):
+        super().__init__()
+        self._impl = [impl]  # in a list: the fused module's parameters belong to the basic operations
+        self.span, self.num_extra_inputs, self.num_extra_outputs, self.fusion = span, extra_inputs, 0, name
+
+    def forward(self, x, *extra):
+        return self._impl[0](x, *extra)
+
+
+def _norm_kind(op) -> Optional[str]:
+    if isinstance(op, O.LayerNorm):
+        return "LayerNorm"
+    if isinstance(op, O.RMSNorm):
+        return "RMSNorm"
+    return None
+
+
+def _is_linear(op) -> bool:
+    return isinstance(op, (O.BasicLinear, O.Linear)) and getattr(op, "parallel_mode", None) is None
+
+
+def _share(dst: torch.nn.Module, name: str, p):
+    if p is None:
+        dst.register_parameter(name, None) if name in dst._parameters else setattr(dst, name, None)
+    else:
+        dst._parameters[name] = p
+
+
+def _fuse_norm_linear(norm, lin) -> Callable:
+    has_bias = getattr(lin, "bias", None) is not None
+    m = LayerNormLinear(lin.in_features, lin.out_features, eps=norm.eps, bias=has_bias,
+                        normalization=_norm_kind(norm), params_dtype=lin.weight.dtype, device="meta",
+                        zero_centered_gamma=norm.zero_centered_gamma)
+    _share(m, "layer_norm_weight", norm.weight)
+    _share(m, "layer_norm_bias", getattr(norm, "bias", None))
+    _share(m, "weight", lin.weight)
+    if has_bias:
+        _share(m, "bias", lin.bias)
+    return m
+
+
+def _fuse_norm_mlp(norm, fc1, act, fc2) -> Callable:
+    has_bias = getattr(fc1, "bias", None) is not None
+    ffn = fc2.in_features
+    m = LayerNormMLP(fc1.in_features, ffn, eps=norm.eps, bias=has_bias, normalization=_norm_kind(norm),
+                     activation=act.act_name, params_dtype=fc1.weight.dtype, device="meta",
+                     zero_centered_gamma=norm.zero_centered_gamma)
+    _share(m, "layer_norm_weight", norm.weight)
+    _share(m, "layer_norm_bias", getattr(norm, "bias", None))
+    _share(m, "fc1_weight", fc1.weight)
+    _share(m, "fc2_weight", fc2.weight)
+    if has_bias:
+        _share(m, "fc1_bias", fc1.bias)
+        _share(m, "fc2_bias", fc2.bias)
+    return m
+
+
+def fuse_operations(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
+    """Greedy longest-match fusion of a list of basic operations."""
+    out: List[torch.nn.Module] = []
+    i = 0
+    while i < len(ops):
+        w = ops[i:i + 4]
+        if (len(w) == 4 and _norm_kind(w[0]) and _is_linear(w[1]) and isinstance(w[2], O._Activation)
+                and _is_linear(w[3]) and (getattr(w[1], "bias", None) is None) == (getattr(w[3], "bias", None) is None)
+                and w[1].out_features == w[3].in_features * (2 if w[2].act_name in ("swiglu", "geglu", "reglu") else 1)):
+            out.append(_Fused(_fuse_norm_mlp(*w), 4, name="norm_mlp"))
+            i += 4
+            continue
+        if len(w) >= 2 and _norm_kind(w[0]) and _is_linear(w[1]):
+            out.append(_Fused(_fuse_norm_linear(w[0], w[1]), 2, name="norm_linear"))
+            i += 2
+            continue
+        if len(w) >= 2 and _is_linear(w[0]) and isinstance(w[1], O.AddExtraInput):
+            lin = w[0]
+            out.append(_Fused(lambda x, extra, lin=lin: lin(x) + extra, 2, extra_inputs=1, name="linear_add"))
+            i += 2
+            continue
+        out.append(ops[i])
+        i += 1
+    return out
+
+
+class Sequential(torch.nn.Module):
+    """Runs its operations in order, fusing neighbours where this library has a fused kernel.
+
+    ``forward(x, *extra_inputs)``: operations that declare ``num_extra_inputs`` take their
+    additional tensors from ``extra_inputs`` in order; operations with ``num_extra_outputs``
+    append to the returned tuple.
+    """
+
+    def __init__(self, *ops: torch.nn.Module):
+        super().__init__()
+        for i, op in enumerate(ops):
+            self.add_module(str(i), op)
+        self._plan: Optional[List[torch.nn.Module]] = None
+        self._plan_key: Optional[Tuple[int, ...]] = None
+
+    def __len__(self):
+        return len(self._modules)
+
+    def __getitem__(self, i):
+        return list(self._modules.values())[i]
+
+    def append(self, op: torch.nn.Module) -> "Sequential":
+        self.add_module(str(len(self._modules)), op)
+        self._plan = None
+        return self
+
+    def _get_plan(self) -> List[torch.nn.Module]:
+        mods = list(self._modules.values())
+        key = tuple(id(m) for m in mods)
+        if self._plan is None or key != self._plan_key:
+            self._plan, self._plan_key = fuse_operations(mods), key
+        return self._plan
+
+    def forward(self, x, *extra_inputs):
+        extra = list(extra_inputs)
+        outs = []
+        for op in self._get_plan():
+            n_in = getattr(op, "num_extra_inputs", 0)
+            args, extra = extra[:n_in], extra[n_in:]
+            y = op(x, *args)
+            if getattr(op, "num_extra_outputs", 0):
+                x, rest = y[0], y[1:]
+                outs.extend(rest)
+            else:
+                x = y
+        assert not extra, "more extra inputs than the operations consume"
+        return (x, *outs) if outs else x

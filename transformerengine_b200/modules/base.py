@@ -157,7 +157,12 @@ class TransformerEngineBaseModule(torch.nn.Module):
     def get_quantizer(self, fwd: bool, idx: int) -> Optional[Quantizer]:
         if not self.fp8:
             return None
-        return self.quantizers["scaling_fwd" if fwd else "scaling_bwd"][idx]
+        q = self.quantizers["scaling_fwd" if fwd else "scaling_bwd"][idx]
+        from .. import debug
+
+        if debug.is_enabled():
+            q = debug.wrap_quantizer(q, getattr(self, "name", None), fwd, idx)
+        return q
 
     # ------------------------------------------------------------------ weights
     def get_quantized_weight(self, weight: torch.Tensor, quantizer: Optional[Quantizer], *, cache_name: str,

@@ -109,7 +109,11 @@ def get():
 
 
 def use_cuda(*tensors) -> bool:
-    """True when the op must run on the GPU extension (any CUDA tensor given)."""
+    """True when the op must run on the GPU extension (any CUDA tensor given, not exporting)."""
+    from ..export import is_in_onnx_export_mode
+
+    if is_in_onnx_export_mode():
+        return False
     for t in tensors:
         if t is not None and getattr(t, "is_cuda", False):
             return True

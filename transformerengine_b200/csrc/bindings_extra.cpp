@@ -153,9 +153,61 @@ void flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
   TORCH_CHECK(e == cudaSuccess, "flash_bwd_dq failed: ", cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------------------- NVFP4
+template <typename T = void>
+T* optr(const OptT& t) {
+  return t.has_value() && t->defined() ? static_cast<T*>(t->data_ptr()) : nullptr;
+}
+
+void nvfp4_amax(const at::Tensor& x, int64_t R, int64_t C, bool with_rht, const at::Tensor& out2) {
+  c10::cuda::CUDAGuard guard(x.device());
+  cudaError_t e = teb200::nvfp4_amax(x.data_ptr(), dtype_code(x), static_cast<int>(R), static_cast<int>(C),
+                                     with_rht ? 1 : 0, out2.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "nvfp4_amax failed: ", cudaGetErrorString(e));
+}
+
+void quantize_nvfp4(const at::Tensor& x, int64_t R, int64_t C, const OptT& amax_row, const OptT& amax_col,
+                    const OptT& row_data, const OptT& row_scale, const OptT& col_data, const OptT& col_scale,
+                    bool with_rht, bool with_2d, bool stochastic, int64_t seed, int64_t offset) {
+  c10::cuda::CUDAGuard guard(x.device());
+  teb200::Nvfp4Args a;
+  a.x = x.data_ptr();
+  a.x_dtype = dtype_code(x);
+  a.R = static_cast<int>(R);
+  a.C = static_cast<int>(C);
+  a.amax_row = optr<float>(amax_row);
+  a.amax_col = optr<float>(amax_col);
+  a.row_data = optr<uint8_t>(row_data);
+  a.row_scale = optr<uint8_t>(row_scale);
+  a.col_data = optr<uint8_t>(col_data);
+  a.col_scale = optr<uint8_t>(col_scale);
+  a.with_rht = with_rht;
+  a.with_2d = with_2d;
+  a.stochastic = stochastic;
+  a.seed = static_cast<uint64_t>(seed);
+  a.offset = static_cast<uint64_t>(offset);
+  TORCH_CHECK(a.row_data == nullptr || a.amax_row != nullptr, "row-wise NVFP4 needs its global amax");
+  TORCH_CHECK(a.col_data == nullptr || a.amax_col != nullptr, "column-wise NVFP4 needs its global amax");
+  cudaError_t e = teb200::quantize_nvfp4(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "quantize_nvfp4 failed: ", cudaGetErrorString(e));
+}
+
+void dequantize_nvfp4(const at::Tensor& q, const at::Tensor& sf, const at::Tensor& amax, int64_t R, int64_t C,
+                      const at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(q.device());
+  cudaError_t e = teb200::dequantize_nvfp4(static_cast<const uint8_t*>(q.data_ptr()),
+                                           static_cast<const uint8_t*>(sf.data_ptr()), amax.data_ptr<float>(),
+                                           static_cast<int>(R), static_cast<int>(C), out.data_ptr(), dtype_code(out),
+                                           cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "dequantize_nvfp4 failed: ", cudaGetErrorString(e));
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("nvfp4_amax", &nvfp4_amax);
+  m.def("quantize_nvfp4", &quantize_nvfp4);
+  m.def("dequantize_nvfp4", &dequantize_nvfp4);
   m.def("comm_gemm", &comm_gemm);
   m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),

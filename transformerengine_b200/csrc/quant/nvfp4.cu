@@ -1,0 +1,330 @@
+// NVFP4 quantization: E2M1 values in 1x16 (or 16x16) blocks, one E4M3 decode scale per block
+// stored in the 128x4-tile layout the tensor core's scale loader reads, and a per-tensor fp32
+// scale derived from the global amax.  The column-wise copy is written transposed ([C, R/2]),
+// optionally after a 16-point randomised Hadamard transform along the token dimension, and
+// rounding can be stochastic (gradients).
+// (Reference behaviour: common/cast/nvfp4/*.cuh, common/hadamard_transform/*.cu.)
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "teb200/api.h"
+#include "teb200/quant.h"
+
+namespace teb200 {
+namespace {
+
+constexpr float kFp32Max = 3.402823466e+38f;
+
+__device__ __forceinline__ size_t swizzled_sf_offset(int i, int j, int k_tiles) {
+  return (static_cast<size_t>(i >> 7) * k_tiles + (j >> 2)) * 512 + (i & 31) * 16 + ((i & 127) >> 5) * 4 + (j & 3);
+}
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) {
+  return __bfloat162float(__float2bfloat16(v));  // fp32 inputs are rounded through bf16, as the 16-bit path sees them
+}
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) {
+  return __bfloat162float(v);
+}
+template <>
+__device__ __forceinline__ float to_f<__half>(__half v) {
+  return __half2float(v);
+}
+
+// signs of the randomised Hadamard transform (fixed vector 1 1 1 -1 1 -1 -1 -1 -1 -1 -1 1 -1 1 -1 -1),
+// bit i set = element i is negated
+constexpr uint32_t kRhtSignMask = 0xD7E8u;
+
+// y = (diag(sign) * H16 / 4)^T applied to 16 values in place: y_j = sum_i x_i sign_i H[i][j] / 4
+__device__ __forceinline__ void rht16(float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i)
+    if ((kRhtSignMask >> i) & 1u) v[i] = -v[i];
+#pragma unroll
+  for (int len = 1; len < 16; len <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 16; i += 2 * len) {
+#pragma unroll
+      for (int j = 0; j < len; ++j) {
+        const float a = v[i + j], b = v[i + j + len];
+        v[i + j] = a + b;
+        v[i + j + len] = a - b;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] *= 0.25f;
+}
+
+__device__ __forceinline__ float global_encode_scale(float amax) {
+  float s = __fdiv_rn(448.0f * 6.0f, amax);  // exact division: the build enables fast math
+  s = fminf(s, kFp32Max);
+  return (amax == 0.f || s == 0.f) ? 1.f : s;
+}
+
+// E4M3 decode scale of a block and the matching fp32 encode multiplier
+__device__ __forceinline__ uint8_t block_scale(float vec_max, float s_enc, float& enc) {
+  float dec = fminf(__fmul_rn(vec_max, __fmul_rn(s_enc, 1.0f / 6.0f)), kFp32Max);
+  dec = fminf(fmaxf(dec, -448.f), 448.f);
+  const __nv_fp8_e4m3 d8(dec);
+  const float decf = static_cast<float>(d8);
+  enc = fminf(__fdiv_rn(1.0f, __fmul_rn(decf, __fdiv_rn(1.0f, s_enc))), kFp32Max);
+  return *reinterpret_cast<const uint8_t*>(&d8);
+}
+
+__device__ __forceinline__ uint32_t e2m1_rn(float x) {
+  const float a = fabsf(x);
+  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
+  return c | (x < 0.f ? 8u : 0u);
+}
+
+__device__ __forceinline__ uint32_t hash32(uint64_t k) {
+  k ^= k >> 33; k *= 0xff51afd7ed558ccdULL; k ^= k >> 33; k *= 0xc4ceb9fe1a85ec53ULL; k ^= k >> 33;
+  return static_cast<uint32_t>(k);
+}
+
+// stochastic rounding onto the E2M1 grid; u uniform in [0, 1)
+__device__ __forceinline__ uint32_t e2m1_sr(float x, float u) {
+  const float a = fminf(fabsf(x), 6.0f);
+  const float grid[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  uint32_t lo = 0;
+#pragma unroll
+  for (int i = 1; i < 8; ++i) lo += (a >= grid[i]);
+  const uint32_t hi = lo < 7 ? lo + 1 : 7;
+  const float span = grid[hi] - grid[lo];
+  const float p_up = span > 0.f ? (a - grid[lo]) / span : 0.f;
+  const uint32_t c = (u < p_up) ? hi : lo;
+  return c | (x < 0.f ? 8u : 0u);
+}
+
+__device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
+  atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));  // valid for non-negative floats
+}
+
+// ------------------------------------------------------------------------------------- amax
+template <typename T>
+__global__ void nvfp4_amax_kernel(const T* __restrict__ x, int R, int C, int with_rht, float* out2) {
+  float m0 = 0.f, m1 = 0.f;
+  // thread = (column, 16-row group): coalesced along columns
+  const long long groups = static_cast<long long>(R / 16) * C;
+  for (long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups;
+       g += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(g % C);
+    const int r0 = static_cast<int>(g / C) * 16;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      v[i] = to_f(x[static_cast<size_t>(r0 + i) * C + c]);
+      m0 = fmaxf(m0, fabsf(v[i]));
+    }
+    if (with_rht) {
+      rht16(v);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m1 = fmaxf(m1, fabsf(v[i]));
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, off));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, off));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomic_max_pos(out2, m0);
+    if (with_rht) atomic_max_pos(out2 + 1, m1);
+  }
+}
+
+// --------------------------------------------------------------------------- row-wise copy
+// block = 16 rows x 16 column blocks; thread (rx, cb) quantizes 16 consecutive values of row rx
+template <typename T>
+__global__ void nvfp4_row_kernel(const T* __restrict__ x, int R, int C, const float* __restrict__ amax,
+                                 uint8_t* __restrict__ data, uint8_t* __restrict__ scale, int with_2d, int stochastic,
+                                 uint64_t seed, uint64_t offset) {
+  const int rx = threadIdx.x & 15, cb = threadIdx.x >> 4;
+  const int r = blockIdx.y * 16 + rx;
+  const int blk = blockIdx.x * 16 + cb;
+  const bool ok = r < R && blk * 16 < C;
+  float v[16];
+  float vmax = 0.f;
+  if (ok) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      v[i] = to_f(x[static_cast<size_t>(r) * C + blk * 16 + i]);
+      vmax = fmaxf(vmax, fabsf(v[i]));
+    }
+  }
+  if (with_2d) {  // one scale per 16x16 block: the 16 threads with the same cb are 16 adjacent lanes
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+  }
+  if (!ok) return;
+  const float s_enc = global_encode_scale(*amax);
+  float enc;
+  const uint8_t sb = block_scale(vmax, s_enc, enc);
+  scale[swizzled_sf_offset(r, blk, ((C >> 4) + 3) >> 2)] = sb;
+  uint32_t w[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
+    uint32_t code;
+    if (stochastic) {
+      const uint64_t idx = static_cast<uint64_t>(r) * C + blk * 16 + i;
+      const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset) >> 8) * (1.0f / 16777216.0f);
+      code = e2m1_sr(sv, u);
+    } else {
+      code = e2m1_rn(sv);
+    }
+    w[i >> 3] |= code << ((i & 7) * 4);
+  }
+  *reinterpret_cast<uint2*>(data + static_cast<size_t>(r) * (C / 2) + blk * 8) = make_uint2(w[0], w[1]);
+}
+
+// ------------------------------------------------------------------------ column-wise copy
+// block = 32 columns x 256 rows; thread (cx, g) quantizes rows [16g, 16g+16) of column cx and the
+// packed bytes go through shared memory so that every output row gets one 128-byte store run
+template <typename T>
+__global__ void nvfp4_col_kernel(const T* __restrict__ x, int R, int C, const float* __restrict__ amax,
+                                 uint8_t* __restrict__ data, uint8_t* __restrict__ scale, int with_rht, int with_2d,
+                                 int stochastic, uint64_t seed, uint64_t offset) {
+  __shared__ uint2 stage[32][17];
+  const int cx = threadIdx.x & 31, g = threadIdx.x >> 5;  // 16 warps: one 16-row group each
+  const int c = blockIdx.x * 32 + cx;
+  const int r0 = blockIdx.y * 256 + g * 16;
+  const bool ok = c < C && r0 < R;
+  float v[16];
+  float vmax = 0.f;
+  if (ok) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = to_f(x[static_cast<size_t>(r0 + i) * C + c]);
+    if (with_rht) rht16(v);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) vmax = fmaxf(vmax, fabsf(v[i]));
+  }
+  if (with_2d) {  // 16x16 blocks: 16 adjacent columns (half a warp) share the scale
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, off));
+  }
+  uint2 packed = make_uint2(0u, 0u);
+  if (ok) {
+    const float s_enc = global_encode_scale(*amax);
+    float enc;
+    const uint8_t sb = block_scale(vmax, s_enc, enc);
+    scale[swizzled_sf_offset(c, r0 >> 4, ((R >> 4) + 3) >> 2)] = sb;
+    uint32_t w[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
+      uint32_t code;
+      if (stochastic) {
+        const uint64_t idx = static_cast<uint64_t>(c) * R + r0 + i;
+        const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset + 0x5bd1e995ULL) >> 8) *
+                        (1.0f / 16777216.0f);
+        code = e2m1_sr(sv, u);
+      } else {
+        code = e2m1_rn(sv);
+      }
+      w[i >> 3] |= code << ((i & 7) * 4);
+    }
+    packed = make_uint2(w[0], w[1]);
+  }
+  stage[cx][g] = packed;
+  __syncthreads();
+  // 32 output rows x 128 bytes: thread t writes 8 bytes (uint2 #(t % 16)) of rows t / 16 and + 16
+  const int q = threadIdx.x & 15;
+#pragma unroll
+  for (int rr = threadIdx.x >> 4; rr < 32; rr += 32) {
+    const int oc = blockIdx.x * 32 + rr;
+    const int orow0 = blockIdx.y * 256 + q * 16;
+    if (oc < C && orow0 < R)
+      *reinterpret_cast<uint2*>(data + static_cast<size_t>(oc) * (R / 2) + orow0 / 2) = stage[rr][q];
+  }
+}
+
+// --------------------------------------------------------------------------------- dequantize
+template <typename T>
+__global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
+                                     const float* __restrict__ amax, int R, int C, T* __restrict__ out) {
+  const long long blocks = static_cast<long long>(R) * (C / 16);
+  const float s_dec = __fdiv_rn(1.0f, global_encode_scale(*amax));
+  const int kt = ((C >> 4) + 3) >> 2;
+  for (long long b = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; b < blocks;
+       b += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int r = static_cast<int>(b / (C / 16)), blk = static_cast<int>(b % (C / 16));
+    const uint8_t sb = sf[swizzled_sf_offset(r, blk, kt)];
+    const float s = static_cast<float>(*reinterpret_cast<const __nv_fp8_e4m3*>(&sb)) * s_dec;
+    const uint2 w2 = *reinterpret_cast<const uint2*>(q + static_cast<size_t>(r) * (C / 2) + blk * 8);
+    const uint32_t w[2] = {w2.x, w2.y};
+    const float grid[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t code = (w[i >> 3] >> ((i & 7) * 4)) & 0xF;
+      const float val = (code & 8 ? -grid[code & 7] : grid[code & 7]) * s;
+      out[static_cast<size_t>(r) * C + blk * 16 + i] = static_cast<T>(val);
+    }
+  }
+}
+
+template <typename T>
+cudaError_t launch_quant(const Nvfp4Args& a, cudaStream_t s) {
+  const T* x = static_cast<const T*>(a.x);
+  if (a.row_data != nullptr) {
+    dim3 grid((a.C / 16 + 15) / 16, (a.R + 15) / 16);
+    nvfp4_row_kernel<T><<<grid, 256, 0, s>>>(x, a.R, a.C, a.amax_row, a.row_data, a.row_scale, a.with_2d, a.stochastic,
+                                             a.seed, a.offset);
+  }
+  if (a.col_data != nullptr) {
+    dim3 grid((a.C + 31) / 32, (a.R + 255) / 256);
+    nvfp4_col_kernel<T><<<grid, 512, 0, s>>>(x, a.R, a.C, a.amax_col, a.col_data, a.col_scale, a.with_rht, a.with_2d,
+                                             a.stochastic, a.seed, a.offset);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t quantize_nvfp4(const Nvfp4Args& a, cudaStream_t s) {
+  if (a.R % 16 != 0 || a.C % 16 != 0) return cudaErrorInvalidValue;
+  switch (a.x_dtype) {
+    case kFloat32: return launch_quant<float>(a, s);
+    case kFloat16: return launch_quant<__half>(a, s);
+    default: return launch_quant<__nv_bfloat16>(a, s);
+  }
+}
+
+cudaError_t nvfp4_amax(const void* x, int dtype, int R, int C, int with_rht, float* out2, cudaStream_t s) {
+  if (R % 16 != 0) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(out2, 0, 2 * sizeof(float), s);
+  if (e != cudaSuccess) return e;
+  const long long groups = static_cast<long long>(R / 16) * C;
+  if (groups == 0) return cudaSuccess;
+  const int grid = static_cast<int>(groups / 256 + 1 < 148 * 8 ? groups / 256 + 1 : 148 * 8);
+  switch (dtype) {
+    case kFloat32: nvfp4_amax_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), R, C, with_rht, out2); break;
+    case kFloat16: nvfp4_amax_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x), R, C, with_rht, out2); break;
+    default:
+      nvfp4_amax_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), R, C, with_rht, out2);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t dequantize_nvfp4(const uint8_t* q, const uint8_t* sf_swizzled, const float* amax, int R, int C, void* out,
+                             int out_dtype, cudaStream_t s) {
+  const long long blocks = static_cast<long long>(R) * (C / 16);
+  if (blocks == 0) return cudaSuccess;
+  const int grid = static_cast<int>(blocks / 256 + 1 < 148 * 8 ? blocks / 256 + 1 : 148 * 8);
+  switch (out_dtype) {
+    case kFloat32: nvfp4_dequant_kernel<float><<<grid, 256, 0, s>>>(q, sf_swizzled, amax, R, C, static_cast<float*>(out)); break;
+    case kFloat16: nvfp4_dequant_kernel<__half><<<grid, 256, 0, s>>>(q, sf_swizzled, amax, R, C, static_cast<__half*>(out)); break;
+    default:
+      nvfp4_dequant_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(q, sf_swizzled, amax, R, C, static_cast<__nv_bfloat16*>(out));
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace teb200

@@ -258,7 +258,8 @@ def apply_rht(x2d: torch.Tensor) -> torch.Tensor:
 
 def nvfp4_global_encode_scale(amax: torch.Tensor) -> torch.Tensor:
     """S_enc = 448*6/amax, clamped to fp32 max; 1 where amax == 0."""
-    s = (448.0 * 6.0) / amax.float()
+    a = amax.float()
+    s = torch.full_like(a, 448.0 * 6.0) / a  # tensor / tensor: "scalar / tensor" is reciprocal-then-multiply on CPU
     s = torch.clamp(s, max=FP32_MAX)
     return torch.where((amax == 0) | (s == 0), torch.ones_like(s), s)
 
@@ -293,12 +294,14 @@ def quantize_nvfp4_2d(x2d: torch.Tensor, global_amax: torch.Tensor) -> Tuple[tor
 
 
 def _nvfp4_encode(xb, vec_max, global_amax, stochastic, generator, R, C):
-    s_enc = nvfp4_global_encode_scale(global_amax.float().reshape(-1)[0])
-    s_dec_global = 1.0 / s_enc
-    dec = vec_max * (s_enc * (1.0 / 6.0))
+    # 1-element tensors, not 0-dim ones: CPU kernels promote a 0-dim operand to a double scalar,
+    # which changes products such as dec * s_dec_global in the last bit
+    s_enc = nvfp4_global_encode_scale(global_amax.float().reshape(-1)[:1])
+    s_dec_global = torch.ones_like(s_enc) / s_enc
+    dec = vec_max * (s_enc * torch.full_like(s_enc, 1.0 / 6.0))
     dec = torch.clamp(dec, max=FP32_MAX)
     dec = torch.clamp(dec, -448.0, 448.0).to(FP8_E4M3)
-    enc = torch.clamp(1.0 / (dec.float() * s_dec_global), max=FP32_MAX)
+    enc = torch.clamp(torch.ones_like(s_enc) / (dec.float() * s_dec_global), max=FP32_MAX)
     scaled = torch.clamp(xb * enc, -6.0, 6.0).reshape(R, C)
     if stochastic:
         rand = torch.rand(scaled.shape, generator=generator, device=scaled.device)
@@ -314,8 +317,8 @@ def dequantize_nvfp4(
     R, Ch = packed.shape
     C = Ch * 2
     vals = e2m1_codes_to_float(unpack_fp4(packed))
-    s_enc = nvfp4_global_encode_scale(global_amax.float().reshape(-1)[0])
-    sd = scales_e4m3[:R, : C // 16].contiguous().view(FP8_E4M3).float() * (1.0 / s_enc)
+    s_enc = nvfp4_global_encode_scale(global_amax.float().reshape(-1)[:1])
+    sd = scales_e4m3[:R, : C // 16].contiguous().view(FP8_E4M3).float() * (torch.ones_like(s_enc) / s_enc)
     return (vals.reshape(R, C // 16, 16) * sd.unsqueeze(-1)).reshape(R, C).to(out_dtype)
 
 

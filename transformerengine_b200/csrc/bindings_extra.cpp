@@ -202,9 +202,108 @@ void dequantize_nvfp4(const at::Tensor& q, const at::Tensor& sf, const at::Tenso
   TORCH_CHECK(e == cudaSuccess, "dequantize_nvfp4 failed: ", cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------------------- MoE router / permutation
+teb200::RouterArgs router_args(const at::Tensor& logits, int64_t topk, bool pre_softmax, double scaling,
+                               int64_t score_fn, const OptT& expert_bias) {
+  teb200::RouterArgs a;
+  a.logits = logits.data_ptr();
+  a.dtype = dtype_code(logits);
+  a.T = static_cast<int>(logits.size(0));
+  a.E = static_cast<int>(logits.size(1));
+  a.topk = static_cast<int>(topk);
+  a.score_fn = static_cast<int>(score_fn);
+  a.use_pre_softmax = pre_softmax ? 1 : 0;
+  a.scaling_factor = static_cast<float>(scaling);
+  a.expert_bias = optr<float>(expert_bias);
+  return a;
+}
+
+std::vector<at::Tensor> router_topk(const at::Tensor& logits, int64_t topk, bool pre_softmax, double scaling,
+                                    int64_t score_fn, const OptT& expert_bias, bool want_scores) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && logits.is_contiguous(), "router logits must be a contiguous [T, E] tensor");
+  teb200::RouterArgs a = router_args(logits, topk, pre_softmax, scaling, score_fn, expert_bias);
+  auto f32 = logits.options().dtype(at::kFloat);
+  at::Tensor probs = at::empty({a.T, a.E}, f32);
+  at::Tensor rmap = at::empty({a.T, a.E}, logits.options().dtype(at::kByte));
+  at::Tensor idx = at::empty({a.T, a.topk}, logits.options().dtype(at::kInt));
+  at::Tensor tpe = at::empty({a.E}, logits.options().dtype(at::kInt));
+  at::Tensor scores = want_scores ? at::empty({a.T, a.E}, f32) : at::Tensor();
+  a.probs = probs.data_ptr<float>();
+  a.routing_map = rmap.data_ptr<uint8_t>();
+  a.topk_idx = idx.data_ptr<int32_t>();
+  a.tokens_per_expert = tpe.data_ptr<int32_t>();
+  a.scores = want_scores ? scores.data_ptr<float>() : nullptr;
+  cudaError_t e = teb200::router_topk_fwd(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "router_topk failed: ", cudaGetErrorString(e));
+  return {probs, rmap, idx, tpe, scores};
+}
+
+at::Tensor router_topk_bwd(const at::Tensor& logits, const at::Tensor& rmap, const at::Tensor& grad_probs, int64_t topk,
+                           bool pre_softmax, double scaling, int64_t score_fn) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  teb200::RouterArgs a = router_args(logits, topk, pre_softmax, scaling, score_fn, OptT());
+  a.routing_map = rmap.data_ptr<uint8_t>();
+  at::Tensor g = at::empty_like(logits);
+  cudaError_t e = teb200::router_topk_bwd(a, grad_probs.data_ptr<float>(), g.data_ptr(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "router_topk_bwd failed: ", cudaGetErrorString(e));
+  return g;
+}
+
+std::vector<at::Tensor> permute_rows(const at::Tensor& inp, const at::Tensor& dest_row, const OptT& probs, int64_t n_out) {
+  c10::cuda::CUDAGuard guard(inp.device());
+  TORCH_CHECK(inp.dim() == 2 && inp.is_contiguous() && dest_row.is_contiguous() && dest_row.scalar_type() == at::kInt);
+  at::Tensor out = at::zeros({n_out, inp.size(1)}, inp.options());
+  at::Tensor pout;
+  const float* pp = nullptr;
+  float* po = nullptr;
+  if (probs.has_value() && probs->defined()) {
+    TORCH_CHECK(probs->scalar_type() == at::kFloat && probs->is_contiguous());
+    pout = at::zeros({n_out}, probs->options());
+    pp = probs->data_ptr<float>();
+    po = pout.data_ptr<float>();
+  }
+  cudaError_t e = teb200::permute_rows(inp.data_ptr(), out.data_ptr(), dest_row.data_ptr<int32_t>(), pp, po,
+                                       static_cast<int>(inp.size(0)), static_cast<int>(dest_row.size(1)),
+                                       static_cast<int>(inp.size(1)), dtype_code(inp), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "permute_rows failed: ", cudaGetErrorString(e));
+  return {out, pout};
+}
+
+at::Tensor unpermute_rows(const at::Tensor& inp, const at::Tensor& dest_row, const OptT& w) {
+  c10::cuda::CUDAGuard guard(inp.device());
+  TORCH_CHECK(inp.dim() == 2 && inp.is_contiguous() && dest_row.is_contiguous() && dest_row.scalar_type() == at::kInt);
+  const int T = static_cast<int>(dest_row.size(0));
+  at::Tensor out = at::empty({T, inp.size(1)}, inp.options());
+  cudaError_t e = teb200::unpermute_rows(inp.data_ptr(), out.data_ptr(), dest_row.data_ptr<int32_t>(), optr<float>(w), T,
+                                         static_cast<int>(dest_row.size(1)), static_cast<int>(inp.size(1)),
+                                         dtype_code(inp), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "unpermute_rows failed: ", cudaGetErrorString(e));
+  return out;
+}
+
+std::vector<at::Tensor> build_dest_rows(const at::Tensor& topk_idx, int64_t E, int64_t align) {
+  c10::cuda::CUDAGuard guard(topk_idx.device());
+  TORCH_CHECK(topk_idx.dim() == 2 && topk_idx.is_contiguous() && topk_idx.scalar_type() == at::kInt);
+  at::Tensor counts = at::empty({E}, topk_idx.options());
+  at::Tensor offsets = at::empty({E + 1}, topk_idx.options());
+  at::Tensor dest = at::empty_like(topk_idx);
+  cudaError_t e = teb200::build_dest_rows(topk_idx.data_ptr<int32_t>(), static_cast<int>(topk_idx.size(0)),
+                                          static_cast<int>(topk_idx.size(1)), static_cast<int>(E),
+                                          static_cast<int>(align), counts.data_ptr<int32_t>(),
+                                          offsets.data_ptr<int32_t>(), dest.data_ptr<int32_t>(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "build_dest_rows failed: ", cudaGetErrorString(e));
+  return {dest, counts, offsets};
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("router_topk", &router_topk);
+  m.def("router_topk_bwd", &router_topk_bwd);
+  m.def("permute_rows", &permute_rows);
+  m.def("unpermute_rows", &unpermute_rows);
+  m.def("build_dest_rows", &build_dest_rows);
   m.def("nvfp4_amax", &nvfp4_amax);
   m.def("quantize_nvfp4", &quantize_nvfp4);
   m.def("dequantize_nvfp4", &dequantize_nvfp4);

@@ -25,6 +25,75 @@ def _dest_rows_from_mask(routing_map: torch.Tensor, align: int = 1):
     return dest, counts, offs
 
 
+class _PermuteRows(torch.autograd.Function):
+    """CUDA row scatter ``out[dest[t, s]] = inp[t]`` (zero rows where nothing lands)."""
+
+    @staticmethod
+    def forward(ctx, inp, dest, probs, n_out):  # type: ignore[override]
+        from ..ops import _ext
+
+        out, pp = _ext.get().permute_rows(inp.contiguous(), dest, None if probs is None else probs.float().contiguous(),
+                                          n_out)
+        ctx.save_for_backward(dest)
+        ctx.has_probs = probs is not None
+        ctx.pdtype = probs.dtype if probs is not None else None
+        return out, (pp.to(probs.dtype) if probs is not None else None)
+
+    @staticmethod
+    def backward(ctx, gout, gpp):  # type: ignore[override]
+        from ..ops import _ext
+
+        (dest,) = ctx.saved_tensors
+        ginp = _ext.get().unpermute_rows(gout.contiguous(), dest, None)
+        gprobs = None
+        if ctx.has_probs and gpp is not None:
+            d = dest.long()
+            gprobs = torch.where(d >= 0, gpp.float()[d.clamp(min=0)], torch.zeros((), device=gpp.device)).to(ctx.pdtype)
+        return ginp, None, gprobs, None
+
+
+class _UnpermuteRows(torch.autograd.Function):
+    """CUDA weighted gather ``out[t] = sum_s w[t, s] * inp[dest[t, s]]``."""
+
+    @staticmethod
+    def forward(ctx, inp, dest, w):  # type: ignore[override]
+        from ..ops import _ext
+
+        wf = None if w is None else w.float().contiguous()
+        out = _ext.get().unpermute_rows(inp.contiguous(), dest, wf)
+        ctx.save_for_backward(inp, dest, wf if wf is not None else torch.empty(0, device=inp.device))
+        ctx.has_w = w is not None
+        ctx.wdtype = w.dtype if w is not None else None
+        return out
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        from ..ops import _ext
+
+        inp, dest, wf = ctx.saved_tensors
+        g = g.contiguous()
+        ginp, pp = _ext.get().permute_rows(g, dest, wf if ctx.has_w else None, inp.shape[0])
+        gw = None
+        if ctx.has_w:
+            ginp = (ginp.float() * pp[:, None]).to(inp.dtype)
+            d = dest.long()
+            valid = d >= 0
+            tok = torch.arange(d.shape[0], device=g.device)[:, None].expand_as(d)[valid]
+            dots = (inp[d[valid]].float() * g[tok].float()).sum(-1)
+            gw = torch.zeros(d.shape, dtype=torch.float32, device=g.device)
+            gw[valid] = dots
+            gw = gw.to(ctx.wdtype)
+        return ginp, None, gw
+
+
+def _cuda_rows_ok(t: torch.Tensor) -> bool:
+    from ..ops import _ext
+
+    return (_ext.use_cuda(t) and hasattr(_ext.get(), "permute_rows") and t.dim() == 2
+            and t.dtype in (torch.float32, torch.bfloat16, torch.float16)
+            and (t.shape[1] * t.element_size()) % 16 == 0 and t.shape[1] % 2 == 0)
+
+
 def moe_permute(inp: torch.Tensor, routing_map: torch.Tensor, num_out_tokens: int = 0, max_token_num: int = -1,
                 map_type: str = "mask") -> Tuple[torch.Tensor, torch.Tensor]:
     out, _, row_id_map = _permute(inp, routing_map, None, num_out_tokens, map_type, 1)
@@ -76,6 +145,9 @@ def _permute(inp, routing_map, probs, num_out_tokens, map_type, align):
     from ..tensor.base import QuantizedTensorStorage
 
     src = inp.dequantize() if isinstance(inp, QuantizedTensorStorage) else inp
+    if _cuda_rows_ok(src) and (probs is None or probs.shape == dest.shape):
+        out, pp = _PermuteRows.apply(src, dest.to(torch.int32).contiguous(), probs, n_out)
+        return out, pp, dest.to(torch.int32)
     out = torch.zeros(n_out, H, dtype=src.dtype, device=src.device).index_put((rows,), src[tok])
     pp = None
     if probs is not None:
@@ -89,6 +161,9 @@ def moe_unpermute(inp: torch.Tensor, row_id_map: torch.Tensor, merging_probs: Op
     """``out[t] = sum_slots w[t, slot] * inp[dest_row[t, slot]]`` (plain sum without weights)."""
     if merging_probs is None:
         merging_probs = probs
+    if _cuda_rows_ok(inp) and (merging_probs is None or merging_probs.shape == row_id_map.shape):
+        out = _UnpermuteRows.apply(inp, row_id_map.to(torch.int32).contiguous(), merging_probs)
+        return out.reshape(restore_shape) if restore_shape is not None else out
     dest = row_id_map.long()
     T = dest.shape[0]
     H = inp.shape[-1]

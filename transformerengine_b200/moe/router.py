@@ -38,6 +38,43 @@ def _group_limited_mask(scores: torch.Tensor, topk: int, num_groups: int, group_
     return keep[:, :, None].expand_as(g).reshape(T, E)
 
 
+_SCORE_FN = {"sigmoid": 0, "softmax": 1, "sqrtsoftplus": 2}
+
+
+class _RouterTopK(torch.autograd.Function):
+    """CUDA fast path: one warp per token computes scores, top-k, probabilities and the map."""
+
+    @staticmethod
+    def forward(ctx, logits2d, topk, pre_softmax, scaling, fn, bias):  # type: ignore[override]
+        from ..ops import _ext
+
+        C_ = _ext.get()
+        probs, rmap, _, _, _ = C_.router_topk(logits2d, topk, pre_softmax, scaling, fn,
+                                              None if bias is None else bias.float().contiguous(), False)
+        ctx.save_for_backward(logits2d, rmap)
+        ctx.cfg = (topk, pre_softmax, scaling, fn)
+        ctx.mark_non_differentiable(rmap)
+        return probs.to(logits2d.dtype), rmap
+
+    @staticmethod
+    def backward(ctx, gprobs, _gmap):  # type: ignore[override]
+        from ..ops import _ext
+
+        logits2d, rmap = ctx.saved_tensors
+        topk, pre, scaling, fn = ctx.cfg
+        g = _ext.get().router_topk_bwd(logits2d, rmap, gprobs.float().contiguous(), topk, pre, scaling, fn)
+        return g, None, None, None, None, None
+
+
+def _cuda_router_ok(logits, topk, num_groups, group_topk, routing_map_format, topk_indices) -> bool:
+    from ..ops import _ext
+
+    return (_ext.use_cuda(logits) and hasattr(_ext.get(), "router_topk") and logits.shape[-1] <= 256 and 1 <= topk <= 8
+            and not (num_groups is not None and group_topk is not None and num_groups > 1)
+            and routing_map_format == "bytemap" and topk_indices is None
+            and logits.dtype in (torch.float32, torch.bfloat16, torch.float16))
+
+
 def fused_topk_with_score_function(logits: torch.Tensor, topk: int, use_pre_softmax: bool = False,
                                    num_groups: Optional[int] = None, group_topk: Optional[int] = None,
                                    scaling_factor: Optional[float] = None, score_function: str = "softmax",
@@ -47,6 +84,11 @@ def fused_topk_with_score_function(logits: torch.Tensor, topk: int, use_pre_soft
     assert logits.dtype != torch.float64, "float64 router logits are not supported"
     shape = logits.shape
     E = shape[-1]
+    if _cuda_router_ok(logits, topk, num_groups, group_topk, routing_map_format, topk_indices):
+        probs, rmap = _RouterTopK.apply(logits.reshape(-1, E).contiguous(), topk, bool(use_pre_softmax),
+                                        float(scaling_factor) if scaling_factor else 1.0, _SCORE_FN[score_function],
+                                        expert_bias)
+        return probs.reshape(shape), rmap.bool().reshape(shape)
     lf = logits.float().reshape(-1, E)
     if score_function == "softmax":
         if use_pre_softmax:

@@ -296,9 +296,112 @@ std::vector<at::Tensor> build_dest_rows(const at::Tensor& topk_idx, int64_t E, i
   return {dest, counts, offsets};
 }
 
+// ---------------------------------------------------------------------------- expert-parallel exchange
+void ep_counts(std::vector<int64_t> counts_ptrs, std::vector<int64_t> flag_ptrs, const at::Tensor& my_counts,
+               const at::Tensor& base, const at::Tensor& splits, const at::Tensor& seg, int64_t L, int64_t rank,
+               int64_t align, int64_t epoch, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(my_counts.device());
+  teb200::EpCountsArgs a;
+  a.ep = static_cast<int>(counts_ptrs.size());
+  for (int r = 0; r < a.ep; ++r) {
+    a.counts_all[r] = reinterpret_cast<int32_t*>(counts_ptrs[r]);
+    a.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  a.my_counts = my_counts.data_ptr<int32_t>();
+  a.base = base.data_ptr<int32_t>();
+  a.splits = splits.data_ptr<int32_t>();
+  a.seg = seg.data_ptr<int32_t>();
+  a.L = static_cast<int>(L);
+  a.rank = static_cast<int>(rank);
+  a.align = static_cast<int>(align);
+  a.epoch = static_cast<uint32_t>(epoch);
+  a.status = status.data_ptr<int>();
+  cudaError_t e = teb200::ep_counts(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "ep_counts failed: ", cudaGetErrorString(e));
+}
+
+void ep_push(const at::Tensor& x, const at::Tensor& within, const at::Tensor& base, const OptT& scale, const OptT& probs,
+             std::vector<int64_t> dst_ptrs, std::vector<int64_t> dst_prob_ptrs, std::vector<int64_t> flag_ptrs,
+             const at::Tensor& rowmap, const at::Tensor& counter, int64_t L, int64_t rank, int64_t cap_rows, int64_t epoch,
+             const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous() && (x.size(1) * x.element_size()) % 16 == 0);
+  teb200::EpPushArgs a;
+  a.ep = static_cast<int>(dst_ptrs.size());
+  for (int r = 0; r < a.ep; ++r) {
+    a.dst[r] = reinterpret_cast<void*>(dst_ptrs[r]);
+    a.dst_probs[r] = dst_prob_ptrs.empty() ? nullptr : reinterpret_cast<float*>(dst_prob_ptrs[r]);
+    a.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  a.x = x.data_ptr();
+  a.within = within.data_ptr<int32_t>();
+  a.base = base.data_ptr<int32_t>();
+  a.scale = optr<float>(scale);
+  a.probs = optr<float>(probs);
+  a.rowmap = rowmap.data_ptr<int32_t>();
+  a.cta_counter = reinterpret_cast<unsigned*>(counter.data_ptr<int32_t>());
+  a.T = static_cast<int>(x.size(0));
+  a.L = static_cast<int>(L);
+  a.rank = static_cast<int>(rank);
+  a.vec_per_row = static_cast<int>(x.size(1) * x.element_size() / 16);
+  a.cap_rows = static_cast<int>(cap_rows);
+  a.is_bf16 = x.scalar_type() == at::kBFloat16;
+  a.epoch = static_cast<uint32_t>(epoch);
+  a.status = status.data_ptr<int>();
+  cudaError_t e = teb200::ep_push(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "ep_push failed: ", cudaGetErrorString(e));
+}
+
+void ep_wait(int64_t flags_ptr, int64_t n, int64_t epoch, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  cudaError_t e = teb200::ep_wait(reinterpret_cast<const uint32_t*>(flags_ptr), static_cast<int>(n),
+                                  static_cast<uint32_t>(epoch), status.data_ptr<int>(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "ep_wait failed: ", cudaGetErrorString(e));
+}
+
+void ep_signal(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t epoch, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(status.device());
+  teb200::EpSignalArgs a;
+  a.ep = static_cast<int>(flag_ptrs.size());
+  for (int r = 0; r < a.ep; ++r) a.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  a.rank = static_cast<int>(rank);
+  a.epoch = static_cast<uint32_t>(epoch);
+  cudaError_t e = teb200::ep_signal(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "ep_signal failed: ", cudaGetErrorString(e));
+}
+
+void ep_pull(std::vector<int64_t> src_ptrs, const at::Tensor& rowmap, const OptT& w, const at::Tensor& out, const OptT& g,
+             const OptT& dots, int64_t L, std::vector<int64_t> src_scalar_ptrs, const OptT& out_scalars) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.dim() == 2 && out.is_contiguous() && (out.size(1) * out.element_size()) % 16 == 0);
+  teb200::EpPullArgs a;
+  a.ep = static_cast<int>(src_ptrs.size());
+  for (int r = 0; r < a.ep; ++r) a.src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
+  a.rowmap = rowmap.data_ptr<int32_t>();
+  a.w = optr<float>(w);
+  a.out = out.data_ptr();
+  a.g = g.has_value() && g->defined() ? g->data_ptr() : nullptr;
+  a.dots = optr<float>(dots);
+  if (!src_scalar_ptrs.empty()) {
+    for (int r = 0; r < a.ep; ++r) a.src_s[r] = reinterpret_cast<const float*>(src_scalar_ptrs[r]);
+    a.out_s = optr<float>(out_scalars);
+  }
+  a.T = static_cast<int>(out.size(0));
+  a.L = static_cast<int>(L);
+  a.vec_per_row = static_cast<int>(out.size(1) * out.element_size() / 16);
+  a.is_bf16 = out.scalar_type() == at::kBFloat16;
+  cudaError_t e = teb200::ep_pull(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "ep_pull failed: ", cudaGetErrorString(e));
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("ep_counts", &ep_counts);
+  m.def("ep_push", &ep_push);
+  m.def("ep_wait", &ep_wait);
+  m.def("ep_signal", &ep_signal);
+  m.def("ep_pull", &ep_pull);
   m.def("router_topk", &router_topk);
   m.def("router_topk_bwd", &router_topk_bwd);
   m.def("permute_rows", &permute_rows);

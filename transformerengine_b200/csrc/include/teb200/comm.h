@@ -44,4 +44,55 @@ struct CommGemmArgs {
 
 cudaError_t comm_gemm(const CommGemmArgs& args, cudaStream_t stream);
 
+// ---------------------------------------------------------------- expert-parallel token exchange
+// ep ranks, L local experts per rank (E = ep * L experts).  Pointer arrays index the peer rank;
+// flag arrays hold one epoch counter per source rank.
+struct EpCountsArgs {
+  int32_t* counts_all[kCommMaxRanks] = {};  // on rank r: [ep][E], row s published by rank s
+  uint32_t* flags[kCommMaxRanks] = {};      // on rank r: [ep]
+  const int32_t* my_counts = nullptr;       // [E] rows this rank sends to each expert
+  int32_t* base = nullptr;                  // out [E]: first row of this rank's tokens in the owner's buffer
+  int32_t* splits = nullptr;                // out [L+1]: padded rows per local expert, then the total
+  int32_t* seg = nullptr;                   // out [L][ep+1]: start of each source's segment, then its end
+  int ep = 0, L = 0, rank = 0, align = 1;
+  uint32_t epoch = 0;
+  int* status = nullptr;
+};
+struct EpPushArgs {
+  const void* x = nullptr;                  // [T, H] rows of this rank
+  const int32_t* within = nullptr;          // [T, E]: rank of token t among this rank's tokens of expert e, or -1
+  const int32_t* base = nullptr;            // [E] from the counts kernel
+  const float* scale = nullptr;             // optional [T, E] multiplier applied while copying
+  const float* probs = nullptr;             // optional [T, E] routing weights sent along
+  void* dst[kCommMaxRanks] = {};            // on rank r: [cap_rows, H]
+  float* dst_probs[kCommMaxRanks] = {};     // on rank r: [cap_rows]
+  uint32_t* flags[kCommMaxRanks] = {};      // on rank r: [ep]
+  int32_t* rowmap = nullptr;                // out [T, E]: destination row of every pair, or -1
+  unsigned* cta_counter = nullptr;          // zero-initialised scratch word
+  int T = 0, ep = 0, L = 0, rank = 0, vec_per_row = 0, cap_rows = 0, is_bf16 = 1;
+  uint32_t epoch = 0;
+  int* status = nullptr;
+};
+struct EpSignalArgs {
+  uint32_t* flags[kCommMaxRanks] = {};
+  int ep = 0, rank = 0;
+  uint32_t epoch = 0;
+};
+struct EpPullArgs {
+  const void* src[kCommMaxRanks] = {};      // on rank r: [cap_rows, H] expert-major rows
+  const int32_t* rowmap = nullptr;          // [T, E]
+  const float* w = nullptr;                 // optional [T, E] weights
+  void* out = nullptr;                      // [T, H]
+  const void* g = nullptr;                  // optional [T, H]: with `dots`, dots[t,e] = <g[t], row(t,e)>
+  float* dots = nullptr;                    // optional [T, E]
+  const float* src_s[kCommMaxRanks] = {};   // optional per-row scalars on rank r: [cap_rows]
+  float* out_s = nullptr;                   // optional [T, E]: the scalar of every pair's row
+  int T = 0, ep = 0, L = 0, vec_per_row = 0, is_bf16 = 1;
+};
+cudaError_t ep_counts(const EpCountsArgs& a, cudaStream_t s);
+cudaError_t ep_push(const EpPushArgs& a, cudaStream_t s);
+cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s);
+cudaError_t ep_signal(const EpSignalArgs& a, cudaStream_t s);
+cudaError_t ep_pull(const EpPullArgs& a, cudaStream_t s);
+
 }  // namespace teb200

@@ -4,6 +4,7 @@ tokens exchanged by all-to-all).
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -19,7 +20,8 @@ from ..modules.linear import Linear
 from ..moe import (fused_moe_aux_loss, fused_topk_with_score_function, moe_permute_and_pad_with_probs,
                    moe_unpermute)
 from ..parallel import distributed as D
-from ..parallel.expert_parallel import ep_combine, ep_dispatch
+from ..parallel.expert_parallel import (ep_combine, ep_dispatch, fused_ep_combine, fused_ep_dispatch,
+                                        get_fused_ep)
 from .llama import _FusedCrossEntropy
 
 
@@ -105,7 +107,12 @@ class MoELayer(torch.nn.Module):
         else:
             tpe, total = tokens_per_expert, T
         aux = fused_moe_aux_loss(scores, tpe, total, cfg.num_experts, topk=cfg.topk, coeff=cfg.aux_loss_coeff)
-        if self.ep_size > 1:
+        fused = self.ep_size > 1 and x.is_cuda and os.environ.get("TEB200_FUSED_EP", "1") == "1" \
+            and x.dtype in (torch.bfloat16, torch.float16)
+        if fused:
+            ep = get_fused_ep(self.ep_group, self.local_experts, cfg.hidden_size, T, x.dtype, cfg.pad_align, cfg.topk)
+            xs, ps, m_splits, state = fused_ep_dispatch(x, probs, rmap, ep)
+        elif self.ep_size > 1:
             xs, ps, m_splits, state = ep_dispatch(x, probs, rmap, self.ep_group, self.local_experts, cfg.pad_align)
         else:
             xs, ps, row_id_map, _, padded = moe_permute_and_pad_with_probs(x, probs, rmap, tokens_per_expert,
@@ -114,7 +121,9 @@ class MoELayer(torch.nn.Module):
         h = self.fc1(xs, m_splits)
         a = _ActScaled.apply(h, ps.float(), "swiglu")
         o = self.fc2(a, m_splits)
-        if self.ep_size > 1:
+        if fused:
+            y = fused_ep_combine(o, state)
+        elif self.ep_size > 1:
             y = ep_combine(o, state)
         else:
             y = moe_unpermute(o, row_id_map)

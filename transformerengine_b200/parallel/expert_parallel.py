@@ -110,3 +110,183 @@ def ep_combine(expert_out: torch.Tensor, state: EPState) -> torch.Tensor:
     vals = ret[dest[valid]]
     out = torch.zeros(state.num_tokens, H, dtype=torch.float32, device=expert_out.device)
     return out.index_add(0, tok, vals.float()).to(expert_out.dtype)
+
+
+# ------------------------------------------------------------------------------------------------
+# Fused path: permutation and all-to-all in one kernel over NVLink peer memory
+# ------------------------------------------------------------------------------------------------
+class FusedExpertParallel:
+    """Symmetric-memory workspace and epoch counter of one expert-parallel group.
+
+    ``dispatch`` stores every routed token row straight into the owning rank's expert-major
+    buffer (``csrc/comm/moe_a2a.cu: ep_push_kernel``); ``combine`` reads the expert outputs back
+    from the owners and sums them per token (``ep_pull_kernel``).  All ranks must call the
+    operations in the same order; every call advances a shared epoch that the flags carry.
+    """
+
+    def __init__(self, group, local_experts: int, hidden: int, max_tokens: int, dtype=torch.bfloat16,
+                 align: int = 128, topk: Optional[int] = None):
+        from .comm_gemm import SymmetricBuffer
+
+        self.group, self.L, self.H, self.dtype, self.align = group, local_experts, hidden, dtype, align
+        self.ep, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.E = self.ep * self.L
+        per_tok = min(topk or self.L, self.L)
+        self.cap = self.ep * max_tokens * per_tok + self.L * align
+        self.cap = (self.cap + align - 1) // align * align
+        es = torch.empty(0, dtype=dtype).element_size()
+        row_bytes = hidden * es
+        assert row_bytes % 16 == 0
+        total = 2 * self.cap * row_bytes + 2 * self.cap * 4 + self.ep * self.E * 4 + 3 * 64 * 4 + 8192
+        self.buf = SymmetricBuffer(total, group)
+        t, self.recv_ptrs = self.buf.carve(self.cap * row_bytes)
+        self.recv = t.view(dtype).reshape(self.cap, hidden)
+        t, self.out_ptrs = self.buf.carve(self.cap * row_bytes)
+        self.out_buf = t.view(dtype).reshape(self.cap, hidden)
+        t, self.recv_probs_ptrs = self.buf.carve(self.cap * 4)
+        self.recv_probs = t.view(torch.float32)
+        t, self.out_s_ptrs = self.buf.carve(self.cap * 4)
+        self.out_s = t.view(torch.float32)
+        _, self.counts_ptrs = self.buf.carve(self.ep * self.E * 4)
+        self.flag_ptrs = []
+        self.flag_local = []
+        for _ in range(3):  # counts published, rows pushed, rows ready to be pulled
+            t, p = self.buf.carve(64 * 4)
+            self.flag_ptrs.append(p)
+            self.flag_local.append(p[self.rank])
+        dev = self.recv.device
+        self.base = torch.zeros(self.E, dtype=torch.int32, device=dev)
+        self.splits = torch.zeros(self.L + 1, dtype=torch.int32, device=dev)
+        self.seg = torch.zeros(self.L * (self.ep + 1), dtype=torch.int32, device=dev)
+        self.counter = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.epoch = 0
+        self.C = _ext_get()
+        self.status = self.C.status(dev.index)
+
+    # ---- primitives -----------------------------------------------------------------------------
+    def _push(self, x, within, probs, scale, rowmap, base):
+        self.epoch += 1
+        self.C.ep_push(x.contiguous(), within, base, scale, probs, self.recv_ptrs,
+                       self.recv_probs_ptrs if probs is not None else [], self.flag_ptrs[1], rowmap, self.counter,
+                       self.L, self.rank, self.cap, self.epoch, self.status)
+        self.C.ep_wait(self.flag_local[1], self.ep, self.epoch, self.status)
+
+    def _publish_and_pull(self, rows, rowmap, T, scalars=None):
+        n = rows.shape[0]
+        self.out_buf[:n].copy_(rows)
+        if scalars is not None:
+            self.out_s[:n].copy_(scalars)
+        self.epoch += 1
+        self.C.ep_signal(self.flag_ptrs[2], self.rank, self.epoch, self.status)
+        self.C.ep_wait(self.flag_local[2], self.ep, self.epoch, self.status)
+        out = torch.empty(T, self.H, dtype=self.dtype, device=rows.device)
+        outs = torch.empty(T, self.E, dtype=torch.float32, device=rows.device) if scalars is not None else None
+        self.C.ep_pull(self.out_ptrs, rowmap, None, out, None, None, self.L,
+                       self.out_s_ptrs if scalars is not None else [], outs)
+        return out, outs
+
+    def _take(self, total: int, seg: List[int], with_probs: bool):
+        """Copy the received rows out of the workspace and zero the padding between expert slabs."""
+        xs = self.recv[:total].clone()
+        ps = self.recv_probs[:total].clone() if with_probs else None
+        pos = 0
+        for el in range(self.L):
+            end = seg[el * (self.ep + 1) + self.ep]
+            nxt = seg[(el + 1) * (self.ep + 1)] if el + 1 < self.L else total
+            if nxt > end:
+                xs[end:nxt] = 0
+                if ps is not None:
+                    ps[end:nxt] = 0
+            pos = nxt
+        return xs, ps
+
+
+def _ext_get():
+    from ..ops import _ext
+
+    return _ext.get()
+
+
+@dataclass
+class FusedEPState:
+    ctx: "FusedExpertParallel"
+    within: torch.Tensor      # [T, E] int32
+    rowmap: torch.Tensor      # [T, E] int32
+    total: int
+    seg: List[int]
+    num_tokens: int
+    base: Optional[torch.Tensor] = None   # [E] int32 row bases of this routing
+
+
+class _FusedDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, probs, routing_map, ep: FusedExpertParallel, holder: dict):  # type: ignore[override]
+        m = routing_map.bool()
+        T = x.shape[0]
+        counts = m.sum(0).to(torch.int32)
+        within = torch.where(m, m.long().cumsum(0) - 1, torch.full((), -1, device=x.device)).to(torch.int32).contiguous()
+        ep.epoch += 1
+        ep.C.ep_counts(ep.counts_ptrs, ep.flag_ptrs[0], counts, ep.base, ep.splits, ep.seg, ep.L, ep.rank, ep.align,
+                       ep.epoch, ep.status)
+        rowmap = torch.empty(T, ep.E, dtype=torch.int32, device=x.device)
+        pf = probs.float().contiguous()
+        base = ep.base.clone()  # later dispatches through the same workspace overwrite ep.base
+        ep._push(x, within, pf, None, rowmap, base)
+        host = torch.cat([ep.splits, ep.seg]).tolist()  # one synchronising read: split sizes for the grouped GEMM
+        splits, seg = host[:ep.L + 1], host[ep.L + 1:]
+        total = splits[ep.L]
+        xs, ps = ep._take(total, seg, True)
+        state = FusedEPState(ep, within, rowmap, total, seg, T, base)
+        ctx.state, ctx.pdtype = state, probs.dtype
+        ctx.mark_non_differentiable(rowmap)
+        ctx.save_for_backward(m)
+        holder["state"] = state
+        holder["m_splits"] = [int(v) for v in splits[:ep.L]]
+        return xs, ps.to(probs.dtype), rowmap
+
+    @staticmethod
+    def backward(ctx, g_xs, g_ps, _g_rowmap):  # type: ignore[override]
+        st = ctx.state
+        (m,) = ctx.saved_tensors
+        gp = g_ps.float().contiguous() if g_ps is not None else torch.zeros(st.total, device=g_xs.device)
+        gx, gs = st.ctx._publish_and_pull(g_xs.contiguous(), st.rowmap, st.num_tokens, gp)
+        gprobs = torch.where(m, gs, torch.zeros((), device=gs.device)).to(ctx.pdtype)
+        return gx, gprobs, None, None, None
+
+
+class _FusedCombine(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, expert_out, state: FusedEPState):  # type: ignore[override]
+        ctx.state = state
+        out, _ = state.ctx._publish_and_pull(expert_out.contiguous(), state.rowmap, state.num_tokens)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        st = ctx.state
+        ep = st.ctx
+        scratch = torch.empty_like(st.rowmap)
+        ep._push(g.contiguous(), st.within, None, None, scratch, st.base)
+        gy, _ = ep._take(st.total, st.seg, False)
+        return gy, None
+
+
+def fused_ep_dispatch(x, probs, routing_map, ep: FusedExpertParallel):
+    """Fused counterpart of :func:`ep_dispatch`: returns (tokens, probs, m_splits, state)."""
+    holder: dict = {}
+    xs, ps, _ = _FusedDispatch.apply(x, probs, routing_map, ep, holder)
+    return xs, ps, holder["m_splits"], holder["state"]
+
+
+def fused_ep_combine(expert_out, state: FusedEPState):
+    return _FusedCombine.apply(expert_out, state)
+
+
+_EP_CONTEXTS: dict = {}
+
+
+def get_fused_ep(group, local_experts: int, hidden: int, max_tokens: int, dtype, align: int, topk: int):
+    key = (id(group), local_experts, hidden, max_tokens, dtype, align, topk)
+    if key not in _EP_CONTEXTS:
+        _EP_CONTEXTS[key] = FusedExpertParallel(group, local_experts, hidden, max_tokens, dtype, align, topk)
+    return _EP_CONTEXTS[key]

@@ -394,9 +394,23 @@ void ep_pull(std::vector<int64_t> src_ptrs, const at::Tensor& rowmap, const OptT
   TORCH_CHECK(e == cudaSuccess, "ep_pull failed: ", cudaGetErrorString(e));
 }
 
+void peer_sum(std::vector<int64_t> src_ptrs, const at::Tensor& out) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous() && (out.numel() * out.element_size()) % 16 == 0);
+  teb200::PeerSumArgs a;
+  a.n = static_cast<int>(src_ptrs.size());
+  for (int r = 0; r < a.n; ++r) a.src[r] = reinterpret_cast<const void*>(src_ptrs[r]);
+  a.out = out.data_ptr();
+  a.vecs = static_cast<long long>(out.numel() * out.element_size() / 16);
+  a.is_bf16 = out.scalar_type() == at::kBFloat16;
+  cudaError_t e = teb200::peer_sum(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "peer_sum failed: ", cudaGetErrorString(e));
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("peer_sum", &peer_sum);
   m.def("ep_counts", &ep_counts);
   m.def("ep_push", &ep_push);
   m.def("ep_wait", &ep_wait);

@@ -89,6 +89,14 @@ struct EpPullArgs {
   float* out_s = nullptr;                   // optional [T, E]: the scalar of every pair's row
   int T = 0, ep = 0, L = 0, vec_per_row = 0, is_bf16 = 1;
 };
+// out[i] = sum_r src[r][i] over 16-byte vectors of 16-bit values (fp32 accumulation)
+struct PeerSumArgs {
+  const void* src[kCommMaxRanks] = {};
+  void* out = nullptr;
+  long long vecs = 0;
+  int n = 0, is_bf16 = 1;
+};
+cudaError_t peer_sum(const PeerSumArgs& a, cudaStream_t s);
 cudaError_t ep_counts(const EpCountsArgs& a, cudaStream_t s);
 cudaError_t ep_push(const EpPushArgs& a, cudaStream_t s);
 cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s);

@@ -234,6 +234,8 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if cp == 1:
         return attention_ref(q, k, v, scale=scale, causal=causal, window=window)
+    if cp_comm_type == "p2p" and _fused_ring_ok(q, k, v, window):
+        return fused_ring_attention(q, k, v, cp_group, scale, causal)
     if cp_comm_type == "p2p":
         return _RingAttention.apply(q, k, v, cp_group, cp_global_ranks, scale, causal, window)
     if cp_comm_type == "all_gather":
@@ -262,3 +264,165 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
         oh = attention_ref(qh, kh, vh, scale=scale, attn_mask=mask)
         return _SeqToHeads.apply(oh, cp_group, False)
     raise ValueError(f"unknown cp_comm_type {cp_comm_type}")
+
+
+# ------------------------------------------------------------------------------------------------
+# Fused ring attention on CUDA: the attention kernel reads the peers' K/V over NVLink itself
+# ------------------------------------------------------------------------------------------------
+class FusedRingAttention:
+    """Workspace of context-parallel attention whose K/V exchange is part of the attention kernel.
+
+    Every rank publishes its K/V shard in symmetric memory; the tcgen05 attention kernels
+    (``csrc/attn``) then read each peer's shard directly through TMA descriptors on the peer
+    address (plain, non-multicast loads), so no K/V tensor is ever staged or sent.  Partial
+    results are merged with their log-sum-exp.  In the backward each rank leaves its dK/dV
+    contribution for every owner in symmetric memory and the owner sums them with peer loads
+    (``csrc/comm/peer_reduce.cu``).  (Reference: ``context_parallel.py:1356`` ring of NCCL
+    send/recv around cuDNN attention calls.)
+    """
+
+    def __init__(self, group, b: int, hk: int, s_local: int, d: int, dtype):
+        from ..ops import _ext
+        from .comm_gemm import SymmetricBuffer
+
+        self.group, self.cp, self.rank = group, dist.get_world_size(group), dist.get_rank(group)
+        self.shape = (b, hk, s_local, d)
+        self.dtype = dtype
+        es = torch.empty(0, dtype=dtype).element_size()
+        self.shard_bytes = b * hk * s_local * d * es
+        total = 2 * self.shard_bytes + self.cp * 2 * self.shard_bytes + 4 * 256 + 8192
+        self.buf = SymmetricBuffer(total, group)
+        t, self.kv_ptrs = self.buf.carve(2 * self.shard_bytes)
+        self.kv = t.view(dtype).reshape(2, b, hk, s_local, d)
+        self.kv_off = self.kv_ptrs[self.rank] - self.buf.ptrs[self.rank]
+        t, self.dkv_ptrs = self.buf.carve(self.cp * 2 * self.shard_bytes)
+        self.dkv = t.view(dtype).reshape(self.cp, 2, b, hk, s_local, d)
+        self.flag_ptrs, self.flag_local = [], []
+        for _ in range(4):  # kv published, kv read, dkv published, dkv read
+            _, p = self.buf.carve(64 * 4)
+            self.flag_ptrs.append(p)
+            self.flag_local.append(p[self.rank])
+        self.epoch = 0
+        self.C = _ext.get()
+        self.status = self.C.status(self.kv.device.index)
+        self.es = es
+
+    def barrier(self, which: int):
+        """All ranks have reached this point of the stream (flags in symmetric memory)."""
+        self.epoch += 1
+        self.C.ep_signal(self.flag_ptrs[which], self.rank, self.epoch, self.status)
+        self.C.ep_wait(self.flag_local[which], self.cp, self.epoch, self.status)
+
+    def peer_kv(self, r: int) -> torch.Tensor:
+        """Rank ``r``'s published K/V as a tensor on peer memory (only this library's kernels read it)."""
+        if r == self.rank:
+            return self.kv
+        return self.buf.handle.get_buffer(r, (2,) + self.shape, self.dtype, self.kv_off // self.es)
+
+    def publish(self, k, v):
+        self.kv[0].copy_(k)
+        self.kv[1].copy_(v)
+        self.barrier(0)
+
+
+def _merge(o_run, lse_run, o, lse, rows: slice):
+    lr = lse_run[:, :, rows]
+    new = torch.logaddexp(lr, lse)
+    w0 = torch.nan_to_num(torch.exp(lr - new), nan=0.0)[..., None]
+    w1 = torch.nan_to_num(torch.exp(lse - new), nan=0.0)[..., None]
+    o_run[:, :, rows] = o_run[:, :, rows] * w0 + o.float() * w1
+    lse_run[:, :, rows] = new
+
+
+def _ring_plan(cp: int, me: int, causal: bool, s: int):
+    """(peer, query rows, key rows, causal flag) of every step."""
+    half = s // 2
+    plan = []
+    for step in range(cp):
+        r = (me - step) % cp
+        if not causal:
+            plan.append((r, slice(0, s), slice(0, s), False))
+        elif r == me:
+            plan.append((r, slice(0, s), slice(0, s), True))
+        elif r < me:
+            plan.append((r, slice(0, s), slice(0, half), False))
+        else:
+            plan.append((r, slice(half, s), slice(0, s), False))
+    return plan
+
+
+class _FusedRingAttn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, ws: FusedRingAttention, scale, causal):  # type: ignore[override]
+        from ..ops import flash
+
+        b, hq, s, d = q.shape
+        ws.publish(k, v)
+        o_run = torch.zeros(b, hq, s, d, dtype=torch.float32, device=q.device)
+        lse_run = torch.full((b, hq, s), float("-inf"), dtype=torch.float32, device=q.device)
+        for r, qrows, krows, csl in _ring_plan(ws.cp, ws.rank, causal, s):
+            kv = ws.peer_kv(r)
+            o, lse = flash.flash_forward_lse(q[:, :, qrows], kv[0][:, :, krows], kv[1][:, :, krows], scale, csl)
+            _merge(o_run, lse_run, o, lse, qrows)
+        ws.barrier(1)  # every rank has finished reading: the shards may be overwritten
+        out = o_run.to(q.dtype)
+        ctx.save_for_backward(q, k, v, out, lse_run)
+        ctx.ws, ctx.scale, ctx.causal = ws, scale, causal
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):  # type: ignore[override]
+        q, k, v, out, lse = ctx.saved_tensors
+        ws, causal = ctx.ws, ctx.causal
+        C_ = ws.C
+        b, hq, s, d = q.shape
+        sc = float(ctx.scale) if ctx.scale is not None else d ** -0.5
+        dout = dout.contiguous()
+        ws.publish(k, v)
+        ws.dkv.zero_()
+        dq = torch.zeros(b, hq, s, d, dtype=torch.float32, device=q.device)
+        for r, qrows, krows, csl in _ring_plan(ws.cp, ws.rank, causal, s):
+            kv = ws.peer_kv(r)
+            qs, os_, dos = q[:, :, qrows], out[:, :, qrows], dout[:, :, qrows]
+            n = qs.shape[2]
+            s_pad = (n + 63) // 64 * 64
+            lse_s = torch.zeros(b, hq, s_pad, dtype=torch.float32, device=q.device)
+            lse_s[:, :, :n] = lse[:, :, qrows]
+            delta = torch.empty_like(lse_s)
+            dq_s = torch.empty(b, hq, n, d, dtype=q.dtype, device=q.device)
+            dk_s, dv_s = ws.dkv[r, 0][:, :, krows], ws.dkv[r, 1][:, :, krows]
+            C_.flash_bwd(dos, qs, kv[0][:, :, krows], kv[1][:, :, krows], os_, lse_s, delta, dq_s, dk_s, dv_s, sc, csl,
+                         True, ws.status)
+            dq[:, :, qrows] += dq_s.float()
+        ws.barrier(1)
+        ws.barrier(2)  # every rank's partial dK/dV are in place
+        dkv = torch.empty((2,) + tuple(k.shape), dtype=k.dtype, device=k.device)
+        slot = ws.rank * 2 * ws.shard_bytes
+        C_.peer_sum([p + slot for p in ws.dkv_ptrs], dkv)
+        ws.barrier(3)  # partial buffers may be reused
+        return dq.to(q.dtype), dkv[0], dkv[1], None, None, None
+
+
+_RING_WS: dict = {}
+
+
+def fused_ring_attention(q, k, v, cp_group, scale, causal):
+    b, hk, s, d = k.shape
+    key = (id(cp_group), b, hk, s, d, k.dtype)
+    if key not in _RING_WS:
+        _RING_WS[key] = FusedRingAttention(cp_group, b, hk, s, d, k.dtype)
+    return _FusedRingAttn.apply(q, k, v, _RING_WS[key], scale, causal)
+
+
+def _fused_ring_ok(q, k, v, window) -> bool:
+    import os
+
+    from ..ops import _ext
+
+    if os.environ.get("TEB200_FUSED_CP", "1") != "1" or not _ext.use_cuda(q):
+        return False
+    if not hasattr(_ext.get(), "flash_fwd") or not hasattr(_ext.get(), "peer_sum"):
+        return False
+    no_window = window is None or (window[0] < 0 and window[1] <= 0)
+    return (q.dtype in (torch.bfloat16, torch.float16) and q.shape[-1] == 128 and v.shape[-1] == 128
+            and q.shape[2] == k.shape[2] and q.shape[2] % 128 == 0 and no_window)

@@ -196,3 +196,44 @@ def test_rope(interleaved):
     assert _rel(y, yr) < 1e-2
     g = ops.rope_apply(y, f, interleaved=interleaved, backward=True)
     assert _rel(g, x) < 2e-2  # the rotation is orthogonal: backward undoes forward
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtypes", [("e4m3", "e4m3"), ("e5m2", "e4m3")])
+def test_fp8_per_tensor_gemm_matches_dequantized_matmul(dtypes):
+    import transformerengine_b200 as te
+    from transformerengine_b200 import ops
+    from transformerengine_b200.tensor.float8 import Float8CurrentScalingQuantizer
+
+    torch.manual_seed(0)
+    M, N, K = 384, 640, 512
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    dt = {"e4m3": torch.float8_e4m3fn, "e5m2": torch.float8_e5m2}
+    qa = Float8CurrentScalingQuantizer(dt[dtypes[0]], device="cuda")(a)
+    qb = Float8CurrentScalingQuantizer(dt[dtypes[1]], device="cuda")(b)
+    out = ops.gemm_nt(ops.as_operand(qa), ops.as_operand(qb), out_dtype=torch.float32)
+    te.ops.check_status()
+    ref = qa.dequantize().float() @ qb.dequantize().float().t()
+    err = (out - ref).abs().max().item() / ref.abs().max().item()
+    assert err < 5e-3, err
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("recipe_name", ["DelayedScaling", "Float8CurrentScaling", "Float8BlockScaling"])
+def test_linear_under_fp8_recipes_on_gpu(recipe_name):
+    import transformerengine_b200 as te
+
+    torch.manual_seed(1)
+    lin = te.Linear(512, 768, bias=True, params_dtype=torch.bfloat16, device="cuda")
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    recipe = getattr(te.recipe, recipe_name)()
+    for _ in range(2):  # the second pass of delayed scaling uses the recorded amax
+        with te.autocast(enabled=True, recipe=recipe):
+            y = lin(x)
+        y.float().square().mean().backward()
+    te.ops.check_status()
+    ref = x.detach().float() @ lin.weight.detach().float().t() + lin.bias.detach().float()
+    rel = (y.float() - ref).norm() / ref.norm()
+    assert rel < 0.08, rel.item()
+    assert torch.isfinite(x.grad.float()).all() and torch.isfinite(lin.weight.grad.float()).all()

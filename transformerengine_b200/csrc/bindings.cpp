@@ -52,7 +52,7 @@ at::Tensor& status_tensor(int device) {
 
 at::Tensor status(int device) { return status_tensor(device); }
 
-// kind: 0 = 16-bit, 1 = mxfp8, 2 = nvfp4.  a [M,K] (or [K,M] when a_mn), b [N,K] (or [K,N]); d [M,N].
+// kind: 0 = 16-bit, 1 = mxfp8, 2 = nvfp4, 3 = per-tensor fp8.  a [M,K] (or [K,M] when a_mn), b [N,K] (or [K,N]); d [M,N].
 void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const OptT& sfa, const OptT& sfb,
           const OptT& bias, const OptT& aux, int epilogue, bool accumulate, bool a_e5m2, bool b_e5m2, bool a_mn,
           bool b_mn, double alpha, const OptT& alpha_dev, const OptT& group_offsets, int num_groups, int sm_count,
@@ -74,7 +74,7 @@ void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, con
                 "16-bit gemm needs matching bf16/fp16 operands");
     g.lda = a.stride(0);
     g.ldb = b.stride(0);
-  } else if (kind == 1) {
+  } else if (kind == 1 || kind == 3) {
     g.K = static_cast<int>(a.size(1));
     g.a_dtype = a_e5m2 ? teb200::kFloat8E5M2 : teb200::kFloat8E4M3;
     g.b_dtype = b_e5m2 ? teb200::kFloat8E5M2 : teb200::kFloat8E4M3;
@@ -106,8 +106,10 @@ void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, con
   g.group_offsets = ptr<int32_t>(group_offsets);
   g.sm_count = sm_count;
   g.status = status_tensor(a.get_device()).data_ptr<int>();
-  cudaError_t e = kind == 0 ? teb200::gemm_bf16(g, stream())
-                            : (kind == 1 ? teb200::gemm_mxfp8(g, stream()) : teb200::gemm_nvfp4(g, stream()));
+  cudaError_t e = kind == 0   ? teb200::gemm_bf16(g, stream())
+                  : kind == 1 ? teb200::gemm_mxfp8(g, stream())
+                  : kind == 3 ? teb200::gemm_fp8(g, stream())
+                              : teb200::gemm_nvfp4(g, stream());
   check(e, "gemm");
 }
 

@@ -156,6 +156,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const int kbyte0 = kb * C::kBlockKBytes;
             tma_load_2d(sa, &tmap_a, &full_bar[stage], kbyte0, ti.m0);
             tma_load_2d(sb, &tmap_b, &full_bar[stage], kbyte0, ti.b_row0);
+            if constexpr (KIND != kKindF8) {
             uint8_t* ssfa = sb + C::kBBytes;
             uint8_t* ssfb = ssfa + C::kSfaBytes;
             // one stage covers kSfTileBytes/512 consecutive 4-scale tiles along K
@@ -168,6 +169,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
               bulk_load_1d(ssfb + j * C::kSfTileBytes,
                            p.sfb + (static_cast<size_t>(ti.sfb_row_tile + j) * p.sf_k_tiles + kt) * 512,
                            C::kSfTileBytes, &full_bar[stage]);
+            }
           }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
@@ -207,6 +209,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               umma_f16(tmem_d, adesc + k * astep, bdesc + k * bstep, p.idesc, (kb | k) != 0);
+          } else if constexpr (KIND == kKindF8) {
+            const uint64_t adesc = umma_desc_k_sw128(sa);
+            const uint64_t bdesc = umma_desc_k_sw128(sb);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) umma_f8(tmem_d, adesc + k * 2, bdesc + k * 2, p.idesc, (kb | k) != 0);
           } else {
             const uint32_t ssfa = sb + C::kBBytes;
             const uint32_t ssfb = ssfa + C::kSfaBytes;
@@ -401,9 +408,9 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
                              : make_tensor_map_2d(&tb, a.b, a.b_dtype, b_rows, a.K, a.ldb, BN, 64, true));
   } else {
     // operands addressed as bytes: fp8 K bytes per row, fp4 K/2 bytes per row
-    const uint64_t kbytes = KIND == kKindMxf8 ? a.K : a.K / 2;
-    const uint64_t lda = KIND == kKindMxf8 ? a.lda : a.lda / 2;
-    const uint64_t ldb = KIND == kKindMxf8 ? a.ldb : a.ldb / 2;
+    const uint64_t kbytes = KIND == kKindNvf4 ? a.K / 2 : a.K;
+    const uint64_t lda = KIND == kKindNvf4 ? a.lda / 2 : a.lda;
+    const uint64_t ldb = KIND == kKindNvf4 ? a.ldb / 2 : a.ldb;
     ok = make_tensor_map_2d(&ta, a.a, kByte, a.M, kbytes, lda, kBlockM, 128, true) &&
          make_tensor_map_2d(&tb, a.b, kByte, b_rows, kbytes, ldb, BN, 128, true);
   }
@@ -419,7 +426,7 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
   p.idesc = make_idesc(KIND, a.a_dtype, a.b_dtype, BN, a.a_mn_major, a.b_mn_major);
   p.num_groups = a.num_groups;
   const int sf_per_elem = KIND == kKindMxf8 ? 32 : 16;
-  p.sf_k_tiles = KIND == kKindF16 ? 0 : ((a.K + sf_per_elem - 1) / sf_per_elem + 3) / 4;
+  p.sf_k_tiles = (KIND == kKindF16 || KIND == kKindF8) ? 0 : ((a.K + sf_per_elem - 1) / sf_per_elem + 3) / 4;
 
   static bool attr_set = false;
   if (!attr_set) {
@@ -493,6 +500,12 @@ cudaError_t gemm_mxfp8(const GemmArgs& a, cudaStream_t stream) {
   if (a.K <= 0 || a.K % 32 != 0) return cudaErrorInvalidValue;
   if (use_pairs() && gemm_pair_supported(a, true)) return gemm_pair_mxfp8(a, stream);
   return pick_bn(a.N, a.M, true) == 128 ? launch<kKindMxf8, 128>(a, stream) : launch<kKindMxf8, 256>(a, stream);
+}
+
+cudaError_t gemm_fp8(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return cudaSuccess;
+  if (a.K <= 0 || a.K % 16 != 0) return cudaErrorInvalidValue;  // TMA row pitch of 16 bytes
+  return pick_bn(a.N, a.M, false) == 128 ? launch<kKindF8, 128>(a, stream) : launch<kKindF8, 256>(a, stream);
 }
 
 cudaError_t gemm_nvfp4(const GemmArgs& a, cudaStream_t stream) {

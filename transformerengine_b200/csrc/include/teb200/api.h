@@ -50,6 +50,7 @@ struct GemmArgs {
 cudaError_t gemm_bf16(const GemmArgs& args, cudaStream_t stream);    // fp16 or bf16 operands
 cudaError_t gemm_mxfp8(const GemmArgs& args, cudaStream_t stream);   // e4m3/e5m2 + ue8m0 per 32
 cudaError_t gemm_nvfp4(const GemmArgs& args, cudaStream_t stream);   // e2m1 + e4m3 per 16
+cudaError_t gemm_fp8(const GemmArgs& args, cudaStream_t stream);     // e4m3/e5m2, per-tensor scales folded into alpha
 
 // CTA-pair (cta_group::2) variants, 256x256 tile per pair of SMs
 bool gemm_pair_supported(const GemmArgs& args, bool mxfp8);

@@ -14,7 +14,7 @@ constexpr int kBlockM = 128;
 constexpr int kNumThreads = 192;
 constexpr int kGroupM = 8;  // m-blocks per scheduling group (L2 reuse of B panels)
 
-enum Kind : int { kKindF16 = 0, kKindMxf8 = 1, kKindNvf4 = 2 };
+enum Kind : int { kKindF16 = 0, kKindMxf8 = 1, kKindNvf4 = 2, kKindF8 = 3 };  // F8: per-tensor scaled e4m3/e5m2
 
 struct KernelParams {
   void* d;
@@ -54,7 +54,7 @@ struct Cfg {
   static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes > 8 ? 8 : (227 * 1024 - 2048) / kStageBytes;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align slack*/ + 1024 /*barriers*/;
   // elements of K covered by one stage / one MMA
-  static constexpr int kBlockK = (KIND == kKindF16) ? 64 : (KIND == kKindMxf8 ? 128 : 256);
+  static constexpr int kBlockK = (KIND == kKindF16) ? 64 : (KIND == kKindNvf4 ? 256 : 128);
   static constexpr int kMmaPerStage = 4;
 };
 
@@ -103,6 +103,10 @@ inline uint32_t make_idesc(int kind, int a_dtype, int b_dtype, int BN, bool a_mn
     d |= fmt << 10; // B format
     d |= (a_mn ? 1u : 0u) << 15;
     d |= (b_mn ? 1u : 0u) << 16;
+  } else if (kind == kKindF8) {
+    d |= 1u << 4;  // fp32 accumulator
+    d |= (a_dtype == kFloat8E5M2 ? 1u : 0u) << 7;
+    d |= (b_dtype == kFloat8E5M2 ? 1u : 0u) << 10;
   } else if (kind == kKindMxf8) {
     d |= (a_dtype == kFloat8E5M2 ? 1u : 0u) << 7;
     d |= (b_dtype == kFloat8E5M2 ? 1u : 0u) << 10;

@@ -20,7 +20,7 @@ import torch
 from . import _ext
 from .ref import quant as Q
 
-KIND_F16, KIND_MXFP8, KIND_NVFP4 = 0, 1, 2
+KIND_F16, KIND_MXFP8, KIND_NVFP4, KIND_FP8 = 0, 1, 2, 3
 EPI_NONE, EPI_BIAS, EPI_GELU, EPI_DGELU = 0, 1, 2, 3
 
 
@@ -197,6 +197,13 @@ def _gemm_cuda(a, b, out, bias, accumulate, epilogue, aux, alpha, group_offsets,
         ad, bd = a.data, b.data
         sfa, sfb = a.scale, b.scale
         a_mn = b_mn = False
+    elif kinds == {"fp8"} and a.k % 16 == 0 and a.data.is_contiguous() and b.data.is_contiguous():
+        kind = KIND_FP8
+        ad, bd = a.data.view(torch.uint8), b.data.view(torch.uint8)
+        sfa = sfb = None
+        a_mn = b_mn = False
+        # per-tensor decode scales folded into the epilogue
+        alpha_dev = (a.scale.float().reshape(-1)[:1] * b.scale.float().reshape(-1)[:1]).contiguous()
     elif kinds == {"nvfp4"} and a.k % 256 == 0:
         kind = KIND_NVFP4
         ad, bd = a.data, b.data

@@ -144,55 +144,64 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader only)
-    if (leader && lane == 0) {
+    // The whole warp walks the loop so that every value is warp-uniform (descriptors stay in
+    // uniform registers); one elected lane issues the tcgen05 instructions.
+    if (leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
       int mb, nb;
+      const uint64_t adesc0 = umma_desc_k_sw128(smem_u32(smem));
+      const uint32_t e_bar0 = map_to_cta(smem_u32(&empty_bar[0]), 0), e_bar1 = map_to_cta(smem_u32(&empty_bar[0]), 1);
+      const uint32_t t_bar0 = map_to_cta(smem_u32(&tfull_bar[0]), 0), t_bar1 = map_to_cta(smem_u32(&tfull_bar[0]), 1);
       for (int t = pair; ok && pair_tile(p, t, mb, nb); t += num_pairs) {
-        if (!mbar_wait_cluster(&tempty_bar[acc], acc_phase ^ 1)) {
-          if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait_cluster(&tempty_bar[acc], acc_phase ^ 1))) {
+          if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * PN;
         for (int kb = 0; kb < num_k_blocks; ++kb) {
-          if (!mbar_wait_cluster(&full_bar[stage], phase)) {
-            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+          if (!__all_sync(0xffffffffu, mbar_wait_cluster(&full_bar[stage], phase))) {
+            if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
-          const uint32_t sb = sa + C::kABytes;
-          const uint64_t adesc = umma_desc_k_sw128(sa);
-          const uint64_t bdesc = umma_desc_k_sw128(sb);
-          if constexpr (KIND == kKindF16) {
+          const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * (C::kStageBytes >> 4));
+          const uint64_t bdesc = adesc + (C::kABytes >> 4);
+          if (elect_one()) {
+            if constexpr (KIND == kKindF16) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_f16_pair(tmem_d, adesc + k * 2, bdesc + k * 2, p.k.idesc, (kb | k) != 0);
-          } else {
-            const uint32_t ssfa = sb + C::kBBytes;
-            const uint32_t ssfb = ssfa + C::kSfaBytes;
-            utccp_sf_pair(tmem_sfa, umma_desc_sf(ssfa));
+              for (int k = 0; k < 4; ++k)
+                umma_f16_pair(tmem_d, adesc + k * 2, bdesc + k * 2, p.k.idesc, (kb | k) != 0);
+            } else {
+              const uint32_t ssfa = smem_u32(smem + stage * C::kStageBytes) + C::kABytes + C::kBBytes;
+              const uint32_t ssfb = ssfa + C::kSfaBytes;
+              utccp_sf_pair(tmem_sfa, umma_desc_sf(ssfa));
 #pragma unroll
-            for (int j = 0; j < PN / 128; ++j) utccp_sf_pair(tmem_sfb + j * 4, umma_desc_sf(ssfb + j * 512));
+              for (int j = 0; j < PN / 128; ++j) utccp_sf_pair(tmem_sfb + j * 4, umma_desc_sf(ssfb + j * 512));
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t idesc = p.k.idesc | (uint32_t(k) << 29) | (uint32_t(k) << 4);
-              umma_mxf8_pair(tmem_d, adesc + k * 2, bdesc + k * 2, idesc, (kb | k) != 0, tmem_sfa, tmem_sfb);
+              for (int k = 0; k < 4; ++k) {
+                const uint32_t idesc = p.k.idesc | (uint32_t(k) << 29) | (uint32_t(k) << 4);
+                umma_mxf8_pair(tmem_d, adesc + k * 2, bdesc + k * 2, idesc, (kb | k) != 0, tmem_sfa, tmem_sfb);
+              }
             }
+            // the stage may be refilled in both CTAs once these MMAs have read it
+            tc_commit_pair(e_bar0 + stage * 8);
+            tc_commit_pair(e_bar1 + stage * 8);
           }
-          // the stage may be refilled in both CTAs once these MMAs have read it
-          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 0));
-          tc_commit_pair(map_to_cta(smem_u32(&empty_bar[stage]), 1));
+          __syncwarp();
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        tc_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 0));
-        tc_commit_pair(map_to_cta(smem_u32(&tfull_bar[acc]), 1));
+        if (elect_one()) {
+          tc_commit_pair(t_bar0 + acc * 8);
+          tc_commit_pair(t_bar1 + acc * 8);
+        }
+        __syncwarp();
         if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }

@@ -177,7 +177,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (values stay warp-uniform); one elected lane issues.
+    {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -185,19 +186,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       bool ok = true;
       TileInfo ti;
       for (int tile = blockIdx.x; ok && get_tile(p, BN, tile, ti); tile += gridDim.x) {
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
-          atomicCAS(p.status, 0, kTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait(&tempty_bar[acc], acc_phase ^ 1))) {
+          if (lane == 0) atomicCAS(p.status, 0, kTimeoutMma);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < num_k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase)) {
-            atomicCAS(p.status, 0, kTimeoutMma);
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) {
+            if (lane == 0) atomicCAS(p.status, 0, kTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after();
+          if (elect_one()) {
           const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
           const uint32_t sb = sa + C::kABytes;
           if constexpr (KIND == kKindF16) {
@@ -241,10 +243,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
           tc_commit(&empty_bar[stage]);  // stage reusable once these MMAs have read it
+          }
+          __syncwarp();
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&tfull_bar[acc]);
+        if (elect_one()) tc_commit(&tfull_bar[acc]);
+        __syncwarp();
         if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }

@@ -375,7 +375,8 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the loop (values stay warp-uniform); one elected lane issues.
+    {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -383,19 +384,20 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       Tile ti;
       for (int t = gemm_cta; ok && comm_tile(p, t, ti); t += gemm_ctas) {
-        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1)) {
-          if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+        if (!__all_sync(0xffffffffu, mbar_wait(&tempty_bar[acc], acc_phase ^ 1))) {
+          if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + acc * BN;
         for (int kb = 0; kb < num_k_blocks; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase)) {
-            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
+          if (!__all_sync(0xffffffffu, mbar_wait(&full_bar[stage], phase))) {
+            if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutMma);
             ok = false;
             break;
           }
           tc_fence_after();
+          if (elect_one()) {
           const uint32_t sa = smem_u32(smem + stage * C::kStageBytes);
           const uint32_t sb = sa + C::kABytes;
           const uint64_t adesc = umma_desc_k_sw128(sa);
@@ -416,10 +418,13 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
           tc_commit(&empty_bar[stage]);
+          }
+          __syncwarp();
           if (++stage == NS) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        tc_commit(&tfull_bar[acc]);
+        if (elect_one()) tc_commit(&tfull_bar[acc]);
+        __syncwarp();
         if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }

@@ -58,10 +58,120 @@ __global__ void rope_kernel(const RopeArgs a) {
   }
 }
 
+// Vector path (16-bit types, d_rot % 16 == 0, 16-byte aligned rows): one block per token, one
+// thread per (head, 8-element group); both operands of a rotation pair are read by the thread
+// that writes them, so the kernel is safe in place and needs no staging.
+template <bool BF>
+__global__ void rope_vec_kernel(const RopeArgs a) {
+  extern __shared__ float cs[];  // cos[d_rot], sin[d_rot]
+  const int si = blockIdx.x, bi = blockIdx.y;
+  int pos = si;
+  if (a.cp_size > 1) {
+    const int half = a.s / 2;
+    pos = si < half ? si + a.cp_rank * half : si + a.s * a.cp_size - (a.cp_rank + 1) * half - half;
+  }
+  pos += a.pos_offset + (a.start_positions ? a.start_positions[bi] : 0);
+  for (int j = threadIdx.x; j < a.d_rot; j += blockDim.x) {
+    float sn, c;
+    sincosf(a.freqs[static_cast<size_t>(pos) * a.d_rot + j], &sn, &c);
+    cs[j] = c;
+    cs[a.d_rot + j] = sn;
+  }
+  __syncthreads();
+  const uint16_t* x = static_cast<const uint16_t*>(a.x) + si * a.stride_s + bi * a.stride_b;
+  uint16_t* out = static_cast<uint16_t*>(a.out) + si * a.stride_s + bi * a.stride_b;
+  const int half = a.d_rot / 2;
+  auto unpack = [](uint32_t w, float& lo, float& hi) {
+    if (BF) {
+      lo = __uint_as_float(w << 16);
+      hi = __uint_as_float(w & 0xffff0000u);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w);
+      lo = __low2float(h);
+      hi = __high2float(h);
+    }
+  };
+  auto pack = [](float lo, float hi) { return BF ? pack_bf16x2(lo, hi) : pack_f16x2(lo, hi); };
+  if (!a.interleaved) {
+    // out[j] = x[j] cos[j] - x[j+half] sin[j];  out[j+half] = x[j+half] cos[j+half] + x[j] sin[j+half]
+    const int groups = half / 8;
+    for (int it = threadIdx.x; it < a.h * groups; it += blockDim.x) {
+      const int hi = it / groups, j0 = (it % groups) * 8;
+      const uint16_t* xh = x + hi * a.stride_h;
+      uint16_t* oh = out + hi * a.stride_h;
+      const uint4 va = *reinterpret_cast<const uint4*>(xh + j0);
+      const uint4 vb = *reinterpret_cast<const uint4*>(xh + j0 + half);
+      const uint32_t* wa = reinterpret_cast<const uint32_t*>(&va);
+      const uint32_t* wb = reinterpret_cast<const uint32_t*>(&vb);
+      uint4 oa, ob;
+      uint32_t* pa = reinterpret_cast<uint32_t*>(&oa);
+      uint32_t* pb = reinterpret_cast<uint32_t*>(&ob);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float a0, a1, b0, b1;
+        unpack(wa[k], a0, a1);
+        unpack(wb[k], b0, b1);
+        const int j = j0 + 2 * k;
+        const float* sn = cs + a.d_rot;
+        if (!a.backward) {
+          pa[k] = pack(a0 * cs[j] - b0 * sn[j], a1 * cs[j + 1] - b1 * sn[j + 1]);
+          pb[k] = pack(b0 * cs[j + half] + a0 * sn[j + half], b1 * cs[j + half + 1] + a1 * sn[j + half + 1]);
+        } else {  // transpose of the forward map
+          pa[k] = pack(a0 * cs[j] + b0 * sn[j + half], a1 * cs[j + 1] + b1 * sn[j + half + 1]);
+          pb[k] = pack(b0 * cs[j + half] - a0 * sn[j], b1 * cs[j + half + 1] - a1 * sn[j + 1]);
+        }
+      }
+      *reinterpret_cast<uint4*>(oh + j0) = oa;
+      *reinterpret_cast<uint4*>(oh + j0 + half) = ob;
+    }
+  } else {
+    // pairs (2i, 2i+1): out[2i] = x[2i] cos - x[2i+1] sin;  out[2i+1] = x[2i+1] cos + x[2i] sin
+    const int groups = a.d_rot / 8;
+    for (int it = threadIdx.x; it < a.h * groups; it += blockDim.x) {
+      const int hi = it / groups, j0 = (it % groups) * 8;
+      const uint16_t* xh = x + hi * a.stride_h;
+      uint16_t* oh = out + hi * a.stride_h;
+      const uint4 va = *reinterpret_cast<const uint4*>(xh + j0);
+      const uint32_t* wa = reinterpret_cast<const uint32_t*>(&va);
+      uint4 oa;
+      uint32_t* pa = reinterpret_cast<uint32_t*>(&oa);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float e, o;
+        unpack(wa[k], e, o);
+        const int j = j0 + 2 * k;
+        const float* sn = cs + a.d_rot;
+        if (!a.backward) pa[k] = pack(e * cs[j] - o * sn[j], o * cs[j + 1] + e * sn[j + 1]);
+        else pa[k] = pack(e * cs[j] + o * sn[j + 1], o * cs[j + 1] - e * sn[j]);
+      }
+      *reinterpret_cast<uint4*>(oh + j0) = oa;
+    }
+  }
+  if (a.out != a.x && a.d_rot < a.d) {  // the part that is not rotated is copied
+    const int rest = a.d - a.d_rot;
+    for (int it = threadIdx.x; it < a.h * rest; it += blockDim.x) {
+      const int hi = it / rest, j = a.d_rot + it % rest;
+      out[hi * a.stride_h + j] = x[hi * a.stride_h + j];
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t rope_apply(const RopeArgs& a, cudaStream_t s) {
   if (a.s <= 0 || a.b <= 0) return cudaSuccess;
+  const bool vec = (a.dtype == kBFloat16 || a.dtype == kFloat16) && a.d_rot % 16 == 0 && a.stride_s % 8 == 0 &&
+                   a.stride_b % 8 == 0 && a.stride_h % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+  if (vec) {
+    dim3 grid(a.s, a.b);
+    const size_t sm = 2 * static_cast<size_t>(a.d_rot) * sizeof(float);
+    const int work = a.h * (a.interleaved ? a.d_rot / 8 : a.d_rot / 16);
+    const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
+    if (a.dtype == kBFloat16) rope_vec_kernel<true><<<grid, threads, sm, s>>>(a);
+    else rope_vec_kernel<false><<<grid, threads, sm, s>>>(a);
+    return cudaGetLastError();
+  }
   const size_t smem = (2 * static_cast<size_t>(a.d_rot) + static_cast<size_t>(a.h) * a.d) * sizeof(float);
   dim3 grid(a.s, a.b);
   cudaError_t e = cudaSuccess;

@@ -48,7 +48,7 @@ class _FlashFunc(torch.autograd.Function):
         q, k, v = _prep(q), _prep(k), _prep(v)
         b, h, sq, d = q.shape
         out = _empty_out(q, out_format)
-        s_pad = (sq + 63) // 64 * 64
+        s_pad = (sq + 127) // 128 * 128  # the backward reads lse / delta in blocks of 128 rows
         lse = torch.empty(b, h, s_pad, dtype=torch.float32, device=q.device)
         sc = float(scale) if scale is not None else d ** -0.5
         C_.flash_fwd(q, k, v, out, lse, sc, bool(causal), bool(bottom_right), C_.status(q.device.index))
@@ -81,7 +81,7 @@ def flash_forward_lse(q, k, v, scale, causal, bottom_right=True):
     q, k, v = _prep(q), _prep(k), _prep(v)
     b, h, sq, d = q.shape
     out = _empty_out(q, "bhsd")
-    s_pad = (sq + 63) // 64 * 64
+    s_pad = (sq + 127) // 128 * 128  # the backward reads lse / delta in blocks of 128 rows
     lse = torch.empty(b, h, s_pad, dtype=torch.float32, device=q.device)
     sc = float(scale) if scale is not None else d ** -0.5
     C_.flash_fwd(q, k, v, out, lse, sc, bool(causal), bool(bottom_right), C_.status(q.device.index))

@@ -385,7 +385,7 @@ class _FusedRingAttn(torch.autograd.Function):
             kv = ws.peer_kv(r)
             qs, os_, dos = q[:, :, qrows], out[:, :, qrows], dout[:, :, qrows]
             n = qs.shape[2]
-            s_pad = (n + 63) // 64 * 64
+            s_pad = (n + 127) // 128 * 128
             lse_s = torch.zeros(b, hq, s_pad, dtype=torch.float32, device=q.device)
             lse_s[:, :, :n] = lse[:, :, qrows]
             delta = torch.empty_like(lse_s)

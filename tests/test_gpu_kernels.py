@@ -237,3 +237,29 @@ def test_linear_under_fp8_recipes_on_gpu(recipe_name):
     rel = (y.float() - ref).norm() / ref.norm()
     assert rel < 0.08, rel.item()
     assert torch.isfinite(x.grad.float()).all() and torch.isfinite(lin.weight.grad.float()).all()
+
+
+@pytest.mark.gpu
+def test_softmax_and_dropout_kernels():
+    from transformerengine_b200.ops import misc
+
+    torch.manual_seed(0)
+    b, h, sq, sk = 2, 3, 40, 72
+    s = torch.randn(b, h, sq, sk, device="cuda", dtype=torch.bfloat16)
+    mask = torch.rand(b, 1, sq, sk, device="cuda") < 0.2
+    for causal in (False, True):
+        p = misc.scaled_masked_softmax(s, mask, 0.7, causal)
+        ref = misc.scaled_masked_softmax(s.cpu(), mask.cpu(), 0.7, causal)
+        assert torch.allclose(p.cpu().float(), ref.float(), atol=1e-2)
+    dp = torch.randn_like(p)
+    dx = misc.softmax_bwd(p, dp, 0.7)
+    assert torch.allclose(dx.cpu().float(), misc.softmax_bwd(p.cpu(), dp.cpu(), 0.7).float(), atol=2e-2)
+    x = torch.randn(1000, 37, device="cuda", dtype=torch.bfloat16)
+    y, keep = misc.dropout_fwd(x, 0.25)
+    frac = (y != 0).float().mean().item()
+    assert 0.70 < frac < 0.80
+    kept = y != 0
+    assert torch.allclose(y[kept].float(), x[kept].float() / 0.75, rtol=1e-2)
+    g = misc.dropout_bwd(torch.ones_like(x), keep, 0.25)
+    nz = x != 0
+    assert torch.equal((g != 0)[nz], kept[nz])

@@ -407,9 +407,69 @@ void peer_sum(std::vector<int64_t> src_ptrs, const at::Tensor& out) {
   TORCH_CHECK(e == cudaSuccess, "peer_sum failed: ", cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------------------- softmax / dropout
+at::Tensor softmax_fwd(const at::Tensor& x, const OptT& mask, double scale, bool causal, int64_t sq, int64_t heads) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous());
+  at::Tensor y = at::empty_like(x);
+  teb200::SoftmaxArgs a;
+  a.x = x.data_ptr(); a.y = y.data_ptr();
+  a.mask = optr<uint8_t>(mask);
+  a.dtype = dtype_code(x);
+  a.cols = static_cast<int>(x.size(-1));
+  a.rows = x.numel() / a.cols;
+  a.sq = static_cast<int>(sq); a.heads = static_cast<int>(heads);
+  a.scale = static_cast<float>(scale);
+  a.causal = causal ? 1 : 0;
+  cudaError_t e = teb200::softmax_fwd(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "softmax_fwd failed: ", cudaGetErrorString(e));
+  return y;
+}
+
+at::Tensor softmax_bwd(const at::Tensor& probs, const at::Tensor& dprobs, double scale) {
+  c10::cuda::CUDAGuard guard(probs.device());
+  TORCH_CHECK(probs.is_contiguous() && dprobs.is_contiguous() && probs.scalar_type() == dprobs.scalar_type());
+  at::Tensor dx = at::empty_like(probs);
+  teb200::SoftmaxArgs a;
+  a.x = probs.data_ptr(); a.dy = dprobs.data_ptr(); a.y = dx.data_ptr();
+  a.dtype = dtype_code(probs);
+  a.cols = static_cast<int>(probs.size(-1));
+  a.rows = probs.numel() / a.cols;
+  a.scale = static_cast<float>(scale);
+  cudaError_t e = teb200::softmax_bwd(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "softmax_bwd failed: ", cudaGetErrorString(e));
+  return dx;
+}
+
+std::vector<at::Tensor> dropout_fwd(const at::Tensor& x, double p, int64_t seed, int64_t offset) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.is_contiguous());
+  at::Tensor y = at::empty_like(x);
+  at::Tensor bits = at::empty({(x.numel() + 7) / 8}, x.options().dtype(at::kByte));
+  cudaError_t e = teb200::dropout_fwd(x.data_ptr(), y.data_ptr(), bits.data_ptr<uint8_t>(), x.numel(), dtype_code(x),
+                                      static_cast<float>(p), static_cast<uint64_t>(seed), static_cast<uint64_t>(offset),
+                                      cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "dropout_fwd failed: ", cudaGetErrorString(e));
+  return {y, bits};
+}
+
+at::Tensor dropout_bwd(const at::Tensor& dy, const at::Tensor& bits, double p) {
+  c10::cuda::CUDAGuard guard(dy.device());
+  TORCH_CHECK(dy.is_contiguous());
+  at::Tensor dx = at::empty_like(dy);
+  cudaError_t e = teb200::dropout_bwd(dy.data_ptr(), bits.data_ptr<uint8_t>(), dx.data_ptr(), dy.numel(), dtype_code(dy),
+                                      static_cast<float>(p), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "dropout_bwd failed: ", cudaGetErrorString(e));
+  return dx;
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("softmax_fwd", &softmax_fwd);
+  m.def("softmax_bwd", &softmax_bwd);
+  m.def("dropout_fwd", &dropout_fwd);
+  m.def("dropout_bwd", &dropout_bwd);
   m.def("peer_sum", &peer_sum);
   m.def("ep_counts", &ep_counts);
   m.def("ep_push", &ep_push);

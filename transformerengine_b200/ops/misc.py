@@ -264,6 +264,13 @@ def multi_tensor_l2norm(tensors: List[torch.Tensor], per_tensor: bool = False):
 def scaled_masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor], scale: float, causal: bool = False):
     """softmax(scale * scores + mask) over the last dim, fp32 accumulation; ``mask`` True = masked out.
     ``causal`` applies a bottom-right aligned upper-triangular mask."""
+    if _ext.use_cuda(scores) and hasattr(_ext.get(), "softmax_fwd") and scores.dim() == 4 and \
+            scores.dtype in (torch.float32, torch.bfloat16, torch.float16) and \
+            (mask is None or (mask.dim() == 4 and mask.shape[1] == 1 and mask.shape[0] == scores.shape[0]
+                              and mask.shape[2:] == scores.shape[2:])):
+        m8 = None if mask is None else mask.to(torch.uint8).contiguous()
+        return _ext.get().softmax_fwd(scores.contiguous(), m8, float(scale), bool(causal), scores.shape[2],
+                                      scores.shape[1])
     s = scores.float() * scale
     if causal:
         sq, sk = s.shape[-2], s.shape[-1]
@@ -277,6 +284,9 @@ def scaled_masked_softmax(scores: torch.Tensor, mask: Optional[torch.Tensor], sc
 
 
 def softmax_bwd(probs: torch.Tensor, dprobs: torch.Tensor, scale: float) -> torch.Tensor:
+    if _ext.use_cuda(probs) and hasattr(_ext.get(), "softmax_bwd") and probs.dtype == dprobs.dtype and \
+            probs.dtype in (torch.float32, torch.bfloat16, torch.float16):
+        return _ext.get().softmax_bwd(probs.contiguous(), dprobs.contiguous(), float(scale))
     p, d = probs.float(), dprobs.float()
     return ((d - (d * p).sum(-1, keepdim=True)) * p * scale).to(probs.dtype)
 
@@ -285,6 +295,12 @@ def dropout_fwd(x: torch.Tensor, p: float, generator=None):
     """Returns (y, keep mask as bool)."""
     if p <= 0.0:
         return x, None
+    if _ext.use_cuda(x) and hasattr(_ext.get(), "dropout_fwd") and generator is None and \
+            x.dtype in (torch.float32, torch.bfloat16, torch.float16):
+        seed = int(torch.cuda.initial_seed()) & 0x7FFFFFFFFFFFFFFF
+        offset = int(torch.randint(0, 2**31 - 1, (1,)).item())  # advances the host generator: a new mask per call
+        y, bits = _ext.get().dropout_fwd(x.contiguous(), float(p), seed, offset)
+        return y, bits
     keep = torch.rand(x.shape, device=x.device, generator=generator) >= p
     return (x.float() * keep / (1 - p)).to(x.dtype), keep
 
@@ -292,4 +308,6 @@ def dropout_fwd(x: torch.Tensor, p: float, generator=None):
 def dropout_bwd(dy: torch.Tensor, keep: Optional[torch.Tensor], p: float):
     if keep is None:
         return dy
+    if keep.dtype == torch.uint8 and _ext.use_cuda(dy):  # packed keep-bits from the CUDA forward
+        return _ext.get().dropout_bwd(dy.contiguous(), keep, float(p))
     return (dy.float() * keep / (1 - p)).to(dy.dtype)

@@ -161,36 +161,17 @@ def run_ours(args):
     n_batches = 4
     host = [torch.randint(0, cfg.vocab_size, (1, args.seq), generator=gen).pin_memory() for _ in range(n_batches)]
     dev = [h.cuda() for h in host]
-    grads = [p for p in model.parameters()]
-
-    def allreduce_grads():
-        if dp == 1:
-            return
-        bucket, size = [], 0
-        for p in grads:
-            if p.grad is None:
-                continue
-            bucket.append(p.grad)
-            size += p.grad.numel()
-            if size >= 64 << 20:
-                _flat_allreduce(bucket, dp)
-                bucket, size = [], 0
-        if bucket:
-            _flat_allreduce(bucket, dp)
-
-    def _flat_allreduce(bucket, n):
-        flat = torch._utils._flatten_dense_tensors(bucket)
-        dist.all_reduce(flat)
-        flat.div_(n)
-        for g, f in zip(bucket, torch._utils._unflatten_dense_tensors(flat, bucket)):
-            g.copy_(f)
+    # data parallel: every gradient is all-reduced (average) as soon as autograd has produced it
+    from transformerengine_b200.parallel.data_parallel import DataParallelGradSync
+    grad_sync = DataParallelGradSync(model.parameters(), None) if dp > 1 else None
 
     def train_step(tokens):
         opt.zero_grad(set_to_none=True)
         with te.autocast(enabled=recipe is not None, recipe=recipe):
             loss = model(tokens, labels=tokens)
         loss.backward()
-        allreduce_grads()
+        if grad_sync is not None:
+            grad_sync.finish()
         opt.step()
         return loss
 

@@ -1,6 +1,6 @@
 """Run one kernel of the library a few times on a fixed case (target for ncu captures).
 
-    python benchmarks/kernel_case.py --kernel gemm_mxfp8|gemm_bf16|quantize|swiglu_quantize|adam|rmsnorm_bwd|cross_entropy|attention
+    python benchmarks/kernel_case.py --kernel gemm_mxfp8|gemm_bf16|quantize|swiglu_quantize|adam|rmsnorm_bwd|cross_entropy|attention|rope|nvfp4_quantize|router|permute
 """
 import argparse
 import os
@@ -62,6 +62,20 @@ def main():
         v = torch.randn(1, 4, 4096, 128, device="cuda", dtype=bf, requires_grad=True)
         do = torch.randn(1, 16, 4096, 128, device="cuda", dtype=bf)
         fn = lambda: flash.flash_attention(q, k, v, None, True).backward(do)  # noqa: E731
+    elif a.kernel == "rope":
+        x = torch.randn(8192, 1, 32, 128, device="cuda", dtype=bf)
+        f = ops.rope_freqs(torch.arange(8192, device="cuda"), 128, 500000.0, False)
+        fn = lambda: ops.rope_apply(x, f)  # noqa: E731
+    elif a.kernel == "nvfp4_quantize":
+        x = torch.randn(T, H, device="cuda", dtype=bf)
+        fn = lambda: qz.quantize_nvfp4(x, with_rht=True)  # noqa: E731
+    elif a.kernel == "router":
+        lg = torch.randn(65536, 64, device="cuda")
+        fn = lambda: te.fused_topk_with_score_function(lg, 6, False, None, None, 1.0, "sigmoid", None)  # noqa: E731
+    elif a.kernel == "permute":
+        x = torch.randn(T, H, device="cuda", dtype=bf)
+        probs, rmap = te.fused_topk_with_score_function(torch.randn(T, 8, device="cuda"), 2)
+        fn = lambda: te.moe_unpermute(te.moe_permute_with_probs(x, probs, rmap)[0], te.moe_permute(x, rmap)[1], probs)  # noqa: E731
     else:
         raise SystemExit(f"unknown kernel {a.kernel}")
     for _ in range(a.reps):

@@ -87,7 +87,6 @@ __global__ void router_fwd_kernel(RouterArgs a) {
   for (int i = 0; i < kMaxPerLane; ++i)
     if (lane + 32 * i >= a.E) sel[i] = kNegInf;
   // top-k by repeated arg-max (ties: lowest expert index)
-  float vals[kMaxPerLane];  // value kept for the k-th pick, valid on the owning lane
   int picked_e[8];
   float picked_raw[8];
   for (int k = 0; k < a.topk; ++k) {
@@ -116,7 +115,6 @@ __global__ void router_fwd_kernel(RouterArgs a) {
       }
     picked_raw[k] = __shfl_sync(0xffffffffu, raw, own_lane);
   }
-  (void)vals;
   // normalise the picked values
   float w[8];
   if (a.score_fn == 1 && !a.use_pre_softmax) {
@@ -266,6 +264,51 @@ __global__ void unpermute_rows_kernel(const T* __restrict__ in, T* __restrict__ 
   }
 }
 
+// 16-bit rows with 16-byte vectors: one thread sums 8 adjacent elements over the slots
+template <bool BF>
+__global__ void unpermute_rows_vec_kernel(const uint4* __restrict__ in, uint4* __restrict__ out,
+                                          const int32_t* __restrict__ dest_row, const float* __restrict__ w, int slots,
+                                          int vec_per_row) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < slots; ++k) {
+      const int d = dest_row[static_cast<size_t>(t) * slots + k];
+      if (d < 0) continue;
+      const float wk = w != nullptr ? w[static_cast<size_t>(t) * slots + k] : 1.f;
+      const uint4 v = in[static_cast<size_t>(d) * vec_per_row + i];
+      const uint32_t* w32 = reinterpret_cast<const uint32_t*>(&v);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float lo, hi;
+        if (BF) {
+          lo = __uint_as_float(w32[j] << 16);
+          hi = __uint_as_float(w32[j] & 0xffff0000u);
+        } else {
+          const __half2 h = *reinterpret_cast<const __half2*>(&w32[j]);
+          lo = __low2float(h);
+          hi = __high2float(h);
+        }
+        acc[2 * j] += wk * lo;
+        acc[2 * j + 1] += wk * hi;
+      }
+    }
+    uint4 o;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (BF) {
+        const __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+        o32[j] = *reinterpret_cast<const uint32_t*>(&b2);
+      } else {
+        const __half2 h2 = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+        o32[j] = *reinterpret_cast<const uint32_t*>(&h2);
+      }
+    }
+    out[static_cast<size_t>(t) * vec_per_row + i] = o;
+  }
+}
+
 // dest rows of an index routing [T, topk]: stable expert-major order with per-expert padding.
 // Single block: counts, exclusive scan, then a serial-in-token assignment per expert lane.
 __global__ void build_dest_rows_kernel(const int32_t* __restrict__ topk_idx, int T, int topk, int E, int align,
@@ -347,6 +390,14 @@ cudaError_t unpermute_rows(const void* in, void* out, const int32_t* dest_row, c
                            int dtype, cudaStream_t s) {
   if (H % 2 != 0) return cudaErrorInvalidValue;
   if (T == 0) return cudaSuccess;
+  if (dtype != kFloat32 && H % 8 == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    if (dtype == kBFloat16)
+      unpermute_rows_vec_kernel<true><<<T, 256, 0, s>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), dest_row, w, topk, H / 8);
+    else
+      unpermute_rows_vec_kernel<false><<<T, 256, 0, s>>>(static_cast<const uint4*>(in), static_cast<uint4*>(out), dest_row, w, topk, H / 8);
+    return cudaGetLastError();
+  }
   switch (dtype) {
     case kFloat32:
       unpermute_rows_kernel<float><<<T, 256, 0, s>>>(static_cast<const float*>(in), static_cast<float*>(out), dest_row, w, T, topk, H);

@@ -263,3 +263,23 @@ def test_softmax_and_dropout_kernels():
     g = misc.dropout_bwd(torch.ones_like(x), keep, 0.25)
     nz = x != 0
     assert torch.equal((g != 0)[nz], kept[nz])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("algo", ["max", "most_recent"])
+def test_delayed_scaling_update_kernel_matches_reference(algo):
+    import transformerengine_b200 as te
+    from transformerengine_b200.quantization import RecipeState, update_delayed_scaling_state
+
+    torch.manual_seed(0)
+    recipe = te.recipe.DelayedScaling(amax_history_len=8, amax_compute_algo=algo, margin=1)
+    st = RecipeState.create(recipe, mode="forward", num_quantizers=6, device=torch.device("cuda"))
+    ref = RecipeState.create(recipe, mode="forward", num_quantizers=6, device=torch.device("cpu"))
+    h = torch.rand(8, 6) * 10
+    h[:, 2] = 0
+    st.amax_history.copy_(h)
+    ref.amax_history.copy_(h)
+    update_delayed_scaling_state(st)
+    update_delayed_scaling_state(ref)
+    assert torch.allclose(st.scale.cpu(), ref.scale, rtol=1e-6)
+    assert torch.equal(st.amax_history.cpu(), ref.amax_history)

@@ -463,9 +463,22 @@ at::Tensor dropout_bwd(const at::Tensor& dy, const at::Tensor& bits, double p) {
   return dx;
 }
 
+void delayed_scaling_update(const at::Tensor& history, const at::Tensor& scale, double fp8_max, int64_t margin,
+                            bool most_recent) {
+  c10::cuda::CUDAGuard guard(history.device());
+  TORCH_CHECK(history.dim() == 2 && history.is_contiguous() && scale.is_contiguous() &&
+              history.scalar_type() == at::kFloat && scale.scalar_type() == at::kFloat && history.size(1) == scale.numel());
+  cudaError_t e = teb200::delayed_scaling_update(history.data_ptr<float>(), scale.data_ptr<float>(),
+                                                 static_cast<int>(history.size(0)), static_cast<int>(history.size(1)),
+                                                 static_cast<float>(fp8_max), static_cast<int>(margin), most_recent ? 1 : 0,
+                                                 cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "delayed_scaling_update failed: ", cudaGetErrorString(e));
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("delayed_scaling_update", &delayed_scaling_update);
   m.def("softmax_fwd", &softmax_fwd);
   m.def("softmax_bwd", &softmax_bwd);
   m.def("dropout_fwd", &dropout_fwd);

@@ -61,6 +61,10 @@ cudaError_t amax_abs(const void* x, int dtype, int64_t n, float* out /*zeroed by
 cudaError_t swizzle_scales(const uint8_t* compact, int rows, int cols, uint8_t* out, cudaStream_t s);
 cudaError_t unswizzle_scales(const uint8_t* swz, int rows, int cols, uint8_t* out, cudaStream_t s);
 
+// delayed scaling: scales from the amax history [H, n], then roll the history and clear slot 0
+cudaError_t delayed_scaling_update(float* history, float* scale, int H, int n, float fp8_max, int margin, int most_recent,
+                                   cudaStream_t s);
+
 // NVFP4: 1x16 (or 16x16) blocks, E4M3 block scales (swizzled), global amax given.
 struct Nvfp4Args {
   const void* x = nullptr;

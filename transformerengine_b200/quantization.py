@@ -223,8 +223,17 @@ def update_delayed_scaling_state(state: DelayedScalingRecipeState, reduced_amax:
     r = state.recipe
     if reduced_amax is not None:
         state.amax_history[0].copy_(reduced_amax)
-    amax = _default_get_amax(state.amax_history, r.amax_compute_algo)
     fmax = get_fp8_max(r, fprop_tensor=(state.mode == "forward"))
+    from .ops import _ext
+
+    if (_ext.use_cuda(state.amax_history) and hasattr(_ext.get(), "delayed_scaling_update")
+            and not callable(r.scaling_factor_compute_algo) and r.amax_compute_algo in ("max", "most_recent")
+            and state.amax_history.is_contiguous() and state.scale.is_contiguous()):
+        # one launch: history max, new scales, roll + clear (csrc/quant/recipe_kernels.cu)
+        _ext.get().delayed_scaling_update(state.amax_history, state.scale, float(fmax), int(r.margin),
+                                          r.amax_compute_algo == "most_recent")
+        return
+    amax = _default_get_amax(state.amax_history, r.amax_compute_algo)
     if callable(r.scaling_factor_compute_algo):
         new_scale = r.scaling_factor_compute_algo(amax, state.scale, fmax, r)
     else:

@@ -85,3 +85,55 @@ def test_dual_chunk_layout():
     assert dual_chunk_positions(4, 4, 1).tolist() == [2, 3, 12, 13]
     cu = torch.tensor([0, 5, 13])
     assert pad_thd_sequences_for_cp(cu, 2).tolist() == [0, 8, 16]
+
+
+def _hier_worker(rank, world, port, result_q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from transformerengine_b200.ops.attention import attention_ref
+        from transformerengine_b200.parallel.context_parallel import (attn_forward_func_with_cp,
+                                                                      get_batch_on_this_cp_rank)
+
+        a2a_groups = [dist.new_group([0, 1]), dist.new_group([2, 3])]
+        p2p_groups = [dist.new_group([0, 2]), dist.new_group([1, 3])]
+        groups = [a2a_groups[rank // 2], p2p_groups[rank % 2]]
+        torch.manual_seed(0)
+        b, hq, hk, s, d = 1, 4, 2, 64, 16
+        q = torch.randn(b, hq, s, d, dtype=torch.float64)
+        k = torch.randn(b, hk, s, d, dtype=torch.float64)
+        v = torch.randn(b, hk, s, d, dtype=torch.float64)
+        do = torch.randn(b, hq, s, d, dtype=torch.float64)
+        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+        ref = attention_ref(qf, kf, vf, causal=True)
+        ref.backward(do)
+        shard = lambda t: get_batch_on_this_cp_rank(t, world, rank, seq_dim=2).contiguous()  # noqa: E731
+        ql, kl, vl = (shard(t).clone().requires_grad_() for t in (q, k, v))
+        out = attn_forward_func_with_cp(ql, kl, vl, cp_group=groups, cp_comm_type="a2a+p2p", causal=True)
+        out.backward(shard(do))
+        errs = [(out - shard(ref.detach())).abs().max().item(), (ql.grad - shard(qf.grad)).abs().max().item(),
+                (kl.grad - shard(kf.grad)).abs().max().item(), (vl.grad - shard(vf.grad)).abs().max().item()]
+        result_q.put((rank, max(errs), None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_hierarchical_cp_matches_single_rank():
+    world = 4
+    ctx = mp.get_context("spawn")
+    result_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_hier_worker, args=(r, world, port, result_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [result_q.get(timeout=180) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, err, tb in results:
+        assert tb is None, tb
+        assert err < 2e-5, (rank, err)

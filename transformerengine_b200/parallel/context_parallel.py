@@ -126,16 +126,19 @@ class _RingAttention(torch.autograd.Function):
     """K/V blocks travel around the ring; partial results are merged with their log-sum-exp."""
 
     @staticmethod
-    def forward(ctx, q, k, v, group, ranks, scale, causal, window):  # type: ignore[override]
+    def forward(ctx, q, k, v, group, ranks, scale, causal, window, pos_table=None):  # type: ignore[override]
         cp, me = dist.get_world_size(group), dist.get_rank(group)
         sq, sk = q.shape[2], k.shape[2]
-        qpos = dual_chunk_positions(sq, cp, me, q.device) if causal else torch.arange(sq, device=q.device) + me * sq
+        if pos_table is None:  # global token positions held by every rank of the ring
+            pos_table = torch.stack([dual_chunk_positions(sk, cp, r, q.device) if causal
+                                     else torch.arange(sk, device=q.device) + r * sk for r in range(cp)])
+        qpos = pos_table[me]
         kv = torch.stack([k, v]).contiguous()
         out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
         lse = torch.full(q.shape[:3], float("-inf"), dtype=torch.float32, device=q.device)
         for step in range(cp):
             src = (me - step) % cp
-            kpos = dual_chunk_positions(sk, cp, src, q.device) if causal else torch.arange(sk, device=q.device) + src * sk
+            kpos = pos_table[src]
             mask = _mask_for(qpos, kpos, causal, window)
             if mask is None or not bool(mask.all()):
                 o_b, lse_b = _block_fwd(q, kv[0], kv[1], scale, mask)
@@ -147,23 +150,22 @@ class _RingAttention(torch.autograd.Function):
             if step != cp - 1:
                 kv = _ring_exchange(kv, group, ranks)
         o = out.to(q.dtype)
-        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.save_for_backward(q, k, v, o, lse, pos_table)
         ctx.cfg = (group, ranks, scale, causal, window)
         return o
 
     @staticmethod
     def backward(ctx, do):  # type: ignore[override]
-        q, k, v, o, lse = ctx.saved_tensors
+        q, k, v, o, lse, pos_table = ctx.saved_tensors
         group, ranks, scale, causal, window = ctx.cfg
         cp, me = dist.get_world_size(group), dist.get_rank(group)
-        sq, sk = q.shape[2], k.shape[2]
-        qpos = dual_chunk_positions(sq, cp, me, q.device) if causal else torch.arange(sq, device=q.device) + me * sq
+        qpos = pos_table[me]
         kv = torch.stack([k, v]).contiguous()
         dkv = torch.zeros(kv.shape, dtype=torch.float32, device=q.device)
         dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
         for step in range(cp):
             src = (me - step) % cp
-            kpos = dual_chunk_positions(sk, cp, src, q.device) if causal else torch.arange(sk, device=q.device) + src * sk
+            kpos = pos_table[src]
             mask = _mask_for(qpos, kpos, causal, window)
             if mask is None or not bool(mask.all()):
                 dq_b, dk_b, dv_b = _block_bwd(do, q, kv[0], kv[1], o, lse, scale, mask)
@@ -175,7 +177,7 @@ class _RingAttention(torch.autograd.Function):
                 dkv = _ring_exchange(dkv, group, ranks)
                 if step != cp - 1:
                     kv = _ring_exchange(kv, group, ranks)
-        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None, None
+        return dq.to(q.dtype), dkv[0].to(k.dtype), dkv[1].to(v.dtype), None, None, None, None, None, None
 
 
 class _AllGatherSeq(torch.autograd.Function):
@@ -229,9 +231,11 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
     """Attention over the full sequence from per-rank shards; returns ``[b, h, s_local, d]``."""
     from ..ops.attention import attention_ref
 
+    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    if cp_comm_type == "a2a+p2p":
+        return _hierarchical_cp(q, k, v, cp_group, scale, causal, window)
     cp = dist.get_world_size(cp_group)
     me = dist.get_rank(cp_group)
-    scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if cp == 1:
         return attention_ref(q, k, v, scale=scale, causal=causal, window=window)
     if cp_comm_type == "p2p" and _fused_ring_ok(q, k, v, window):
@@ -264,6 +268,27 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
         oh = attention_ref(qh, kh, vh, scale=scale, attn_mask=mask)
         return _SeqToHeads.apply(oh, cp_group, False)
     raise ValueError(f"unknown cp_comm_type {cp_comm_type}")
+
+
+def _hierarchical_cp(q, k, v, groups, scale, causal, window):
+    """Two-level context parallelism (reference ``context_parallel.py:5020``): Ulysses all-to-all
+    inside the first group (the NVLink island), ring attention across the second.  The global
+    context-parallel rank of a process is ``p2p_rank * a2a_size + a2a_rank``."""
+    assert isinstance(groups, (list, tuple)) and len(groups) == 2, "a2a+p2p needs [a2a_group, p2p_group]"
+    a2a_group, p2p_group = groups
+    A, P = dist.get_world_size(a2a_group), dist.get_world_size(p2p_group)
+    s_l = q.shape[2]
+    assert q.shape[1] % A == 0 and k.shape[1] % A == 0, "heads must divide by the all-to-all group size"
+    qh, kh, vh = (_SeqToHeads.apply(t, a2a_group, True) for t in (q, k, v))
+
+    def positions(rp):  # tokens of ring rank rp after the all-to-all: the island's shards in rank order
+        if causal:
+            return torch.cat([dual_chunk_positions(s_l, A * P, rp * A + ra, q.device) for ra in range(A)])
+        return torch.cat([torch.arange(s_l, device=q.device) + (rp * A + ra) * s_l for ra in range(A)])
+
+    pos_table = torch.stack([positions(rp) for rp in range(P)])
+    oh = _RingAttention.apply(qh, kh, vh, p2p_group, None, scale, causal, window, pos_table)
+    return _SeqToHeads.apply(oh, a2a_group, False)
 
 
 # ------------------------------------------------------------------------------------------------

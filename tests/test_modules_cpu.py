@@ -276,3 +276,24 @@ def test_fused_adam_matches_torch_adamw():
     sd = o1.state_dict()
     o3 = te.FusedAdam(a, lr=1e-2)
     o3.load_state_dict(sd)
+
+
+def test_fsdp2_hooks_reassemble_row_shards():
+    """Gathering the row shards' raw bytes (and MXFP8 scale tiles) gives the quantized full tensor."""
+    from transformerengine_b200.tensor.float8 import Float8CurrentScalingQuantizer
+    from transformerengine_b200.tensor.mxfp8 import MXFP8Quantizer
+
+    torch.manual_seed(0)
+    w = torch.randn(256, 64)
+    q = MXFP8Quantizer(columnwise=False)
+    full = q(w)
+    shards = [q(w[:128]), q(w[128:])]
+    outs, meta = zip(*[s.fsdp_pre_all_gather() for s in shards])
+    gathered = tuple(torch.cat([o[i] for o in outs]) for i in range(2))
+    rebuilt, _ = shards[0].fsdp_post_all_gather(gathered, meta[0])
+    assert torch.equal(rebuilt.dequantize(), full.dequantize())
+    q8 = Float8CurrentScalingQuantizer(torch.float8_e4m3fn, device="cpu")
+    f = q8(w)
+    (data,), m8 = f.fsdp_pre_all_gather()
+    rebuilt8, _ = f.fsdp_post_all_gather((torch.cat([data[:128], data[128:]]),), m8)
+    assert torch.equal(rebuilt8.dequantize(), f.dequantize())

@@ -92,6 +92,23 @@ class Float8Tensor(Float8TensorStorage, QuantizedTensor):
         return (_make_float8_tensor_in_reduce_ex,
                 (self._data, self._fp8_dtype, self._scale_inv, self._dtype, self._shape, self._transpose))
 
+    # ---- FSDP2 extension points (reference: tensor/float8_tensor.py:938-1075): shards travel as raw bytes,
+    # the per-tensor scale is identical on all ranks (its amax is reduced over the shard group)
+    def fsdp_pre_all_gather(self, mesh=None, orig_size=None, contiguous_orig_stride=None, module=None, mp_policy=None):
+        if self._data is None:
+            self.update_usage(rowwise_usage=True)
+        return (self._data.view(torch.uint8),), (self._scale_inv, self._fp8_dtype, self._dtype, self._quantizer)
+
+    def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype=None, *, out=None):
+        (data,) = all_gather_outputs
+        scale_inv, fp8_dtype, dtype, quantizer = metadata
+        if out is not None:
+            out._data, out._transpose, out._scale_inv = data, None, scale_inv
+            return None
+        full = Float8Tensor(shape=data.shape, dtype=dtype, data=data, fp8_scale_inv=scale_inv, fp8_dtype=fp8_dtype,
+                            quantizer=quantizer)
+        return full, all_gather_outputs
+
 
 def _make_float8_tensor_in_reduce_ex(data, fp8_dtype, scale_inv, dtype, shape, data_transpose=None):
     return Float8Tensor(shape=shape, dtype=dtype, data=data, fp8_scale_inv=scale_inv, fp8_dtype=fp8_dtype,

@@ -122,6 +122,27 @@ class MXFP8Tensor(MXFP8TensorStorage, QuantizedTensor):
                 (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
                  self._fp8_dtype, self._dtype, self._shape, None, True))
 
+    # ---- FSDP2 extension points (reference: tensor/mxfp8_tensor.py:606-757).  Row shards must be whole
+    # 128-row scale tiles; then the row-wise data and its tile-major scales of the shards concatenate
+    # byte-wise into the full tensor's, and the column-wise copy is rebuilt after the gather.
+    def fsdp_pre_all_gather(self, mesh=None, orig_size=None, contiguous_orig_stride=None, module=None, mp_policy=None):
+        assert self._rowwise_data is not None, "FSDP gathers the row-wise copy"
+        R, _ = self._rows_cols()
+        assert R % 128 == 0, "MXFP8 parameter shards must hold a multiple of 128 rows"
+        return ((self._rowwise_data.view(torch.uint8), self._rowwise_scale_inv.reshape(R // 128, -1)),
+                (self._fp8_dtype, self._dtype, self._quantizer))
+
+    def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype=None, *, out=None):
+        data, scales = all_gather_outputs
+        fp8_dtype, dtype, quantizer = metadata
+        full = MXFP8Tensor(shape=data.shape, dtype=dtype, rowwise_data=data, rowwise_scale_inv=scales.reshape(-1),
+                           columnwise_data=None, columnwise_scale_inv=None, fp8_dtype=fp8_dtype, quantizer=quantizer)
+        if out is not None:
+            out._rowwise_data, out._rowwise_scale_inv = full._rowwise_data, full._rowwise_scale_inv
+            out._columnwise_data = out._columnwise_scale_inv = None
+            return None
+        return full, all_gather_outputs
+
 
 def _make_mxfp8_tensor_in_reduce_ex(rowwise_data, rowwise_scale_inv, columnwise_data, columnwise_scale_inv,
                                     fp8_dtype, dtype, shape, quantizer=None, with_gemm_swizzled_scales=True):

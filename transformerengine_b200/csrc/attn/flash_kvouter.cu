@@ -22,7 +22,7 @@ struct KvCfg {
   static constexpr int kOffV = kKBytes;
   static constexpr int kOffRing = kOffV + kVBytes;
   static constexpr int kOffBar = kOffRing + kRing * kStageBytes;
-  static constexpr int kNumBars = 1 + 2 * kRing + 2 + 2 + 2 + 1;
+  static constexpr int kNumBars = 1 + 2 * kRing + 2 + 2 + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16 + 1024;
   static constexpr int kColS = 0, kColDp = 128, kColDv = 256, kColDk = 384;
 };
@@ -42,8 +42,7 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   uint64_t* r_empty = r_full + C::kRing;   // [kRing]
   uint64_t* s_full = r_empty + C::kRing;   // [2]
   uint64_t* p_ready = s_full + 2;          // [2]
-  uint64_t* pd_done = p_ready + 2;         // [2]
-  uint64_t* acc_done = pd_done + 2;
+  uint64_t* acc_done = p_ready + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -75,7 +74,6 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     for (int u = 0; u < 2; ++u) {
       mbar_init(&s_full[u], 1);
       mbar_init(&p_ready[u], 8);
-      mbar_init(&pd_done[u], 1);
     }
     mbar_init(acc_done, 1);
     mbar_fence_init();
@@ -166,8 +164,7 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 #pragma unroll
           for (int k = 1; k < 4; ++k)
             umma_f16_ts(tmem_base + C::kColDk, cd + (k >> 1) * 32 + (k & 1) * 8, q + k * (2048 >> 4), idesc_acc, 1);
-          tc_commit(&pd_done[u]);
-          tc_commit(&r_empty[st]);
+            tc_commit(&r_empty[st]);
         }
         __syncwarp();
       }
@@ -228,9 +225,8 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           wd[c / 2 + 1] = pack16<BF>(dv[2], dv[3]);
         }
       }
-      if (it >= 2) {
-        if (!mbar_wait(&pd_done[u], ((it >> 1) - 1) & 1)) { ok = false; break; }
-      }
+      // no wait for block it-2's products here: this block's scores were written after them (the
+      // tensor pipe runs in issue order), so their operands have been read
       // P^T and dS^T return through TMEM over the columns this thread has just read
       tmem_st_32x16(lane_base + C::kColS + u * 64 + half * 32, wp);
       tmem_st_32x16(lane_base + C::kColDp + u * 64 + half * 32, wd);

@@ -131,7 +131,7 @@ def _permute(inp, routing_map, probs, num_out_tokens, map_type, align):
         dest_flat[order] = torch.arange(order.numel(), device=inp.device)
         dest = dest_flat.reshape(T, topk)
         n_out = T * topk
-        if num_out_tokens and num_out_tokens < n_out:  # capacity drop: rows beyond the budget vanish
+        if num_out_tokens and num_out_tokens < n_out:  # capacity drop: rows beyond num_out_tokens vanish
             dest = torch.where(dest < num_out_tokens, dest, torch.full_like(dest, -1))
             n_out = num_out_tokens
     else:

@@ -163,7 +163,8 @@ def run_ours(args):
     dev = [h.cuda() for h in host]
     # data parallel: every gradient is all-reduced (average) as soon as autograd has produced it
     from transformerengine_b200.parallel.data_parallel import DataParallelGradSync
-    grad_sync = DataParallelGradSync(model.parameters(), None) if dp > 1 else None
+    grad_sync = DataParallelGradSync(model.parameters(), None,
+                                     overlap=os.environ.get("TEB200_DP_OVERLAP", "1") == "1") if dp > 1 else None
 
     def train_step(tokens):
         opt.zero_grad(set_to_none=True)

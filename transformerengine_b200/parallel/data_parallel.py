@@ -19,11 +19,12 @@ import torch.distributed as dist
 
 class DataParallelGradSync:
     def __init__(self, params: Iterable[torch.nn.Parameter], group=None, min_bytes: int = 32 << 20,
-                 average: bool = True):
+                 average: bool = True, overlap: bool = True):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.min_bytes = min_bytes
         self.average = average
+        self.overlap = overlap  # False: collect during backward, reduce everything in finish()
         self._pending: List[torch.Tensor] = []
         self._pending_bytes = 0
         self._works: list = []
@@ -41,7 +42,7 @@ class DataParallelGradSync:
             return
         self._pending.append(g)
         self._pending_bytes += g.numel() * g.element_size()
-        if self._pending_bytes >= self.min_bytes:
+        if self.overlap and self._pending_bytes >= self.min_bytes:
             self._flush()
 
     def _flush(self) -> None:

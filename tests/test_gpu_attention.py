@@ -98,3 +98,84 @@ def test_dot_product_attention_uses_own_kernel():
     _close(out.reshape(256, 2, 4, 128).permute(1, 2, 0, 3), ref, 2e-2)
     assert q.grad is not None and torch.isfinite(q.grad.float()).all()
     assert hasattr(C_, "flash_fwd")
+
+
+VARLEN_CASES = [
+    # q lengths, kv lengths (None: same), causal, bottom_right, gaps between sequences (padded offsets)
+    ([300, 128, 517, 64, 1], None, True, True, None),
+    ([300, 128, 517, 64, 1], None, False, True, None),
+    ([100, 260], [356, 260], True, True, None),
+    ([256, 40, 0, 129], None, True, True, [3, 0, 5, 2]),
+]
+
+
+@pytest.mark.parametrize("case", VARLEN_CASES)
+def test_flash_varlen_matches_per_sequence_reference(case):
+    """Packed sequences in one launch versus the fp32 reference run sequence by sequence."""
+    import transformerengine_b200 as te
+    from transformerengine_b200.ops import flash
+
+    lq, lk, causal, br, gaps = case
+    lk = lk or lq
+    gaps = gaps or [0] * len(lq)
+    hq, hk = 4, 2
+
+    def offsets(lens):
+        cu, off, pos = [0], [], 0
+        for n, g in zip(lens, gaps):
+            off.append(pos)
+            pos += n + g
+            cu.append(cu[-1] + n)
+        off.append(pos)
+        return cu, off
+
+    cu_q, off_q = offsets(lq)
+    cu_k, off_k = offsets(lk)
+    torch.manual_seed(0)
+    q = torch.randn(off_q[-1], hq, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(off_k[-1], hk, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(off_k[-1], hk, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    do = torch.randn_like(q)
+    assert flash.supported_varlen(q, k, v)
+    t = lambda x: torch.tensor(x, dtype=torch.int32, device="cuda")
+    padded = any(gaps)
+    o = flash.flash_attention_varlen(q, k, v, t(cu_q), t(cu_k), None, causal, br,
+                                     cu_seqlens_q_padded=t(off_q) if padded else None,
+                                     cu_seqlens_kv_padded=t(off_k) if padded else None)
+    o.backward(do)
+    te.ops.check_status()
+    ro, rdq, rdk, rdv = (torch.zeros_like(x, dtype=torch.float32) for x in (q, q, k, v))
+    for i in range(len(lq)):
+        if lq[i] == 0:
+            continue
+        sq, sk = slice(off_q[i], off_q[i] + lq[i]), slice(off_k[i], off_k[i] + lk[i])
+        bh = lambda x: x.detach().permute(1, 0, 2).unsqueeze(0)
+        r = _ref(bh(q[sq]), bh(k[sk]), bh(v[sk]), bh(do[sq]), causal, br)
+        ro[sq], rdq[sq], rdk[sk], rdv[sk] = (x.squeeze(0).permute(1, 0, 2) for x in r)
+    _close(o, ro, 2e-2)
+    _close(q.grad, rdq, 3e-2)
+    _close(k.grad, rdk, 3e-2)
+    _close(v.grad, rdv, 3e-2)
+
+
+def test_dot_product_attention_thd_uses_varlen_kernel():
+    import transformerengine_b200 as te
+
+    lens = [200, 312]
+    cu = torch.tensor([0, 200, 512], dtype=torch.int32, device="cuda")
+    attn = te.DotProductAttention(4, 128, num_gqa_groups=2, qkv_format="thd", attn_mask_type="padding_causal").cuda()
+    torch.manual_seed(1)
+    q = torch.randn(512, 4, 128, device="cuda", dtype=torch.bfloat16)
+    k = torch.randn(512, 2, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(512, 2, 128, device="cuda", dtype=torch.bfloat16)
+    o = attn(q, k, v, cu_seqlens_q=cu, cu_seqlens_kv=cu, max_seqlen_q=312, max_seqlen_kv=312)
+    te.ops.check_status()
+    assert o.shape == (512, 4 * 128)
+    from transformerengine_b200.ops.attention import attention_ref
+
+    pos = 0
+    for n in lens:
+        bh = lambda x: x[pos:pos + n].float().permute(1, 0, 2).unsqueeze(0)
+        r = attention_ref(bh(q), bh(k), bh(v), causal=True).squeeze(0).permute(1, 0, 2).reshape(n, -1)
+        _close(o[pos:pos + n], r, 2e-2)
+        pos += n

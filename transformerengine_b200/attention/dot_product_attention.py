@@ -11,7 +11,10 @@ from typing import Any, Callable, Dict, List, Optional, Tuple, Union
 
 import torch
 
+import sys
+
 from .. import ops
+from ..ops import flash
 from ..parallel import distributed as D
 
 _MASK_TYPES = ("no_mask", "padding", "causal", "padding_causal", "causal_bottom_right",
@@ -95,21 +98,24 @@ class DotProductAttention(torch.nn.Module):
         if inference_params is not None:
             query_layer, key_layer, value_layer, fmt, mask_type, cu_seqlens_q, cu_seqlens_kv = \
                 inference_params.step(self.layer_number, query_layer, key_layer, value_layer, fmt, mask_type)
+        thd_extra = (cu_seqlens_q_padded, cu_seqlens_kv_padded, max_seqlen_q, max_seqlen_kv) \
+            if inference_params is None else (None, None, None, None)
         if checkpoint_core_attention:
             def run(q, k, v):
                 return self._core(q, k, v, fmt, mask_type, window, attention_mask, cu_seqlens_q, cu_seqlens_kv,
-                                  core_attention_bias_type, core_attention_bias, alibi_slopes)
+                                  core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra)
             return D.checkpoint(run, query_layer, key_layer, value_layer,
                                 get_rng_state_tracker=self.get_rng_state_tracker)
         out = self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
-                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes)
+                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra)
         if inference_params is not None:
             out = inference_params.unpack_output(out)
         return out
 
-    def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes):
+    def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes,
+              thd_extra=(None, None, None, None)):
         if fmt == "thd":
-            return self._thd(q, k, v, mask_type, window, cu_q, cu_kv)
+            return self._thd(q, k, v, mask_type, window, cu_q, cu_kv, *thd_extra)
         # -> [b, h, s, d] views
         if fmt == "sbhd":
             qb, kb, vb = (t.permute(1, 2, 0, 3) for t in (q, k, v))
@@ -157,26 +163,45 @@ class DotProductAttention(torch.nn.Module):
             return o.permute(2, 0, 1, 3).reshape(sq, b, hq * o.shape[-1])
         return o.permute(0, 2, 1, 3).reshape(b, sq, hq * o.shape[-1])
 
-    def _thd(self, q, k, v, mask_type, window, cu_q, cu_kv):
+    def _thd(self, q, k, v, mask_type, window, cu_q, cu_kv, cu_q_padded=None, cu_kv_padded=None, max_sq=None,
+             max_skv=None):
+        """Packed sequences: one launch of the variable-length attention kernels when they apply,
+        else one attention call per sequence.  Tokens outside every sequence give zeros."""
         assert cu_q is not None, "thd format needs cu_seqlens_q"
         cu_kv = cu_kv if cu_kv is not None else cu_q
-        cq, ck = cu_q.tolist(), cu_kv.tolist()
+        if cu_kv_padded is None and cu_q_padded is not None and cu_kv is cu_q:
+            cu_kv_padded = cu_q_padded
         causal = "causal" in mask_type
-        outs = []
+        dropout = self.attention_dropout if self.training else 0.0
+        no_window = window is None or (window[0] < 0 and window[1] in (-1, 0) and (window[1] == -1 or causal))
+        if q.is_cuda and no_window and dropout == 0.0 and self.softmax_type == "vanilla" and \
+                sys.modules[ops.attention.__module__]._USE_OWN_FLASH and flash.supported_varlen(q, k, v):
+            o = flash.flash_attention_varlen(q, k, v, cu_q, cu_kv, scale=self.softmax_scale, causal=causal,
+                                             bottom_right="bottom_right" in mask_type, max_seqlen_q=max_sq,
+                                             max_seqlen_kv=max_skv, cu_seqlens_q_padded=cu_q_padded,
+                                             cu_seqlens_kv_padded=cu_kv_padded)
+            return o.reshape(o.shape[0], -1)
+        cq, ck = cu_q.tolist(), cu_kv.tolist()
+        oq = cq if cu_q_padded is None else cu_q_padded.tolist()
+        ok_ = ck if cu_kv_padded is None else cu_kv_padded.tolist()
+        out = None
         for i in range(len(cq) - 1):
-            qi = q[cq[i]:cq[i + 1]].permute(1, 0, 2).unsqueeze(0)
-            ki = k[ck[i]:ck[i + 1]].permute(1, 0, 2).unsqueeze(0)
-            vi = v[ck[i]:ck[i + 1]].permute(1, 0, 2).unsqueeze(0)
-            if qi.shape[2] == 0:
+            lq, lk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
+            if lq == 0:
                 continue
+            qi = q[oq[i]:oq[i] + lq].permute(1, 0, 2).unsqueeze(0)
+            ki = k[ok_[i]:ok_[i] + lk].permute(1, 0, 2).unsqueeze(0)
+            vi = v[ok_[i]:ok_[i] + lk].permute(1, 0, 2).unsqueeze(0)
             o = ops.attention(qi, ki, vi, scale=self.softmax_scale, causal=causal, window=window,
                               softmax_type=self.softmax_type, sink=self.softmax_offset,
-                              bottom_right="bottom_right" in mask_type or qi.shape[2] == ki.shape[2])
-            outs.append(o.squeeze(0).permute(1, 0, 2))
-        o = torch.cat(outs, dim=0)
-        if o.shape[0] < q.shape[0]:  # padding tokens after the last sequence
-            o = torch.cat([o, o.new_zeros(q.shape[0] - o.shape[0], *o.shape[1:])], dim=0)
-        return o.reshape(o.shape[0], -1)
+                              bottom_right="bottom_right" in mask_type or lq == lk)
+            o = o.squeeze(0).permute(1, 0, 2)
+            if out is None:
+                out = o.new_zeros(q.shape[0], *o.shape[1:])
+            out = torch.cat([out[:oq[i]], o, out[oq[i] + lq:]], dim=0)  # differentiable placement
+        if out is None:
+            out = q.new_zeros(q.shape[0], q.shape[1], v.shape[-1])
+        return out.reshape(out.shape[0], -1)
 
 
 class _null:

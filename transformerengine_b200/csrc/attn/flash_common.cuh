@@ -44,7 +44,41 @@ struct FlashParams {
   int s_pad;
   int* status;
   long long* timeline;  // optional [64][16] clock stamps of CTA 0 (profiling aid), else nullptr
+  // packed variable-length sequences (nullptr: fixed lengths); then sq / sk above are the maxima
+  const int* cu_q;
+  const int* cu_k;
+  const int* off_q;
+  const int* off_k;
+  int bottom_right;
+  int gsplit;       // dK/dV pass: CTAs per group of query heads (partials o_sg elements apart)
+  long long o_sg;
+  int pair_balance;  // query-stationary kernels: a CTA takes 128-row tiles i and last - i (equal causal work)
 };
+
+// Where sequence b starts in the token dimension, and which batch coordinate the TMA maps take.
+struct SeqView {
+  int q_off, k_off, bt;
+};
+
+// Turn the launch-wide parameters into those of sequence b: with packed sequences the lengths come
+// from the cumulative arrays (clamped to the launch's maxima, which sized the grid and lse/delta).
+__device__ __forceinline__ SeqView localize(FlashParams& p, int b) {
+  SeqView v = {0, 0, b};
+  if (p.cu_q != nullptr) {
+    int sq = p.cu_q[b + 1] - p.cu_q[b];
+    int sk = p.cu_k[b + 1] - p.cu_k[b];
+    sq = sq < 0 ? 0 : (sq > p.sq ? p.sq : sq);
+    sk = sk < 0 ? 0 : (sk > p.sk ? p.sk : sk);
+    p.sq = sq;
+    p.sk = sk;
+    p.causal_off = p.bottom_right ? sk - sq : 0;
+    v.q_off = p.off_q[b];
+    v.k_off = p.off_k[b];
+    v.bt = 0;
+    p.o_sb = 0;
+  }
+  return v;
+}
 
 // 4-D tile load: coordinates (d, s, h, b)
 __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0, int c1,

@@ -32,7 +32,7 @@ template <bool BF>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                     const FlashParams p) {
+                     const FlashParams p_launch) {
   using C = KvCfg;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -48,18 +48,24 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int kb = blockIdx.x;
-  const int hk = blockIdx.y;
+  const int hk = static_cast<int>(blockIdx.y) / p_launch.gsplit;
+  const int gs = static_cast<int>(blockIdx.y) % p_launch.gsplit;  // which part of the head group
   const int b = blockIdx.z;
+  FlashParams p = p_launch;
+  const SeqView sv = localize(p, b);
+  p.out = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(sv.k_off) * p.o_ss + gs * p.o_sg;
+  p.out2 = reinterpret_cast<uint16_t*>(p.out2) + static_cast<long long>(sv.k_off) * p.o_ss + gs * p.o_sg;
   const int G = p.hq / p.hk;
+  const int Gl = G / p.gsplit;  // query heads of this CTA
   const int kv0 = kb * 128;
-  const int nq = (p.sq + 63) / 64;
+  const int nq = kv0 < p.sk ? (p.sq + 63) / 64 : 0;  // a key block past the sequence's end has no work
   int i_start = 0;
   if (p.causal) {
     const int first_q = kv0 - p.causal_off;  // first query row that sees key kv0
     i_start = first_q <= 0 ? 0 : first_q / 64;
   }
   const int ni = nq > i_start ? nq - i_start : 0;
-  const int N = G * ni;
+  const int N = Gl * ni;
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_q);
@@ -92,19 +98,19 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     if (lane == 0 && N > 0) {
       mbar_expect_tx(kv_full, C::kKBytes + C::kVBytes);
       for (int pn = 0; pn < 2; ++pn) {
-        tma_load_4d(smem + pn * 16384, &tmap_k, kv_full, pn * 64, kv0, hk, b);
-        tma_load_4d(smem + C::kOffV + pn * 16384, &tmap_v, kv_full, pn * 64, kv0, hk, b);
+        tma_load_4d(smem + pn * 16384, &tmap_k, kv_full, pn * 64, sv.k_off + kv0, hk, sv.bt);
+        tma_load_4d(smem + C::kOffV + pn * 16384, &tmap_v, kv_full, pn * 64, sv.k_off + kv0, hk, sv.bt);
       }
       for (int it = 0; it < N; ++it) {
         const int st = it % C::kRing;
-        const int h = hk * G + it / ni;
+        const int h = hk * G + gs * Gl + it / ni;
         const int qr = (i_start + it % ni) * 64;
         if (!mbar_wait(&r_empty[st], ((it / C::kRing) & 1) ^ 1)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         uint8_t* base = smem + C::kOffRing + st * C::kStageBytes;
         mbar_expect_tx(&r_full[st], 2 * C::kQBlk + 2 * C::kVecBytes);
         for (int pn = 0; pn < 2; ++pn) {
-          tma_load_4d(base + pn * 8192, &tmap_q, &r_full[st], pn * 64, qr, h, b);
-          tma_load_4d(base + C::kQBlk + pn * 8192, &tmap_do, &r_full[st], pn * 64, qr, h, b);
+          tma_load_4d(base + pn * 8192, &tmap_q, &r_full[st], pn * 64, sv.q_off + qr, h, sv.bt);
+          tma_load_4d(base + C::kQBlk + pn * 8192, &tmap_do, &r_full[st], pn * 64, sv.q_off + qr, h, sv.bt);
         }
         const size_t off = (static_cast<size_t>(b) * p.hq + h) * p.s_pad + qr;
         bulk_load_1d(base + 2 * C::kQBlk, p.lse + off, C::kVecBytes, &r_full[st]);
@@ -287,7 +293,8 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 // delta[b, h, s] = sum_d dO * O, one warp per row
 __global__ void flash_delta_kernel(const uint16_t* __restrict__ o, const uint16_t* __restrict__ dout, float* delta,
                                    int b, int h, int s, int s_pad, long long o_sb, long long o_sh, long long o_ss,
-                                   long long d_sb, long long d_sh, long long d_ss, int is_bf16) {
+                                   long long d_sb, long long d_sh, long long d_ss, int is_bf16,
+                                   const int* __restrict__ cu_q, const int* __restrict__ off_q) {
   const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long rows = static_cast<long long>(b) * h * s;
   if (row >= rows) return;
@@ -295,8 +302,15 @@ __global__ void flash_delta_kernel(const uint16_t* __restrict__ o, const uint16_
   const int si = static_cast<int>(row % s);
   const int hi = static_cast<int>((row / s) % h);
   const int bi = static_cast<int>(row / (static_cast<long long>(s) * h));
-  const uint2 a = *reinterpret_cast<const uint2*>(o + bi * o_sb + hi * o_sh + si * o_ss + lane * 4);
-  const uint2 g = *reinterpret_cast<const uint2*>(dout + bi * d_sb + hi * d_sh + si * d_ss + lane * 4);
+  long long tok = si;   // row of the [.., s, d] views
+  long long bo = bi;    // their batch index
+  if (cu_q != nullptr) {  // packed sequences: s is the longest length, the views have one batch entry
+    if (si >= cu_q[bi + 1] - cu_q[bi]) return;
+    tok = off_q[bi] + si;
+    bo = 0;
+  }
+  const uint2 a = *reinterpret_cast<const uint2*>(o + bo * o_sb + hi * o_sh + tok * o_ss + lane * 4);
+  const uint2 g = *reinterpret_cast<const uint2*>(dout + bo * d_sb + hi * d_sh + tok * d_ss + lane * 4);
   float acc = 0.f;
   const uint32_t aw[2] = {a.x, a.y}, gw[2] = {g.x, g.y};
 #pragma unroll
@@ -324,10 +338,15 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
   using C = KvCfg;
   CUtensorMap tq, tk, tv, tdo;
   const bool bf = a.is_bf16;
-  const bool ok = make_tensor_map_bhsd(&tq, a.q, bf, a.b, a.hq, a.sq, a.q_sb, a.q_sh, a.q_ss, 64) &&
-                  make_tensor_map_bhsd(&tk, a.k, bf, a.b, a.hk, a.sk, a.k_sb, a.k_sh, a.k_ss, 128) &&
-                  make_tensor_map_bhsd(&tv, a.v, bf, a.b, a.hk, a.sk, a.v_sb, a.v_sh, a.v_ss, 128) &&
-                  make_tensor_map_bhsd(&tdo, a.dout, bf, a.b, a.hq, a.sq, a.do_sb, a.do_sh, a.do_ss, 64);
+  const bool varlen = a.cu_q != nullptr;
+  if (varlen && (a.cu_k == nullptr || a.off_q == nullptr || a.off_k == nullptr || a.tq <= 0 || a.tk <= 0))
+    return cudaErrorInvalidValue;
+  if (a.b <= 0 || a.sq <= 0 || a.sk <= 0) return cudaSuccess;
+  const int mb = varlen ? 1 : a.b, msq = varlen ? a.tq : a.sq, msk = varlen ? a.tk : a.sk;
+  const bool ok = make_tensor_map_bhsd(&tq, a.q, bf, mb, a.hq, msq, a.q_sb, a.q_sh, a.q_ss, 64) &&
+                  make_tensor_map_bhsd(&tk, a.k, bf, mb, a.hk, msk, a.k_sb, a.k_sh, a.k_ss, 128) &&
+                  make_tensor_map_bhsd(&tv, a.v, bf, mb, a.hk, msk, a.v_sb, a.v_sh, a.v_ss, 128) &&
+                  make_tensor_map_bhsd(&tdo, a.dout, bf, mb, a.hq, msq, a.do_sb, a.do_sh, a.do_ss, 64);
   if (!ok) return cudaErrorInvalidValue;
   if (a.s_pad % 64 != 0 || a.s_pad < ((a.sq + 63) / 64) * 64) return cudaErrorInvalidValue;
   if (a.dk_sb != a.dv_sb || a.dk_sh != a.dv_sh || a.dk_ss != a.dv_ss) return cudaErrorInvalidValue;
@@ -343,6 +362,10 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
       p.o_ss % 8)
     return cudaErrorInvalidValue;
   p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status;
+  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.off_q = a.off_q; p.off_k = a.off_k; p.bottom_right = a.bottom_right ? 1 : 0;
+  p.gsplit = a.gsplit < 1 ? 1 : a.gsplit;
+  p.o_sg = a.dk_sg;
+  if ((a.hq / a.hk) % p.gsplit != 0 || p.o_sg % 8 != 0) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(flash_kvouter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
@@ -351,7 +374,7 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     attr_set = true;
   }
-  dim3 grid((a.sk + 127) / 128, a.hk, a.b);
+  dim3 grid((a.sk + 127) / 128, a.hk * p.gsplit, a.b);
   if (bf) flash_kvouter_kernel<true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   else flash_kvouter_kernel<false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
@@ -365,7 +388,7 @@ cudaError_t flash_delta(const FlashArgs& a, cudaStream_t stream) {
   const unsigned grid = static_cast<unsigned>((rows + warps - 1) / warps);
   attn::flash_delta_kernel<<<grid, warps * 32, 0, stream>>>(
       reinterpret_cast<const uint16_t*>(a.out), reinterpret_cast<const uint16_t*>(a.dout), a.delta, a.b, a.hq, a.sq,
-      a.s_pad, a.o_sb, a.o_sh, a.o_ss, a.do_sb, a.do_sh, a.do_ss, a.is_bf16 ? 1 : 0);
+      a.s_pad, a.o_sb, a.o_sh, a.o_ss, a.do_sb, a.do_sh, a.do_ss, a.is_bf16 ? 1 : 0, a.cu_q, a.off_q);
   return cudaGetLastError();
 }
 

@@ -15,6 +15,8 @@
 // block doubles as the MN-major B operand of P V, a K block as the MN-major B operand of dS K,
 // so nothing is transposed and shared memory holds only Q, dO and the K/V rings.
 // (Reference behaviour: common/fused_attn/fused_attn_f16_arbitrary_seqlen.cu, cuDNN graphs.)
+#include <cstdlib>
+
 #include "flash_common.cuh"
 #include "flash_qouter_softmax.cuh"
 
@@ -65,7 +67,7 @@ template <int MODE, bool BF>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                    const FlashParams p) {
+                    const FlashParams p_launch) {
   using C = QCfg<MODE>;
   constexpr int KS = C::kKvStages;
   constexpr int SB = C::kSBufs;
@@ -86,16 +88,27 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   // heaviest query blocks of every head first
+  FlashParams p = p_launch;
   const int nqb = (p.sq + 255) / 256;
   const int qb = nqb - 1 - static_cast<int>(blockIdx.x) / p.hq;
   const int h = static_cast<int>(blockIdx.x) % p.hq;
   const int b = blockIdx.y;
+  const SeqView sv = localize(p, b);
+  p.out = reinterpret_cast<uint16_t*>(p.out) + static_cast<long long>(sv.q_off) * p.o_ss;
   const int hk = h / (p.hq / p.hk);
-  const int q0 = qb * 256;
+  // first query row of the CTA's two tiles: neighbours, or (few CTAs, causal mask) tile i with tile
+  // last - i, so that every CTA walks the same number of key blocks in total
+  int qrow[2] = {qb * 256, qb * 256 + 128};
+  if (p_launch.pair_balance) {
+    const int nqt = (p_launch.sq + 127) / 128;
+    const int lo = static_cast<int>(blockIdx.x) / p.hq, hi = nqt - 1 - lo;
+    qrow[0] = lo < hi ? lo * 128 : nqt * 128;  // the middle tile of an odd count runs alone
+    qrow[1] = hi * 128;
+  }
   int n[2];
   constexpr int BK = C::kBlockKv;
-  n[0] = kv_blocks_of_tile(p, q0, BK);
-  n[1] = kv_blocks_of_tile(p, q0 + 128, BK);
+  n[0] = kv_blocks_of_tile(p, qrow[0], BK);
+  n[1] = kv_blocks_of_tile(p, qrow[1], BK);
   const int nmax = n[0] > n[1] ? n[0] : n[1];
 
   if (threadIdx.x == 0) {
@@ -134,9 +147,9 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_expect_tx(q_full, C::kQBytes + C::kDoBytes);
       for (int t = 0; t < 2; ++t)
         for (int pn = 0; pn < 2; ++pn) {
-          tma_load_4d(smem + t * 32768 + pn * 16384, &tmap_q, q_full, pn * 64, q0 + t * 128, h, b);
+          tma_load_4d(smem + t * 32768 + pn * 16384, &tmap_q, q_full, pn * 64, sv.q_off + qrow[t], h, sv.bt);
           if (MODE == kDq)
-            tma_load_4d(smem + C::kOffDo + t * 32768 + pn * 16384, &tmap_do, q_full, pn * 64, q0 + t * 128, h, b);
+            tma_load_4d(smem + C::kOffDo + t * 32768 + pn * 16384, &tmap_do, q_full, pn * 64, sv.q_off + qrow[t], h, sv.bt);
         }
       for (int j = 0; j < nmax; ++j) {
         const int st = j % KS;
@@ -144,11 +157,11 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!mbar_wait(&k_empty[st], par)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         mbar_expect_tx(&k_full[st], C::kKvBytes);
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(smem + C::kOffK + st * C::kKvBytes + pn * C::kPanel, &tmap_k, &k_full[st], pn * 64, j * BK, hk, b);
+          tma_load_4d(smem + C::kOffK + st * C::kKvBytes + pn * C::kPanel, &tmap_k, &k_full[st], pn * 64, sv.k_off + j * BK, hk, sv.bt);
         if (!mbar_wait(&v_empty[st], par)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         mbar_expect_tx(&v_full[st], C::kKvBytes);
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(smem + C::kOffV + st * C::kKvBytes + pn * C::kPanel, &tmap_v, &v_full[st], pn * 64, j * BK, hk, b);
+          tma_load_4d(smem + C::kOffV + st * C::kKvBytes + pn * C::kPanel, &tmap_v, &v_full[st], pn * 64, sv.k_off + j * BK, hk, sv.bt);
       }
     }
   } else if (warp == 1) {
@@ -244,7 +257,7 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else {
     const int t = (warp - 2) >> 3;
-    qouter_softmax_role<MODE, BF, C>(p, smem, s_full, p_ready, pv_done, xchg, tmem_base, warp, lane, q0, h, b, n[t], t);
+    qouter_softmax_role<MODE, BF, C>(p, smem, s_full, p_ready, pv_done, xchg, tmem_base, warp, lane, qrow[t] - t * 128, h, b, n[t], t);
   }
 
   tc_fence_before();
@@ -289,10 +302,14 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
   using C = QCfg<MODE>;
   CUtensorMap tq, tk, tv, tdo;
   const bool bf = a.is_bf16;
-  bool ok = make_tensor_map_bhsd(&tq, a.q, bf, a.b, a.hq, a.sq, a.q_sb, a.q_sh, a.q_ss, 128) &&
-            make_tensor_map_bhsd(&tk, a.k, bf, a.b, a.hk, a.sk, a.k_sb, a.k_sh, a.k_ss, C::kBlockKv) &&
-            make_tensor_map_bhsd(&tv, a.v, bf, a.b, a.hk, a.sk, a.v_sb, a.v_sh, a.v_ss, C::kBlockKv);
-  if (MODE == kDq) ok = ok && make_tensor_map_bhsd(&tdo, a.dout, bf, a.b, a.hq, a.sq, a.do_sb, a.do_sh, a.do_ss, 128);
+  const bool varlen = a.cu_q != nullptr;
+  if (varlen && (a.cu_k == nullptr || a.off_q == nullptr || a.off_k == nullptr || a.tq <= 0 || a.tk <= 0))
+    return cudaErrorInvalidValue;
+  const int mb = varlen ? 1 : a.b, msq = varlen ? a.tq : a.sq, msk = varlen ? a.tk : a.sk;
+  bool ok = make_tensor_map_bhsd(&tq, a.q, bf, mb, a.hq, msq, a.q_sb, a.q_sh, a.q_ss, 128) &&
+            make_tensor_map_bhsd(&tk, a.k, bf, mb, a.hk, msk, a.k_sb, a.k_sh, a.k_ss, C::kBlockKv) &&
+            make_tensor_map_bhsd(&tv, a.v, bf, mb, a.hk, msk, a.v_sb, a.v_sh, a.v_ss, C::kBlockKv);
+  if (MODE == kDq) ok = ok && make_tensor_map_bhsd(&tdo, a.dout, bf, mb, a.hq, msq, a.do_sb, a.do_sh, a.do_ss, 128);
   else tdo = tq;
   if (!ok) return cudaErrorInvalidValue;
   FlashParams p = {};
@@ -306,6 +323,10 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
   else { p.out = a.dq; p.o_sb = a.dq_sb; p.o_sh = a.dq_sh; p.o_ss = a.dq_ss; }
   if ((reinterpret_cast<uintptr_t>(p.out) & 15) || p.o_sb % 8 || p.o_sh % 8 || p.o_ss % 8) return cudaErrorInvalidValue;
   p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status; p.timeline = a.timeline;
+  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.off_q = a.off_q; p.off_k = a.off_k; p.bottom_right = a.bottom_right ? 1 : 0;
+  p.gsplit = 1; p.o_sg = 0;
+  if (a.sq <= 0 || a.b <= 0) return cudaSuccess;
+  if (a.s_pad < a.sq) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(flash_qouter_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -317,6 +338,11 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
     attr_set = true;
   }
   dim3 grid(((a.sq + 255) / 256) * a.hq, a.b);
+  static const bool allow_pair = []() {
+    const char* e = std::getenv("TEB200_ATTN_PAIR");
+    return e == nullptr || e[0] != '0';
+  }();
+  p.pair_balance = allow_pair && a.causal && static_cast<long long>(grid.x) * grid.y <= 148 ? 1 : 0;
   if (bf) flash_qouter_kernel<MODE, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   else flash_qouter_kernel<MODE, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();

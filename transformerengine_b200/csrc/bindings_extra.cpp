@@ -2,6 +2,7 @@
 // (attention, softmax, dropout, MoE router / permutation, NVFP4, fused
 // communication).  Kept separate so that touching one family does not rebuild
 // the rest.
+#include <cstdlib>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <teb200/api.h>
@@ -132,6 +133,34 @@ void flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, co
   TORCH_CHECK(e == cudaSuccess, "flash_fwd failed: ", cudaGetErrorString(e));
 }
 
+
+// dK/dV of a few key heads underfill the GPU (tensor-parallel shards): split every head group over
+// several CTAs that write partial sums, and add the partials afterwards.
+void run_dkdv(teb200::FlashArgs& a, const at::Tensor& k, const at::Tensor& dk, const at::Tensor& dv, bool zero_fill) {
+  const int64_t ctas = static_cast<int64_t>((a.sk + 127) / 128) * a.hk * a.b;
+  const int group = a.hq / a.hk;
+  static const bool allow_split = []() {
+    const char* e = std::getenv("TEB200_ATTN_GSPLIT");
+    return e == nullptr || e[0] != '0';
+  }();
+  if (allow_split && group > 1 && ctas < 2 * 148) {
+    auto opts = dk.options();
+    std::vector<int64_t> shape = {group, k.size(0), k.size(1), k.size(2), 128};
+    at::Tensor pk = zero_fill ? at::zeros(shape, opts) : at::empty(shape, opts);
+    at::Tensor pv = zero_fill ? at::zeros(shape, opts) : at::empty(shape, opts);
+    a.dk = pk.data_ptr(); a.dv = pv.data_ptr();
+    a.dk_sb = a.dv_sb = pk.stride(1); a.dk_sh = a.dv_sh = pk.stride(2); a.dk_ss = a.dv_ss = pk.stride(3);
+    a.gsplit = group; a.dk_sg = pk.stride(0);
+    cudaError_t e = teb200::flash_bwd_dkdv(a, cur_stream());
+    TORCH_CHECK(e == cudaSuccess, "flash_bwd_dkdv (split) failed: ", cudaGetErrorString(e));
+    at::sum_out(const_cast<at::Tensor&>(dk), pk, at::IntArrayRef{0});
+    at::sum_out(const_cast<at::Tensor&>(dv), pv, at::IntArrayRef{0});
+    return;
+  }
+  cudaError_t e = teb200::flash_bwd_dkdv(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_bwd_dkdv failed: ", cudaGetErrorString(e));
+}
+
 void flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                const at::Tensor& out, const at::Tensor& lse, const at::Tensor& delta, const at::Tensor& dq,
                const at::Tensor& dk, const at::Tensor& dv, double scale, bool causal, bool bottom_right,
@@ -147,10 +176,61 @@ void flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
   fill_strides(dv, a.dv_sb, a.dv_sh, a.dv_ss);
   cudaError_t e = teb200::flash_delta(a, cur_stream());
   TORCH_CHECK(e == cudaSuccess, "flash_delta failed: ", cudaGetErrorString(e));
-  e = teb200::flash_bwd_dkdv(a, cur_stream());
-  TORCH_CHECK(e == cudaSuccess, "flash_bwd_dkdv failed: ", cudaGetErrorString(e));
+  run_dkdv(a, k, dk, dv, false);
   e = teb200::flash_bwd_dq(a, cur_stream());
   TORCH_CHECK(e == cudaSuccess, "flash_bwd_dq failed: ", cudaGetErrorString(e));
+}
+
+// Packed variable-length sequences: q / out / dout / dq are [1, hq, tq, d] views, k / v / dk / dv
+// [1, hk, tk, d]; cu_* hold cumulative lengths, off_* the first token of every sequence.
+void set_varlen(teb200::FlashArgs& a, const at::Tensor& q, const at::Tensor& k, const at::Tensor& cu_q,
+                const at::Tensor& cu_k, const at::Tensor& off_q, const at::Tensor& off_k, int64_t max_sq,
+                int64_t max_sk) {
+  for (const at::Tensor* t : {&cu_q, &cu_k, &off_q, &off_k})
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kInt && t->is_contiguous() && t->numel() == cu_q.numel(),
+                "cumulative sequence lengths must be contiguous int32 CUDA tensors of equal length");
+  TORCH_CHECK(q.size(0) == 1 && k.size(0) == 1 && cu_q.numel() >= 2, "packed attention takes [1, h, t, d] views");
+  a.cu_q = cu_q.data_ptr<int>(); a.cu_k = cu_k.data_ptr<int>();
+  a.off_q = off_q.data_ptr<int>(); a.off_k = off_k.data_ptr<int>();
+  a.b = static_cast<int>(cu_q.numel() - 1);
+  a.tq = static_cast<int>(q.size(2)); a.tk = static_cast<int>(k.size(2));
+  a.sq = static_cast<int>(max_sq); a.sk = static_cast<int>(max_sk);
+}
+
+void flash_fwd_varlen(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
+                      const at::Tensor& lse, const at::Tensor& cu_q, const at::Tensor& cu_k, const at::Tensor& off_q,
+                      const at::Tensor& off_k, int64_t max_sq, int64_t max_sk, double scale, bool causal,
+                      bool bottom_right, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  set_varlen(a, q, k, cu_q, cu_k, off_q, off_k, max_sq, max_sk);
+  TORCH_CHECK(lse.size(0) == a.b && lse.size(1) == a.hq && lse.size(2) >= max_sq, "lse must be [sequences, hq, >= max_sq]");
+  cudaError_t e = teb200::flash_fwd(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_fwd (packed) failed: ", cudaGetErrorString(e));
+}
+
+void flash_bwd_varlen(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
+                      const at::Tensor& out, const at::Tensor& lse, const at::Tensor& delta, const at::Tensor& dq,
+                      const at::Tensor& dk, const at::Tensor& dv, const at::Tensor& cu_q, const at::Tensor& cu_k,
+                      const at::Tensor& off_q, const at::Tensor& off_k, int64_t max_sq, int64_t max_sk, double scale,
+                      bool causal, bool bottom_right, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(q.device());
+  teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  set_varlen(a, q, k, cu_q, cu_k, off_q, off_k, max_sq, max_sk);
+  TORCH_CHECK(lse.size(0) == a.b && lse.size(2) % 128 == 0 && lse.size(2) >= max_sq && delta.sizes() == lse.sizes(),
+              "lse / delta must be [sequences, hq, s_pad] with s_pad a multiple of 128");
+  a.dout = dout.data_ptr();
+  a.delta = delta.data_ptr<float>();
+  a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
+  fill_strides(dout, a.do_sb, a.do_sh, a.do_ss);
+  fill_strides(dq, a.dq_sb, a.dq_sh, a.dq_ss);
+  fill_strides(dk, a.dk_sb, a.dk_sh, a.dk_ss);
+  fill_strides(dv, a.dv_sb, a.dv_sh, a.dv_ss);
+  cudaError_t e = teb200::flash_delta(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_delta (packed) failed: ", cudaGetErrorString(e));
+  run_dkdv(a, k, dk, dv, true);
+  e = teb200::flash_bwd_dq(a, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "flash_bwd_dq (packed) failed: ", cudaGetErrorString(e));
 }
 
 // ---------------------------------------------------------------------------- NVFP4
@@ -502,5 +582,7 @@ void register_extra(py::module_& m) {
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
         py::arg("timeline") = py::none());
   m.def("flash_bwd", &flash_bwd);
+  m.def("flash_fwd_varlen", &flash_fwd_varlen);
+  m.def("flash_bwd_varlen", &flash_bwd_varlen);
 }
 

@@ -78,6 +78,20 @@ struct FlashArgs {
   long long dq_sb = 0, dq_sh = 0, dq_ss = 0, dk_sb = 0, dk_sh = 0, dk_ss = 0, dv_sb = 0, dv_sh = 0, dv_ss = 0;
   int* status = nullptr;
   long long* timeline = nullptr;  // optional [64][16] clock stamps written by CTA 0 (profiling aid)
+  // Packed variable-length sequences: when cu_q is set, q/out/dout/dq are [1, hq, tq, d] and k/v/dk/dv
+  // [1, hk, tk, d] views of token-major tensors, b counts the sequences, sq / sk are the LONGEST
+  // sequence lengths; sequence i has cu_q[i+1] - cu_q[i] queries that start at token off_q[i]
+  // (same for keys).  All four are int32 device arrays of b + 1 entries.
+  const int* cu_q = nullptr;
+  const int* cu_k = nullptr;
+  const int* off_q = nullptr;
+  const int* off_k = nullptr;
+  int tq = 0, tk = 0;
+  // dK/dV pass: split every group of query heads that shares a key head over gsplit CTAs; CTA g writes
+  // its partial sums at dk + g * dk_sg (elements), the caller adds the gsplit partials.  Fills the GPU
+  // when key heads x key blocks are fewer than the SMs (tensor parallel shards).
+  int gsplit = 1;
+  long long dk_sg = 0;
 };
 cudaError_t flash_fwd(const FlashArgs& args, cudaStream_t stream);
 cudaError_t flash_delta(const FlashArgs& args, cudaStream_t stream);     // delta = rowsum(dO * O)

@@ -20,6 +20,21 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
+from . import thd as _thd
+
+
+def _step_metadata(lens_old: List[int], lens_new: List[int], tables: List[List[int]], device):
+    """Device-side description of one decoding step, shared by all layers: page table
+    ``[sequences, width]`` (-1 where unused) and the cumulative new / resulting lengths."""
+    width = max((len(t) for t in tables), default=1) or 1
+    pt = [list(t) + [-1] * (width - len(t)) for t in tables]
+    cu_new, cu_kv = [0], [0]
+    for o, n in zip(lens_old, lens_new):
+        cu_new.append(cu_new[-1] + n)
+        cu_kv.append(cu_kv[-1] + o + n)
+    mk = lambda x: torch.tensor(x, dtype=torch.int32, device=device)  # noqa: E731
+    return mk(pt).reshape(len(tables), width), mk(cu_new), mk(cu_kv), cu_kv[-1]
+
 
 class KVCacheManager:
     """Interface of a cache manager (custom managers may subclass it)."""
@@ -48,6 +63,7 @@ class NonPagedKVCacheManager(KVCacheManager):
         self.lengths: Dict[int, int] = {}                       # seq id -> tokens cached BEFORE this step
         self.step_dict: "OrderedDict[int, int]" = OrderedDict()
         self.free_slots = list(range(max_batch_size - 1, -1, -1))
+        self._meta = None  # device metadata of the current step (built by the first layer)
 
     def allocate_memory(self, layer_number):
         dev = self.device or ("cuda" if torch.cuda.is_available() else "cpu")
@@ -66,6 +82,7 @@ class NonPagedKVCacheManager(KVCacheManager):
                 self.slots[sid] = self.free_slots.pop()
                 self.lengths[sid] = 0
         self.step_dict = OrderedDict(step_dict)
+        self._meta = None
 
     def post_step(self):
         for sid, n in self.step_dict.items():
@@ -75,16 +92,15 @@ class NonPagedKVCacheManager(KVCacheManager):
         if layer_number not in self.cache:
             self.allocate_memory(layer_number)
         kc, vc = self.cache[layer_number]
-        ks, vs, lens = [], [], []
-        for i, (sid, n) in enumerate(self.step_dict.items()):
-            slot, old = self.slots[sid], self.lengths[sid]
-            assert old + n <= self.max_seq, "sequence exceeds max_sequence_length"
-            kc[slot, old:old + n] = new_k[cu_new[i]:cu_new[i + 1]]
-            vc[slot, old:old + n] = new_v[cu_new[i]:cu_new[i + 1]]
-            ks.append(kc[slot, :old + n])
-            vs.append(vc[slot, :old + n])
-            lens.append(old + n)
-        return torch.cat(ks, dim=0), torch.cat(vs, dim=0), lens
+        olds = [self.lengths[sid] for sid in self.step_dict]
+        news = list(self.step_dict.values())
+        assert all(o + n <= self.max_seq for o, n in zip(olds, news)), "sequence exceeds max_sequence_length"
+        if self._meta is None or self._meta[0].device != kc.device:
+            # the whole slab is one "page" per slot: page size = max_seq, page table = slot
+            self._meta = _step_metadata(olds, news, [[self.slots[sid]] for sid in self.step_dict], kc.device)
+        pt, cu_n, cu_kv, total = self._meta
+        k, v = _thd.kv_cache_step(new_k[:cu_new[-1]], new_v[:cu_new[-1]], kc, vc, pt, cu_n, cu_kv, total)
+        return k, v, [o + n for o, n in zip(olds, news)]
 
 
 class PagedKVCacheManager(KVCacheManager):
@@ -101,6 +117,7 @@ class PagedKVCacheManager(KVCacheManager):
         self.page_table: "OrderedDict[int, List[int]]" = OrderedDict()
         self.lengths: Dict[int, int] = {}
         self.step_dict: "OrderedDict[int, int]" = OrderedDict()
+        self._meta = None
 
     def allocate_memory(self, layer_number):
         dev = self.device or ("cuda" if torch.cuda.is_available() else "cpu")
@@ -122,6 +139,7 @@ class PagedKVCacheManager(KVCacheManager):
             for _ in range(max(need, 0)):
                 self.page_table[sid].append(self.free_pages.pop())
         self.step_dict = OrderedDict(step_dict)
+        self._meta = None
 
     def post_step(self):
         for sid, n in self.step_dict.items():
@@ -139,21 +157,13 @@ class PagedKVCacheManager(KVCacheManager):
         if layer_number not in self.cache:
             self.allocate_memory(layer_number)
         kc, vc = self.cache[layer_number]
-        ps = self.page_size
-        ks, vs, lens = [], [], []
-        for i, (sid, n) in enumerate(self.step_dict.items()):
-            old = self.lengths[sid]
-            pages = torch.tensor(self.page_table[sid], device=kc.device, dtype=torch.long)
-            pos = torch.arange(old, old + n, device=kc.device)
-            pg, off = pages[pos // ps], pos % ps
-            kc[pg, off] = new_k[cu_new[i]:cu_new[i + 1]]
-            vc[pg, off] = new_v[cu_new[i]:cu_new[i + 1]]
-            tot = old + n
-            npg = -(-tot // ps)
-            ks.append(kc[pages[:npg]].reshape(npg * ps, self.h, self.dk)[:tot])
-            vs.append(vc[pages[:npg]].reshape(npg * ps, self.h, self.dv)[:tot])
-            lens.append(tot)
-        return torch.cat(ks, dim=0), torch.cat(vs, dim=0), lens
+        olds = [self.lengths[sid] for sid in self.step_dict]
+        news = list(self.step_dict.values())
+        if self._meta is None or self._meta[0].device != kc.device:
+            self._meta = _step_metadata(olds, news, [self.page_table[sid] for sid in self.step_dict], kc.device)
+        pt, cu_n, cu_kv, total = self._meta
+        k, v = _thd.kv_cache_step(new_k[:cu_new[-1]], new_v[:cu_new[-1]], kc, vc, pt, cu_n, cu_kv, total)
+        return k, v, [o + n for o, n in zip(olds, news)]
 
 
 class InferenceParams:
@@ -226,13 +236,13 @@ class InferenceParams:
                 q, k, v = (t.transpose(0, 1) for t in (q, k, v))
             b, s = q.shape[0], q.shape[1]
             assert nb <= b, "step_dict names more sequences than the batch holds"
-            qp = torch.cat([q[i, :n] for i, n in enumerate(lens_new)], dim=0)
-            kp = torch.cat([k[i, :n] for i, n in enumerate(lens_new)], dim=0)
-            vp = torch.cat([v[i, :n] for i, n in enumerate(lens_new)], dim=0)
             cu = [0]
             for n in lens_new:
                 cu.append(cu[-1] + n)
+            cu_t = torch.tensor(cu, dtype=torch.int32, device=q.device)
+            qp, kp, vp = (_thd.convert_bshd_to_thd(t, cu_t, cu[-1]) for t in (q, k, v))
             self._orig = (qkv_format, b, s)
+            self._cu_new = cu_t
         kf, vf, lens_kv = self.cache_manager.step(layer_number, kp, vp, cu)
         cu_kv = [0]
         for n in lens_kv:
@@ -247,10 +257,5 @@ class InferenceParams:
         fmt, b, s = self._orig
         if fmt == "thd":
             return out
-        lens_new = list(self.step_dict.values())
-        res = out.new_zeros(b, s, out.shape[-1])
-        pos = 0
-        for i, n in enumerate(lens_new):
-            res[i, :n] = out[pos:pos + n]
-            pos += n
+        res = _thd.convert_thd_to_bshd(out, self._cu_new, b, s)
         return res.transpose(0, 1) if fmt == "sbhd" else res

@@ -233,6 +233,162 @@ void flash_bwd_varlen(const at::Tensor& dout, const at::Tensor& q, const at::Ten
   TORCH_CHECK(e == cudaSuccess, "flash_bwd_dq (packed) failed: ", cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------------------- packed sequences / KV cache
+namespace {
+const int* cu_ptr(const at::Tensor& cu) {
+  TORCH_CHECK(cu.is_cuda() && cu.scalar_type() == at::kInt && cu.is_contiguous() && cu.numel() >= 2,
+              "cumulative sequence lengths must be a contiguous int32 CUDA tensor of at least 2 entries");
+  return cu.data_ptr<int>();
+}
+int thd_dtype(const at::Tensor& t) {
+  if (t.scalar_type() == at::kFloat) return 0;
+  if (t.scalar_type() == at::kHalf) return 1;
+  TORCH_CHECK(t.scalar_type() == at::kBFloat16, "expected fp32, fp16 or bf16");
+  return 2;
+}
+void thd_check(cudaError_t e, const char* what) { TORCH_CHECK(e == cudaSuccess, what, " failed: ", cudaGetErrorString(e)); }
+}  // namespace
+
+at::Tensor thd_get_partitioned_indices(const at::Tensor& cu, int64_t total_tokens, int64_t world, int64_t rank) {
+  c10::cuda::CUDAGuard guard(cu.device());
+  at::Tensor out = at::empty({total_tokens / world}, cu.options());
+  thd_check(teb200::thd_partition_indices(out.data_ptr<int>(), cu_ptr(cu), static_cast<int>(cu.numel() - 1),
+                                          static_cast<int>(total_tokens), static_cast<int>(world),
+                                          static_cast<int>(rank), cur_stream()), "thd_get_partitioned_indices");
+  return out;
+}
+
+// tensor [t, ...] or [2, t, ...] (stacked K/V)
+at::Tensor thd_read_half_tensor(const at::Tensor& tensor, const at::Tensor& cu, int64_t half_idx, bool stacked) {
+  c10::cuda::CUDAGuard guard(tensor.device());
+  at::Tensor x = tensor.contiguous();
+  const int seq_dim = stacked ? 1 : 0;
+  const int64_t t = x.size(seq_dim);
+  const int64_t row_bytes = x.numel() / (t * (stacked ? x.size(0) : 1)) * x.element_size();
+  auto shape = x.sizes().vec();
+  shape[seq_dim] = t / 2;
+  at::Tensor half = at::empty(shape, x.options());
+  thd_check(teb200::thd_read_half(half.data_ptr(), x.data_ptr(), cu_ptr(cu), static_cast<int>(cu.numel() - 1),
+                                  static_cast<int>(t), stacked ? static_cast<int>(x.size(0)) : 1,
+                                  static_cast<int>(row_bytes), static_cast<int>(half_idx), cur_stream()),
+            "thd_read_half_tensor");
+  return half;
+}
+
+void thd_second_half_lse_correction(const at::Tensor& lse, const at::Tensor& lse_per_step, const at::Tensor& cu) {
+  c10::cuda::CUDAGuard guard(lse.device());
+  TORCH_CHECK(lse.dim() == 2 && lse.is_contiguous() && lse.scalar_type() == at::kFloat && lse_per_step.is_contiguous() &&
+              lse_per_step.scalar_type() == at::kFloat && lse_per_step.size(0) == lse.size(0) &&
+              lse_per_step.size(1) * 2 == lse.size(1), "lse must be fp32 [heads, t], lse_per_step [heads, t / 2]");
+  thd_check(teb200::thd_lse_half(lse.data_ptr<float>(), lse_per_step.data_ptr<float>(), cu_ptr(cu),
+                                 static_cast<int>(cu.numel() - 1), static_cast<int>(lse.size(0)),
+                                 static_cast<int>(lse.size(1)), 0, cur_stream()), "thd_second_half_lse_correction");
+}
+
+at::Tensor thd_read_second_half_lse(const at::Tensor& lse, const at::Tensor& cu) {
+  c10::cuda::CUDAGuard guard(lse.device());
+  TORCH_CHECK(lse.dim() == 2 && lse.is_contiguous() && lse.scalar_type() == at::kFloat, "lse must be fp32 [heads, t]");
+  at::Tensor half = at::empty({lse.size(0), lse.size(1) / 2}, lse.options());
+  thd_check(teb200::thd_lse_half(lse.data_ptr<float>(), half.data_ptr<float>(), cu_ptr(cu),
+                                 static_cast<int>(cu.numel() - 1), static_cast<int>(lse.size(0)),
+                                 static_cast<int>(lse.size(1)), 1, cur_stream()), "thd_read_second_half_lse");
+  return half;
+}
+
+void thd_out_correction(const at::Tensor& out, const at::Tensor& out_per_step, const at::Tensor& lse,
+                        const at::Tensor& lse_per_step, const at::Tensor& cu, bool only_second_half) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.dim() == 3 && out.is_contiguous() && out_per_step.is_contiguous() &&
+              out.scalar_type() == out_per_step.scalar_type(), "out / out_per_step must be contiguous [t, h, d] of one dtype");
+  const int64_t t = out.size(0), ts = only_second_half ? t / 2 : t;
+  TORCH_CHECK(out_per_step.size(0) == ts && lse.is_contiguous() && lse_per_step.is_contiguous() &&
+              lse.scalar_type() == at::kFloat && lse_per_step.scalar_type() == at::kFloat && lse.size(0) == out.size(1) &&
+              lse.size(1) == t && lse_per_step.size(0) == out.size(1) && lse_per_step.size(1) == ts,
+              "lse must be fp32 [h, t] and the per-step tensors must cover t (or t / 2) tokens");
+  thd_check(teb200::thd_out_correction(out.data_ptr(), out_per_step.data_ptr(), lse.data_ptr<float>(),
+                                       lse_per_step.data_ptr<float>(), cu_ptr(cu), static_cast<int>(cu.numel() - 1),
+                                       static_cast<int>(out.size(1)), static_cast<int>(out.size(2)),
+                                       static_cast<int>(t), only_second_half ? 1 : 0, thd_dtype(out), cur_stream()),
+            "thd_out_correction");
+}
+
+void thd_grad_correction(const at::Tensor& grad, const at::Tensor& grad_per_step, const at::Tensor& cu,
+                         int64_t mode_first, int64_t mode_second, bool stacked) {
+  c10::cuda::CUDAGuard guard(grad.device());
+  TORCH_CHECK(grad.is_contiguous() && grad_per_step.is_contiguous() && grad.scalar_type() == grad_per_step.scalar_type(),
+              "grad / grad_per_step must be contiguous and of one dtype");
+  const int seq_dim = stacked ? 1 : 0;
+  const int64_t t = grad.size(seq_dim), ts = grad_per_step.size(seq_dim);
+  const int64_t lead = stacked ? grad.size(0) : 1;
+  const int64_t row = grad.numel() / (t * lead);
+  thd_check(teb200::thd_grad_correction(grad.data_ptr(), grad_per_step.data_ptr(), cu_ptr(cu),
+                                        static_cast<int>(cu.numel() - 1), static_cast<int>(lead), static_cast<int>(row),
+                                        static_cast<int>(t), static_cast<int>(ts), static_cast<int>(mode_first),
+                                        static_cast<int>(mode_second), thd_dtype(grad), cur_stream()),
+            "thd_grad_correction");
+}
+
+at::Tensor convert_thd_to_bshd(const at::Tensor& tensor, const at::Tensor& cu, int64_t b, int64_t max_seq_len) {
+  c10::cuda::CUDAGuard guard(tensor.device());
+  at::Tensor x = tensor.contiguous();
+  auto shape = x.sizes().vec();
+  shape[0] = max_seq_len;
+  shape.insert(shape.begin(), b);
+  at::Tensor out = at::zeros(shape, x.options());
+  TORCH_CHECK(cu.numel() - 1 <= b, "more sequences than batch entries");
+  const int64_t row_bytes = x.numel() / std::max<int64_t>(x.size(0), 1) * x.element_size();
+  thd_check(teb200::thd_bshd_convert(x.data_ptr(), out.data_ptr(), cu_ptr(cu), static_cast<int>(cu.numel() - 1),
+                                     static_cast<int>(x.size(0)), static_cast<int>(max_seq_len),
+                                     static_cast<int>(row_bytes), 1, cur_stream()), "convert_thd_to_bshd");
+  return out;
+}
+
+at::Tensor convert_bshd_to_thd(const at::Tensor& tensor, const at::Tensor& cu, int64_t t) {
+  c10::cuda::CUDAGuard guard(tensor.device());
+  at::Tensor x = tensor.contiguous();
+  auto shape = x.sizes().vec();
+  shape.erase(shape.begin());
+  shape[0] = t;
+  at::Tensor out = at::zeros(shape, x.options());
+  TORCH_CHECK(cu.numel() - 1 <= x.size(0), "more sequences than batch entries");
+  const int64_t row_bytes = x.numel() / std::max<int64_t>(x.size(0) * x.size(1), 1) * x.element_size();
+  thd_check(teb200::thd_bshd_convert(out.data_ptr(), x.data_ptr(), cu_ptr(cu), static_cast<int>(cu.numel() - 1),
+                                     static_cast<int>(t), static_cast<int>(x.size(1)), static_cast<int>(row_bytes), 0,
+                                     cur_stream()), "convert_bshd_to_thd");
+  return out;
+}
+
+// caches [num_pages, page_size, h, d]; new_k / new_v [sum new, h, d]; returns packed (k, v) of all live sequences
+std::vector<at::Tensor> kv_cache_step(const at::Tensor& new_k, const at::Tensor& new_v, const at::Tensor& cache_k,
+                                      const at::Tensor& cache_v, const at::Tensor& page_table, const at::Tensor& cu_new,
+                                      const at::Tensor& cu_kv, int64_t total, const at::Tensor& status) {
+  c10::cuda::CUDAGuard guard(cache_k.device());
+  TORCH_CHECK(cache_k.is_contiguous() && cache_v.is_contiguous() && cache_k.dim() == 4 && cache_v.dim() == 4,
+              "caches must be contiguous [pages, page_size, h, d]");
+  TORCH_CHECK(page_table.is_cuda() && page_table.scalar_type() == at::kInt && page_table.is_contiguous() &&
+              page_table.dim() == 2 && page_table.size(0) == cu_kv.numel() - 1 && cu_new.numel() == cu_kv.numel(),
+              "page_table must be int32 [sequences, width]");
+  at::Tensor nk = new_k.contiguous(), nv = new_v.contiguous();
+  TORCH_CHECK(nk.scalar_type() == cache_k.scalar_type() && nv.scalar_type() == cache_v.scalar_type(),
+              "new tokens and cache must have one dtype");
+  at::Tensor out_k = at::empty({total, cache_k.size(2), cache_k.size(3)}, cache_k.options());
+  at::Tensor out_v = at::empty({total, cache_v.size(2), cache_v.size(3)}, cache_v.options());
+  teb200::KvCacheArgs a;
+  a.new_k = nk.data_ptr(); a.new_v = nv.data_ptr();
+  a.cache_k = cache_k.data_ptr(); a.cache_v = cache_v.data_ptr();
+  a.out_k = out_k.data_ptr(); a.out_v = out_v.data_ptr();
+  a.cu_new = cu_ptr(cu_new); a.cu_kv = cu_ptr(cu_kv); a.page_table = page_table.data_ptr<int>();
+  a.nb = static_cast<int>(cu_kv.numel() - 1); a.width = static_cast<int>(page_table.size(1));
+  a.page_size = static_cast<int>(cache_k.size(1)); a.num_pages = static_cast<int>(cache_k.size(0));
+  a.total = static_cast<int>(total);
+  a.row_bytes_k = static_cast<int>(cache_k.size(2) * cache_k.size(3) * cache_k.element_size());
+  a.row_bytes_v = static_cast<int>(cache_v.size(2) * cache_v.size(3) * cache_v.element_size());
+  TORCH_CHECK(nk.numel() * nk.element_size() % a.row_bytes_k == 0, "new_k rows do not match the cache rows");
+  a.status = status.data_ptr<int>();
+  thd_check(teb200::kv_cache_step(a, cur_stream()), "kv_cache_step");
+  return {out_k, out_v};
+}
+
 // ---------------------------------------------------------------------------- NVFP4
 template <typename T = void>
 T* optr(const OptT& t) {
@@ -582,6 +738,15 @@ void register_extra(py::module_& m) {
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
         py::arg("timeline") = py::none());
   m.def("flash_bwd", &flash_bwd);
+  m.def("thd_get_partitioned_indices", &thd_get_partitioned_indices);
+  m.def("thd_read_half_tensor", &thd_read_half_tensor);
+  m.def("thd_second_half_lse_correction", &thd_second_half_lse_correction);
+  m.def("thd_read_second_half_lse", &thd_read_second_half_lse);
+  m.def("thd_out_correction", &thd_out_correction);
+  m.def("thd_grad_correction", &thd_grad_correction);
+  m.def("convert_thd_to_bshd", &convert_thd_to_bshd);
+  m.def("convert_bshd_to_thd", &convert_bshd_to_thd);
+  m.def("kv_cache_step", &kv_cache_step);
   m.def("flash_fwd_varlen", &flash_fwd_varlen);
   m.def("flash_bwd_varlen", &flash_bwd_varlen);
 }

@@ -143,4 +143,44 @@ cudaError_t unpermute_rows(const void* in, void* out, const int32_t* dest_row, c
 cudaError_t build_dest_rows(const int32_t* topk_idx, int T, int topk, int E, int align, int32_t* counts,
                             int32_t* offsets, int32_t* dest_row, cudaStream_t s);
 
+// ---------------------------------------------------------------- packed sequences ("thd") and KV cache
+// cu: int32 cumulative sequence lengths [nb + 1] on the device.  dtype: 0 fp32, 1 fp16, 2 bf16.
+// Context parallel layout: every sequence is cut into 2 * world chunks, rank r holds chunks r and
+// 2 * world - 1 - r ("first half" and "second half" of its local tokens).
+cudaError_t thd_partition_indices(int* out, const int* cu, int nb, int total_tokens, int world, int rank,
+                                  cudaStream_t s);
+// half [lead, t/2, row] <- the first (0) or second (1) half of every sequence of full [lead, t, row]
+cudaError_t thd_read_half(void* half, const void* full, const int* cu, int nb, int t, int lead, int row_bytes,
+                          int half_idx, cudaStream_t s);
+// lse [heads, t], half [heads, t/2]; mode 0: lse(second halves) = logaddexp(lse, half); mode 1: half = lse(second halves)
+cudaError_t thd_lse_half(float* lse, float* half, const int* cu, int nb, int heads, int t, int mode, cudaStream_t s);
+// out [t, heads, d] += step [t or t/2, heads, d] * exp(lse_step - lse)
+cudaError_t thd_out_correction(void* out, const void* step, const float* lse, const float* lse_step, const int* cu,
+                               int nb, int heads, int d, int t, int only_second_half, int dtype, cudaStream_t s);
+// grad [lead, t, row] (op)= step [lead, t_step, row] per half of every sequence; modes: 0 leave, 1 copy, 2 add
+cudaError_t thd_grad_correction(void* grad, const void* step, const int* cu, int nb, int lead, int row, int t,
+                                int t_step, int mode_first, int mode_second, int dtype, cudaStream_t s);
+// packed [t, row] <-> padded [nb, s_max, row] (the destination must be zero-filled by the caller)
+cudaError_t thd_bshd_convert(void* packed, void* padded, const int* cu, int nb, int t, int s_max, int row_bytes,
+                             int to_bshd, cudaStream_t s);
+
+// One decoding step of a (paged) KV cache: append every sequence's new tokens to the cache and gather
+// all live sequences' keys / values, old and new, into packed [total, row] tensors.  A contiguous
+// cache is the case page_size = max sequence length, width = 1, page_table[i] = slot of sequence i.
+struct KvCacheArgs {
+  const void* new_k = nullptr;  // [sum new, row]
+  const void* new_v = nullptr;
+  void* cache_k = nullptr;      // [num_pages, page_size, row]
+  void* cache_v = nullptr;
+  void* out_k = nullptr;        // [total, row]
+  void* out_v = nullptr;
+  const int* cu_new = nullptr;  // [nb + 1] cumulative new tokens
+  const int* cu_kv = nullptr;   // [nb + 1] cumulative lengths after the step
+  const int* page_table = nullptr;  // [nb, width]
+  int nb = 0, width = 0, page_size = 0, num_pages = 0, total = 0;
+  int row_bytes_k = 0, row_bytes_v = 0;
+  int* status = nullptr;
+};
+cudaError_t kv_cache_step(const KvCacheArgs& a, cudaStream_t s);
+
 }  // namespace teb200

@@ -137,3 +137,62 @@ def test_hierarchical_cp_matches_single_rank():
     for rank, err, tb in results:
         assert tb is None, tb
         assert err < 2e-5, (rank, err)
+
+
+def _thd_worker(rank, world, port, causal, result_q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from transformerengine_b200.attention import thd
+        from transformerengine_b200.ops.attention import attention_ref
+        from transformerengine_b200.parallel.context_parallel import attn_forward_func_with_cp
+
+        torch.manual_seed(0)
+        lens = [8, 24, 16]
+        cu = torch.tensor([0, 8, 32, 48], dtype=torch.int32)
+        t, hq, hk, d = 48, 4, 2, 16
+        q = torch.randn(t, hq, d, dtype=torch.float64)
+        k = torch.randn(t, hk, d, dtype=torch.float64)
+        v = torch.randn(t, hk, d, dtype=torch.float64)
+        do = torch.randn(t, hq, d, dtype=torch.float64)
+        qf, kf, vf = (x.clone().requires_grad_() for x in (q, k, v))
+        bh = lambda x: x.permute(1, 0, 2).unsqueeze(0)  # noqa: E731
+        ref = torch.cat([attention_ref(bh(qf[a:b]), bh(kf[a:b]), bh(vf[a:b]), causal=causal).squeeze(0).permute(1, 0, 2)
+                         for a, b in zip(cu[:-1].tolist(), cu[1:].tolist())])
+        ref.backward(do)
+        idx = thd.thd_get_partitioned_indices(cu, t, world, rank).long()
+        ql, kl, vl = (x[idx].clone().requires_grad_() for x in (q, k, v))
+        out = attn_forward_func_with_cp(ql, kl, vl, cp_group=dist.group.WORLD, cp_comm_type="p2p", causal=causal,
+                                        qkv_format="thd", cu_seqlens=cu // world)
+        out.backward(do[idx])
+        errs = [
+            (out - ref.detach()[idx]).abs().max().item(),
+            (ql.grad - qf.grad[idx]).abs().max().item(),
+            (kl.grad - kf.grad[idx]).abs().max().item(),
+            (vl.grad - vf.grad[idx]).abs().max().item(),
+        ]
+        result_q.put((rank, max(errs), None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("world", [2, 4])
+def test_thd_ring_attention_matches_per_sequence_attention(world, causal):
+    ctx = mp.get_context("spawn")
+    result_q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_thd_worker, args=(r, world, port, causal, result_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [result_q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err, tb in results:
+        assert tb is None, f"rank {rank} failed:\n{tb}"
+        assert err < 1e-4, f"rank {rank}: max error {err}"

@@ -72,6 +72,38 @@ def _worker(rank, world, port, result_q):
                     m = r.float().abs().max().item()
                     if not e <= 3e-2 * max(m, 1e-3):
                         bad[f"{nm} causal={causal} it={it}"] = (e, m)
+        # packed sequences: ring over NCCL, every product one launch of the variable-length kernels
+        from transformerengine_b200.attention import thd
+
+        lens = [256 * world, 512 * world, 128 * world]
+        cu = torch.tensor([0] + [sum(lens[:i + 1]) for i in range(len(lens))], dtype=torch.int32, device="cuda")
+        t = int(cu[-1])
+        for causal in (True, False):
+            torch.manual_seed(20)
+            q = torch.randn(t, hq, d, device="cuda", dtype=torch.bfloat16)
+            k = torch.randn(t, hk, d, device="cuda", dtype=torch.bfloat16)
+            v = torch.randn(t, hk, d, device="cuda", dtype=torch.bfloat16)
+            do = torch.randn(t, hq, d, device="cuda", dtype=torch.bfloat16)
+            qf, kf, vf = (x.float().requires_grad_() for x in (q, k, v))
+            bh = lambda x: x.permute(1, 0, 2).unsqueeze(0)  # noqa: E731
+            ref = torch.cat([attention_ref(bh(qf[a:e]), bh(kf[a:e]), bh(vf[a:e]), causal=causal).squeeze(0).permute(1, 0, 2)
+                             for a, e in zip(cu[:-1].tolist(), cu[1:].tolist())])
+            ref.backward(do.float())
+            idx = thd.thd_get_partitioned_indices(cu, t, world, rank).long()
+            ql, kl, vl = (x[idx].clone().requires_grad_() for x in (q, k, v))
+            out = attn_forward_func_with_cp(ql, kl, vl, cp_group=g, cp_comm_type="p2p", causal=causal,
+                                            qkv_format="thd", cu_seqlens=cu // world)
+            out.backward(do[idx])
+            torch.cuda.synchronize()
+            te.check_status()
+            log(f"thd causal={causal} done")
+            pairs = {"out": (out, ref.detach()[idx]), "dq": (ql.grad, qf.grad[idx]), "dk": (kl.grad, kf.grad[idx]),
+                     "dv": (vl.grad, vf.grad[idx])}
+            for nm, (a, r) in pairs.items():
+                e = (a.float() - r.float()).abs().max().item()
+                m = r.float().abs().max().item()
+                if not e <= 3e-2 * max(m, 1e-3):
+                    bad[f"thd {nm} causal={causal}"] = (e, m)
         result_q.put((rank, bad))
     except Exception:  # noqa: BLE001
         import traceback

@@ -172,6 +172,14 @@ class DotProductAttention(torch.nn.Module):
         if cu_kv_padded is None and cu_q_padded is not None and cu_kv is cu_q:
             cu_kv_padded = cu_q_padded
         causal = "causal" in mask_type
+        if self.cp_group is not None and D.get_world_size(self.cp_group) > 1:
+            # cu_q holds the lengths of this rank's shard (dual-chunk layout of every sequence)
+            from ..parallel.context_parallel_thd import thd_ring_attention
+
+            assert self.cp_comm_type == "p2p", "packed sequences support the ring (p2p) context-parallel mode"
+            o = thd_ring_attention(q, k, v, cu_q, cp_group=self.cp_group, scale=self.softmax_scale, causal=causal,
+                                   cp_global_ranks=self.cp_global_ranks, max_seqlen=max_sq)
+            return o.reshape(o.shape[0], -1)
         dropout = self.attention_dropout if self.training else 0.0
         no_window = window is None or (window[0] < 0 and window[1] in (-1, 0) and (window[1] == -1 or causal))
         if q.is_cuda and no_window and dropout == 0.0 and self.softmax_type == "vanilla" and \

@@ -89,10 +89,10 @@ def thd_out_correction(out: torch.Tensor, out_per_step: torch.Tensor, lse: torch
         return
     if only_second_half:
         idx = _half_index(cu_seqlens, 1, out.shape[0]).to(out.device)
-        w = torch.exp(lse_per_step - lse[:, idx]).t().unsqueeze(-1)
+        w = torch.nan_to_num(torch.exp(lse_per_step - lse[:, idx]), nan=0.0).t().unsqueeze(-1)
         out[idx] = (out[idx].float() + out_per_step.float() * w).to(out.dtype)
     else:
-        w = torch.exp(lse_per_step - lse).t().unsqueeze(-1)
+        w = torch.nan_to_num(torch.exp(lse_per_step - lse), nan=0.0).t().unsqueeze(-1)
         out.copy_((out.float() + out_per_step.float() * w).to(out.dtype))
 
 

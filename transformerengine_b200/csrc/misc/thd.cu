@@ -100,7 +100,8 @@ __global__ void thd_out_correction_kernel(T* __restrict__ out, const T* __restri
                                           int only_second_half) {
   const int j = blockIdx.x, h = blockIdx.y;
   const int tok = only_second_half ? half_token(cu, nb, j, 1) : j;
-  const float w = __expf(lse_step[static_cast<size_t>(h) * t_step + j] - lse[static_cast<size_t>(h) * t + tok]);
+  const float ls = lse_step[static_cast<size_t>(h) * t_step + j];
+  const float w = ls == -INFINITY ? 0.f : __expf(ls - lse[static_cast<size_t>(h) * t + tok]);  // empty partial result
   T* o = out + (static_cast<size_t>(tok) * heads + h) * d;
   const T* s = step + (static_cast<size_t>(j) * heads + h) * d;
   for (int c = threadIdx.x; c < d; c += blockDim.x) o[c] = from_f<T>(to_f<T>(o[c]) + to_f<T>(s[c]) * w);

@@ -227,8 +227,16 @@ def _a2a(x, group, to_heads):
 
 
 def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", scale: Optional[float] = None,
-                              causal: bool = True, window=None, cp_global_ranks=None, cp_stream=None):
-    """Attention over the full sequence from per-rank shards; returns ``[b, h, s_local, d]``."""
+                              causal: bool = True, window=None, cp_global_ranks=None, cp_stream=None,
+                              qkv_format: str = "bhsd", cu_seqlens=None, max_seqlen=None):
+    """Attention over the full sequence from per-rank shards; returns ``[b, h, s_local, d]``
+    (``[t_local, h, d]`` for ``qkv_format="thd"``, which takes the local cumulative lengths)."""
+    if qkv_format == "thd":
+        from .context_parallel_thd import thd_ring_attention
+
+        assert cp_comm_type == "p2p" and cu_seqlens is not None, "packed sequences: ring mode with cu_seqlens"
+        return thd_ring_attention(q, k, v, cu_seqlens, cp_group=cp_group, scale=scale, causal=causal,
+                                  cp_global_ranks=cp_global_ranks, max_seqlen=max_seqlen)
     from ..ops.attention import attention_ref
 
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])

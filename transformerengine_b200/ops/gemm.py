@@ -50,7 +50,15 @@ def as_operand(t, usage: str = "rowwise") -> Operand:
     from ..tensor.nvfp4 import NVFP4TensorStorage
     from ..tensor.blockwise import Float8BlockwiseQTensorStorage
 
+    from ..tensor.hybrid import HybridQuantizedTensorStorage, IdentityTensorStorage
+
     row = usage == "rowwise"
+    if isinstance(t, HybridQuantizedTensorStorage):  # each direction has its own format
+        child = t._rowwise if row else t._columnwise
+        assert child is not None, f"hybrid operand lacks the {usage} copy"
+        return as_operand(child, usage)
+    if isinstance(t, IdentityTensorStorage):
+        return as_operand(t._data.reshape(t._shape), usage)
     if isinstance(t, MXFP8TensorStorage):
         R, C = t._rows_cols()
         if row:

@@ -70,3 +70,34 @@ def test_linear_with_hybrid_weight_quantizer_in_custom_recipe():
     assert x.grad is not None and lin.weight.grad is not None
     gref = torch.ones(32, 96) @ lin.weight
     assert (x.grad - gref).abs().max() < 0.1 * gref.abs().max() + 0.05
+
+
+def test_grouped_tensor_members_share_one_buffer_and_quantize_per_member():
+    from transformerengine_b200.tensor import GroupedTensor
+
+    g = GroupedTensor.make_grouped_tensor_with_shapes(3, [(32, 64)] * 3, dtype=torch.bfloat16)
+    assert g.all_same_shape() and g.logical_shape == (96, 64) and g.first_dims is None
+    ws = [torch.randn(32, 64) for _ in range(3)]
+    g.quantize(ws)
+    m = g.split_into_quantized_tensors()
+    assert m[1].data_ptr() == g.data.data_ptr() + 32 * 64 * 2  # views of the packed buffer
+    torch.testing.assert_close(g.stacked()[2].float(), ws[2].bfloat16().float())
+    assert g.tensor_offsets.tolist() == [0, 2048, 4096, 6144]
+
+    # ragged members (tokens per expert) with an MXFP8 quantizer
+    first = torch.tensor([32, 96, 64])
+    gq = GroupedTensor.make_grouped_tensor(3, first, None, 192, 64, quantizer=MXFP8Quantizer(torch.float8_e4m3fn))
+    assert not gq.all_same_first_dim() and gq.get_common_last_dim() == 64
+    xs = [torch.randn(int(n), 64) for n in first]
+    parts = gq.quantize(xs)
+    assert gq.has_data() and gq.has_columnwise_data()
+    for p, x in zip(parts, xs):
+        assert as_operand(p, "rowwise").kind == "mxfp8"
+        assert (p.dequantize(dtype=torch.float32) - x).abs().max() < 0.25
+    saved, obj = gq.prepare_for_saving()
+    assert obj.restore_from_saved(saved) == []
+    assert gq.rowwise_data.numel() == 192 * 64
+
+    w = torch.arange(2 * 4 * 8, dtype=torch.float32)
+    gw = GroupedTensor.make_grouped_tensor_from_rowwise_data(num_tensors=2, tensor_shape=(4, 8), rowwise_data=w)
+    assert gw.split_into_quantized_tensors()[1][0, 0] == 32

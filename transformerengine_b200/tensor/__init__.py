@@ -6,3 +6,4 @@ from .nvfp4 import NVFP4Tensor, NVFP4TensorStorage, NVFP4Quantizer
 from .blockwise import Float8BlockwiseQTensor, Float8BlockwiseQTensorStorage, Float8BlockQuantizer
 from .hybrid import (HybridQuantizedTensor, HybridQuantizedTensorStorage, HybridQuantizer, IdentityQuantizer,
                      IdentityTensor, IdentityTensorStorage)
+from .grouped import GroupedTensor, GroupedTensorStorage

@@ -106,3 +106,33 @@ def test_quantize_master_weights_single_rank():
     master = torch.arange(16, dtype=torch.float32)
     quantize_master_weights([w], [master], [8])
     assert torch.equal(w.detach().reshape(-1)[8:24], master) and w.detach().reshape(-1)[:8].abs().sum() == 0
+
+
+def test_debug_per_tensor_scaling_and_fake_quant():
+    """PerTensorScaling swaps the recipe's quantizer for FP8 current scaling on the chosen tensors;
+    FakeQuant rounds to the low-precision grid and runs the GEMM in high precision."""
+    torch.manual_seed(0)
+    lin = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu", name="enc.fc")
+    x = torch.randn(32, 64)
+    with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+        base = lin(x)
+    debug_api.initialize({"pts": {"enabled": True, "layers": {"layer_names": ["enc.fc"]},
+                                  "features": {"PerTensorScaling": {"tensors": ["activation", "weight"], "gemms": ["fprop"]},
+                                               "LogFp8TensorStats": {"tensors": ["activation"], "stats": ["mse"]}}}})
+    try:
+        with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+            y = lin(x)
+        ref = x @ lin.weight.t()
+        assert (y - ref).abs().max() < 0.1 * ref.abs().max()
+        assert not torch.equal(y, base)  # per-tensor scales round differently from 1x32 block scales
+        assert any(r["stat"] == "mse" for r in debug_api.records())
+    finally:
+        debug_api.end_debug()
+    debug_api.initialize({"fq": {"enabled": True, "layers": {"layer_names": ["enc.fc"]},
+                                 "features": {"FakeQuant": {"tensors": ["activation"], "gemms": ["fprop"]}}}})
+    try:
+        with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+            z = lin(x)
+        assert (z - x @ lin.weight.t()).abs().max() < 0.1 * ref.abs().max()
+    finally:
+        debug_api.end_debug()

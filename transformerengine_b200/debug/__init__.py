@@ -230,6 +230,16 @@ class _FakeQuantizer(Quantizer):
         p.set_usage(rowwise=True, columnwise=False)
         return p.quantize_impl(tensor, dtype).dequantize().to(tensor.dtype)
 
+    def update_quantized(self, src, dst, *, noop_flag=None):
+        dst.copy_(self.quantize_impl(src))
+        return dst
+
+    def make_empty(self, shape, *, dtype=torch.float32, device=None, requires_grad=False):
+        return torch.empty(tuple(shape), dtype=dtype, device=device, requires_grad=requires_grad)
+
+    def copy(self):
+        return _FakeQuantizer(self.parent.copy())
+
 
 def wrap_quantizer(parent: Optional[Quantizer], layer_name: Optional[str], fwd: bool, idx: int):
     """Called by modules for every quantizer slot; returns the quantizer the module should use."""
@@ -246,6 +256,20 @@ def wrap_quantizer(parent: Optional[Quantizer], layer_name: Optional[str], fwd: 
         return None
     if isinstance(parent, DebugQuantizer):
         return parent
+    if "PerTensorScaling" in feats and _wants(feats["PerTensorScaling"], tname):
+        # replace the recipe's quantizer by FP8 per-tensor current scaling for the chosen tensors
+        # (reference: debug/features/per_tensor_scaling.py:61)
+        from ..tensor.float8 import Float8CurrentScalingQuantizer
+
+        fp8_dtype = getattr(parent, "dtype", None)
+        if fp8_dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+            fp8_dtype = torch.float8_e4m3fn if fwd else torch.float8_e5m2
+        swapped = Float8CurrentScalingQuantizer(fp8_dtype, rowwise=parent.rowwise_usage,
+                                                columnwise=parent.columnwise_usage)
+        swapped.internal = parent.internal
+        parent = swapped
+    if "FakeQuant" in feats and _wants(feats["FakeQuant"], tname):
+        parent = _FakeQuantizer(parent)
     return DebugQuantizer(parent, layer_name, tname, feats)
 
 

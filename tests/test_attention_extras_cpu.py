@@ -1,0 +1,55 @@
+"""Score-modifier attention and the latent-attention query projection (CPU path)."""
+import math
+
+import torch
+
+import transformerengine_b200 as te
+from transformerengine_b200.attention.fused_mla_q_uproj import FusedMLAQUpProjRopeQuant
+from transformerengine_b200.tensor import MXFP8Quantizer
+
+
+def test_score_mod_edits_scores_before_softmax():
+    torch.manual_seed(0)
+    b, s, h, d = 2, 16, 2, 8
+    attn = te.DotProductAttention(h, d, qkv_format="bshd", attn_mask_type="causal")
+    q, k, v = (torch.randn(b, s, h, d, requires_grad=True) for _ in range(3))
+    slopes = torch.tensor([0.5, 0.25]).reshape(1, h, 1, 1)
+    dist = (torch.arange(s)[None, :] - torch.arange(s)[:, None]).float().reshape(1, 1, s, s)
+
+    def mod(score, tensors):
+        return score + tensors["slopes"] * tensors["dist"]
+
+    out = attn(q, k, v, score_mod=mod, score_mod_tensors={"slopes": slopes, "dist": dist})
+    out.sum().backward()
+    qt, kt, vt = (t.detach().transpose(1, 2) for t in (q, k, v))
+    sc = qt @ kt.transpose(-1, -2) / math.sqrt(d) + slopes * dist
+    sc = sc.masked_fill(torch.triu(torch.ones(s, s, dtype=torch.bool), 1), float("-inf"))
+    ref = (sc.softmax(-1) @ vt).transpose(1, 2).reshape(b, s, h * d)
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    assert q.grad is not None and q.grad.abs().sum() > 0
+
+
+def test_fused_mla_query_projection_matches_composed_math():
+    torch.manual_seed(0)
+    s, b, k_dim, nh, d, d_rot = 32, 2, 64, 2, 64, 32
+    assert FusedMLAQUpProjRopeQuant.is_supported()
+    x = torch.randn(s * b, k_dim)
+    w = torch.randn(nh * d, k_dim) * 0.1
+    ang = torch.rand(s, d_rot // 2) * 6.28
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1), torch.cat([ang.sin(), ang.sin()], -1)
+    q, saved = FusedMLAQUpProjRopeQuant.run(x, w, cos, sin, s, b, head_dim=d)
+    assert saved is x and tuple(q.logical_shape) == (s, b, nh, d)
+    ref = (x @ w.t()).reshape(s, b, nh, d)
+    rot = ref[..., d - d_rot:]
+    r1, r2 = rot[..., :d_rot // 2], rot[..., d_rot // 2:]
+    c, sn = cos.reshape(s, 1, 1, d_rot), sin.reshape(s, 1, 1, d_rot)
+    ref = torch.cat([ref[..., :d - d_rot], rot * c + torch.cat([-r2, r1], -1) * sn], -1)
+    got = q.dequantize(dtype=torch.float32)
+    assert (got - ref).abs().max() < 0.08 * ref.abs().max()
+    assert q.get_usages() == {"rowwise": True, "columnwise": True}
+
+    # FP8 path: an MXFP8 primary weight keeps the projection in MXFP8 and returns the columnwise activation
+    wq = MXFP8Quantizer(torch.float8_e4m3fn)(w)
+    q2, saved2 = FusedMLAQUpProjRopeQuant.run(x, wq, cos, sin, s, b, head_dim=d)
+    assert saved2.get_usages() == {"rowwise": False, "columnwise": True}
+    assert (q2.dequantize(dtype=torch.float32) - ref).abs().max() < 0.15 * ref.abs().max()

@@ -22,6 +22,8 @@ from .attention.dot_product_attention import DotProductAttention
 from .attention.multi_head_attention import MultiheadAttention
 from .attention.rope import RotaryPositionEmbedding, apply_rotary_pos_emb
 from .attention.inference import InferenceParams, KVCacheManager, NonPagedKVCacheManager, PagedKVCacheManager
+from .attention.fused_mla_q_uproj import FusedMLAQUpProjRopeQuant
+from .attention import thd  # noqa: F401  packed-sequence helpers
 from .transformer import TransformerLayer
 from .modules.grouped_linear import GroupedLinear, Fp8Padding, Fp8Unpadding
 from .moe import (fused_topk_with_score_function, fused_compute_score_for_moe_aux_loss, fused_moe_aux_loss,

@@ -91,29 +91,37 @@ class DotProductAttention(torch.nn.Module):
                 attn_mask_type: Optional[str] = None, window_size: Optional[Tuple[int, int]] = None,
                 checkpoint_core_attention: bool = False, core_attention_bias_type: str = "no_bias",
                 core_attention_bias: Optional[torch.Tensor] = None, alibi_slopes: Optional[torch.Tensor] = None,
-                fast_zero_fill: bool = True, inference_params=None, pad_between_seqs: Optional[bool] = None):
+                fast_zero_fill: bool = True, inference_params=None, pad_between_seqs: Optional[bool] = None,
+                score_mod: Optional[Callable] = None, score_mod_bprop: Optional[Callable] = None,
+                score_mod_tensors: Optional[Dict[str, torch.Tensor]] = None,
+                score_mod_bprop_tensors: Optional[Dict[str, torch.Tensor]] = None):
         fmt = qkv_format or self.qkv_format
         mask_type = attn_mask_type or self.attn_mask_type
         window = window_size if window_size is not None else self.window_size
         if inference_params is not None:
             query_layer, key_layer, value_layer, fmt, mask_type, cu_seqlens_q, cu_seqlens_kv = \
                 inference_params.step(self.layer_number, query_layer, key_layer, value_layer, fmt, mask_type)
+        # score_mod(score, tensors) -> score edits the scaled scores; autograd differentiates it, so the
+        # backward callback of the reference's graph-based interface is accepted and not needed
+        score = (score_mod, score_mod_tensors)
+        assert score_mod is None or (fmt != "thd" and inference_params is None), \
+            "score_mod is supported for sbhd / bshd training inputs"
         thd_extra = (cu_seqlens_q_padded, cu_seqlens_kv_padded, max_seqlen_q, max_seqlen_kv) \
             if inference_params is None else (None, None, None, None)
         if checkpoint_core_attention:
             def run(q, k, v):
                 return self._core(q, k, v, fmt, mask_type, window, attention_mask, cu_seqlens_q, cu_seqlens_kv,
-                                  core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra)
+                                  core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score)
             return D.checkpoint(run, query_layer, key_layer, value_layer,
                                 get_rng_state_tracker=self.get_rng_state_tracker)
         out = self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
-                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra)
+                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score)
         if inference_params is not None:
             out = inference_params.unpack_output(out)
         return out
 
     def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes,
-              thd_extra=(None, None, None, None)):
+              thd_extra=(None, None, None, None), score=(None, None)):
         if fmt == "thd":
             return self._thd(q, k, v, mask_type, window, cu_q, cu_kv, *thd_extra)
         # -> [b, h, s, d] views
@@ -158,7 +166,7 @@ class DotProductAttention(torch.nn.Module):
                 o = ops.attention(qb, kb, vb, scale=self.softmax_scale, causal=causal, window=window, attn_mask=mask,
                                   bias=the_bias, dropout_p=dropout, softmax_type=self.softmax_type,
                                   sink=self.softmax_offset, bottom_right=bottom_right or sq == sk,
-                                  out_format=fmt)
+                                  out_format=fmt, score_mod=score[0], score_mod_tensors=score[1])
         if fmt == "sbhd":
             return o.permute(2, 0, 1, 3).reshape(sq, b, hq * o.shape[-1])
         return o.permute(0, 2, 1, 3).reshape(b, sq, hq * o.shape[-1])

@@ -37,8 +37,10 @@ def _build_mask(sq, sk, device, causal, window, bottom_right=True):
 
 
 def attention_ref(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None, bias=None, dropout_p=0.0,
-                  softmax_type="vanilla", sink=None, bottom_right=True, generator=None, return_lse=False):
-    """fp32 attention on ``[b, h, s, d]`` tensors; k/v may have fewer heads (GQA)."""
+                  softmax_type="vanilla", sink=None, bottom_right=True, generator=None, return_lse=False,
+                  score_mod=None, score_mod_tensors=None):
+    """fp32 attention on ``[b, h, s, d]`` tensors; k/v may have fewer heads (GQA).
+    ``score_mod(score, tensors) -> score`` edits the scaled scores ``[b, h, sq, sk]`` before masking."""
     b, hq, sq, d = q.shape
     hk, sk = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
@@ -50,6 +52,8 @@ def attention_ref(q, k, v, *, scale=None, causal=False, window=None, attn_mask=N
     s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
     if bias is not None:
         s = s + bias.float()
+    if score_mod is not None:
+        s = score_mod(s, score_mod_tensors or {})
     m = _build_mask(sq, sk, q.device, causal, window, bottom_right)
     if m is not None:
         s = s.masked_fill(m, float("-inf"))
@@ -78,7 +82,8 @@ _USE_OWN_FLASH = os.environ.get("TEB200_ATTN", "own") != "library"
 
 
 def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None, bias=None, dropout_p=0.0,
-              softmax_type="vanilla", sink=None, bottom_right=True, out_format="bhsd"):
+              softmax_type="vanilla", sink=None, bottom_right=True, out_format="bhsd", score_mod=None,
+              score_mod_tensors=None):
     """Differentiable attention on ``[b, h, s, d]``; ``out_format`` names the memory layout of the
     returned ``[b, h, s, d]`` view ("bhsd", "sbhd" or "bshd") when the fused kernel runs.
 
@@ -87,6 +92,7 @@ def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None,
     else runs the reference math, which autograd differentiates.
     """
     plain = attn_mask is None and bias is None and dropout_p == 0.0 and softmax_type == "vanilla" and \
+        score_mod is None and \
         (window is None or (window[0] < 0 and window[1] <= 0))
     if _ext.use_cuda(q) and plain and q.dtype in (torch.bfloat16, torch.float16):
         from . import flash
@@ -97,7 +103,8 @@ def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None,
             return torch.nn.functional.scaled_dot_product_attention(
                 q, k, v, is_causal=causal, scale=scale, enable_gqa=q.shape[1] != k.shape[1])
     return attention_ref(q, k, v, scale=scale, causal=causal, window=window, attn_mask=attn_mask, bias=bias,
-                         dropout_p=dropout_p, softmax_type=softmax_type, sink=sink, bottom_right=bottom_right)
+                         dropout_p=dropout_p, softmax_type=softmax_type, sink=sink, bottom_right=bottom_right,
+                         score_mod=score_mod, score_mod_tensors=score_mod_tensors)
 
 
 def merge_attention_states(o1, lse1, o2, lse2) -> Tuple[torch.Tensor, torch.Tensor]:

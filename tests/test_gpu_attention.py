@@ -179,3 +179,39 @@ def test_dot_product_attention_thd_uses_varlen_kernel():
         r = attention_ref(bh(q), bh(k), bh(v), causal=True).squeeze(0).permute(1, 0, 2).reshape(n, -1)
         _close(o[pos:pos + n], r, 2e-2)
         pos += n
+
+
+WINDOW_CASES = [
+    # b, hq, hk, sq, sk, causal, bottom_right, (left, right)
+    (1, 4, 2, 1024, 1024, True, True, (256, 0)),
+    (2, 2, 2, 512, 512, True, True, (100, 0)),
+    (1, 4, 1, 700, 700, False, True, (64, 32)),
+    (1, 2, 2, 300, 556, True, True, (128, 0)),
+    (1, 2, 1, 512, 512, False, True, (-1, 17)),
+    (1, 4, 1, 8192, 8192, True, True, (1024, 0)),
+]
+
+
+@pytest.mark.parametrize("case", WINDOW_CASES)
+def test_flash_sliding_window_matches_reference(case):
+    import transformerengine_b200 as te
+    from transformerengine_b200.ops import flash
+    from transformerengine_b200.ops.attention import attention_ref
+
+    b, hq, hk, sq, sk, causal, br, window = case
+    torch.manual_seed(0)
+    dtype = torch.bfloat16
+    q = torch.randn(b, hq, sq, 128, device="cuda", dtype=dtype, requires_grad=True)
+    k = torch.randn(b, hk, sk, 128, device="cuda", dtype=dtype, requires_grad=True)
+    v = torch.randn(b, hk, sk, 128, device="cuda", dtype=dtype, requires_grad=True)
+    do = torch.randn(b, hq, sq, 128, device="cuda", dtype=dtype)
+    o = flash.flash_attention(q, k, v, None, causal, br, window=window)
+    o.backward(do)
+    te.ops.check_status()
+    qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ro = attention_ref(qf, kf, vf, causal=causal, window=window, bottom_right=br)
+    ro.backward(do.float())
+    _close(o, ro, 2e-2)
+    _close(q.grad, qf.grad, 3e-2)
+    _close(k.grad, kf.grad, 3e-2)
+    _close(v.grad, vf.grad, 3e-2)

@@ -52,6 +52,9 @@ struct FlashParams {
   int bottom_right;
   int gsplit;       // dK/dV pass: CTAs per group of query heads (partials o_sg elements apart)
   long long o_sg;
+  // sliding window: with `causal` set, key j is visible to query i when j <= i + causal_off (which
+  // includes the right extent win_right) and, when has_lo, j >= i + lo_off
+  int win_left, win_right, has_lo, lo_off;
   int pair_balance;  // query-stationary kernels: a CTA takes 128-row tiles i and last - i (equal causal work)
 };
 
@@ -71,7 +74,8 @@ __device__ __forceinline__ SeqView localize(FlashParams& p, int b) {
     sk = sk < 0 ? 0 : (sk > p.sk ? p.sk : sk);
     p.sq = sq;
     p.sk = sk;
-    p.causal_off = p.bottom_right ? sk - sq : 0;
+    p.causal_off = (p.bottom_right ? sk - sq : 0) + p.win_right;
+    p.lo_off = (p.bottom_right ? sk - sq : 0) - p.win_left;
     v.q_off = p.off_q[b];
     v.k_off = p.off_k[b];
     v.bt = 0;
@@ -142,6 +146,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// Fill the mask fields of the launch parameters from the caller's arguments.
+inline void set_mask_params(FlashParams& p, const FlashArgs& a) {
+  const int base = a.bottom_right ? a.sk - a.sq : 0;
+  p.bottom_right = a.bottom_right ? 1 : 0;
+  p.win_right = a.causal ? 0 : (a.window_right >= 0 ? a.window_right : 0);
+  p.causal = (a.causal || a.window_right >= 0) ? 1 : 0;
+  p.causal_off = base + p.win_right;
+  p.has_lo = a.window_left >= 0 ? 1 : 0;
+  p.win_left = a.window_left >= 0 ? a.window_left : 0;
+  p.lo_off = base - p.win_left;
 }
 
 // 4-D tensor map over a [b, h, s, d] view; strides in elements, box = [rows x 64 elements]

@@ -28,7 +28,7 @@ struct KvCfg {
 };
 static_assert(KvCfg::kStageBytes % 1024 == 0, "ring stages must keep the swizzle alignment");
 
-template <bool BF>
+template <bool BF, bool WIN>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -58,7 +58,11 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   const int G = p.hq / p.hk;
   const int Gl = G / p.gsplit;  // query heads of this CTA
   const int kv0 = kb * 128;
-  const int nq = kv0 < p.sk ? (p.sq + 63) / 64 : 0;  // a key block past the sequence's end has no work
+  int nq = kv0 < p.sk ? (p.sq + 63) / 64 : 0;  // a key block past the sequence's end has no work
+  if (WIN && nq > 0) {  // sliding window: the last query that still sees the block's last key
+    const int q_last = min(kv0 + 127, p.sk - 1) - p.lo_off;
+    nq = q_last < 0 ? 0 : min(nq, q_last / 64 + 1);
+  }
   int i_start = 0;
   if (p.causal) {
     const int first_q = kv0 - p.causal_off;  // first query row that sees key kv0
@@ -196,9 +200,11 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       __syncwarp();
       tc_fence_after();
       const float* vec = reinterpret_cast<const float*>(smem + C::kOffRing + st * C::kStageBytes + 2 * C::kQBlk);
-      const bool need_mask = (kv0 + 128 > p.sk) || (qr + 64 > p.sq) || (p.causal && kv0 + 127 > qr + p.causal_off);
+      const bool need_mask = (kv0 + 128 > p.sk) || (qr + 64 > p.sq) || (p.causal && kv0 + 127 > qr + p.causal_off) ||
+                             (WIN && qr + 63 > kv0 - p.lo_off);
       // key kv_row is visible to query q iff q >= q_min (and the key exists)
       const int q_min = kv_row < p.sk ? (p.causal ? kv_row - p.causal_off : 0) : 0x7fffffff;
+      const int q_max = WIN ? kv_row - p.lo_off : 0x7fffffff;
       uint32_t wp[16], wd[16];
       {
         uint32_t s[32], dp[32];
@@ -218,7 +224,7 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
             float y = x * (__uint_as_float(dp[c + e]) - dl[e]);
             if (need_mask) {
               const int q = qr + half * 32 + c + e;
-              const bool vis = q >= q_min && q < p.sq;
+              const bool vis = q >= q_min && q <= q_max && q < p.sq;
               x = vis ? x : 0.f;
               y = vis ? y : 0.f;
             }
@@ -352,8 +358,7 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
   if (a.dk_sb != a.dv_sb || a.dk_sh != a.dv_sh || a.dk_ss != a.dv_ss) return cudaErrorInvalidValue;
   FlashParams p = {};
   p.b = a.b; p.hq = a.hq; p.hk = a.hk; p.sq = a.sq; p.sk = a.sk;
-  p.causal = a.causal ? 1 : 0;
-  p.causal_off = a.bottom_right ? a.sk - a.sq : 0;
+  set_mask_params(p, a);
   p.scale = a.scale;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.is_bf16 = bf ? 1 : 0;
@@ -362,21 +367,28 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
       p.o_ss % 8)
     return cudaErrorInvalidValue;
   p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status;
-  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.off_q = a.off_q; p.off_k = a.off_k; p.bottom_right = a.bottom_right ? 1 : 0;
+  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.off_q = a.off_q; p.off_k = a.off_k;
   p.gsplit = a.gsplit < 1 ? 1 : a.gsplit;
   p.o_sg = a.dk_sg;
   if ((a.hq / a.hk) % p.gsplit != 0 || p.o_sg % 8 != 0) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_kvouter_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(flash_kvouter_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-    if (e != cudaSuccess) return e;
+    const void* fns[4] = {reinterpret_cast<const void*>(flash_kvouter_kernel<true, false>),
+                          reinterpret_cast<const void*>(flash_kvouter_kernel<false, false>),
+                          reinterpret_cast<const void*>(flash_kvouter_kernel<true, true>),
+                          reinterpret_cast<const void*>(flash_kvouter_kernel<false, true>)};
+    for (const void* fn : fns) {
+      cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      if (e != cudaSuccess) return e;
+    }
     attr_set = true;
   }
   dim3 grid((a.sk + 127) / 128, a.hk * p.gsplit, a.b);
-  if (bf) flash_kvouter_kernel<true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
-  else flash_kvouter_kernel<false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  const bool win = p.has_lo != 0;
+  if (bf && !win) flash_kvouter_kernel<true, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else if (!win) flash_kvouter_kernel<false, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else if (bf) flash_kvouter_kernel<true, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else flash_kvouter_kernel<false, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 

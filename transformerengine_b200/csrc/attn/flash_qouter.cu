@@ -63,7 +63,8 @@ __device__ __forceinline__ int kv_blocks_of_tile(const FlashParams& p, int row0,
   return kv_end <= 0 ? 0 : (kv_end + bk - 1) / bk;
 }
 
-template <int MODE, bool BF>
+// WIN: sliding-window lower bound compiled in (kept out of the plain causal kernels)
+template <int MODE, bool BF, bool WIN>
 __global__ void __launch_bounds__(kThreads, 1)
 flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
@@ -109,6 +110,19 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   constexpr int BK = C::kBlockKv;
   n[0] = kv_blocks_of_tile(p, qrow[0], BK);
   n[1] = kv_blocks_of_tile(p, qrow[1], BK);
+  // sliding window: both tiles start at the first key block that the earlier tile can see
+  int jbase = 0;
+  if (WIN) {
+    int lo = 0x7fffffff;
+    for (int t = 0; t < 2; ++t)
+      if (n[t] > 0) {
+        const int first = qrow[t] + p.lo_off;
+        lo = min(lo, first > 0 ? first / BK : 0);
+      }
+    jbase = lo == 0x7fffffff ? 0 : lo;
+    n[0] = n[0] > jbase ? n[0] - jbase : 0;
+    n[1] = n[1] > jbase ? n[1] - jbase : 0;
+  }
   const int nmax = n[0] > n[1] ? n[0] : n[1];
 
   if (threadIdx.x == 0) {
@@ -157,11 +171,11 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!mbar_wait(&k_empty[st], par)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         mbar_expect_tx(&k_full[st], C::kKvBytes);
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(smem + C::kOffK + st * C::kKvBytes + pn * C::kPanel, &tmap_k, &k_full[st], pn * 64, sv.k_off + j * BK, hk, sv.bt);
+          tma_load_4d(smem + C::kOffK + st * C::kKvBytes + pn * C::kPanel, &tmap_k, &k_full[st], pn * 64, sv.k_off + (jbase + j) * BK, hk, sv.bt);
         if (!mbar_wait(&v_empty[st], par)) { atomicCAS(p.status, 0, kFlashTimeoutProducer); break; }
         mbar_expect_tx(&v_full[st], C::kKvBytes);
         for (int pn = 0; pn < 2; ++pn)
-          tma_load_4d(smem + C::kOffV + st * C::kKvBytes + pn * C::kPanel, &tmap_v, &v_full[st], pn * 64, sv.k_off + j * BK, hk, sv.bt);
+          tma_load_4d(smem + C::kOffV + st * C::kKvBytes + pn * C::kPanel, &tmap_v, &v_full[st], pn * 64, sv.k_off + (jbase + j) * BK, hk, sv.bt);
       }
     }
   } else if (warp == 1) {
@@ -257,7 +271,7 @@ flash_qouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
   } else {
     const int t = (warp - 2) >> 3;
-    qouter_softmax_role<MODE, BF, C>(p, smem, s_full, p_ready, pv_done, xchg, tmem_base, warp, lane, qrow[t] - t * 128, h, b, n[t], t);
+    qouter_softmax_role<MODE, BF, C, WIN>(p, smem, s_full, p_ready, pv_done, xchg, tmem_base, warp, lane, qrow[t] - t * 128, h, b, n[t], t, jbase);
   }
 
   tc_fence_before();
@@ -314,8 +328,7 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
   if (!ok) return cudaErrorInvalidValue;
   FlashParams p = {};
   p.b = a.b; p.hq = a.hq; p.hk = a.hk; p.sq = a.sq; p.sk = a.sk;
-  p.causal = a.causal ? 1 : 0;
-  p.causal_off = a.bottom_right ? a.sk - a.sq : 0;
+  set_mask_params(p, a);
   p.scale = a.scale;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.is_bf16 = bf ? 1 : 0;
@@ -323,18 +336,20 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
   else { p.out = a.dq; p.o_sb = a.dq_sb; p.o_sh = a.dq_sh; p.o_ss = a.dq_ss; }
   if ((reinterpret_cast<uintptr_t>(p.out) & 15) || p.o_sb % 8 || p.o_sh % 8 || p.o_ss % 8) return cudaErrorInvalidValue;
   p.lse = a.lse; p.delta = a.delta; p.s_pad = a.s_pad; p.status = a.status; p.timeline = a.timeline;
-  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.off_q = a.off_q; p.off_k = a.off_k; p.bottom_right = a.bottom_right ? 1 : 0;
+  p.cu_q = a.cu_q; p.cu_k = a.cu_k; p.off_q = a.off_q; p.off_k = a.off_k;
   p.gsplit = 1; p.o_sg = 0;
   if (a.sq <= 0 || a.b <= 0) return cudaSuccess;
   if (a.s_pad < a.sq) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(flash_qouter_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         C::kSmemBytes);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(flash_qouter_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               C::kSmemBytes);
-    if (e != cudaSuccess) return e;
+    const void* fns[4] = {reinterpret_cast<const void*>(flash_qouter_kernel<MODE, true, false>),
+                          reinterpret_cast<const void*>(flash_qouter_kernel<MODE, false, false>),
+                          reinterpret_cast<const void*>(flash_qouter_kernel<MODE, true, true>),
+                          reinterpret_cast<const void*>(flash_qouter_kernel<MODE, false, true>)};
+    for (const void* fn : fns) {
+      cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+      if (e != cudaSuccess) return e;
+    }
     attr_set = true;
   }
   dim3 grid(((a.sq + 255) / 256) * a.hq, a.b);
@@ -342,9 +357,12 @@ static cudaError_t launch_qouter(const FlashArgs& a, cudaStream_t stream) {
     const char* e = std::getenv("TEB200_ATTN_PAIR");
     return e == nullptr || e[0] != '0';
   }();
-  p.pair_balance = allow_pair && a.causal && static_cast<long long>(grid.x) * grid.y <= 148 ? 1 : 0;
-  if (bf) flash_qouter_kernel<MODE, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
-  else flash_qouter_kernel<MODE, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  p.pair_balance = allow_pair && a.causal && a.window_left < 0 && static_cast<long long>(grid.x) * grid.y <= 148 ? 1 : 0;
+  const bool win = p.has_lo != 0;
+  if (bf && !win) flash_qouter_kernel<MODE, true, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else if (!win) flash_qouter_kernel<MODE, false, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else if (bf) flash_qouter_kernel<MODE, true, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
+  else flash_qouter_kernel<MODE, false, true><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   return cudaGetLastError();
 }
 

@@ -40,11 +40,11 @@ __device__ __forceinline__ bool xchg_pair(unsigned long long* slots, int mine, i
   return true;
 }
 
-template <int MODE, bool BF, class C>
+template <int MODE, bool BF, class C, bool WIN>
 __device__ __forceinline__ void qouter_softmax_role(const FlashParams& p, uint8_t* smem, uint64_t* s_full,
                                                     uint64_t* p_ready, uint64_t* pv_done, unsigned long long* xchg,
                                                     uint32_t tmem_base, int warp, int lane, int q0, int h, int b,
-                                                    int nt, int t) {
+                                                    int nt, int t, int jbase) {
   constexpr int kModeFwd = 0;
   const int wi = (warp - 2) & 7;
   const int half = wi >> 2;                // which 32 score columns / which 64 output columns
@@ -72,9 +72,12 @@ __device__ __forceinline__ void qouter_softmax_role(const FlashParams& p, uint8_
     __syncwarp();
     tc_fence_after();
     if (stamp) p.timeline[j * 16 + 1] = clock64();
-    const int kv0 = j * BK + half * HC;   // first key of this thread's columns
-    const bool need_mask = (j * BK + BK > p.sk) || (p.causal && j * BK + BK - 1 > q0 + t * 128 + p.causal_off);
+    const int kb0 = (jbase + j) * BK;     // first key of the block
+    const int kv0 = kb0 + half * HC;      // first key of this thread's columns
+    const bool need_mask = (kb0 + BK > p.sk) || (p.causal && kb0 + BK - 1 > q0 + t * 128 + p.causal_off) ||
+                           (WIN && kb0 < q0 + t * 128 + 127 + p.lo_off);
     const int lim = p.causal ? min(p.sk - 1, q_row + p.causal_off) : p.sk - 1;  // last visible key
+    const int lo = WIN ? q_row + p.lo_off : 0;                                 // first visible key
     if (MODE == kModeFwd) {
       // pass 1: block maximum of this thread's columns, 32 at a time
       float mx4[4] = {NEG_INF, NEG_INF, NEG_INF, NEG_INF};
@@ -86,7 +89,7 @@ __device__ __forceinline__ void qouter_softmax_role(const FlashParams& p, uint8_
         if (need_mask) {
 #pragma unroll
           for (int c = 0; c < 32; ++c)
-            if (kv0 + c0 + c > lim) s[c] = __float_as_uint(NEG_INF);
+            if (kv0 + c0 + c > lim || kv0 + c0 + c < lo) s[c] = __float_as_uint(NEG_INF);
         }
 #pragma unroll
         for (int c = 0; c < 32; c += 4) {
@@ -123,7 +126,7 @@ __device__ __forceinline__ void qouter_softmax_role(const FlashParams& p, uint8_
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float x = fmaf(__uint_as_float(s[c + e]), p.scale_log2, -m_eff);
-            if (need_mask && kv0 + c0 + c + e > lim) x = NEG_INF;
+            if (need_mask && (kv0 + c0 + c + e > lim || kv0 + c0 + c + e < lo)) x = NEG_INF;
             e4[e] = fast_exp2(x);
             sum4[e] += e4[e];
           }
@@ -163,8 +166,8 @@ __device__ __forceinline__ void qouter_softmax_role(const FlashParams& p, uint8_
         float p0 = fast_exp2(fmaf(__uint_as_float(s[c]), p.scale_log2, -lse2));
         float p1 = fast_exp2(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -lse2));
         if (need_mask) {
-          if (kv0 + c > lim) p0 = 0.f;
-          if (kv0 + c + 1 > lim) p1 = 0.f;
+          if (kv0 + c > lim || kv0 + c < lo) p0 = 0.f;
+          if (kv0 + c + 1 > lim || kv0 + c + 1 < lo) p1 = 0.f;
         }
         const float d0 = p0 * (__uint_as_float(dp[c]) - delta);
         const float d1 = p1 * (__uint_as_float(dp[c + 1]) - delta);

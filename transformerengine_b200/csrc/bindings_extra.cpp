@@ -122,9 +122,10 @@ teb200::FlashArgs flash_args(const at::Tensor& q, const at::Tensor& k, const at:
 
 void flash_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
                const at::Tensor& lse, double scale, bool causal, bool bottom_right, const at::Tensor& status,
-               const OptT& timeline) {
+               const OptT& timeline, int64_t window_left, int64_t window_right) {
   c10::cuda::CUDAGuard guard(q.device());
   teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  a.window_left = static_cast<int>(window_left); a.window_right = static_cast<int>(window_right);
   if (timeline.has_value() && timeline->defined()) {
     TORCH_CHECK(timeline->scalar_type() == at::kLong && timeline->numel() >= 1024, "timeline must be int64 [64, 16]");
     a.timeline = reinterpret_cast<long long*>(timeline->data_ptr());
@@ -164,9 +165,10 @@ void run_dkdv(teb200::FlashArgs& a, const at::Tensor& k, const at::Tensor& dk, c
 void flash_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                const at::Tensor& out, const at::Tensor& lse, const at::Tensor& delta, const at::Tensor& dq,
                const at::Tensor& dk, const at::Tensor& dv, double scale, bool causal, bool bottom_right,
-               const at::Tensor& status) {
+               const at::Tensor& status, int64_t window_left, int64_t window_right) {
   c10::cuda::CUDAGuard guard(q.device());
   teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  a.window_left = static_cast<int>(window_left); a.window_right = static_cast<int>(window_right);
   a.dout = dout.data_ptr();
   a.delta = delta.data_ptr<float>();
   a.dq = dq.data_ptr(); a.dk = dk.data_ptr(); a.dv = dv.data_ptr();
@@ -736,8 +738,11 @@ void register_extra(py::module_& m) {
   m.def("comm_gemm", &comm_gemm);
   m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
-        py::arg("timeline") = py::none());
-  m.def("flash_bwd", &flash_bwd);
+        py::arg("timeline") = py::none(), py::arg("window_left") = -1, py::arg("window_right") = -1);
+  m.def("flash_bwd", &flash_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+        py::arg("lse"), py::arg("delta"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("scale"),
+        py::arg("causal"), py::arg("bottom_right"), py::arg("status"), py::arg("window_left") = -1,
+        py::arg("window_right") = -1);
   m.def("thd_get_partitioned_indices", &thd_get_partitioned_indices);
   m.def("thd_read_half_tensor", &thd_read_half_tensor);
   m.def("thd_second_half_lse_correction", &thd_second_half_lse_correction);

@@ -92,6 +92,9 @@ struct FlashArgs {
   // when key heads x key blocks are fewer than the SMs (tensor parallel shards).
   int gsplit = 1;
   long long dk_sg = 0;
+  // Sliding window: query i (diagonal-aligned like the causal mask) sees keys in
+  // [i - window_left, i + window_right]; -1 = unbounded.  causal forces window_right = 0.
+  int window_left = -1, window_right = -1;
 };
 cudaError_t flash_fwd(const FlashArgs& args, cudaStream_t stream);
 cudaError_t flash_delta(const FlashArgs& args, cudaStream_t stream);     // delta = rowsum(dO * O)

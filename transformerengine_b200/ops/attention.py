@@ -91,15 +91,16 @@ def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None,
     (16-bit, no bias / arbitrary mask / dropout, head dim 64 or 128); everything
     else runs the reference math, which autograd differentiates.
     """
+    no_window = window is None or (window[0] < 0 and (window[1] < 0 or (causal and window[1] == 0)))
     plain = attn_mask is None and bias is None and dropout_p == 0.0 and softmax_type == "vanilla" and \
-        score_mod is None and \
-        (window is None or (window[0] < 0 and window[1] <= 0))
+        score_mod is None
     if _ext.use_cuda(q) and plain and q.dtype in (torch.bfloat16, torch.float16):
         from . import flash
 
         if _USE_OWN_FLASH and flash.supported(q, k, v, causal):
-            return flash.flash_attention(q, k, v, scale, causal, bottom_right, out_format)
-        if _USE_LIBRARY_SDPA and (not causal or q.shape[2] == k.shape[2] or not bottom_right):
+            return flash.flash_attention(q, k, v, scale, causal, bottom_right, out_format,
+                                         None if no_window else window)
+        if _USE_LIBRARY_SDPA and no_window and (not causal or q.shape[2] == k.shape[2] or not bottom_right):
             return torch.nn.functional.scaled_dot_product_attention(
                 q, k, v, is_causal=causal, scale=scale, enable_gqa=q.shape[1] != k.shape[1])
     return attention_ref(q, k, v, scale=scale, causal=causal, window=window, attn_mask=attn_mask, bias=bias,

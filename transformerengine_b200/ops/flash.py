@@ -43,7 +43,7 @@ def _empty_out(q: torch.Tensor, out_format: str) -> torch.Tensor:
 
 class _FlashFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, bottom_right, out_format):  # type: ignore[override]
+    def forward(ctx, q, k, v, scale, causal, bottom_right, out_format, window):  # type: ignore[override]
         C_ = _ext.get()
         q, k, v = _prep(q), _prep(k), _prep(v)
         b, h, sq, d = q.shape
@@ -51,28 +51,34 @@ class _FlashFunc(torch.autograd.Function):
         s_pad = (sq + 127) // 128 * 128  # the backward reads lse / delta in blocks of 128 rows
         lse = torch.empty(b, h, s_pad, dtype=torch.float32, device=q.device)
         sc = float(scale) if scale is not None else d ** -0.5
-        C_.flash_fwd(q, k, v, out, lse, sc, bool(causal), bool(bottom_right), C_.status(q.device.index))
+        wl, wr = (-1, -1) if window is None else (int(window[0]), int(window[1]))
+        C_.flash_fwd(q, k, v, out, lse, sc, bool(causal), bool(bottom_right), C_.status(q.device.index),
+                     window_left=wl, window_right=wr)
         ctx.save_for_backward(q, k, v, out, lse)
-        ctx.cfg = (sc, bool(causal), bool(bottom_right))
+        ctx.cfg = (sc, bool(causal), bool(bottom_right), wl, wr)
         return out
 
     @staticmethod
     def backward(ctx, dout):  # type: ignore[override]
         C_ = _ext.get()
         q, k, v, out, lse = ctx.saved_tensors
-        sc, causal, bottom_right = ctx.cfg
+        sc, causal, bottom_right, wl, wr = ctx.cfg
         dout = _prep(dout)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
         if dk.stride() != dv.stride():
             dv = torch.empty_strided(dk.shape, dk.stride(), dtype=dk.dtype, device=dk.device)
         delta = torch.empty_like(lse)
         C_.flash_bwd(dout, q, k, v, out, lse, delta, dq, dk, dv, sc, causal, bottom_right,
-                     C_.status(q.device.index))
-        return dq, dk, dv, None, None, None, None
+                     C_.status(q.device.index), window_left=wl, window_right=wr)
+        return dq, dk, dv, None, None, None, None, None
 
 
-def flash_attention(q, k, v, scale, causal, bottom_right=True, out_format: str = "bhsd"):
-    return _FlashFunc.apply(q, k, v, scale, causal, bottom_right, out_format)
+def flash_attention(q, k, v, scale, causal, bottom_right=True, out_format: str = "bhsd", window=None):
+    """``window = (left, right)``: query i sees keys [i - left, i + right] around the (bottom-right or
+    top-left aligned) diagonal, -1 = unbounded; ``causal`` forces right = 0."""
+    if window is not None and window[0] < 0 and window[1] < 0:
+        window = None
+    return _FlashFunc.apply(q, k, v, scale, causal, bottom_right, out_format, window)
 
 
 def flash_forward_lse(q, k, v, scale, causal, bottom_right=True):

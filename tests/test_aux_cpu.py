@@ -136,3 +136,22 @@ def test_debug_per_tensor_scaling_and_fake_quant():
         assert (z - x @ lin.weight.t()).abs().max() < 0.1 * ref.abs().max()
     finally:
         debug_api.end_debug()
+
+
+def test_torch_compile_wraps_modules_without_changing_results():
+    """``torch.compile`` may wrap library modules (quantized autocast included); the kernels stay
+    opaque calls and the results equal eager execution."""
+    torch.manual_seed(0)
+    lin = te.Linear(64, 64, params_dtype=torch.float32, device="cpu")
+    x = torch.randn(32, 64)
+
+    def fn(inp):
+        with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+            return lin(inp)
+
+    eager = fn(x)
+    compiled = torch.compile(fn, backend="aot_eager")(x)
+    torch.testing.assert_close(compiled, eager, rtol=0, atol=0)
+    xg = x.clone().requires_grad_()
+    torch.compile(fn, backend="aot_eager")(xg).sum().backward()
+    assert xg.grad is not None and lin.weight.grad is not None

@@ -47,9 +47,10 @@ flash_kvouter_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int kb = blockIdx.x;
-  const int hk = static_cast<int>(blockIdx.y) / p_launch.gsplit;
-  const int gs = static_cast<int>(blockIdx.y) % p_launch.gsplit;  // which part of the head group
+  // heads vary fastest, so CTAs start in order of decreasing causal work over ALL heads
+  const int kb = blockIdx.y;
+  const int hk = static_cast<int>(blockIdx.x) / p_launch.gsplit;
+  const int gs = static_cast<int>(blockIdx.x) % p_launch.gsplit;  // which part of the head group
   const int b = blockIdx.z;
   FlashParams p = p_launch;
   const SeqView sv = localize(p, b);
@@ -383,7 +384,7 @@ cudaError_t flash_bwd_dkdv(const FlashArgs& a, cudaStream_t stream) {
     }
     attr_set = true;
   }
-  dim3 grid((a.sk + 127) / 128, a.hk * p.gsplit, a.b);
+  dim3 grid(a.hk * p.gsplit, (a.sk + 127) / 128, a.b);
   const bool win = p.has_lo != 0;
   if (bf && !win) flash_kvouter_kernel<true, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);
   else if (!win) flash_kvouter_kernel<false, false><<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, p);

@@ -7,6 +7,7 @@ from typing import Callable, Dict, Optional, Tuple, Union
 
 import torch
 
+from .. import distributed_weight as DW
 from ..parallel import distributed as D
 from ..quantization import FP8GlobalStateManager
 from ..tensor.base import QuantizedTensorStorage, prepare_for_saving, restore_from_saved
@@ -17,7 +18,8 @@ from .base import TransformerEngineBaseModule, WeightGradStore, get_default_init
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, inp, weight, bias, module, cfg: F.LinearConfig, is_first_microbatch, fp8_output, weight_q):  # type: ignore[override]
-        in_features = weight.shape[-1]
+        dist_w = DW.is_distributed_weight(weight)   # the parameter is a shard; weight_q holds the full matrix
+        in_features = (weight_q.size(-1) if F._is_q(weight_q) else weight_q.shape[-1]) if dist_w else weight.shape[-1]
         lead = inp.shape[:-1]
         x2d = inp.reshape(-1, in_features)
         fp8 = module.fp8
@@ -45,7 +47,8 @@ class _Linear(torch.autograd.Function):
                 save_x.update_usage(rowwise_usage=False) if save_x.get_usages()["columnwise"] else None
             keep_x = save_x if need_wgrad else None
             # the quantized weight is a cached object shared across calls: keep a reference, do not strip it
-            ctx.wq = weight_q if F._is_q(weight_q) else None
+            ctx.wq = weight_q if (F._is_q(weight_q) and not dist_w) else None
+            ctx.dist_w = dist_w
             flat, objs = prepare_for_saving(keep_x)
             ctx.save_for_backward(*flat, weight, bias)
             ctx.objs = objs
@@ -75,6 +78,10 @@ class _Linear(torch.autograd.Function):
         wq = ctx.wq
         module, cfg = ctx.module, ctx.cfg
         w_use = wq if wq is not None else weight
+        w_full = None
+        if ctx.dist_w:  # assemble the full weight again instead of keeping it alive since the forward
+            w_full = DW.materialize_weight_for_backward(weight)[0].detach()
+            w_use = module.quantize_full_weight(w_full, cfg.activation_dtype)
         dy2d = grad_output.reshape(-1, grad_output.shape[-1])
         if dy2d.dtype != cfg.activation_dtype:
             dy2d = dy2d.to(cfg.activation_dtype)
@@ -98,7 +105,11 @@ class _Linear(torch.autograd.Function):
             if ctx.gathered_in_fwd:
                 in_q = module.get_quantizer(True, 0) if ctx.fp8 else None
                 xw = F.gather_input(keep_x, cfg, in_q, False, True)
-            dw = F.linear_wgrad(dyq, xw, weight, cfg)
+            if ctx.dist_w:
+                full_grad = F.linear_wgrad(dyq, xw, w_full, cfg)
+                dw = DW.finalize_weight_grads(weight, [full_grad])[0]
+            else:
+                dw = F.linear_wgrad(dyq, xw, weight, cfg)
         if h is not None:
             h.wait()
         if dx is not None:
@@ -253,6 +264,15 @@ class Linear(TransformerEngineBaseModule):
             b = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0)
         return w, b
 
+    def quantize_full_weight(self, full: torch.Tensor, dtype):
+        """Quantize (or cast) a freshly assembled full weight of a distributed parameter; not cached."""
+        q = self.get_quantizer(True, 1)
+        if q is None:
+            return full if full.dtype == dtype else full.to(dtype)
+        q.set_usage(rowwise=True, columnwise=True)
+        q.internal = True
+        return q(full)
+
     def forward(self, inp: torch.Tensor, is_first_microbatch: Optional[bool] = None, fp8_output: bool = False,
                 fp8_grad: bool = False):
         self.prepare_forward(num_gemms=1)
@@ -263,9 +283,13 @@ class Linear(TransformerEngineBaseModule):
         if inp.is_floating_point() and not isinstance(inp, QuantizedTensorStorage) and not torch.is_autocast_enabled():
             self.cfg.activation_dtype = inp.dtype
         weight, bias = self._get_weight_bias()
-        wq = self.get_quantized_weight(weight, self.get_quantizer(True, 1), cache_name="weight",
-                                       is_first_microbatch=is_first_microbatch,
-                                       need_columnwise=torch.is_grad_enabled() and inp.requires_grad or True)
+        if DW.is_distributed_weight(weight):
+            wq = self.quantize_full_weight(DW.materialize_weight_for_forward(weight)[0].detach(),
+                                           self.cfg.activation_dtype)
+        else:
+            wq = self.get_quantized_weight(weight, self.get_quantizer(True, 1), cache_name="weight",
+                                           is_first_microbatch=is_first_microbatch,
+                                           need_columnwise=torch.is_grad_enabled() and inp.requires_grad or True)
         if isinstance(wq, torch.Tensor) and not isinstance(wq, QuantizedTensorStorage) and wq.dtype != self.cfg.activation_dtype:
             wq = wq.to(self.cfg.activation_dtype)
         b_use = bias if self.apply_bias else None

@@ -1,0 +1,41 @@
+"""Factory zoo: every factory trains a Linear through ``CustomRecipe`` close to the fp32 result."""
+import pytest
+import torch
+
+import transformerengine_b200 as te
+from transformerengine_b200.custom_recipes import custom_gemm, quantizer_factories as qf, quantizer_factory_zoo as zoo
+from transformerengine_b200.tensor import MXFP8Quantizer
+
+FACTORIES = [qf.high_precision_factory, qf.identity_factory, qf.current_scaling_factory, qf.float8_block_scaling_factory,
+             qf.mxfp8_factory, qf.nvfp4_factory, zoo.mxfp8_fwd_nvfp4_bwd_factory,
+             zoo.high_precision_fwd_mxfp8_bwd_factory, zoo.mxfp8_fwd_high_precision_bwd_factory,
+             zoo.nvfp4_1d_weight_factory]
+
+
+@pytest.mark.parametrize("factory", FACTORIES, ids=lambda f: f.__name__)
+def test_factory_trains_a_linear(factory):
+    torch.manual_seed(0)
+    lin = te.Linear(128, 128, bias=False, params_dtype=torch.float32, device="cpu")
+    x = torch.randn(64, 128, requires_grad=True)
+    with te.autocast(enabled=True, recipe=te.recipe.CustomRecipe(qfactory=factory)):
+        y = lin(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ref = x.detach() @ lin.weight.detach().t()
+    tol = 0.35 if "nvfp4" in factory.__name__ else 0.1
+    assert (y - ref).abs().max() < tol * ref.abs().max()
+    gx = dy @ lin.weight.detach()
+    gw = dy.t() @ x.detach()
+    assert (x.grad - gx).abs().max() < tol * gx.abs().max() * 1.5
+    assert (lin.weight.grad - gw).abs().max() < tol * gw.abs().max() * 1.5
+
+
+def test_custom_gemm_layouts_on_quantized_operands():
+    torch.manual_seed(0)
+    w, x, dy = torch.randn(64, 32), torch.randn(96, 32), torch.randn(96, 64)
+    q = MXFP8Quantizer(torch.float8_e4m3fn)
+    wq, xq = q(w), q(x)
+    wd, xd = wq.dequantize(dtype=torch.float32), xq.dequantize(dtype=torch.float32)
+    torch.testing.assert_close(custom_gemm(wq, xq, layout="TN"), xd @ wd.t())
+    torch.testing.assert_close(custom_gemm(wq, dy, layout="NN"), dy @ wd)
+    torch.testing.assert_close(custom_gemm(xq, dy, layout="NT"), dy.t() @ xd)

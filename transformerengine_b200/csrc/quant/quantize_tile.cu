@@ -190,7 +190,7 @@ __device__ __forceinline__ uint32_t hmax2_u(uint32_t a, uint32_t b) {
 constexpr int QPITCH = TR + 16;  // bytes per column of the transposed fp8 staging tile
 
 template <int PRO, int ACT>
-__global__ void __launch_bounds__(NT, 3) quantize_tile_kernel(const QuantArgs a, const int MODE) {
+__global__ void __launch_bounds__(NT, 4) quantize_tile_kernel(const QuantArgs a, const int MODE) {
   __shared__ __align__(16) __nv_bfloat16 tile[TR * PITCH];
   // the transposed fp8 staging tile reuses the bf16 tile once every thread holds its column data in registers
   uint8_t* tq = reinterpret_cast<uint8_t*>(tile);

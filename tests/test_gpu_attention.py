@@ -215,3 +215,30 @@ def test_flash_sliding_window_matches_reference(case):
     _close(q.grad, qf.grad, 3e-2)
     _close(k.grad, kf.grad, 3e-2)
     _close(v.grad, vf.grad, 3e-2)
+
+
+def test_flash_varlen_with_sliding_window():
+    import transformerengine_b200 as te
+    from transformerengine_b200.ops import flash
+    from transformerengine_b200.ops.attention import attention_ref
+
+    lens, window = [400, 130, 700], (96, 0)
+    cu = [0, 400, 530, 1230]
+    torch.manual_seed(0)
+    q = torch.randn(cu[-1], 4, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(cu[-1], 2, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(cu[-1], 2, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    do = torch.randn_like(q)
+    cut = torch.tensor(cu, dtype=torch.int32, device="cuda")
+    o = flash.flash_attention_varlen(q, k, v, cut, cut, None, True, True, window=window)
+    o.backward(do)
+    te.ops.check_status()
+    bh = lambda x: x.permute(1, 0, 2).unsqueeze(0)  # noqa: E731
+    for a, b in zip(cu[:-1], cu[1:]):
+        qf, kf, vf = (bh(t[a:b].detach().float()).requires_grad_() for t in (q, k, v))
+        ro = attention_ref(qf, kf, vf, causal=True, window=window)
+        ro.backward(bh(do[a:b].float()))
+        _close(bh(o[a:b]), ro, 2e-2)
+        _close(bh(q.grad[a:b]), qf.grad, 3e-2)
+        _close(bh(k.grad[a:b]), kf.grad, 3e-2)
+        _close(bh(v.grad[a:b]), vf.grad, 3e-2)

@@ -189,13 +189,12 @@ class DotProductAttention(torch.nn.Module):
                                    cp_global_ranks=self.cp_global_ranks, max_seqlen=max_sq)
             return o.reshape(o.shape[0], -1)
         dropout = self.attention_dropout if self.training else 0.0
-        no_window = window is None or (window[0] < 0 and window[1] in (-1, 0) and (window[1] == -1 or causal))
-        if q.is_cuda and no_window and dropout == 0.0 and self.softmax_type == "vanilla" and \
+        if q.is_cuda and dropout == 0.0 and self.softmax_type == "vanilla" and \
                 sys.modules[ops.attention.__module__]._USE_OWN_FLASH and flash.supported_varlen(q, k, v):
             o = flash.flash_attention_varlen(q, k, v, cu_q, cu_kv, scale=self.softmax_scale, causal=causal,
                                              bottom_right="bottom_right" in mask_type, max_seqlen_q=max_sq,
                                              max_seqlen_kv=max_skv, cu_seqlens_q_padded=cu_q_padded,
-                                             cu_seqlens_kv_padded=cu_kv_padded)
+                                             cu_seqlens_kv_padded=cu_kv_padded, window=window)
             return o.reshape(o.shape[0], -1)
         cq, ck = cu_q.tolist(), cu_kv.tolist()
         oq = cq if cu_q_padded is None else cu_q_padded.tolist()

@@ -202,9 +202,10 @@ void set_varlen(teb200::FlashArgs& a, const at::Tensor& q, const at::Tensor& k, 
 void flash_fwd_varlen(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& out,
                       const at::Tensor& lse, const at::Tensor& cu_q, const at::Tensor& cu_k, const at::Tensor& off_q,
                       const at::Tensor& off_k, int64_t max_sq, int64_t max_sk, double scale, bool causal,
-                      bool bottom_right, const at::Tensor& status) {
+                      bool bottom_right, const at::Tensor& status, int64_t window_left, int64_t window_right) {
   c10::cuda::CUDAGuard guard(q.device());
   teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  a.window_left = static_cast<int>(window_left); a.window_right = static_cast<int>(window_right);
   set_varlen(a, q, k, cu_q, cu_k, off_q, off_k, max_sq, max_sk);
   TORCH_CHECK(lse.size(0) == a.b && lse.size(1) == a.hq && lse.size(2) >= max_sq, "lse must be [sequences, hq, >= max_sq]");
   cudaError_t e = teb200::flash_fwd(a, cur_stream());
@@ -215,9 +216,11 @@ void flash_bwd_varlen(const at::Tensor& dout, const at::Tensor& q, const at::Ten
                       const at::Tensor& out, const at::Tensor& lse, const at::Tensor& delta, const at::Tensor& dq,
                       const at::Tensor& dk, const at::Tensor& dv, const at::Tensor& cu_q, const at::Tensor& cu_k,
                       const at::Tensor& off_q, const at::Tensor& off_k, int64_t max_sq, int64_t max_sk, double scale,
-                      bool causal, bool bottom_right, const at::Tensor& status) {
+                      bool causal, bool bottom_right, const at::Tensor& status, int64_t window_left,
+                      int64_t window_right) {
   c10::cuda::CUDAGuard guard(q.device());
   teb200::FlashArgs a = flash_args(q, k, v, out, lse, scale, causal, bottom_right, status);
+  a.window_left = static_cast<int>(window_left); a.window_right = static_cast<int>(window_right);
   set_varlen(a, q, k, cu_q, cu_k, off_q, off_k, max_sq, max_sk);
   TORCH_CHECK(lse.size(0) == a.b && lse.size(2) % 128 == 0 && lse.size(2) >= max_sq && delta.sizes() == lse.sizes(),
               "lse / delta must be [sequences, hq, s_pad] with s_pad a multiple of 128");
@@ -752,7 +755,14 @@ void register_extra(py::module_& m) {
   m.def("convert_thd_to_bshd", &convert_thd_to_bshd);
   m.def("convert_bshd_to_thd", &convert_bshd_to_thd);
   m.def("kv_cache_step", &kv_cache_step);
-  m.def("flash_fwd_varlen", &flash_fwd_varlen);
-  m.def("flash_bwd_varlen", &flash_bwd_varlen);
+  m.def("flash_fwd_varlen", &flash_fwd_varlen, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+        py::arg("lse"), py::arg("cu_q"), py::arg("cu_k"), py::arg("off_q"), py::arg("off_k"), py::arg("max_sq"),
+        py::arg("max_sk"), py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
+        py::arg("window_left") = -1, py::arg("window_right") = -1);
+  m.def("flash_bwd_varlen", &flash_bwd_varlen, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"),
+        py::arg("out"), py::arg("lse"), py::arg("delta"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("cu_q"),
+        py::arg("cu_k"), py::arg("off_q"), py::arg("off_k"), py::arg("max_sq"), py::arg("max_sk"), py::arg("scale"),
+        py::arg("causal"), py::arg("bottom_right"), py::arg("status"), py::arg("window_left") = -1,
+        py::arg("window_right") = -1);
 }
 

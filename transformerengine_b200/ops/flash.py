@@ -116,7 +116,7 @@ def _thd_view(t: torch.Tensor) -> torch.Tensor:
 
 class _FlashVarlenFunc(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, cu_q, cu_k, off_q, off_k, max_sq, max_sk, scale, causal, bottom_right):  # type: ignore[override]
+    def forward(ctx, q, k, v, cu_q, cu_k, off_q, off_k, max_sq, max_sk, scale, causal, bottom_right, window):  # type: ignore[override]
         C_ = _ext.get()
         tq, hq, d = q.shape
         nseq = cu_q.numel() - 1
@@ -125,30 +125,32 @@ class _FlashVarlenFunc(torch.autograd.Function):
         lse = torch.empty(nseq, hq, s_pad, dtype=torch.float32, device=q.device)
         sc = float(scale) if scale is not None else d ** -0.5
         qv, kv, vv = _thd_view(q), _thd_view(k), _thd_view(v)
+        wl, wr = (-1, -1) if window is None else (int(window[0]), int(window[1]))
         C_.flash_fwd_varlen(qv, kv, vv, _thd_view(out), lse, cu_q, cu_k, off_q, off_k, max_sq, max_sk, sc,
-                            bool(causal), bool(bottom_right), C_.status(q.device.index))
+                            bool(causal), bool(bottom_right), C_.status(q.device.index), window_left=wl,
+                            window_right=wr)
         ctx.save_for_backward(qv, kv, vv, out, lse, cu_q, cu_k, off_q, off_k)
-        ctx.cfg = (sc, bool(causal), bool(bottom_right), max_sq, max_sk)
+        ctx.cfg = (sc, bool(causal), bool(bottom_right), max_sq, max_sk, wl, wr)
         return out
 
     @staticmethod
     def backward(ctx, dout):  # type: ignore[override]
         C_ = _ext.get()
         qv, kv, vv, out, lse, cu_q, cu_k, off_q, off_k = ctx.saved_tensors
-        sc, causal, bottom_right, max_sq, max_sk = ctx.cfg
+        sc, causal, bottom_right, max_sq, max_sk, wl, wr = ctx.cfg
         dq = torch.zeros(qv.shape[2], qv.shape[1], 128, dtype=qv.dtype, device=qv.device)
         dk = torch.zeros(kv.shape[2], kv.shape[1], 128, dtype=qv.dtype, device=qv.device)
         dv = torch.zeros_like(dk)
         delta = torch.empty_like(lse)
         C_.flash_bwd_varlen(_thd_view(dout), qv, kv, vv, _thd_view(out), lse, delta, _thd_view(dq), _thd_view(dk),
                             _thd_view(dv), cu_q, cu_k, off_q, off_k, max_sq, max_sk, sc, causal, bottom_right,
-                            C_.status(qv.device.index))
-        return (dq, dk, dv) + (None,) * 9
+                            C_.status(qv.device.index), window_left=wl, window_right=wr)
+        return (dq, dk, dv) + (None,) * 10
 
 
 def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_kv, scale=None, causal=False, bottom_right=True,
                            max_seqlen_q=None, max_seqlen_kv=None, cu_seqlens_q_padded=None,
-                           cu_seqlens_kv_padded=None):
+                           cu_seqlens_kv_padded=None, window=None):
     """Attention over packed sequences.  ``q`` is ``[tq, hq, 128]``, ``k`` / ``v`` ``[tk, hk, 128]``;
     sequence i owns ``cu_seqlens[i+1] - cu_seqlens[i]`` tokens starting at ``cu_seqlens_padded[i]``
     (``cu_seqlens[i]`` when no padded offsets are given).  Returns ``[tq, hq, 128]``."""
@@ -162,5 +164,7 @@ def flash_attention_varlen(q, k, v, cu_seqlens_q, cu_seqlens_kv, scale=None, cau
         max_seqlen_kv = int((cu_k[1:] - cu_k[:-1]).max())
     if max_seqlen_q <= 0 or max_seqlen_kv <= 0:
         return torch.zeros_like(q)
+    if window is not None and window[0] < 0 and (window[1] < 0 or (causal and window[1] == 0)):
+        window = None
     return _FlashVarlenFunc.apply(q, k, v, cu_q, cu_k, off_q, off_k, int(max_seqlen_q), int(max_seqlen_kv), scale,
-                                  causal, bottom_right)
+                                  causal, bottom_right, window)

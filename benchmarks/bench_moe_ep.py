@@ -44,6 +44,7 @@ def main():
     ap.add_argument("--experts", type=int, default=8)
     ap.add_argument("--topk", type=int, default=2)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--profile", action="store_true", help="print rank 0's kernel table of the fused forward + backward")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -78,6 +79,15 @@ def main():
     res["fused_fwd_bwd_ms"] = timed(lambda: fused(True), a.iters)
     res["nccl_fwd_bwd_ms"] = timed(lambda: base(True), a.iters)
     te.check_status()
+    if a.profile:
+        from torch.profiler import ProfilerActivity, profile
+
+        with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+            for _ in range(3):
+                fused(True)
+            torch.cuda.synchronize()
+        if rank == 0:
+            print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=22, max_name_column_width=60))
     wire = a.tokens * a.topk * (ep - 1) / ep * a.hidden * 2
     res["nvlink_bytes_per_direction_fwd"] = 2 * wire
     res["nvlink_roofline_fwd_ms"] = 2 * wire / 770e9 * 1e3  # measured 770 GB/s per direction

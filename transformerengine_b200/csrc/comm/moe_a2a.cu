@@ -83,45 +83,47 @@ __global__ void ep_counts_kernel(EpCountsArgs a) {
 }
 
 // ---- push ------------------------------------------------------------------------------------------
-// one CTA per (token, expert) pair with within[t][e] >= 0
+// CTAs stride over the (token, expert) pairs; a pair with within[t][e] >= 0 is one row copy
 __global__ void ep_push_kernel(EpPushArgs a) {
   const int E = a.ep * a.L;
-  const long long pair = blockIdx.x;
-  const int t = static_cast<int>(pair / E), e = static_cast<int>(pair % E);
-  const int w = a.within[pair];
-  if (w >= 0) {
+  const long long npairs = static_cast<long long>(a.T) * E;
+  for (long long pair = blockIdx.x; pair < npairs; pair += gridDim.x) {
+    const int t = static_cast<int>(pair / E), e = static_cast<int>(pair % E);
+    const int w = a.within[pair];
+    if (w < 0) {
+      if (threadIdx.x == 0) a.rowmap[pair] = -1;
+      continue;
+    }
     const int r = e / a.L;
     const int row = a.base[e] + w;
     if (threadIdx.x == 0) a.rowmap[pair] = row;
-    if (row < a.cap_rows) {
-      const uint4* src = reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * a.vec_per_row;
-      uint4* dst = reinterpret_cast<uint4*>(a.dst[r]) + static_cast<size_t>(row) * a.vec_per_row;
-      if (a.scale == nullptr) {
-        for (int i = threadIdx.x; i < a.vec_per_row; i += blockDim.x) dst[i] = src[i];
-      } else {
-        const float sc = a.scale[pair];
-        for (int i = threadIdx.x; i < a.vec_per_row; i += blockDim.x) {
-          uint4 v = src[i];
-          uint32_t* w32 = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (a.is_bf16) {
-              const float lo = __uint_as_float(w32[k] << 16) * sc, hi = __uint_as_float(w32[k] & 0xffff0000u) * sc;
-              w32[k] = pack_bf16x2(lo, hi);
-            } else {
-              const __half2 h = *reinterpret_cast<const __half2*>(&w32[k]);
-              w32[k] = pack_f16x2(__low2float(h) * sc, __high2float(h) * sc);
-            }
-          }
-          dst[i] = v;
-        }
-      }
-      if (a.probs != nullptr && threadIdx.x == 0) a.dst_probs[r][row] = a.probs[pair];
-    } else if (threadIdx.x == 0) {
-      atomicCAS(a.status, 0, kBadArgument);  // destination buffer too small for this routing
+    if (row >= a.cap_rows) {
+      if (threadIdx.x == 0) atomicCAS(a.status, 0, kBadArgument);  // destination buffer too small for this routing
+      continue;
     }
-  } else if (threadIdx.x == 0) {
-    a.rowmap[pair] = -1;
+    const uint4* src = reinterpret_cast<const uint4*>(a.x) + static_cast<size_t>(t) * a.vec_per_row;
+    uint4* dst = reinterpret_cast<uint4*>(a.dst[r]) + static_cast<size_t>(row) * a.vec_per_row;
+    if (a.scale == nullptr) {
+      for (int i = threadIdx.x; i < a.vec_per_row; i += blockDim.x) dst[i] = src[i];
+    } else {
+      const float sc = a.scale[pair];
+      for (int i = threadIdx.x; i < a.vec_per_row; i += blockDim.x) {
+        uint4 v = src[i];
+        uint32_t* w32 = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          if (a.is_bf16) {
+            const float lo = __uint_as_float(w32[k] << 16) * sc, hi = __uint_as_float(w32[k] & 0xffff0000u) * sc;
+            w32[k] = pack_bf16x2(lo, hi);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w32[k]);
+            w32[k] = pack_f16x2(__low2float(h) * sc, __high2float(h) * sc);
+          }
+        }
+        dst[i] = v;
+      }
+    }
+    if (a.probs != nullptr && threadIdx.x == 0) a.dst_probs[r][row] = a.probs[pair];
   }
   // completion: the last CTA tells every peer that this rank's rows have landed
   __threadfence_system();
@@ -239,7 +241,9 @@ cudaError_t ep_push(const EpPushArgs& a, cudaStream_t s) {
     ep_signal_kernel<<<1, 32, 0, s>>>(sg);
     return cudaGetLastError();
   }
-  ep_push_kernel<<<static_cast<unsigned>(pairs), 128, 0, s>>>(a);
+  // a few CTAs per SM: every CTA ends with one system-scope fence and one atomic on the completion counter
+  const long long want = 148LL * 16;
+  ep_push_kernel<<<static_cast<unsigned>(pairs < want ? pairs : want), 256, 0, s>>>(a);
   return cudaGetLastError();
 }
 cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s) {

@@ -224,7 +224,11 @@ class _FusedDispatch(torch.autograd.Function):
         m = routing_map.bool()
         T = x.shape[0]
         counts = m.sum(0).to(torch.int32)
-        within = torch.where(m, m.long().cumsum(0) - 1, torch.full((), -1, device=x.device)).to(torch.int32).contiguous()
+        # rank of token t among this rank's tokens of expert e: scan along the token axis of the
+        # TRANSPOSED mask (a scan over the outer dim of [T, E] is ~300x slower in torch)
+        mt = m.t().contiguous()
+        within_t = torch.where(mt, mt.cumsum(1, dtype=torch.int32) - 1, torch.full((), -1, dtype=torch.int32, device=x.device))
+        within = within_t.t().contiguous()
         ep.epoch += 1
         ep.C.ep_counts(ep.counts_ptrs, ep.flag_ptrs[0], counts, ep.base, ep.splits, ep.seg, ep.L, ep.rank, ep.align,
                        ep.epoch, ep.status)

@@ -1,6 +1,6 @@
 """Per-kernel time table of one training step (torch.profiler, CUDA activity only).
 
-    python benchmarks/profile_step.py --layers 2 [--seq 8192] [--recipe mxfp8]
+    python benchmarks/profile_step.py --layers 2 [--seq 8192] [--recipe mxfp8] [--model llama|mixtral]
 """
 import argparse
 import os
@@ -10,7 +10,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import transformerengine_b200 as te  # noqa: E402
-from transformerengine_b200.models import llama  # noqa: E402
+from transformerengine_b200.models import llama, mixtral  # noqa: E402
 
 
 def main():
@@ -19,9 +19,14 @@ def main():
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--recipe", default="mxfp8")
     ap.add_argument("--rows", type=int, default=40)
+    ap.add_argument("--model", default="llama", choices=["llama", "mixtral"])
     a = ap.parse_args()
-    cfg = llama.LlamaConfig.llama3_8b(num_layers=a.layers)
-    model = llama.LlamaModel(cfg)
+    if a.model == "mixtral":
+        cfg = mixtral.MixtralConfig.mixtral_8x7b(num_layers=a.layers)
+        model = mixtral.MixtralModel(cfg)
+    else:
+        cfg = llama.LlamaConfig.llama3_8b(num_layers=a.layers)
+        model = llama.LlamaModel(cfg)
     opt = te.FusedAdam(model.parameters(), lr=1e-4, master_weights=True)
     rec = te.recipe.MXFP8BlockScaling() if a.recipe == "mxfp8" else None
     tok = torch.randint(0, cfg.vocab_size, (1, a.seq), device="cuda")

@@ -114,6 +114,7 @@ class _GroupedLinear(torch.autograd.Function):
         dx = torch.empty(dy.shape[0], K, dtype=adt, device=dy.device)
         dws = [None] * G
         dbs = [None] * G
+        x_hp = None  # input dequantized ONCE when it was saved as one quantized tensor
         for g in range(G):
             sl = slice(offs[g], offs[g + 1])
             if module.use_bias:
@@ -132,8 +133,12 @@ class _GroupedLinear(torch.autograd.Function):
                     # the input was quantized as one tensor: re-quantize this slab's rows columnwise
                     in_q = module.get_quantizer(True, 0)
                     in_q.set_usage(rowwise=False, columnwise=True)
-                    xg = in_q(ctx.xq.dequantize(dtype=adt)[sl]) if isinstance(ctx.xq, QuantizedTensorStorage) \
-                        else in_q(ctx.xq[sl])
+                    if isinstance(ctx.xq, QuantizedTensorStorage):
+                        if x_hp is None:
+                            x_hp = ctx.xq.dequantize(dtype=adt)
+                        xg = in_q(x_hp[sl])
+                    else:
+                        xg = in_q(ctx.xq[sl])
                 dws[g] = gemm_nt(as_operand(dyq, "columnwise"), as_operand(xg, "columnwise"),
                                  out_dtype=weights[g].dtype if weights[g].dtype != torch.float32 else torch.float32)
             else:

@@ -20,7 +20,9 @@ def _dest_rows_from_mask(routing_map: torch.Tensor, align: int = 1):
     padded = (counts + align - 1) // align * align if align > 1 else counts
     offs = torch.zeros(E + 1, dtype=torch.int64, device=m.device)
     offs[1:] = padded.cumsum(0)
-    within = m.long().cumsum(0) - 1  # rank of the token inside its expert
+    # rank of the token inside its expert: scan the inner dim of the transposed mask (the scan over
+    # the outer dim of [T, E] is orders of magnitude slower on the GPU)
+    within = (m.t().contiguous().cumsum(1) - 1).t()
     dest = torch.where(m, within + offs[:-1][None, :], torch.full_like(within, -1))
     return dest, counts, offs
 

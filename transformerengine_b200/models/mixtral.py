@@ -69,8 +69,10 @@ class _ActScaled(torch.autograd.Function):
         x, probs = ctx.saved_tensors
         dy = dy.contiguous()
         dx, _, _ = ops.activation_bwd(dy, x, ctx.act, row_scale=probs)
-        unscaled = ops.activation.activation_fwd_ref(x, ctx.act)
-        dprobs = (dy.float() * unscaled).sum(-1).to(probs.dtype)
+        # d(probs)[r] = <dy[r], act(x)[r]>: the unscaled activation from the fused kernel, the row dots
+        # as one batched product (the fp32 mul + sum pair cost three passes over [rows, ffn])
+        unscaled, _ = ops.activation_fwd(x, ctx.act)
+        dprobs = torch.bmm(dy.unsqueeze(1), unscaled.to(dy.dtype).unsqueeze(2)).reshape(-1).to(probs.dtype)
         return dx, dprobs, None
 
 

@@ -93,3 +93,13 @@ def test_thd_bshd_round_trip_and_kv_cache_step():
     torch.testing.assert_close(v, -k)
     torch.testing.assert_close(ck[2, 1], new_k[0])
     torch.testing.assert_close(ck[5, :3], new_k[1:])
+
+
+def test_sequence_order_and_cp_rank_order_round_trip():
+    cu = torch.tensor([0, 8, 24, 32], dtype=torch.int32)
+    x = torch.arange(32, dtype=torch.float32).reshape(32, 1)
+    r = thd.thd_sequence_order_to_cp_rank_order(x, cu, 2, 32)
+    # the first half is rank 0's shard: chunks 0 and 3 of every sequence
+    assert r[:4, 0].tolist() == [0, 1, 6, 7] and r[16:20, 0].tolist() == [2, 3, 4, 5]
+    back = thd.thd_reorder_between_sequence_and_cp_rank_order(r, cu, 2, True, 32)
+    assert torch.equal(back, x)

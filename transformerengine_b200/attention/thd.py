@@ -180,3 +180,32 @@ def kv_cache_step(new_k: torch.Tensor, new_v: torch.Tensor, cache_k: torch.Tenso
         ks.append(cache_k[pages[allp // ps], allp % ps])
         vs.append(cache_v[pages[allp // ps], allp % ps])
     return torch.cat(ks, dim=0), torch.cat(vs, dim=0)
+
+
+def _cp_rank_order_index(cu_seqlens: torch.Tensor, total_tokens: int, cp_size: int) -> torch.Tensor:
+    """Token indices (sequence order) listed rank by rank: position j of the result is the token that
+    sits at position j of the concatenation of all ranks' shards."""
+    return torch.cat([thd_get_partitioned_indices(cu_seqlens, total_tokens, cp_size, r).long() for r in range(cp_size)])
+
+
+def thd_sequence_order_to_cp_rank_order(inp: torch.Tensor, cu_seqlens: torch.Tensor, cp_size: int,
+                                        total_tokens: int) -> torch.Tensor:
+    """Reorder packed tokens from sequence order to the concatenation of the context-parallel ranks'
+    shards (what an all-gather over the group produces)."""
+    assert inp.shape[0] == total_tokens and total_tokens % (2 * cp_size) == 0
+    return inp.index_select(0, _cp_rank_order_index(cu_seqlens, total_tokens, cp_size).to(inp.device))
+
+
+def thd_cp_rank_order_to_sequence_order(inp: torch.Tensor, cu_seqlens: torch.Tensor, cp_size: int,
+                                        total_tokens: int) -> torch.Tensor:
+    """Inverse of :func:`thd_sequence_order_to_cp_rank_order`."""
+    assert inp.shape[0] == total_tokens and total_tokens % (2 * cp_size) == 0
+    out = torch.empty_like(inp)
+    out.index_copy_(0, _cp_rank_order_index(cu_seqlens, total_tokens, cp_size).to(inp.device), inp)
+    return out
+
+
+def thd_reorder_between_sequence_and_cp_rank_order(inp: torch.Tensor, cu_seqlens: torch.Tensor, cp_size: int,
+                                                   cp_rank_to_sequence_order: bool, total_tokens: int) -> torch.Tensor:
+    fn = thd_cp_rank_order_to_sequence_order if cp_rank_to_sequence_order else thd_sequence_order_to_cp_rank_order
+    return fn(inp, cu_seqlens, cp_size, total_tokens)

@@ -53,3 +53,20 @@ def test_fused_mla_query_projection_matches_composed_math():
     q2, saved2 = FusedMLAQUpProjRopeQuant.run(x, wq, cos, sin, s, b, head_dim=d)
     assert saved2.get_usages() == {"rowwise": False, "columnwise": True}
     assert (q2.dequantize(dtype=torch.float32) - ref).abs().max() < 0.15 * ref.abs().max()
+
+
+def test_fused_qkv_split_and_rope_matches_separate_calls():
+    from transformerengine_b200.attention.rope import (RotaryPositionEmbedding, apply_fused_qkv_rotary_pos_emb,
+                                                       apply_rotary_pos_emb)
+
+    torch.manual_seed(0)
+    s, b, g, d = 16, 2, 2, 32
+    qkv = torch.randn(s, b, g, 4 * d + d + d, requires_grad=True)
+    freqs = RotaryPositionEmbedding(d)(s)
+    q, k, v = apply_fused_qkv_rotary_pos_emb(qkv, freqs, freqs, [4 * d, d, d])
+    assert q.shape == (s, b, 4 * g, d) and k.shape == (s, b, g, d) and v.shape == (s, b, g, d)
+    torch.testing.assert_close(q, apply_rotary_pos_emb(qkv[..., :4 * d].reshape(s, b, 4 * g, d), freqs))
+    torch.testing.assert_close(k, apply_rotary_pos_emb(qkv[..., 4 * d:5 * d], freqs))
+    torch.testing.assert_close(v, qkv[..., 5 * d:])
+    (q.sum() + k.sum() + v.sum()).backward()
+    assert qkv.grad.abs().sum() > 0

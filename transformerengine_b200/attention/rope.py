@@ -73,3 +73,29 @@ def apply_rotary_pos_emb(t: torch.Tensor, freqs: torch.Tensor, tensor_format: st
         return torch.cat(outs, dim=0)
     assert tensor_format in ("sbhd", "bshd")
     return _RopeFn.apply(t, freqs, tensor_format, interleaved, cp_size, cp_rank, start_positions)
+
+
+def apply_fused_qkv_rotary_pos_emb(qkv: torch.Tensor, q_freqs: torch.Tensor, k_freqs: torch.Tensor,
+                                   qkv_split_arg_list, tensor_format: str = "sbhd",
+                                   start_positions: Optional[torch.Tensor] = None, interleaved: bool = False,
+                                   cu_seqlens: Optional[torch.Tensor] = None, cp_size: int = 1, cp_rank: int = 0):
+    """Split a packed QKV projection and rotate Q and K.
+
+    ``qkv`` is ``[s, b, g, q + k + v]`` (or ``[b, s, ...]``) with, per key/value group ``g``, ``q`` query
+    channels (``q / d`` heads), ``k`` key channels and ``v = d`` value channels
+    (``qkv_split_arg_list = [q, k, v]``).  Returns ``(q [.., g * q/d, d], k [.., g * k/d, d], v [.., g, d])``
+    with the rotation applied to Q and K; the split is a view, the two rotations are the RoPE kernel.
+    (Reference: ``pytorch/attention/rope.py:465``.)"""
+    assert tensor_format in ("sbhd", "bshd") and len(qkv_split_arg_list) == 3
+    nq, nk, nv = (int(x) for x in qkv_split_arg_list)
+    assert qkv.shape[-1] == nq + nk + nv and nq % nv == 0 and nk % nv == 0, "split sizes must be whole heads"
+    d = nv
+    q, k, v = torch.split(qkv, [nq, nk, nv], dim=-1)
+    lead = qkv.shape[:2]
+    q = q.reshape(*lead, -1, d)
+    k = k.reshape(*lead, -1, d)
+    q = apply_rotary_pos_emb(q, q_freqs, tensor_format, start_positions=start_positions, interleaved=interleaved,
+                             cp_size=cp_size, cp_rank=cp_rank)
+    k = apply_rotary_pos_emb(k, k_freqs, tensor_format, start_positions=start_positions, interleaved=interleaved,
+                             cp_size=cp_size, cp_rank=cp_rank)
+    return q, k, v

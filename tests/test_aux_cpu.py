@@ -155,3 +155,14 @@ def test_torch_compile_wraps_modules_without_changing_results():
     xg = x.clone().requires_grad_()
     torch.compile(fn, backend="aot_eager")(xg).sum().backward()
     assert xg.grad is not None and lin.weight.grad is not None
+
+
+def test_numerics_debug_counts_saturated_and_flushed_values():
+    from transformerengine_b200 import numerics_debug as nd
+
+    x = torch.tensor([0.0, 1e-9, 3.0, 1e6, -1e6])
+    q = x.clamp(-448, 448).to(torch.float8_e4m3fn).float()
+    assert nd.fp8_tensor_statistics(q, "e4m3") == (2, 2)
+    nd.debug(True)
+    assert nd.is_debug()
+    nd.debug(False)

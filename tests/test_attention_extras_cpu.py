@@ -1,6 +1,8 @@
 """Score-modifier attention and the latent-attention query projection (CPU path)."""
 import math
 
+import pytest
+
 import torch
 
 import transformerengine_b200 as te
@@ -70,3 +72,41 @@ def test_fused_qkv_split_and_rope_matches_separate_calls():
     torch.testing.assert_close(v, qkv[..., 5 * d:])
     (q.sum() + k.sum() + v.sum()).backward()
     assert qkv.grad.abs().sum() > 0
+
+
+def test_causal_cross_attention_is_top_left_aligned():
+    """'causal' keeps the diagonal at the top-left corner when sq != sk; only '*_bottom_right' moves it."""
+    torch.manual_seed(0)
+    b, h, sq, sk, d = 1, 2, 4, 7, 8
+    q, k, v = torch.randn(sq, b, h, d), torch.randn(sk, b, h, d), torch.randn(sk, b, h, d)
+    dpa = te.DotProductAttention(h, d, attention_dropout=0.0, attention_type="cross", qkv_format="sbhd")
+    score = torch.einsum("sbhd,tbhd->bhst", q, k) / d ** 0.5
+    i, j = torch.arange(sq)[:, None], torch.arange(sk)[None, :]
+    for mask_type, allowed in (("causal", j <= i), ("causal_bottom_right", j <= i + (sk - sq))):
+        p = torch.softmax(score.masked_fill(~allowed, float("-inf")), dim=-1)
+        want = torch.einsum("bhst,tbhd->sbhd", p, v).reshape(sq, b, h * d)
+        got = dpa(q, k, v, attn_mask_type=mask_type)
+        assert torch.allclose(got, want, atol=1e-5), mask_type
+
+
+def test_context_parallel_refuses_what_it_does_not_implement(monkeypatch):
+    """With a context-parallel group of more than one rank, arguments outside scale / causal / window
+    raise instead of being dropped."""
+    from transformerengine_b200.parallel import distributed as D
+
+    dpa = te.DotProductAttention(2, 8, attention_dropout=0.0, qkv_format="sbhd")
+    dpa.set_context_parallel_group(object(), [0, 1], None, "p2p")
+    monkeypatch.setattr(D, "get_world_size", lambda group=None: 2)
+    q = torch.randn(4, 1, 2, 8)
+    with pytest.raises(NotImplementedError, match="alibi"):
+        dpa(q, q, q, core_attention_bias_type="alibi")
+    with pytest.raises(NotImplementedError, match="mask"):
+        dpa(q, q, q, attn_mask_type="padding", attention_mask=torch.zeros(1, 1, 1, 4, dtype=torch.bool))
+    dpa_drop = te.DotProductAttention(2, 8, attention_dropout=0.1, qkv_format="sbhd")
+    dpa_drop.set_context_parallel_group(object(), [0, 1], None, "p2p")
+    with pytest.raises(NotImplementedError, match="dropout"):
+        dpa_drop(q, q, q)
+    cu = torch.tensor([0, 4], dtype=torch.int32)
+    with pytest.raises(NotImplementedError, match="sliding window"):
+        dpa(q.reshape(4, 2, 8), q.reshape(4, 2, 8), q.reshape(4, 2, 8), qkv_format="thd", cu_seqlens_q=cu,
+            attn_mask_type="padding_causal", window_size=(2, 0))

@@ -16,6 +16,21 @@ def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
 
+def test_linear_fp32_parameters_keep_fp32_math():
+    """fp32 parameters and activations are not rounded to bf16 on the way into the GEMM."""
+    torch.manual_seed(0)
+    lin = te.Linear(384, 640, params_dtype=torch.float32, device=DEV)
+    x = torch.randn(200, 384, device=DEV, requires_grad=True)
+    y = lin(x)
+    y.square().sum().backward()
+    xr = x.detach().clone().requires_grad_()
+    w, b = lin.weight.detach().clone().requires_grad_(), lin.bias.detach().clone().requires_grad_()
+    yr = torch.nn.functional.linear(xr.double(), w.double(), b.double())
+    yr.square().sum().backward()
+    assert _rel(y, yr) < 1e-5
+    assert _rel(x.grad, xr.grad) < 1e-5 and _rel(lin.weight.grad, w.grad) < 1e-5
+
+
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 520, 264), (1024, 1024, 4096), (64, 96, 32)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gemm_16bit(M, N, K, dtype):

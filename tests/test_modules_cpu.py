@@ -214,6 +214,42 @@ def test_unsafe_pickle_is_refused():
         m.set_extra_state(blob)
 
 
+def test_nested_pickle_in_tensor_storage_is_refused(tmp_path):
+    """A tensor pickled by value goes through ``torch.storage._load_from_bytes``; a payload smuggled
+    in that nested archive must not run, and neither may a function of the recipe module."""
+    import os
+
+    m = te.Linear(8, 8, device="cpu")
+    marker = tmp_path / "pwned"
+
+    class Evil:
+        def __reduce__(self):
+            return (os.system, (f"touch {marker}",))
+
+    inner = io.BytesIO()
+    torch.save(Evil(), inner)
+
+    class Wrapper:
+        def __reduce__(self):
+            return (torch.storage._load_from_bytes, (inner.getvalue(),))
+
+    blob = torch.frombuffer(bytearray(pickle.dumps({"recipe": Wrapper()})), dtype=torch.uint8)
+    with pytest.raises(Exception):
+        m.set_extra_state(blob)
+    assert not marker.exists()
+    # an attribute of the recipe module that is not a recipe class is refused as well
+    payload = b"\x80\x04" + pickle.GLOBAL + b"transformer_engine.common.recipe\n_install_pickle_alias\n" + pickle.STOP
+    with pytest.raises(pickle.UnpicklingError):
+        m.set_extra_state(torch.frombuffer(bytearray(payload), dtype=torch.uint8))
+    # honest tensors still load through the weights-only stand-in
+    good = te.Linear(32, 64, device="cpu", params_dtype=torch.float32)
+    with te.autocast(enabled=True, recipe=R.DelayedScaling(amax_history_len=4)):
+        good(torch.randn(32, 32)).sum().backward()
+    fresh = te.Linear(32, 64, device="cpu", params_dtype=torch.float32)
+    fresh.set_extra_state(good.get_extra_state())
+    assert isinstance(fresh.fp8_meta["recipe"], R.DelayedScaling)
+
+
 def test_parameters_split_names_and_weight_cache():
     m = te.Linear(32, 96, parameters_split=("query", "key", "value"), device="cpu", params_dtype=torch.float32)
     names = dict(m.named_parameters()).keys()
@@ -297,3 +333,33 @@ def test_fsdp2_hooks_reassemble_row_shards():
     (data,), m8 = f.fsdp_pre_all_gather()
     rebuilt8, _ = f.fsdp_post_all_gather((torch.cat([data[:128], data[128:]]),), m8)
     assert torch.equal(rebuilt8.dequantize(), f.dequantize())
+
+
+@pytest.mark.parametrize("use_reentrant", [True, False])
+def test_checkpoint_is_consistent_under_delayed_scaling(use_reentrant):
+    """Activation recompute quantizes with the scales of the first run and records no second amax:
+    outputs, gradients and the amax histories equal the run without recompute bit for bit."""
+    def run(ckpt):
+        torch.manual_seed(0)
+        m1 = te.Linear(32, 32, device="cpu", params_dtype=torch.float32)
+        m2 = te.Linear(32, 32, device="cpu", params_dtype=torch.float32)
+        rec = R.DelayedScaling(amax_history_len=4)
+        seen = []
+        for step in range(3):
+            x = (torch.randn(16, 32) * (step + 1)).requires_grad_()
+            with te.autocast(enabled=True, recipe=rec):
+                if ckpt:
+                    y = te.checkpoint(m2, te.checkpoint(m1, x, use_reentrant=use_reentrant),
+                                      use_reentrant=use_reentrant)
+                else:
+                    y = m2(m1(x))
+            y.square().sum().backward()
+            seen.append([y.detach().clone(), m1.weight.grad.clone(), m2.weight.grad.clone(), x.grad.clone()]
+                        + [m._states[k].amax_history.clone() for m in (m1, m2) for k in ("scaling_fwd", "scaling_bwd")]
+                        + [m._states[k].scale.clone() for m in (m1, m2) for k in ("scaling_fwd", "scaling_bwd")])
+            m1.weight.grad = m2.weight.grad = None
+        return seen
+
+    for plain, ckpt in zip(run(False), run(True)):
+        for a, b in zip(plain, ckpt):
+            assert torch.equal(a, b)

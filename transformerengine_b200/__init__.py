@@ -10,6 +10,7 @@ a pure-PyTorch reference path with the same numerics.
 """
 from .common import recipe  # noqa: F401
 from . import ops  # noqa: F401
+from . import ops as functional  # noqa: F401  (the functional layer under an unambiguous name)
 from .ops import check_status  # noqa: F401
 from . import tensor  # noqa: F401
 from .quantization import (autocast, fp8_autocast, quantized_model_init, fp8_model_init, FP8GlobalStateManager,

@@ -132,7 +132,9 @@ class DotProductAttention(torch.nn.Module):
         b, hq, sq, d = qb.shape
         sk = kb.shape[2]
         causal = "causal" in mask_type
-        bottom_right = "bottom_right" in mask_type or (causal and self.attention_type == "cross")
+        # 'causal' aligns the diagonal to the top-left corner, '*_bottom_right' to the bottom-right one, for
+        # self- and cross-attention alike (reference: dot_product_attention.py:1746-1754)
+        bottom_right = "bottom_right" in mask_type
         mask = None
         if "padding" in mask_type:
             if attention_mask is not None:
@@ -156,6 +158,17 @@ class DotProductAttention(torch.nn.Module):
         if self.cp_group is not None and D.get_world_size(self.cp_group) > 1:
             from ..parallel.context_parallel import attn_forward_func_with_cp
 
+            # the context-parallel paths implement scale / causal / window only: refuse the rest loudly
+            unsupported = [name for name, on in (
+                ("a padding or arbitrary attention mask", mask is not None),
+                ("core_attention_bias / alibi", the_bias is not None),
+                ("attention dropout", dropout > 0.0),
+                (f"softmax_type={self.softmax_type!r}", self.softmax_type != "vanilla"),
+                ("score_mod", score[0] is not None),
+                ("bottom-right causal alignment with sq != sk", causal and bottom_right and sq != sk),
+            ) if on]
+            if unsupported:
+                raise NotImplementedError("context parallelism does not support: " + "; ".join(unsupported))
             o = attn_forward_func_with_cp(qb, kb, vb, cp_group=self.cp_group, cp_comm_type=self.cp_comm_type,
                                           scale=self.softmax_scale, causal=causal, window=window,
                                           cp_global_ranks=self.cp_global_ranks, cp_stream=self.cp_stream)
@@ -185,6 +198,15 @@ class DotProductAttention(torch.nn.Module):
             from ..parallel.context_parallel_thd import thd_ring_attention
 
             assert self.cp_comm_type == "p2p", "packed sequences support the ring (p2p) context-parallel mode"
+            unsupported = [name for name, on in (
+                ("a sliding window", window is not None and tuple(window) not in ((-1, -1), (-1, 0))),
+                ("bottom-right causal alignment", "bottom_right" in mask_type),
+                ("attention dropout", self.training and self.attention_dropout > 0.0),
+                (f"softmax_type={self.softmax_type!r}", self.softmax_type != "vanilla"),
+            ) if on]
+            if unsupported:
+                raise NotImplementedError("context parallelism over packed sequences does not support: "
+                                          + "; ".join(unsupported))
             o = thd_ring_attention(q, k, v, cu_q, cp_group=self.cp_group, scale=self.softmax_scale, causal=causal,
                                    cp_global_ranks=self.cp_global_ranks, max_seqlen=max_sq)
             return o.reshape(o.shape[0], -1)

@@ -226,9 +226,25 @@ void norm_bwd(bool layernorm, const at::Tensor& dy, const at::Tensor& x, const O
 }
 
 // lists[k][i]: tensor i of list k.  Splits into launches of <= kMtMaxTensors tensors / kMtMaxBlocks blocks.
+// The kernels index raw pointers with 16-byte vector accesses: every entry must be dense, as long as its
+// partner in list 0, of one dtype per list and 16-byte aligned.
 template <typename Launch>
 void multi_tensor_apply(const std::vector<std::vector<at::Tensor>>& lists, int64_t chunk, Launch&& launch) {
   const size_t nt = lists[0].size();
+  for (size_t k = 0; k < lists.size(); ++k) {
+    TORCH_CHECK(lists[k].size() == nt, "multi_tensor_apply: list ", k, " has ", lists[k].size(), " tensors, list 0 has ", nt);
+    for (size_t i = 0; i < nt; ++i) {
+      const at::Tensor& x = lists[k][i];
+      TORCH_CHECK(x.is_cuda(), "multi_tensor_apply: tensor ", i, " of list ", k, " is not on a GPU");
+      TORCH_CHECK(x.is_contiguous(), "multi_tensor_apply: tensor ", i, " of list ", k,
+                  " is not contiguous (an expanded or strided view; call .contiguous() first)");
+      TORCH_CHECK(x.numel() == lists[0][i].numel(), "multi_tensor_apply: tensor ", i, " of list ", k, " has ",
+                  x.numel(), " elements, its partner in list 0 has ", lists[0][i].numel());
+      TORCH_CHECK(x.scalar_type() == lists[k][0].scalar_type(), "multi_tensor_apply: list ", k, " mixes dtypes");
+      TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0 || x.numel() == 0, "multi_tensor_apply: tensor ",
+                  i, " of list ", k, " is not 16-byte aligned (a sliced view; clone it)");
+    }
+  }
   teb200::MultiTensorTable tab;
   int nten = 0, nblk = 0, base = 0;
   for (size_t i = 0; i < nt; ++i) {
@@ -267,7 +283,8 @@ void multi_tensor_apply(const std::vector<std::vector<at::Tensor>>& lists, int64
 
 void multi_tensor_adam(std::vector<std::vector<at::Tensor>> lists, double lr, double beta1, double beta2, double eps,
                        int64_t step, bool adamw, bool bias_correction, double weight_decay, double grad_scale,
-                       const OptT& inv_scale, const OptT& noop, int64_t chunk) {
+                       const OptT& inv_scale, const OptT& noop, int64_t chunk, const OptT& step_dev,
+                       const OptT& lr_dev, bool remainders) {
   TORCH_CHECK(lists.size() == 4 || lists.size() == 5, "adam expects [g, p, m, v] or [g, p, m, v, master]");
   if (lists[0].empty()) return;
   c10::cuda::CUDAGuard guard(lists[0][0].device());
@@ -283,7 +300,22 @@ void multi_tensor_adam(std::vector<std::vector<at::Tensor>> lists, double lr, do
   a.grad_dtype = to_dtype(lists[0][0]);
   a.param_dtype = to_dtype(lists[1][0]);
   a.state_dtype = to_dtype(lists[2][0]);
-  a.has_master = lists.size() == 5;
+  a.has_master = lists.size() == 5 ? (remainders ? 2 : 1) : 0;
+  if (remainders) {
+    TORCH_CHECK(lists.size() == 5 && lists[4][0].scalar_type() == at::kShort && lists[1][0].scalar_type() == at::kBFloat16,
+                "parameter remainders need bf16 parameters and an int16 list");
+  } else if (lists.size() == 5) {
+    TORCH_CHECK(lists[4][0].scalar_type() == at::kFloat, "master weights must be fp32");
+  }
+  a.bias_correction = bias_correction;
+  if (step_dev.has_value()) {
+    TORCH_CHECK(step_dev->scalar_type() == at::kInt && step_dev->is_cuda(), "device step counter must be int32 on the GPU");
+    a.step_dev = step_dev->data_ptr<int>();
+  }
+  if (lr_dev.has_value()) {
+    TORCH_CHECK(lr_dev->scalar_type() == at::kFloat && lr_dev->is_cuda(), "device learning rate must be fp32 on the GPU");
+    a.lr_dev = lr_dev->data_ptr<float>();
+  }
   a.grad_scale = static_cast<float>(grad_scale);
   a.inv_scale_dev = ptr<float>(inv_scale);
   a.noop = ptr<int>(noop);

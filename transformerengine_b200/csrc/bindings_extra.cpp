@@ -33,11 +33,13 @@ int dtype_code(const at::Tensor& t) {
 // Fused collective GEMM.  `a` is the LOCAL gathered buffer [M, K] (all-gather) or the local
 // operand [M, K_local] (reduce-scatter); peer buffers are passed as raw device addresses taken
 // from the symmetric-memory rendezvous.
-void comm_gemm(int64_t mode, int64_t rank, int64_t world, int64_t epoch, int64_t copy_ctas, const at::Tensor& a,
+void comm_gemm(int64_t mode, int64_t rank, int64_t world, const at::Tensor& epoch_dev, int64_t copy_ctas, const at::Tensor& a,
                const OptT& sfa, const at::Tensor& b, const OptT& sfb, const OptT& d, const OptT& bias, bool a_e5m2,
                bool b_e5m2, std::vector<int64_t> a_ptrs, std::vector<int64_t> sfa_ptrs,
                std::vector<int64_t> ready_ptrs, int64_t chunk_flags_ptr, std::vector<int64_t> stage_ptrs,
-               std::vector<int64_t> tile_flag_ptrs, const OptT& out, int64_t N, const at::Tensor& status) {
+               std::vector<int64_t> tile_flag_ptrs, const OptT& out, int64_t N, const at::Tensor& status,
+               std::vector<int64_t> side_src_ptrs, const OptT& side_dst, const OptT& side_dst_sf,
+               std::vector<int64_t> side_geom) {
   c10::cuda::CUDAGuard guard(a.device());
   teb200::CommGemmArgs c;
   teb200::GemmArgs& g = c.g;
@@ -73,7 +75,9 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, int64_t epoch, int64_t
   c.mode = static_cast<int>(mode);
   c.rank = static_cast<int>(rank);
   c.world = static_cast<int>(world);
-  c.epoch = static_cast<uint32_t>(epoch);
+  TORCH_CHECK(epoch_dev.scalar_type() == at::kInt && epoch_dev.numel() >= 2 && epoch_dev.is_cuda(),
+              "comm_gemm: the call counter must be two int32 words on the GPU");
+  c.epoch_dev = reinterpret_cast<uint32_t*>(epoch_dev.data_ptr<int>());
   c.copy_ctas = static_cast<int>(copy_ctas);
   for (int r = 0; r < world && r < teb200::kCommMaxRanks; ++r) {
     if (!a_ptrs.empty()) c.a_full[r] = reinterpret_cast<const uint8_t*>(a_ptrs[r]);
@@ -86,6 +90,28 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, int64_t epoch, int64_t
   c.sf_bytes_per_mblock = mx ? static_cast<long long>(((g.K + 31) / 32 + 3) / 4) * 512 : 0;
   c.chunk_flags = reinterpret_cast<uint32_t*>(chunk_flags_ptr);
   c.out = (out.has_value() && out->defined()) ? out->data_ptr() : nullptr;
+  if (!side_src_ptrs.empty()) {
+    // side_geom = [rows, row_bytes, dst_pitch, dst_piece_off, row_tiles, sf_chunk]
+    TORCH_CHECK(side_geom.size() == 6 && side_dst.has_value() && side_dst->defined(), "comm_gemm: bad side gather");
+    TORCH_CHECK(static_cast<int64_t>(side_src_ptrs.size()) >= world, "comm_gemm: side gather needs one pointer per rank");
+    for (int r = 0; r < world && r < teb200::kCommMaxRanks; ++r)
+      c.side.src[r] = reinterpret_cast<const uint8_t*>(side_src_ptrs[r]);
+    c.side.dst = static_cast<uint8_t*>(side_dst->data_ptr());
+    c.side.dst_sf = (side_dst_sf.has_value() && side_dst_sf->defined()) ? static_cast<uint8_t*>(side_dst_sf->data_ptr()) : nullptr;
+    c.side.rows = static_cast<int>(side_geom[0]);
+    c.side.row_bytes = static_cast<int>(side_geom[1]);
+    c.side.dst_pitch = side_geom[2];
+    c.side.dst_piece_off = side_geom[3];
+    c.side.row_tiles = static_cast<int>(side_geom[4]);
+    c.side.sf_chunk = static_cast<int>(side_geom[5]);
+    TORCH_CHECK(side_dst->numel() * side_dst->element_size() >=
+                    (c.side.rows - 1) * c.side.dst_pitch + (world - 1) * c.side.dst_piece_off + c.side.row_bytes,
+                "comm_gemm: side gather destination too small");
+    if (c.side.sf_chunk > 0)
+      TORCH_CHECK(c.side.dst_sf != nullptr && side_dst_sf->numel() * side_dst_sf->element_size() >=
+                      static_cast<int64_t>(c.side.row_tiles) * world * c.side.sf_chunk,
+                  "comm_gemm: side gather scale destination too small");
+  }
   cudaError_t e = teb200::comm_gemm(c, cur_stream());
   TORCH_CHECK(e == cudaSuccess, "comm_gemm failed: ", cudaGetErrorString(e));
 }
@@ -738,7 +764,12 @@ void register_extra(py::module_& m) {
   m.def("nvfp4_amax", &nvfp4_amax);
   m.def("quantize_nvfp4", &quantize_nvfp4);
   m.def("dequantize_nvfp4", &dequantize_nvfp4);
-  m.def("comm_gemm", &comm_gemm);
+  m.def("comm_gemm", &comm_gemm, py::arg("mode"), py::arg("rank"), py::arg("world"), py::arg("epoch_dev"),
+        py::arg("copy_ctas"), py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("bias"),
+        py::arg("a_e5m2"), py::arg("b_e5m2"), py::arg("a_ptrs"), py::arg("sfa_ptrs"), py::arg("ready_ptrs"),
+        py::arg("chunk_flags_ptr"), py::arg("stage_ptrs"), py::arg("tile_flag_ptrs"), py::arg("out"), py::arg("N"),
+        py::arg("status"), py::arg("side_src_ptrs") = std::vector<int64_t>(), py::arg("side_dst") = py::none(),
+        py::arg("side_dst_sf") = py::none(), py::arg("side_geom") = std::vector<int64_t>());
   m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
         py::arg("timeline") = py::none(), py::arg("window_left") = -1, py::arg("window_right") = -1);

@@ -22,7 +22,8 @@ constexpr int BN = 256;
 struct CommParams {
   KernelParams k;
   int mode, rank, world;
-  uint32_t epoch;
+  uint32_t* epoch_dev;   // calls completed on this (context, buffer slot); this call is number *epoch_dev + 1
+  uint32_t* done_ctas;   // CTAs of this launch that have finished; the last one advances *epoch_dev
   int copy_ctas;
   int mb_per_rank;   // 128-row blocks owned by one rank
   int num_n;         // column tiles
@@ -34,6 +35,7 @@ struct CommParams {
   uint8_t* stage[kCommMaxRanks];
   uint32_t* tile_flags[kCommMaxRanks];
   void* out;
+  SideGather side;
 };
 
 struct Tile {
@@ -78,6 +80,21 @@ __device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want) {
   return true;
 }
 
+// The call number lives in device memory so that a launch recorded in a CUDA graph stays correct on
+// every replay: each CTA reads it on entry, and the CTA that finishes last stores the new value (all
+// CTAs of the launch have read the old one by then; the next launch on the stream sees the new one).
+__device__ __forceinline__ uint32_t read_epoch(const CommParams& p) {
+  return *reinterpret_cast<const volatile uint32_t*>(p.epoch_dev) + 1u;
+}
+__device__ __forceinline__ void cta_done(const CommParams& p, uint32_t epoch) {
+  __threadfence();
+  if (atomicAdd(p.done_ctas, 1u) == gridDim.x - 1) {
+    *reinterpret_cast<volatile uint32_t*>(p.done_ctas) = 0u;
+    *reinterpret_cast<volatile uint32_t*>(p.epoch_dev) = epoch;
+    __threadfence();
+  }
+}
+
 // ---------------------------------------------------------------- copy CTAs (all-gather)
 // One thread per copy CTA streams peer rows through a ring of shared-memory slots with bulk
 // async copies: peer global -> shared (completion on an mbarrier), shared -> local global
@@ -86,13 +103,13 @@ __device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want) {
 constexpr int kCopyPiece = 32 * 1024;
 constexpr int kCopySlots = 6;
 
-__device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars) {
+__device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars, uint32_t epoch) {
   const int tid = threadIdx.x;
   if (cta == 0 && tid < p.world && tid != p.rank) {
     // this rank's rows were written by earlier kernels of this stream: publish them to every peer
-    st_release_sys(p.ready[tid] + p.rank, p.epoch);
+    st_release_sys(p.ready[tid] + p.rank, epoch);
   }
-  if (tid != 0) return;
+  if (tid != 0 || p.mode != kCommAllGather) return;
   for (int i = 0; i < kCopySlots; ++i) mbar_init(&bars[i], 1);
   mbar_fence_init();
   const int items = (p.world - 1) * p.mb_per_rank;
@@ -134,7 +151,7 @@ __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint6
     piece(q, src, dst, bytes, mb, srank);
     if (q % pieces_per_item == 0) {
       // first piece of an item: the source rank must have published its rows for this call
-      if (!wait_flag_ge(p.ready[p.rank] + srank, p.epoch)) {
+      if (!wait_flag_ge(p.ready[p.rank] + srank, epoch)) {
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
@@ -167,7 +184,7 @@ __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint6
       tma_store_wait<0>();
       fence_proxy_async_all();
       __threadfence();
-      st_release_gpu(p.chunk_flags + mb, p.epoch);
+      st_release_gpu(p.chunk_flags + mb, epoch);
     }
   }
   if (!ok) {
@@ -175,9 +192,101 @@ __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint6
     tma_store_wait<0>();
     for (int it = cta; it < items; it += p.copy_ctas) {
       const int srank = (p.rank + 1 + it / p.mb_per_rank) % p.world;
-      st_release_gpu(p.chunk_flags + srank * p.mb_per_rank + it % p.mb_per_rank, p.epoch);
+      st_release_gpu(p.chunk_flags + srank * p.mb_per_rank + it % p.mb_per_rank, epoch);
     }
   }
+}
+
+// ---------------------------------------------------------------- side gather (bulk overlap)
+// Run by warp 0 of every copy CTA after the gated gather.  A piece is up to 32 KB of whole rows of one
+// rank's staged operand: one bulk load brings it into a shared-memory slot, then every lane stores the
+// rows it owns to their (strided) place in the local gathered operand.  Scale chunks travel the same way
+// as single-row pieces.
+__device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars, uint32_t epoch) {
+  const SideGather& g = p.side;
+  if (g.rows <= 0) return;
+  const int lane = threadIdx.x;  // caller guarantees threadIdx.x < 32
+  if (lane == 0) {
+    for (int i = 0; i < kCopySlots; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  const int rpp = kCopyPiece / g.row_bytes;                 // rows per piece
+  const int data_pieces = (g.rows + rpp - 1) / rpp;
+  const int sf_pieces = g.sf_chunk > 0 ? g.row_tiles : 0;
+  const int per_rank = data_pieces + sf_pieces;
+  const int items = p.world * per_rank;
+  const int total = cta < items ? (items - cta + p.copy_ctas - 1) / p.copy_ctas : 0;
+  const long long data_bytes = static_cast<long long>(g.rows) * g.row_bytes;
+
+  // item q of this CTA -> source pointer, rows, bytes per row, destination of row 0, destination pitch
+  auto piece = [&](int q, const uint8_t*& src, uint8_t*& dst, int& nrows, int& rbytes, long long& pitch, int& srank) {
+    const int it = cta + q * p.copy_ctas;
+    srank = (p.rank + 1 + it / per_rank) % p.world;  // own piece last
+    const int j = it % per_rank;
+    if (j < data_pieces) {
+      const int r0 = j * rpp;
+      nrows = g.rows - r0 < rpp ? g.rows - r0 : rpp;
+      rbytes = g.row_bytes;
+      src = g.src[srank] + static_cast<long long>(r0) * g.row_bytes;
+      dst = g.dst + static_cast<long long>(srank) * g.dst_piece_off + static_cast<long long>(r0) * g.dst_pitch;
+      pitch = g.dst_pitch;
+    } else {
+      const int t = j - data_pieces;
+      nrows = 1;
+      rbytes = g.sf_chunk;
+      src = g.src[srank] + data_bytes + static_cast<long long>(t) * g.sf_chunk;
+      dst = g.dst_sf + (static_cast<long long>(t) * p.world + srank) * g.sf_chunk;
+      pitch = g.sf_chunk;
+    }
+  };
+  int last_rank_ok = -1;
+  auto issue_load = [&](int q) {  // lane 0 only
+    const uint8_t* src; uint8_t* dst; int nrows, rbytes, srank; long long pitch;
+    piece(q, src, dst, nrows, rbytes, pitch, srank);
+    if (srank != p.rank && srank != last_rank_ok) {
+      if (!wait_flag_ge(p.ready[p.rank] + srank, epoch)) {
+        if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
+      }
+      last_rank_ok = srank;
+    }
+    const int slot = q % kCopySlots;
+    const uint32_t bytes = static_cast<uint32_t>(nrows) * rbytes;
+    mbar_expect_tx(&bars[slot], bytes);
+    bulk_load_1d(smem + slot * kCopyPiece, src, bytes, &bars[slot]);
+  };
+  int issued = 0;
+  if (lane == 0)
+    for (; issued < total && issued < kCopySlots - 1; ++issued) issue_load(issued);
+  issued = __shfl_sync(0xffffffffu, issued, 0);
+  bool ok = true;
+  for (int q = 0; q < total && ok; ++q) {
+    const int slot = q % kCopySlots;
+    const uint32_t phase = (q / kCopySlots) & 1;
+    if (!__all_sync(0xffffffffu, mbar_wait(&bars[slot], phase))) {
+      if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
+      ok = false;
+      break;
+    }
+    const uint8_t* src; uint8_t* dst; int nrows, rbytes, srank; long long pitch;
+    piece(q, src, dst, nrows, rbytes, pitch, srank);
+    if (pitch == rbytes) {
+      if (lane == 0) bulk_store_1d(dst, smem + slot * kCopyPiece, static_cast<uint32_t>(nrows) * rbytes);
+    } else {
+      for (int r = lane; r < nrows; r += 32)
+        bulk_store_1d(dst + static_cast<long long>(r) * pitch, smem + slot * kCopyPiece + r * rbytes, rbytes);
+    }
+    tma_store_commit();
+    if (issued < total) {
+      // the slot of piece `issued` was last read by the stores of piece q - 1: every lane waits for its own
+      tma_store_wait_read<1>();
+      __syncwarp();
+      if (lane == 0) issue_load(issued);
+      ++issued;
+    }
+  }
+  tma_store_wait<0>();
+  __syncwarp();
 }
 
 // ---------------------------------------------------------------- reduce tail (reduce-scatter)
@@ -190,9 +299,9 @@ __device__ __forceinline__ size_t stage_tile_offset(const CommParams& p, int src
 
 // Executed by the four epilogue warps (128 threads, named barrier 1) after their tile loop.
 template <typename T>
-__device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et) {
+__device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, uint32_t epoch) {
   const int items = p.mb_per_rank * p.num_n;
-  const uint32_t expected = p.epoch * static_cast<uint32_t>(p.num_n) * 2u;  // two half tiles per tile
+  const uint32_t expected = epoch * static_cast<uint32_t>(p.num_n) * 2u;  // two half tiles per tile
   const uint8_t* stage = p.stage[p.rank];
   T* out = reinterpret_cast<T*>(p.out);
   const int N = p.k.N;
@@ -269,7 +378,7 @@ struct CommSmem {
   static constexpr int kStages = MODE == kCommReduceScatter ? 3 : C::kStages;
   static constexpr int kBytes = kStages * C::kStageBytes + kStagingBytes + 1024 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory plan exceeds the per-CTA limit");
-  static_assert(kCopySlots * kCopyPiece <= kStages * C::kStageBytes || MODE != kCommAllGather,
+  static_assert(kCopySlots * kCopyPiece <= kStages * C::kStageBytes + kStagingBytes,
                 "copy ring must fit in front of the barriers");
 };
 
@@ -293,15 +402,22 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int lane = threadIdx.x & 31;
 
   int gemm_ctas = gridDim.x, gemm_cta = blockIdx.x;
-  if (MODE == kCommAllGather) {
+  if (p.copy_ctas > 0) {
     gemm_ctas = gridDim.x - p.copy_ctas;
     gemm_cta = blockIdx.x - p.copy_ctas;
     if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
-      copy_cta_loop(p, blockIdx.x, smem, bars);
+      const uint32_t ep = read_epoch(p);
+      if (warp == 0) {
+        copy_cta_loop(p, blockIdx.x, smem, bars, ep);  // publishes this rank's rows; gated gather (all-gather mode)
+        __syncwarp();
+        side_gather_loop(p, blockIdx.x, smem, bars + kCopySlots, ep);
+        if (lane == 0) cta_done(p, ep);
+      }
       return;  // copy CTAs never touch TMEM or the pipeline barriers
     }
   }
   const int num_k_blocks = (p.k.K + C::kBlockK - 1) / C::kBlockK;
+  const uint32_t epoch = read_epoch(p);
 
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_a);
@@ -337,7 +453,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = gemm_cta; ok && comm_tile(p, t, ti); t += gemm_ctas) {
         if (MODE == kCommAllGather && ti.mb / p.mb_per_rank != p.rank) {
           // rows of a peer: wait until a copy CTA has landed this 128-row block in local memory
-          if (!wait_ge_gpu(p.chunk_flags + ti.mb, p.epoch)) {
+          if (!wait_ge_gpu(p.chunk_flags + ti.mb, epoch)) {
             if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
           }
           fence_proxy_async_all();  // generic-proxy writes of the copy CTA -> TMA (async proxy) reads
@@ -568,8 +684,8 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (halves >= 1) red_release_sys_add(pending[(halves - 1) & 1], 1u);
         if (dbg) dbg[gemm_cta * 4 + 2] = gtimer();
       }
-      if (p.k.d_dtype == kBFloat16) reduce_tail<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et);
-      else reduce_tail<__half>(p, gemm_cta, gemm_ctas, et);
+      if (p.k.d_dtype == kBFloat16) reduce_tail<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et, epoch);
+      else reduce_tail<__half>(p, gemm_cta, gemm_ctas, et, epoch);
       if (dbg && et == 0) dbg[gemm_cta * 4 + 3] = gtimer();
     }
   }
@@ -580,6 +696,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
+  if (threadIdx.x == 0) cta_done(p, epoch);
 }
 
 template <int KIND, int MODE>
@@ -605,14 +722,26 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   k.idesc = make_idesc(KIND, g.a_dtype, g.b_dtype, BN, false, false);
   k.num_groups = 0;
   k.sf_k_tiles = KIND == kKindF16 ? 0 : ((g.K + 31) / 32 + 3) / 4;
-  p.mode = MODE; p.rank = a.rank; p.world = a.world; p.epoch = a.epoch;
+  p.mode = MODE; p.rank = a.rank; p.world = a.world; p.epoch_dev = a.epoch_dev; p.done_ctas = a.epoch_dev + 1;
   p.mb_per_rank = g.M / kBlockM / a.world;
   p.num_n = (g.N + BN - 1) / BN;
   const int sms = g.sm_count > 0 ? g.sm_count : device_sm_count();
-  int copy = MODE == kCommAllGather ? a.copy_ctas : 0;
-  if (copy < 1 && MODE == kCommAllGather) copy = 1;
+  const bool side = a.side.rows > 0;
+  int copy = (MODE == kCommAllGather || side) ? a.copy_ctas : 0;
+  if (copy < 1 && (MODE == kCommAllGather || side)) copy = 1;
   if (copy > sms / 2) copy = sms / 2;
   p.copy_ctas = copy;
+  p.side = a.side;
+  if (side) {
+    if (a.side.row_bytes <= 0 || a.side.row_bytes % 16 != 0 || a.side.row_bytes > kCopyPiece ||
+        a.side.sf_chunk % 16 != 0 || a.side.sf_chunk > kCopyPiece || a.side.dst == nullptr ||
+        a.side.dst_pitch % 16 != 0 || a.side.dst_piece_off % 16 != 0 ||
+        reinterpret_cast<uintptr_t>(a.side.dst) % 16 != 0 || (a.side.sf_chunk > 0 && a.side.dst_sf == nullptr))
+      return cudaErrorInvalidValue;
+    for (int r = 0; r < a.world; ++r)
+      if (a.side.src[r] == nullptr || a.ready[r] == nullptr || reinterpret_cast<uintptr_t>(a.side.src[r]) % 16 != 0)
+        return cudaErrorInvalidValue;
+  }
   for (int r = 0; r < kCommMaxRanks; ++r) {
     p.a_full[r] = a.a_full[r]; p.sfa_full[r] = a.sfa_full[r]; p.ready[r] = a.ready[r];
     p.stage[r] = a.stage[r]; p.tile_flags[r] = a.tile_flags[r];
@@ -636,7 +765,7 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
 
 cudaError_t comm_gemm(const CommGemmArgs& a, cudaStream_t stream) {
   const GemmArgs& g = a.g;
-  if (a.world < 2 || a.world > kCommMaxRanks) return cudaErrorInvalidValue;
+  if (a.world < 2 || a.world > kCommMaxRanks || a.epoch_dev == nullptr) return cudaErrorInvalidValue;
   if (g.M % (kBlockM * a.world) != 0 || g.N % 8 != 0 || g.K <= 0) return cudaErrorInvalidValue;
   if (g.d_dtype != kBFloat16 && g.d_dtype != kFloat16) return cudaErrorInvalidValue;
   const bool mx = g.sfa != nullptr;

@@ -21,11 +21,29 @@ namespace teb200 {
 constexpr int kCommMaxRanks = 8;
 enum CommMode : int { kCommNone = 0, kCommAllGather = 1, kCommReduceScatter = 2 };
 
+// Optional second all-gather carried out by copy CTAs of the same kernel while the GEMM runs (the
+// operand of the weight-gradient GEMM that follows: bulk overlap).  Every rank stages a piece of
+// `rows` rows x `row_bytes` bytes (contiguous) followed by `row_tiles` scale chunks of `sf_chunk`
+// bytes; piece s lands at dst + s * dst_piece_off with row pitch dst_pitch, its scale chunk t at
+// dst_sf + (t * world + s) * sf_chunk.  Consumers are later kernels of the stream (no flags).
+struct SideGather {
+  const uint8_t* src[kCommMaxRanks] = {};  // staged pieces of every rank (symmetric memory)
+  uint8_t* dst = nullptr;
+  uint8_t* dst_sf = nullptr;
+  int rows = 0;                  // 0: no side gather
+  int row_bytes = 0;             // multiple of 16, <= 32768
+  long long dst_pitch = 0, dst_piece_off = 0;
+  int row_tiles = 0, sf_chunk = 0;
+};
+
 struct CommGemmArgs {
   GemmArgs g;  // M = gathered rows; for all-gather g.a / g.sfa point at the LOCAL gathered buffer
   int mode = kCommNone;
   int rank = 0, world = 1;
-  uint32_t epoch = 0;  // 1, 2, 3, ... per call on this context (identical on all ranks)
+  // two local device words: [0] calls completed so far on this (context, buffer slot), identical on all
+  // ranks, advanced by the kernel itself (so launches recorded in a CUDA graph replay correctly);
+  // [1] scratch counter of finished CTAs, zero between launches
+  uint32_t* epoch_dev = nullptr;
   int copy_ctas = 8;
 
   // ---- all-gather: gathered buffers of every rank (index = rank), same layout everywhere
@@ -40,6 +58,8 @@ struct CommGemmArgs {
   uint8_t* stage[kCommMaxRanks] = {};       // stage[r] on rank r: [world][M/world][N] of d_dtype
   uint32_t* tile_flags[kCommMaxRanks] = {}; // tile_flags[r] on rank r: [world][M/world/128] counters
   void* out = nullptr;                      // local result [M/world, N], dtype d_dtype
+
+  SideGather side;  // needs `ready` (both modes) and copy_ctas >= 1
 };
 
 cudaError_t comm_gemm(const CommGemmArgs& args, cudaStream_t stream);

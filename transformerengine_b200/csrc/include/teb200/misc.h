@@ -25,10 +25,16 @@ struct AdamArgs {
   int grad_dtype = 2;      // lists: 0 = grad, 1 = param (model dtype), 2 = exp_avg, 3 = exp_avg_sq, 4 = master
   int param_dtype = 2;
   int state_dtype = 0;     // fp32 or bf16 moments
-  int has_master = 1;
+  int has_master = 1;      // 0: none, 1: fp32 master in list 4, 2: list 4 holds int16 remainders (the low 16 bits of
+                           // the fp32 value whose rounded high half is the bf16 parameter)
   float grad_scale = 1.f;  // gradients are multiplied by this (1/loss_scale, 1/accumulation steps)
   const float* inv_scale_dev = nullptr;  // optional device scalar multiplied into the gradient
   const int* noop = nullptr;             // skip the update when *noop != 0
+  // capturable mode: step count and learning rate live on the device, so a captured launch stays
+  // valid across replays (bias corrections are then computed in the kernel from *step_dev)
+  const int* step_dev = nullptr;
+  const float* lr_dev = nullptr;
+  int bias_correction = 1;
   int64_t chunk = 0;
 };
 cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nblocks, const AdamArgs& a, cudaStream_t s);

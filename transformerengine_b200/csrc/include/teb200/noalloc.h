@@ -7,14 +7,14 @@
 // component that is forbidden to grow the process' device footprint.  The
 // regular norm backward needs a scratch buffer for its two-stage reduction of
 // the weight gradient; here that scratch is a fixed array that lives inside the
-// library image on every GPU that loads it (kNoAllocScratchFloats * 4 bytes,
+// library image on every GPU that loads it (TEB200_NOALLOC_SCRATCH_FLOATS * 4 bytes,
 // held until the process exits).
 //
 // Rules of use:
 //   * The first call on a device looks up the device address of the scratch
 //     array; make that first call outside any stream capture.
 //   * Problem sizes whose scratch need, teb200_norm_bwd_noalloc_scratch_floats(R, C),
-//     exceeds kNoAllocScratchFloats are rejected with cudaErrorInvalidValue and a
+//     exceeds TEB200_NOALLOC_SCRATCH_FLOATS are rejected with cudaErrorInvalidValue and a
 //     message on stderr; nothing is launched.
 //   * All calls share the one array.  Two calls that may run at the same time on
 //     one GPU (different streams) race on it; serialize them.  Nothing in the

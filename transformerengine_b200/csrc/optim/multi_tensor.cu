@@ -34,10 +34,47 @@ __global__ void __launch_bounds__(NT) adam_kernel(const MultiTensorTable t, cons
   P* p = static_cast<P*>(t.ptr[1][ti]);
   S* m = static_cast<S*>(t.ptr[2][ti]);
   S* v = static_cast<S*>(t.ptr[3][ti]);
-  float* master = a.has_master ? static_cast<float*>(t.ptr[4][ti]) : nullptr;
+  float* master = a.has_master == 1 ? static_cast<float*>(t.ptr[4][ti]) : nullptr;
+  int16_t* rem = a.has_master == 2 ? static_cast<int16_t*>(t.ptr[4][ti]) : nullptr;
   const float gs = a.grad_scale * (a.inv_scale_dev ? *a.inv_scale_dev : 1.f);
   const float b1 = a.beta1, b2 = a.beta2;
-  const float rbc1 = 1.f / a.bias_correction1, rbc2 = 1.f / a.bias_correction2;
+  float rbc1 = 1.f / a.bias_correction1, rbc2 = 1.f / a.bias_correction2;
+  if (a.step_dev != nullptr && a.bias_correction) {
+    const float st = static_cast<float>(*a.step_dev);
+    rbc1 = 1.f / (1.f - powf(b1, st));
+    rbc2 = 1.f / (1.f - powf(b2, st));
+  }
+  const float lr = a.lr_dev != nullptr ? *a.lr_dev : a.lr;
+  if (rem != nullptr) {
+    // bf16 parameter + 16-bit remainder = the fp32 value, split so that the parameter is the fp32 value
+    // rounded half up: a negative remainder means the high half was incremented
+    if constexpr (sizeof(P) == 2) {
+      uint16_t* pb = reinterpret_cast<uint16_t*>(p);
+      for (int64_t i = start + threadIdx.x; i < end; i += NT) {
+        const int16_t r = rem[i];
+        uint32_t hi = pb[i];
+        if (r < 0) hi -= 1u;
+        float w = __uint_as_float((hi << 16) | static_cast<uint16_t>(r));
+        float gr = ldf(g, i) * gs;
+        float mv = ldf(m, i), vv = ldf(v, i);
+        if (!a.adamw) gr += a.weight_decay * w;
+        mv = b1 * mv + (1.f - b1) * gr;
+        vv = b2 * vv + (1.f - b2) * gr * gr;
+        float upd = (mv * rbc1) / (sqrtf(vv * rbc2) + a.eps);
+        if (a.adamw) upd += a.weight_decay * w;
+        w -= lr * upd;
+        const uint32_t u = __float_as_uint(w);
+        const int16_t nr = static_cast<int16_t>(u & 0xffffu);
+        uint32_t nh = u >> 16;
+        if (nr < 0) nh += 1u;
+        m[i] = static_cast<S>(mv);
+        v[i] = static_cast<S>(vv);
+        rem[i] = nr;
+        pb[i] = static_cast<uint16_t>(nh);
+      }
+    }
+    return;
+  }
   // 4 elements per thread per iteration; tensors are 16-byte aligned and chunks are multiples of 4
   for (int64_t i = start + threadIdx.x * 4; i < end; i += NT * 4) {
     float gv[4], pv[4], mv[4], vv[4];
@@ -82,7 +119,7 @@ __global__ void __launch_bounds__(NT) adam_kernel(const MultiTensorTable t, cons
         const float denom = sqrtf(vv[k] * rbc2) + a.eps;
         float upd = (mv[k] * rbc1) / denom;
         if (a.adamw) upd += a.weight_decay * pv[k];
-        pv[k] -= a.lr * upd;
+        pv[k] -= lr * upd;
       }
     }
     if (cnt == 4) {

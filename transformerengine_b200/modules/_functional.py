@@ -88,29 +88,79 @@ def _comm_kind(a_op, b_op):
     return None
 
 
-def fused_all_gather_gemm(x_local, w_op, bias, cfg: LinearConfig, quantizer, out_dtype, tag: str):
+def _side_pack(t, world: int):
+    """Describe ``t`` (this rank's rows of a wgrad operand) for the side gather of a fused kernel.
+    Returns (spec, data, scales, rebuild) or None when the layout is not covered."""
+    from ..parallel.comm_gemm import SideSpec
+
+    if isinstance(t, MXFP8TensorStorage):
+        cd, cs = t._columnwise_data, t._columnwise_scale_inv
+        if cd is None or not cd.is_cuda:
+            return None
+        C, R = cd.shape
+        if R % 128 != 0 or R > 32768:
+            return None
+
+        def rebuild(gd, gsf, t=t, C=C, R=R):
+            return MXFP8TensorStorage(rowwise_data=None, rowwise_scale_inv=None, columnwise_data=gd.view(C, world * R),
+                                      columnwise_scale_inv=gsf, fp8_dtype=t._fp8_dtype, quantizer=t._quantizer,
+                                      shape=(world * R, C), dtype=t._dtype)
+
+        return SideSpec.for_mxfp8_columnwise(C, R), cd, cs, rebuild
+    if isinstance(t, torch.Tensor) and not _is_q(t) and t.is_cuda and t.dim() == 2 and t.is_contiguous() \
+            and t.dtype in (torch.bfloat16, torch.float16):
+        R, K = t.shape
+        rb = K * t.element_size()
+        if rb % 16 != 0 or rb > 32768:
+            return None
+
+        def rebuild(gd, gsf, dt=t.dtype, R=R, K=K):
+            return gd.view(dt).reshape(world * R, K)
+
+        return SideSpec.for_rows(R, rb), t, None, rebuild
+    return None
+
+
+def fused_all_gather_gemm(x_local, w_op, bias, cfg: LinearConfig, quantizer, out_dtype, tag: str, *,
+                          columnwise: bool = False, side=None):
     """Sequence-parallel all-gather of ``x_local`` fused into ``gather(x) @ w^T``.
-    Returns None when this operand pair is not covered (caller falls back to NCCL + GEMM)."""
+
+    ``columnwise`` also produces the column-wise copy of the local rows when they are quantized here
+    (the caller keeps it for the weight gradient).  ``side`` is this rank's piece of a second operand
+    that the same kernel gathers next to the GEMM (``_side_pack`` layouts).
+    Returns None when this operand pair is not covered (caller falls back to NCCL + GEMM), else
+    ``(out, x_local as used, gathered side or None)``."""
     from ..parallel import comm_gemm
 
-    xq = quantize_for_gemm(x_local, quantizer, True, False) if not _is_q(x_local) else x_local
+    xq = quantize_for_gemm(x_local, quantizer, True, columnwise) if not _is_q(x_local) else x_local
     a_op = as_operand(xq, "rowwise")
     kind = _comm_kind(a_op, w_op)
     if kind is None or out_dtype not in (torch.bfloat16, torch.float16):
         return None
     T = a_op.rows * cfg.tp_size
+    pack = _side_pack(side, cfg.tp_size) if side is not None else None
     ctx = comm_gemm.get_all_gather_gemm(f"{cfg.name}.{tag}", cfg.tp_group, T, a_op.k, kind == "mx",
-                                        a_op.data.dtype)
-    return ctx(a_op, w_op, bias=bias, out_dtype=out_dtype)
+                                        a_op.data.dtype, side=pack[0] if pack else None)
+    if pack is None:
+        return ctx(a_op, w_op, bias=bias, out_dtype=out_dtype), xq, None
+    out, gd, gsf = ctx(a_op, w_op, bias=bias, out_dtype=out_dtype, side=(pack[1], pack[2]))
+    return out, xq, pack[3](gd, gsf)
 
 
-def fused_gemm_reduce_scatter(a_op, b_op, bias, cfg: LinearConfig, out_dtype, tag: str):
+def fused_gemm_reduce_scatter(a_op, b_op, bias, cfg: LinearConfig, out_dtype, tag: str, *, side=None):
+    """``reduce_scatter(a @ b^T)`` in one kernel; ``side`` as in :func:`fused_all_gather_gemm`.
+    Returns None when not covered, else ``(out, gathered side or None)``."""
     from ..parallel import comm_gemm
 
     if _comm_kind(a_op, b_op) is None or out_dtype not in (torch.bfloat16, torch.float16):
         return None
-    ctx = comm_gemm.get_gemm_reduce_scatter(f"{cfg.name}.{tag}", cfg.tp_group, a_op.rows, b_op.rows, out_dtype)
-    return ctx(a_op, b_op, bias=bias)
+    pack = _side_pack(side, cfg.tp_size) if side is not None else None
+    ctx = comm_gemm.get_gemm_reduce_scatter(f"{cfg.name}.{tag}", cfg.tp_group, a_op.rows, b_op.rows, out_dtype,
+                                            side=pack[0] if pack else None)
+    if pack is None:
+        return ctx(a_op, b_op, bias=bias), None
+    out, gd, gsf = ctx(a_op, b_op, bias=bias, side=(pack[1], pack[2]))
+    return out, pack[3](gd, gsf)
 
 
 def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False):
@@ -120,9 +170,9 @@ def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False
     fuse_bias = bias is not None and not (cfg.parallel_mode == "row" and cfg.tp_size > 1)
     a, b = as_operand(x, "rowwise"), as_operand(w, "rowwise")
     if cfg.parallel_mode == "row" and not gelu and _fused_comm_ok(cfg, a.rows // max(cfg.tp_size, 1), x, w):
-        out = fused_gemm_reduce_scatter(a, b, bias, cfg, out_dtype, "fprop")
-        if out is not None:
-            return out, None
+        res = fused_gemm_reduce_scatter(a, b, bias, cfg, out_dtype, "fprop")
+        if res is not None:
+            return res[0], None
     if gelu:
         aux = torch.empty(a.rows, b.rows, dtype=out_dtype, device=a.data.device)
         out = gemm_nt(a, b, out_dtype=out_dtype, bias=bias if fuse_bias else None, epilogue=ops.gemm.EPI_GELU, aux=aux)
@@ -141,18 +191,18 @@ def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False
 def row_parallel_grad_output(dy_local, w, cfg: LinearConfig, quantizer, need_dgrad: bool, need_wgrad: bool, out_dtype):
     """Backward of a row-parallel layer under sequence parallelism: grad_output arrives sharded on
     rows.  Returns (gathered grad_output for the wgrad / dgrad GEMMs, dx or None).  With fused
-    collectives the all-gather runs inside the dgrad GEMM and only the columnwise copy (wgrad
-    operand) is gathered by NCCL."""
-    import copy as _copy
-
+    collectives the all-gather runs inside the dgrad GEMM, whose copy CTAs also gather the columnwise
+    copy (the wgrad operand) while the tiles are computed."""
     if need_dgrad and _fused_comm_ok(cfg, dy_local.shape[0], dy_local):
         dq = quantize_for_gemm(dy_local, quantizer, True, need_wgrad)
         w_op = as_operand(w, "columnwise")
         if _comm_kind(as_operand(dq, "rowwise"), w_op) is not None:
-            dx = fused_all_gather_gemm(dq, w_op, None, cfg, None, out_dtype, "dgrad")
-            total = None
-            if need_wgrad:
+            side = dq if need_wgrad and _side_pack(dq, cfg.tp_size) is not None else None
+            dx, _, total = fused_all_gather_gemm(dq, w_op, None, cfg, None, out_dtype, "dgrad", side=side)
+            if need_wgrad and total is None:
                 if _is_q(dq):
+                    import copy as _copy
+
                     col = _copy.copy(dq)
                     col.update_usage(rowwise_usage=False)
                     total = D.gather_mxfp8_along_first_dim(col, cfg.tp_group)
@@ -162,14 +212,19 @@ def row_parallel_grad_output(dy_local, w, cfg: LinearConfig, quantizer, need_dgr
     return gather_input(dy_local, cfg, quantizer, need_dgrad, need_wgrad), None
 
 
-def linear_dgrad(dy, w, cfg: LinearConfig, out_dtype, *, async_comm: bool = False):
+def linear_dgrad(dy, w, cfg: LinearConfig, out_dtype, *, async_comm: bool = False, side=None):
     """``dx = dy @ W``; column-parallel layers then reduce-scatter / all-reduce.
-    Returns (dx2d, comm handle or None)."""
+
+    ``side``: this rank's rows of the layer input that the weight gradient needs gathered (sequence
+    parallel column-parallel layers); the fused kernel gathers it while it computes.
+    Returns (dx2d, comm handle or None, gathered side or None)."""
     a, b = as_operand(dy, "rowwise"), as_operand(w, "columnwise")
     if cfg.parallel_mode == "column" and _fused_comm_ok(cfg, a.rows // max(cfg.tp_size, 1), dy):
-        dx = fused_gemm_reduce_scatter(a, b, None, cfg, out_dtype, "dgrad")
-        if dx is not None:
-            return dx, None
+        if side is not None and _side_pack(side, cfg.tp_size) is None:
+            side = None
+        res = fused_gemm_reduce_scatter(a, b, None, cfg, out_dtype, "dgrad", side=side)
+        if res is not None:
+            return res[0], None, res[1]
     dx = gemm_nt(a, b, out_dtype=out_dtype)
     h = None
     if cfg.parallel_mode == "column" and cfg.tp_size > 1:
@@ -177,7 +232,17 @@ def linear_dgrad(dy, w, cfg: LinearConfig, out_dtype, *, async_comm: bool = Fals
             dx, h = D.reduce_scatter_along_first_dim(dx, cfg.tp_group, async_op=async_comm)
         else:
             dx, h = D.allreduce(dx, cfg.tp_group, async_op=async_comm)
-    return dx, h
+    return dx, h, None
+
+
+def gathered_wgrad_input(keep_x, total, cfg: LinearConfig, quantizer):
+    """The full-sequence wgrad operand of a sequence-parallel column-parallel layer: what the fused
+    dgrad kernel gathered (quantized now if it travelled in 16 bits), else an NCCL gather."""
+    if total is None:
+        return gather_input(keep_x, cfg, quantizer, False, True)
+    if not _is_q(total) and quantizer is not None:
+        return quantize_for_gemm(total, quantizer, False, True)
+    return total
 
 
 def linear_wgrad(dy, x, weight: torch.Tensor, cfg: LinearConfig):

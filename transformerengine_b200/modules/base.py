@@ -65,15 +65,29 @@ class _SafeUnpickler(pickle.Unpickler):
     _TORCH = {("torch._utils", "_rebuild_tensor_v2"), ("torch._utils", "_rebuild_tensor"),
               ("torch", "Size"), ("torch", "device"), ("torch", "dtype"),
               ("torch.serialization", "_get_layout"), ("torch._tensor", "_rebuild_from_type_v2"),
-              ("torch.storage", "_load_from_bytes"), ("collections", "OrderedDict"),
+              ("collections", "OrderedDict"),
               ("_codecs", "encode"), ("numpy.core.multiarray", "_reconstruct"), ("numpy", "ndarray"),
               ("numpy", "dtype"), ("numpy.core.multiarray", "scalar"), ("numpy._core.multiarray", "scalar"),
               ("numpy._core.multiarray", "_reconstruct")}
 
+    # the only names of the recipe module a checkpoint may reference (classes and enums, no functions)
+    _RECIPE_NAMES = {"Recipe", "DelayedScaling", "Float8CurrentScaling", "MXFP8BlockScaling", "Float8BlockScaling",
+                     "NVFP4BlockScaling", "CustomRecipe", "Format", "_FormatHelper", "MMParams", "QParams"}
+
+    @staticmethod
+    def _storage_from_bytes(b):
+        """Stand-in for ``torch.storage._load_from_bytes`` (which unpickles without restriction):
+        the nested archive is read with the weights-only loader, which refuses arbitrary globals."""
+        return torch.load(io.BytesIO(b), weights_only=True)
+
     def find_class(self, module, name):
         if module in ("transformer_engine.common.recipe", "transformerengine_b200.common.recipe"):
+            if name not in self._RECIPE_NAMES:
+                raise pickle.UnpicklingError(f"refusing to load {module}.{name} from _extra_state")
             from ..common import recipe as r
             return getattr(r, name)
+        if (module, name) == ("torch.storage", "_load_from_bytes"):
+            return self._storage_from_bytes
         if module == "builtins" and name in self._BUILTINS:
             return super().find_class(module, name)
         if (module, name) in self._TORCH:
@@ -93,6 +107,7 @@ class TransformerEngineBaseModule(torch.nn.Module):
         self.quantizers: Dict[str, List[Optional[Quantizer]]] = {"scaling_fwd": [], "scaling_bwd": []}
         self._states: Dict[str, Optional[RecipeState]] = {"scaling_fwd": None, "scaling_bwd": None}
         self._weight_cache: Dict[str, Any] = {}
+        self._recompute_scales: List[torch.Tensor] = []  # forward scales of checkpointed runs awaiting recompute
         self.tp_group = None
         self.tp_size = 1
         self.sequence_parallel = False
@@ -149,8 +164,28 @@ class TransformerEngineBaseModule(torch.nn.Module):
 
     def prepare_forward(self, num_gemms: int = 1) -> None:
         self.init_fp8_metadata(num_gemms)
-        if self.fp8 and isinstance(self._states["scaling_fwd"], DelayedScalingRecipeState):
-            FP8GlobalStateManager.add_pending(self._states["scaling_fwd"], forward=True)
+        st = self._states["scaling_fwd"]
+        if self.fp8 and isinstance(st, DelayedScalingRecipeState):
+            from ..parallel import distributed as D
+
+            if D.is_in_recompute() and self._recompute_scales:
+                # second run of a checkpointed region: quantize with the scales of the first run, and put
+                # the live scales and the amax slot back afterwards (the recompute records nothing new)
+                old = self._recompute_scales.pop(0)
+                live_scale, live_amax = st.scale.clone(), st.amax_history[0].clone()
+                st.scale.copy_(old)
+
+                def restore(st=st, live_scale=live_scale, live_amax=live_amax):
+                    st.scale.copy_(live_scale)
+                    st.amax_history[0].copy_(live_amax)
+
+                D.add_recompute_restore(restore)
+                if torch.is_grad_enabled():
+                    FP8GlobalStateManager.add_pending(self._states["scaling_bwd"], forward=False)
+                return
+            if D.in_checkpoint_forward():
+                self._recompute_scales.append(st.scale.clone())
+            FP8GlobalStateManager.add_pending(st, forward=True)
             if torch.is_grad_enabled():
                 FP8GlobalStateManager.add_pending(self._states["scaling_bwd"], forward=False)
 

@@ -98,27 +98,34 @@ class _LayerNormLinear(torch.autograd.Function):
         grad_on = any(ctx.needs_input_grad)
         need_wgrad = weight.requires_grad and grad_on
         sp_gather = cfg.parallel_mode == "column" and cfg.sequence_parallel and cfg.tp_size > 1
+        # sequence parallel with fused collectives and MXFP8: the norm writes this rank's rows quantized
+        # (both copies in one pass), the all-gather moves FP8 and the columnwise copy is kept for wgrad
+        sp_fused_q = sp_gather and isinstance(in_q, F.MXFP8Quantizer) and F._fused_comm_ok(cfg, x2d.shape[0], x2d) \
+            and x2d.shape[0] % 128 == 0
         if in_q is not None:
-            in_q.set_usage(rowwise=True, columnwise=need_wgrad and not sp_gather)
+            in_q.set_usage(rowwise=True, columnwise=need_wgrad and (not sp_gather or sp_fused_q))
             in_q.internal = True
         ln_hp, ln_q, mu, rs = ops.norm_fwd(x2d, ln_w, ln_b, module.eps, module.zero_centered_gamma,
                                            module.normalization == "LayerNorm",
-                                           quantizer=in_q if not sp_gather else None,
-                                           want_hp=return_ln_out or in_q is None or sp_gather)
+                                           quantizer=in_q if (not sp_gather or sp_fused_q) else None,
+                                           want_hp=return_ln_out or in_q is None or (sp_gather and not sp_fused_q))
         out = None
         ln_total = None
+        ln_local = ln_q if (sp_fused_q and ln_q is not None) else ln_hp
         if sp_gather:
-            if F._fused_comm_ok(cfg, ln_hp.shape[0], ln_hp):
-                out = F.fused_all_gather_gemm(ln_hp, F.as_operand(wq, "rowwise"), bias, cfg, in_q,
-                                              cfg.activation_dtype, "fprop")
+            if F._fused_comm_ok(cfg, x2d.shape[0], x2d):
+                res = F.fused_all_gather_gemm(ln_local, F.as_operand(wq, "rowwise"), bias, cfg, in_q,
+                                              cfg.activation_dtype, "fprop", columnwise=need_wgrad)
+                if res is not None:
+                    out, ln_local = res[0], res[1]
             if out is None:
-                ln_total = F.gather_input(ln_hp, cfg, in_q, True, need_wgrad)
+                ln_total = F.gather_input(ln_local, cfg, in_q, True, need_wgrad)
         else:
             ln_total = ln_q if ln_q is not None else ln_hp
         if out is None:
             out, _ = F.linear_fprop(ln_total, wq, bias, cfg, cfg.activation_dtype)
         if grad_on:
-            keep = (ln_hp if sp_gather else ln_total) if need_wgrad else None
+            keep = (ln_local if sp_gather else ln_total) if need_wgrad else None
             if F._is_q(keep) and keep.get_usages()["columnwise"]:
                 keep.update_usage(rowwise_usage=False)
             ctx.wq = wq if F._is_q(wq) else None  # cached object shared across calls: not stripped
@@ -152,13 +159,14 @@ class _LayerNormLinear(torch.autograd.Function):
         go_q = module.get_quantizer(False, 0) if ctx.fp8 else None
         db = F.bias_grad(dy2d, bias.dtype) if bias is not None else None
         dyq = F.quantize_for_gemm(dy2d, go_q, True, ctx.requires_wgrad)
-        dln, h = F.linear_dgrad(dyq, w_use, cfg, cfg.activation_dtype, async_comm=True)
+        dln, h, x_total = F.linear_dgrad(dyq, w_use, cfg, cfg.activation_dtype, async_comm=True,
+                                         side=keep if (ctx.sp_gather and ctx.requires_wgrad) else None)
         dw = None
         if ctx.requires_wgrad:
             xw = keep
             if ctx.sp_gather:
                 in_q = module.get_quantizer(True, 0) if ctx.fp8 else None
-                xw = F.gather_input(keep, cfg, in_q, False, True)
+                xw = F.gathered_wgrad_input(keep, x_total, cfg, in_q)
             dw = F.linear_wgrad(dyq, xw, weight, cfg)
         if h is not None:
             h.wait()

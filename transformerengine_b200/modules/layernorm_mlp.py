@@ -36,21 +36,27 @@ class _LayerNormMLP(torch.autograd.Function):
         grad = any(ctx.needs_input_grad)
         q_in1, q_in2 = module.get_quantizer(True, 0), module.get_quantizer(True, 3)
         sp = cfg1.sequence_parallel and cfg1.tp_size > 1
+        sp_fused_q = sp and isinstance(q_in1, F.MXFP8Quantizer) and F._fused_comm_ok(cfg1, x2d.shape[0], x2d) \
+            and x2d.shape[0] % 128 == 0
         if q_in1 is not None:
-            q_in1.set_usage(rowwise=True, columnwise=grad and not sp)
+            q_in1.set_usage(rowwise=True, columnwise=grad and (not sp or sp_fused_q))
             q_in1.internal = True
         is_ln = module.normalization == "LayerNorm"
         ln_hp, ln_q, mu, rs = ops.norm_fwd(x2d, ln_w, ln_b, module.eps, module.zero_centered_gamma, is_ln,
-                                           quantizer=q_in1 if not sp else None,
-                                           want_hp=return_ln_out or q_in1 is None or sp)
+                                           quantizer=q_in1 if (not sp or sp_fused_q) else None,
+                                           want_hp=return_ln_out or q_in1 is None or (sp and not sp_fused_q))
         act = module.activation
         fc1_out = None
         ln_total = None
+        ln_local = ln_q if (sp_fused_q and ln_q is not None) else ln_hp
         if sp:
-            if F._fused_comm_ok(cfg1, ln_hp.shape[0], ln_hp):
-                fc1_out = F.fused_all_gather_gemm(ln_hp, F.as_operand(w1q, "rowwise"), fc1_b, cfg1, q_in1, adt, "fprop")
+            if F._fused_comm_ok(cfg1, x2d.shape[0], x2d):
+                res = F.fused_all_gather_gemm(ln_local, F.as_operand(w1q, "rowwise"), fc1_b, cfg1, q_in1, adt, "fprop",
+                                              columnwise=grad)
+                if res is not None:
+                    fc1_out, ln_local = res[0], res[1]
             if fc1_out is None:
-                ln_total = F.gather_input(ln_hp, cfg1, q_in1, True, grad)
+                ln_total = F.gather_input(ln_local, cfg1, q_in1, True, grad)
         else:
             ln_total = ln_q if ln_q is not None else ln_hp
         if fc1_out is None:
@@ -62,7 +68,7 @@ class _LayerNormMLP(torch.autograd.Function):
         act_in = act_q if act_q is not None else act_hp
         out, _ = F.linear_fprop(act_in, w2q, fc2_b, cfg2, adt)
         if grad:
-            keep_ln = ln_hp if sp else ln_total
+            keep_ln = ln_local if sp else ln_total
             if F._is_q(keep_ln) and keep_ln.get_usages()["columnwise"]:
                 keep_ln.update_usage(rowwise_usage=False)
             if F._is_q(act_in) and act_in.get_usages()["columnwise"]:
@@ -106,7 +112,7 @@ class _LayerNormMLP(torch.autograd.Function):
             dyq = F.quantize_for_gemm(dy2d, q_go2, True, True)
         # fc2 dgrad (row-parallel: no collective after dgrad) and wgrad
         if dact is None:
-            dact, _ = F.linear_dgrad(dyq, w2, cfg2, adt)
+            dact, _, _ = F.linear_dgrad(dyq, w2, cfg2, adt)
         dw2 = F.linear_wgrad(dyq, act_in, fc2_w, cfg2) if fc2_w.requires_grad else None
         # activation backward fused with quantization (+ fc1 bias gradient)
         if q_go1 is not None:
@@ -117,13 +123,14 @@ class _LayerNormMLP(torch.autograd.Function):
         dfc1 = dfc1_q if dfc1_q is not None else dfc1_hp
         if db1 is not None:
             db1 = db1.to(fc1_b.dtype)
-        dln, h = F.linear_dgrad(dfc1, w1, cfg1, adt, async_comm=True)
+        dln, h, x_total = F.linear_dgrad(dfc1, w1, cfg1, adt, async_comm=True,
+                                         side=keep_ln if (ctx.sp and fc1_w.requires_grad) else None)
         dw1 = None
         if fc1_w.requires_grad:
             xw = keep_ln
             if ctx.sp:
                 q_in1 = module.get_quantizer(True, 0) if ctx.fp8 else None
-                xw = F.gather_input(keep_ln, cfg1, q_in1, False, True)
+                xw = F.gathered_wgrad_input(keep_ln, x_total, cfg1, q_in1)
             dw1 = F.linear_wgrad(dfc1, xw, fc1_w, cfg1)
         if h is not None:
             h.wait()

@@ -33,8 +33,10 @@ class _Linear(torch.autograd.Function):
         if sp_col:
             save_x = x2d  # local rows; gathered again in backward for wgrad
             if F._fused_comm_ok(cfg, x2d.shape[0], x2d):
-                out = F.fused_all_gather_gemm(x2d, F.as_operand(weight_q, "rowwise"), bias, cfg, in_q,
-                                              cfg.activation_dtype, "fprop")
+                res = F.fused_all_gather_gemm(x2d, F.as_operand(weight_q, "rowwise"), bias, cfg, in_q,
+                                              cfg.activation_dtype, "fprop", columnwise=need_wgrad)
+                if res is not None:
+                    out, save_x = res[0], res[1]  # the quantized local rows carry the wgrad (columnwise) copy
             if out is None:
                 xq = F.gather_input(x2d, cfg, in_q, True, need_wgrad)
         else:
@@ -98,13 +100,15 @@ class _Linear(torch.autograd.Function):
                                                  cfg.activation_dtype)
         else:
             dyq = F.quantize_for_gemm(dy2d, go_q, ctx.requires_dgrad, ctx.requires_wgrad)
+        x_total = None
         if ctx.requires_dgrad and dx is None:
-            dx, h = F.linear_dgrad(dyq, w_use, cfg, cfg.activation_dtype, async_comm=True)
+            dx, h, x_total = F.linear_dgrad(dyq, w_use, cfg, cfg.activation_dtype, async_comm=True,
+                                            side=keep_x if (ctx.gathered_in_fwd and ctx.requires_wgrad) else None)
         if ctx.requires_wgrad:
             xw = keep_x
             if ctx.gathered_in_fwd:
                 in_q = module.get_quantizer(True, 0) if ctx.fp8 else None
-                xw = F.gather_input(keep_x, cfg, in_q, False, True)
+                xw = F.gathered_wgrad_input(keep_x, x_total, cfg, in_q)
             if ctx.dist_w:
                 full_grad = F.linear_wgrad(dyq, xw, w_full, cfg)
                 dw = DW.finalize_weight_grads(weight, [full_grad])[0]

@@ -1,5 +1,10 @@
 """Functional ops.  Each op runs a hand-written sm_100a kernel for CUDA tensors and
-the pure-PyTorch reference for CPU tensors."""
+the pure-PyTorch reference for CPU tensors.
+
+The reference publishes its operation fuser under this name (``te.ops.Sequential``,
+``te.ops.BasicLinear``, ... ``pytorch/ops/__init__.py``); those names resolve here too and
+forward to :mod:`transformerengine_b200.fusible`.  The functional layer is also importable as
+``transformerengine_b200.functional``."""
 from . import _ext
 from .quantize import (amax, quantize_fp8, dequantize_fp8, quantize_mxfp8, dequantize_mxfp8, quantize_nvfp4,
                        dequantize_nvfp4, swizzle_scales, unswizzle_scales)
@@ -26,3 +31,17 @@ def check_status(device=None) -> None:
         names = {1: "producer wait", 2: "MMA wait", 3: "epilogue wait", 4: "peer flag wait", 5: "store wait",
                  6: "bad argument"}
         raise RuntimeError(f"device kernel reported status {code} ({names.get(code, 'unknown')})")
+
+
+def __getattr__(name):
+    """Fuser names (``Sequential``, ``BasicLinear``, ``FusibleOperation`` ...) looked up lazily: the fuser
+    imports the modules, which import this package."""
+    if name.startswith("__"):
+        raise AttributeError(name)
+    from .. import fusible
+
+    if name in ("basic", "fused"):  # reference sub-packages: te.ops.basic.Bias, te.ops.fused.*
+        return fusible
+    if hasattr(fusible, name):
+        return getattr(fusible, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

@@ -150,6 +150,10 @@ def gemm_nt(
             out.zero_()
         return out
     if _ext.use_cuda(a.data):
+        if any(o.kind == "hp" and o.data.dtype in (torch.float32, torch.float64) for o in (a, b)):
+            # fp32 operands keep fp32 math (the tcgen05 kernels take 16-bit and narrower inputs and would
+            # round them to bf16): library matmul in fp32, same epilogue semantics as the oracle
+            return _gemm_ref(a, b, out, bias, accumulate, epilogue, aux, alpha, group_offsets, num_groups)
         return _gemm_cuda(a, b, out, bias, accumulate, epilogue, aux, alpha, group_offsets, num_groups, sm_count)
     return _gemm_ref(a, b, out, bias, accumulate, epilogue, aux, alpha, group_offsets, num_groups)
 

@@ -160,24 +160,38 @@ def _filter_empty(lists):
 
 
 def multi_tensor_adam(lists: Sequence[List[torch.Tensor]], lr, beta1, beta2, eps, step, adamw=True,
-                      bias_correction=True, weight_decay=0.0, grad_scale=1.0, inv_scale=None, noop=None):
-    """lists = [grads, params, exp_avg, exp_avg_sq (, master fp32)]; updates in place."""
+                      bias_correction=True, weight_decay=0.0, grad_scale=1.0, inv_scale=None, noop=None,
+                      remainders: bool = False):
+    """lists = [grads, params, exp_avg, exp_avg_sq (, master fp32 | int16 remainders)]; updates in place.
+
+    ``step`` and ``lr`` may be device tensors (int32 / fp32 scalars): the kernel then reads them at run
+    time, which keeps a launch captured in a CUDA graph valid for later steps.  With ``remainders`` the
+    fifth list holds the low 16 bits of each fp32 weight and the bf16 parameter is its rounded high half
+    (reference: ``store_param_remainders``, ``pytorch/optimizers/fused_adam.py:74-149``)."""
     lists = _filter_empty(lists)
     if not lists[0]:
         return
+    step_t = step if isinstance(step, torch.Tensor) else None
+    lr_t = lr if isinstance(lr, torch.Tensor) else None
     if _ext.use_cuda(lists[0][0]):
-        _ext.get().multi_tensor_adam([list(l) for l in lists], lr, beta1, beta2, eps, int(step), adamw,
-                                     bias_correction, weight_decay, grad_scale, inv_scale, noop, MT_CHUNK)
+        _ext.get().multi_tensor_adam([list(l) for l in lists], 0.0 if lr_t is not None else float(lr), beta1, beta2,
+                                     eps, 1 if step_t is not None else int(step), adamw, bias_correction,
+                                     weight_decay, grad_scale, inv_scale, noop, MT_CHUNK, step_t, lr_t, remainders)
         return
     if noop is not None and int(noop.item()) != 0:
         return
+    step = int(step_t.item()) if step_t is not None else step
+    lr = float(lr_t.item()) if lr_t is not None else lr
     bc1 = 1 - beta1 ** step if bias_correction else 1.0
     bc2 = 1 - beta2 ** step if bias_correction else 1.0
     gs = grad_scale * (float(inv_scale.item()) if inv_scale is not None else 1.0)
-    has_master = len(lists) == 5
+    has_master = len(lists) == 5 and not remainders
     for i in range(len(lists[0])):
         g = lists[0][i].float() * gs
-        p = lists[4][i] if has_master else lists[1][i].float()
+        if remainders:
+            p = join_param_remainder(lists[1][i], lists[4][i])
+        else:
+            p = lists[4][i] if has_master else lists[1][i].float()
         m, v = lists[2][i].float(), lists[3][i].float()
         if not adamw:
             g = g + weight_decay * p
@@ -189,9 +203,28 @@ def multi_tensor_adam(lists: Sequence[List[torch.Tensor]], lr, beta1, beta2, eps
         pn = p - lr * upd
         lists[2][i].copy_(m)
         lists[3][i].copy_(v)
+        if remainders:
+            hi, lo = split_param_remainder(pn)
+            lists[1][i].copy_(hi)
+            lists[4][i].copy_(lo)
+            continue
         if has_master:
             lists[4][i].copy_(pn)
         lists[1][i].copy_(pn)
+
+
+def split_param_remainder(w: torch.Tensor):
+    """fp32 -> (bf16 parameter, int16 remainder): the remainder is the low half of the fp32 bits and the
+    parameter the high half, incremented when the remainder is negative (round half up)."""
+    u = w.contiguous().view(torch.int32)
+    lo = (u & 0xFFFF).to(torch.int16)  # wraps to the signed low half
+    hi = (u >> 16) + (lo < 0).to(torch.int32)
+    return hi.to(torch.int16).view(torch.bfloat16), lo
+
+
+def join_param_remainder(p_bf16: torch.Tensor, rem: torch.Tensor) -> torch.Tensor:
+    hi = p_bf16.contiguous().view(torch.int16).to(torch.int32) - (rem < 0).to(torch.int32)
+    return ((hi << 16) | (rem.to(torch.int32) & 0xFFFF)).view(torch.float32)
 
 
 def multi_tensor_sgd(lists, lr, momentum=0.0, dampening=0.0, weight_decay=0.0, nesterov=False, first_run=False,

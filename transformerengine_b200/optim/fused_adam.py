@@ -28,10 +28,17 @@ class FusedAdam(torch.optim.Optimizer):
         assert exp_avg_dtype in (torch.float32, torch.bfloat16), "moments are fp32 or bf16"
         defaults = dict(lr=lr, bias_correction=bias_correction, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
+        if store_param_remainders and not master_weights:
+            raise RuntimeError("store_param_remainders splits the fp32 master weights; it needs master_weights=True")
+        if master_weight_dtype != torch.float32:
+            raise NotImplementedError("master weights are kept in fp32 (or as bf16 + 16-bit remainders)")
         self.adam_w_mode = adam_w_mode
         self.set_grad_none = set_grad_none
+        # capturable: the step count (and a tensor learning rate) stay on the device, so ``step()`` issues
+        # the same launches every time and can be recorded in a CUDA graph
         self.capturable = capturable
         self.master_weights = master_weights
+        self.store_param_remainders = store_param_remainders
         self.state_dtype = exp_avg_dtype
         self.use_decoupled_grad = use_decoupled_grad
         self._noop = None
@@ -55,8 +62,37 @@ class FusedAdam(torch.optim.Optimizer):
             st["exp_avg_sq"] = torch.zeros(base.shape, dtype=self.state_dtype, device=base.device)
             if self.master_weights or isinstance(p, QuantizedTensor):
                 hp = getattr(p, "_high_precision_init_val", None)
-                st["master_param"] = (hp.to(base.device) if hp is not None else base).float().clone()
+                master = (hp.to(base.device) if hp is not None else base).float().clone()
+                if self.store_param_remainders and p.dtype == torch.bfloat16 and not isinstance(p, QuantizedTensor):
+                    # the bf16 parameter already is the high half of the master weight: keep only the low half
+                    hi, lo = ops.misc.split_param_remainder(master)
+                    p.data.copy_(hi)
+                    st["param_remainder"] = lo
+                else:
+                    st["master_param"] = master
         return st
+
+    def _step_value(self, group):
+        """Host int, or (capturable) an int32 device scalar advanced by a device op."""
+        if not self.capturable:
+            group["step"] = group.get("step", 0) + 1
+            return group["step"]
+        st = group.get("step")
+        if not isinstance(st, torch.Tensor):
+            dev = next((p.device for p in group["params"]), torch.device("cpu"))
+            st = group["step"] = torch.full((), int(st or 0), dtype=torch.int32, device=dev)
+        st += 1
+        return st
+
+    def _lr_value(self, group):
+        lr = group["lr"]
+        if self.capturable and not isinstance(lr, torch.Tensor):
+            cache = group.get("_lr_dev")
+            if cache is None or cache[0] != lr:
+                dev = next((p.device for p in group["params"]), torch.device("cpu"))
+                cache = group["_lr_dev"] = (lr, torch.full((), float(lr), dtype=torch.float32, device=dev))
+            return cache[1]
+        return lr
 
     @torch.no_grad()
     def step(self, closure=None, grad_scaler=None):  # type: ignore[override]
@@ -64,7 +100,8 @@ class FusedAdam(torch.optim.Optimizer):
         for group in self.param_groups:
             if not group["params"]:
                 continue
-            group["step"] = group.get("step", 0) + 1
+            step = self._step_value(group)
+            lr = self._lr_value(group)
             b1, b2 = group["betas"]
             buckets = {}
             quantized = []
@@ -72,28 +109,32 @@ class FusedAdam(torch.optim.Optimizer):
                 g = getattr(p, "decoupled_grad", None) if self.use_decoupled_grad else p.grad
                 if g is None:
                     continue
+                if getattr(p, "grad_added_to_main_grad", False) and g.numel() > 1 and g.stride() == (0,) * g.dim():
+                    continue  # placeholder returned when the wgrad GEMM accumulated into main_grad
+                if not g.is_contiguous():
+                    g = g.contiguous()
                 st = self._init_state(p)
                 if isinstance(p, QuantizedTensor):
                     quantized.append((p, g, st))
                     continue
-                has_master = "master_param" in st
-                key = (g.dtype, p.dtype, has_master)
+                mode = 2 if "param_remainder" in st else (1 if "master_param" in st else 0)
+                key = (g.dtype, p.dtype, mode)
                 b = buckets.setdefault(key, [[], [], [], [], []])
                 b[0].append(g)
                 b[1].append(p.data)
                 b[2].append(st["exp_avg"])
                 b[3].append(st["exp_avg_sq"])
-                if has_master:
-                    b[4].append(st["master_param"])
-            for (gd, pd, has_master), lists in buckets.items():
-                ls = lists if has_master else lists[:4]
-                ops.multi_tensor_adam(ls, group["lr"], b1, b2, group["eps"], group["step"], self.adam_w_mode,
-                                      group["bias_correction"], group["weight_decay"])
+                if mode:
+                    b[4].append(st["param_remainder"] if mode == 2 else st["master_param"])
+            for (gd, pd, mode), lists in buckets.items():
+                ls = lists if mode else lists[:4]
+                ops.multi_tensor_adam(ls, lr, b1, b2, group["eps"], step, self.adam_w_mode,
+                                      group["bias_correction"], group["weight_decay"], remainders=mode == 2)
             for p, g, st in quantized:
-                # quantized parameters: update the fp32 master, then re-quantize in place
-                tmp = st["master_param"].clone()
+                # quantized (FP8 / block-scaled) parameters: update the fp32 master, then re-quantize in place
+                tmp = torch.empty_like(st["master_param"])
                 ops.multi_tensor_adam([[g.float()], [tmp], [st["exp_avg"]], [st["exp_avg_sq"]], [st["master_param"]]],
-                                      group["lr"], b1, b2, group["eps"], group["step"], self.adam_w_mode,
+                                      lr, b1, b2, group["eps"], step, self.adam_w_mode,
                                       group["bias_correction"], group["weight_decay"])
                 p.quantize_(st["master_param"])
         bump_weights_epoch()
@@ -101,6 +142,10 @@ class FusedAdam(torch.optim.Optimizer):
 
     def state_dict(self):  # type: ignore[override]
         sd = super().state_dict()
+        for g in sd["param_groups"]:
+            g.pop("_lr_dev", None)
+            if isinstance(g.get("step"), torch.Tensor):
+                g["step"] = int(g["step"].item())
         for st in sd["state"].values():
             for k in ("exp_avg", "exp_avg_sq"):
                 if k in st and st[k].dtype != torch.float32:

@@ -56,24 +56,104 @@ def _status(dev) -> torch.Tensor:
     return _ext.get().status(dev.index if dev.index is not None else torch.cuda.current_device())
 
 
+class SideSpec:
+    """Shape of an operand that the copy CTAs of a fused kernel gather next to the GEMM (the
+    weight-gradient operand of the layer: what the reference calls bulk overlap,
+    ``common/comm_gemm_overlap/comm_gemm_overlap.cpp:444-498``).
+
+    Every rank contributes ``rows x row_bytes`` bytes.  ``interleave=True`` places piece ``s`` at byte
+    column ``s * row_bytes`` of a ``[rows, world * row_bytes]`` result (the transposed, column-wise copy
+    of a row-sharded MXFP8 tensor, whose ``row_tiles`` scale chunks of ``sf_chunk`` bytes are merged the
+    same way); ``interleave=False`` stacks the pieces along the rows (a row-sharded 16-bit tensor)."""
+
+    def __init__(self, rows: int, row_bytes: int, interleave: bool, row_tiles: int = 0, sf_chunk: int = 0):
+        assert row_bytes % 16 == 0 and 0 < row_bytes <= 32768, "side gather rows must be 16..32768 bytes, multiple of 16"
+        assert sf_chunk % 16 == 0 and sf_chunk <= 32768
+        self.rows, self.row_bytes, self.interleave = rows, row_bytes, interleave
+        self.row_tiles, self.sf_chunk = row_tiles, sf_chunk
+
+    def key(self):
+        return (self.rows, self.row_bytes, self.interleave, self.row_tiles, self.sf_chunk)
+
+    @property
+    def data_bytes(self) -> int:
+        return self.rows * self.row_bytes
+
+    @property
+    def sf_bytes(self) -> int:
+        return self.row_tiles * self.sf_chunk
+
+    @staticmethod
+    def for_mxfp8_columnwise(C: int, rows_local: int) -> "SideSpec":
+        """Column-wise copy ``[C, rows_local]`` (+ swizzled scale tiles) of a row-sharded MXFP8 tensor."""
+        assert rows_local % 128 == 0
+        return SideSpec(C, rows_local, True, round_up(C, 128) // 128, rows_local // 128 * 512)
+
+    @staticmethod
+    def for_rows(rows_local: int, row_bytes: int) -> "SideSpec":
+        return SideSpec(rows_local, row_bytes, False)
+
+
+class _SideStage:
+    """Symmetric staging of the side operand (two slots) plus the launch arguments describing it."""
+
+    def __init__(self, buf: SymmetricBuffer, spec: SideSpec, world: int):
+        self.spec, self.world = spec, world
+        self.stage, self.ptrs = [], []
+        for _ in range(2):
+            t, p = buf.carve(spec.data_bytes + spec.sf_bytes)
+            self.stage.append(t)
+            self.ptrs.append(p)
+
+    @staticmethod
+    def nbytes(spec: Optional[SideSpec]) -> int:
+        return 0 if spec is None else 2 * (spec.data_bytes + spec.sf_bytes + 256)
+
+    def launch_args(self, slot: int, data: torch.Tensor, sf: Optional[torch.Tensor]):
+        """Stage this rank's piece and allocate the gathered result.  Returns (kwargs, data_out, sf_out)."""
+        sp, w = self.spec, self.world
+        st = self.stage[slot]
+        flat = data.reshape(-1).view(torch.uint8)
+        assert flat.numel() == sp.data_bytes, "side operand does not match the context's shape"
+        st[:sp.data_bytes].copy_(flat)
+        sf_out = None
+        if sp.sf_bytes:
+            st[sp.data_bytes:sp.data_bytes + sp.sf_bytes].copy_(sf.reshape(-1).view(torch.uint8)[:sp.sf_bytes])
+            sf_out = torch.empty(sp.sf_bytes * w, dtype=torch.uint8, device=st.device)
+        if sp.interleave:
+            out = torch.empty(sp.rows, w * sp.row_bytes, dtype=torch.uint8, device=st.device)
+            pitch, piece_off = w * sp.row_bytes, sp.row_bytes
+        else:
+            out = torch.empty(w * sp.rows, sp.row_bytes, dtype=torch.uint8, device=st.device)
+            pitch, piece_off = sp.row_bytes, sp.rows * sp.row_bytes
+        kw = dict(side_src_ptrs=self.ptrs[slot], side_dst=out, side_dst_sf=sf_out,
+                  side_geom=[sp.rows, sp.row_bytes, pitch, piece_off, sp.row_tiles, sp.sf_chunk])
+        return kw, out, sf_out
+
+
 class AllGatherGemm:
     """Context of one all-gather -> GEMM site (fixed gathered shape ``[T, K]``)."""
 
-    def __init__(self, group, T: int, K: int, *, mxfp8: bool, dtype=torch.bfloat16, copy_ctas: int = 12):
+    def __init__(self, group, T: int, K: int, *, mxfp8: bool, dtype=torch.bfloat16, copy_ctas: int = 12,
+                 side: Optional[SideSpec] = None):
         self.group, self.T, self.K, self.mx = group, T, K, mxfp8
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert T % (128 * self.world) == 0, "gathered rows must be a multiple of 128 * tp"
         self.elem = 1 if mxfp8 else torch.empty(0, dtype=dtype).element_size()
         self.dtype = torch.uint8 if mxfp8 else dtype
         self.copy_ctas = copy_ctas
-        self.epoch = 0
+        self.calls = 0
         a_bytes = T * K * self.elem
         sf_bytes = (T // 128) * round_up(K // 32, 4) // 4 * 512 if mxfp8 else 0
         self.sf_bytes = sf_bytes
-        nflags = 256 + T // 128
-        self.buf = SymmetricBuffer(2 * (a_bytes + sf_bytes) + 4 * nflags + 4096, group)
+        nflags = 64 + T // 128
+        self.buf = SymmetricBuffer(2 * (a_bytes + sf_bytes + 4 * nflags + 1024) + 4096 + _SideStage.nbytes(side), group)
         self.a, self.a_ptrs, self.sf, self.sf_ptrs = [], [], [], []
-        for _ in range(2):  # double buffered: a peer may still read call n while call n+1 is staged
+        self.ready_ptrs, self.chunk_ptr = [], []
+        # Double buffered: a peer may still read call n while call n+1 is staged.  Every slot is a channel
+        # of its own (flags included) whose call number is kept on the device by the kernel, so the same
+        # launch arguments stay valid when a captured graph replays them.
+        for _ in range(2):
             t, p = self.buf.carve(a_bytes)
             self.a.append(t.view(self.dtype).reshape(T, K))
             self.a_ptrs.append(p)
@@ -81,19 +161,23 @@ class AllGatherGemm:
                 t, p = self.buf.carve(sf_bytes)
                 self.sf.append(t)
                 self.sf_ptrs.append(p)
-        self.ready, self.ready_ptrs = self.buf.carve(4 * 64)
-        self.chunk, chunk_ptrs = self.buf.carve(4 * (T // 128))
-        self.chunk_ptr = chunk_ptrs[self.rank]
+            _, p = self.buf.carve(4 * 64)
+            self.ready_ptrs.append(p)
+            _, p = self.buf.carve(4 * (T // 128))
+            self.chunk_ptr.append(p[self.rank])
+        self.epoch_dev = [torch.zeros(2, dtype=torch.int32, device=self.a[0].device) for _ in range(2)]
+        self.side = _SideStage(self.buf, side, self.world) if side is not None else None
 
-    def __call__(self, x_local, w, *, bias=None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    def __call__(self, x_local, w, *, bias=None, out_dtype=torch.bfloat16, side=None):
         """``x_local``: this rank's rows (plain 16-bit tensor or MXFP8 with a rowwise copy);
-        ``w``: the local weight ``[N, K]`` of the same kind.  Returns ``[T, N]``."""
+        ``w``: the local weight ``[N, K]`` of the same kind.  Returns ``[T, N]``; with ``side=(data, scales)``
+        (this rank's piece of the side operand) returns ``(out, gathered_data, gathered_scales)``."""
         a_op = x_local if isinstance(x_local, Operand) else as_operand(x_local, "rowwise")
         b_op = w if isinstance(w, Operand) else as_operand(w, "rowwise")
         rows = self.T // self.world
         assert a_op.rows == rows and a_op.k == self.K
-        self.epoch += 1
-        slot = self.epoch & 1
+        self.calls += 1
+        slot = self.calls & 1
         lo = self.rank * rows
         self.a[slot][lo:lo + rows].copy_(a_op.data.view(self.dtype) if self.mx else a_op.data)
         sfa = None
@@ -103,57 +187,67 @@ class AllGatherGemm:
             sfa = self.sf[slot]
         N = b_op.rows
         out = torch.empty(self.T, N, dtype=out_dtype, device=self.a[slot].device)
-        _ext.get().comm_gemm(1, self.rank, self.world, self.epoch, self.copy_ctas, self.a[slot], sfa, b_op.data,
-                             b_op.scale if self.mx else None, out, bias,
+        kw, sd, ssf = ({}, None, None) if side is None else self.side.launch_args(slot, side[0], side[1])
+        _ext.get().comm_gemm(1, self.rank, self.world, self.epoch_dev[slot], self.copy_ctas, self.a[slot], sfa,
+                             b_op.data, b_op.scale if self.mx else None, out, bias,
                              a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,
-                             self.a_ptrs[slot], self.sf_ptrs[slot] if self.mx else [], self.ready_ptrs,
-                             self.chunk_ptr, [], [], None, N, _status(out.device))
-        return out
+                             self.a_ptrs[slot], self.sf_ptrs[slot] if self.mx else [], self.ready_ptrs[slot],
+                             self.chunk_ptr[slot], [], [], None, N, _status(out.device), **kw)
+        return out if side is None else (out, sd, ssf)
 
     def gathered(self) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """The gathered operand of the last call (valid once that call's kernel has run)."""
-        slot = self.epoch & 1
+        slot = self.calls & 1
         return self.a[slot], (self.sf[slot] if self.mx else None)
 
 
 class GemmReduceScatter:
     """Context of one GEMM -> reduce-scatter site (fixed output shape ``[T, N]`` before scattering)."""
 
-    def __init__(self, group, T: int, N: int, *, dtype=torch.bfloat16):
+    def __init__(self, group, T: int, N: int, *, dtype=torch.bfloat16, side: Optional[SideSpec] = None,
+                 copy_ctas: int = 8):
         self.group, self.T, self.N, self.dtype = group, T, N, dtype
+        self.copy_ctas = copy_ctas
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert T % (128 * self.world) == 0 and N % 8 == 0
-        self.epoch = 0
         stage_bytes = T * round_up(N, 256) * 2  # one 64 KB record per 128 x 256 output tile
         mbl = T // 128 // self.world
-        self.buf = SymmetricBuffer(2 * stage_bytes + 4 * self.world * mbl * 2 + 4096, group)
+        self.buf = SymmetricBuffer(2 * stage_bytes + 4 * self.world * mbl * 2 + 8192 + _SideStage.nbytes(side), group)
         self.stage_ptrs = []
         for _ in range(2):
             _, p = self.buf.carve(stage_bytes)
             self.stage_ptrs.append(p)
-        # one counter array per staging buffer: each call adds ceil(N/256) per (source, block)
+        # one counter array per staging buffer: each call adds 2 * ceil(N/256) per (source, block); the
+        # number of calls made on a buffer is kept on the device by the kernel
         self.flag_ptrs = []
         for _ in range(2):
             _, p = self.buf.carve(4 * self.world * mbl)
             self.flag_ptrs.append(p)
-        self.calls = [0, 0]
+        self.calls = 0
+        self.epoch_dev = [torch.zeros(2, dtype=torch.int32, device=self.buf.tensor.device) for _ in range(2)]
+        self.side, self.ready_ptrs = None, [[], []]
+        if side is not None:
+            self.side = _SideStage(self.buf, side, self.world)
+            self.ready_ptrs = [self.buf.carve(4 * 64)[1] for _ in range(2)]
 
-    def __call__(self, x, w, *, bias=None, timeline: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``x`` [T, K/tp], ``w`` [N, K/tp] (16-bit or MXFP8 rowwise).  Returns this rank's ``[T/tp, N]``."""
+    def __call__(self, x, w, *, bias=None, timeline: Optional[torch.Tensor] = None, side=None):
+        """``x`` [T, K/tp], ``w`` [N, K/tp] (16-bit or MXFP8 rowwise).  Returns this rank's ``[T/tp, N]``; with
+        ``side=(data, scales)`` returns ``(out, gathered_data, gathered_scales)``."""
         a_op = x if isinstance(x, Operand) else as_operand(x, "rowwise")
         b_op = w if isinstance(w, Operand) else as_operand(w, "rowwise")
         assert a_op.rows == self.T and b_op.rows == self.N
-        self.epoch += 1
-        slot = self.epoch & 1
-        self.calls[slot] += 1
+        self.calls += 1
+        slot = self.calls & 1
         mx = a_op.kind == "mxfp8"
         out = torch.empty(self.T // self.world, self.N, dtype=self.dtype, device=a_op.data.device)
-        _ext.get().comm_gemm(2, self.rank, self.world, self.calls[slot], 0, a_op.data, a_op.scale if mx else None,
+        kw, sd, ssf = ({}, None, None) if side is None else self.side.launch_args(slot, side[0], side[1])
+        _ext.get().comm_gemm(2, self.rank, self.world, self.epoch_dev[slot], self.copy_ctas if side is not None else 0,
+                             a_op.data, a_op.scale if mx else None,
                              b_op.data, b_op.scale if mx else None, timeline, bias,
                              a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,
-                             [], [], [], 0, self.stage_ptrs[slot], self.flag_ptrs[slot], out, self.N,
-                             _status(out.device))
-        return out
+                             [], [], self.ready_ptrs[slot], 0, self.stage_ptrs[slot], self.flag_ptrs[slot], out, self.N,
+                             _status(out.device), **kw)
+        return out if side is None else (out, sd, ssf)
 
 
 # --------------------------------------------------------------------------- registry (initialize_ub equivalent)
@@ -179,17 +273,19 @@ def enabled_for(group) -> bool:
     return _ENABLED["group"] is not None and group is not None and _ENABLED["group"] == group
 
 
-def get_all_gather_gemm(name: str, group, T: int, K: int, mxfp8: bool, dtype) -> AllGatherGemm:
-    key = ("ag", name, T, K, mxfp8, dtype)
+def get_all_gather_gemm(name: str, group, T: int, K: int, mxfp8: bool, dtype,
+                        side: Optional[SideSpec] = None) -> AllGatherGemm:
+    key = ("ag", name, T, K, mxfp8, dtype, side.key() if side is not None else None)
     ctx = _CONTEXTS.get(key)
     if ctx is None:
-        ctx = _CONTEXTS[key] = AllGatherGemm(group, T, K, mxfp8=mxfp8, dtype=dtype)
+        ctx = _CONTEXTS[key] = AllGatherGemm(group, T, K, mxfp8=mxfp8, dtype=dtype, side=side)
     return ctx
 
 
-def get_gemm_reduce_scatter(name: str, group, T: int, N: int, dtype) -> GemmReduceScatter:
-    key = ("rs", name, T, N, dtype)
+def get_gemm_reduce_scatter(name: str, group, T: int, N: int, dtype,
+                            side: Optional[SideSpec] = None) -> GemmReduceScatter:
+    key = ("rs", name, T, N, dtype, side.key() if side is not None else None)
     ctx = _CONTEXTS.get(key)
     if ctx is None:
-        ctx = _CONTEXTS[key] = GemmReduceScatter(group, T, N, dtype=dtype)
+        ctx = _CONTEXTS[key] = GemmReduceScatter(group, T, N, dtype=dtype, side=side)
     return ctx

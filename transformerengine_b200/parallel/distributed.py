@@ -145,10 +145,43 @@ class CudaRNGStatesTracker:
 
 # --------------------------------------------------------------------------- activation recompute
 _IN_RECOMPUTE = [False]
+_IN_CHECKPOINT_FORWARD = [0]
+_RECOMPUTE_RESTORE: list = []
 
 
 def is_in_recompute() -> bool:
+    """True while a checkpointed region is being run again in the backward pass."""
     return _IN_RECOMPUTE[0]
+
+
+def in_checkpoint_forward() -> bool:
+    """True during the first (activation-discarding) run of a checkpointed region.  Modules with
+    delayed-scaling state stash their forward scales then, because the recompute must quantize with
+    the same scales although the amax history has moved on in between
+    (reference: ``copy_forward_fp8_meta_tensors_for_recompute``, ``pytorch/module/base.py:1601-1649``)."""
+    return _IN_CHECKPOINT_FORWARD[0] > 0
+
+
+def add_recompute_restore(fn: Callable) -> None:
+    """Run ``fn`` once the current recompute forward has finished (puts live quantization state back)."""
+    _RECOMPUTE_RESTORE.append(fn)
+
+
+def _run_recompute_restores() -> None:
+    todo = list(_RECOMPUTE_RESTORE)
+    _RECOMPUTE_RESTORE.clear()
+    for fn in reversed(todo):
+        fn()
+
+
+def _consume_first_module_flag() -> None:
+    """A checkpointed block has run the forward of its modules without autograd, so none of them took
+    the 'first quantized module' token; take it here so that only the first block's recompute owns the
+    backward amax reduction."""
+    from ..quantization import FP8GlobalStateManager
+
+    if FP8GlobalStateManager.is_fp8_enabled():
+        FP8GlobalStateManager.IS_FIRST_FP8_MODULE = False
 
 
 class _CheckpointFunction(torch.autograd.Function):
@@ -167,8 +200,13 @@ class _CheckpointFunction(torch.autograd.Function):
         ctx.tracker_states = rng_tracker_fn().get_states() if rng_tracker_fn is not None else None
         ctx.autocast_state = FP8GlobalStateManager.get_autocast_state()
         ctx.torch_autocast = torch.is_autocast_enabled()
-        with torch.no_grad():
-            out = run_function(*args, **kwargs)
+        _IN_CHECKPOINT_FORWARD[0] += 1
+        try:
+            with torch.no_grad():
+                out = run_function(*args, **kwargs)
+        finally:
+            _IN_CHECKPOINT_FORWARD[0] -= 1
+        _consume_first_module_flag()
         ctx.tensor_idx = [i for i, a in enumerate(args) if torch.is_tensor(a)]
         ctx.others = [None if torch.is_tensor(a) else a for a in args]
         ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
@@ -198,6 +236,7 @@ class _CheckpointFunction(torch.autograd.Function):
                 out = ctx.run_function(*args, **ctx.kwargs)
         finally:
             _IN_RECOMPUTE[0] = False
+            _run_recompute_restores()
             FP8GlobalStateManager.set_autocast_state(cur_state)
             torch.set_rng_state(cpu_rng)
             if cuda_rng is not None:
@@ -225,6 +264,14 @@ def checkpoint(function: Callable, *args, distribute_saved_activations: bool = F
 
         def ctx_fn():
             @contextlib.contextmanager
+            def forward_ctx():
+                _IN_CHECKPOINT_FORWARD[0] += 1
+                try:
+                    yield
+                finally:
+                    _IN_CHECKPOINT_FORWARD[0] -= 1
+
+            @contextlib.contextmanager
             def recompute_ctx():
                 cur = FP8GlobalStateManager.get_autocast_state()
                 FP8GlobalStateManager.set_autocast_state(st)
@@ -233,8 +280,9 @@ def checkpoint(function: Callable, *args, distribute_saved_activations: bool = F
                     yield
                 finally:
                     _IN_RECOMPUTE[0] = False
+                    _run_recompute_restores()
                     FP8GlobalStateManager.set_autocast_state(cur)
-            return contextlib.nullcontext(), recompute_ctx()
+            return forward_ctx(), recompute_ctx()
 
         return torch_ckpt(function, *args, use_reentrant=False, context_fn=ctx_fn, **kwargs)
     return _CheckpointFunction.apply(function, get_rng_state_tracker, kwargs, *args)

@@ -1,12 +1,18 @@
 """Flagship benchmark: one Llama-3-8B-architecture pre-training step (forward, backward,
 fused Adam with fp32 master weights) at seq 8192, micro-batch 1, MXFP8 block scaling.
 
-    python bench.py --gpus N --steps K --warmup W [--impl ours|reference]
+    python bench.py --gpus N --steps K --warmup W [--impl ours|reference] [--config NAME]
 
 N = 1: single GPU.  N = 2, 4: data parallel (one sequence per GPU, gradient
-all-reduce).  N = 8: tensor parallel with sequence parallelism.  Launched with
-``torch.distributed.run`` for N > 1.  Prints one JSON line from rank 0.
-Weights are random N(0, 0.02), token ids uniform over the vocabulary.
+all-reduce).  N = 8: tensor parallel with sequence parallelism, fused collective GEMMs, the
+whole step replayed from one CUDA graph.  Launched with ``torch.distributed.run`` for N > 1.
+Prints one JSON line from rank 0.  Weights are random N(0, 0.02), token ids uniform over the
+vocabulary.
+
+``--config`` selects the other benchmark configurations: ``layer12288`` (one sequence-parallel
+TransformerLayer, hidden 12288, forward + backward, TP = N), ``llama70b-nvfp4`` (70B-architecture
+layers under NVFP4 with full recompute, TP = N, 5 layers per GPU: 40 at N = 8) and ``mixtral``
+(8x7B-architecture MoE, expert parallel over N ranks, 4 layers per GPU below N = 8).
 """
 import argparse
 import json
@@ -30,10 +36,13 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     # development knobs; the defaults are the benchmarked configuration
-    ap.add_argument("--layers", type=int, default=32)
-    ap.add_argument("--seq", type=int, default=SEQ)
+    ap.add_argument("--config", default="llama8b", choices=["llama8b", "layer12288", "llama70b-nvfp4", "mixtral"],
+                    help="which BASELINE configuration to run (default: the Llama-3-8B-architecture step)")
+    ap.add_argument("--layers", type=int, default=0, help="0 = the configuration's layer count")
+    ap.add_argument("--seq", type=int, default=0, help="0 = the configuration's sequence length")
     ap.add_argument("--recompute", type=int, default=-1, help="-1 auto, 0 off, 1 per-layer recompute")
-    ap.add_argument("--recipe", default="mxfp8")
+    ap.add_argument("--recipe", default="", help="override the configuration's recipe")
+    ap.add_argument("--graph", type=int, default=-1, help="-1 auto (whole-step CUDA graph where supported), 0 off, 1 on")
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--fused-comm", type=int, default=1, help="fuse TP collectives into the GEMM kernels")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
@@ -128,74 +137,229 @@ def timed_loop(step_fn, steps, world, sampler_index=None):
     return ms, clocks
 
 
+def build_case(args, rank, world):
+    """Model, optimizer and data of the selected BASELINE configuration.
+
+    Returns a dict with ``step(tokens) -> loss`` (one full training iteration), the pinned host batches, the
+    tokens processed per step over all ranks, FLOPs per token and the description for the JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    import transformerengine_b200 as te
+    from transformerengine_b200.models import llama, mixtral
+    from transformerengine_b200.parallel import distributed as D
+    from transformerengine_b200.parallel.data_parallel import DataParallelGradSync
+
+    recipes = {"mxfp8": te.recipe.MXFP8BlockScaling, "nvfp4": te.recipe.NVFP4BlockScaling,
+               "delayed": te.recipe.DelayedScaling, "current": te.recipe.Float8CurrentScaling,
+               "block": te.recipe.Float8BlockScaling, "bf16": None}
+    name = args.config
+    n_batches = 4
+
+    def want_graph(tp, recipe_name):
+        """Whole-step CUDA graph: on by request, by default for tensor-parallel steps (their kernels are too
+        short for the eager launch path).  The NVFP4 stochastic-rounding offset is drawn on the host per
+        call, and expert-parallel steps read split sizes on the host: both stay eager."""
+        if recipe_name == "nvfp4" or name == "mixtral":
+            return False
+        return args.graph == 1 or (args.graph < 0 and tp > 1)
+
+    def adam(params, graph):
+        return te.FusedAdam(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, master_weights=True,
+                            capturable=graph)
+
+    if name in ("llama8b", "llama70b-nvfp4"):
+        if name == "llama8b":
+            tp = args.tp if args.tp > 0 else (world if world == 8 else 1)
+            seq = args.seq or 8192
+            cfg = llama.LlamaConfig.llama3_8b(num_layers=args.layers or 32)
+            recipe_name = args.recipe or "mxfp8"
+            recompute = bool(args.recompute) if args.recompute >= 0 else False
+            model_name = "llama3-8b-arch" if cfg.num_layers == 32 else f"llama3-8b-arch-{cfg.num_layers}L"
+        else:
+            # 70B-architecture layers: 40 layers fill 8 x 180 GB under TP=8; fewer GPUs hold 5 layers per GPU
+            tp = args.tp if args.tp > 0 else world
+            seq = args.seq or 4096
+            cfg = llama.LlamaConfig.llama3_70b(num_layers=args.layers or 5 * world)
+            recipe_name = args.recipe or "nvfp4"
+            recompute = bool(args.recompute) if args.recompute >= 0 else True
+            model_name = f"llama3-70b-arch-{cfg.num_layers}L"
+        dp = world // tp
+        assert dp == 1 or tp == 1, "this benchmark runs pure DP or pure TP"
+        cfg.recompute = recompute
+        tp_group = dist.group.WORLD if tp > 1 else None
+        # every rank initialises its own shard: different seeds under tensor parallelism
+        torch.manual_seed(1000 + (rank if tp > 1 else 0))
+        if tp > 1 and args.fused_comm:
+            te.initialize_ub(tp_group=tp_group)
+        model = llama.LlamaModel(cfg, tp_group=tp_group, sequence_parallel=True)
+        if dp > 1:
+            for p in model.parameters():
+                dist.broadcast(p.data, 0)
+        graph = want_graph(tp, recipe_name)
+        opt = adam(model.parameters(), graph)
+        recipe = recipes[recipe_name]() if recipes[recipe_name] is not None else None
+        grad_sync = DataParallelGradSync(model.parameters(), None,
+                                         overlap=os.environ.get("TEB200_DP_OVERLAP", "1") == "1") if dp > 1 else None
+
+        def step(tokens):
+            opt.zero_grad(set_to_none=True)
+            with te.autocast(enabled=recipe is not None, recipe=recipe):
+                loss = model(tokens, labels=tokens)
+            loss.backward()
+            if tp > 1:
+                D.allreduce_sequence_parallel_grads(model, tp_group)   # replicated norm weights see 1/tp of the rows
+            if grad_sync is not None:
+                grad_sync.finish()
+            opt.step()
+            return loss
+
+        gen = torch.Generator().manual_seed(1234 + rank * (1 if dp > 1 else 0))
+        host = [torch.randint(0, cfg.vocab_size, (1, seq), generator=gen).pin_memory() for _ in range(n_batches)]
+        return dict(step=step, host=host, tokens_per_step=seq * dp, flops_per_token=cfg.flops_per_token(seq),
+                    scaling="weak" if tp == 1 else "strong", sync=world > 1, recipe=recipe_name, graph=graph,
+                    before_capture=lambda: opt.zero_grad(set_to_none=True),
+                    config={"model": model_name, "global_batch": dp, "seq_len": seq,
+                            "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
+                            "recipe": recipe_name, "optimizer": "fused-adam fp32 master",
+                            "fused_comm_gemm": bool(tp > 1 and args.fused_comm), "recompute": recompute})
+
+    if name == "layer12288":
+        # one sequence-parallel TransformerLayer, forward + backward (no optimizer: a layer microbenchmark)
+        tp = args.tp if args.tp > 0 else world
+        seq, mb, H, FFN, NH = args.seq or 2048, 2, 12288, 49152, 96
+        recipe_name = args.recipe or "mxfp8"
+        tp_group = dist.group.WORLD if tp > 1 else None
+        torch.manual_seed(1000 + rank)
+        if tp > 1 and args.fused_comm:
+            te.initialize_ub(tp_group=tp_group)
+        init = lambda t: torch.nn.init.normal_(t, 0.0, 0.02)  # noqa: E731
+        layer = te.TransformerLayer(H, FFN, NH, layernorm_epsilon=1e-5, hidden_dropout=0.0, attention_dropout=0.0,
+                                    init_method=init, output_layer_init_method=init, self_attn_mask_type="causal",
+                                    tp_group=tp_group, tp_size=tp, params_dtype=torch.bfloat16,
+                                    sequence_parallel=tp > 1, set_parallel_mode=tp > 1, fuse_qkv_params=True,
+                                    activation="gelu", normalization="LayerNorm", device="cuda",
+                                    attn_input_format="sbhd")
+        recipe = recipes[recipe_name]() if recipes[recipe_name] is not None else None
+        gen = torch.Generator().manual_seed(1234)
+        host = [torch.randn(seq // tp, mb, H, generator=gen).to(torch.bfloat16).pin_memory() for _ in range(n_batches)]
+
+        def step(x):
+            for p in layer.parameters():
+                p.grad = None
+            x = x.detach().requires_grad_()
+            with te.autocast(enabled=recipe is not None, recipe=recipe):
+                y = layer(x)
+            loss = y.float().square().mean()
+            loss.backward()
+            return loss
+
+        per_layer = H * 3 * H + H * H + 2 * H * FFN
+        return dict(step=step, host=host, tokens_per_step=seq * mb, scaling="strong", sync=world > 1,
+                    flops_per_token=6.0 * per_layer + 6.0 * seq * H, recipe=recipe_name,
+                    graph=want_graph(tp, recipe_name),
+                    config={"model": "transformer-layer-h12288", "global_batch": mb, "seq_len": seq,
+                            "parallelism": f"tp{tp}-sp" if tp > 1 else "single", "recipe": recipe_name,
+                            "optimizer": "none (forward + backward of one layer)",
+                            "fused_comm_gemm": bool(tp > 1 and args.fused_comm), "recompute": False})
+
+    if name == "mixtral":
+        # expert parallel over all ranks; attention / router / embeddings are replicated and data parallel.
+        # The full 32-layer model holds 46.7 G parameters: 8 ranks fit it, fewer ranks run 4 layers per GPU.
+        ep = world
+        seq = args.seq or 4096
+        layers = args.layers or (32 if world == 8 else 4 * world)
+        recipe_name = args.recipe or "mxfp8"
+        cfg = mixtral.MixtralConfig.mixtral_8x7b(num_layers=layers)
+        ep_group = dist.group.WORLD if ep > 1 else None
+        torch.manual_seed(0)
+        model = mixtral.MixtralModel(cfg, ep_group=ep_group)
+        expert_ids = {id(p) for n, p in model.named_parameters() if ".moe.fc" in n}
+        shared = [p for p in model.parameters() if id(p) not in expert_ids]
+        if ep > 1:
+            for p in shared:
+                dist.broadcast(p.data, 0)
+        opt = adam(model.parameters(), False)
+        recipe = recipes[recipe_name]() if recipes[recipe_name] is not None else None
+        grad_sync = DataParallelGradSync(shared, None, average=False) if ep > 1 else None
+
+        def step(tokens):
+            opt.zero_grad(set_to_none=True)
+            with te.autocast(enabled=recipe is not None, recipe=recipe):
+                loss = model(tokens, labels=tokens)
+            (loss / ep).backward()     # mean over the ranks' sequences: shared gradients are summed below
+            if grad_sync is not None:
+                grad_sync.finish()
+            opt.step()
+            return loss
+
+        gen = torch.Generator().manual_seed(1234 + rank)
+        host = [torch.randint(0, cfg.vocab_size, (1, seq), generator=gen).pin_memory() for _ in range(n_batches)]
+        h, f = cfg.hidden_size, cfg.ffn_hidden_size
+        hd = h // cfg.num_heads
+        active = layers * (h * (h + 2 * cfg.num_kv_heads * hd) + h * h + cfg.topk * 3 * h * f + h * cfg.num_experts) \
+            + cfg.vocab_size * h
+        return dict(step=step, host=host, tokens_per_step=seq * ep, scaling="weak", sync=world > 1,
+                    flops_per_token=6.0 * active + 6.0 * layers * seq * h, recipe=recipe_name, graph=False,
+                    config={"model": "mixtral-8x7b-arch" if layers == 32 else f"mixtral-8x7b-arch-{layers}L",
+                            "global_batch": ep, "seq_len": seq, "parallelism": f"ep{ep}" if ep > 1 else "single",
+                            "recipe": recipe_name, "optimizer": "fused-adam fp32 master",
+                            "fused_ep": os.environ.get("TEB200_FUSED_EP", "1") == "1", "recompute": False})
+    raise SystemExit(f"unknown --config {name}")
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     import transformerengine_b200 as te
-    from transformerengine_b200.models import llama
     from transformerengine_b200.ops import _ext
 
     rank, local, world = init_dist(args.gpus)
-    torch.manual_seed(0)
-    tp = args.tp if args.tp > 0 else (world if world == 8 else 1)
-    dp = world // tp
-    assert dp == 1 or tp == 1, "this benchmark runs pure DP or pure TP"
-    cfg = llama.LlamaConfig.llama3_8b(num_layers=args.layers)
-    # single-GPU / DP ranks hold the whole model and optimizer (~128 GB); activations of one 8192-token
-    # sequence add ~30 GB, which fits in 180 GB without recompute
-    cfg.recompute = bool(args.recompute) if args.recompute >= 0 else False
-    tp_group = dist.group.WORLD if tp > 1 else None
-    if tp > 1 and args.fused_comm:
-        te.initialize_ub(tp_group=tp_group)
-    model = llama.LlamaModel(cfg, tp_group=tp_group, sequence_parallel=True)
-    if dp > 1:
-        for p in model.parameters():
-            dist.broadcast(p.data, 0)
-    opt = te.FusedAdam(model.parameters(), lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                       master_weights=True)
-    recipe = {"mxfp8": te.recipe.MXFP8BlockScaling(), "nvfp4": te.recipe.NVFP4BlockScaling(),
-              "delayed": te.recipe.DelayedScaling(), "current": te.recipe.Float8CurrentScaling(),
-              "bf16": None}[args.recipe]
-    gen = torch.Generator().manual_seed(1234 + rank * (1 if dp > 1 else 0))
-    n_batches = 4
-    host = [torch.randint(0, cfg.vocab_size, (1, args.seq), generator=gen).pin_memory() for _ in range(n_batches)]
+    case = build_case(args, rank, world)
+    train_step, host = case["step"], case["host"]
+    n_batches = len(host)
     dev = [h.cuda() for h in host]
-    # data parallel: every gradient is all-reduced (average) as soon as autograd has produced it
-    from transformerengine_b200.parallel.data_parallel import DataParallelGradSync
-    grad_sync = DataParallelGradSync(model.parameters(), None,
-                                     overlap=os.environ.get("TEB200_DP_OVERLAP", "1") == "1") if dp > 1 else None
+    # One CUDA graph holds the whole iteration (forward, backward, collectives, optimizer): the host issues
+    # one launch per step.
+    use_graph = case["graph"]
+    C_ = _ext.get()
+    if use_graph:
+        static_in = torch.empty_like(dev[0])
+        static_in.copy_(dev[0])
+        gstep = te.graph.capture_step(train_step, (static_in,), warmup=max(args.warmup, 3),
+                                      sync_group=dist.group.WORLD if case["sync"] else None,
+                                      before_capture=case.get("before_capture"))
+        per_step = gstep.kernels_per_replay
 
-    def train_step(tokens):
-        opt.zero_grad(set_to_none=True)
-        with te.autocast(enabled=recipe is not None, recipe=recipe):
-            loss = model(tokens, labels=tokens)
-        loss.backward()
-        if grad_sync is not None:
-            grad_sync.finish()
-        opt.step()
-        return loss
+        def step_device(i):
+            gstep(dev[i % n_batches])
 
-    def step_device(i):
-        train_step(dev[i % n_batches])
+        def run_e2e(i):
+            return gstep(host[i % n_batches])                     # H2D of this step's inputs from pinned memory
+    else:
+        per_step = None
+
+        def step_device(i):
+            train_step(dev[i % n_batches])
+
+        def run_e2e(i):
+            return train_step(host[i % n_batches].cuda(non_blocking=True))
 
     losses = []
 
     def step_e2e(i):
-        tok = host[i % n_batches].cuda(non_blocking=True)   # H2D of this step's inputs from pinned memory
-        loss = train_step(tok)
-        losses.append(float(loss.item()))                    # D2H read of the step's result
+        losses.append(float(run_e2e(i).item()))                   # D2H read of the step's result
 
     for i in range(args.warmup):
         step_device(i)
     torch.cuda.synchronize()
     te.check_status()
-    C_ = _ext.get()
     l0 = C_.launch_count()
     ms, clocks = timed_loop(step_device, args.steps, world, physical_gpu_index(local))
-    launches = C_.launch_count() - l0
+    launches = per_step * args.steps if per_step is not None else C_.launch_count() - l0
     te.check_status()
-    tokens_per_step = args.seq * dp
+    tokens_per_step = case["tokens_per_step"]
     value = tokens_per_step * args.steps / (ms / 1e3)
     e2e = None
     if not args.skip_e2e:
@@ -204,18 +368,16 @@ def run_ours(args):
         e2e = {"value": tokens_per_step * args.steps / (ms2 / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": host[0].numel() * host[0].element_size(), "d2h_bytes_per_step": 4,
                "ms_per_step": ms2 / args.steps, "last_loss": losses[-1] if losses else None}
+    te.check_status()
     if rank == 0:
-        tflops = value * cfg.flops_per_token(args.seq) / 1e12 / world
+        tflops = value * case["flops_per_token"] / 1e12 / world
+        cfg = dict(case["config"])
+        cfg["cuda_graph"] = "whole step" if use_graph else "off"
+        cfg["l2"] = "inputs and weights far exceed the 126 MB L2"
         out = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-               "scaling": "weak" if tp == 1 else "strong", "vs_baseline": None, "dtype": "bf16+" + args.recipe,
-               "data": "synthetic", "impl": "ours",
-               "config": {"model": "llama3-8b-arch" if args.layers == 32 else f"llama3-8b-arch-{args.layers}L",
-                          "global_batch": dp, "seq_len": args.seq,
-                          "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
-                          "recipe": args.recipe, "optimizer": "fused-adam fp32 master",
-                          "fused_comm_gemm": bool(tp > 1 and args.fused_comm), "recompute": cfg.recompute,
-                          "l2": "inputs and weights (16 GB) far exceed the 126 MB L2"},
+               "scaling": case["scaling"], "vs_baseline": None, "dtype": "bf16+" + case["recipe"],
+               "data": "synthetic", "impl": "ours", "config": cfg,
                "tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
                "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30}
         print(json.dumps(out), flush=True)
@@ -244,6 +406,10 @@ def run_reference(args):
     torch.manual_seed(0)
     tp = args.tp if args.tp > 0 else (world if world == 8 else 1)
     dp = world // tp
+    if args.config != "llama8b":
+        print(json.dumps({"impl": "reference", "unavailable": "the reference arm covers --config llama8b only"}), flush=True)
+        return
+    args.layers, args.seq = args.layers or 32, args.seq or SEQ
     V, H, L, NH, NKV, FFN = 128256, 4096, args.layers, 32, 8, 14336
     tp_group = dist.group.WORLD if tp > 1 else None
     init = lambda t: torch.nn.init.normal_(t, 0.0, 0.02)  # noqa: E731

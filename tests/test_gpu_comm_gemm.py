@@ -93,6 +93,110 @@ def _worker(rank, world, port, result_q):
                 e = rel(got, ref)
                 if not e < 1e-2:
                     bad[f"rs mx={mx} it={it}"] = e
+        # ---- side gather (the wgrad operand travels next to the GEMM), shapes with more tiles than SMs
+        from transformerengine_b200.parallel.comm_gemm import SideSpec
+        from transformerengine_b200.parallel.distributed import gather_mxfp8_along_first_dim
+
+        T2, K2, N2 = 1024 * world, 1024, 4096          # (T2/128) * (N2/256) = 128 * world tiles
+        R = T2 // world
+        torch.manual_seed(300 + rank)
+        xl = torch.randn(R, K2, device="cuda", dtype=torch.bfloat16)
+        torch.manual_seed(9)
+        w2 = torch.randn(N2, K2, device="cuda", dtype=torch.bfloat16)
+        q2 = MXFP8Quantizer(rowwise=True, columnwise=True)
+        ag_mx = AllGatherGemm(g, T2, K2, mxfp8=True, side=SideSpec.for_mxfp8_columnwise(K2, R))
+        ag_hp = AllGatherGemm(g, T2, K2, mxfp8=False, side=SideSpec.for_rows(R, K2 * 2))
+        wq = MXFP8Quantizer(columnwise=False)(w2)
+        for it in range(3):
+            xi = xl * (it + 1)
+            xq = q2(xi)
+            full = gather_mxfp8_along_first_dim(xq, g)  # NCCL oracle for both copies
+            out, gd, gsf = ag_mx(xq, wq, side=(xq._columnwise_data, xq._columnwise_scale_inv))
+            ref = ops.gemm_nt(ops.as_operand(full, "rowwise"), ops.as_operand(wq), out_dtype=torch.bfloat16)
+            torch.cuda.synchronize()
+            te.check_status()
+            if not torch.equal(out, ref):
+                bad[f"ag+side mx it={it} out"] = rel(out, ref)
+            if not torch.equal(gd.view(K2, T2), full._columnwise_data.view(K2, T2)):
+                bad[f"ag+side mx it={it} data"] = 1.0
+            if not torch.equal(gsf.view(-1), full._columnwise_scale_inv.view(-1)[:gsf.numel()]):
+                bad[f"ag+side mx it={it} scales"] = 1.0
+            xg = torch.empty(T2, K2, device="cuda", dtype=torch.bfloat16)
+            dist.all_gather_into_tensor(xg, xi)
+            out, gd, _ = ag_hp(xi, w2, side=(xi, None))
+            torch.cuda.synchronize()
+            te.check_status()
+            if not torch.equal(gd.view(torch.bfloat16).reshape(T2, K2), xg):
+                bad[f"ag+side hp it={it} data"] = 1.0
+            if not torch.equal(out, ops.gemm_nt(xg, w2, out_dtype=torch.bfloat16)):
+                bad[f"ag+side hp it={it} out"] = 1.0
+        log("ag side done")
+        # reduce-scatter with a side gather of an unrelated operand (the layer input of a column-parallel layer)
+        torch.manual_seed(400 + rank)
+        xr = torch.randn(T2, K2, device="cuda", dtype=torch.bfloat16)
+        wr = torch.randn(N2, K2, device="cuda", dtype=torch.bfloat16)
+        C3 = 768
+        sl = torch.randn(R, C3, device="cuda", dtype=torch.bfloat16)
+        rs_mx = GemmReduceScatter(g, T2, N2, side=SideSpec.for_mxfp8_columnwise(C3, R))
+        for it in range(3):
+            xi = xr * (it + 1)
+            qa, qb = MXFP8Quantizer(columnwise=False)(xi), MXFP8Quantizer(columnwise=False)(wr)
+            sq = q2(sl * (it + 1))
+            full = gather_mxfp8_along_first_dim(sq, g)
+            part = ops.gemm_nt(ops.as_operand(qa), ops.as_operand(qb), out_dtype=torch.float32)
+            ref = torch.empty(R, N2, device="cuda", dtype=torch.float32)
+            dist.reduce_scatter_tensor(ref, part)
+            got, gd, gsf = rs_mx(qa, qb, side=(sq._columnwise_data, sq._columnwise_scale_inv))
+            torch.cuda.synchronize()
+            te.check_status()
+            e = rel(got, ref)
+            if not e < 1e-2:
+                bad[f"rs+side it={it} out"] = e
+            if not torch.equal(gd.view(C3, T2), full._columnwise_data.view(C3, T2)):
+                bad[f"rs+side it={it} data"] = 1.0
+            if not torch.equal(gsf.view(-1), full._columnwise_scale_inv.view(-1)[:gsf.numel()]):
+                bad[f"rs+side it={it} scales"] = 1.0
+        log("rs side done")
+        # ---- the same launches recorded in a CUDA graph and replayed (odd number of calls per context)
+        sync = torch.zeros(1, device="cuda")
+        x_static = xl.clone()
+        side_stream = torch.cuda.Stream()
+        side_stream.wait_stream(torch.cuda.current_stream())
+
+        def body():
+            dist.all_reduce(sync)          # replay boundary: no rank runs ahead into the next replay
+            outs = []
+            for k in range(3):
+                xq_ = q2(x_static * (k + 1))
+                o, d_, s_ = ag_mx(xq_, wq, side=(xq_._columnwise_data, xq_._columnwise_scale_inv))
+                r_, _, _ = rs_mx(MXFP8Quantizer(columnwise=False)(o[:, :K2].contiguous()),
+                                 MXFP8Quantizer(columnwise=False)(wr), side=(xq_._columnwise_data[:C3].contiguous(),
+                                                                            xq_._columnwise_scale_inv[:C3 // 128 * (R // 128) * 512]))
+                outs.append((o, d_, r_))
+            return outs
+
+        with torch.cuda.stream(side_stream):
+            body()
+        torch.cuda.current_stream().wait_stream(side_stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            g_outs = body()
+        for rep in range(3):
+            x_static.copy_(xl * (rep + 2))
+            graph.replay()
+            torch.cuda.synchronize()
+            te.check_status()
+            snap = [(o.clone(), d_.clone(), r_.clone()) for o, d_, r_ in g_outs]
+            e_outs = body()   # eager launches interleaved with replays: the device-side call counters carry on
+            torch.cuda.synchronize()
+            te.check_status()
+            for k, ((o, d_, r_), (eo, ed, er)) in enumerate(zip(snap, e_outs)):
+                if not (torch.equal(o, eo) and torch.equal(d_, ed)):
+                    bad[f"graph rep={rep} call={k} ag"] = rel(o, eo)
+                if not rel(r_, er) < 1e-2:
+                    bad[f"graph rep={rep} call={k} rs"] = rel(r_, er)
+        log("graph done")
         result_q.put((rank, bad))
     except Exception:  # noqa: BLE001
         import traceback
@@ -106,7 +210,7 @@ def _worker(rank, world, port, result_q):
 
 
 def test_fused_collective_gemms():
-    world = min(torch.cuda.device_count(), 4)
+    world = torch.cuda.device_count() if torch.cuda.device_count() in (2, 4, 8) else min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
     ctx = mp.get_context("spawn")
@@ -116,7 +220,7 @@ def test_fused_collective_gemms():
     for p in procs:
         p.start()
     try:
-        res = [q.get(timeout=150) for _ in procs]
+        res = [q.get(timeout=240) for _ in procs]
     finally:
         for p in procs:
             p.join(timeout=20)

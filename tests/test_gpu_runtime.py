@@ -89,3 +89,136 @@ def test_graphed_callable_matches_eager(quantized):
     assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
     assert torch.allclose(x2.grad.float(), gx_ref.float(), atol=3e-2, rtol=3e-2)
     assert torch.isfinite(mod.fc1_weight.grad.float()).all() and gw_ref.shape == mod.fc1_weight.grad.shape
+
+
+def test_bounded_wait_expires_and_reports():
+    """A wait on a flag that nothing sets gives up after its limit, records the peer-flag status code and
+    returns: the context stays usable (the benign form of a lost peer)."""
+    import transformerengine_b200 as te
+    from transformerengine_b200.ops import _ext
+
+    C = _ext.get()
+    dev = torch.cuda.current_device()
+    st = C.status(dev)
+    st.zero_()
+    flags = torch.zeros(8, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    C.ep_wait(flags.data_ptr(), 4, 1, st, limit_cycles=2_000_000)   # about a millisecond of SM clocks
+    t1.record()
+    torch.cuda.synchronize()
+    assert t0.elapsed_time(t1) < 200.0
+    assert int(st[0].item()) == 4  # kTimeoutPeerFlag
+    with pytest.raises(RuntimeError, match="peer flag"):
+        te.check_status()
+    te.check_status()  # the status word was cleared by the failed check
+    # a flag that IS set lets the wait through, and kernels keep running on the same context
+    flags.fill_(1)
+    C.ep_wait(flags.data_ptr(), 4, 1, st, limit_cycles=2_000_000)
+    torch.cuda.synchronize()
+    te.check_status()
+    assert torch.ones(4, device="cuda").sum().item() == 4.0
+
+
+def test_graphed_callables_pipeline_order_and_weight_caching():
+    """Two model chunks, two micro-batches, captured in a 1F1B-like order from one pool; weights quantized
+    outside the forward graphs and refreshed in place when they change."""
+    import transformerengine_b200 as te
+
+    torch.manual_seed(0)
+    recipe = te.recipe.MXFP8BlockScaling()
+    chunks = [te.Linear(256, 256, bias=False, params_dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    xs = [torch.randn(128, 256, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+
+    def eager(mbs):
+        for c in chunks:
+            c.zero_grad(set_to_none=True)
+        outs = []
+        for x in mbs:
+            with te.autocast(enabled=True, recipe=recipe):
+                y = chunks[1](chunks[0](x.clone().requires_grad_()))
+            y.float().sum().backward()
+            outs.append(y.detach().clone())
+        return outs, [c.weight.grad.detach().clone() for c in chunks]
+
+    ref_out, ref_grad = eager(xs)
+    for c in chunks:
+        c.zero_grad(set_to_none=True)
+    sample = [(xs[mb].clone().requires_grad_(),) for mb in range(2) for _ in range(2)]
+    g0, g1 = te.make_graphed_callables(tuple(chunks), sample, num_warmup_iters=2, enabled=True, recipe=recipe,
+                                       cache_quantized_params=True, _order=[1, 2, 1, 2, -2, -1, -2, -1])
+    for c in chunks:
+        c.zero_grad(set_to_none=True)
+
+    def graphed(mbs, first):
+        outs = []
+        hs = []
+        for i, x in enumerate(mbs):
+            h = g0(x.clone().requires_grad_(), is_first_microbatch=first and i == 0)
+            hs.append(g1(h, is_first_microbatch=first and i == 0))
+        for y in hs:
+            y.float().sum().backward()
+            outs.append(y.detach().clone())
+        return outs
+
+    out = graphed(xs, True)
+    torch.cuda.synchronize()
+    te.check_status()
+    for a, b in zip(out, ref_out):
+        assert torch.allclose(a.float(), b.float(), atol=2e-2, rtol=2e-2)
+    for c, g in zip(chunks, ref_grad):
+        assert torch.allclose(c.weight.grad.float(), g.float(), atol=5e-2, rtol=5e-2)
+    # change the weights: without a refresh the graphs keep the cached FP8 weights, with it they follow
+    with torch.no_grad():
+        for c in chunks:
+            c.weight.mul_(2.0)
+    stale = graphed(xs, False)
+    fresh = graphed(xs, True)
+    torch.cuda.synchronize()
+    assert torch.allclose(stale[0].float(), ref_out[0].float(), atol=2e-2, rtol=2e-2)
+    assert torch.allclose(fresh[0].float(), 4.0 * ref_out[0].float(), atol=8e-2, rtol=3e-2)
+
+
+def test_fused_adam_capturable_and_param_remainders():
+    import transformerengine_b200 as te
+
+    torch.manual_seed(0)
+    shapes = [(257, 33), (1024,), (64, 64)]
+    base = [torch.randn(s, device="cuda", dtype=torch.bfloat16) for s in shapes]
+    grads = [[torch.randn(s, device="cuda", dtype=torch.bfloat16) for s in shapes] for _ in range(4)]
+
+    def run(**kw):
+        ps = [torch.nn.Parameter(b.clone()) for b in base]
+        opt = te.FusedAdam(ps, lr=1e-2, betas=(0.9, 0.95), weight_decay=0.1, master_weights=True, **kw)
+        for gs in grads:
+            for p, g in zip(ps, gs):
+                p.grad = g.clone()
+            opt.step()
+        torch.cuda.synchronize()
+        return ps, opt
+
+    ref, _ = run()
+    cap, opt_c = run(capturable=True)
+    assert isinstance(opt_c.param_groups[0]["step"], torch.Tensor) and int(opt_c.param_groups[0]["step"].item()) == 4
+    rem, opt_r = run(store_param_remainders=True)
+    for a, b, c in zip(ref, cap, rem):
+        assert torch.equal(a, b)                      # device step counter: same update
+        assert (a.float() - c.float()).abs().max().item() <= 2.0 ** -7 * a.float().abs().max().item() + 1e-6
+    # the bf16 parameter and its remainder rebuild the fp32 master exactly
+    st = opt_r.state[rem[0]]
+    assert "param_remainder" in st and "master_param" not in st
+    from transformerengine_b200.ops.misc import join_param_remainder
+
+    master_ref = run()[1].state  # fp32 masters of a plain run
+    m = join_param_remainder(rem[0].data, st["param_remainder"])
+    other = list(master_ref.values())[0]["master_param"]
+    assert torch.allclose(m, other, atol=1e-6, rtol=1e-6)
+    # strided or expanded gradients are made dense instead of being read out of bounds
+    p = torch.nn.Parameter(torch.zeros(8, 16, device="cuda", dtype=torch.bfloat16))
+    o = te.FusedAdam([p], lr=1e-2, master_weights=True)
+    p.grad = torch.ones(1, device="cuda", dtype=torch.bfloat16).expand(8, 16)
+    o.step()
+    torch.cuda.synchronize()
+    assert torch.isfinite(p.float()).all() and (p != 0).all()

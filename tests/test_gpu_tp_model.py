@@ -1,0 +1,200 @@
+"""A tensor-parallel (+ sequence-parallel) Llama built FROM the single-GPU weights reproduces the
+single-GPU loss and gradients, with the collectives fused into the GEMMs and with NCCL, eagerly and
+from a whole-step CUDA graph.  Needs 2 GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _shard_state(full, cfg, rank, tp):
+    """Slice a single-GPU state dict into rank ``rank``'s tensor-parallel shard."""
+    d = cfg.hidden_size // cfg.num_heads
+    hq, hk, F = cfg.num_heads * d, cfg.num_kv_heads * d, cfg.ffn_hidden_size
+
+    def rows(t, n):  # rank's slice of n equal row blocks
+        per = t.shape[0] // n
+        return t[rank * per:(rank + 1) * per]
+
+    out = {}
+    for k, v in full.items():
+        if k.endswith("_extra_state"):
+            continue
+        if k.endswith("layernorm_qkv.weight"):
+            q, kk, vv = torch.split(v, (hq, hk, hk), dim=0)
+            out[k] = torch.cat([rows(q, tp), rows(kk, tp), rows(vv, tp)], 0)
+        elif k.endswith("fc1_weight"):
+            g, u = torch.split(v, (F, F), dim=0)
+            out[k] = torch.cat([rows(g, tp), rows(u, tp)], 0)
+        elif k.endswith("proj.weight") or k.endswith("fc2_weight"):
+            per = v.shape[1] // tp
+            out[k] = v[:, rank * per:(rank + 1) * per]
+        elif k in ("embedding.weight", "lm_head.weight"):
+            out[k] = rows(v, tp)
+        else:
+            out[k] = v
+    return {k: v.contiguous() for k, v in out.items()}
+
+
+def _unshard_grad(name, g, cfg, tp, group):
+    """All-gather a sharded gradient back into the single-GPU layout."""
+    d = cfg.hidden_size // cfg.num_heads
+    hq, hk, F = cfg.num_heads * d // tp, cfg.num_kv_heads * d // tp, cfg.ffn_hidden_size // tp
+    parts = [torch.empty_like(g) for _ in range(tp)]
+    dist.all_gather(parts, g.contiguous(), group=group)
+    if name.endswith("layernorm_qkv.weight"):
+        sp = [torch.split(p, (hq, hk, hk), dim=0) for p in parts]
+        return torch.cat([torch.cat([s[i] for s in sp], 0) for i in range(3)], 0)
+    if name.endswith("fc1_weight"):
+        sp = [torch.split(p, (F, F), dim=0) for p in parts]
+        return torch.cat([torch.cat([s[i] for s in sp], 0) for i in range(2)], 0)
+    if name.endswith("proj.weight") or name.endswith("fc2_weight"):
+        return torch.cat(parts, 1)
+    if name in ("embedding.weight", "lm_head.weight"):
+        return torch.cat(parts, 0)
+    return g  # replicated (already reduced over the group)
+
+
+def _worker(rank, world, port, result_q):
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
+    bad = {}
+    try:
+        import transformerengine_b200 as te
+        from transformerengine_b200.models import llama
+        from transformerengine_b200.parallel import distributed as D
+
+        g = dist.group.WORLD
+
+        def rel(a, b):
+            return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+        cfg = llama.LlamaConfig.tiny(hidden_size=512, num_heads=4, num_kv_heads=2, ffn_hidden_size=1024,
+                                     vocab_size=1024, num_layers=2)
+        torch.manual_seed(0)
+        ref_model = llama.LlamaModel(cfg)  # same seed on every rank: identical full weights
+        full = {k: v.detach().clone() for k, v in ref_model.state_dict().items() if isinstance(v, torch.Tensor)}
+        tokens = torch.randint(0, cfg.vocab_size, (1, 256), device="cuda")
+
+        def run_single(recipe):
+            ref_model.zero_grad(set_to_none=True)
+            with te.autocast(enabled=recipe is not None, recipe=recipe):
+                loss = ref_model(tokens, labels=tokens)
+            loss.backward()
+            return loss.detach().float(), {n: p.grad.detach().clone() for n, p in ref_model.named_parameters()}
+
+        for recipe_name in ("bf16", "mxfp8"):
+            recipe = te.recipe.MXFP8BlockScaling() if recipe_name == "mxfp8" else None
+            loss_ref, grads_ref = run_single(recipe)
+            for fused in (False, True):
+                te.destroy_ub()
+                if fused:
+                    te.initialize_ub(tp_group=g)
+                model = llama.LlamaModel(cfg, tp_group=g, sequence_parallel=True)
+                missing = model.load_state_dict(_shard_state(full, cfg, rank, world), strict=False)
+                assert not [k for k in missing.missing_keys if not k.endswith("_extra_state")], missing
+                with te.autocast(enabled=recipe is not None, recipe=recipe):
+                    loss = model(tokens, labels=tokens)
+                loss.backward()
+                D.allreduce_sequence_parallel_grads(model, g)
+                torch.cuda.synchronize()
+                te.check_status()
+                tag = f"{recipe_name} fused={fused}"
+                # bf16: same math up to summation order; MXFP8: the sharded GEMMs quantize the same values
+                # (block scales are per 32 elements of a row / column, shards are multiples of 128)
+                tol = 2e-2 if recipe_name == "bf16" else 6e-2
+                if abs(loss.item() - loss_ref.item()) > tol * max(1.0, abs(loss_ref.item())):
+                    bad[f"{tag} loss"] = (loss.item(), loss_ref.item())
+                for n, p in model.named_parameters():
+                    assert p.grad is not None, n
+                    gfull = _unshard_grad(n, p.grad, cfg, world, g)
+                    e = rel(gfull, grads_ref[n])
+                    if not e < tol:
+                        bad[f"{tag} grad {n}"] = e
+                del model
+            te.destroy_ub()
+
+        # ---- whole-step CUDA graph equals the eager steps (fused collectives, MXFP8, capturable Adam)
+        recipe = te.recipe.MXFP8BlockScaling()
+
+        def build():
+            te.destroy_ub()
+            te.initialize_ub(tp_group=g)
+            m = llama.LlamaModel(cfg, tp_group=g, sequence_parallel=True)
+            m.load_state_dict(_shard_state(full, cfg, rank, world), strict=False)
+            o = te.FusedAdam(m.parameters(), lr=1e-3, master_weights=True, capturable=True)
+
+            def step(tok):
+                o.zero_grad(set_to_none=True)
+                with te.autocast(enabled=True, recipe=recipe):
+                    loss = m(tok, labels=tok)
+                loss.backward()
+                D.allreduce_sequence_parallel_grads(m, g)
+                o.step()
+                return loss
+            return m, o, step
+
+        batches = [torch.randint(0, cfg.vocab_size, (1, 256), device="cuda") for _ in range(5)]
+        for b in batches:
+            dist.broadcast(b, 0)
+        # eager: two steps on batch 0 (what the capture's warm-up does), then batches 1..4
+        m1, o1, step1 = build()
+        want = [step1(b).item() for b in [batches[0], batches[0]] + batches[1:]][2:]
+        m2, o2, step2 = build()
+        static = batches[0].clone()
+        gs = te.graph.capture_step(step2, (static,), warmup=2, sync_group=g,
+                                   before_capture=lambda: o2.zero_grad(set_to_none=True))
+        got = [gs(b).item() for b in batches[1:]]
+        te.check_status()
+        for i, (a, b) in enumerate(zip(got, want)):
+            if abs(a - b) > 2e-2 * max(1.0, abs(b)):
+                bad[f"graph step {i}"] = (a, b)
+        if gs.kernels_per_replay <= 0:
+            bad["graph kernels"] = gs.kernels_per_replay
+        result_q.put((rank, bad))
+    except Exception:  # noqa: BLE001
+        import traceback
+        result_q.put((rank, {"exception": traceback.format_exc()[-3000:]}))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:  # noqa: BLE001
+            pass
+
+
+def test_tensor_parallel_llama_matches_single_gpu():
+    world = 2
+    if torch.cuda.device_count() < world:
+        pytest.skip("needs 2 GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = [q.get(timeout=280) for _ in procs]
+    finally:
+        for p in procs:
+            p.join(timeout=20)
+            if p.is_alive():
+                p.kill()  # exact child processes started above
+    for rank, bad in res:
+        assert not bad, f"rank {rank}: {bad}"

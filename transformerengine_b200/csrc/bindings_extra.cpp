@@ -619,10 +619,10 @@ void ep_push(const at::Tensor& x, const at::Tensor& within, const at::Tensor& ba
   TORCH_CHECK(e == cudaSuccess, "ep_push failed: ", cudaGetErrorString(e));
 }
 
-void ep_wait(int64_t flags_ptr, int64_t n, int64_t epoch, const at::Tensor& status) {
+void ep_wait(int64_t flags_ptr, int64_t n, int64_t epoch, const at::Tensor& status, int64_t limit_cycles) {
   c10::cuda::CUDAGuard guard(status.device());
   cudaError_t e = teb200::ep_wait(reinterpret_cast<const uint32_t*>(flags_ptr), static_cast<int>(n),
-                                  static_cast<uint32_t>(epoch), status.data_ptr<int>(), cur_stream());
+                                  static_cast<uint32_t>(epoch), status.data_ptr<int>(), cur_stream(), limit_cycles);
   TORCH_CHECK(e == cudaSuccess, "ep_wait failed: ", cudaGetErrorString(e));
 }
 
@@ -753,7 +753,8 @@ void register_extra(py::module_& m) {
   m.def("peer_sum", &peer_sum);
   m.def("ep_counts", &ep_counts);
   m.def("ep_push", &ep_push);
-  m.def("ep_wait", &ep_wait);
+  m.def("ep_wait", &ep_wait, py::arg("flags_ptr"), py::arg("n"), py::arg("epoch"), py::arg("status"),
+        py::arg("limit_cycles") = 0);
   m.def("ep_signal", &ep_signal);
   m.def("ep_pull", &ep_pull);
   m.def("router_topk", &router_topk);

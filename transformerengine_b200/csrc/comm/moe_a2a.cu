@@ -139,8 +139,8 @@ __global__ void ep_push_kernel(EpPushArgs a) {
 }
 
 // ---- wait / signal ------------------------------------------------------------------------------------
-__global__ void ep_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status) {
-  if (threadIdx.x < n && !wait_flag_ge(flags + threadIdx.x, epoch)) atomicCAS(status, 0, kTimeoutPeerFlag);
+__global__ void ep_wait_kernel(const uint32_t* flags, int n, uint32_t epoch, int* status, long long limit) {
+  if (threadIdx.x < n && !wait_flag_ge(flags + threadIdx.x, epoch, limit)) atomicCAS(status, 0, kTimeoutPeerFlag);
 }
 __global__ void ep_signal_kernel(EpSignalArgs a) {
   __threadfence_system();
@@ -246,8 +246,8 @@ cudaError_t ep_push(const EpPushArgs& a, cudaStream_t s) {
   ep_push_kernel<<<static_cast<unsigned>(pairs < want ? pairs : want), 256, 0, s>>>(a);
   return cudaGetLastError();
 }
-cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s) {
-  ep_wait_kernel<<<1, 32, 0, s>>>(flags, n, epoch, status);
+cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s, long long limit_cycles) {
+  ep_wait_kernel<<<1, 32, 0, s>>>(flags, n, epoch, status, limit_cycles > 0 ? limit_cycles : kWaitCycles);
   return cudaGetLastError();
 }
 cudaError_t ep_signal(const EpSignalArgs& a, cudaStream_t s) {

@@ -119,7 +119,10 @@ struct PeerSumArgs {
 cudaError_t peer_sum(const PeerSumArgs& a, cudaStream_t s);
 cudaError_t ep_counts(const EpCountsArgs& a, cudaStream_t s);
 cudaError_t ep_push(const EpPushArgs& a, cudaStream_t s);
-cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s);
+// waits (bounded by limit_cycles SM clock cycles; 0 = the library default of about one second) until the n
+// flags reach `epoch`; on expiry *status becomes kTimeoutPeerFlag and the kernel returns
+cudaError_t ep_wait(const uint32_t* flags, int n, uint32_t epoch, int* status, cudaStream_t s,
+                    long long limit_cycles = 0);
 cudaError_t ep_signal(const EpSignalArgs& a, cudaStream_t s);
 cudaError_t ep_pull(const EpPullArgs& a, cudaStream_t s);
 

@@ -31,6 +31,17 @@ def weights_epoch() -> int:
     return _WEIGHTS_EPOCH[0]
 
 
+# While set, quantized-weight caches are served without looking at parameter versions: a CUDA graph
+# captured with cached weights re-quantizes them in place through ``requantize_cached_weights``.
+_FREEZE_WEIGHT_CACHE = [False]
+
+
+def freeze_weight_caches(flag: bool) -> bool:
+    old = _FREEZE_WEIGHT_CACHE[0]
+    _FREEZE_WEIGHT_CACHE[0] = bool(flag)
+    return old
+
+
 def get_distributed_world_size(group=None) -> int:
     if not torch.distributed.is_available() or not torch.distributed.is_initialized():
         return 1
@@ -216,16 +227,25 @@ class TransformerEngineBaseModule(torch.nn.Module):
         quantizer.internal = True
         key = (weight._version, weights_epoch(), need_columnwise, id(quantizer))
         ent = self._weight_cache.get(cache_name)
-        if ent is not None and is_first_microbatch is not True:
-            if is_first_microbatch is False or ent[0] == key:
+        if ent is not None and (is_first_microbatch is not True or _FREEZE_WEIGHT_CACHE[0]):
+            if is_first_microbatch is False or ent[0] == key or _FREEZE_WEIGHT_CACHE[0]:
                 if not need_columnwise or ent[1].get_usages()["columnwise"]:
                     return ent[1]
         q = quantizer(weight.detach())
-        self._weight_cache[cache_name] = (key, q)
+        self._weight_cache[cache_name] = (key, q, weight, quantizer)
         return q
 
     def reset_weight_cache(self) -> None:
         self._weight_cache.clear()
+
+    def requantize_cached_weights(self) -> None:
+        """Quantize every cached weight again INTO its existing storage, so that kernels recorded in a
+        CUDA graph (which hold those addresses) see the new values."""
+        for name, (key, q, weight, quantizer) in list(self._weight_cache.items()):
+            quantizer.set_usage(rowwise=True, columnwise=q.get_usages()["columnwise"])
+            quantizer.internal = True
+            quantizer.update_quantized(weight.detach(), q)
+            self._weight_cache[name] = ((weight._version, weights_epoch()) + tuple(key[2:]), q, weight, quantizer)
 
     # ------------------------------------------------------------------ checkpoint
     def get_extra_state(self) -> torch.Tensor:

@@ -56,6 +56,34 @@ def allreduce(x: torch.Tensor, group, async_op: bool = False):
     return x, h
 
 
+def allreduce_sequence_parallel_grads(model_or_params, group, *, average: bool = False) -> int:
+    """Sum, over the tensor-parallel group, the gradients of every parameter marked ``sequence_parallel``.
+
+    Under sequence parallelism the norm weights (and the biases added after a row-parallel layer) are
+    replicated, but each rank sees only its slice of the sequence, so each rank holds a partial
+    gradient.  Without this reduction the replicas drift apart.  One flat all-reduce per dtype; call it
+    after ``backward()`` and before the optimizer step.  Returns the number of gradients reduced."""
+    if get_world_size(group) == 1:
+        return 0
+    params = model_or_params.parameters() if isinstance(model_or_params, torch.nn.Module) else model_or_params
+    by_dtype: Dict[torch.dtype, list] = {}
+    for p in params:
+        if getattr(p, "sequence_parallel", False) and p.grad is not None:
+            by_dtype.setdefault(p.grad.dtype, []).append(p.grad)
+    n = 0
+    for grads in by_dtype.values():
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=group)
+        if average:
+            flat.div_(get_world_size(group))
+        off = 0
+        for g in grads:
+            g.copy_(flat[off:off + g.numel()].view_as(g))
+            off += g.numel()
+        n += len(grads)
+    return n
+
+
 def gather_mxfp8_along_first_dim(q, group):
     """All-gather an MXFP8 tensor sharded on its row dim without dequantizing.
 

@@ -44,6 +44,7 @@ def parse():
     ap.add_argument("--recipe", default="", help="override the configuration's recipe")
     ap.add_argument("--graph", type=int, default=-1, help="-1 auto (whole-step CUDA graph where supported), 0 off, 1 on")
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--profile", default="", help="write a per-kernel device-time table of 2 extra steps (rank 0) here")
     ap.add_argument("--fused-comm", type=int, default=1, help="fuse TP collectives into the GEMM kernels")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
     return ap.parse_args()
@@ -308,6 +309,68 @@ def build_case(args, rank, world):
     raise SystemExit(f"unknown --config {name}")
 
 
+def profile_steps(step_fn, path, rank, world, ms_per_step):
+    """Two more steps under torch.profiler (CUDA activity, rank 0): device time per kernel name, NCCL kernels
+    included, and the share of the step in which no kernel ran.  Profiled steps are never timed for the result."""
+    import torch
+    import torch.distributed as dist
+
+    n = 2
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if rank != 0:
+        for i in range(n):
+            step_fn(i)
+        torch.cuda.synchronize()
+        return
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as prof:
+        for i in range(n):
+            step_fn(i)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA]
+    spans = sorted((e.time_range.start, e.time_range.end) for e in ev)
+    busy, cur_s, cur_e = 0.0, None, None
+    for s0, e0 in spans:   # union of kernel intervals (kernels on different streams overlap)
+        if cur_e is None or s0 > cur_e:
+            busy += (cur_e - cur_s) if cur_e is not None else 0.0
+            cur_s, cur_e = s0, e0
+        else:
+            cur_e = max(cur_e, e0)
+    busy += (cur_e - cur_s) if cur_e is not None else 0.0
+    wall = (spans[-1][1] - spans[0][0]) if spans else 0.0
+    table = prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=80)
+    with open(path, "w") as f:
+        f.write(f"steps profiled: {n}; timed (unprofiled) step: {ms_per_step:.2f} ms\n")
+        f.write(f"device span of the profiled steps: {wall / 1e3 / n:.2f} ms/step; some kernel running: "
+                f"{busy / 1e3 / n:.2f} ms/step; idle: {(wall - busy) / 1e3 / n:.2f} ms/step\n\n")
+        f.write(table)
+
+
+def finish_process_group(world, graphs=()):
+    """Leave the job cleanly.  Captured graphs hold NCCL kernels: release them before the communicator goes,
+    and never let a stuck teardown keep the process (the result line is already printed)."""
+    import threading
+
+    import torch
+    import torch.distributed as dist
+
+    for g in graphs:
+        g.release()
+    torch.cuda.synchronize()
+    if world <= 1:
+        return
+    dist.barrier()
+    torch.cuda.synchronize()
+    t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+    t.start()
+    t.join(timeout=20)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if t.is_alive():
+        os._exit(0)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -369,6 +432,8 @@ def run_ours(args):
                "h2d_bytes_per_step": host[0].numel() * host[0].element_size(), "d2h_bytes_per_step": 4,
                "ms_per_step": ms2 / args.steps, "last_loss": losses[-1] if losses else None}
     te.check_status()
+    if args.profile:
+        profile_steps(step_device, args.profile, rank, world, ms / args.steps)
     if rank == 0:
         tflops = value * case["flops_per_token"] / 1e12 / world
         cfg = dict(case["config"])
@@ -381,8 +446,7 @@ def run_ours(args):
                "tflops_per_gpu": tflops, "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches),
                "peak_mem_gb": torch.cuda.max_memory_allocated() / 2**30}
         print(json.dumps(out), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish_process_group(world, [gstep] if use_graph else [])
 
 
 def run_reference(args):
@@ -500,6 +564,11 @@ def run_reference(args):
 
 
 if __name__ == "__main__":
+    if os.environ.get("TEB200_HANG_DUMP_S"):
+        # development aid: print every thread's Python stack and exit if the run takes longer than this
+        import faulthandler
+
+        faulthandler.dump_traceback_later(int(os.environ["TEB200_HANG_DUMP_S"]), exit=True)
     a = parse()
     if a.impl == "reference":
         run_reference(a)

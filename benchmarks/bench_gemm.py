@@ -1,4 +1,7 @@
-"""GEMM microbenchmark: tcgen05 kernels of this library vs torch.matmul (cuBLAS).
+"""GEMM microbenchmark: tcgen05 kernels of this library vs the libraries on the same box:
+torch.matmul (cuBLAS bf16) and ``torch._scaled_mm`` with block-wise E8M0 scales (the cuBLASLt MXFP8
+path that the reference calls, ``common/gemm/cublaslt_gemm.cu:500-535``).  The library GEMMs are
+timed for comparison only; nothing in the package calls them.
 
     python benchmarks/bench_gemm.py [--shapes llama|layer12288] [--iters 20]
 
@@ -68,7 +71,21 @@ def main():
         oa, ob = ops.as_operand(qa), ops.as_operand(qb)
         t_mx = time_fn(lambda: ops.gemm_nt(oa, ob, out=out), args.iters, flush)
         te.check_status()
+        # library MXFP8: same FP8 payload and the same 128x4-tile scale layout, viewed with torch's dtypes
+        t_lib_mx, lib_err = None, None
+        try:
+            a8, b8 = oa.data.view(torch.float8_e4m3fn), ob.data.view(torch.float8_e4m3fn)
+            sa, sb = oa.scale.view(torch.float8_e8m0fnu), ob.scale.view(torch.float8_e8m0fnu)
+            ref = torch._scaled_mm(a8, b8.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16)
+            ours = ops.gemm_nt(oa, ob, out_dtype=torch.bfloat16)
+            lib_err = ((ours.float() - ref.float()).norm() / ref.float().norm()).item()
+            t_lib_mx = time_fn(lambda: torch._scaled_mm(a8, b8.t(), scale_a=sa, scale_b=sb, out_dtype=torch.bfloat16),
+                               args.iters, flush)
+        except Exception as e:  # noqa: BLE001  (library path unavailable in this torch build)
+            lib_err = f"{type(e).__name__}: {str(e)[:120]}"
         row = dict(M=M, N=N, K=K, cublas_bf16_ms=t_lib, ours_bf16_ms=t_bf, ours_mxfp8_ms=t_mx,
+                   cublaslt_mxfp8_ms=t_lib_mx, cublaslt_mxfp8_tflops=(fl / t_lib_mx / 1e9) if t_lib_mx else None,
+                   ours_over_cublaslt_mxfp8=(t_lib_mx / t_mx) if t_lib_mx else None, mxfp8_rel_diff_vs_library=lib_err,
                    cublas_tflops=fl / t_lib / 1e9, ours_bf16_tflops=fl / t_bf / 1e9, ours_mxfp8_tflops=fl / t_mx / 1e9,
                    ours_bf16_frac_of_measured=fl / t_bf / 1e9 / peak)
         rows.append(row)

@@ -117,9 +117,11 @@ def _worker(rank, world, port, result_q):
                 torch.cuda.synchronize()
                 te.check_status()
                 tag = f"{recipe_name} fused={fused}"
-                # bf16: same math up to summation order; MXFP8: the sharded GEMMs quantize the same values
-                # (block scales are per 32 elements of a row / column, shards are multiples of 128)
-                tol = 2e-2 if recipe_name == "bf16" else 6e-2
+                # bf16: same math up to summation order.  MXFP8: the sharded GEMMs quantize the same blocks
+                # (32 elements of a row / column, shards are multiples of 128), but a last-bit difference of
+                # a partial sum can move an FP8 rounding decision by one step (2^-4 relative), so two correct
+                # runs differ by a few percent in the norm; the NCCL and the fused path give identical values
+                tol = 2e-2 if recipe_name == "bf16" else 1e-1
                 if abs(loss.item() - loss_ref.item()) > tol * max(1.0, abs(loss_ref.item())):
                     bad[f"{tag} loss"] = (loss.item(), loss_ref.item())
                 for n, p in model.named_parameters():
@@ -168,6 +170,7 @@ def _worker(rank, world, port, result_q):
                 bad[f"graph step {i}"] = (a, b)
         if gs.kernels_per_replay <= 0:
             bad["graph kernels"] = gs.kernels_per_replay
+        gs.release()
         result_q.put((rank, bad))
     except Exception:  # noqa: BLE001
         import traceback

@@ -70,8 +70,21 @@ __device__ __forceinline__ unsigned long long gtimer() {
 }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-__device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want) {
+// Once any wait of this process has run out, the status word is set and the results are void anyway:
+// later waits give up at once instead of each spending its full limit (a lost peer then costs about one
+// limit per kernel, not one per tile).
+__device__ __forceinline__ bool already_failed(const int* status) {
+  return status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0;
+}
+__device__ __forceinline__ bool wait_flag_ge_or_failed(const uint32_t* p, uint32_t want, const int* status) {
+  if (ld_acquire_sys(p) >= want) return true;
+  if (already_failed(status)) return false;
+  return wait_flag_ge(p, want);
+}
+
+__device__ __forceinline__ bool wait_ge_gpu(const uint32_t* p, uint32_t want, const int* status = nullptr) {
   if (ld_acquire_gpu(p) >= want) return true;
+  if (already_failed(status)) return false;
   const long long t0 = clock64();
   while (ld_acquire_gpu(p) < want) {
     if (clock64() - t0 > kWaitCycles) return false;
@@ -151,7 +164,7 @@ __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint6
     piece(q, src, dst, bytes, mb, srank);
     if (q % pieces_per_item == 0) {
       // first piece of an item: the source rank must have published its rows for this call
-      if (!wait_flag_ge(p.ready[p.rank] + srank, epoch)) {
+      if (!wait_flag_ge_or_failed(p.ready[p.rank] + srank, epoch, p.k.status)) {
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
@@ -245,7 +258,7 @@ __device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, ui
     const uint8_t* src; uint8_t* dst; int nrows, rbytes, srank; long long pitch;
     piece(q, src, dst, nrows, rbytes, pitch, srank);
     if (srank != p.rank && srank != last_rank_ok) {
-      if (!wait_flag_ge(p.ready[p.rank] + srank, epoch)) {
+      if (!wait_flag_ge_or_failed(p.ready[p.rank] + srank, epoch, p.k.status)) {
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
       last_rank_ok = srank;
@@ -309,7 +322,7 @@ __device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, 
     const int mbl = it % p.mb_per_rank, nb = it / p.mb_per_rank;
     if (et < p.world) {
       // one waiter per source rank
-      if (!wait_flag_ge(p.tile_flags[p.rank] + et * p.mb_per_rank + mbl, expected)) {
+      if (!wait_flag_ge_or_failed(p.tile_flags[p.rank] + et * p.mb_per_rank + mbl, expected, p.k.status)) {
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
@@ -453,7 +466,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = gemm_cta; ok && comm_tile(p, t, ti); t += gemm_ctas) {
         if (MODE == kCommAllGather && ti.mb / p.mb_per_rank != p.rank) {
           // rows of a peer: wait until a copy CTA has landed this 128-row block in local memory
-          if (!wait_ge_gpu(p.chunk_flags + ti.mb, epoch)) {
+          if (!wait_ge_gpu(p.chunk_flags + ti.mb, epoch, p.k.status)) {
             if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
           }
           fence_proxy_async_all();  // generic-proxy writes of the copy CTA -> TMA (async proxy) reads

@@ -110,6 +110,14 @@ class GraphedStep:
         self.replays += 1
         return self.static_outputs if self._is_tuple else self.static_outputs[0]
 
+    def release(self) -> None:
+        """Drop the recorded graph and its memory pool.  Do this before destroying a process group whose
+        collectives were recorded: tearing down a communicator that a live graph still references can block."""
+        self.static_outputs = ()
+        if self.graph is not None:
+            self.graph.reset()
+            self.graph = None
+
 
 def capture_step(step_fn: Callable, static_inputs: Sequence[torch.Tensor] = (), **kw) -> GraphedStep:
     """Record ``step_fn`` (a whole iteration) into one CUDA graph; see :class:`GraphedStep`."""

@@ -37,6 +37,17 @@ def get_batch_on_this_cp_rank(x: torch.Tensor, cp_size: int, cp_rank: int, seq_d
     return torch.cat([chunks[cp_rank], chunks[2 * cp_size - 1 - cp_rank]], dim=seq_dim)
 
 
+def _natural_order_index(half: int, cp_size: int, device=None) -> torch.Tensor:
+    """Index that reorders a sequence stored as the ranks' dual-chunk shards back to back (rank 0's two
+    chunks, rank 1's two chunks, ...) into natural token order: ``natural = stored.index_select(dim, idx)``."""
+    slot = [0] * (2 * cp_size)  # slot[c] = where chunk c sits in the stored order
+    for r in range(cp_size):
+        slot[r] = 2 * r
+        slot[2 * cp_size - 1 - r] = 2 * r + 1
+    a = torch.arange(half, device=device)
+    return torch.cat([a + slot[c] * half for c in range(2 * cp_size)])
+
+
 def pad_thd_sequences_for_cp(cu_seqlens: torch.Tensor, cp_size: int) -> torch.Tensor:
     """Cumulative lengths after padding every sequence to a multiple of ``2*cp``."""
     lens = cu_seqlens[1:] - cu_seqlens[:-1]
@@ -250,9 +261,30 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
         return fused_ring_attention(q, k, v, cp_group, scale, causal)
     if cp_comm_type == "p2p":
         return _RingAttention.apply(q, k, v, cp_group, cp_global_ranks, scale, causal, window)
+    from ..ops.attention import attention as attn_op
+
+    no_window = window is None or (window[0] < 0 and (window[1] < 0 or (causal and window[1] == 0)))
     if cp_comm_type == "all_gather":
         sq, sk = q.shape[2], k.shape[2]
         kg, vg = _AllGatherSeq.apply(k, cp_group), _AllGatherSeq.apply(v, cp_group)
+        if no_window:
+            # No s x s mask: with the gathered K/V put back in natural order, each of this rank's two
+            # query chunks is an ordinary causal attention (diagonal at the bottom-right corner) over the
+            # keys up to its own end, so the attention kernels run as they are.
+            if causal:
+                half = sk // 2
+                order = _natural_order_index(half, cp, q.device)
+                kf = torch.cat([kg[i] for i in range(cp)], dim=2).index_select(2, order)
+                vf = torch.cat([vg[i] for i in range(cp)], dim=2).index_select(2, order)
+                hq_ = sq // 2
+                outs = []
+                for qc, chunk in ((q[:, :, :hq_], me), (q[:, :, hq_:], 2 * cp - 1 - me)):
+                    n = (chunk + 1) * half
+                    outs.append(attn_op(qc, kf[:, :, :n], vf[:, :, :n], scale=scale, causal=True, bottom_right=True))
+                return torch.cat(outs, dim=2)
+            kf = torch.cat([kg[i] for i in range(cp)], dim=2)
+            vf = torch.cat([vg[i] for i in range(cp)], dim=2)
+            return attn_op(q, kf, vf, scale=scale, causal=False)
         kf = torch.cat([kg[i] for i in range(cp)], dim=2)
         vf = torch.cat([vg[i] for i in range(cp)], dim=2)
         if causal:
@@ -267,13 +299,17 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
         assert q.shape[1] % cp == 0 and k.shape[1] % cp == 0, "Ulysses needs heads divisible by the CP size"
         qh, kh, vh = (_SeqToHeads.apply(t, cp_group, True) for t in (q, k, v))
         s_full = qh.shape[2]
-        if causal:  # chunks arrive in rank order: positions follow the dual-chunk layout of every rank
-            pos = torch.cat([dual_chunk_positions(q.shape[2], cp, r, q.device) for r in range(cp)])
-            mask = _mask_for(pos, pos, True, window)
+        if causal:
+            # chunks arrive in rank order (dual-chunk layout of every rank): put the sequence in natural
+            # order, run plain causal attention over the head shard, and undo the permutation
+            order = _natural_order_index(q.shape[2] // 2, cp, q.device)
+            inverse = torch.empty_like(order)
+            inverse[order] = torch.arange(order.numel(), device=order.device)
+            qn, kn, vn = (t.index_select(2, order) for t in (qh, kh, vh))
+            on = attn_op(qn, kn, vn, scale=scale, causal=True, window=None if no_window else window)
+            oh = on.index_select(2, inverse)
         else:
-            mask = _mask_for(torch.arange(s_full, device=q.device), torch.arange(s_full, device=q.device), False,
-                             window)
-        oh = attention_ref(qh, kh, vh, scale=scale, attn_mask=mask)
+            oh = attn_op(qh, kh, vh, scale=scale, causal=False, window=None if no_window else window)
         return _SeqToHeads.apply(oh, cp_group, False)
     raise ValueError(f"unknown cp_comm_type {cp_comm_type}")
 

@@ -166,3 +166,23 @@ def test_numerics_debug_counts_saturated_and_flushed_values():
     nd.debug(True)
     assert nd.is_debug()
     nd.debug(False)
+
+
+def test_typed_config_reads_env_once_and_overrides():
+    from transformerengine_b200.utils import config as C
+
+    cfg = C.Config.from_env({"TEB200_FUSED_EP": "0", "TEB200_GEMM_BN": "128", "TEB200_ATTN": "library"})
+    assert cfg.fused_ep is False and cfg.gemm_tile_n == 128 and cfg.attention_backend == "library"
+    assert C.Config.from_env({}).fused_ep is True
+    import pytest as _pytest
+
+    with _pytest.raises(ValueError):
+        C.Config.from_env({"TEB200_GEMM_BN": "96"})
+    with _pytest.raises(ValueError):
+        C.Config.from_env({"TEB200_ATTN": "magic"})
+    before = C.get_config().fused_context_parallel
+    with C.override(fused_context_parallel=not before):
+        assert C.get_config().fused_context_parallel is (not before)
+    assert C.get_config().fused_context_parallel is before
+    text = C.get_config().describe()
+    assert "TEB200_FUSED_EP" in text and "NVTE_ALLOW_UNSAFE_PICKLE_EXTRA_STATE" in text

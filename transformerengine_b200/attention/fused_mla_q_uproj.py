@@ -23,7 +23,9 @@ from ..tensor.mxfp8 import MXFP8Quantizer, MXFP8TensorStorage
 class FusedMLAQUpProjRopeQuant:
     @classmethod
     def is_supported(cls) -> bool:
-        return int(os.environ.get("NVTE_FUSED_MLA_Q_UPROJ", "1")) > 0
+        from ..utils.config import get_config
+
+        return get_config().fused_mla_q_uproj
 
     @staticmethod
     def _rope_last(q: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:

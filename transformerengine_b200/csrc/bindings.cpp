@@ -246,39 +246,29 @@ void multi_tensor_apply(const std::vector<std::vector<at::Tensor>>& lists, int64
     }
   }
   teb200::MultiTensorTable tab;
-  int nten = 0, nblk = 0, base = 0;
+  int nten = 0, base = 0;
+  int64_t nchunks = 0;
+  tab.chunk_start[0] = 0;
+  auto flush = [&]() {
+    if (nten == 0) return;
+    tab.ntensors = nten;
+    launch(tab, static_cast<int>(nchunks), base);
+    base += nten;
+    nten = 0;
+    nchunks = 0;
+  };
   for (size_t i = 0; i < nt; ++i) {
     const int64_t n = lists[0][i].numel();
     if (n == 0) continue;
+    const int64_t c = (n + chunk - 1) / chunk;
+    if (nten == teb200::kMtMaxTensors || nchunks + c > (int64_t{1} << 30)) flush();
     for (size_t k = 0; k < lists.size(); ++k) tab.ptr[k][nten] = lists[k][i].data_ptr();
     tab.numel[nten] = n;
-    const int64_t nchunks = (n + chunk - 1) / chunk;
+    nchunks += c;
     ++nten;
-    for (int64_t c = 0; c < nchunks; ++c) {
-      tab.block_tensor[nblk] = static_cast<uint8_t>(nten - 1);
-      tab.block_chunk[nblk] = static_cast<int32_t>(c);
-      ++nblk;
-      const bool last_chunk = c == nchunks - 1;
-      const bool tensors_full = nten == teb200::kMtMaxTensors && last_chunk;
-      const bool blocks_full = nblk == teb200::kMtMaxBlocks;
-      const bool final_item = i == nt - 1 && last_chunk;
-      if (tensors_full || blocks_full || final_item) {
-        launch(tab, nblk, base);
-        nblk = 0;
-        if (last_chunk) {
-          base += nten;
-          nten = 0;
-        } else {
-          // carry the unfinished tensor over as slot 0 of the next table
-          for (size_t k = 0; k < lists.size(); ++k) tab.ptr[k][0] = tab.ptr[k][nten - 1];
-          tab.numel[0] = tab.numel[nten - 1];
-          base += nten - 1;
-          nten = 1;
-        }
-      }
-    }
+    tab.chunk_start[nten] = static_cast<int32_t>(nchunks);
   }
-  if (nblk > 0) launch(tab, nblk, base);
+  flush();
 }
 
 void multi_tensor_adam(std::vector<std::vector<at::Tensor>> lists, double lr, double beta1, double beta2, double eps,

@@ -7,6 +7,11 @@
 //   CTA rank 0 (leader): TMA producer, MMA issuer for the pair, epilogue of rows 0..127
 //   CTA rank 1 (partner): TMA producer (signals the leader's barriers), epilogue of rows 128..255
 //
+// Epilogue: the four epilogue warps of each CTA move the accumulator TMEM -> registers -> shared memory
+// (128-byte-swizzled boxes) and release the accumulator as soon as the last column has been read; TMA
+// stores (or TMA reduce-adds when accumulating into fp32) carry the boxes to global memory while the
+// next tile's MMAs already run.
+//
 // "Stage full" barriers live in the leader and count the bytes of both CTAs; "stage empty" and
 // "accumulator full" are committed to the same-offset barrier of both CTAs; "accumulator empty"
 // lives in the leader and is arrived on by the epilogue warps of both CTAs.  All loads fill
@@ -31,11 +36,15 @@ struct PairCfg {
   static constexpr int kSfaBytes = KIND == kKindMxf8 ? 512 : 0;
   static constexpr int kSfbBytes = KIND == kKindMxf8 ? 512 * (PN / 128) : 0;
   static constexpr int kStageBytes = ((kABytes + kBBytes + kSfaBytes + kSfbBytes + 1023) / 1024) * 1024;
-  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;
+  // epilogue staging: two boxes of 128 rows x 128 bytes (ping-pong), written by the epilogue warps and
+  // read by TMA stores, so the accumulator is drained at shared-memory speed
+  static constexpr int kBoxBytes = 128 * 128;
+  static constexpr int kStagingBytes = 2 * kBoxBytes;
+  static constexpr int kStages = (227 * 1024 - 2048 - kStagingBytes) / kStageBytes;
   static constexpr int kSfaCols = KIND == kKindMxf8 ? 4 : 0;
   static constexpr int kSfbCols = KIND == kKindMxf8 ? 4 * (PN / 128) : 0;
   static constexpr int kAccStages = (2 * PN + kSfaCols + kSfbCols <= 512) ? 2 : 1;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 2048;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 2048;
   static constexpr int kBlockK = KIND == kKindF16 ? 64 : 128;
   // bytes that land per stage over BOTH CTAs (every CTA loads the whole B scale block)
   static constexpr uint32_t kTxBytes = 2u * (kABytes + kBBytes + kSfaBytes + kSfbBytes);
@@ -62,11 +71,12 @@ template <int KIND>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
-                 const PairParams p) {
+                 const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
   using C = PairCfg<KIND>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kStages * C::kStageBytes);
+  uint8_t* staging = smem + C::kStages * C::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + C::kStagingBytes);
   uint64_t* full_bar = bars;                       // used in the leader only
   uint64_t* empty_bar = bars + C::kStages;         // one copy per CTA
   uint64_t* tfull_bar = bars + 2 * C::kStages;     // one copy per CTA
@@ -84,6 +94,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (threadIdx.x == 0) {
     prefetch_tensormap(&tmap_a);
     prefetch_tensormap(&tmap_b);
+    prefetch_tensormap(&tmap_d);
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(&full_bar[i], 1);
       mbar_init(&empty_bar[i], 1);
@@ -208,42 +219,57 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
+    const int et = quarter * 32 + lane;       // row of this thread inside the CTA's 128 rows
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
-    const bool bf = p.k.d_dtype == kBFloat16;
+    const int dt = p.k.d_dtype;
+    const bool wide = dt == kFloat32;          // a box (128 bytes per row) holds 32 fp32 or 64 16-bit columns
+    const int box_cols = wide ? 32 : 64;
+    const int boxes_per_tile = PN / box_cols;
+    uint32_t box_count = 0;                    // boxes handed to TMA so far (ping-pong over two buffers)
+    uint8_t* my_row = staging + et * 128;
+    const int sw = et & 7;
     int mb, nb;
+    bool dead = false;  // a wait ran out: keep walking the loop (the named barriers need all four warps), wait no more
     for (int t = pair; pair_tile(p, t, mb, nb); t += num_pairs) {
-      if (!mbar_wait_cluster(&tfull_bar[acc], acc_phase)) {
+      if (!dead && !mbar_wait_cluster(&tfull_bar[acc], acc_phase)) {
         if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
-        break;
+        dead = true;
       }
       tc_fence_after();
-      const int row = mb * PM + static_cast<int>(rank) * 128 + quarter * 32 + lane;
+      const int row0 = mb * PM + static_cast<int>(rank) * 128;
       const int n0 = nb * PN;
-      const bool row_ok = row < p.k.M;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * PN;
-      {
 #pragma unroll 1
-        for (int c0 = 0; c0 < PN; c0 += 32) {
+      for (int bx = 0; bx < boxes_per_tile; ++bx, ++box_count) {
+        uint8_t* buf = my_row + (box_count & 1) * C::kBoxBytes;
+        if (box_count >= 2) {
+          // the store that last read this buffer (two boxes ago) must have finished reading it
+          if (et == 0) tma_store_wait_read<1>();
+          named_bar_sync(1, 128);
+        }
+        const int chunks = wide ? 1 : 2;       // 32 accumulator columns per chunk
+#pragma unroll 1
+        for (int ch = 0; ch < chunks; ++ch) {
+          const int c0 = bx * box_cols + ch * 32;
           uint32_t r[32];
           tmem_ld_32x32(taddr + c0, r);
           tmem_ld_wait();
-          if (c0 + 32 >= PN) {
+          if (bx == boxes_per_tile - 1 && ch == chunks - 1) {
+            // every column of the accumulator is in registers: the MMA warp may overwrite it
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
           }
-          const int col0 = n0 + c0;
-          if (!row_ok || col0 >= p.k.N) continue;
           float v[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-          const int ncols = min(32, p.k.N - col0);
           if (p.k.bias != nullptr) {
+            const int col0 = n0 + c0;
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              if (i < ncols) {
+              if (col0 + i < p.k.N) {
                 float b;
                 if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
                 else if (p.k.bias_dtype == kBFloat16)
@@ -253,56 +279,41 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           }
-          const size_t off = static_cast<size_t>(row) * p.k.ldd + col0;
-          if (p.k.d_dtype == kFloat32) {
-            float* dp = reinterpret_cast<float*>(p.k.d) + off;
-            if (ncols == 32 && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
+          if (wide) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 4) {
-                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                if (p.k.accumulate) {
-                  const float4 old = *reinterpret_cast<const float4*>(dp + i);
-                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                }
-                *reinterpret_cast<float4*>(dp + i) = o;
-              }
-            } else {
-              for (int i = 0; i < ncols; ++i) dp[i] = v[i] + (p.k.accumulate ? dp[i] : 0.f);
-            }
+            for (int c = 0; c < 8; ++c)
+              *reinterpret_cast<float4*>(buf + ((c ^ sw) << 4)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
           } else {
-            uint16_t* dp = reinterpret_cast<uint16_t*>(p.k.d) + off;
-            if (ncols == 32 && !p.k.accumulate && (reinterpret_cast<uintptr_t>(dp) & 15) == 0) {
 #pragma unroll
-              for (int i = 0; i < 32; i += 8) {
-                uint4 o;
-                if (bf) {
-                  o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
-                                 pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
-                } else {
-                  o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
-                                 pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
-                }
-                *reinterpret_cast<uint4*>(dp + i) = o;
+            for (int c = 0; c < 4; ++c) {
+              const int i = 8 * c;
+              uint4 o;
+              if (dt == kBFloat16) {
+                o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
+                               pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
+              } else {
+                o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
+                               pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
               }
-            } else {
-              for (int i = 0; i < ncols; ++i) {
-                float x = v[i];
-                if (bf) {
-                  __nv_bfloat16* q = reinterpret_cast<__nv_bfloat16*>(dp) + i;
-                  if (p.k.accumulate) x += __bfloat162float(*q);
-                  *q = __float2bfloat16(x);
-                } else {
-                  __half* q = reinterpret_cast<__half*>(dp) + i;
-                  if (p.k.accumulate) x += __half2float(*q);
-                  *q = __float2half(x);
-                }
-              }
+              *reinterpret_cast<uint4*>(buf + (((ch * 4 + c) ^ sw) << 4)) = o;
             }
           }
+        }
+        fence_proxy_async_smem();  // generic-proxy writes to shared memory -> TMA (async proxy) read
+        named_bar_sync(1, 128);
+        if (et == 0) {
+          const uint8_t* src = staging + (box_count & 1) * C::kBoxBytes;
+          const int col = n0 + bx * box_cols;
+          if (col < p.k.N && row0 < p.k.M) {   // boxes wholly outside the matrix are skipped, the rest is clipped
+            if (p.k.accumulate) tma_reduce_add_2d(&tmap_d, src, col, row0);
+            else tma_store_2d(&tmap_d, src, col, row0);
+          }
+          tma_store_commit();
         }
       }
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
+    if (et == 0) tma_store_wait<0>();  // shared memory stays valid until the last store has read it
   }
 
   tc_fence_before();
@@ -334,6 +345,10 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
     ok = ok && make_tensor_map_2d(&tsa, a.sfa, kFloat32, ta_tiles, 128, 128, 1, 128, false) &&
          make_tensor_map_2d(&tsb, a.sfb, kFloat32, tb_tiles, 128, 128, 1, 128, false);
   }
+  // output boxes: 128 rows x 128 bytes, 128-byte swizzle (what the epilogue writes to shared memory)
+  CUtensorMap td;
+  const int d_es = a.d_dtype == kFloat32 ? 4 : 2;
+  ok = ok && make_tensor_map_2d(&td, a.d, a.d_dtype, a.M, a.N, a.ldd, 128, 128 / d_es, true);
   if (!ok) return cudaErrorInvalidValue;
   PairParams p = {};
   KernelParams& k = p.k;
@@ -381,7 +396,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   long long pairs = max_pairs < sms / 2 ? max_pairs : sms / 2;
   if (tiles < pairs) pairs = tiles;
   if (pairs < 1) pairs = 1;
-  gemm_pair_kernel<KIND><<<static_cast<int>(pairs * 2), kNumThreads, C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, p);
+  gemm_pair_kernel<KIND><<<static_cast<int>(pairs * 2), kNumThreads, C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, td, p);
   return cudaGetLastError();
 }
 
@@ -392,6 +407,10 @@ bool gemm_pair_supported(const GemmArgs& a, bool mxfp8) {
   if (a.epilogue != kEpiNone && a.epilogue != kEpiBias) return false;
   if (a.M < 256 || a.N < 256) return false;
   if (mxfp8 && a.K % 128 != 0) return false;
+  // the epilogue leaves through TMA: 16-byte aligned output rows; accumulation is a TMA reduce-add (fp32 only)
+  const int d_es = a.d_dtype == kFloat32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(a.d) & 15) != 0 || (a.ldd * d_es) % 16 != 0) return false;
+  if (a.accumulate && a.d_dtype != kFloat32) return false;
   return true;
 }
 

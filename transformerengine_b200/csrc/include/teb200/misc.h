@@ -7,15 +7,18 @@
 namespace teb200 {
 
 // ---------------------------------------------------------------- multi-tensor apply
-constexpr int kMtMaxTensors = 24;
-constexpr int kMtMaxBlocks = 320;
+// One launch covers up to kMtMaxTensors tensors of any size.  The work is cut in chunks of `chunk`
+// elements; chunk c of the launch belongs to the tensor ti with chunk_start[ti] <= c < chunk_start[ti+1].
+// A fixed grid (a few blocks per SM) strides over the chunks, so the number of launches depends on the
+// number of tensors only and no launch ends in a part-filled wave of blocks.
+constexpr int kMtMaxTensors = 56;
 constexpr int kMtLists = 5;
 
 struct MultiTensorTable {
   void* ptr[kMtLists][kMtMaxTensors];
   int64_t numel[kMtMaxTensors];
-  uint8_t block_tensor[kMtMaxBlocks];
-  int32_t block_chunk[kMtMaxBlocks];
+  int32_t chunk_start[kMtMaxTensors + 1];
+  int32_t ntensors;
 };
 
 struct AdamArgs {
@@ -37,7 +40,7 @@ struct AdamArgs {
   int bias_correction = 1;
   int64_t chunk = 0;
 };
-cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nblocks, const AdamArgs& a, cudaStream_t s);
+cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nchunks, const AdamArgs& a, cudaStream_t s);
 
 struct SgdArgs {
   float lr = 0, momentum = 0, dampening = 0, weight_decay = 0, grad_scale = 1.f;
@@ -46,12 +49,12 @@ struct SgdArgs {
   const int* noop = nullptr;
   int64_t chunk = 0;
 };
-cudaError_t multi_tensor_sgd(const MultiTensorTable& t, int nblocks, const SgdArgs& a, cudaStream_t s);
+cudaError_t multi_tensor_sgd(const MultiTensorTable& t, int nchunks, const SgdArgs& a, cudaStream_t s);
 // out (list 1) = in (list 0) * scale, dtype conversions allowed; sets *noop on non-finite input
-cudaError_t multi_tensor_scale(const MultiTensorTable& t, int nblocks, int in_dtype, int out_dtype, float scale,
+cudaError_t multi_tensor_scale(const MultiTensorTable& t, int nchunks, int in_dtype, int out_dtype, float scale,
                                int* noop, int64_t chunk, cudaStream_t s);
 // sum of squares of list 0 accumulated into out[0] (and per tensor into per_tensor[i] when not null)
-cudaError_t multi_tensor_l2norm_sq(const MultiTensorTable& t, int nblocks, int dtype, float* out,
+cudaError_t multi_tensor_l2norm_sq(const MultiTensorTable& t, int nchunks, int dtype, float* out,
                                    float* per_tensor, int tensor_base, int64_t chunk, cudaStream_t s);
 
 // ---------------------------------------------------------------- cross entropy

@@ -1,6 +1,7 @@
-// Multi-tensor optimizer kernels: one launch updates up to kMtMaxTensors tensors,
-// each split in chunks that map to thread blocks through a table passed by value
-// in the kernel arguments (no device-side table upload, CUDA-graph friendly).
+// Multi-tensor optimizer kernels: one launch updates up to kMtMaxTensors tensors of any size.
+// The tensors are cut in chunks; a fixed grid strides over the chunks and finds each chunk's
+// tensor in a prefix table passed by value in the kernel arguments (no device-side table upload,
+// CUDA-graph friendly).
 // Math follows the reference Adam functor (common/multi_tensor/adam.cu:124-143):
 //   m = b1*m + (1-b1)*g ; v = b2*v + (1-b2)*g*g ; denom = sqrt(v/bc2) + eps
 //   AdamW: p -= lr*((m/bc1)/denom + wd*p) ; L2 mode adds wd*p to g first.
@@ -13,7 +14,18 @@
 namespace teb200 {
 namespace {
 
-constexpr int NT = 512;
+constexpr int NT = 256;
+
+// Chunk c -> tensor index (advancing ti; c only grows inside a block's loop) and the chunk's element range.
+__device__ __forceinline__ bool mt_chunk(const MultiTensorTable& t, int c, int nchunks, int64_t chunk, int& ti,
+                                         int64_t& start, int64_t& end) {
+  if (c >= nchunks) return false;
+  while (c >= t.chunk_start[ti + 1]) ++ti;
+  start = static_cast<int64_t>(c - t.chunk_start[ti]) * chunk;
+  const int64_t n = t.numel[ti];
+  end = start + chunk < n ? start + chunk : n;
+  return true;
+}
 
 template <typename T>
 struct alignas(sizeof(T) * 4) V4 {
@@ -24,12 +36,12 @@ template <typename T>
 __device__ __forceinline__ float ldf(const T* p, int64_t i) { return static_cast<float>(p[i]); }
 
 template <typename G, typename P, typename S>
-__global__ void __launch_bounds__(NT) adam_kernel(const MultiTensorTable t, const AdamArgs a) {
+__global__ void __launch_bounds__(NT) adam_kernel(const __grid_constant__ MultiTensorTable t, const AdamArgs a,
+                                                  const int nchunks) {
   if (a.noop != nullptr && *a.noop != 0) return;
-  const int ti = t.block_tensor[blockIdx.x];
-  const int64_t n = t.numel[ti];
-  const int64_t start = static_cast<int64_t>(t.block_chunk[blockIdx.x]) * a.chunk;
-  const int64_t end = start + a.chunk < n ? start + a.chunk : n;
+  int ti = 0;
+  int64_t start, end;
+  for (int c = blockIdx.x; mt_chunk(t, c, nchunks, a.chunk, ti, start, end); c += gridDim.x) {
   const G* g = static_cast<const G*>(t.ptr[0][ti]);
   P* p = static_cast<P*>(t.ptr[1][ti]);
   S* m = static_cast<S*>(t.ptr[2][ti]);
@@ -73,7 +85,7 @@ __global__ void __launch_bounds__(NT) adam_kernel(const MultiTensorTable t, cons
         pb[i] = static_cast<uint16_t>(nh);
       }
     }
-    return;
+    continue;
   }
   // 4 elements per thread per iteration; tensors are 16-byte aligned and chunks are multiples of 4
   for (int64_t i = start + threadIdx.x * 4; i < end; i += NT * 4) {
@@ -149,15 +161,16 @@ __global__ void __launch_bounds__(NT) adam_kernel(const MultiTensorTable t, cons
       }
     }
   }
+  }
 }
 
 template <typename G, typename P>
-__global__ void __launch_bounds__(NT) sgd_kernel(const MultiTensorTable t, const SgdArgs a) {
+__global__ void __launch_bounds__(NT) sgd_kernel(const __grid_constant__ MultiTensorTable t, const SgdArgs a,
+                                                 const int nchunks) {
   if (a.noop != nullptr && *a.noop != 0) return;
-  const int ti = t.block_tensor[blockIdx.x];
-  const int64_t n = t.numel[ti];
-  const int64_t start = static_cast<int64_t>(t.block_chunk[blockIdx.x]) * a.chunk;
-  const int64_t end = start + a.chunk < n ? start + a.chunk : n;
+  int ti = 0;
+  int64_t start, end;
+  for (int c = blockIdx.x; mt_chunk(t, c, nchunks, a.chunk, ti, start, end); c += gridDim.x) {
   const G* g = static_cast<const G*>(t.ptr[0][ti]);
   P* p = static_cast<P*>(t.ptr[1][ti]);
   float* mom = static_cast<float*>(t.ptr[2][ti]);
@@ -176,57 +189,76 @@ __global__ void __launch_bounds__(NT) sgd_kernel(const MultiTensorTable t, const
     if (master) master[i] = w;
     p[i] = static_cast<P>(w);
   }
+  }
 }
 
 template <typename I, typename O>
-__global__ void __launch_bounds__(NT) scale_kernel(const MultiTensorTable t, float scale, int* noop, int64_t chunk) {
-  const int ti = t.block_tensor[blockIdx.x];
-  const int64_t n = t.numel[ti];
-  const int64_t start = static_cast<int64_t>(t.block_chunk[blockIdx.x]) * chunk;
-  const int64_t end = start + chunk < n ? start + chunk : n;
-  const I* in = static_cast<const I*>(t.ptr[0][ti]);
-  O* out = static_cast<O*>(t.ptr[1][ti]);
+__global__ void __launch_bounds__(NT) scale_kernel(const __grid_constant__ MultiTensorTable t, float scale, int* noop,
+                                                   int64_t chunk, const int nchunks) {
   bool bad = false;
-  for (int64_t i = start + threadIdx.x; i < end; i += NT) {
-    const float x = ldf(in, i);
-    bad |= !isfinite(x);
-    out[i] = static_cast<O>(x * scale);
+  int ti = 0;
+  int64_t start, end;
+  for (int c = blockIdx.x; mt_chunk(t, c, nchunks, chunk, ti, start, end); c += gridDim.x) {
+    const I* in = static_cast<const I*>(t.ptr[0][ti]);
+    O* out = static_cast<O*>(t.ptr[1][ti]);
+    for (int64_t i = start + threadIdx.x; i < end; i += NT) {
+      const float x = ldf(in, i);
+      bad |= !isfinite(x);
+      out[i] = static_cast<O>(x * scale);
+    }
   }
   if (bad && noop != nullptr) *noop = 1;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(NT) l2norm_kernel(const MultiTensorTable t, float* out, float* per_tensor,
-                                                    int tensor_base, int64_t chunk) {
-  const int ti = t.block_tensor[blockIdx.x];
-  const int64_t n = t.numel[ti];
-  const int64_t start = static_cast<int64_t>(t.block_chunk[blockIdx.x]) * chunk;
-  const int64_t end = start + chunk < n ? start + chunk : n;
-  const T* in = static_cast<const T*>(t.ptr[0][ti]);
-  float s = 0.f;
-  for (int64_t i = start + threadIdx.x; i < end; i += NT) {
-    const float x = ldf(in, i);
-    s += x * x;
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+__global__ void __launch_bounds__(NT) l2norm_kernel(const __grid_constant__ MultiTensorTable t, float* out,
+                                                    float* per_tensor, int tensor_base, int64_t chunk,
+                                                    const int nchunks) {
   __shared__ float red[NT / 32];
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    float tot = 0.f;
-    for (int i = 0; i < NT / 32; ++i) tot += red[i];
-    atomicAdd(out, tot);
-    if (per_tensor != nullptr) atomicAdd(per_tensor + tensor_base + ti, tot);
+  int ti = 0;
+  int64_t start, end;
+  for (int c = blockIdx.x; mt_chunk(t, c, nchunks, chunk, ti, start, end); c += gridDim.x) {
+    const T* in = static_cast<const T*>(t.ptr[0][ti]);
+    float s = 0.f;
+    for (int64_t i = start + threadIdx.x; i < end; i += NT) {
+      const float x = ldf(in, i);
+      s += x * x;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float tot = 0.f;
+      for (int i = 0; i < NT / 32; ++i) tot += red[i];
+      atomicAdd(out, tot);
+      if (per_tensor != nullptr) atomicAdd(per_tensor + tensor_base + ti, tot);
+    }
+    __syncthreads();
   }
 }
 
 }  // namespace
 
-#define TEB_ADAM(G, P, S) adam_kernel<G, P, S><<<nblocks, NT, 0, s>>>(t, a)
+// a few blocks per SM stride over all chunks of the launch
+int mt_grid(int nchunks) {
+  static int sms[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (sms[dev] == 0) {
+    int n = 148;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms[dev] = n > 0 ? n : 148;
+  }
+  const int cap = sms[dev] * 6;
+  return nchunks < cap ? nchunks : cap;
+}
 
-cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nblocks, const AdamArgs& a, cudaStream_t s) {
-  if (nblocks <= 0) return cudaSuccess;
+#define TEB_ADAM(G, P, S) adam_kernel<G, P, S><<<mt_grid(nchunks), NT, 0, s>>>(t, a, nchunks)
+
+cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nchunks, const AdamArgs& a, cudaStream_t s) {
+  if (nchunks <= 0) return cudaSuccess;
   using bf = __nv_bfloat16;
   const int g = a.grad_dtype, p = a.param_dtype, st = a.state_dtype;
   if (st == kFloat32) {
@@ -248,22 +280,22 @@ cudaError_t multi_tensor_adam(const MultiTensorTable& t, int nblocks, const Adam
   return cudaGetLastError();
 }
 
-cudaError_t multi_tensor_sgd(const MultiTensorTable& t, int nblocks, const SgdArgs& a, cudaStream_t s) {
-  if (nblocks <= 0) return cudaSuccess;
+cudaError_t multi_tensor_sgd(const MultiTensorTable& t, int nchunks, const SgdArgs& a, cudaStream_t s) {
+  if (nchunks <= 0) return cudaSuccess;
   using bf = __nv_bfloat16;
-  if (a.grad_dtype == kFloat32 && a.param_dtype == kFloat32) sgd_kernel<float, float><<<nblocks, NT, 0, s>>>(t, a);
-  else if (a.grad_dtype == kBFloat16 && a.param_dtype == kBFloat16) sgd_kernel<bf, bf><<<nblocks, NT, 0, s>>>(t, a);
-  else if (a.grad_dtype == kFloat32 && a.param_dtype == kBFloat16) sgd_kernel<float, bf><<<nblocks, NT, 0, s>>>(t, a);
-  else if (a.grad_dtype == kFloat16 && a.param_dtype == kFloat16) sgd_kernel<__half, __half><<<nblocks, NT, 0, s>>>(t, a);
+  if (a.grad_dtype == kFloat32 && a.param_dtype == kFloat32) sgd_kernel<float, float><<<mt_grid(nchunks), NT, 0, s>>>(t, a, nchunks);
+  else if (a.grad_dtype == kBFloat16 && a.param_dtype == kBFloat16) sgd_kernel<bf, bf><<<mt_grid(nchunks), NT, 0, s>>>(t, a, nchunks);
+  else if (a.grad_dtype == kFloat32 && a.param_dtype == kBFloat16) sgd_kernel<float, bf><<<mt_grid(nchunks), NT, 0, s>>>(t, a, nchunks);
+  else if (a.grad_dtype == kFloat16 && a.param_dtype == kFloat16) sgd_kernel<__half, __half><<<mt_grid(nchunks), NT, 0, s>>>(t, a, nchunks);
   else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }
 
-cudaError_t multi_tensor_scale(const MultiTensorTable& t, int nblocks, int in_dtype, int out_dtype, float scale,
+cudaError_t multi_tensor_scale(const MultiTensorTable& t, int nchunks, int in_dtype, int out_dtype, float scale,
                                int* noop, int64_t chunk, cudaStream_t s) {
-  if (nblocks <= 0) return cudaSuccess;
+  if (nchunks <= 0) return cudaSuccess;
   using bf = __nv_bfloat16;
-#define TEB_SCALE(I, O) scale_kernel<I, O><<<nblocks, NT, 0, s>>>(t, scale, noop, chunk)
+#define TEB_SCALE(I, O) scale_kernel<I, O><<<mt_grid(nchunks), NT, 0, s>>>(t, scale, noop, chunk, nchunks)
   if (in_dtype == kFloat32 && out_dtype == kFloat32) TEB_SCALE(float, float);
   else if (in_dtype == kBFloat16 && out_dtype == kBFloat16) TEB_SCALE(bf, bf);
   else if (in_dtype == kBFloat16 && out_dtype == kFloat32) TEB_SCALE(bf, float);
@@ -275,12 +307,12 @@ cudaError_t multi_tensor_scale(const MultiTensorTable& t, int nblocks, int in_dt
   return cudaGetLastError();
 }
 
-cudaError_t multi_tensor_l2norm_sq(const MultiTensorTable& t, int nblocks, int dtype, float* out, float* per_tensor,
+cudaError_t multi_tensor_l2norm_sq(const MultiTensorTable& t, int nchunks, int dtype, float* out, float* per_tensor,
                                    int tensor_base, int64_t chunk, cudaStream_t s) {
-  if (nblocks <= 0) return cudaSuccess;
-  if (dtype == kFloat32) l2norm_kernel<float><<<nblocks, NT, 0, s>>>(t, out, per_tensor, tensor_base, chunk);
-  else if (dtype == kBFloat16) l2norm_kernel<__nv_bfloat16><<<nblocks, NT, 0, s>>>(t, out, per_tensor, tensor_base, chunk);
-  else if (dtype == kFloat16) l2norm_kernel<__half><<<nblocks, NT, 0, s>>>(t, out, per_tensor, tensor_base, chunk);
+  if (nchunks <= 0) return cudaSuccess;
+  if (dtype == kFloat32) l2norm_kernel<float><<<mt_grid(nchunks), NT, 0, s>>>(t, out, per_tensor, tensor_base, chunk, nchunks);
+  else if (dtype == kBFloat16) l2norm_kernel<__nv_bfloat16><<<mt_grid(nchunks), NT, 0, s>>>(t, out, per_tensor, tensor_base, chunk, nchunks);
+  else if (dtype == kFloat16) l2norm_kernel<__half><<<mt_grid(nchunks), NT, 0, s>>>(t, out, per_tensor, tensor_base, chunk, nchunks);
   else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }

@@ -20,6 +20,7 @@ from ..modules.linear import Linear
 from ..moe import (fused_moe_aux_loss, fused_topk_with_score_function, moe_permute_and_pad_with_probs,
                    moe_unpermute)
 from ..parallel import distributed as D
+from ..utils.config import get_config
 from ..parallel.expert_parallel import (ep_combine, ep_dispatch, fused_ep_combine, fused_ep_dispatch,
                                         get_fused_ep)
 from .llama import _FusedCrossEntropy
@@ -110,7 +111,7 @@ class MoELayer(torch.nn.Module):
         else:
             tpe, total = tokens_per_expert, T
         aux = fused_moe_aux_loss(scores, tpe, total, cfg.num_experts, topk=cfg.topk, coeff=cfg.aux_loss_coeff)
-        fused = self.ep_size > 1 and x.is_cuda and os.environ.get("TEB200_FUSED_EP", "1") == "1" \
+        fused = self.ep_size > 1 and x.is_cuda and get_config().fused_ep \
             and x.dtype in (torch.bfloat16, torch.float16)
         if fused:
             ep = get_fused_ep(self.ep_group, self.local_experts, cfg.hidden_size, T, x.dtype, cfg.pad_align, cfg.topk)

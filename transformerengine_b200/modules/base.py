@@ -286,7 +286,9 @@ class TransformerEngineBaseModule(torch.nn.Module):
             raw = state.read()
         else:
             raise RuntimeError("Unsupported checkpoint format.")
-        if os.getenv(_UNSAFE_PICKLE_ENV, "0") == "1":
+        from ..utils.config import get_config
+
+        if get_config().allow_unsafe_pickle_extra_state or os.getenv(_UNSAFE_PICKLE_ENV, "0") == "1":
             obj = pickle.loads(raw)
         else:
             obj = _SafeUnpickler(io.BytesIO(raw)).load()

@@ -77,8 +77,11 @@ def attention_ref(q, k, v, *, scale=None, causal=False, window=None, attn_mask=N
 
 
 _USE_LIBRARY_SDPA = True
-# TEB200_ATTN=library routes the plain 16-bit case to torch's SDPA instead of csrc/attn (A/B timing)
-_USE_OWN_FLASH = os.environ.get("TEB200_ATTN", "own") != "library"
+# attention_backend='library' (TEB200_ATTN=library) routes the plain 16-bit case to torch's SDPA instead of
+# csrc/attn (A/B timing)
+from ..utils.config import get_config as _get_config  # noqa: E402
+
+_USE_OWN_FLASH = _get_config().attention_backend != "library"
 
 
 def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None, bias=None, dropout_p=0.0,

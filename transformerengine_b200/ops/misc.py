@@ -7,7 +7,7 @@ import torch
 
 from . import _ext
 
-MT_CHUNK = 512 * 1024
+MT_CHUNK = 16 * 1024  # elements per chunk; a fixed grid of blocks strides over the chunks of a launch
 
 
 # ----------------------------------------------------------------------------- RoPE

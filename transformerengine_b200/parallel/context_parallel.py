@@ -484,11 +484,10 @@ def fused_ring_attention(q, k, v, cp_group, scale, causal):
 
 
 def _fused_ring_ok(q, k, v, window) -> bool:
-    import os
-
     from ..ops import _ext
+    from ..utils.config import get_config
 
-    if os.environ.get("TEB200_FUSED_CP", "1") != "1" or not _ext.use_cuda(q):
+    if not get_config().fused_context_parallel or not _ext.use_cuda(q):
         return False
     if not hasattr(_ext.get(), "flash_fwd") or not hasattr(_ext.get(), "peer_sum"):
         return False

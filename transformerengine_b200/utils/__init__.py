@@ -8,7 +8,9 @@ from typing import Dict, List
 
 import torch
 
-_NVTX_ENABLED = os.environ.get("TEB200_NVTX", "0") == "1"
+from .config import Config, get_config, override, reload_from_env, set_config  # noqa: F401,E402
+
+_NVTX_ENABLED = get_config().nvtx
 
 
 @contextlib.contextmanager

@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--profile", default="", help="write a per-kernel device-time table of 2 extra steps (rank 0) here")
     ap.add_argument("--fused-comm", type=int, default=1, help="fuse TP collectives into the GEMM kernels")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
+    ap.add_argument("--zero", type=int, default=0, help="data parallel: shard the optimizer over the ranks")
     return ap.parse_args()
 
 
@@ -198,10 +199,17 @@ def build_case(args, rank, world):
             for p in model.parameters():
                 dist.broadcast(p.data, 0)
         graph = want_graph(tp, recipe_name)
-        opt = adam(model.parameters(), graph)
+        overlap = os.environ.get("TEB200_DP_OVERLAP", "1") == "1"
+        zero = None
+        if dp > 1 and args.zero:
+            from transformerengine_b200.parallel.data_parallel import ShardedOptimizerDataParallel
+
+            zero = ShardedOptimizerDataParallel(model.parameters(), None, overlap=overlap)
+            opt = adam(zero.owned_parameters(), graph)
+        else:
+            opt = adam(model.parameters(), graph)
         recipe = recipes[recipe_name]() if recipes[recipe_name] is not None else None
-        grad_sync = DataParallelGradSync(model.parameters(), None,
-                                         overlap=os.environ.get("TEB200_DP_OVERLAP", "1") == "1") if dp > 1 else None
+        grad_sync = DataParallelGradSync(model.parameters(), None, overlap=overlap) if (dp > 1 and zero is None) else None
 
         def step(tokens):
             opt.zero_grad(set_to_none=True)
@@ -212,7 +220,11 @@ def build_case(args, rank, world):
                 D.allreduce_sequence_parallel_grads(model, tp_group)   # replicated norm weights see 1/tp of the rows
             if grad_sync is not None:
                 grad_sync.finish()
+            if zero is not None:
+                zero.finish_grads()
             opt.step()
+            if zero is not None:
+                zero.sync_parameters()
             return loss
 
         gen = torch.Generator().manual_seed(1234 + rank * (1 if dp > 1 else 0))
@@ -222,7 +234,8 @@ def build_case(args, rank, world):
                     before_capture=lambda: opt.zero_grad(set_to_none=True),
                     config={"model": model_name, "global_batch": dp, "seq_len": seq,
                             "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
-                            "recipe": recipe_name, "optimizer": "fused-adam fp32 master",
+                            "recipe": recipe_name,
+                            "optimizer": "fused-adam fp32 master" + (" sharded over the ranks" if zero is not None else ""),
                             "fused_comm_gemm": bool(tp > 1 and args.fused_comm), "recompute": recompute})
 
     if name == "layer12288":

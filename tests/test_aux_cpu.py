@@ -186,3 +186,102 @@ def test_typed_config_reads_env_once_and_overrides():
     assert C.get_config().fused_context_parallel is before
     text = C.get_config().describe()
     assert "TEB200_FUSED_EP" in text and "NVTE_ALLOW_UNSAFE_PICKLE_EXTRA_STATE" in text
+
+
+def test_debug_freq_window_struct_yaml_and_nvfp4(tmp_path):
+    torch.manual_seed(0)
+    cfg_file = tmp_path / "debug.yaml"
+    cfg_file.write_text("""
+stats:
+  enabled: true
+  layers:
+    layer_name_regex_pattern: "blk\\\\.[0-9]+\\\\.fc"
+  features:
+    LogTensorStats:
+      tensors_struct:
+        - tensor: activation
+          stats: [mean, std, zeros%]
+          freq: 2
+        - tensor: weight
+          stats: [l2_norm]
+          start_step: 1
+          end_step: 1
+    LogNvfp4TensorStats:
+      tensors: [activation]
+      stats: [saturated%, mse, scale_inv_max]
+""")
+    lin = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu", name="blk.3.fc")
+    x = torch.randn(32, 64)
+    debug_api.initialize(str(cfg_file), log_dir=str(tmp_path))
+    try:
+        for _ in range(3):
+            with te.autocast(enabled=True, recipe=te.recipe.NVFP4BlockScaling()):
+                lin(x)
+            debug_api.step()
+        recs = debug_api.records()
+        by = {}
+        for r in recs:
+            by.setdefault((r["tensor"], r["stat"]), []).append(r["iteration"])
+        assert by[("activation", "mean")] == [0, 2]          # every second iteration
+        assert by[("weight", "l2_norm")] == [1]               # only inside its step window
+        assert by[("activation", "saturated%")] == [0, 1, 2]
+        mean = [r["value"] for r in recs if r["stat"] == "mean"][0]
+        std = [r["value"] for r in recs if r["stat"] == "std"][0]
+        assert abs(mean - x.mean().item()) < 1e-5 and abs(std - x.std().item()) < 1e-4
+        sat = [r["value"] for r in recs if r["stat"] == "saturated%"][0]
+        assert 0.0 <= sat <= 100.0
+    finally:
+        debug_api.end_debug()
+
+
+def _debug_reduce_worker(rank, world, port, result_q):
+    import torch.distributed as dist
+
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.manual_seed(0)
+        full = torch.randn(64, 64)
+        lin = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu", name="enc.fc")
+        debug_api.initialize({"s": {"enabled": True, "layers": {"layer_names": ["enc.fc"]},
+                                    "features": {"LogTensorStats": {"tensors": ["activation"],
+                                                                    "stats": ["min", "max", "mean", "std", "l2_norm"]}}}})
+        debug_api.set_tensor_reduction_group(dist.group.WORLD)
+        shard = full.chunk(world, dim=0)[rank].contiguous()      # every rank sees its rows only
+        with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+            lin(shard)
+        debug_api.step()
+        got = {r["stat"]: r["value"] for r in debug_api.records()}
+        want = {"min": full.min().item(), "max": full.max().item(), "mean": full.mean().item(),
+                "std": full.std().item(), "l2_norm": full.norm().item()}
+        err = max(abs(got[k] - want[k]) for k in want)
+        debug_api.end_debug()
+        result_q.put((rank, err, None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_debug_stats_are_reduced_over_the_group():
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_debug_reduce_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, err, tb in res:
+        assert tb is None, tb
+        assert err < 1e-4, (rank, err)

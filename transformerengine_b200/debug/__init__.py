@@ -19,6 +19,12 @@ Configuration is a dict (or a YAML file with the same content)::
         }
     }, log_dir="debug_logs")
 
+Every feature accepts ``freq`` (collect every n-th iteration), ``start_step`` and ``end_step``, and the
+reference's ``tensors_struct`` list form (``[{"tensor": "activation", "stats": [...], "freq": 10}, ...]``).
+``LogNvfp4TensorStats`` adds ``saturated%`` (share of values on the largest FP4 code).  Statistics are
+buffered as mergeable aggregates and, after ``set_tensor_reduction_group(group)``, reduced over that
+group at ``debug_api.step()`` so that sharded tensors report one global value (``debug/stats.py``).
+
 Tensor names: ``activation`` (forward input), ``weight``, ``output``, ``gradient`` (grad output),
 ``dgrad`` (grad input).  A module takes part when it was built with ``name=...`` and a section's
 pattern matches the name.  ``debug_api.step()`` advances the iteration counter used in the logs.
@@ -33,6 +39,7 @@ from typing import Any, Dict, List, Optional
 import torch
 
 from ..tensor.base import QuantizedTensorStorage, Quantizer
+from .stats import QUANT_STATS, TENSOR_STATS, StatsBuffer, quant_aggregates, tensor_aggregates
 
 _FWD_SLOTS = ("activation", "weight", "output")
 _BWD_SLOTS = ("gradient", "dgrad")
@@ -45,49 +52,6 @@ def tensor_name_of_slot(fwd: bool, idx: int) -> str:
     return names[idx % len(names)]
 
 
-def _stat(name: str, x: torch.Tensor) -> float:
-    xf = x.float()
-    if name == "min":
-        return xf.min().item()
-    if name == "max":
-        return xf.max().item()
-    if name == "mean":
-        return xf.mean().item()
-    if name == "std":
-        return xf.std().item()
-    if name == "l1_norm":
-        return xf.abs().sum().item()
-    if name == "l2_norm":
-        return xf.norm().item()
-    if name in ("cur_amax", "amax"):
-        return xf.abs().max().item()
-    if name == "dynamic_range":
-        a = xf.abs()
-        nz = a[a > 0]
-        return (torch.log2(a.max()) - torch.log2(nz.min())).item() if nz.numel() else 0.0
-    raise ValueError(f"unknown statistic {name}")
-
-
-def _quant_stat(name: str, x: torch.Tensor, q: QuantizedTensorStorage) -> float:
-    dq = q.dequantize().float()
-    xf = x.float()
-    if name == "underflows%":
-        return 100.0 * ((dq == 0) & (xf != 0)).float().mean().item()
-    if name == "overflows%":
-        return 100.0 * (dq.abs() < xf.abs() * 0.5).float().mean().item()
-    if name == "mse":
-        return (dq - xf).square().mean().item()
-    if name in ("scale_inv_min", "scale_inv_max"):
-        s = getattr(q, "_rowwise_scale_inv", None)
-        if s is None:
-            s = getattr(q, "_scale_inv", None)
-        if s is None:
-            return float("nan")
-        s = s.float() if s.dtype != torch.uint8 else torch.exp2(s.float() - 127.0)
-        return (s.min() if name.endswith("min") else s.max()).item()
-    raise ValueError(f"unknown quantized statistic {name}")
-
-
 class _DebugState:
     def __init__(self):
         self.enabled = False
@@ -96,6 +60,13 @@ class _DebugState:
         self.iteration = 0
         self.records: List[Dict[str, Any]] = []
         self.reduction_group = None
+        self.buffer = StatsBuffer()
+
+    def finalize(self) -> None:
+        """Turn the buffered aggregates of the current iteration into records (reducing over the group)."""
+        for (layer, tensor, stat), value in self.buffer.drain(self.reduction_group):
+            self.records.append({"stat": stat, "value": value, "layer": layer, "tensor": tensor,
+                                 "iteration": self.iteration})
 
     def features_for(self, layer_name: Optional[str]) -> Dict[str, Dict[str, Any]]:
         out: Dict[str, Dict[str, Any]] = {}
@@ -128,11 +99,14 @@ class debug_api:  # noqa: N801  (namespace with the reference's spelling)
         _STATE.log_dir = log_dir
         _STATE.iteration = 0
         _STATE.records = []
+        _STATE.buffer = StatsBuffer()
         if log_dir:
             os.makedirs(log_dir, exist_ok=True)
 
     @staticmethod
     def step():
+        """End of an iteration: reduce and record its statistics, then advance the iteration counter."""
+        _STATE.finalize()
         _STATE.iteration += 1
 
     @staticmethod
@@ -147,6 +121,7 @@ class debug_api:  # noqa: N801  (namespace with the reference's spelling)
 
     @staticmethod
     def flush():
+        _STATE.finalize()
         if _STATE.log_dir and _STATE.records:
             with open(os.path.join(_STATE.log_dir, "tensor_stats.jsonl"), "a") as f:
                 for r in _STATE.records:
@@ -155,15 +130,45 @@ class debug_api:  # noqa: N801  (namespace with the reference's spelling)
 
     @staticmethod
     def records() -> List[Dict[str, Any]]:
+        _STATE.finalize()
         return _STATE.records
 
 
-def _wants(cfg: Dict[str, Any], tensor: str) -> bool:
-    t = cfg.get("tensors")
-    if t is not None and tensor not in t:
+def _active_now(cfg: Dict[str, Any]) -> bool:
+    """``freq`` / ``start_step`` / ``end_step`` window of a feature (or of one tensors_struct entry)."""
+    it = _STATE.iteration
+    if it < int(cfg.get("start_step", 0)):
         return False
+    end = cfg.get("end_step")
+    if end is not None and it > int(end):
+        return False
+    freq = int(cfg.get("freq", 1))
+    return freq <= 1 or (it - int(cfg.get("start_step", 0))) % freq == 0
+
+
+def _entries(cfg: Dict[str, Any], tensor: str):
+    """The settings that apply to ``tensor`` now: the feature's own (``tensors`` / ``stats``) and every
+    matching ``tensors_struct`` entry, each filtered by its time window."""
+    out = []
     g = cfg.get("gemms")
-    return g is None or any(x in g for x in _GEMM_OF[tensor])
+    if g is not None and not any(x in g for x in _GEMM_OF[tensor]):
+        return out
+    struct = cfg.get("tensors_struct")
+    if struct:
+        for e in struct:
+            merged = {k: v for k, v in cfg.items() if k != "tensors_struct"}
+            merged.update(e)
+            if merged.get("tensor", tensor) == tensor and _active_now(merged):
+                out.append(merged)
+        return out
+    t = cfg.get("tensors")
+    if (t is None or tensor in t) and _active_now(cfg):
+        out.append(cfg)
+    return out
+
+
+def _wants(cfg: Dict[str, Any], tensor: str) -> bool:
+    return bool(_entries(cfg, tensor))
 
 
 class DebugQuantizer(Quantizer):
@@ -186,15 +191,14 @@ class DebugQuantizer(Quantizer):
             raise AttributeError(name)
         return getattr(parent, name)
 
-    def _log(self, rec: Dict[str, Any]):
-        rec.update(layer=self.layer_name, tensor=self.tensor_name, iteration=_STATE.iteration)
-        _STATE.records.append(rec)
-
     def quantize_impl(self, tensor, dtype=None):
         f = self.features
-        if "LogTensorStats" in f and _wants(f["LogTensorStats"], self.tensor_name):
-            for s in f["LogTensorStats"].get("stats", ["min", "max", "mean", "std"]):
-                self._log({"stat": s, "value": _stat(s, tensor)})
+        if "LogTensorStats" in f:
+            for e in _entries(f["LogTensorStats"], self.tensor_name):
+                for s in e.get("stats", ["min", "max", "mean", "std"]):
+                    if s not in TENSOR_STATS:
+                        raise ValueError(f"LogTensorStats: unknown statistic {s!r}")
+                    _STATE.buffer.feed(self.layer_name, self.tensor_name, s, tensor_aggregates(tensor, TENSOR_STATS[s]))
         if "DumpTensors" in f and _wants(f["DumpTensors"], self.tensor_name) and _STATE.log_dir:
             d = os.path.join(_STATE.log_dir, f["DumpTensors"].get("dir", "dumps"))
             os.makedirs(d, exist_ok=True)
@@ -202,9 +206,13 @@ class DebugQuantizer(Quantizer):
                 d, f"{self.layer_name}.{self.tensor_name}.{_STATE.iteration}.pt".replace("/", "_")))
         q = self.parent.quantize_impl(tensor, dtype) if self.parent is not None else tensor
         for feat in ("LogFp8TensorStats", "LogNvfp4TensorStats"):
-            if feat in f and _wants(f[feat], self.tensor_name) and isinstance(q, QuantizedTensorStorage):
-                for s in f[feat].get("stats", ["underflows%", "mse"]):
-                    self._log({"stat": s, "value": _quant_stat(s, tensor, q)})
+            if feat in f and isinstance(q, QuantizedTensorStorage):
+                for e in _entries(f[feat], self.tensor_name):
+                    for s in e.get("stats", ["underflows%", "mse"]):
+                        if s not in QUANT_STATS:
+                            raise ValueError(f"{feat}: unknown statistic {s!r}")
+                        _STATE.buffer.feed(self.layer_name, self.tensor_name, s,
+                                           quant_aggregates(tensor, q, QUANT_STATS[s]))
         return q
 
     def make_empty(self, shape, *, dtype=torch.float32, device=None, requires_grad=False):

@@ -49,7 +49,7 @@ def test_norm_linear_and_residual_fusion():
     kinds = [getattr(p, "fusion", type(p).__name__) for p in seq._get_plan()]
     assert kinds == ["norm_mlp", "AddExtraInput", "MakeExtraOutput"]
     seq2 = F.Sequential(seq[0], seq[1], F.Dropout(0.0), seq[3], F.AddExtraInput())
-    assert [getattr(p, "fusion", type(p).__name__) for p in seq2._get_plan()] == ["norm_linear", "Dropout", "linear_add"]
+    assert [getattr(p, "fusion", type(p).__name__) for p in seq2._get_plan()] == ["norm_linear", "Dropout", "linear_bias_add"]
     xx, rr = torch.randn(4, 16), torch.randn(4, 16)
     assert torch.allclose(seq2(xx, rr), seq[3](seq[1](seq[0](xx))) + rr, atol=1e-5)
     x, res = torch.randn(4, 16), torch.randn(4, 16)
@@ -66,3 +66,88 @@ def test_quantize_op_under_autocast():
     with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
         y = q(x)
     assert y.shape == x.shape and not torch.equal(y, x) and (y - x).abs().max() < 0.3
+
+
+def _unfused(ops, x, *extra):
+    """Run copies of the operations one by one (no fusion)."""
+    ref = copy.deepcopy(list(ops))
+    xr = x.clone().requires_grad_()
+    h, extra, outs = xr, list(extra), []
+    for op in ref:
+        n = getattr(op, "num_extra_inputs", 0)
+        args, extra = extra[:n], extra[n:]
+        h = op(h, *args)
+        if getattr(op, "num_extra_outputs", 0):
+            h, rest = h[0], h[1:]
+            outs.extend(rest)
+    return ref, xr, h, outs
+
+
+def test_linear_chains_forward_and_backward_match_unfused():
+    torch.manual_seed(2)
+    kw = dict(dtype=torch.float32, device="cpu")
+    cases = [
+        ([F.BasicLinear(16, 32, **kw), F.Bias(32, **kw), F.GELU()], "linear_bias_gelu", 0),
+        ([F.Linear(16, 32, **kw), F.SwiGLU(), F.AddExtraInput()], "linear_bias_swiglu_add", 1),
+        ([F.BasicLinear(16, 16, **kw), F.ConstantScale(0.5), F.AddExtraInput()], "linear_scale_add", 1),
+        ([F.Linear(16, 16, **kw), F.AddExtraInput()], "linear_bias_add", 1),
+    ]
+    for ops, name, n_extra in cases:
+        for op in ops:
+            for p in op.parameters():
+                if p.dim() == 1:
+                    torch.nn.init.normal_(p, 0.0, 0.5)   # non-zero biases
+        seq = F.Sequential(*ops)
+        plan = seq._get_plan()
+        assert len(plan) == 1 and plan[0].fusion == name, [getattr(p, "fusion", type(p).__name__) for p in plan]
+        x = torch.randn(8, 16)
+        out_dim = 16 if name != "linear_bias_gelu" else 32
+        extra = [torch.randn(8, 16 if "swiglu" in name or out_dim == 16 else 32).requires_grad_() for _ in range(n_extra)]
+        xg = x.clone().requires_grad_()
+        y = seq(xg, *extra)
+        y.square().sum().backward()
+        got_extra = [e.grad.clone() for e in extra]
+        for e in extra:
+            e.grad = None
+        ref, xr, h, _ = _unfused(ops, x, *extra)
+        h.square().sum().backward()
+        assert torch.allclose(y, h, atol=1e-5), name
+        assert torch.allclose(xg.grad, xr.grad, atol=1e-5), name
+        for (n1, p1), (n2, p2) in zip(seq.named_parameters(), torch.nn.Sequential(*ref).named_parameters()):
+            assert torch.allclose(p1.grad, p2.grad, atol=1e-5), (name, n1)
+        for a, e in zip(got_extra, extra):
+            assert torch.allclose(a, e.grad, atol=1e-6), name
+
+
+def test_fork_norm_adds_branch_gradient_in_the_norm_backward():
+    torch.manual_seed(3)
+    kw = dict(dtype=torch.float32, device="cpu")
+    ops = [F.MakeExtraOutput(), F.RMSNorm(16, **kw), F.BasicLinear(16, 16, **kw)]
+    seq = F.Sequential(*ops)
+    assert [getattr(p, "fusion", type(p).__name__) for p in seq._get_plan()] == ["fork_norm", "BasicLinear"]
+    x = torch.randn(8, 16)
+    xg = x.clone().requires_grad_()
+    y, fork = seq(xg)
+    (y.square().sum() + (fork * 0.3).sum()).backward()
+    ref, xr, h, outs = _unfused(ops, x)
+    (h.square().sum() + (outs[0] * 0.3).sum()).backward()
+    assert torch.allclose(y, h, atol=1e-5) and torch.allclose(fork, x)
+    assert torch.allclose(xg.grad, xr.grad, atol=1e-5)
+    assert torch.allclose(seq[1].weight.grad, ref[1].weight.grad, atol=1e-5)
+
+
+def test_linear_chain_under_mxfp8_autocast():
+    torch.manual_seed(4)
+    kw = dict(dtype=torch.float32, device="cpu")
+    ops = [F.Linear(64, 128, **kw), F.GELU(), F.AddExtraInput()]
+    seq = F.Sequential(*ops)
+    x, r = torch.randn(32, 64), torch.randn(32, 128)
+    xg = x.clone().requires_grad_()
+    with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+        y = seq(xg, r)
+    y.square().sum().backward()
+    ref, xr, h, _ = _unfused(ops, x, r)     # high precision, unfused
+    h.square().sum().backward()
+    rel = lambda a, b: ((a - b).norm() / b.norm()).item()  # noqa: E731
+    assert rel(y, h) < 0.05 and rel(xg.grad, xr.grad) < 0.1 and rel(seq[0].weight.grad, ref[0].weight.grad) < 0.1
+    assert rel(seq[0].bias.grad, ref[0].bias.grad) < 0.1

@@ -6,8 +6,14 @@ Fusions applied (greedy, longest first):
 
 * ``Norm, Linear, Activation, Linear``  -> one LayerNormMLP pass (norm+quantize, fc1, act+quantize, fc2)
 * ``Norm, Linear``                       -> LayerNormLinear (norm output is written quantized)
-* ``Linear, Activation``                 -> GEMM followed by the activation(+quantize) kernel
-* ``AddExtraInput`` after a ``Linear``   -> residual add on the GEMM output
+* ``Linear (, Bias) (, Activation) (, AddExtraInput)`` and ``Linear, ConstantScale (, AddExtraInput)``
+                                         -> ``fused.LinearChain``: scale and bias in the GEMM epilogue; in the
+                                            backward ONE kernel yields the activation gradient, the bias
+                                            gradient and the quantized operands of dgrad / wgrad
+* ``MakeExtraOutput, Norm``              -> ``fused.ForkNorm``: the norm backward kernel adds the gradient of
+                                            the forked (residual) branch
+* tensor-parallel ``Linear`` operations run the collective inside the GEMM kernel once ``initialize_ub`` was
+  called (the reference's Userbuffers forward / backward linear fusions)
 
 The fused modules share the ``Parameter`` objects of the basic operations, so state dicts and
 optimizers only ever see the basic operations.
@@ -15,9 +21,10 @@ optimizers only ever see the basic operations.
 from .ops import (FusibleOperation, BasicLinear, Bias, Linear, LayerNorm, RMSNorm, GELU, ReLU, SiLU, SwiGLU, GEGLU,
                   ReGLU, QGELU, SReLU, Quantize, Identity, Reshape, ConstantScale, Dropout, AddExtraInput,
                   MakeExtraOutput, AllReduce, AllGather, ReduceScatter, L2Normalization)
+from .fused import ForkNorm, LinearChain
 from .sequential import Sequential, fuse_operations
 
 __all__ = ["FusibleOperation", "BasicLinear", "Bias", "Linear", "LayerNorm", "RMSNorm", "GELU", "ReLU", "SiLU",
            "SwiGLU", "GEGLU", "ReGLU", "QGELU", "SReLU", "Quantize", "Identity", "Reshape", "ConstantScale",
            "Dropout", "AddExtraInput", "MakeExtraOutput", "AllReduce", "AllGather", "ReduceScatter",
-           "L2Normalization", "Sequential", "fuse_operations"]
+           "L2Normalization", "Sequential", "fuse_operations", "LinearChain", "ForkNorm"]

@@ -7,6 +7,7 @@ from typing import Callable, List, Optional, Tuple
 import torch
 
 from . import ops as O
+from .fused import ForkNorm, LinearChain
 from ..modules.layernorm_linear import LayerNormLinear
 from ..modules.layernorm_mlp import LayerNormMLP
 
@@ -89,11 +90,29 @@ def fuse_operations(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
             out.append(_Fused(_fuse_norm_linear(w[0], w[1]), 2, name="norm_linear"))
             i += 2
             continue
-        if len(w) >= 2 and _is_linear(w[0]) and isinstance(w[1], O.AddExtraInput):
-            lin = w[0]
-            out.append(_Fused(lambda x, extra, lin=lin: lin(x) + extra, 2, extra_inputs=1, name="linear_add"))
+        if len(w) >= 2 and isinstance(w[0], O.MakeExtraOutput) and _norm_kind(w[1]):
+            # residual fork followed by a norm: the norm backward adds the fork's gradient itself
+            out.append(ForkNorm(w[1], _norm_kind(w[1]) == "LayerNorm"))
             i += 2
             continue
+        if _is_linear(ops[i]) and not getattr(ops[i], "return_bias", False):
+            # Linear (+Bias) (+ConstantScale, bias-free only) (+Activation) (+AddExtraInput): one chain with a
+            # fused backward (activation gradient + bias gradient + quantization in one kernel)
+            lin, j = ops[i], i + 1
+            own_bias = getattr(lin, "bias", None) is not None and getattr(lin, "apply_bias", True)
+            bias_op, scale, act, add = None, 1.0, None, False
+            if j < len(ops) and isinstance(ops[j], O.Bias) and not own_bias:
+                bias_op, j = ops[j], j + 1
+            if j < len(ops) and isinstance(ops[j], O.ConstantScale) and bias_op is None and not own_bias:
+                scale, j = float(ops[j].scale), j + 1
+            if j < len(ops) and isinstance(ops[j], O._Activation) and scale == 1.0:
+                act, j = ops[j].act_name, j + 1
+            if j < len(ops) and isinstance(ops[j], O.AddExtraInput):
+                add, j = True, j + 1
+            if j > i + 1:
+                out.append(LinearChain(lin, bias_op, scale, act, add))
+                i = j
+                continue
         out.append(ops[i])
         i += 1
     return out

@@ -160,9 +160,8 @@ def build_case(args, rank, world):
 
     def want_graph(tp, recipe_name):
         """Whole-step CUDA graph: on by request, by default for tensor-parallel steps (their kernels are too
-        short for the eager launch path).  The NVFP4 stochastic-rounding offset is drawn on the host per
-        call, and expert-parallel steps read split sizes on the host: both stay eager."""
-        if recipe_name == "nvfp4" or name == "mixtral":
+        short for the eager launch path).  Expert-parallel steps read split sizes on the host and stay eager."""
+        if name == "mixtral":
             return False
         return args.graph == 1 or (args.graph < 0 and tp > 1)
 

@@ -298,3 +298,52 @@ def test_delayed_scaling_update_kernel_matches_reference(algo):
     update_delayed_scaling_state(ref)
     assert torch.allclose(st.scale.cpu(), ref.scale, rtol=1e-6)
     assert torch.equal(st.amax_history.cpu(), ref.amax_history)
+
+
+@pytest.mark.parametrize("dim", [1, 2])
+@pytest.mark.parametrize("R,C", [(256, 384), (300, 160), (128, 128)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fp8_block128_quantizer_matches_reference(dim, R, C, dtype):
+    from transformerengine_b200.tensor.blockwise import Float8BlockQuantizer
+
+    x = (torch.randn(R, C, device=DEV) * torch.logspace(-3, 2, C, device=DEV)).to(dtype)
+    q = Float8BlockQuantizer(torch.float8_e4m3fn, rowwise=True, columnwise=True, block_scaling_dim=dim)
+    got = q(x)
+    dims = (128, 128) if dim == 2 else (1, 128)
+    rq, rs = Q.quantize_fp8_blockwise(x, torch.float8_e4m3fn, dims, True, 0.0)
+    cq, cs = Q.quantize_fp8_blockwise(x.t().contiguous(), torch.float8_e4m3fn, dims, True, 0.0)
+    assert torch.equal(got._rowwise_data.view(torch.uint8), rq.view(torch.uint8))
+    assert torch.equal(got._columnwise_data.view(torch.uint8), cq.view(torch.uint8))
+    assert torch.equal(got._rowwise_scale_inv, rs) and torch.equal(got._columnwise_scale_inv, cs)
+    assert _rel(got.dequantize(dtype=torch.float32), x) < 0.05
+    # the UE8M0 tiles hold the same scales: block scale of (row i, 128-block kb) repeated four times
+    if C % 32 == 0:
+        mx = Q.unswizzle_scales(got._rowwise_mx_scale, R, ((C + 127) // 128) * 4)
+        want = rs.repeat_interleave(128, 0)[:R] if dim == 2 else rs
+        assert torch.equal(torch.exp2(mx.float() - 127.0)[:, ::4], want)
+
+
+def test_fp8_block_scaled_gemm_runs_on_the_block_scaled_tensor_core_path():
+    """1 x 128 activations times 128 x 128 weights: exact product of the dequantized operands."""
+    from transformerengine_b200.tensor.blockwise import Float8BlockQuantizer
+
+    M, N, K = 512, 768, 1024
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.05
+    qa = Float8BlockQuantizer(torch.float8_e4m3fn, block_scaling_dim=1)(a)
+    qw = Float8BlockQuantizer(torch.float8_e4m3fn, block_scaling_dim=2)(w)
+    oa, ow = ops.as_operand(qa, "rowwise"), ops.as_operand(qw, "rowwise")
+    assert oa.kind == "mxfp8" and ow.kind == "mxfp8"
+    out = ops.gemm_nt(oa, ow, out_dtype=torch.float32)
+    te.check_status()
+    ref = qa.dequantize(dtype=torch.float32) @ qw.dequantize(dtype=torch.float32).t()
+    assert _rel(out, ref) < 1e-5
+    # wgrad-style product through the column-wise copies
+    g = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    qg = Float8BlockQuantizer(torch.float8_e5m2, block_scaling_dim=1)(g)
+    dw = ops.gemm_nt(ops.as_operand(qg, "columnwise"), ops.as_operand(qa, "columnwise"), out_dtype=torch.float32)
+    refw = Q.dequantize_fp8_blockwise(qg._columnwise_data.view(torch.float8_e5m2), qg._columnwise_scale_inv, (1, 128),
+                                      torch.float32) @ \
+        Q.dequantize_fp8_blockwise(qa._columnwise_data.view(torch.float8_e4m3fn), qa._columnwise_scale_inv, (1, 128),
+                                   torch.float32).t()
+    assert _rel(dw, refw) < 1e-5

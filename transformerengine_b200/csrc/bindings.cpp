@@ -113,6 +113,33 @@ void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, con
   check(e, "gemm");
 }
 
+// FP8 with 128-wide block scales; returns nothing, fills the given outputs (any of the two copies may be absent)
+void quantize_block128(const at::Tensor& x, int64_t dim, bool e5m2, bool pow2, double eps, const OptT& row_data,
+                       const OptT& row_sinv, const OptT& row_mx, const OptT& col_data, const OptT& col_sinv,
+                       const OptT& col_mx) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "quantize_block128 expects a row-major matrix");
+  teb200::BlockQuantArgs a;
+  a.x = x.data_ptr();
+  a.x_dtype = to_dtype(x);
+  a.R = static_cast<int>(x.size(0));
+  a.C = static_cast<int>(x.size(1));
+  a.ld = x.stride(0);
+  a.dim = static_cast<int>(dim);
+  a.e5m2 = e5m2;
+  a.pow2 = pow2;
+  a.eps = static_cast<float>(eps);
+  a.row_data = ptr<uint8_t>(row_data);
+  a.row_sinv = ptr<float>(row_sinv);
+  a.row_mx = ptr<uint8_t>(row_mx);
+  a.col_data = ptr<uint8_t>(col_data);
+  a.col_sinv = ptr<float>(col_sinv);
+  a.col_mx = ptr<uint8_t>(col_mx);
+  TORCH_CHECK((a.row_data == nullptr) == (a.row_sinv == nullptr) && (a.col_data == nullptr) == (a.col_sinv == nullptr),
+              "quantize_block128: data and scales of a copy go together");
+  check(teb200::quantize_block128(a, stream()), "quantize_block128");
+}
+
 // mode: 0 = mxfp8, 1 = per-tensor fp8, 2 = no quantization (produce y only)
 void quantize(int mode, int prologue, int act, const at::Tensor& x, const OptT& dy, int64_t R, int64_t C,
               const OptT& y, const OptT& row_data, const OptT& row_scale, const OptT& col_data, const OptT& col_scale,
@@ -419,6 +446,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("launch_count", &launch_count);
   m.def("gemm", &gemm);
   m.def("quantize", &quantize);
+  m.def("quantize_block128", &quantize_block128);
   m.def("dequantize_mxfp8", &dequantize_mxfp8);
   m.def("dequantize_fp8", &dequantize_fp8);
   m.def("amax", &amax);

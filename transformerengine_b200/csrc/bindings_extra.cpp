@@ -435,7 +435,8 @@ void nvfp4_amax(const at::Tensor& x, int64_t R, int64_t C, bool with_rht, const 
 
 void quantize_nvfp4(const at::Tensor& x, int64_t R, int64_t C, const OptT& amax_row, const OptT& amax_col,
                     const OptT& row_data, const OptT& row_scale, const OptT& col_data, const OptT& col_scale,
-                    bool with_rht, bool with_2d, bool stochastic, int64_t seed, int64_t offset) {
+                    bool with_rht, bool with_2d, bool stochastic, int64_t seed, int64_t offset,
+                    const OptT& offset_dev) {
   c10::cuda::CUDAGuard guard(x.device());
   teb200::Nvfp4Args a;
   a.x = x.data_ptr();
@@ -453,6 +454,10 @@ void quantize_nvfp4(const at::Tensor& x, int64_t R, int64_t C, const OptT& amax_
   a.stochastic = stochastic;
   a.seed = static_cast<uint64_t>(seed);
   a.offset = static_cast<uint64_t>(offset);
+  if (offset_dev.has_value() && offset_dev->defined()) {
+    TORCH_CHECK(offset_dev->scalar_type() == at::kLong && offset_dev->is_cuda(), "the device RNG counter must be int64 on the GPU");
+    a.offset_dev = reinterpret_cast<const unsigned long long*>(offset_dev->data_ptr<int64_t>());
+  }
   TORCH_CHECK(a.row_data == nullptr || a.amax_row != nullptr, "row-wise NVFP4 needs its global amax");
   TORCH_CHECK(a.col_data == nullptr || a.amax_col != nullptr, "column-wise NVFP4 needs its global amax");
   cudaError_t e = teb200::quantize_nvfp4(a, cur_stream());

@@ -6,11 +6,12 @@
 //
 //   CTA rank 0 (leader): TMA producer, MMA issuer for the pair, epilogue of rows 0..127
 //   CTA rank 1 (partner): TMA producer (signals the leader's barriers), epilogue of rows 128..255
+//   (10 warps per CTA: producer, MMA issuer, eight epilogue warps)
 //
-// Epilogue: the four epilogue warps of each CTA move the accumulator TMEM -> registers -> shared memory
-// (128-byte-swizzled boxes) and release the accumulator as soon as the last column has been read; TMA
-// stores (or TMA reduce-adds when accumulating into fp32) carry the boxes to global memory while the
-// next tile's MMAs already run.
+// Epilogue: eight warps per CTA read the whole accumulator into registers (four back-to-back TMEM loads
+// per thread, one wait), release it at once, then convert and stage the values in shared memory
+// (128-byte-swizzled boxes); TMA stores (TMA reduce-adds when accumulating into fp32) carry the boxes to
+// global memory while the next tile's MMAs already run.
 //
 // "Stage full" barriers live in the leader and count the bytes of both CTAs; "stage empty" and
 // "accumulator full" are committed to the same-offset barrier of both CTAs; "accumulator empty"
@@ -26,6 +27,7 @@ namespace {
 
 using namespace gemm_detail;
 
+constexpr int kPairThreads = 64 + 8 * 32;  // producer warp, MMA warp, eight epilogue warps
 constexpr int PM = 256;   // rows per pair tile
 constexpr int PN = 256;   // columns per pair tile
 
@@ -68,7 +70,7 @@ __device__ __forceinline__ bool pair_tile(const PairParams& p, int t, int& mb, i
 }
 
 template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kNumThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
@@ -101,7 +103,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int i = 0; i < C::kAccStages; ++i) {
       mbar_init(&tfull_bar[i], 1);
-      mbar_init(&tempty_bar[i], 8);  // four epilogue warps in each of the two CTAs
+      mbar_init(&tempty_bar[i], 16);  // eight epilogue warps in each of the two CTAs
     }
     mbar_fence_init();
   }
@@ -217,21 +219,26 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
+    // Eight warps: warp w reads the TMEM lanes of quarter w % 4 (its rows) and the column half (w - 2) / 4.
+    // Each thread pulls its 128 accumulator columns with four back-to-back loads and ONE wait, releases the
+    // accumulator, and only then converts and stages the values: the tensor core waits for loads, not stores.
     const int quarter = warp & 3;
-    const int et = quarter * 32 + lane;       // row of this thread inside the CTA's 128 rows
+    const int half = (warp - 2) >> 2;          // 0: columns 0..127, 1: columns 128..255
+    const int et = quarter * 32 + lane;        // row of this thread inside the CTA's 128 rows
+    const bool issuer = quarter == ((2 + half * 4) & 3) && lane == 0;  // lane 0 of the first warp of this half
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
     const int dt = p.k.d_dtype;
     const bool wide = dt == kFloat32;          // a box (128 bytes per row) holds 32 fp32 or 64 16-bit columns
-    const int box_cols = wide ? 32 : 64;
-    const int boxes_per_tile = PN / box_cols;
-    uint32_t box_count = 0;                    // boxes handed to TMA so far (ping-pong over two buffers)
-    uint8_t* my_row = staging + et * 128;
+    uint8_t* box = staging + half * C::kBoxBytes;   // one 16 KB box buffer per column half
+    uint8_t* my_row = box + et * 128;
     const int sw = et & 7;
+    const uint32_t bar_id = 1 + half;
+    bool box_in_flight = false;                // a TMA store may still be reading this half's buffer
     int mb, nb;
-    bool dead = false;  // a wait ran out: keep walking the loop (the named barriers need all four warps), wait no more
+    bool dead = false;  // a wait ran out: keep walking the loop (the named barriers need every warp), wait no more
     for (int t = pair; pair_tile(p, t, mb, nb); t += num_pairs) {
       if (!dead && !mbar_wait_cluster(&tfull_bar[acc], acc_phase)) {
         if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
@@ -239,81 +246,86 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tc_fence_after();
       const int row0 = mb * PM + static_cast<int>(rank) * 128;
-      const int n0 = nb * PN;
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * PN;
-#pragma unroll 1
-      for (int bx = 0; bx < boxes_per_tile; ++bx, ++box_count) {
-        uint8_t* buf = my_row + (box_count & 1) * C::kBoxBytes;
-        if (box_count >= 2) {
-          // the store that last read this buffer (two boxes ago) must have finished reading it
-          if (et == 0) tma_store_wait_read<1>();
-          named_bar_sync(1, 128);
-        }
-        const int chunks = wide ? 1 : 2;       // 32 accumulator columns per chunk
-#pragma unroll 1
-        for (int ch = 0; ch < chunks; ++ch) {
-          const int c0 = bx * box_cols + ch * 32;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c0, r);
-          tmem_ld_wait();
-          if (bx == boxes_per_tile - 1 && ch == chunks - 1) {
-            // every column of the accumulator is in registers: the MMA warp may overwrite it
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
-          }
-          float v[32];
+      const int n0 = nb * PN + half * 128;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * PN + half * 128;
+      uint32_t r[4][32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-          if (p.k.bias != nullptr) {
-            const int col0 = n0 + c0;
+      for (int j = 0; j < 4; ++j) tmem_ld_32x32(taddr + j * 32, r[j]);
+      tmem_ld_wait();
+      // every column of the accumulator is in registers: the MMA warp may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      if (p.k.bias != nullptr) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (col0 + i < p.k.N) {
-                float b;
-                if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
-                else if (p.k.bias_dtype == kBFloat16)
-                  b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
-                else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
-                v[i] += b;
-              }
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = n0 + j * 32 + i;
+            float b = 0.f;
+            if (col < p.k.N) {
+              if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col];
+              else if (p.k.bias_dtype == kBFloat16) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col]);
+              else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col]);
             }
+            r[j][i] = __float_as_uint(__uint_as_float(r[j][i]) * alpha + b);
+          }
+        }
+      } else if (alpha != 1.0f) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[j][i] = __float_as_uint(__uint_as_float(r[j][i]) * alpha);
+      }
+      const int nboxes = wide ? 4 : 2;
+#pragma unroll
+      for (int bx = 0; bx < 4; ++bx) {
+        if (bx < nboxes) {
+          if (box_in_flight) {
+            if (issuer) tma_store_wait_read<0>();   // the previous store has finished reading the buffer
+            named_bar_sync(bar_id, 128);
           }
           if (wide) {
 #pragma unroll
             for (int c = 0; c < 8; ++c)
-              *reinterpret_cast<float4*>(buf + ((c ^ sw) << 4)) = make_float4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+              *reinterpret_cast<uint4*>(my_row + ((c ^ sw) << 4)) =
+                  make_uint4(r[bx][4 * c], r[bx][4 * c + 1], r[bx][4 * c + 2], r[bx][4 * c + 3]);
           } else {
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int i = 8 * c;
-              uint4 o;
-              if (dt == kBFloat16) {
-                o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
-                               pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
-              } else {
-                o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
-                               pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
+            for (int hh = 0; hh < 2; ++hh) {
+              const int j = (2 * bx + hh) & 3;   // bx < 2 on this path
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const int i = 8 * c;
+                const float v0 = __uint_as_float(r[j][i]), v1 = __uint_as_float(r[j][i + 1]);
+                const float v2 = __uint_as_float(r[j][i + 2]), v3 = __uint_as_float(r[j][i + 3]);
+                const float v4 = __uint_as_float(r[j][i + 4]), v5 = __uint_as_float(r[j][i + 5]);
+                const float v6 = __uint_as_float(r[j][i + 6]), v7 = __uint_as_float(r[j][i + 7]);
+                uint4 o;
+                if (dt == kBFloat16)
+                  o = make_uint4(pack_bf16x2(v0, v1), pack_bf16x2(v2, v3), pack_bf16x2(v4, v5), pack_bf16x2(v6, v7));
+                else
+                  o = make_uint4(pack_f16x2(v0, v1), pack_f16x2(v2, v3), pack_f16x2(v4, v5), pack_f16x2(v6, v7));
+                *reinterpret_cast<uint4*>(my_row + (((hh * 4 + c) ^ sw) << 4)) = o;
               }
-              *reinterpret_cast<uint4*>(buf + (((ch * 4 + c) ^ sw) << 4)) = o;
             }
           }
-        }
-        fence_proxy_async_smem();  // generic-proxy writes to shared memory -> TMA (async proxy) read
-        named_bar_sync(1, 128);
-        if (et == 0) {
-          const uint8_t* src = staging + (box_count & 1) * C::kBoxBytes;
-          const int col = n0 + bx * box_cols;
-          if (col < p.k.N && row0 < p.k.M) {   // boxes wholly outside the matrix are skipped, the rest is clipped
-            if (p.k.accumulate) tma_reduce_add_2d(&tmap_d, src, col, row0);
-            else tma_store_2d(&tmap_d, src, col, row0);
+          fence_proxy_async_smem();  // generic-proxy writes to shared memory -> TMA (async proxy) read
+          named_bar_sync(bar_id, 128);
+          if (issuer) {
+            const int col = n0 + bx * (wide ? 32 : 64);
+            if (col < p.k.N && row0 < p.k.M) {   // boxes wholly outside the matrix are skipped, the rest is clipped
+              if (p.k.accumulate) tma_reduce_add_2d(&tmap_d, box, col, row0);
+              else tma_store_2d(&tmap_d, box, col, row0);
+            }
+            tma_store_commit();
           }
-          tma_store_commit();
+          box_in_flight = true;
         }
       }
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
-    if (et == 0) tma_store_wait<0>();  // shared memory stays valid until the last store has read it
+    if (issuer) tma_store_wait<0>();  // shared memory stays valid until the last store has read it
   }
 
   tc_fence_before();
@@ -380,7 +392,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   if (max_pairs == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms - sms % 2);
-    cfg.blockDim = dim3(kNumThreads);
+    cfg.blockDim = dim3(kPairThreads);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cudaLaunchAttribute at;
     at.id = cudaLaunchAttributeClusterDimension;
@@ -396,7 +408,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   long long pairs = max_pairs < sms / 2 ? max_pairs : sms / 2;
   if (tiles < pairs) pairs = tiles;
   if (pairs < 1) pairs = 1;
-  gemm_pair_kernel<KIND><<<static_cast<int>(pairs * 2), kNumThreads, C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, td, p);
+  gemm_pair_kernel<KIND><<<static_cast<int>(pairs * 2), kPairThreads, C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, td, p);
   return cudaGetLastError();
 }
 

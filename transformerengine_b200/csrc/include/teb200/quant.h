@@ -65,6 +65,29 @@ cudaError_t unswizzle_scales(const uint8_t* swz, int rows, int cols, uint8_t* ou
 cudaError_t delayed_scaling_update(float* history, float* scale, int H, int n, float fp8_max, int margin, int most_recent,
                                    cudaStream_t s);
 
+// FP8 with one scale per 1 x 128 (dim = 1) or 128 x 128 (dim = 2) block.  Compact fp32 decode scales:
+// row-wise [R, ceil(C/128)] or [ceil(R/128), ceil(C/128)]; column-wise (for the transposed copy [C, R])
+// [C, ceil(R/128)] or [ceil(C/128), ceil(R/128)].  row_mx / col_mx (optional, power-of-two scales only):
+// the same scales as UE8M0 bytes in the 128x4-tile GEMM layout of an operand with 32-element blocks,
+// zero-initialised by the caller, padded to ru(rows,128) * ru(ceil(k/32),4) bytes.
+struct BlockQuantArgs {
+  const void* x = nullptr;
+  int x_dtype = 2;
+  int R = 0, C = 0;
+  long long ld = 0;
+  int dim = 1;
+  int e5m2 = 0;
+  int pow2 = 1;
+  float eps = 0.f;
+  uint8_t* row_data = nullptr;
+  float* row_sinv = nullptr;
+  uint8_t* row_mx = nullptr;
+  uint8_t* col_data = nullptr;
+  float* col_sinv = nullptr;
+  uint8_t* col_mx = nullptr;
+};
+cudaError_t quantize_block128(const BlockQuantArgs& a, cudaStream_t s);
+
 // NVFP4: 1x16 (or 16x16) blocks, E4M3 block scales (swizzled), global amax given.
 struct Nvfp4Args {
   const void* x = nullptr;
@@ -80,6 +103,9 @@ struct Nvfp4Args {
   int with_2d = 0;                  // 16x16 block scales
   int stochastic = 0;
   uint64_t seed = 0, offset = 0;
+  // optional device counter added to `offset` by the kernels: a launch recorded in a CUDA graph then draws
+  // new random numbers on every replay (the caller advances the counter with a device op)
+  const unsigned long long* offset_dev = nullptr;
 };
 cudaError_t quantize_nvfp4(const Nvfp4Args& a, cudaStream_t s);
 // amax of x and of RHT(x^T) in one pass: out[0] = amax(x), out[1] = amax(RHT(x^T))

@@ -145,7 +145,8 @@ __global__ void nvfp4_amax_kernel(const T* __restrict__ x, int R, int C, int wit
 template <typename T>
 __global__ void nvfp4_row_kernel(const T* __restrict__ x, int R, int C, const float* __restrict__ amax,
                                  uint8_t* __restrict__ data, uint8_t* __restrict__ scale, int with_2d, int stochastic,
-                                 uint64_t seed, uint64_t offset) {
+                                 uint64_t seed, uint64_t offset, const unsigned long long* __restrict__ offset_dev) {
+  if (offset_dev != nullptr) offset += *offset_dev;  // call counter kept on the device (valid under graph replay)
   const int rx = threadIdx.x & 15, cb = threadIdx.x >> 4;
   const int r = blockIdx.y * 16 + rx;
   const int blk = blockIdx.x * 16 + cb;
@@ -191,7 +192,9 @@ __global__ void nvfp4_row_kernel(const T* __restrict__ x, int R, int C, const fl
 template <typename T>
 __global__ void nvfp4_col_kernel(const T* __restrict__ x, int R, int C, const float* __restrict__ amax,
                                  uint8_t* __restrict__ data, uint8_t* __restrict__ scale, int with_rht, int with_2d,
-                                 int stochastic, uint64_t seed, uint64_t offset) {
+                                 int stochastic, uint64_t seed, uint64_t offset,
+                                 const unsigned long long* __restrict__ offset_dev) {
+  if (offset_dev != nullptr) offset += *offset_dev;
   __shared__ uint2 stage[32][17];
   const int cx = threadIdx.x & 31, g = threadIdx.x >> 5;  // 16 warps: one 16-row group each
   const int c = blockIdx.x * 32 + cx;
@@ -276,12 +279,12 @@ cudaError_t launch_quant(const Nvfp4Args& a, cudaStream_t s) {
   if (a.row_data != nullptr) {
     dim3 grid((a.C / 16 + 15) / 16, (a.R + 15) / 16);
     nvfp4_row_kernel<T><<<grid, 256, 0, s>>>(x, a.R, a.C, a.amax_row, a.row_data, a.row_scale, a.with_2d, a.stochastic,
-                                             a.seed, a.offset);
+                                             a.seed, a.offset, a.offset_dev);
   }
   if (a.col_data != nullptr) {
     dim3 grid((a.C + 31) / 32, (a.R + 255) / 256);
     nvfp4_col_kernel<T><<<grid, 512, 0, s>>>(x, a.R, a.C, a.amax_col, a.col_data, a.col_scale, a.with_rht, a.with_2d,
-                                             a.stochastic, a.seed, a.offset);
+                                             a.stochastic, a.seed, a.offset, a.offset_dev);
   }
   return cudaGetLastError();
 }

@@ -83,6 +83,13 @@ def as_operand(t, usage: str = "rowwise") -> Operand:
             t.update_usage(columnwise_usage=True)
         return Operand("fp8", t._transpose, t._scale_inv, t._fp8_dtype, rows=C, k=R)
     if isinstance(t, Float8BlockwiseQTensorStorage):
+        # power-of-two block scales exist as UE8M0 tiles too (written by the quantize kernel): the operand then
+        # IS an MXFP8 operand; fp32 scales (or tensors quantized on the CPU) multiply in high precision
+        R, C = t._rows_cols()
+        if row and t._rowwise_data is not None and t._rowwise_mx_scale is not None:
+            return Operand("mxfp8", t._rowwise_data.reshape(R, C), t._rowwise_mx_scale, t._fp8_dtype, rows=R, k=C)
+        if not row and t._columnwise_data is not None and t._columnwise_mx_scale is not None:
+            return Operand("mxfp8", t._columnwise_data, t._columnwise_mx_scale, t._fp8_dtype, rows=C, k=R)
         hp = t.dequantize(dtype=torch.bfloat16 if t._dtype == torch.float32 else t._dtype)
         return as_operand(hp, usage)
     t2d = t.reshape(-1, t.shape[-1])

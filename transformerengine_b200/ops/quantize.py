@@ -212,13 +212,20 @@ def _quantize_nvfp4_cuda(x2d, rowwise, columnwise, with_rht, with_2d, sr, reduce
     rs = torch.zeros(mx_scale_numel(R, C // 16), dtype=torch.uint8, device=dev) if rowwise else None
     cd = torch.empty(C, R // 2, dtype=torch.uint8, device=dev) if columnwise else None
     cs = torch.zeros(mx_scale_numel(C, R // 16), dtype=torch.uint8, device=dev) if columnwise else None
-    seed = offset = 0
+    seed, ctr = 0, None
     if sr:
-        st = torch.cuda.get_rng_state(dev)
+        # the stream of random numbers is (seed, call counter): the counter lives on the device and is advanced
+        # by a device op, so there is no host synchronisation and a captured graph draws new numbers per replay
         seed = int(torch.cuda.initial_seed())
-        offset = int(torch.randint(0, 2**31 - 1, (1,)).item())
-    C_.quantize_nvfp4(x2d, R, C, ar, ac, rd, rs, cd, cs, bool(with_rht), bool(with_2d), bool(sr), seed, offset)
+        ctr = _SR_COUNTERS.get(dev)
+        if ctr is None:
+            ctr = _SR_COUNTERS[dev] = torch.zeros(1, dtype=torch.int64, device=dev)
+        ctr.add_(0x9E3779B1)
+    C_.quantize_nvfp4(x2d, R, C, ar, ac, rd, rs, cd, cs, bool(with_rht), bool(with_2d), bool(sr), seed, 0, ctr)
     return rd, rs, ar, cd, cs, ac
+
+
+_SR_COUNTERS: dict = {}
 
 
 def dequantize_nvfp4(packed, scales_swizzled, amax_t, R, C, out_dtype):

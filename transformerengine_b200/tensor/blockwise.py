@@ -1,10 +1,11 @@
 """FP8 block-scaled tensors (1x128 vectors or 128x128 squares, fp32 scales).
 
-Reference: ``pytorch/tensor/float8_blockwise_tensor.py:28-258``.  On Blackwell
-the reference converts these to MXFP8 before the GEMM
-(``pytorch/csrc/extensions/gemm.cpp:312-323``); this library dequantizes the
-block scales into the MXFP8 kernel the same way when power-of-two scales are
-used, and otherwise multiplies in high precision.
+Reference: ``pytorch/tensor/float8_blockwise_tensor.py:28-258``.  On Blackwell the reference converts
+these to MXFP8 before the GEMM (``pytorch/csrc/extensions/gemm.cpp:312-323``).  Here the quantize
+kernel (``csrc/quant/blockwise.cu``) writes, next to the compact fp32 scales, the same power-of-two
+scales as UE8M0 bytes in the tensor core's 128x4-tile layout (each 128-block scale repeated for its
+four 32-element sub-blocks), so the block-scaled tcgen05 GEMM multiplies these tensors exactly and
+with no conversion pass.  With fp32 (non power-of-two) scales the GEMM operands are dequantized.
 """
 from __future__ import annotations
 
@@ -27,6 +28,9 @@ class Float8BlockwiseQTensorStorage(QuantizedTensorStorage):
         self._is_2D_scaled = is_2D_scaled
         self._quantizer = quantizer
         self._dtype = dtype
+        # UE8M0 copies of the scales in the GEMM layout (set by the CUDA quantizer for power-of-two scales)
+        self._rowwise_mx_scale = None
+        self._columnwise_mx_scale = None
         if shape is None:
             shape = tuple(rowwise_data.shape) if rowwise_data is not None else tuple(reversed(columnwise_data.shape))
         self._shape = tuple(shape)
@@ -42,9 +46,9 @@ class Float8BlockwiseQTensorStorage(QuantizedTensorStorage):
 
     def update_usage(self, rowwise_usage=None, columnwise_usage=None):
         if rowwise_usage is False:
-            self._rowwise_data = self._rowwise_scale_inv = None
+            self._rowwise_data = self._rowwise_scale_inv = self._rowwise_mx_scale = None
         if columnwise_usage is False:
-            self._columnwise_data = self._columnwise_scale_inv = None
+            self._columnwise_data = self._columnwise_scale_inv = self._columnwise_mx_scale = None
 
     def _dequantize_impl(self, dtype=None):
         dtype = dtype or self._dtype
@@ -60,14 +64,16 @@ class Float8BlockwiseQTensorStorage(QuantizedTensorStorage):
         return self._dequantize_impl(dtype)
 
     def prepare_for_saving(self):
-        ts = [self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv]
+        ts = [self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
+              self._rowwise_mx_scale, self._columnwise_mx_scale]
         self._rowwise_data = self._rowwise_scale_inv = self._columnwise_data = self._columnwise_scale_inv = None
+        self._rowwise_mx_scale = self._columnwise_mx_scale = None
         return ts, self
 
     def restore_from_saved(self, tensors):
-        (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data,
-         self._columnwise_scale_inv) = tensors[:4]
-        return tensors[4:]
+        (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
+         self._rowwise_mx_scale, self._columnwise_mx_scale) = tensors[:6]
+        return tensors[6:]
 
 
 class Float8BlockwiseQTensor(Float8BlockwiseQTensorStorage, QuantizedTensor):
@@ -117,7 +123,38 @@ class Float8BlockQuantizer(Quantizer):
         self.force_pow_2_scales = force_pow_2_scales
         self.block_scaling_dim = block_scaling_dim
 
+    def _parts_cuda(self, x2d, rowwise, columnwise):
+        """One kernel: both copies, compact fp32 scales and (power-of-two scales) GEMM-layout UE8M0 scales."""
+        from ..ops import _ext
+        from ..ops.ref.quant import round_up
+
+        x2d = x2d if x2d.stride(-1) == 1 else x2d.contiguous()
+        R, C = x2d.shape
+        dev, two_d, pow2 = x2d.device, self.block_scaling_dim == 2, bool(self.force_pow_2_scales)
+        rkt, ckt = (C + 127) // 128, (R + 127) // 128
+        rd = rs = rmx = cd = cs = cmx = None
+        if rowwise:
+            rd = torch.empty(R, C, dtype=torch.uint8, device=dev)
+            rs = torch.empty((round_up(R, 128) // 128 if two_d else R), rkt, dtype=torch.float32, device=dev)
+            if pow2 and C % 32 == 0:
+                rmx = torch.zeros(round_up(R, 128) * rkt * 4, dtype=torch.uint8, device=dev)
+        if columnwise:
+            cd = torch.empty(C, R, dtype=torch.uint8, device=dev)
+            cs = torch.empty((round_up(C, 128) // 128 if two_d else C), ckt, dtype=torch.float32, device=dev)
+            if pow2 and R % 32 == 0:
+                cmx = torch.zeros(round_up(C, 128) * ckt * 4, dtype=torch.uint8, device=dev)
+        _ext.get().quantize_block128(x2d, 2 if two_d else 1, self.dtype == torch.float8_e5m2, pow2,
+                                     float(self.amax_epsilon), rd, rs, rmx, cd, cs, cmx)
+        return rd, rs, cd, cs, rmx, cmx
+
     def _parts(self, x2d, rowwise, columnwise):
+        from ..ops import _ext
+
+        if _ext.use_cuda(x2d) and x2d.dtype in (torch.bfloat16, torch.float16, torch.float32):
+            return self._parts_cuda(x2d, rowwise, columnwise)
+        return self._parts_ref(x2d, rowwise, columnwise) + (None, None)
+
+    def _parts_ref(self, x2d, rowwise, columnwise):
         dims = (128, 128) if self.block_scaling_dim == 2 else (1, 128)
         rd = rs = cd = cs = None
         if rowwise:
@@ -129,31 +166,36 @@ class Float8BlockQuantizer(Quantizer):
             cd = q.view(torch.uint8)
         return rd, rs, cd, cs
 
-    def _wrap(self, rd, rs, cd, cs, shape, hp_dtype, requires_grad=False):
+    def _wrap(self, rd, rs, cd, cs, shape, hp_dtype, requires_grad=False, rmx=None, cmx=None):
         kw = dict(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd, columnwise_scale_inv=cs,
                   fp8_dtype=self.dtype, is_2D_scaled=self.block_scaling_dim == 2, quantizer=self, shape=shape,
                   dtype=hp_dtype)
-        if self.internal:
-            return Float8BlockwiseQTensorStorage(**kw)
-        return Float8BlockwiseQTensor(requires_grad=requires_grad, **kw)
+        out = Float8BlockwiseQTensorStorage(**kw) if self.internal else \
+            Float8BlockwiseQTensor(requires_grad=requires_grad, **kw)
+        out._rowwise_mx_scale, out._columnwise_mx_scale = rmx, cmx
+        return out
 
     def quantize_impl(self, tensor, dtype=None):
         shape = tuple(tensor.shape)
-        rd, rs, cd, cs = self._parts(tensor.reshape(-1, shape[-1]), self.rowwise_usage, self.columnwise_usage)
+        rd, rs, cd, cs, rmx, cmx = self._parts(tensor.reshape(-1, shape[-1]), self.rowwise_usage,
+                                               self.columnwise_usage)
         if rd is not None:
             rd = rd.reshape(shape)
-        return self._wrap(rd, rs, cd, cs, shape, dtype or tensor.dtype)
+        return self._wrap(rd, rs, cd, cs, shape, dtype or tensor.dtype, rmx=rmx, cmx=cmx)
 
     def update_quantized(self, src, dst, *, noop_flag=None):
         shape = tuple(dst._shape)
-        rd, rs, cd, cs = self._parts(src.reshape(-1, shape[-1]), dst._rowwise_data is not None,
-                                     dst._columnwise_data is not None)
+        rd, rs, cd, cs, rmx, cmx = self._parts(src.reshape(-1, shape[-1]), dst._rowwise_data is not None,
+                                               dst._columnwise_data is not None)
         if rd is not None:
             dst._rowwise_data.copy_(rd.reshape(shape))
             dst._rowwise_scale_inv.copy_(rs)
+            dst._rowwise_mx_scale = rmx if dst._rowwise_mx_scale is None or rmx is None else dst._rowwise_mx_scale.copy_(rmx)
         if cd is not None:
             dst._columnwise_data.copy_(cd)
             dst._columnwise_scale_inv.copy_(cs)
+            dst._columnwise_mx_scale = cmx if dst._columnwise_mx_scale is None or cmx is None \
+                else dst._columnwise_mx_scale.copy_(cmx)
         return dst
 
     def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):

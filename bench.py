@@ -402,9 +402,16 @@ def run_ours(args):
     if use_graph:
         static_in = torch.empty_like(dev[0])
         static_in.copy_(dev[0])
-        gstep = te.graph.capture_step(train_step, (static_in,), warmup=max(args.warmup, 3),
-                                      sync_group=dist.group.WORLD if case["sync"] else None,
-                                      before_capture=case.get("before_capture"))
+        try:
+            gstep = te.graph.capture_step(train_step, (static_in,), warmup=max(args.warmup, 3),
+                                          sync_group=dist.group.WORLD if case["sync"] else None,
+                                          before_capture=case.get("before_capture"))
+        except Exception as e:  # noqa: BLE001  (the step stays correct without the graph: run it eagerly)
+            print(f"[rank {rank}] whole-step capture failed ({type(e).__name__}: {str(e)[:200]}); running eagerly",
+                  file=sys.stderr, flush=True)
+            torch.cuda.synchronize()
+            use_graph = False
+    if use_graph:
         per_step = gstep.kernels_per_replay
 
         def step_device(i):

@@ -27,7 +27,9 @@ namespace {
 
 using namespace gemm_detail;
 
-constexpr int kPairThreads = 64 + 8 * 32;  // producer warp, MMA warp, eight epilogue warps
+// producer warp, MMA warp and EW epilogue warps (4: each warp drains both column halves in turn; 8: one half
+// per warp, the accumulator is released after a single round of loads)
+constexpr int pair_threads(int ew) { return 64 + ew * 32; }
 constexpr int PM = 256;   // rows per pair tile
 constexpr int PN = 256;   // columns per pair tile
 
@@ -69,8 +71,8 @@ __device__ __forceinline__ bool pair_tile(const PairParams& p, int t, int& mb, i
   return true;
 }
 
-template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+template <int KIND, int EW>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(pair_threads(EW), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
@@ -103,7 +105,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int i = 0; i < C::kAccStages; ++i) {
       mbar_init(&tfull_bar[i], 1);
-      mbar_init(&tempty_bar[i], 16);  // eight epilogue warps in each of the two CTAs
+      mbar_init(&tempty_bar[i], 2 * EW);  // every epilogue warp of the two CTAs
     }
     mbar_fence_init();
   }
@@ -223,20 +225,19 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // Eight warps: warp w reads the TMEM lanes of quarter w % 4 (its rows) and the column half (w - 2) / 4.
     // Each thread pulls its 128 accumulator columns with four back-to-back loads and ONE wait, releases the
     // accumulator, and only then converts and stages the values: the tensor core waits for loads, not stores.
+    constexpr int kHalvesPerWarp = EW == 8 ? 1 : 2;
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;          // 0: columns 0..127, 1: columns 128..255
+    const int half0 = EW == 8 ? (warp - 2) >> 2 : 0;   // 0: columns 0..127, 1: columns 128..255
     const int et = quarter * 32 + lane;        // row of this thread inside the CTA's 128 rows
-    const bool issuer = quarter == ((2 + half * 4) & 3) && lane == 0;  // lane 0 of the first warp of this half
+    const bool issuer = quarter == 2 && lane == 0;     // lane 0 of the first warp of a group of four
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
     const int dt = p.k.d_dtype;
     const bool wide = dt == kFloat32;          // a box (128 bytes per row) holds 32 fp32 or 64 16-bit columns
-    uint8_t* box = staging + half * C::kBoxBytes;   // one 16 KB box buffer per column half
-    uint8_t* my_row = box + et * 128;
     const int sw = et & 7;
-    const uint32_t bar_id = 1 + half;
-    bool box_in_flight = false;                // a TMA store may still be reading this half's buffer
+    const uint32_t bar_id = 1 + (EW == 8 ? half0 : 0);   // the four warps that share a box buffer
+    uint32_t in_flight = 0;                    // bit h: a TMA store may still be reading the buffer of half h
     int mb, nb;
     bool dead = false;  // a wait ran out: keep walking the loop (the named barriers need every warp), wait no more
     for (int t = pair; pair_tile(p, t, mb, nb); t += num_pairs) {
@@ -246,16 +247,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       tc_fence_after();
       const int row0 = mb * PM + static_cast<int>(rank) * 128;
+#pragma unroll 1
+      for (int hh = 0; hh < kHalvesPerWarp; ++hh) {
+      const int half = half0 + hh;
+      uint8_t* box = staging + half * C::kBoxBytes;   // one 16 KB box buffer per column half
+      uint8_t* my_row = box + et * 128;
       const int n0 = nb * PN + half * 128;
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * PN + half * 128;
       uint32_t r[4][32];
 #pragma unroll
       for (int j = 0; j < 4; ++j) tmem_ld_32x32(taddr + j * 32, r[j]);
       tmem_ld_wait();
-      // every column of the accumulator is in registers: the MMA warp may overwrite it
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      if (hh == kHalvesPerWarp - 1) {
+        // every column of the accumulator is in registers: the MMA warp may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      }
       if (p.k.bias != nullptr) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -281,8 +289,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
       for (int bx = 0; bx < 4; ++bx) {
         if (bx < nboxes) {
-          if (box_in_flight) {
-            if (issuer) tma_store_wait_read<0>();   // the previous store has finished reading the buffer
+          if (in_flight & (1u << half)) {
+            if (issuer) tma_store_wait_read<0>();   // every earlier store has finished reading shared memory
             named_bar_sync(bar_id, 128);
           }
           if (wide) {
@@ -320,8 +328,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             tma_store_commit();
           }
-          box_in_flight = true;
+          in_flight |= 1u << half;
         }
+      }
       }
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
@@ -337,7 +346,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <int KIND>
+template <int KIND, int EW>
 cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   using C = PairCfg<KIND>;
   CUtensorMap ta, tb, tsa, tsb;
@@ -380,7 +389,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   p.num_n = (a.N + PN - 1) / PN;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<KIND, EW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          C::kSmemBytes);
     if (e != cudaSuccess) return e;
     attr_set = true;
@@ -392,7 +401,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   if (max_pairs == 0) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms - sms % 2);
-    cfg.blockDim = dim3(kPairThreads);
+    cfg.blockDim = dim3(pair_threads(EW));
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cudaLaunchAttribute at;
     at.id = cudaLaunchAttributeClusterDimension;
@@ -402,13 +411,13 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
     cfg.attrs = &at;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<KIND>, &cfg) != cudaSuccess || n <= 0) n = sms / 2;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<KIND, EW>, &cfg) != cudaSuccess || n <= 0) n = sms / 2;
     max_pairs = n;
   }
   long long pairs = max_pairs < sms / 2 ? max_pairs : sms / 2;
   if (tiles < pairs) pairs = tiles;
   if (pairs < 1) pairs = 1;
-  gemm_pair_kernel<KIND><<<static_cast<int>(pairs * 2), kPairThreads, C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, td, p);
+  gemm_pair_kernel<KIND, EW><<<static_cast<int>(pairs * 2), pair_threads(EW), C::kSmemBytes, stream>>>(ta, tb, tsa, tsb, td, p);
   return cudaGetLastError();
 }
 
@@ -426,7 +435,17 @@ bool gemm_pair_supported(const GemmArgs& a, bool mxfp8) {
   return true;
 }
 
-cudaError_t gemm_pair_bf16(const GemmArgs& a, cudaStream_t s) { return launch_pair<kKindF16>(a, s); }
-cudaError_t gemm_pair_mxfp8(const GemmArgs& a, cudaStream_t s) { return launch_pair<kKindMxf8>(a, s); }
+// TEB200_GEMM_EPI_WARPS=4 selects the four-warp epilogue (experiment knob; default eight)
+static int epilogue_warps() {
+  static const char* env = getenv("TEB200_GEMM_EPI_WARPS");
+  return (env != nullptr && atoi(env) == 4) ? 4 : 8;
+}
+
+cudaError_t gemm_pair_bf16(const GemmArgs& a, cudaStream_t s) {
+  return epilogue_warps() == 4 ? launch_pair<kKindF16, 4>(a, s) : launch_pair<kKindF16, 8>(a, s);
+}
+cudaError_t gemm_pair_mxfp8(const GemmArgs& a, cudaStream_t s) {
+  return epilogue_warps() == 4 ? launch_pair<kKindMxf8, 4>(a, s) : launch_pair<kKindMxf8, 8>(a, s);
+}
 
 }  // namespace teb200

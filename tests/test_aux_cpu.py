@@ -285,3 +285,79 @@ def test_debug_stats_are_reduced_over_the_group():
     for rank, err, tb in res:
         assert tb is None, tb
         assert err < 1e-4, (rank, err)
+
+
+def test_newton_schulz_orthogonalises_and_save_original_input():
+    torch.manual_seed(0)
+    g = torch.randn(24, 64)
+    x = te.newton_schulz(g, steps=8)
+    s = torch.linalg.svdvals(x.float())
+    assert s.max() < 1.3 and s.min() > 0.5          # singular values pulled towards 1
+    xt = te.newton_schulz(g.t().contiguous(), steps=8)
+    assert torch.allclose(xt, x.t(), atol=1e-4)
+    # save_original_input: same result, the unquantized input is what is kept for the backward
+    lin = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu", save_original_input=True)
+    ref = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu")
+    ref.load_state_dict(lin.state_dict())
+    inp = torch.randn(32, 64)
+    outs = []
+    for m in (lin, ref):
+        xi = inp.clone().requires_grad_()
+        with te.autocast(enabled=True, recipe=te.recipe.MXFP8BlockScaling()):
+            y = m(xi)
+        y.square().sum().backward()
+        outs.append((y.detach(), xi.grad, m.weight.grad))
+    for a, b in zip(*outs):
+        assert torch.allclose(a, b, atol=1e-6)
+    import pytest as _pytest
+
+    with _pytest.raises(NotImplementedError):
+        te.Linear(8, 8, device="cpu", symmetric_ar_type="multimem_all_reduce")
+
+
+def _ns_worker(rank, world, port, result_q):
+    import torch.distributed as dist
+
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.manual_seed(0)
+        full = torch.randn(16, 96)
+        want = te.newton_schulz(full, steps=6)
+        shard = full.chunk(world, dim=1)[rank].contiguous()
+        got = te.newton_schulz(shard, steps=6, group=dist.group.WORLD, partition_dim=1)
+        err = (got - want.chunk(world, dim=1)[rank]).abs().max().item()
+        # row-sharded tall matrix
+        tall = full.t().contiguous()
+        got_t = te.newton_schulz(tall.chunk(world, dim=0)[rank].contiguous(), steps=6, group=dist.group.WORLD,
+                                 partition_dim=0)
+        err = max(err, (got_t - want.t().chunk(world, dim=0)[rank]).abs().max().item())
+        result_q.put((rank, err, None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_newton_schulz_on_a_sharded_matrix():
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ns_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, err, tb in res:
+        assert tb is None, tb
+        assert err < 1e-4, (rank, err)

@@ -42,6 +42,8 @@ def parallel_cross_entropy(inp: torch.Tensor, target: torch.Tensor, label_smooth
     With ``dist_process_group`` the vocabulary dimension is sharded over that group (rank ``r``
     holds entries ``[r*V/tp, (r+1)*V/tp)``) and only three floats per row cross the group.
     Returns the mean over non-ignored tokens when ``reduce_loss``, else the per-token losses.
+    ``is_cg_capturable`` needs no special path: forward and backward never synchronise with the host, so the
+    function can always be recorded in a CUDA graph.
     """
     if label_smoothing != 0.0:
         raise NotImplementedError("label smoothing is not supported by the fused kernel")

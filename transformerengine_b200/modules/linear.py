@@ -40,8 +40,10 @@ class _Linear(torch.autograd.Function):
             if out is None:
                 xq = F.gather_input(x2d, cfg, in_q, True, need_wgrad)
         else:
-            xq = F.quantize_for_gemm(x2d, in_q, True, need_wgrad)
-            save_x = xq
+            keep_original = getattr(module, "save_original_input", False) and need_wgrad
+            xq = F.quantize_for_gemm(x2d, in_q, True, need_wgrad and not keep_original)
+            # save_original_input: keep the unquantized input and quantize its wgrad copy in the backward
+            save_x = x2d if keep_original else xq
         if out is None:
             out, _ = F.linear_fprop(xq, weight_q, bias, cfg, cfg.activation_dtype)
         if grad_on:
@@ -109,6 +111,8 @@ class _Linear(torch.autograd.Function):
             if ctx.gathered_in_fwd:
                 in_q = module.get_quantizer(True, 0) if ctx.fp8 else None
                 xw = F.gathered_wgrad_input(keep_x, x_total, cfg, in_q)
+            elif ctx.fp8 and not F._is_q(keep_x) and getattr(module, "save_original_input", False):
+                xw = F.quantize_for_gemm(keep_x, module.get_quantizer(True, 0), False, True)
             if ctx.dist_w:
                 full_grad = F.linear_wgrad(dyq, xw, w_full, cfg)
                 dw = DW.finalize_weight_grads(weight, [full_grad])[0]
@@ -155,8 +159,17 @@ class Linear(TransformerEngineBaseModule):
         self.get_rng_state_tracker, self.rng_tracker_name = get_rng_state_tracker, rng_tracker_name
         self.name = name
         self.ub_name = ub_name
+        # ub_* requests: in this library the collectives are fused into the GEMM kernels for every tensor-parallel
+        # module once ``initialize_ub(tp_group=...)`` was called (bulk overlap of the wgrad operands included);
+        # a request without that call is reported at the first forward
         self.ub_overlap_ag, self.ub_overlap_rs = ub_overlap_ag, ub_overlap_rs
-        self.symmetric_ar_type = symmetric_ar_type
+        self._ub_requested = any((ub_overlap_ag, ub_overlap_rs, ub_overlap_rs_dgrad, ub_bulk_dgrad, ub_bulk_wgrad))
+        if symmetric_ar_type is not None:
+            raise NotImplementedError("symmetric_ar_type: the symmetric-memory all-reduce variants are not built; "
+                                      "tensor-parallel all-reduces use NCCL or, with sequence parallelism, the "
+                                      "fused reduce-scatter kernels")
+        self.symmetric_ar_type = None
+        self.save_original_input = save_original_input
         if tp_group is None:
             self.tp_size = tp_size
             if tp_size == 1:
@@ -279,6 +292,15 @@ class Linear(TransformerEngineBaseModule):
 
     def forward(self, inp: torch.Tensor, is_first_microbatch: Optional[bool] = None, fp8_output: bool = False,
                 fp8_grad: bool = False):
+        if self._ub_requested:
+            from ..parallel import comm_gemm
+
+            if self.tp_size > 1 and not comm_gemm.enabled_for(self.tp_group):
+                import warnings
+
+                warnings.warn("ub_overlap_* / ub_bulk_* was requested but initialize_ub(tp_group=...) has not been "
+                              "called: the collectives of this module run on NCCL")
+            self._ub_requested = False
         self.prepare_forward(num_gemms=1)
         if inp.dtype in (torch.bfloat16, torch.float16, torch.float32) and torch.is_autocast_enabled():
             self.cfg.activation_dtype = torch.get_autocast_gpu_dtype()

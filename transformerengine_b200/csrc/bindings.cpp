@@ -56,7 +56,7 @@ at::Tensor status(int device) { return status_tensor(device); }
 void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, const OptT& sfa, const OptT& sfb,
           const OptT& bias, const OptT& aux, int epilogue, bool accumulate, bool a_e5m2, bool b_e5m2, bool a_mn,
           bool b_mn, double alpha, const OptT& alpha_dev, const OptT& group_offsets, int num_groups, int sm_count,
-          int64_t K_override) {
+          int64_t K_override, int64_t sf_k_tiles) {
   c10::cuda::CUDAGuard guard(a.device());
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && d.dim() == 2, "gemm operands must be 2-D");
   TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1 && d.stride(1) == 1, "gemm operands must be row-major");
@@ -105,6 +105,7 @@ void gemm(int kind, const at::Tensor& a, const at::Tensor& b, at::Tensor& d, con
   g.num_groups = num_groups;
   g.group_offsets = ptr<int32_t>(group_offsets);
   g.sm_count = sm_count;
+  g.sf_k_tiles = static_cast<int>(sf_k_tiles);
   g.status = status_tensor(a.get_device()).data_ptr<int>();
   cudaError_t e = kind == 0   ? teb200::gemm_bf16(g, stream())
                   : kind == 1 ? teb200::gemm_mxfp8(g, stream())
@@ -444,7 +445,11 @@ void register_extra(py::module_& m);  // bindings of kernels added in other tran
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("status", &status);
   m.def("launch_count", &launch_count);
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("kind"), py::arg("a"), py::arg("b"), py::arg("d"), py::arg("sfa"), py::arg("sfb"),
+        py::arg("bias"), py::arg("aux"), py::arg("epilogue"), py::arg("accumulate"), py::arg("a_e5m2"),
+        py::arg("b_e5m2"), py::arg("a_mn"), py::arg("b_mn"), py::arg("alpha"), py::arg("alpha_dev"),
+        py::arg("group_offsets"), py::arg("num_groups"), py::arg("sm_count"), py::arg("K_override") = 0,
+        py::arg("sf_k_tiles") = 0);
   m.def("quantize", &quantize);
   m.def("quantize_block128", &quantize_block128);
   m.def("dequantize_mxfp8", &dequantize_mxfp8);

@@ -351,7 +351,7 @@ cudaError_t launch_pair(const GemmArgs& a, cudaStream_t stream) {
   using C = PairCfg<KIND>;
   CUtensorMap ta, tb, tsa, tsb;
   bool ok;
-  const int k_tiles = KIND == kKindMxf8 ? ((a.K + 31) / 32 + 3) / 4 : 0;
+  const int k_tiles = KIND == kKindMxf8 ? (a.sf_k_tiles > 0 ? a.sf_k_tiles : ((a.K + 31) / 32 + 3) / 4) : 0;
   if (KIND == kKindF16) {
     ok = make_tensor_map_2d(&ta, a.a, a.a_dtype, a.M, a.K, a.lda, 128, 64, true) &&
          make_tensor_map_2d(&tb, a.b, a.b_dtype, a.N, a.K, a.ldb, PN / 2, 64, true);

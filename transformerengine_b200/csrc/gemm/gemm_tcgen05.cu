@@ -432,6 +432,7 @@ cudaError_t launch(const GemmArgs& a, cudaStream_t stream) {
   p.num_groups = a.num_groups;
   const int sf_per_elem = KIND == kKindMxf8 ? 32 : 16;
   p.sf_k_tiles = (KIND == kKindF16 || KIND == kKindF8) ? 0 : ((a.K + sf_per_elem - 1) / sf_per_elem + 3) / 4;
+  if (a.sf_k_tiles > 0 && p.sf_k_tiles > 0) p.sf_k_tiles = a.sf_k_tiles;
 
   static bool attr_set = false;
   if (!attr_set) {

@@ -44,6 +44,10 @@ struct GemmArgs {
   // B rows [g*N, (g+1)*N).  `group_offsets` is a device array [num_groups+1] of row offsets.
   int num_groups = 0;
   const int32_t* group_offsets = nullptr;
+  // Block-scaled kinds: k-tiles (of 4 scales) per row tile in the scale buffers of BOTH operands when they are
+  // views of wider tensors (a slab of the contraction dim: data pointers and sfa / sfb point at the slab's
+  // first column / first k-tile, the pitch stays that of the whole tensor).  0: derived from K.
+  int sf_k_tiles = 0;
 };
 
 // dense / grouped tcgen05 GEMMs

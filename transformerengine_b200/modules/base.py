@@ -242,6 +242,9 @@ class TransformerEngineBaseModule(torch.nn.Module):
         """Quantize every cached weight again INTO its existing storage, so that kernels recorded in a
         CUDA graph (which hold those addresses) see the new values."""
         for name, (key, q, weight, quantizer) in list(self._weight_cache.items()):
+            if weight is None:      # derived entries (stacked operands of grouped layers): rebuilt on next use
+                del self._weight_cache[name]
+                continue
             quantizer.set_usage(rowwise=True, columnwise=q.get_usages()["columnwise"])
             quantizer.internal = True
             quantizer.update_quantized(weight.detach(), q)

@@ -67,9 +67,7 @@ class _GroupedLinear(torch.autograd.Function):
             if aligned and x2d.shape[0] > 0:
                 xq = in_q(x2d)  # one quantization for all slabs
                 a = as_operand(xq, "rowwise")
-                b_data = torch.cat([as_operand(w, "rowwise").data for w in wqs], 0)
-                b_scale = torch.cat([as_operand(w, "rowwise").scale for w in wqs], 0)
-                b = Operand("mxfp8", b_data, b_scale, in_q.dtype, rows=G * N, k=K)
+                b = module.stacked_weight_operand(wqs, "rowwise")
                 if _can_group(m_splits, a, True):
                     gemm_nt(a, b, out=out, group_offsets=_offsets(m_splits, x2d.device), num_groups=G)
                 else:
@@ -115,6 +113,38 @@ class _GroupedLinear(torch.autograd.Function):
         dws = [None] * G
         dbs = [None] * G
         x_hp = None  # input dequantized ONCE when it was saved as one quantized tensor
+        if ctx.fp8q and isinstance(ctx.xq, QuantizedTensorStorage) and dy.is_cuda and dy.shape[0] > 0 \
+                and N % 32 == 0 and all(m % 128 == 0 for m in m_splits):
+            # Slabs are whole 128-row tiles: grad_output is quantized ONCE (both copies), dgrad is one grouped
+            # launch over the stacked column-wise weights, and every wgrad GEMM reads its slab as a view of the
+            # column-wise copies (contraction over the slab's rows) -- nothing is dequantized or re-quantized.
+            from ..ops.gemm import contraction_slab
+
+            gq = module.get_quantizer(False, 0)
+            gq.set_usage(rowwise=True, columnwise=True)
+            gq.internal = True
+            dyq = gq(dy)
+            wcol = module.stacked_weight_operand(ctx.wqs, "columnwise")        # [G * K, N]
+            gemm_nt(as_operand(dyq, "rowwise"), wcol, out=dx, group_offsets=_offsets(m_splits, dy.device), num_groups=G)
+            dy_col, x_col = as_operand(dyq, "columnwise"), as_operand(ctx.xq, "columnwise")
+            for g in range(G):
+                if module.use_bias:
+                    dbs[g] = dy[offs[g]:offs[g + 1]].float().sum(0).to(weights[g].dtype)
+                if m_splits[g] == 0:
+                    dws[g] = torch.zeros_like(weights[g])
+                    continue
+                dws[g] = gemm_nt(contraction_slab(dy_col, offs[g], offs[g + 1]),
+                                 contraction_slab(x_col, offs[g], offs[g + 1]),
+                                 out_dtype=weights[g].dtype if weights[g].dtype != torch.float32 else torch.float32)
+                if module.fuse_wgrad_accumulation and hasattr(weights[g], "main_grad"):
+                    weights[g].main_grad.add_(dws[g].float())
+                    dws[g] = None
+            if ctx.reduce_bwd_amax:
+                FP8GlobalStateManager.reduce_and_update_fp8_tensors(forward=False)
+            res = [dx.reshape(ctx.inp_shape), None, None, None] + dws
+            if module.use_bias:
+                res += dbs
+            return tuple(res)
         for g in range(G):
             sl = slice(offs[g], offs[g + 1])
             if module.use_bias:
@@ -158,6 +188,21 @@ class _GroupedLinear(torch.autograd.Function):
 
 
 class GroupedLinear(TransformerEngineBaseModule):
+    def stacked_weight_operand(self, wqs, usage: str) -> Operand:
+        """All groups' quantized weights as ONE grouped-GEMM operand (rows of group g at ``[g*rows, (g+1)*rows)``).
+        The concatenation is cached until the weights change (it is redone once per optimizer step)."""
+        from .base import weights_epoch
+
+        key = (usage, weights_epoch(), tuple(id(w) for w in wqs))
+        ent = self._weight_cache.get(f"stacked_{usage}")
+        if ent is not None and ent[0] == key:
+            return ent[1]
+        ops_ = [as_operand(w, usage) for w in wqs]
+        op = Operand("mxfp8", torch.cat([o.data for o in ops_], 0), torch.cat([o.scale for o in ops_], 0),
+                     ops_[0].fp8_dtype, rows=sum(o.rows for o in ops_), k=ops_[0].k)
+        self._weight_cache[f"stacked_{usage}"] = (key, op, None, None)
+        return op
+
     def __init__(self, num_gemms: int, in_features: int, out_features: int, sequence_parallel: bool = False,
                  fuse_wgrad_accumulation: bool = False, tp_group=None, tp_size: int = 1,
                  get_rng_state_tracker: Optional[Callable] = None, rng_tracker_name: Optional[str] = None,

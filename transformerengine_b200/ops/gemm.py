@@ -37,6 +37,7 @@ class Operand:
     k: int = 0
     rht: bool = False
     hp_fallback: Optional[torch.Tensor] = None  # dequantized values (set lazily)
+    sf_k_tiles: int = 0  # MXFP8 view of a slab of the contraction dim: k-tiles per row tile of the WHOLE tensor
 
 
 def as_operand(t, usage: str = "rowwise") -> Operand:
@@ -96,6 +97,18 @@ def as_operand(t, usage: str = "rowwise") -> Operand:
     if row:
         return Operand("hp", t2d, rows=t2d.shape[0], k=t2d.shape[1])
     return Operand("hp", t2d.t(), rows=t2d.shape[1], k=t2d.shape[0])
+
+
+def contraction_slab(op: Operand, k0: int, k1: int) -> Operand:
+    """View of an MXFP8 (or 16-bit) operand restricted to columns ``[k0, k1)`` of its contraction dim, both
+    multiples of 128: no copy; block scales are addressed with the whole tensor's tile pitch."""
+    assert k0 % 128 == 0 and k1 % 128 == 0 and 0 <= k0 <= k1 <= op.k
+    if op.kind == "hp":
+        return Operand("hp", op.data[:, k0:k1], rows=op.rows, k=k1 - k0)
+    assert op.kind == "mxfp8", "contraction slabs are implemented for MXFP8 and 16-bit operands"
+    total = op.sf_k_tiles or (Q.round_up((op.k + 31) // 32, 4) // 4)
+    return Operand("mxfp8", op.data[:, k0:k1], op.scale[(k0 // 128) * 512:], op.fp8_dtype, rows=op.rows, k=k1 - k0,
+                   sf_k_tiles=total)
 
 
 def _dequant_operand(op: Operand, dtype=torch.float32) -> torch.Tensor:
@@ -258,9 +271,12 @@ def _gemm_cuda(a, b, out, bias, accumulate, epilogue, aux, alpha, group_offsets,
             d.copy_(out)
     if bias is not None and epilogue == EPI_NONE:
         epilogue = EPI_BIAS
+    sfk = max(a.sf_k_tiles, b.sf_k_tiles) if kind == KIND_MXFP8 else 0
+    if sfk:
+        assert a.sf_k_tiles == b.sf_k_tiles, "slab views of the contraction dim must come from equally long tensors"
     C_.gemm(kind, ad, bd, d, sfa, sfb, bias, aux, epilogue, accumulate,
             a.fp8_dtype == torch.float8_e5m2, b.fp8_dtype == torch.float8_e5m2, a_mn, b_mn, float(alpha), alpha_dev,
-            group_offsets, num_groups, sm_count, 0)
+            group_offsets, num_groups, sm_count, 0, sfk)
     if d is not out:
         out.copy_(d)
     return out

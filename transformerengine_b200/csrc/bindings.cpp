@@ -4,6 +4,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <teb200/api.h>
+#include <teb200/nvtx.h>
 #include <teb200/misc.h>
 #include <teb200/norm.h>
 #include <teb200/quant.h>
@@ -443,27 +444,27 @@ void rope(const at::Tensor& x, at::Tensor& out, const at::Tensor& freqs, int64_t
 void register_extra(py::module_& m);  // bindings of kernels added in other translation units
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("status", &status);
-  m.def("launch_count", &launch_count);
-  m.def("gemm", &gemm, py::arg("kind"), py::arg("a"), py::arg("b"), py::arg("d"), py::arg("sfa"), py::arg("sfb"),
+  m.def("status", teb200::traced("teb200.status", &status));
+  m.def("launch_count", teb200::traced("teb200.launch_count", &launch_count));
+  m.def("gemm", teb200::traced("teb200.gemm", &gemm), py::arg("kind"), py::arg("a"), py::arg("b"), py::arg("d"), py::arg("sfa"), py::arg("sfb"),
         py::arg("bias"), py::arg("aux"), py::arg("epilogue"), py::arg("accumulate"), py::arg("a_e5m2"),
         py::arg("b_e5m2"), py::arg("a_mn"), py::arg("b_mn"), py::arg("alpha"), py::arg("alpha_dev"),
         py::arg("group_offsets"), py::arg("num_groups"), py::arg("sm_count"), py::arg("K_override") = 0,
         py::arg("sf_k_tiles") = 0);
-  m.def("quantize", &quantize);
-  m.def("quantize_block128", &quantize_block128);
-  m.def("dequantize_mxfp8", &dequantize_mxfp8);
-  m.def("dequantize_fp8", &dequantize_fp8);
-  m.def("amax", &amax);
-  m.def("swizzle", &swizzle);
-  m.def("norm_fwd", &norm_fwd);
-  m.def("norm_bwd", &norm_bwd);
-  m.def("norm_bwd_workspace", &norm_bwd_workspace);
-  m.def("multi_tensor_adam", &multi_tensor_adam);
-  m.def("multi_tensor_sgd", &multi_tensor_sgd);
-  m.def("multi_tensor_scale", &multi_tensor_scale);
-  m.def("multi_tensor_l2norm_sq", &multi_tensor_l2norm_sq);
-  m.def("cross_entropy", &cross_entropy);
-  m.def("rope", &rope);
+  m.def("quantize", teb200::traced("teb200.quantize", &quantize));
+  m.def("quantize_block128", teb200::traced("teb200.quantize_block128", &quantize_block128));
+  m.def("dequantize_mxfp8", teb200::traced("teb200.dequantize_mxfp8", &dequantize_mxfp8));
+  m.def("dequantize_fp8", teb200::traced("teb200.dequantize_fp8", &dequantize_fp8));
+  m.def("amax", teb200::traced("teb200.amax", &amax));
+  m.def("swizzle", teb200::traced("teb200.swizzle", &swizzle));
+  m.def("norm_fwd", teb200::traced("teb200.norm_fwd", &norm_fwd));
+  m.def("norm_bwd", teb200::traced("teb200.norm_bwd", &norm_bwd));
+  m.def("norm_bwd_workspace", teb200::traced("teb200.norm_bwd_workspace", &norm_bwd_workspace));
+  m.def("multi_tensor_adam", teb200::traced("teb200.multi_tensor_adam", &multi_tensor_adam));
+  m.def("multi_tensor_sgd", teb200::traced("teb200.multi_tensor_sgd", &multi_tensor_sgd));
+  m.def("multi_tensor_scale", teb200::traced("teb200.multi_tensor_scale", &multi_tensor_scale));
+  m.def("multi_tensor_l2norm_sq", teb200::traced("teb200.multi_tensor_l2norm_sq", &multi_tensor_l2norm_sq));
+  m.def("cross_entropy", teb200::traced("teb200.cross_entropy", &cross_entropy));
+  m.def("rope", teb200::traced("teb200.rope", &rope));
   register_extra(m);
 }

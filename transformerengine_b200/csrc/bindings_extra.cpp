@@ -6,6 +6,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <teb200/api.h>
+#include <teb200/nvtx.h>
 #include <teb200/comm.h>
 #include <teb200/misc.h>
 #include <teb200/quant.h>
@@ -750,53 +751,53 @@ void delayed_scaling_update(const at::Tensor& history, const at::Tensor& scale, 
 }  // namespace
 
 void register_extra(py::module_& m) {
-  m.def("delayed_scaling_update", &delayed_scaling_update);
-  m.def("softmax_fwd", &softmax_fwd);
-  m.def("softmax_bwd", &softmax_bwd);
-  m.def("dropout_fwd", &dropout_fwd);
-  m.def("dropout_bwd", &dropout_bwd);
-  m.def("peer_sum", &peer_sum);
-  m.def("ep_counts", &ep_counts);
-  m.def("ep_push", &ep_push);
-  m.def("ep_wait", &ep_wait, py::arg("flags_ptr"), py::arg("n"), py::arg("epoch"), py::arg("status"),
+  m.def("delayed_scaling_update", teb200::traced("teb200.delayed_scaling_update", &delayed_scaling_update));
+  m.def("softmax_fwd", teb200::traced("teb200.softmax_fwd", &softmax_fwd));
+  m.def("softmax_bwd", teb200::traced("teb200.softmax_bwd", &softmax_bwd));
+  m.def("dropout_fwd", teb200::traced("teb200.dropout_fwd", &dropout_fwd));
+  m.def("dropout_bwd", teb200::traced("teb200.dropout_bwd", &dropout_bwd));
+  m.def("peer_sum", teb200::traced("teb200.peer_sum", &peer_sum));
+  m.def("ep_counts", teb200::traced("teb200.ep_counts", &ep_counts));
+  m.def("ep_push", teb200::traced("teb200.ep_push", &ep_push));
+  m.def("ep_wait", teb200::traced("teb200.ep_wait", &ep_wait), py::arg("flags_ptr"), py::arg("n"), py::arg("epoch"), py::arg("status"),
         py::arg("limit_cycles") = 0);
-  m.def("ep_signal", &ep_signal);
-  m.def("ep_pull", &ep_pull);
-  m.def("router_topk", &router_topk);
-  m.def("router_topk_bwd", &router_topk_bwd);
-  m.def("permute_rows", &permute_rows);
-  m.def("unpermute_rows", &unpermute_rows);
-  m.def("build_dest_rows", &build_dest_rows);
-  m.def("nvfp4_amax", &nvfp4_amax);
-  m.def("quantize_nvfp4", &quantize_nvfp4);
-  m.def("dequantize_nvfp4", &dequantize_nvfp4);
-  m.def("comm_gemm", &comm_gemm, py::arg("mode"), py::arg("rank"), py::arg("world"), py::arg("epoch_dev"),
+  m.def("ep_signal", teb200::traced("teb200.ep_signal", &ep_signal));
+  m.def("ep_pull", teb200::traced("teb200.ep_pull", &ep_pull));
+  m.def("router_topk", teb200::traced("teb200.router_topk", &router_topk));
+  m.def("router_topk_bwd", teb200::traced("teb200.router_topk_bwd", &router_topk_bwd));
+  m.def("permute_rows", teb200::traced("teb200.permute_rows", &permute_rows));
+  m.def("unpermute_rows", teb200::traced("teb200.unpermute_rows", &unpermute_rows));
+  m.def("build_dest_rows", teb200::traced("teb200.build_dest_rows", &build_dest_rows));
+  m.def("nvfp4_amax", teb200::traced("teb200.nvfp4_amax", &nvfp4_amax));
+  m.def("quantize_nvfp4", teb200::traced("teb200.quantize_nvfp4", &quantize_nvfp4));
+  m.def("dequantize_nvfp4", teb200::traced("teb200.dequantize_nvfp4", &dequantize_nvfp4));
+  m.def("comm_gemm", teb200::traced("teb200.comm_gemm", &comm_gemm), py::arg("mode"), py::arg("rank"), py::arg("world"), py::arg("epoch_dev"),
         py::arg("copy_ctas"), py::arg("a"), py::arg("sfa"), py::arg("b"), py::arg("sfb"), py::arg("d"), py::arg("bias"),
         py::arg("a_e5m2"), py::arg("b_e5m2"), py::arg("a_ptrs"), py::arg("sfa_ptrs"), py::arg("ready_ptrs"),
         py::arg("chunk_flags_ptr"), py::arg("stage_ptrs"), py::arg("tile_flag_ptrs"), py::arg("out"), py::arg("N"),
         py::arg("status"), py::arg("side_src_ptrs") = std::vector<int64_t>(), py::arg("side_dst") = py::none(),
         py::arg("side_dst_sf") = py::none(), py::arg("side_geom") = std::vector<int64_t>());
-  m.def("flash_fwd", &flash_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
+  m.def("flash_fwd", teb200::traced("teb200.flash_fwd", &flash_fwd), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
         py::arg("timeline") = py::none(), py::arg("window_left") = -1, py::arg("window_right") = -1);
-  m.def("flash_bwd", &flash_bwd, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+  m.def("flash_bwd", teb200::traced("teb200.flash_bwd", &flash_bwd), py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
         py::arg("lse"), py::arg("delta"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("scale"),
         py::arg("causal"), py::arg("bottom_right"), py::arg("status"), py::arg("window_left") = -1,
         py::arg("window_right") = -1);
-  m.def("thd_get_partitioned_indices", &thd_get_partitioned_indices);
-  m.def("thd_read_half_tensor", &thd_read_half_tensor);
-  m.def("thd_second_half_lse_correction", &thd_second_half_lse_correction);
-  m.def("thd_read_second_half_lse", &thd_read_second_half_lse);
-  m.def("thd_out_correction", &thd_out_correction);
-  m.def("thd_grad_correction", &thd_grad_correction);
-  m.def("convert_thd_to_bshd", &convert_thd_to_bshd);
-  m.def("convert_bshd_to_thd", &convert_bshd_to_thd);
-  m.def("kv_cache_step", &kv_cache_step);
-  m.def("flash_fwd_varlen", &flash_fwd_varlen, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
+  m.def("thd_get_partitioned_indices", teb200::traced("teb200.thd_get_partitioned_indices", &thd_get_partitioned_indices));
+  m.def("thd_read_half_tensor", teb200::traced("teb200.thd_read_half_tensor", &thd_read_half_tensor));
+  m.def("thd_second_half_lse_correction", teb200::traced("teb200.thd_second_half_lse_correction", &thd_second_half_lse_correction));
+  m.def("thd_read_second_half_lse", teb200::traced("teb200.thd_read_second_half_lse", &thd_read_second_half_lse));
+  m.def("thd_out_correction", teb200::traced("teb200.thd_out_correction", &thd_out_correction));
+  m.def("thd_grad_correction", teb200::traced("teb200.thd_grad_correction", &thd_grad_correction));
+  m.def("convert_thd_to_bshd", teb200::traced("teb200.convert_thd_to_bshd", &convert_thd_to_bshd));
+  m.def("convert_bshd_to_thd", teb200::traced("teb200.convert_bshd_to_thd", &convert_bshd_to_thd));
+  m.def("kv_cache_step", teb200::traced("teb200.kv_cache_step", &kv_cache_step));
+  m.def("flash_fwd_varlen", teb200::traced("teb200.flash_fwd_varlen", &flash_fwd_varlen), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"),
         py::arg("lse"), py::arg("cu_q"), py::arg("cu_k"), py::arg("off_q"), py::arg("off_k"), py::arg("max_sq"),
         py::arg("max_sk"), py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
         py::arg("window_left") = -1, py::arg("window_right") = -1);
-  m.def("flash_bwd_varlen", &flash_bwd_varlen, py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"),
+  m.def("flash_bwd_varlen", teb200::traced("teb200.flash_bwd_varlen", &flash_bwd_varlen), py::arg("dout"), py::arg("q"), py::arg("k"), py::arg("v"),
         py::arg("out"), py::arg("lse"), py::arg("delta"), py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("cu_q"),
         py::arg("cu_k"), py::arg("off_q"), py::arg("off_k"), py::arg("max_sq"), py::arg("max_sk"), py::arg("scale"),
         py::arg("causal"), py::arg("bottom_right"), py::arg("status"), py::arg("window_left") = -1,

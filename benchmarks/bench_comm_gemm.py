@@ -3,7 +3,12 @@
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/bench_comm_gemm.py
 
 Device time (CUDA events), max over ranks.  Roofline of a fused op = the slower of
-(FLOPs / GEMM rate of the dense kernel measured here) and (bytes over NVLink / 770 GB/s).
+(FLOPs / the measured peak of the dtype) and (bytes over NVLink / 770 GB/s, the measured peer copy rate).
+The dtype peaks are the best rates measured on this pool with large GEMMs: bf16 = the cuBLAS burst figure
+of MEASURED_PEAKS.json (1640 TFLOP/s fallback), MXFP8 = 3100 TFLOP/s (cuBLASLt block-scaled GEMM through
+``torch._scaled_mm``, ``benchmarks/bench_gemm.py``); override with --peak-bf16 / --peak-mxfp8.
+Also reports the fused kernel against the NCCL collective followed by this library's dense GEMM, and
+(``--side 1``) the fused kernel carrying the side gather of the weight-gradient operand (bulk overlap).
 """
 import argparse
 import json
@@ -42,7 +47,14 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="llama")
     ap.add_argument("--copy-ctas", type=int, default=12)
+    ap.add_argument("--peak-bf16", type=float, default=0.0, help="TFLOP/s; 0 = MEASURED_PEAKS.json or 1640")
+    ap.add_argument("--peak-mxfp8", type=float, default=3100.0, help="TFLOP/s")
+    ap.add_argument("--side", type=int, default=1, help="also time the kernels with the wgrad side gather")
     a = ap.parse_args()
+    peak_bf16 = a.peak_bf16
+    if peak_bf16 <= 0:
+        pk = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+        peak_bf16 = json.load(open(pk)).get("bf16_tflops", 1640.4) if os.path.exists(pk) else 1640.4
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
@@ -81,16 +93,42 @@ def main():
             t_rs_nccl = timed(lambda: dist.reduce_scatter_tensor(outrs, part))
             te.check_status()
             elem = 1 if mx else 2
-            ag_bytes = T * H * elem * (world - 1) / world
+            peak = (a.peak_mxfp8 if mx else peak_bf16) * 1e12
+            flops = 2.0 * T * H * Fl
+            ag_bytes = T * H * elem * (world - 1) / world + (T * H / 32 * (world - 1) / world if mx else 0)
             rs_bytes = T * H * 2 * (world - 1) / world
-            roof_ag = max(t_ag_gemm, ag_bytes / LINK_GBS / 1e6)
-            roof_rs = max(t_rs_gemm, rs_bytes / LINK_GBS / 1e6)
+            roof_ag = max(flops / peak * 1e3, ag_bytes / LINK_GBS / 1e6)
+            roof_rs = max(flops / peak * 1e3, rs_bytes / LINK_GBS / 1e6)
+            extra = {}
+            if a.side and mx:
+                # the same kernels carrying the column-wise copy of the local rows for the wgrad that follows
+                from transformerengine_b200.parallel.comm_gemm import SideSpec
+
+                R = T // world
+                q2 = MXFP8Quantizer(rowwise=True, columnwise=True)
+                xs = q2(xl)
+                ag_s = AllGatherGemm(g, T, H, mxfp8=True, copy_ctas=a.copy_ctas, side=SideSpec.for_mxfp8_columnwise(H, R))
+                rs_s = GemmReduceScatter(g, T, H, side=SideSpec.for_mxfp8_columnwise(H, R))
+                side = (xs._columnwise_data, xs._columnwise_scale_inv)
+                t_ag_side = timed(lambda: ag_s(xs, w1_o, side=side))
+                t_rs_side = timed(lambda: rs_s(x2_o, w2_o, side=side))
+                te.check_status()
+                side_bytes = (T * H + T * H / 32) * (world - 1) / world
+                extra = dict(ag_fused_with_side_ms=t_ag_side, rs_fused_with_side_ms=t_rs_side,
+                             ag_side_roofline_ms=max(flops / peak * 1e3, (ag_bytes + side_bytes) / LINK_GBS / 1e6),
+                             rs_side_roofline_ms=max(flops / peak * 1e3, max(rs_bytes, side_bytes) / LINK_GBS / 1e6))
+                extra["ag_side_frac_of_roofline"] = extra["ag_side_roofline_ms"] / t_ag_side
+                extra["rs_side_frac_of_roofline"] = extra["rs_side_roofline_ms"] / t_rs_side
+                del ag_s, rs_s
             if rank == 0:
-                print(json.dumps(dict(T=T, H=H, F_local=Fl, mxfp8=mx, world=world,
+                print(json.dumps(dict(T=T, H=H, F_local=Fl, mxfp8=mx, world=world, peak_tflops=peak / 1e12,
                                       ag_fused_ms=t_ag_fused, ag_gemm_ms=t_ag_gemm, ag_nccl_ms=t_ag_nccl,
                                       ag_roofline_ms=roof_ag, ag_frac_of_roofline=roof_ag / t_ag_fused,
+                                      ag_fused_over_nccl_plus_gemm=(t_ag_nccl + t_ag_gemm) / t_ag_fused,
                                       rs_fused_ms=t_rs_fused, rs_gemm_ms=t_rs_gemm, rs_nccl_ms=t_rs_nccl,
-                                      rs_roofline_ms=roof_rs, rs_frac_of_roofline=roof_rs / t_rs_fused)), flush=True)
+                                      rs_roofline_ms=roof_rs, rs_frac_of_roofline=roof_rs / t_rs_fused,
+                                      rs_fused_over_nccl_plus_gemm=(t_rs_nccl + t_rs_gemm) / t_rs_fused, **extra)),
+                      flush=True)
             del ag, rs
     dist.destroy_process_group()
 

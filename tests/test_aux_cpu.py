@@ -361,3 +361,83 @@ def test_newton_schulz_on_a_sharded_matrix():
     for rank, err, tb in res:
         assert tb is None, tb
         assert err < 1e-4, (rank, err)
+
+
+def _partial_cast_worker(rank, world, port, result_q):
+    import torch.distributed as dist
+
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from transformerengine_b200.tensor import Float8CurrentScalingQuantizer, MXFP8Quantizer
+        from transformerengine_b200.tensor.utils import post_all_gather_processing, quantize_master_weights
+
+        torch.manual_seed(0)
+        R, C = 64, 96
+        master_full = torch.randn(R, C) * 3
+        n = R * C
+        # uneven split in the middle of a row and of a 32-block
+        cut = 37 * C + 50
+        lo, hi = (0, cut) if rank == 0 else (cut, n)
+        shard = master_full.reshape(-1)[lo:hi].clone()
+        errs = {}
+        for name, make in (("mxfp8", lambda: MXFP8Quantizer(torch.float8_e4m3fn)),
+                           ("fp8cs", lambda: Float8CurrentScalingQuantizer(torch.float8_e4m3fn, device="cpu"))):
+            q = make()
+            w = q(torch.zeros(R, C))                 # the model weight to refresh (both copies for MXFP8)
+            quantize_master_weights([w], [shard], [lo], group=dist.group.WORLD)
+            # what a framework does next: every rank contributes the bytes it wrote (sum of disjoint parts)
+            def gather(t, mask):
+                buf = torch.where(mask, t.view(torch.uint8).reshape(-1), torch.zeros((), dtype=torch.uint8)).int()
+                dist.all_reduce(buf)
+                t.view(torch.uint8).reshape(-1).copy_(buf.to(torch.uint8))
+            flat = torch.arange(n)
+            mine = (flat >= lo) & (flat < hi)
+            if name == "mxfp8":
+                gather(w._rowwise_data, mine)
+                mine_t = mine.reshape(R, C).t().contiguous().reshape(-1)
+                gather(w._columnwise_data, mine_t)
+            else:
+                gather(w._data, mine)
+            post_all_gather_processing([w])
+            ref = make()(master_full)
+            if name == "mxfp8":
+                ok = torch.equal(w._rowwise_data.view(torch.uint8), ref._rowwise_data.view(torch.uint8)) and \
+                    torch.equal(w._columnwise_data.view(torch.uint8), ref._columnwise_data.view(torch.uint8)) and \
+                    torch.equal(w._rowwise_scale_inv, ref._rowwise_scale_inv) and \
+                    torch.equal(w._columnwise_scale_inv, ref._columnwise_scale_inv)
+            else:
+                ok = torch.equal(w._data.view(torch.uint8), ref._data.view(torch.uint8)) and \
+                    torch.allclose(w._scale_inv.reshape(-1), ref._scale_inv.reshape(-1))
+            errs[name] = ok
+        result_q.put((rank, errs, None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_sharded_master_weights_cast_with_partial_amax():
+    """Each rank casts only its shard; only amaxes cross the group; the assembled bytes equal a
+    quantization of the full master weight."""
+    import socket
+
+    import torch.multiprocessing as mp
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_partial_cast_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, errs, tb in res:
+        assert tb is None, tb
+        assert errs == {"mxfp8": True, "fp8cs": True}, (rank, errs)

@@ -46,7 +46,7 @@ def timed(fn, iters=10):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--shapes", default="llama")
-    ap.add_argument("--copy-ctas", type=int, default=12)
+    ap.add_argument("--copy-ctas", type=int, default=0, help="0 = chosen by the library per shape")
     ap.add_argument("--peak-bf16", type=float, default=0.0, help="TFLOP/s; 0 = MEASURED_PEAKS.json or 1640")
     ap.add_argument("--peak-mxfp8", type=float, default=3100.0, help="TFLOP/s")
     ap.add_argument("--side", type=int, default=1, help="also time the kernels with the wgrad side gather")
@@ -75,7 +75,7 @@ def main():
                 xl_o, w1_o, x2_o, w2_o = q(xl), q(w1), q(x2), q(w2)
             else:
                 xl_o, w1_o, x2_o, w2_o = xl, w1, x2, w2
-            ag = AllGatherGemm(g, T, H, mxfp8=mx, copy_ctas=a.copy_ctas)
+            ag = AllGatherGemm(g, T, H, mxfp8=mx, copy_ctas=a.copy_ctas or None)
             rs = GemmReduceScatter(g, T, H)
             xg = torch.empty(T, H, device="cuda", dtype=torch.bfloat16)
             dist.all_gather_into_tensor(xg, xl)
@@ -107,8 +107,8 @@ def main():
                 R = T // world
                 q2 = MXFP8Quantizer(rowwise=True, columnwise=True)
                 xs = q2(xl)
-                ag_s = AllGatherGemm(g, T, H, mxfp8=True, copy_ctas=a.copy_ctas, side=SideSpec.for_mxfp8_columnwise(H, R))
-                rs_s = GemmReduceScatter(g, T, H, side=SideSpec.for_mxfp8_columnwise(H, R))
+                ag_s = AllGatherGemm(g, T, H, mxfp8=True, copy_ctas=a.copy_ctas or None, side=SideSpec.for_mxfp8_columnwise(H, R))
+                rs_s = GemmReduceScatter(g, T, H, side=SideSpec.for_mxfp8_columnwise(H, R), copy_ctas=a.copy_ctas or None)
                 side = (xs._columnwise_data, xs._columnwise_scale_inv)
                 t_ag_side = timed(lambda: ag_s(xs, w1_o, side=side))
                 t_rs_side = timed(lambda: rs_s(x2_o, w2_o, side=side))

@@ -65,6 +65,7 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, const at::Tensor& epoc
   if (mode == teb200::kCommAllGather) {
     g.d = d->data_ptr();
     g.ldd = d->stride(0);
+    if (out.has_value() && out->defined()) g.aux = out->data_ptr();  // optional timeline buffer, as below
   } else if (d.has_value() && d->defined()) {
     g.aux = d->data_ptr();  // optional int64 [ctas, 4] timeline buffer (profiling aid)
   }

@@ -8,6 +8,8 @@
 //     reduces the blocks this rank owns once every rank has delivered them.
 // Tiles are visited in an order rotated by the rank so that at any time the ranks
 // pull from / push to different peers.
+#include <type_traits>
+
 #include <teb200/comm.h>
 #include <teb200/gemm_common.cuh>
 #include <teb200/ptx.cuh>
@@ -18,6 +20,12 @@ namespace {
 using namespace gemm_detail;
 
 constexpr int BN = 256;
+// warp 0: TMA producer, warp 1: MMA issuer, warps 2..9: epilogue (two groups of four, one per 128-column half
+// of the tile), warp 10: hands the staged half tiles to the copy engine and signals the owners
+constexpr int kEpiWarps = 8;
+constexpr int kEpiThreads = kEpiWarps * 32;
+constexpr int kStoreWarp = 2 + kEpiWarps;
+constexpr int kCommThreads = (kStoreWarp + 1) * 32;
 
 struct CommParams {
   KernelParams k;
@@ -310,14 +318,17 @@ __device__ __forceinline__ size_t stage_tile_offset(const CommParams& p, int src
   return ((static_cast<size_t>(src) * p.mb_per_rank + mbl) * p.num_n + nb) * 65536;
 }
 
-// Executed by the four epilogue warps (128 threads, named barrier 1) after their tile loop.
-template <typename T>
+// Executed by the eight epilogue warps (kEpiThreads threads, named barrier 1) after their tile loop.  A thread
+// keeps U vectors x world sources (about eight 16-byte loads) in flight, which is what lets the tail run near
+// the memory rate instead of at one DRAM round trip per vector.
+template <typename T, int U, int WMAX>
 __device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, uint32_t epoch) {
   const int items = p.mb_per_rank * p.num_n;
   const uint32_t expected = epoch * static_cast<uint32_t>(p.num_n) * 2u;  // two half tiles per tile
   const uint8_t* stage = p.stage[p.rank];
   T* out = reinterpret_cast<T*>(p.out);
   const int N = p.k.N;
+  constexpr bool kBf = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value;
   for (int it = cta; it < items; it += num_ctas) {
     const int mbl = it % p.mb_per_rank, nb = it / p.mb_per_rank;
     if (et < p.world) {
@@ -326,69 +337,88 @@ __device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, 
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
-    named_bar_sync(1, 128);
+    named_bar_sync(1, kEpiThreads);
     const int c_lo = nb * BN;
-    for (int v = et; v < kBlockM * 32; v += 128) {
-      const int r = v >> 5, cv = v & 31;  // row, 8-column vector index inside the 256-column tile
-      const int c = c_lo + cv * 8;
-      if (c >= N) continue;
-      const int half = cv >> 4, chunk = (cv & 15) ^ (r & 7);
-      const size_t in_tile = static_cast<size_t>(half) * 32768 + static_cast<size_t>(r) * 256 + chunk * 16;
-      float acc[8];
+    const uint8_t* tile0 = stage + stage_tile_offset(p, 0, mbl, nb);
+    const size_t src_pitch = stage_tile_offset(p, 1, 0, 0);
+    for (int v0 = et; v0 < kBlockM * 32; v0 += kEpiThreads * U) {
+      uint4 raw[U][WMAX];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-      uint4 raw[kCommMaxRanks];
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * kEpiThreads;
+        const int r = v >> 5, cv = v & 31;  // row, 8-column vector index inside the 256-column tile
+        const int half = cv >> 4, chunk = (cv & 15) ^ (r & 7);
+        const size_t in_tile = static_cast<size_t>(half) * 32768 + static_cast<size_t>(r) * 256 + chunk * 16;
 #pragma unroll
-      for (int sr = 0; sr < kCommMaxRanks; ++sr)
-        if (sr < p.world) raw[sr] = __ldcg(reinterpret_cast<const uint4*>(stage + stage_tile_offset(p, sr, mbl, nb) + in_tile));
+        for (int sr = 0; sr < WMAX; ++sr)
+          if (sr < p.world) raw[u][sr] = __ldcg(reinterpret_cast<const uint4*>(tile0 + sr * src_pitch + in_tile));
+      }
 #pragma unroll
-      for (int sr = 0; sr < kCommMaxRanks; ++sr) {
-        if (sr < p.world) {
-          const uint32_t w[4] = {raw[sr].x, raw[sr].y, raw[sr].z, raw[sr].w};
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * kEpiThreads;
+        const int r = v >> 5, cv = v & 31;
+        const int c = c_lo + cv * 8;
+        if (c >= N) continue;
+        float acc[8];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (p.k.d_dtype == kBFloat16) {
-              acc[2 * j] += __uint_as_float(w[j] << 16);
-              acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
-            } else {
-              const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
-              acc[2 * j] += __low2float(h);
-              acc[2 * j + 1] += __high2float(h);
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int sr = 0; sr < WMAX; ++sr) {
+          if (sr < p.world) {
+            const uint32_t w[4] = {raw[u][sr].x, raw[u][sr].y, raw[u][sr].z, raw[u][sr].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (kBf) {
+                acc[2 * j] += __uint_as_float(w[j] << 16);
+                acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+              } else {
+                const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+                acc[2 * j] += __low2float(h);
+                acc[2 * j + 1] += __high2float(h);
+              }
             }
           }
         }
-      }
-      if (p.k.bias != nullptr) {
+        if (p.k.bias != nullptr) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float b;
-          if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[c + i];
-          else if (p.k.bias_dtype == kBFloat16) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[c + i]);
-          else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[c + i]);
-          acc[i] += b;
+          for (int i = 0; i < 8; ++i) {
+            float b;
+            if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[c + i];
+            else if (p.k.bias_dtype == kBFloat16) b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[c + i]);
+            else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[c + i]);
+            acc[i] += b;
+          }
         }
+        uint4 o;
+        if (kBf) {
+          o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                         pack_bf16x2(acc[6], acc[7]));
+        } else {
+          o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]),
+                         pack_f16x2(acc[6], acc[7]));
+        }
+        *reinterpret_cast<uint4*>(out + static_cast<size_t>(mbl * kBlockM + r) * N + c) = o;
       }
-      uint4 o;
-      if (p.k.d_dtype == kBFloat16) {
-        o = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
-                       pack_bf16x2(acc[6], acc[7]));
-      } else {
-        o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]),
-                       pack_f16x2(acc[6], acc[7]));
-      }
-      *reinterpret_cast<uint4*>(out + static_cast<size_t>(mbl * kBlockM + r) * N + c) = o;
     }
-    named_bar_sync(1, 128);
+    named_bar_sync(1, kEpiThreads);
   }
 }
 
-// Shared-memory plan: the reduce-scatter kernel trades one pipeline stage for a 64 KB output
-// staging area from which whole half tiles leave as single bulk stores to the owner rank.
+template <typename T>
+__device__ __forceinline__ void reduce_tail_any(const CommParams& p, int cta, int num_ctas, int et, uint32_t epoch) {
+  if (p.world <= 2) reduce_tail<T, 4, 2>(p, cta, num_ctas, et, epoch);
+  else if (p.world <= 4) reduce_tail<T, 2, 4>(p, cta, num_ctas, et, epoch);
+  else reduce_tail<T, 1, kCommMaxRanks>(p, cta, num_ctas, et, epoch);
+}
+
+// Shared-memory plan: one pipeline stage is traded for a 64 KB output staging area (two half tiles) from
+// which the epilogue's stores leave: 32 KB bulk stores to the owner rank (reduce-scatter) or TMA stores of
+// 128-byte-swizzled boxes to the local output (all-gather).
 template <int KIND, int MODE>
 struct CommSmem {
   using C = Cfg<KIND, BN>;
-  static constexpr int kStagingBytes = MODE == kCommReduceScatter ? 2 * 32768 : 0;
-  static constexpr int kStages = MODE == kCommReduceScatter ? 3 : C::kStages;
+  static constexpr int kStagingBytes = 2 * 32768;
+  static constexpr int kStages = 3;
   static constexpr int kBytes = kStages * C::kStageBytes + kStagingBytes + 1024 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory plan exceeds the per-CTA limit");
   static_assert(kCopySlots * kCopyPiece <= kStages * C::kStageBytes + kStagingBytes,
@@ -396,20 +426,23 @@ struct CommSmem {
 };
 
 template <int KIND, int MODE>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(kCommThreads, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const CommParams p) {
+                 const __grid_constant__ CUtensorMap tmap_d, const CommParams p) {
   using C = Cfg<KIND, BN>;
   constexpr int NS = CommSmem<KIND, MODE>::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* staging = smem + NS * C::kStageBytes;  // reduce-scatter: two 32 KB half-tile buffers
+  uint8_t* staging = smem + NS * C::kStageBytes;  // two 32 KB half-tile buffers of the epilogue
   uint64_t* bars = reinterpret_cast<uint64_t*>(staging + CommSmem<KIND, MODE>::kStagingBytes);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + NS;
   uint64_t* tfull_bar = bars + 2 * NS;
   uint64_t* tempty_bar = tfull_bar + C::kAccStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + C::kAccStages);
+  uint64_t* staged_bar = tempty_bar + C::kAccStages;  // [2] epilogue group -> store warp: half tile is in shared memory
+  uint64_t* free_bar = staged_bar + 2;                // [2] store warp -> epilogue group: staging buffer may be rewritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(free_bar + 2);
+  unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.k.aux);  // optional [grid, 4] timestamps
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -421,9 +454,12 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (static_cast<int>(blockIdx.x) < p.copy_ctas) {
       const uint32_t ep = read_epoch(p);
       if (warp == 0) {
+        if (dbg && lane == 0) dbg[blockIdx.x * 4 + 0] = gtimer();
         copy_cta_loop(p, blockIdx.x, smem, bars, ep);  // publishes this rank's rows; gated gather (all-gather mode)
         __syncwarp();
+        if (dbg && lane == 0) dbg[blockIdx.x * 4 + 1] = gtimer();
         side_gather_loop(p, blockIdx.x, smem, bars + kCopySlots, ep);
+        if (dbg && lane == 0) dbg[blockIdx.x * 4 + 2] = gtimer();
         if (lane == 0) cta_done(p, ep);
       }
       return;  // copy CTAs never touch TMEM or the pipeline barriers
@@ -441,7 +477,11 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int i = 0; i < C::kAccStages; ++i) {
       mbar_init(&tfull_bar[i], 1);
-      mbar_init(&tempty_bar[i], 4);
+      mbar_init(&tempty_bar[i], kEpiWarps);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&staged_bar[i], 4);
+      mbar_init(&free_bar[i], 1);
     }
     mbar_fence_init();
   }
@@ -557,149 +597,153 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
       }
     }
-  } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;
-    const int et = quarter * 32 + lane;  // 0..127 inside the epilogue group
+  } else if (warp < kStoreWarp) {
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Group g (four warps) owns columns [128 g, 128 g + 128) of every tile.  A thread pulls its 128 accumulator
+    // values with four back-to-back TMEM loads and ONE wait, and the accumulator is released right away (all
+    // eight warps have read it by then): the tensor core waits for a TMEM read, never for a store.  The values
+    // are then packed into the group's 32 KB staging buffer and handed to the store warp through an mbarrier.
+    const int quarter = warp & 3;              // TMEM lanes this warp may read
+    const int g = (warp - 2) >> 2;             // column half
+    const int row = quarter * 32 + lane;       // row inside the tile
+    const int et = (warp - 2) * 32 + lane;     // 0..255 inside the epilogue group
     int acc = 0;
     uint32_t acc_phase = 0;
     const float alpha = p.k.alpha * (p.k.alpha_dev ? *p.k.alpha_dev : 1.0f);
     const bool bf = p.k.d_dtype == kBFloat16;
-    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(p.k.aux);  // optional timeline, 4 stamps per CTA
-    if (dbg && et == 0) dbg[gemm_cta * 4 + 0] = gtimer();
-    uint32_t halves = 0;                       // half tiles sent so far (reduce-scatter)
-    uint32_t* pending[2] = {nullptr, nullptr}; // owner counters to bump once a half tile has landed
+    if (dbg && et == 0) dbg[blockIdx.x * 4 + 0] = gtimer();
+    const int sw = row & 7;
+    uint8_t* buf = staging + g * 32768;
+    uint32_t n_local = 0;  // tiles handled so far
+    bool dead = false;     // a wait ran out: keep walking and arriving (others wait on us), wait no more
     Tile ti;
-    for (int t = gemm_cta; comm_tile(p, t, ti); t += gemm_ctas) {
-      if (!mbar_wait(&tfull_bar[acc], acc_phase)) {
+    for (int t = gemm_cta; comm_tile(p, t, ti); t += gemm_ctas, ++n_local) {
+      if (!dead && !mbar_wait(&tfull_bar[acc], acc_phase)) {
         if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
-        break;
+        dead = true;
       }
       tc_fence_after();
-      const int m0 = ti.mb * kBlockM, n0 = ti.nb * BN;
-      const int row = m0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN;
-      if (MODE == kCommReduceScatter) {
-        const int owner = ti.mb / p.mb_per_rank, mbl = ti.mb % p.mb_per_rank;
-        uint8_t* dst_tile = p.stage[owner] + stage_tile_offset(p, p.rank, mbl, ti.nb);
-        uint32_t* flag = p.tile_flags[owner] + p.rank * p.mb_per_rank + mbl;
-        const int r_in = quarter * 32 + lane;
-#pragma unroll 1
-        for (int half = 0; half < 2; ++half) {
-          uint8_t* buf = staging + (halves & 1) * 32768;
-          if (et == 0 && halves >= 2) {
-            // the bulk store that last used this buffer (two half tiles ago) has completed:
-            // its data is in the owner's memory, so the owner's counter may move
-            tma_store_wait<1>();
-            fence_proxy_async_all();
-            __threadfence_system();
-            red_release_sys_add(pending[halves & 1], 1u);
-          }
-          named_bar_sync(1, 128);
-#pragma unroll 1
-          for (int c0 = 0; c0 < 128; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + half * 128 + c0, r);
-            tmem_ld_wait();
-            if (half == 1 && c0 == 96) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-            }
+      const int n0 = ti.nb * BN;
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + acc * BN + g * 128;
+      uint32_t r[4][32];
 #pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 o;
-              float v[8];
+      for (int j = 0; j < 4; ++j) tmem_ld_32x32(taddr + j * 32, r[j]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      // the store of the previous tile has read this group's staging buffer
+      if (!dead && !mbar_wait(&free_bar[g], (n_local & 1) ^ 1)) {
+        if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
+        dead = true;
+      }
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[i + j]) * alpha;
-              if (bf) {
-                o = make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]),
-                               pack_bf16x2(v[6], v[7]));
-              } else {
-                o = make_uint4(pack_f16x2(v[0], v[1]), pack_f16x2(v[2], v[3]), pack_f16x2(v[4], v[5]),
-                               pack_f16x2(v[6], v[7]));
-              }
-              const int chunk = ((c0 + i) >> 3) ^ (r_in & 7);
-              *reinterpret_cast<uint4*>(buf + r_in * 256 + chunk * 16) = o;
+      for (int j = 0; j < 4; ++j) {
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[j][i]) * alpha;
+        if (MODE == kCommAllGather && p.k.bias != nullptr) {
+          const int col0 = n0 + g * 128 + j * 32;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + i < p.k.N) {
+              float b;
+              if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
+              else if (p.k.bias_dtype == kBFloat16)
+                b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
+              else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
+              v[i] += b;
             }
           }
-          fence_proxy_async_smem();  // generic-proxy writes to shared memory -> bulk (async proxy) read
-          named_bar_sync(1, 128);
-          if (et == 0) {
-            bulk_store_1d(dst_tile + half * 32768, buf, 32768);
-            tma_store_commit();
-            pending[halves & 1] = flag;
-          }
-          ++halves;
         }
-      } else {
-        uint16_t* drow = reinterpret_cast<uint16_t*>(p.k.d) + static_cast<size_t>(row) * p.k.ldd;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c0, r);
-          tmem_ld_wait();
-          if (c0 + 32 >= BN) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[acc]);
-          }
-          const int col0 = n0 + c0;
-          if (row >= p.k.M || col0 >= p.k.N) continue;
-          float v[32];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * alpha;
-          if (p.k.bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (col0 + i < p.k.N) {
-                float b;
-                if (p.k.bias_dtype == kFloat32) b = reinterpret_cast<const float*>(p.k.bias)[col0 + i];
-                else if (p.k.bias_dtype == kBFloat16)
-                  b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.k.bias)[col0 + i]);
-                else b = __half2float(reinterpret_cast<const __half*>(p.k.bias)[col0 + i]);
-                v[i] += b;
-              }
-            }
-          }
-          uint16_t* dp = drow + col0;
-          if (col0 + 32 <= p.k.N) {
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint4 o;
-              if (bf) {
-                o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]),
-                               pack_bf16x2(v[i + 4], v[i + 5]), pack_bf16x2(v[i + 6], v[i + 7]));
-              } else {
-                o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]),
-                               pack_f16x2(v[i + 4], v[i + 5]), pack_f16x2(v[i + 6], v[i + 7]));
-              }
-              *reinterpret_cast<uint4*>(dp + i) = o;
-            }
+        for (int c = 0; c < 4; ++c) {
+          const int i = 8 * c;
+          uint4 o;
+          if (bf) {
+            o = make_uint4(pack_bf16x2(v[i], v[i + 1]), pack_bf16x2(v[i + 2], v[i + 3]), pack_bf16x2(v[i + 4], v[i + 5]),
+                           pack_bf16x2(v[i + 6], v[i + 7]));
           } else {
-            for (int i = 0; col0 + i < p.k.N; ++i) {
-              if (bf) reinterpret_cast<__nv_bfloat16*>(dp)[i] = __float2bfloat16(v[i]);
-              else reinterpret_cast<__half*>(dp)[i] = __float2half(v[i]);
-            }
+            o = make_uint4(pack_f16x2(v[i], v[i + 1]), pack_f16x2(v[i + 2], v[i + 3]), pack_f16x2(v[i + 4], v[i + 5]),
+                           pack_f16x2(v[i + 6], v[i + 7]));
+          }
+          const int chunk = j * 4 + c;  // 16-byte chunk of this thread's 256 bytes (128 columns)
+          if (MODE == kCommReduceScatter) {
+            // owner-side layout: rows of 256 bytes, chunks XOR-swizzled with (row & 7)
+            *reinterpret_cast<uint4*>(buf + row * 256 + ((chunk ^ sw) << 4)) = o;
+          } else {
+            // two TMA boxes of 128 rows x 128 bytes (64 columns each), 128-byte swizzle
+            *reinterpret_cast<uint4*>(buf + (chunk >> 3) * 16384 + row * 128 + (((chunk & 7) ^ sw) << 4)) = o;
           }
         }
       }
+      fence_proxy_async_smem();  // generic-proxy writes to shared memory -> bulk / TMA (async proxy) read
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&staged_bar[g]);
       if (++acc == C::kAccStages) { acc = 0; acc_phase ^= 1; }
     }
-    if (dbg && et == 0) dbg[gemm_cta * 4 + 1] = gtimer();
+    if (dbg && et == 0) dbg[blockIdx.x * 4 + 1] = gtimer();
     if (MODE == kCommReduceScatter) {
-      if (et == 0) {
-        // last one or two half tiles: wait for their stores, then bump the owners' counters
-        tma_store_wait<0>();
-        fence_proxy_async_all();
-        __threadfence_system();
-        if (halves >= 2) red_release_sys_add(pending[halves & 1], 1u);
-        if (halves >= 1) red_release_sys_add(pending[(halves - 1) & 1], 1u);
-        if (dbg) dbg[gemm_cta * 4 + 2] = gtimer();
+      if (p.k.d_dtype == kBFloat16) reduce_tail_any<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et, epoch);
+      else reduce_tail_any<__half>(p, gemm_cta, gemm_ctas, et, epoch);
+      if (dbg && et == 0) dbg[blockIdx.x * 4 + 3] = gtimer();
+    }
+  } else if (lane == 0) {
+    // ------------------------------------------------------------ store warp (one thread)
+    // Hands every staged half tile to the copy engine: a 32 KB bulk store into the owner rank's staging
+    // buffer (reduce-scatter) or two TMA box stores to the local output (all-gather).  A staging buffer is
+    // given back as soon as its store has READ it.  The owner's counter is bumped one tile later, when the
+    // stores it announces have completed, so that neither NVLink latency nor the release fence sits between
+    // two tiles of the epilogue warps.
+    uint32_t n_local = 0;
+    uint32_t* prev_flag = nullptr;
+    bool dead = false;
+    Tile ti;
+    for (int t = gemm_cta; comm_tile(p, t, ti); t += gemm_ctas, ++n_local) {
+      const int m0 = ti.mb * kBlockM, n0 = ti.nb * BN;
+      uint8_t* dst_tile = nullptr;
+      uint32_t* flag = nullptr;
+      if (MODE == kCommReduceScatter) {
+        const int owner = ti.mb / p.mb_per_rank, mbl = ti.mb % p.mb_per_rank;
+        dst_tile = p.stage[owner] + stage_tile_offset(p, p.rank, mbl, ti.nb);
+        flag = p.tile_flags[owner] + p.rank * p.mb_per_rank + mbl;
       }
-      if (p.k.d_dtype == kBFloat16) reduce_tail<__nv_bfloat16>(p, gemm_cta, gemm_ctas, et, epoch);
-      else reduce_tail<__half>(p, gemm_cta, gemm_ctas, et, epoch);
-      if (dbg && et == 0) dbg[gemm_cta * 4 + 3] = gtimer();
+#pragma unroll 1
+      for (int g = 0; g < 2; ++g) {
+        if (!dead && !mbar_wait(&staged_bar[g], n_local & 1)) {
+          if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutEpilogue);
+          dead = true;
+        }
+        const uint8_t* buf = staging + g * 32768;
+        if (MODE == kCommReduceScatter) {
+          bulk_store_1d(dst_tile + g * 32768, buf, 32768);
+        } else {
+#pragma unroll
+          for (int b = 0; b < 2; ++b) {
+            const int col = n0 + g * 128 + b * 64;
+            if (col < p.k.N) tma_store_2d(&tmap_d, buf + b * 16384, col, m0);  // clipped at the matrix edge
+          }
+        }
+        tma_store_commit();
+      }
+      tma_store_wait_read<1>();
+      mbar_arrive(&free_bar[0]);
+      tma_store_wait_read<0>();
+      mbar_arrive(&free_bar[1]);
+      if (MODE == kCommReduceScatter) {
+        if (prev_flag != nullptr) {
+          tma_store_wait<2>();       // everything but this tile's two stores has completed
+          fence_proxy_async_all();   // async-proxy writes (the bulk stores) before the generic-proxy release
+          red_release_sys_add(prev_flag, 2u);
+        }
+        prev_flag = flag;
+      }
+    }
+    tma_store_wait<0>();  // every store has completed (shared memory may go, data is at its place)
+    if (dbg) dbg[blockIdx.x * 4 + 2] = gtimer();
+    if (MODE == kCommReduceScatter && prev_flag != nullptr) {
+      fence_proxy_async_all();
+      red_release_sys_add(prev_flag, 2u);
     }
   }
 
@@ -725,6 +769,10 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
     ok = make_tensor_map_2d(&ta, g.a, kByte, g.M, g.K, g.lda, kBlockM, 128, true) &&
          make_tensor_map_2d(&tb, g.b, kByte, g.N, g.K, g.ldb, BN, 128, true);
   }
+  // all-gather mode stores the output through TMA boxes of 128 rows x 64 16-bit columns
+  CUtensorMap td = ta;
+  if (MODE == kCommAllGather)
+    ok = ok && make_tensor_map_2d(&td, g.d, g.d_dtype, g.M, g.N, g.ldd, 128, 64, true);
   if (!ok) return cudaErrorInvalidValue;
   CommParams p = {};
   KernelParams& k = p.k;
@@ -770,7 +818,7 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   }
   // every CTA must be resident at once (copy CTAs and GEMM CTAs wait on one another; the
   // reduce tail waits on peers): one CTA per SM, never more CTAs than SMs
-  comm_gemm_kernel<KIND, MODE><<<sms, kNumThreads, CommSmem<KIND, MODE>::kBytes, stream>>>(ta, tb, p);
+  comm_gemm_kernel<KIND, MODE><<<sms, kCommThreads, CommSmem<KIND, MODE>::kBytes, stream>>>(ta, tb, td, p);
   return cudaGetLastError();
 }
 

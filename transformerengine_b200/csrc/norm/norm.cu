@@ -161,18 +161,36 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const T* __restrict__ dy, 
   }
 }
 
+// Column sums of the per-part partial dgamma / dbeta.  One block owns 32 columns; its 16 thread rows walk the
+// parts interleaved (128-byte coalesced loads), then combine through shared memory.
+constexpr int FIN_COLS = 32, FIN_ROWS = 16;
+
 template <typename W>
-__global__ void norm_bwd_finalize_kernel(const float* __restrict__ ws, int parts, int C, W* __restrict__ dgamma,
-                                         W* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+__global__ void __launch_bounds__(FIN_COLS * FIN_ROWS)
+norm_bwd_finalize_kernel(const float* __restrict__ ws, int parts, int C, W* __restrict__ dgamma,
+                         W* __restrict__ dbeta) {
+  __shared__ float sg[FIN_ROWS][FIN_COLS + 1], sb[FIN_ROWS][FIN_COLS + 1];
+  const int tx = threadIdx.x % FIN_COLS, ty = threadIdx.x / FIN_COLS;
+  const int c = blockIdx.x * FIN_COLS + tx;
   float g = 0.f, b = 0.f;
-  for (int p = 0; p < parts; ++p) {
-    g += ws[static_cast<size_t>(p) * 2 * C + c];
-    b += ws[static_cast<size_t>(p) * 2 * C + C + c];
+  if (c < C) {
+    for (int p = ty; p < parts; p += FIN_ROWS) {
+      g += ws[static_cast<size_t>(p) * 2 * C + c];
+      if (dbeta != nullptr) b += ws[static_cast<size_t>(p) * 2 * C + C + c];
+    }
   }
-  dgamma[c] = static_cast<W>(g);
-  if (dbeta != nullptr) dbeta[c] = static_cast<W>(b);
+  sg[ty][tx] = g;
+  sb[ty][tx] = b;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+#pragma unroll
+    for (int r = 1; r < FIN_ROWS; ++r) {
+      g += sg[r][tx];
+      b += sb[r][tx];
+    }
+    dgamma[c] = static_cast<W>(g);
+    if (dbeta != nullptr) dbeta[c] = static_cast<W>(b);
+  }
 }
 
 template <typename T, typename W>
@@ -210,7 +228,7 @@ cudaError_t bwd_t(const NormArgs& a, cudaStream_t s) {
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  norm_bwd_finalize_kernel<W><<<(a.C + 255) / 256, 256, 0, s>>>(a.workspace, parts, a.C, static_cast<W*>(a.dgamma),
+  norm_bwd_finalize_kernel<W><<<(a.C + FIN_COLS - 1) / FIN_COLS, FIN_COLS * FIN_ROWS, 0, s>>>(a.workspace, parts, a.C, static_cast<W*>(a.dgamma),
                                                                 a.layernorm ? static_cast<W*>(a.dbeta) : nullptr);
   return cudaGetLastError();
 }

@@ -56,6 +56,30 @@ def _status(dev) -> torch.Tensor:
     return _ext.get().status(dev.index if dev.index is not None else torch.cuda.current_device())
 
 
+# Measured on B200 / NVSwitch: one copy CTA (a ring of 32 KB pieces through shared memory) moves about
+# 35 GB/s; all of them together saturate near 700 GB/s of the 770 GB/s a peer copy reaches.
+_COPY_CTA_BPS, _LINK_BPS, _SMS = 35e9, 700e9, 148
+
+
+def auto_copy_ctas(cta_bytes: float, link_in_bytes: float, flops: float, mxfp8: bool) -> int:
+    """Number of SMs given to copying instead of to the GEMM: the count that minimises the slower of
+    (bytes the copy CTAs move / their rate), (GEMM time on the remaining SMs) and (inbound NVLink time).
+    ``TEB200_COPY_CTAS`` overrides it."""
+    from ..utils.config import get_config
+
+    forced = int(getattr(get_config(), "copy_ctas", 0) or 0)
+    if forced > 0:
+        return forced
+    gemm_rate = 2.4e15 if mxfp8 else 1.3e15
+    floor = link_in_bytes / _LINK_BPS
+    best, best_t = 4, float("inf")
+    for c in range(4, 41, 2):
+        t = max(cta_bytes / min(c * _COPY_CTA_BPS, _LINK_BPS), flops / (gemm_rate * (_SMS - c) / _SMS), floor)
+        if t < best_t * 0.995:
+            best, best_t = c, t
+    return best
+
+
 class SideSpec:
     """Shape of an operand that the copy CTAs of a fused kernel gather next to the GEMM (the
     weight-gradient operand of the layer: what the reference calls bulk overlap,
@@ -134,14 +158,15 @@ class _SideStage:
 class AllGatherGemm:
     """Context of one all-gather -> GEMM site (fixed gathered shape ``[T, K]``)."""
 
-    def __init__(self, group, T: int, K: int, *, mxfp8: bool, dtype=torch.bfloat16, copy_ctas: int = 12,
-                 side: Optional[SideSpec] = None):
+    def __init__(self, group, T: int, K: int, *, mxfp8: bool, dtype=torch.bfloat16,
+                 copy_ctas: Optional[int] = None, side: Optional[SideSpec] = None):
         self.group, self.T, self.K, self.mx = group, T, K, mxfp8
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert T % (128 * self.world) == 0, "gathered rows must be a multiple of 128 * tp"
         self.elem = 1 if mxfp8 else torch.empty(0, dtype=dtype).element_size()
         self.dtype = torch.uint8 if mxfp8 else dtype
-        self.copy_ctas = copy_ctas
+        self.copy_ctas = copy_ctas   # None: chosen per output width from the bytes to move and the FLOPs
+        self._auto: Dict[int, int] = {}
         self.calls = 0
         a_bytes = T * K * self.elem
         sf_bytes = (T // 128) * round_up(K // 32, 4) // 4 * 512 if mxfp8 else 0
@@ -168,7 +193,8 @@ class AllGatherGemm:
         self.epoch_dev = [torch.zeros(2, dtype=torch.int32, device=self.a[0].device) for _ in range(2)]
         self.side = _SideStage(self.buf, side, self.world) if side is not None else None
 
-    def __call__(self, x_local, w, *, bias=None, out_dtype=torch.bfloat16, side=None):
+    def __call__(self, x_local, w, *, bias=None, out_dtype=torch.bfloat16, side=None,
+                 timeline: Optional[torch.Tensor] = None):
         """``x_local``: this rank's rows (plain 16-bit tensor or MXFP8 with a rowwise copy);
         ``w``: the local weight ``[N, K]`` of the same kind.  Returns ``[T, N]``; with ``side=(data, scales)``
         (this rank's piece of the side operand) returns ``(out, gathered_data, gathered_scales)``."""
@@ -188,11 +214,20 @@ class AllGatherGemm:
         N = b_op.rows
         out = torch.empty(self.T, N, dtype=out_dtype, device=self.a[slot].device)
         kw, sd, ssf = ({}, None, None) if side is None else self.side.launch_args(slot, side[0], side[1])
-        _ext.get().comm_gemm(1, self.rank, self.world, self.epoch_dev[slot], self.copy_ctas, self.a[slot], sfa,
+        cc = self.copy_ctas
+        if cc is None:
+            cc = self._auto.get(N)
+            if cc is None:
+                w = self.world
+                gathered = (self.T * self.K * self.elem + self.sf_bytes) * (w - 1) / w
+                side_all = 0 if side is None else (self.side.spec.data_bytes + self.side.spec.sf_bytes) * w
+                cc = self._auto[N] = auto_copy_ctas(gathered + side_all, gathered + side_all * (w - 1) / w,
+                                                    2.0 * self.T * self.K * N, self.mx)
+        _ext.get().comm_gemm(1, self.rank, self.world, self.epoch_dev[slot], cc, self.a[slot], sfa,
                              b_op.data, b_op.scale if self.mx else None, out, bias,
                              a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,
                              self.a_ptrs[slot], self.sf_ptrs[slot] if self.mx else [], self.ready_ptrs[slot],
-                             self.chunk_ptr[slot], [], [], None, N, _status(out.device), **kw)
+                             self.chunk_ptr[slot], [], [], timeline, N, _status(out.device), **kw)
         return out if side is None else (out, sd, ssf)
 
     def gathered(self) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -205,9 +240,10 @@ class GemmReduceScatter:
     """Context of one GEMM -> reduce-scatter site (fixed output shape ``[T, N]`` before scattering)."""
 
     def __init__(self, group, T: int, N: int, *, dtype=torch.bfloat16, side: Optional[SideSpec] = None,
-                 copy_ctas: int = 8):
+                 copy_ctas: Optional[int] = None):
         self.group, self.T, self.N, self.dtype = group, T, N, dtype
-        self.copy_ctas = copy_ctas
+        self.copy_ctas = copy_ctas   # None: chosen per contraction length (only used with a side gather)
+        self._auto: Dict[int, int] = {}
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         assert T % (128 * self.world) == 0 and N % 8 == 0
         stage_bytes = T * round_up(N, 256) * 2  # one 64 KB record per 128 x 256 output tile
@@ -241,7 +277,18 @@ class GemmReduceScatter:
         mx = a_op.kind == "mxfp8"
         out = torch.empty(self.T // self.world, self.N, dtype=self.dtype, device=a_op.data.device)
         kw, sd, ssf = ({}, None, None) if side is None else self.side.launch_args(slot, side[0], side[1])
-        _ext.get().comm_gemm(2, self.rank, self.world, self.epoch_dev[slot], self.copy_ctas if side is not None else 0,
+        cc = 0
+        if side is not None:
+            cc = self.copy_ctas
+            if cc is None:
+                cc = self._auto.get(a_op.k)
+                if cc is None:
+                    w = self.world
+                    side_all = (self.side.spec.data_bytes + self.side.spec.sf_bytes) * w
+                    partial_in = self.T * self.N * 2 * (w - 1) / w      # what the peers push into this rank
+                    cc = self._auto[a_op.k] = auto_copy_ctas(side_all, partial_in + side_all * (w - 1) / w,
+                                                             2.0 * self.T * self.N * a_op.k, mx)
+        _ext.get().comm_gemm(2, self.rank, self.world, self.epoch_dev[slot], cc,
                              a_op.data, a_op.scale if mx else None,
                              b_op.data, b_op.scale if mx else None, timeline, bias,
                              a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,

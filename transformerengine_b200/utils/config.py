@@ -41,6 +41,8 @@ class Config:
         env="NVTE_ALLOW_UNSAFE_PICKLE_EXTRA_STATE", help="load _extra_state with the unrestricted unpickler"))
     wait_limit_cycles: int = field(default=0, metadata=dict(
         env="TEB200_WAIT_LIMIT_CYCLES", help="limit of host-launched flag waits in SM clock cycles (0: about one second)"))
+    copy_ctas: int = field(default=0, metadata=dict(
+        env="TEB200_COPY_CTAS", help="SMs that copy instead of computing in a fused collective GEMM (0: automatic)"))
     # mirrored switches of the native kernels (read there at first launch)
     gemm_cta_pairs: bool = field(default=True, metadata=dict(
         env="TEB200_GEMM_2CTA", help="dense GEMMs on cta_group::2 pairs (0: single-CTA kernels)"))

@@ -44,6 +44,7 @@ struct CommParams {
   uint32_t* tile_flags[kCommMaxRanks];
   void* out;
   SideGather side;
+  int side_tma;  // the side gather's interleaved pieces leave through one 2-D TMA store each (rows <= 1 KB)
 };
 
 struct Tile {
@@ -223,7 +224,8 @@ __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint6
 // rank's staged operand: one bulk load brings it into a shared-memory slot, then every lane stores the
 // rows it owns to their (strided) place in the local gathered operand.  Scale chunks travel the same way
 // as single-row pieces.
-__device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars, uint32_t epoch) {
+__device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars, uint32_t epoch,
+                                 const CUtensorMap* tmap_side) {
   const SideGather& g = p.side;
   if (g.rows <= 0) return;
   const int lane = threadIdx.x;  // caller guarantees threadIdx.x < 32
@@ -293,6 +295,12 @@ __device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, ui
     piece(q, src, dst, nrows, rbytes, pitch, srank);
     if (pitch == rbytes) {
       if (lane == 0) bulk_store_1d(dst, smem + slot * kCopyPiece, static_cast<uint32_t>(nrows) * rbytes);
+    } else if (p.side_tma) {
+      // the piece is a box of the gathered operand seen as [rows, pitch / 4] 32-bit words: one store request
+      // instead of one per row (rows past the operand's end are clipped by the tensor map)
+      if (lane == 0)
+        tma_store_2d(tmap_side, smem + slot * kCopyPiece, static_cast<int>((dst - g.dst) % pitch) >> 2,
+                     static_cast<int>((dst - g.dst) / pitch));
     } else {
       for (int r = lane; r < nrows; r += 32)
         bulk_store_1d(dst + static_cast<long long>(r) * pitch, smem + slot * kCopyPiece + r * rbytes, rbytes);
@@ -428,7 +436,8 @@ struct CommSmem {
 template <int KIND, int MODE>
 __global__ void __launch_bounds__(kCommThreads, 1)
 comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_d, const CommParams p) {
+                 const __grid_constant__ CUtensorMap tmap_d, const __grid_constant__ CUtensorMap tmap_side,
+                 const CommParams p) {
   using C = Cfg<KIND, BN>;
   constexpr int NS = CommSmem<KIND, MODE>::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -458,7 +467,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         copy_cta_loop(p, blockIdx.x, smem, bars, ep);  // publishes this rank's rows; gated gather (all-gather mode)
         __syncwarp();
         if (dbg && lane == 0) dbg[blockIdx.x * 4 + 1] = gtimer();
-        side_gather_loop(p, blockIdx.x, smem, bars + kCopySlots, ep);
+        side_gather_loop(p, blockIdx.x, smem, bars + kCopySlots, ep, &tmap_side);
         if (dbg && lane == 0) dbg[blockIdx.x * 4 + 2] = gtimer();
         if (lane == 0) cta_done(p, ep);
       }
@@ -793,6 +802,7 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   if (copy > sms / 2) copy = sms / 2;
   p.copy_ctas = copy;
   p.side = a.side;
+  CUtensorMap ts = ta;
   if (side) {
     if (a.side.row_bytes <= 0 || a.side.row_bytes % 16 != 0 || a.side.row_bytes > kCopyPiece ||
         a.side.sf_chunk % 16 != 0 || a.side.sf_chunk > kCopyPiece || a.side.dst == nullptr ||
@@ -802,6 +812,12 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
     for (int r = 0; r < a.world; ++r)
       if (a.side.src[r] == nullptr || a.ready[r] == nullptr || reinterpret_cast<uintptr_t>(a.side.src[r]) % 16 != 0)
         return cudaErrorInvalidValue;
+    if (a.side.dst_pitch != a.side.row_bytes && a.side.row_bytes <= 1024 && a.side.dst_pitch % a.side.row_bytes == 0) {
+      const int rpp = kCopyPiece / a.side.row_bytes;  // rows per piece (32..256)
+      p.side_tma = rpp <= 256 &&
+                   make_tensor_map_2d(&ts, a.side.dst, kFloat32, a.side.rows, a.side.dst_pitch / 4, a.side.dst_pitch / 4,
+                                      rpp, a.side.row_bytes / 4, false);
+    }
   }
   for (int r = 0; r < kCommMaxRanks; ++r) {
     p.a_full[r] = a.a_full[r]; p.sfa_full[r] = a.sfa_full[r]; p.ready[r] = a.ready[r];
@@ -818,7 +834,7 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   }
   // every CTA must be resident at once (copy CTAs and GEMM CTAs wait on one another; the
   // reduce tail waits on peers): one CTA per SM, never more CTAs than SMs
-  comm_gemm_kernel<KIND, MODE><<<sms, kCommThreads, CommSmem<KIND, MODE>::kBytes, stream>>>(ta, tb, td, p);
+  comm_gemm_kernel<KIND, MODE><<<sms, kCommThreads, CommSmem<KIND, MODE>::kBytes, stream>>>(ta, tb, td, ts, p);
   return cudaGetLastError();
 }
 

@@ -77,8 +77,8 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, const at::Tensor& epoc
   c.mode = static_cast<int>(mode);
   c.rank = static_cast<int>(rank);
   c.world = static_cast<int>(world);
-  TORCH_CHECK(epoch_dev.scalar_type() == at::kInt && epoch_dev.numel() >= 2 && epoch_dev.is_cuda(),
-              "comm_gemm: the call counter must be two int32 words on the GPU");
+  TORCH_CHECK(epoch_dev.scalar_type() == at::kInt && epoch_dev.numel() >= 3 && epoch_dev.is_cuda(),
+              "comm_gemm: the call counters must be three int32 words on the GPU");
   c.epoch_dev = reinterpret_cast<uint32_t*>(epoch_dev.data_ptr<int>());
   c.copy_ctas = static_cast<int>(copy_ctas);
   for (int r = 0; r < world && r < teb200::kCommMaxRanks; ++r) {

@@ -112,6 +112,7 @@ __device__ __forceinline__ void cta_done(const CommParams& p, uint32_t epoch) {
   __threadfence();
   if (atomicAdd(p.done_ctas, 1u) == gridDim.x - 1) {
     *reinterpret_cast<volatile uint32_t*>(p.done_ctas) = 0u;
+    *reinterpret_cast<volatile uint32_t*>(p.done_ctas + 1) = 0u;  // the side gather's piece counter
     *reinterpret_cast<volatile uint32_t*>(p.epoch_dev) = epoch;
     __threadfence();
   }
@@ -124,6 +125,7 @@ __device__ __forceinline__ void cta_done(const CommParams& p, uint32_t epoch) {
 // the NVLink round trip; plain per-thread loads keep only a few KB in flight.
 constexpr int kCopyPiece = 32 * 1024;
 constexpr int kCopySlots = 6;
+constexpr int kHelperSlots = 4;  // ring of a GEMM CTA that joins the side gather: inside its pipeline stages
 
 __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars, uint32_t epoch) {
   const int tid = threadIdx.x;
@@ -224,13 +226,19 @@ __device__ void copy_cta_loop(const CommParams& p, int cta, uint8_t* smem, uint6
 // rank's staged operand: one bulk load brings it into a shared-memory slot, then every lane stores the
 // rows it owns to their (strided) place in the local gathered operand.  Scale chunks travel the same way
 // as single-row pieces.
-__device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, uint64_t* bars, uint32_t epoch,
+// Pieces are handed out by a device-wide counter, so that the GEMM CTAs can join once their tiles are done
+// (their producer warp, over the freed pipeline stages): the gather then ends a few microseconds after the
+// math instead of leaving 130 SMs idle while a dozen copy CTAs finish.  `bars` holds SLOTS mbarriers followed
+// by SLOTS ints (the item that each slot carries).
+template <int SLOTS>
+__device__ void side_gather_loop(const CommParams& p, uint8_t* smem, uint64_t* bars, uint32_t epoch,
                                  const CUtensorMap* tmap_side) {
   const SideGather& g = p.side;
   if (g.rows <= 0) return;
   const int lane = threadIdx.x;  // caller guarantees threadIdx.x < 32
+  int* slot_item = reinterpret_cast<int*>(bars + SLOTS);
   if (lane == 0) {
-    for (int i = 0; i < kCopySlots; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < SLOTS; ++i) mbar_init(&bars[i], 1);
     mbar_fence_init();
   }
   __syncwarp();
@@ -239,12 +247,11 @@ __device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, ui
   const int sf_pieces = g.sf_chunk > 0 ? g.row_tiles : 0;
   const int per_rank = data_pieces + sf_pieces;
   const int items = p.world * per_rank;
-  const int total = cta < items ? (items - cta + p.copy_ctas - 1) / p.copy_ctas : 0;
   const long long data_bytes = static_cast<long long>(g.rows) * g.row_bytes;
+  uint32_t* next_item = p.done_ctas + 1;  // reset by the CTA that finishes last (cta_done)
 
-  // item q of this CTA -> source pointer, rows, bytes per row, destination of row 0, destination pitch
-  auto piece = [&](int q, const uint8_t*& src, uint8_t*& dst, int& nrows, int& rbytes, long long& pitch, int& srank) {
-    const int it = cta + q * p.copy_ctas;
+  // item -> source pointer, rows, bytes per row, destination of row 0, destination pitch
+  auto piece = [&](int it, const uint8_t*& src, uint8_t*& dst, int& nrows, int& rbytes, long long& pitch, int& srank) {
     srank = (p.rank + 1 + it / per_rank) % p.world;  // own piece last
     const int j = it % per_rank;
     if (j < data_pieces) {
@@ -264,35 +271,46 @@ __device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, ui
     }
   };
   int last_rank_ok = -1;
-  auto issue_load = [&](int q) {  // lane 0 only
+  // lane 0 only: claim the next item and start its load into the slot of piece number `n`; false: none left
+  auto claim_and_load = [&](int n) -> bool {
+    const int it = static_cast<int>(atomicAdd(next_item, 1u));
+    if (it >= items) return false;
     const uint8_t* src; uint8_t* dst; int nrows, rbytes, srank; long long pitch;
-    piece(q, src, dst, nrows, rbytes, pitch, srank);
+    piece(it, src, dst, nrows, rbytes, pitch, srank);
     if (srank != p.rank && srank != last_rank_ok) {
       if (!wait_flag_ge_or_failed(p.ready[p.rank] + srank, epoch, p.k.status)) {
         if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
       last_rank_ok = srank;
     }
-    const int slot = q % kCopySlots;
+    const int slot = n % SLOTS;
+    slot_item[slot] = it;
     const uint32_t bytes = static_cast<uint32_t>(nrows) * rbytes;
     mbar_expect_tx(&bars[slot], bytes);
     bulk_load_1d(smem + slot * kCopyPiece, src, bytes, &bars[slot]);
+    return true;
   };
   int issued = 0;
-  if (lane == 0)
-    for (; issued < total && issued < kCopySlots - 1; ++issued) issue_load(issued);
+  int more = 1;
+  if (lane == 0) {
+    while (issued < SLOTS - 1 && more) {
+      if (claim_and_load(issued)) ++issued;
+      else more = 0;
+    }
+  }
+  __syncwarp();
   issued = __shfl_sync(0xffffffffu, issued, 0);
-  bool ok = true;
-  for (int q = 0; q < total && ok; ++q) {
-    const int slot = q % kCopySlots;
-    const uint32_t phase = (q / kCopySlots) & 1;
+  more = __shfl_sync(0xffffffffu, more, 0);
+  for (int q = 0; q < issued; ++q) {
+    const int slot = q % SLOTS;
+    const uint32_t phase = (q / SLOTS) & 1;
     if (!__all_sync(0xffffffffu, mbar_wait(&bars[slot], phase))) {
       if (lane == 0 && p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
-      ok = false;
       break;
     }
+    const int it = *reinterpret_cast<volatile int*>(&slot_item[slot]);
     const uint8_t* src; uint8_t* dst; int nrows, rbytes, srank; long long pitch;
-    piece(q, src, dst, nrows, rbytes, pitch, srank);
+    piece(it, src, dst, nrows, rbytes, pitch, srank);
     if (pitch == rbytes) {
       if (lane == 0) bulk_store_1d(dst, smem + slot * kCopyPiece, static_cast<uint32_t>(nrows) * rbytes);
     } else if (p.side_tma) {
@@ -306,12 +324,15 @@ __device__ void side_gather_loop(const CommParams& p, int cta, uint8_t* smem, ui
         bulk_store_1d(dst + static_cast<long long>(r) * pitch, smem + slot * kCopyPiece + r * rbytes, rbytes);
     }
     tma_store_commit();
-    if (issued < total) {
+    if (more) {
       // the slot of piece `issued` was last read by the stores of piece q - 1: every lane waits for its own
       tma_store_wait_read<1>();
       __syncwarp();
-      if (lane == 0) issue_load(issued);
-      ++issued;
+      int got = 0;
+      if (lane == 0) got = claim_and_load(issued) ? 1 : 0;
+      got = __shfl_sync(0xffffffffu, got, 0);
+      if (got) ++issued;
+      else more = 0;
     }
   }
   tma_store_wait<0>();
@@ -429,6 +450,7 @@ struct CommSmem {
   static constexpr int kStages = 3;
   static constexpr int kBytes = kStages * C::kStageBytes + kStagingBytes + 1024 + 1024;
   static_assert(kBytes <= 227 * 1024, "shared memory plan exceeds the per-CTA limit");
+  static_assert(kHelperSlots * kCopyPiece <= kStages * C::kStageBytes, "helper ring must fit in the pipeline stages");
   static_assert(kCopySlots * kCopyPiece <= kStages * C::kStageBytes + kStagingBytes,
                 "copy ring must fit in front of the barriers");
 };
@@ -467,7 +489,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         copy_cta_loop(p, blockIdx.x, smem, bars, ep);  // publishes this rank's rows; gated gather (all-gather mode)
         __syncwarp();
         if (dbg && lane == 0) dbg[blockIdx.x * 4 + 1] = gtimer();
-        side_gather_loop(p, blockIdx.x, smem, bars + kCopySlots, ep, &tmap_side);
+        side_gather_loop<kCopySlots>(p, smem, bars + kCopySlots, ep, &tmap_side);
         if (dbg && lane == 0) dbg[blockIdx.x * 4 + 2] = gtimer();
         if (lane == 0) cta_done(p, ep);
       }
@@ -507,6 +529,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
+    bool helper_ok = false;
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -550,6 +573,22 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (++stage == NS) { stage = 0; phase ^= 1; }
         }
       }
+      if (p.side.rows > 0) {
+        // every stage has been consumed by the tensor core: the pipeline's shared memory is free
+        for (int i = 0; ok && i < NS; ++i) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1)) {
+            if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutProducer);
+            ok = false;
+          }
+          if (++stage == NS) { stage = 0; phase ^= 1; }
+        }
+        helper_ok = ok;
+      }
+    }
+    if (p.side.rows > 0) {
+      // join the side gather with the pieces that the copy CTAs have not claimed yet
+      helper_ok = __shfl_sync(0xffffffffu, helper_ok ? 1 : 0, 0) != 0;
+      if (helper_ok) side_gather_loop<kHelperSlots>(p, smem, bars + 32, epoch, &tmap_side);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer

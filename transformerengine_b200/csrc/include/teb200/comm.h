@@ -40,9 +40,9 @@ struct CommGemmArgs {
   GemmArgs g;  // M = gathered rows; for all-gather g.a / g.sfa point at the LOCAL gathered buffer
   int mode = kCommNone;
   int rank = 0, world = 1;
-  // two local device words: [0] calls completed so far on this (context, buffer slot), identical on all
+  // three local device words: [0] calls completed so far on this (context, buffer slot), identical on all
   // ranks, advanced by the kernel itself (so launches recorded in a CUDA graph replay correctly);
-  // [1] scratch counter of finished CTAs, zero between launches
+  // [1] scratch counter of finished CTAs, [2] next unclaimed piece of the side gather; both zero between launches
   uint32_t* epoch_dev = nullptr;
   int copy_ctas = 8;
 

@@ -57,24 +57,35 @@ def _status(dev) -> torch.Tensor:
 
 
 # Measured on B200 / NVSwitch: one copy CTA (a ring of 32 KB pieces through shared memory) moves about
-# 35 GB/s; all of them together saturate near 700 GB/s of the 770 GB/s a peer copy reaches.
-_COPY_CTA_BPS, _LINK_BPS, _SMS = 35e9, 700e9, 148
+# 32 GB/s; all of them together saturate near 700 GB/s of the 770 GB/s a peer copy reaches.
+_COPY_CTA_BPS, _LINK_BPS, _SMS = 32e9, 700e9, 148
 
 
-def auto_copy_ctas(cta_bytes: float, link_in_bytes: float, flops: float, mxfp8: bool) -> int:
-    """Number of SMs given to copying instead of to the GEMM: the count that minimises the slower of
-    (bytes the copy CTAs move / their rate), (GEMM time on the remaining SMs) and (inbound NVLink time).
-    ``TEB200_COPY_CTAS`` overrides it."""
+def auto_copy_ctas(gated_bytes: float, side_bytes: float, other_link_bytes: float, flops: float, mxfp8: bool,
+                   world: int) -> int:
+    """Number of SMs given to copying instead of to the GEMM, from a small time model of the fused kernel.
+
+    ``gated_bytes``: the gathered GEMM operand (peer rows; the GEMM visits the shards in order, so shard i
+    must have landed after i / world of the GEMM).  ``side_bytes``: the side gather, which the copy CTAs
+    take up once the gated gather is through and which the GEMM CTAs help to finish after their last tile.
+    ``other_link_bytes``: inbound NVLink traffic of the GEMM itself (reduce-scatter partials).
+    ``TEB200_COPY_CTAS`` overrides the choice."""
     from ..utils.config import get_config
 
     forced = int(getattr(get_config(), "copy_ctas", 0) or 0)
     if forced > 0:
         return forced
     gemm_rate = 2.4e15 if mxfp8 else 1.3e15
-    floor = link_in_bytes / _LINK_BPS
+    everyone = min(_SMS * _COPY_CTA_BPS, _LINK_BPS)
+    floor = (gated_bytes + other_link_bytes + side_bytes * (world - 1) / world) / _LINK_BPS
     best, best_t = 4, float("inf")
     for c in range(4, 41, 2):
-        t = max(cta_bytes / min(c * _COPY_CTA_BPS, _LINK_BPS), flops / (gemm_rate * (_SMS - c) / _SMS), floor)
+        rate = min(c * _COPY_CTA_BPS, _LINK_BPS)
+        t_gemm = max(flops / (gemm_rate * (_SMS - c) / _SMS), (gated_bytes + other_link_bytes) / _LINK_BPS)
+        if gated_bytes:
+            t_gemm = max(t_gemm, gated_bytes * world / ((world - 1) * rate))
+        carried = max(0.0, t_gemm - gated_bytes / rate) * rate
+        t = max(t_gemm + max(0.0, side_bytes - carried) / everyone, floor)
         if t < best_t * 0.995:
             best, best_t = c, t
     return best
@@ -190,7 +201,7 @@ class AllGatherGemm:
             self.ready_ptrs.append(p)
             _, p = self.buf.carve(4 * (T // 128))
             self.chunk_ptr.append(p[self.rank])
-        self.epoch_dev = [torch.zeros(2, dtype=torch.int32, device=self.a[0].device) for _ in range(2)]
+        self.epoch_dev = [torch.zeros(4, dtype=torch.int32, device=self.a[0].device) for _ in range(2)]
         self.side = _SideStage(self.buf, side, self.world) if side is not None else None
 
     def __call__(self, x_local, w, *, bias=None, out_dtype=torch.bfloat16, side=None,
@@ -221,8 +232,7 @@ class AllGatherGemm:
                 w = self.world
                 gathered = (self.T * self.K * self.elem + self.sf_bytes) * (w - 1) / w
                 side_all = 0 if side is None else (self.side.spec.data_bytes + self.side.spec.sf_bytes) * w
-                cc = self._auto[N] = auto_copy_ctas(gathered + side_all, gathered + side_all * (w - 1) / w,
-                                                    2.0 * self.T * self.K * N, self.mx)
+                cc = self._auto[N] = auto_copy_ctas(gathered, side_all, 0.0, 2.0 * self.T * self.K * N, self.mx, w)
         _ext.get().comm_gemm(1, self.rank, self.world, self.epoch_dev[slot], cc, self.a[slot], sfa,
                              b_op.data, b_op.scale if self.mx else None, out, bias,
                              a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,
@@ -260,7 +270,7 @@ class GemmReduceScatter:
             _, p = self.buf.carve(4 * self.world * mbl)
             self.flag_ptrs.append(p)
         self.calls = 0
-        self.epoch_dev = [torch.zeros(2, dtype=torch.int32, device=self.buf.tensor.device) for _ in range(2)]
+        self.epoch_dev = [torch.zeros(4, dtype=torch.int32, device=self.buf.tensor.device) for _ in range(2)]
         self.side, self.ready_ptrs = None, [[], []]
         if side is not None:
             self.side = _SideStage(self.buf, side, self.world)
@@ -286,8 +296,8 @@ class GemmReduceScatter:
                     w = self.world
                     side_all = (self.side.spec.data_bytes + self.side.spec.sf_bytes) * w
                     partial_in = self.T * self.N * 2 * (w - 1) / w      # what the peers push into this rank
-                    cc = self._auto[a_op.k] = auto_copy_ctas(side_all, partial_in + side_all * (w - 1) / w,
-                                                             2.0 * self.T * self.N * a_op.k, mx)
+                    cc = self._auto[a_op.k] = auto_copy_ctas(0.0, side_all, partial_in,
+                                                             2.0 * self.T * self.N * a_op.k, mx, w)
         _ext.get().comm_gemm(2, self.rank, self.world, self.epoch_dev[slot], cc,
                              a_op.data, a_op.scale if mx else None,
                              b_op.data, b_op.scale if mx else None, timeline, bias,

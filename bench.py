@@ -47,7 +47,8 @@ def parse():
     ap.add_argument("--profile", default="", help="write a per-kernel device-time table of 2 extra steps (rank 0) here")
     ap.add_argument("--fused-comm", type=int, default=1, help="fuse TP collectives into the GEMM kernels")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
-    ap.add_argument("--zero", type=int, default=0, help="data parallel: shard the optimizer over the ranks")
+    ap.add_argument("--zero", type=int, default=-1,
+                    help="data parallel: shard the optimizer over the ranks (-1: on whenever there is data parallelism)")
     return ap.parse_args()
 
 
@@ -200,7 +201,7 @@ def build_case(args, rank, world):
         graph = want_graph(tp, recipe_name)
         overlap = os.environ.get("TEB200_DP_OVERLAP", "1") == "1"
         zero = None
-        if dp > 1 and args.zero:
+        if dp > 1 and args.zero != 0:
             from transformerengine_b200.parallel.data_parallel import ShardedOptimizerDataParallel
 
             zero = ShardedOptimizerDataParallel(model.parameters(), None, overlap=overlap)

@@ -869,6 +869,12 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
     cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<KIND, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          CommSmem<KIND, MODE>::kBytes);
     if (e != cudaSuccess) return e;
+    // the protocol needs every CTA of the grid resident at once: refuse a configuration that cannot be
+    int per_sm = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, comm_gemm_kernel<KIND, MODE>, kCommThreads,
+                                                      CommSmem<KIND, MODE>::kBytes);
+    if (e != cudaSuccess) return e;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
     attr_set = true;
   }
   // every CTA must be resident at once (copy CTAs and GEMM CTAs wait on one another; the

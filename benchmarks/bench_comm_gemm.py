@@ -9,6 +9,10 @@ of MEASURED_PEAKS.json (1640 TFLOP/s fallback), MXFP8 = 3100 TFLOP/s (cuBLASLt b
 ``torch._scaled_mm``, ``benchmarks/bench_gemm.py``); override with --peak-bf16 / --peak-mxfp8.
 Also reports the fused kernel against the NCCL collective followed by this library's dense GEMM, and
 (``--side 1``) the fused kernel carrying the side gather of the weight-gradient operand (bulk overlap).
+``--timeline 1`` adds the kernels' own time stamps (``%globaltimer`` written by every CTA of one extra launch on
+rank 0, microseconds after the first CTA started, as min / mean / max over the CTAs of a role): when the copy
+CTAs finished the gated gather and the side gather, when the GEMM CTAs finished their tiles, when their last
+store had completed, and when the reduce tail ended.
 """
 import argparse
 import json
@@ -43,8 +47,30 @@ def timed(fn, iters=10):
     return float(t.item())
 
 
+def stamps(fn, n_copy):
+    """One launch of ``fn(timeline=...)``; returns {phase: [min, mean, max] us} per role (rank-local)."""
+    tl = torch.zeros(148, 4, dtype=torch.int64, device="cuda")
+    dist.barrier()
+    torch.cuda.synchronize()
+    fn(tl)
+    torch.cuda.synchronize()
+    t = tl.cpu().double()
+    t0 = t[:, 0][t[:, 0] > 0].min()
+
+    def mmm(rows, col):
+        if rows.numel() == 0 or (rows[:, col] <= 0).all():
+            return None
+        x = (rows[:, col][rows[:, col] > 0] - t0) / 1e3
+        return [round(float(x.min()), 1), round(float(x.mean()), 1), round(float(x.max()), 1)]
+
+    cp, gm = t[:n_copy], t[n_copy:]
+    return {"copy_ctas": n_copy, "copy_gated_done": mmm(cp, 1), "copy_side_done": mmm(cp, 2),
+            "gemm_tiles_done": mmm(gm, 1), "gemm_stores_done": mmm(gm, 2), "reduce_tail_done": mmm(gm, 3)}
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--timeline", type=int, default=0, help="add in-kernel time stamps of one launch per kernel")
     ap.add_argument("--shapes", default="llama")
     ap.add_argument("--copy-ctas", type=int, default=0, help="0 = chosen by the library per shape")
     ap.add_argument("--peak-bf16", type=float, default=0.0, help="TFLOP/s; 0 = MEASURED_PEAKS.json or 1640")
@@ -119,7 +145,15 @@ def main():
                              rs_side_roofline_ms=max(flops / peak * 1e3, max(rs_bytes, side_bytes) / LINK_GBS / 1e6))
                 extra["ag_side_frac_of_roofline"] = extra["ag_side_roofline_ms"] / t_ag_side
                 extra["rs_side_frac_of_roofline"] = extra["rs_side_roofline_ms"] / t_rs_side
+                if a.timeline:
+                    extra["ag_side_stamps_us"] = stamps(lambda tl: ag_s(xs, w1_o, side=side, timeline=tl),
+                                                        a.copy_ctas or ag_s._auto[Fl])
+                    extra["rs_side_stamps_us"] = stamps(lambda tl: rs_s(x2_o, w2_o, side=side, timeline=tl),
+                                                        a.copy_ctas or rs_s._auto[Fl])
                 del ag_s, rs_s
+            if a.timeline:
+                extra["ag_stamps_us"] = stamps(lambda tl: ag(xl_o, w1_o, timeline=tl), a.copy_ctas or ag._auto[Fl])
+                extra["rs_stamps_us"] = stamps(lambda tl: rs(x2_o, w2_o, timeline=tl), 0)
             if rank == 0:
                 print(json.dumps(dict(T=T, H=H, F_local=Fl, mxfp8=mx, world=world, peak_tflops=peak / 1e12,
                                       ag_fused_ms=t_ag_fused, ag_gemm_ms=t_ag_gemm, ag_nccl_ms=t_ag_nccl,

@@ -110,3 +110,42 @@ def test_context_parallel_refuses_what_it_does_not_implement(monkeypatch):
     with pytest.raises(NotImplementedError, match="sliding window"):
         dpa(q.reshape(4, 2, 8), q.reshape(4, 2, 8), q.reshape(4, 2, 8), qkv_format="thd", cu_seqlens_q=cu,
             attn_mask_type="padding_causal", window_size=(2, 0))
+
+
+@pytest.mark.parametrize("layout", ["grouped", "blocked"])
+@pytest.mark.parametrize("fmt", ["sbhd", "bshd"])
+def test_rotate_packed_qkv_in_place_matches_separate_rotations(layout, fmt):
+    from transformerengine_b200.attention.rope import (RotaryPositionEmbedding, apply_rotary_pos_emb,
+                                                       rotate_packed_qkv_)
+
+    torch.manual_seed(0)
+    s, b, hq, hk, d = 6, 2, 4, 2, 16
+    g = hq // hk
+    freqs = RotaryPositionEmbedding(d)(s)
+    base = torch.randn((s, b, (hq + 2 * hk) * d) if fmt == "sbhd" else (b, s, (hq + 2 * hk) * d), dtype=torch.float64)
+    lead = base.shape[:2]
+
+    def split(m):
+        if layout == "grouped":
+            m5 = m.reshape(*lead, hk, g + 2, d)
+            q, k, v = torch.split(m5, (g, 1, 1), dim=-2)
+            return q.reshape(*lead, hq, d), k.reshape(*lead, hk, d), v.reshape(*lead, hk, d)
+        q, k, v = torch.split(m, (hq * d, hk * d, hk * d), dim=-1)
+        return q.reshape(*lead, hq, d), k.reshape(*lead, hk, d), v.reshape(*lead, hk, d)
+
+    w = torch.randn_like(base)
+    a = base.clone().requires_grad_(True)
+    q, k, v = split(a * 1.0)
+    ref = torch.cat([apply_rotary_pos_emb(q, freqs, fmt).flatten(2), apply_rotary_pos_emb(k, freqs, fmt).flatten(2),
+                     v.flatten(2)], dim=-1)
+    bt = base.clone().requires_grad_(True)
+    mixed = bt * 1.0                                 # a non-leaf the rotation may overwrite
+    out = rotate_packed_qkv_(mixed, freqs, freqs, fmt, layout, hq, hk, d)
+    assert out.data_ptr() == mixed.data_ptr()        # in place
+    q2, k2, v2 = split(out)
+    got = torch.cat([q2.flatten(2), k2.flatten(2), v2.flatten(2)], dim=-1)
+    torch.testing.assert_close(got, ref)
+    wq = torch.randn_like(ref)
+    (ref * wq).sum().backward()
+    (got * wq).sum().backward()
+    torch.testing.assert_close(bt.grad, a.grad)

@@ -441,3 +441,23 @@ def test_sharded_master_weights_cast_with_partial_amax():
     for rank, errs, tb in res:
         assert tb is None, tb
         assert errs == {"mxfp8": True, "fp8cs": True}, (rank, errs)
+
+
+def test_helper_ops_cpu_paths():
+    """column sums, splits -> offsets, slab re-padding and last-dim padding (the oracle paths of the kernels)."""
+    import torch
+    from transformerengine_b200 import ops
+
+    x = torch.randn(37, 24)
+    torch.testing.assert_close(ops.column_sum(x), x.sum(0))
+    s = torch.tensor([3, 0, 5, 2], dtype=torch.int64)
+    assert ops.splits_to_offsets(s, multiplier=4).tolist() == [0, 12, 12, 32, 40]
+    rows = torch.arange(10 * 8, dtype=torch.float32).reshape(10, 8)
+    padded = ops.repad_rows(rows, [3, 0, 5, 2], [4, 0, 8, 4])
+    assert padded.shape == (16, 8)
+    assert torch.equal(padded[:3], rows[:3]) and padded[3].abs().sum() == 0
+    assert torch.equal(padded[4:9], rows[3:8]) and padded[9:12].abs().sum() == 0
+    assert torch.equal(ops.repad_rows(padded, [4, 0, 8, 4], [3, 0, 5, 2]), rows)
+    p = ops.pad_last_dim(rows, 12)
+    assert p.shape == (10, 12) and torch.equal(p[:, :8], rows) and p[:, 8:].abs().sum() == 0
+    assert torch.equal(ops.pad_last_dim(p, 8), rows)

@@ -347,3 +347,75 @@ def test_fp8_block_scaled_gemm_runs_on_the_block_scaled_tensor_core_path():
         Q.dequantize_fp8_blockwise(qa._columnwise_data.view(torch.float8_e4m3fn), qa._columnwise_scale_inv, (1, 128),
                                    torch.float32).t()
     assert _rel(dw, refw) < 1e-5
+
+
+@pytest.mark.gpu
+def test_helper_kernels_match_torch():
+    """column_sum, splits_to_offsets, repad_rows, pad_last_dim against plain torch."""
+    import torch
+    from transformerengine_b200 import ops
+
+    torch.manual_seed(0)
+    for R, C, dt in ((8192, 4096, torch.bfloat16), (1000, 264, torch.float16), (65, 4104, torch.float32)):
+        x = torch.randn(R, C, device="cuda", dtype=dt)
+        got = ops.column_sum(x, torch.float32)
+        torch.testing.assert_close(got, x.float().sum(0), rtol=1e-4, atol=1e-2)
+        assert torch.equal(got, ops.column_sum(x, torch.float32))          # deterministic
+    xs = torch.randn(512, 1024, device="cuda", dtype=torch.bfloat16)[:, 128:640]   # row stride != width
+    torch.testing.assert_close(ops.column_sum(xs, torch.bfloat16).float(), xs.float().sum(0), rtol=2e-2, atol=0.3)
+    for n in (1, 8, 300, 2500):
+        s = torch.randint(0, 1000, (n,), device="cuda", dtype=torch.int64)
+        ref = torch.cat([torch.zeros(1, dtype=torch.int64, device="cuda"), torch.cumsum(s, 0)]) * 3
+        assert torch.equal(ops.splits_to_offsets(s, 3, torch.int64), ref)
+        assert torch.equal(ops.splits_to_offsets(s.int(), 3, torch.int32), ref.int())
+    m = [37, 0, 128, 5, 1000]
+    p = [(v + 127) // 128 * 128 for v in m]
+    rows = torch.randn(sum(m), 512, device="cuda", dtype=torch.bfloat16)
+    padded = ops.repad_rows(rows, m, p)
+    ref = torch.cat([torch.nn.functional.pad(c, (0, 0, 0, pp - mm)) for c, mm, pp in zip(torch.split(rows, m), m, p)])
+    assert torch.equal(padded, ref)
+    assert torch.equal(ops.repad_rows(padded, p, m), rows)
+    mt, pt = torch.tensor(m, device="cuda", dtype=torch.int32), torch.tensor(p, device="cuda", dtype=torch.int32)
+    assert torch.equal(ops.repad_rows(rows, mt, pt), ref)                   # splits given on the device
+    h = torch.randn(4, 16, 8, 72, device="cuda", dtype=torch.bfloat16)
+    hp = ops.pad_last_dim(h, 128)
+    assert hp.shape == (4, 16, 8, 128) and torch.equal(hp[..., :72], h) and hp[..., 72:].abs().sum() == 0
+    assert torch.equal(ops.pad_last_dim(hp, 72), h)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["grouped", "blocked"])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope_packed_qkv_one_launch(layout, interleaved):
+    """Query and key heads of a packed QKV tensor rotated by ONE kernel (in place and out of place, forward and
+    backward, separate key angles) against the plain rotation of the split views."""
+    import torch
+    from transformerengine_b200 import ops
+
+    torch.manual_seed(1)
+    s, b, hq, hk, d = 96, 2, 8, 2, 128
+    g = hq // hk
+    x = torch.randn(s, b, hq + 2 * hk, d, device="cuda", dtype=torch.bfloat16)
+    fq = ops.rope_freqs(torch.arange(s, device="cuda"), d, 10000.0, interleaved)
+    fk = ops.rope_freqs(torch.arange(s, device="cuda"), d, 500000.0, interleaved)
+
+    def split(t):
+        if layout == "grouped":
+            t5 = t.unflatten(2, (hk, g + 2))
+            return t5[:, :, :, :g].reshape(s, b, hq, d), t5[:, :, :, g], t5[:, :, :, g + 1]
+        return t[:, :, :hq], t[:, :, hq:hq + hk], t[:, :, hq + hk:]
+
+    for backward in (False, True):
+        y = ops.rope_qkv(x, fq, fk, layout=layout, hq=hq, hk=hk, interleaved=interleaved, backward=backward)
+        q, k, v = split(x)
+        yq, yk, yv = split(y)
+        assert torch.equal(yq, ops.rope_apply(q.contiguous(), fq, interleaved=interleaved, backward=backward))
+        assert torch.equal(yk, ops.rope_apply(k.contiguous(), fk, interleaved=interleaved, backward=backward))
+        assert torch.equal(yv, v)
+    z = x.clone()
+    ops.rope_qkv(z, fq, fk, layout=layout, hq=hq, hk=hk, interleaved=interleaved, inplace=True)
+    assert torch.equal(z, ops.rope_qkv(x, fq, fk, layout=layout, hq=hq, hk=hk, interleaved=interleaved))
+    # the strided [s, b, h, d] view of a batch-first tensor
+    xb = x.transpose(0, 1).contiguous()
+    yb = ops.rope_qkv(xb.transpose(0, 1), fq, fq, layout=layout, hq=hq, hk=hk, interleaved=interleaved)
+    assert torch.equal(yb, ops.rope_qkv(x, fq, fq, layout=layout, hq=hq, hk=hk, interleaved=interleaved))

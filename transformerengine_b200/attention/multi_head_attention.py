@@ -17,7 +17,7 @@ from ..modules.layernorm_linear import LayerNorm, LayerNormLinear, RMSNorm
 from ..modules.linear import Linear
 from ..parallel import distributed as D
 from .dot_product_attention import DotProductAttention
-from .rope import apply_rotary_pos_emb
+from .rope import apply_rotary_pos_emb, rotate_packed_qkv_
 
 
 class MultiheadAttention(torch.nn.Module):
@@ -153,6 +153,18 @@ class MultiheadAttention(torch.nn.Module):
             else:
                 mixed = self.qkv(hidden_states, is_first_microbatch=is_first_microbatch)
             lead = mixed.shape[:-1]
+            rope_done = False
+            if (rotary_pos_emb is not None and inference_params is None and self.qkv_format in ("sbhd", "bshd")
+                    and not (self.qk_norm_type is not None and self.qk_norm_before_rope)
+                    and mixed.dim() == 3 and mixed.is_contiguous()):
+                # split + both rotations in one launch, in place on the projection output
+                q_emb, k_emb = rotary_pos_emb if isinstance(rotary_pos_emb, (tuple, list)) else (rotary_pos_emb,) * 2
+                cpg = self.core_attention.cp_group
+                cp_size = D.get_world_size(cpg) if cpg is not None else 1
+                mixed = rotate_packed_qkv_(mixed, q_emb, k_emb, self.qkv_format,
+                                           "grouped" if self.qkv_weight_interleaved else "blocked", hq, hk, d,
+                                           cp_size=cp_size, cp_rank=D.get_rank(cpg) if cp_size > 1 else 0)
+                rope_done = True
             if self.qkv_weight_interleaved:
                 g = hq // hk
                 mixed = mixed.reshape(*lead, hk, g + 2, d)
@@ -180,7 +192,7 @@ class MultiheadAttention(torch.nn.Module):
             q = ql.reshape(*ql.shape[:-1], hq, d)
         if self.qk_norm_type is not None and self.qk_norm_before_rope:
             q, k = self._qk_norm(q, self.q_norm), self._qk_norm(k, self.k_norm)
-        if rotary_pos_emb is not None:
+        if rotary_pos_emb is not None and not (self.attention_type == "self" and rope_done):
             q_emb, k_emb = rotary_pos_emb if isinstance(rotary_pos_emb, (tuple, list)) else (rotary_pos_emb,) * 2
             fmt = self.qkv_format
             if fmt in ("sbhd", "bshd") and inference_params is None:

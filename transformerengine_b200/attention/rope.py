@@ -75,6 +75,53 @@ def apply_rotary_pos_emb(t: torch.Tensor, freqs: torch.Tensor, tensor_format: st
     return _RopeFn.apply(t, freqs, tensor_format, interleaved, cp_size, cp_rank, start_positions)
 
 
+class _RopeQkvFn(torch.autograd.Function):
+    """Rotation of the query and key heads of a packed QKV projection, in place, one launch."""
+
+    @staticmethod
+    def forward(ctx, mixed, q_freqs, k_freqs, fmt, layout, hq, hk, d, interleaved, cp_size, cp_rank, start_positions,
+                inplace):  # type: ignore[override]
+        lead = mixed.shape[:2]
+        x4 = mixed.view(*lead, hq + 2 * hk, d)
+        x = x4 if fmt == "sbhd" else x4.transpose(0, 1)
+        fq = q_freqs.reshape(q_freqs.shape[0], q_freqs.shape[-1])
+        fk = fq if k_freqs is q_freqs else k_freqs.reshape(k_freqs.shape[0], k_freqs.shape[-1])
+        y = ops.rope_qkv(x, fq, fk, layout=layout, hq=hq, hk=hk, interleaved=interleaved, cp_size=cp_size,
+                         cp_rank=cp_rank, start_positions=start_positions, inplace=inplace)
+        ctx.save_for_backward(fq, fk, start_positions if start_positions is not None else torch.empty(0))
+        ctx.cfg = (fmt, layout, hq, hk, d, interleaved, cp_size, cp_rank, start_positions is not None)
+        if inplace:
+            ctx.mark_dirty(mixed)
+            return mixed
+        y = y if fmt == "sbhd" else y.transpose(0, 1)
+        return y.reshape(mixed.shape)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        fq, fk, sp = ctx.saved_tensors
+        fmt, layout, hq, hk, d, interleaved, cp_size, cp_rank, has_sp = ctx.cfg
+        g = g.contiguous()
+        g4 = g.view(*g.shape[:2], hq + 2 * hk, d)
+        x = g4 if fmt == "sbhd" else g4.transpose(0, 1)
+        # out of place: the incoming gradient may be shared with other consumers
+        y = ops.rope_qkv(x, fq, fq if fk is fq else fk, layout=layout, hq=hq, hk=hk, interleaved=interleaved, backward=True,
+                         cp_size=cp_size, cp_rank=cp_rank, start_positions=sp if has_sp else None)
+        y = y if fmt == "sbhd" else y.transpose(0, 1)
+        return (y.reshape(g.shape),) + (None,) * 12
+
+
+def rotate_packed_qkv_(mixed: torch.Tensor, q_freqs: torch.Tensor, k_freqs: torch.Tensor, tensor_format: str, layout: str,
+                       hq: int, hk: int, head_dim: int, *, interleaved: bool = False, cp_size: int = 1, cp_rank: int = 0,
+                       start_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Rotate the query and key heads of ``mixed`` (``[s, b, (hq + 2 hk) * d]`` or ``[b, s, ...]``, the output of a
+    fused QKV projection) in place and return it; value heads are untouched.  ``layout``: ``"grouped"`` (per
+    key/value group: its query heads, the key head, the value head) or ``"blocked"`` (all queries, all keys, all
+    values)."""
+    assert mixed.dim() == 3 and mixed.is_contiguous() and mixed.shape[-1] == (hq + 2 * hk) * head_dim
+    return _RopeQkvFn.apply(mixed, q_freqs, k_freqs, tensor_format, layout, hq, hk, head_dim, interleaved, cp_size,
+                            cp_rank, start_positions, True)
+
+
 def apply_fused_qkv_rotary_pos_emb(qkv: torch.Tensor, q_freqs: torch.Tensor, k_freqs: torch.Tensor,
                                    qkv_split_arg_list, tensor_format: str = "sbhd",
                                    start_positions: Optional[torch.Tensor] = None, interleaved: bool = False,
@@ -84,12 +131,22 @@ def apply_fused_qkv_rotary_pos_emb(qkv: torch.Tensor, q_freqs: torch.Tensor, k_f
     ``qkv`` is ``[s, b, g, q + k + v]`` (or ``[b, s, ...]``) with, per key/value group ``g``, ``q`` query
     channels (``q / d`` heads), ``k`` key channels and ``v = d`` value channels
     (``qkv_split_arg_list = [q, k, v]``).  Returns ``(q [.., g * q/d, d], k [.., g * k/d, d], v [.., g, d])``
-    with the rotation applied to Q and K; the split is a view, the two rotations are the RoPE kernel.
+    with the rotation applied to Q and K.  With one key head per group (the usual GQA packing) split and both
+    rotations are one kernel launch; other packings rotate Q and K separately.
     (Reference: ``pytorch/attention/rope.py:465``.)"""
     assert tensor_format in ("sbhd", "bshd") and len(qkv_split_arg_list) == 3
     nq, nk, nv = (int(x) for x in qkv_split_arg_list)
     assert qkv.shape[-1] == nq + nk + nv and nq % nv == 0 and nk % nv == 0, "split sizes must be whole heads"
     d = nv
+    if nk == nv and qkv.dim() == 4 and qkv.is_contiguous() and cu_seqlens is None:
+        # one key and one value head per group: the packed tensor is the "grouped" head layout of the kernel
+        g, qpg = qkv.shape[2], nq // d
+        flat = qkv.reshape(qkv.shape[0], qkv.shape[1], -1)
+        rot = _RopeQkvFn.apply(flat, q_freqs, k_freqs, tensor_format, "grouped", g * qpg, g, d, interleaved, cp_size,
+                               cp_rank, start_positions, False)
+        rot = rot.reshape(*qkv.shape[:2], g, qpg + 2, d)
+        q, k, v = torch.split(rot, (qpg, 1, 1), dim=-2)
+        return (q.reshape(*qkv.shape[:2], g * qpg, d), k.reshape(*qkv.shape[:2], g, d), v.reshape(*qkv.shape[:2], g, d))
     q, k, v = torch.split(qkv, [nq, nk, nv], dim=-1)
     lead = qkv.shape[:2]
     q = q.reshape(*lead, -1, d)

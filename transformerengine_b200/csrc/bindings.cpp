@@ -419,7 +419,8 @@ void cross_entropy(const at::Tensor& logits, const at::Tensor& targets, const Op
 
 // x, out: 4-D views [s, b, h, d] (any strides with unit stride on d)
 void rope(const at::Tensor& x, at::Tensor& out, const at::Tensor& freqs, int64_t d_rot, bool interleaved,
-          bool backward, int64_t pos_offset, int64_t cp_size, int64_t cp_rank, const OptT& start_positions) {
+          bool backward, int64_t pos_offset, int64_t cp_size, int64_t cp_rank, const OptT& start_positions,
+          int64_t qkv_mode, int64_t q_per_group, int64_t hq, int64_t hk, const OptT& freqs_k) {
   c10::cuda::CUDAGuard guard(x.device());
   TORCH_CHECK(x.dim() == 4 && x.stride(3) == 1 && out.strides() == x.strides(), "rope expects [s,b,h,d] views");
   teb200::RopeArgs a;
@@ -436,6 +437,18 @@ void rope(const at::Tensor& x, at::Tensor& out, const at::Tensor& freqs, int64_t
   a.cp_size = static_cast<int>(cp_size);
   a.cp_rank = static_cast<int>(cp_rank);
   a.start_positions = ptr<int32_t>(start_positions);
+  a.qkv_mode = static_cast<int>(qkv_mode);
+  a.q_per_group = static_cast<int>(q_per_group);
+  a.hq = static_cast<int>(hq);
+  a.hk = static_cast<int>(hk);
+  if (qkv_mode != 0) {
+    TORCH_CHECK(qkv_mode == 1 ? (q_per_group > 0 && a.h % (q_per_group + 2) == 0) : (qkv_mode == 2 && hq + 2 * hk == a.h),
+                "rope: the packed QKV head layout does not match the tensor");
+    if (freqs_k.has_value() && freqs_k->defined()) {
+      TORCH_CHECK(freqs_k->sizes() == freqs.sizes(), "rope: key angles must have the shape of the query angles");
+      a.freqs_k = freqs_k->data_ptr<float>();
+    }
+  }
   check(teb200::rope_apply(a, stream()), "rope");
 }
 
@@ -465,6 +478,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("multi_tensor_scale", teb200::traced("teb200.multi_tensor_scale", &multi_tensor_scale));
   m.def("multi_tensor_l2norm_sq", teb200::traced("teb200.multi_tensor_l2norm_sq", &multi_tensor_l2norm_sq));
   m.def("cross_entropy", teb200::traced("teb200.cross_entropy", &cross_entropy));
-  m.def("rope", teb200::traced("teb200.rope", &rope));
+  m.def("rope", teb200::traced("teb200.rope", &rope), py::arg("x"), py::arg("out"), py::arg("freqs"), py::arg("d_rot"),
+        py::arg("interleaved"), py::arg("backward"), py::arg("pos_offset"), py::arg("cp_size"), py::arg("cp_rank"),
+        py::arg("start_positions"), py::arg("qkv_mode") = 0, py::arg("q_per_group") = 0, py::arg("hq") = 0,
+        py::arg("hk") = 0, py::arg("freqs_k") = py::none());
   register_extra(m);
 }

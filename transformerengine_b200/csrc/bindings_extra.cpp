@@ -749,9 +749,70 @@ void delayed_scaling_update(const at::Tensor& history, const at::Tensor& scale, 
   TORCH_CHECK(e == cudaSuccess, "delayed_scaling_update failed: ", cudaGetErrorString(e));
 }
 
+// ---------------------------------------------------------------------------- column sums, offsets, padding
+at::Tensor column_sum(const at::Tensor& x, at::ScalarType out_dtype) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "column_sum expects a [R, C] matrix with contiguous rows");
+  const int R = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1));
+  at::Tensor out = at::empty({C}, x.options().dtype(out_dtype));
+  if (R == 0) return out.zero_();
+  at::Tensor ws = at::empty({teb200::column_sum_parts(R, C), C}, x.options().dtype(at::kFloat));
+  cudaError_t e = teb200::column_sum(x.data_ptr(), dtype_code(x), R, C, x.stride(0), out.data_ptr(), dtype_code(out),
+                                     ws.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "column_sum failed: ", cudaGetErrorString(e));
+  return out;
+}
+
+at::Tensor splits_to_offsets(const at::Tensor& splits, int64_t multiplier, bool out_int64) {
+  c10::cuda::CUDAGuard guard(splits.device());
+  TORCH_CHECK(splits.dim() == 1 && splits.is_contiguous() &&
+                  (splits.scalar_type() == at::kInt || splits.scalar_type() == at::kLong),
+              "splits_to_offsets expects a 1-D int32 / int64 tensor");
+  const int n = static_cast<int>(splits.numel());
+  at::Tensor out = at::empty({n + 1}, splits.options().dtype(out_int64 ? at::kLong : at::kInt));
+  cudaError_t e = teb200::splits_to_offsets(splits.data_ptr(), splits.scalar_type() == at::kLong, n, multiplier,
+                                            out.data_ptr(), out_int64, cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "splits_to_offsets failed: ", cudaGetErrorString(e));
+  return out;
+}
+
+// in [rows_in, C], offsets: int32 device tensors of groups + 1 entries; out has out_rows rows
+at::Tensor repad_rows(const at::Tensor& in, const at::Tensor& in_offsets, const at::Tensor& out_offsets, int64_t out_rows) {
+  c10::cuda::CUDAGuard guard(in.device());
+  TORCH_CHECK(in.dim() == 2 && in.is_contiguous(), "repad_rows expects a contiguous [rows, C] matrix");
+  TORCH_CHECK(in_offsets.scalar_type() == at::kInt && out_offsets.scalar_type() == at::kInt &&
+                  in_offsets.numel() == out_offsets.numel() && in_offsets.numel() >= 2,
+              "repad_rows: offsets are int32 tensors of groups + 1 entries");
+  at::Tensor out = at::empty({out_rows, in.size(1)}, in.options());
+  const int row_bytes = static_cast<int>(in.size(1) * in.element_size());
+  cudaError_t e = teb200::repad_rows(in.data_ptr(), out.data_ptr(), in_offsets.data_ptr<int>(), out_offsets.data_ptr<int>(),
+                                     static_cast<int>(in_offsets.numel() - 1), row_bytes, static_cast<int>(out_rows),
+                                     cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "repad_rows failed: ", cudaGetErrorString(e));
+  return out;
+}
+
+at::Tensor pad_last_dim(const at::Tensor& in, int64_t new_cols) {
+  c10::cuda::CUDAGuard guard(in.device());
+  TORCH_CHECK(in.dim() >= 1 && in.is_contiguous(), "pad_last_dim expects a contiguous tensor");
+  const int64_t C = in.size(-1);
+  const int64_t R = C > 0 ? in.numel() / C : 0;
+  auto shape = in.sizes().vec();
+  shape.back() = new_cols;
+  at::Tensor out = at::empty(shape, in.options());
+  cudaError_t e = teb200::pad_last_dim(in.data_ptr(), out.data_ptr(), R, static_cast<int>(C * in.element_size()),
+                                       static_cast<int>(new_cols * in.element_size()), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "pad_last_dim failed: ", cudaGetErrorString(e));
+  return out;
+}
+
 }  // namespace
 
 void register_extra(py::module_& m) {
+  m.def("column_sum", teb200::traced("teb200.column_sum", &column_sum));
+  m.def("splits_to_offsets", teb200::traced("teb200.splits_to_offsets", &splits_to_offsets));
+  m.def("repad_rows", teb200::traced("teb200.repad_rows", &repad_rows));
+  m.def("pad_last_dim", teb200::traced("teb200.pad_last_dim", &pad_last_dim));
   m.def("delayed_scaling_update", teb200::traced("teb200.delayed_scaling_update", &delayed_scaling_update));
   m.def("softmax_fwd", teb200::traced("teb200.softmax_fwd", &softmax_fwd));
   m.def("softmax_bwd", teb200::traced("teb200.softmax_bwd", &softmax_bwd));

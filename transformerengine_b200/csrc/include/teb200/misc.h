@@ -96,6 +96,13 @@ struct RopeArgs {
   int pos_offset = 0;  // added to the sequence index (context parallel / KV cache)
   int cp_size = 1, cp_rank = 0;  // dual-chunk position remap when cp_size > 1
   const int32_t* start_positions = nullptr;  // optional [b]
+  // Packed QKV projection output: the h "heads" of a token are query, key and value heads of one tensor and
+  // only the first two kinds are rotated (queries with freqs, keys with freqs_k), so that the split and both
+  // rotations are ONE launch, in place.  qkv_mode 1: per key/value group [q_per_group query heads, 1 key, 1 value];
+  // qkv_mode 2: [hq query heads | hk key heads | hk value heads].  16-bit types, d_rot % 16 == 0 only.
+  int qkv_mode = 0;
+  int q_per_group = 0, hq = 0, hk = 0;
+  const float* freqs_k = nullptr;  // null: same angles as the queries
 };
 cudaError_t rope_apply(const RopeArgs& a, cudaStream_t s);
 
@@ -151,6 +158,22 @@ cudaError_t unpermute_rows(const void* in, void* out, const int32_t* dest_row, c
 // row counts padded to `align`.  counts [E], offsets [E+1] written on device.
 cudaError_t build_dest_rows(const int32_t* topk_idx, int T, int topk, int E, int align, int32_t* counts,
                             int32_t* offsets, int32_t* dest_row, cudaStream_t s);
+
+// ---------------------------------------------------------------- column sums, offsets, padding
+// out[c] = sum_r x[r, c] (bias gradient), deterministic two-stage reduction.  workspace: column_sum_parts(R, C) * C floats.
+int column_sum_parts(int R, int C);
+cudaError_t column_sum(const void* x, int x_dtype, int R, int C, long long ld, void* out, int out_dtype, float* workspace,
+                       cudaStream_t s);
+// out[0] = 0, out[i + 1] = multiplier * (splits[0] + ... + splits[i]); int32 or int64 on either side, all on the device
+cudaError_t splits_to_offsets(const void* splits, int splits_is_int64, int n, long long multiplier, void* out,
+                              int out_is_int64, cudaStream_t s);
+// Rows of `groups` slabs copied from in (slab g = rows [in_offsets[g], in_offsets[g+1])) to out (slab g =
+// rows [out_offsets[g], out_offsets[g+1])): longer destination slabs are zero-filled (padding), shorter ones cut
+// (unpadding).  Offsets are int32 device arrays of groups + 1 entries; max_out_rows bounds out_offsets[groups].
+cudaError_t repad_rows(const void* in, void* out, const int* in_offsets, const int* out_offsets, int groups, int row_bytes,
+                       int max_out_rows, cudaStream_t s);
+// out [R, cp_bytes] = in [R, c_bytes] zero-padded (or cut) along the last dimension; byte counts multiples of 4
+cudaError_t pad_last_dim(const void* in, void* out, long long R, int c_bytes, int cp_bytes, cudaStream_t s);
 
 // ---------------------------------------------------------------- packed sequences ("thd") and KV cache
 // cu: int32 cumulative sequence lengths [nb + 1] on the device.  dtype: 0 fp32, 1 fp16, 2 bf16.

@@ -61,9 +61,19 @@ __global__ void rope_kernel(const RopeArgs a) {
 // Vector path (16-bit types, d_rot % 16 == 0, 16-byte aligned rows): one block per token, one
 // thread per (head, 8-element group); both operands of a rotation pair are read by the thread
 // that writes them, so the kernel is safe in place and needs no staging.
+// kind of head `hi` of a packed QKV tensor: 0 query, 1 key, 2 value (plain tensors: always 0)
+__device__ __forceinline__ int qkv_role(const RopeArgs& a, int hi) {
+  if (a.qkv_mode == 1) {
+    const int r = hi % (a.q_per_group + 2);
+    return r < a.q_per_group ? 0 : (r == a.q_per_group ? 1 : 2);
+  }
+  if (a.qkv_mode == 2) return hi < a.hq ? 0 : (hi < a.hq + a.hk ? 1 : 2);
+  return 0;
+}
+
 template <bool BF>
 __global__ void rope_vec_kernel(const RopeArgs a) {
-  extern __shared__ float cs[];  // cos[d_rot], sin[d_rot]
+  extern __shared__ float cs_all[];  // cos[d_rot], sin[d_rot] of the queries, then (packed QKV, own key angles) of the keys
   const int si = blockIdx.x, bi = blockIdx.y;
   int pos = si;
   if (a.cp_size > 1) {
@@ -71,11 +81,17 @@ __global__ void rope_vec_kernel(const RopeArgs a) {
     pos = si < half ? si + a.cp_rank * half : si + a.s * a.cp_size - (a.cp_rank + 1) * half - half;
   }
   pos += a.pos_offset + (a.start_positions ? a.start_positions[bi] : 0);
+  const bool own_k = a.qkv_mode != 0 && a.freqs_k != nullptr && a.freqs_k != a.freqs;
   for (int j = threadIdx.x; j < a.d_rot; j += blockDim.x) {
     float sn, c;
     sincosf(a.freqs[static_cast<size_t>(pos) * a.d_rot + j], &sn, &c);
-    cs[j] = c;
-    cs[a.d_rot + j] = sn;
+    cs_all[j] = c;
+    cs_all[a.d_rot + j] = sn;
+    if (own_k) {
+      sincosf(a.freqs_k[static_cast<size_t>(pos) * a.d_rot + j], &sn, &c);
+      cs_all[2 * a.d_rot + j] = c;
+      cs_all[3 * a.d_rot + j] = sn;
+    }
   }
   __syncthreads();
   const uint16_t* x = static_cast<const uint16_t*>(a.x) + si * a.stride_s + bi * a.stride_b;
@@ -99,8 +115,17 @@ __global__ void rope_vec_kernel(const RopeArgs a) {
       const int hi = it / groups, j0 = (it % groups) * 8;
       const uint16_t* xh = x + hi * a.stride_h;
       uint16_t* oh = out + hi * a.stride_h;
+      const int role = qkv_role(a, hi);
       const uint4 va = *reinterpret_cast<const uint4*>(xh + j0);
       const uint4 vb = *reinterpret_cast<const uint4*>(xh + j0 + half);
+      if (role == 2) {  // value head: untouched in place, copied otherwise
+        if (a.out != a.x) {
+          *reinterpret_cast<uint4*>(oh + j0) = va;
+          *reinterpret_cast<uint4*>(oh + j0 + half) = vb;
+        }
+        continue;
+      }
+      const float* cs = cs_all + ((role == 1 && own_k) ? 2 * a.d_rot : 0);
       const uint32_t* wa = reinterpret_cast<const uint32_t*>(&va);
       const uint32_t* wb = reinterpret_cast<const uint32_t*>(&vb);
       uint4 oa, ob;
@@ -131,7 +156,13 @@ __global__ void rope_vec_kernel(const RopeArgs a) {
       const int hi = it / groups, j0 = (it % groups) * 8;
       const uint16_t* xh = x + hi * a.stride_h;
       uint16_t* oh = out + hi * a.stride_h;
+      const int role = qkv_role(a, hi);
       const uint4 va = *reinterpret_cast<const uint4*>(xh + j0);
+      if (role == 2) {
+        if (a.out != a.x) *reinterpret_cast<uint4*>(oh + j0) = va;
+        continue;
+      }
+      const float* cs = cs_all + ((role == 1 && own_k) ? 2 * a.d_rot : 0);
       const uint32_t* wa = reinterpret_cast<const uint32_t*>(&va);
       uint4 oa;
       uint32_t* pa = reinterpret_cast<uint32_t*>(&oa);
@@ -163,9 +194,10 @@ cudaError_t rope_apply(const RopeArgs& a, cudaStream_t s) {
   const bool vec = (a.dtype == kBFloat16 || a.dtype == kFloat16) && a.d_rot % 16 == 0 && a.stride_s % 8 == 0 &&
                    a.stride_b % 8 == 0 && a.stride_h % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+  if (a.qkv_mode != 0 && !vec) return cudaErrorInvalidValue;  // the packed-QKV form exists in the vector kernel only
   if (vec) {
     dim3 grid(a.s, a.b);
-    const size_t sm = 2 * static_cast<size_t>(a.d_rot) * sizeof(float);
+    const size_t sm = (a.qkv_mode != 0 ? 4 : 2) * static_cast<size_t>(a.d_rot) * sizeof(float);
     const int work = a.h * (a.interleaved ? a.d_rot / 8 : a.d_rot / 16);
     const int threads = work >= 256 ? 256 : (work >= 128 ? 128 : 64);
     if (a.dtype == kBFloat16) rope_vec_kernel<true><<<grid, threads, sm, s>>>(a);

@@ -278,4 +278,5 @@ def linear_wgrad(dy, x, weight: torch.Tensor, cfg: LinearConfig):
 
 
 def bias_grad(dy2d: torch.Tensor, dtype) -> torch.Tensor:
-    return dy2d.float().sum(dim=0).to(dtype)
+    """Column sums of the output gradient (one two-stage reduction kernel on CUDA)."""
+    return ops.column_sum(dy2d, dtype)

@@ -279,9 +279,7 @@ class Fp8Padding(torch.nn.Module):
         padded = [(m + align - 1) // align * align for m in m_splits]
         if padded == list(m_splits):
             return inp, list(m_splits)
-        chunks = torch.split(inp.reshape(-1, inp.shape[-1]), list(m_splits), dim=0)
-        out = [torch.nn.functional.pad(c, (0, 0, 0, p - m)) for c, m, p in zip(chunks, m_splits, padded)]
-        return torch.cat(out, dim=0), padded
+        return ops.repad_rows(inp.reshape(-1, inp.shape[-1]), list(m_splits), padded), padded
 
 
 class Fp8Unpadding(torch.nn.Module):
@@ -296,5 +294,4 @@ class Fp8Unpadding(torch.nn.Module):
         padded = [(m + align - 1) // align * align for m in m_splits]
         if padded == list(m_splits):
             return inp
-        chunks = torch.split(inp.reshape(-1, inp.shape[-1]), padded, dim=0)
-        return torch.cat([c[:m] for c, m in zip(chunks, m_splits)], dim=0)
+        return ops.repad_rows(inp.reshape(-1, inp.shape[-1]), padded, list(m_splits))

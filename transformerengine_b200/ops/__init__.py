@@ -11,9 +11,10 @@ from .quantize import (amax, quantize_fp8, dequantize_fp8, quantize_mxfp8, dequa
 from .gemm import gemm_nt, general_gemm, as_operand, Operand, set_mn_major_operands
 from .norm import norm_fwd, norm_bwd
 from .activation import activation_fwd, activation_bwd, is_gated
-from .misc import (rope_apply, rope_freqs, cross_entropy_fwd_bwd, cross_entropy_stats, cross_entropy_parallel_grad,
+from .misc import (rope_apply, rope_qkv, rope_freqs, cross_entropy_fwd_bwd, cross_entropy_stats, cross_entropy_parallel_grad,
                    multi_tensor_adam, multi_tensor_sgd, multi_tensor_scale, multi_tensor_l2norm,
-                   scaled_masked_softmax, softmax_bwd, dropout_fwd, dropout_bwd)
+                   scaled_masked_softmax, softmax_bwd, dropout_fwd, dropout_bwd,
+                   column_sum, splits_to_offsets, repad_rows, pad_last_dim)
 from .attention import attention, attention_ref, merge_attention_states
 
 

@@ -74,6 +74,47 @@ def rope_apply(x_sbhd: torch.Tensor, freqs: torch.Tensor, *, interleaved=False, 
     return y
 
 
+def rope_qkv(x_sbhd: torch.Tensor, q_freqs: torch.Tensor, k_freqs: torch.Tensor, *, layout: str, hq: int, hk: int,
+             interleaved=False, backward=False, cp_size=1, cp_rank=0, start_positions=None, inplace=False) -> torch.Tensor:
+    """Rotary embedding of the query and key heads of a packed QKV projection ``[s, b, hq + 2 hk, d]`` in ONE launch;
+    value heads pass through.  ``layout``: ``"grouped"`` = per key/value group ``[hq / hk query heads, key, value]``,
+    ``"blocked"`` = ``[hq query heads | hk key heads | hk value heads]``.  (Reference: the fused QKV RoPE of
+    ``common/fused_rope/fused_rope.cu:505,551``.)"""
+    assert layout in ("grouped", "blocked") and x_sbhd.shape[2] == hq + 2 * hk and hq % hk == 0
+    d_rot = q_freqs.shape[-1]
+    g = hq // hk
+    if _ext.use_cuda(x_sbhd) and x_sbhd.stride(-1) == 1 and x_sbhd.dtype in (torch.bfloat16, torch.float16) \
+            and d_rot % 16 == 0 and x_sbhd.data_ptr() % 16 == 0 and all(st % 8 == 0 for st in x_sbhd.stride()[:3]):
+        out = x_sbhd if inplace else torch.empty_strided(x_sbhd.shape, x_sbhd.stride(), dtype=x_sbhd.dtype,
+                                                         device=x_sbhd.device)
+        sp = start_positions.to(torch.int32) if start_positions is not None else None
+        fq = q_freqs.float().contiguous()
+        fk = None if k_freqs is q_freqs else k_freqs.float().contiguous()
+        _ext.get().rope(x_sbhd, out, fq, d_rot, interleaved, backward, 0, cp_size, cp_rank, sp,
+                        qkv_mode=1 if layout == "grouped" else 2, q_per_group=g, hq=hq, hk=hk, freqs_k=fk)
+        return out
+    # composed path: the plain rotation on the query and key views
+    out = x_sbhd if inplace else x_sbhd.clone()
+    s_, b_, _, d = x_sbhd.shape
+    if layout == "grouped":
+        v5 = out.unflatten(2, (hk, g + 2))   # always a view: the rotated heads are written back through it
+        qv, kv = v5[:, :, :, :g].reshape(s_, b_, hq, d), v5[:, :, :, g]
+        q_new = rope_apply(qv, q_freqs, interleaved=interleaved, backward=backward, cp_size=cp_size, cp_rank=cp_rank,
+                           start_positions=start_positions)
+        k_new = rope_apply(kv, k_freqs, interleaved=interleaved, backward=backward, cp_size=cp_size, cp_rank=cp_rank,
+                           start_positions=start_positions)
+        v5[:, :, :, :g].copy_(q_new.reshape(s_, b_, hk, g, d))
+        v5[:, :, :, g].copy_(k_new)
+    else:
+        q_new = rope_apply(out[:, :, :hq], q_freqs, interleaved=interleaved, backward=backward, cp_size=cp_size,
+                           cp_rank=cp_rank, start_positions=start_positions)
+        k_new = rope_apply(out[:, :, hq:hq + hk], k_freqs, interleaved=interleaved, backward=backward, cp_size=cp_size,
+                           cp_rank=cp_rank, start_positions=start_positions)
+        out[:, :, :hq].copy_(q_new)
+        out[:, :, hq:hq + hk].copy_(k_new)
+    return out
+
+
 # ----------------------------------------------------------------------------- cross entropy
 def cross_entropy_ref(logits, targets, label_smoothing=0.0, ignore_index=-100):
     lf = logits.float().reshape(-1, logits.shape[-1])
@@ -344,3 +385,65 @@ def dropout_bwd(dy: torch.Tensor, keep: Optional[torch.Tensor], p: float):
     if keep.dtype == torch.uint8 and _ext.use_cuda(dy):  # packed keep-bits from the CUDA forward
         return _ext.get().dropout_bwd(dy.contiguous(), keep, float(p))
     return (dy.float() * keep / (1 - p)).to(dy.dtype)
+
+
+# ----------------------------------------------------------------------------- column sums, offsets, padding
+def column_sum(x2d: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """``out[c] = sum_r x[r, c]`` in fp32 (the bias gradient of a linear layer); deterministic."""
+    out_dtype = out_dtype or x2d.dtype
+    if _ext.use_cuda(x2d) and x2d.dim() == 2 and x2d.stride(1) == 1 and x2d.shape[1] % 8 == 0 \
+            and x2d.dtype in (torch.bfloat16, torch.float16, torch.float32) \
+            and out_dtype in (torch.bfloat16, torch.float16, torch.float32) \
+            and x2d.data_ptr() % 16 == 0 and (x2d.stride(0) * x2d.element_size()) % 16 == 0:
+        return _ext.get().column_sum(x2d, out_dtype)
+    return x2d.float().sum(dim=0).to(out_dtype)
+
+
+def splits_to_offsets(splits: torch.Tensor, multiplier: int = 1, dtype=torch.int32) -> torch.Tensor:
+    """Exclusive prefix sums ``[0, s0, s0 + s1, ...] * multiplier`` of a device tensor of split sizes, without a
+    host round trip (reference: ``common/util/splits_to_offsets.cu:61``)."""
+    assert dtype in (torch.int32, torch.int64)
+    if _ext.use_cuda(splits) and splits.dtype in (torch.int32, torch.int64) and splits.dim() == 1:
+        return _ext.get().splits_to_offsets(splits.contiguous(), int(multiplier), dtype == torch.int64)
+    z = torch.zeros(1, dtype=torch.int64, device=splits.device)
+    return (torch.cat([z, torch.cumsum(splits.to(torch.int64), 0)]) * int(multiplier)).to(dtype)
+
+
+def repad_rows(x2d: torch.Tensor, in_splits, out_splits) -> torch.Tensor:
+    """Copy row slabs of sizes ``in_splits`` into slabs of sizes ``out_splits``: longer slabs are zero-filled at
+    their end (padding for FP8 alignment), shorter ones cut (unpadding).  Splits are lists of ints or device
+    tensors; one launch for all slabs (reference: ``common/util/padding.cu:46,130``)."""
+    host = not isinstance(in_splits, torch.Tensor)
+    if host:
+        ins = torch.tensor(list(in_splits), dtype=torch.int32)
+        outs = torch.tensor(list(out_splits), dtype=torch.int32)
+        out_rows = int(outs.sum())
+    else:
+        ins, outs = in_splits, out_splits
+        out_rows = None
+    if _ext.use_cuda(x2d) and x2d.dim() == 2 and (x2d.shape[1] * x2d.element_size()) % 16 == 0:
+        z = torch.zeros(1, dtype=torch.int32)
+        if host:
+            io = torch.cat([z, torch.cumsum(ins, 0).to(torch.int32)]).to(x2d.device, non_blocking=True)
+            oo = torch.cat([z, torch.cumsum(outs, 0).to(torch.int32)]).to(x2d.device, non_blocking=True)
+        else:
+            io, oo = splits_to_offsets(ins.to(x2d.device)), splits_to_offsets(outs.to(x2d.device))
+            out_rows = int(outs.sum())  # the result's shape is host data: device splits cost one read here
+        return _ext.get().repad_rows(x2d.contiguous(), io, oo, out_rows)
+    il = [int(v) for v in (ins.tolist())]
+    ol = [int(v) for v in (outs.tolist())]
+    chunks = torch.split(x2d, il, dim=0)
+    res = []
+    for c, m, p in zip(chunks, il, ol):
+        res.append(c[:p] if p <= m else torch.nn.functional.pad(c, (0, 0, 0, p - m)))
+    return torch.cat(res, dim=0) if res else x2d[:0]
+
+
+def pad_last_dim(x: torch.Tensor, new_cols: int) -> torch.Tensor:
+    """Zero-pad (or cut) the last dimension to ``new_cols`` (head-dim padding of block-scaled attention inputs)."""
+    C = x.shape[-1]
+    if new_cols == C:
+        return x
+    if _ext.use_cuda(x) and (C * x.element_size()) % 4 == 0 and (new_cols * x.element_size()) % 4 == 0:
+        return _ext.get().pad_last_dim(x.contiguous(), int(new_cols))
+    return x[..., :new_cols] if new_cols < C else torch.nn.functional.pad(x, (0, new_cols - C))

@@ -142,6 +142,10 @@ def test_rotate_packed_qkv_in_place_matches_separate_rotations(layout, fmt):
     mixed = bt * 1.0                                 # a non-leaf the rotation may overwrite
     out = rotate_packed_qkv_(mixed, freqs, freqs, fmt, layout, hq, hk, d)
     assert out.data_ptr() == mixed.data_ptr()        # in place
+    view_in = (bt * 1.0).reshape(-1).reshape(base.shape)   # a view: rotated into a new tensor instead
+    out_v = rotate_packed_qkv_(view_in, freqs, freqs, fmt, layout, hq, hk, d)
+    assert out_v.data_ptr() != view_in.data_ptr()
+    torch.testing.assert_close(out_v, out)
     q2, k2, v2 = split(out)
     got = torch.cat([q2.flatten(2), k2.flatten(2), v2.flatten(2)], dim=-1)
     torch.testing.assert_close(got, ref)

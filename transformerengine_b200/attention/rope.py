@@ -114,12 +114,14 @@ def rotate_packed_qkv_(mixed: torch.Tensor, q_freqs: torch.Tensor, k_freqs: torc
                        hq: int, hk: int, head_dim: int, *, interleaved: bool = False, cp_size: int = 1, cp_rank: int = 0,
                        start_positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Rotate the query and key heads of ``mixed`` (``[s, b, (hq + 2 hk) * d]`` or ``[b, s, ...]``, the output of a
-    fused QKV projection) in place and return it; value heads are untouched.  ``layout``: ``"grouped"`` (per
-    key/value group: its query heads, the key head, the value head) or ``"blocked"`` (all queries, all keys, all
-    values)."""
+    fused QKV projection) with one kernel launch and return the result; value heads pass through.  The rotation
+    runs in place when autograd allows it (``mixed`` is not a view made inside another function), else into a new
+    tensor.  ``layout``: ``"grouped"`` (per key/value group: its query heads, the key head, the value head) or
+    ``"blocked"`` (all queries, all keys, all values)."""
     assert mixed.dim() == 3 and mixed.is_contiguous() and mixed.shape[-1] == (hq + 2 * hk) * head_dim
+    inplace = not mixed._is_view() and not (mixed.is_leaf and mixed.requires_grad)
     return _RopeQkvFn.apply(mixed, q_freqs, k_freqs, tensor_format, layout, hq, hk, head_dim, interleaved, cp_size,
-                            cp_rank, start_positions, True)
+                            cp_rank, start_positions, inplace)
 
 
 def apply_fused_qkv_rotary_pos_emb(qkv: torch.Tensor, q_freqs: torch.Tensor, k_freqs: torch.Tensor,

@@ -87,3 +87,20 @@ def test_linear_under_nvfp4_recipe():
     rel = (y.float() - ref).norm() / ref.norm()
     assert rel < 0.2, rel.item()
     assert torch.isfinite(x.grad.float()).all() and torch.isfinite(lin.weight.grad.float()).all()
+
+
+@pytest.mark.parametrize("shape", [(8192, 4096), (1040, 272)])
+@pytest.mark.parametrize("with_rht", [False, True])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_one_pass_row_and_column_kernel_is_bitwise_the_two_single_copy_kernels(shape, with_rht, dtype):
+    """Asking for both copies runs the kernel that reads the input once; asking for one copy at a time runs the
+    single-copy kernels.  Same functions on the same values: every byte must agree (partial tiles included)."""
+    from transformerengine_b200.ops import quantize as qz
+
+    torch.manual_seed(1)
+    x = (torch.randn(*shape, device="cuda") * 2).to(dtype)
+    both = qz.quantize_nvfp4(x, with_rht=with_rht)
+    row = qz.quantize_nvfp4(x, rowwise=True, columnwise=False, with_rht=with_rht)
+    col = qz.quantize_nvfp4(x, rowwise=False, columnwise=True, with_rht=with_rht)
+    assert torch.equal(both[0], row[0]) and torch.equal(both[1], row[1]) and torch.equal(both[2], row[2])
+    assert torch.equal(both[3], col[3]) and torch.equal(both[4], col[4]) and torch.equal(both[5], col[5])

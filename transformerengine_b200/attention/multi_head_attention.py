@@ -17,6 +17,7 @@ from ..modules.layernorm_linear import LayerNorm, LayerNormLinear, RMSNorm
 from ..modules.linear import Linear
 from ..parallel import distributed as D
 from .dot_product_attention import DotProductAttention
+from ..utils.config import get_config
 from .rope import apply_rotary_pos_emb, rotate_packed_qkv_
 
 
@@ -156,7 +157,7 @@ class MultiheadAttention(torch.nn.Module):
             rope_done = False
             if (rotary_pos_emb is not None and inference_params is None and self.qkv_format in ("sbhd", "bshd")
                     and not (self.qk_norm_type is not None and self.qk_norm_before_rope)
-                    and mixed.dim() == 3 and mixed.is_contiguous()):
+                    and mixed.dim() == 3 and mixed.is_contiguous() and get_config().fused_qkv_rope):
                 # split + both rotations in one launch, in place on the projection output
                 q_emb, k_emb = rotary_pos_emb if isinstance(rotary_pos_emb, (tuple, list)) else (rotary_pos_emb,) * 2
                 cpg = self.core_attention.cp_group

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "teb200/api.h"
 #include "teb200/quant.h"
 
@@ -249,6 +251,156 @@ __global__ void nvfp4_col_kernel(const T* __restrict__ x, int R, int C, const fl
   }
 }
 
+// ------------------------------------------------------------- row-wise + column-wise, one read
+// Both copies from ONE pass over the input: a CTA loads a 64 x 128 tile into shared memory (as the fp32 values
+// both quantizers work on), then every thread quantizes two 16-value row segments and two 16-value column
+// segments (rotated by the Hadamard transform when asked) with the very functions of the single-copy kernels,
+// so the bytes are identical to theirs.  Packed outputs leave through shared memory in 64-byte (rows) and
+// 32-byte (columns) runs.  1 x 16 block scales only (16 x 16 scales belong to weights, which are quantized
+// once per step by the single-copy kernels).
+constexpr int FT_R = 64, FT_C = 128;
+constexpr int FT_PITCH = FT_C + FT_C / 32 + 1;  // one word of skew per 32 columns plus an odd pitch: the 8-value
+                                                // stores of the load, the row reads and the column reads are all
+                                                // free of bank conflicts
+__device__ __forceinline__ int ft_col(int c) { return c + (c >> 5); }
+
+template <typename T>
+__device__ __forceinline__ void ft_load8(const T* p, float (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = to_f(p[i]);
+}
+template <>
+__device__ __forceinline__ void ft_load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(p);  // 16-byte aligned: checked at launch
+  const uint32_t u[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(u[i] << 16);
+    v[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void ft_load8<__half>(const __half* p, float (&v)[8]) {
+  const uint4 w = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&w);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __low2float(h[i]);
+    v[2 * i + 1] = __high2float(h[i]);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+nvfp4_rowcol_kernel(const T* __restrict__ x, int R, int C, const float* __restrict__ amax_row,
+                    const float* __restrict__ amax_col, uint8_t* __restrict__ row_data, uint8_t* __restrict__ row_scale,
+                    uint8_t* __restrict__ col_data, uint8_t* __restrict__ col_scale, int with_rht, int stochastic,
+                    uint64_t seed, uint64_t offset, const unsigned long long* __restrict__ offset_dev) {
+  if (offset_dev != nullptr) offset += *offset_dev;
+  __shared__ float tile[FT_R][FT_PITCH];
+  __shared__ uint2 rstage[FT_R][FT_C / 16 + 1];   // packed row segments: 8 per row
+  __shared__ uint2 cstage[FT_C][FT_R / 16 + 1];   // packed column segments: 4 per column
+  const int r_base = blockIdx.y * FT_R, c_base = blockIdx.x * FT_C;
+  const int tid = threadIdx.x;
+  // load: 64 rows x 128 columns, 8 consecutive values per thread and step (coalesced rows)
+  for (int v = tid; v < FT_R * (FT_C / 8); v += 256) {
+    const int rr = v / (FT_C / 8), cc = (v % (FT_C / 8)) * 8;
+    const int r = r_base + rr, c = c_base + cc;
+    float v8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (r < R && c < C) ft_load8<T>(x + static_cast<size_t>(r) * C + c, v8);  // C % 16 == 0: all 8 inside or outside
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tile[rr][ft_col(cc) + i] = v8[i];  // the 8 values stay inside one group of 32 columns
+  }
+  __syncthreads();
+  const float s_enc_row = global_encode_scale(*amax_row);
+  const float s_enc_col = global_encode_scale(*amax_col);
+  // ---- row segments: item = (cb, rx), rx fastest so that a warp reads 32 different rows (no bank conflicts)
+#pragma unroll 1
+  for (int it = tid; it < FT_R * (FT_C / 16); it += 256) {
+    const int rx = it % FT_R, cb = it / FT_R;
+    const int r = r_base + rx, blk = (c_base >> 4) + cb;
+    uint2 packed = make_uint2(0u, 0u);
+    if (r < R && blk * 16 < C) {
+      float v[16];
+      float vmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        v[i] = tile[rx][ft_col(cb * 16) + i];
+        vmax = fmaxf(vmax, fabsf(v[i]));
+      }
+      float enc;
+      const uint8_t sb = block_scale(vmax, s_enc_row, enc);
+      row_scale[swizzled_sf_offset(r, blk, ((C >> 4) + 3) >> 2)] = sb;
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
+        uint32_t code;
+        if (stochastic) {
+          const uint64_t idx = static_cast<uint64_t>(r) * C + blk * 16 + i;
+          const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset) >> 8) * (1.0f / 16777216.0f);
+          code = e2m1_sr(sv, u);
+        } else {
+          code = e2m1_rn(sv);
+        }
+        w[i >> 3] |= code << ((i & 7) * 4);
+      }
+      packed = make_uint2(w[0], w[1]);
+    }
+    rstage[rx][cb] = packed;
+  }
+  // ---- column segments: item = (g, cx), cx fastest (a warp reads 32 adjacent columns of one row at a time)
+#pragma unroll 1
+  for (int it = tid; it < FT_C * (FT_R / 16); it += 256) {
+    const int cx = it % FT_C, g = it / FT_C;
+    const int c = c_base + cx, r0 = r_base + g * 16;
+    uint2 packed = make_uint2(0u, 0u);
+    if (c < C && r0 < R) {
+      float v[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = tile[g * 16 + i][ft_col(cx)];
+      if (with_rht) rht16(v);
+      float vmax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) vmax = fmaxf(vmax, fabsf(v[i]));
+      float enc;
+      const uint8_t sb = block_scale(vmax, s_enc_col, enc);
+      col_scale[swizzled_sf_offset(c, r0 >> 4, ((R >> 4) + 3) >> 2)] = sb;
+      uint32_t w[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
+        uint32_t code;
+        if (stochastic) {
+          const uint64_t idx = static_cast<uint64_t>(c) * R + r0 + i;
+          const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset + 0x5bd1e995ULL) >> 8) *
+                          (1.0f / 16777216.0f);
+          code = e2m1_sr(sv, u);
+        } else {
+          code = e2m1_rn(sv);
+        }
+        w[i >> 3] |= code << ((i & 7) * 4);
+      }
+      packed = make_uint2(w[0], w[1]);
+    }
+    cstage[cx][g] = packed;
+  }
+  __syncthreads();
+  // ---- stores: 8 threads write the 64 bytes of a row segment run, 4 threads the 32 bytes of a column's
+  for (int v = tid; v < FT_R * (FT_C / 16); v += 256) {
+    const int rx = v / (FT_C / 16), q = v % (FT_C / 16);
+    const int r = r_base + rx, blk = (c_base >> 4) + q;
+    if (r < R && blk * 16 < C)
+      *reinterpret_cast<uint2*>(row_data + static_cast<size_t>(r) * (C / 2) + blk * 8) = rstage[rx][q];
+  }
+  for (int v = tid; v < FT_C * (FT_R / 16); v += 256) {
+    const int cx = v / (FT_R / 16), q = v % (FT_R / 16);
+    const int c = c_base + cx, r0 = r_base + q * 16;
+    if (c < C && r0 < R)
+      *reinterpret_cast<uint2*>(col_data + static_cast<size_t>(c) * (R / 2) + r0 / 2) = cstage[cx][q];
+  }
+}
+
 // --------------------------------------------------------------------------------- dequantize
 template <typename T>
 __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ q, const uint8_t* __restrict__ sf,
@@ -276,6 +428,17 @@ __global__ void nvfp4_dequant_kernel(const uint8_t* __restrict__ q, const uint8_
 template <typename T>
 cudaError_t launch_quant(const Nvfp4Args& a, cudaStream_t s) {
   const T* x = static_cast<const T*>(a.x);
+  static const bool fused_ok = []() {
+    const char* e = getenv("TEB200_NVFP4_FUSED");  // "0": always the single-copy kernels (A/B timing)
+    return e == nullptr || e[0] != '0';
+  }();
+  if (fused_ok && a.row_data != nullptr && a.col_data != nullptr && !a.with_2d &&
+      (reinterpret_cast<uintptr_t>(a.x) & 15) == 0) {
+    dim3 grid((a.C + FT_C - 1) / FT_C, (a.R + FT_R - 1) / FT_R);
+    nvfp4_rowcol_kernel<T><<<grid, 256, 0, s>>>(x, a.R, a.C, a.amax_row, a.amax_col, a.row_data, a.row_scale, a.col_data,
+                                                a.col_scale, a.with_rht, a.stochastic, a.seed, a.offset, a.offset_dev);
+    return cudaGetLastError();
+  }
   if (a.row_data != nullptr) {
     dim3 grid((a.C / 16 + 15) / 16, (a.R + 15) / 16);
     nvfp4_row_kernel<T><<<grid, 256, 0, s>>>(x, a.R, a.C, a.amax_row, a.row_data, a.row_scale, a.with_2d, a.stochastic,

@@ -43,11 +43,15 @@ class Config:
         env="TEB200_WAIT_LIMIT_CYCLES", help="limit of host-launched flag waits in SM clock cycles (0: about one second)"))
     copy_ctas: int = field(default=0, metadata=dict(
         env="TEB200_COPY_CTAS", help="SMs that copy instead of computing in a fused collective GEMM (0: automatic)"))
+    fused_qkv_rope: bool = field(default=True, metadata=dict(
+        env="TEB200_FUSED_QKV_ROPE", help="rotate the query and key heads of a packed QKV projection with one launch"))
     # mirrored switches of the native kernels (read there at first launch)
     gemm_cta_pairs: bool = field(default=True, metadata=dict(
         env="TEB200_GEMM_2CTA", help="dense GEMMs on cta_group::2 pairs (0: single-CTA kernels)"))
     gemm_tile_n: int = field(default=0, metadata=dict(
         env="TEB200_GEMM_BN", help="force the single-CTA GEMM tile width (0: automatic)"))
+    nvfp4_one_pass: bool = field(default=True, metadata=dict(
+        env="TEB200_NVFP4_FUSED", help="NVFP4 row-wise and column-wise copies from one read of the input"))
     attention_group_split: bool = field(default=True, metadata=dict(
         env="TEB200_ATTN_GSPLIT", help="split dK/dV head groups over CTAs when few heads underfill the GPU"))
 

@@ -80,10 +80,33 @@ __device__ __forceinline__ uint8_t block_scale(float vec_max, float s_enc, float
   return *reinterpret_cast<const uint8_t*>(&d8);
 }
 
-__device__ __forceinline__ uint32_t e2m1_rn(float x) {
-  const float a = fabsf(x);
-  uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.0f);
-  return c | (x < 0.f ? 8u : 0u);
+// Two values -> one byte of E2M1 codes (lo in bits 0-3, hi in bits 4-7) with the conversion instruction of
+// sm_100a: round to nearest even onto {0, 0.5, 1, 1.5, 2, 3, 4, 6}, saturating at +-6 (ties: 0.25 -> 0,
+// 0.75 -> 1, 1.25 -> 1, 1.75 -> 2, 2.5 -> 2, 3.5 -> 4, 5 -> 4).  A zero input yields code 0 whatever its sign.
+__device__ __forceinline__ uint32_t e2m1x2_rn(float lo, float hi) {
+  if ((__float_as_uint(lo) << 1) == 0u) lo = 0.f;
+  if ((__float_as_uint(hi) << 1) == 0u) hi = 0.f;
+  uint32_t out;
+  asm("{\n"
+      ".reg .b8 t;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n"
+      "cvt.u32.u8 %0, t;\n"
+      "}\n"
+      : "=r"(out)
+      : "f"(hi), "f"(lo));
+  return out;
+}
+
+// 16 scaled values -> 8 bytes of codes, round to nearest
+__device__ __forceinline__ void pack16_rn(const float (&v)[16], float enc, uint32_t (&w)[2]) {
+  w[0] = 0u;
+  w[1] = 0u;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float a = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
+    const float b = fminf(fmaxf(__fmul_rn(v[i + 1], enc), -6.f), 6.f);
+    w[i >> 3] |= e2m1x2_rn(a, b) << ((i & 7) * 4);
+  }
 }
 
 __device__ __forceinline__ uint32_t hash32(uint64_t k) {
@@ -172,18 +195,16 @@ __global__ void nvfp4_row_kernel(const T* __restrict__ x, int R, int C, const fl
   const uint8_t sb = block_scale(vmax, s_enc, enc);
   scale[swizzled_sf_offset(r, blk, ((C >> 4) + 3) >> 2)] = sb;
   uint32_t w[2] = {0u, 0u};
+  if (stochastic) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
-    uint32_t code;
-    if (stochastic) {
+    for (int i = 0; i < 16; ++i) {
+      const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
       const uint64_t idx = static_cast<uint64_t>(r) * C + blk * 16 + i;
       const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset) >> 8) * (1.0f / 16777216.0f);
-      code = e2m1_sr(sv, u);
-    } else {
-      code = e2m1_rn(sv);
+      w[i >> 3] |= e2m1_sr(sv, u) << ((i & 7) * 4);
     }
-    w[i >> 3] |= code << ((i & 7) * 4);
+  } else {
+    pack16_rn(v, enc, w);
   }
   *reinterpret_cast<uint2*>(data + static_cast<size_t>(r) * (C / 2) + blk * 8) = make_uint2(w[0], w[1]);
 }
@@ -222,19 +243,17 @@ __global__ void nvfp4_col_kernel(const T* __restrict__ x, int R, int C, const fl
     const uint8_t sb = block_scale(vmax, s_enc, enc);
     scale[swizzled_sf_offset(c, r0 >> 4, ((R >> 4) + 3) >> 2)] = sb;
     uint32_t w[2] = {0u, 0u};
+    if (stochastic) {
 #pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
-      uint32_t code;
-      if (stochastic) {
+      for (int i = 0; i < 16; ++i) {
+        const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
         const uint64_t idx = static_cast<uint64_t>(c) * R + r0 + i;
         const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset + 0x5bd1e995ULL) >> 8) *
                         (1.0f / 16777216.0f);
-        code = e2m1_sr(sv, u);
-      } else {
-        code = e2m1_rn(sv);
+        w[i >> 3] |= e2m1_sr(sv, u) << ((i & 7) * 4);
       }
-      w[i >> 3] |= code << ((i & 7) * 4);
+    } else {
+      pack16_rn(v, enc, w);
     }
     packed = make_uint2(w[0], w[1]);
   }
@@ -332,18 +351,16 @@ nvfp4_rowcol_kernel(const T* __restrict__ x, int R, int C, const float* __restri
       const uint8_t sb = block_scale(vmax, s_enc_row, enc);
       row_scale[swizzled_sf_offset(r, blk, ((C >> 4) + 3) >> 2)] = sb;
       uint32_t w[2] = {0u, 0u};
+      if (stochastic) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
-        uint32_t code;
-        if (stochastic) {
+        for (int i = 0; i < 16; ++i) {
+          const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
           const uint64_t idx = static_cast<uint64_t>(r) * C + blk * 16 + i;
           const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset) >> 8) * (1.0f / 16777216.0f);
-          code = e2m1_sr(sv, u);
-        } else {
-          code = e2m1_rn(sv);
+          w[i >> 3] |= e2m1_sr(sv, u) << ((i & 7) * 4);
         }
-        w[i >> 3] |= code << ((i & 7) * 4);
+      } else {
+        pack16_rn(v, enc, w);
       }
       packed = make_uint2(w[0], w[1]);
     }
@@ -367,19 +384,17 @@ nvfp4_rowcol_kernel(const T* __restrict__ x, int R, int C, const float* __restri
       const uint8_t sb = block_scale(vmax, s_enc_col, enc);
       col_scale[swizzled_sf_offset(c, r0 >> 4, ((R >> 4) + 3) >> 2)] = sb;
       uint32_t w[2] = {0u, 0u};
+      if (stochastic) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
-        uint32_t code;
-        if (stochastic) {
+        for (int i = 0; i < 16; ++i) {
+          const float sv = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
           const uint64_t idx = static_cast<uint64_t>(c) * R + r0 + i;
           const float u = (hash32(idx * 0x9E3779B97F4A7C15ULL + seed * 0xD1B54A32D192ED03ULL + offset + 0x5bd1e995ULL) >> 8) *
                           (1.0f / 16777216.0f);
-          code = e2m1_sr(sv, u);
-        } else {
-          code = e2m1_rn(sv);
+          w[i >> 3] |= e2m1_sr(sv, u) << ((i & 7) * 4);
         }
-        w[i >> 3] |= code << ((i & 7) * 4);
+      } else {
+        pack16_rn(v, enc, w);
       }
       packed = make_uint2(w[0], w[1]);
     }

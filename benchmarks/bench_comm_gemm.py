@@ -70,6 +70,7 @@ def stamps(fn, n_copy):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--kinds", default="mxfp8,bf16", help="operand kinds to time")
     ap.add_argument("--timeline", type=int, default=0, help="add in-kernel time stamps of one launch per kernel")
     ap.add_argument("--shapes", default="llama")
     ap.add_argument("--copy-ctas", type=int, default=0, help="0 = chosen by the library per shape")
@@ -92,7 +93,7 @@ def main():
     q = MXFP8Quantizer(columnwise=False)
     for T, H, F in shapes:
         Fl = F // world
-        for mx in (True, False):
+        for mx in [k == "mxfp8" for k in a.kinds.split(",")]:
             xl = torch.randn(T // world, H, device="cuda", dtype=torch.bfloat16)
             w1 = torch.randn(Fl, H, device="cuda", dtype=torch.bfloat16)
             x2 = torch.randn(T, Fl, device="cuda", dtype=torch.bfloat16)

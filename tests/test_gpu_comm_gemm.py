@@ -93,6 +93,33 @@ def _worker(rank, world, port, result_q):
                 e = rel(got, ref)
                 if not e < 1e-2:
                     bad[f"rs mx={mx} it={it}"] = e
+            # all-reduce: the same product, every rank ends with all rows (two contexts' worth of calls: the
+            # result buffer is double buffered, an earlier result must survive one further call)
+            from transformerengine_b200.parallel.comm_gemm import GemmAllReduce
+
+            ar = GemmAllReduce(g, T, N)
+            prev = None
+            for it in range(4):
+                xi = xr * (it + 1)
+                if mx:
+                    q = MXFP8Quantizer(columnwise=False)
+                    a_op, b_op = q(xi), q(wr)
+                    part = ops.gemm_nt(ops.as_operand(a_op), ops.as_operand(b_op), out_dtype=torch.float32)
+                else:
+                    a_op, b_op = xi, wr
+                    part = ops.gemm_nt(xi, wr, out_dtype=torch.float32)
+                dist.all_reduce(part)
+                got = ar(a_op, b_op)
+                torch.cuda.synchronize()
+                log(f"ar call mx={mx} it={it} done")
+                te.check_status()
+                e = rel(got, part)
+                if not e < 1e-2:
+                    bad[f"ar mx={mx} it={it}"] = e
+                if prev is not None and not torch.equal(prev[0], prev[1]):
+                    bad[f"ar mx={mx} it={it} previous result overwritten"] = 1.0
+                prev = (got, got.clone())
+            del ar
         # ---- side gather (the wgrad operand travels next to the GEMM), shapes with more tiles than SMs
         from transformerengine_b200.parallel.comm_gemm import SideSpec
         from transformerengine_b200.parallel.distributed import gather_mxfp8_along_first_dim

@@ -40,7 +40,7 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, const at::Tensor& epoc
                std::vector<int64_t> ready_ptrs, int64_t chunk_flags_ptr, std::vector<int64_t> stage_ptrs,
                std::vector<int64_t> tile_flag_ptrs, const OptT& out, int64_t N, const at::Tensor& status,
                std::vector<int64_t> side_src_ptrs, const OptT& side_dst, const OptT& side_dst_sf,
-               std::vector<int64_t> side_geom) {
+               std::vector<int64_t> side_geom, std::vector<int64_t> out_all_ptrs, std::vector<int64_t> ar_flag_ptrs) {
   c10::cuda::CUDAGuard guard(a.device());
   teb200::CommGemmArgs c;
   teb200::GemmArgs& g = c.g;
@@ -87,7 +87,13 @@ void comm_gemm(int64_t mode, int64_t rank, int64_t world, const at::Tensor& epoc
     if (!ready_ptrs.empty()) c.ready[r] = reinterpret_cast<uint32_t*>(ready_ptrs[r]);
     if (!stage_ptrs.empty()) c.stage[r] = reinterpret_cast<uint8_t*>(stage_ptrs[r]);
     if (!tile_flag_ptrs.empty()) c.tile_flags[r] = reinterpret_cast<uint32_t*>(tile_flag_ptrs[r]);
+    if (!out_all_ptrs.empty()) c.out_all[r] = reinterpret_cast<uint8_t*>(out_all_ptrs[r]);
+    if (!ar_flag_ptrs.empty()) c.ar_flags[r] = reinterpret_cast<uint32_t*>(ar_flag_ptrs[r]);
   }
+  if (mode == teb200::kCommAllReduce)
+    TORCH_CHECK(static_cast<int64_t>(out_all_ptrs.size()) >= world && static_cast<int64_t>(ar_flag_ptrs.size()) >= world &&
+                    out.has_value() && out->defined() && out->size(0) == a.size(0),
+                "comm_gemm: all-reduce needs the result buffer [M, N] and its address and counters on every rank");
   c.a_row_bytes = a.stride(0) * a.element_size();
   c.sf_bytes_per_mblock = mx ? static_cast<long long>(((g.K + 31) / 32 + 3) / 4) * 512 : 0;
   c.chunk_flags = reinterpret_cast<uint32_t*>(chunk_flags_ptr);
@@ -838,7 +844,8 @@ void register_extra(py::module_& m) {
         py::arg("a_e5m2"), py::arg("b_e5m2"), py::arg("a_ptrs"), py::arg("sfa_ptrs"), py::arg("ready_ptrs"),
         py::arg("chunk_flags_ptr"), py::arg("stage_ptrs"), py::arg("tile_flag_ptrs"), py::arg("out"), py::arg("N"),
         py::arg("status"), py::arg("side_src_ptrs") = std::vector<int64_t>(), py::arg("side_dst") = py::none(),
-        py::arg("side_dst_sf") = py::none(), py::arg("side_geom") = std::vector<int64_t>());
+        py::arg("side_dst_sf") = py::none(), py::arg("side_geom") = std::vector<int64_t>(),
+        py::arg("out_all_ptrs") = std::vector<int64_t>(), py::arg("ar_flag_ptrs") = std::vector<int64_t>());
   m.def("flash_fwd", teb200::traced("teb200.flash_fwd", &flash_fwd), py::arg("q"), py::arg("k"), py::arg("v"), py::arg("out"), py::arg("lse"),
         py::arg("scale"), py::arg("causal"), py::arg("bottom_right"), py::arg("status"),
         py::arg("timeline") = py::none(), py::arg("window_left") = -1, py::arg("window_right") = -1);

@@ -43,6 +43,9 @@ struct CommParams {
   uint8_t* stage[kCommMaxRanks];
   uint32_t* tile_flags[kCommMaxRanks];
   void* out;
+  uint8_t* out_all[kCommMaxRanks];   // all-reduce: result buffers of every rank, else null
+  uint32_t* ar_flags[kCommMaxRanks];
+  int allreduce;
   SideGather side;
   int side_tma;  // the side gather's interleaved pieces leave through one 2-D TMA store each (rows <= 1 KB)
 };
@@ -426,7 +429,27 @@ __device__ void reduce_tail(const CommParams& p, int cta, int num_ctas, int et, 
           o = make_uint4(pack_f16x2(acc[0], acc[1]), pack_f16x2(acc[2], acc[3]), pack_f16x2(acc[4], acc[5]),
                          pack_f16x2(acc[6], acc[7]));
         }
-        *reinterpret_cast<uint4*>(out + static_cast<size_t>(mbl * kBlockM + r) * N + c) = o;
+        if (!p.allreduce) {
+          *reinterpret_cast<uint4*>(out + static_cast<size_t>(mbl * kBlockM + r) * N + c) = o;
+        } else {
+          // the reduced row goes to its place in the full result of every rank
+          const size_t at = (static_cast<size_t>(p.rank) * p.mb_per_rank * kBlockM + mbl * kBlockM + r) * N + c;
+#pragma unroll
+          for (int dr = 0; dr < WMAX; ++dr)
+            if (dr < p.world) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.out_all[dr]) + at) = o;
+        }
+      }
+    }
+    named_bar_sync(1, kEpiThreads);
+  }
+  if (p.allreduce) {
+    // this CTA's rows are on their way: tell every rank, then wait until every rank's CTAs have told us
+    __threadfence_system();
+    named_bar_sync(1, kEpiThreads);
+    if (et < p.world) red_release_sys_add(p.ar_flags[et] + p.rank, 1u);
+    if (et < p.world) {
+      if (!wait_flag_ge_or_failed(p.ar_flags[p.rank] + et, epoch * static_cast<uint32_t>(num_ctas), p.k.status)) {
+        if (p.k.status) atomicCAS(p.k.status, 0, kTimeoutPeerFlag);
       }
     }
     named_bar_sync(1, kEpiThreads);
@@ -864,6 +887,14 @@ cudaError_t launch_comm(const CommGemmArgs& a, cudaStream_t stream) {
   }
   p.a_row_bytes = a.a_row_bytes; p.sf_bytes_per_mblock = a.sf_bytes_per_mblock;
   p.chunk_flags = a.chunk_flags; p.out = a.out;
+  p.allreduce = a.mode == kCommAllReduce ? 1 : 0;
+  for (int r = 0; r < kCommMaxRanks; ++r) {
+    p.out_all[r] = a.out_all[r];
+    p.ar_flags[r] = a.ar_flags[r];
+  }
+  if (p.allreduce)
+    for (int r = 0; r < a.world; ++r)
+      if (a.out_all[r] == nullptr || a.ar_flags[r] == nullptr) return cudaErrorInvalidValue;
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(comm_gemm_kernel<KIND, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -894,7 +925,7 @@ cudaError_t comm_gemm(const CommGemmArgs& a, cudaStream_t stream) {
   if (mx && g.K % 128 != 0) return cudaErrorInvalidValue;
   if (a.mode == kCommAllGather)
     return mx ? launch_comm<kKindMxf8, kCommAllGather>(a, stream) : launch_comm<kKindF16, kCommAllGather>(a, stream);
-  if (a.mode == kCommReduceScatter)
+  if (a.mode == kCommReduceScatter || a.mode == kCommAllReduce)
     return mx ? launch_comm<kKindMxf8, kCommReduceScatter>(a, stream)
               : launch_comm<kKindF16, kCommReduceScatter>(a, stream);
   return cudaErrorInvalidValue;

@@ -10,6 +10,11 @@
 //                       buffer (peer stores) and bumps a per-block counter there; after its own
 //                       tiles each CTA reduces the blocks it owns as soon as all ranks delivered.
 //
+//   kCommAllReduce    : out[M, N] = sum_ranks (X_r * W_r^T) on EVERY rank (row-parallel layers without sequence
+//                       parallelism).  The reduce-scatter kernel whose tail writes the reduced rows of this rank
+//                       into the output buffer of every rank (peer stores) and returns once all ranks' rows have
+//                       landed here (one counter per source rank).
+//
 // All waits on flags are bounded (status code kTimeoutPeerFlag, see ptx.cuh).  No load in
 // these kernels is a cluster-wide broadcast.  Replaces the reference's Userbuffers
 // pipelines (common/comm_gemm_overlap/comm_gemm_overlap.cpp:611-760, 1044-1217).
@@ -19,7 +24,7 @@
 namespace teb200 {
 
 constexpr int kCommMaxRanks = 8;
-enum CommMode : int { kCommNone = 0, kCommAllGather = 1, kCommReduceScatter = 2 };
+enum CommMode : int { kCommNone = 0, kCommAllGather = 1, kCommReduceScatter = 2, kCommAllReduce = 3 };
 
 // Optional second all-gather carried out by copy CTAs of the same kernel while the GEMM runs (the
 // operand of the weight-gradient GEMM that follows: bulk overlap).  Every rank stages a piece of
@@ -58,6 +63,10 @@ struct CommGemmArgs {
   uint8_t* stage[kCommMaxRanks] = {};       // stage[r] on rank r: [world][M/world][N] of d_dtype
   uint32_t* tile_flags[kCommMaxRanks] = {}; // tile_flags[r] on rank r: [world][M/world/128] counters
   void* out = nullptr;                      // local result [M/world, N], dtype d_dtype
+
+  // ---- all-reduce (reduce-scatter fields above, `out` unused)
+  uint8_t* out_all[kCommMaxRanks] = {};     // out_all[r]: the [M, N] result buffer of rank r (symmetric memory)
+  uint32_t* ar_flags[kCommMaxRanks] = {};   // ar_flags[r] on rank r: [world] counters of CTAs whose rows have landed
 
   SideGather side;  // needs `ready` (both modes) and copy_ctas >= 1
 };

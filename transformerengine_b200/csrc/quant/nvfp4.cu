@@ -82,10 +82,8 @@ __device__ __forceinline__ uint8_t block_scale(float vec_max, float s_enc, float
 
 // Two values -> one byte of E2M1 codes (lo in bits 0-3, hi in bits 4-7) with the conversion instruction of
 // sm_100a: round to nearest even onto {0, 0.5, 1, 1.5, 2, 3, 4, 6}, saturating at +-6 (ties: 0.25 -> 0,
-// 0.75 -> 1, 1.25 -> 1, 1.75 -> 2, 2.5 -> 2, 3.5 -> 4, 5 -> 4).  A zero input yields code 0 whatever its sign.
+// 0.75 -> 1, 1.25 -> 1, 1.75 -> 2, 2.5 -> 2, 3.5 -> 4, 5 -> 4).
 __device__ __forceinline__ uint32_t e2m1x2_rn(float lo, float hi) {
-  if ((__float_as_uint(lo) << 1) == 0u) lo = 0.f;
-  if ((__float_as_uint(hi) << 1) == 0u) hi = 0.f;
   uint32_t out;
   asm("{\n"
       ".reg .b8 t;\n"
@@ -97,14 +95,15 @@ __device__ __forceinline__ uint32_t e2m1x2_rn(float lo, float hi) {
   return out;
 }
 
-// 16 scaled values -> 8 bytes of codes, round to nearest
+// 16 scaled values -> 8 bytes of codes, round to nearest.  v * enc + (+0) is the product itself, except that a
+// negative zero becomes +0 (so a zero always gets code 0); the conversion saturates, no clamp is needed.
 __device__ __forceinline__ void pack16_rn(const float (&v)[16], float enc, uint32_t (&w)[2]) {
   w[0] = 0u;
   w[1] = 0u;
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
-    const float a = fminf(fmaxf(__fmul_rn(v[i], enc), -6.f), 6.f);
-    const float b = fminf(fmaxf(__fmul_rn(v[i + 1], enc), -6.f), 6.f);
+    const float a = __fmaf_rn(v[i], enc, 0.f);
+    const float b = __fmaf_rn(v[i + 1], enc, 0.f);
     w[i >> 3] |= e2m1x2_rn(a, b) << ((i & 7) * 4);
   }
 }
@@ -133,25 +132,45 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {
 }
 
 // ------------------------------------------------------------------------------------- amax
+// thread = (pair of adjacent columns, 16-row group): 4-byte loads for the 16-bit types, coalesced along the columns
+template <typename T>
+__device__ __forceinline__ void amax_load2(const T* p, float& a, float& b) {
+  a = to_f(p[0]);
+  b = to_f(p[1]);
+}
+template <>
+__device__ __forceinline__ void amax_load2<__nv_bfloat16>(const __nv_bfloat16* p, float& a, float& b) {
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(p);  // C is even and the base 4-byte aligned: checked at launch
+  a = __uint_as_float(w << 16);
+  b = __uint_as_float(w & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void amax_load2<__half>(const __half* p, float& a, float& b) {
+  const __half2 h = *reinterpret_cast<const __half2*>(p);
+  a = __low2float(h);
+  b = __high2float(h);
+}
+
 template <typename T>
 __global__ void nvfp4_amax_kernel(const T* __restrict__ x, int R, int C, int with_rht, float* out2) {
   float m0 = 0.f, m1 = 0.f;
-  // thread = (column, 16-row group): coalesced along columns
-  const long long groups = static_cast<long long>(R / 16) * C;
+  const int cp = C / 2;
+  const long long groups = static_cast<long long>(R / 16) * cp;
   for (long long g = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups;
        g += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int c = static_cast<int>(g % C);
-    const int r0 = static_cast<int>(g / C) * 16;
-    float v[16];
+    const int c = static_cast<int>(g % cp) * 2;
+    const int r0 = static_cast<int>(g / cp) * 16;
+    float va[16], vb[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-      v[i] = to_f(x[static_cast<size_t>(r0 + i) * C + c]);
-      m0 = fmaxf(m0, fabsf(v[i]));
+      amax_load2<T>(x + static_cast<size_t>(r0 + i) * C + c, va[i], vb[i]);
+      m0 = fmaxf(m0, fmaxf(fabsf(va[i]), fabsf(vb[i])));
     }
     if (with_rht) {
-      rht16(v);
+      rht16(va);
+      rht16(vb);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) m1 = fmaxf(m1, fabsf(v[i]));
+      for (int i = 0; i < 16; ++i) m1 = fmaxf(m1, fmaxf(fabsf(va[i]), fabsf(vb[i])));
     }
   }
 #pragma unroll
@@ -479,10 +498,10 @@ cudaError_t quantize_nvfp4(const Nvfp4Args& a, cudaStream_t s) {
 }
 
 cudaError_t nvfp4_amax(const void* x, int dtype, int R, int C, int with_rht, float* out2, cudaStream_t s) {
-  if (R % 16 != 0) return cudaErrorInvalidValue;
+  if (R % 16 != 0 || C % 2 != 0 || (reinterpret_cast<uintptr_t>(x) & 3) != 0) return cudaErrorInvalidValue;
   cudaError_t e = cudaMemsetAsync(out2, 0, 2 * sizeof(float), s);
   if (e != cudaSuccess) return e;
-  const long long groups = static_cast<long long>(R / 16) * C;
+  const long long groups = static_cast<long long>(R / 16) * (C / 2);
   if (groups == 0) return cudaSuccess;
   const int grid = static_cast<int>(groups / 256 + 1 < 148 * 8 ? groups / 256 + 1 : 148 * 8);
   switch (dtype) {

@@ -163,6 +163,21 @@ def fused_gemm_reduce_scatter(a_op, b_op, bias, cfg: LinearConfig, out_dtype, ta
     return out, pack[3](gd, gsf)
 
 
+def fused_gemm_all_reduce(a_op, b_op, bias, cfg: LinearConfig, out_dtype):
+    """``all_reduce(a @ b^T)`` in one kernel (row-parallel layer without sequence parallelism); None when not covered.
+    The result is copied out of the kernel's double-buffered symmetric buffer, so it may be kept."""
+    from ..parallel import comm_gemm
+
+    if not (cfg.tp_size > 1 and not cfg.sequence_parallel and comm_gemm.enabled_for(cfg.tp_group)):
+        return None
+    if a_op.rows % (128 * cfg.tp_size) != 0 or not getattr(a_op.data, "is_cuda", False):
+        return None
+    if _comm_kind(a_op, b_op) is None or out_dtype not in (torch.bfloat16, torch.float16):
+        return None
+    ctx = comm_gemm.get_gemm_all_reduce(f"{cfg.name}.fprop", cfg.tp_group, a_op.rows, b_op.rows, out_dtype)
+    return ctx(a_op, b_op, bias=bias).clone()
+
+
 def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False):
     """``x`` [T, in] (plain or quantized, already gathered), ``w`` [out, in].
     Returns (out2d after the row-parallel collective, pre-gelu aux or None)."""
@@ -173,6 +188,10 @@ def linear_fprop(x, w, bias, cfg: LinearConfig, out_dtype, *, gelu: bool = False
         res = fused_gemm_reduce_scatter(a, b, bias, cfg, out_dtype, "fprop")
         if res is not None:
             return res[0], None
+    if cfg.parallel_mode == "row" and not gelu and not cfg.sequence_parallel and cfg.tp_size > 1:
+        res = fused_gemm_all_reduce(a, b, bias, cfg, out_dtype)
+        if res is not None:
+            return res, None
     if gelu:
         aux = torch.empty(a.rows, b.rows, dtype=out_dtype, device=a.data.device)
         out = gemm_nt(a, b, out_dtype=out_dtype, bias=bias if fuse_bias else None, epilogue=ops.gemm.EPI_GELU, aux=aux)

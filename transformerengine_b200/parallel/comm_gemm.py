@@ -307,6 +307,52 @@ class GemmReduceScatter:
         return out if side is None else (out, sd, ssf)
 
 
+class GemmAllReduce:
+    """Context of one GEMM -> all-reduce site (row-parallel layer without sequence parallelism): every rank ends
+    with the full ``[T, N]`` sum.  The reduce-scatter kernel with a tail that writes this rank's reduced rows into
+    the result buffer of every rank and returns when all ranks' rows have arrived.  The result is a view of a
+    double-buffered symmetric buffer: it stays valid until the second next call on this context.
+    (Reference: the GEMM + all-reduce of ``common/include/transformer_engine/comm_gemm.h:138``.)"""
+
+    def __init__(self, group, T: int, N: int, *, dtype=torch.bfloat16):
+        self.group, self.T, self.N, self.dtype = group, T, N, dtype
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert T % (128 * self.world) == 0 and N % 8 == 0
+        stage_bytes = T * round_up(N, 256) * 2
+        out_bytes = T * N * 2
+        mbl = T // 128 // self.world
+        self.buf = SymmetricBuffer(2 * (stage_bytes + out_bytes + 4 * self.world * mbl + 4 * 64) + 8192, group)
+        self.stage_ptrs, self.flag_ptrs, self.out, self.out_ptrs, self.ar_ptrs = [], [], [], [], []
+        for _ in range(2):
+            _, p = self.buf.carve(stage_bytes)
+            self.stage_ptrs.append(p)
+            _, p = self.buf.carve(4 * self.world * mbl)
+            self.flag_ptrs.append(p)
+            t, p = self.buf.carve(out_bytes)
+            self.out.append(t.view(dtype).reshape(T, N))
+            self.out_ptrs.append(p)
+            _, p = self.buf.carve(4 * 64)
+            self.ar_ptrs.append(p)
+        self.calls = 0
+        self.epoch_dev = [torch.zeros(4, dtype=torch.int32, device=self.buf.tensor.device) for _ in range(2)]
+
+    def __call__(self, x, w, *, bias=None):
+        """``x`` [T, K/tp], ``w`` [N, K/tp] (16-bit or MXFP8 rowwise).  Returns the summed ``[T, N]``."""
+        a_op = x if isinstance(x, Operand) else as_operand(x, "rowwise")
+        b_op = w if isinstance(w, Operand) else as_operand(w, "rowwise")
+        assert a_op.rows == self.T and b_op.rows == self.N
+        self.calls += 1
+        slot = self.calls & 1
+        mx = a_op.kind == "mxfp8"
+        out = self.out[slot]
+        _ext.get().comm_gemm(3, self.rank, self.world, self.epoch_dev[slot], 0,
+                             a_op.data, a_op.scale if mx else None, b_op.data, b_op.scale if mx else None, None, bias,
+                             a_op.fp8_dtype == torch.float8_e5m2, b_op.fp8_dtype == torch.float8_e5m2,
+                             [], [], [], 0, self.stage_ptrs[slot], self.flag_ptrs[slot], out, self.N,
+                             _status(out.device), out_all_ptrs=self.out_ptrs[slot], ar_flag_ptrs=self.ar_ptrs[slot])
+        return out
+
+
 # --------------------------------------------------------------------------- registry (initialize_ub equivalent)
 _CONTEXTS: Dict[tuple, object] = {}
 _ENABLED = {"group": None}
@@ -336,6 +382,14 @@ def get_all_gather_gemm(name: str, group, T: int, K: int, mxfp8: bool, dtype,
     ctx = _CONTEXTS.get(key)
     if ctx is None:
         ctx = _CONTEXTS[key] = AllGatherGemm(group, T, K, mxfp8=mxfp8, dtype=dtype, side=side)
+    return ctx
+
+
+def get_gemm_all_reduce(name: str, group, T: int, N: int, dtype) -> GemmAllReduce:
+    key = ("ar", name, T, N, dtype)
+    ctx = _CONTEXTS.get(key)
+    if ctx is None:
+        ctx = _CONTEXTS[key] = GemmAllReduce(group, T, N, dtype=dtype)
     return ctx
 
 

@@ -47,6 +47,8 @@ def parse():
     ap.add_argument("--profile", default="", help="write a per-kernel device-time table of 2 extra steps (rank 0) here")
     ap.add_argument("--fused-comm", type=int, default=1, help="fuse TP collectives into the GEMM kernels")
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
+    ap.add_argument("--param-remainders", type=int, default=1,
+                    help="keep the fp32 master weights as bf16 parameter + 16-bit remainder (same values, fewer bytes)")
     ap.add_argument("--zero", type=int, default=-1,
                     help="data parallel: shard the optimizer over the ranks (-1: on whenever there is data parallelism)")
     return ap.parse_args()
@@ -167,8 +169,10 @@ def build_case(args, rank, world):
         return args.graph == 1 or (args.graph < 0 and tp > 1)
 
     def adam(params, graph):
+        # fp32 master weights; stored as the bf16 parameter plus its 16-bit remainder (the same fp32 value, 4 bytes
+        # less traffic per parameter and step) unless --param-remainders 0
         return te.FusedAdam(params, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, master_weights=True,
-                            capturable=graph)
+                            capturable=graph, store_param_remainders=bool(args.param_remainders))
 
     if name in ("llama8b", "llama70b-nvfp4"):
         if name == "llama8b":
@@ -235,7 +239,8 @@ def build_case(args, rank, world):
                     config={"model": model_name, "global_batch": dp, "seq_len": seq,
                             "parallelism": f"tp{tp}-sp" if tp > 1 else (f"dp{dp}" if dp > 1 else "single"),
                             "recipe": recipe_name,
-                            "optimizer": "fused-adam fp32 master" + (" sharded over the ranks" if zero is not None else ""),
+                            "optimizer": "fused-adam fp32 master" + (" (bf16 parameter + 16-bit remainder)" if args.param_remainders else "")
+                            + (" sharded over the ranks" if zero is not None else ""),
                             "fused_comm_gemm": bool(tp > 1 and args.fused_comm), "recompute": recompute})
 
     if name == "layer12288":
@@ -317,7 +322,8 @@ def build_case(args, rank, world):
                     flops_per_token=6.0 * active + 6.0 * layers * seq * h, recipe=recipe_name, graph=False,
                     config={"model": "mixtral-8x7b-arch" if layers == 32 else f"mixtral-8x7b-arch-{layers}L",
                             "global_batch": ep, "seq_len": seq, "parallelism": f"ep{ep}" if ep > 1 else "single",
-                            "recipe": recipe_name, "optimizer": "fused-adam fp32 master",
+                            "recipe": recipe_name,
+                            "optimizer": "fused-adam fp32 master" + (" (bf16 parameter + 16-bit remainder)" if args.param_remainders else ""),
                             "fused_ep": os.environ.get("TEB200_FUSED_EP", "1") == "1", "recompute": False})
     raise SystemExit(f"unknown --config {name}")
 

@@ -57,36 +57,21 @@ __global__ void __launch_bounds__(NT) adam_kernel(const __grid_constant__ MultiT
     rbc2 = 1.f / (1.f - powf(b2, st));
   }
   const float lr = a.lr_dev != nullptr ? *a.lr_dev : a.lr;
-  if (rem != nullptr) {
-    // bf16 parameter + 16-bit remainder = the fp32 value, split so that the parameter is the fp32 value
-    // rounded half up: a negative remainder means the high half was incremented
-    if constexpr (sizeof(P) == 2) {
-      uint16_t* pb = reinterpret_cast<uint16_t*>(p);
-      for (int64_t i = start + threadIdx.x; i < end; i += NT) {
-        const int16_t r = rem[i];
-        uint32_t hi = pb[i];
-        if (r < 0) hi -= 1u;
-        float w = __uint_as_float((hi << 16) | static_cast<uint16_t>(r));
-        float gr = ldf(g, i) * gs;
-        float mv = ldf(m, i), vv = ldf(v, i);
-        if (!a.adamw) gr += a.weight_decay * w;
-        mv = b1 * mv + (1.f - b1) * gr;
-        vv = b2 * vv + (1.f - b2) * gr * gr;
-        float upd = (mv * rbc1) / (sqrtf(vv * rbc2) + a.eps);
-        if (a.adamw) upd += a.weight_decay * w;
-        w -= lr * upd;
-        const uint32_t u = __float_as_uint(w);
-        const int16_t nr = static_cast<int16_t>(u & 0xffffu);
-        uint32_t nh = u >> 16;
-        if (nr < 0) nh += 1u;
-        m[i] = static_cast<S>(mv);
-        v[i] = static_cast<S>(vv);
-        rem[i] = nr;
-        pb[i] = static_cast<uint16_t>(nh);
-      }
-    }
-    continue;
-  }
+  // bf16 parameter + 16-bit remainder = the fp32 value, split so that the parameter is the fp32 value rounded
+  // half up: a negative remainder means the high half was incremented
+  auto join = [](uint16_t hi16, int16_t r) {
+    uint32_t hi = hi16;
+    if (r < 0) hi -= 1u;
+    return __uint_as_float((hi << 16) | static_cast<uint16_t>(r));
+  };
+  auto split = [](float w, uint16_t& hi16, int16_t& r) {
+    const uint32_t u = __float_as_uint(w);
+    r = static_cast<int16_t>(u & 0xffffu);
+    uint32_t nh = u >> 16;
+    if (r < 0) nh += 1u;
+    hi16 = static_cast<uint16_t>(nh);
+  };
+  if (rem != nullptr && sizeof(P) != 2) continue;  // remainders belong to 16-bit parameters (checked by the caller)
   // 4 elements per thread per iteration; tensors are 16-byte aligned and chunks are multiples of 4
   for (int64_t i = start + threadIdx.x * 4; i < end; i += NT * 4) {
     float gv[4], pv[4], mv[4], vv[4];
@@ -99,6 +84,11 @@ __global__ void __launch_bounds__(NT) adam_kernel(const __grid_constant__ MultiT
         const V4<float> p4 = *reinterpret_cast<const V4<float>*>(master + i);
 #pragma unroll
         for (int k = 0; k < 4; ++k) pv[k] = p4.v[k];
+      } else if (rem) {
+        const V4<uint16_t> h4 = *reinterpret_cast<const V4<uint16_t>*>(reinterpret_cast<const uint16_t*>(p) + i);
+        const V4<int16_t> r4 = *reinterpret_cast<const V4<int16_t>*>(rem + i);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) pv[k] = join(h4.v[k], r4.v[k]);
       } else {
         const V4<P> p4 = *reinterpret_cast<const V4<P>*>(p + i);
 #pragma unroll
@@ -115,7 +105,8 @@ __global__ void __launch_bounds__(NT) adam_kernel(const __grid_constant__ MultiT
       for (int k = 0; k < 4; ++k) {
         if (k < cnt) {
           gv[k] = ldf(g, i + k) * gs;
-          pv[k] = master ? master[i + k] : ldf(p, i + k);
+          pv[k] = master ? master[i + k]
+                         : (rem ? join(reinterpret_cast<const uint16_t*>(p)[i + k], rem[i + k]) : ldf(p, i + k));
           mv[k] = ldf(m, i + k);
           vv[k] = ldf(v, i + k);
         }
@@ -148,7 +139,16 @@ __global__ void __launch_bounds__(NT) adam_kernel(const __grid_constant__ MultiT
       *reinterpret_cast<V4<S>*>(m + i) = m4;
       *reinterpret_cast<V4<S>*>(v + i) = v4;
       if (master) *reinterpret_cast<V4<float>*>(master + i) = w4;
-      *reinterpret_cast<V4<P>*>(p + i) = p4;
+      if (rem) {
+        V4<uint16_t> h4;
+        V4<int16_t> r4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) split(pv[k], h4.v[k], r4.v[k]);
+        *reinterpret_cast<V4<int16_t>*>(rem + i) = r4;
+        *reinterpret_cast<V4<uint16_t>*>(reinterpret_cast<uint16_t*>(p) + i) = h4;
+      } else {
+        *reinterpret_cast<V4<P>*>(p + i) = p4;
+      }
     } else {
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -156,7 +156,15 @@ __global__ void __launch_bounds__(NT) adam_kernel(const __grid_constant__ MultiT
           m[i + k] = static_cast<S>(mv[k]);
           v[i + k] = static_cast<S>(vv[k]);
           if (master) master[i + k] = pv[k];
-          p[i + k] = static_cast<P>(pv[k]);
+          if (rem) {
+            uint16_t h;
+            int16_t r;
+            split(pv[k], h, r);
+            rem[i + k] = r;
+            reinterpret_cast<uint16_t*>(p)[i + k] = h;
+          } else {
+            p[i + k] = static_cast<P>(pv[k]);
+          }
         }
       }
     }

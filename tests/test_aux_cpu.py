@@ -2,6 +2,8 @@
 export mode, utilities."""
 import os
 
+import pytest
+
 import torch
 
 import transformerengine_b200 as te
@@ -461,3 +463,62 @@ def test_helper_ops_cpu_paths():
     p = ops.pad_last_dim(rows, 12)
     assert p.shape == (10, 12) and torch.equal(p[:, :8], rows) and p[:, 8:].abs().sum() == 0
     assert torch.equal(ops.pad_last_dim(p, 8), rows)
+
+
+@pytest.mark.parametrize("opts", [dict(retain_pinned_cpu_buffers=True), dict(double_buffering=True),
+                                  dict(manual_synchronization=True)])
+def test_cpu_offload_options(opts):
+    """Every option of the offload context changes behaviour, none changes the gradients; two iterations."""
+    torch.manual_seed(0)
+    layers = [torch.nn.Linear(512, 512) for _ in range(3)]
+    res = get_cpu_offload_context(enabled=True, num_layers=2, model_layers=3, **opts)
+    ctx, sync = res[0], res[1]
+    manual = res[2] if len(res) > 2 else None
+    assert (manual is not None) == bool(opts.get("manual_synchronization"))
+    for _ in range(2):
+        x = torch.randn(256, 512, requires_grad=True)
+        h = x
+        for i, l in enumerate(layers):
+            with ctx:
+                h = torch.tanh(l(h))
+            h = sync(h)
+            if manual is not None:
+                manual.start_offload_layer(i)
+                manual.release_activation_forward_gpu_memory(i)
+        if manual is not None:
+            manual.start_reload_layer(1)
+        h.sum().backward()
+        ref = x.detach().clone().requires_grad_()
+        hr = ref
+        for l in layers:
+            hr = torch.tanh(l(hr))
+        hr.sum().backward()
+        assert torch.allclose(x.grad, ref.grad, atol=1e-6)
+        assert not ctx.handler.store            # everything saved has been handed back
+    assert ctx.handler.iteration == 2
+
+
+def test_cpu_offload_two_forward_passes_in_flight():
+    """Entries are keyed by forward pass: a second forward before the first backward does not mix them up."""
+    torch.manual_seed(1)
+    layers = [torch.nn.Linear(512, 512) for _ in range(2)]
+    ctx, sync = get_cpu_offload_context(enabled=True, num_layers=2, model_layers=2)
+    outs, xs = [], []
+    for _ in range(2):
+        x = torch.randn(256, 512, requires_grad=True)
+        h = x
+        for l in layers:
+            with ctx:
+                h = torch.tanh(l(h))
+            h = sync(h)
+        outs.append(h)
+        xs.append(x)
+    for h, x in zip(outs, xs):
+        h.sum().backward()
+        ref = x.detach().clone().requires_grad_()
+        hr = ref
+        for l in layers:
+            hr = torch.tanh(l(hr))
+        hr.sum().backward()
+        assert torch.allclose(x.grad, ref.grad, atol=1e-6)
+    assert not ctx.handler.store

@@ -34,6 +34,48 @@ def test_cpu_offload_on_gpu():
     assert torch.equal(g0, g1)
 
 
+@pytest.mark.parametrize("opts", [dict(retain_pinned_cpu_buffers=True), dict(double_buffering=True),
+                                  dict(manual_synchronization=True),
+                                  dict(retain_pinned_cpu_buffers=True, double_buffering=True)])
+def test_cpu_offload_options_on_gpu(opts):
+    """Pinned-buffer pool, double-buffered reloads and manual control of the copies: same gradients as without
+    offloading over three iterations; the pool stops allocating after the first iteration."""
+    import transformerengine_b200 as te
+
+    torch.manual_seed(3)
+    layers = [te.Linear(512, 512, bias=False, params_dtype=torch.bfloat16, device="cuda") for _ in range(4)]
+    res = te.get_cpu_offload_context(enabled=True, num_layers=3, model_layers=4, **opts)
+    ctx, sync = res[0], res[1]
+    manual = res[2] if len(res) > 2 else None
+    allocs = []
+    for it in range(3):
+        x = torch.randn(512, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        h = x
+        for i, l in enumerate(layers):
+            with ctx:
+                h = torch.tanh(l(h))
+            h = sync(h)
+            if manual is not None:
+                manual.start_offload_layer(i)
+                manual.release_activation_forward_gpu_memory(i)
+        if manual is not None:
+            manual.start_reload_layer(2)
+        h.float().sum().backward()
+        ref = x.detach().clone().requires_grad_()
+        hr = ref
+        for l in layers:
+            hr = torch.tanh(l(hr))
+        hr.float().sum().backward()
+        torch.cuda.synchronize()
+        assert torch.equal(x.grad, ref.grad), (opts, it)
+        assert not ctx.handler.store
+        allocs.append(ctx.handler.host_allocations)
+    if opts.get("retain_pinned_cpu_buffers"):
+        assert allocs[1] == allocs[0] and allocs[2] == allocs[0]
+    else:
+        assert allocs[2] > allocs[0]
+
+
 def test_kv_cache_decoding_with_attention_kernels():
     import transformerengine_b200 as te
 

@@ -363,3 +363,45 @@ def test_checkpoint_is_consistent_under_delayed_scaling(use_reentrant):
     for plain, ckpt in zip(run(False), run(True)):
         for a, b in zip(plain, ckpt):
             assert torch.equal(a, b)
+
+
+def test_unimplemented_options_are_refused_not_ignored():
+    import transformerengine_b200 as te
+
+    with pytest.raises(NotImplementedError):
+        te.GroupedLinear(2, 16, 16, delay_wgrad_compute=True, device="cpu")
+    with pytest.raises(NotImplementedError):
+        te.LayerNormLinear(16, 16, return_layernorm_output_gathered=True, device="cpu")
+    with pytest.raises(NotImplementedError):
+        te.LayerNormMLP(16, 32, activation_params={"limit": 7.0}, device="cpu")
+    with pytest.raises(NotImplementedError):
+        te.DotProductAttention(2, 16, return_max_logit=True)
+    lin = te.Linear(16, 16, device="cpu", params_dtype=torch.float32)
+    with pytest.raises(NotImplementedError):
+        lin(torch.randn(4, 16), fp8_output=True)
+    opt = te.FusedAdam(lin.parameters(), lr=1e-3)
+    with pytest.raises(NotImplementedError):
+        opt.step(grad_scaler=object())
+
+
+def test_transformer_layer_passes_rotary_interleaving_to_attention():
+    import transformerengine_b200 as te
+
+    torch.manual_seed(0)
+    kw = dict(hidden_size=64, ffn_hidden_size=128, num_attention_heads=4, hidden_dropout=0.0, attention_dropout=0.0,
+              params_dtype=torch.float32, device="cpu", fuse_qkv_params=True)
+    a = te.TransformerLayer(**kw, rotary_pos_interleaved=False)
+    b = te.TransformerLayer(**kw, rotary_pos_interleaved=True)
+    b.load_state_dict(a.state_dict())
+    assert b.self_attention.rotary_pos_interleaved and not a.self_attention.rotary_pos_interleaved
+    x = torch.randn(8, 2, 64)
+    freqs = te.RotaryPositionEmbedding(16)(8)
+    ya, yb = a(x, rotary_pos_emb=freqs), b(x, rotary_pos_emb=freqs)
+    assert not torch.allclose(ya, yb)          # the two pairings of channels rotate differently
+    # the interleaved layer equals rotating with pairs (2i, 2i + 1): check through the functional form
+    from transformerengine_b200.attention.rope import apply_rotary_pos_emb
+
+    q = torch.randn(8, 2, 4, 16)
+    r1 = apply_rotary_pos_emb(q, freqs, "sbhd", interleaved=True)
+    r2 = apply_rotary_pos_emb(q, freqs, "sbhd", interleaved=True, fused=False)
+    torch.testing.assert_close(r1, r2)

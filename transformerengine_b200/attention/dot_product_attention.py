@@ -41,6 +41,8 @@ class DotProductAttention(torch.nn.Module):
                  softmax_scale: Optional[float] = None, softmax_type: str = "vanilla",
                  return_max_logit: bool = False) -> None:
         super().__init__()
+        if return_max_logit:
+            raise NotImplementedError("return_max_logit: the attention kernels do not export the maximum logit")
         assert attn_mask_type in _MASK_TYPES, f"unknown attn_mask_type {attn_mask_type}"
         assert qkv_format in ("sbhd", "bshd", "thd")
         self.qkv_format = qkv_format
@@ -98,6 +100,12 @@ class DotProductAttention(torch.nn.Module):
         fmt = qkv_format or self.qkv_format
         mask_type = attn_mask_type or self.attn_mask_type
         window = window_size if window_size is not None else self.window_size
+        # fast_zero_fill is a hint for a zero-filling strategy of padded outputs that these kernels do not need
+        # (they write every row of the output); pad_between_seqs is implied by passing padded cumulative lengths
+        if pad_between_seqs and fmt == "thd" and cu_seqlens_q_padded is None:
+            raise ValueError("pad_between_seqs=True needs cu_seqlens_q_padded / cu_seqlens_kv_padded")
+        if (score_mod_bprop is not None or score_mod_bprop_tensors is not None) and score_mod is None:
+            raise ValueError("score_mod_bprop without score_mod")
         if inference_params is not None:
             query_layer, key_layer, value_layer, fmt, mask_type, cu_seqlens_q, cu_seqlens_kv = \
                 inference_params.step(self.layer_number, query_layer, key_layer, value_layer, fmt, mask_type)

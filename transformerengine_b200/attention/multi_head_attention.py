@@ -38,8 +38,10 @@ class MultiheadAttention(torch.nn.Module):
                  normalization: str = "LayerNorm", device: Union[torch.device, str] = None,
                  qkv_format: str = "sbhd", name: Optional[str] = None, qk_norm_type: Optional[str] = None,
                  qk_norm_eps: float = 1e-6, qk_norm_before_rope: bool = False, seq_length: Optional[int] = None,
-                 micro_batch_size: Optional[int] = None, softmax_type: str = "vanilla") -> None:
+                 micro_batch_size: Optional[int] = None, softmax_type: str = "vanilla",
+                 rotary_pos_interleaved: bool = False) -> None:
         super().__init__()
+        self.rotary_pos_interleaved = rotary_pos_interleaved
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.qkv_format = qkv_format
@@ -164,6 +166,7 @@ class MultiheadAttention(torch.nn.Module):
                 cp_size = D.get_world_size(cpg) if cpg is not None else 1
                 mixed = rotate_packed_qkv_(mixed, q_emb, k_emb, self.qkv_format,
                                            "grouped" if self.qkv_weight_interleaved else "blocked", hq, hk, d,
+                                           interleaved=self.rotary_pos_interleaved,
                                            cp_size=cp_size, cp_rank=D.get_rank(cpg) if cp_size > 1 else 0)
                 rope_done = True
             if self.qkv_weight_interleaved:
@@ -200,19 +203,23 @@ class MultiheadAttention(torch.nn.Module):
                 sdim = 0 if fmt == "sbhd" else 1
                 cp_size = D.get_world_size(self.core_attention.cp_group) if self.core_attention.cp_group is not None else 1
                 cp_rank = D.get_rank(self.core_attention.cp_group) if cp_size > 1 else 0
-                q = apply_rotary_pos_emb(q, q_emb, fmt, cp_size=cp_size, cp_rank=cp_rank)
-                k = apply_rotary_pos_emb(k, k_emb, fmt, cp_size=cp_size, cp_rank=cp_rank)
+                il = self.rotary_pos_interleaved
+                q = apply_rotary_pos_emb(q, q_emb, fmt, cp_size=cp_size, cp_rank=cp_rank, interleaved=il)
+                k = apply_rotary_pos_emb(k, k_emb, fmt, cp_size=cp_size, cp_rank=cp_rank, interleaved=il)
             elif inference_params is not None:
                 start = inference_params.sequence_start_positions(q.shape[1 if fmt == "sbhd" else 0], q.device)
-                q = apply_rotary_pos_emb(q, q_emb, fmt, start_positions=start)
-                k = apply_rotary_pos_emb(k, k_emb, fmt, start_positions=start)
+                q = apply_rotary_pos_emb(q, q_emb, fmt, start_positions=start, interleaved=self.rotary_pos_interleaved)
+                k = apply_rotary_pos_emb(k, k_emb, fmt, start_positions=start, interleaved=self.rotary_pos_interleaved)
             else:
-                q = apply_rotary_pos_emb(q, q_emb, "thd", cu_seqlens=cu_seqlens_q)
-                k = apply_rotary_pos_emb(k, k_emb, "thd", cu_seqlens=cu_seqlens_kv if cu_seqlens_kv is not None else cu_seqlens_q)
+                q = apply_rotary_pos_emb(q, q_emb, "thd", cu_seqlens=cu_seqlens_q, interleaved=self.rotary_pos_interleaved)
+                k = apply_rotary_pos_emb(k, k_emb, "thd", cu_seqlens=cu_seqlens_kv if cu_seqlens_kv is not None else cu_seqlens_q,
+                                         interleaved=self.rotary_pos_interleaved)
         if self.qk_norm_type is not None and not self.qk_norm_before_rope:
             q, k = self._qk_norm(q, self.q_norm), self._qk_norm(k, self.k_norm)
         ctx = self.core_attention(q, k, v, attention_mask=attention_mask, qkv_format=self.qkv_format,
                                   cu_seqlens_q=cu_seqlens_q, cu_seqlens_kv=cu_seqlens_kv,
+                                  cu_seqlens_q_padded=cu_seqlens_q_padded, cu_seqlens_kv_padded=cu_seqlens_kv_padded,
+                                  pad_between_seqs=pad_between_seqs, fast_zero_fill=fast_zero_fill,
                                   max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv,
                                   attn_mask_type=attn_mask_type, window_size=window_size,
                                   checkpoint_core_attention=checkpoint_core_attention,

@@ -62,7 +62,13 @@ def apply_rotary_pos_emb(t: torch.Tensor, freqs: torch.Tensor, tensor_format: st
                          start_positions: Optional[torch.Tensor] = None, interleaved: bool = False,
                          fused: bool = True, cu_seqlens: Optional[torch.Tensor] = None, cp_size: int = 1,
                          cp_rank: int = 0) -> torch.Tensor:
-    """Rotate the first ``freqs.shape[-1]`` channels of ``t`` (``sbhd``, ``bshd`` or ``thd``)."""
+    """Rotate the first ``freqs.shape[-1]`` channels of ``t`` (``sbhd``, ``bshd`` or ``thd``).  ``fused=False``
+    selects the plain PyTorch formula (differentiated by autograd) instead of the kernel."""
+    if not fused and tensor_format in ("sbhd", "bshd") and cp_size == 1:
+        x = t if tensor_format == "sbhd" else t.transpose(0, 1)
+        f = freqs.reshape(freqs.shape[0], freqs.shape[-1])
+        y = ops.misc.rope_ref(x, f.float(), f.shape[-1], interleaved, False, 0, 1, 0, start_positions)
+        return y if tensor_format == "sbhd" else y.transpose(0, 1)
     if tensor_format == "thd":
         assert cu_seqlens is not None, "thd format needs cu_seqlens"
         outs = []

@@ -213,6 +213,13 @@ class GroupedLinear(TransformerEngineBaseModule):
                  save_original_input: bool = False, single_grouped_weight: bool = False,
                  single_grouped_bias: bool = False, name: Optional[str] = None) -> None:
         super().__init__()
+        # options of the reference that this module does not implement are refused, not ignored
+        for opt, val in (("delay_wgrad_compute", delay_wgrad_compute), ("save_original_input", save_original_input),
+                         ("single_grouped_weight", single_grouped_weight), ("single_grouped_bias", single_grouped_bias)):
+            if val:
+                raise NotImplementedError(f"GroupedLinear({opt}=True) is not implemented")
+        if ub_overlap_rs or ub_overlap_ag:
+            raise NotImplementedError("GroupedLinear has no fused collective path (ub_overlap_*)")
         params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"

@@ -195,6 +195,11 @@ class LayerNormLinear(TransformerEngineBaseModule):
                  ub_bulk_dgrad: bool = False, ub_name: Optional[str] = None, delay_wgrad_compute: bool = False,
                  symmetric_ar_type: Optional[str] = None, name: Optional[str] = None) -> None:
         super().__init__()
+        if return_layernorm_output_gathered:
+            raise NotImplementedError("return_layernorm_output_gathered is not implemented: the normalized output is "
+                                      "returned as this rank's rows")
+        if symmetric_ar_type is not None:
+            raise NotImplementedError("symmetric_ar_type: use te.initialize_ub (fused GEMM + collective kernels) instead")
         params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
@@ -294,6 +299,9 @@ class LayerNormLinear(TransformerEngineBaseModule):
 
     def forward(self, inp: torch.Tensor, is_first_microbatch: Optional[bool] = None, fp8_output: bool = False,
                 fp8_grad: bool = False):
+        if fp8_output or fp8_grad:
+            raise NotImplementedError("fp8_output / fp8_grad: quantized layer outputs and input gradients are not "
+                                      "implemented; the next layer quantizes its own input")
         self.prepare_forward(num_gemms=1)
         self.cfg.activation_dtype = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else inp.dtype
         weight, bias = self._get_weight_bias()

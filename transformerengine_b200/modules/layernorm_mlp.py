@@ -157,6 +157,17 @@ class LayerNormMLP(TransformerEngineBaseModule):
                  ub_bulk_dgrad: bool = False, ub_bulk_wgrad: bool = False, delay_wgrad_compute: bool = False,
                  symmetric_ar_type: Optional[str] = None, checkpoint: bool = False, name: Optional[str] = None):
         super().__init__()
+        if activation_params:
+            raise NotImplementedError("activation_params (parametrised activations) are not implemented")
+        if return_layernorm_output_gathered:
+            raise NotImplementedError("return_layernorm_output_gathered is not implemented")
+        if symmetric_ar_type is not None:
+            raise NotImplementedError("symmetric_ar_type: use te.initialize_ub (fused GEMM + collective kernels) instead")
+        if checkpoint:
+            import warnings
+
+            warnings.warn("LayerNormMLP(checkpoint=True): selective recompute inside the module is not implemented; "
+                          "wrap the module in te.checkpoint to trade compute for memory", stacklevel=2)
         params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"

@@ -292,6 +292,9 @@ class Linear(TransformerEngineBaseModule):
 
     def forward(self, inp: torch.Tensor, is_first_microbatch: Optional[bool] = None, fp8_output: bool = False,
                 fp8_grad: bool = False):
+        if fp8_output or fp8_grad:
+            raise NotImplementedError("fp8_output / fp8_grad: quantized layer outputs and input gradients are not "
+                                      "implemented; the next layer quantizes its own input")
         if self._ub_requested:
             from ..parallel import comm_gemm
 

@@ -96,6 +96,9 @@ class FusedAdam(torch.optim.Optimizer):
 
     @torch.no_grad()
     def step(self, closure=None, grad_scaler=None):  # type: ignore[override]
+        if grad_scaler is not None:
+            raise NotImplementedError("FusedAdam.step(grad_scaler=...): unscale with torch.amp.GradScaler.unscale_ "
+                                      "before the step, or pass the inverse scale through multi_tensor_adam")
         loss = closure() if closure is not None else None
         for group in self.param_groups:
             if not group["params"]:

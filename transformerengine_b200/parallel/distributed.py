@@ -284,6 +284,9 @@ def checkpoint(function: Callable, *args, distribute_saved_activations: bool = F
                get_rng_state_tracker: Optional[Callable] = None, tp_group=None, use_reentrant: bool = True,
                **kwargs):
     """Recompute ``function`` in the backward pass instead of storing its activations."""
+    if distribute_saved_activations:
+        raise NotImplementedError("distribute_saved_activations: saved inputs are kept whole on every rank "
+                                  "(use sequence parallelism to shard them)")
     if not use_reentrant:
         from torch.utils.checkpoint import checkpoint as torch_ckpt
         from ..quantization import FP8GlobalStateManager

@@ -141,6 +141,9 @@ class NVFP4Quantizer(Quantizer):
                  amax_reduction_group=None, with_rht=False, with_post_rht_amax=True,
                  with_2d_quantization=False, stochastic_rounding=False, with_random_sign_mask=True):
         super().__init__(rowwise=rowwise, columnwise=columnwise)
+        if with_rht and not with_random_sign_mask:
+            raise NotImplementedError("the Hadamard transform always uses the fixed random sign vector "
+                                      "(with_random_sign_mask=False is not implemented)")
         self.dtype = fp4_dtype
         self.with_amax_reduction = with_amax_reduction
         self.amax_reduction_group = amax_reduction_group

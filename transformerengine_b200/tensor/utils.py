@@ -123,7 +123,12 @@ def quantize_master_weights(model_weights: Sequence[torch.Tensor], master_weight
     :func:`post_all_gather_processing`).  The column-wise MXFP8 copy is written in place as well (scattered
     positions of the transposed copy), so it needs the same all-gather.  Other formats (and plain weights)
     assemble the full fp32 tensor with an all-reduce and quantize it on every rank.
+    ``fsdp_shard_model_weights`` / ``manual_post_all_gather_processing`` (FSDP-sharded model weights, deferred
+    post-processing) are not implemented and are refused.
     """
+    if fsdp_shard_model_weights is not None or manual_post_all_gather_processing:
+        raise NotImplementedError("quantize_master_weights: FSDP-sharded model weights and manual post-all-gather "
+                                  "processing are not implemented")
     from .float8 import Float8TensorStorage
     from .mxfp8 import MXFP8TensorStorage
 

@@ -89,7 +89,8 @@ class TransformerLayer(torch.nn.Module):
                            zero_centered_gamma=zero_centered_gamma, qkv_weight_interleaved=qkv_weight_interleaved,
                            bias=bias, normalization=normalization, device=device, qkv_format=attn_input_format,
                            qk_norm_type=qk_norm_type, qk_norm_eps=qk_norm_eps,
-                           qk_norm_before_rope=qk_norm_before_rope, softmax_type=softmax_type)
+                           qk_norm_before_rope=qk_norm_before_rope, softmax_type=softmax_type,
+                           rotary_pos_interleaved=rotary_pos_interleaved)
         self.self_attention = MultiheadAttention(hidden_size, num_attention_heads, **attn_kwargs,
                                                  input_layernorm=not output_layernorm, attention_type="self",
                                                  attn_mask_type=self_attn_mask_type, window_size=window_size,
@@ -151,7 +152,9 @@ class TransformerLayer(torch.nn.Module):
             checkpoint_core_attention=checkpoint_core_attention, rotary_pos_emb=rotary_pos_emb,
             core_attention_bias_type=core_attention_bias_type, core_attention_bias=core_attention_bias,
             alibi_slopes=alibi_slopes, cu_seqlens_q=cu_seqlens_q, cu_seqlens_kv=cu_seqlens_kv,
-            max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv)
+            cu_seqlens_q_padded=cu_seqlens_q_padded, cu_seqlens_kv_padded=cu_seqlens_kv_padded,
+            max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv, fast_zero_fill=fast_zero_fill,
+            pad_between_seqs=pad_between_seqs)
         if self.parallel_attention_mlp:
             mlp_out = self.layernorm_mlp(hidden_states, is_first_microbatch=is_first_microbatch)
             out = hidden_states + torch.nn.functional.dropout(attn_out + mlp_out, p=self.hidden_dropout,

@@ -182,11 +182,25 @@ def moe_unpermute(inp: torch.Tensor, row_id_map: torch.Tensor, merging_probs: Op
     return out
 
 
+def _chunk_sort_rows(n_rows: int, split_sizes: torch.Tensor, sorted_index: torch.Tensor) -> torch.Tensor:
+    """Source row of every output row when the chunks of ``split_sizes`` rows are reordered by ``sorted_index``;
+    computed on the device of ``split_sizes`` without reading the sizes back to the host."""
+    sizes = split_sizes.to(torch.int64)
+    idx = sorted_index.to(torch.int64)
+    start = torch.cumsum(sizes, 0) - sizes                 # first input row of every chunk
+    out_sizes = sizes[idx]
+    out_end = torch.cumsum(out_sizes, 0)                   # one past the last output row of every output chunk
+    rows = torch.arange(n_rows, device=sizes.device)
+    chunk = torch.searchsorted(out_end, rows, right=True).clamp_(max=idx.numel() - 1)
+    return start[idx][chunk] + (rows - (out_end - out_sizes)[chunk])
+
+
 def moe_sort_chunks_by_index(inp: torch.Tensor, split_sizes: torch.Tensor, sorted_index: torch.Tensor) -> torch.Tensor:
     """Split ``inp`` into consecutive chunks of ``split_sizes`` rows and concatenate them in the
-    order given by ``sorted_index`` (expert-parallel token exchange)."""
-    chunks = torch.split(inp, [int(s) for s in split_sizes.tolist()], dim=0)
-    return torch.cat([chunks[int(i)] for i in sorted_index.tolist()], dim=0)
+    order given by ``sorted_index`` (expert-parallel token exchange).  One gather, no host synchronisation:
+    the split sizes stay on the device (they must add up to the number of rows)."""
+    src = _chunk_sort_rows(inp.shape[0], split_sizes.to(inp.device), sorted_index.to(inp.device))
+    return inp.index_select(0, src)
 
 
 def moe_sort_chunks_by_index_with_probs(inp, probs, split_sizes, sorted_index):

@@ -151,3 +151,47 @@ def test_linear_chain_under_mxfp8_autocast():
     rel = lambda a, b: ((a - b).norm() / b.norm()).item()  # noqa: E731
     assert rel(y, h) < 0.05 and rel(xg.grad, xr.grad) < 0.1 and rel(seq[0].weight.grad, ref[0].weight.grad) < 0.1
     assert rel(seq[0].bias.grad, ref[0].bias.grad) < 0.1
+
+
+def test_grouped_mlp_fusion_matches_per_expert_reference():
+    """GroupedLinear, ScaledSwiGLU, GroupedLinear: fused into one stand-in; forward and all gradients equal the
+    per-expert loop in plain torch."""
+    import transformerengine_b200 as te
+    from transformerengine_b200 import fusible as F
+
+    torch.manual_seed(0)
+    G, H, FF = 3, 32, 48
+    splits = [5, 0, 7]
+    seq = F.Sequential(F.GroupedLinear(G, H, 2 * FF, bias=False, device="cpu", dtype=torch.float32),
+                       F.ScaledSwiGLU(),
+                       F.GroupedLinear(G, FF, H, bias=False, device="cpu", dtype=torch.float32))
+    plan = F.fuse_operations(list(seq))
+    assert len(plan) == 1 and plan[0].fusion == "grouped_mlp"
+    x = torch.randn(sum(splits), H, requires_grad=True)
+    probs = torch.rand(sum(splits), requires_grad=True)
+    st = torch.tensor(splits)
+    y = seq(x, st, probs, st)
+    w = torch.randn_like(y)
+    (y * w).sum().backward()
+    # reference
+    xr, pr = x.detach().clone().requires_grad_(), probs.detach().clone().requires_grad_()
+    outs, r0 = [], 0
+    w1 = [getattr(seq[0], f"weight{i}").detach().clone().requires_grad_() for i in range(G)]
+    w2 = [getattr(seq[2], f"weight{i}").detach().clone().requires_grad_() for i in range(G)]
+    for i, m in enumerate(splits):
+        xs = xr[r0:r0 + m]
+        h = xs @ w1[i].t()
+        a, b = h[:, :FF], h[:, FF:]
+        act = torch.nn.functional.silu(a) * b * pr[r0:r0 + m, None]
+        outs.append(act @ w2[i].t())
+        r0 += m
+    yr = torch.cat(outs)
+    torch.testing.assert_close(y, yr, rtol=1e-5, atol=1e-5)
+    (yr * w).sum().backward()
+    torch.testing.assert_close(x.grad, xr.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(probs.grad, pr.grad, rtol=1e-4, atol=1e-5)
+    for i in (0, 2):
+        torch.testing.assert_close(getattr(seq[0], f"weight{i}").grad, w1[i].grad, rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(getattr(seq[2], f"weight{i}").grad, w2[i].grad, rtol=1e-4, atol=1e-5)
+    # the state dict shows the experts' weights under the basic operations
+    assert "0.impl.weight0" in seq.state_dict()

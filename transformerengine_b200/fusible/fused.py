@@ -14,6 +14,10 @@ backward (reference: ``pytorch/ops/fused/forward_linear_bias_activation.py``,
 
 ``ForkNorm`` covers ``MakeExtraOutput, RMSNorm / LayerNorm``: the norm backward kernel adds the
 gradient of the forked branch while it writes dx (no separate add pass).
+
+``GroupedMLP`` covers ``GroupedLinear, ScaledSwiGLU, GroupedLinear`` (an MoE expert MLP, reference
+``pytorch/ops/fused/grouped_mlp.py``): the split sizes are read once for both grouped GEMMs and the scaled
+activation is one kernel forward and one kernel for the input gradient.
 """
 from __future__ import annotations
 
@@ -183,3 +187,26 @@ class ForkNorm(torch.nn.Module):
             w = w.to(x.dtype)
             b = b.to(x.dtype) if b is not None else None
         return _ForkNormFn.apply(x, w, b, n.eps, n.zero_centered_gamma, self.layernorm)
+
+
+class GroupedMLP(torch.nn.Module):
+    """Stand-in for ``GroupedLinear, ScaledSwiGLU, GroupedLinear``: ``forward(x, split_sizes, scales, split_sizes)``
+    (the extra inputs of the three basic operations, in order).  The parameters stay with the basic operations."""
+
+    is_fused_op = True
+
+    def __init__(self, fc1, act, fc2):
+        super().__init__()
+        self._ops = [fc1, act, fc2]
+        self.span, self.num_extra_inputs, self.num_extra_outputs, self.fusion = 3, 3, 0, "grouped_mlp"
+
+    def forward(self, x, splits1, scales, splits2):
+        from .ops import _ScaledGluFn, _splits_list
+
+        fc1, act, fc2 = self._ops
+        m_splits = _splits_list(splits1)                      # one host read for both grouped GEMMs
+        if splits2 is not splits1:
+            assert _splits_list(splits2) == m_splits, "both grouped linears of an expert MLP see the same slabs"
+        h = fc1.impl(x, m_splits)
+        h = _ScaledGluFn.apply(h, scales.reshape(-1), act.act_name)
+        return fc2.impl(h, m_splits)

@@ -221,6 +221,84 @@ class MakeExtraOutput(FusibleOperation):
         return x, x
 
 
+def _splits_list(split_sizes) -> list:
+    """Row counts per group as host ints (the grouped GEMM front end sizes its launches on the host)."""
+    if isinstance(split_sizes, torch.Tensor):
+        return [int(v) for v in split_sizes.tolist()]
+    return [int(v) for v in split_sizes]
+
+
+class GroupedLinear(FusibleOperation):
+    """``y_i = x_i W_i^T + b_i`` over ``num_groups`` consecutive row slabs of the input (MoE experts).  The slab
+    sizes arrive as the extra input ``split_sizes`` (tensor or list of ``num_groups`` ints).  Parameters
+    ``weight{i}`` / ``bias{i}``.  (Reference: ``pytorch/ops/basic/grouped_linear.py:135``.)"""
+
+    num_extra_inputs = 1
+
+    def __init__(self, num_groups: int, in_features: int, out_features: int, *, bias: bool = True, device=None,
+                 dtype=None, accumulate_into_main_grad: bool = False, single_grouped_weight: bool = False,
+                 single_grouped_bias: bool = False, delay_wgrad_compute: bool = False, scale_bias: bool = False):
+        super().__init__()
+        if scale_bias:
+            raise NotImplementedError("GroupedLinear(scale_bias=True) is not implemented")
+        from ..modules.grouped_linear import GroupedLinear as _TEGroupedLinear
+
+        self.num_groups, self.in_features, self.out_features = num_groups, in_features, out_features
+        # the module owns the (stacked) parameters: they appear as impl.weight{i} / impl.bias{i} in the state dict
+        # and as weight{i} / bias{i} attributes of this operation
+        self.impl = _TEGroupedLinear(num_groups, in_features, out_features, bias=bias, params_dtype=dtype, device=device,
+                                     fuse_wgrad_accumulation=accumulate_into_main_grad,
+                                     single_grouped_weight=single_grouped_weight,
+                                     single_grouped_bias=single_grouped_bias, delay_wgrad_compute=delay_wgrad_compute)
+
+    def __getattr__(self, name):
+        if name != "impl" and (name.startswith("weight") or name.startswith("bias")) and "impl" in self._modules:
+            return getattr(self._modules["impl"], name)
+        return super().__getattr__(name)
+
+    def forward(self, x, split_sizes):
+        return self.impl(x, _splits_list(split_sizes))
+
+
+class _ScaledGluFn(torch.autograd.Function):
+    """Gated activation with every output row multiplied by its scale: one kernel forward, one kernel for the
+    input gradient (both take the row scale as a prologue), a row dot product for the scale gradient."""
+
+    @staticmethod
+    def forward(ctx, x, scales, act):  # type: ignore[override]
+        y, _ = K.activation_fwd(x, act, row_scale=scales)
+        ctx.save_for_backward(x, scales)
+        ctx.act = act
+        return y.to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):  # type: ignore[override]
+        x, scales = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx, _, _ = K.activation_bwd(dy, x, ctx.act, row_scale=scales)
+        dscales = None
+        if ctx.needs_input_grad[1]:
+            unscaled, _ = K.activation_fwd(x, ctx.act)
+            dscales = (dy * unscaled.to(dy.dtype)).sum(-1, dtype=torch.float32).to(scales.dtype).reshape(scales.shape)
+        return dx.to(x.dtype), dscales, None
+
+
+class ScaledSwiGLU(FusibleOperation):
+    """``y = swiglu(x) * scales[:, None]``: the middle operation of an MoE expert MLP, where ``scales`` (extra
+    input, one value per row) are the routing probabilities.  (Reference: ``pytorch/ops/basic/swiglu.py:598``.)"""
+
+    num_extra_inputs = 1
+    act_name = "swiglu"
+
+    def __init__(self, glu_interleave_size: Optional[int] = None):
+        super().__init__()
+        if glu_interleave_size is not None:
+            raise NotImplementedError("interleaved gate / linear halves (glu_interleave_size) are not implemented")
+
+    def forward(self, x, scales):
+        return _ScaledGluFn.apply(x, scales.reshape(-1), self.act_name)
+
+
 class _CollFn(torch.autograd.Function):
     """Collective on dim 0 whose backward is the adjoint collective."""
 

@@ -7,7 +7,7 @@ from typing import Callable, List, Optional, Tuple
 import torch
 
 from . import ops as O
-from .fused import ForkNorm, LinearChain
+from .fused import ForkNorm, GroupedMLP, LinearChain
 from ..modules.layernorm_linear import LayerNormLinear
 from ..modules.layernorm_mlp import LayerNormMLP
 
@@ -85,6 +85,12 @@ def fuse_operations(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
                 and w[1].out_features == w[3].in_features * (2 if w[2].act_name in ("swiglu", "geglu", "reglu") else 1)):
             out.append(_Fused(_fuse_norm_mlp(*w), 4, name="norm_mlp"))
             i += 4
+            continue
+        if (len(w) >= 3 and isinstance(w[0], O.GroupedLinear) and isinstance(w[1], O.ScaledSwiGLU)
+                and isinstance(w[2], O.GroupedLinear) and w[0].num_groups == w[2].num_groups
+                and w[0].out_features == 2 * w[2].in_features):
+            out.append(GroupedMLP(w[0], w[1], w[2]))
+            i += 3
             continue
         if len(w) >= 2 and _norm_kind(w[0]) and _is_linear(w[1]):
             out.append(_Fused(_fuse_norm_linear(w[0], w[1]), 2, name="norm_linear"))

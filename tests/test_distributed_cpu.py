@@ -99,3 +99,72 @@ def test_tp2_sequence_parallel_matches_unsharded(use_fp8):
         p.join(timeout=60)
     for rank, bad in res:
         assert not bad, f"rank {rank}: {bad}"
+
+
+def _gather_worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        from transformerengine_b200.parallel import distributed as D
+        from transformerengine_b200.tensor import MXFP8Quantizer
+        from transformerengine_b200.tensor.blockwise import Float8BlockQuantizer
+        from transformerengine_b200.tensor.float8 import Float8Quantizer
+        from transformerengine_b200.tensor.nvfp4 import NVFP4Quantizer
+
+        torch.manual_seed(100 + rank)
+        R, C = 128, 256
+        x = torch.randn(R, C)
+        full = torch.empty(world * R, C)
+        dist.all_gather_into_tensor(full, x)
+        bad = {}
+
+        def check(name, qt, atol):
+            g = D.gather_quantized_along_first_dim(qt, None)
+            # the gathered tensor dequantizes to the gathered dequantized pieces, through either copy
+            want = torch.empty(world * R, C)
+            dist.all_gather_into_tensor(want, qt.dequantize(dtype=torch.float32).contiguous())
+            got = g.dequantize(dtype=torch.float32)
+            if got.shape != want.shape or (got - want).abs().max() > atol:
+                bad[name + " rowwise"] = float((got - want).abs().max())
+            g.update_usage(rowwise_usage=False)
+            got_c = g.dequantize(dtype=torch.float32)
+            ref_c = qt
+            ref_c.update_usage(rowwise_usage=False)
+            want_c = torch.empty(world * R, C)
+            dist.all_gather_into_tensor(want_c, ref_c.dequantize(dtype=torch.float32).contiguous())
+            if (got_c - want_c).abs().max() > atol:
+                bad[name + " columnwise"] = float((got_c - want_c).abs().max())
+
+        # per-tensor FP8: the same scale everywhere (as after an amax reduction over the group)
+        amax = full.abs().max().reshape(1)
+        scale = (448.0 / amax).float()
+        fq = Float8Quantizer(scale, torch.zeros(1), torch.float8_e4m3fn, rowwise=True, columnwise=True)
+        check("float8", fq(x), 0.0)
+        check("mxfp8", MXFP8Quantizer(rowwise=True, columnwise=True)(x), 0.0)
+        for dim in (1, 2):
+            check(f"block{dim}d", Float8BlockQuantizer(rowwise=True, columnwise=True, block_scaling_dim=dim)(x), 0.0)
+        nq = NVFP4Quantizer(rowwise=True, columnwise=True, with_amax_reduction=True, amax_reduction_group=dist.group.WORLD)
+        check("nvfp4", nq(x), 0.0)
+        q.put((rank, bad, None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        q.put((rank, {}, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_quantized_tensors_are_gathered_without_dequantizing():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gather_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, bad, tb in res:
+        assert tb is None, tb
+        assert not bad, f"rank {rank}: {bad}"

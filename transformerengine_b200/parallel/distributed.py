@@ -115,6 +115,104 @@ def gather_mxfp8_along_first_dim(q, group):
                               fp8_dtype=q._fp8_dtype, quantizer=q._quantizer, shape=shape, dtype=q._dtype)
 
 
+def _gather_cols(t2d: torch.Tensor, group) -> torch.Tensor:
+    """All-gather ``[A, B]`` pieces into ``[A, world * B]`` (piece r at columns ``[r * B, (r + 1) * B)``)."""
+    ws = get_world_size(group)
+    g, _ = gather_along_first_dim(t2d.reshape(1, *t2d.shape), group)     # [ws, A, B]
+    return g.permute(1, 0, 2).reshape(t2d.shape[0], ws * t2d.shape[1]).contiguous()
+
+
+def gather_float8_along_first_dim(q, group):
+    """All-gather a per-tensor-scaled FP8 tensor sharded on its rows: one byte per value crosses the wire.
+    Every rank must have quantized with the SAME scale (delayed scaling with the amax reduced over a group that
+    contains ``group``, or current scaling with the amax reduced over ``group``)."""
+    from ..tensor.float8 import Float8TensorStorage
+
+    ws = get_world_size(group)
+    if ws == 1:
+        return q
+    R, C = q._rows_cols()
+    data = tr = None
+    if q._data is not None:
+        data, _ = gather_along_first_dim(q._data.reshape(R, C).view(torch.uint8), group)
+        data = data.view(q._data.dtype)
+    if q._transpose is not None:
+        tr = _gather_cols(q._transpose.reshape(C, R).view(torch.uint8), group).view(q._transpose.dtype)
+    return Float8TensorStorage(data=data, fp8_scale_inv=q._scale_inv, fp8_dtype=q._fp8_dtype, data_transpose=tr,
+                               quantizer=q._quantizer, shape=(R * ws, C), dtype=q._dtype)
+
+
+def gather_nvfp4_along_first_dim(q, group):
+    """All-gather an NVFP4 tensor sharded on its rows without dequantizing (half a byte per value plus one scale
+    byte per 16).  The tensor-wide amaxes must already agree on all ranks (``with_amax_reduction`` over ``group``);
+    the local row count must be a multiple of 128 so that whole scale tiles move."""
+    from ..tensor.nvfp4 import NVFP4TensorStorage
+    from ..ops.ref.quant import round_up
+
+    ws = get_world_size(group)
+    if ws == 1:
+        return q
+    R, C = q._rows_cols()
+    assert R % 128 == 0, "quantized all-gather needs a multiple of 128 local rows"
+    rd = rs = cd = cs = None
+    if q._rowwise_data is not None:
+        rd, _ = gather_along_first_dim(q._rowwise_data.reshape(R, C // 2), group)
+        rs, _ = gather_along_first_dim(q._rowwise_scale_inv.reshape(-1), group)
+    if q._columnwise_data is not None:
+        cd = _gather_cols(q._columnwise_data.reshape(C, R // 2), group)
+        kt = round_up(R // 16, 4) // 4           # k-tiles (4 scales each) per 128-row tile of the [C, R/16] scale matrix
+        ct = round_up(C, 128) // 128
+        s, _ = gather_along_first_dim(q._columnwise_scale_inv.reshape(1, ct, kt, 512), group)   # [ws, ct, kt, 512]
+        cs = s.permute(1, 0, 2, 3).reshape(-1).contiguous()
+    return NVFP4TensorStorage(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd, columnwise_scale_inv=cs,
+                              amax_rowwise=q._amax_rowwise, amax_columnwise=q._amax_columnwise, fp4_dtype=q._fp4_dtype,
+                              quantizer=q._quantizer, shape=(R * ws, C), dtype=q._dtype,
+                              columnwise_rht=q._columnwise_rht)
+
+
+def gather_blockwise_along_first_dim(q, group):
+    """All-gather a block-scaled FP8 tensor (1 x 128 or 128 x 128 blocks) sharded on its rows without dequantizing;
+    the local row count must be a multiple of 128 (whole blocks of the column-wise copy)."""
+    from ..tensor.blockwise import Float8BlockwiseQTensorStorage
+
+    ws = get_world_size(group)
+    if ws == 1:
+        return q
+    R, C = q._rows_cols()
+    assert R % 128 == 0, "quantized all-gather needs a multiple of 128 local rows"
+    rd = rs = cd = cs = None
+    if q._rowwise_data is not None:
+        rd, _ = gather_along_first_dim(q._rowwise_data.reshape(R, C).view(torch.uint8), group)
+        rd = rd.view(q._rowwise_data.dtype)
+        rs, _ = gather_along_first_dim(q._rowwise_scale_inv, group)          # [R or R/128, C/128]: rows stack
+    if q._columnwise_data is not None:
+        cd = _gather_cols(q._columnwise_data.reshape(C, R).view(torch.uint8), group).view(q._columnwise_data.dtype)
+        cs = _gather_cols(q._columnwise_scale_inv, group)                      # [C or C/128, R/128]: columns stack
+    out = Float8BlockwiseQTensorStorage(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd,
+                                        columnwise_scale_inv=cs, fp8_dtype=q._fp8_dtype, is_2D_scaled=q._is_2D_scaled,
+                                        quantizer=q._quantizer, shape=(R * ws, C), dtype=q._dtype)
+    return out
+
+
+def gather_quantized_along_first_dim(q, group):
+    """All-gather any quantized tensor sharded on its rows in its quantized form (reference:
+    ``pytorch/distributed.py`` ``gather_along_first_dim`` with a quantizer)."""
+    from ..tensor.blockwise import Float8BlockwiseQTensorStorage
+    from ..tensor.float8 import Float8TensorStorage
+    from ..tensor.mxfp8 import MXFP8TensorStorage
+    from ..tensor.nvfp4 import NVFP4TensorStorage
+
+    if isinstance(q, MXFP8TensorStorage):
+        return gather_mxfp8_along_first_dim(q, group)
+    if isinstance(q, Float8TensorStorage):
+        return gather_float8_along_first_dim(q, group)
+    if isinstance(q, NVFP4TensorStorage):
+        return gather_nvfp4_along_first_dim(q, group)
+    if isinstance(q, Float8BlockwiseQTensorStorage):
+        return gather_blockwise_along_first_dim(q, group)
+    raise TypeError(f"no quantized all-gather for {type(q).__name__}")
+
+
 # --------------------------------------------------------------------------- RNG tracker
 class CudaRNGStatesTracker:
     """Named RNG states so that tensor-parallel ranks can draw the same or different

@@ -522,3 +522,16 @@ def test_cpu_offload_two_forward_passes_in_flight():
         hr.sum().backward()
         assert torch.allclose(x.grad, ref.grad, atol=1e-6)
     assert not ctx.handler.store
+
+
+def test_grouped_helper_ops_cpu_paths():
+    from transformerengine_b200 import ops
+
+    x = torch.randn(12, 16)
+    offs = torch.tensor([0, 5, 5, 12], dtype=torch.int32)
+    got = ops.grouped_column_sum(x, offs)
+    assert torch.allclose(got[0], x[:5].sum(0)) and got[1].abs().sum() == 0 and torch.allclose(got[2], x[5:].sum(0))
+    b = torch.randn(3, 16)
+    y = ops.grouped_bias_add_(x.clone(), b, offs)
+    assert torch.allclose(y[:5], x[:5] + b[0]) and torch.allclose(y[5:], x[5:] + b[2])
+    assert torch.allclose(ops.row_dot(x, y), (x * y).sum(-1))

@@ -419,3 +419,25 @@ def test_rope_packed_qkv_one_launch(layout, interleaved):
     xb = x.transpose(0, 1).contiguous()
     yb = ops.rope_qkv(xb.transpose(0, 1), fq, fq, layout=layout, hq=hq, hk=hk, interleaved=interleaved)
     assert torch.equal(yb, ops.rope_qkv(x, fq, fq, layout=layout, hq=hq, hk=hk, interleaved=interleaved))
+
+
+@pytest.mark.gpu
+def test_grouped_sums_bias_add_and_row_dot():
+    import torch
+    from transformerengine_b200 import ops
+
+    torch.manual_seed(2)
+    m = [300, 0, 1029, 7]
+    offs = torch.tensor([0, 300, 300, 1329, 1336], dtype=torch.int32, device="cuda")
+    for dt in (torch.bfloat16, torch.float32):
+        x = torch.randn(sum(m), 520, device="cuda", dtype=dt)
+        got = ops.grouped_column_sum(x, offs, torch.float32)
+        ref = torch.stack([c.float().sum(0) for c in torch.split(x, m)])
+        torch.testing.assert_close(got, ref, rtol=1e-4, atol=2e-2)
+        bias = torch.randn(4, 520, device="cuda", dtype=dt)
+        y = x.clone()
+        ops.grouped_bias_add_(y, bias, offs)
+        refy = torch.cat([c + bias[g] for g, c in enumerate(torch.split(x, m))])
+        torch.testing.assert_close(y, refy)
+        a, b = torch.randn(777, 1032, device="cuda", dtype=dt), torch.randn(777, 1032, device="cuda", dtype=dt)
+        torch.testing.assert_close(ops.row_dot(a, b), (a.float() * b.float()).sum(-1), rtol=1e-4, atol=1e-2)

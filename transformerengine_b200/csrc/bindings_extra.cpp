@@ -769,6 +769,41 @@ at::Tensor column_sum(const at::Tensor& x, at::ScalarType out_dtype) {
   return out;
 }
 
+at::Tensor grouped_column_sum(const at::Tensor& x, const at::Tensor& offsets, at::ScalarType out_dtype) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "grouped_column_sum expects a [R, C] matrix with contiguous rows");
+  TORCH_CHECK(offsets.scalar_type() == at::kInt && offsets.is_cuda() && offsets.numel() >= 2, "offsets: int32 device tensor");
+  const int G = static_cast<int>(offsets.numel() - 1), C = static_cast<int>(x.size(1));
+  at::Tensor out = at::empty({G, C}, x.options().dtype(out_dtype));
+  cudaError_t e = teb200::grouped_column_sum(x.data_ptr(), dtype_code(x), offsets.data_ptr<int>(), G, C, x.stride(0),
+                                             out.data_ptr(), dtype_code(out), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "grouped_column_sum failed: ", cudaGetErrorString(e));
+  return out;
+}
+
+void grouped_bias_add(at::Tensor& x, const at::Tensor& bias, const at::Tensor& offsets) {
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && bias.dim() == 2 && bias.is_contiguous() && bias.size(1) == x.size(1) &&
+                  bias.scalar_type() == x.scalar_type() && bias.size(0) == offsets.numel() - 1,
+              "grouped_bias_add: x [R, C], bias [G, C] of the same dtype, offsets [G + 1]");
+  TORCH_CHECK(offsets.scalar_type() == at::kInt && offsets.is_cuda(), "offsets: int32 device tensor");
+  cudaError_t e = teb200::grouped_bias_add(x.data_ptr(), bias.data_ptr(), dtype_code(x), offsets.data_ptr<int>(),
+                                           static_cast<int>(bias.size(0)), static_cast<int>(x.size(1)), x.stride(0),
+                                           static_cast<int>(x.size(0)), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "grouped_bias_add failed: ", cudaGetErrorString(e));
+}
+
+at::Tensor row_dot(const at::Tensor& a, const at::Tensor& b) {
+  c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.sizes() == b.sizes() && a.stride(1) == 1 && b.stride(1) == 1 &&
+                  a.scalar_type() == b.scalar_type(), "row_dot expects two [R, C] matrices of one dtype");
+  at::Tensor out = at::empty({a.size(0)}, a.options().dtype(at::kFloat));
+  cudaError_t e = teb200::row_dot(a.data_ptr(), b.data_ptr(), dtype_code(a), a.size(0), static_cast<int>(a.size(1)),
+                                  a.stride(0), b.stride(0), out.data_ptr<float>(), cur_stream());
+  TORCH_CHECK(e == cudaSuccess, "row_dot failed: ", cudaGetErrorString(e));
+  return out;
+}
+
 at::Tensor splits_to_offsets(const at::Tensor& splits, int64_t multiplier, bool out_int64) {
   c10::cuda::CUDAGuard guard(splits.device());
   TORCH_CHECK(splits.dim() == 1 && splits.is_contiguous() &&
@@ -817,6 +852,9 @@ at::Tensor pad_last_dim(const at::Tensor& in, int64_t new_cols) {
 void register_extra(py::module_& m) {
   m.def("column_sum", teb200::traced("teb200.column_sum", &column_sum));
   m.def("splits_to_offsets", teb200::traced("teb200.splits_to_offsets", &splits_to_offsets));
+  m.def("grouped_column_sum", teb200::traced("teb200.grouped_column_sum", &grouped_column_sum));
+  m.def("grouped_bias_add", teb200::traced("teb200.grouped_bias_add", &grouped_bias_add));
+  m.def("row_dot", teb200::traced("teb200.row_dot", &row_dot));
   m.def("repad_rows", teb200::traced("teb200.repad_rows", &repad_rows));
   m.def("pad_last_dim", teb200::traced("teb200.pad_last_dim", &pad_last_dim));
   m.def("delayed_scaling_update", teb200::traced("teb200.delayed_scaling_update", &delayed_scaling_update));

@@ -164,6 +164,16 @@ cudaError_t build_dest_rows(const int32_t* topk_idx, int T, int topk, int E, int
 int column_sum_parts(int R, int C);
 cudaError_t column_sum(const void* x, int x_dtype, int R, int C, long long ld, void* out, int out_dtype, float* workspace,
                        cudaStream_t s);
+// per-slab column sums (bias gradients of a grouped linear layer): out[g][c] = sum of x[r][c] over the rows
+// offsets[g] .. offsets[g+1]; offsets = int32 device array of groups + 1 entries
+cudaError_t grouped_column_sum(const void* x, int x_dtype, const int* offsets, int groups, int C, long long ld, void* out,
+                               int out_dtype, cudaStream_t s);
+// x[r][c] += bias[g][c] for the rows of slab g, all slabs in one launch; max_rows bounds offsets[groups]
+cudaError_t grouped_bias_add(void* x, const void* bias, int dtype, const int* offsets, int groups, int C, long long ld,
+                             int max_rows, cudaStream_t s);
+// out[r] = <a[r], b[r]> in fp32 (gradient of a per-row scale: routing probabilities of a scaled activation)
+cudaError_t row_dot(const void* a, const void* b, int dtype, long long R, int C, long long lda, long long ldb, float* out,
+                    cudaStream_t s);
 // out[0] = 0, out[i + 1] = multiplier * (splits[0] + ... + splits[i]); int32 or int64 on either side, all on the device
 cudaError_t splits_to_offsets(const void* splits, int splits_is_int64, int n, long long multiplier, void* out,
                               int out_is_int64, cudaStream_t s);

@@ -148,6 +148,76 @@ __global__ void pad_last_dim_kernel(const uint8_t* __restrict__ in, uint8_t* __r
   }
 }
 
+// out[g][c] = sum over the rows of slab g (offsets[g] .. offsets[g+1]) of x[r][c]; one block per (256 columns, slab)
+template <typename T, typename O>
+__global__ void __launch_bounds__(32 * CS_ROWS)
+grouped_colsum_kernel(const T* __restrict__ x, const int* __restrict__ offsets, int C, long long ld, O* __restrict__ out) {
+  __shared__ float sm[CS_ROWS][CS_COLS + 8];
+  const int lane = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c0 = blockIdx.x * CS_COLS + lane * 8;
+  const int g = blockIdx.y;
+  const int r0 = offsets[g], r1 = offsets[g + 1];
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  if (c0 < C) {
+    for (int r = r0 + ry; r < r1; r += CS_ROWS) {
+      float v[8];
+      load8<T>(x + static_cast<long long>(r) * ld + c0, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += v[i];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) sm[ry][lane * 8 + i] = acc[i];
+  __syncthreads();
+  for (int c = threadIdx.x; c < CS_COLS; c += 32 * CS_ROWS) {
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < CS_ROWS; ++r) s += sm[r][c];
+    const int col = blockIdx.x * CS_COLS + c;
+    if (col < C) out[static_cast<size_t>(g) * C + col] = static_cast<O>(s);
+  }
+}
+
+// x[r][c] += bias[g(r)][c] for the rows of every slab; one block per row, the slab found by binary search
+template <typename T>
+__global__ void grouped_bias_add_kernel(T* __restrict__ x, const T* __restrict__ bias, const int* __restrict__ offsets,
+                                        int groups, int C, long long ld) {
+  const int total = offsets[groups];
+  for (int r = blockIdx.x; r < total; r += gridDim.x) {
+    int lo = 0, hi = groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (offsets[mid] <= r) lo = mid;
+      else hi = mid;
+    }
+    T* row = x + static_cast<long long>(r) * ld;
+    const T* b = bias + static_cast<size_t>(lo) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) row[c] = static_cast<T>(static_cast<float>(row[c]) + static_cast<float>(b[c]));
+  }
+}
+
+// out[r] = sum_c a[r][c] * b[r][c] in fp32; one warp per row, 8 values per load
+template <typename T>
+__global__ void row_dot_kernel(const T* __restrict__ a, const T* __restrict__ b, long long R, int C, long long lda,
+                               long long ldb, float* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long r = warp; r < R; r += nwarps) {
+    float acc = 0.f;
+    for (int c = lane * 8; c < C; c += 256) {
+      float va[8], vb[8];
+      load8<T>(a + r * lda + c, va);
+      load8<T>(b + r * ldb + c, vb);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc += va[i] * vb[i];
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) out[r] = acc;
+  }
+}
+
 }  // namespace
 
 int column_sum_parts(int R, int C) {
@@ -180,6 +250,56 @@ cudaError_t column_sum(const void* x, int x_dtype, int R, int C, long long ld, v
   if (out_dtype == kFloat32) colsum_final_kernel<float><<<fg, 256, 0, s>>>(workspace, parts, C, static_cast<float*>(out));
   else if (out_dtype == kBFloat16) colsum_final_kernel<__nv_bfloat16><<<fg, 256, 0, s>>>(workspace, parts, C, static_cast<__nv_bfloat16*>(out));
   else if (out_dtype == kFloat16) colsum_final_kernel<__half><<<fg, 256, 0, s>>>(workspace, parts, C, static_cast<__half*>(out));
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+cudaError_t grouped_column_sum(const void* x, int x_dtype, const int* offsets, int groups, int C, long long ld, void* out,
+                               int out_dtype, cudaStream_t s) {
+  if (groups <= 0 || C <= 0) return cudaSuccess;
+  const size_t es = dtype_size(x_dtype);
+  if (C % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) != 0 || (ld * es) % 16 != 0) return cudaErrorInvalidValue;
+  dim3 grid((C + CS_COLS - 1) / CS_COLS, groups);
+#define TEB_GCS(T, O) grouped_colsum_kernel<T, O><<<grid, 32 * CS_ROWS, 0, s>>>(static_cast<const T*>(x), offsets, C, ld, static_cast<O*>(out))
+  if (x_dtype == kBFloat16 && out_dtype == kBFloat16) TEB_GCS(__nv_bfloat16, __nv_bfloat16);
+  else if (x_dtype == kBFloat16 && out_dtype == kFloat32) TEB_GCS(__nv_bfloat16, float);
+  else if (x_dtype == kFloat16 && out_dtype == kFloat16) TEB_GCS(__half, __half);
+  else if (x_dtype == kFloat16 && out_dtype == kFloat32) TEB_GCS(__half, float);
+  else if (x_dtype == kFloat32 && out_dtype == kFloat32) TEB_GCS(float, float);
+  else return cudaErrorInvalidValue;
+#undef TEB_GCS
+  return cudaGetLastError();
+}
+
+cudaError_t grouped_bias_add(void* x, const void* bias, int dtype, const int* offsets, int groups, int C, long long ld,
+                             int max_rows, cudaStream_t s) {
+  if (groups <= 0 || C <= 0 || max_rows <= 0) return cudaSuccess;
+  const int grid = max_rows < 148 * 16 ? max_rows : 148 * 16;
+  if (dtype == kBFloat16)
+    grouped_bias_add_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(bias), offsets, groups, C, ld);
+  else if (dtype == kFloat16)
+    grouped_bias_add_kernel<__half><<<grid, 256, 0, s>>>(static_cast<__half*>(x), static_cast<const __half*>(bias), offsets, groups, C, ld);
+  else if (dtype == kFloat32)
+    grouped_bias_add_kernel<float><<<grid, 256, 0, s>>>(static_cast<float*>(x), static_cast<const float*>(bias), offsets, groups, C, ld);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+cudaError_t row_dot(const void* a, const void* b, int dtype, long long R, int C, long long lda, long long ldb, float* out,
+                    cudaStream_t s) {
+  if (R <= 0) return cudaSuccess;
+  const size_t es = dtype_size(dtype);
+  if (C % 8 != 0 || (reinterpret_cast<uintptr_t>(a) & 15) != 0 || (reinterpret_cast<uintptr_t>(b) & 15) != 0 ||
+      (lda * es) % 16 != 0 || (ldb * es) % 16 != 0)
+    return cudaErrorInvalidValue;
+  const long long blocks = (R + 7) / 8;  // eight warps (rows) per block
+  const int grid = static_cast<int>(blocks < 148 * 16 ? blocks : 148 * 16);
+  if (dtype == kBFloat16)
+    row_dot_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(a), static_cast<const __nv_bfloat16*>(b), R, C, lda, ldb, out);
+  else if (dtype == kFloat16)
+    row_dot_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(a), static_cast<const __half*>(b), R, C, lda, ldb, out);
+  else if (dtype == kFloat32)
+    row_dot_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(a), static_cast<const float*>(b), R, C, lda, ldb, out);
   else return cudaErrorInvalidValue;
   return cudaGetLastError();
 }

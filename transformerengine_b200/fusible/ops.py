@@ -279,7 +279,7 @@ class _ScaledGluFn(torch.autograd.Function):
         dscales = None
         if ctx.needs_input_grad[1]:
             unscaled, _ = K.activation_fwd(x, ctx.act)
-            dscales = (dy * unscaled.to(dy.dtype)).sum(-1, dtype=torch.float32).to(scales.dtype).reshape(scales.shape)
+            dscales = K.row_dot(dy.reshape(-1, dy.shape[-1]), unscaled.to(dy.dtype).reshape(-1, dy.shape[-1])).to(scales.dtype).reshape(scales.shape)
         return dx.to(x.dtype), dscales, None
 
 

@@ -22,11 +22,23 @@ from . import _functional as F
 from .base import TransformerEngineBaseModule, get_default_init_method
 
 
+_OFFSET_CACHE: dict = {}
+
+
 def _offsets(m_splits: List[int], device) -> torch.Tensor:
-    offs = [0]
-    for m in m_splits:
-        offs.append(offs[-1] + int(m))
-    return torch.tensor(offs, dtype=torch.int32, device=device)
+    """Row offsets of the slabs as an int32 device tensor; the last few are kept (a forward and its backward ask
+    for the same offsets several times, each miss is a host-to-device copy)."""
+    key = (tuple(int(m) for m in m_splits), str(device))
+    t = _OFFSET_CACHE.get(key)
+    if t is None:
+        offs = [0]
+        for m in key[0]:
+            offs.append(offs[-1] + m)
+        t = torch.tensor(offs, dtype=torch.int32, device=device)
+        if len(_OFFSET_CACHE) >= 64:
+            _OFFSET_CACHE.pop(next(iter(_OFFSET_CACHE)))
+        _OFFSET_CACHE[key] = t
+    return t
 
 
 def _can_group(m_splits, x_ops, quantized: bool) -> bool:
@@ -92,9 +104,9 @@ class _GroupedLinear(torch.autograd.Function):
                     if m_splits[g]:
                         gemm_nt(x2d[offs[g]:offs[g + 1]], weights[g].to(adt), out=out[offs[g]:offs[g + 1]])
             xq = x2d
-        for g in range(G):
-            if biases[g] is not None and m_splits[g]:
-                out[offs[g]:offs[g + 1]] += biases[g].to(adt)
+        if biases[0] is not None:
+            # every slab gets its expert's bias: one launch for all of them
+            ops.grouped_bias_add_(out, torch.stack([b.to(adt) for b in biases]), _offsets(m_splits, out.device))
         if grad_on:
             ctx.module, ctx.m_splits, ctx.offs, ctx.adt, ctx.fp8q = module, list(m_splits), offs, adt, quant_ok
             ctx.xq, ctx.wqs = xq, wqs
@@ -127,9 +139,10 @@ class _GroupedLinear(torch.autograd.Function):
             wcol = module.stacked_weight_operand(ctx.wqs, "columnwise")        # [G * K, N]
             gemm_nt(as_operand(dyq, "rowwise"), wcol, out=dx, group_offsets=_offsets(m_splits, dy.device), num_groups=G)
             dy_col, x_col = as_operand(dyq, "columnwise"), as_operand(ctx.xq, "columnwise")
+            if module.use_bias:
+                db_all = ops.grouped_column_sum(dy, _offsets(m_splits, dy.device), torch.float32)
+                dbs = [db_all[g].to(weights[g].dtype) for g in range(G)]
             for g in range(G):
-                if module.use_bias:
-                    dbs[g] = dy[offs[g]:offs[g + 1]].float().sum(0).to(weights[g].dtype)
                 if m_splits[g] == 0:
                     dws[g] = torch.zeros_like(weights[g])
                     continue
@@ -145,10 +158,11 @@ class _GroupedLinear(torch.autograd.Function):
             if module.use_bias:
                 res += dbs
             return tuple(res)
+        if module.use_bias:
+            db_all = ops.grouped_column_sum(dy, _offsets(m_splits, dy.device), torch.float32)
+            dbs = [db_all[g].to(weights[g].dtype) for g in range(G)]
         for g in range(G):
             sl = slice(offs[g], offs[g + 1])
-            if module.use_bias:
-                dbs[g] = dy[sl].float().sum(0).to(weights[g].dtype)
             if m_splits[g] == 0:
                 dws[g] = torch.zeros_like(weights[g])
                 continue

@@ -14,7 +14,8 @@ from .activation import activation_fwd, activation_bwd, is_gated
 from .misc import (rope_apply, rope_qkv, rope_freqs, cross_entropy_fwd_bwd, cross_entropy_stats, cross_entropy_parallel_grad,
                    multi_tensor_adam, multi_tensor_sgd, multi_tensor_scale, multi_tensor_l2norm,
                    scaled_masked_softmax, softmax_bwd, dropout_fwd, dropout_bwd,
-                   column_sum, splits_to_offsets, repad_rows, pad_last_dim)
+                   column_sum, splits_to_offsets, repad_rows, pad_last_dim, grouped_column_sum,
+                   grouped_bias_add_, row_dot)
 from .attention import attention, attention_ref, merge_attention_states
 
 

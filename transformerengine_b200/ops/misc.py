@@ -399,6 +399,42 @@ def column_sum(x2d: torch.Tensor, out_dtype=None) -> torch.Tensor:
     return x2d.float().sum(dim=0).to(out_dtype)
 
 
+def _vec_ok(t: torch.Tensor) -> bool:
+    return (_ext.use_cuda(t) and t.dim() == 2 and t.stride(1) == 1 and t.shape[1] % 8 == 0
+            and t.dtype in (torch.bfloat16, torch.float16, torch.float32) and t.data_ptr() % 16 == 0
+            and (t.stride(0) * t.element_size()) % 16 == 0)
+
+
+def grouped_column_sum(x2d: torch.Tensor, offsets: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """Per-slab column sums ``out[g] = x[offsets[g]:offsets[g+1]].sum(0)`` (the bias gradients of a grouped linear
+    layer) in one launch; ``offsets``: int32 tensor of ``groups + 1`` row offsets."""
+    out_dtype = out_dtype or x2d.dtype
+    if _vec_ok(x2d) and offsets.is_cuda and (out_dtype == x2d.dtype or out_dtype == torch.float32):
+        return _ext.get().grouped_column_sum(x2d, offsets.to(torch.int32).contiguous(), out_dtype)
+    o = [int(v) for v in offsets.tolist()]
+    return torch.stack([x2d[o[g]:o[g + 1]].float().sum(0) for g in range(len(o) - 1)]).to(out_dtype)
+
+
+def grouped_bias_add_(x2d: torch.Tensor, bias_gc: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """``x[offsets[g]:offsets[g+1]] += bias[g]`` for every slab, in place, one launch."""
+    if _ext.use_cuda(x2d) and x2d.dim() == 2 and x2d.stride(1) == 1 and offsets.is_cuda \
+            and x2d.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        _ext.get().grouped_bias_add(x2d, bias_gc.to(x2d.dtype).contiguous(), offsets.to(torch.int32).contiguous())
+        return x2d
+    o = [int(v) for v in offsets.tolist()]
+    for g in range(len(o) - 1):
+        if o[g + 1] > o[g]:
+            x2d[o[g]:o[g + 1]] += bias_gc[g].to(x2d.dtype)
+    return x2d
+
+
+def row_dot(a2d: torch.Tensor, b2d: torch.Tensor) -> torch.Tensor:
+    """``out[r] = <a[r], b[r]>`` in fp32: one pass over both operands (gradient of a per-row scale)."""
+    if _vec_ok(a2d) and _vec_ok(b2d) and a2d.dtype == b2d.dtype and a2d.shape == b2d.shape:
+        return _ext.get().row_dot(a2d, b2d)
+    return (a2d.float() * b2d.float()).sum(-1)
+
+
 def splits_to_offsets(splits: torch.Tensor, multiplier: int = 1, dtype=torch.int32) -> torch.Tensor:
     """Exclusive prefix sums ``[0, s0, s0 + s1, ...] * multiplier`` of a device tensor of split sizes, without a
     host round trip (reference: ``common/util/splits_to_offsets.cu:61``)."""

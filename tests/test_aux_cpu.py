@@ -535,3 +535,34 @@ def test_grouped_helper_ops_cpu_paths():
     y = ops.grouped_bias_add_(x.clone(), b, offs)
     assert torch.allclose(y[:5], x[:5] + b[0]) and torch.allclose(y[5:], x[5:] + b[2])
     assert torch.allclose(ops.row_dot(x, y), (x * y).sum(-1))
+
+
+def test_canary_guard_bands_catch_out_of_bounds_writes():
+    from transformerengine_b200.utils.canary import GuardedAllocation
+
+    g = GuardedAllocation(guard_bytes=256)
+    a = g.empty((4, 8), torch.float32, device="cpu", name="a")
+    b = g.empty((3,), torch.uint8, device="cpu", name="b")
+    a.normal_()
+    b.zero_()
+    g.check()                                        # writes inside the tensors are fine
+    raw_b = g._allocs[1][1]
+    raw_b[256 + 3] = 0                               # one byte past the end of b (inside its alignment padding)
+    bad = g.violations()
+    assert len(bad) == 1 and bad[0].startswith("b: byte 3")
+    with pytest.raises(AssertionError):
+        g.check()
+
+
+def test_canary_intercepts_wrapper_allocations():
+    from transformerengine_b200.utils.canary import GuardedAllocation
+
+    g = GuardedAllocation(guard_bytes=256)
+    with g.intercept(device_type="cpu"):
+        a = torch.empty(5, 7, dtype=torch.float32, device="cpu")
+        z = torch.zeros((3, 2), dtype=torch.int32, device="cpu")
+        plain = torch.empty(4)                       # no device named: passes through
+    assert len(g._allocs) == 2 and a.shape == (5, 7) and z.abs().sum() == 0 and plain.shape == (4,)
+    a.fill_(1.0)
+    g.check()
+    assert torch.empty(2, device="cpu").shape == (2,)   # restored

@@ -441,3 +441,35 @@ def test_grouped_sums_bias_add_and_row_dot():
         torch.testing.assert_close(y, refy)
         a, b = torch.randn(777, 1032, device="cuda", dtype=dt), torch.randn(777, 1032, device="cuda", dtype=dt)
         torch.testing.assert_close(ops.row_dot(a, b), (a.float() * b.float()).sum(-1), rtol=1e-4, atol=1e-2)
+
+
+@pytest.mark.gpu
+def test_kernels_stay_inside_their_outputs():
+    """Guard bands around every output that the Python wrappers allocate: quantizers with swizzled scale layouts
+    on shapes with partial tiles, GEMMs with TMA-store epilogues on ragged widths, strided RoPE, norm."""
+    import torch
+    from transformerengine_b200 import ops
+    from transformerengine_b200.ops import quantize as qz
+    from transformerengine_b200.tensor import MXFP8Quantizer
+    from transformerengine_b200.utils.canary import GuardedAllocation
+
+    torch.manual_seed(5)
+    g = GuardedAllocation()
+    x = torch.randn(1040, 272, device="cuda", dtype=torch.bfloat16)
+    a = torch.randn(300, 512, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(264, 512, device="cuda", dtype=torch.bfloat16)
+    xq = torch.randn(384, 640, device="cuda", dtype=torch.bfloat16)
+    with g.intercept():
+        qz.quantize_nvfp4(x, with_rht=True)                       # one-pass kernel, partial tiles
+        qz.quantize_nvfp4(x, rowwise=True, columnwise=False)
+        qz.quantize_mxfp8(xq, torch.float8_e4m3fn)                # tile quantizer, swizzled scales
+        ops.gemm_nt(a, b, out_dtype=torch.bfloat16)               # ragged M and N
+        qa, qb = MXFP8Quantizer(columnwise=False)(a), MXFP8Quantizer(columnwise=False)(b)
+        ops.gemm_nt(ops.as_operand(qa), ops.as_operand(qb), out_dtype=torch.bfloat16)
+        ops.column_sum(a, torch.float32)
+        ops.norm_fwd(a, torch.ones(512, device="cuda", dtype=torch.bfloat16), None, 1e-5, False, False)
+        f = ops.rope_freqs(torch.arange(96, device="cuda"), 128, 10000.0, False)
+        ops.rope_qkv(torch.randn(96, 2, 12, 128, device="cuda", dtype=torch.bfloat16), f, f, layout="grouped", hq=8, hk=2)
+    torch.cuda.synchronize()
+    assert len(g._allocs) >= 8
+    g.check()

@@ -264,3 +264,28 @@ def test_fused_adam_capturable_and_param_remainders():
     o.step()
     torch.cuda.synchronize()
     assert torch.isfinite(p.float()).all() and (p != 0).all()
+
+
+def test_compile_ops_trace_the_kernels_as_single_nodes_on_gpu():
+    """A norm -> linear -> SwiGLU -> linear block through the ``torch.library`` operators, compiled as one graph
+    (no graph breaks) in bf16 on the GPU: forward and gradients against eager PyTorch."""
+    import transformerengine_b200.compile_ops as cops
+
+    torch.manual_seed(4)
+    x = torch.randn(256, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.ones(512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w1 = (torch.randn(1024, 512, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_()
+    w2 = (torch.randn(512, 512, device="cuda", dtype=torch.bfloat16) * 0.05).requires_grad_()
+
+    def block(x, g, w1, w2):
+        return cops.linear(cops.swiglu(cops.linear(cops.rmsnorm(x, g, 1e-5), w1)), w2)
+
+    y = torch.compile(block, backend="aot_eager", fullgraph=True)(x, g, w1, w2)
+    xf = x.float()
+    h = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * g.float()).to(torch.bfloat16)
+    u = (h.float() @ w1.float().t()).to(torch.bfloat16).float()
+    a = (torch.nn.functional.silu(u[:, :512]) * u[:, 512:]).to(torch.bfloat16)
+    ref = a.float() @ w2.float().t()
+    assert ((y.float() - ref).norm() / ref.norm()) < 2e-2
+    y.float().sum().backward()
+    assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in (x, g, w1, w2))

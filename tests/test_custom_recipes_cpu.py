@@ -39,3 +39,46 @@ def test_custom_gemm_layouts_on_quantized_operands():
     torch.testing.assert_close(custom_gemm(wq, xq, layout="TN"), xd @ wd.t())
     torch.testing.assert_close(custom_gemm(wq, dy, layout="NN"), dy @ wd)
     torch.testing.assert_close(custom_gemm(xq, dy, layout="NT"), dy.t() @ xd)
+
+
+def test_delayed_scaling_request_equals_the_delayed_scaling_recipe():
+    """A custom recipe whose factory asks for library-managed delayed scaling trains exactly like the DelayedScaling
+    recipe with the same parameters (scales follow the amax history, updated at region exit)."""
+    from transformerengine_b200.common import recipe as R
+    from transformerengine_b200.custom_recipes.quantizer_factories import tensor_type
+
+    def factory(role):
+        if tensor_type(role) in ("output", "grad_input"):
+            return None
+        return te.DelayedScalingRequest(amax_history_len=4, margin=0)
+
+    def run(rec):
+        torch.manual_seed(0)
+        lin = te.Linear(32, 32, bias=False, params_dtype=torch.float32, device="cpu")
+        outs = []
+        for step in range(4):
+            x = (torch.randn(16, 32) * (step + 1)).requires_grad_()
+            with te.autocast(enabled=True, recipe=rec):
+                y = lin(x)
+            y.square().sum().backward()
+            outs.append((y.detach().clone(), x.grad.clone(), lin.weight.grad.clone()))
+            lin.weight.grad = None
+        return outs
+
+    a = run(R.CustomRecipe(qfactory=factory))
+    b = run(R.DelayedScaling(amax_history_len=4, margin=0))
+    for (ya, gxa, gwa), (yb, gxb, gwb) in zip(a, b):
+        torch.testing.assert_close(ya, yb, rtol=0, atol=0)
+        torch.testing.assert_close(gxa, gxb, rtol=0, atol=0)
+        torch.testing.assert_close(gwa, gwb, rtol=0, atol=0)
+
+
+def test_top_level_names_of_the_reference_front_end_exist():
+    for name in ("DType", "Float8Quantizer", "MXFP8Tensor", "NVFP4Quantizer", "Float8BlockwiseQTensor",
+                 "HybridQuantizer", "IdentityQuantizer", "QuantizedTensor", "Quantizer", "QuantizerRole",
+                 "DelayedScalingRequest", "ManualOffloadSynchronizer", "mark_not_offload", "prepare_for_saving",
+                 "restore_from_saved", "interleave_glu_tensor", "get_device_compute_capability",
+                 "UserBufferQuantizationMode", "constants", "load_framework_extension"):
+        assert hasattr(te, name), name
+    assert te.DType.kFloat8E4M3 == te.constants.TE_DType[torch.float8_e4m3fn]
+    assert str(te.QuantizerRole(module_type="linear", tensor_type="input")) == "module_type=linear|tensor_type=input"

@@ -44,4 +44,29 @@ from .cross_entropy import parallel_cross_entropy
 from .newton_schulz import newton_schulz
 from .parallel.context_parallel import get_batch_on_this_cp_rank, pad_thd_sequences_for_cp
 
+# names that reference code imports from the top level of the package
+from . import constants  # noqa: F401
+from .constants import DType, UserBufferQuantizationMode  # noqa: F401
+from .quantization import QuantizerRole, QuantizerRequest, DelayedScalingRequest  # noqa: F401
+from .tensor import (Quantizer, QuantizedTensor, QuantizedTensorStorage, Float8Quantizer,  # noqa: F401
+                     Float8CurrentScalingQuantizer, Float8Tensor, Float8TensorStorage, MXFP8Quantizer, MXFP8Tensor,
+                     MXFP8TensorStorage, NVFP4Quantizer, NVFP4Tensor, NVFP4TensorStorage, Float8BlockQuantizer,
+                     Float8BlockwiseQTensor, Float8BlockwiseQTensorStorage)
+from .tensor.hybrid import (HybridQuantizer, HybridQuantizedTensor, HybridQuantizedTensorStorage,  # noqa: F401
+                            IdentityQuantizer, IdentityTensor, IdentityTensorStorage)
+from .tensor.base import prepare_for_saving, restore_from_saved, restore_from_func_ctx  # noqa: F401
+from .cpu_offload import ManualOffloadSynchronizer, mark_not_offload  # noqa: F401
+from .utils import (get_device_compute_capability, get_cudnn_version, is_bf16_available, torch_version,  # noqa: F401
+                    interleave_glu_tensor, deinterleave_glu_tensor)
+
+
+def load_framework_extension(framework: str = "torch") -> None:
+    """Load (building it first if needed) the native extension; only the PyTorch front end exists."""
+    if framework not in ("torch", "pytorch"):
+        raise ValueError(f"no {framework} front end in this library")
+    from .ops import _ext
+
+    _ext.get()
+
+
 __version__ = "0.1.0"

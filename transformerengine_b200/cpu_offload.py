@@ -52,6 +52,18 @@ class _Entry:
         self.served = False    # handed to the backward pass at least once
 
 
+def mark_not_offload(*tensors) -> None:
+    """Keep these tensors on the device even when they are saved inside an offload context (tensors that the
+    backward pass needs first, or that are shared with other layers)."""
+    for t in tensors:
+        if isinstance(t, torch.Tensor):
+            t._te_do_not_offload = True
+        elif t is not None and hasattr(t, "get_data_tensors"):
+            for d in t.get_data_tensors():
+                if d is not None:
+                    d._te_do_not_offload = True
+
+
 class _OffloadHandler:
     def __init__(self, num_layers: int, model_layers: int, min_numel: int = 1 << 16, *, retain_pinned: bool = False,
                  double_buffering: bool = False, manual: bool = False, stream=None):
@@ -76,7 +88,8 @@ class _OffloadHandler:
 
     def should_offload(self, t) -> bool:
         return (self.layer < self.num_offload and isinstance(t, torch.Tensor) and t.numel() >= self.min_numel
-                and not isinstance(t, torch.nn.Parameter) and (t.is_cuda or not self.cuda))
+                and not isinstance(t, torch.nn.Parameter) and (t.is_cuda or not self.cuda)
+                and not getattr(t, "_te_do_not_offload", False))
 
     # ------------------------------------------------------------------ device -> host
     def _host_buffer(self, t: torch.Tensor) -> torch.Tensor:

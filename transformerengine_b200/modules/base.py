@@ -176,6 +176,13 @@ class TransformerEngineBaseModule(torch.nn.Module):
     def prepare_forward(self, num_gemms: int = 1) -> None:
         self.init_fp8_metadata(num_gemms)
         st = self._states["scaling_fwd"]
+        if self.fp8:
+            # a custom recipe whose factory asked for delayed scaling: its amax histories are reduced and turned
+            # into scales at region exit like those of the DelayedScaling recipe
+            for key, fwd in (("scaling_fwd", True), ("scaling_bwd", False)):
+                inner = getattr(self._states.get(key), "delayed", None)
+                if inner is not None and (fwd or torch.is_grad_enabled()):
+                    FP8GlobalStateManager.add_pending(inner, forward=fwd)
         if self.fp8 and isinstance(st, DelayedScalingRecipeState):
             from ..parallel import distributed as D
 

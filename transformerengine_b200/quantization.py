@@ -8,6 +8,8 @@ For delayed scaling, amaxes recorded during the region are reduced (MAX over
 """
 from __future__ import annotations
 
+import dataclasses
+
 import os
 from contextlib import contextmanager
 from typing import Dict, List, Optional, Tuple
@@ -98,6 +100,43 @@ def check_recipe_support(recipe: Recipe) -> None:
 
 
 # --------------------------------------------------------------------------- recipe state
+
+@dataclasses.dataclass(frozen=True)
+class QuantizerRole:
+    """Which tensor slot asks a ``CustomRecipe`` factory for a quantizer: the kind of module (``"linear"``,
+    ``"grouped_linear"``, ``"dpa"``), the tensor (``"input"``, ``"weight"``, ``"output"``, ``"grad_output"``,
+    ``"grad_input"``) and the module instance's name.  Factories may also be handed the plain strings this
+    library uses (``"linear_input"`` ...); ``custom_recipes.quantizer_factories.tensor_type`` reads both.
+    (Reference: ``pytorch/quantization.py:57``.)"""
+
+    module_type: str = ""
+    tensor_type: str = ""
+    name: str = ""
+
+    def __str__(self) -> str:
+        parts = [f"{k}={v}" for k, v in (("module_type", self.module_type), ("tensor_type", self.tensor_type),
+                                         ("name", self.name)) if v]
+        return "|".join(parts) if parts else "QuantizerRole()"
+
+
+@dataclasses.dataclass(frozen=True)
+class QuantizerRequest:
+    """Base class of the requests a ``CustomRecipe`` factory may return instead of a quantizer when the quantizer
+    needs state that the library manages."""
+
+
+@dataclasses.dataclass(frozen=True)
+class DelayedScalingRequest(QuantizerRequest):
+    """Ask for a per-tensor FP8 quantizer whose scale follows an amax history kept by the library."""
+
+    fp8_format: object = None          # recipe.Format; None = HYBRID
+    margin: int = 0
+    amax_history_len: int = 1024
+    amax_compute_algo: object = "max"
+    scaling_factor_compute_algo: object = None
+    reduce_amax: bool = True
+
+
 class RecipeState:
     """Per-module, per-direction quantization state; builds the quantizers.
 
@@ -200,9 +239,26 @@ class CustomRecipeState(RecipeState):
     _FWD = ("linear_input", "linear_weight", "linear_output")
     _BWD = ("linear_grad_output", "linear_grad_input")
 
+    delayed: Optional["DelayedScalingRecipeState"] = None   # state behind the slots that asked for delayed scaling
+
     def make_quantizers(self):
         roles = self._FWD if self.mode == "forward" else self._BWD
-        return [self.recipe.qfactory(roles[i % len(roles)]) for i in range(self.num_quantizers)]
+        out = [self.recipe.qfactory(roles[i % len(roles)]) for i in range(self.num_quantizers)]
+        asked = [i for i, q in enumerate(out) if isinstance(q, DelayedScalingRequest)]
+        if asked:
+            first = out[asked[0]]
+            if any(out[i] != first for i in asked):
+                raise ValueError("all DelayedScalingRequest objects of one module must carry the same parameters")
+            kw = dict(margin=first.margin, amax_history_len=first.amax_history_len,
+                      amax_compute_algo=first.amax_compute_algo,
+                      scaling_factor_compute_algo=first.scaling_factor_compute_algo, reduce_amax=first.reduce_amax)
+            if first.fp8_format is not None:
+                kw["fp8_format"] = first.fp8_format
+            self.delayed = DelayedScalingRecipeState(DelayedScaling(**kw), mode=self.mode, num_quantizers=len(asked),
+                                                     device=self.device)
+            for q, i in zip(self.delayed.make_quantizers(), asked):
+                out[i] = q
+        return out
 
 
 # --------------------------------------------------------------------------- delayed-scaling update

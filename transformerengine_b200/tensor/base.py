@@ -296,3 +296,14 @@ def restore_from_saved(objs, saved):
             saved = o.restore_from_saved(saved)
             out.append(o)
     return out
+
+
+def restore_from_func_ctx(ctx, return_saved_tensors: bool = False):
+    """Rebuild the tensors that ``prepare_for_saving`` split, from an autograd context that kept the objects in
+    ``ctx.tensor_objects`` and the raw tensors in ``ctx.saved_tensors``; the objects are dropped from the context."""
+    if getattr(ctx, "tensor_objects", None) is None:
+        raise AttributeError("ctx must have .tensor_objects to restore saved tensors")
+    saved = list(ctx.saved_tensors)
+    out = restore_from_saved(ctx.tensor_objects, list(saved))
+    ctx.tensor_objects = None
+    return (out, saved) if return_saved_tensors else out

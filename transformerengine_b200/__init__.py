@@ -55,6 +55,13 @@ from .tensor import (Quantizer, QuantizedTensor, QuantizedTensorStorage, Float8Q
 from .tensor.hybrid import (HybridQuantizer, HybridQuantizedTensor, HybridQuantizedTensorStorage,  # noqa: F401
                             IdentityQuantizer, IdentityTensor, IdentityTensorStorage)
 from .tensor.base import prepare_for_saving, restore_from_saved, restore_from_func_ctx  # noqa: F401
+# unpickling entry points of the quantized tensor classes (pickles written by this library name them)
+from .tensor.float8 import _make_float8_tensor_in_reduce_ex  # noqa: F401
+from .tensor.mxfp8 import _make_mxfp8_tensor_in_reduce_ex  # noqa: F401
+from .tensor.nvfp4 import _make_nvfp4_tensor_in_reduce_ex  # noqa: F401
+from .tensor.blockwise import _make_blockwise_in_reduce_ex as _make_float8_blockwise_tensor_in_reduce_ex  # noqa: F401
+from .tensor.hybrid import _make_identity_tensor_in_reduce_ex  # noqa: F401
+from .tensor.hybrid import _make_hybrid_tensor_in_reduce_ex as _make_hybrid_quantized_tensor_in_reduce_ex  # noqa: F401
 from .cpu_offload import ManualOffloadSynchronizer, mark_not_offload  # noqa: F401
 from .utils import (get_device_compute_capability, get_cudnn_version, is_bf16_available, torch_version,  # noqa: F401
                     interleave_glu_tensor, deinterleave_glu_tensor)

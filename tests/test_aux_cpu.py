@@ -566,3 +566,30 @@ def test_canary_intercepts_wrapper_allocations():
     a.fill_(1.0)
     g.check()
     assert torch.empty(2, device="cpu").shape == (2,)   # restored
+
+
+def test_reference_module_names_resolve_and_work():
+    """``distributed``, ``jit``, ``cpp_extensions``, ``fp8``, ``module`` ... exist under the reference's names."""
+    import importlib
+
+    for m in ("distributed", "jit", "cpp_extensions", "fp8", "float8_tensor", "quantized_tensor", "permutation",
+              "router", "ep", "module", "constants", "custom_recipes", "numerics_debug", "compile_ops"):
+        importlib.import_module("transformerengine_b200." + m)
+    from transformerengine_b200 import cpp_extensions as ce, distributed as D, jit
+
+    x, b = torch.randn(4, 8, requires_grad=True), torch.randn(8)
+    ref = torch.nn.functional.gelu(x + b, approximate="tanh")
+    assert torch.allclose(jit.bias_gelu_fused(x, b), ref, atol=1e-6)
+    dx, db = jit.bgrad_dgelu_fused(torch.ones(4, 8), x.detach(), b)
+    (gx,) = torch.autograd.grad(ref.sum(), x)
+    assert torch.allclose(dx, gx, atol=1e-6) and torch.allclose(db, gx.sum(0), atol=1e-5)
+    r = torch.randn(4, 8)
+    assert torch.allclose(jit.bias_dropout_add_fused_inference(x.detach(), b, r, 0.1), r + x.detach() + b)
+    # grouped GEMM, list form: out[i] = B[i] @ A[i]^T
+    A = [torch.randn(6, 8), torch.randn(6, 8)]
+    B = [torch.randn(3, 8), torch.randn(5, 8)]
+    out = [torch.empty(8, 6)]
+    ce.general_grouped_gemm(A, B, out, out_dtype=torch.float32, m_splits=[3, 5], single_output=True)
+    assert torch.allclose(out[0][:3], B[0] @ A[0].t(), atol=1e-5) and torch.allclose(out[0][3:], B[1] @ A[1].t(), atol=1e-5)
+    assert D.get_distributed_world_size(None) == 1 and D.split_tensor_into_1d_equal_chunks(r, None).numel() == 32
+    assert not D.is_fp8_activation_recompute_enabled() and not D.in_fp8_activation_recompute_phase()

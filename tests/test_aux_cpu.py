@@ -593,3 +593,15 @@ def test_reference_module_names_resolve_and_work():
     assert torch.allclose(out[0][:3], B[0] @ A[0].t(), atol=1e-5) and torch.allclose(out[0][3:], B[1] @ A[1].t(), atol=1e-5)
     assert D.get_distributed_world_size(None) == 1 and D.split_tensor_into_1d_equal_chunks(r, None).numel() == 32
     assert not D.is_fp8_activation_recompute_enabled() and not D.in_fp8_activation_recompute_phase()
+
+
+def test_quickstart_example_runs_and_learns():
+    import importlib.util
+    import os as _os
+
+    path = _os.path.join(_os.path.dirname(_os.path.dirname(_os.path.abspath(__file__))), "examples", "quickstart.py")
+    spec = importlib.util.spec_from_file_location("quickstart_example", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    losses = mod.main(["--recipe", "mxfp8", "--steps", "6", "--hidden", "256", "--seq", "64"])
+    assert losses[-1] < losses[0]

@@ -92,6 +92,50 @@ class Float8Tensor(Float8TensorStorage, QuantizedTensor):
         return (_make_float8_tensor_in_reduce_ex,
                 (self._data, self._fp8_dtype, self._scale_inv, self._dtype, self._shape, self._transpose))
 
+    # ---- structural ops that keep the FP8 payload (what FSDP2 does to a parameter when it shards it: chunk along
+    # dim 0, allocate a padded buffer, copy the chunk into a slice of it, flatten).  One scale covers the tensor,
+    # so every piece shares the scale tensor of its source.
+    def _piece(self, data: torch.Tensor) -> "Float8Tensor":
+        return Float8Tensor(shape=tuple(data.shape), dtype=self._dtype, data=data, fp8_scale_inv=self._scale_inv,
+                            fp8_dtype=self._fp8_dtype, quantizer=self._quantizer, requires_grad=False)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        aten = torch.ops.aten
+        t = args[0] if args else None
+        if isinstance(t, Float8Tensor) and t._data is not None:
+            data = t._data.reshape(t._shape)
+            if func == aten.split.Tensor:
+                dim = args[2] if len(args) > 2 else kwargs.get("dim", 0)
+                return tuple(t._piece(d) for d in torch.split(data, args[1], dim=dim))
+            if func == aten.slice.Tensor:
+                return t._piece(aten.slice.Tensor(data, *args[1:], **kwargs))
+            if func == aten.narrow.default:
+                return t._piece(aten.narrow.default(data, *args[1:], **kwargs))
+            if func in (aten.view.default, aten._unsafe_view.default, aten.reshape.default):
+                return t._piece(data.view(*args[1:]) if func != aten.reshape.default else data.reshape(*args[1:]))
+            if func == aten.as_strided.default:
+                size, stride = tuple(args[1]), tuple(args[2])
+                offset = args[3] if len(args) > 3 and args[3] is not None else 0
+                return t._piece(torch.as_strided(data, size, stride, offset))
+            if func == aten.new_zeros.default:
+                # zero bytes are zero values in both FP8 formats
+                size = tuple(args[1])
+                dev = kwargs.get("device") or data.device
+                return t._piece(torch.zeros(size, dtype=data.dtype, device=dev))
+            if func in (aten.empty_like.default, aten.zeros_like.default):
+                return t._piece(torch.zeros_like(data))
+            if func == aten.copy_.default and isinstance(args[1], Float8Tensor) and args[1]._data is not None \
+                    and args[1]._fp8_dtype == t._fp8_dtype and tuple(args[1]._shape) == tuple(t._shape):
+                src = args[1]
+                data.copy_(src._data.reshape(src._shape))
+                if src._scale_inv is not t._scale_inv:
+                    t._scale_inv.copy_(src._scale_inv)
+                t._transpose = None
+                return t
+        return super().__torch_dispatch__(func, types, args, kwargs)
+
     # ---- FSDP2 extension points (reference: tensor/float8_tensor.py:938-1075): shards travel as raw bytes,
     # the per-tensor scale is identical on all ranks (its amax is reduced over the shard group)
     def fsdp_pre_all_gather(self, mesh=None, orig_size=None, contiguous_orig_stride=None, module=None, mp_policy=None):

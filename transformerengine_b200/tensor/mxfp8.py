@@ -122,6 +122,58 @@ class MXFP8Tensor(MXFP8TensorStorage, QuantizedTensor):
                 (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
                  self._fp8_dtype, self._dtype, self._shape, None, True))
 
+    # ---- structural ops that keep the MXFP8 payload when FSDP2 shards a parameter along its rows (chunk, padded
+    # buffer, copy into a slice).  Only whole 128-row scale tiles can be cut: other requests take the generic
+    # (dequantizing) path, and the parameter is then sharded in high precision.  Pieces carry the row-wise copy only.
+    def _row_piece(self, r0: int, r1: int) -> "MXFP8Tensor":
+        R, C = self._rows_cols()
+        per_tile = self._rowwise_scale_inv.numel() // ((R + 127) // 128)
+        data = self._rowwise_data.reshape(R, C)[r0:r1]
+        sc = self._rowwise_scale_inv.reshape(-1)[(r0 // 128) * per_tile:((r1 + 127) // 128) * per_tile]
+        return MXFP8Tensor(shape=(r1 - r0, C), dtype=self._dtype, rowwise_data=data, rowwise_scale_inv=sc,
+                           columnwise_data=None, columnwise_scale_inv=None, fp8_dtype=self._fp8_dtype,
+                           quantizer=self._quantizer)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        aten = torch.ops.aten
+        t = args[0] if args else None
+        if isinstance(t, MXFP8Tensor) and t._rowwise_data is not None and len(t._shape) == 2:
+            R, C = t._rows_cols()
+            if func == aten.split.Tensor and (args[2] if len(args) > 2 else kwargs.get("dim", 0)) == 0 \
+                    and isinstance(args[1], int) and args[1] % 128 == 0 and R % 128 == 0:
+                return tuple(t._row_piece(r, min(r + args[1], R)) for r in range(0, R, args[1]))
+            if func == aten.slice.Tensor:
+                dim = args[1] if len(args) > 1 else 0
+                start = args[2] if len(args) > 2 and args[2] is not None else 0
+                end = min(args[3], R) if len(args) > 3 and args[3] is not None else R
+                step = args[4] if len(args) > 4 else 1
+                if dim == 0 and step == 1 and start % 128 == 0 and (end % 128 == 0 or end == R) and end > start:
+                    return t._row_piece(start, end)
+            if func == aten.new_zeros.default and len(args[1]) == 2 and args[1][1] == C and args[1][0] % 128 == 0:
+                rows = args[1][0]
+                dev = kwargs.get("device") or t._rowwise_data.device
+                per_tile = t._rowwise_scale_inv.numel() // ((R + 127) // 128)
+                return MXFP8Tensor(shape=(rows, C), dtype=t._dtype,
+                                   rowwise_data=torch.zeros(rows, C, dtype=t._rowwise_data.dtype, device=dev),
+                                   rowwise_scale_inv=torch.zeros(rows // 128 * per_tile, dtype=torch.uint8, device=dev),
+                                   columnwise_data=None, columnwise_scale_inv=None, fp8_dtype=t._fp8_dtype,
+                                   quantizer=t._quantizer)
+            if func == aten.view.default and tuple(args[1]) in ((-1,), (R * C,)):
+                # the flat alias that FSDP2 keeps of a sharded parameter: same buffers, 1-D shape (never computed on)
+                return MXFP8Tensor(shape=(R * C,), dtype=t._dtype, rowwise_data=t._rowwise_data,
+                                   rowwise_scale_inv=t._rowwise_scale_inv, columnwise_data=None,
+                                   columnwise_scale_inv=None, fp8_dtype=t._fp8_dtype, quantizer=t._quantizer)
+            if func == aten.copy_.default and isinstance(args[1], MXFP8Tensor) and args[1]._rowwise_data is not None \
+                    and tuple(args[1]._shape) == tuple(t._shape) and args[1]._fp8_dtype == t._fp8_dtype:
+                src = args[1]
+                t._rowwise_data.reshape(R, C).copy_(src._rowwise_data.reshape(R, C))
+                t._rowwise_scale_inv.reshape(-1).copy_(src._rowwise_scale_inv.reshape(-1))
+                t._columnwise_data = t._columnwise_scale_inv = None
+                return t
+        return super().__torch_dispatch__(func, types, args, kwargs)
+
     # ---- FSDP2 extension points (reference: tensor/mxfp8_tensor.py:606-757).  Row shards must be whole
     # 128-row scale tiles; then the row-wise data and its tile-major scales of the shards concatenate
     # byte-wise into the full tensor's, and the column-wise copy is rebuilt after the gather.

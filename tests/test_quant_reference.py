@@ -121,3 +121,20 @@ def test_make_empty_and_update_quantized():
     x = torch.randn(64, 64)
     q.update_quantized(x, t)
     assert torch.equal(t.dequantize(dtype=torch.float32), q(x).dequantize(dtype=torch.float32))
+
+
+def test_standalone_hadamard_transform_matches_the_quantizer():
+    import torch
+    from transformerengine_b200 import ops
+    from transformerengine_b200.ops import quantize as qz
+
+    torch.manual_seed(0)
+    x = torch.randn(64, 48)
+    y = ops.hadamard_transform(x)
+    torch.testing.assert_close(y.norm(), x.norm(), rtol=1e-5, atol=1e-5)          # orthogonal
+    torch.testing.assert_close(ops.hadamard_transform(x, transposed=True), ops.hadamard_transform(x.t().contiguous()))
+    # the quantizer's column-wise amax is the amax of the rotated transpose
+    xb = x.to(torch.bfloat16)
+    res = qz.quantize_nvfp4(xb, with_rht=True)
+    want = ops.hadamard_transform(xb.float(), transposed=True).abs().max()
+    torch.testing.assert_close(res[5].reshape(()).float(), want, rtol=1e-6, atol=0)

@@ -8,6 +8,7 @@ forward to :mod:`transformerengine_b200.fusible`.  The functional layer is also 
 from . import _ext
 from .quantize import (amax, quantize_fp8, dequantize_fp8, quantize_mxfp8, dequantize_mxfp8, quantize_nvfp4,
                        dequantize_nvfp4, swizzle_scales, unswizzle_scales)
+from .quantize import hadamard_transform  # noqa: F401
 from .gemm import gemm_nt, general_gemm, as_operand, Operand, set_mn_major_operands
 from .norm import norm_fwd, norm_bwd
 from .activation import activation_fwd, activation_bwd, is_gated

@@ -235,3 +235,14 @@ def dequantize_nvfp4(packed, scales_swizzled, amax_t, R, C, out_dtype):
         return out
     s = Q.unswizzle_scales(scales_swizzled, R, C // 16)
     return Q.dequantize_nvfp4(packed.reshape(R, C // 2), s, amax_t, out_dtype)
+
+
+def hadamard_transform(x2d: torch.Tensor, transposed: bool = False) -> torch.Tensor:
+    """The 16-point randomised Hadamard transform that the NVFP4 quantizer applies, as a stand-alone operation:
+    every block of 16 consecutive values of a row is multiplied by ``diag(signs) H16 / 4`` (an orthogonal matrix,
+    fixed sign vector).  ``transposed=True`` rotates the rows of ``x^T`` (blocks of 16 consecutive ROWS of ``x``, the
+    token dimension of a weight-gradient operand) and returns ``[C, R]``.  Inside the quantizer the rotation is fused
+    with the cast; this form exists for analysis and tests.  (Reference: ``common/hadamard_transform/hadamard_transform.cu:328``.)"""
+    x = x2d.t().contiguous() if transposed else x2d
+    assert x.dim() == 2 and x.shape[1] % 16 == 0, "the rotated dimension must be a multiple of 16"
+    return Q.apply_rht(x)

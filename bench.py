@@ -49,7 +49,7 @@ def parse():
     ap.add_argument("--tp", type=int, default=0, help="tensor-parallel size; 0 = 8 at 8 GPUs, else 1")
     ap.add_argument("--param-remainders", type=int, default=0,
                     help="keep the fp32 master weights as bf16 parameter + 16-bit remainder (same values, 15 GB less "
-                         "memory; measured 7 % slower per step than plain fp32 masters, so off by default)")
+                         "memory; measured 1 % slower per step than plain fp32 masters, so off by default)")
     ap.add_argument("--zero", type=int, default=-1,
                     help="data parallel: shard the optimizer over the ranks (-1: on whenever there is data parallelism)")
     return ap.parse_args()

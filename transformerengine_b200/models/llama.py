@@ -35,6 +35,15 @@ class LlamaConfig:
     params_dtype: torch.dtype = torch.bfloat16
     recompute: bool = False  # recompute each layer's activations in backward
     quantize_lm_head: bool = True
+    # Variations on the architecture, used by the sibling families (Mistral, Gemma, Qwen3); the defaults are Llama's.
+    head_dim: Optional[int] = None            # None: hidden_size // num_heads
+    activation: str = "swiglu"                # gated activation of the MLP ("geglu" for Gemma)
+    zero_centered_gamma: bool = False         # norm weights stored as (gamma - 1)
+    embedding_scale: Optional[float] = None   # multiply the token embeddings (Gemma: sqrt(hidden_size))
+    tie_embeddings: bool = False              # the output head shares the embedding table
+    sliding_window: Optional[int] = None      # attend to the last N tokens only (Mistral)
+    qk_norm: bool = False                     # RMSNorm over each head of q and k, before the rotation (Qwen3)
+    qk_norm_eps: float = 1e-6
 
     @staticmethod
     def llama3_8b(**kw) -> "LlamaConfig":
@@ -51,18 +60,25 @@ class LlamaConfig:
         d.update(kw)
         return LlamaConfig(**d)
 
+    @property
+    def dim_per_head(self) -> int:
+        return self.head_dim or self.hidden_size // self.num_heads
+
     def num_params(self) -> int:
         h, f, v = self.hidden_size, self.ffn_hidden_size, self.vocab_size
-        hd = h // self.num_heads
-        per_layer = h * (h + 2 * self.num_kv_heads * hd) + h * h + 3 * h * f + 2 * h
-        return self.num_layers * per_layer + 2 * v * h + h
+        hd = self.dim_per_head
+        q = self.num_heads * hd
+        per_layer = h * (q + 2 * self.num_kv_heads * hd) + q * h + 3 * h * f + 2 * h + (2 * hd if self.qk_norm else 0)
+        return self.num_layers * per_layer + (1 if self.tie_embeddings else 2) * v * h + h
 
     def flops_per_token(self, seq_len: int) -> float:
         """Training FLOPs per token (fwd+bwd = 3x forward; causal attention counts half the square)."""
         h, f, v = self.hidden_size, self.ffn_hidden_size, self.vocab_size
-        hd = h // self.num_heads
-        gemm = self.num_layers * (h * (h + 2 * self.num_kv_heads * hd) + h * h + 3 * h * f) + v * h
-        attn = self.num_layers * 2 * seq_len * h / 2  # QK^T and PV, causal
+        hd = self.dim_per_head
+        q = self.num_heads * hd
+        gemm = self.num_layers * (h * (q + 2 * self.num_kv_heads * hd) + q * h + 3 * h * f) + v * h
+        span = min(seq_len, 2 * self.sliding_window) if self.sliding_window else seq_len
+        attn = self.num_layers * 2 * span * q / 2  # QK^T and PV, causal
         return 6.0 * gemm + 6.0 * attn
 
 
@@ -172,22 +188,30 @@ class LlamaModel(torch.nn.Module):
         init = lambda t: torch.nn.init.normal_(t, 0.0, cfg.init_std)  # noqa: E731
         self.embedding = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, tp_group, self.sp, cfg.params_dtype,
                                                 device, cfg.init_std)
+        window = (cfg.sliding_window - 1, 0) if cfg.sliding_window else None
         self.layers = torch.nn.ModuleList([
             TransformerLayer(cfg.hidden_size, cfg.ffn_hidden_size, cfg.num_heads, num_gqa_groups=cfg.num_kv_heads,
                              layernorm_epsilon=cfg.rms_eps, hidden_dropout=0.0, attention_dropout=0.0,
                              init_method=init, output_layer_init_method=init, layer_number=i + 1,
-                             self_attn_mask_type="causal", tp_group=tp_group, tp_size=self.tp_size,
+                             kv_channels=cfg.head_dim, self_attn_mask_type="causal", window_size=window,
+                             tp_group=tp_group, tp_size=self.tp_size,
                              params_dtype=cfg.params_dtype, sequence_parallel=self.sp,
                              set_parallel_mode=self.tp_size > 1, fuse_qkv_params=True, qkv_weight_interleaved=False,
-                             bias=False, activation="swiglu", normalization="RMSNorm", device=device,
-                             attn_input_format="sbhd")
+                             zero_centered_gamma=cfg.zero_centered_gamma,
+                             bias=False, activation=cfg.activation, normalization="RMSNorm", device=device,
+                             attn_input_format="sbhd", qk_norm_type="RMSNorm" if cfg.qk_norm else None,
+                             qk_norm_eps=cfg.qk_norm_eps, qk_norm_before_rope=True)
             for i in range(cfg.num_layers)])
         self.final_norm = RMSNorm(cfg.hidden_size, eps=cfg.rms_eps, sequence_parallel=self.sp,
-                                  params_dtype=cfg.params_dtype, device=device)
+                                  params_dtype=cfg.params_dtype, zero_centered_gamma=cfg.zero_centered_gamma,
+                                  device=device)
         self.lm_head = Linear(cfg.hidden_size, cfg.vocab_size, bias=False, init_method=init,
                               params_dtype=cfg.params_dtype, device=device, tp_group=tp_group, tp_size=self.tp_size,
                               parallel_mode="column" if self.tp_size > 1 else None, sequence_parallel=self.sp)
-        self.rope = RotaryPositionEmbedding(cfg.hidden_size // cfg.num_heads, rotary_base=cfg.rope_theta)
+        if cfg.tie_embeddings:
+            # one table for both ends (vocabulary-sharded the same way under tensor parallelism)
+            self.lm_head.weight = self.embedding.weight
+        self.rope = RotaryPositionEmbedding(cfg.dim_per_head, rotary_base=cfg.rope_theta)
         self._rope_cache = {}
 
     def _freqs(self, s: int, device):
@@ -197,15 +221,43 @@ class LlamaModel(torch.nn.Module):
             self._rope_cache[(s, str(device))] = f
         return f
 
-    def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None):
+    logits_seq_first = True  # forward returns [s, b, vocab]
+
+    def make_inference_params(self, max_batch_size: int, max_sequence_length: int, **kw):
+        """Key/value cache for incremental decoding with this model (``is_paged``, ``page_size``,
+        ``total_num_pages`` pass through to ``InferenceParams``)."""
+        from ..attention.inference import InferenceParams
+        cfg = self.cfg
+        p = next(self.parameters())
+        kw.setdefault("device", p.device)
+        return InferenceParams(max_batch_size, max_sequence_length, num_heads_kv=cfg.num_kv_heads // self.tp_size,
+                               head_dim_k=cfg.dim_per_head, dtype=cfg.params_dtype,
+                               qkv_format="sbhd", **kw)
+
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int, **kw) -> torch.Tensor:
+        """Decoding on the key/value cache; see ``models.generation.generate`` for the options."""
+        from .generation import generate
+        return generate(self, prompt, max_new_tokens, **kw)
+
+    def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None, inference_params=None):
         """tokens [b, s] int64.  Returns the mean next-token loss when ``labels`` is given
-        (labels are shifted inside), else logits ``[s, b, vocab(/tp)]``."""
+        (labels are shifted inside), else logits ``[s, b, vocab(/tp)]``.  With ``inference_params`` the tokens
+        are the NEW tokens of each sequence (``inference_params.pre_step`` names their counts) and attention
+        runs against the key/value cache."""
         b, s = tokens.shape
         ids = tokens.t().contiguous()  # [s, b]
         x = self.embedding(ids)
-        freqs = self._freqs(s, x.device)
+        if self.cfg.embedding_scale is not None:
+            x = x * torch.tensor(self.cfg.embedding_scale, dtype=x.dtype)   # rounded to the activation dtype first
+        if inference_params is not None:
+            assert not self.sp, "incremental decoding runs without sequence parallelism"
+            freqs = self._freqs(inference_params.max_sequence_length, x.device)
+        else:
+            freqs = self._freqs(s, x.device)
         for layer in self.layers:
-            if self.cfg.recompute and torch.is_grad_enabled():
+            if inference_params is not None:
+                x = layer(x, rotary_pos_emb=freqs, inference_params=inference_params)
+            elif self.cfg.recompute and torch.is_grad_enabled():
                 x = D.checkpoint(layer, x, rotary_pos_emb=freqs)
             else:
                 x = layer(x, rotary_pos_emb=freqs)

@@ -147,8 +147,8 @@ class MixtralBlock(torch.nn.Module):
         self.pre_moe_norm = RMSNorm(cfg.hidden_size, eps=cfg.rms_eps, params_dtype=cfg.params_dtype, device=device)
         self.moe = MoELayer(cfg, ep_group, device)
 
-    def forward(self, x, freqs):
-        x = x + self.attn(x, rotary_pos_emb=freqs)
+    def forward(self, x, freqs, inference_params=None):
+        x = x + self.attn(x, rotary_pos_emb=freqs, inference_params=inference_params)
         s, b, h = x.shape
         y, aux = self.moe(self.pre_moe_norm(x).reshape(s * b, h))
         return x + y.reshape(s, b, h), aux
@@ -168,13 +168,30 @@ class MixtralModel(torch.nn.Module):
                               params_dtype=cfg.params_dtype, device=device)
         self.rope = RotaryPositionEmbedding(cfg.hidden_size // cfg.num_heads, rotary_base=cfg.rope_theta)
 
-    def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None):
+    logits_seq_first = True  # forward returns [s, b, vocab]
+
+    def make_inference_params(self, max_batch_size: int, max_sequence_length: int, **kw):
+        """Key/value cache for incremental decoding with this model."""
+        from ..attention.inference import InferenceParams
+        cfg = self.cfg
+        kw.setdefault("device", self.embedding.weight.device)
+        return InferenceParams(max_batch_size, max_sequence_length, num_heads_kv=cfg.num_kv_heads,
+                               head_dim_k=cfg.hidden_size // cfg.num_heads, dtype=cfg.params_dtype,
+                               qkv_format="sbhd", **kw)
+
+    def generate(self, prompt: torch.Tensor, max_new_tokens: int, **kw) -> torch.Tensor:
+        """Decoding on the key/value cache; see ``models.generation.generate`` for the options."""
+        from .generation import generate
+        return generate(self, prompt, max_new_tokens, **kw)
+
+    def forward(self, tokens: torch.Tensor, labels: Optional[torch.Tensor] = None, inference_params=None):
         ids = tokens.t().contiguous()
         x = self.embedding(ids)
-        freqs = self.rope(tokens.shape[1]).to(x.device)
+        n_pos = tokens.shape[1] if inference_params is None else inference_params.max_sequence_length
+        freqs = self.rope(n_pos).to(x.device)
         aux_total = 0.0
         for layer in self.layers:
-            x, aux = layer(x, freqs)
+            x, aux = layer(x, freqs, inference_params)
             aux_total = aux_total + aux
         logits = self.lm_head(self.final_norm(x))
         if labels is None:

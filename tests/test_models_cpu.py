@@ -198,3 +198,111 @@ def test_checkpoint_loads_into_tensor_parallel_shards():
         p.join(120)
         assert p.exitcode == 0
     assert torch.allclose(got.transpose(0, 1), want, atol=2e-5), float((got.transpose(0, 1) - want).abs().max())
+
+
+# ------------------------------------------------------------------ GPT-2, BERT, T5
+def _perturb(m, names):
+    with torch.no_grad():
+        for k, p in m.named_parameters():
+            if any(n in k for n in names):
+                p.add_(torch.randn_like(p) * 0.1)
+
+
+def test_gpt2_checkpoint_matches_hugging_face():
+    from transformerengine_b200.models.gpt import gpt_from_hf
+    T = transformers
+    ref = T.GPT2LMHeadModel(T.GPT2Config(vocab_size=128, n_positions=64, n_embd=64, n_layer=2, n_head=4,
+                                         attn_implementation="eager", resid_pdrop=0.0, embd_pdrop=0.0,
+                                         attn_pdrop=0.0)).eval()
+    _perturb(ref, ("ln_", "bias"))
+    ours = gpt_from_hf(ref, device="cpu", params_dtype=torch.float32).eval()
+    assert ours.lm_head.weight is ours.embedding.weight
+    assert sum(p.numel() for p in ours.parameters()) == ours.cfg.num_params()
+    tokens = torch.randint(0, 128, (2, 12))
+    with torch.no_grad():
+        want = ref(tokens).logits
+        got = ours(tokens).transpose(0, 1)
+    assert torch.allclose(got, want, atol=2e-5), float((got - want).abs().max())
+    assert torch.equal(ours.generate(tokens, 4), _greedy_by_recompute(ours, tokens, 4))
+    loss = ours.train()(tokens, labels=tokens)
+    want_loss = ref(tokens, labels=tokens).loss
+    # the library's loss averages over all b * s rows (the last position has no target and counts as ignored)
+    assert torch.allclose(loss, want_loss, atol=1e-4), (float(loss), float(want_loss))
+
+
+def test_bert_checkpoint_matches_hugging_face():
+    from transformerengine_b200.models.bert import bert_from_hf
+    T = transformers
+    ref = T.BertForMaskedLM(T.BertConfig(vocab_size=128, max_position_embeddings=64, hidden_size=64,
+                                         num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                                         hidden_act="gelu_pytorch_tanh", attn_implementation="eager",
+                                         hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)).eval()
+    _perturb(ref, ("LayerNorm", "bias"))
+    ours = bert_from_hf(ref, device="cpu", params_dtype=torch.float32).eval()
+    tokens = torch.randint(0, 128, (2, 12))
+    mask = torch.ones(2, 12, dtype=torch.long)
+    mask[1, 8:] = 0
+    segments = torch.randint(0, 2, (2, 12))
+    with torch.no_grad():
+        want = ref(tokens, attention_mask=mask, token_type_ids=segments).logits
+        got = ours(tokens, mask, segments).transpose(0, 1)
+    assert torch.isfinite(got).all()
+    assert torch.allclose(got[mask.bool()], want[mask.bool()], atol=2e-5)
+    labels = tokens.clone()
+    labels[mask == 0] = -100
+    loss = ours.train()(tokens, mask, segments, labels=labels)
+    loss.backward()
+    want_loss = ref(tokens, attention_mask=mask, token_type_ids=segments, labels=labels).loss
+    assert torch.allclose(loss, want_loss, atol=1e-4)
+    assert ours.word_embeddings.weight.grad is not None
+
+
+@pytest.mark.parametrize("mlp,tied", [("gated-gelu", False), ("relu", True)])
+def test_t5_checkpoint_matches_hugging_face(mlp, tied):
+    from transformerengine_b200.models.t5 import t5_from_hf
+    T = transformers
+    ref = T.T5ForConditionalGeneration(T.T5Config(
+        vocab_size=128, d_model=64, d_kv=24, d_ff=128, num_layers=2, num_decoder_layers=2, num_heads=4,
+        relative_attention_num_buckets=8, relative_attention_max_distance=16, feed_forward_proj=mlp,
+        tie_word_embeddings=tied, dropout_rate=0.0, decoder_start_token_id=0, attn_implementation="eager")).eval()
+    with torch.no_grad():
+        for k, p in ref.named_parameters():
+            if "layer_norm" in k:
+                p.add_(torch.randn_like(p) * 0.1)
+            elif "relative" in k:
+                p.normal_(0, 0.5)
+            elif k == "shared.weight":
+                p.mul_(0.3)
+    ours = t5_from_hf(ref, device="cpu", params_dtype=torch.float32).eval()
+    assert ours.cfg.scale_decoder_outputs == tied
+    tokens, dec = torch.randint(1, 128, (2, 20)), torch.randint(1, 128, (2, 9))
+    mask = torch.ones(2, 20, dtype=torch.long)
+    mask[1, 13:] = 0
+    with torch.no_grad():
+        want = ref(input_ids=tokens, attention_mask=mask, decoder_input_ids=dec).logits
+        got = ours(tokens, mask, decoder_tokens=dec).transpose(0, 1)
+    assert torch.allclose(got, want, atol=5e-5, rtol=1e-5), float((got - want).abs().max())
+    labels = torch.randint(1, 128, (2, 9))
+    labels[0, 6:] = -100
+    loss = ours.train()(tokens, mask, labels=labels)
+    loss.backward()
+    want_loss = ref(input_ids=tokens, attention_mask=mask, labels=labels).loss
+    assert torch.allclose(loss, want_loss, atol=1e-4), (float(loss), float(want_loss))
+    # greedy decoding: first tokens agree with the reference implementation's own loop
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        theirs = ref.generate(input_ids=tokens, attention_mask=mask, max_new_tokens=3, do_sample=False)
+    mine = ours.generate(tokens, 3, mask)
+    assert torch.equal(mine[:, :2], theirs[:, :2])
+
+
+def test_relative_position_buckets():
+    from transformerengine_b200.models.t5 import relative_position_bucket
+    rel = torch.arange(-40, 41)
+    uni = relative_position_bucket(rel, False, 8, 16)
+    assert uni[rel >= 0].eq(0).all()                       # a causal stack never looks ahead
+    assert uni[rel == -1] == 1 and uni[rel == -3] == 3     # exact buckets for small offsets
+    assert uni[rel <= -16].eq(7).all()                     # one bucket beyond max_distance
+    assert (uni[:-1] >= uni[1:]).all()                     # monotone in the distance
+    bi = relative_position_bucket(rel, True, 8, 16)
+    assert bi[rel < 0].max() < 4 <= bi[rel > 0].min()      # half of the buckets per direction

@@ -74,6 +74,47 @@ def _worker(rank, world, port, q):
             want = ref.weight.grad.chunk(world, dim=0)[rank]
             if not torch.allclose(g, want, rtol=1e-4, atol=1e-4):
                 bad[f"{name}: wgrad shard"] = float((g - want).abs().max())
+        # several optimizer steps: the shards are re-quantized by the optimizer (fp32 master weights), and what the
+        # next forward pass sees must be exactly the gathered shards (one scale for per-tensor FP8, fresh bytes for
+        # MXFP8), i.e. training makes progress and all ranks hold the same full weight
+        for name, rec, cls in (("current", R.Float8CurrentScaling(), Float8Tensor),
+                               ("mxfp8", R.MXFP8BlockScaling(), MXFP8Tensor)):
+            torch.manual_seed(0)
+            with te.quantized_model_init(enabled=True, recipe=rec):
+                lin = te.Linear(256, 256, bias=False, params_dtype=torch.float32, device="cpu")
+            fully_shard(lin)
+            opt = te.FusedAdam(lin.parameters(), lr=1e-2, master_weights=True)
+            torch.manual_seed(7 + rank)
+            x = torch.randn(128, 256)
+            seen, losses = [], []
+            orig = lin.get_quantized_weight
+
+            def spy(weight, quantizer, **kw):
+                seen.append((type(weight), weight.dequantize().clone()))
+                return orig(weight, quantizer, **kw)
+
+            lin.get_quantized_weight = spy
+            for _ in range(4):
+                opt.zero_grad()
+                with te.autocast(enabled=True, recipe=rec):
+                    loss = lin(x).square().mean()
+                loss.backward()
+                opt.step()
+                losses.append(float(loss.detach()))
+            if not all(t is cls for t, _ in seen):
+                bad[f"{name}: gathered parameter type"] = str([t.__name__ for t, _ in seen])
+            if not losses[-1] < 0.7 * losses[0]:
+                bad[f"{name}: no progress over optimizer steps"] = str(losses)
+            # the weight of the last forward pass == the shards after the third step, gathered in high precision
+            local = lin.weight._local_tensor
+            # (roll back one step is not possible; compare the NEXT gather instead)
+            with te.autocast(enabled=True, recipe=rec):
+                lin(x)
+            parts = [torch.empty(256 // world, 256) for _ in range(world)]
+            dist.all_gather(parts, local.dequantize().contiguous())
+            full = torch.cat(parts)
+            if not torch.equal(seen[-1][1], full):
+                bad[f"{name}: gathered weight != shards"] = float((seen[-1][1] - full).abs().max())
         q.put((rank, bad, None))
     except Exception:  # noqa: BLE001
         import traceback

@@ -405,3 +405,52 @@ def test_transformer_layer_passes_rotary_interleaving_to_attention():
     r1 = apply_rotary_pos_emb(q, freqs, "sbhd", interleaved=True)
     r2 = apply_rotary_pos_emb(q, freqs, "sbhd", interleaved=True, fused=False)
     torch.testing.assert_close(r1, r2)
+
+
+@pytest.mark.parametrize("name", ["delayed", "current", "mxfp8", "block"])
+@pytest.mark.parametrize("kind", ["layernorm_linear", "layernorm_mlp", "grouped_linear", "transformer_layer"])
+def test_quantized_model_init_covers_every_module(name, kind):
+    """Parameters created under ``quantized_model_init`` are quantized tensors in every GEMM module, and a module
+    built that way computes exactly what a high-precision module holding the dequantized values computes."""
+    from transformerengine_b200.tensor.base import QuantizedTensorStorage
+    rec = {"delayed": R.DelayedScaling, "current": R.Float8CurrentScaling, "mxfp8": R.MXFP8BlockScaling,
+           "block": R.Float8BlockScaling}[name]()
+
+    def build():
+        torch.manual_seed(0)
+        kw = dict(params_dtype=torch.float32, device="cpu")
+        if kind == "layernorm_linear":
+            return te.LayerNormLinear(128, 256, normalization="RMSNorm", bias=True, **kw), 1
+        if kind == "layernorm_mlp":
+            return te.LayerNormMLP(128, 256, normalization="RMSNorm", activation="swiglu", bias=False, **kw), 2
+        if kind == "grouped_linear":
+            return te.GroupedLinear(2, 128, 128, bias=False, **kw), 2
+        return te.TransformerLayer(128, 256, 4, hidden_dropout=0.0, attention_dropout=0.0, fuse_qkv_params=False,
+                                   **kw), 6          # query / key / value, proj, fc1, fc2
+
+    with te.quantized_model_init(enabled=True, recipe=rec, preserve_high_precision_init_val=True):
+        q, expect = build()
+    ref, _ = build()
+    quantized = [p for p in q.parameters() if isinstance(p, QuantizedTensorStorage)]
+    assert len(quantized) == expect
+    assert all(getattr(p, "_high_precision_init_val", None) is not None for p in quantized)
+    with torch.no_grad():
+        for p, pr in zip(q.parameters(), ref.parameters()):
+            pr.copy_(p.dequantize() if isinstance(p, QuantizedTensorStorage) else p)
+    x = torch.randn(32, 2, 128) if kind == "transformer_layer" else torch.randn(64, 128)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    extra = ([32, 32],) if kind == "grouped_linear" else ()
+    with te.autocast(enabled=True, recipe=rec):
+        ya, yb = q(xa, *extra), ref(xb, *extra)
+    ya.square().sum().backward()
+    yb.square().sum().backward()
+    assert torch.allclose(ya, yb, atol=1e-6)
+    assert torch.allclose(xa.grad, xb.grad, atol=1e-5)
+    for p, pr in zip(q.parameters(), ref.parameters()):
+        assert p.grad is not None and p.grad.shape == pr.grad.shape
+        assert torch.allclose(p.grad, pr.grad, atol=1e-4), float((p.grad - pr.grad).abs().max())
+    # the optimizer keeps fp32 masters that start from the unrounded initial values and writes back quantized
+    opt = te.FusedAdam(q.parameters(), lr=1e-2, master_weights=True)
+    before = quantized[0].dequantize().clone()
+    opt.step()
+    assert isinstance(quantized[0], QuantizedTensorStorage) and not torch.equal(before, quantized[0].dequantize())

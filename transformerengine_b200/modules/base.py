@@ -166,6 +166,33 @@ class TransformerEngineBaseModule(torch.nn.Module):
         if pending is not None:
             self._apply_loaded_state(pending)
 
+    def _quantize_primary_weights(self, weight_names) -> None:
+        """``quantized_model_init``: replace the named high-precision weights by quantized parameters (both copies,
+        so that forward, dgrad and wgrad read the parameter's own payload).  The quantizers come from a recipe state
+        of their own: they describe how the PARAMETER is stored, whatever recipe later forward passes run under."""
+        from ..quantization import RecipeState
+
+        recipe = FP8GlobalStateManager.FP8_MODEL_INIT_RECIPE
+        st = RecipeState.create(recipe, mode="forward", num_quantizers=3, device=self._param_device())
+        self._primary_state = st
+        q = st.make_quantizers()[1]
+        q.internal = False
+        for n in weight_names:
+            w = getattr(self, n)
+            hp = w.detach()
+            qt = q.copy()(hp) if hasattr(q, "copy") else q(hp)
+            p = torch.nn.Parameter(qt)
+            if self.preserve_high_precision_init_val:
+                # kept on the host until the optimizer has built its master weights from it
+                # (reference: module/base.py, get_/clear_high_precision_init_val on the parameter)
+                p._high_precision_init_val = hp.cpu().clone()
+                p.get_high_precision_init_val = (lambda p=p: getattr(p, "_high_precision_init_val", None))
+                p.clear_high_precision_init_val = (lambda p=p: p.__dict__.pop("_high_precision_init_val", None) and None)
+            for attr in ("tensor_model_parallel", "partition_dim", "partition_stride", "sequence_parallel"):
+                if hasattr(w, attr):
+                    setattr(p, attr, getattr(w, attr))
+            self.register_parameter(n, p)
+
     def _param_device(self):
         for p in self.parameters(recurse=False):
             return p.device
@@ -229,6 +256,8 @@ class TransformerEngineBaseModule(torch.nn.Module):
         if quantizer is None:
             return weight
         if isinstance(weight, QuantizedTensorStorage):
+            if need_columnwise and hasattr(weight, "ensure_columnwise"):
+                weight.ensure_columnwise()
             return weight
         quantizer.set_usage(rowwise=True, columnwise=need_columnwise)
         quantizer.internal = True

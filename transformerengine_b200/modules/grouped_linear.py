@@ -264,6 +264,9 @@ class GroupedLinear(TransformerEngineBaseModule):
             if bias:
                 self.register_parameter(f"bias{i}", torch.nn.Parameter(
                     torch.zeros(out_features, device=device, dtype=params_dtype)))
+        if self.primary_weights_in_fp8:
+            self._quantize_primary_weights([f"weight{i}" for i in range(num_gemms)])
+            self._stacked = None
 
     def forward(self, inp: torch.Tensor, m_splits: List[int], is_first_microbatch: Optional[bool] = None):
         assert len(m_splits) == self.num_gemms, "one row count per GEMM"

@@ -271,6 +271,9 @@ class LayerNormLinear(TransformerEngineBaseModule):
                 self.register_parameter(f"{n}bias", bp)
             off += s
         self._fused_weight_storage = wt if len(names) > 1 else None
+        if self.primary_weights_in_fp8:
+            self._quantize_primary_weights(self.weight_names)
+            self._fused_weight_storage = None
         self.cfg = F.LinearConfig(parallel_mode=self.parallel_mode, sequence_parallel=self.sequence_parallel,
                                   tp_group=self.tp_group, tp_size=self.tp_size,
                                   fuse_wgrad_accumulation=fuse_wgrad_accumulation, activation_dtype=params_dtype,
@@ -290,7 +293,7 @@ class LayerNormLinear(TransformerEngineBaseModule):
                 for i, x in enumerate(ws)):
             w = _ConcatView.apply(self._fused_weight_storage, *ws)
         else:
-            w = torch.cat(ws, dim=0)
+            w = torch.cat([x.dequantize() if isinstance(x, QuantizedTensorStorage) else x for x in ws], dim=0)
         b = None
         if self.use_bias:
             bs = [getattr(self, n) for n in self.bias_names]

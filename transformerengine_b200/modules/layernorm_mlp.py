@@ -227,6 +227,8 @@ class LayerNormMLP(TransformerEngineBaseModule):
                     setattr(self.fc2_bias, "sequence_parallel", True)
         else:
             self.fc1_bias = self.fc2_bias = None
+        if self.primary_weights_in_fp8:
+            self._quantize_primary_weights(("fc1_weight", "fc2_weight"))
         mode1 = "column" if set_parallel_mode else None
         mode2 = "row" if set_parallel_mode else None
         self.cfg1 = F.LinearConfig(parallel_mode=mode1, sequence_parallel=self.sequence_parallel,

@@ -227,7 +227,8 @@ class Linear(TransformerEngineBaseModule):
         self._fused_weight_storage = weight_tensor if len(names) > 1 else None
         self._fused_bias_storage = bias_tensor if (len(names) > 1 and bias) else None
         if self.primary_weights_in_fp8:
-            self._quantize_primary_weights()
+            self._quantize_primary_weights(self.weight_names)
+            self._fused_weight_storage = None
         self.cfg = F.LinearConfig(parallel_mode=self.parallel_mode, sequence_parallel=self.sequence_parallel,
                                   tp_group=self.tp_group, tp_size=self.tp_size,
                                   fuse_wgrad_accumulation=fuse_wgrad_accumulation,
@@ -240,24 +241,6 @@ class Linear(TransformerEngineBaseModule):
                 init_method(w)
         else:
             init_method(w)
-
-    def _quantize_primary_weights(self) -> None:
-        """``quantized_model_init``: replace 16-bit weights by quantized parameters."""
-        from ..quantization import RecipeState
-
-        recipe = FP8GlobalStateManager.FP8_MODEL_INIT_RECIPE
-        st = RecipeState.create(recipe, mode="forward", num_quantizers=3, device=self._param_device())
-        self._primary_state = st
-        q = st.make_quantizers()[1]
-        q.internal = False
-        for n in self.weight_names:
-            w = getattr(self, n)
-            hp = w.detach()
-            qt = q.copy()(hp) if hasattr(q, "copy") else q(hp)
-            if self.preserve_high_precision_init_val:
-                qt._high_precision_init_val = hp.cpu().clone()
-            self.register_parameter(n, torch.nn.Parameter(qt))
-        self._fused_weight_storage = None
 
     def set_tensor_parallel_group(self, tp_group) -> None:
         super().set_tensor_parallel_group(tp_group)

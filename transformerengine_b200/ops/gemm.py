@@ -65,6 +65,8 @@ def as_operand(t, usage: str = "rowwise") -> Operand:
         if row:
             assert t._rowwise_data is not None, "MXFP8 operand lacks the rowwise copy"
             return Operand("mxfp8", t._rowwise_data.reshape(R, C), t._rowwise_scale_inv, t._fp8_dtype, rows=R, k=C)
+        if t._columnwise_data is None:
+            t.ensure_columnwise()      # a parameter re-gathered by FSDP2 for the backward pass: row-wise bytes only
         assert t._columnwise_data is not None, "MXFP8 operand lacks the columnwise copy"
         return Operand("mxfp8", t._columnwise_data, t._columnwise_scale_inv, t._fp8_dtype, rows=C, k=R)
     if isinstance(t, NVFP4TensorStorage):

@@ -15,6 +15,13 @@ from ..modules.base import bump_weights_epoch
 from ..tensor.base import QuantizedTensor
 
 
+def _local(t):
+    """The shard this rank owns when ``t`` is a ``DTensor`` (FSDP2 ``fully_shard`` parameters and their gradients):
+    the optimizer state is kept for, and the kernels run on, the local shard; plain tensors pass through."""
+    loc = getattr(t, "_local_tensor", None)
+    return loc if loc is not None else t
+
+
 class FusedAdam(torch.optim.Optimizer):
     def __init__(self, params, lr: float = 1e-3, bias_correction: bool = True, betas=(0.9, 0.999),
                  eps: float = 1e-8, adam_w_mode: bool = True, weight_decay: float = 0.0, amsgrad: bool = False,
@@ -54,8 +61,10 @@ class FusedAdam(torch.optim.Optimizer):
                 elif p.grad is not None:
                     p.grad.zero_()
 
-    def _init_state(self, p):
-        st = self.state[p]
+    def _init_state(self, key, p):
+        """``key`` is the parameter the optimizer was given, ``p`` its local data (the same object unless the
+        parameter is a sharded ``DTensor``)."""
+        st = self.state[key]
         if "exp_avg" not in st:
             base = p.dequantize() if isinstance(p, QuantizedTensor) else p.detach()
             st["exp_avg"] = torch.zeros(base.shape, dtype=self.state_dtype, device=base.device)
@@ -114,9 +123,13 @@ class FusedAdam(torch.optim.Optimizer):
                     continue
                 if getattr(p, "grad_added_to_main_grad", False) and g.numel() > 1 and g.stride() == (0,) * g.dim():
                     continue  # placeholder returned when the wgrad GEMM accumulated into main_grad
+                g = _local(g)
                 if not g.is_contiguous():
                     g = g.contiguous()
-                st = self._init_state(p)
+                key_param, p = p, _local(p)
+                if p.numel() == 0:
+                    continue    # this rank's shard of a small sharded parameter is empty
+                st = self._init_state(key_param, p)
                 if isinstance(p, QuantizedTensor):
                     quantized.append((p, g, st))
                     continue

@@ -141,6 +141,11 @@ class Float8Tensor(Float8TensorStorage, QuantizedTensor):
     def fsdp_pre_all_gather(self, mesh=None, orig_size=None, contiguous_orig_stride=None, module=None, mp_policy=None):
         if self._data is None:
             self.update_usage(rowwise_usage=True)
+        q = self._quantizer
+        if mesh is not None and hasattr(q, "with_amax_reduction") and not q.with_amax_reduction:
+            # the gathered tensor has ONE scale: from now on every re-quantization of this shard (the optimizer's
+            # write-back) takes its amax over all shards, so that the ranks keep agreeing on that scale
+            q.with_amax_reduction, q.amax_reduction_group = True, mesh.get_group(mesh.ndim - 1)
         return (self._data.view(torch.uint8),), (self._scale_inv, self._fp8_dtype, self._dtype, self._quantizer)
 
     def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype=None, *, out=None):

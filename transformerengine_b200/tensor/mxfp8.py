@@ -55,6 +55,20 @@ class MXFP8TensorStorage(QuantizedTensorStorage):
         if columnwise_usage is False:
             self._columnwise_data = self._columnwise_scale_inv = None
 
+    def ensure_columnwise(self) -> None:
+        """Build the column-wise copy from the row-wise one when it is missing (a parameter that FSDP2 has just
+        gathered carries only the row-wise bytes).  The row-wise values are exact in bf16, so this is a second
+        rounding of already rounded values, along the other direction; only dgrad reads the result."""
+        if self._columnwise_data is not None or self._rowwise_data is None or len(self._shape) != 2:
+            return
+        R, C = self._rows_cols()
+        if R % 32 or C % 32:
+            return
+        hp = ops.dequantize_mxfp8(self._rowwise_data.reshape(R, C), self._rowwise_scale_inv, self._fp8_dtype,
+                                  torch.bfloat16)
+        _, _, cd, cs = ops.quantize_mxfp8(hp, self._fp8_dtype, rowwise=False, columnwise=True)
+        self._columnwise_data, self._columnwise_scale_inv = cd, cs
+
     def _dequantize_impl(self, dtype=None):
         dtype = dtype or self._dtype
         R, C = self._rows_cols()
@@ -165,6 +179,14 @@ class MXFP8Tensor(MXFP8TensorStorage, QuantizedTensor):
                 return MXFP8Tensor(shape=(R * C,), dtype=t._dtype, rowwise_data=t._rowwise_data,
                                    rowwise_scale_inv=t._rowwise_scale_inv, columnwise_data=None,
                                    columnwise_scale_inv=None, fp8_dtype=t._fp8_dtype, quantizer=t._quantizer)
+            if func == aten.as_strided.default and tuple(args[1]) == (R, C) and tuple(args[2]) == (C, 1) \
+                    and not (len(args) > 3 and args[3]):
+                # FSDP2 restrides the gathered tensor to the parameter's original (contiguous) layout: an alias
+                # over the same buffers, so that later all-gathers into them show through the parameter
+                return MXFP8Tensor(shape=(R, C), dtype=t._dtype, rowwise_data=t._rowwise_data,
+                                   rowwise_scale_inv=t._rowwise_scale_inv, columnwise_data=t._columnwise_data,
+                                   columnwise_scale_inv=t._columnwise_scale_inv, fp8_dtype=t._fp8_dtype,
+                                   quantizer=t._quantizer)
             if func == aten.copy_.default and isinstance(args[1], MXFP8Tensor) and args[1]._rowwise_data is not None \
                     and tuple(args[1]._shape) == tuple(t._shape) and args[1]._fp8_dtype == t._fp8_dtype:
                 src = args[1]

@@ -82,3 +82,52 @@ def test_top_level_names_of_the_reference_front_end_exist():
         assert hasattr(te, name), name
     assert te.DType.kFloat8E4M3 == te.constants.TE_DType[torch.float8_e4m3fn]
     assert str(te.QuantizerRole(module_type="linear", tensor_type="input")) == "module_type=linear|tensor_type=input"
+
+
+def test_delayed_scaling_requests_as_children_of_a_hybrid_quantizer():
+    """Requests may stand in for the children of a ``HybridQuantizer``: the recipe state gives each child its own
+    slot of the amax history.  Two delayed children reproduce the DelayedScaling recipe bit for bit; a delayed
+    row-wise child next to an MXFP8 column-wise child runs and keeps a history."""
+    from transformerengine_b200.common import recipe as R
+    from transformerengine_b200.custom_recipes.quantizer_factories import tensor_type
+    from transformerengine_b200.tensor.mxfp8 import MXFP8Quantizer
+
+    req = te.DelayedScalingRequest(amax_history_len=4, margin=0)
+
+    def both(role):
+        if tensor_type(role) in ("output", "grad_input"):
+            return None
+        return te.HybridQuantizer(rowwise_quantizer=req, columnwise_quantizer=req)
+
+    def mixed(role):
+        if tensor_type(role) in ("output", "grad_input"):
+            return None
+        return te.HybridQuantizer(rowwise_quantizer=req, columnwise_quantizer=MXFP8Quantizer())
+
+    def run(rec):
+        torch.manual_seed(0)
+        lin = te.Linear(32, 32, bias=False, params_dtype=torch.float32, device="cpu")
+        outs = []
+        for step in range(4):
+            x = (torch.randn(32, 32) * (step + 1)).requires_grad_()
+            with te.autocast(enabled=True, recipe=rec):
+                y = lin(x)
+            y.square().sum().backward()
+            outs.append((y.detach().clone(), x.grad.clone(), lin.weight.grad.clone()))
+            lin.weight.grad = None
+        return outs, lin
+
+    a, _ = run(R.CustomRecipe(qfactory=both))
+    b, _ = run(R.DelayedScaling(amax_history_len=4, margin=0))
+    for ta, tb in zip(a, b):
+        for u, v in zip(ta, tb):
+            torch.testing.assert_close(u, v, rtol=0, atol=0)
+    c, lin = run(R.CustomRecipe(qfactory=mixed))
+    for (yc, gx, gw), (yb, _, _) in zip(c, b):
+        assert torch.isfinite(gx).all() and torch.isfinite(gw).all()
+        assert (yc - yb).abs().max() < 0.1 * yb.abs().max()
+    inner = lin._states["scaling_fwd"].delayed
+    assert inner is not None and inner.amax_history.shape[1] == 2       # input and weight: one row-wise child each
+    assert float(inner.scale.min()) > 0 and not torch.equal(inner.scale, torch.ones_like(inner.scale))
+    with pytest.raises(RuntimeError, match="unresolved"):
+        te.HybridQuantizer(rowwise_quantizer=req, columnwise_quantizer=MXFP8Quantizer())(torch.randn(32, 32))

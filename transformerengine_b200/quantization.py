@@ -122,7 +122,9 @@ class QuantizerRole:
 @dataclasses.dataclass(frozen=True)
 class QuantizerRequest:
     """Base class of the requests a ``CustomRecipe`` factory may return instead of a quantizer when the quantizer
-    needs state that the library manages."""
+    needs state that the library manages.  A request may also stand in for a child of a ``HybridQuantizer``."""
+
+    _is_quantizer_request = True
 
 
 @dataclasses.dataclass(frozen=True)
@@ -243,11 +245,21 @@ class CustomRecipeState(RecipeState):
 
     def make_quantizers(self):
         roles = self._FWD if self.mode == "forward" else self._BWD
+        from .tensor.hybrid import HybridQuantizer
+
         out = [self.recipe.qfactory(roles[i % len(roles)]) for i in range(self.num_quantizers)]
-        asked = [i for i, q in enumerate(out) if isinstance(q, DelayedScalingRequest)]
+        # (place to put the quantizer, request): whole slots, and children of hybrid quantizers
+        asked = []
+        for i, q in enumerate(out):
+            if isinstance(q, DelayedScalingRequest):
+                asked.append(((out, i), q))
+            elif isinstance(q, HybridQuantizer):
+                for side in ("rowwise_quantizer", "columnwise_quantizer"):
+                    if isinstance(getattr(q, side), DelayedScalingRequest):
+                        asked.append(((q, side), getattr(q, side)))
         if asked:
-            first = out[asked[0]]
-            if any(out[i] != first for i in asked):
+            first = asked[0][1]
+            if any(r != first for _, r in asked):
                 raise ValueError("all DelayedScalingRequest objects of one module must carry the same parameters")
             kw = dict(margin=first.margin, amax_history_len=first.amax_history_len,
                       amax_compute_algo=first.amax_compute_algo,
@@ -256,8 +268,11 @@ class CustomRecipeState(RecipeState):
                 kw["fp8_format"] = first.fp8_format
             self.delayed = DelayedScalingRecipeState(DelayedScaling(**kw), mode=self.mode, num_quantizers=len(asked),
                                                      device=self.device)
-            for q, i in zip(self.delayed.make_quantizers(), asked):
-                out[i] = q
+            for q, ((holder, where), _) in zip(self.delayed.make_quantizers(), asked):
+                if isinstance(holder, list):
+                    holder[where] = q
+                else:
+                    holder.set_child(where, q)
         return out
 
 

@@ -215,18 +215,33 @@ class HybridQuantizer(Quantizer):
                  columnwise_source: str = "original"):
         super().__init__(rowwise=True, columnwise=True)
         for name, q in (("rowwise", rowwise_quantizer), ("columnwise", columnwise_quantizer)):
-            if not isinstance(q, Quantizer):
-                raise TypeError(f"the {name} quantizer must be a Quantizer, got {type(q).__name__}")
-        if rowwise_quantizer is columnwise_quantizer:
+            if not isinstance(q, Quantizer) and not getattr(q, "_is_quantizer_request", False):
+                raise TypeError(f"the {name} quantizer must be a Quantizer (or a QuantizerRequest that the recipe "
+                                f"state resolves), got {type(q).__name__}")
+        if rowwise_quantizer is columnwise_quantizer and isinstance(rowwise_quantizer, Quantizer):
             raise ValueError("the rowwise and columnwise quantizers must be distinct objects")
         if columnwise_source not in self._SOURCES:
             raise ValueError(f"columnwise_source must be one of {self._SOURCES}")
-        self.rowwise_quantizer, self.columnwise_quantizer = rowwise_quantizer, columnwise_quantizer
         self.columnwise_source = columnwise_source
-        rowwise_quantizer.set_usage(rowwise=True, columnwise=False)
-        columnwise_quantizer.set_usage(rowwise=False, columnwise=True)
+        self.set_child("rowwise_quantizer", rowwise_quantizer)
+        self.set_child("columnwise_quantizer", columnwise_quantizer)
+
+    def set_child(self, side: str, q) -> None:
+        """Install a child and pin it to its direction.  A ``QuantizerRequest`` is kept as a placeholder until the
+        recipe state that owns this quantizer replaces it (``CustomRecipeState.make_quantizers``)."""
+        assert side in ("rowwise_quantizer", "columnwise_quantizer")
+        setattr(self, side, q)
+        if isinstance(q, Quantizer):
+            q.set_usage(rowwise=side == "rowwise_quantizer", columnwise=side == "columnwise_quantizer")
+
+    def _resolved(self) -> None:
+        for side in ("rowwise_quantizer", "columnwise_quantizer"):
+            if not isinstance(getattr(self, side), Quantizer):
+                raise RuntimeError(f"HybridQuantizer.{side} is an unresolved {type(getattr(self, side)).__name__}: "
+                                   "requests are resolved when a CustomRecipe factory returns the quantizer to a module")
 
     def copy(self) -> "HybridQuantizer":
+        self._resolved()
         q = HybridQuantizer(rowwise_quantizer=self.rowwise_quantizer.copy(),
                             columnwise_quantizer=self.columnwise_quantizer.copy(),
                             columnwise_source=self.columnwise_source)
@@ -235,6 +250,7 @@ class HybridQuantizer(Quantizer):
         return q
 
     def _children(self, tensor: torch.Tensor):
+        self._resolved()
         need_row = self.rowwise_usage or (self.columnwise_usage and self.columnwise_source == "rowwise_dequantized")
         row = col = None
         for q in (self.rowwise_quantizer, self.columnwise_quantizer):

@@ -605,3 +605,50 @@ def test_quickstart_example_runs_and_learns():
     spec.loader.exec_module(mod)
     losses = mod.main(["--recipe", "mxfp8", "--steps", "6", "--hidden", "256", "--seq", "64"])
     assert losses[-1] < losses[0]
+
+
+def test_newton_schulz_schedules_and_context_form():
+    import os as _os
+    import torch.distributed as _dist
+    from transformerengine_b200.newton_schulz import (CusolverMpCtx, get_coefficient_iterator, get_coefficients,
+                                                      newton_schulz)
+    assert get_coefficients(7, "simple") == [(3.4445, -4.7750, 2.0315)] * 7
+    q = get_coefficients(7, "quintic")
+    assert q[5] == q[0] and len(q) == 7                                   # cycles
+    pe = get_coefficients(10, "polar_express")
+    assert pe[8] == pe[9] == (1.875, -1.25, 0.375) and abs(pe[0][0] - 8.2051) < 1e-4   # last one repeats
+    assert list(get_coefficient_iterator(3, [(1, 2, 3)], "repeat_last")) == [(1, 2, 3)] * 3
+    with pytest.raises(ValueError):
+        get_coefficients(3, "unknown")
+    torch.manual_seed(0)
+    g = torch.randn(48, 96)
+    # the tuned schedules push the singular values into a band around 1 (they do not converge to exactly 1)
+    for kind, lo, hi in (("quintic", 0.6, 1.25), ("polar_express", 0.9, 1.1)):
+        o = newton_schulz(g, 8, get_coefficients(8, kind), compute_dtype=torch.float32)
+        sv = torch.linalg.svdvals(o.float())
+        assert lo < float(sv.min()) and float(sv.max()) < hi, (kind, float(sv.min()), float(sv.max()))
+    with pytest.raises(ValueError):
+        newton_schulz(g, 4, get_coefficients(3))
+    # reference call form: context, in place, nothing returned (single-rank group)
+    if not _dist.is_initialized():
+        _os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        _os.environ.setdefault("MASTER_PORT", "29533")
+        _dist.init_process_group("gloo", rank=0, world_size=1)
+        made = True
+    else:
+        made = False
+    try:
+        ctx = CusolverMpCtx(_dist.group.WORLD)
+        x = g.clone()
+        want = newton_schulz(g, 5, get_coefficients(5))
+        assert newton_schulz(x, ctx, 5) is None
+        torch.testing.assert_close(x, want)
+        y = g.clone()
+        newton_schulz(y, ctx, num_iterations=6, coefficients=get_coefficients(6, "polar_express"))
+        torch.testing.assert_close(y, newton_schulz(g, 6, get_coefficients(6, "polar_express")))
+        ctx.destroy()
+        with pytest.raises(RuntimeError):
+            newton_schulz(x, ctx, 5)
+    finally:
+        if made:
+            _dist.destroy_process_group()

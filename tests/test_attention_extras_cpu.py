@@ -153,3 +153,38 @@ def test_rotate_packed_qkv_in_place_matches_separate_rotations(layout, fmt):
     (ref * wq).sum().backward()
     (got * wq).sum().backward()
     torch.testing.assert_close(bt.grad, a.grad)
+
+
+def test_bottom_right_diagonal_and_packed_inputs():
+    """``bottom_right_diagonal`` picks the corner a sliding window is aligned to when s_q != s_kv (default for
+    non-causal masks: bottom right, as in the reference); ``qkv_layer`` / ``kv_layer`` are unpacked as views."""
+    torch.manual_seed(0)
+    b, h, sq, sk, d = 2, 2, 4, 7, 8
+    q, k, v = torch.randn(b, sq, h, d), torch.randn(b, sk, h, d), torch.randn(b, sk, h, d)
+    dpa = te.DotProductAttention(h, d, attention_dropout=0.0, qkv_format="bshd", attn_mask_type="no_mask",
+                                 attention_type="cross")
+
+    def ref(bottom_right, w):
+        s = torch.einsum("bqhd,bkhd->bhqk", q, k) / d ** 0.5
+        qi = torch.arange(sq)[:, None] + ((sk - sq) if bottom_right else 0)
+        ki = torch.arange(sk)[None]
+        p = torch.softmax(s.masked_fill((ki < qi - w[0]) | (ki > qi + w[1]), float("-inf")), -1)
+        return torch.einsum("bhqk,bkhd->bqhd", p, v).reshape(b, sq, h * d)
+
+    w = (1, 1)
+    torch.testing.assert_close(dpa(q, k, v, window_size=w), ref(True, w))
+    torch.testing.assert_close(dpa(q, k, v, window_size=w, bottom_right_diagonal=False), ref(False, w))
+    top_left = te.DotProductAttention(h, d, attention_dropout=0.0, qkv_format="bshd", attn_mask_type="no_mask",
+                                      attention_type="cross", bottom_right_diagonal=False)
+    torch.testing.assert_close(top_left(q, k, v, window_size=w), ref(False, w))
+    qkv = torch.randn(b, 5, 3, h, d)
+    assert torch.equal(dpa(qkv_layer=qkv, attn_mask_type="causal"),
+                       dpa(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], attn_mask_type="causal"))
+    kv = torch.randn(b, sk, h, 2, d)
+    assert torch.equal(dpa(q, kv_layer=kv, qkv_interleave_dim=-2), dpa(q, kv[..., 0, :], kv[..., 1, :]))
+    with pytest.raises(ValueError):
+        dpa(q, k, v, kv_layer=kv, qkv_interleave_dim=-2)
+    with pytest.raises(ValueError):
+        dpa(qkv_layer=qkv, qkv_interleave_dim=-1)
+    with pytest.raises(NotImplementedError):
+        dpa(q, k, v, fp8_output=True)

@@ -652,3 +652,72 @@ def test_newton_schulz_schedules_and_context_form():
     finally:
         if made:
             _dist.destroy_process_group()
+
+
+def _ce_worker(rank, world, port, result_q):
+    import torch.distributed as dist
+
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.manual_seed(0)
+        full = torch.randn(12, 64)
+        tgt = torch.randint(0, 64, (12,))
+        tgt[3] = -100
+        errs = []
+        for eps in (0.0, 0.2):
+            xf = full.clone().requires_grad_()
+            want = torch.nn.functional.cross_entropy(xf, tgt, label_smoothing=eps, reduction="none")
+            want.sum().backward()
+            xs = full.chunk(world, dim=1)[rank].clone().requires_grad_()
+            got = parallel_cross_entropy(xs, tgt, eps, False, dist.group.WORLD)
+            got.sum().backward()
+            errs.append(float((got - want).abs().max()))
+            errs.append(float((xs.grad - xf.grad.chunk(world, dim=1)[rank]).abs().max()))
+        result_q.put((rank, max(errs), None))
+    except Exception:  # noqa: BLE001
+        import traceback
+
+        result_q.put((rank, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_parallel_cross_entropy_label_smoothing_single_rank_and_vocab_sharded():
+    import socket
+
+    import torch.multiprocessing as mp
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 6, 50, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_()
+    t = torch.randint(0, 50, (4, 6))
+    t[0, 2] = -100
+    for reduce in (False, True):
+        a = parallel_cross_entropy(x, t, 0.1, reduce)
+        b = torch.nn.functional.cross_entropy(x2.reshape(-1, 50), t.reshape(-1), label_smoothing=0.1,
+                                              reduction="mean" if reduce else "none")
+        torch.testing.assert_close(a.reshape(-1), b.reshape(-1))
+        x.grad = x2.grad = None
+        a.sum().backward()
+        b.sum().backward()
+        torch.testing.assert_close(x.grad, x2.grad)
+    torch.testing.assert_close(parallel_cross_entropy(None, t, _input=x.detach()), parallel_cross_entropy(x.detach(), t))
+    with pytest.raises(ValueError):
+        parallel_cross_entropy(x, t, 1.5)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ce_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err, tb in res:
+        assert tb is None, tb
+        assert err < 1e-5, (rank, err)

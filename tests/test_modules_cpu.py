@@ -454,3 +454,24 @@ def test_quantized_model_init_covers_every_module(name, kind):
     before = quantized[0].dequantize().clone()
     opt.step()
     assert isinstance(quantized[0], QuantizedTensorStorage) and not torch.equal(before, quantized[0].dequantize())
+
+
+def test_grouped_linear_output_buffers():
+    """``out`` / ``dgrad_out`` receive the forward output and the input gradient; rows past ``sum(m_splits)`` stay
+    untouched."""
+    torch.manual_seed(0)
+    gl = te.GroupedLinear(2, 16, 24, bias=True, params_dtype=torch.float32, device="cpu", use_grouped_tensor=True)
+    x = torch.randn(10, 16, requires_grad=True)
+    x2 = x.detach().clone().requires_grad_()
+    out, dgrad = torch.full((12, 24), 7.0), torch.full((12, 16), 7.0)
+    y = gl(x, [4, 6], out=out, dgrad_out=dgrad)
+    y2 = gl(x2, [4, 6])
+    assert y.data_ptr() == out.data_ptr() and torch.equal(y[:10], y2) and (out[10:] == 7).all()
+    y[:10].square().sum().backward()
+    y2.square().sum().backward()
+    assert torch.equal(x.grad, x2.grad) and torch.equal(dgrad[:10], x2.grad) and (dgrad[10:] == 7).all()
+    assert x.grad.data_ptr() == dgrad.data_ptr()
+    with pytest.raises(ValueError):
+        gl(x, [4, 6], out=torch.empty(12, 23))
+    with pytest.raises(TypeError):
+        te.GroupedLinear(2, 16, 24, device="cpu", use_grouped_tensor="yes")

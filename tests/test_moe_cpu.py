@@ -146,3 +146,57 @@ def test_expert_parallel_matches_local():
         p.join(timeout=60)
     for rank, bad in res:
         assert not bad, f"rank {rank}: {bad}"
+
+
+def test_router_quantile_balancing_histogram_and_map_formats():
+    """The QB histogram counts, per expert, the bias that expert would have needed to enter each token's top-k
+    (cutoff - raw sigmoid score) in uniform bins; routing itself is the usual biased-sigmoid top-k."""
+    from transformerengine_b200.router import (QBHistogramMode, RoutingMapFormat, fused_compute_score_for_moe_aux_loss,
+                                               fused_topk_with_score_function)
+    torch.manual_seed(0)
+    T, E, k, bins = 37, 10, 3, 8
+    logits = torch.randn(T, E, requires_grad=True)
+    bias = torch.randn(E) * 0.2
+    hist = torch.zeros(E, bins, dtype=torch.int32)
+    bounds = torch.tensor([-0.5, 0.5])
+    probs, rmap = fused_topk_with_score_function(logits, k, False, None, None, 1.5, "sigmoid", bias,
+                                                 qb_histogram=hist, qb_bin_bounds=bounds,
+                                                 qb_histogram_mode="fused_atomic")
+    ref_probs, ref_map = fused_topk_with_score_function(logits, k, False, None, None, 1.5, "sigmoid", bias)
+    assert torch.equal(rmap, ref_map)
+    torch.testing.assert_close(probs, ref_probs)
+    want = torch.zeros(E, bins, dtype=torch.int32)
+    raw = torch.sigmoid(logits.detach())
+    for t in range(T):
+        cutoff = (raw[t] + bias).sort(descending=True).values[k]
+        for e in range(E):
+            b = int(torch.floor((cutoff - raw[t, e] + 0.5) * bins / 1.0))
+            want[e, min(max(b, 0), bins - 1)] += 1
+    assert torch.equal(hist, want) and int(hist.sum()) == T * E
+    # accumulates in place; both mode names give the same counts
+    fused_topk_with_score_function(logits, k, False, None, None, 1.5, "sigmoid", bias, qb_histogram=hist,
+                                   qb_bin_bounds=bounds, qb_histogram_mode="two_kernel")
+    assert torch.equal(hist, 2 * want)
+    probs.sum().backward()
+    assert logits.grad is not None and torch.isfinite(logits.grad).all()
+    for bad in (dict(score_function="softmax"), dict(expert_bias=None), dict(num_groups=2, group_topk=1),
+                dict(qb_histogram_mode="other"), dict(qb_bin_bounds=torch.tensor([1.0, 0.0]))):
+        kw = dict(logits=logits, topk=k, use_pre_softmax=False, num_groups=None, group_topk=None, scaling_factor=None,
+                  score_function="sigmoid", expert_bias=bias, qb_histogram=hist, qb_bin_bounds=bounds,
+                  qb_histogram_mode="two_kernel")
+        kw.update(bad)
+        with pytest.raises(ValueError):
+            fused_topk_with_score_function(**kw)
+    with pytest.raises(ValueError):
+        fused_topk_with_score_function(logits, k, qb_histogram=hist)
+    # routing map formats: enum, int and string spellings; bit e % 8 of byte e // 8
+    _, packed = fused_topk_with_score_function(logits, k, routing_map_format=RoutingMapFormat.BITMAP_U8)
+    _, plain = fused_topk_with_score_function(logits, k, routing_map_format=0)
+    assert packed.dtype == torch.uint8 and packed.shape == (T, 2)
+    unpacked = torch.stack([(packed[:, e // 8] >> (e % 8)) & 1 for e in range(E)], dim=1).bool()
+    assert torch.equal(unpacked, plain)
+    m2, _ = fused_compute_score_for_moe_aux_loss(logits, k, "sigmoid", routing_map_format="bitmap_u8")
+    assert m2.shape == (T, 2) and m2.dtype == torch.uint8
+    assert int(QBHistogramMode.FUSED_ATOMIC) == 1
+    with pytest.raises(ValueError):
+        fused_topk_with_score_function(logits, k, routing_map_format="BITMAP")

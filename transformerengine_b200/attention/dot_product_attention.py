@@ -39,8 +39,10 @@ class DotProductAttention(torch.nn.Module):
                  tp_group=None, layer_number: Optional[int] = None, attention_type: str = "self", cp_group=None,
                  cp_global_ranks: Optional[List[int]] = None, cp_stream=None, cp_comm_type: str = "p2p",
                  softmax_scale: Optional[float] = None, softmax_type: str = "vanilla",
-                 return_max_logit: bool = False) -> None:
+                 return_max_logit: bool = False, bottom_right_diagonal: Optional[bool] = None,
+                 name: Optional[str] = None) -> None:
         super().__init__()
+        self.bottom_right_diagonal, self.name = bottom_right_diagonal, name
         if return_max_logit:
             raise NotImplementedError("return_max_logit: the attention kernels do not export the maximum logit")
         assert attn_mask_type in _MASK_TYPES, f"unknown attn_mask_type {attn_mask_type}"
@@ -86,8 +88,8 @@ class DotProductAttention(torch.nn.Module):
         self.cp_group, self.cp_global_ranks, self.cp_stream, self.cp_comm_type = cp_group, cp_global_ranks, cp_stream, cp_comm_type
 
     # ------------------------------------------------------------------
-    def forward(self, query_layer: torch.Tensor, key_layer: torch.Tensor, value_layer: torch.Tensor,
-                attention_mask=None, qkv_format: Optional[str] = None, cu_seqlens_q: Optional[torch.Tensor] = None,
+    def forward(self, query_layer: Optional[torch.Tensor] = None, key_layer: Optional[torch.Tensor] = None,
+                value_layer: Optional[torch.Tensor] = None, attention_mask=None, qkv_format: Optional[str] = None, cu_seqlens_q: Optional[torch.Tensor] = None,
                 cu_seqlens_kv: Optional[torch.Tensor] = None, cu_seqlens_q_padded=None, cu_seqlens_kv_padded=None,
                 max_seqlen_q: Optional[int] = None, max_seqlen_kv: Optional[int] = None,
                 attn_mask_type: Optional[str] = None, window_size: Optional[Tuple[int, int]] = None,
@@ -96,9 +98,28 @@ class DotProductAttention(torch.nn.Module):
                 fast_zero_fill: bool = True, inference_params=None, pad_between_seqs: Optional[bool] = None,
                 score_mod: Optional[Callable] = None, score_mod_bprop: Optional[Callable] = None,
                 score_mod_tensors: Optional[Dict[str, torch.Tensor]] = None,
-                score_mod_bprop_tensors: Optional[Dict[str, torch.Tensor]] = None):
+                score_mod_bprop_tensors: Optional[Dict[str, torch.Tensor]] = None,
+                bottom_right_diagonal: Optional[bool] = None, fp8_output: bool = False, bf16_backward: bool = False,
+                num_splits: Optional[int] = None, qkv_layer: Optional[torch.Tensor] = None,
+                kv_layer: Optional[torch.Tensor] = None, qkv_interleave_dim: int = -3):
+        """``bottom_right_diagonal``: corner that the sliding window and the ALiBi diagonal are aligned to when
+        ``s_q != s_kv`` (None: top-left for ``causal`` / ``padding_causal``, bottom-right otherwise; the causal
+        mask types fix it).  ``qkv_layer`` / ``kv_layer``: one packed buffer holding q, k, v (or k, v) along
+        ``qkv_interleave_dim`` (-3: ``...3hd``, -2: ``...h3d``) instead of separate tensors; the pieces are
+        zero-copy views.  ``bf16_backward`` and ``num_splits`` are accepted for compatibility (the backward
+        pass always runs in 16 bits; the kernels choose their own split of the key sequence)."""
+        if fp8_output:
+            raise NotImplementedError("fp8_output: the attention kernels write 16-bit outputs")
+        if qkv_layer is not None or kv_layer is not None:
+            query_layer, key_layer, value_layer = _unpack_qkv(query_layer, key_layer, value_layer, qkv_layer,
+                                                              kv_layer, qkv_interleave_dim, inference_params)
         fmt = qkv_format or self.qkv_format
         mask_type = attn_mask_type or self.attn_mask_type
+        brd = self.bottom_right_diagonal if bottom_right_diagonal is None else bottom_right_diagonal
+        if mask_type in ("causal", "padding_causal"):
+            brd = False
+        if brd is None or mask_type in ("causal_bottom_right", "padding_causal_bottom_right"):
+            brd = True
         window = window_size if window_size is not None else self.window_size
         # fast_zero_fill is a hint for a zero-filling strategy of padded outputs that these kernels do not need
         # (they write every row of the output); pad_between_seqs is implied by passing padded cumulative lengths
@@ -119,17 +140,18 @@ class DotProductAttention(torch.nn.Module):
         if checkpoint_core_attention:
             def run(q, k, v):
                 return self._core(q, k, v, fmt, mask_type, window, attention_mask, cu_seqlens_q, cu_seqlens_kv,
-                                  core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score)
+                                  core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score, brd)
             return D.checkpoint(run, query_layer, key_layer, value_layer,
                                 get_rng_state_tracker=self.get_rng_state_tracker)
         out = self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
-                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score)
+                         cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score,
+                         brd)
         if inference_params is not None:
             out = inference_params.unpack_output(out)
         return out
 
     def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes,
-              thd_extra=(None, None, None, None), score=(None, None)):
+              thd_extra=(None, None, None, None), score=(None, None), bottom_right_diagonal=None):
         if fmt == "thd":
             return self._thd(q, k, v, mask_type, window, cu_q, cu_kv, *thd_extra)
         # -> [b, h, s, d] views
@@ -143,6 +165,10 @@ class DotProductAttention(torch.nn.Module):
         # 'causal' aligns the diagonal to the top-left corner, '*_bottom_right' to the bottom-right one, for
         # self- and cross-attention alike (reference: dot_product_attention.py:1746-1754)
         bottom_right = "bottom_right" in mask_type
+        windowed = window is not None and (window[0] >= 0 or window[1] >= 0)
+        if bottom_right_diagonal is not None and not causal and (windowed or bias_type == "alibi"):
+            # without a causal mask only the sliding window and the ALiBi diagonal have a corner to align to
+            bottom_right = bottom_right_diagonal
         mask = None
         if "padding" in mask_type:
             if attention_mask is not None:
@@ -255,6 +281,34 @@ class _null:
 
     def __exit__(self, *a):
         return False
+
+
+def _unpack_qkv(q, k, v, qkv_layer, kv_layer, dim, inference_params):
+    """q, k, v as views of a packed buffer (reference: the ``qkv_layer`` / ``kv_layer`` arguments of
+    ``DotProductAttention.forward``)."""
+    if qkv_layer is not None and kv_layer is not None:
+        raise ValueError("qkv_layer and kv_layer are mutually exclusive")
+    if inference_params is not None:
+        raise ValueError("packed inputs (qkv_layer / kv_layer) are not supported with KV caching")
+    if dim not in (-3, -2):
+        raise ValueError(f"qkv_interleave_dim must be -3 (e.g. bs3hd) or -2 (e.g. bsh3d), got {dim}")
+    packed = qkv_layer if qkv_layer is not None else kv_layer
+    if packed.stride(-1) != 1:
+        raise ValueError("the packed tensor must have stride 1 in its last dimension")
+    if qkv_layer is not None:
+        if q is not None or k is not None or v is not None:
+            raise ValueError("qkv_layer already packs q, k and v: pass None for query_layer, key_layer, value_layer")
+        if qkv_layer.shape[dim] != 3:
+            raise ValueError(f"qkv_layer must have size 3 at dim {dim}, got shape {tuple(qkv_layer.shape)}")
+        return tuple(qkv_layer.select(dim, i) for i in range(3))
+    if q is None:
+        raise ValueError("kv_layer packs only k and v: query_layer is required")
+    if k is not None or v is not None:
+        raise ValueError("kv_layer already packs k and v: pass None for key_layer and value_layer")
+    if kv_layer.dim() != q.dim() + 1 or kv_layer.shape[dim] != 2:
+        raise ValueError(f"kv_layer must have one more dimension than query_layer and size 2 at dim {dim}, got "
+                         f"shape {tuple(kv_layer.shape)}")
+    return (q,) + tuple(kv_layer.select(dim, i) for i in range(2))
 
 
 def _alibi_bias(h, sq, sk, slopes, device, bottom_right=True):

@@ -39,9 +39,10 @@ class MultiheadAttention(torch.nn.Module):
                  qkv_format: str = "sbhd", name: Optional[str] = None, qk_norm_type: Optional[str] = None,
                  qk_norm_eps: float = 1e-6, qk_norm_before_rope: bool = False, seq_length: Optional[int] = None,
                  micro_batch_size: Optional[int] = None, softmax_type: str = "vanilla",
-                 rotary_pos_interleaved: bool = False) -> None:
+                 rotary_pos_interleaved: bool = False, bottom_right_diagonal: Optional[bool] = None) -> None:
         super().__init__()
         self.rotary_pos_interleaved = rotary_pos_interleaved
+        self.bottom_right_diagonal = bottom_right_diagonal
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.qkv_format = qkv_format
@@ -145,7 +146,8 @@ class MultiheadAttention(torch.nn.Module):
                 inference_params=None, rotary_pos_emb=None, core_attention_bias_type: str = "no_bias",
                 core_attention_bias: Optional[torch.Tensor] = None, alibi_slopes: Optional[torch.Tensor] = None,
                 cu_seqlens_q=None, cu_seqlens_kv=None, cu_seqlens_q_padded=None, cu_seqlens_kv_padded=None,
-                max_seqlen_q=None, max_seqlen_kv=None, fast_zero_fill: bool = True, pad_between_seqs=None):
+                max_seqlen_q=None, max_seqlen_kv=None, fast_zero_fill: bool = True, pad_between_seqs=None,
+                bottom_right_diagonal: Optional[bool] = None):
         d = self.hidden_size_per_attention_head
         hq, hk = self.num_attention_heads_per_partition, self.num_gqa_groups_per_partition
         ln_out = None
@@ -225,7 +227,9 @@ class MultiheadAttention(torch.nn.Module):
                                   checkpoint_core_attention=checkpoint_core_attention,
                                   core_attention_bias_type=core_attention_bias_type,
                                   core_attention_bias=core_attention_bias, alibi_slopes=alibi_slopes,
-                                  inference_params=inference_params)
+                                  inference_params=inference_params,
+                                  bottom_right_diagonal=(self.bottom_right_diagonal if bottom_right_diagonal is None
+                                                         else bottom_right_diagonal))
         proj = self.proj(ctx, is_first_microbatch=is_first_microbatch)
         if self.return_bias:
             out, b = proj

@@ -225,8 +225,14 @@ class GroupedLinear(TransformerEngineBaseModule):
                  device: Union[torch.device, str] = None, ub_overlap_rs: bool = False, ub_overlap_ag: bool = False,
                  ub_name: Optional[str] = None, delay_wgrad_compute: bool = False,
                  save_original_input: bool = False, single_grouped_weight: bool = False,
-                 single_grouped_bias: bool = False, name: Optional[str] = None) -> None:
+                 single_grouped_bias: bool = False, use_grouped_tensor: Optional[bool] = None,
+                 name: Optional[str] = None) -> None:
         super().__init__()
+        # accepted for compatibility: there is one path here, a grouped GEMM over the stacked expert operands
+        # (what the reference selects with use_grouped_tensor=True), for discrete weight{i} parameters
+        if use_grouped_tensor is not None and not isinstance(use_grouped_tensor, bool):
+            raise TypeError(f"use_grouped_tensor must be a bool or None, got {type(use_grouped_tensor)}")
+        self.use_grouped_tensor = True if use_grouped_tensor is None else use_grouped_tensor
         # options of the reference that this module does not implement are refused, not ignored
         for opt, val in (("delay_wgrad_compute", delay_wgrad_compute), ("save_original_input", save_original_input),
                          ("single_grouped_weight", single_grouped_weight), ("single_grouped_bias", single_grouped_bias)):
@@ -268,7 +274,31 @@ class GroupedLinear(TransformerEngineBaseModule):
             self._quantize_primary_weights([f"weight{i}" for i in range(num_gemms)])
             self._stacked = None
 
-    def forward(self, inp: torch.Tensor, m_splits: List[int], is_first_microbatch: Optional[bool] = None):
+    def forward(self, inp: torch.Tensor, m_splits: List[int], is_first_microbatch: Optional[bool] = None,
+                out: Optional[torch.Tensor] = None, dgrad_out: Optional[torch.Tensor] = None):
+        """``out`` / ``dgrad_out``: caller-owned buffers ``[tokens, out_features]`` / ``[tokens, in_features]``
+        (2-D, contiguous, not requiring grad, activation dtype) that receive the forward output and the input
+        gradient; the returned tensor (and the gradient autograd hands on) are views of them.  Only the first
+        ``sum(m_splits)`` rows are written.  The results are copied into the buffers (one extra pass each)."""
+        if out is not None or dgrad_out is not None:
+            rows = int(sum(m_splits))
+            for name, buf, width in (("out", out, self.out_features), ("dgrad_out", dgrad_out, self.in_features)):
+                if buf is None:
+                    continue
+                if buf.dim() != 2 or not buf.is_contiguous() or buf.requires_grad or buf.shape[1] != width \
+                        or buf.shape[0] < rows:
+                    raise ValueError(f"{name} must be a contiguous 2-D tensor without grad of shape "
+                                     f"[>= {rows}, {width}], got {tuple(buf.shape)}")
+            if dgrad_out is not None and inp.requires_grad:
+                inp = _GradInto.apply(inp, dgrad_out, rows)
+            res = self.forward(inp, m_splits, is_first_microbatch)
+            if out is None:
+                return res
+            y, rest = (res[0], res[1:]) if isinstance(res, tuple) else (res, ())
+            if y.dtype != out.dtype:
+                raise ValueError(f"out has dtype {out.dtype}, the layer computes in {y.dtype}")
+            out[:rows].copy_(y[:rows])
+            return (out,) + tuple(rest) if rest else out
         assert len(m_splits) == self.num_gemms, "one row count per GEMM"
         self.prepare_forward(num_gemms=self.num_gemms)
         adt = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else inp.dtype
@@ -278,6 +308,24 @@ class GroupedLinear(TransformerEngineBaseModule):
             out = _GroupedLinear.apply(inp, m_splits, _NoBias(self), adt, *ws)
             return out, [b.to(adt) for b in bs]
         return _GroupedLinear.apply(inp, m_splits, self, adt, *ws, *bs)
+
+
+class _GradInto(torch.autograd.Function):
+    """Identity whose backward writes the incoming gradient into a caller-owned buffer."""
+
+    @staticmethod
+    def forward(ctx, x, buf, rows):  # type: ignore[override]
+        ctx.buf, ctx.rows = buf, rows
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        buf, rows = ctx.buf, ctx.rows
+        g2 = g.reshape(-1, g.shape[-1])
+        if buf.dtype != g2.dtype or g2.shape[0] > buf.shape[0]:
+            return g, None, None
+        buf[:rows].copy_(g2[:rows])
+        return buf[:g2.shape[0]].view(g.shape), None, None
 
 
 class _NoBias:

@@ -193,7 +193,8 @@ class LayerNormLinear(TransformerEngineBaseModule):
                  zero_centered_gamma: bool = False, device: Union[torch.device, str] = None,
                  ub_overlap_ag: bool = False, ub_overlap_rs_dgrad: bool = False, ub_bulk_wgrad: bool = False,
                  ub_bulk_dgrad: bool = False, ub_name: Optional[str] = None, delay_wgrad_compute: bool = False,
-                 symmetric_ar_type: Optional[str] = None, name: Optional[str] = None) -> None:
+                 symmetric_ar_type: Optional[str] = None, name: Optional[str] = None,
+                 ub_overlap_rs: bool = False) -> None:
         super().__init__()
         if return_layernorm_output_gathered:
             raise NotImplementedError("return_layernorm_output_gathered is not implemented: the normalized output is "

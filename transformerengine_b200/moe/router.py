@@ -10,10 +10,61 @@ Everything is differentiable through ``probs``.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+import enum
+import math
+from typing import Optional, Tuple, Union
 
 import torch
 import torch.nn.functional as F
+
+
+class RoutingMapFormat(enum.IntEnum):
+    """Layout of the routing map: ``BYTEMAP`` bool ``[T, E]``; ``BITMAP_U8`` uint8 ``[T, ceil(E / 8)]`` with bit
+    ``e % 8`` of byte ``e // 8`` set when the token goes to expert ``e``."""
+    BYTEMAP = 0
+    BITMAP_U8 = 1
+
+
+class QBHistogramMode(enum.IntEnum):
+    """How the reference builds the quantile-balancing histogram (a second kernel, or atomics inside the router
+    kernel).  Both give the same histogram; the names are accepted for compatibility."""
+    TWO_KERNEL = 0
+    FUSED_ATOMIC = 1
+
+
+def _map_format(fmt: Union[str, int, RoutingMapFormat]) -> int:
+    if isinstance(fmt, str):
+        if fmt not in ("bytemap", "bitmap_u8"):
+            raise ValueError(f"routing_map_format string must be 'bytemap' or 'bitmap_u8', got {fmt!r}")
+        return int(fmt == "bitmap_u8")
+    if isinstance(fmt, int) and int(fmt) in (0, 1):
+        return int(fmt)
+    raise ValueError(f"routing_map_format must be 'bytemap' / 'bitmap_u8', a RoutingMapFormat or 0 / 1; got {fmt!r}")
+
+
+def _pack_bitmap(rmap: torch.Tensor) -> torch.Tensor:
+    """bool ``[T, E]`` -> uint8 ``[T, ceil(E / 8)]``, least significant bit first."""
+    T, E = rmap.shape
+    Ep = (E + 7) // 8 * 8
+    bits = F.pad(rmap, (0, Ep - E)).reshape(T, Ep // 8, 8).to(torch.uint8)
+    weights = (2 ** torch.arange(8, device=rmap.device)).to(torch.uint8)
+    return (bits * weights).sum(-1).to(torch.uint8)
+
+
+def _check_bin_bounds(bounds: torch.Tensor) -> Tuple[float, float]:
+    """``[lower, upper]`` of the histogram bins, read on the host once per version of the tensor."""
+    if not (isinstance(bounds, torch.Tensor) and bounds.dtype == torch.float32 and tuple(bounds.shape) == (2,)):
+        raise ValueError("qb_bin_bounds must be a float32 tensor [lower, upper]")
+    cached = getattr(bounds, "_qb_checked", None)
+    if cached is not None and cached[0] == bounds._version:
+        return cached[1]
+    if bounds.is_cuda and torch.cuda.is_current_stream_capturing():
+        raise RuntimeError("qb_bin_bounds must be validated by an eager router call before CUDA graph capture")
+    lower, upper = bounds.detach().cpu().tolist()
+    if not (math.isfinite(lower) and math.isfinite(upper) and lower < upper):
+        raise ValueError(f"qb_bin_bounds must be finite with lower < upper, got [{lower}, {upper}]")
+    bounds._qb_checked = (bounds._version, (lower, upper))
+    return lower, upper
 
 
 def _score(logits: torch.Tensor, score_function: str) -> torch.Tensor:
@@ -78,12 +129,42 @@ def _cuda_router_ok(logits, topk, num_groups, group_topk, routing_map_format, to
 def fused_topk_with_score_function(logits: torch.Tensor, topk: int, use_pre_softmax: bool = False,
                                    num_groups: Optional[int] = None, group_topk: Optional[int] = None,
                                    scaling_factor: Optional[float] = None, score_function: str = "softmax",
-                                   expert_bias: Optional[torch.Tensor] = None, routing_map_format: str = "bytemap",
-                                   topk_indices: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Returns ``(probs [T, E] in the dtype of logits, routing_map bool [T, E])``."""
-    assert logits.dtype != torch.float64, "float64 router logits are not supported"
+                                   expert_bias: Optional[torch.Tensor] = None,
+                                   routing_map_format: Union[str, int, RoutingMapFormat] = "bytemap",
+                                   topk_indices: Optional[torch.Tensor] = None,
+                                   qb_histogram: Optional[torch.Tensor] = None,
+                                   qb_bin_bounds: Optional[torch.Tensor] = None,
+                                   qb_histogram_mode: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Returns ``(probs [T, E] in the dtype of logits, routing_map)``; the map is bool ``[T, E]``, bit-packed uint8
+    with ``routing_map_format="bitmap_u8"``, or the dense indices when ``topk_indices`` (an output buffer
+    ``[T, topk]``) is given.
+
+    Quantile balancing (``qb_histogram`` int32 ``[E, bins]``, ``qb_bin_bounds`` fp32 ``[lower, upper]``,
+    ``qb_histogram_mode``; sigmoid scores with ``expert_bias`` only): besides routing, every (token, expert) pair
+    adds one count to ``qb_histogram[e, bin]`` where the binned value is ``cutoff_t - sigmoid(logit_te)``, the
+    bias expert ``e`` would have needed to enter token ``t``'s top-k (``cutoff_t``: the (k+1)-th largest biased
+    score of the token); ``bins`` uniform bins span ``[lower, upper)``, values outside go to the end bins.  The
+    caller turns the histogram into per-expert bias updates (a quantile per expert).
+    (Reference: ``common/fused_router/fused_topk_with_score_function.cu``, the QB epilogue.)"""
+    if logits.dtype == torch.float64:
+        raise ValueError("float64 router logits are not supported")
+    routing_map_format = "bitmap_u8" if _map_format(routing_map_format) else "bytemap"
     shape = logits.shape
     E = shape[-1]
+    qb = (qb_histogram, qb_bin_bounds, qb_histogram_mode)
+    if any(a is not None for a in qb):
+        if any(a is None for a in qb):
+            raise ValueError("qb_histogram, qb_bin_bounds and qb_histogram_mode must be provided together")
+        if score_function != "sigmoid":
+            raise ValueError("quantile balancing only supports score_function='sigmoid'")
+        if expert_bias is None:
+            raise ValueError("quantile balancing requires expert_bias")
+        if num_groups is not None or group_topk is not None:
+            raise ValueError("quantile balancing does not support grouped top-k")
+        if qb_histogram_mode not in ("two_kernel", "fused_atomic"):
+            raise ValueError(f"qb_histogram_mode must be 'two_kernel' or 'fused_atomic', got {qb_histogram_mode!r}")
+        return _route_with_qb_histogram(logits, topk, scaling_factor, expert_bias, routing_map_format, topk_indices,
+                                        qb_histogram, qb_bin_bounds)
     if _cuda_router_ok(logits, topk, num_groups, group_topk, routing_map_format, topk_indices):
         probs, rmap = _RouterTopK.apply(logits.reshape(-1, E).contiguous(), topk, bool(use_pre_softmax),
                                         float(scaling_factor) if scaling_factor else 1.0, _SCORE_FN[score_function],
@@ -120,19 +201,51 @@ def fused_topk_with_score_function(logits: torch.Tensor, topk: int, use_pre_soft
     if topk_indices is not None:
         topk_indices.copy_(idx.reshape(topk_indices.shape))
         return probs.to(logits.dtype).reshape(shape), topk_indices
-    if routing_map_format in ("bitmap_u8", 1):
-        Ep = (E + 7) // 8 * 8
-        bits = F.pad(rmap, (0, Ep - E)).reshape(-1, Ep // 8, 8).to(torch.uint8)
-        weights = (2 ** torch.arange(8, device=lf.device)).to(torch.uint8)
-        rmap = (bits * weights).sum(-1).to(torch.uint8).reshape(*shape[:-1], Ep // 8)
-        return probs.to(logits.dtype).reshape(shape), rmap
+    if routing_map_format == "bitmap_u8":
+        return probs.to(logits.dtype).reshape(shape), _pack_bitmap(rmap).reshape(*shape[:-1], -1)
     return probs.to(logits.dtype).reshape(shape), rmap.reshape(shape)
 
 
-def fused_compute_score_for_moe_aux_loss(logits: torch.Tensor, topk: int, score_function: str = "softmax"
+def _route_with_qb_histogram(logits, topk, scaling_factor, expert_bias, routing_map_format, topk_indices, histogram,
+                             bin_bounds):
+    shape = logits.shape
+    E = shape[-1]
+    if topk >= E:
+        raise ValueError("quantile balancing needs a (topk + 1)-th expert: topk must be smaller than the number of experts")
+    if histogram.dtype != torch.int32 or histogram.dim() != 2 or histogram.shape[0] != E:
+        raise ValueError(f"qb_histogram must be an int32 tensor [num_experts, num_bins], got {tuple(histogram.shape)}")
+    lower, upper = _check_bin_bounds(bin_bounds)
+    bins = histogram.shape[1]
+    lf = logits.float().reshape(-1, E)
+    raw = torch.sigmoid(lf)
+    biased = raw.detach() + expert_bias.float()
+    vals, idx = biased.topk(topk + 1, dim=-1)        # sorted: the last column is the cutoff
+    cutoff, idx = vals[:, topk], idx[:, :topk]
+    with torch.no_grad():
+        b = torch.floor((cutoff[:, None] - raw.detach() - lower) * (bins / (upper - lower))).clamp_(0, bins - 1).long()
+        flat = (torch.arange(E, device=lf.device)[None, :] * bins + b).reshape(-1)
+        histogram.view(-1).index_add_(0, flat, torch.ones_like(flat, dtype=torch.int32))
+    kept = raw.gather(1, idx)                          # the bias only chooses; the kept values are the raw scores
+    if topk > 1:
+        kept = kept / (kept.sum(-1, keepdim=True) + 1e-20)
+    if scaling_factor:
+        kept = kept * scaling_factor
+    probs = torch.zeros_like(lf).scatter(1, idx, kept).to(logits.dtype).reshape(shape)
+    if topk_indices is not None:
+        topk_indices.copy_(idx.reshape(topk_indices.shape))
+        return probs, topk_indices
+    rmap = torch.zeros(lf.shape, dtype=torch.bool, device=lf.device).scatter_(1, idx, True)
+    if routing_map_format == "bitmap_u8":
+        return probs, _pack_bitmap(rmap).reshape(*shape[:-1], -1)
+    return probs, rmap.reshape(shape)
+
+
+def fused_compute_score_for_moe_aux_loss(logits: torch.Tensor, topk: int, score_function: str = "softmax",
+                                         routing_map_format: Union[str, int, RoutingMapFormat] = "bytemap"
                                          ) -> Tuple[torch.Tensor, torch.Tensor]:
     """Scores used by the auxiliary loss: full score-function output (normalised over experts for
     sigmoid / sqrt-softplus) and the plain top-k routing map.  Returns ``(routing_map, scores)``."""
+    packed = _map_format(routing_map_format) == 1
     E = logits.shape[-1]
     lf = logits.float().reshape(-1, E)
     scores = _score(lf, score_function)
@@ -140,6 +253,8 @@ def fused_compute_score_for_moe_aux_loss(logits: torch.Tensor, topk: int, score_
         scores = scores / (scores.sum(-1, keepdim=True) + 1e-20)
     idx = scores.detach().topk(topk, dim=-1).indices
     rmap = torch.zeros(lf.shape, dtype=torch.bool, device=lf.device).scatter_(1, idx, True)
+    if packed:
+        return _pack_bitmap(rmap).reshape(*logits.shape[:-1], -1), scores.reshape(logits.shape)
     return rmap.reshape(logits.shape), scores.reshape(logits.shape)
 
 

@@ -359,11 +359,15 @@ _ENABLED = {"group": None}
 
 
 def initialize_ub(shape=None, tp_size: Optional[int] = None, use_fp8: bool = False, dtype=torch.bfloat16,
-                  ub_cfgs=None, bootstrap_backend=None, tp_group=None, quantization_modes=None, **_unused) -> None:
+                  ub_cfgs=None, bootstrap_backend=None, tp_group=None, quantization_modes=None,
+                  with_cublasmp: bool = False, **_unused) -> None:
     """Turn on fused collective GEMMs for tensor-parallel modules of ``tp_group``.
 
     Contexts (symmetric buffers + flags) are created lazily per call site and shape.
     """
+    if with_cublasmp:
+        raise NotImplementedError("with_cublasmp: the collective GEMMs of this library are its own kernels over "
+                                  "symmetric memory; there is no cuBLASMp path")
     _ENABLED["group"] = tp_group if tp_group is not None else dist.group.WORLD
 
 

@@ -57,8 +57,11 @@ class TransformerLayer(torch.nn.Module):
                  activation: str = "gelu", activation_params: Optional[dict] = None, normalization: str = "LayerNorm",
                  device: Union[torch.device, str] = None, attn_input_format: str = "sbhd", name: Optional[str] = None,
                  qk_norm_type: Optional[str] = None, qk_norm_eps: float = 1e-6, qk_norm_before_rope: bool = False,
-                 softmax_type: str = "vanilla") -> None:
+                 softmax_type: str = "vanilla", bottom_right_diagonal: Optional[bool] = None,
+                 enc_dec_bottom_right_diagonal: Optional[bool] = None) -> None:
         super().__init__()
+        self.bottom_right_diagonal = bottom_right_diagonal
+        self.enc_dec_bottom_right_diagonal = enc_dec_bottom_right_diagonal
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
@@ -143,8 +146,12 @@ class TransformerLayer(torch.nn.Module):
                 core_attention_bias_type: str = "no_bias", core_attention_bias: Optional[torch.Tensor] = None,
                 alibi_slopes: Optional[torch.Tensor] = None, cu_seqlens_q=None, cu_seqlens_kv=None,
                 cu_seqlens_q_padded=None, cu_seqlens_kv_padded=None, max_seqlen_q=None, max_seqlen_kv=None,
-                fast_zero_fill: bool = True, pad_between_seqs=None):
+                fast_zero_fill: bool = True, pad_between_seqs=None, bottom_right_diagonal: Optional[bool] = None,
+                enc_dec_bottom_right_diagonal: Optional[bool] = None):
         mask_type = self_attn_mask_type or self.self_attn_mask_type
+        brd = self.bottom_right_diagonal if bottom_right_diagonal is None else bottom_right_diagonal
+        enc_dec_brd = (self.enc_dec_bottom_right_diagonal if enc_dec_bottom_right_diagonal is None
+                       else enc_dec_bottom_right_diagonal)
         window = window_size if window_size is not None else self.window_size
         attn_out = self.self_attention(
             hidden_states, attention_mask=attention_mask, attn_mask_type=mask_type, window_size=window,
@@ -154,7 +161,7 @@ class TransformerLayer(torch.nn.Module):
             alibi_slopes=alibi_slopes, cu_seqlens_q=cu_seqlens_q, cu_seqlens_kv=cu_seqlens_kv,
             cu_seqlens_q_padded=cu_seqlens_q_padded, cu_seqlens_kv_padded=cu_seqlens_kv_padded,
             max_seqlen_q=max_seqlen_q, max_seqlen_kv=max_seqlen_kv, fast_zero_fill=fast_zero_fill,
-            pad_between_seqs=pad_between_seqs)
+            pad_between_seqs=pad_between_seqs, bottom_right_diagonal=brd)
         if self.parallel_attention_mlp:
             mlp_out = self.layernorm_mlp(hidden_states, is_first_microbatch=is_first_microbatch)
             out = hidden_states + torch.nn.functional.dropout(attn_out + mlp_out, p=self.hidden_dropout,
@@ -171,7 +178,8 @@ class TransformerLayer(torch.nn.Module):
                                          attn_mask_type=enc_dec_attn_mask_type or self.enc_dec_attn_mask_type,
                                          window_size=enc_dec_window_size if enc_dec_window_size is not None else self.enc_dec_window_size,
                                          encoder_output=encoder_output, is_first_microbatch=is_first_microbatch,
-                                         checkpoint_core_attention=checkpoint_core_attention)
+                                         checkpoint_core_attention=checkpoint_core_attention,
+                                         bottom_right_diagonal=enc_dec_brd)
             if self.apply_residual_connection_post_layernorm:
                 io, ib, residual = inter
             else:

@@ -475,3 +475,46 @@ def test_grouped_linear_output_buffers():
         gl(x, [4, 6], out=torch.empty(12, 23))
     with pytest.raises(TypeError):
         te.GroupedLinear(2, 16, 24, device="cpu", use_grouped_tensor="yes")
+
+
+@pytest.mark.parametrize("dtypes", [(torch.float16, torch.float16), (torch.uint8, torch.float16),
+                                    (torch.uint8, torch.uint8), (torch.bfloat16, torch.float32)])
+def test_fused_adam_scaled_states(dtypes):
+    """Moments stored in fp16 / FP8 bytes (with a per-tensor scale) or mixed dtypes track the fp32-state optimizer;
+    the state API returns and accepts unscaled fp32 values; checkpoints hold fp32 moments."""
+    def run(**kw):
+        torch.manual_seed(0)
+        p = torch.nn.Parameter(torch.randn(64, 32))
+        opt = te.FusedAdam([p], lr=1e-2, **kw)
+        for i in range(20):
+            torch.manual_seed(i)
+            p.grad = torch.randn(64, 32) * 0.1
+            opt.step()
+        return p, opt
+
+    ref, ref_opt = run()
+    p, opt = run(exp_avg_dtype=dtypes[0], exp_avg_sq_dtype=dtypes[1])
+    st = opt.state[p]
+    assert st["exp_avg"].dtype == dtypes[0] and st["exp_avg_sq"].dtype == dtypes[1]
+    tol = 2e-2 if torch.uint8 in dtypes else 2e-3
+    assert (p - ref).abs().max() < tol
+    m = opt.get_unscaled_state(p, "exp_avg")
+    assert m.dtype == torch.float32
+    rel = (m - ref_opt.state[ref]["exp_avg"]).abs().max() / ref_opt.state[ref]["exp_avg"].abs().max()
+    assert rel < (0.2 if dtypes[0] == torch.uint8 else 1e-2)     # E4M3 rounds by up to 6 % per step
+    sd = opt.state_dict()
+    assert sd["state"][0]["exp_avg"].dtype == torch.float32 and sd["state"][0]["exp_avg_sq"].dtype == torch.float32
+    opt2 = te.FusedAdam([p], lr=1e-2, exp_avg_dtype=dtypes[0], exp_avg_sq_dtype=dtypes[1])
+    opt2.load_state_dict(sd)
+    torch.testing.assert_close(opt2.get_unscaled_state(p, "exp_avg_sq"), opt.get_unscaled_state(p, "exp_avg_sq"))
+    # set_scaled_state: an fp32 value goes in, the stored form is scaled and rounded
+    new = torch.randn(64, 32) * 3.0
+    opt.set_scaled_state(p, "exp_avg", new)
+    back = opt.get_unscaled_state(p, "exp_avg")
+    assert (back - new).abs().max() <= (0.07 if dtypes[0] == torch.uint8 else 0.02) * new.abs().max()
+    # initialize_state before any step, with master weights taken from the parameter
+    q = torch.nn.Parameter(torch.randn(8, 8).bfloat16())
+    o3 = te.FusedAdam([q], master_weights=True, exp_avg_dtype=dtypes[0], exp_avg_sq_dtype=dtypes[1])
+    o3.initialize_state(q)
+    assert torch.equal(o3.get_unscaled_state(q, "master_param"), q.detach().float())
+    assert float(o3.get_unscaled_state(q, "exp_avg").abs().max()) == 0.0

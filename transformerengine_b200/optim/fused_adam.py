@@ -31,8 +31,9 @@ class FusedAdam(torch.optim.Optimizer):
                  store_param_remainders: bool = False):
         if amsgrad:
             raise RuntimeError("FusedAdam does not support the AMSGrad variant.")
-        assert exp_avg_dtype == exp_avg_sq_dtype, "both moments use one dtype"
-        assert exp_avg_dtype in (torch.float32, torch.bfloat16), "moments are fp32 or bf16"
+        for name, dt in (("exp_avg_dtype", exp_avg_dtype), ("exp_avg_sq_dtype", exp_avg_sq_dtype)):
+            if dt not in (torch.float32, torch.bfloat16, torch.float16, torch.uint8):
+                raise RuntimeError(f"{name} must be float32, bfloat16, float16 or uint8 (FP8 E4M3), got {dt}")
         defaults = dict(lr=lr, bias_correction=bias_correction, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
         if store_param_remainders and not master_weights:
@@ -46,7 +47,15 @@ class FusedAdam(torch.optim.Optimizer):
         self.capturable = capturable
         self.master_weights = master_weights
         self.store_param_remainders = store_param_remainders
-        self.state_dtype = exp_avg_dtype
+        # fp32 / bf16 moments are read and written by the multi-tensor kernel itself (both must then share a dtype);
+        # float16 and uint8 (FP8 E4M3 bytes) moments are stored divided by a per-tensor scale and pass through fp32
+        # temporaries around the kernel: less memory, two more passes over the state
+        self.name_to_dtype_map = {"exp_avg": exp_avg_dtype, "exp_avg_sq": exp_avg_sq_dtype,
+                                  "master_param": master_weight_dtype}
+        self._scaled_states = any(d in (torch.float16, torch.uint8) for d in (exp_avg_dtype, exp_avg_sq_dtype)) \
+            or exp_avg_dtype != exp_avg_sq_dtype
+        self.state_dtype = torch.float32 if self._scaled_states else exp_avg_dtype   # dtype the kernel sees
+        self._scales = {}      # param -> {state name -> fp32 scale tensor [1]} for the scaled states
         self.use_decoupled_grad = use_decoupled_grad
         self._noop = None
 
@@ -67,8 +76,11 @@ class FusedAdam(torch.optim.Optimizer):
         st = self.state[key]
         if "exp_avg" not in st:
             base = p.dequantize() if isinstance(p, QuantizedTensor) else p.detach()
-            st["exp_avg"] = torch.zeros(base.shape, dtype=self.state_dtype, device=base.device)
-            st["exp_avg_sq"] = torch.zeros(base.shape, dtype=self.state_dtype, device=base.device)
+            for name in ("exp_avg", "exp_avg_sq"):
+                dt = self.name_to_dtype_map[name] if self._scaled_states else self.state_dtype
+                st[name] = torch.zeros(base.shape, dtype=dt, device=base.device)
+                if dt in (torch.float16, torch.uint8):
+                    self._scales.setdefault(key, {})[name] = torch.ones(1, dtype=torch.float32, device=base.device)
             if self.master_weights or isinstance(p, QuantizedTensor):
                 hp = getattr(p, "_high_precision_init_val", None)
                 master = (hp.to(base.device) if hp is not None else base).float().clone()
@@ -80,6 +92,68 @@ class FusedAdam(torch.optim.Optimizer):
                 else:
                     st["master_param"] = master
         return st
+
+    # ---- optimizer states in high precision (reference: optimizers/fused_adam.py, get_unscaled_state /
+    # set_scaled_state / initialize_state; distributed optimizers use them to save and re-shard the states)
+    _FP8_MAX, _FP16_MAX = 448.0, 65504.0
+
+    def _decode(self, key, name, stored):
+        dt = stored.dtype
+        if dt == torch.uint8:
+            return stored.view(torch.float8_e4m3fn).float() * self._scales[key][name]
+        if dt == torch.float16:
+            return stored.float() * self._scales[key][name]
+        return stored.float() if dt == torch.bfloat16 else stored
+
+    def _encode(self, key, name, value, stored):
+        dt = stored.dtype
+        if dt in (torch.uint8, torch.float16):
+            scale = self._scales[key][name]
+            amax = value.abs().amax().float().clamp(min=1e-30)
+            scale.copy_((amax / (self._FP8_MAX if dt == torch.uint8 else self._FP16_MAX)).reshape(1))
+            q = value.float() / scale
+            if dt == torch.uint8:
+                stored.copy_(q.clamp(-self._FP8_MAX, self._FP8_MAX).to(torch.float8_e4m3fn).view(torch.uint8))
+            else:
+                stored.copy_(q.to(torch.float16))
+        else:
+            stored.copy_(value)
+
+    def get_unscaled_state(self, param, state_name: str, skip_unscale: bool = False) -> torch.Tensor:
+        """The state ``exp_avg`` / ``exp_avg_sq`` / ``master_param`` of ``param`` in fp32 (bf16 states come back as
+        bf16 with ``skip_unscale``; a master weight kept as 16-bit remainders comes back as the int16 remainders).
+        Sharded (``DTensor``) parameters give the local shard's state."""
+        st = self.state[param]
+        if state_name == "master_param" and "param_remainder" in st:
+            return st["param_remainder"]
+        stored = _local(st[state_name])
+        if stored.dtype == torch.bfloat16 and skip_unscale:
+            return stored
+        return self._decode(param, state_name, stored)
+
+    def set_scaled_state(self, param, state_name: str, unscaled_state: torch.Tensor) -> None:
+        """Overwrite a state from its fp32 value (scaled and rounded to the state's storage dtype); the int16
+        remainders for a master weight kept as remainders."""
+        st = self.state[param]
+        if state_name == "master_param" and self.store_param_remainders and _local(param).dtype == torch.bfloat16 \
+                and not isinstance(_local(param), QuantizedTensor):
+            assert unscaled_state.dtype == torch.int16, "a master weight kept as remainders is set from int16"
+            st["param_remainder"] = unscaled_state.clone() if "param_remainder" not in st else \
+                st["param_remainder"].copy_(unscaled_state)
+            return
+        assert unscaled_state.dtype == torch.float32, "states are set from fp32 values"
+        if "exp_avg" not in st:
+            self._init_state(param, _local(param))
+        if state_name == "master_param" and "master_param" not in st:
+            st["master_param"] = unscaled_state.clone()
+            return
+        self._encode(param, state_name, unscaled_state, _local(st[state_name]))
+
+    def initialize_state(self, param, store_param_remainders: bool = False) -> None:
+        """Create the states of ``param`` before the first step (moments zero, master weight from the parameter)."""
+        if store_param_remainders and not self.store_param_remainders:
+            raise RuntimeError("the optimizer was built without store_param_remainders")
+        self._init_state(param, _local(param))
 
     def _step_value(self, group):
         """Host int, or (capturable) an int32 device scalar advanced by a device op."""
@@ -117,6 +191,7 @@ class FusedAdam(torch.optim.Optimizer):
             b1, b2 = group["betas"]
             buckets = {}
             quantized = []
+            rescale = []        # (param, state, fp32 exp_avg, fp32 exp_avg_sq) of scaled states, written back below
             for p in group["params"]:
                 g = getattr(p, "decoupled_grad", None) if self.use_decoupled_grad else p.grad
                 if g is None:
@@ -131,13 +206,21 @@ class FusedAdam(torch.optim.Optimizer):
                     continue    # this rank's shard of a small sharded parameter is empty
                 st = self._init_state(key_param, p)
                 if isinstance(p, QuantizedTensor):
-                    quantized.append((p, g, st))
+                    quantized.append((key_param, p, g, st))
                     continue
                 mode = 2 if "param_remainder" in st else (1 if "master_param" in st else 0)
                 key = (g.dtype, p.dtype, mode)
                 b = buckets.setdefault(key, [[], [], [], [], []])
                 b[0].append(g)
                 b[1].append(p.data)
+                if self._scaled_states:
+                    m, v = (self._decode(key_param, n, st[n]).contiguous() for n in ("exp_avg", "exp_avg_sq"))
+                    rescale.append((key_param, st, m, v))
+                    b[2].append(m)
+                    b[3].append(v)
+                    if mode:
+                        b[4].append(st["param_remainder"] if mode == 2 else st["master_param"])
+                    continue
                 b[2].append(st["exp_avg"])
                 b[3].append(st["exp_avg_sq"])
                 if mode:
@@ -146,13 +229,22 @@ class FusedAdam(torch.optim.Optimizer):
                 ls = lists if mode else lists[:4]
                 ops.multi_tensor_adam(ls, lr, b1, b2, group["eps"], step, self.adam_w_mode,
                                       group["bias_correction"], group["weight_decay"], remainders=mode == 2)
-            for p, g, st in quantized:
+            for kp, p, g, st in quantized:
                 # quantized (FP8 / block-scaled) parameters: update the fp32 master, then re-quantize in place
                 tmp = torch.empty_like(st["master_param"])
-                ops.multi_tensor_adam([[g.float()], [tmp], [st["exp_avg"]], [st["exp_avg_sq"]], [st["master_param"]]],
+                if self._scaled_states:
+                    m, v = (self._decode(kp, n, st[n]).contiguous() for n in ("exp_avg", "exp_avg_sq"))
+                    rescale.append((kp, st, m, v))
+                else:
+                    m, v = st["exp_avg"], st["exp_avg_sq"]
+                ops.multi_tensor_adam([[g.float()], [tmp], [m], [v], [st["master_param"]]],
                                       lr, b1, b2, group["eps"], step, self.adam_w_mode,
                                       group["bias_correction"], group["weight_decay"])
                 p.quantize_(st["master_param"])
+            for kp, st, m, v in rescale:
+                for name, val in (("exp_avg", m), ("exp_avg_sq", v)):
+                    if val is not st[name]:
+                        self._encode(kp, name, val, st[name])
         bump_weights_epoch()
         return loss
 
@@ -162,18 +254,29 @@ class FusedAdam(torch.optim.Optimizer):
             g.pop("_lr_dev", None)
             if isinstance(g.get("step"), torch.Tensor):
                 g["step"] = int(g["step"].item())
-        for st in sd["state"].values():
+        params = [p for g in self.param_groups for p in g["params"]]
+        for idx, st in sd["state"].items():
             for k in ("exp_avg", "exp_avg_sq"):
                 if k in st and st[k].dtype != torch.float32:
-                    st[k] = st[k].float()  # checkpoints always hold unscaled fp32 moments
+                    key = params[idx] if isinstance(idx, int) and idx < len(params) else None
+                    # checkpoints always hold unscaled fp32 moments
+                    st[k] = self._decode(key, k, st[k]) if st[k].dtype in (torch.uint8, torch.float16) else st[k].float()
         return sd
 
     def load_state_dict(self, state_dict):  # type: ignore[override]
         super().load_state_dict(state_dict)
-        for st in self.state.values():
+        for key, st in self.state.items():
             for k in ("exp_avg", "exp_avg_sq"):
-                if k in st and st[k].dtype != self.state_dtype:
-                    st[k] = st[k].to(self.state_dtype)
+                if k not in st:
+                    continue
+                want = self.name_to_dtype_map[k] if self._scaled_states else self.state_dtype
+                if want in (torch.uint8, torch.float16):
+                    value = st[k].float()
+                    st[k] = torch.zeros(value.shape, dtype=want, device=value.device)
+                    self._scales.setdefault(key, {})[k] = torch.ones(1, dtype=torch.float32, device=value.device)
+                    self._encode(key, k, value, st[k])
+                elif st[k].dtype != want:
+                    st[k] = st[k].to(want)
             if "master_param" in st:
                 st["master_param"] = st["master_param"].float()
         bump_weights_epoch()

@@ -39,6 +39,10 @@ def _step_metadata(lens_old: List[int], lens_new: List[int], tables: List[List[i
 class KVCacheManager:
     """Interface of a cache manager (custom managers may subclass it)."""
 
+    def reset(self) -> None:
+        """Forget every sequence (the cache memory stays allocated)."""
+        raise NotImplementedError
+
     def allocate_memory(self, layer_number: int) -> None:
         raise NotImplementedError
 
@@ -87,6 +91,13 @@ class NonPagedKVCacheManager(KVCacheManager):
     def post_step(self):
         for sid, n in self.step_dict.items():
             self.lengths[sid] += n
+
+    def reset(self) -> None:
+        self.slots.clear()
+        self.lengths.clear()
+        self.step_dict = OrderedDict()
+        self.free_slots = list(range(self.max_batch_size - 1, -1, -1))
+        self._meta = None
 
     def step(self, layer_number, new_k, new_v, cu_new):
         if layer_number not in self.cache:
@@ -145,13 +156,64 @@ class PagedKVCacheManager(KVCacheManager):
         for sid, n in self.step_dict.items():
             self.lengths[sid] += n
 
-    def get_page_table(self, device=None) -> torch.Tensor:
-        """``[num_live_sequences, max_pages_per_seq]`` int32 table, -1 where unused."""
-        width = max((len(p) for p in self.page_table.values()), default=0)
-        t = torch.full((len(self.page_table), width), -1, dtype=torch.int32, device=device)
-        for i, pages in enumerate(self.page_table.values()):
+    def get_page_table(self, sequences: Optional[List[int]] = None, device=None) -> torch.Tensor:
+        """``[num_sequences, max_pages_per_seq]`` int32 table of the live sequences (or of ``sequences``, in that
+        order), -1 where unused."""
+        tables = [self.page_table[s] for s in sequences] if sequences is not None else list(self.page_table.values())
+        width = max((len(p) for p in tables), default=0)
+        t = torch.full((len(tables), width), -1, dtype=torch.int32, device=device)
+        for i, pages in enumerate(tables):
             t[i, :len(pages)] = torch.tensor(pages, dtype=torch.int32)
         return t
+
+    # ---- bookkeeping queries and manual page management (reference: attention/inference.py, PagedKVCacheManager)
+    def reset(self) -> None:
+        self.free_pages = list(range(self.total_num_pages - 1, -1, -1))
+        self.page_table = OrderedDict()
+        self.lengths = {}
+        self.step_dict = OrderedDict()
+        self._meta = None
+
+    def get_sequence_count(self) -> int:
+        return len(self.page_table)
+
+    def get_sequence_lengths(self) -> List[int]:
+        """Cached tokens of every live sequence (before the step in flight)."""
+        return [self.lengths[s] for s in self.page_table]
+
+    def has_free_page(self) -> bool:
+        return len(self.free_pages) > 0
+
+    def get_page_count(self, seq: int) -> int:
+        return len(self.page_table.get(seq, ()))
+
+    def get_page_list(self, seq: int) -> List[int]:
+        return list(self.page_table.get(seq, ()))
+
+    def allocate_page(self, seq: int) -> None:
+        if not self.free_pages:
+            raise RuntimeError("KV cache is full!")
+        self.page_table.setdefault(seq, []).append(self.free_pages.pop())
+        self.lengths.setdefault(seq, 0)
+
+    def allocate_sequence(self, seq: int, context_len: int) -> None:
+        """Reserve the pages ``context_len`` tokens of a new sequence need."""
+        for _ in range(-(-context_len // self.page_size)):
+            self.allocate_page(seq)
+
+    def deallocate_sequence(self, seq: int) -> None:
+        self.free_pages.extend(self.page_table.pop(seq, ()))
+        self.lengths.pop(seq, None)
+
+    def print_cache(self) -> None:
+        import logging
+
+        log = logging.getLogger("PagedKVCacheManager")
+        used = sum(len(p) for p in self.page_table.values())
+        log.debug("total pages: %s (used %s, free %s); sequences: %s", self.total_num_pages, used,
+                  len(self.free_pages), len(self.page_table))
+        for i, (seq, pages) in enumerate(self.page_table.items()):
+            log.debug("  batch index %s: seq_id %s, tokens %s, pages %s", i, seq, self.lengths.get(seq, 0), pages)
 
     def step(self, layer_number, new_k, new_v, cu_new):
         if layer_number not in self.cache:
@@ -197,6 +259,11 @@ class InferenceParams:
     def reset(self):
         self.pre_step(OrderedDict())
         self.sequences = OrderedDict()
+        if hasattr(self.cache_manager, "reset"):
+            try:
+                self.cache_manager.reset()
+            except NotImplementedError:
+                pass
 
     def allocate_memory(self, layer_number: int):
         self.cache_manager.allocate_memory(layer_number)
@@ -213,6 +280,24 @@ class InferenceParams:
 
     def get_seqlens_pre_step(self) -> torch.Tensor:
         return torch.tensor(list(self.sequences.values()), dtype=torch.int32)
+
+    def convert_paged_to_nonpaged(self, layer_number: int):
+        """The paged cache of one layer as contiguous ``[sequences, pages_per_seq * page_size, h, d]`` tensors
+        (sequences in batch order; positions past a sequence's length hold whatever its last page holds)."""
+        assert self.is_paged, "the cache is not paged"
+        k, v = self.cache_manager.cache[layer_number]
+        table = self.cache_manager.get_page_table(device=k.device).clamp(min=0).long()
+        n, w = table.shape
+        gather = lambda c: c[table.reshape(-1)].reshape(n, w * c.shape[1], *c.shape[2:]).contiguous()  # noqa: E731
+        return gather(k), gather(v)
+
+    def __repr__(self) -> str:
+        kind = f"paged (page_size={self.page_size}, total_num_pages={self.total_num_pages})" if self.is_paged \
+            else "non-paged"
+        return (f"InferenceParams({kind}, max_batch_size={self.max_batch_size}, "
+                f"max_sequence_length={self.max_sequence_length}, num_heads_kv={self.num_heads_kv}, "
+                f"head_dim_k={self.head_dim_k}, head_dim_v={self.head_dim_v}, dtype={self.dtype}, "
+                f"sequences={dict(self.sequences)})")
 
     def sequence_start_positions(self, batch: int, device) -> torch.Tensor:
         """Position of each sequence's first new token (RoPE offset)."""

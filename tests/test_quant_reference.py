@@ -138,3 +138,70 @@ def test_standalone_hadamard_transform_matches_the_quantizer():
     res = qz.quantize_nvfp4(xb, with_rht=True)
     want = ops.hadamard_transform(xb.float(), transposed=True).abs().max()
     torch.testing.assert_close(res[5].reshape(()).float(), want, rtol=1e-6, atol=0)
+
+
+def test_quantizer_and_tensor_conveniences():
+    """Small API of the quantizers / quantized tensors: shapes of the scale buffers and the column-wise copy,
+    determinism flags, wrapping existing bytes, metadata, make_like, clear, copy_from_storage."""
+    import transformerengine_b200 as te
+    from transformerengine_b200.tensor.blockwise import Float8BlockQuantizer
+    from transformerengine_b200.tensor.float8 import Float8CurrentScalingQuantizer, Float8Quantizer
+    from transformerengine_b200.tensor.mxfp8 import MXFP8Quantizer
+    from transformerengine_b200.tensor.nvfp4 import NVFP4Quantizer
+
+    x = torch.randn(64, 96)
+    mx = MXFP8Quantizer()
+    q = mx(x)
+    assert mx.get_scale_shape(x.shape, False) == (128, 4) and q._rowwise_scale_inv.numel() == 128 * 4
+    assert mx.get_scale_shape(x.shape, True) == (128, 4) and mx.get_columnwise_shape(x.shape) == (96, 64)
+    assert tuple(q._columnwise_data.shape) == mx.get_columnwise_shape(x.shape)
+    nv = NVFP4Quantizer()
+    n = nv(x)
+    assert nv.get_scale_shape(x.shape, False) == (128, 8) and n._rowwise_scale_inv.numel() == 128 * 8
+    assert nv.convert_shape_for_fp4((64, 96)) == (64, 48) == tuple(n._rowwise_data.shape)
+    blk = Float8BlockQuantizer(block_scaling_dim=2)
+    assert blk.get_scale_shape((300, 200), False) == (3, 2) and blk.get_scale_shape((300, 200), True) == (2, 3)
+    assert Float8BlockQuantizer(block_scaling_dim=1).get_scale_shape((300, 200), False) == (300, 2)
+    cur = Float8CurrentScalingQuantizer(torch.float8_e4m3fn)
+    delayed = Float8Quantizer(torch.ones(1), torch.zeros(1), torch.float8_e4m3fn)
+    assert [z.is_requantization_safe() for z in (mx, nv, blk, cur, delayed)] == [True, True, True, True, False]
+    assert not NVFP4Quantizer(stochastic_rounding=True).is_requantization_safe()
+    assert te.HybridQuantizer(rowwise_quantizer=MXFP8Quantizer(),
+                              columnwise_quantizer=Float8CurrentScalingQuantizer(torch.float8_e4m3fn)).is_requantization_safe()
+    a, b = mx.multi_quantize([x, 2 * x])
+    assert torch.equal(a.dequantize() * 2, b.dequantize())
+    # wrapping bytes that already exist
+    back = mx.create_tensor_from_data(q._rowwise_data, q._rowwise_scale_inv, fake_dtype=torch.float32)
+    assert torch.equal(back.dequantize(), q.dequantize())
+    c = cur(x)
+    again = cur.create_tensor_from_data(c._data, scale_inv=c._scale_inv)
+    assert torch.equal(again.dequantize(), c.dequantize())
+    # current scaling with an amax the caller already has; scale / amax outputs
+    amax, scale = x.abs().amax().reshape(1).clone(), torch.zeros(1)
+    pre = Float8CurrentScalingQuantizer(torch.float8_e4m3fn, use_existing_amax=True, amax=amax, scale=scale)
+    assert torch.equal(pre(x).dequantize(), c.dequantize()) and float(scale) > 0
+    # tensor conveniences
+    meta = c.get_metadata()
+    rebuilt = type(c)(shape=c.shape, dtype=c.dtype, **meta)
+    assert torch.equal(rebuilt.dequantize(), c.dequantize())
+    like = type(c).make_like(c, dtype=torch.bfloat16, requires_grad=True)
+    assert like.dtype == torch.bfloat16 and like.requires_grad and like._data is c._data
+    c.update_usage(columnwise_usage=True)
+    assert c._transpose is not None
+    c.remove_caches()
+    assert c._transpose is None
+    dst = mx.make_empty(x.shape)
+    dst.copy_from_storage(q)
+    assert torch.equal(dst.dequantize(), q.dequantize())
+    with pytest.raises(ValueError):
+        mx.make_empty((32, 96)).copy_from_storage(q)
+    q.update_quantizer(MXFP8Quantizer(rowwise=True, columnwise=False))
+    with pytest.raises(TypeError):
+        q.update_quantizer(cur)
+    q.clear()
+    assert q._rowwise_data.numel() == 0
+    h = te.HybridQuantizer(rowwise_quantizer=Float8CurrentScalingQuantizer(torch.float8_e4m3fn),
+                           columnwise_quantizer=MXFP8Quantizer())
+    assert not h.with_amax_reduction and h.amax_reduction_group is None
+    h.with_amax_reduction = True
+    assert h.rowwise_quantizer.with_amax_reduction

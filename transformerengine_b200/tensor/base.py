@@ -75,6 +75,35 @@ class QuantizedTensorStorage:
         c = self._shape[-1]
         return self.numel() // max(c, 1), c
 
+    # -- conveniences shared by all formats (reference: quantized_tensor.py, QuantizedTensorStorage) -------------
+    def update_quantizer(self, quantizer: "Quantizer") -> None:
+        """Bind another quantizer (of the same kind) to this tensor: later in-place updates use it."""
+        if self._quantizer is not None and type(quantizer) is not type(self._quantizer):
+            raise TypeError(f"cannot replace a {type(self._quantizer).__name__} by a {type(quantizer).__name__}")
+        self._quantizer = quantizer
+
+    def copy_from_storage(self, src: "QuantizedTensorStorage") -> None:
+        """Copy the payload of ``src`` (same class, shape and set of copies) into this object's buffers."""
+        if type(src) is not type(self) and not (isinstance(src, type(self)) or isinstance(self, type(src))):
+            raise TypeError(f"cannot copy a {type(src).__name__} into a {type(self).__name__}")
+        if tuple(src._shape) != tuple(self._shape):
+            raise ValueError(f"shape mismatch: {tuple(src._shape)} vs {tuple(self._shape)}")
+        for name, val in vars(src).items():
+            mine = getattr(self, name, None)
+            if isinstance(val, torch.Tensor) and name.startswith("_") and name not in ("_quantizer",):
+                if isinstance(mine, torch.Tensor) and mine.shape == val.shape:
+                    mine.copy_(val)
+                elif mine is None:
+                    raise ValueError(f"the destination lacks the buffer {name}")
+            elif isinstance(mine, torch.Tensor) and val is None and name.startswith("_"):
+                raise ValueError(f"the source lacks the buffer {name}")
+
+    def clear(self) -> None:
+        """Release the payload (the object stays, its buffers become empty tensors)."""
+        for name, val in list(vars(self).items()):
+            if isinstance(val, torch.Tensor) and name.startswith("_"):
+                setattr(self, name, torch.empty(0, dtype=val.dtype, device=val.device))
+
 
 class Quantizer(abc.ABC):
     """Builder of quantized tensors.
@@ -117,20 +146,54 @@ class Quantizer(abc.ABC):
         ...
 
     @abc.abstractmethod
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
         ...
 
     def calibrate(self, tensor: torch.Tensor) -> None:
         """Record statistics without quantizing (``autocast(calibrating=True)``)."""
 
-    def is_quantizable(self, tensor: torch.Tensor) -> bool:
+    def is_quantizable(self, inp: torch.Tensor) -> bool:
+        """Whether ``inp`` can be quantized by this quantizer as it is (shape constraints of the format)."""
         return True
+
+    def is_requantization_safe(self) -> bool:
+        """Whether quantizing the same input again reproduces the same payload (False for quantizers with state
+        that moves, such as delayed scaling, or with random rounding): callers may then drop a quantized value and
+        rebuild it later."""
+        return False
+
+    def multi_quantize(self, tensors) -> list:
+        """Quantize a list of tensors with this quantizer's settings."""
+        return [self.quantize(t) for t in tensors]
+
+    def get_columnwise_shape(self, shape: Iterable[int]) -> Tuple[int, ...]:
+        """Shape of the column-wise copy of a tensor of ``shape``: stored transposed, ``[last dim, product of the
+        leading dims]``."""
+        shape = tuple(shape)
+        if not shape:
+            return ()
+        rows = 1
+        for d in shape[:-1]:
+            rows *= d
+        return (shape[-1], rows)
 
     def supports_only_rowwise_all_gather(self) -> bool:
         return False
 
     def get_usages(self) -> Dict[str, bool]:
         return {"rowwise": self.rowwise_usage, "columnwise": self.columnwise_usage}
+
+
+def pin_payload(obj):
+    """Move the payload tensors of a quantized tensor on the host into page-locked memory (``make_empty(...,
+    pin_memory=True)``: staging buffers of asynchronous host <-> device copies)."""
+    for name, val in list(vars(obj).items()):
+        if isinstance(val, torch.Tensor) and name.startswith("_") and val.device.type == "cpu" and not val.is_pinned():
+            setattr(obj, name, val.pin_memory())
+        elif isinstance(val, QuantizedTensorStorage):
+            pin_payload(val)
+    return obj
 
 
 def _stride_for(shape) -> Tuple[int, ...]:
@@ -270,6 +333,32 @@ class QuantizedTensor(torch.Tensor):
 
     def to_dtype(self, dtype: torch.dtype):
         return self._new_like(dtype=dtype)
+
+    def get_metadata(self) -> Dict[str, Any]:
+        """Everything but shape / dtype / requires_grad that ``type(self)(...)`` needs to rebuild this tensor: the
+        payload tensors and the format fields, by constructor keyword."""
+        import inspect
+
+        out: Dict[str, Any] = {}
+        params = inspect.signature(type(self).__new__).parameters
+        alias = {"fp8_scale_inv": "_scale_inv", "data_transpose": "_transpose"}
+        for name in params:
+            if name in ("cls", "shape", "dtype", "requires_grad", "device"):
+                continue
+            attr = alias.get(name, "_" + name)
+            if hasattr(self, attr):
+                out[name] = getattr(self, attr)
+        return out
+
+    @classmethod
+    def make_like(cls, tensor: "QuantizedTensor", *, shape=None, dtype=None,
+                  requires_grad: bool = False) -> "QuantizedTensor":
+        """A tensor that shares ``tensor``'s payload and quantizer under another logical dtype / requires_grad
+        (``shape`` must describe the same number of elements)."""
+        if shape is not None and tuple(shape) != tuple(tensor._shape):
+            raise ValueError(f"make_like keeps the payload, whose shape is {tuple(tensor._shape)}; reshape the source "
+                             f"to {tuple(shape)} first")
+        return tensor._new_like(requires_grad=requires_grad, dtype=dtype)
 
 
 def prepare_for_saving(*tensors):

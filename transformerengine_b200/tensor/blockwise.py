@@ -14,7 +14,7 @@ from typing import Iterable
 import torch
 
 from ..ops.ref import quant as Q
-from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer, pin_payload
 
 
 class Float8BlockwiseQTensorStorage(QuantizedTensorStorage):
@@ -123,6 +123,26 @@ class Float8BlockQuantizer(Quantizer):
         self.force_pow_2_scales = force_pow_2_scales
         self.block_scaling_dim = block_scaling_dim
 
+    def is_requantization_safe(self) -> bool:
+        return True
+
+    def is_quantizable(self, inp) -> bool:
+        return inp.dim() >= 2
+
+    def get_scale_shape(self, shape, columnwise: bool):
+        """Shape of the fp32 block scales of a tensor of ``shape``: one per 1 x 128 block (``block_scaling_dim=1``)
+        or per 128 x 128 block (2).  The column-wise copy is stored transposed, so its scales are those of a
+        ``[last dim, rows]`` matrix."""
+        shape = tuple(shape)
+        C = shape[-1]
+        R = 1
+        for d in shape[:-1]:
+            R *= d
+        if columnwise:
+            R, C = C, R
+        outer = (R + 127) // 128 if self.block_scaling_dim == 2 else R
+        return (outer, (C + 127) // 128)
+
     def _parts_cuda(self, x2d, rowwise, columnwise):
         """One kernel: both copies, compact fp32 scales and (power-of-two scales) GEMM-layout UE8M0 scales."""
         from ..ops import _ext
@@ -198,7 +218,8 @@ class Float8BlockQuantizer(Quantizer):
                 else dst._columnwise_mx_scale.copy_(cmx)
         return dst
 
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
         x = torch.zeros(tuple(shape), dtype=dtype, device=device)
         was, self.internal = self.internal, False
         try:
@@ -206,4 +227,4 @@ class Float8BlockQuantizer(Quantizer):
         finally:
             self.internal = was
         out.requires_grad_(requires_grad)
-        return out
+        return pin_payload(out) if pin_memory else out

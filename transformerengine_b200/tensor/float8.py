@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from ..ops.ref import quant as Q
-from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer, pin_payload
 
 
 class Float8TensorStorage(QuantizedTensorStorage):
@@ -92,6 +92,11 @@ class Float8Tensor(Float8TensorStorage, QuantizedTensor):
         return (_make_float8_tensor_in_reduce_ex,
                 (self._data, self._fp8_dtype, self._scale_inv, self._dtype, self._shape, self._transpose))
 
+    def remove_caches(self) -> None:
+        """Drop the transposed copy (it is rebuilt from the row-wise bytes when a GEMM needs it)."""
+        if self._data is not None:
+            self._transpose = None
+
     # ---- structural ops that keep the FP8 payload (what FSDP2 does to a parameter when it shards it: chunk along
     # dim 0, allocate a padded buffer, copy the chunk into a slice of it, flatten).  One scale covers the tensor,
     # so every piece shares the scale tensor of its source.
@@ -167,6 +172,22 @@ def _make_float8_tensor_in_reduce_ex(data, fp8_dtype, scale_inv, dtype, shape, d
 class _Float8QuantizerBase(Quantizer):
     dtype: torch.dtype
 
+    def create_tensor_from_data(self, data: torch.Tensor, fake_dtype: torch.dtype = torch.float32,
+                                requires_grad: bool = False, internal: bool = False, scale_inv=None):
+        """Wrap existing FP8 bytes (uint8, or a float8 tensor viewed as bytes) as a tensor of this quantizer; the
+        decode scale is ``scale_inv``, or the reciprocal of the quantizer's current scale."""
+        if data.dtype != torch.uint8:
+            data = data.view(torch.uint8)
+        if scale_inv is None:
+            scale = getattr(self, "scale", None)
+            scale_inv = torch.ones(1, dtype=torch.float32, device=data.device) if scale is None \
+                else scale.detach().float().reshape(1).reciprocal().to(data.device)
+        if internal:
+            return Float8TensorStorage(data=data, fp8_scale_inv=scale_inv, fp8_dtype=self.dtype, quantizer=self,
+                                       shape=tuple(data.shape), dtype=fake_dtype)
+        return Float8Tensor(shape=tuple(data.shape), dtype=fake_dtype, data=data, fp8_scale_inv=scale_inv,
+                            fp8_dtype=self.dtype, quantizer=self, requires_grad=requires_grad)
+
     def _wrap(self, data, tr, scale_inv, shape, hp_dtype, requires_grad=False):
         if self.internal:
             return Float8TensorStorage(data=data, fp8_scale_inv=scale_inv, fp8_dtype=self.dtype,
@@ -174,7 +195,8 @@ class _Float8QuantizerBase(Quantizer):
         return Float8Tensor(shape=shape, dtype=hp_dtype, data=data, fp8_scale_inv=scale_inv,
                             fp8_dtype=self.dtype, data_transpose=tr, quantizer=self, requires_grad=requires_grad)
 
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
         shape = tuple(shape)
         C = shape[-1]
         R = 1
@@ -185,9 +207,10 @@ class _Float8QuantizerBase(Quantizer):
         si = torch.ones(1, dtype=torch.float32, device=device)
         was, self.internal = self.internal, False
         try:
-            return self._wrap(data, tr, si, shape, dtype, requires_grad)
+            out = self._wrap(data, tr, si, shape, dtype, requires_grad)
         finally:
             self.internal = was
+        return pin_payload(out) if pin_memory else out
 
 
 class Float8Quantizer(_Float8QuantizerBase):
@@ -238,19 +261,38 @@ class Float8CurrentScalingQuantizer(_Float8QuantizerBase):
 
     def __init__(self, fp8_dtype: torch.dtype, device=None, *, rowwise=True, columnwise=True,
                  with_amax_reduction=False, amax_reduction_group=None, force_pow_2_scales=False,
-                 amax_epsilon=0.0):
+                 amax_epsilon=0.0, use_existing_amax: bool = False, scale: Optional[torch.Tensor] = None,
+                 amax: Optional[torch.Tensor] = None):
         super().__init__(rowwise=rowwise, columnwise=columnwise)
         self.dtype = fp8_dtype
         self.with_amax_reduction = with_amax_reduction
         self.amax_reduction_group = amax_reduction_group
         self.force_pow_2_scales = force_pow_2_scales
         self.amax_epsilon = amax_epsilon
+        # use_existing_amax: the caller (a fused producer kernel, say) has already written the tensor's amax into
+        # ``amax``; the quantizer then skips its own reduction pass.  ``scale`` / ``amax`` (fp32 [1]), when given,
+        # receive the values used by the latest quantization.
+        self.use_existing_amax = use_existing_amax
+        self.scale, self.amax = scale, amax
+        if use_existing_amax and amax is None:
+            raise ValueError("use_existing_amax needs the amax tensor")
+
+    def is_requantization_safe(self) -> bool:
+        return True
 
     def _scale_for(self, tensor):
-        amax = ops.amax(tensor)
+        if self.use_existing_amax:
+            amax = self.amax.detach().float().reshape(-1)[:1].clone().to(tensor.device)
+        else:
+            amax = ops.amax(tensor)
         if self.with_amax_reduction and self.amax_reduction_group is not None:
             torch.distributed.all_reduce(amax, op=torch.distributed.ReduceOp.MAX, group=self.amax_reduction_group)
-        return Q.compute_scale_from_amax(amax, Q.fp8_max(self.dtype), 0, self.force_pow_2_scales, self.amax_epsilon)
+        scale = Q.compute_scale_from_amax(amax, Q.fp8_max(self.dtype), 0, self.force_pow_2_scales, self.amax_epsilon)
+        if self.amax is not None and not self.use_existing_amax:
+            self.amax.copy_(amax.reshape(self.amax.shape))
+        if self.scale is not None:
+            self.scale.copy_(scale.reshape(self.scale.shape))
+        return scale
 
     def quantize_impl(self, tensor, dtype=None):
         shape = tuple(tensor.shape)

@@ -104,8 +104,9 @@ class IdentityQuantizer(Quantizer):
             dst._data = new.clone()
         return dst
 
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
-        data = torch.empty(tuple(shape), dtype=self.dtype or dtype, device=device)
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
+        data = torch.empty(tuple(shape), dtype=self.dtype or dtype, device=device, pin_memory=pin_memory)
         return IdentityTensor(data=data, quantizer=self, shape=tuple(shape), dtype=dtype, requires_grad=requires_grad)
 
     def is_requantization_safe(self) -> bool:
@@ -279,18 +280,55 @@ class HybridQuantizer(Quantizer):
         dst._rowwise, dst._columnwise = row, col
         return dst
 
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
         shape = tuple(shape)
         for q in (self.rowwise_quantizer, self.columnwise_quantizer):
             q.internal = True
-        row = self.rowwise_quantizer.make_empty(shape, dtype=dtype, device=device) if self.rowwise_usage else None
-        col = self.columnwise_quantizer.make_empty(shape, dtype=dtype, device=device) if self.columnwise_usage else None
+        self._resolved()
+        kw = dict(dtype=dtype, device=device, pin_memory=pin_memory)
+        row = self.rowwise_quantizer.make_empty(shape, **kw) if self.rowwise_usage else None
+        col = self.columnwise_quantizer.make_empty(shape, **kw) if self.columnwise_usage else None
         return HybridQuantizedTensor(rowwise=row, columnwise=col, quantizer=self, shape=shape, dtype=dtype,
                                      requires_grad=requires_grad)
 
     def calibrate(self, tensor: torch.Tensor) -> None:
         self.rowwise_quantizer.calibrate(tensor)
         self.columnwise_quantizer.calibrate(tensor)
+
+    def is_requantization_safe(self) -> bool:
+        if self.rowwise_usage and not self.rowwise_quantizer.is_requantization_safe():
+            return False
+        if self.columnwise_usage and not self.columnwise_quantizer.is_requantization_safe():
+            return False
+        # a column-wise copy derived from the dequantized row-wise copy inherits the row-wise quantizer's determinism
+        return not (self.columnwise_usage and self.columnwise_source == "rowwise_dequantized"
+                    and not self.rowwise_quantizer.is_requantization_safe())
+
+    # amax reduction over a process group is a property of the children that compute an amax (current scaling,
+    # NVFP4); setting it here sets it on every child that has the notion
+    @property
+    def with_amax_reduction(self) -> bool:
+        return any(getattr(q, "with_amax_reduction", False) for q in (self.rowwise_quantizer, self.columnwise_quantizer))
+
+    @with_amax_reduction.setter
+    def with_amax_reduction(self, value: bool) -> None:
+        for q in (self.rowwise_quantizer, self.columnwise_quantizer):
+            if hasattr(q, "with_amax_reduction"):
+                q.with_amax_reduction = value
+
+    @property
+    def amax_reduction_group(self):
+        for q in (self.rowwise_quantizer, self.columnwise_quantizer):
+            if getattr(q, "amax_reduction_group", None) is not None:
+                return q.amax_reduction_group
+        return None
+
+    @amax_reduction_group.setter
+    def amax_reduction_group(self, group) -> None:
+        for q in (self.rowwise_quantizer, self.columnwise_quantizer):
+            if hasattr(q, "amax_reduction_group"):
+                q.amax_reduction_group = group
 
     def supports_only_rowwise_all_gather(self) -> bool:
         return True

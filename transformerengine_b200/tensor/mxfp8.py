@@ -230,12 +230,40 @@ class MXFP8Quantizer(Quantizer):
         super().__init__(rowwise=rowwise, columnwise=columnwise)
         self.dtype = fp8_dtype
 
-    def is_quantizable(self, tensor):
-        if tensor.dim() < 2:
+    def is_quantizable(self, inp):
+        if inp.dim() < 2:
             return False
-        C = tensor.shape[-1]
-        R = tensor.numel() // max(C, 1)
+        C = inp.shape[-1]
+        R = inp.numel() // max(C, 1)
         return C % 32 == 0 and R % 32 == 0
+
+    def is_requantization_safe(self) -> bool:
+        return True
+
+    def get_scale_shape(self, shape: Iterable[int], columnwise: bool):
+        """``(outer, inner)`` extent of the UE8M0 scale buffer of a tensor of ``shape`` (one scale per 32 values,
+        padded to whole 128 x 4 tiles; the buffer itself is flat and tile-swizzled).  The column-wise copy is stored
+        transposed, so its scales are those of a ``[last dim, rows]`` matrix."""
+        shape = tuple(shape)
+        C = shape[-1]
+        R = 1
+        for d in shape[:-1]:
+            R *= d
+        if columnwise:
+            return (Q.round_up(C, 128), Q.round_up(R // 32, 4))
+        return (Q.round_up(R, 128), Q.round_up(C // 32, 4))
+
+    def create_tensor_from_data(self, data: torch.Tensor, scale_inv: torch.Tensor,
+                                fake_dtype: torch.dtype = torch.float32, fp8_dtype: Optional[torch.dtype] = None,
+                                requires_grad: bool = False):
+        """Wrap existing row-wise bytes and their (tile-swizzled) scales as a tensor of this quantizer."""
+        data = data if data.dtype == torch.uint8 else data.view(torch.uint8)
+        outer, inner = self.get_scale_shape(data.shape, False)
+        if scale_inv.numel() != outer * inner:
+            raise ValueError(f"scale_inv must hold {outer * inner} bytes for data of shape {tuple(data.shape)}")
+        return MXFP8Tensor(shape=tuple(data.shape), dtype=fake_dtype, rowwise_data=data,
+                           rowwise_scale_inv=scale_inv.reshape(-1), columnwise_data=None, columnwise_scale_inv=None,
+                           fp8_dtype=fp8_dtype or self.dtype, quantizer=self, requires_grad=requires_grad)
 
     def _wrap(self, rd, rs, cd, cs, shape, hp_dtype, requires_grad=False):
         kw = dict(rowwise_data=rd, rowwise_scale_inv=rs, columnwise_data=cd, columnwise_scale_inv=cs,
@@ -266,19 +294,21 @@ class MXFP8Quantizer(Quantizer):
             dst._columnwise_scale_inv.copy_(cs)
         return dst
 
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
         shape = tuple(shape)
         C = shape[-1]
         R = 1
         for s in shape[:-1]:
             R *= s
         rd = rs = cd = cs = None
+        kw = dict(dtype=torch.uint8, device=device, pin_memory=pin_memory)
         if self.rowwise_usage:
-            rd = torch.empty(shape, dtype=torch.uint8, device=device)
-            rs = torch.zeros(Q.round_up(R, 128) * Q.round_up(C // 32, 4), dtype=torch.uint8, device=device)
+            rd = torch.empty(shape, **kw)
+            rs = torch.zeros(Q.round_up(R, 128) * Q.round_up(C // 32, 4), **kw)
         if self.columnwise_usage:
-            cd = torch.empty(C, R, dtype=torch.uint8, device=device)
-            cs = torch.zeros(Q.round_up(C, 128) * Q.round_up(R // 32, 4), dtype=torch.uint8, device=device)
+            cd = torch.empty(C, R, **kw)
+            cs = torch.zeros(Q.round_up(C, 128) * Q.round_up(R // 32, 4), **kw)
         was, self.internal = self.internal, False
         try:
             return self._wrap(rd, rs, cd, cs, shape, dtype, requires_grad)

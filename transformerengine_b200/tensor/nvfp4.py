@@ -11,13 +11,13 @@ cancels in the wgrad GEMM because both operands carry the same rotation.
 """
 from __future__ import annotations
 
-from typing import Iterable, Optional
+from typing import Tuple, Iterable, Optional
 
 import torch
 
 from .. import ops
 from ..ops.ref import quant as Q
-from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer
+from .base import QuantizedTensor, QuantizedTensorStorage, Quantizer, pin_payload
 
 
 class NVFP4TensorStorage(QuantizedTensorStorage):
@@ -153,12 +153,36 @@ class NVFP4Quantizer(Quantizer):
         self.stochastic_rounding = stochastic_rounding
         self.generator: Optional[torch.Generator] = None
 
-    def is_quantizable(self, tensor):
-        if tensor.dim() < 2:
+    def is_quantizable(self, inp):
+        if inp.dim() < 2:
             return False
-        C = tensor.shape[-1]
-        R = tensor.numel() // max(C, 1)
+        C = inp.shape[-1]
+        R = inp.numel() // max(C, 1)
         return C % 16 == 0 and R % 16 == 0
+
+    def is_requantization_safe(self) -> bool:
+        return not self.stochastic_rounding
+
+    def get_scale_shape(self, shape: Iterable[int], columnwise: bool):
+        """``(outer, inner)`` extent of the E4M3 block-scale buffer of a tensor of ``shape`` (one scale per 16
+        values, padded to whole 128 x 4 tiles; the buffer itself is flat and tile-swizzled).  The column-wise copy
+        is stored transposed."""
+        shape = tuple(shape)
+        C = shape[-1]
+        R = 1
+        for d in shape[:-1]:
+            R *= d
+        if columnwise:
+            R, C = C, R
+        return (Q.round_up(R, 128), Q.round_up(C // 16, 4))
+
+    @staticmethod
+    def convert_shape_for_fp4(shape: Iterable[int]) -> Tuple[int, ...]:
+        """Shape of the packed byte buffer of a tensor of ``shape``: two E2M1 values per byte along the last dim."""
+        shape = tuple(shape)
+        if shape[-1] % 2:
+            raise ValueError(f"the last dimension must be even to pack FP4 pairs, got {shape}")
+        return shape[:-1] + (shape[-1] // 2,)
 
     def _reduce(self, amax):
         if self.with_amax_reduction and self.amax_reduction_group is not None:
@@ -201,7 +225,8 @@ class NVFP4Quantizer(Quantizer):
             dst._amax_columnwise.copy_(ac)
         return dst
 
-    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False):
+    def make_empty(self, shape: Iterable[int], *, dtype=torch.float32, device=None, requires_grad=False,
+                   pin_memory: bool = False):
         shape = tuple(shape)
         C = shape[-1]
         R = 1
@@ -218,6 +243,7 @@ class NVFP4Quantizer(Quantizer):
             ac = torch.zeros(1, dtype=torch.float32, device=device)
         was, self.internal = self.internal, False
         try:
-            return self._wrap((rd, rs, ar, cd, cs, ac), shape, dtype, requires_grad)
+            out = self._wrap((rd, rs, ar, cd, cs, ac), shape, dtype, requires_grad)
         finally:
             self.internal = was
+        return pin_payload(out) if pin_memory else out

@@ -205,3 +205,61 @@ def test_quantizer_and_tensor_conveniences():
     assert not h.with_amax_reduction and h.amax_reduction_group is None
     h.with_amax_reduction = True
     assert h.rowwise_quantizer.with_amax_reduction
+
+
+@pytest.mark.parametrize("mode", ["MAE", "MSE"])
+def test_nvfp4_four_over_six_never_loses_to_standard_scaling(mode):
+    """Adaptive block scaling keeps, per 16-value block, the better of map-to-6 and map-to-4: against the standard
+    quantization with the same tensor scale no block gets a larger error, some get a smaller one, and the chosen
+    block scales are either the standard ones or 1.5 x larger."""
+    from transformerengine_b200.ops import quantize as OQ
+    from transformerengine_b200.ops.ref import quant as Q
+    torch.manual_seed(0)
+    x = (torch.randn(64, 128) * torch.rand(64, 1) * 3).to(torch.bfloat16).float()
+    rd6, rs6, ar6, *_ = OQ.quantize_nvfp4(x, columnwise=False, e4m3_max=256.0)
+    rd, rs, ar, *_ = OQ.quantize_nvfp4(x, columnwise=False, four_over_six=mode, e4m3_max=256.0)
+    assert torch.equal(ar, ar6) and torch.allclose(ar, x.abs().amax() * 448 / 256)
+    d6 = OQ.dequantize_nvfp4(rd6, rs6, ar6, 64, 128, torch.float32)
+    d = OQ.dequantize_nvfp4(rd, rs, ar, 64, 128, torch.float32)
+    metric = (lambda e: e.abs()) if mode == "MAE" else (lambda e: e.square())
+    e6 = metric(d6 - x).reshape(64, 8, 16).sum(-1)
+    e = metric(d - x).reshape(64, 8, 16).sum(-1)
+    assert (e <= e6 + 1e-6).all() and (e < e6 - 1e-6).float().mean() > 0.05
+    s6 = Q.unswizzle_scales(rs6, 64, 8).view(torch.float8_e4m3fn).float()
+    s = Q.unswizzle_scales(rs, 64, 8).view(torch.float8_e4m3fn).float()
+    changed = s != s6
+    assert changed.any() and ((s[changed] / s6[changed]) - 1.5).abs().max() < 0.2      # 1.5 x, both rounded to E4M3
+    assert (e[changed] < e6[changed]).all()          # map-to-4 is only taken where it wins (ties keep map-to-6)
+    with pytest.raises(NotImplementedError):
+        OQ.quantize_nvfp4(x, with_rht=True, four_over_six=mode)
+
+
+def test_nvfp4_four_over_six_recipe_and_quantizer_rebuild_on_recipe_change():
+    import transformerengine_b200 as te
+    from transformerengine_b200.common import recipe as R
+    torch.manual_seed(0)
+    lin = te.Linear(128, 128, bias=False, params_dtype=torch.float32, device="cpu")
+    x = torch.randn(64, 128) * torch.rand(64, 1) * 3
+    want = x @ lin.weight.t()
+
+    def err(rec):
+        with te.autocast(enabled=True, recipe=rec), torch.no_grad():
+            return float((lin(x) - want).abs().mean())
+
+    plain = err(R.NVFP4BlockScaling(disable_rht=True, disable_stochastic_rounding=True))
+    adaptive = err(R.NVFP4BlockScaling(disable_rht=True, disable_stochastic_rounding=True, nvfp4_4over6="all"))
+    q = lin.quantizers["scaling_fwd"]
+    assert q[0].nvfp4_use_4over6 and q[0].nvfp4_e4m3_max == 256 and q[1].nvfp4_use_4over6
+    assert adaptive < plain                       # the same module picked up the new recipe's quantizers
+    only_w = R.NVFP4BlockScaling(disable_rht=True, disable_stochastic_rounding=True, nvfp4_4over6="weights",
+                                 nvfp4_4over6_e4m3_use_256="none", nvfp4_4over6_err_mode="mse")
+    err(only_w)
+    q = lin.quantizers["scaling_fwd"]
+    assert not q[0].nvfp4_use_4over6 and q[1].nvfp4_use_4over6 and q[1].nvfp4_e4m3_max == 448
+    assert q[1].nvfp4_4over6_err_mode == "MSE"
+    with pytest.raises(ValueError):
+        err(R.NVFP4BlockScaling(nvfp4_4over6="all"))              # needs the transform switched off
+    with pytest.raises(NotImplementedError):
+        err(R.NVFP4BlockScaling(row_scaled_activation=True))
+    with pytest.raises(AssertionError):
+        R.NVFP4BlockScaling(nvfp4_4over6="some")

@@ -241,6 +241,9 @@ class NVFP4BlockScaling(Recipe):
         default_factory=lambda: _env_flag("NVTE_NVFP4_ROW_SCALED_ACTIVATION")
     )
     nvfp4_4over6: str = field(default_factory=lambda: os.getenv("NVTE_NVFP4_4OVER6", "none"))
+    nvfp4_4over6_e4m3_use_256: str = field(default_factory=lambda: os.getenv("NVTE_NVFP4_4OVER6_E4M3_USE_256", "all"))
+    nvfp4_4over6_err_mode: str = field(
+        default_factory=lambda: os.getenv("NVTE_NVFP4_4OVER6_ERR_MODE", "MAE").upper())
     fp4_format: Format = Format.E2M1
     fp8_format: Format = Format.E4M3
     fp8_dpa: bool = False
@@ -255,6 +258,11 @@ class NVFP4BlockScaling(Recipe):
     def __post_init__(self) -> None:
         assert self.fp4_format == Format.E2M1
         assert self.fp8_format == Format.E4M3
+        scopes = ("none", "weights", "activations", "all")
+        assert self.nvfp4_4over6 in scopes, f"nvfp4_4over6 must be one of {scopes}"
+        assert self.nvfp4_4over6_e4m3_use_256 in scopes, f"nvfp4_4over6_e4m3_use_256 must be one of {scopes}"
+        self.nvfp4_4over6_err_mode = str(self.nvfp4_4over6_err_mode).upper()
+        assert self.nvfp4_4over6_err_mode in ("MAE", "MSE"), "nvfp4_4over6_err_mode must be 'MAE' or 'MSE'"
         rht = not self.disable_rht
         self.fp4_quant_fwd_inp = QParams(
             random_hadamard_transform=rht, stochastic_rounding=False, fp4_2d_quantization=False

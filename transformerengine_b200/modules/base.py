@@ -147,6 +147,13 @@ class TransformerEngineBaseModule(torch.nn.Module):
             self.fp8_meta.get("num_gemms") == num_gemms
         if same and recipe.delayed():
             same = cur.amax_history_len == recipe.amax_history_len
+        elif same and cur is not recipe:
+            # stateless recipes: the quantizers are a function of the recipe's fields, so another object of the same
+            # class with other settings (formats, Hadamard transform, block shapes, ...) needs new quantizers
+            try:
+                same = bool(cur == recipe)
+            except Exception:  # noqa: BLE001  (user recipe classes without a usable __eq__)
+                same = False
         self.fp8_meta["recipe"] = recipe
         self.fp8_meta["num_gemms"] = num_gemms
         if same:

@@ -169,30 +169,42 @@ def unswizzle_scales(swz: torch.Tensor, rows: int, cols: int) -> torch.Tensor:
 
 # ----------------------------------------------------------------------------- NVFP4
 def quantize_nvfp4(x2d, *, rowwise=True, columnwise=True, with_rht=False, with_2d=False, stochastic_rounding=False,
-                   amax_reduce: Optional[Callable] = None, generator=None):
-    """Returns (row_data [R,C/2], row_scale swz, amax_row, col_data_t [C,R/2], col_scale swz, amax_col)."""
+                   amax_reduce: Optional[Callable] = None, generator=None, four_over_six: Optional[str] = None,
+                   e4m3_max: float = 448.0):
+    """Returns (row_data [R,C/2], row_scale swz, amax_row, col_data_t [C,R/2], col_scale swz, amax_col).
+
+    ``four_over_six`` (``"MAE"`` / ``"MSE"``): adaptive block scaling, every block keeps the better of the
+    map-to-6 and map-to-4 quantizations (``ref/quant.py``); it runs as tensor operations on any device (no fused
+    kernel: meant for post-training / RL weights and activations, not for the pre-training hot path) and excludes
+    the Hadamard transform and stochastic rounding.  ``e4m3_max`` bounds the block scales (256 leaves room for the
+    1.5 x larger map-to-4 scale); it is folded into the returned amax (``amax * 448 / e4m3_max``), so the decode
+    side, which derives the tensor scale from that amax, needs no change."""
     R, C = x2d.shape
     reduce = amax_reduce or (lambda a: a)
-    if _ext.use_cuda(x2d) and hasattr(_ext.get(), "quantize_nvfp4"):
+    if four_over_six and (with_rht or stochastic_rounding):
+        raise NotImplementedError("4-over-6 NVFP4 scaling does not combine with the Hadamard transform or "
+                                  "stochastic rounding")
+    if _ext.use_cuda(x2d) and hasattr(_ext.get(), "quantize_nvfp4") and not four_over_six and e4m3_max == 448.0:
         return _quantize_nvfp4_cuda(x2d, rowwise, columnwise, with_rht, with_2d, stochastic_rounding, reduce)
     xr = x2d.to(torch.bfloat16).float() if x2d.dtype == torch.float32 else x2d.float()
+    widen = 448.0 / float(e4m3_max)
     rd = rs = ar = cd = cs = ac = None
     if rowwise:
-        ar = reduce(Q.amax_abs(xr))
+        ar = reduce(Q.amax_abs(xr)) * widen
         if with_2d:
-            d, s = Q.quantize_nvfp4_2d(xr, ar)
+            d, s = Q.quantize_nvfp4_2d(xr, ar, four_over_six)
         else:
-            d, s = Q.quantize_nvfp4_1d(xr, ar, stochastic_rounding, generator)
+            d, s = Q.quantize_nvfp4_1d(xr, ar, stochastic_rounding, generator, four_over_six)
         rd, rs = d, Q.swizzle_scales(s)
     if columnwise:
         xt = xr.t().contiguous()
         if with_rht:
             xt = Q.apply_rht(xt)
-        ac = reduce(Q.amax_abs(xt))
+        ac = reduce(Q.amax_abs(xt)) * widen
         if with_2d:
-            d, s = Q.quantize_nvfp4_2d(xt, ac)
+            d, s = Q.quantize_nvfp4_2d(xt, ac, four_over_six)
         else:
-            d, s = Q.quantize_nvfp4_1d(xt, ac, stochastic_rounding, generator)
+            d, s = Q.quantize_nvfp4_1d(xt, ac, stochastic_rounding, generator, four_over_six)
         cd, cs = d, Q.swizzle_scales(s)
     return rd, rs, ar, cd, cs, ac
 

@@ -269,6 +269,7 @@ def quantize_nvfp4_1d(
     global_amax: torch.Tensor,
     stochastic: bool = False,
     generator: Optional[torch.Generator] = None,
+    four_over_six: Optional[str] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """1x16 block NVFP4 quantization along the last dim.
 
@@ -279,10 +280,14 @@ def quantize_nvfp4_1d(
     assert C % NVFP4_BLOCK == 0
     xb = x2d.float().reshape(R, C // NVFP4_BLOCK, NVFP4_BLOCK)
     vec_max = xb.abs().amax(dim=-1, keepdim=True)
+    if four_over_six:
+        assert not stochastic, "4-over-6 selection compares deterministic candidates"
+        return _nvfp4_encode_4over6(xb, vec_max, global_amax, R, C, four_over_six, rows_per_tile=1)
     return _nvfp4_encode(xb, vec_max, global_amax, stochastic, generator, R, C)
 
 
-def quantize_nvfp4_2d(x2d: torch.Tensor, global_amax: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+def quantize_nvfp4_2d(x2d: torch.Tensor, global_amax: torch.Tensor,
+                      four_over_six: Optional[str] = None) -> Tuple[torch.Tensor, torch.Tensor]:
     """16x16 block NVFP4 quantization (weights): one scale shared by 16 rows."""
     R, C = x2d.shape
     assert C % NVFP4_BLOCK == 0 and R % NVFP4_BLOCK == 0
@@ -290,7 +295,39 @@ def quantize_nvfp4_2d(x2d: torch.Tensor, global_amax: torch.Tensor) -> Tuple[tor
     bmax = blocks.abs().amax(dim=(1, 3))  # [R/16, C/16]
     vec_max = bmax.repeat_interleave(16, dim=0).unsqueeze(-1)  # [R, C/16, 1]
     xb = x2d.float().reshape(R, C // 16, 16)
+    if four_over_six:
+        return _nvfp4_encode_4over6(xb, vec_max, global_amax, R, C, four_over_six, rows_per_tile=16)
     return _nvfp4_encode(xb, vec_max, global_amax, False, None, R, C)
+
+
+def _nvfp4_encode_4over6(xb, vec_max, global_amax, R, C, err_mode: str, rows_per_tile: int):
+    """Adaptive block scaling ("4 over 6"): every block is quantized twice, with its amax mapped to 6 (the largest
+    E2M1 value, the standard choice) and mapped to 4 (a block scale 1.5 times larger, which puts the values on a
+    grid with a finer top end), and keeps whichever reconstructs the block with the smaller error (``"MAE"``: sum
+    of absolute errors, ``"MSE"``: of squared errors, measured on the original values; ties keep 6).  A 16 x 16
+    tile (``rows_per_tile == 16``) chooses once for the whole tile.  The caller passes a ``global_amax`` scaled so
+    that 1.5 x the block scale still fits E4M3 (global bound 256 instead of 448).
+    (Reference: ``pytorch/custom_recipes/reference_nvfp4.py``, the 4over6 path; restated here.)"""
+    assert err_mode in ("MAE", "MSE")
+    s_enc = nvfp4_global_encode_scale(global_amax.float().reshape(-1)[:1])
+    s_dec_global = torch.ones_like(s_enc) / s_enc
+    base = torch.clamp(vec_max * (s_enc * torch.full_like(s_enc, 1.0 / 6.0)), max=FP32_MAX)
+    cands = []
+    for factor in (1.0, 1.5):                                   # map to 6, map to 4
+        dec = torch.clamp(base * factor, -448.0, 448.0).to(FP8_E4M3)
+        enc = torch.clamp(torch.ones_like(s_enc) / (dec.float() * s_dec_global), max=FP32_MAX)
+        codes = cast_to_e2m1_codes(torch.clamp(xb * enc, -6.0, 6.0).reshape(R, C))
+        recon = e2m1_codes_to_float(codes).reshape(xb.shape) * (dec.float() * s_dec_global)
+        diff = (xb - recon).abs() if err_mode == "MAE" else (xb - recon).square()
+        err = diff.sum(dim=-1)                                   # [R, C/16]
+        if rows_per_tile > 1:
+            err = err.reshape(R // rows_per_tile, rows_per_tile, -1).sum(dim=1).repeat_interleave(rows_per_tile, dim=0)
+        cands.append((codes, dec.squeeze(-1), err))
+    (c6, d6, e6), (c4, d4, e4) = cands
+    use4 = e4 < e6                                               # [R, C/16]
+    codes = torch.where(use4.repeat_interleave(NVFP4_BLOCK, dim=1), c4, c6)
+    dec = torch.where(use4, d4.float(), d6.float()).to(FP8_E4M3)
+    return pack_fp4(codes), dec.view(torch.uint8)
 
 
 def _nvfp4_encode(xb, vec_max, global_amax, stochastic, generator, R, C):

@@ -231,9 +231,22 @@ class NVFP4BlockScalingRecipeState(RecipeState):
                 qp = r.fp4_quant_fwd_weight if i % 3 == 1 else r.fp4_quant_fwd_inp
             else:
                 qp = r.fp4_quant_bwd_grad
+            # adaptive (4-over-6) block scaling of the forward tensors the recipe names; gradients keep the
+            # standard scaling (reference: quantization.py, NVFP4BlockScalingRecipeState.make_quantizers)
+            is_weight = self.mode == "forward" and i % 3 == 1
+            scope = "weights" if is_weight else "activations"
+            adaptive = self.mode == "forward" and r.nvfp4_4over6 in ("all", scope)
+            if adaptive and (qp.random_hadamard_transform or qp.stochastic_rounding):
+                raise ValueError("NVFP4 4over6 quantization does not support the random Hadamard transform or "
+                                 "stochastic rounding: set disable_rht=True (and disable_stochastic_rounding=True)")
+            bound = 256 if adaptive and r.nvfp4_4over6_e4m3_use_256 in ("all", scope) else 448
             out.append(NVFP4Quantizer(with_rht=qp.random_hadamard_transform,
                                       with_2d_quantization=qp.fp4_2d_quantization,
-                                      stochastic_rounding=qp.stochastic_rounding))
+                                      stochastic_rounding=qp.stochastic_rounding,
+                                      row_scaled_nvfp4=(self.mode == "forward" and not is_weight
+                                                        and r.row_scaled_activation),
+                                      nvfp4_use_4over6=adaptive, nvfp4_e4m3_max=bound,
+                                      nvfp4_4over6_err_mode=r.nvfp4_4over6_err_mode))
         return out
 
 

@@ -139,8 +139,26 @@ class NVFP4Quantizer(Quantizer):
 
     def __init__(self, fp4_dtype=None, *, rowwise=True, columnwise=True, with_amax_reduction=False,
                  amax_reduction_group=None, with_rht=False, with_post_rht_amax=True,
-                 with_2d_quantization=False, stochastic_rounding=False, with_random_sign_mask=True):
+                 with_2d_quantization=False, stochastic_rounding=False, with_random_sign_mask=True,
+                 row_scaled_nvfp4: bool = False, nvfp4_use_4over6: bool = False, nvfp4_e4m3_max: int = 448,
+                 nvfp4_4over6_err_mode: str = "MAE"):
         super().__init__(rowwise=rowwise, columnwise=columnwise)
+        if row_scaled_nvfp4:
+            raise NotImplementedError("row_scaled_nvfp4 (one tensor scale per row) is not implemented: the GEMM "
+                                      "epilogues apply one scale per operand")
+        nvfp4_4over6_err_mode = str(nvfp4_4over6_err_mode).upper()
+        if nvfp4_use_4over6:
+            if nvfp4_4over6_err_mode not in ("MAE", "MSE"):
+                raise ValueError(f"nvfp4_4over6_err_mode must be 'MAE' or 'MSE', got {nvfp4_4over6_err_mode!r}")
+            if with_rht or stochastic_rounding:
+                raise NotImplementedError("4-over-6 NVFP4 scaling does not combine with the Hadamard transform or "
+                                          "stochastic rounding")
+            if nvfp4_e4m3_max not in (256, 448):
+                raise ValueError("nvfp4_e4m3_max must be 256 or 448")
+        self.row_scaled_nvfp4 = False
+        self.nvfp4_use_4over6 = bool(nvfp4_use_4over6)
+        self.nvfp4_e4m3_max = int(nvfp4_e4m3_max) if nvfp4_use_4over6 else 448
+        self.nvfp4_4over6_err_mode = nvfp4_4over6_err_mode
         if with_rht and not with_random_sign_mask:
             raise NotImplementedError("the Hadamard transform always uses the fixed random sign vector "
                                       "(with_random_sign_mask=False is not implemented)")
@@ -201,7 +219,9 @@ class NVFP4Quantizer(Quantizer):
     def _quantize_parts(self, x2d, rowwise, columnwise):
         return ops.quantize_nvfp4(x2d, rowwise=rowwise, columnwise=columnwise, with_rht=self.with_rht,
                                   with_2d=self.with_2d_quantization, stochastic_rounding=self.stochastic_rounding,
-                                  amax_reduce=self._reduce, generator=self.generator)
+                                  amax_reduce=self._reduce, generator=self.generator,
+                                  four_over_six=self.nvfp4_4over6_err_mode if self.nvfp4_use_4over6 else None,
+                                  e4m3_max=float(self.nvfp4_e4m3_max))
 
     def quantize_impl(self, tensor, dtype=None):
         shape = tuple(tensor.shape)

@@ -188,3 +188,14 @@ def test_bottom_right_diagonal_and_packed_inputs():
         dpa(qkv_layer=qkv, qkv_interleave_dim=-1)
     with pytest.raises(NotImplementedError):
         dpa(q, k, v, fp8_output=True)
+
+
+def test_fp8_attention_flags_are_refused_not_ignored():
+    from transformerengine_b200.common import recipe as R
+    dpa = te.DotProductAttention(2, 8, attention_dropout=0.0, qkv_format="bshd")
+    q = torch.randn(1, 4, 2, 8)
+    with te.autocast(enabled=True, recipe=R.DelayedScaling(fp8_dpa=True)):
+        with pytest.raises(NotImplementedError, match="fp8_dpa"):
+            dpa(q, q, q)
+    with te.autocast(enabled=True, recipe=R.DelayedScaling()):
+        assert dpa(q, q, q).shape == (1, 4, 16)

@@ -518,3 +518,74 @@ def test_fused_adam_scaled_states(dtypes):
     o3.initialize_state(q)
     assert torch.equal(o3.get_unscaled_state(q, "master_param"), q.detach().float())
     assert float(o3.get_unscaled_state(q, "exp_avg").abs().max()) == 0.0
+
+
+def _mx(t):
+    from transformerengine_b200.tensor.mxfp8 import MXFP8Quantizer
+    return MXFP8Quantizer()(t.detach()).dequantize()
+
+
+@pytest.mark.parametrize("override", ["high_precision", "dequantized"])
+def test_backward_override_runs_the_backward_gemms_unquantized(override):
+    """``recipe.backward_override``: the forward pass is the quantized one, the backward GEMMs take the original
+    operands (``high_precision``) or the dequantized forward operands (``dequantized``), unquantized."""
+    torch.manual_seed(0)
+    pick = (lambda t: t.detach()) if override == "high_precision" else _mx
+    rec, plain = R.MXFP8BlockScaling(backward_override=override), R.MXFP8BlockScaling()
+    x = torch.randn(32, 64)
+
+    def run(m, recipe):
+        xi = x.clone().requires_grad_()
+        m.zero_grad()
+        with te.autocast(enabled=True, recipe=recipe):
+            y = m(xi)
+        y.square().sum().backward()
+        return y.detach(), xi.grad
+
+    lin = te.Linear(64, 96, bias=True, params_dtype=torch.float32, device="cpu")
+    y0, _ = run(lin, plain)
+    y, gx = run(lin, rec)
+    dy = 2 * y
+    assert torch.equal(y, y0)
+    torch.testing.assert_close(gx, dy @ pick(lin.weight))
+    torch.testing.assert_close(lin.weight.grad, dy.t() @ pick(x))
+    torch.testing.assert_close(lin.bias.grad, dy.sum(0))
+
+    lnl = te.LayerNormLinear(64, 96, normalization="RMSNorm", bias=False, params_dtype=torch.float32, device="cpu")
+    y0, _ = run(lnl, plain)
+    y, gx = run(lnl, rec)
+    assert torch.equal(y, y0)
+    ln = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + lnl.eps) * lnl.layer_norm_weight.detach()
+    torch.testing.assert_close(lnl.weight.grad, (2 * y).t() @ pick(ln), rtol=1e-4, atol=1e-5)
+
+    # LayerNormMLP against autograd through a straight-through emulation: forward values of the quantized run,
+    # gradients of the unquantized products
+    mlp = te.LayerNormMLP(64, 128, normalization="RMSNorm", activation="gelu", bias=True, params_dtype=torch.float32,
+                          device="cpu")
+    y0, _ = run(mlp, plain)
+    y, gx = run(mlp, rec)
+    assert torch.equal(y, y0)
+    w1, b1, w2, b2, g = (p.detach().clone().requires_grad_() for p in (mlp.fc1_weight, mlp.fc1_bias, mlp.fc2_weight,
+                                                                        mlp.fc2_bias, mlp.layer_norm_weight))
+    xi = x.clone().requires_grad_()
+    ln = xi * torch.rsqrt(xi.pow(2).mean(-1, keepdim=True) + mlp.eps) * g
+    sel = (lambda t: t) if override == "high_precision" else (lambda t: t + (_mx(t) - t).detach())
+
+    def ste_linear(a, w, b):
+        hp = sel(a) @ sel(w).t() + b
+        return hp + ((_mx(a) @ _mx(w).t() + b) - hp).detach()
+
+    fc1 = ste_linear(ln, w1, b1)
+    act = fc1 * (0.5 + 0.5 * torch.tanh(fc1 * (0.79788456 + 0.03567741 * fc1 * fc1)))
+    out = ste_linear(act, w2, b2)
+    torch.testing.assert_close(out.detach(), y, rtol=1e-4, atol=1e-5)
+    out.square().sum().backward()
+    torch.testing.assert_close(gx, xi.grad, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(mlp.fc1_weight.grad, w1.grad, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(mlp.fc2_weight.grad, w2.grad, rtol=1e-3, atol=1e-4)
+    torch.testing.assert_close(mlp.fc1_bias.grad, b1.grad, rtol=1e-3, atol=1e-4)
+
+    gl = te.GroupedLinear(2, 64, 64, bias=False, params_dtype=torch.float32, device="cpu")
+    with pytest.raises(NotImplementedError, match="backward_override"):
+        with te.autocast(enabled=True, recipe=rec):
+            gl(x, [16, 16])

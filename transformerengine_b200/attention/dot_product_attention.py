@@ -110,6 +110,12 @@ class DotProductAttention(torch.nn.Module):
         pass always runs in 16 bits; the kernels choose their own split of the key sequence)."""
         if fp8_output:
             raise NotImplementedError("fp8_output: the attention kernels write 16-bit outputs")
+        from ..quantization import FP8GlobalStateManager
+        if FP8GlobalStateManager.is_fp8_enabled():
+            rec = FP8GlobalStateManager.get_fp8_recipe()
+            if getattr(rec, "fp8_dpa", False) or getattr(rec, "fp8_mha", False):
+                raise NotImplementedError("recipe.fp8_dpa / fp8_mha: FP8 attention is not built; the attention "
+                                          "kernels take fp16 / bf16 (leave both flags False)")
         if qkv_layer is not None or kv_layer is not None:
             query_layer, key_layer, value_layer = _unpack_qkv(query_layer, key_layer, value_layer, qkv_layer,
                                                               kv_layer, qkv_interleave_dim, inference_params)

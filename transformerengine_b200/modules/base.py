@@ -173,6 +173,17 @@ class TransformerEngineBaseModule(torch.nn.Module):
         if pending is not None:
             self._apply_loaded_state(pending)
 
+    def backward_override(self) -> Optional[str]:
+        """``recipe.backward_override`` of the active recipe (None, ``"high_precision"`` or ``"dequantized"``).
+        Modules that implement it run their backward GEMMs unquantized; the others refuse it."""
+        recipe = self.fp8_meta.get("recipe")
+        return getattr(recipe, "backward_override", None) if recipe is not None else None
+
+    def _refuse_backward_override(self) -> None:
+        if self.fp8 and self.backward_override() is not None:
+            raise NotImplementedError(f"recipe.backward_override={self.backward_override()!r} is implemented by "
+                                      f"Linear, LayerNormLinear and LayerNormMLP, not by {type(self).__name__}")
+
     def _quantize_primary_weights(self, weight_names) -> None:
         """``quantized_model_init``: replace the named high-precision weights by quantized parameters (both copies,
         so that forward, dgrad and wgrad read the parameter's own payload).  The quantizers come from a recipe state

@@ -301,6 +301,7 @@ class GroupedLinear(TransformerEngineBaseModule):
             return (out,) + tuple(rest) if rest else out
         assert len(m_splits) == self.num_gemms, "one row count per GEMM"
         self.prepare_forward(num_gemms=self.num_gemms)
+        self._refuse_backward_override()
         adt = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else inp.dtype
         ws = [getattr(self, f"weight{i}") for i in range(self.num_gemms)]
         bs = [getattr(self, f"bias{i}") for i in range(self.num_gemms)] if self.use_bias else []

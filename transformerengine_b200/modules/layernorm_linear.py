@@ -98,17 +98,23 @@ class _LayerNormLinear(torch.autograd.Function):
         grad_on = any(ctx.needs_input_grad)
         need_wgrad = weight.requires_grad and grad_on
         sp_gather = cfg.parallel_mode == "column" and cfg.sequence_parallel and cfg.tp_size > 1
+        # recipe.backward_override: quantized forward, unquantized backward GEMMs on the original ("high_precision")
+        # or on the dequantized forward operands ("dequantized")
+        override = module.backward_override() if (fp8 and grad_on) else None
+        if override is not None and cfg.tp_size > 1:
+            raise NotImplementedError("recipe.backward_override is implemented for modules without tensor parallelism")
         # sequence parallel with fused collectives and MXFP8: the norm writes this rank's rows quantized
         # (both copies in one pass), the all-gather moves FP8 and the columnwise copy is kept for wgrad
         sp_fused_q = sp_gather and isinstance(in_q, F.MXFP8Quantizer) and F._fused_comm_ok(cfg, x2d.shape[0], x2d) \
             and x2d.shape[0] % 128 == 0
         if in_q is not None:
-            in_q.set_usage(rowwise=True, columnwise=need_wgrad and (not sp_gather or sp_fused_q))
+            in_q.set_usage(rowwise=True, columnwise=need_wgrad and (not sp_gather or sp_fused_q) and override is None)
             in_q.internal = True
         ln_hp, ln_q, mu, rs = ops.norm_fwd(x2d, ln_w, ln_b, module.eps, module.zero_centered_gamma,
                                            module.normalization == "LayerNorm",
                                            quantizer=in_q if (not sp_gather or sp_fused_q) else None,
-                                           want_hp=return_ln_out or in_q is None or (sp_gather and not sp_fused_q))
+                                           want_hp=return_ln_out or in_q is None or (sp_gather and not sp_fused_q)
+                                           or override == "high_precision")
         out = None
         ln_total = None
         ln_local = ln_q if (sp_fused_q and ln_q is not None) else ln_hp
@@ -126,13 +132,16 @@ class _LayerNormLinear(torch.autograd.Function):
             out, _ = F.linear_fprop(ln_total, wq, bias, cfg, cfg.activation_dtype)
         if grad_on:
             keep = (ln_local if sp_gather else ln_total) if need_wgrad else None
+            if override == "high_precision" and need_wgrad:
+                keep = ln_hp
             if F._is_q(keep) and keep.get_usages()["columnwise"]:
                 keep.update_usage(rowwise_usage=False)
             ctx.wq = wq if F._is_q(wq) else None  # cached object shared across calls: not stripped
             flat, objs = prepare_for_saving(keep)
             ctx.save_for_backward(*flat, x2d, ln_w, ln_b, mu, rs, weight, bias)
             ctx.objs = objs
-            ctx.module, ctx.cfg, ctx.fp8 = module, cfg, fp8
+            ctx.module, ctx.cfg, ctx.fp8 = module, cfg, fp8 and override is None
+            ctx.override = override
             ctx.inp_shape = inp.shape
             ctx.sp_gather = sp_gather
             ctx.requires_wgrad = need_wgrad
@@ -155,6 +164,11 @@ class _LayerNormLinear(torch.autograd.Function):
         wq = ctx.wq
         module, cfg = ctx.module, ctx.cfg
         w_use = wq if wq is not None else weight
+        if ctx.override is not None:
+            adt = cfg.activation_dtype
+            hp = lambda t: t.dequantize(dtype=adt) if F._is_q(t) else (t if t.dtype == adt else t.to(adt))  # noqa: E731
+            w_use = hp(weight) if ctx.override == "high_precision" else hp(w_use)
+            keep = hp(keep) if keep is not None else None
         dy2d = grad_output.reshape(-1, grad_output.shape[-1]).to(cfg.activation_dtype).contiguous()
         go_q = module.get_quantizer(False, 0) if ctx.fp8 else None
         db = F.bias_grad(dy2d, bias.dtype) if bias is not None else None

@@ -36,15 +36,21 @@ class _LayerNormMLP(torch.autograd.Function):
         grad = any(ctx.needs_input_grad)
         q_in1, q_in2 = module.get_quantizer(True, 0), module.get_quantizer(True, 3)
         sp = cfg1.sequence_parallel and cfg1.tp_size > 1
+        # recipe.backward_override: quantized forward, unquantized backward GEMMs on the original ("high_precision")
+        # or on the dequantized forward operands ("dequantized")
+        override = module.backward_override() if (fp8 and grad) else None
+        if override is not None and cfg1.tp_size > 1:
+            raise NotImplementedError("recipe.backward_override is implemented for modules without tensor parallelism")
+        hp_bwd = override == "high_precision"
         sp_fused_q = sp and isinstance(q_in1, F.MXFP8Quantizer) and F._fused_comm_ok(cfg1, x2d.shape[0], x2d) \
             and x2d.shape[0] % 128 == 0
         if q_in1 is not None:
-            q_in1.set_usage(rowwise=True, columnwise=grad and (not sp or sp_fused_q))
+            q_in1.set_usage(rowwise=True, columnwise=grad and (not sp or sp_fused_q) and override is None)
             q_in1.internal = True
         is_ln = module.normalization == "LayerNorm"
         ln_hp, ln_q, mu, rs = ops.norm_fwd(x2d, ln_w, ln_b, module.eps, module.zero_centered_gamma, is_ln,
                                            quantizer=q_in1 if (not sp or sp_fused_q) else None,
-                                           want_hp=return_ln_out or q_in1 is None or (sp and not sp_fused_q))
+                                           want_hp=return_ln_out or q_in1 is None or (sp and not sp_fused_q) or hp_bwd)
         act = module.activation
         fc1_out = None
         ln_total = None
@@ -62,13 +68,15 @@ class _LayerNormMLP(torch.autograd.Function):
         if fc1_out is None:
             fc1_out, _ = F.linear_fprop(ln_total, w1q, fc1_b, cfg1, adt)
         if q_in2 is not None:
-            q_in2.set_usage(rowwise=True, columnwise=grad)
+            q_in2.set_usage(rowwise=True, columnwise=grad and override is None)
             q_in2.internal = True
-        act_hp, act_q = ops.activation_fwd(fc1_out, act, quantizer=q_in2, want_hp=q_in2 is None)
+        act_hp, act_q = ops.activation_fwd(fc1_out, act, quantizer=q_in2, want_hp=q_in2 is None or hp_bwd)
         act_in = act_q if act_q is not None else act_hp
         out, _ = F.linear_fprop(act_in, w2q, fc2_b, cfg2, adt)
         if grad:
             keep_ln = ln_local if sp else ln_total
+            if hp_bwd:
+                keep_ln, act_in = ln_hp, act_hp
             if F._is_q(keep_ln) and keep_ln.get_usages()["columnwise"]:
                 keep_ln.update_usage(rowwise_usage=False)
             if F._is_q(act_in) and act_in.get_usages()["columnwise"]:
@@ -78,7 +86,8 @@ class _LayerNormMLP(torch.autograd.Function):
             flat, objs = prepare_for_saving(keep_ln, act_in)
             ctx.save_for_backward(*flat, x2d, ln_w, ln_b, mu, rs, fc1_out, fc1_w, fc1_b, fc2_w, fc2_b)
             ctx.objs = objs
-            ctx.module, ctx.fp8 = module, fp8
+            ctx.module, ctx.fp8 = module, fp8 and override is None
+            ctx.override = override
             ctx.inp_shape = inp.shape
             ctx.sp = sp
             ctx.return_ln_out = return_ln_out
@@ -101,6 +110,10 @@ class _LayerNormMLP(torch.autograd.Function):
         adt = cfg1.activation_dtype
         w1 = w1q if w1q is not None else fc1_w
         w2 = w2q if w2q is not None else fc2_w
+        if ctx.override is not None:
+            hp = lambda t: t.dequantize(dtype=adt) if F._is_q(t) else (t if t.dtype == adt else t.to(adt))  # noqa: E731
+            w1, w2 = (hp(fc1_w), hp(fc2_w)) if ctx.override == "high_precision" else (hp(w1), hp(w2))
+            keep_ln, act_in = hp(keep_ln), hp(act_in)
         dy2d = grad_output.reshape(-1, grad_output.shape[-1]).to(adt).contiguous()
         q_go2 = module.get_quantizer(False, 2) if ctx.fp8 else None
         q_go1 = module.get_quantizer(False, 0) if ctx.fp8 else None

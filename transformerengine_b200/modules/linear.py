@@ -26,6 +26,12 @@ class _Linear(torch.autograd.Function):
         in_q = module.get_quantizer(True, 0)
         grad_on = any(ctx.needs_input_grad)
         need_wgrad = weight.requires_grad and grad_on
+        # recipe.backward_override: quantized forward, unquantized backward GEMMs on the original operands
+        # ("high_precision") or on the dequantized forward operands ("dequantized")
+        override = module.backward_override() if (fp8 and grad_on) else None
+        if override is not None and (cfg.tp_size > 1 or dist_w):
+            raise NotImplementedError("recipe.backward_override is implemented for modules without tensor "
+                                      "parallelism and without distributed weights")
         if x2d.dtype != cfg.activation_dtype and not F._is_q(x2d):
             x2d = x2d.to(cfg.activation_dtype)
         out = None
@@ -40,14 +46,15 @@ class _Linear(torch.autograd.Function):
             if out is None:
                 xq = F.gather_input(x2d, cfg, in_q, True, need_wgrad)
         else:
-            keep_original = getattr(module, "save_original_input", False) and need_wgrad
-            xq = F.quantize_for_gemm(x2d, in_q, True, need_wgrad and not keep_original)
+            keep_original = (getattr(module, "save_original_input", False) or override == "high_precision") \
+                and need_wgrad
+            xq = F.quantize_for_gemm(x2d, in_q, True, need_wgrad and not keep_original and override is None)
             # save_original_input: keep the unquantized input and quantize its wgrad copy in the backward
             save_x = x2d if keep_original else xq
         if out is None:
             out, _ = F.linear_fprop(xq, weight_q, bias, cfg, cfg.activation_dtype)
         if grad_on:
-            if F._is_q(save_x) and need_wgrad:
+            if F._is_q(save_x) and need_wgrad and override is None:
                 save_x.update_usage(rowwise_usage=False) if save_x.get_usages()["columnwise"] else None
             keep_x = save_x if need_wgrad else None
             # the quantized weight is a cached object shared across calls: keep a reference, do not strip it
@@ -57,7 +64,8 @@ class _Linear(torch.autograd.Function):
             ctx.save_for_backward(*flat, weight, bias)
             ctx.objs = objs
             ctx.module, ctx.cfg = module, cfg
-            ctx.fp8 = fp8
+            ctx.fp8 = fp8 and override is None
+            ctx.override = override
             ctx.inp_shape = inp.shape
             ctx.use_bias = bias is not None
             ctx.requires_dgrad = inp.requires_grad
@@ -82,6 +90,11 @@ class _Linear(torch.autograd.Function):
         wq = ctx.wq
         module, cfg = ctx.module, ctx.cfg
         w_use = wq if wq is not None else weight
+        if ctx.override is not None:
+            adt = cfg.activation_dtype
+            hp = lambda t: t.dequantize(dtype=adt) if F._is_q(t) else (t if t.dtype == adt else t.to(adt))  # noqa: E731
+            w_use = hp(weight) if ctx.override == "high_precision" else hp(w_use)
+            keep_x = hp(keep_x) if keep_x is not None else None
         w_full = None
         if ctx.dist_w:  # assemble the full weight again instead of keeping it alive since the forward
             w_full = DW.materialize_weight_for_backward(weight)[0].detach()

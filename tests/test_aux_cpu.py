@@ -721,3 +721,47 @@ def test_parallel_cross_entropy_label_smoothing_single_rank_and_vocab_sharded():
     for rank, err, tb in res:
         assert tb is None, tb
         assert err < 1e-5, (rank, err)
+
+
+def test_distributed_module_helpers():
+    from transformerengine_b200 import distributed as D
+    from transformerengine_b200.common import recipe as R
+    tracker = D.CudaRNGStatesTracker()
+    tracker.add("model-parallel-rng", 4321)
+    assert "model-parallel-rng" in D.get_all_rng_states()
+    before = D.get_all_rng_states()["model-parallel-rng"].clone()
+    w = torch.empty(8, 8)
+    D.initialize_affine_weight_gpu(w, lambda t: torch.nn.init.normal_(t), lambda: tracker, partition_dim=1, stride=1)
+    assert w.tensor_model_parallel and w.partition_dim == 1
+    assert not torch.equal(D.get_all_rng_states()["model-parallel-rng"], before)        # the fork advanced the stream
+    saved = dict(D.get_all_rng_states())
+    D.set_all_rng_states({})
+    assert D.get_all_rng_states() == {}
+    D.set_all_rng_states(saved)
+    assert isinstance(D.graph_safe_rng_available(), bool) and not D.is_graph_safe_rng_state(torch.zeros(1))
+    assert D.has_te_modules(te.Linear(8, 8, device="cpu")) and not D.has_te_modules(torch.nn.Linear(8, 8))
+    assert D.has_te_modules(lambda x: x) and te.TransformerLayer in D.get_te_classes()
+    # a hand-written checkpoint of a delayed-scaling layer: the two contexts mark the two passes, and the recompute
+    # reproduces the first forward although the amax history moved in between
+    lin = te.Linear(32, 32, bias=False, params_dtype=torch.float32, device="cpu")
+    rec = R.DelayedScaling(amax_history_len=2)
+    x = torch.randn(16, 32)
+    with te.autocast(enabled=True, recipe=rec):
+        lin(x * 5)                                   # fills the history
+    fwd_ctx, re_ctx = D.get_activation_recompute_contexts()
+    with te.autocast(enabled=True, recipe=rec):
+        with fwd_ctx, torch.no_grad():
+            assert D.is_fp8_activation_recompute_enabled() and not D.in_fp8_activation_recompute_phase()
+            y1 = lin(x)
+    with te.autocast(enabled=True, recipe=rec):
+        lin(x * 0.01)                                # scales change
+    with te.autocast(enabled=True, recipe=rec):
+        with re_ctx:
+            assert D.in_fp8_activation_recompute_phase()
+            y2 = lin(x)
+    assert not D.in_fp8_activation_recompute_phase() and not D.is_fp8_activation_recompute_enabled()
+    assert torch.equal(y1, y2)
+    te.checkpoint(lambda t: t * 2, torch.ones(2, requires_grad=True), use_reentrant=False)
+    assert not D.use_reentrant_activation_recompute()
+    te.checkpoint(lambda t: t * 2, torch.ones(2, requires_grad=True))
+    assert D.use_reentrant_activation_recompute()

@@ -8,8 +8,10 @@ import torch.distributed as dist
 from .constants import dist_group_type  # noqa: F401
 from .parallel.distributed import (CudaRNGStatesTracker, allreduce, allreduce_sequence_parallel_grads,  # noqa: F401
                                    checkpoint, gather_along_first_dim, gather_quantized_along_first_dim,
-                                   in_checkpoint_forward, is_in_recompute, reduce_scatter_along_first_dim,
+                                   get_all_rng_states, in_checkpoint_forward, is_in_recompute,
+                                   reduce_scatter_along_first_dim, set_all_rng_states,
                                    set_tensor_model_parallel_attributes)
+from .parallel import distributed as _impl
 from .parallel.distributed import get_rank as get_distributed_rank  # noqa: F401
 from .parallel.distributed import get_world_size as get_distributed_world_size  # noqa: F401
 
@@ -59,3 +61,88 @@ def prepare_te_modules_for_fsdp(fsdp_root: torch.nn.Module) -> None:
         if isinstance(m, TransformerEngineBaseModule):
             m.fsdp_wrapped = True
             m.fsdp_group = getattr(fsdp_root, "process_group", None)
+
+
+def graph_safe_rng_available() -> bool:
+    """Whether this PyTorch can register generator states with a CUDA graph (so that captured random draws advance
+    between replays)."""
+    return (hasattr(torch.cuda.CUDAGraph, "register_generator_state") and hasattr(torch.Generator, "graphsafe_set_state")
+            and hasattr(torch.Generator, "graphsafe_get_state") and hasattr(torch.Generator, "clone_state"))
+
+
+def is_graph_safe_rng_state(state) -> bool:
+    return graph_safe_rng_available() and isinstance(state, torch.Generator)
+
+
+def initialize_affine_weight_gpu(weight: torch.Tensor, init_method, get_rng_state_tracker, partition_dim: int = 0,
+                                 stride: int = 1, set_tp_attributes: bool = True) -> None:
+    """Initialise a tensor-parallel weight shard under the tracker's model-parallel random stream (every rank
+    draws its own values) and tag it with its partitioning."""
+    if set_tp_attributes:
+        set_tensor_model_parallel_attributes(weight, True, partition_dim, stride)
+    if get_rng_state_tracker is None:
+        init_method(weight)
+        return
+    with get_rng_state_tracker().fork():
+        init_method(weight)
+
+
+class activation_recompute_forward:  # noqa: N801  (a context manager with the reference's spelling)
+    """Marks the two passes of a checkpointed region for code that drives recomputation itself instead of calling
+    ``checkpoint``: ``activation_recompute=True, recompute_phase=False`` around the first (activation-discarding)
+    forward, ``recompute_phase=True`` around the second one in the backward pass.  Modules with delayed-scaling
+    state stash their forward scales in the first and reuse them in the second."""
+
+    def __init__(self, activation_recompute: bool = False, recompute_phase: bool = False):
+        self.activation_recompute, self.recompute_phase = activation_recompute, recompute_phase
+
+    def __enter__(self):
+        self._was = (_impl._IN_CHECKPOINT_FORWARD[0], _impl._IN_RECOMPUTE[0])
+        if self.activation_recompute and not self.recompute_phase:
+            _impl._IN_CHECKPOINT_FORWARD[0] += 1
+        if self.activation_recompute and self.recompute_phase:
+            _impl._IN_RECOMPUTE[0] = True
+        return self
+
+    def __exit__(self, *exc):
+        _impl._IN_CHECKPOINT_FORWARD[0], _impl._IN_RECOMPUTE[0] = self._was
+        if self.activation_recompute and self.recompute_phase:
+            _impl._run_recompute_restores()
+        return False
+
+    def __call__(self, fn):
+        import functools
+
+        @functools.wraps(fn)
+        def wrapped(*a, **k):
+            with activation_recompute_forward(self.activation_recompute, self.recompute_phase):
+                return fn(*a, **k)
+        return wrapped
+
+
+def get_activation_recompute_contexts():
+    """``(forward context, recompute context)`` for a hand-written checkpoint."""
+    return activation_recompute_forward(True, False), activation_recompute_forward(True, True)
+
+
+def use_reentrant_activation_recompute() -> bool:
+    """Whether the checkpoint in flight uses the re-entrant autograd function (the default of ``checkpoint``)."""
+    return getattr(_impl, "_USE_REENTRANT", [True])[0]
+
+
+def get_te_classes():
+    """Module classes of this library (what ``has_te_modules`` looks for)."""
+    from .attention.dot_product_attention import DotProductAttention
+    from .attention.multi_head_attention import MultiheadAttention
+    from .modules.base import TransformerEngineBaseModule
+    from .modules.layernorm_linear import LayerNorm, RMSNorm
+    from .transformer import TransformerLayer
+    return (LayerNorm, RMSNorm, TransformerEngineBaseModule, DotProductAttention, MultiheadAttention, TransformerLayer)
+
+
+def has_te_modules(network) -> bool:
+    """Whether ``network`` contains modules of this library (anything that is not an ``nn.Module`` counts as yes:
+    a bare callable cannot be inspected)."""
+    if isinstance(network, torch.nn.Module):
+        return any(isinstance(m, get_te_classes()) for m in network.modules())
+    return True

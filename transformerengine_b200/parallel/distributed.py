@@ -214,6 +214,20 @@ def gather_quantized_along_first_dim(q, group):
 
 
 # --------------------------------------------------------------------------- RNG tracker
+# every state that any CudaRNGStatesTracker has registered, by name: CUDA-graph capture code walks this registry to
+# register the generators it must keep in step (reference: pytorch/distributed.py, _ALL_ACTIVE_RNG_STATES)
+_ALL_ACTIVE_RNG_STATES: Dict[str, torch.Tensor] = {}
+
+
+def get_all_rng_states() -> Dict[str, torch.Tensor]:
+    return _ALL_ACTIVE_RNG_STATES
+
+
+def set_all_rng_states(states: Dict[str, torch.Tensor]) -> None:
+    global _ALL_ACTIVE_RNG_STATES
+    _ALL_ACTIVE_RNG_STATES = states
+
+
 class CudaRNGStatesTracker:
     """Named RNG states so that tensor-parallel ranks can draw the same or different
     random numbers on demand (dropout inside vs outside TP regions)."""
@@ -230,6 +244,7 @@ class CudaRNGStatesTracker:
 
     def set_states(self, states: Dict[str, torch.Tensor]) -> None:
         self.states_ = states
+        _ALL_ACTIVE_RNG_STATES.update(states)
 
     @staticmethod
     def _get_state():
@@ -254,6 +269,7 @@ class CudaRNGStatesTracker:
         else:
             torch.manual_seed(seed)
         self.states_[name] = self._get_state()
+        _ALL_ACTIVE_RNG_STATES[name] = self.states_[name]
         self._set_state(orig)
 
     @contextlib.contextmanager
@@ -266,12 +282,14 @@ class CudaRNGStatesTracker:
             yield
         finally:
             self.states_[name] = self._get_state()
+            _ALL_ACTIVE_RNG_STATES[name] = self.states_[name]
             self._set_state(orig)
 
 
 # --------------------------------------------------------------------------- activation recompute
 _IN_RECOMPUTE = [False]
 _IN_CHECKPOINT_FORWARD = [0]
+_USE_REENTRANT = [True]      # flavour of the checkpoint in flight (or of the latest one)
 _RECOMPUTE_RESTORE: list = []
 
 
@@ -385,6 +403,7 @@ def checkpoint(function: Callable, *args, distribute_saved_activations: bool = F
     if distribute_saved_activations:
         raise NotImplementedError("distribute_saved_activations: saved inputs are kept whole on every rank "
                                   "(use sequence parallelism to shard them)")
+    _USE_REENTRANT[0] = bool(use_reentrant)
     if not use_reentrant:
         from torch.utils.checkpoint import checkpoint as torch_ckpt
         from ..quantization import FP8GlobalStateManager

@@ -765,3 +765,34 @@ def test_distributed_module_helpers():
     assert not D.use_reentrant_activation_recompute()
     te.checkpoint(lambda t: t * 2, torch.ones(2, requires_grad=True))
     assert D.use_reentrant_activation_recompute()
+
+
+def test_offload_graph_and_tensor_util_helpers():
+    from transformerengine_b200 import cpu_offload as CO
+    from transformerengine_b200 import graph as G
+    from transformerengine_b200.tensor import utils as TU
+    from transformerengine_b200.tensor.float8 import Float8CurrentScalingQuantizer
+    assert not CO.is_cpu_offload_enabled()
+    ctx, sync = CO.get_cpu_offload_context(enabled=True, num_layers=1, model_layers=2)
+    lin = torch.nn.Linear(512, 512)
+    x = torch.randn(256, 512, requires_grad=True)
+    with ctx:
+        assert CO.is_cpu_offload_enabled()
+        keep = torch.tanh(x)
+        CO.mark_not_offload(keep)
+        CO.mark_activation_offload(keep)            # back to a candidate
+        CO.start_offload(keep)
+        y = lin(keep).square()
+    assert not CO.is_cpu_offload_enabled()
+    sync(y).sum().backward()
+    assert x.grad is not None and ctx.handler.bytes_offloaded > 0
+    assert not G.is_graph_capturing()
+    G.set_capture_start()
+    assert G.is_graph_capturing()
+    G.set_capture_end()
+    q = Float8CurrentScalingQuantizer(torch.float8_e4m3fn)(torch.randn(32, 32))
+    assert q._transpose is not None
+    TU.clear_columnwise_cache(q)
+    assert q._transpose is None and q._data is not None
+    assert not TU.is_custom(q) and not TU.is_custom(torch.zeros(1)) and not TU.is_custom(None)
+    assert TU.cast_master_weights_to_fp8 is TU.quantize_master_weights

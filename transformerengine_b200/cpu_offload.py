@@ -64,6 +64,42 @@ def mark_not_offload(*tensors) -> None:
                     d._te_do_not_offload = True
 
 
+_ACTIVE_CONTEXTS = [0]       # offload contexts currently entered
+
+
+def is_cpu_offload_enabled() -> bool:
+    """True inside an active offload context (modules use it to decide whether saved tensors may leave the GPU)."""
+    return _ACTIVE_CONTEXTS[0] > 0
+
+
+def mark_activation_offload(*tensors) -> None:
+    """Mark tensors as activations that MAY be offloaded (clears a ``mark_not_offload`` mark).  Every tensor saved
+    inside an offload context is a candidate already, so this only matters after ``mark_not_offload``."""
+    for t in tensors:
+        if isinstance(t, torch.Tensor):
+            t._te_do_not_offload = False
+        elif t is not None and hasattr(t, "get_data_tensors"):
+            for d in t.get_data_tensors():
+                if d is not None:
+                    d._te_do_not_offload = False
+
+
+def start_offload(*tensors, offload_base_tensor: bool = False) -> None:
+    """Mark the point on the current stream where ``tensors`` are fully computed: their device-to-host copy, issued
+    when they are saved for backward, waits for this point and not for later work on the stream.
+    ``offload_base_tensor`` is accepted; views are offloaded as the tensors they are (each saved view is copied on
+    its own)."""
+    if not torch.cuda.is_available():
+        return
+    ev = torch.cuda.Event()
+    ev.record(torch.cuda.current_stream())
+    for t in tensors:
+        parts = [t] if isinstance(t, torch.Tensor) else (
+            [d for d in t.get_data_tensors() if d is not None] if (t is not None and hasattr(t, "get_data_tensors")) else [])
+        for p in parts:
+            p._te_ready_event = ev
+
+
 class _OffloadHandler:
     def __init__(self, num_layers: int, model_layers: int, min_numel: int = 1 << 16, *, retain_pinned: bool = False,
                  double_buffering: bool = False, manual: bool = False, stream=None):
@@ -108,7 +144,11 @@ class _OffloadHandler:
             return
         if self.cuda and t.is_cuda:
             e.host = self._host_buffer(t)
-            self.d2h.wait_stream(torch.cuda.current_stream())
+            ready = getattr(t, "_te_ready_event", None)
+            if ready is not None:
+                self.d2h.wait_event(ready)         # start_offload: the producer finished here, later work need not
+            else:
+                self.d2h.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.d2h):
                 e.host.copy_(t, non_blocking=True)
                 e.event = torch.cuda.Event()
@@ -244,12 +284,14 @@ class _OffloadContext:
         if self.handler is not None:
             self._hooks = torch.autograd.graph.saved_tensors_hooks(self.handler.pack, self.handler.unpack)
             self._hooks.__enter__()
+            _ACTIVE_CONTEXTS[0] += 1
         return self
 
     def __exit__(self, *exc):
         if self._hooks is not None:
             self._hooks.__exit__(*exc)
             self._hooks = None
+            _ACTIVE_CONTEXTS[0] -= 1
         return False
 
 

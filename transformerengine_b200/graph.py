@@ -28,6 +28,28 @@ import torch
 from .quantization import DelayedScalingRecipeState, FP8GlobalStateManager, autocast
 
 
+_IS_GRAPH_CAPTURING = [False]
+
+
+def set_capture_start() -> None:
+    """Mark the beginning of a capture (``make_graphed_callables`` does this itself; frameworks that capture by
+    hand call it so that modules can tell, via ``is_graph_capturing``, that host synchronisations are off limits)."""
+    _IS_GRAPH_CAPTURING[0] = True
+
+
+def set_capture_end() -> None:
+    _IS_GRAPH_CAPTURING[0] = False
+
+
+def is_graph_capturing() -> bool:
+    return _IS_GRAPH_CAPTURING[0]
+
+
+def graph_pool_handle():
+    """An opaque token naming a CUDA-graph memory pool, to share one pool between several captures."""
+    return torch.cuda.graph_pool_handle()
+
+
 def _tree_tensors(args):
     return tuple(a for a in args if isinstance(a, torch.Tensor))
 
@@ -290,6 +312,15 @@ def make_graphed_callables(modules: Union[Callable, Sequence[Callable]], sample_
     are captured in schedule order from one pool, so a backward frees its activations for the forwards that
     follow it, like the eager schedule.  Returns one callable per chunk.
     """
+    if not _IS_GRAPH_CAPTURING[0]:
+        set_capture_start()
+        try:
+            return make_graphed_callables(modules, sample_args, num_warmup_iters, allow_unused_input, sample_kwargs,
+                                          enabled, calibrating, recipe, amax_reduction_group, cache_quantized_params,
+                                          pool, fp8_enabled, fp8_recipe, fp8_weight_caching, _order,
+                                          retain_graph_in_backward)
+        finally:
+            set_capture_end()
     if fp8_enabled is not None:
         enabled = fp8_enabled
     if fp8_recipe is not None:

@@ -170,3 +170,18 @@ def post_all_gather_processing(model_weights: Sequence[torch.Tensor]) -> None:
     for w in model_weights:
         if isinstance(w, QuantizedTensorStorage) and hasattr(w, "update_usage"):
             w.update_usage(rowwise_usage=True, columnwise_usage=True)
+
+
+def clear_columnwise_cache(tensor: QuantizedTensorStorage) -> None:
+    """Drop the column-wise copy of a quantized tensor that keeps its row-wise bytes (a parameter gathered by FSDP2
+    builds that copy on demand, and FSDP cannot free what it did not allocate)."""
+    usages = tensor.get_usages() if hasattr(tensor, "get_usages") else {}
+    if usages.get("rowwise") and usages.get("columnwise"):
+        tensor.update_usage(columnwise_usage=False)
+
+
+def is_custom(x=None) -> bool:
+    """Whether a quantizer / quantized tensor comes from a user recipe (``custom`` attribute); plain tensors do not."""
+    if x is None or (isinstance(x, torch.Tensor) and not isinstance(x, QuantizedTensorStorage)):
+        return False
+    return bool(getattr(x, "custom", False))

@@ -200,3 +200,65 @@ def test_router_quantile_balancing_histogram_and_map_formats():
     assert int(QBHistogramMode.FUSED_ATOMIC) == 1
     with pytest.raises(ValueError):
         fused_topk_with_score_function(logits, k, routing_map_format="BITMAP")
+
+
+def _ep_buffer_worker(rank, world, port, q):
+    import os
+    import torch.distributed as dist
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import transformerengine_b200 as te
+        E, K, T, H, align = 4, 2, 10, 16, 4
+        L = E // world
+        te.ep_bootstrap(dist.group.WORLD, num_experts=E, max_tokens_per_rank=T, hidden_dim=H, num_topk=K)
+        assert te.is_ep_bootstrapped()
+        buf = te.EpBuffer(K, T, H, L, alignment=align, payload_dtype=torch.float32)
+        torch.manual_seed(10 + rank)
+        x = torch.randn(T, H, requires_grad=True)
+        logits = torch.randn(T, E)
+        w, idx = torch.softmax(logits, -1).topk(K, dim=-1)
+        w = w.clone().requires_grad_()
+        counts = te.ep_prepare(buf, idx)
+        recv, recv_w, tpe = te.ep_dispatch(buf, x, idx, w)
+        assert torch.equal(tpe, counts) and int(buf.total_recv_tokens) == recv.shape[0] == int(tpe.sum())
+        assert (tpe % align == 0).all() and recv_w.shape == (recv.shape[0],)
+        # "experts": expert e of this rank multiplies by (global expert id + 1); weights applied by the caller
+        scale = torch.cat([torch.full((int(n),), float(rank * L + e + 1)) for e, n in enumerate(tpe.tolist())])
+        out = te.ep_combine(buf, recv * (scale * recv_w)[:, None])
+        x2, w2 = x.detach().clone().requires_grad_(), w.detach().clone().requires_grad_()
+        want = x2 * sum(w2[:, k:k + 1] * (idx[:, k:k + 1] + 1).float() for k in range(K))
+        err = float((out - want).abs().max())
+        out.square().sum().backward()
+        want.square().sum().backward()
+        gerr = max(float((x.grad - x2.grad).abs().max()), float((w.grad - w2.grad).abs().max()))
+        q.put((rank, err, gerr, None))
+        te.ep_finalize()
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, None, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_expert_parallel_buffer_api_over_gloo():
+    """The reference-style buffer API (bootstrap, EpBuffer, prepare / dispatch / combine) on two gloo ranks: every
+    token's expert outputs come back summed, rows arrive grouped by local expert and padded to the alignment."""
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ep_buffer_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err, gerr, tb in res:
+        assert tb is None, tb
+        assert err < 1e-5 and gerr < 1e-4, (rank, err, gerr)

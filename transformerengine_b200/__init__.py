@@ -30,7 +30,8 @@ from .modules.grouped_linear import GroupedLinear, Fp8Padding, Fp8Unpadding
 from .moe import (fused_topk_with_score_function, fused_compute_score_for_moe_aux_loss, fused_moe_aux_loss,
                   moe_permute, moe_permute_with_probs, moe_permute_and_pad_with_probs, moe_unpermute,
                   moe_sort_chunks_by_index, moe_sort_chunks_by_index_with_probs)
-from .parallel.expert_parallel import ep_dispatch, ep_combine
+from .ep import (ep_dispatch, ep_combine, ep_bootstrap, ep_finalize, ep_prepare, is_ep_bootstrapped,  # noqa: F401
+                 is_symm_backed, EpBuffer)
 from .parallel.distributed import checkpoint, CudaRNGStatesTracker
 from .optim import FusedAdam, FusedSGD
 from .parallel.comm_gemm import initialize_ub, destroy_ub

@@ -796,3 +796,46 @@ def test_offload_graph_and_tensor_util_helpers():
     assert q._transpose is None and q._data is not None
     assert not TU.is_custom(q) and not TU.is_custom(torch.zeros(1)) and not TU.is_custom(None)
     assert TU.cast_master_weights_to_fp8 is TU.quantize_master_weights
+
+
+def test_utils_helpers():
+    from transformerengine_b200 import utils as U
+    w = torch.empty(256, 256)
+    U.init_method_normal(0.5)(w)
+    assert 0.45 < float(w.std()) < 0.55
+    U.scaled_init_method_normal(0.5, 8)(w)
+    assert 0.11 < float(w.std()) < 0.14                       # 0.5 / sqrt(16)
+    U.init_method_constant(2.0)(w)
+    assert float(w.min()) == 2.0
+    U.get_default_init_method()(w)
+    assert 0.02 < float(w.std()) < 0.026
+    assert U.divide(12, 4) == 3 and U.ceil_div(7, 2) == 4 and U.round_up_to_nearest_multiple(70, 32) == 96
+    with pytest.raises(ValueError):
+        U.divide(10, 3)
+    a = torch.randn(4, 6, requires_grad=True)
+    parts = U.SplitAlongDim.apply(a, 1, 2)
+    assert len(parts) == 3
+    (parts[0].sum() + 2 * parts[2].sum()).backward()
+    assert torch.equal(a.grad, torch.tensor([1.0, 1, 0, 0, 2, 2]).expand(4, 6))
+    assert U.combine_tensors([torch.ones(2, 3), torch.zeros(2, 3)], 1).shape == (2, 2, 3)
+    assert [p.shape for p in U.split_tensor_along_dim(torch.zeros(4, 6), 1, 3, True)] == [(4, 2)] * 3
+    assert U.requires_grad(None, a) and not U.requires_grad(torch.zeros(1))
+    assert U.cast_if_needed(a.detach(), torch.bfloat16).dtype == torch.bfloat16 and U.cast_if_needed(None, torch.float32) is None
+    t = torch.zeros(10)
+    U.clear_tensor_data(t)
+    assert t.numel() == 0
+    assert U.check_dim_for_fp8_exec(torch.zeros(8, 16)) and not U.check_dim_for_fp8_exec(torch.zeros(8, 8))
+    with pytest.raises(ValueError):
+        U.assert_dim_for_fp8_exec(torch.zeros(3, 16))
+    assert U.needs_quantized_gemm(te.tensor.MXFP8Quantizer()(torch.randn(32, 32))) and not U.needs_quantized_gemm(t)
+    U.validate_rng_states_func(lambda: te.CudaRNGStatesTracker())
+    with pytest.raises(TypeError):
+        U.validate_rng_states_func(lambda: object())
+    with pytest.raises(AssertionError):
+        U.assert_viewless_tensor(torch.zeros(4)[1:])
+    assert U.get_cached_ones_tensor(4, torch.float32, "cpu") is U.get_cached_ones_tensor(4, torch.float32, "cpu")
+    assert U.devices_match("cpu", torch.device("cpu")) and U.canonicalize_dtype(None) == torch.get_default_dtype()
+    assert U.attention_mask_func(torch.zeros(2), torch.tensor([True, False])).tolist() == [-10000.0, 0.0]
+    with U.get_nvtx_range_context("x"):
+        pass
+    assert U.all_close(torch.ones(2), torch.ones(2))

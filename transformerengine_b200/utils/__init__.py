@@ -115,3 +115,4 @@ def deinterleave_glu_tensor(tensor: torch.Tensor, interleave_size: int) -> torch
     rest = tensor.shape[1:]
     t = tensor.reshape(blocks, 2, interleave_size, *rest)
     return torch.cat([t[:, 0].reshape(n // 2, *rest), t[:, 1].reshape(n // 2, *rest)], dim=0).contiguous()
+from .helpers import *  # noqa: F401,F403,E402

@@ -164,3 +164,8 @@ def apply_fused_qkv_rotary_pos_emb(qkv: torch.Tensor, q_freqs: torch.Tensor, k_f
     k = apply_rotary_pos_emb(k, k_freqs, tensor_format, start_positions=start_positions, interleaved=interleaved,
                              cp_size=cp_size, cp_rank=cp_rank)
     return q, k, v
+
+
+# names of the reference's autograd functions (``pytorch/attention/rope.py``) for code that calls ``.apply`` on them
+FusedRoPEFunc = _RopeFn
+FusedQKVRoPEFunc = _RopeQkvFn

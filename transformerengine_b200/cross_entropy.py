@@ -100,3 +100,6 @@ def parallel_cross_entropy(inp: torch.Tensor, target: torch.Tensor, label_smooth
     if reduce_loss:
         return loss.sum() / (tgt != -100).sum().clamp(min=1)
     return loss.reshape(shape)
+
+
+CrossEntropyFunction = _PerTokenCrossEntropy   # the reference's name of the per-token autograd function

@@ -410,3 +410,7 @@ class WeightGradStore:
         q, self._queue = self._queue, []
         for fn in q:
             fn()
+
+
+# communicator registry queries under the reference's names (``module/base.py``)
+from ..parallel.comm_gemm import destroy_ub, initialize_ub, is_ub_initialized  # noqa: E402,F401

@@ -376,6 +376,11 @@ def destroy_ub() -> None:
     _ENABLED["group"] = None
 
 
+def is_ub_initialized() -> bool:
+    """Whether ``initialize_ub`` has switched the fused collective GEMMs on."""
+    return _ENABLED["group"] is not None
+
+
 def enabled_for(group) -> bool:
     return _ENABLED["group"] is not None and group is not None and _ENABLED["group"] == group
 

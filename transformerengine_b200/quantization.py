@@ -82,6 +82,17 @@ def get_fp8_torch_dtype(recipe: Recipe, fprop_tensor: bool = True) -> torch.dtyp
     return torch.float8_e5m2
 
 
+def get_fp8_te_dtype(recipe: Recipe, fprop_tensor: bool = True):
+    """The FP8 format of a recipe's forward / backward tensors as the library's ``DType`` enum."""
+    from .constants import DType
+    return DType.kFloat8E4M3 if get_fp8_torch_dtype(recipe, fprop_tensor) == torch.float8_e4m3fn else DType.kFloat8E5M2
+
+
+def get_fp4_te_dtype(recipe: Recipe):
+    from .constants import DType
+    return DType.kFloat4E2M1
+
+
 def get_fp8_max(recipe: Recipe, fprop_tensor: bool = True) -> float:
     fmt = getattr(recipe, "fp8_format", Format.HYBRID)
     return fmt.value.max_fwd if fprop_tensor else fmt.value.max_bwd

@@ -2,6 +2,7 @@
 (test model: reference ``tests/pytorch/test_fusible_ops.py``)."""
 import copy
 
+import pytest
 import torch
 
 import transformerengine_b200 as te
@@ -195,3 +196,35 @@ def test_grouped_mlp_fusion_matches_per_expert_reference():
         torch.testing.assert_close(getattr(seq[2], f"weight{i}").grad, w2[i].grad, rtol=1e-4, atol=1e-5)
     # the state dict shows the experts' weights under the basic operations
     assert "0.impl.weight0" in seq.state_dict()
+
+
+def test_gated_unit_variants():
+    """The gated units outside the fused kernels' set against their formulas; the gate acts on the FIRST half."""
+    from transformerengine_b200 import fusible as ops
+    torch.manual_seed(0)
+    x = (torch.randn(6, 16) * 4).requires_grad_()
+    a, b = x.detach().chunk(2, dim=-1)
+    torch.testing.assert_close(ops.GLU()(x), torch.sigmoid(a) * b)
+    ac, bc = a.clamp(max=7.0), b.clamp(-7.0, 7.0) + 1.0
+    torch.testing.assert_close(ops.ClampedSwiGLU()(x), ac * torch.sigmoid(1.702 * ac) * bc)
+    torch.testing.assert_close(ops.ClampedSwiGLU(limit=2.0, alpha=1.0, glu_linear_offset=0.0)(x),
+                               a.clamp(max=2.0) * torch.sigmoid(a.clamp(max=2.0)) * b.clamp(-2.0, 2.0))
+    torch.testing.assert_close(ops.SiTUGLU()(x), 4 * torch.tanh(a / 4) * torch.sigmoid(a) * 25 * torch.tanh(b / 25))
+    torch.testing.assert_close(ops.QGEGLU()(x), a * torch.sigmoid(1.702 * a) * b)
+    torch.testing.assert_close(ops.SReGLU()(x), torch.relu(a).square() * b)
+    s = torch.rand(6, requires_grad=True)
+    y = ops.ScaledSReLU()(x, s)
+    torch.testing.assert_close(y, torch.relu(x.detach()).square() * s.detach()[:, None])
+    y.sum().backward()
+    torch.testing.assert_close(s.grad, torch.relu(x.detach()).square().sum(-1))
+    torch.testing.assert_close(ops.ScaledClampedQGeGLU()(x, s), ops.ClampedSwiGLU()(x) * s[:, None])
+    torch.testing.assert_close(ops.ScaledSiTUGLU(beta1=2.0)(x, s), ops.SiTUGLU(beta1=2.0)(x) * s[:, None])
+    # inside a Sequential: linear -> gated unit -> linear, with the scale as an extra input
+    seq = ops.Sequential(ops.Linear(16, 32, bias=False, device="cpu", dtype=torch.float32),
+                         ops.ScaledSiTUGLU(), ops.Linear(16, 8, bias=False, device="cpu", dtype=torch.float32))
+    out = seq(x.detach(), s.detach())
+    assert out.shape == (6, 8) and torch.isfinite(out).all()
+    with pytest.raises(ValueError):
+        ops.SiTUGLU(beta1=0.0)
+    with pytest.raises(NotImplementedError):
+        ops.GLU(glu_interleave_size=2)

@@ -21,12 +21,14 @@ optimizers only ever see the basic operations.
 from .ops import (FusibleOperation, BasicLinear, Bias, Linear, LayerNorm, RMSNorm, GELU, ReLU, SiLU, SwiGLU, GEGLU,
                   ReGLU, QGELU, SReLU, Quantize, Identity, Reshape, ConstantScale, Dropout, AddExtraInput,
                   MakeExtraOutput, AllReduce, AllGather, ReduceScatter, L2Normalization, GroupedLinear,
-                  ScaledSwiGLU)
+                  ScaledSwiGLU, GLU, QGEGLU, SReGLU, ClampedSwiGLU, SiTUGLU, ScaledSReLU, ScaledClampedQGeGLU,
+                  ScaledSiTUGLU)
 from .fused import ForkNorm, GroupedMLP, LinearChain
 from .sequential import Sequential, fuse_operations
 
 __all__ = ["FusibleOperation", "BasicLinear", "Bias", "Linear", "LayerNorm", "RMSNorm", "GELU", "ReLU", "SiLU",
            "SwiGLU", "GEGLU", "ReGLU", "QGELU", "SReLU", "Quantize", "Identity", "Reshape", "ConstantScale",
            "Dropout", "AddExtraInput", "MakeExtraOutput", "AllReduce", "AllGather", "ReduceScatter",
-           "L2Normalization", "GroupedLinear", "ScaledSwiGLU", "Sequential", "fuse_operations", "LinearChain", "ForkNorm",
+           "L2Normalization", "GroupedLinear", "ScaledSwiGLU", "GLU", "QGEGLU", "SReGLU", "ClampedSwiGLU", "SiTUGLU",
+           "ScaledSReLU", "ScaledClampedQGeGLU", "ScaledSiTUGLU", "Sequential", "fuse_operations", "LinearChain", "ForkNorm",
            "GroupedMLP"]

@@ -128,6 +128,73 @@ class ReGLU(_Activation):
     act_name = "reglu"
 
 
+class QGEGLU(_Activation):
+    act_name = "qgeglu"
+
+
+class SReGLU(_Activation):
+    act_name = "sreglu"
+
+
+def _halves(x):
+    """(gate input a, linear input b): the gating function applies to the FIRST half of the last dimension."""
+    return x.float().chunk(2, dim=-1)
+
+
+class _ElementwiseGLU(FusibleOperation):
+    """Gated units outside the fused activation kernels' set: fp32 tensor math that autograd differentiates
+    (a handful of element-wise launches on a GPU; the kernels cover gelu / silu / relu / qgelu / srelu gates)."""
+
+    def __init__(self, *, cache_quantized_input: bool = False, glu_interleave_size: Optional[int] = None):
+        super().__init__()
+        if glu_interleave_size is not None:
+            raise NotImplementedError("interleaved gate / linear halves (glu_interleave_size) are not implemented")
+        self.cache_quantized_input = cache_quantized_input
+
+    def _glu(self, a, b):
+        raise NotImplementedError
+
+    def forward(self, x):
+        a, b = _halves(x)
+        return self._glu(a, b).to(x.dtype)
+
+
+class GLU(_ElementwiseGLU):
+    """``sigmoid(a) * b`` (reference: ``pytorch/ops/basic/activation.py``, ``GLU``)."""
+
+    def _glu(self, a, b):
+        return torch.sigmoid(a) * b
+
+
+class ClampedSwiGLU(_ElementwiseGLU):
+    """The GPT-OSS gated unit: ``a' = min(a, limit)``, ``b' = clamp(b, -limit, limit) + glu_linear_offset``,
+    ``y = a' * sigmoid(alpha * a') * b'`` (reference: ``pytorch/ops/basic/swiglu.py``, ``ClampedSwiGLU``)."""
+
+    def __init__(self, *, limit: float = 7.0, alpha: float = 1.702, glu_linear_offset: float = 1.0, **kw):
+        super().__init__(**kw)
+        self.limit, self.alpha, self.glu_linear_offset = float(limit), float(alpha), float(glu_linear_offset)
+
+    def _glu(self, a, b):
+        a = torch.clamp(a, max=self.limit)
+        b = torch.clamp(b, -self.limit, self.limit) + self.glu_linear_offset
+        return a * torch.sigmoid(self.alpha * a) * b
+
+
+class SiTUGLU(_ElementwiseGLU):
+    """Soft-capped SiLU gated unit: ``beta1 * tanh(a / beta1) * sigmoid(a) * beta2 * tanh(b / beta2)``
+    (reference: ``pytorch/ops/basic/swiglu.py``, ``SiTUGLU``)."""
+
+    def __init__(self, *, beta1: float = 4.0, beta2: float = 25.0, **kw):
+        super().__init__(**kw)
+        self.beta1, self.beta2 = float(beta1), float(beta2)
+        for name, v in (("beta1", self.beta1), ("beta2", self.beta2)):
+            if not (v > 0.0 and v != float("inf")):
+                raise ValueError(f"{name} must be finite and positive, got {v}")
+
+    def _glu(self, a, b):
+        return self.beta1 * torch.tanh(a / self.beta1) * torch.sigmoid(a) * (self.beta2 * torch.tanh(b / self.beta2))
+
+
 class _QuantizeFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, quantizer, keep):  # type: ignore[override]
@@ -297,6 +364,57 @@ class ScaledSwiGLU(FusibleOperation):
 
     def forward(self, x, scales):
         return _ScaledGluFn.apply(x, scales.reshape(-1), self.act_name)
+
+
+class _ScaledElementwise(FusibleOperation):
+    """``y = f(x) * scales[..., None]`` with one extra input (a scale per row: the routing probability of an MoE
+    expert MLP); fp32 tensor math that autograd differentiates, scale gradient included."""
+
+    num_extra_inputs = 1
+
+    def __init__(self, glu_interleave_size: Optional[int] = None, *, activation_recompute_in_mlp: bool = False):
+        super().__init__()
+        if glu_interleave_size is not None:
+            raise NotImplementedError("interleaved gate / linear halves (glu_interleave_size) are not implemented")
+        if activation_recompute_in_mlp:
+            raise NotImplementedError("activation_recompute_in_mlp: wrap the MLP in te.checkpoint instead")
+
+    def _f(self, x):
+        raise NotImplementedError
+
+    def forward(self, x, scales):
+        y = self._f(x.float())
+        return (y * scales.float().reshape(*y.shape[:-1], 1)).to(x.dtype)
+
+
+class ScaledSReLU(_ScaledElementwise):
+    """Squared ReLU times a per-row scale (reference: ``pytorch/ops/basic/activation.py``, ``ScaledSReLU``)."""
+
+    def _f(self, x):
+        return torch.relu(x).square()
+
+
+class ScaledClampedQGeGLU(_ScaledElementwise):
+    """``ClampedSwiGLU`` numerics times a per-row scale (reference: ``pytorch/ops/basic/swiglu.py``)."""
+
+    def __init__(self, glu_interleave_size: Optional[int] = None, *, limit: float = 7.0, alpha: float = 1.702,
+                 glu_linear_offset: float = 1.0, **kw):
+        super().__init__(glu_interleave_size, **kw)
+        self._inner = ClampedSwiGLU(limit=limit, alpha=alpha, glu_linear_offset=glu_linear_offset)
+
+    def _f(self, x):
+        return self._inner._glu(*x.chunk(2, dim=-1))
+
+
+class ScaledSiTUGLU(_ScaledElementwise):
+    """``SiTUGLU`` times a per-row scale (reference: ``pytorch/ops/basic/swiglu.py``)."""
+
+    def __init__(self, glu_interleave_size: Optional[int] = None, *, beta1: float = 4.0, beta2: float = 25.0, **kw):
+        super().__init__(glu_interleave_size, **kw)
+        self._inner = SiTUGLU(beta1=beta1, beta2=beta2)
+
+    def _f(self, x):
+        return self._inner._glu(*x.chunk(2, dim=-1))
 
 
 class _CollFn(torch.autograd.Function):

@@ -589,3 +589,38 @@ def test_backward_override_runs_the_backward_gemms_unquantized(override):
     with pytest.raises(NotImplementedError, match="backward_override"):
         with te.autocast(enabled=True, recipe=rec):
             gl(x, [16, 16])
+
+
+def test_layernorm_mlp_clamped_swiglu_and_glu():
+    """``activation="clamped_swiglu"`` with ``activation_params`` (the GPT-OSS gated unit) and ``"glu"``: forward
+    and gradients against autograd through the formulas."""
+    torch.manual_seed(0)
+    x = torch.randn(16, 32) * 3
+    for act, params in (("clamped_swiglu", dict(limit=2.0, alpha=1.5, glu_linear_offset=0.5)), ("clamped_swiglu", None),
+                        ("glu", None)):
+        mlp = te.LayerNormMLP(32, 64, normalization="RMSNorm", activation=act, activation_params=params, bias=False,
+                              params_dtype=torch.float32, device="cpu")
+        assert mlp.fc1_weight.shape == (128, 32)
+        xi = x.clone().requires_grad_()
+        y = mlp(xi)
+        y.square().sum().backward()
+        xr = x.clone().requires_grad_()
+        g, w1, w2 = (p.detach().clone().requires_grad_() for p in (mlp.layer_norm_weight, mlp.fc1_weight, mlp.fc2_weight))
+        ln = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + mlp.eps) * g
+        a, b = (ln @ w1.t()).chunk(2, dim=-1)
+        if act == "glu":
+            h = torch.sigmoid(a) * b
+        else:
+            p = dict(limit=7.0, alpha=1.702, glu_linear_offset=1.0)
+            p.update(params or {})
+            ac = a.clamp(max=p["limit"])
+            h = ac * torch.sigmoid(p["alpha"] * ac) * (b.clamp(-p["limit"], p["limit"]) + p["glu_linear_offset"])
+        want = h @ w2.t()
+        want.square().sum().backward()
+        torch.testing.assert_close(y, want, rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(xi.grad, xr.grad, rtol=1e-3, atol=1e-4)
+        torch.testing.assert_close(mlp.fc1_weight.grad, w1.grad, rtol=1e-3, atol=1e-4)
+    with pytest.raises(NotImplementedError):
+        te.LayerNormMLP(32, 64, activation="swiglu", activation_params=dict(limit=1.0), device="cpu")
+    with pytest.raises(ValueError):
+        te.LayerNormMLP(32, 64, activation="clamped_swiglu", activation_params=dict(beta=1.0), device="cpu")

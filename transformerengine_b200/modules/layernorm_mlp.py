@@ -70,7 +70,8 @@ class _LayerNormMLP(torch.autograd.Function):
         if q_in2 is not None:
             q_in2.set_usage(rowwise=True, columnwise=grad and override is None)
             q_in2.internal = True
-        act_hp, act_q = ops.activation_fwd(fc1_out, act, quantizer=q_in2, want_hp=q_in2 is None or hp_bwd)
+        act_hp, act_q = ops.activation_fwd(fc1_out, act, quantizer=q_in2, want_hp=q_in2 is None or hp_bwd,
+                                           params=module.activation_params)
         act_in = act_q if act_q is not None else act_hp
         out, _ = F.linear_fprop(act_in, w2q, fc2_b, cfg2, adt)
         if grad:
@@ -131,7 +132,8 @@ class _LayerNormMLP(torch.autograd.Function):
         if q_go1 is not None:
             q_go1.set_usage(rowwise=True, columnwise=True)
             q_go1.internal = True
-        dfc1_hp, dfc1_q, db1 = ops.activation_bwd(dact, fc1_out, module.activation, quantizer=q_go1,
+        dfc1_hp, dfc1_q, db1 = ops.activation_bwd(dact, fc1_out, module.activation, params=module.activation_params,
+                                                  quantizer=q_go1,
                                                   want_hp=q_go1 is None, want_dbias=fc1_b is not None)
         dfc1 = dfc1_q if dfc1_q is not None else dfc1_hp
         if db1 is not None:
@@ -170,8 +172,12 @@ class LayerNormMLP(TransformerEngineBaseModule):
                  ub_bulk_dgrad: bool = False, ub_bulk_wgrad: bool = False, delay_wgrad_compute: bool = False,
                  symmetric_ar_type: Optional[str] = None, checkpoint: bool = False, name: Optional[str] = None):
         super().__init__()
-        if activation_params:
-            raise NotImplementedError("activation_params (parametrised activations) are not implemented")
+        if activation_params and activation != "clamped_swiglu":
+            raise NotImplementedError(f"activation_params are the limit / alpha / glu_linear_offset of "
+                                      f"activation='clamped_swiglu'; activation={activation!r} takes none")
+        if activation_params and set(activation_params) - {"limit", "alpha", "glu_linear_offset"}:
+            raise ValueError(f"unknown activation_params {sorted(activation_params)}")
+        self.activation_params = dict(activation_params) if activation_params else None
         if return_layernorm_output_gathered:
             raise NotImplementedError("return_layernorm_output_gathered is not implemented")
         if symmetric_ar_type is not None:

@@ -19,7 +19,32 @@ PLAIN = ("gelu", "silu", "relu", "qgelu", "srelu")
 
 
 def is_gated(name: str) -> bool:
-    return name in GATED or name == "glu"
+    return name in GATED or name in ("glu", "clamped_swiglu")
+
+
+def _clamped_params(params):
+    p = dict(limit=7.0, alpha=1.702, glu_linear_offset=1.0)
+    p.update(params or {})
+    return float(p["limit"]), float(p["alpha"]), float(p["glu_linear_offset"])
+
+
+def _clamped_swiglu_fwd(x1, x2, params):
+    """GPT-OSS gated unit: gate input capped at ``limit``, sigmoid(alpha x) gate, linear half clamped to
+    +-limit and shifted by ``glu_linear_offset`` (reference: ``common/util/math.h``, ``clamped_silu``)."""
+    limit, alpha, off = _clamped_params(params)
+    a = torch.clamp(x1, max=limit)
+    return a * torch.sigmoid(alpha * a) * (torch.clamp(x2, -limit, limit) + off)
+
+
+def _clamped_swiglu_bwd(df, x1, x2, params):
+    limit, alpha, off = _clamped_params(params)
+    a = torch.clamp(x1, max=limit)
+    s = torch.sigmoid(alpha * a)
+    act = a * s
+    dact = (s + alpha * a * s * (1 - s)) * (x1 <= limit)
+    lin = torch.clamp(x2, -limit, limit) + off
+    dlin = ((x2 >= -limit) & (x2 <= limit)).to(df.dtype)
+    return torch.cat([df * lin * dact, df * act * dlin], dim=-1)
 
 
 def _act(x, name):
@@ -58,9 +83,12 @@ def _dact(x, name):
     raise ValueError(name)
 
 
-def activation_fwd_ref(x, name, row_scale=None):
+def activation_fwd_ref(x, name, row_scale=None, params=None):
     xf = x.float()
-    if is_gated(name):
+    if name == "clamped_swiglu":
+        n = x.shape[-1] // 2
+        y = _clamped_swiglu_fwd(xf[..., :n], xf[..., n:], params)
+    elif is_gated(name):
         n = x.shape[-1] // 2
         base = GATED.get(name, "sigmoid")
         y = _act(xf[..., :n], base) * xf[..., n:]
@@ -71,10 +99,13 @@ def activation_fwd_ref(x, name, row_scale=None):
     return y
 
 
-def activation_bwd_ref(dy, x, name, row_scale=None):
+def activation_bwd_ref(dy, x, name, row_scale=None, params=None):
     xf, df = x.float(), dy.float()
     if row_scale is not None:
         df = df * row_scale.float().reshape(*df.shape[:-1], 1)
+    if name == "clamped_swiglu":
+        n = x.shape[-1] // 2
+        return _clamped_swiglu_bwd(df, xf[..., :n], xf[..., n:], params)
     if is_gated(name):
         n = x.shape[-1] // 2
         base = GATED.get(name, "sigmoid")
@@ -89,8 +120,10 @@ def _cuda_ok(x, name, C_out):
             and C_out % 32 == 0 and (name in PLAIN or name in GATED))
 
 
-def activation_fwd(x, name: str, quantizer=None, want_hp: bool = True, row_scale: Optional[torch.Tensor] = None):
-    """Returns (y or None, y_quantized or None)."""
+def activation_fwd(x, name: str, quantizer=None, want_hp: bool = True, row_scale: Optional[torch.Tensor] = None,
+                   params: Optional[dict] = None):
+    """Returns (y or None, y_quantized or None).  ``params``: ``limit`` / ``alpha`` / ``glu_linear_offset`` of
+    ``"clamped_swiglu"`` (which, like ``"glu"``, runs as tensor math on every device)."""
     C_in = x.shape[-1]
     C_out = C_in // 2 if is_gated(name) else C_in
     R = x.numel() // C_in
@@ -118,12 +151,12 @@ def activation_fwd(x, name: str, quantizer=None, want_hp: bool = True, row_scale
         elif quantizer is not None:
             yq = quantizer(y)
         return y, yq
-    y = activation_fwd_ref(x, name, row_scale).to(x.dtype)
+    y = activation_fwd_ref(x, name, row_scale, params).to(x.dtype)
     return y, (quantizer(y) if quantizer is not None else None)
 
 
 def activation_bwd(dy, x, name: str, quantizer=None, want_hp: bool = True, want_dbias: bool = False,
-                   row_scale: Optional[torch.Tensor] = None):
+                   row_scale: Optional[torch.Tensor] = None, params: Optional[dict] = None):
     """Returns (dx or None, dx_quantized or None, dbias or None)."""
     C_in = x.shape[-1]
     R = x.numel() // C_in
@@ -149,6 +182,6 @@ def activation_bwd(dy, x, name: str, quantizer=None, want_hp: bool = True, want_
         elif quantizer is not None:
             dq = quantizer(dx)
         return dx, dq, (r["dbias"] if want_dbias else None)
-    dx = activation_bwd_ref(dy, x, name, row_scale).to(x.dtype)
+    dx = activation_bwd_ref(dy, x, name, row_scale, params).to(x.dtype)
     db = dx.reshape(-1, C_in).float().sum(0) if want_dbias else None
     return dx, (quantizer(dx) if quantizer is not None else None), db

@@ -77,12 +77,18 @@ def _worker(rank, world, port, q):
         # several optimizer steps: the shards are re-quantized by the optimizer (fp32 master weights), and what the
         # next forward pass sees must be exactly the gathered shards (one scale for per-tensor FP8, fresh bytes for
         # MXFP8), i.e. training makes progress and all ranks hold the same full weight
+        from transformerengine_b200.tensor.blockwise import Float8BlockwiseQTensor
+        from transformerengine_b200.tensor.nvfp4 import NVFP4Tensor
         for name, rec, cls in (("current", R.Float8CurrentScaling(), Float8Tensor),
-                               ("mxfp8", R.MXFP8BlockScaling(), MXFP8Tensor)):
+                               ("mxfp8", R.MXFP8BlockScaling(), MXFP8Tensor),
+                               ("nvfp4", R.NVFP4BlockScaling(), NVFP4Tensor),
+                               ("block", R.Float8BlockScaling(), Float8BlockwiseQTensor)):
             torch.manual_seed(0)
             with te.quantized_model_init(enabled=True, recipe=rec):
                 lin = te.Linear(256, 256, bias=False, params_dtype=torch.float32, device="cpu")
             fully_shard(lin)
+            if not isinstance(lin.weight._local_tensor, cls):
+                bad[f"{name}: shard type"] = type(lin.weight._local_tensor).__name__
             opt = te.FusedAdam(lin.parameters(), lr=1e-2, master_weights=True)
             torch.manual_seed(7 + rank)
             x = torch.randn(128, 256)

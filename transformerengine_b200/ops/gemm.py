@@ -74,6 +74,8 @@ def as_operand(t, usage: str = "rowwise") -> Operand:
         if row:
             return Operand("nvfp4", t._rowwise_data.reshape(R, C // 2), t._rowwise_scale_inv, amax=t._amax_rowwise,
                            rows=R, k=C)
+        if t._columnwise_data is None:
+            t.ensure_columnwise()      # a parameter re-gathered by FSDP2: row-wise bytes only
         return Operand("nvfp4", t._columnwise_data, t._columnwise_scale_inv, amax=t._amax_columnwise, rows=C, k=R,
                        rht=t._columnwise_rht)
     if isinstance(t, Float8TensorStorage):
@@ -89,6 +91,8 @@ def as_operand(t, usage: str = "rowwise") -> Operand:
         # power-of-two block scales exist as UE8M0 tiles too (written by the quantize kernel): the operand then
         # IS an MXFP8 operand; fp32 scales (or tensors quantized on the CPU) multiply in high precision
         R, C = t._rows_cols()
+        if not row and t._columnwise_data is None:
+            t.ensure_columnwise()      # a parameter re-gathered by FSDP2: row-wise bytes only
         if row and t._rowwise_data is not None and t._rowwise_mx_scale is not None:
             return Operand("mxfp8", t._rowwise_data.reshape(R, C), t._rowwise_mx_scale, t._fp8_dtype, rows=R, k=C)
         if not row and t._columnwise_data is not None and t._columnwise_mx_scale is not None:

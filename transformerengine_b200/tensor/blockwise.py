@@ -50,6 +50,20 @@ class Float8BlockwiseQTensorStorage(QuantizedTensorStorage):
         if columnwise_usage is False:
             self._columnwise_data = self._columnwise_scale_inv = self._columnwise_mx_scale = None
 
+    def ensure_columnwise(self) -> None:
+        """Build the column-wise copy from the row-wise one when it is missing (a parameter gathered by FSDP2 carries
+        the row-wise bytes only).  With 128 x 128 blocks (weights) both copies hold the same values, so this equals
+        a direct quantization; with 1 x 128 blocks it is a second rounding along the other direction."""
+        if self._columnwise_data is not None or self._rowwise_data is None or len(self._shape) != 2 \
+                or self._quantizer is None:
+            return
+        q = self._quantizer.copy()
+        q.set_usage(rowwise=False, columnwise=True)
+        q.internal = True
+        tmp = q.quantize_impl(self._dequantize_impl(torch.bfloat16 if self._dtype == torch.float32 else self._dtype))
+        self._columnwise_data, self._columnwise_scale_inv = tmp._columnwise_data, tmp._columnwise_scale_inv
+        self._columnwise_mx_scale = tmp._columnwise_mx_scale
+
     def _dequantize_impl(self, dtype=None):
         dtype = dtype or self._dtype
         R, C = self._rows_cols()
@@ -106,6 +120,100 @@ class Float8BlockwiseQTensor(Float8BlockwiseQTensorStorage, QuantizedTensor):
         return (_make_blockwise_in_reduce_ex,
                 (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
                  self._fp8_dtype, self._is_2D_scaled, self._dtype, self._shape))
+
+
+    # ---- FSDP2 (``fully_shard``): the parameter is cut along its rows into whole 128-row blocks; a piece carries the
+    # row-wise bytes, the matching rows of the fp32 block scales and (when the quantize kernel wrote them) of the
+    # tile-major UE8M0 scales.  Other cuts take the generic (dequantizing) path.
+    def _alias(self, shape, data, scales, mx) -> "Float8BlockwiseQTensor":
+        out = Float8BlockwiseQTensor(shape=shape, dtype=self._dtype, rowwise_data=data, rowwise_scale_inv=scales,
+                                     columnwise_data=None, columnwise_scale_inv=None, fp8_dtype=self._fp8_dtype,
+                                     is_2D_scaled=self._is_2D_scaled, quantizer=self._quantizer)
+        out._rowwise_mx_scale = mx
+        return out
+
+    def _row_piece(self, r0: int, r1: int) -> "Float8BlockwiseQTensor":
+        R, C = self._rows_cols()
+        br = 128 if self._is_2D_scaled else 1
+        mx = self._rowwise_mx_scale
+        if mx is not None:
+            per_tile = mx.numel() // ((R + 127) // 128)
+            mx = mx.reshape(-1)[(r0 // 128) * per_tile:((r1 + 127) // 128) * per_tile]
+        return self._alias((r1 - r0, C), self._rowwise_data.reshape(R, C)[r0:r1],
+                           self._rowwise_scale_inv[r0 // br:-(-r1 // br)], mx)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        aten = torch.ops.aten
+        t = args[0] if args else None
+        if isinstance(t, Float8BlockwiseQTensor) and t._rowwise_data is not None and len(t._shape) == 2:
+            R, C = t._rows_cols()
+            if func == aten.split.Tensor and (args[2] if len(args) > 2 else kwargs.get("dim", 0)) == 0 \
+                    and isinstance(args[1], int) and args[1] % 128 == 0 and R % 128 == 0:
+                return tuple(t._row_piece(r, min(r + args[1], R)) for r in range(0, R, args[1]))
+            if func == aten.slice.Tensor:
+                dim = args[1] if len(args) > 1 else 0
+                start = args[2] if len(args) > 2 and args[2] is not None else 0
+                end = min(args[3], R) if len(args) > 3 and args[3] is not None else R
+                step = args[4] if len(args) > 4 else 1
+                if dim == 0 and step == 1 and start % 128 == 0 and (end % 128 == 0 or end == R) and end > start:
+                    return t._row_piece(start, end)
+            if func == aten.new_zeros.default and len(args[1]) == 2 and args[1][1] == C and args[1][0] % 128 == 0:
+                rows = args[1][0]
+                dev = kwargs.get("device") or t._rowwise_data.device
+                br = 128 if t._is_2D_scaled else 1
+                mx = t._rowwise_mx_scale
+                if mx is not None:
+                    mx = torch.zeros(rows // 128 * (mx.numel() // ((R + 127) // 128)), dtype=torch.uint8, device=dev)
+                return t._alias((rows, C), torch.zeros(rows, C, dtype=t._rowwise_data.dtype, device=dev),
+                                torch.ones(rows // br, t._rowwise_scale_inv.shape[1], dtype=torch.float32, device=dev),
+                                mx)
+            if func == aten.view.default and tuple(args[1]) in ((-1,), (R * C,)):
+                return t._alias((R * C,), t._rowwise_data, t._rowwise_scale_inv, t._rowwise_mx_scale)
+            if func == aten.as_strided.default and tuple(args[1]) == (R, C) and tuple(args[2]) == (C, 1) \
+                    and not (len(args) > 3 and args[3]):
+                out = t._alias((R, C), t._rowwise_data, t._rowwise_scale_inv, t._rowwise_mx_scale)
+                out._columnwise_data, out._columnwise_scale_inv = t._columnwise_data, t._columnwise_scale_inv
+                out._columnwise_mx_scale = t._columnwise_mx_scale
+                return out
+            if func == aten.copy_.default and isinstance(args[1], Float8BlockwiseQTensor) \
+                    and args[1]._rowwise_data is not None and tuple(args[1]._shape) == tuple(t._shape) \
+                    and args[1]._is_2D_scaled == t._is_2D_scaled:
+                src = args[1]
+                t._rowwise_data.reshape(R, C).copy_(src._rowwise_data.reshape(R, C))
+                t._rowwise_scale_inv.copy_(src._rowwise_scale_inv)
+                if t._rowwise_mx_scale is not None and src._rowwise_mx_scale is not None:
+                    t._rowwise_mx_scale.reshape(-1).copy_(src._rowwise_mx_scale.reshape(-1))
+                else:
+                    t._rowwise_mx_scale = None
+                t._columnwise_data = t._columnwise_scale_inv = t._columnwise_mx_scale = None
+                return t
+        return super().__torch_dispatch__(func, types, args, kwargs)
+
+    def fsdp_pre_all_gather(self, mesh=None, orig_size=None, contiguous_orig_stride=None, module=None, mp_policy=None):
+        assert self._rowwise_data is not None, "FSDP gathers the row-wise copy"
+        R, C = self._rows_cols()
+        assert R % 128 == 0, "block-scaled parameter shards must hold a multiple of 128 rows"
+        parts = [self._rowwise_data.reshape(R, C).view(torch.uint8),
+                 self._rowwise_scale_inv.contiguous().view(torch.uint8)]          # fp32 scales travel as bytes
+        if self._rowwise_mx_scale is not None:
+            parts.append(self._rowwise_mx_scale.reshape(R // 128, -1))
+        return tuple(parts), (self._fp8_dtype, self._is_2D_scaled, self._dtype, self._quantizer)
+
+    def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype=None, *, out=None):
+        data, scales = all_gather_outputs[0], all_gather_outputs[1].view(torch.float32)
+        mx = all_gather_outputs[2].reshape(-1) if len(all_gather_outputs) > 2 else None
+        fp8_dtype, is_2d, dtype, quantizer = metadata
+        if out is not None:
+            out._rowwise_data, out._rowwise_scale_inv, out._rowwise_mx_scale = data, scales, mx
+            out._columnwise_data = out._columnwise_scale_inv = out._columnwise_mx_scale = None
+            return None
+        full = Float8BlockwiseQTensor(shape=tuple(data.shape), dtype=dtype, rowwise_data=data, rowwise_scale_inv=scales,
+                                      columnwise_data=None, columnwise_scale_inv=None, fp8_dtype=fp8_dtype,
+                                      is_2D_scaled=is_2d, quantizer=quantizer)
+        full._rowwise_mx_scale = mx
+        return full, all_gather_outputs
 
 
 def _make_blockwise_in_reduce_ex(rd, rs, cd, cs, fp8_dtype, is_2d, dtype, shape):

@@ -57,6 +57,24 @@ class NVFP4TensorStorage(QuantizedTensorStorage):
         if columnwise_usage is False:
             self._columnwise_data = self._columnwise_scale_inv = self._amax_columnwise = None
 
+    def ensure_columnwise(self) -> None:
+        """Build the column-wise copy from the row-wise one when it is missing (a parameter gathered by FSDP2 carries
+        the row-wise bytes only).  Weights use 16 x 16 blocks without the Hadamard transform, for which both copies
+        hold the same values, so re-quantizing the dequantized row-wise copy reproduces what a direct quantization
+        gives; with 1-D blocks it is a second rounding along the other direction."""
+        if self._columnwise_data is not None or self._rowwise_data is None or len(self._shape) != 2:
+            return
+        q = self._quantizer
+        R, C = self._rows_cols()
+        if q is None or R % 16 or C % 16:
+            return
+        hp = ops.dequantize_nvfp4(self._rowwise_data.reshape(R, C // 2), self._rowwise_scale_inv, self._amax_rowwise,
+                                  R, C, torch.bfloat16)
+        two_d = bool(getattr(q, "with_2d_quantization", False))
+        _, _, _, cd, cs, ac = ops.quantize_nvfp4(hp, rowwise=False, columnwise=True, with_rht=False, with_2d=two_d)
+        self._columnwise_data, self._columnwise_scale_inv, self._amax_columnwise = cd, cs, ac
+        self._columnwise_rht = False
+
     def _dequantize_impl(self, dtype=None):
         dtype = dtype or self._dtype
         R, C = self._rows_cols()
@@ -121,6 +139,92 @@ class NVFP4Tensor(NVFP4TensorStorage, QuantizedTensor):
                 (self._rowwise_data, self._rowwise_scale_inv, self._columnwise_data, self._columnwise_scale_inv,
                  self._amax_rowwise, self._amax_columnwise, self._fp4_dtype, self._dtype, self._shape,
                  self._columnwise_rht))
+
+
+    # ---- FSDP2 (``fully_shard``): the parameter is cut along its rows into whole 128-row scale tiles; a piece
+    # carries the row-wise bytes, its slice of the tile-major E4M3 scales and the tensor amax (shared: one decode
+    # scale per tensor).  Same structural ops as the MXFP8 tensor; anything else takes the generic (dequantizing)
+    # path and the parameter is then sharded in high precision.
+    def _alias(self, shape, data, scales) -> "NVFP4Tensor":
+        return NVFP4Tensor(shape=shape, dtype=self._dtype, rowwise_data=data, rowwise_scale_inv=scales,
+                           columnwise_data=None, columnwise_scale_inv=None, amax_rowwise=self._amax_rowwise,
+                           amax_columnwise=None, fp4_dtype=self._fp4_dtype, quantizer=self._quantizer)
+
+    def _row_piece(self, r0: int, r1: int) -> "NVFP4Tensor":
+        R, C = self._rows_cols()
+        per_tile = self._rowwise_scale_inv.numel() // ((R + 127) // 128)
+        data = self._rowwise_data.reshape(R, C // 2)[r0:r1]
+        sc = self._rowwise_scale_inv.reshape(-1)[(r0 // 128) * per_tile:((r1 + 127) // 128) * per_tile]
+        return self._alias((r1 - r0, C), data, sc)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        aten = torch.ops.aten
+        t = args[0] if args else None
+        if isinstance(t, NVFP4Tensor) and t._rowwise_data is not None and len(t._shape) == 2 \
+                and t._amax_rowwise is not None:
+            R, C = t._rows_cols()
+            if func == aten.split.Tensor and (args[2] if len(args) > 2 else kwargs.get("dim", 0)) == 0 \
+                    and isinstance(args[1], int) and args[1] % 128 == 0 and R % 128 == 0:
+                return tuple(t._row_piece(r, min(r + args[1], R)) for r in range(0, R, args[1]))
+            if func == aten.slice.Tensor:
+                dim = args[1] if len(args) > 1 else 0
+                start = args[2] if len(args) > 2 and args[2] is not None else 0
+                end = min(args[3], R) if len(args) > 3 and args[3] is not None else R
+                step = args[4] if len(args) > 4 else 1
+                if dim == 0 and step == 1 and start % 128 == 0 and (end % 128 == 0 or end == R) and end > start:
+                    return t._row_piece(start, end)
+            if func == aten.new_zeros.default and len(args[1]) == 2 and args[1][1] == C and args[1][0] % 128 == 0:
+                rows = args[1][0]
+                dev = kwargs.get("device") or t._rowwise_data.device
+                per_tile = t._rowwise_scale_inv.numel() // ((R + 127) // 128)
+                out = t._alias((rows, C), torch.zeros(rows, C // 2, dtype=torch.uint8, device=dev),
+                               torch.zeros(rows // 128 * per_tile, dtype=torch.uint8, device=dev))
+                out._amax_rowwise = t._amax_rowwise.clone().to(dev)
+                return out
+            if func == aten.view.default and tuple(args[1]) in ((-1,), (R * C,)):
+                # the flat alias that FSDP2 keeps of a sharded parameter: same buffers, never computed on
+                return t._alias((R * C,), t._rowwise_data, t._rowwise_scale_inv)
+            if func == aten.as_strided.default and tuple(args[1]) == (R, C) and tuple(args[2]) == (C, 1) \
+                    and not (len(args) > 3 and args[3]):
+                out = t._alias((R, C), t._rowwise_data, t._rowwise_scale_inv)
+                out._columnwise_data, out._columnwise_scale_inv = t._columnwise_data, t._columnwise_scale_inv
+                out._amax_columnwise, out._columnwise_rht = t._amax_columnwise, t._columnwise_rht
+                return out
+            if func == aten.copy_.default and isinstance(args[1], NVFP4Tensor) and args[1]._rowwise_data is not None \
+                    and tuple(args[1]._shape) == tuple(t._shape):
+                src = args[1]
+                t._rowwise_data.reshape(R, C // 2).copy_(src._rowwise_data.reshape(R, C // 2))
+                t._rowwise_scale_inv.reshape(-1).copy_(src._rowwise_scale_inv.reshape(-1))
+                t._amax_rowwise.copy_(src._amax_rowwise)
+                t._columnwise_data = t._columnwise_scale_inv = t._amax_columnwise = None
+                return t
+        return super().__torch_dispatch__(func, types, args, kwargs)
+
+    def fsdp_pre_all_gather(self, mesh=None, orig_size=None, contiguous_orig_stride=None, module=None, mp_policy=None):
+        assert self._rowwise_data is not None, "FSDP gathers the row-wise copy"
+        R, C = self._rows_cols()
+        assert R % 128 == 0, "NVFP4 parameter shards must hold a multiple of 128 rows"
+        q = self._quantizer
+        if mesh is not None and q is not None and not q.with_amax_reduction:
+            # one decode scale per tensor: re-quantizations of a shard (the optimizer's write-back) take the amax
+            # over all shards from now on
+            q.with_amax_reduction, q.amax_reduction_group = True, mesh.get_group(mesh.ndim - 1)
+        return ((self._rowwise_data.reshape(R, C // 2), self._rowwise_scale_inv.reshape(R // 128, -1)),
+                (self._amax_rowwise, self._fp4_dtype, self._dtype, self._quantizer))
+
+    def fsdp_post_all_gather(self, all_gather_outputs, metadata, param_dtype=None, *, out=None):
+        data, scales = all_gather_outputs
+        amax, fp4_dtype, dtype, quantizer = metadata
+        if out is not None:
+            out._rowwise_data, out._rowwise_scale_inv, out._amax_rowwise = data, scales.reshape(-1), amax
+            out._columnwise_data = out._columnwise_scale_inv = out._amax_columnwise = None
+            return None
+        full = NVFP4Tensor(shape=(data.shape[0], data.shape[1] * 2), dtype=dtype, rowwise_data=data,
+                           rowwise_scale_inv=scales.reshape(-1), columnwise_data=None, columnwise_scale_inv=None,
+                           amax_rowwise=amax, amax_columnwise=None, fp4_dtype=fp4_dtype, quantizer=quantizer)
+        return full, all_gather_outputs
 
 
 def _make_nvfp4_tensor_in_reduce_ex(rd, rs, cd, cs, ar, ac, fp4_dtype, dtype, shape, columnwise_rht=False):

@@ -37,7 +37,7 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     # development knobs; the defaults are the benchmarked configuration
     ap.add_argument("--config", default="llama8b", choices=["llama8b", "layer12288", "llama70b-nvfp4", "mixtral"],
-                    help="which BASELINE configuration to run (default: the Llama-3-8B-architecture step)")
+                    help="which benchmark configuration to run (default: the Llama-3-8B-architecture step)")
     ap.add_argument("--layers", type=int, default=0, help="0 = the configuration's layer count")
     ap.add_argument("--seq", type=int, default=0, help="0 = the configuration's sequence length")
     ap.add_argument("--recompute", type=int, default=-1, help="-1 auto, 0 off, 1 per-layer recompute")
@@ -144,7 +144,7 @@ def timed_loop(step_fn, steps, world, sampler_index=None):
 
 
 def build_case(args, rank, world):
-    """Model, optimizer and data of the selected BASELINE configuration.
+    """Model, optimizer and data of the selected benchmark configuration.
 
     Returns a dict with ``step(tokens) -> loss`` (one full training iteration), the pinned host batches, the
     tokens processed per step over all ranks, FLOPs per token and the description for the JSON line."""

@@ -199,3 +199,13 @@ def test_fp8_attention_flags_are_refused_not_ignored():
             dpa(q, q, q)
     with te.autocast(enabled=True, recipe=R.DelayedScaling()):
         assert dpa(q, q, q).shape == (1, 4, 16)
+
+
+def test_attention_backend_report():
+    from transformerengine_b200.attention.utils import AttentionParams, get_attention_backend
+    backend, why = get_attention_backend(AttentionParams())
+    if not torch.cuda.is_available():
+        assert backend == "reference_math" and any("oracle" in w for w in why)
+    backend, why = get_attention_backend(AttentionParams(device="cpu", head_dim=64, attention_dropout=0.1))
+    assert backend == "reference_math" and why
+    assert any("FP8" in w for w in get_attention_backend(AttentionParams(fp8=True))[1])

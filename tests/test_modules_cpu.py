@@ -624,3 +624,64 @@ def test_layernorm_mlp_clamped_swiglu_and_glu():
         te.LayerNormMLP(32, 64, activation="swiglu", activation_params=dict(limit=1.0), device="cpu")
     with pytest.raises(ValueError):
         te.LayerNormMLP(32, 64, activation="clamped_swiglu", activation_params=dict(beta=1.0), device="cpu")
+
+
+@pytest.mark.parametrize("kind", ["LayerNorm", "RMSNorm", "Linear", "LayerNormLinear", "LayerNormMLP", "GroupedLinear",
+                                  "MultiheadAttention", "TransformerLayer"])
+def test_deferred_init_on_the_meta_device(kind):
+    """``device="meta"`` builds a module without memory; ``reset_parameters()`` materialises and initialises it
+    (test model: the reference's ``tests/pytorch/test_deferred_init.py``)."""
+    import copy
+    import pickle
+    args, kw = {"LayerNorm": ((64,), {}), "RMSNorm": ((64,), {}), "Linear": ((64, 128), dict(bias=True)),
+                "LayerNormLinear": ((64, 128), dict(bias=True)), "LayerNormMLP": ((64, 128), dict(bias=True)),
+                "GroupedLinear": ((2, 64, 64), dict(bias=True)),
+                "MultiheadAttention": ((64, 4), dict(fuse_qkv_params=True)),
+                "TransformerLayer": ((64, 128, 4), dict(fuse_qkv_params=False, hidden_dropout=0.0,
+                                                        attention_dropout=0.0))}[kind]
+    cls = getattr(te, kind)
+    init = lambda t: torch.nn.init.normal_(t, 0.0, 0.5)  # noqa: E731
+    if kind not in ("LayerNorm", "RMSNorm"):
+        kw = dict(kw, init_method=init)
+    m = cls(*args, params_dtype=torch.float32, device="meta", **kw)
+    assert all(p.device.type == "meta" for p in m.parameters())
+    for sub in m.modules():
+        if hasattr(sub, "reset_parameters"):
+            sub.reset_parameters()
+    assert all(p.device.type != "meta" for p in m.parameters()), [n for n, p in m.named_parameters() if p.is_meta]
+    for name, p in m.named_parameters():
+        if "layer_norm_weight" in name or name.endswith("norm.weight") or (kind in ("LayerNorm", "RMSNorm") and name == "weight"):
+            assert (p == 1).all(), name
+        elif "bias" in name:
+            assert (p == 0).all(), name
+        elif "weight" in name and p.dim() == 2 and "proj" not in name and "fc2" not in name:
+            assert 0.4 < float(p.detach().std()) < 0.6, name
+    x = torch.randn(8, 2, 64) if kind in ("MultiheadAttention", "TransformerLayer") else torch.randn(16, 64)
+    y = m(x, [8, 8]) if kind == "GroupedLinear" else m(x)
+    assert torch.isfinite(y if isinstance(y, torch.Tensor) else y[0]).all()
+    # re-initialising a live module keeps the statistics; copies and pickles still work
+    stats = {n: (float(p.detach().mean()), float(p.detach().std())) for n, p in m.named_parameters() if p.dim() == 2}
+    for sub in m.modules():
+        if hasattr(sub, "reset_parameters"):
+            sub.reset_parameters()
+    for n, p in m.named_parameters():
+        if p.dim() == 2:
+            assert abs(float(p.detach().std()) - stats[n][1]) < 0.1 * max(stats[n][1], 1e-3), n
+    copy.deepcopy(m)
+    pickle.loads(pickle.dumps(m))
+
+
+def test_deferred_init_with_quantized_parameters():
+    from transformerengine_b200.tensor.base import QuantizedTensorStorage
+    rec = R.MXFP8BlockScaling()
+    with te.quantized_model_init(enabled=True, recipe=rec):
+        lin = te.Linear(128, 128, bias=False, params_dtype=torch.float32, device="meta")
+    assert lin.weight.is_meta
+    lin.reset_parameters()
+    assert isinstance(lin.weight, QuantizedTensorStorage) and not lin.weight.is_meta
+    assert 0.015 < float(lin.weight.dequantize().std()) < 0.03
+    with te.autocast(enabled=True, recipe=rec):
+        assert torch.isfinite(lin(torch.randn(32, 128))).all()
+    before = lin.weight.dequantize().clone()
+    lin.reset_parameters()                     # a quantized parameter is re-drawn and re-quantized in place
+    assert not torch.equal(before, lin.weight.dequantize())

@@ -184,13 +184,70 @@ class TransformerEngineBaseModule(torch.nn.Module):
             raise NotImplementedError(f"recipe.backward_override={self.backward_override()!r} is implemented by "
                                       f"Linear, LayerNormLinear and LayerNormMLP, not by {type(self).__name__}")
 
+    def __getstate__(self):
+        # the initialisers are closures (not picklable); a module restored from a pickle keeps its values and can
+        # not be re-initialised
+        state = self.__dict__.copy()
+        state.pop("_init_fns", None)
+        return state
+
+    # ------------------------------------------------------------------ deferred initialisation
+    def _param_init_fns(self) -> Dict[str, Any]:
+        """``{parameter name: in-place initialiser}`` of this module's parameters (set by the constructors)."""
+        return getattr(self, "_init_fns", {})
+
+    def reset_parameters(self, defer_init: bool = False) -> None:
+        """(Re-)initialise the parameters.  Parameters that were created on the ``meta`` device (``device="meta"``:
+        construction without memory, as FSDP and checkpoint loaders want) are materialised first, on the GPU when
+        there is one; the weights then get the module's ``init_method``, biases zeros, norm weights their identity
+        value, and parameters created under ``quantized_model_init`` are quantized from the fresh values.
+        (Reference: ``module/base.py`` ``reset_parameters``.)"""
+        if defer_init:
+            return
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        for name, fn in self._param_init_fns().items():
+            p = getattr(self, name, None)
+            if p is None:
+                continue
+            if isinstance(p, QuantizedTensorStorage):
+                hp = torch.empty(tuple(p.shape), dtype=p.dtype, device=p.device)
+                with torch.no_grad():
+                    fn(hp)
+                    p.quantize_(hp)
+                continue
+            if p.device.type == "meta":
+                new = torch.nn.Parameter(torch.empty(tuple(p.shape), dtype=p.dtype, device=dev),
+                                         requires_grad=p.requires_grad)
+                for attr in ("tensor_model_parallel", "partition_dim", "partition_stride", "sequence_parallel"):
+                    if hasattr(p, attr):
+                        setattr(new, attr, getattr(p, attr))
+                self.register_parameter(name, new)
+                p = new
+            with torch.no_grad():
+                fn(p)
+        if hasattr(self, "_fused_weight_storage"):
+            views = [getattr(self, n) for n in getattr(self, "weight_names", [])]
+            st = self._fused_weight_storage
+            if st is not None and (st.device.type == "meta" or any(v.device != st.device for v in views)):
+                self._fused_weight_storage = None      # the materialised parameters are separate tensors now
+        pending = getattr(self, "_deferred_quantize", None)
+        if pending:
+            self._deferred_quantize = None
+            self._quantize_primary_weights(pending)
+        self._weight_cache.clear()
+
     def _quantize_primary_weights(self, weight_names) -> None:
         """``quantized_model_init``: replace the named high-precision weights by quantized parameters (both copies,
         so that forward, dgrad and wgrad read the parameter's own payload).  The quantizers come from a recipe state
         of their own: they describe how the PARAMETER is stored, whatever recipe later forward passes run under."""
         from ..quantization import RecipeState
 
-        recipe = FP8GlobalStateManager.FP8_MODEL_INIT_RECIPE
+        if any(getattr(self, n).device.type == "meta" for n in weight_names):
+            # nothing to quantize yet: done by reset_parameters once the weights exist
+            self._deferred_quantize = list(weight_names)
+            self._model_init_recipe = FP8GlobalStateManager.FP8_MODEL_INIT_RECIPE
+            return
+        recipe = getattr(self, "_model_init_recipe", None) or FP8GlobalStateManager.FP8_MODEL_INIT_RECIPE
         st = RecipeState.create(recipe, mode="forward", num_quantizers=3, device=self._param_device())
         self._primary_state = st
         q = st.make_quantizers()[1]

@@ -270,6 +270,9 @@ class GroupedLinear(TransformerEngineBaseModule):
             if bias:
                 self.register_parameter(f"bias{i}", torch.nn.Parameter(
                     torch.zeros(out_features, device=device, dtype=params_dtype)))
+        self._init_fns = {f"weight{i}": init_method for i in range(num_gemms)}
+        if bias:
+            self._init_fns.update({f"bias{i}": torch.nn.init.zeros_ for i in range(num_gemms)})
         if self.primary_weights_in_fp8:
             self._quantize_primary_weights([f"weight{i}" for i in range(num_gemms)])
             self._stacked = None

@@ -59,7 +59,18 @@ class _NormBase(torch.nn.Module):
             if p is not None:
                 setattr(p, "sequence_parallel", sequence_parallel)
 
-    def reset_parameters(self) -> None:
+    def reset_parameters(self, defer_init: bool = False) -> None:
+        """Norm weights to their identity value (0 with ``zero_centered_gamma``), bias to 0; parameters created on
+        the ``meta`` device are materialised first."""
+        if defer_init:
+            return
+        dev = "cuda" if torch.cuda.is_available() else "cpu"
+        for name in ("weight", "bias"):
+            p = getattr(self, name)
+            if p is not None and p.device.type == "meta":
+                new = torch.nn.Parameter(torch.empty(tuple(p.shape), dtype=p.dtype, device=dev))
+                setattr(new, "sequence_parallel", getattr(p, "sequence_parallel", False))
+                self.register_parameter(name, new)
         with torch.no_grad():
             self.weight.fill_(0.0 if self.zero_centered_gamma else 1.0)
             if self.bias is not None:
@@ -286,6 +297,19 @@ class LayerNormLinear(TransformerEngineBaseModule):
                 self.register_parameter(f"{n}bias", bp)
             off += s
         self._fused_weight_storage = wt if len(names) > 1 else None
+
+        def init_w(w, f=init_method):
+            if get_rng_state_tracker is not None and parallel_mode is not None:
+                with get_rng_state_tracker().fork():
+                    return f(w)
+            return f(w)
+
+        self._init_fns = {"layer_norm_weight": torch.nn.init.zeros_ if zero_centered_gamma else torch.nn.init.ones_}
+        if normalization == "LayerNorm":
+            self._init_fns["layer_norm_bias"] = torch.nn.init.zeros_
+        self._init_fns.update({n: init_w for n in self.weight_names})
+        if bias:
+            self._init_fns.update({n: torch.nn.init.zeros_ for n in self.bias_names})
         if self.primary_weights_in_fp8:
             self._quantize_primary_weights(self.weight_names)
             self._fused_weight_storage = None

@@ -246,6 +246,20 @@ class LayerNormMLP(TransformerEngineBaseModule):
                     setattr(self.fc2_bias, "sequence_parallel", True)
         else:
             self.fc1_bias = self.fc2_bias = None
+        def init_with(f):
+            def run(w):
+                if get_rng_state_tracker is not None and set_parallel_mode:
+                    with get_rng_state_tracker().fork():
+                        return f(w)
+                return f(w)
+            return run
+
+        self._init_fns = {"layer_norm_weight": torch.nn.init.zeros_ if zero_centered_gamma else torch.nn.init.ones_,
+                          "fc1_weight": init_with(init_method), "fc2_weight": init_with(output_layer_init_method)}
+        if normalization == "LayerNorm":
+            self._init_fns["layer_norm_bias"] = torch.nn.init.zeros_
+        if bias:
+            self._init_fns.update(fc1_bias=torch.nn.init.zeros_, fc2_bias=torch.nn.init.zeros_)
         if self.primary_weights_in_fp8:
             self._quantize_primary_weights(("fc1_weight", "fc2_weight"))
         mode1 = "column" if set_parallel_mode else None

@@ -239,6 +239,17 @@ class Linear(TransformerEngineBaseModule):
             off += s
         self._fused_weight_storage = weight_tensor if len(names) > 1 else None
         self._fused_bias_storage = bias_tensor if (len(names) > 1 and bias) else None
+        tracker, tracker_name = get_rng_state_tracker, rng_tracker_name
+
+        def init_w(w, f=init_method):
+            if tracker is not None and parallel_mode is not None:
+                with (tracker().fork(tracker_name) if tracker_name else tracker().fork()):
+                    return f(w)
+            return f(w)
+
+        self._init_fns = {n: init_w for n in self.weight_names}
+        if bias:
+            self._init_fns.update({n: torch.nn.init.zeros_ for n in self.bias_names})
         if self.primary_weights_in_fp8:
             self._quantize_primary_weights(self.weight_names)
             self._fused_weight_storage = None

@@ -263,3 +263,45 @@ def test_nvfp4_four_over_six_recipe_and_quantizer_rebuild_on_recipe_change():
         err(R.NVFP4BlockScaling(row_scaled_activation=True))
     with pytest.raises(AssertionError):
         R.NVFP4BlockScaling(nvfp4_4over6="some")
+
+
+@pytest.mark.parametrize("shape", [(64, 64), (256, 288), (320, 96)])
+def test_mxfp8_2d_quantization(shape):
+    """32 x 32 block scales: the row-wise scale is constant over the 32 rows of a block, the column-wise copy is
+    the transpose of the row-wise one, and the values are those of a per-block reference
+    (test model: the reference's ``tests/pytorch/test_mxfp8_2d_quantize.py``)."""
+    import transformerengine_b200 as te
+    from transformerengine_b200.common import recipe as R
+    from transformerengine_b200.ops.ref import quant as Q
+    from transformerengine_b200.tensor.mxfp8 import MXFP8Quantizer
+    torch.manual_seed(0)
+    rows, cols = shape
+    x = (torch.randn(rows, cols) * torch.rand(rows, 1) * 4).to(torch.bfloat16).float()
+    q = MXFP8Quantizer(with_2d_quantization=True)(x)
+    rs = Q.unswizzle_scales(q._rowwise_scale_inv, rows, cols // 32)
+    cs = Q.unswizzle_scales(q._columnwise_scale_inv, cols, rows // 32)
+    assert torch.equal(rs.reshape(rows // 32, 32, -1), rs[::32][:, None].expand(-1, 32, -1))
+    assert torch.equal(cs.reshape(cols // 32, 32, -1), cs[::32][:, None].expand(-1, 32, -1))
+    assert torch.equal(rs[::32], cs[::32].t())
+    assert torch.equal(q._columnwise_data, q._rowwise_data.reshape(rows, cols).t())
+    # per-block reference: scale 2^ceil(log2(amax / 448)), values rounded to E4M3
+    blocks = x.reshape(rows // 32, 32, cols // 32, 32)
+    amax = blocks.abs().amax(dim=(1, 3))
+    scale_inv = torch.exp2(torch.ceil(torch.log2(amax / 448.0)))
+    want = (blocks / scale_inv[:, None, :, None]).to(torch.float8_e4m3fn).float() * scale_inv[:, None, :, None]
+    torch.testing.assert_close(q.dequantize(), want.reshape(rows, cols), rtol=0, atol=0)
+    col_only = MXFP8Quantizer(with_2d_quantization=True, rowwise=False)(x)
+    torch.testing.assert_close(col_only.dequantize(), q.dequantize(), rtol=0, atol=0)
+    if shape == (64, 64):
+        lin = te.Linear(64, 64, bias=False, params_dtype=torch.float32, device="cpu")
+        with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling(enable_2d_quantization=True)):
+            y = lin(x.requires_grad_())
+        qs = lin.quantizers["scaling_fwd"]
+        assert qs[1].with_2d_quantization and not qs[0].with_2d_quantization
+        wd = MXFP8Quantizer(with_2d_quantization=True)(lin.weight.detach()).dequantize()
+        xd = MXFP8Quantizer()(x.detach()).dequantize()
+        torch.testing.assert_close(y, xd @ wd.t(), rtol=1e-5, atol=1e-5)
+        y.sum().backward()
+        # dgrad reads the column-wise copy of the weight: with 2-D blocks it is the same matrix
+        go = MXFP8Quantizer(torch.float8_e4m3fn)(torch.ones(64, 64)).dequantize()
+        torch.testing.assert_close(x.grad, go @ wd, rtol=1e-5, atol=1e-5)

@@ -120,9 +120,16 @@ def dequantize_fp8(data_u8, scale_inv, fp8_dtype, out_dtype):
 
 
 # ----------------------------------------------------------------------------- MXFP8
-def quantize_mxfp8(x2d, fp8_dtype, rowwise=True, columnwise=True):
-    """Returns (row_data u8 [R,C], row_scales swizzled, col_data_t u8 [C,R], col_scales swizzled)."""
+def quantize_mxfp8(x2d, fp8_dtype, rowwise=True, columnwise=True, two_d: bool = False):
+    """Returns (row_data u8 [R,C], row_scales swizzled, col_data_t u8 [C,R], col_scales swizzled).
+    ``two_d``: one scale per 32 x 32 block (weights; tensor operations on any device, used once per weight
+    update), else per 1 x 32 block along each direction (the fused kernel on a GPU)."""
     R, C = x2d.shape
+    if two_d:
+        xr = x2d.to(torch.bfloat16).float()
+        rd, rs, cd, cs = Q.quantize_mxfp8_2d(xr, fp8_dtype, rowwise, columnwise)
+        return (rd.view(torch.uint8) if rd is not None else None, Q.swizzle_scales(rs) if rs is not None else None,
+                cd.view(torch.uint8) if cd is not None else None, Q.swizzle_scales(cs) if cs is not None else None)
     if _ext.use_cuda(x2d):
         if x2d.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             x2d = x2d.float()

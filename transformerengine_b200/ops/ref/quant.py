@@ -127,6 +127,25 @@ def quantize_mxfp8_rowwise(x2d: torch.Tensor, dtype: torch.dtype) -> Tuple[torch
     return q, e
 
 
+def quantize_mxfp8_2d(x2d: torch.Tensor, dtype: torch.dtype, rowwise: bool = True, columnwise: bool = True):
+    """MXFP8 with one scale per 32 x 32 block (weights): the row-wise scales repeat over the 32 rows of a block,
+    the column-wise ones over its 32 columns, so both copies hold the SAME values (the column-wise data is the
+    transpose of the row-wise data) in the ordinary MXFP8 layout.  Returns the tuple of ``quantize_mxfp8``.
+    (Reference: ``MXFP8Quantizer(with_2d_quantization=True)``, ``MXFP8BlockScaling(enable_2d_quantization=True)``.)"""
+    R, C = x2d.shape
+    assert R % MX_BLOCK == 0 and C % MX_BLOCK == 0, f"2-D MXFP8 blocks need both dims to be multiples of 32, got {R}x{C}"
+    m = fp8_max(dtype)
+    xb = x2d.float().reshape(R // MX_BLOCK, MX_BLOCK, C // MX_BLOCK, MX_BLOCK)
+    e = float_to_e8m0(xb.abs().amax(dim=(1, 3)) * (1.0 / m))                   # [R/32, C/32]
+    q = torch.clamp(xb * e8m0_rcp(e)[:, None, :, None], -m, m).to(dtype).reshape(R, C)
+    rd = rs = cd = cs = None
+    if rowwise:
+        rd, rs = q, e.repeat_interleave(MX_BLOCK, dim=0)                         # [R, C/32]
+    if columnwise:
+        cd, cs = q.t().contiguous(), e.t().contiguous().repeat_interleave(MX_BLOCK, dim=0)   # [C, R], [C, R/32]
+    return rd, rs, cd, cs
+
+
 def quantize_mxfp8(
     x2d: torch.Tensor, dtype: torch.dtype, rowwise: bool = True, columnwise: bool = True
 ):

@@ -214,7 +214,11 @@ class Float8CurrentScalingRecipeState(RecipeState):
 
 class MXFP8BlockScalingRecipeState(RecipeState):
     def make_quantizers(self):
-        return [MXFP8Quantizer(self.dtype) for _ in range(self.num_quantizers)]
+        # enable_2d_quantization: weights (slot 1 of every forward GEMM) use 32 x 32 blocks, so that their row-wise
+        # and column-wise copies hold the same values
+        two_d = self.mode == "forward" and getattr(self.recipe, "enable_2d_quantization", False)
+        return [MXFP8Quantizer(self.dtype, with_2d_quantization=two_d and i % 3 == 1)
+                for i in range(self.num_quantizers)]
 
 
 class Float8BlockScalingRecipeState(RecipeState):

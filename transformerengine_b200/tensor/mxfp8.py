@@ -226,9 +226,12 @@ def _make_mxfp8_tensor_in_reduce_ex(rowwise_data, rowwise_scale_inv, columnwise_
 
 
 class MXFP8Quantizer(Quantizer):
-    def __init__(self, fp8_dtype: torch.dtype = torch.float8_e4m3fn, *, rowwise=True, columnwise=True):
+    def __init__(self, fp8_dtype: torch.dtype = torch.float8_e4m3fn, *, rowwise=True, columnwise=True,
+                 with_2d_quantization: bool = False):
         super().__init__(rowwise=rowwise, columnwise=columnwise)
         self.dtype = fp8_dtype
+        # one scale per 32 x 32 block instead of per 1 x 32: both copies then hold the same values (weights)
+        self.with_2d_quantization = bool(with_2d_quantization)
 
     def is_quantizable(self, inp):
         if inp.dim() < 2:
@@ -276,7 +279,7 @@ class MXFP8Quantizer(Quantizer):
         shape = tuple(tensor.shape)
         x2d = tensor.reshape(-1, shape[-1])
         rd, rs, cd, cs = ops.quantize_mxfp8(x2d, self.dtype, rowwise=self.rowwise_usage,
-                                            columnwise=self.columnwise_usage)
+                                            columnwise=self.columnwise_usage, two_d=self.with_2d_quantization)
         if rd is not None:
             rd = rd.reshape(shape)
         return self._wrap(rd, rs, cd, cs, shape, dtype or tensor.dtype)
@@ -285,7 +288,8 @@ class MXFP8Quantizer(Quantizer):
         shape = tuple(dst._shape)
         rd, rs, cd, cs = ops.quantize_mxfp8(src.reshape(-1, shape[-1]), self.dtype,
                                             rowwise=dst._rowwise_data is not None,
-                                            columnwise=dst._columnwise_data is not None)
+                                            columnwise=dst._columnwise_data is not None,
+                                            two_d=self.with_2d_quantization)
         if rd is not None:
             dst._rowwise_data.copy_(rd.reshape(shape))
             dst._rowwise_scale_inv.copy_(rs)

@@ -66,7 +66,8 @@ class MXFP8TensorStorage(QuantizedTensorStorage):
             return
         hp = ops.dequantize_mxfp8(self._rowwise_data.reshape(R, C), self._rowwise_scale_inv, self._fp8_dtype,
                                   torch.bfloat16)
-        _, _, cd, cs = ops.quantize_mxfp8(hp, self._fp8_dtype, rowwise=False, columnwise=True)
+        two_d = bool(getattr(self._quantizer, "with_2d_quantization", False))    # then the rebuilt copy is exact
+        _, _, cd, cs = ops.quantize_mxfp8(hp, self._fp8_dtype, rowwise=False, columnwise=True, two_d=two_d)
         self._columnwise_data, self._columnwise_scale_inv = cd, cs
 
     def _dequantize_impl(self, dtype=None):

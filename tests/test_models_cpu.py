@@ -306,3 +306,32 @@ def test_relative_position_buckets():
     assert (uni[:-1] >= uni[1:]).all()                     # monotone in the distance
     bi = relative_position_bucket(rel, True, 8, 16)
     assert bi[rel < 0].max() < 4 <= bi[rel > 0].min()      # half of the buckets per direction
+
+
+def test_layers_inside_a_hugging_face_pretrained_model(tmp_path):
+    """A ``transformers.PreTrainedModel`` that contains this library's layers saves (safetensors) and loads back
+    (test model: the reference's ``tests/pytorch/test_hf_integration.py``)."""
+    import transformerengine_b200 as te
+    from transformers.configuration_utils import PretrainedConfig
+    from transformers.modeling_utils import PreTrainedModel
+
+    class SimpleModel(PreTrainedModel):
+        config_class = PretrainedConfig
+
+        def __init__(self, config):
+            super().__init__(config)
+            self.my_layer = te.TransformerLayer(hidden_size=64, num_attention_heads=4, ffn_hidden_size=128,
+                                                layer_number=None, device="cpu", params_dtype=torch.float32,
+                                                hidden_dropout=0.0, attention_dropout=0.0)
+            self.post_init()
+
+        def forward(self, hidden_states, attention_mask=None):
+            return self.my_layer(hidden_states, attention_mask)
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        model = SimpleModel(PretrainedConfig()).eval()
+        model.save_pretrained(tmp_path / "simple_model")
+        again = SimpleModel.from_pretrained(tmp_path / "simple_model").eval()
+    x = torch.randn(8, 2, 64)
+    assert torch.equal(model(x), again(x))

@@ -196,3 +196,60 @@ def test_thd_ring_attention_matches_per_sequence_attention(world, causal):
     for rank, err, tb in results:
         assert tb is None, f"rank {rank} failed:\n{tb}"
         assert err < 1e-4, f"rank {rank}: max error {err}"
+
+
+def _cp_utils_worker(rank, world, port, q):
+    import os
+    import torch.distributed as dist
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        import transformerengine_b200 as te
+        cu = torch.tensor([0, 5, 12, 14])
+        ids = torch.arange(100, 114)
+        labels = torch.arange(14)
+        f = 2 * world
+        ids_p, lab_p, cu_p = te.pad_thd_sequences_for_cp(ids[None], labels[None], cu, f)
+        pos = te.generate_positional_ids_for_cp(cu, f)
+        mine = te.get_batch_on_this_cp_rank(cu_p, ids_p, lab_p, pos, dist.group.WORLD)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, tuple(t.tolist() for t in mine))
+        q.put((rank, ids_p.tolist(), lab_p.tolist(), cu_p.tolist(), pos.tolist(), gathered, None))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, None, None, None, None, None, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_packed_batch_helpers_reference_call_forms():
+    """Pad a packed batch for context parallelism, number its positions, cut it into the ranks' dual chunks."""
+    import socket
+    import torch.multiprocessing as mp
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_cp_utils_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+    for r in res:
+        assert r[-1] is None, r[-1]
+    _, ids_p, lab_p, cu_p, pos, gathered, _ = res[0]
+    assert cu_p == [0, 8, 16, 20]                                  # 5 -> 8, 7 -> 8, 2 -> 4
+    assert ids_p[:8] == [100, 101, 102, 103, 104, 0, 0, 0] and lab_p[5:8] == [-100] * 3
+    assert pos == list(range(8)) + list(range(8)) + list(range(4))
+    # rank r owns chunk r and chunk 2 * cp - 1 - r of every padded sequence; together they are the whole batch
+    r0, r1 = gathered
+    assert r0[2] == [0, 1, 6, 7, 0, 1, 6, 7, 0, 3] and r1[2] == [2, 3, 4, 5, 2, 3, 4, 5, 1, 2]
+    assert sorted(r0[0] + r1[0]) == sorted(ids_p)
+    # this library's own call forms still work
+    import transformerengine_b200 as te
+    assert te.pad_thd_sequences_for_cp(torch.tensor([0, 5, 12, 14]), 2).tolist() == [0, 8, 16, 20]
+    assert te.get_batch_on_this_cp_rank(torch.arange(8)[None], 2, 0).tolist() == [[0, 1, 6, 7]]

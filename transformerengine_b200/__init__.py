@@ -43,7 +43,8 @@ from .cpu_offload import get_cpu_offload_context
 from .export import onnx_export, is_in_onnx_export_mode
 from .cross_entropy import parallel_cross_entropy
 from .newton_schulz import newton_schulz, CusolverMpCtx
-from .parallel.context_parallel import get_batch_on_this_cp_rank, pad_thd_sequences_for_cp
+from .parallel.context_parallel import (get_batch_on_this_cp_rank, pad_thd_sequences_for_cp,  # noqa: F401
+                                        generate_positional_ids_for_cp)
 
 # names that reference code imports from the top level of the package
 from . import constants  # noqa: F401

@@ -29,8 +29,16 @@ def dual_chunk_positions(s_local: int, cp_size: int, cp_rank: int, device=None) 
     return torch.cat([a + cp_rank * half, a + (2 * cp_size - 1 - cp_rank) * half])
 
 
-def get_batch_on_this_cp_rank(x: torch.Tensor, cp_size: int, cp_rank: int, seq_dim: int = 1) -> torch.Tensor:
-    """Slice a full-sequence tensor to the two chunks owned by ``cp_rank``."""
+def get_batch_on_this_cp_rank(x: torch.Tensor, cp_size=None, cp_rank=None, seq_dim=1, cp_group=None,
+                              qvk_format: str = "thd"):
+    """Slice a full-sequence tensor to the two chunks owned by ``cp_rank``: ``(x, cp_size, cp_rank, seq_dim)``.
+
+    Reference call form for packed batches, ``(cu_seqlens_padded, input_ids_padded, labels_padded,
+    position_ids_padded, cp_group=None, qvk_format="thd")``: every sequence (padded to a multiple of ``2 * cp``)
+    gives this rank its chunk ``r`` and its chunk ``2 * cp - 1 - r``; returns the three sliced tensors."""
+    if isinstance(cp_size, torch.Tensor) or (cp_size is None and cp_rank is None):
+        return _thd_batch_on_this_cp_rank(x, cp_size, cp_rank, seq_dim if isinstance(seq_dim, torch.Tensor) else None,
+                                          cp_group, qvk_format)
     if cp_size == 1:
         return x
     chunks = x.chunk(2 * cp_size, dim=seq_dim)
@@ -48,14 +56,80 @@ def _natural_order_index(half: int, cp_size: int, device=None) -> torch.Tensor:
     return torch.cat([a + slot[c] * half for c in range(2 * cp_size)])
 
 
-def pad_thd_sequences_for_cp(cu_seqlens: torch.Tensor, cp_size: int) -> torch.Tensor:
-    """Cumulative lengths after padding every sequence to a multiple of ``2*cp``."""
+def _thd_batch_on_this_cp_rank(cu_seqlens_padded, input_ids, labels, position_ids, cp_group, qvk_format):
+    if qvk_format not in ("thd", "bshd", "sbhd"):
+        raise ValueError(f"Unsupported qvk_format: {qvk_format}!")
+    if qvk_format != "thd":
+        raise ValueError(f"Support not implemented yet for qvk_format: {qvk_format}!")
+    cp = dist.get_world_size(cp_group) if dist.is_initialized() else 1
+    if cp == 1:
+        return input_ids, labels, position_ids
+    rank = dist.get_rank(cp_group)
+    total = int(cu_seqlens_padded[-1])
+    starts = cu_seqlens_padded[:-1].tolist()
+    sizes = ((cu_seqlens_padded[1:] - cu_seqlens_padded[:-1]) // (2 * cp)).tolist()
+    pieces = []
+    for st, n in zip(starts, sizes):
+        pieces.append(torch.arange(st + rank * n, st + (rank + 1) * n))
+        pieces.append(torch.arange(st + (2 * cp - 1 - rank) * n, st + (2 * cp - rank) * n))
+    idx = torch.cat(pieces)
+
+    def cut(t):
+        if t is None:
+            return None
+        if t.dim() == 1:
+            dim = 0
+        elif t.shape[1] == total:
+            dim = 1
+        elif t.shape[0] == total:
+            dim = 0
+        else:
+            raise ValueError("Make sure the inputs are in THD format and padded correctly.")
+        if t.shape[dim] != total:
+            raise ValueError("the tensor's token dimension does not match cu_seqlens_padded[-1]")
+        return t.index_select(dim, idx.to(t.device))
+
+    return cut(input_ids), cut(labels), cut(position_ids)
+
+
+def generate_positional_ids_for_cp(cu_seqlens: torch.Tensor, divisibility_factor: int,
+                                   dtype: torch.dtype = torch.long) -> torch.Tensor:
+    """Position ids of a packed batch whose sequences are padded to multiples of ``divisibility_factor``: every
+    sequence counts from 0 through its padding."""
+    lens = (cu_seqlens[1:] - cu_seqlens[:-1]).tolist()
+    f = divisibility_factor
+    return torch.cat([torch.arange(-(-n // f) * f, dtype=dtype) for n in lens])
+
+
+def pad_thd_sequences_for_cp(cu_seqlens: torch.Tensor, cp_size=None, *rest, **kw):
+    """Cumulative lengths after padding every sequence to a multiple of ``2*cp``: ``(cu_seqlens, cp_size)``.
+
+    Reference call form ``(input_ids, labels, cu_seqlens, divisibility_factor, padding_token_id=0,
+    padding_label_id=-100)``: pads the packed tokens and labels themselves and returns
+    ``(input_ids_padded, labels_padded, cu_seqlens_padded)``."""
+    if isinstance(cp_size, torch.Tensor):
+        return _pad_thd_tokens(cu_seqlens, cp_size, *rest, **kw)
     lens = cu_seqlens[1:] - cu_seqlens[:-1]
     m = 2 * cp_size
     padded = (lens + m - 1) // m * m
     out = torch.zeros_like(cu_seqlens)
     out[1:] = padded.cumsum(0)
     return out
+
+
+def _pad_thd_tokens(input_ids, labels, cu_seqlens, divisibility_factor, padding_token_id: int = 0,
+                    padding_label_id: int = -100):
+    ids = input_ids.squeeze(0) if input_ids.dim() == 2 else input_ids
+    lab = labels.squeeze(0) if labels.dim() == 2 else labels
+    f = divisibility_factor
+    bounds = cu_seqlens.tolist()
+    out_ids, out_lab, new_cu = [], [], [0]
+    for a, b in zip(bounds[:-1], bounds[1:]):
+        pad = -(-(b - a) // f) * f - (b - a)
+        out_ids += [ids[a:b], ids.new_full((pad,), padding_token_id)]
+        out_lab += [lab[a:b], lab.new_full((pad,), padding_label_id)]
+        new_cu.append(new_cu[-1] + b - a + pad)
+    return torch.cat(out_ids), torch.cat(out_lab), torch.tensor(new_cu, dtype=cu_seqlens.dtype, device=cu_seqlens.device)
 
 
 # --------------------------------------------------------------------------- block attention with explicit backward

@@ -6,14 +6,54 @@ import torch
 import torch.distributed as dist
 
 from .constants import dist_group_type  # noqa: F401
-from .parallel.distributed import (CudaRNGStatesTracker, allreduce, allreduce_sequence_parallel_grads,  # noqa: F401
-                                   checkpoint, gather_along_first_dim, gather_quantized_along_first_dim,
+from .parallel.distributed import (CudaRNGStatesTracker, allreduce_sequence_parallel_grads,  # noqa: F401
+                                   checkpoint, gather_quantized_along_first_dim,
                                    get_all_rng_states, in_checkpoint_forward, is_in_recompute,
-                                   reduce_scatter_along_first_dim, set_all_rng_states,
-                                   set_tensor_model_parallel_attributes)
+                                   set_all_rng_states, set_tensor_model_parallel_attributes)
 from .parallel import distributed as _impl
 from .parallel.distributed import get_rank as get_distributed_rank  # noqa: F401
 from .parallel.distributed import get_world_size as get_distributed_world_size  # noqa: F401
+
+
+def gather_along_first_dim(inp, process_group=None, async_op: bool = False, quantizer=None, output_tensor=None,
+                           external_coalescing: bool = False, group=None):
+    """All-gather along dim 0; returns ``(tensor, handle)``.  With ``quantizer`` (or a quantized ``inp``) the
+    QUANTIZED payload travels: the input is quantized first and the result is a quantized tensor of the gathered
+    shape (row-wise copy; formats that need it rebuild their column-wise copy from the gathered rows)."""
+    from .tensor.base import QuantizedTensorStorage
+    g = process_group if process_group is not None else group
+    if external_coalescing:
+        raise NotImplementedError("external_coalescing: issue the gathers inside torch.distributed's own coalescing "
+                                  "manager instead")
+    if quantizer is not None or isinstance(inp, QuantizedTensorStorage):
+        q = inp if isinstance(inp, QuantizedTensorStorage) else quantizer(inp)
+        return gather_quantized_along_first_dim(q, g), None
+    out, handle = _impl.gather_along_first_dim(inp, g, async_op=async_op)
+    if output_tensor is not None:
+        if handle is not None:
+            handle.wait()
+            handle = None
+        output_tensor.copy_(out)
+        out = output_tensor
+    return out, handle
+
+
+def reduce_scatter_along_first_dim(inp, tp_group=None, async_op: bool = False, output=None, group=None):
+    """Reduce-scatter along dim 0; returns ``(tensor, handle)``."""
+    out, handle = _impl.reduce_scatter_along_first_dim(inp, tp_group if tp_group is not None else group,
+                                                      async_op=async_op)
+    if output is not None:
+        if handle is not None:
+            handle.wait()
+            handle = None
+        output.copy_(out)
+        out = output
+    return out, handle
+
+
+def allreduce(inp, tp_group=None, async_op: bool = False, group=None):
+    """All-reduce (sum); returns ``(tensor, handle)``."""
+    return _impl.allreduce(inp, tp_group if tp_group is not None else group, async_op=async_op)
 
 
 def is_fp8_activation_recompute_enabled() -> bool:

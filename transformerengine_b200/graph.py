@@ -303,7 +303,11 @@ def make_graphed_callables(modules: Union[Callable, Sequence[Callable]], sample_
                            calibrating: bool = False, recipe=None, amax_reduction_group=None,
                            cache_quantized_params: bool = False, pool=None, fp8_enabled: Optional[bool] = None,
                            fp8_recipe=None, fp8_weight_caching: Optional[bool] = None, _order=None,
-                           retain_graph_in_backward: bool = False):
+                           retain_graph_in_backward: bool = False, fp8_calibrating: Optional[bool] = None,
+                           fp8_group=None, pre_warmup_hook: Optional[Callable] = None,
+                           post_warmup_hook: Optional[Callable] = None, _num_layers_per_chunk=None,
+                           _reuse_graph_input_output_buffers: bool = False, clone_param_grads_on_return: bool = False,
+                           capture_time_hooks=None):
     """Graph one callable or a tuple of callables (``sample_args`` then holds one tuple per callable).
 
     ``_order`` (a pipeline schedule such as ``[1, 2, 1, 2, -2, -1, -2, -1]``: ``+c`` = forward of chunk ``c``'s
@@ -318,7 +322,13 @@ def make_graphed_callables(modules: Union[Callable, Sequence[Callable]], sample_
             return make_graphed_callables(modules, sample_args, num_warmup_iters, allow_unused_input, sample_kwargs,
                                           enabled, calibrating, recipe, amax_reduction_group, cache_quantized_params,
                                           pool, fp8_enabled, fp8_recipe, fp8_weight_caching, _order,
-                                          retain_graph_in_backward)
+                                          retain_graph_in_backward, fp8_calibrating=fp8_calibrating,
+                                          fp8_group=fp8_group, pre_warmup_hook=pre_warmup_hook,
+                                          post_warmup_hook=post_warmup_hook,
+                                          _num_layers_per_chunk=_num_layers_per_chunk,
+                                          _reuse_graph_input_output_buffers=_reuse_graph_input_output_buffers,
+                                          clone_param_grads_on_return=clone_param_grads_on_return,
+                                          capture_time_hooks=capture_time_hooks)
         finally:
             set_capture_end()
     if fp8_enabled is not None:
@@ -327,6 +337,16 @@ def make_graphed_callables(modules: Union[Callable, Sequence[Callable]], sample_
         recipe = fp8_recipe
     if fp8_weight_caching is not None:
         cache_quantized_params = fp8_weight_caching
+    if fp8_calibrating is not None:
+        calibrating = fp8_calibrating
+    if fp8_group is not None:
+        amax_reduction_group = fp8_group
+    for opt, val in (("_num_layers_per_chunk", _num_layers_per_chunk),
+                     ("_reuse_graph_input_output_buffers", _reuse_graph_input_output_buffers),
+                     ("clone_param_grads_on_return", clone_param_grads_on_return),
+                     ("capture_time_hooks", capture_time_hooks)):
+        if val:
+            raise NotImplementedError(f"make_graphed_callables({opt}=...) is not implemented")
     if calibrating:
         raise NotImplementedError("calibration runs eagerly: graph the callables after calibrating")
     if retain_graph_in_backward:
@@ -378,12 +398,16 @@ def make_graphed_callables(modules: Union[Callable, Sequence[Callable]], sample_
     # first real step do not depend on how many warm-up runs were made
     te_mods = [m for u in units for m in u.te_mods]
     saved = _save_delayed_state(te_mods)
+    if pre_warmup_hook is not None:
+        pre_warmup_hook()
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
         for u in units:
             u.warmup(num_warmup_iters)
     torch.cuda.current_stream().wait_stream(side)
+    if post_warmup_hook is not None:
+        post_warmup_hook()
     _restore_delayed_state(saved)
     FP8GlobalStateManager._pending = {"forward": [], "backward": []}
     for kind, u in schedule:

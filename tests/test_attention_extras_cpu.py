@@ -209,3 +209,19 @@ def test_attention_backend_report():
     backend, why = get_attention_backend(AttentionParams(device="cpu", head_dim=64, attention_dropout=0.1))
     assert backend == "reference_math" and why
     assert any("FP8" in w for w in get_attention_backend(AttentionParams(fp8=True))[1])
+
+
+def test_attention_backend_logging(caplog):
+    import logging
+    from transformerengine_b200.utils import config as C
+    dpa = te.DotProductAttention(2, 8, attention_dropout=0.0, qkv_format="bshd", layer_number=3)
+    q = torch.randn(1, 4, 2, 8)
+    with C.override(debug=True, debug_level=1), caplog.at_level(logging.DEBUG, logger="DotProductAttention"):
+        dpa(q, q, q)
+        dpa(q, q, q)                        # the same configuration is reported once
+    lines = [r.getMessage() for r in caplog.records if r.name == "DotProductAttention"]
+    assert sum("layer 3" in ln for ln in lines) == 1 and any("reference_math" in ln for ln in lines)
+    caplog.clear()
+    with caplog.at_level(logging.DEBUG, logger="DotProductAttention"):
+        dpa(q, q, q)
+    assert not [r for r in caplog.records if r.name == "DotProductAttention"]

@@ -16,6 +16,7 @@ import sys
 from .. import ops
 from ..ops import flash
 from ..parallel import distributed as D
+from ..utils.config import get_config
 
 _MASK_TYPES = ("no_mask", "padding", "causal", "padding_causal", "causal_bottom_right",
                "padding_causal_bottom_right", "arbitrary")
@@ -156,8 +157,43 @@ class DotProductAttention(torch.nn.Module):
             out = inference_params.unpack_output(out)
         return out
 
+    _logged: set = set()
+
+    def _log_backend(self, q, k, v, fmt, mask_type, window, attention_mask, bias_type, score) -> None:
+        """``NVTE_DEBUG=1``: one log line per distinct configuration (every call with ``NVTE_DEBUG_LEVEL=2``) naming
+        the path taken; level 1 adds the reasons (reference: ``AttentionLogging`` in
+        ``attention/dot_product_attention/utils.py``)."""
+        import logging
+
+        from .utils import AttentionParams, get_attention_backend
+        cfg = get_config()
+        thd = fmt == "thd"
+        p = AttentionParams(
+            qkv_dtype=q.dtype, qkv_format=fmt, num_heads=q.shape[-2], num_gqa_groups=k.shape[-2], head_dim=q.shape[-1],
+            head_dim_v=v.shape[-1], max_seqlen_q=q.shape[0] if thd else q.shape[0 if fmt == "sbhd" else 1],
+            max_seqlen_kv=k.shape[0] if thd else k.shape[0 if fmt == "sbhd" else 1], attn_mask_type=mask_type,
+            window_size=window, core_attention_bias_type=bias_type, attention_dropout=self.attention_dropout,
+            softmax_type=self.softmax_type, has_attention_mask=attention_mask is not None,
+            score_mod=score[0] is not None,
+            context_parallel=self.cp_group is not None and D.get_world_size(self.cp_group) > 1,
+            cp_comm_type=self.cp_comm_type, is_training=self.training, device=q.device.type)
+        key = (p.qkv_dtype, fmt, p.num_heads, p.num_gqa_groups, p.head_dim, mask_type, window, bias_type,
+               p.has_attention_mask, p.attention_dropout > 0 and p.is_training, p.softmax_type, p.device)
+        if cfg.debug_level < 2 and key in DotProductAttention._logged:
+            return
+        DotProductAttention._logged.add(key)
+        backend, why = get_attention_backend(p)
+        log = logging.getLogger("DotProductAttention")
+        log.info("layer %s: %s (format %s, heads %d/%d, head dim %d, mask %s)", self.layer_number, backend, fmt,
+                 p.num_heads, p.num_gqa_groups, p.head_dim, mask_type)
+        if cfg.debug_level >= 1:
+            for w in why:
+                log.debug("  %s", w)
+
     def _core(self, q, k, v, fmt, mask_type, window, attention_mask, cu_q, cu_kv, bias_type, bias, alibi_slopes,
               thd_extra=(None, None, None, None), score=(None, None), bottom_right_diagonal=None):
+        if get_config().debug:
+            self._log_backend(q, k, v, fmt, mask_type, window, attention_mask, bias_type, score)
         if fmt == "thd":
             return self._thd(q, k, v, mask_type, window, cu_q, cu_kv, *thd_extra)
         # -> [b, h, s, d] views

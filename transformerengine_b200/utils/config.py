@@ -45,6 +45,10 @@ class Config:
         env="TEB200_COPY_CTAS", help="SMs that copy instead of computing in a fused collective GEMM (0: automatic)"))
     fused_qkv_rope: bool = field(default=True, metadata=dict(
         env="TEB200_FUSED_QKV_ROPE", help="rotate the query and key heads of a packed QKV projection with one launch"))
+    debug: bool = field(default=False, metadata=dict(
+        env="NVTE_DEBUG", help="log which attention path every configuration takes (logger 'DotProductAttention')"))
+    debug_level: int = field(default=0, metadata=dict(
+        env="NVTE_DEBUG_LEVEL", help="0: the chosen path; 1: also the conditions that ruled the others out; 2: every call"))
     # mirrored switches of the native kernels (read there at first launch)
     gemm_cta_pairs: bool = field(default=True, metadata=dict(
         env="TEB200_GEMM_2CTA", help="dense GEMMs on cta_group::2 pairs (0: single-CTA kernels)"))

@@ -101,7 +101,9 @@ class QuantizedTensorStorage:
     def clear(self) -> None:
         """Release the payload (the object stays, its buffers become empty tensors)."""
         for name, val in list(vars(self).items()):
-            if isinstance(val, torch.Tensor) and name.startswith("_"):
+            if isinstance(val, QuantizedTensorStorage):
+                val.clear()                      # per-direction children of a hybrid tensor
+            elif isinstance(val, torch.Tensor) and name.startswith("_"):
                 setattr(self, name, torch.empty(0, dtype=val.dtype, device=val.device))
 
 

@@ -104,15 +104,21 @@ def _hier_worker(rank, world, port, result_q):
         k = torch.randn(b, hk, s, d, dtype=torch.float64)
         v = torch.randn(b, hk, s, d, dtype=torch.float64)
         do = torch.randn(b, hq, s, d, dtype=torch.float64)
-        qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
-        ref = attention_ref(qf, kf, vf, causal=True)
-        ref.backward(do)
-        shard = lambda t: get_batch_on_this_cp_rank(t, world, rank, seq_dim=2).contiguous()  # noqa: E731
-        ql, kl, vl = (shard(t).clone().requires_grad_() for t in (q, k, v))
-        out = attn_forward_func_with_cp(ql, kl, vl, cp_group=groups, cp_comm_type="a2a+p2p", causal=True)
-        out.backward(shard(do))
-        errs = [(out - shard(ref.detach())).abs().max().item(), (ql.grad - shard(qf.grad)).abs().max().item(),
-                (kl.grad - shard(kf.grad)).abs().max().item(), (vl.grad - shard(vf.grad)).abs().max().item()]
+        errs = []
+        for causal, window in ((True, None), (False, None), (True, (12, 0))):
+            qf, kf, vf = (t.clone().requires_grad_() for t in (q, k, v))
+            ref = attention_ref(qf, kf, vf, causal=causal, window=window)
+            ref.backward(do)
+            if causal:      # dual-chunk shards
+                shard = lambda t: get_batch_on_this_cp_rank(t, world, rank, seq_dim=2).contiguous()  # noqa: E731
+            else:           # contiguous shards
+                shard = lambda t: t.chunk(world, dim=2)[rank].contiguous()  # noqa: E731
+            ql, kl, vl = (shard(t).clone().requires_grad_() for t in (q, k, v))
+            out = attn_forward_func_with_cp(ql, kl, vl, cp_group=groups, cp_comm_type="a2a+p2p", causal=causal,
+                                            window=window)
+            out.backward(shard(do))
+            errs += [(out - shard(ref.detach())).abs().max().item(), (ql.grad - shard(qf.grad)).abs().max().item(),
+                     (kl.grad - shard(kf.grad)).abs().max().item(), (vl.grad - shard(vf.grad)).abs().max().item()]
         result_q.put((rank, max(errs), None))
     except Exception:  # noqa: BLE001
         import traceback

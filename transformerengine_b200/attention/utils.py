@@ -70,8 +70,6 @@ def get_attention_backend(p: AttentionParams) -> Tuple[str, List[str]]:
         why.append("an explicit mask tensor runs the reference math (padding given as cu_seqlens stays on the kernels)")
     if p.score_mod:
         why.append("score_mod runs the reference math")
-    if p.context_parallel and p.cp_comm_type in ("a2a+p2p",):
-        why.append("hierarchical context parallelism runs fp32 block math")
     blockers = [w for w in why if "FP8" not in w]
     if not blockers and not p.fp8:
         if get_config().attention_backend == "library":

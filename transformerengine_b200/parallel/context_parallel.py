@@ -389,23 +389,37 @@ def attn_forward_func_with_cp(q, k, v, *, cp_group, cp_comm_type: str = "p2p", s
 
 
 def _hierarchical_cp(q, k, v, groups, scale, causal, window):
-    """Two-level context parallelism (reference ``context_parallel.py:5020``): Ulysses all-to-all
-    inside the first group (the NVLink island), ring attention across the second.  The global
-    context-parallel rank of a process is ``p2p_rank * a2a_size + a2a_rank``."""
+    """Two-level context parallelism (reference ``context_parallel.py:5020``): Ulysses all-to-all inside the first
+    group (the NVLink island), then attention across the second group.  The global context-parallel rank of a
+    process is ``p2p_rank * a2a_size + a2a_rank``.
+
+    After the all-to-all a process holds ``1 / a2a_size`` of the heads and the tokens of its whole island.  With
+    the causal dual-chunk layout those tokens are ``2 * a2a_size`` half-chunks which, put in the right order, are
+    exactly the two contiguous chunks that rank ``p2p_rank`` of a ``p2p_size``-way dual-chunk layout owns.  So the
+    second level is ordinary context-parallel attention over the outer group: the keys and values are gathered
+    across the islands and every query chunk runs as one causal call of the attention kernels (no s x s mask, no
+    fp32 block math)."""
     assert isinstance(groups, (list, tuple)) and len(groups) == 2, "a2a+p2p needs [a2a_group, p2p_group]"
     a2a_group, p2p_group = groups
-    A, P = dist.get_world_size(a2a_group), dist.get_world_size(p2p_group)
+    A = dist.get_world_size(a2a_group)
     s_l = q.shape[2]
     assert q.shape[1] % A == 0 and k.shape[1] % A == 0, "heads must divide by the all-to-all group size"
     qh, kh, vh = (_SeqToHeads.apply(t, a2a_group, True) for t in (q, k, v))
-
-    def positions(rp):  # tokens of ring rank rp after the all-to-all: the island's shards in rank order
-        if causal:
-            return torch.cat([dual_chunk_positions(s_l, A * P, rp * A + ra, q.device) for ra in range(A)])
-        return torch.cat([torch.arange(s_l, device=q.device) + (rp * A + ra) * s_l for ra in range(A)])
-
-    pos_table = torch.stack([positions(rp) for rp in range(P)])
-    oh = _RingAttention.apply(qh, kh, vh, p2p_group, None, scale, causal, window, pos_table)
+    if causal and A > 1:
+        # island member ra contributed chunk (rp * A + ra) then chunk (2 * A * P - 1 - rp * A - ra): first halves in
+        # member order, second halves in reverse member order
+        half = s_l // 2
+        a = torch.arange(half, device=q.device)
+        order = torch.cat([ra * s_l + a for ra in range(A)] + [ra * s_l + half + a for ra in reversed(range(A))])
+        inverse = torch.empty_like(order)
+        inverse[order] = torch.arange(order.numel(), device=order.device)
+        qh, kh, vh = (t.index_select(2, order) for t in (qh, kh, vh))
+    else:
+        inverse = None
+    oh = attn_forward_func_with_cp(qh, kh, vh, cp_group=p2p_group, cp_comm_type="all_gather", scale=scale,
+                                   causal=causal, window=window)
+    if inverse is not None:
+        oh = oh.index_select(2, inverse)
     return _SeqToHeads.apply(oh, a2a_group, False)
 
 

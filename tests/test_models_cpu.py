@@ -159,14 +159,19 @@ def _free_port():
     return p
 
 
-def _tp_worker(rank, world, port, sd, tokens, q):
+def _tp_worker(rank, world, port, sd, tokens, q, family="llama"):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
+        from transformerengine_b200.models.gemma import GemmaConfig, GemmaModel
         from transformerengine_b200.models.llama import LlamaConfig, LlamaModel
-        cfg = LlamaConfig(vocab_size=128, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2,
-                          ffn_hidden_size=128, rope_theta=10000.0, params_dtype=torch.float32)
-        m = LlamaModel(cfg, tp_group=dist.group.WORLD, device="cpu").eval()
+        base = dict(vocab_size=128, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, ffn_hidden_size=128,
+                    rope_theta=10000.0, params_dtype=torch.float32)
+        if family == "gemma":
+            m = GemmaModel(GemmaConfig(**base, head_dim=32, rms_eps=1e-6), tp_group=dist.group.WORLD, device="cpu").eval()
+            assert m.lm_head.weight is m.embedding.weight and m.embedding.weight.shape == (64, 64)
+        else:
+            m = LlamaModel(LlamaConfig(**base), tp_group=dist.group.WORLD, device="cpu").eval()
         hf.load_hf_llama(m, sd)
         with torch.no_grad():
             logits = m(tokens)                         # [s, b, vocab / tp]
@@ -178,10 +183,11 @@ def _tp_worker(rank, world, port, sd, tokens, q):
         dist.destroy_process_group()
 
 
-def test_checkpoint_loads_into_tensor_parallel_shards():
+@pytest.mark.parametrize("family", ["llama", "gemma"])
+def test_checkpoint_loads_into_tensor_parallel_shards(family):
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
-        ref = _hf_model("llama").eval()
+        ref = _hf_model(family).eval()
     _randomize(ref)
     tokens = torch.randint(0, 128, (2, 8))
     with torch.no_grad():
@@ -190,7 +196,7 @@ def test_checkpoint_loads_into_tensor_parallel_shards():
     ctx = mp.get_context("spawn")
     q = ctx.SimpleQueue()
     port = _free_port()
-    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, sd, tokens, q)) for r in range(2)]
+    procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, sd, tokens, q, family)) for r in range(2)]
     for p in procs:
         p.start()
     got = q.get()

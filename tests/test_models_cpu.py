@@ -167,6 +167,18 @@ def _tp_worker(rank, world, port, sd, tokens, q, family="llama"):
         from transformerengine_b200.models.llama import LlamaConfig, LlamaModel
         base = dict(vocab_size=128, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, ffn_hidden_size=128,
                     rope_theta=10000.0, params_dtype=torch.float32)
+        if family == "gpt2":
+            from transformerengine_b200.models.gpt import GPTConfig, GPTModel, load_hf_gpt2
+            m = GPTModel(GPTConfig(vocab_size=128, max_positions=64, hidden_size=64, num_layers=2, num_heads=4,
+                                   params_dtype=torch.float32), tp_group=dist.group.WORLD, device="cpu").eval()
+            load_hf_gpt2(m, sd)
+            with torch.no_grad():
+                logits = m(tokens)
+            parts = [torch.empty_like(logits) for _ in range(world)]
+            dist.all_gather(parts, logits)
+            if rank == 0:
+                q.put(torch.cat(parts, dim=-1))
+            return
         if family == "gemma":
             m = GemmaModel(GemmaConfig(**base, head_dim=32, rms_eps=1e-6), tp_group=dist.group.WORLD, device="cpu").eval()
             assert m.lm_head.weight is m.embedding.weight and m.embedding.weight.shape == (64, 64)
@@ -183,11 +195,18 @@ def _tp_worker(rank, world, port, sd, tokens, q, family="llama"):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("family", ["llama", "gemma"])
+@pytest.mark.parametrize("family", ["llama", "gemma", "gpt2"])
 def test_checkpoint_loads_into_tensor_parallel_shards(family):
     with warnings.catch_warnings():
         warnings.simplefilter("ignore")
-        ref = _hf_model(family).eval()
+        if family == "gpt2":
+            T = transformers
+            ref = T.GPT2LMHeadModel(T.GPT2Config(vocab_size=128, n_positions=64, n_embd=64, n_layer=2, n_head=4,
+                                                 attn_implementation="eager", resid_pdrop=0.0, embd_pdrop=0.0,
+                                                 attn_pdrop=0.0)).eval()
+            _perturb(ref, ("ln_", "bias"))
+        else:
+            ref = _hf_model(family).eval()
     _randomize(ref)
     tokens = torch.randint(0, 128, (2, 8))
     with torch.no_grad():

@@ -149,35 +149,51 @@ def gpt_config_from_hf(hf_config, **overrides) -> GPTConfig:
     return GPTConfig(**d)
 
 
-def convert_hf_gpt2_state_dict(hf_sd: Mapping[str, torch.Tensor], num_layers: int) -> Dict[str, torch.Tensor]:
-    """``transformers.GPT2LMHeadModel`` state dict -> ``GPTModel`` (unsharded).  GPT-2 stores its projections as
-    ``[in, out]`` (``Conv1D``); they are transposed to the ``[out, in]`` of this library's GEMMs."""
-    out = {"embedding.weight": hf_sd["transformer.wte.weight"], "lm_head.weight": hf_sd["transformer.wte.weight"],
+def convert_hf_gpt2_state_dict(hf_sd: Mapping[str, torch.Tensor], num_layers: int, tp_rank: int = 0,
+                               tp_size: int = 1) -> Dict[str, torch.Tensor]:
+    """``transformers.GPT2LMHeadModel`` state dict -> ``GPTModel`` (this rank's tensor-parallel shard).  GPT-2 stores
+    its projections as ``[in, out]`` (``Conv1D``); they are transposed to the ``[out, in]`` of this library's GEMMs.
+    Column-parallel matrices are cut along their output rows (q, k and v each on their own), row-parallel ones
+    along their input columns, the embedding table along the vocabulary; norms, positions and the biases of the
+    row-parallel layers are replicated."""
+    r, n = tp_rank, tp_size
+    rows = lambda w: w[r * (w.shape[0] // n):(r + 1) * (w.shape[0] // n)]           # noqa: E731
+    cols = lambda w: w[:, r * (w.shape[1] // n):(r + 1) * (w.shape[1] // n)]        # noqa: E731
+    wte = rows(hf_sd["transformer.wte.weight"])
+    out = {"embedding.weight": wte, "lm_head.weight": wte,
            "position_embedding.weight": hf_sd["transformer.wpe.weight"],
            "final_norm.weight": hf_sd["transformer.ln_f.weight"], "final_norm.bias": hf_sd["transformer.ln_f.bias"]}
     for i in range(num_layers):
         h, t = f"transformer.h.{i}.", f"layers.{i}."
+        qkv_w = hf_sd[h + "attn.c_attn.weight"].t()                     # [3h, h]: q rows, k rows, v rows
+        qkv_b = hf_sd[h + "attn.c_attn.bias"]
         out.update({
             t + "self_attention.layernorm_qkv.layer_norm_weight": hf_sd[h + "ln_1.weight"],
             t + "self_attention.layernorm_qkv.layer_norm_bias": hf_sd[h + "ln_1.bias"],
-            t + "self_attention.layernorm_qkv.weight": hf_sd[h + "attn.c_attn.weight"].t().contiguous(),
-            t + "self_attention.layernorm_qkv.bias": hf_sd[h + "attn.c_attn.bias"],
-            t + "self_attention.proj.weight": hf_sd[h + "attn.c_proj.weight"].t().contiguous(),
+            t + "self_attention.layernorm_qkv.weight": torch.cat([rows(p) for p in qkv_w.chunk(3, dim=0)]).contiguous(),
+            t + "self_attention.layernorm_qkv.bias": torch.cat([rows(p) for p in qkv_b.chunk(3, dim=0)]),
+            t + "self_attention.proj.weight": cols(hf_sd[h + "attn.c_proj.weight"].t()).contiguous(),
             t + "self_attention.proj.bias": hf_sd[h + "attn.c_proj.bias"],
             t + "layernorm_mlp.layer_norm_weight": hf_sd[h + "ln_2.weight"],
             t + "layernorm_mlp.layer_norm_bias": hf_sd[h + "ln_2.bias"],
-            t + "layernorm_mlp.fc1_weight": hf_sd[h + "mlp.c_fc.weight"].t().contiguous(),
-            t + "layernorm_mlp.fc1_bias": hf_sd[h + "mlp.c_fc.bias"],
-            t + "layernorm_mlp.fc2_weight": hf_sd[h + "mlp.c_proj.weight"].t().contiguous(),
+            t + "layernorm_mlp.fc1_weight": rows(hf_sd[h + "mlp.c_fc.weight"].t()).contiguous(),
+            t + "layernorm_mlp.fc1_bias": rows(hf_sd[h + "mlp.c_fc.bias"]),
+            t + "layernorm_mlp.fc2_weight": cols(hf_sd[h + "mlp.c_proj.weight"].t()).contiguous(),
             t + "layernorm_mlp.fc2_bias": hf_sd[h + "mlp.c_proj.bias"],
         })
     return out
 
 
-def gpt_from_hf(hf_model, device=None, **config_overrides) -> GPTModel:
+def load_hf_gpt2(model: GPTModel, hf_sd: Mapping[str, torch.Tensor]) -> None:
+    """Fill a ``GPTModel`` (tensor-parallel or not) from a ``transformers.GPT2LMHeadModel`` state dict."""
+    from .hf import _load
+    rank = D.get_rank(model.tp_group) if model.tp_size > 1 else 0
+    _load(model, convert_hf_gpt2_state_dict(hf_sd, model.cfg.num_layers, rank, model.tp_size))
+
+
+def gpt_from_hf(hf_model, tp_group=None, device=None, **config_overrides) -> GPTModel:
     """A ``GPTModel`` with the weights of a ``transformers.GPT2LMHeadModel`` (``activation_function`` must be the
     tanh GELU, ``gelu_new``, which is GPT-2's)."""
-    from .hf import _load
-    model = GPTModel(gpt_config_from_hf(hf_model.config, **config_overrides), device=device)
-    _load(model, convert_hf_gpt2_state_dict(hf_model.state_dict(), model.cfg.num_layers))
+    model = GPTModel(gpt_config_from_hf(hf_model.config, **config_overrides), tp_group=tp_group, device=device)
+    load_hf_gpt2(model, hf_model.state_dict())
     return model

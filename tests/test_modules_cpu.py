@@ -685,3 +685,29 @@ def test_deferred_init_with_quantized_parameters():
     before = lin.weight.dequantize().clone()
     lin.reset_parameters()                     # a quantized parameter is re-drawn and re-quantized in place
     assert not torch.equal(before, lin.weight.dequantize())
+
+
+@pytest.mark.parametrize("kind", ["Linear", "LayerNormLinear", "LayerNormMLP"])
+def test_delayed_weight_gradients(kind):
+    """``delay_wgrad_compute``: the backward pass returns the input gradient and postpones the weight-gradient
+    GEMMs until ``backward_dw()`` (zero-bubble pipeline schedules)."""
+    def build(delay):
+        torch.manual_seed(0)
+        kw = dict(params_dtype=torch.float32, device="cpu", delay_wgrad_compute=delay, bias=True)
+        return {"Linear": lambda: te.Linear(32, 48, **kw), "LayerNormLinear": lambda: te.LayerNormLinear(32, 48, **kw),
+                "LayerNormMLP": lambda: te.LayerNormMLP(32, 64, **kw)}[kind]()
+
+    a, b = build(True), build(False)
+    x = torch.randn(16, 32)
+    xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
+        ya, yb = a(xa), b(xb)
+    ya.square().sum().backward()
+    yb.square().sum().backward()
+    assert a.need_backward_dw() and not b.need_backward_dw()
+    assert torch.equal(xa.grad, xb.grad)
+    weights = [p for p in a.parameters() if p.dim() == 2]
+    assert all(p.grad is None for p in weights)
+    a.backward_dw()
+    for (n, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        torch.testing.assert_close(pa.grad, pb.grad, msg=n)

@@ -694,11 +694,11 @@ def test_delayed_weight_gradients(kind):
     def build(delay):
         torch.manual_seed(0)
         kw = dict(params_dtype=torch.float32, device="cpu", delay_wgrad_compute=delay, bias=True)
-        return {"Linear": lambda: te.Linear(32, 48, **kw), "LayerNormLinear": lambda: te.LayerNormLinear(32, 48, **kw),
+        return {"Linear": lambda: te.Linear(32, 64, **kw), "LayerNormLinear": lambda: te.LayerNormLinear(32, 64, **kw),
                 "LayerNormMLP": lambda: te.LayerNormMLP(32, 64, **kw)}[kind]()
 
     a, b = build(True), build(False)
-    x = torch.randn(16, 32)
+    x = torch.randn(32, 32)
     xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
     with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
         ya, yb = a(xa), b(xb)

@@ -74,10 +74,12 @@ def get_attention_backend(p: AttentionParams) -> Tuple[str, List[str]]:
     if not blockers and not p.fp8:
         if get_config().attention_backend == "library":
             return LIBRARY, ["attention_backend='library' was requested (A/B timing)"]
+        if get_config().attention_backend == "reference":
+            return REFERENCE, ["attention_backend='reference' was requested (numerics debugging)"]
         return FUSED, []
     windowed = p.window_size is not None and (p.window_size[0] >= 0 or p.window_size[1] > 0)
     plain = not any(k in w for w in blockers for k in ("bias", "dropout", "softmax_type", "mask", "score_mod"))
     if plain and not windowed and p.qkv_format != "thd" and not p.context_parallel \
-            and p.qkv_dtype in (torch.bfloat16, torch.float16):
+            and p.qkv_dtype in (torch.bfloat16, torch.float16) and get_config().attention_backend != "reference":
         return LIBRARY, why
     return REFERENCE, why

@@ -81,7 +81,8 @@ _USE_LIBRARY_SDPA = True
 # csrc/attn (A/B timing)
 from ..utils.config import get_config as _get_config  # noqa: E402
 
-_USE_OWN_FLASH = _get_config().attention_backend != "library"
+_USE_OWN_FLASH = _get_config().attention_backend == "own"
+_USE_LIBRARY_SDPA = _get_config().attention_backend != "reference"
 
 
 def attention(q, k, v, *, scale=None, causal=False, window=None, attn_mask=None, bias=None, dropout_p=0.0,

@@ -27,7 +27,9 @@ def _env_bool(v: str) -> bool:
 class Config:
     # name of the environment variable and a help line live in the field metadata
     attention_backend: str = field(default="own", metadata=dict(
-        env="TEB200_ATTN", help="'own': tcgen05 attention kernels of this library; 'library': torch SDPA for A/B timing"))
+        env="TEB200_ATTN", help="'own': tcgen05 attention kernels of this library; 'library': torch SDPA for A/B "
+                                "timing; 'reference': fp32 reference math everywhere (numerics debugging; also chosen "
+                                "by NVTE_FUSED_ATTN=0 together with NVTE_FLASH_ATTN=0)"))
     fused_context_parallel: bool = field(default=True, metadata=dict(
         env="TEB200_FUSED_CP", help="attention kernels read peer K/V over NVLink instead of an NCCL ring"))
     fused_ep: bool = field(default=True, metadata=dict(
@@ -77,12 +79,16 @@ class Config:
             else:
                 val = raw
             setattr(cfg, f.name, val)
+        # the reference's switches: with both of its fused backends off only its unfused PyTorch path is left
+        if environ.get("TEB200_ATTN") is None and environ.get("NVTE_FUSED_ATTN") == "0" \
+                and environ.get("NVTE_FLASH_ATTN") == "0":
+            cfg.attention_backend = "reference"
         cfg.validate()
         return cfg
 
     def validate(self) -> None:
-        if self.attention_backend not in ("own", "library"):
-            raise ValueError(f"attention_backend must be 'own' or 'library', got {self.attention_backend!r}")
+        if self.attention_backend not in ("own", "library", "reference"):
+            raise ValueError(f"attention_backend must be 'own', 'library' or 'reference', got {self.attention_backend!r}")
         if self.gemm_tile_n not in (0, 128, 256):
             raise ValueError("gemm_tile_n must be 0, 128 or 256")
         if self.wait_limit_cycles < 0:

@@ -367,7 +367,7 @@ def test_checkpoint_is_consistent_under_delayed_scaling(use_reentrant):
 
 def test_unimplemented_options_are_refused_not_ignored():
     import transformerengine_b200 as te
-
+        te.GroupedLinear(2, 16, 16, save_original_input=True, device="cpu")
     with pytest.raises(NotImplementedError):
         te.GroupedLinear(2, 16, 16, delay_wgrad_compute=True, device="cpu")
     with pytest.raises(NotImplementedError):
@@ -687,7 +687,7 @@ def test_deferred_init_with_quantized_parameters():
     assert not torch.equal(before, lin.weight.dequantize())
 
 
-@pytest.mark.parametrize("kind", ["Linear", "LayerNormLinear", "LayerNormMLP"])
+@pytest.mark.parametrize("kind", ["Linear", "LayerNormLinear", "LayerNormMLP", "GroupedLinear"])
 def test_delayed_weight_gradients(kind):
     """``delay_wgrad_compute``: the backward pass returns the input gradient and postpones the weight-gradient
     GEMMs until ``backward_dw()`` (zero-bubble pipeline schedules)."""
@@ -695,13 +695,15 @@ def test_delayed_weight_gradients(kind):
         torch.manual_seed(0)
         kw = dict(params_dtype=torch.float32, device="cpu", delay_wgrad_compute=delay, bias=True)
         return {"Linear": lambda: te.Linear(32, 64, **kw), "LayerNormLinear": lambda: te.LayerNormLinear(32, 64, **kw),
-                "LayerNormMLP": lambda: te.LayerNormMLP(32, 64, **kw)}[kind]()
+                "LayerNormMLP": lambda: te.LayerNormMLP(32, 64, **kw),
+                "GroupedLinear": lambda: te.GroupedLinear(2, 32, 64, **kw)}[kind]()
 
     a, b = build(True), build(False)
-    x = torch.randn(32, 32)
+    x = torch.randn(64, 32)
     xa, xb = x.clone().requires_grad_(), x.clone().requires_grad_()
+    extra = ([32, 32],) if kind == "GroupedLinear" else ()
     with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling()):
-        ya, yb = a(xa), b(xb)
+        ya, yb = a(xa, *extra), b(xb, *extra)
     ya.square().sum().backward()
     yb.square().sum().backward()
     assert a.need_backward_dw() and not b.need_backward_dw()

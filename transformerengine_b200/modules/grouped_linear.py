@@ -19,7 +19,7 @@ from ..quantization import FP8GlobalStateManager, get_align_size_for_quantizatio
 from ..tensor.base import QuantizedTensorStorage
 from ..tensor.mxfp8 import MXFP8Quantizer
 from . import _functional as F
-from .base import TransformerEngineBaseModule, get_default_init_method
+from .base import TransformerEngineBaseModule, WeightGradStore, get_default_init_method
 
 
 _OFFSET_CACHE: dict = {}
@@ -146,12 +146,9 @@ class _GroupedLinear(torch.autograd.Function):
                 if m_splits[g] == 0:
                     dws[g] = torch.zeros_like(weights[g])
                     continue
-                dws[g] = gemm_nt(contraction_slab(dy_col, offs[g], offs[g + 1]),
-                                 contraction_slab(x_col, offs[g], offs[g + 1]),
-                                 out_dtype=weights[g].dtype if weights[g].dtype != torch.float32 else torch.float32)
-                if module.fuse_wgrad_accumulation and hasattr(weights[g], "main_grad"):
-                    weights[g].main_grad.add_(dws[g].float())
-                    dws[g] = None
+                dws[g] = _wgrad(module, weights[g], lambda a=contraction_slab(dy_col, offs[g], offs[g + 1]),
+                                b=contraction_slab(x_col, offs[g], offs[g + 1]), w=weights[g]: gemm_nt(
+                                    a, b, out_dtype=w.dtype if w.dtype != torch.float32 else torch.float32))
             if ctx.reduce_bwd_amax:
                 FP8GlobalStateManager.reduce_and_update_fp8_tensors(forward=False)
             res = [dx.reshape(ctx.inp_shape), None, None, None] + dws
@@ -183,22 +180,40 @@ class _GroupedLinear(torch.autograd.Function):
                         xg = in_q(x_hp[sl])
                     else:
                         xg = in_q(ctx.xq[sl])
-                dws[g] = gemm_nt(as_operand(dyq, "columnwise"), as_operand(xg, "columnwise"),
-                                 out_dtype=weights[g].dtype if weights[g].dtype != torch.float32 else torch.float32)
+                dws[g] = _wgrad(module, weights[g], lambda a=as_operand(dyq, "columnwise"),
+                                b=as_operand(xg, "columnwise"), w=weights[g]: gemm_nt(
+                                    a, b, out_dtype=w.dtype if w.dtype != torch.float32 else torch.float32))
             else:
                 w = weights[g].to(adt)
                 gemm_nt(as_operand(dy[sl], "rowwise"), as_operand(w, "columnwise"), out=dx[sl])
-                dws[g] = gemm_nt(as_operand(dy[sl], "columnwise"), as_operand(ctx.xq[sl], "columnwise"),
-                                 out_dtype=weights[g].dtype)
-            if module.fuse_wgrad_accumulation and hasattr(weights[g], "main_grad"):
-                weights[g].main_grad.add_(dws[g].float())
-                dws[g] = None
+                dws[g] = _wgrad(module, weights[g], lambda a=as_operand(dy[sl], "columnwise"),
+                                b=as_operand(ctx.xq[sl], "columnwise"), w=weights[g]: gemm_nt(a, b, out_dtype=w.dtype))
         if ctx.fp8q and ctx.reduce_bwd_amax:
             FP8GlobalStateManager.reduce_and_update_fp8_tensors(forward=False)
         res = [dx.reshape(ctx.inp_shape), None, None, None] + dws
         if module.use_bias:
             res += dbs
         return tuple(res)
+
+
+def _wgrad(module, weight, compute):
+    """Run (or, with ``delay_wgrad_compute``, queue for ``backward_dw()``) one expert's weight-gradient GEMM;
+    with ``fuse_wgrad_accumulation`` the result goes into ``weight.main_grad`` and nothing is returned."""
+    def finish(dw):
+        if module.fuse_wgrad_accumulation and hasattr(weight, "main_grad"):
+            weight.main_grad.add_(dw.float())
+            return None
+        return dw
+
+    store = module.wgrad_store
+    if store is not None and store.delay_wgrad_compute():
+        def deferred():
+            dw = finish(compute())
+            if dw is not None:
+                weight.grad = dw if weight.grad is None else weight.grad + dw
+        store.put(deferred)
+        return None
+    return finish(compute())
 
 
 class GroupedLinear(TransformerEngineBaseModule):
@@ -234,7 +249,7 @@ class GroupedLinear(TransformerEngineBaseModule):
             raise TypeError(f"use_grouped_tensor must be a bool or None, got {type(use_grouped_tensor)}")
         self.use_grouped_tensor = True if use_grouped_tensor is None else use_grouped_tensor
         # options of the reference that this module does not implement are refused, not ignored
-        for opt, val in (("delay_wgrad_compute", delay_wgrad_compute), ("save_original_input", save_original_input),
+        for opt, val in (("save_original_input", save_original_input),
                          ("single_grouped_weight", single_grouped_weight), ("single_grouped_bias", single_grouped_bias)):
             if val:
                 raise NotImplementedError(f"GroupedLinear({opt}=True) is not implemented")
@@ -244,6 +259,7 @@ class GroupedLinear(TransformerEngineBaseModule):
         if device is None:
             device = "cuda" if torch.cuda.is_available() else "cpu"
         self.num_gemms = num_gemms
+        self.wgrad_store = WeightGradStore(delay_wgrad_compute)
         self.use_bias, self.return_bias = bias, return_bias
         self.apply_bias = bias and not return_bias
         self.fuse_wgrad_accumulation = fuse_wgrad_accumulation

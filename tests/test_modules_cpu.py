@@ -367,9 +367,9 @@ def test_checkpoint_is_consistent_under_delayed_scaling(use_reentrant):
 
 def test_unimplemented_options_are_refused_not_ignored():
     import transformerengine_b200 as te
-        te.GroupedLinear(2, 16, 16, save_original_input=True, device="cpu")
+
     with pytest.raises(NotImplementedError):
-        te.GroupedLinear(2, 16, 16, delay_wgrad_compute=True, device="cpu")
+        te.GroupedLinear(2, 16, 16, save_original_input=True, device="cpu")
     with pytest.raises(NotImplementedError):
         te.LayerNormLinear(16, 16, return_layernorm_output_gathered=True, device="cpu")
     with pytest.raises(NotImplementedError):

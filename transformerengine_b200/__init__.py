@@ -35,7 +35,7 @@ from .ep import (ep_dispatch, ep_combine, ep_bootstrap, ep_finalize, ep_prepare,
 from .parallel.distributed import checkpoint, CudaRNGStatesTracker
 from .optim import FusedAdam, FusedSGD
 from .parallel.comm_gemm import initialize_ub, destroy_ub
-from . import optim as optimizers  # noqa: F401
+from . import optimizers  # noqa: F401  (the reference's package name; implementations in optim/)
 from . import fusible  # noqa: F401  (operation fuser: fusible.Sequential and the basic operations)
 from . import debug  # noqa: F401
 from .graph import make_graphed_callables

@@ -839,3 +839,43 @@ def test_utils_helpers():
     with U.get_nvtx_range_context("x"):
         pass
     assert U.all_close(torch.ones(2), torch.ones(2))
+
+
+def test_code_written_for_the_reference_runs_after_installing_the_alias():
+    """In a fresh interpreter: after ``install_as_transformer_engine()`` the reference's import lines resolve to
+    this package's modules (same objects), and a small training step written against them runs."""
+    import subprocess
+    import sys
+    code = r'''
+import transformerengine_b200.compat as compat
+compat.install_as_transformer_engine()
+import torch
+import transformer_engine
+import transformer_engine.pytorch as te
+from transformer_engine.common.recipe import DelayedScaling, Format
+from transformer_engine.common import recipe
+from transformer_engine.pytorch.distributed import checkpoint, CudaRNGStatesTracker
+from transformer_engine.pytorch.module.linear import Linear
+from transformer_engine.pytorch.tensor.float8_tensor import Float8Tensor
+from transformer_engine.pytorch.optimizers import FusedAdam
+from transformer_engine.pytorch.attention.inference import InferenceParams
+import transformerengine_b200 as ours
+assert te is ours and Linear is ours.Linear and recipe.DelayedScaling is DelayedScaling
+assert te.Float8Tensor is Float8Tensor
+layer = te.TransformerLayer(64, 128, 4, hidden_dropout=0.0, attention_dropout=0.0, params_dtype=torch.float32, device="cpu")
+opt = FusedAdam(layer.parameters(), lr=1e-3)
+x = torch.randn(8, 2, 64, requires_grad=True)
+with te.fp8_autocast(enabled=True, fp8_recipe=DelayedScaling(fp8_format=Format.HYBRID, amax_history_len=4)):
+    y = checkpoint(layer, x)
+y.square().mean().backward()
+opt.step()
+try:
+    import transformer_engine_torch
+    raise SystemExit("the compiled extension of the reference must not resolve")
+except ImportError:
+    pass
+print("ALIAS-OK")
+'''
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                         cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert res.returncode == 0 and "ALIAS-OK" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]

@@ -79,3 +79,9 @@ def load_framework_extension(framework: str = "torch") -> None:
 
 
 __version__ = "0.1.0"
+
+from . import compat  # noqa: E402,F401
+import os as _os  # noqa: E402
+
+if _os.environ.get("TEB200_ALIAS_TRANSFORMER_ENGINE", "0") == "1":
+    compat.install_as_transformer_engine()

@@ -859,6 +859,9 @@ from transformer_engine.pytorch.module.linear import Linear
 from transformer_engine.pytorch.tensor.float8_tensor import Float8Tensor
 from transformer_engine.pytorch.optimizers import FusedAdam
 from transformer_engine.pytorch.attention.inference import InferenceParams
+from transformer_engine.pytorch.attention.dot_product_attention.utils import get_attention_backend
+import transformer_engine.pytorch.ops as te_ops
+assert te_ops.Sequential is ours.fusible.Sequential
 import transformerengine_b200 as ours
 assert te is ours and Linear is ours.Linear and recipe.DelayedScaling is DelayedScaling
 assert te.Float8Tensor is Float8Tensor

@@ -28,8 +28,21 @@ _OURS = "transformerengine_b200"
 _INSTALLED = [False]
 
 
+# reference modules whose counterpart here sits at another place
+_RENAMED = {
+    "transformer_engine.pytorch.attention.dot_product_attention.utils": _OURS + ".attention.utils",
+    "transformer_engine.pytorch.attention.dot_product_attention.context_parallel": _OURS + ".parallel.context_parallel",
+    "transformer_engine.pytorch.attention.dot_product_attention.dot_product_attention":
+        _OURS + ".attention.dot_product_attention",
+    "transformer_engine.pytorch.ops": _OURS + ".fusible",
+    "transformer_engine.pytorch.utils": _OURS + ".utils",
+}
+
+
 def _target(fullname: str):
     """Name of this package's module behind a ``transformer_engine...`` name, or None."""
+    if fullname in _RENAMED:
+        return _RENAMED[fullname]
     if fullname == "transformer_engine.pytorch":
         return _OURS
     if fullname.startswith("transformer_engine.pytorch."):
@@ -97,4 +110,8 @@ def install_as_transformer_engine() -> None:
     root.pytorch = importlib.import_module("transformer_engine.pytorch")
     root.common = importlib.import_module("transformer_engine.common")
     importlib.import_module("transformer_engine.common.recipe")
+    # names below a parent that is a plain module here (the reference's dot_product_attention is a package) cannot go
+    # through the finder: register them directly
+    for alias, target in _RENAMED.items():
+        sys.modules.setdefault(alias, importlib.import_module(target))
     _INSTALLED[0] = True

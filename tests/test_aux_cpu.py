@@ -861,9 +861,9 @@ from transformer_engine.pytorch.optimizers import FusedAdam
 from transformer_engine.pytorch.attention.inference import InferenceParams
 from transformer_engine.pytorch.attention.dot_product_attention.utils import get_attention_backend
 import transformer_engine.pytorch.ops as te_ops
-assert te_ops.Sequential is ours.fusible.Sequential
 import transformerengine_b200 as ours
 assert te is ours and Linear is ours.Linear and recipe.DelayedScaling is DelayedScaling
+assert te_ops.Sequential is ours.fusible.Sequential and callable(get_attention_backend)
 assert te.Float8Tensor is Float8Tensor
 layer = te.TransformerLayer(64, 128, 4, hidden_dropout=0.0, attention_dropout=0.0, params_dtype=torch.float32, device="cpu")
 opt = FusedAdam(layer.parameters(), lr=1e-3)

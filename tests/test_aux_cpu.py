@@ -882,3 +882,28 @@ print("ALIAS-OK")
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
                          cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert res.returncode == 0 and "ALIAS-OK" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
+
+
+def test_multi_tensor_ops_in_the_applier_convention():
+    from transformerengine_b200.optimizers import (MultiTensorApply, multi_tensor_applier, multi_tensor_l2norm,
+                                                   multi_tensor_scale, multi_tensor_scale_tensor,
+                                                   multi_tensor_unscale_l2norm)
+    torch.manual_seed(0)
+    grads = [torch.randn(5, 7), torch.randn(3), torch.randn(2, 2, 2)]
+    flag = torch.zeros(1, dtype=torch.int32)
+    total, each = multi_tensor_applier(multi_tensor_l2norm, flag, [grads], True)
+    want = torch.stack([g.norm() for g in grads])
+    torch.testing.assert_close(each, want)
+    torch.testing.assert_close(total, want.square().sum().sqrt().reshape(1))
+    total2, each2 = MultiTensorApply(2048 * 32)(multi_tensor_l2norm, flag, [grads], False)
+    assert each2.numel() == 0 and torch.equal(total2, total)
+    t3, _ = multi_tensor_applier(multi_tensor_unscale_l2norm, flag, [grads], torch.tensor(0.5), False)
+    torch.testing.assert_close(t3, total * 0.5)
+    out = [torch.empty_like(g) for g in grads]
+    multi_tensor_applier(multi_tensor_scale, flag, [grads, out], 0.25)
+    assert all(torch.allclose(o, g * 0.25) for o, g in zip(out, grads)) and int(flag) == 0
+    multi_tensor_applier(multi_tensor_scale_tensor, flag, [grads, out], torch.tensor(2.0))
+    assert all(torch.allclose(o, g * 2) for o, g in zip(out, grads))
+    bad = [torch.tensor([1.0, float("inf")])]
+    multi_tensor_applier(multi_tensor_scale, flag, [bad, [torch.empty(2)]], 1.0)
+    assert int(flag) == 1

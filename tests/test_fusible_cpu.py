@@ -228,3 +228,48 @@ def test_gated_unit_variants():
         ops.SiTUGLU(beta1=0.0)
     with pytest.raises(NotImplementedError):
         ops.GLU(glu_interleave_size=2)
+
+
+def test_user_registered_fusion_pass():
+    """A fusion pass of the user's own replaces [GELU, ConstantScale] by one module; it runs before the built-in
+    fusions when prepended, and the plan is rebuilt when the registry changes."""
+    from transformerengine_b200 import fusible as ops
+    calls = []
+
+    class GeluTimes(torch.nn.Module):
+        def __init__(self, scale):
+            super().__init__()
+            self.scale = scale
+
+        def forward(self, x):
+            return torch.nn.functional.gelu(x, approximate="tanh") * self.scale
+
+    def fuse_gelu_scale(oplist, *, recipe):
+        calls.append(recipe)
+        out, i = [], 0
+        while i < len(oplist):
+            if i + 1 < len(oplist) and isinstance(oplist[i], ops.GELU) and isinstance(oplist[i + 1], ops.ConstantScale):
+                out.append(GeluTimes(float(oplist[i + 1].scale)))
+                i += 2
+            else:
+                out.append(oplist[i])
+                i += 1
+        return out
+
+    seq = ops.Sequential(ops.Linear(16, 16, bias=False, device="cpu", dtype=torch.float32), ops.GELU(),
+                         ops.ConstantScale(3.0))
+    x = torch.randn(4, 16, requires_grad=True)
+    want = seq(x)
+    ops.register_forward_backward_fusion(fuse_gelu_scale, prepend=True)
+    try:
+        got = seq(x)
+        assert calls == [None] and any(isinstance(m, GeluTimes) for m in seq._get_plan())
+        torch.testing.assert_close(got, want)
+        got.sum().backward()
+        assert x.grad is not None
+    finally:
+        ops.unregister_fusion(fuse_gelu_scale)
+    assert not any(isinstance(m, GeluTimes) for m in seq._get_plan())
+    with pytest.raises(NotImplementedError):
+        ops.register_backward_fusion(fuse_gelu_scale)
+    assert ops.BasicOperation is ops.FusibleOperation

@@ -24,11 +24,21 @@ from .ops import (FusibleOperation, BasicLinear, Bias, Linear, LayerNorm, RMSNor
                   ScaledSwiGLU, GLU, QGEGLU, SReGLU, ClampedSwiGLU, SiTUGLU, ScaledSReLU, ScaledClampedQGeGLU,
                   ScaledSiTUGLU)
 from .fused import ForkNorm, GroupedMLP, LinearChain
-from .sequential import Sequential, fuse_operations
+from .sequential import (Sequential, fuse_operations, register_backward_fusion, register_forward_backward_fusion,
+                         register_forward_fusion, unregister_fusion)
+
+BasicOperation = FusibleOperation     # the reference's names of the operation base classes
+FusedOperation = FusibleOperation
+# The reference has one fused class per pattern and per pass; here one chain module covers the linear patterns in
+# both passes and one module the residual-fork + norm pattern.  The reference's class names point at them.
+ForwardLinearBiasActivation = ForwardLinearBiasAdd = ForwardLinearScaleAdd = LinearChain
+BackwardActivationBias = BackwardLinearAdd = BackwardLinearScale = LinearChain
+BackwardAddRMSNorm = ForkNorm
 
 __all__ = ["FusibleOperation", "BasicLinear", "Bias", "Linear", "LayerNorm", "RMSNorm", "GELU", "ReLU", "SiLU",
            "SwiGLU", "GEGLU", "ReGLU", "QGELU", "SReLU", "Quantize", "Identity", "Reshape", "ConstantScale",
            "Dropout", "AddExtraInput", "MakeExtraOutput", "AllReduce", "AllGather", "ReduceScatter",
            "L2Normalization", "GroupedLinear", "ScaledSwiGLU", "GLU", "QGEGLU", "SReGLU", "ClampedSwiGLU", "SiTUGLU",
-           "ScaledSReLU", "ScaledClampedQGeGLU", "ScaledSiTUGLU", "Sequential", "fuse_operations", "LinearChain", "ForkNorm",
+           "ScaledSReLU", "ScaledClampedQGeGLU", "ScaledSiTUGLU", "Sequential", "fuse_operations", "register_forward_fusion", "register_backward_fusion",
+           "register_forward_backward_fusion", "unregister_fusion", "BasicOperation", "FusedOperation", "LinearChain", "ForkNorm",
            "GroupedMLP"]

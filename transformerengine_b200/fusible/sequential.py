@@ -74,8 +74,55 @@ def _fuse_norm_mlp(norm, fc1, act, fc2) -> Callable:
     return m
 
 
+# user fusion passes: functions ``ops -> ops`` (reference: ``pytorch/ops/fuser.py`` register_*_fusion)
+_FUSIONS_FIRST: List[Callable] = []
+_FUSIONS_LAST: List[Callable] = []
+
+
+def register_forward_backward_fusion(op_fusion_func: Callable, prepend: bool = False) -> None:
+    """Register a fusion pass of your own: ``op_fusion_func(ops, *, recipe) -> updated ops`` receives the list of
+    operations of a ``Sequential`` and may replace runs of them by a module that does their work (``recipe`` is the
+    active quantization recipe or None).  A replacement is any ``torch.nn.Module`` called as
+    ``module(x, *extra_inputs)``; it declares ``num_extra_inputs`` / ``num_extra_outputs`` when it consumes or
+    produces extra tensors, and its backward is whatever autograd records for it.  ``prepend=True`` runs the pass
+    before the built-in fusions (so it sees the basic operations), the default after them."""
+    (_FUSIONS_FIRST if prepend else _FUSIONS_LAST).append(op_fusion_func)
+
+
+def register_forward_fusion(op_fusion_func: Callable, prepend: bool = False) -> None:
+    """Same registry as ``register_forward_backward_fusion``: a fused module here always carries both passes (its
+    backward is its autograd graph), so there is no separate forward-only pass."""
+    register_forward_backward_fusion(op_fusion_func, prepend)
+
+
+def register_backward_fusion(op_fusion_func: Callable, prepend: bool = False) -> None:
+    raise NotImplementedError("backward passes are not fused separately here: a fused module owns its backward "
+                              "through autograd; register the pair with register_forward_backward_fusion")
+
+
+def unregister_fusion(op_fusion_func: Callable) -> None:
+    for lst in (_FUSIONS_FIRST, _FUSIONS_LAST):
+        while op_fusion_func in lst:
+            lst.remove(op_fusion_func)
+
+
+def _active_recipe():
+    from ..quantization import FP8GlobalStateManager
+    return FP8GlobalStateManager.get_fp8_recipe() if FP8GlobalStateManager.is_fp8_enabled() else None
+
+
 def fuse_operations(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
-    """Greedy longest-match fusion of a list of basic operations."""
+    """Greedy longest-match fusion of a list of basic operations (user passes before and after the built-in one)."""
+    ops = list(ops)
+    for fn in _FUSIONS_FIRST:
+        ops = list(fn(ops, recipe=_active_recipe()))
+    ops = _builtin_fusions(ops)
+    for fn in _FUSIONS_LAST:
+        ops = list(fn(ops, recipe=_active_recipe()))
+    return ops
+
+
+def _builtin_fusions(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
     out: List[torch.nn.Module] = []
     i = 0
     while i < len(ops):
@@ -153,6 +200,7 @@ class Sequential(torch.nn.Module):
     def _get_plan(self) -> List[torch.nn.Module]:
         mods = list(self._modules.values())
         key = tuple(id(m) for m in mods)
+        key = key + (len(_FUSIONS_FIRST), len(_FUSIONS_LAST))
         if self._plan is None or key != self._plan_key:
             self._plan, self._plan_key = fuse_operations(mods), key
         return self._plan

@@ -186,19 +186,62 @@ def test_bottom_right_diagonal_and_packed_inputs():
         dpa(q, k, v, kv_layer=kv, qkv_interleave_dim=-2)
     with pytest.raises(ValueError):
         dpa(qkv_layer=qkv, qkv_interleave_dim=-1)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="autocast"):
         dpa(q, k, v, fp8_output=True)
 
 
-def test_fp8_attention_flags_are_refused_not_ignored():
+def _fp8_rt(t, dtype):
+    """Per-tensor FP8 rounding with the scale of the tensor's own amax (fp32 math)."""
+    f = t.float()
+    scale = torch.finfo(dtype).max / f.abs().max()
+    return ((f * scale).to(dtype).float() / scale).to(t.dtype)
+
+
+def test_fp8_attention_rounds_the_boundary_tensors():
+    """``recipe.fp8_dpa``: Q, K, V (and the output with ``fp8_mha`` / ``fp8_output``) are rounded to the forward FP8
+    format, the gradients dO and dQ / dK / dV to the gradient format; without the flags nothing changes."""
     from transformerengine_b200.common import recipe as R
-    dpa = te.DotProductAttention(2, 8, attention_dropout=0.0, qkv_format="bshd")
-    q = torch.randn(1, 4, 2, 8)
-    with te.autocast(enabled=True, recipe=R.DelayedScaling(fp8_dpa=True)):
-        with pytest.raises(NotImplementedError, match="fp8_dpa"):
-            dpa(q, q, q)
+    torch.manual_seed(0)
+    dpa = te.DotProductAttention(2, 8, attention_dropout=0.0, qkv_format="bshd", attn_mask_type="causal")
+    q, k, v = (torch.randn(2, 6, 2, 8, requires_grad=True) for _ in range(3))
+    go = torch.randn(2, 6, 16)
+    plain = dpa(q, k, v)
     with te.autocast(enabled=True, recipe=R.DelayedScaling()):
-        assert dpa(q, q, q).shape == (1, 4, 16)
+        assert torch.equal(dpa(q, k, v), plain)
+
+    def expected(quantize_out, bwd):
+        qq, kk, vv = (t.detach().clone().requires_grad_() for t in (q, k, v))
+        e4, e5 = torch.float8_e4m3fn, torch.float8_e5m2
+        ste = lambda t: _fp8_rt(t.detach(), e4) + (t - t.detach())  # noqa: E731  (straight-through rounding)
+        o = dpa(ste(qq), ste(kk), ste(vv))
+        out = _fp8_rt(o.detach(), e4) if quantize_out else o.detach()
+        o.backward(_fp8_rt(go, e5) if bwd else go)
+        grads = [(_fp8_rt(t.grad, e5) if bwd else t.grad) for t in (qq, kk, vv)]
+        return out, grads
+
+    for rec, kw, quantize_out, bwd in ((R.DelayedScaling(fp8_dpa=True), {}, False, True),
+                                       (R.Float8CurrentScaling(fp8_dpa=True, fp8_mha=True), {}, True, True),
+                                       (R.DelayedScaling(fp8_dpa=True), dict(fp8_output=True, bf16_backward=True),
+                                        True, False)):
+        for t in (q, k, v):
+            t.grad = None
+        with te.autocast(enabled=True, recipe=rec):
+            o = dpa(q, k, v, **kw)
+        o.backward(go)
+        want_o, want_g = expected(quantize_out, bwd)
+        torch.testing.assert_close(o, want_o, rtol=0, atol=1e-6)
+        for t, g in zip((q, k, v), want_g):
+            torch.testing.assert_close(t.grad, g, rtol=0, atol=1e-6)
+        assert not torch.equal(o, plain)
+    # MXFP8 recipes round with 1 x 32 block scales where the shape allows, else with the per-tensor scale
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling(fp8_dpa=True)):
+        o = dpa(q, k, v)
+    assert o.shape == plain.shape and torch.isfinite(o).all() and (o - plain).abs().max() < 0.2
+    big = te.DotProductAttention(2, 32, attention_dropout=0.0, qkv_format="bshd")
+    x = torch.randn(2, 8, 2, 32)
+    with te.autocast(enabled=True, recipe=R.MXFP8BlockScaling(fp8_dpa=True)):
+        o = big(x, x, x)
+    assert (o - big(x, x, x)).abs().max() < 0.2 and not torch.equal(o, big(x, x, x))
 
 
 def test_attention_backend_report():

@@ -107,16 +107,12 @@ class DotProductAttention(torch.nn.Module):
         ``s_q != s_kv`` (None: top-left for ``causal`` / ``padding_causal``, bottom-right otherwise; the causal
         mask types fix it).  ``qkv_layer`` / ``kv_layer``: one packed buffer holding q, k, v (or k, v) along
         ``qkv_interleave_dim`` (-3: ``...3hd``, -2: ``...h3d``) instead of separate tensors; the pieces are
-        zero-copy views.  ``bf16_backward`` and ``num_splits`` are accepted for compatibility (the backward
-        pass always runs in 16 bits; the kernels choose their own split of the key sequence)."""
-        if fp8_output:
-            raise NotImplementedError("fp8_output: the attention kernels write 16-bit outputs")
-        from ..quantization import FP8GlobalStateManager
-        if FP8GlobalStateManager.is_fp8_enabled():
-            rec = FP8GlobalStateManager.get_fp8_recipe()
-            if getattr(rec, "fp8_dpa", False) or getattr(rec, "fp8_mha", False):
-                raise NotImplementedError("recipe.fp8_dpa / fp8_mha: FP8 attention is not built; the attention "
-                                          "kernels take fp16 / bf16 (leave both flags False)")
+        zero-copy views.  Under a recipe with ``fp8_dpa`` / ``fp8_mha`` the tensors entering and leaving the
+        attention are rounded to FP8 (``attention/fp8_emulation.py``; the kernels stay 16-bit): ``fp8_output`` rounds
+        the output too, ``bf16_backward`` keeps the gradients unrounded.  ``num_splits`` is accepted for
+        compatibility (the kernels choose their own split of the key sequence)."""
+        from .fp8_emulation import plan as _fp8_plan
+        fp8 = _fp8_plan(fp8_output, bf16_backward)      # recipe.fp8_dpa / fp8_mha, fp8_output: FP8 rounding at the boundaries
         if qkv_layer is not None or kv_layer is not None:
             query_layer, key_layer, value_layer = _unpack_qkv(query_layer, key_layer, value_layer, qkv_layer,
                                                               kv_layer, qkv_interleave_dim, inference_params)
@@ -134,6 +130,8 @@ class DotProductAttention(torch.nn.Module):
             raise ValueError("pad_between_seqs=True needs cu_seqlens_q_padded / cu_seqlens_kv_padded")
         if (score_mod_bprop is not None or score_mod_bprop_tensors is not None) and score_mod is None:
             raise ValueError("score_mod_bprop without score_mod")
+        if fp8 is not None:
+            query_layer, key_layer, value_layer = fp8.inputs(query_layer, key_layer, value_layer)
         if inference_params is not None:
             query_layer, key_layer, value_layer, fmt, mask_type, cu_seqlens_q, cu_seqlens_kv = \
                 inference_params.step(self.layer_number, query_layer, key_layer, value_layer, fmt, mask_type)
@@ -148,14 +146,15 @@ class DotProductAttention(torch.nn.Module):
             def run(q, k, v):
                 return self._core(q, k, v, fmt, mask_type, window, attention_mask, cu_seqlens_q, cu_seqlens_kv,
                                   core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score, brd)
-            return D.checkpoint(run, query_layer, key_layer, value_layer,
-                                get_rng_state_tracker=self.get_rng_state_tracker)
+            out = D.checkpoint(run, query_layer, key_layer, value_layer,
+                               get_rng_state_tracker=self.get_rng_state_tracker)
+            return out if fp8 is None else fp8.output(out)
         out = self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
                          cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score,
                          brd)
         if inference_params is not None:
             out = inference_params.unpack_output(out)
-        return out
+        return out if fp8 is None else fp8.output(out)
 
     _logged: set = set()
 

@@ -50,7 +50,8 @@ def get_attention_backend(p: AttentionParams) -> Tuple[str, List[str]]:
 
     why: List[str] = []
     if p.fp8:
-        why.append("FP8 attention is not built (inputs are taken in fp16 / bf16)")
+        why.append("FP8 attention: Q, K, V, the output and the gradients are rounded to FP8 at the kernels' boundary; "
+                   "the kernels themselves run in 16 bits")
     if p.device != "cuda" or not torch.cuda.is_available() or not _ext.available():
         why.append("no CUDA device / extension: the reference math runs (this is the CPU oracle path)")
         return REFERENCE, why
@@ -71,12 +72,12 @@ def get_attention_backend(p: AttentionParams) -> Tuple[str, List[str]]:
     if p.score_mod:
         why.append("score_mod runs the reference math")
     blockers = [w for w in why if "FP8" not in w]
-    if not blockers and not p.fp8:
+    if not blockers:
         if get_config().attention_backend == "library":
             return LIBRARY, ["attention_backend='library' was requested (A/B timing)"]
         if get_config().attention_backend == "reference":
             return REFERENCE, ["attention_backend='reference' was requested (numerics debugging)"]
-        return FUSED, []
+        return FUSED, [w for w in why if "FP8" in w]
     windowed = p.window_size is not None and (p.window_size[0] >= 0 or p.window_size[1] > 0)
     plain = not any(k in w for w in blockers for k in ("bias", "dropout", "softmax_type", "mask", "score_mod"))
     if plain and not windowed and p.qkv_format != "thd" and not p.context_parallel \

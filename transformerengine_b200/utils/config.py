@@ -51,6 +51,8 @@ class Config:
         env="NVTE_DEBUG", help="log which attention path every configuration takes (logger 'DotProductAttention')"))
     debug_level: int = field(default=0, metadata=dict(
         env="NVTE_DEBUG_LEVEL", help="0: the chosen path; 1: also the conditions that ruled the others out; 2: every call"))
+    fp8_dpa_bwd: bool = field(default=True, metadata=dict(
+        env="NVTE_FP8_DPA_BWD", help="with recipe.fp8_dpa: also round the attention gradients to FP8 (0: 16-bit backward)"))
     # mirrored switches of the native kernels (read there at first launch)
     gemm_cta_pairs: bool = field(default=True, metadata=dict(
         env="TEB200_GEMM_2CTA", help="dense GEMMs on cta_group::2 pairs (0: single-CTA kernels)"))

@@ -112,12 +112,11 @@ class _LayerNormLinear(torch.autograd.Function):
         # recipe.backward_override: quantized forward, unquantized backward GEMMs on the original ("high_precision")
         # or on the dequantized forward operands ("dequantized")
         override = module.backward_override() if (fp8 and grad_on) else None
-        if override is not None and cfg.tp_size > 1:
-            raise NotImplementedError("recipe.backward_override is implemented for modules without tensor parallelism")
         # sequence parallel with fused collectives and MXFP8: the norm writes this rank's rows quantized
         # (both copies in one pass), the all-gather moves FP8 and the columnwise copy is kept for wgrad
+        # (with a backward override the backward needs no quantized copy: plain gather of the quantized rows)
         sp_fused_q = sp_gather and isinstance(in_q, F.MXFP8Quantizer) and F._fused_comm_ok(cfg, x2d.shape[0], x2d) \
-            and x2d.shape[0] % 128 == 0
+            and x2d.shape[0] % 128 == 0 and override is None
         if in_q is not None:
             in_q.set_usage(rowwise=True, columnwise=need_wgrad and (not sp_gather or sp_fused_q) and override is None)
             in_q.internal = True
@@ -130,13 +129,13 @@ class _LayerNormLinear(torch.autograd.Function):
         ln_total = None
         ln_local = ln_q if (sp_fused_q and ln_q is not None) else ln_hp
         if sp_gather:
-            if F._fused_comm_ok(cfg, x2d.shape[0], x2d):
+            if override is None and F._fused_comm_ok(cfg, x2d.shape[0], x2d):
                 res = F.fused_all_gather_gemm(ln_local, F.as_operand(wq, "rowwise"), bias, cfg, in_q,
                                               cfg.activation_dtype, "fprop", columnwise=need_wgrad)
                 if res is not None:
                     out, ln_local = res[0], res[1]
             if out is None:
-                ln_total = F.gather_input(ln_local, cfg, in_q, True, need_wgrad)
+                ln_total = F.gather_input(ln_local, cfg, in_q, True, need_wgrad and override is None)
         else:
             ln_total = ln_q if ln_q is not None else ln_hp
         if out is None:
@@ -145,6 +144,8 @@ class _LayerNormLinear(torch.autograd.Function):
             keep = (ln_local if sp_gather else ln_total) if need_wgrad else None
             if override == "high_precision" and need_wgrad:
                 keep = ln_hp
+            elif override == "dequantized" and need_wgrad and sp_gather:
+                keep = F.quantize_for_gemm(ln_hp, in_q, True, False)    # this rank's rows as the forward saw them
             if F._is_q(keep) and keep.get_usages()["columnwise"]:
                 keep.update_usage(rowwise_usage=False)
             ctx.wq = wq if F._is_q(wq) else None  # cached object shared across calls: not stripped

@@ -39,11 +39,9 @@ class _LayerNormMLP(torch.autograd.Function):
         # recipe.backward_override: quantized forward, unquantized backward GEMMs on the original ("high_precision")
         # or on the dequantized forward operands ("dequantized")
         override = module.backward_override() if (fp8 and grad) else None
-        if override is not None and cfg1.tp_size > 1:
-            raise NotImplementedError("recipe.backward_override is implemented for modules without tensor parallelism")
         hp_bwd = override == "high_precision"
         sp_fused_q = sp and isinstance(q_in1, F.MXFP8Quantizer) and F._fused_comm_ok(cfg1, x2d.shape[0], x2d) \
-            and x2d.shape[0] % 128 == 0
+            and x2d.shape[0] % 128 == 0 and override is None
         if q_in1 is not None:
             q_in1.set_usage(rowwise=True, columnwise=grad and (not sp or sp_fused_q) and override is None)
             q_in1.internal = True
@@ -56,13 +54,13 @@ class _LayerNormMLP(torch.autograd.Function):
         ln_total = None
         ln_local = ln_q if (sp_fused_q and ln_q is not None) else ln_hp
         if sp:
-            if F._fused_comm_ok(cfg1, x2d.shape[0], x2d):
+            if override is None and F._fused_comm_ok(cfg1, x2d.shape[0], x2d):
                 res = F.fused_all_gather_gemm(ln_local, F.as_operand(w1q, "rowwise"), fc1_b, cfg1, q_in1, adt, "fprop",
                                               columnwise=grad)
                 if res is not None:
                     fc1_out, ln_local = res[0], res[1]
             if fc1_out is None:
-                ln_total = F.gather_input(ln_local, cfg1, q_in1, True, grad)
+                ln_total = F.gather_input(ln_local, cfg1, q_in1, True, grad and override is None)
         else:
             ln_total = ln_q if ln_q is not None else ln_hp
         if fc1_out is None:
@@ -78,6 +76,8 @@ class _LayerNormMLP(torch.autograd.Function):
             keep_ln = ln_local if sp else ln_total
             if hp_bwd:
                 keep_ln, act_in = ln_hp, act_hp
+            elif override == "dequantized" and sp:
+                keep_ln = F.quantize_for_gemm(ln_hp, q_in1, True, False)    # this rank's rows as the forward saw them
             if F._is_q(keep_ln) and keep_ln.get_usages()["columnwise"]:
                 keep_ln.update_usage(rowwise_usage=False)
             if F._is_q(act_in) and act_in.get_usages()["columnwise"]:

@@ -29,21 +29,26 @@ class _Linear(torch.autograd.Function):
         # recipe.backward_override: quantized forward, unquantized backward GEMMs on the original operands
         # ("high_precision") or on the dequantized forward operands ("dequantized")
         override = module.backward_override() if (fp8 and grad_on) else None
-        if override is not None and (cfg.tp_size > 1 or dist_w):
-            raise NotImplementedError("recipe.backward_override is implemented for modules without tensor "
-                                      "parallelism and without distributed weights")
+        if override is not None and dist_w:
+            raise NotImplementedError("recipe.backward_override is not implemented for distributed weights")
         if x2d.dtype != cfg.activation_dtype and not F._is_q(x2d):
             x2d = x2d.to(cfg.activation_dtype)
         out = None
         sp_col = cfg.parallel_mode == "column" and cfg.sequence_parallel and cfg.tp_size > 1
         if sp_col:
             save_x = x2d  # local rows; gathered again in backward for wgrad
-            if F._fused_comm_ok(cfg, x2d.shape[0], x2d):
+            if override is not None:
+                # the backward runs on 16-bit operands: gather the quantized rows for this GEMM only and keep this
+                # rank's rows unquantized ("high_precision") or as what the forward quantizer made of them
+                xq = F.gather_input(x2d, cfg, in_q, True, False)
+                if override == "dequantized" and need_wgrad:
+                    save_x = F.quantize_for_gemm(x2d, in_q, True, False)
+            elif F._fused_comm_ok(cfg, x2d.shape[0], x2d):
                 res = F.fused_all_gather_gemm(x2d, F.as_operand(weight_q, "rowwise"), bias, cfg, in_q,
                                               cfg.activation_dtype, "fprop", columnwise=need_wgrad)
                 if res is not None:
                     out, save_x = res[0], res[1]  # the quantized local rows carry the wgrad (columnwise) copy
-            if out is None:
+            if out is None and override is None:
                 xq = F.gather_input(x2d, cfg, in_q, True, need_wgrad)
         else:
             keep_original = (getattr(module, "save_original_input", False) or override == "high_precision") \

@@ -273,3 +273,36 @@ def test_user_registered_fusion_pass():
     with pytest.raises(NotImplementedError):
         ops.register_backward_fusion(fuse_gelu_scale)
     assert ops.BasicOperation is ops.FusibleOperation
+
+
+def test_backward_override_runs_the_basic_operations():
+    """Under ``recipe.backward_override`` the fuser leaves the basic operations unfused (their modules run the 16-bit
+    backward); the plan is rebuilt when the override changes."""
+    from transformerengine_b200.common import recipe as R
+    from transformerengine_b200.tensor.mxfp8 import MXFP8Quantizer
+    torch.manual_seed(0)
+    seq = te.ops.Sequential(te.ops.Linear(64, 64, bias=False, device="cpu", dtype=torch.float32), te.ops.GELU())
+    x = torch.randn(32, 64)
+
+    def run(recipe):
+        xi = x.clone().requires_grad_()
+        seq.zero_grad()
+        with te.autocast(enabled=True, recipe=recipe):
+            y = seq(xi)
+            fused = any(getattr(op, "is_fused_op", False) for op in seq._get_plan())
+        y.sum().backward()
+        return y.detach(), xi.grad, seq[0].weight.grad.clone(), fused
+
+    y0, gx0, gw0, fused0 = run(R.MXFP8BlockScaling())
+    y1, gx1, gw1, fused1 = run(R.MXFP8BlockScaling(backward_override="high_precision"))
+    assert fused0 and not fused1
+    torch.testing.assert_close(y1, y0)
+    # the 16-bit backward: gradients of the unquantized products at the forward's (quantized) pre-activation
+    w = seq[0].weight.detach()
+    mx = lambda t: MXFP8Quantizer()(t).dequantize()  # noqa: E731
+    pre = (mx(x) @ mx(w).t()).requires_grad_()
+    torch.nn.functional.gelu(pre, approximate="tanh").sum().backward()
+    torch.testing.assert_close(gx1, pre.grad @ w, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(gw1, pre.grad.t() @ x, rtol=1e-4, atol=1e-5)
+    assert not torch.allclose(gx1, gx0, rtol=1e-4, atol=1e-5)
+    assert run(R.MXFP8BlockScaling())[3]                    # fused again without the override

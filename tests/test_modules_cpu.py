@@ -585,10 +585,28 @@ def test_backward_override_runs_the_backward_gemms_unquantized(override):
     torch.testing.assert_close(mlp.fc2_weight.grad, w2.grad, rtol=1e-3, atol=1e-4)
     torch.testing.assert_close(mlp.fc1_bias.grad, b1.grad, rtol=1e-3, atol=1e-4)
 
-    gl = te.GroupedLinear(2, 64, 64, bias=False, params_dtype=torch.float32, device="cpu")
-    with pytest.raises(NotImplementedError, match="backward_override"):
-        with te.autocast(enabled=True, recipe=rec):
-            gl(x, [16, 16])
+    # GroupedLinear: slabs of 32 rows (quantized one by one) and of 128 rows (quantized as one tensor)
+    for rows in (32, 128):
+        gl = te.GroupedLinear(2, 64, 96, bias=True, params_dtype=torch.float32, device="cpu")
+        xg = torch.randn(2 * rows, 64)
+
+        def run_g(recipe):
+            xi = xg.clone().requires_grad_()
+            gl.zero_grad()
+            with te.autocast(enabled=True, recipe=recipe):
+                y = gl(xi, [rows, rows])
+            y.square().sum().backward()
+            return y.detach(), xi.grad
+
+        y0, _ = run_g(plain)
+        y, gx = run_g(rec)
+        assert torch.equal(y, y0)
+        dy = 2 * y
+        for g, w in enumerate((gl.weight0, gl.weight1)):
+            sl = slice(g * rows, (g + 1) * rows)
+            torch.testing.assert_close(gx[sl], dy[sl] @ pick(w), rtol=1e-4, atol=1e-5)
+            torch.testing.assert_close(w.grad, dy[sl].t() @ pick(xg[sl]), rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(gl.bias1.grad, dy[rows:].sum(0), rtol=1e-4, atol=1e-5)
 
 
 def test_layernorm_mlp_clamped_swiglu_and_glu():

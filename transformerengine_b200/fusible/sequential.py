@@ -111,12 +111,19 @@ def _active_recipe():
     return FP8GlobalStateManager.get_fp8_recipe() if FP8GlobalStateManager.is_fp8_enabled() else None
 
 
+def _backward_override():
+    return getattr(_active_recipe(), "backward_override", None)
+
+
 def fuse_operations(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
     """Greedy longest-match fusion of a list of basic operations (user passes before and after the built-in one)."""
     ops = list(ops)
     for fn in _FUSIONS_FIRST:
         ops = list(fn(ops, recipe=_active_recipe()))
-    ops = _builtin_fusions(ops)
+    if not _backward_override():
+        # the fused operations bring their own quantized backward passes; under recipe.backward_override the basic
+        # operations run instead (their modules implement the 16-bit backward)
+        ops = _builtin_fusions(ops)
     for fn in _FUSIONS_LAST:
         ops = list(fn(ops, recipe=_active_recipe()))
     return ops
@@ -200,7 +207,7 @@ class Sequential(torch.nn.Module):
     def _get_plan(self) -> List[torch.nn.Module]:
         mods = list(self._modules.values())
         key = tuple(id(m) for m in mods)
-        key = key + (len(_FUSIONS_FIRST), len(_FUSIONS_LAST))
+        key = key + (len(_FUSIONS_FIRST), len(_FUSIONS_LAST), _backward_override())
         if self._plan is None or key != self._plan_key:
             self._plan, self._plan_key = fuse_operations(mods), key
         return self._plan

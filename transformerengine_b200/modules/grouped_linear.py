@@ -67,10 +67,13 @@ class _GroupedLinear(torch.autograd.Function):
             offs.append(offs[-1] + int(m))
         in_q = module.get_quantizer(True, 0)
         quant_ok = fp8 and in_q is not None and all(m % 32 == 0 for m in m_splits) and K % 32 == 0
+        # recipe.backward_override: quantized forward, 16-bit backward GEMMs on the original ("high_precision") or the
+        # dequantized forward operands ("dequantized")
+        override = module.backward_override() if (quant_ok and grad_on) else None
         xq = None
         wqs = []
         if quant_ok:
-            in_q.set_usage(rowwise=True, columnwise=grad_on)
+            in_q.set_usage(rowwise=True, columnwise=grad_on and override is None)
             in_q.internal = True
             aligned = all(m % 128 == 0 for m in m_splits) and isinstance(in_q, MXFP8Quantizer)
             for g in range(G):
@@ -109,7 +112,8 @@ class _GroupedLinear(torch.autograd.Function):
             ops.grouped_bias_add_(out, torch.stack([b.to(adt) for b in biases]), _offsets(m_splits, out.device))
         if grad_on:
             ctx.module, ctx.m_splits, ctx.offs, ctx.adt, ctx.fp8q = module, list(m_splits), offs, adt, quant_ok
-            ctx.xq, ctx.wqs = xq, wqs
+            ctx.xq, ctx.wqs = (x2d if override == "high_precision" else xq), wqs
+            ctx.override = override
             ctx.save_for_backward(*weights)
             ctx.inp_shape = inp.shape
             ctx.reduce_bwd_amax = FP8GlobalStateManager.is_first_fp8_module() if fp8 else False
@@ -125,7 +129,20 @@ class _GroupedLinear(torch.autograd.Function):
         dws = [None] * G
         dbs = [None] * G
         x_hp = None  # input dequantized ONCE when it was saved as one quantized tensor
-        if ctx.fp8q and isinstance(ctx.xq, QuantizedTensorStorage) and dy.is_cuda and dy.shape[0] > 0 \
+        fp8q, xq, w_hp = ctx.fp8q, ctx.xq, None
+        if ctx.override is not None:
+            fp8q = False
+            if ctx.override == "dequantized":
+                w_hp = [wq.dequantize(dtype=adt) for wq in ctx.wqs]
+                if isinstance(xq, list):      # one quantized tensor per slab (None for an empty slab)
+                    pieces = xq
+                    xq = torch.zeros(dy.shape[0], K, dtype=adt, device=dy.device)
+                    for g, piece in enumerate(pieces):
+                        if piece is not None:
+                            xq[offs[g]:offs[g + 1]] = piece.dequantize(dtype=adt)
+                else:
+                    xq = xq.dequantize(dtype=adt)
+        if fp8q and isinstance(ctx.xq, QuantizedTensorStorage) and dy.is_cuda and dy.shape[0] > 0 \
                 and N % 32 == 0 and all(m % 128 == 0 for m in m_splits):
             # Slabs are whole 128-row tiles: grad_output is quantized ONCE (both copies), dgrad is one grouped
             # launch over the stacked column-wise weights, and every wgrad GEMM reads its slab as a view of the
@@ -163,7 +180,7 @@ class _GroupedLinear(torch.autograd.Function):
             if m_splits[g] == 0:
                 dws[g] = torch.zeros_like(weights[g])
                 continue
-            if ctx.fp8q:
+            if fp8q:
                 gq = module.get_quantizer(False, 2 * g)
                 gq.set_usage(rowwise=True, columnwise=True)
                 gq.internal = True
@@ -184,11 +201,11 @@ class _GroupedLinear(torch.autograd.Function):
                                 b=as_operand(xg, "columnwise"), w=weights[g]: gemm_nt(
                                     a, b, out_dtype=w.dtype if w.dtype != torch.float32 else torch.float32))
             else:
-                w = weights[g].to(adt)
+                w = w_hp[g] if w_hp is not None else weights[g].to(adt)
                 gemm_nt(as_operand(dy[sl], "rowwise"), as_operand(w, "columnwise"), out=dx[sl])
                 dws[g] = _wgrad(module, weights[g], lambda a=as_operand(dy[sl], "columnwise"),
-                                b=as_operand(ctx.xq[sl], "columnwise"), w=weights[g]: gemm_nt(a, b, out_dtype=w.dtype))
-        if ctx.fp8q and ctx.reduce_bwd_amax:
+                                b=as_operand(xq[sl], "columnwise"), w=weights[g]: gemm_nt(a, b, out_dtype=w.dtype))
+        if fp8q and ctx.reduce_bwd_amax:
             FP8GlobalStateManager.reduce_and_update_fp8_tensors(forward=False)
         res = [dx.reshape(ctx.inp_shape), None, None, None] + dws
         if module.use_bias:
@@ -320,7 +337,6 @@ class GroupedLinear(TransformerEngineBaseModule):
             return (out,) + tuple(rest) if rest else out
         assert len(m_splits) == self.num_gemms, "one row count per GEMM"
         self.prepare_forward(num_gemms=self.num_gemms)
-        self._refuse_backward_override()
         adt = torch.get_autocast_gpu_dtype() if torch.is_autocast_enabled() else inp.dtype
         ws = [getattr(self, f"weight{i}") for i in range(self.num_gemms)]
         bs = [getattr(self, f"bias{i}") for i in range(self.num_gemms)] if self.use_bias else []

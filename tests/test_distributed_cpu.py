@@ -173,3 +173,57 @@ def test_quantized_tensors_are_gathered_without_dequantizing():
     for rank, bad, tb in res:
         assert tb is None, tb
         assert not bad, f"rank {rank}: {bad}"
+
+
+def _ln_gathered_worker(rank, world, port, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.manual_seed(0)
+        x = torch.randn(8 * world, 32)
+        bad = {}
+        for kind in ("linear", "mlp"):
+            torch.manual_seed(1)
+            kw = dict(normalization="RMSNorm", params_dtype=torch.float32, device="cpu", tp_group=dist.group.WORLD,
+                      sequence_parallel=True, return_layernorm_output=True, return_layernorm_output_gathered=True)
+            if kind == "linear":
+                m = te.LayerNormLinear(32, 16 * world, parallel_mode="column", bias=False, **kw)
+            else:
+                m = te.LayerNormMLP(32, 16 * world, set_parallel_mode=True, bias=False, **kw)
+            g = m.layer_norm_weight.detach()
+            xs = x.chunk(world)[rank].clone().requires_grad_()
+            out, ln = m(xs)
+            xf = x.clone().requires_grad_()
+            want = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + m.eps) * g
+            if ln.shape != want.shape or not torch.allclose(ln, want, atol=1e-5):
+                bad[kind + ":ln"] = tuple(ln.shape)
+            # a loss on the gathered output alone, different on every rank: the local rows' gradient is the SUM of
+            # all ranks' gradients for them
+            w = torch.arange(1, world + 1, dtype=torch.float32)
+            (ln.square().sum() * w[rank] + 0.0 * out.sum()).backward()
+            (want.square().sum() * w.sum()).backward()
+            if not torch.allclose(xs.grad, xf.grad.chunk(world)[rank], rtol=1e-4, atol=1e-5):
+                bad[kind + ":dx"] = float((xs.grad - xf.grad.chunk(world)[rank]).abs().max())
+        q.put((rank, bad))
+    except Exception:  # noqa: BLE001
+        import traceback
+        q.put((rank, {"exception": traceback.format_exc()[-1500:]}))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_return_layernorm_output_gathered():
+    """``return_layernorm_output_gathered``: with sequence parallelism the returned normalized output holds all
+    rows; its gradient is reduce-scattered back onto the ranks' own rows."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ln_gathered_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, bad in res:
+        assert not bad, f"rank {rank}: {bad}"

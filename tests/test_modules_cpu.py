@@ -371,8 +371,6 @@ def test_unimplemented_options_are_refused_not_ignored():
     with pytest.raises(NotImplementedError):
         te.GroupedLinear(2, 16, 16, save_original_input=True, device="cpu")
     with pytest.raises(NotImplementedError):
-        te.LayerNormLinear(16, 16, return_layernorm_output_gathered=True, device="cpu")
-    with pytest.raises(NotImplementedError):
         te.LayerNormMLP(16, 32, activation_params={"limit": 7.0}, device="cpu")
     with pytest.raises(NotImplementedError):
         te.DotProductAttention(2, 16, return_max_logit=True)

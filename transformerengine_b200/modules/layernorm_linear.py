@@ -222,9 +222,9 @@ class LayerNormLinear(TransformerEngineBaseModule):
                  symmetric_ar_type: Optional[str] = None, name: Optional[str] = None,
                  ub_overlap_rs: bool = False) -> None:
         super().__init__()
-        if return_layernorm_output_gathered:
-            raise NotImplementedError("return_layernorm_output_gathered is not implemented: the normalized output is "
-                                      "returned as this rank's rows")
+        # with sequence parallelism the returned normalized output is this rank's rows, or all rows (gathered over
+        # the tensor-parallel group; gradients reduce-scatter back) with return_layernorm_output_gathered
+        self.return_layernorm_output_gathered = return_layernorm_output_gathered
         if symmetric_ar_type is not None:
             raise NotImplementedError("symmetric_ar_type: use te.initialize_ub (fused GEMM + collective kernels) instead")
         params_dtype = torch.get_default_dtype() if params_dtype is None else params_dtype
@@ -361,6 +361,10 @@ class LayerNormLinear(TransformerEngineBaseModule):
         res = _LayerNormLinear.apply(inp, ln_w, ln_b, weight, b_use, self, self.cfg, wq,
                                      self.return_layernorm_output, is_first_microbatch)
         out, ln_out = (res if self.return_layernorm_output else (res, None))
+        if ln_out is not None and self.return_layernorm_output_gathered and self.sequence_parallel \
+                and self.parallel_mode == "column":
+            from ..parallel.distributed import gather_rows_with_grad
+            ln_out = gather_rows_with_grad(ln_out, self.cfg.tp_group)
         if self.return_bias:
             if self.return_layernorm_output:
                 return out, (bias.to(adt) if bias is not None else None), ln_out

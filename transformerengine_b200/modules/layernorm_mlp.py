@@ -178,8 +178,9 @@ class LayerNormMLP(TransformerEngineBaseModule):
         if activation_params and set(activation_params) - {"limit", "alpha", "glu_linear_offset"}:
             raise ValueError(f"unknown activation_params {sorted(activation_params)}")
         self.activation_params = dict(activation_params) if activation_params else None
-        if return_layernorm_output_gathered:
-            raise NotImplementedError("return_layernorm_output_gathered is not implemented")
+        # with sequence parallelism: return all rows of the normalized output (gathered over the tensor-parallel
+        # group; gradients reduce-scatter back) instead of this rank's rows
+        self.return_layernorm_output_gathered = return_layernorm_output_gathered
         if symmetric_ar_type is not None:
             raise NotImplementedError("symmetric_ar_type: use te.initialize_ub (fused GEMM + collective kernels) instead")
         if checkpoint:
@@ -298,6 +299,10 @@ class LayerNormMLP(TransformerEngineBaseModule):
         res = _LayerNormMLP.apply(inp, ln_w, ln_b, self.fc1_weight, fc1_b, self.fc2_weight, fc2_b, self, w1q, w2q,
                                   self.return_layernorm_output)
         out, ln_out = (res if self.return_layernorm_output else (res, None))
+        if ln_out is not None and self.return_layernorm_output_gathered and self.cfg1.sequence_parallel \
+                and self.cfg1.tp_size > 1:
+            from ..parallel.distributed import gather_rows_with_grad
+            ln_out = gather_rows_with_grad(ln_out, self.cfg1.tp_group)
         if self.return_bias:
             fb = cast(self.fc2_bias) if self.use_bias else None
             if self.return_layernorm_output:

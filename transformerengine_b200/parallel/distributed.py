@@ -49,6 +49,22 @@ def reduce_scatter_along_first_dim(x: torch.Tensor, group, async_op: bool = Fals
     return out, h
 
 
+class _GatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):  # type: ignore[override]
+        ctx.group = group
+        return gather_along_first_dim(x, group)[0]
+
+    @staticmethod
+    def backward(ctx, g):  # type: ignore[override]
+        return reduce_scatter_along_first_dim(g, ctx.group)[0], None
+
+
+def gather_rows_with_grad(x: torch.Tensor, group) -> torch.Tensor:
+    """All-gather along dim 0 whose backward reduce-scatters the gradient (sequence-parallel activations)."""
+    return x if get_world_size(group) == 1 else _GatherRows.apply(x, group)
+
+
 def allreduce(x: torch.Tensor, group, async_op: bool = False):
     if get_world_size(group) == 1:
         return x, None

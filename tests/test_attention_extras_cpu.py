@@ -268,3 +268,42 @@ def test_attention_backend_logging(caplog):
     with caplog.at_level(logging.DEBUG, logger="DotProductAttention"):
         dpa(q, q, q)
     assert not [r for r in caplog.records if r.name == "DotProductAttention"]
+
+
+def test_return_max_logit():
+    """``return_max_logit``: per-head maximum of the scaled scores that the mask leaves visible (GQA, causal,
+    sliding window, padding mask), computed in blocks of query rows."""
+    from transformerengine_b200.ops.attention import max_attention_logit
+    torch.manual_seed(0)
+    b, sq, h, g, d = 2, 12, 4, 2, 8
+    q, k, v = torch.randn(b, sq, h, d), torch.randn(b, sq, g, d), torch.randn(b, sq, g, d)
+    scores = torch.einsum("bqhd,bkhd->bhqk", q, k.repeat_interleave(h // g, dim=2)) / d ** 0.5
+    qi, ki = torch.arange(sq)[:, None], torch.arange(sq)[None, :]
+
+    def want(masked):
+        return scores.masked_fill(masked, float("-inf")).amax(dim=(0, 2, 3))
+
+    dpa = te.DotProductAttention(h, d, num_gqa_groups=g, attention_dropout=0.0, qkv_format="bshd",
+                                 attn_mask_type="causal", return_max_logit=True)
+    plain = te.DotProductAttention(h, d, num_gqa_groups=g, attention_dropout=0.0, qkv_format="bshd",
+                                   attn_mask_type="causal")
+    out, mx = dpa(q, k, v)
+    assert torch.equal(out, plain(q, k, v)) and mx.shape == (h,) and mx.dtype == torch.float32
+    torch.testing.assert_close(mx, want(ki > qi))
+    _, mx = dpa(q, k, v, attn_mask_type="no_mask")
+    torch.testing.assert_close(mx, want(torch.zeros(sq, sq, dtype=torch.bool)))
+    _, mx = dpa(q, k, v, window_size=(3, 0))
+    torch.testing.assert_close(mx, want((ki > qi) | (ki < qi - 3)))
+    pad = torch.zeros(b, 1, 1, sq, dtype=torch.bool)
+    pad[1, ..., 8:] = True
+    _, mx = dpa(q, k, v, attn_mask_type="padding", attention_mask=pad)
+    full = pad.reshape(b, 1, 1, sq) | pad.reshape(b, 1, sq, 1)
+    torch.testing.assert_close(mx, want(full))
+    _, mx = dpa(q, k, v, checkpoint_core_attention=True)
+    torch.testing.assert_close(mx, want(ki > qi))
+    # the blocked pass gives the same maximum whatever the block size
+    qb, kb = q.permute(0, 2, 1, 3), k.permute(0, 2, 1, 3)
+    torch.testing.assert_close(max_attention_logit(qb, kb, causal=True, chunk_bytes=1), want(ki > qi))
+    with pytest.raises(NotImplementedError):
+        dpa(q.reshape(-1, h, d), k.reshape(-1, g, d), v.reshape(-1, g, d), qkv_format="thd",
+            cu_seqlens_q=torch.tensor([0, 12, 24], dtype=torch.int32))

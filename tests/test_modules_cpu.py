@@ -372,8 +372,6 @@ def test_unimplemented_options_are_refused_not_ignored():
         te.GroupedLinear(2, 16, 16, save_original_input=True, device="cpu")
     with pytest.raises(NotImplementedError):
         te.LayerNormMLP(16, 32, activation_params={"limit": 7.0}, device="cpu")
-    with pytest.raises(NotImplementedError):
-        te.DotProductAttention(2, 16, return_max_logit=True)
     lin = te.Linear(16, 16, device="cpu", params_dtype=torch.float32)
     with pytest.raises(NotImplementedError):
         lin(torch.randn(4, 16), fp8_output=True)

@@ -44,8 +44,9 @@ class DotProductAttention(torch.nn.Module):
                  name: Optional[str] = None) -> None:
         super().__init__()
         self.bottom_right_diagonal, self.name = bottom_right_diagonal, name
-        if return_max_logit:
-            raise NotImplementedError("return_max_logit: the attention kernels do not export the maximum logit")
+        # return_max_logit: forward returns (output, per-head maximum of the masked scaled scores); the maximum
+        # comes from a pass of its own over Q K^T (the attention kernels do not export it)
+        self.return_max_logit, self._max_logit = return_max_logit, None
         assert attn_mask_type in _MASK_TYPES, f"unknown attn_mask_type {attn_mask_type}"
         assert qkv_format in ("sbhd", "bshd", "thd")
         self.qkv_format = qkv_format
@@ -148,13 +149,15 @@ class DotProductAttention(torch.nn.Module):
                                   core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score, brd)
             out = D.checkpoint(run, query_layer, key_layer, value_layer,
                                get_rng_state_tracker=self.get_rng_state_tracker)
-            return out if fp8 is None else fp8.output(out)
+            out = out if fp8 is None else fp8.output(out)
+            return (out, self._max_logit) if self.return_max_logit else out
         out = self._core(query_layer, key_layer, value_layer, fmt, mask_type, window, attention_mask, cu_seqlens_q,
                          cu_seqlens_kv, core_attention_bias_type, core_attention_bias, alibi_slopes, thd_extra, score,
                          brd)
         if inference_params is not None:
             out = inference_params.unpack_output(out)
-        return out if fp8 is None else fp8.output(out)
+        out = out if fp8 is None else fp8.output(out)
+        return (out, self._max_logit) if self.return_max_logit else out
 
     _logged: set = set()
 
@@ -194,6 +197,8 @@ class DotProductAttention(torch.nn.Module):
         if get_config().debug:
             self._log_backend(q, k, v, fmt, mask_type, window, attention_mask, bias_type, score)
         if fmt == "thd":
+            if self.return_max_logit:
+                raise NotImplementedError("return_max_logit is implemented for sbhd / bshd inputs")
             return self._thd(q, k, v, mask_type, window, cu_q, cu_kv, *thd_extra)
         # -> [b, h, s, d] views
         if fmt == "sbhd":
@@ -241,6 +246,7 @@ class DotProductAttention(torch.nn.Module):
                 (f"softmax_type={self.softmax_type!r}", self.softmax_type != "vanilla"),
                 ("score_mod", score[0] is not None),
                 ("bottom-right causal alignment with sq != sk", causal and bottom_right and sq != sk),
+                ("return_max_logit", self.return_max_logit),
             ) if on]
             if unsupported:
                 raise NotImplementedError("context parallelism does not support: " + "; ".join(unsupported))
@@ -250,6 +256,13 @@ class DotProductAttention(torch.nn.Module):
         else:
             ctx = self.get_rng_state_tracker().fork() if (self.get_rng_state_tracker is not None and dropout > 0) \
                 else _null()
+            if self.return_max_logit:
+                if score[0] is not None:
+                    raise NotImplementedError("return_max_logit with score_mod")
+                from ..ops.attention import max_attention_logit
+                self._max_logit = max_attention_logit(qb, kb, scale=self.softmax_scale, causal=causal, window=window,
+                                                      attn_mask=mask, bias=the_bias,
+                                                      bottom_right=bottom_right or sq == sk)
             with ctx:
                 o = ops.attention(qb, kb, vb, scale=self.softmax_scale, causal=causal, window=window, attn_mask=mask,
                                   bias=the_bias, dropout_p=dropout, softmax_type=self.softmax_type,

@@ -76,6 +76,38 @@ def attention_ref(q, k, v, *, scale=None, causal=False, window=None, attn_mask=N
     return (o, lse) if return_lse else o
 
 
+@torch.no_grad()
+def max_attention_logit(q, k, *, scale=None, causal=False, window=None, attn_mask=None, bias=None,
+                        bottom_right=True, chunk_bytes: int = 256 << 20) -> torch.Tensor:
+    """Per-head maximum of the scaled, biased and masked attention scores of ``[b, h, s, d]`` tensors (fp32 ``[h]``;
+    the quantity "QK-clip" optimizers watch).  A pass of its own over Q K^T in blocks of query rows, so that no
+    ``s x s`` score tensor is kept.  (Reference: ``return_max_logit`` of
+    ``attention/dot_product_attention/backends.py``.)"""
+    b, hq, sq, d = q.shape
+    hk, sk = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    kf = k.float()
+    if hk != hq:
+        kf = kf.repeat_interleave(hq // hk, dim=1)
+    kt = kf.transpose(-1, -2)
+    m = _build_mask(sq, sk, q.device, causal, window, bottom_right)
+    rows = max(1, min(sq, chunk_bytes // max(4 * b * hq * sk, 1)))
+    best = torch.full((hq,), float("-inf"), dtype=torch.float32, device=q.device)
+    for r0 in range(0, sq, rows):
+        r1 = min(r0 + rows, sq)
+        s = torch.matmul(q[:, :, r0:r1].float(), kt) * scale
+        if bias is not None:
+            bb = bias.float()
+            s = s + (bb[..., r0:r1, :] if bb.shape[-2] == sq else bb)
+        if m is not None:
+            s = s.masked_fill(m[r0:r1], float("-inf"))
+        if attn_mask is not None:
+            am = attn_mask
+            s = s.masked_fill(am[..., r0:r1, :] if am.shape[-2] == sq else am, float("-inf"))
+        best = torch.maximum(best, s.amax(dim=(0, 2, 3)))
+    return best
+
+
 _USE_LIBRARY_SDPA = True
 # attention_backend='library' (TEB200_ATTN=library) routes the plain 16-bit case to torch's SDPA instead of
 # csrc/attn (A/B timing)

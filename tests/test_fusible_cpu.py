@@ -226,8 +226,24 @@ def test_gated_unit_variants():
     assert out.shape == (6, 8) and torch.isfinite(out).all()
     with pytest.raises(ValueError):
         ops.SiTUGLU(beta1=0.0)
-    with pytest.raises(NotImplementedError):
-        ops.GLU(glu_interleave_size=2)
+    # block-interleaved layout: a1 a2 b1 b2 a3 a4 b3 b4 gives the same result as a1..a4 b1..b4, gradients included
+    xi = torch.randn(6, 16, requires_grad=True)
+    blocks = xi.reshape(6, 4, 2, 2)                                  # [row, pair, gate / linear, 2]
+    plain = torch.cat([blocks[:, :, 0].reshape(6, 8), blocks[:, :, 1].reshape(6, 8)], -1).detach().requires_grad_()
+    sc = torch.rand(6)
+    for inter, ref, extra in ((ops.GLU(glu_interleave_size=2), ops.GLU(), ()),
+                              (ops.ClampedSwiGLU(glu_interleave_size=2), ops.ClampedSwiGLU(), ()),
+                              (ops.ScaledSwiGLU(glu_interleave_size=2), ops.ScaledSwiGLU(), (sc,)),
+                              (ops.ScaledSiTUGLU(glu_interleave_size=2), ops.ScaledSiTUGLU(), (sc,))):
+        xi.grad = plain.grad = None
+        y, want = inter(xi, *extra), ref(plain, *extra)
+        torch.testing.assert_close(y, want)
+        y.square().sum().backward()
+        want.square().sum().backward()
+        g = plain.grad.reshape(6, 2, 4, 2).transpose(1, 2).reshape(6, 16)   # back to the interleaved layout
+        torch.testing.assert_close(xi.grad, g)
+    with pytest.raises(ValueError):
+        ops.GLU(glu_interleave_size=3)(xi)
 
 
 def test_user_registered_fusion_pass():

@@ -136,6 +136,19 @@ class SReGLU(_Activation):
     act_name = "sreglu"
 
 
+def _deinterleave(x, block: Optional[int]):
+    """Block-interleaved gated input -> ``[gates | linear units]``: with ``glu_interleave_size = block`` the last
+    dimension holds alternating blocks of ``block`` gate inputs and ``block`` linear inputs (``a1 a2 b1 b2 a3 a4 b3
+    b4`` for block 2) instead of all gates followed by all linear units.  Plain reshapes, so autograd routes the
+    gradient back into the interleaved layout.  (Reference: ``pytorch/ops/basic/swiglu.py:130-139``.)"""
+    if block is None:
+        return x
+    n = x.shape[-1]
+    if block <= 0 or n % (2 * block):
+        raise ValueError(f"glu_interleave_size={block} does not divide the gated width {n} into gate / linear pairs")
+    return x.reshape(-1, n // (2 * block), 2, block).transpose(1, 2).reshape(x.shape)
+
+
 def _halves(x):
     """(gate input a, linear input b): the gating function applies to the FIRST half of the last dimension."""
     return x.float().chunk(2, dim=-1)
@@ -147,15 +160,14 @@ class _ElementwiseGLU(FusibleOperation):
 
     def __init__(self, *, cache_quantized_input: bool = False, glu_interleave_size: Optional[int] = None):
         super().__init__()
-        if glu_interleave_size is not None:
-            raise NotImplementedError("interleaved gate / linear halves (glu_interleave_size) are not implemented")
+        self.glu_interleave_size = glu_interleave_size
         self.cache_quantized_input = cache_quantized_input
 
     def _glu(self, a, b):
         raise NotImplementedError
 
     def forward(self, x):
-        a, b = _halves(x)
+        a, b = _halves(_deinterleave(x, self.glu_interleave_size))
         return self._glu(a, b).to(x.dtype)
 
 
@@ -359,11 +371,10 @@ class ScaledSwiGLU(FusibleOperation):
 
     def __init__(self, glu_interleave_size: Optional[int] = None):
         super().__init__()
-        if glu_interleave_size is not None:
-            raise NotImplementedError("interleaved gate / linear halves (glu_interleave_size) are not implemented")
+        self.glu_interleave_size = glu_interleave_size
 
     def forward(self, x, scales):
-        return _ScaledGluFn.apply(x, scales.reshape(-1), self.act_name)
+        return _ScaledGluFn.apply(_deinterleave(x, self.glu_interleave_size), scales.reshape(-1), self.act_name)
 
 
 class _ScaledElementwise(FusibleOperation):
@@ -374,8 +385,7 @@ class _ScaledElementwise(FusibleOperation):
 
     def __init__(self, glu_interleave_size: Optional[int] = None, *, activation_recompute_in_mlp: bool = False):
         super().__init__()
-        if glu_interleave_size is not None:
-            raise NotImplementedError("interleaved gate / linear halves (glu_interleave_size) are not implemented")
+        self.glu_interleave_size = glu_interleave_size
         if activation_recompute_in_mlp:
             raise NotImplementedError("activation_recompute_in_mlp: wrap the MLP in te.checkpoint instead")
 
@@ -383,7 +393,8 @@ class _ScaledElementwise(FusibleOperation):
         raise NotImplementedError
 
     def forward(self, x, scales):
-        y = self._f(x.float())
+        gated = type(self) is not ScaledSReLU      # the squared ReLU has no gate / linear halves to reorder
+        y = self._f(_deinterleave(x, self.glu_interleave_size if gated else None).float())
         return (y * scales.float().reshape(*y.shape[:-1], 1)).to(x.dtype)
 
 

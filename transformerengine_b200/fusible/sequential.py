@@ -141,6 +141,7 @@ def _builtin_fusions(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
             i += 4
             continue
         if (len(w) >= 3 and isinstance(w[0], O.GroupedLinear) and isinstance(w[1], O.ScaledSwiGLU)
+                and w[1].glu_interleave_size is None    # the fused expert MLP reads [gates | linear units]
                 and isinstance(w[2], O.GroupedLinear) and w[0].num_groups == w[2].num_groups
                 and w[0].out_features == 2 * w[2].in_features):
             out.append(GroupedMLP(w[0], w[1], w[2]))

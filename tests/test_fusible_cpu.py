@@ -232,6 +232,8 @@ def test_gated_unit_variants():
     plain = torch.cat([blocks[:, :, 0].reshape(6, 8), blocks[:, :, 1].reshape(6, 8)], -1).detach().requires_grad_()
     sc = torch.rand(6)
     for inter, ref, extra in ((ops.GLU(glu_interleave_size=2), ops.GLU(), ()),
+                              (ops.SwiGLU(glu_interleave_size=2), ops.SwiGLU(), ()),
+                              (ops.GEGLU(glu_interleave_size=2), ops.GEGLU(), ()),
                               (ops.ClampedSwiGLU(glu_interleave_size=2), ops.ClampedSwiGLU(), ()),
                               (ops.ScaledSwiGLU(glu_interleave_size=2), ops.ScaledSwiGLU(), (sc,)),
                               (ops.ScaledSiTUGLU(glu_interleave_size=2), ops.ScaledSiTUGLU(), (sc,))):
@@ -244,6 +246,15 @@ def test_gated_unit_variants():
         torch.testing.assert_close(xi.grad, g)
     with pytest.raises(ValueError):
         ops.GLU(glu_interleave_size=3)(xi)
+    with pytest.raises(ValueError):
+        ops.GELU(glu_interleave_size=2)
+    # an interleaved gated unit stays a basic operation (the fused linear + activation reads [gates | linear units])
+    lin = ops.Linear(16, 16, bias=False, device="cpu", dtype=torch.float32)
+    fused = ops.Sequential(lin, ops.SwiGLU())
+    inter = ops.Sequential(lin, ops.SwiGLU(glu_interleave_size=2))
+    assert any(getattr(op, "is_fused_op", False) for op in fused._get_plan())
+    assert not any(getattr(op, "is_fused_op", False) for op in inter._get_plan())
+    torch.testing.assert_close(inter(x.detach()), ops.SwiGLU(glu_interleave_size=2)(lin(x.detach())))
 
 
 def test_user_registered_fusion_pass():

@@ -88,12 +88,15 @@ class _ActFn(torch.autograd.Function):
 class _Activation(FusibleOperation):
     act_name = "gelu"
 
-    def __init__(self, *, cache_quantized_input: bool = False):
+    def __init__(self, *, cache_quantized_input: bool = False, glu_interleave_size: Optional[int] = None):
         super().__init__()
         self.cache_quantized_input = cache_quantized_input
+        if glu_interleave_size is not None and not self.act_name.endswith("glu"):
+            raise ValueError(f"glu_interleave_size is an option of the gated units, not of {type(self).__name__}")
+        self.glu_interleave_size = glu_interleave_size      # block-interleaved gates / linear units: _deinterleave
 
     def forward(self, x):
-        return _ActFn.apply(x, self.act_name)
+        return _ActFn.apply(_deinterleave(x, self.glu_interleave_size), self.act_name)
 
 
 class GELU(_Activation):

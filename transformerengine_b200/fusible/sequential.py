@@ -129,12 +129,17 @@ def fuse_operations(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
     return ops
 
 
+def _plain_act(op) -> bool:
+    """An activation the fused modules can absorb (an interleaved gated layout runs as a basic operation)."""
+    return isinstance(op, O._Activation) and op.glu_interleave_size is None
+
+
 def _builtin_fusions(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
     out: List[torch.nn.Module] = []
     i = 0
     while i < len(ops):
         w = ops[i:i + 4]
-        if (len(w) == 4 and _norm_kind(w[0]) and _is_linear(w[1]) and isinstance(w[2], O._Activation)
+        if (len(w) == 4 and _norm_kind(w[0]) and _is_linear(w[1]) and _plain_act(w[2])
                 and _is_linear(w[3]) and (getattr(w[1], "bias", None) is None) == (getattr(w[3], "bias", None) is None)
                 and w[1].out_features == w[3].in_features * (2 if w[2].act_name in ("swiglu", "geglu", "reglu") else 1)):
             out.append(_Fused(_fuse_norm_mlp(*w), 4, name="norm_mlp"))
@@ -166,7 +171,7 @@ def _builtin_fusions(ops: List[torch.nn.Module]) -> List[torch.nn.Module]:
                 bias_op, j = ops[j], j + 1
             if j < len(ops) and isinstance(ops[j], O.ConstantScale) and bias_op is None and not own_bias:
                 scale, j = float(ops[j].scale), j + 1
-            if j < len(ops) and isinstance(ops[j], O._Activation) and scale == 1.0:
+            if j < len(ops) and _plain_act(ops[j]) and scale == 1.0:
                 act, j = ops[j].act_name, j + 1
             if j < len(ops) and isinstance(ops[j], O.AddExtraInput):
                 add, j = True, j + 1
